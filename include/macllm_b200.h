@@ -1,0 +1,378 @@
+/*
+ * macllm_b200.h - C ABI of the B200-native continuous-batching step.
+ *
+ * This is the boundary a host written in another language binds (the reference's Rust engine would
+ * bind it through a thin FFI crate in place of crates/macllm-kernels and of the candle-backed
+ * DecoderModel).  Every entry point mirrors one item of the reference's model/session/KV-reservation
+ * traits (src/architecture.rs) or of its kernel crate (crates/macllm-kernels/src/paged_attention.rs);
+ * the item is cited above each declaration.
+ *
+ * Conventions
+ *   - Every function returns an int32 status: 0 = ok, MK_KV_EXHAUSTED (1) = the paged KV pool cannot
+ *     serve the request and nothing was mutated, negative = fatal.  mk_last_error() returns the
+ *     calling thread's last message.
+ *   - Handles are opaque, created and destroyed by the library, and must be used from the thread that
+ *     created them (one host thread per GPU), like the reference's !Send model and sessions
+ *     (src/decoder.rs:2704-2709).
+ *   - There is no CPU fallback: calls that need the GPU fail with a negative status when no CUDA
+ *     device is usable.
+ *   - Pointers are host pointers unless the parameter name ends in _dev.
+ */
+#ifndef MACLLM_B200_H
+#define MACLLM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MK_OK 0
+#define MK_KV_EXHAUSTED 1
+#define MK_FATAL (-1)
+
+/* GGML tensor type ids (src/gguf.rs:283-297). */
+#define MK_TYPE_F32 0
+#define MK_TYPE_F16 1
+#define MK_TYPE_Q8_0 8
+#define MK_TYPE_Q4_K 12
+#define MK_TYPE_Q6_K 14
+
+/* Matmul path selection for mk_k_qmatmul. */
+#define MK_PATH_AUTO 0
+#define MK_PATH_GEMV 1   /* integer dp4a kernel */
+#define MK_PATH_TENSOR 2 /* tcgen05 kernel */
+
+typedef struct mk_model mk_model;
+typedef struct mk_session mk_session;
+typedef struct mk_reservation mk_reservation;
+typedef struct mk_engine mk_engine;
+
+const char* mk_last_error(void);
+/* Library version string and the CUDA architecture it was built for. */
+const char* mk_version(void);
+/* Number of usable CUDA devices (0 when none; never fails). */
+int32_t mk_device_count(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Model / session / KV reservation  (traits CausalLm, CausalLmSession, CausalLmKvReservation,
+ * src/architecture.rs:803-1246)
+ * ---------------------------------------------------------------------------------------------- */
+
+/* ModelLoadConfig (src/runtime.rs:18-91): KV geometry and prefix-cache capacity. */
+typedef struct mk_load_config {
+    int32_t device_ordinal;
+    int32_t block_tokens;            /* tokens per KV block (reference default 16) */
+    int32_t slab_blocks;             /* blocks per lazily allocated slab (reference default 8) */
+    int64_t kv_capacity_tokens;      /* max_blocks = ceil(capacity / block_tokens) (src/runtime.rs:194) */
+    int64_t prefix_capacity_tokens;  /* 0 disables the exact-token prefix cache */
+    int32_t kv_dtype;                /* MK_TYPE_F16 or MK_TYPE_F32 */
+    int32_t max_batch_tokens;        /* largest packed token count of one forward */
+    int32_t max_batch_lanes;         /* largest lane count of one forward */
+    int32_t matmul_path;             /* MK_PATH_AUTO / MK_PATH_GEMV / MK_PATH_TENSOR */
+} mk_load_config;
+
+/* CausalLm::runtime_spec (src/architecture.rs:312-316,1039). */
+typedef struct mk_runtime_spec {
+    int32_t vocab_size;
+    int32_t max_context;
+    int32_t n_layers;
+    int32_t hidden_size;
+    int32_t n_stop_tokens;
+    uint32_t stop_token_ids[8];
+    int64_t weight_bytes;            /* algorithmic bytes of all matrices as stored in the file */
+    int64_t weight_bytes_per_token;  /* bytes one decode row touches (MoE: experts_per_token experts) */
+    int64_t kv_bytes_per_token;      /* K+V bytes one cached token occupies over all layers */
+} mk_runtime_spec;
+
+/* KvCacheCapacity (src/architecture.rs:1170-1172; src/decoder.rs:3682-3694). */
+typedef struct mk_kv_capacity {
+    int64_t block_tokens;
+    int64_t total_blocks;
+    int64_t free_blocks;   /* free + not yet allocated */
+    int64_t retired_blocks;
+} mk_kv_capacity;
+
+/* PagedKvPoolStats (crates/macllm-kv/src/cache.rs:270-291). */
+typedef struct mk_pool_stats {
+    int64_t allocated_blocks;
+    int64_t free_blocks;
+    int64_t live_blocks;
+    int64_t reserved_blocks;
+    int64_t retired_blocks;
+    int64_t shared_blocks;
+    int64_t live_references;
+    int64_t slabs;
+    int64_t submitted_epoch;
+    int64_t completed_epoch;
+} mk_pool_stats;
+
+/* PrefixCacheDiagnostics (src/architecture.rs:855-867). */
+typedef struct mk_prefix_diagnostics {
+    int64_t entries;
+    int64_t cached_blocks;
+    int64_t capacity_blocks;
+    int64_t hits;
+    int64_t misses;
+    int64_t matched_tokens;
+    int64_t insertions;
+    int64_t evictions;
+} mk_prefix_diagnostics;
+
+/* LoadedRuntime::load (src/runtime.rs:104-145) for a GGUF file. */
+int32_t mk_model_load_gguf(const char* path, const mk_load_config* cfg, mk_model** out);
+int32_t mk_model_free(mk_model* m);
+int32_t mk_model_spec(mk_model* m, mk_runtime_spec* out);
+
+/* CausalLm::new_session / CausalLmSession::{clear_cache, cache_len} (src/architecture.rs:803-833,1074). */
+int32_t mk_session_new(mk_model* m, mk_session** out);
+int32_t mk_session_free(mk_session* s);
+int32_t mk_session_clear(mk_session* s);
+int32_t mk_session_len(mk_session* s, int64_t* out);
+/* Block table of a session: slot indices and generations (PagedKvBlockTable, cache.rs:1434-1865).
+ * Pass capacity in *n, get the entry count back. */
+int32_t mk_session_block_table(mk_session* s, uint32_t* slots, uint64_t* generations, int32_t* n);
+
+/* CausalLm::reset_session_for_prompt (src/architecture.rs:1086-1097; src/decoder.rs:3494-3532). */
+int32_t mk_reset_session_for_prompt(mk_model* m, mk_session* s, const uint32_t* tokens, int32_t n, int64_t* cached_tokens);
+/* CausalLm::publish_prompt_prefix (src/architecture.rs:1102; src/decoder.rs:3534-3603). */
+int32_t mk_publish_prompt_prefix(mk_model* m, mk_session* s, const uint32_t* tokens, int32_t n);
+
+int32_t mk_kv_capacity_query(mk_model* m, mk_kv_capacity* out);
+int32_t mk_pool_stats_query(mk_model* m, mk_pool_stats* out);
+int32_t mk_prefix_diagnostics_query(mk_model* m, mk_prefix_diagnostics* out);
+
+/* CausalLmKvReservationInput / CausalLmBatchInput (src/architecture.rs:874-1025). */
+typedef struct mk_lane {
+    mk_session* session;
+    const uint32_t* input_ids; /* may be NULL for mk_reserve_batch */
+    int32_t n_tokens;
+    int32_t start_pos;
+} mk_lane;
+
+/* CausalLm::reserve_batch_kv (src/architecture.rs:1180-1185; src/decoder.rs:3696-3758): host only,
+ * no device write.  MK_KV_EXHAUSTED guarantees nothing was mutated. */
+int32_t mk_reserve_batch(mk_model* m, const mk_lane* lanes, int32_t n_lanes, mk_reservation** out);
+/* Dropping a reservation rolls it back (cache.rs:3001-3005). */
+int32_t mk_reservation_drop(mk_reservation* r);
+
+#define MK_FWD_WANT_LOGITS 1u  /* copy [lanes, vocab] f32 logits to the host at the barrier */
+#define MK_FWD_WANT_TOKENS 2u  /* on-device greedy selection, one u32 per lane */
+
+/* CausalLm::forward_batch_tokens_reserved (src/architecture.rs:1218-1227; src/decoder.rs:4203-4269):
+ * validates every lane before any mutation, consumes the reservation, enqueues the whole tick on the
+ * model's stream and returns without waiting. */
+int32_t mk_forward_batch_reserved(mk_model* m, const mk_lane* lanes, int32_t n_lanes, mk_reservation* r, uint32_t flags);
+/* CausalLm::read_output_to_cpu (src/architecture.rs:1229-1235; src/decoder.rs:3779-3783): the
+ * completion barrier; also releases KV pages retired before this tick.  logits may be NULL. */
+int32_t mk_read_output(mk_model* m, float* logits, uint32_t* tokens);
+/* CausalLm::synchronize (src/architecture.rs:1241-1243). */
+int32_t mk_synchronize(mk_model* m);
+/* Device time of the last completed forward in milliseconds (CUDA events on the model's stream). */
+int32_t mk_last_forward_ms(mk_model* m, float* out);
+/* Kernel launches issued by this model since load. */
+int32_t mk_launch_count(mk_model* m, int64_t* out);
+
+/* ------------------------------------------------------------------------------------------------
+ * Engine: the scheduler tick  (ServingScheduler, src/engine.rs:1578-2770; GenerationCore,
+ * src/generation.rs:787-1266)
+ * ---------------------------------------------------------------------------------------------- */
+
+/* EngineConfig (src/engine.rs:309-384). */
+typedef struct mk_engine_config {
+    int32_t max_active_sequences;
+    int32_t scheduler_token_budget;
+    int32_t prefill_token_quantum;
+    int32_t queue_capacity;
+    int32_t record_logits;      /* keep the logits row of every sampled position (parity runs) */
+    int32_t host_sampling;      /* 1 = read logits back and sample on the host like the reference */
+} mk_engine_config;
+
+/* SamplingConfig + GenerationConfig (src/sampling.rs:15-33; src/generation.rs). */
+typedef struct mk_request {
+    const uint32_t* prompt;
+    int32_t n_prompt;
+    int32_t max_new_tokens;
+    int32_t ignore_stop_tokens;
+    float temperature;
+    int32_t top_k;
+    float top_p;
+    float repetition_penalty;
+    float presence_penalty;
+    float frequency_penalty;
+    uint64_t seed;
+} mk_request;
+
+/* One packed forward of the schedule: which request ran which token range (the shape the reference's
+ * tests assert, InvocationTrace::Packed, src/engine.rs:3107-3300). */
+typedef struct mk_tick_lane {
+    int32_t request_id;
+    int32_t start_pos;
+    int32_t n_tokens;
+} mk_tick_lane;
+
+typedef struct mk_engine_stats {
+    int64_t ticks;
+    int64_t prefill_tokens;
+    int64_t decode_tokens;
+    int64_t completed_requests;
+    int64_t failed_requests;
+    int64_t kv_shrinks;          /* candidate lanes dropped because the pool was exhausted */
+    double device_ms;            /* sum of per-tick device times */
+} mk_engine_stats;
+
+int32_t mk_engine_new(mk_model* m, const mk_engine_config* cfg, mk_engine** out);
+int32_t mk_engine_free(mk_engine* e);
+/* EngineHandle::submit_batch (src/engine.rs:976-1053): an atomic batch is admitted only when all of
+ * its members fit.  Returns the ids assigned to the requests in ids[n]. */
+int32_t mk_engine_submit(mk_engine* e, const mk_request* reqs, int32_t n, int32_t atomic_batch, int32_t* ids);
+/* ServingScheduler::drive_once (src/engine.rs:1938-1964): admit, run one tick, finalize.
+ * *ran_lanes receives the number of lanes in the packed forward (0 when idle). */
+int32_t mk_engine_step(mk_engine* e, int32_t* ran_lanes);
+/* Run ticks until every submitted request has finished. */
+int32_t mk_engine_run(mk_engine* e);
+int32_t mk_engine_pending(mk_engine* e, int32_t* out);
+/* Generated tokens of a request (capacity in *n, count out); *finished: 0 running, 1 done, 2 failed. */
+int32_t mk_engine_result(mk_engine* e, int32_t request_id, uint32_t* tokens, int32_t* n, int32_t* finished, int64_t* cached_tokens);
+/* Logits rows recorded for a request when record_logits is set: [n_rows][vocab]. */
+int32_t mk_engine_logits(mk_engine* e, int32_t request_id, float* out, int32_t* n_rows);
+/* Lanes of tick `tick` (0-based); capacity in *n. */
+int32_t mk_engine_trace(mk_engine* e, int64_t tick, mk_tick_lane* lanes, int32_t* n);
+int32_t mk_engine_stats_query(mk_engine* e, mk_engine_stats* out);
+
+/* ------------------------------------------------------------------------------------------------
+ * Host-only paged-KV pool and prefix cache, exposed for parity tests of block tables, refcounts and
+ * prefix hits (crates/macllm-kv/src/cache.rs, prefix_cache.rs).  No GPU needed.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct mk_kvpool mk_kvpool;
+typedef struct mk_kvtable mk_kvtable;
+
+int32_t mk_kvpool_new(int32_t block_tokens, int32_t slab_blocks, int64_t max_blocks, mk_kvpool** out);
+int32_t mk_kvpool_free(mk_kvpool* p);
+int32_t mk_kvpool_stats(mk_kvpool* p, mk_pool_stats* out);
+int32_t mk_kvtable_new(mk_kvpool* p, mk_kvtable** out);
+int32_t mk_kvtable_free(mk_kvtable* t);
+int32_t mk_kvtable_len(mk_kvtable* t, int64_t* out);
+int32_t mk_kvtable_blocks(mk_kvtable* t, uint32_t* slots, uint64_t* generations, int32_t* n);
+int32_t mk_kvtable_clear(mk_kvtable* t);
+/* PagedKvBlockTable::fork_prefix (cache.rs:1565-1571): a new table sharing the first `tokens` tokens. */
+int32_t mk_kvtable_fork_prefix(mk_kvtable* t, int64_t tokens, mk_kvtable** out);
+/* PagedKvBlockTable::attach_prefix (cache.rs:1486-1563): make an empty table share `src`'s blocks. */
+int32_t mk_kvtable_attach_prefix(mk_kvtable* t, mk_kvtable* src, int64_t tokens);
+/* SharedPagedKvPool::reserve_batch + commit in one step (cache.rs:2331-2445,2947-2979): append
+ * n_tokens[i] tokens to tables[i]; MK_KV_EXHAUSTED mutates nothing.  When commit == 0 the reservation
+ * is rolled back instead.  copies_out (optional, capacity in *n_copies as triples) receives the
+ * copy-on-write (src_slot, dst_slot, rows) triples. */
+int32_t mk_kvpool_append_batch(mk_kvpool* p, mk_kvtable** tables, const int32_t* n_tokens, int32_t n, int32_t commit,
+                               int64_t* copies_out, int32_t* n_copies);
+/* Page table of an uncommitted reservation (cache.rs:2707-2851): rows are (compact slab index,
+ * block in slab).  Performs reserve -> build -> rollback. */
+int32_t mk_kvpool_page_table(mk_kvpool* p, mk_kvtable** tables, const int32_t* n_tokens, int32_t n, uint32_t* pages /*[rows][2]*/,
+                             int32_t* n_rows, int32_t* lane_offsets, int32_t* lane_counts, int32_t* lane_lens);
+/* Epoch protocol (cache.rs:1278-1319): submit marks a new device epoch, complete releases pages
+ * retired up to that epoch. */
+int32_t mk_kvpool_submit_epoch(mk_kvpool* p, int64_t* epoch);
+int32_t mk_kvpool_complete_epoch(mk_kvpool* p, int64_t epoch);
+
+typedef struct mk_prefix_cache mk_prefix_cache;
+int32_t mk_prefix_cache_new(int32_t block_tokens, int64_t capacity_blocks, mk_prefix_cache** out);
+int32_t mk_prefix_cache_free(mk_prefix_cache* c);
+/* TokenPrefixCache::insert (prefix_cache.rs:181-249): value is an opaque id, cost in blocks.
+ * evicted_out receives the values evicted to make room (capacity in *n_evicted). */
+int32_t mk_prefix_cache_insert(mk_prefix_cache* c, const uint32_t* tokens, int32_t n, int64_t value, int64_t cost,
+                               int64_t* evicted_out, int32_t* n_evicted);
+/* TokenPrefixCache::lookup_aligned_common_prefix (prefix_cache.rs:316-359): longest stored
+ * block-aligned prefix strictly shorter than the prompt; *value = -1 on a miss. */
+int32_t mk_prefix_cache_lookup(mk_prefix_cache* c, const uint32_t* tokens, int32_t n, int64_t* value, int64_t* matched_tokens);
+int32_t mk_prefix_cache_evict_lru(mk_prefix_cache* c, int64_t* value);
+int32_t mk_prefix_cache_diagnostics(mk_prefix_cache* c, mk_prefix_diagnostics* out);
+/* Chained block digest (prefix_cache.rs:556-594): 32 bytes per full block of `tokens`. */
+int32_t mk_prefix_block_digests(int32_t block_tokens, const uint32_t* tokens, int32_t n, uint8_t* digests, int32_t* n_blocks);
+/* SHA-256 of a byte string (known-answer check). */
+int32_t mk_sha256(const uint8_t* data, int64_t n, uint8_t out[32]);
+
+/* Host sampler (Sampler::sample_with_generated, src/sampling.rs:95-169): penalties, then greedy
+ * first-index argmax when temperature <= 0. */
+int32_t mk_host_sample_greedy(float* logits, int32_t vocab, const uint32_t* history, int32_t n_history, float repetition_penalty,
+                              const uint32_t* generated, int32_t n_generated, float presence_penalty, float frequency_penalty,
+                              uint32_t* token);
+
+/* Seed-model writer: fills `out` with `rows` x `cols` weights drawn from N(0, std) by a counter-based
+ * generator keyed by (seed, stream), quantised to GGML type `type` (row_bytes(type, cols) per row).
+ * Used to build the synthetic GGUF checkpoints both this library and the CPU oracle load. */
+int32_t mk_seed_tensor(uint64_t seed, uint64_t stream, float std, int32_t type, int64_t rows, int64_t cols, void* out);
+int64_t mk_row_bytes(int32_t type, int64_t cols);
+
+/* ------------------------------------------------------------------------------------------------
+ * Kernel-level entry points (unit parity).  Host buffers in and out; each call stages its operands
+ * in HBM, runs the sm_100a kernel and reads the result back.
+ * ---------------------------------------------------------------------------------------------- */
+
+/* Activation quantisation feeding LinearOp::Quantized (src/model_weights.rs:346-377): act_kind 0 =
+ * 256-wide blocks (d [T][K/256], bsums [T][K/16]), 1 = 32-wide blocks (d [T][K/32]). */
+int32_t mk_k_quantize(int32_t act_kind, const float* x, int32_t T, int32_t K, int8_t* qs, float* d, int16_t* bsums);
+
+/* Residual add + RMSNorm (rms_norm, src/model_weights.rs:563-565; finish_mixer, src/decoder.rs:2684-2699):
+ * h += a_scale * (post_w ? rmsnorm(a, post_w) : a); normed_out = norm_w ? rmsnorm(h, norm_w) : h.
+ * a, post_w, norm_w and normed_out may be NULL. */
+int32_t mk_k_add_norm(float* h, const float* a, float a_scale, const float* post_w, const float* norm_w, float eps, int32_t rows,
+                      int32_t dim, float* normed_out);
+
+/* LinearOp::forward for a quantised matrix (src/model_weights.rs:346-377): y [T][rows] = x [T][cols] . W^T,
+ * W given as GGUF block bytes of `type`. */
+int32_t mk_k_qmatmul(int32_t type, const void* w, int64_t rows, int64_t cols, const float* x, int32_t T, float* y, int32_t path);
+
+/* TokenEmbedding::forward_validated (src/model_weights.rs:489-502). */
+int32_t mk_k_embed(int32_t type, const void* w, int64_t rows, int64_t cols, const uint32_t* ids, int32_t T, float scale, float* out);
+
+/* DenseFeedForward gate (src/decoder.rs:298-305): out = act(gate) * up, act 0 = SiLU, 1 = tanh-GELU. */
+int32_t mk_k_actmul(const float* gate, const float* up, int32_t T, int32_t F, int32_t act, float* out);
+
+/* One attention layer step of a ragged batch: builds the batch descriptor on the device, applies the
+ * optional per-head RMSNorm and RoPE, scatters K/V into the paged pool and runs paged attention
+ * (macllm_kernels::paged_attention_batch, crates/macllm-kernels/src/paged_attention.rs:18-179,614-709;
+ * write_layer, crates/macllm-kv/src/cache.rs:2543-2643; RotaryEmbedding::apply, src/decoder.rs:203-257). */
+typedef struct mk_attn_case {
+    int32_t lanes, total_tokens;
+    int32_t q_heads, kv_heads, head_dim;
+    int32_t block_tokens, layers, layer, pool_blocks;
+    int32_t kv_f16;               /* 1: pools are f16, 0: f32 */
+    float scale, softcap;         /* softcap 0 disables */
+    int32_t window;               /* 0 = full causal */
+    int32_t rotary_dim;           /* 0 = no rotation (NoPE layer) */
+    int32_t rope_capacity;
+    float norm_eps;
+    const int32_t* start_pos;     /* [lanes] */
+    const int32_t* lane_len;      /* [lanes] */
+    const int32_t* table_off;     /* [lanes] offsets into tables */
+    const int32_t* table_len;     /* [lanes] */
+    const uint32_t* tables;       /* concatenated block ids */
+    float* q;                     /* [T][q_heads*head_dim], unrotated */
+    const float* k;               /* [T][kv_heads*head_dim] */
+    const float* v;
+    const float* q_norm_w;        /* [head_dim] or NULL */
+    const float* k_norm_w;
+    const float* cos_table;       /* [rope_capacity][rotary_dim/2] or NULL */
+    const float* sin_table;
+    void* k_pool;                 /* [pool_blocks][layers][kv_heads][block_tokens][head_dim], updated in place */
+    void* v_pool;
+    float* out;                   /* [T][q_heads*head_dim] */
+    float* q_rot_out;             /* optional: rotated queries */
+    int64_t* slots_out;           /* optional [T] */
+    int32_t* positions_out;       /* optional [T] */
+    int32_t* last_index_out;      /* optional [lanes] */
+    int32_t* cu_seqlens_out;      /* optional [lanes+1] */
+} mk_attn_case;
+int32_t mk_k_attention_step(const mk_attn_case* c);
+
+/* argmax of src/sampling.rs:425-433 for each row of logits [B][vocab]. */
+int32_t mk_k_argmax(const float* logits, int32_t B, int32_t vocab, uint32_t* out);
+
+/* selected_softmax_routes (src/decoder.rs:448-554): sel_experts / sel_weights are [T][k], best first. */
+int32_t mk_k_moe_route(const float* logits, int32_t T, int32_t experts, int32_t k, int32_t* sel_experts, float* sel_weights);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MACLLM_B200_H */

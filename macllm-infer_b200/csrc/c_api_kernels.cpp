@@ -1,0 +1,286 @@
+// C ABI, part 1: kernel-level entry points used for unit parity.  Host buffers in, host buffers out;
+// each call stages its operands in HBM, runs the sm_100a kernel and reads the result back.
+#include "../../include/macllm_b200.h"
+#include "c_api_util.h"
+#include "device_util.h"
+#include "kernels.h"
+#include "qgemm_tc.h"
+#include <vector>
+#include <cstring>
+
+using namespace mk;
+
+namespace {
+
+struct ActBufs {
+    DevBuf qs, d, bs;
+    ActQ view(int T, int K, int kind) {
+        qs.ensure((size_t)T * K);
+        d.ensure((size_t)T * (kind == ACT_Q8K ? K / 256 : K / 32) * 4);
+        bs.ensure((size_t)T * (K / 16) * 2 + 16);
+        ActQ a;
+        a.qs = qs.as<int8_t>();
+        a.d = d.as<float>();
+        a.bsums = bs.as<int16_t>();
+        return a;
+    }
+};
+
+int act_kind_for(int wtype) { return wtype == QT_Q8_0 ? ACT_Q80 : ACT_Q8K; }
+
+}  // namespace
+
+extern "C" {
+
+int32_t mk_k_quantize(int32_t act_kind, const float* x, int32_t T, int32_t K, int8_t* qs, float* d, int16_t* bsums) {
+    return guarded([&] {
+        require_device();
+        if (K % 256 != 0 && act_kind == ACT_Q8K) throw std::runtime_error("mk_k_quantize: K must be a multiple of 256");
+        if (K % 32 != 0) throw std::runtime_error("mk_k_quantize: K must be a multiple of 32");
+        DevBuf dx((size_t)T * K * 4);
+        dx.upload(x, (size_t)T * K * 4);
+        ActBufs ab;
+        ActQ a = ab.view(T, K, act_kind);
+        NormQuantArgs na;
+        na.h = dx.as<float>();
+        na.rows = T;
+        na.dim = K;
+        na.act_kind = act_kind;
+        na.out = a;
+        launch_add_norm_quant(na, nullptr);
+        MK_CUDA(cudaDeviceSynchronize());
+        ab.qs.download(qs, (size_t)T * K);
+        ab.d.download(d, (size_t)T * (act_kind == ACT_Q8K ? K / 256 : K / 32) * 4);
+        if (act_kind == ACT_Q8K && bsums) ab.bs.download(bsums, (size_t)T * (K / 16) * 2);
+        MK_CUDA(cudaDeviceSynchronize());
+    });
+}
+
+int32_t mk_k_add_norm(float* h, const float* a, float a_scale, const float* post_w, const float* norm_w, float eps,
+                      int32_t rows, int32_t dim, float* normed_out) {
+    return guarded([&] {
+        require_device();
+        size_t n = (size_t)rows * dim * 4;
+        DevBuf dh(n), da, dpw, dnw, dout(n);
+        dh.upload(h, n);
+        NormQuantArgs na;
+        na.h = dh.as<float>();
+        if (a) { da.upload(a, n); na.a = da.as<float>(); }
+        if (post_w) { dpw.upload(post_w, (size_t)dim * 4); na.post_w = dpw.as<float>(); }
+        if (norm_w) { dnw.upload(norm_w, (size_t)dim * 4); na.norm_w = dnw.as<float>(); }
+        na.a_scale = a_scale;
+        na.eps = eps;
+        na.rows = rows;
+        na.dim = dim;
+        na.normed_out = dout.as<float>();
+        launch_add_norm_quant(na, nullptr);
+        MK_CUDA(cudaDeviceSynchronize());
+        dh.download(h, n);
+        if (normed_out) dout.download(normed_out, n);
+        MK_CUDA(cudaDeviceSynchronize());
+    });
+}
+
+int32_t mk_k_qmatmul(int32_t type, const void* w, int64_t rows, int64_t cols, const float* x, int32_t T, float* y,
+                     int32_t path) {
+    return guarded([&] {
+        require_device();
+        DeviceWeight dw;
+        upload_weight(type, w, rows, cols, dw);
+        int kind = act_kind_for(type);
+        DevBuf dx((size_t)T * cols * 4), dy((size_t)T * rows * 4);
+        dx.upload(x, (size_t)T * cols * 4);
+        ActBufs ab;
+        ActQ a = ab.view(T, (int)cols, kind);
+        NormQuantArgs na;
+        na.h = dx.as<float>();
+        na.rows = T;
+        na.dim = (int)cols;
+        na.act_kind = kind;
+        na.out = a;
+        launch_add_norm_quant(na, nullptr);
+        if (path == MK_PATH_TENSOR || (path == MK_PATH_AUTO && qgemm_tc_preferred(dw.w, T))) {
+            QgemmWorkspace ws;
+            launch_qgemm_tc(dw.w, a, kind, T, dy.as<float>(), (int)rows, 1.0f, 0.f, ws, nullptr);
+        } else {
+            launch_qgemv(dw.w, a, T, dy.as<float>(), (int)rows, 1.0f, 0.f, nullptr);
+        }
+        MK_CUDA(cudaDeviceSynchronize());
+        dy.download(y, (size_t)T * rows * 4);
+        MK_CUDA(cudaDeviceSynchronize());
+    });
+}
+
+int32_t mk_k_embed(int32_t type, const void* w, int64_t rows, int64_t cols, const uint32_t* ids, int32_t T, float scale,
+                   float* out) {
+    return guarded([&] {
+        require_device();
+        for (int i = 0; i < T; ++i)
+            if ((int64_t)ids[i] >= rows) throw std::runtime_error("mk_k_embed: token id out of range");
+        DeviceWeight dw;
+        upload_weight(type, w, rows, cols, dw);
+        DevBuf di((size_t)T * 4), dout((size_t)T * cols * 4);
+        di.upload(ids, (size_t)T * 4);
+        launch_embed(dw.w, di.as<uint32_t>(), T, scale, dout.as<float>(), nullptr);
+        MK_CUDA(cudaDeviceSynchronize());
+        dout.download(out, (size_t)T * cols * 4);
+        MK_CUDA(cudaDeviceSynchronize());
+    });
+}
+
+int32_t mk_k_actmul(const float* gate, const float* up, int32_t T, int32_t F, int32_t act, float* out) {
+    return guarded([&] {
+        require_device();
+        size_t n = (size_t)T * F * 4;
+        DevBuf dg(n), du(n), dout(n);
+        dg.upload(gate, n);
+        du.upload(up, n);
+        launch_actmul_quant(dg.as<float>(), du.as<float>(), F, T, F, act, ACT_Q8K, ActQ{}, dout.as<float>(), nullptr);
+        MK_CUDA(cudaDeviceSynchronize());
+        dout.download(out, n);
+        MK_CUDA(cudaDeviceSynchronize());
+    });
+}
+
+int32_t mk_k_attention_step(const mk_attn_case* c) {
+    return guarded([&] {
+        require_device();
+        const int T = c->total_tokens, lanes = c->lanes, d = c->head_dim;
+        const int esz = c->kv_f16 ? 2 : 4;
+        size_t pool_elems = (size_t)c->pool_blocks * c->layers * c->kv_heads * c->block_tokens * d;
+        DevBuf kpool(pool_elems * esz), vpool(pool_elems * esz);
+        kpool.upload(c->k_pool, pool_elems * esz);
+        vpool.upload(c->v_pool, pool_elems * esz);
+        size_t qn = (size_t)T * c->q_heads * d * 4, kn = (size_t)T * c->kv_heads * d * 4;
+        DevBuf dq(qn), dk(kn), dv(kn), dout(qn);
+        dq.upload(c->q, qn);
+        dk.upload(c->k, kn);
+        dv.upload(c->v, kn);
+
+        std::vector<LaneHeader> hdr(lanes);
+        int total_blocks = 0, tiles = 0;
+        int q_tile = attention_q_tile(c->q_heads, c->kv_heads);
+        for (int l = 0; l < lanes; ++l) {
+            hdr[l].start_pos = c->start_pos[l];
+            hdr[l].n_tokens = c->lane_len[l];
+            hdr[l].table_off = c->table_off[l];
+            hdr[l].n_blocks = c->table_len[l];
+            total_blocks = std::max(total_blocks, c->table_off[l] + c->table_len[l]);
+            tiles += (c->lane_len[l] + q_tile - 1) / q_tile;
+        }
+        DevBuf dhdr((size_t)lanes * sizeof(LaneHeader)), dtab((size_t)std::max(total_blocks, 1) * 4);
+        dhdr.upload(hdr.data(), (size_t)lanes * sizeof(LaneHeader));
+        dtab.upload(c->tables, (size_t)total_blocks * 4);
+        DevBuf cu((size_t)(lanes + 1) * 4), pos((size_t)T * 4), tl((size_t)T * 4), slots((size_t)T * 8), last((size_t)lanes * 4),
+            tile_lane((size_t)tiles * 4), tile_row((size_t)tiles * 4), ntiles(4), err(4);
+        err.zero();
+        BatchDesc b;
+        b.lanes = lanes;
+        b.T = T;
+        b.max_tiles = tiles;
+        b.hdr = dhdr.as<LaneHeader>();
+        b.tables = dtab.as<uint32_t>();
+        b.cu_seqlens = cu.as<int32_t>();
+        b.positions = pos.as<int32_t>();
+        b.token_lane = tl.as<int32_t>();
+        b.slots = slots.as<int64_t>();
+        b.last_index = last.as<int32_t>();
+        b.tile_lane = tile_lane.as<int32_t>();
+        b.tile_row0 = tile_row.as<int32_t>();
+        b.n_tiles = ntiles.as<int32_t>();
+        b.error_flag = err.as<int32_t>();
+        launch_build_batch(b, c->block_tokens, q_tile, nullptr);
+
+        DevBuf dcos, dsin, dqn, dkn;
+        RopeKvArgs r;
+        r.q = dq.as<float>();
+        r.k = dk.as<float>();
+        r.v = dv.as<float>();
+        r.ldq = c->q_heads * d;
+        r.ldk = r.ldv = c->kv_heads * d;
+        if (c->q_norm_w) { dqn.upload(c->q_norm_w, (size_t)d * 4); r.q_norm_w = dqn.as<float>(); }
+        if (c->k_norm_w) { dkn.upload(c->k_norm_w, (size_t)d * 4); r.k_norm_w = dkn.as<float>(); }
+        r.norm_eps = c->norm_eps;
+        if (c->cos_table && c->rotary_dim > 0) {
+            size_t tn = (size_t)c->rope_capacity * (c->rotary_dim / 2) * 4;
+            dcos.upload(c->cos_table, tn);
+            dsin.upload(c->sin_table, tn);
+            r.cos_t = dcos.as<float>();
+            r.sin_t = dsin.as<float>();
+            r.rotary_dim = c->rotary_dim;
+        }
+        r.positions = b.positions;
+        r.slots = b.slots;
+        r.k_pool = kpool.ptr();
+        r.v_pool = vpool.ptr();
+        r.kv_f16 = c->kv_f16;
+        r.T = T;
+        r.q_heads = c->q_heads;
+        r.kv_heads = c->kv_heads;
+        r.d = d;
+        r.block_tokens = c->block_tokens;
+        r.layers = c->layers;
+        r.layer = c->layer;
+        launch_rope_kv(r, nullptr);
+
+        AttnArgs at;
+        at.q = dq.as<float>();
+        at.out = dout.as<float>();
+        at.k_pool = kpool.ptr();
+        at.v_pool = vpool.ptr();
+        at.kv_f16 = c->kv_f16;
+        at.batch = b;
+        at.q_heads = c->q_heads;
+        at.kv_heads = c->kv_heads;
+        at.d = d;
+        at.block_tokens = c->block_tokens;
+        at.layers = c->layers;
+        at.layer = c->layer;
+        at.scale = c->scale;
+        at.softcap = c->softcap;
+        at.window = c->window;
+        at.q_tile = q_tile;
+        launch_paged_attention(at, nullptr);
+        MK_CUDA(cudaDeviceSynchronize());
+
+        int32_t flag = 0;
+        err.download(&flag, 4);
+        dout.download(c->out, qn);
+        if (c->q_rot_out) dq.download(c->q_rot_out, qn);
+        if (c->slots_out) slots.download(c->slots_out, (size_t)T * 8);
+        if (c->positions_out) pos.download(c->positions_out, (size_t)T * 4);
+        if (c->last_index_out) last.download(c->last_index_out, (size_t)lanes * 4);
+        if (c->cu_seqlens_out) cu.download(c->cu_seqlens_out, (size_t)(lanes + 1) * 4);
+        kpool.download(c->k_pool, pool_elems * esz);
+        vpool.download(c->v_pool, pool_elems * esz);
+        MK_CUDA(cudaDeviceSynchronize());
+        if (flag != 0) throw std::runtime_error("mk_k_attention_step: batch descriptor index out of range (flag " + std::to_string(flag) + ")");
+    });
+}
+
+int32_t mk_k_argmax(const float* logits, int32_t B, int32_t vocab, uint32_t* out) {
+    return guarded([&] {
+        require_device();
+        DevBuf dl((size_t)B * vocab * 4), dout((size_t)B * 4);
+        dl.upload(logits, (size_t)B * vocab * 4);
+        launch_argmax(dl.as<float>(), B, vocab, dout.as<uint32_t>(), nullptr);
+        MK_CUDA(cudaDeviceSynchronize());
+        dout.download(out, (size_t)B * 4);
+        MK_CUDA(cudaDeviceSynchronize());
+    });
+}
+
+int32_t mk_k_moe_route(const float* logits, int32_t T, int32_t experts, int32_t k, int32_t* sel_experts, float* sel_weights) {
+    return guarded([&] {
+        require_device();
+        DevBuf dl((size_t)T * experts * 4), de((size_t)T * k * 4), dw((size_t)T * k * 4);
+        dl.upload(logits, (size_t)T * experts * 4);
+        launch_moe_route(dl.as<float>(), T, experts, k, de.as<int32_t>(), dw.as<float>(), nullptr);
+        MK_CUDA(cudaDeviceSynchronize());
+        de.download(sel_experts, (size_t)T * k * 4);
+        dw.download(sel_weights, (size_t)T * k * 4);
+        MK_CUDA(cudaDeviceSynchronize());
+    });
+}
+
+}  // extern "C"

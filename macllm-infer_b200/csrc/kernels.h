@@ -1,0 +1,122 @@
+// Host-side launchers of the sm_100a kernels.  All pointers are device pointers unless noted.
+#pragma once
+#include "common.cuh"
+
+namespace mk {
+
+// ---- activation preparation -------------------------------------------------------------
+// Row-wise residual add, RMSNorm and 8-bit activation quantisation in one pass:
+//   a' = post_w ? rmsnorm(a, post_w) : a          (Gemma-style sandwich norm)
+//   h  = h + a_scale * a'                          (skipped when a == nullptr)
+//   n  = norm_w ? rmsnorm(h, norm_w) : h
+//   normed_out (optional f32) = n ; quantised blocks of n -> out (optional)
+// When row_index != nullptr, row r reads h[row_index[r]] and no residual is written back
+// (used to gather the last token of each sequence before the output projection).
+struct NormQuantArgs {
+    float* h = nullptr;
+    const float* a = nullptr;
+    float a_scale = 1.f;
+    const float* post_w = nullptr;
+    const float* norm_w = nullptr;
+    float eps = 1e-5f;
+    int rows = 0, dim = 0;
+    float* normed_out = nullptr;
+    const int32_t* row_index = nullptr;
+    int act_kind = ACT_Q8K;
+    ActQ out;
+};
+void launch_add_norm_quant(const NormQuantArgs& a, cudaStream_t s);
+
+// out = quantise(act(gate) * up) ; act 0 = SiLU, 1 = tanh-GELU.  gate/up are [T][F] with row stride ld.
+void launch_actmul_quant(const float* gate, const float* up, int ld, int T, int F, int act, int act_kind,
+                         ActQ out, float* f32_out, cudaStream_t s);
+
+// ---- quantised matmul ---------------------------------------------------------------------
+// y[t][n] = (sum_k x[t][k] W[n][k]) * out_scale, then optional tanh softcap; integer block dots
+// against 8-bit activation blocks (CUDA-core path, any T; best for T <= 8).
+void launch_qgemv(const QWeight& W, const ActQ& x, int T, float* y, int ldy, float out_scale, float softcap,
+                  cudaStream_t s);
+// F32 weight matrix (MoE router): y[t][n] = sum_k x[t][k] W[n][k], f32 activations.
+void launch_f32_gemv(const float* W, int out, int in, const float* x, int T, float* y, cudaStream_t s);
+
+// ---- embedding ------------------------------------------------------------------------------
+void launch_embed(const QWeight& W, const uint32_t* ids, int T, float scale, float* out, cudaStream_t s);
+
+// ---- batch descriptor -----------------------------------------------------------------------
+// Per-lane header uploaded by the host each tick.
+struct LaneHeader {
+    int32_t start_pos;    // absolute position of the lane's first token in this tick
+    int32_t n_tokens;     // tokens of this lane in the tick
+    int32_t table_off;    // offset of the lane's block table inside the concatenated table array
+    int32_t n_blocks;     // entries of that table
+};
+struct BatchDesc {
+    int lanes = 0, T = 0, max_tiles = 0;
+    const LaneHeader* hdr = nullptr;   // [lanes]
+    const uint32_t* tables = nullptr;  // concatenated block ids
+    int32_t* cu_seqlens = nullptr;     // [lanes+1]
+    int32_t* positions = nullptr;      // [T]
+    int32_t* token_lane = nullptr;     // [T]
+    int64_t* slots = nullptr;          // [T]  block*block_tokens + row
+    int32_t* last_index = nullptr;     // [lanes] packed index of each lane's last token
+    int32_t* tile_lane = nullptr;      // [max_tiles] attention query tiles: lane
+    int32_t* tile_row0 = nullptr;      // [max_tiles] first query row (within the lane's chunk)
+    int32_t* n_tiles = nullptr;        // [1]
+    int32_t* error_flag = nullptr;     // [1] set non-zero when an index is out of range
+};
+void launch_build_batch(const BatchDesc& b, int block_tokens, int q_tile, cudaStream_t s);
+
+// ---- RoPE + QK-norm + paged KV scatter --------------------------------------------------------
+struct RopeKvArgs {
+    float* q = nullptr;            // [T][q_heads*d]  rotated in place
+    const float* k = nullptr;      // [T][kv_heads*d]
+    const float* v = nullptr;      // [T][kv_heads*d]
+    int ldq = 0, ldk = 0, ldv = 0;
+    const float* q_norm_w = nullptr;  // [d] or null
+    const float* k_norm_w = nullptr;  // [d] or null
+    float norm_eps = 1e-6f;
+    const float* cos_t = nullptr;  // [capacity][rotary_dim/2], null on NoPE layers
+    const float* sin_t = nullptr;
+    int rotary_dim = 0;
+    const int32_t* positions = nullptr;  // [T]
+    const int64_t* slots = nullptr;      // [T]
+    void* k_pool = nullptr;        // [blocks][layers][kv_heads][block_tokens][d]
+    void* v_pool = nullptr;
+    int kv_f16 = 1;
+    int T = 0, q_heads = 0, kv_heads = 0, d = 0, block_tokens = 16, layers = 0, layer = 0;
+};
+void launch_rope_kv(const RopeKvArgs& a, cudaStream_t s);
+
+// Copy `rows` token rows of every layer and head from block src to block dst (copy-on-write).
+void launch_cow_copy(void* k_pool, void* v_pool, int kv_f16, int64_t src_block, int64_t dst_block, int rows,
+                     int layers, int kv_heads, int block_tokens, int d, cudaStream_t s);
+
+// ---- attention ---------------------------------------------------------------------------------
+struct AttnArgs {
+    const float* q = nullptr;  // [T][q_heads*d]
+    float* out = nullptr;      // [T][q_heads*d]
+    const void* k_pool = nullptr;
+    const void* v_pool = nullptr;
+    int kv_f16 = 1;
+    BatchDesc batch;
+    int q_heads = 0, kv_heads = 0, d = 0, block_tokens = 16, layers = 0, layer = 0;
+    float scale = 1.f, softcap = 0.f;
+    int window = 0;  // 0 = full causal
+    int q_tile = 0;
+};
+void launch_paged_attention(const AttnArgs& a, cudaStream_t s);
+int attention_q_tile(int q_heads, int kv_heads);
+
+// ---- sampling ------------------------------------------------------------------------------------
+// First-index argmax of each row of logits [B][vocab].
+void launch_argmax(const float* logits, int B, int vocab, uint32_t* out, cudaStream_t s);
+
+// ---- MoE -------------------------------------------------------------------------------------------
+// Top-k routing with (logit desc, index asc) order and softmax over the selected k.
+void launch_moe_route(const float* logits, int T, int experts, int k, int32_t* sel_experts, float* sel_weights,
+                      cudaStream_t s);
+
+// Small helpers
+void launch_add_inplace(float* h, const float* a, float scale, int64_t n, cudaStream_t s);
+
+}  // namespace mk

@@ -1,0 +1,147 @@
+"""NumPy-facing wrappers of the kernel-level C ABI entry points (mk_k_*).
+
+Each function mirrors one operator of the reference's path (cited in include/macllm_b200.h) and runs
+the sm_100a kernel through the shared library; host arrays in, host arrays out.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _capi as capi
+
+
+def _p(a: np.ndarray | None):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def row_bytes(qtype: int, cols: int) -> int:
+    return int(capi.lib().mk_row_bytes(qtype, cols))
+
+
+def seed_tensor(seed: int, stream: int, std: float, qtype: int, rows: int, cols: int) -> np.ndarray:
+    """N(0, std) weights from the counter-based generator, quantised to `qtype`; returns raw block bytes."""
+    rb = row_bytes(qtype, cols)
+    if rb < 0:
+        raise capi.MkError(f"unsupported type {qtype} for {cols} columns")
+    out = np.empty(rows * rb, dtype=np.uint8)
+    capi.check(capi.lib().mk_seed_tensor(seed, stream, std, qtype, rows, cols, _p(out)))
+    return out
+
+
+def quantize(x: np.ndarray, act_kind: int = 0):
+    x = _f32(x)
+    T, K = x.shape
+    qs = np.empty((T, K), dtype=np.int8)
+    d = np.empty((T, K // (256 if act_kind == 0 else 32)), dtype=np.float32)
+    bs = np.zeros((T, K // 16), dtype=np.int16)
+    capi.check(capi.lib().mk_k_quantize(act_kind, _p(x), T, K, _p(qs), _p(d), _p(bs)))
+    return qs, d, bs
+
+
+def add_norm(h, a=None, a_scale=1.0, post_w=None, norm_w=None, eps=1e-5):
+    """Returns (updated residual, normed output)."""
+    h = _f32(h).copy()
+    rows, dim = h.shape
+    a = None if a is None else _f32(a)
+    post_w = None if post_w is None else _f32(post_w)
+    norm_w = None if norm_w is None else _f32(norm_w)
+    out = np.empty_like(h)
+    capi.check(capi.lib().mk_k_add_norm(_p(h), _p(a), a_scale, _p(post_w), _p(norm_w), eps, rows, dim, _p(out)))
+    return h, out
+
+
+def qmatmul(qtype: int, w_bytes: np.ndarray, rows: int, cols: int, x: np.ndarray, path: int = capi.PATH_AUTO) -> np.ndarray:
+    x = _f32(x)
+    T = x.shape[0]
+    w_bytes = np.ascontiguousarray(w_bytes)
+    y = np.empty((T, rows), dtype=np.float32)
+    capi.check(capi.lib().mk_k_qmatmul(qtype, _p(w_bytes), rows, cols, _p(x), T, _p(y), path))
+    return y
+
+
+def embed(qtype: int, w_bytes: np.ndarray, rows: int, cols: int, ids, scale: float = 1.0) -> np.ndarray:
+    ids = np.ascontiguousarray(ids, dtype=np.uint32)
+    out = np.empty((len(ids), cols), dtype=np.float32)
+    w_bytes = np.ascontiguousarray(w_bytes)
+    capi.check(capi.lib().mk_k_embed(qtype, _p(w_bytes), rows, cols, _p(ids), len(ids), scale, _p(out)))
+    return out
+
+
+def actmul(gate, up, act: int = 0) -> np.ndarray:
+    gate, up = _f32(gate), _f32(up)
+    T, F = gate.shape
+    out = np.empty_like(gate)
+    capi.check(capi.lib().mk_k_actmul(_p(gate), _p(up), T, F, act, _p(out)))
+    return out
+
+
+def argmax(logits) -> np.ndarray:
+    logits = _f32(logits)
+    B, V = logits.shape
+    out = np.empty(B, dtype=np.uint32)
+    capi.check(capi.lib().mk_k_argmax(_p(logits), B, V, _p(out)))
+    return out
+
+
+def moe_route(logits, k: int):
+    logits = _f32(logits)
+    T, E = logits.shape
+    sel = np.empty((T, k), dtype=np.int32)
+    w = np.empty((T, k), dtype=np.float32)
+    capi.check(capi.lib().mk_k_moe_route(_p(logits), T, E, k, _p(sel), _p(w)))
+    return sel, w
+
+
+def attention_step(q, k, v, k_pool, v_pool, tables, start_pos, lane_len, *, q_heads, kv_heads, head_dim, block_tokens,
+                   layers, layer, scale, softcap=0.0, window=0, cos_table=None, sin_table=None, rotary_dim=0,
+                   q_norm_w=None, k_norm_w=None, norm_eps=1e-6):
+    """One attention layer step of a ragged batch.  `tables` is a list of per-lane block-id lists.
+    k_pool / v_pool ([blocks, layers, kv_heads, block_tokens, head_dim], f16 or f32) are updated in place.
+    Returns dict(out, q_rot, slots, positions, last_index, cu_seqlens)."""
+    q = _f32(q).copy()
+    k, v = _f32(k), _f32(v)
+    lanes = len(lane_len)
+    T = int(sum(lane_len))
+    assert k_pool.dtype == v_pool.dtype and k_pool.dtype in (np.float16, np.float32)
+    flat, offs, lens = [], [], []
+    for t in tables:
+        offs.append(len(flat))
+        lens.append(len(t))
+        flat.extend(int(b) for b in t)
+    tab = np.asarray(flat if flat else [0], dtype=np.uint32)
+    sp = np.asarray(start_pos, dtype=np.int32)
+    ll = np.asarray(lane_len, dtype=np.int32)
+    to = np.asarray(offs, dtype=np.int32)
+    tl = np.asarray(lens, dtype=np.int32)
+    out = np.empty_like(q)
+    q_rot = np.empty_like(q)
+    slots = np.empty(T, dtype=np.int64)
+    pos = np.empty(T, dtype=np.int32)
+    last = np.empty(lanes, dtype=np.int32)
+    cu = np.empty(lanes + 1, dtype=np.int32)
+    cos_table = None if cos_table is None else _f32(cos_table)
+    sin_table = None if sin_table is None else _f32(sin_table)
+    q_norm_w = None if q_norm_w is None else _f32(q_norm_w)
+    k_norm_w = None if k_norm_w is None else _f32(k_norm_w)
+    c = capi.AttnCase()
+    c.lanes, c.total_tokens = lanes, T
+    c.q_heads, c.kv_heads, c.head_dim = q_heads, kv_heads, head_dim
+    c.block_tokens, c.layers, c.layer, c.pool_blocks = block_tokens, layers, layer, k_pool.shape[0]
+    c.kv_f16 = 1 if k_pool.dtype == np.float16 else 0
+    c.scale, c.softcap, c.window = scale, softcap, window
+    c.rotary_dim = rotary_dim if cos_table is not None else 0
+    c.rope_capacity = 0 if cos_table is None else cos_table.shape[0]
+    c.norm_eps = norm_eps
+    for name, arr in (("start_pos", sp), ("lane_len", ll), ("table_off", to), ("table_len", tl), ("tables", tab), ("q", q),
+                      ("k", k), ("v", v), ("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w), ("cos_table", cos_table),
+                      ("sin_table", sin_table), ("k_pool", k_pool), ("v_pool", v_pool), ("out", out), ("q_rot_out", q_rot),
+                      ("slots_out", slots), ("positions_out", pos), ("last_index_out", last), ("cu_seqlens_out", cu)):
+        setattr(c, name, None if arr is None else arr.ctypes.data)
+    capi.check(capi.lib().mk_k_attention_step(C.byref(c)))
+    return dict(out=out, q_rot=q_rot, slots=slots, positions=pos, last_index=last, cu_seqlens=cu)

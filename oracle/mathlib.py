@@ -1,0 +1,195 @@
+"""ctypes/NumPy front of oracle_math.cpp (the C++ restatement of the reference's CPU arithmetic).
+
+TEST INFRASTRUCTURE ONLY - see oracle/__init__.py.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+LIB = HERE / "liboracle_math.so"
+
+F32, F16, Q8_0, Q4_K, Q6_K = 0, 1, 8, 12, 14
+
+_lib = None
+
+
+def build(force: bool = False) -> Path:
+    src = HERE / "oracle_math.cpp"
+    if force or not LIB.exists() or LIB.stat().st_mtime < src.stat().st_mtime:
+        subprocess.run(["make", "-C", str(HERE), "-B" if force else "-s", "liboracle_math.so"], check=True,
+                       capture_output=True)
+    return LIB
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB.exists():
+            build()
+        h = C.CDLL(str(LIB))
+        h.orc_row_bytes.restype = C.c_int64
+        h.orc_row_bytes.argtypes = [C.c_int, C.c_int64]
+        h.orc_argmax.restype = C.c_int64
+        h.orc_f16_to_f32.restype = C.c_float
+        h.orc_f16_to_f32.argtypes = [C.c_uint16]
+        h.orc_f32_to_f16.restype = C.c_uint16
+        h.orc_f32_to_f16.argtypes = [C.c_float]
+        h.orc_num_threads.restype = C.c_int
+        _lib = h
+    return _lib
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def row_bytes(t: int, cols: int) -> int:
+    return int(lib().orc_row_bytes(t, C.c_int64(cols)))
+
+
+def num_threads() -> int:
+    return int(lib().orc_num_threads())
+
+
+def dequant(t: int, w: np.ndarray, rows: int, cols: int) -> np.ndarray:
+    w = np.ascontiguousarray(w)
+    out = np.empty((rows, cols), dtype=np.float32)
+    lib().orc_dequant(t, _p(w), C.c_int64(rows), C.c_int64(cols), _p(out))
+    return out
+
+
+def quantize_q8k(x: np.ndarray):
+    x = _f32(x)
+    T, K = x.shape
+    qs = np.empty((T, K), np.int8)
+    d = np.empty((T, K // 256), np.float32)
+    bs = np.empty((T, K // 16), np.int16)
+    for t in range(T):
+        lib().orc_quantize_q8k(_p(x[t]), C.c_int64(K), _p(qs[t]), _p(d[t]), _p(bs[t]))
+    return qs, d, bs
+
+
+def quantize_q80(x: np.ndarray):
+    x = _f32(x)
+    T, K = x.shape
+    qs = np.empty((T, K), np.int8)
+    d = np.empty((T, K // 32), np.uint16)
+    for t in range(T):
+        lib().orc_quantize_q80(_p(x[t]), C.c_int64(K), _p(qs[t]), _p(d[t]))
+    return qs, d.view(np.float16).astype(np.float32)
+
+
+def qmatmul(t: int, w: np.ndarray, rows: int, cols: int, x: np.ndarray, mode: int = 1) -> np.ndarray:
+    """y [T, rows] = x [T, cols] . W^T ; mode 1 = 8-bit activation blocks + integer dots, 2 = dequantised f32."""
+    x = _f32(x)
+    w = np.ascontiguousarray(w)
+    T = x.shape[0]
+    y = np.empty((T, rows), dtype=np.float32)
+    lib().orc_qmatmul(t, _p(w), C.c_int64(rows), C.c_int64(cols), _p(x), C.c_int64(T), _p(y), mode)
+    return y
+
+
+def fake_quant_rows(t: int, x: np.ndarray) -> np.ndarray:
+    x = _f32(x)
+    out = np.empty_like(x)
+    lib().orc_fake_quant_rows(t, _p(x), C.c_int64(x.shape[0]), C.c_int64(x.shape[1]), _p(out))
+    return out
+
+
+def embed(t: int, w: np.ndarray, cols: int, ids, scale: float = 1.0) -> np.ndarray:
+    ids = np.ascontiguousarray(ids, dtype=np.uint32)
+    w = np.ascontiguousarray(w)
+    out = np.empty((len(ids), cols), dtype=np.float32)
+    lib().orc_embed(t, _p(w), C.c_int64(cols), _p(ids), C.c_int64(len(ids)), C.c_float(scale), _p(out))
+    return out
+
+
+def rmsnorm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
+    x = _f32(x)
+    w = _f32(w)
+    rows, dim = x.shape
+    y = np.empty_like(x)
+    lib().orc_rmsnorm(_p(x), _p(w), C.c_float(eps), C.c_int64(rows), C.c_int64(dim), _p(y))
+    return y
+
+
+def act_mul(gate: np.ndarray, up: np.ndarray, act: int) -> np.ndarray:
+    gate, up = _f32(gate), _f32(up)
+    out = np.empty_like(gate)
+    lib().orc_act_mul(_p(gate), _p(up), C.c_int64(gate.size), act, _p(out))
+    return out
+
+
+def softcap(x: np.ndarray, cap: float) -> np.ndarray:
+    x = _f32(x).copy()
+    lib().orc_softcap(_p(x), C.c_int64(x.size), C.c_float(cap))
+    return x
+
+
+def rope_tables(theta: float, rotary_dim: int, capacity: int):
+    cos = np.empty((capacity, rotary_dim // 2), np.float32)
+    sin = np.empty_like(cos)
+    lib().orc_rope_tables(C.c_double(theta), rotary_dim, C.c_int64(capacity), _p(cos), _p(sin))
+    return cos, sin
+
+
+def rope_apply(x: np.ndarray, heads: int, d: int, rotary_dim: int, pos, cos, sin) -> np.ndarray:
+    """x [T, heads*d]; returns rotated copy."""
+    x = _f32(x).copy()
+    pos = np.ascontiguousarray(pos, dtype=np.int32)
+    lib().orc_rope_apply(_p(x), C.c_int64(x.shape[0]), heads, d, rotary_dim, _p(pos), _p(cos), _p(sin))
+    return x
+
+
+def kv_scatter(k, v, k_pool, v_pool, slots, kv_heads, d, block_tokens, layers, layer):
+    k, v = _f32(k), _f32(v)
+    slots = np.ascontiguousarray(slots, dtype=np.int64)
+    f16 = 1 if k_pool.dtype == np.float16 else 0
+    lib().orc_kv_scatter(_p(k), _p(v), _p(k_pool), _p(v_pool), f16, _p(slots), C.c_int64(len(slots)), kv_heads, d,
+                         block_tokens, layers, layer)
+
+
+def paged_attention(q, k_pool, v_pool, page_table, page_off, start_pos, lane_len, *, q_heads, kv_heads, d, block_tokens,
+                    layers, layer, scale, softcap=0.0, window=0, mode=1) -> np.ndarray:
+    q = _f32(q)
+    out = np.empty_like(q)
+    pt = np.ascontiguousarray(page_table, dtype=np.uint32)
+    po = np.ascontiguousarray(page_off, dtype=np.int32)
+    sp = np.ascontiguousarray(start_pos, dtype=np.int32)
+    ll = np.ascontiguousarray(lane_len, dtype=np.int32)
+    f16 = 1 if k_pool.dtype == np.float16 else 0
+    lib().orc_paged_attention(_p(q), _p(out), _p(k_pool), _p(v_pool), f16, _p(pt), _p(po), _p(sp), _p(ll), len(ll), q_heads,
+                              kv_heads, d, block_tokens, layers, layer, C.c_float(scale), C.c_float(softcap), window, mode)
+    return out
+
+
+def moe_route(logits: np.ndarray, k: int):
+    logits = _f32(logits)
+    T, E = logits.shape
+    sel = np.empty((T, k), np.int32)
+    w = np.empty((T, k), np.float32)
+    lib().orc_moe_route(_p(logits), C.c_int64(T), E, k, _p(sel), _p(w))
+    return sel, w
+
+
+def argmax(v: np.ndarray) -> int:
+    v = _f32(v)
+    return int(lib().orc_argmax(_p(v), C.c_int64(v.size)))
+
+
+def apply_penalties(logits, history, rep, generated, presence, frequency) -> np.ndarray:
+    logits = _f32(logits).copy()
+    h = np.ascontiguousarray(history, dtype=np.uint32)
+    g = np.ascontiguousarray(generated, dtype=np.uint32)
+    lib().orc_apply_penalties(_p(logits), C.c_int64(logits.size), _p(h), C.c_int64(len(h)), C.c_float(rep), _p(g),
+                              C.c_int64(len(g)), C.c_float(presence), C.c_float(frequency))
+    return logits

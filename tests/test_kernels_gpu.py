@@ -1,0 +1,212 @@
+"""Parity of the sm_100a kernels against the CPU oracle, through the C ABI (needs a GPU)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+QTYPES = {"q4_k": 12, "q6_k": 14, "q8_0": 8}
+
+
+@pytest.fixture(scope="module")
+def ops(mk):
+    import importlib
+    return importlib.import_module("macllm_infer_b200.ops")
+
+
+def _weights(ops, qtype, rows, cols, stream=1):
+    return ops.seed_tensor(0, stream, 0.02, qtype, rows, cols)
+
+
+@pytest.mark.parametrize("kind", [0, 1])
+def test_quantize_bit_exact(ops, orc, kind):
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((7, 1024)).astype(np.float32)
+    x[2, 256:512] = 0.0                      # an all-zero block
+    x[3, 5] = -x[3, 9]                       # a sign tie on the block maximum
+    x[3, 5] = abs(x[3]).max() + 1.0
+    x[3, 9] = -x[3, 5]
+    qs, d, bs = ops.quantize(x, kind)
+    if kind == 0:
+        oq, od, ob = orc.quantize_q8k(x)
+        assert np.array_equal(bs, ob)
+    else:
+        oq, od = orc.quantize_q80(x)
+    assert np.array_equal(qs, oq)
+    assert np.array_equal(d, od)
+
+
+@pytest.mark.parametrize("name", list(QTYPES))
+@pytest.mark.parametrize("T", [1, 3, 8, 19])
+def test_qgemv_matches_oracle(ops, orc, name, T):
+    qtype = QTYPES[name]
+    rows, cols = 384, 2048
+    w = _weights(ops, qtype, rows, cols)
+    rng = np.random.default_rng(T)
+    x = rng.standard_normal((T, cols)).astype(np.float32)
+    got = ops.qmatmul(qtype, w, rows, cols, x, 1)
+    want = orc.qmatmul(qtype, w, rows, cols, x, 1)
+    # integer block dots are exact; only the f32 accumulation order over blocks differs
+    assert np.max(np.abs(got - want)) <= 2e-5 * max(1.0, np.max(np.abs(want)))
+
+
+@pytest.mark.parametrize("name", list(QTYPES))
+@pytest.mark.parametrize("T,rows,cols", [(9, 128, 256), (40, 300, 1024), (64, 2048, 2048), (130, 512, 5632), (257, 256, 768)])
+def test_qgemm_tensor_matches_oracle(ops, orc, name, T, rows, cols):
+    qtype = QTYPES[name]
+    w = _weights(ops, qtype, rows, cols, stream=3)
+    rng = np.random.default_rng(T + rows)
+    x = rng.standard_normal((T, cols)).astype(np.float32)
+    got = ops.qmatmul(qtype, w, rows, cols, x, 2)
+    want = orc.qmatmul(qtype, w, rows, cols, x, 1)
+    # operands rounded once to f16 (rel 2^-11 each), f32 accumulation
+    scale = np.sqrt(cols) * 0.02
+    assert np.max(np.abs(got - want)) <= 2e-3 * scale
+    cos = float((got * want).sum() / np.sqrt((got * got).sum() * (want * want).sum()))
+    assert cos >= 0.999999
+
+
+@pytest.mark.parametrize("name", ["q4_k", "q6_k", "q8_0", "f32"])
+def test_embed_rows_exact(ops, orc, name):
+    qtype = {"f32": 0, **QTYPES}[name]
+    rows, cols = 300, 512
+    w = _weights(ops, qtype, rows, cols, stream=5)
+    ids = np.array([0, 299, 17, 17, 123], dtype=np.uint32)
+    got = ops.embed(qtype, w, rows, cols, ids, 1.0)
+    want = orc.embed(qtype, w, cols, ids, 1.0)
+    assert np.array_equal(got, want)
+    got = ops.embed(qtype, w, rows, cols, ids, 59.866)
+    want = orc.embed(qtype, w, cols, ids, 59.866)
+    assert np.array_equal(got, want)
+
+
+def test_add_norm(ops, orc):
+    rng = np.random.default_rng(3)
+    rows, dim = 5, 2048
+    h = rng.standard_normal((rows, dim)).astype(np.float32)
+    a = rng.standard_normal((rows, dim)).astype(np.float32)
+    w = (1 + 0.1 * rng.standard_normal(dim)).astype(np.float32)
+    pw = (1 + 0.1 * rng.standard_normal(dim)).astype(np.float32)
+    h2, n = ops.add_norm(h, a, 1.0, None, w, 1e-5)
+    assert np.array_equal(h2, h + a)
+    want = orc.rmsnorm(h + a, w, 1e-5)
+    assert np.max(np.abs(n - want)) < 1e-5
+    # sandwich form: post-norm on the branch output before the residual add
+    h3, n3 = ops.add_norm(h, a, 1.0, pw, w, 1e-6)
+    want_h = h + orc.rmsnorm(a, pw, 1e-6)
+    assert np.max(np.abs(h3 - want_h)) < 1e-5
+    assert np.max(np.abs(n3 - orc.rmsnorm(want_h, w, 1e-6))) < 2e-5
+
+
+@pytest.mark.parametrize("act", [0, 1])
+def test_actmul(ops, orc, act):
+    rng = np.random.default_rng(4)
+    g = (3 * rng.standard_normal((3, 5632))).astype(np.float32)
+    u = rng.standard_normal((3, 5632)).astype(np.float32)
+    got = ops.actmul(g, u, act)
+    want = orc.act_mul(g, u, act)
+    assert np.max(np.abs(got - want)) < 2e-6 * max(1.0, np.max(np.abs(want)))
+
+
+def test_argmax_first_index_and_total_order(ops, orc):
+    rng = np.random.default_rng(5)
+    logits = rng.standard_normal((6, 32000)).astype(np.float32)
+    logits[1, 100] = logits[1, 20000] = 9.0          # tie: first index wins
+    logits[2, :] = -0.0
+    logits[2, 7] = 0.0                                # +0 > -0 in the total order
+    logits[3, :] = -5.0
+    logits[4, 31999] = 50.0
+    got = ops.argmax(logits)
+    want = [orc.argmax(r) for r in logits]
+    assert list(got) == want
+    assert got[1] == 100 and got[2] == 7 and got[3] == 0 and got[4] == 31999
+
+
+def test_moe_route(ops, orc):
+    rng = np.random.default_rng(6)
+    logits = rng.standard_normal((33, 128)).astype(np.float32)
+    logits[0, 3] = logits[0, 90] = 4.0               # tie -> lower index first
+    logits[1, :] = 0.5                                # all equal -> experts 0..7
+    logits[2, 10] = 0.0
+    logits[2, 4] = -0.0
+    sel, w = ops.moe_route(logits, 8)
+    osel, ow = orc.moe_route(logits, 8)
+    assert np.array_equal(sel, osel)
+    assert np.max(np.abs(w - ow)) < 1e-6
+    assert list(sel[1]) == list(range(8))
+
+
+def _attn_case(rng, lanes_spec, q_heads, kv_heads, d, bt, layers, layer, kv_dtype):
+    """lanes_spec: list of (start_pos, n_tokens).  Builds pools with random history and disjoint tables."""
+    blocks_needed = [-(-(s + n) // bt) for s, n in lanes_spec]
+    pool_blocks = sum(blocks_needed) + 3
+    perm = rng.permutation(pool_blocks)
+    tables, off = [], 0
+    for nb in blocks_needed:
+        tables.append([int(b) for b in perm[off:off + nb]])
+        off += nb
+    shape = (pool_blocks, layers, kv_heads, bt, d)
+    k_pool = rng.standard_normal(shape).astype(np.float32).astype(kv_dtype)
+    v_pool = rng.standard_normal(shape).astype(np.float32).astype(kv_dtype)
+    T = sum(n for _, n in lanes_spec)
+    q = rng.standard_normal((T, q_heads * d)).astype(np.float32)
+    k = rng.standard_normal((T, kv_heads * d)).astype(np.float32)
+    v = rng.standard_normal((T, kv_heads * d)).astype(np.float32)
+    return tables, k_pool, v_pool, q, k, v
+
+
+@pytest.mark.parametrize("kv_dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("geom", [(32, 4, 64), (16, 4, 128), (16, 8, 256), (2, 1, 4)])
+@pytest.mark.parametrize("window,softcap", [(0, 0.0), (24, 0.0), (0, 50.0)])
+def test_attention_step_matches_oracle(ops, orc, kv_dtype, geom, window, softcap):
+    q_heads, kv_heads, d = geom
+    bt, layers, layer = 16, 3, 1
+    rng = np.random.default_rng(q_heads * 1000 + d + window)
+    lanes_spec = [(0, 17), (40, 1), (5, 33), (63, 1), (16, 16), (0, 1), (100, 70)]
+    tables, k_pool, v_pool, q, k, v = _attn_case(rng, lanes_spec, q_heads, kv_heads, d, bt, layers, layer, kv_dtype)
+    rotary = d
+    cos, sin = orc.rope_tables(10000.0, rotary, 256)
+    qn = (1 + 0.1 * rng.standard_normal(d)).astype(np.float32)
+    kn = (1 + 0.1 * rng.standard_normal(d)).astype(np.float32)
+    scale = 1.0 / np.sqrt(d)
+    kp, vp = k_pool.copy(), v_pool.copy()
+    res = ops.attention_step(q, k, v, kp, vp, tables, [s for s, _ in lanes_spec], [n for _, n in lanes_spec],
+                             q_heads=q_heads, kv_heads=kv_heads, head_dim=d, block_tokens=bt, layers=layers, layer=layer,
+                             scale=scale, softcap=softcap, window=window, cos_table=cos, sin_table=sin, rotary_dim=rotary,
+                             q_norm_w=qn, k_norm_w=kn, norm_eps=1e-6)
+    # oracle: same steps
+    pos = np.concatenate([np.arange(s, s + n) for s, n in lanes_spec]).astype(np.int32)
+    slots = np.concatenate([[tables[i][p // bt] * bt + p % bt for p in range(s, s + n)]
+                            for i, (s, n) in enumerate(lanes_spec)]).astype(np.int64)
+    assert np.array_equal(res["positions"], pos)
+    assert np.array_equal(res["slots"], slots)
+    cu = np.concatenate([[0], np.cumsum([n for _, n in lanes_spec])])
+    assert np.array_equal(res["cu_seqlens"], cu)
+    assert np.array_equal(res["last_index"], cu[1:] - 1)
+    T = len(pos)
+    qh = orc.rmsnorm(q.reshape(T * q_heads, d), qn, 1e-6).reshape(T, q_heads * d)
+    kh = orc.rmsnorm(k.reshape(T * kv_heads, d), kn, 1e-6).reshape(T, kv_heads * d)
+    q_rot = orc.rope_apply(qh, q_heads, d, rotary, pos, cos, sin)
+    k_rot = orc.rope_apply(kh, kv_heads, d, rotary, pos, cos, sin)
+    assert np.max(np.abs(res["q_rot"] - q_rot)) < 2e-6
+    okp, ovp = k_pool.copy(), v_pool.copy()
+    orc.kv_scatter(k_rot, v, okp, ovp, slots, kv_heads, d, bt, layers, layer)
+    tol_pool = 0 if kv_dtype == np.float32 else 2e-3
+    assert np.max(np.abs(kp.astype(np.float32) - okp.astype(np.float32))) <= max(tol_pool, 2e-6)
+    assert np.array_equal(vp, ovp)
+    flat = np.concatenate(tables).astype(np.uint32)
+    page_off = np.concatenate([[0], np.cumsum([len(t) for t in tables])[:-1]]).astype(np.int32)
+    for mode in (0, 1):
+        want = orc.paged_attention(q_rot, okp, ovp, flat, page_off, [s for s, _ in lanes_spec], [n for _, n in lanes_spec],
+                                   q_heads=q_heads, kv_heads=kv_heads, d=d, block_tokens=bt, layers=layers, layer=layer,
+                                   scale=scale, softcap=softcap, window=window, mode=mode)
+        assert np.max(np.abs(res["out"] - want)) < (2e-5 if kv_dtype == np.float32 else 2e-3)
+
+
+def test_attention_nope_layer_leaves_queries_unrotated(ops, orc):
+    rng = np.random.default_rng(9)
+    q_heads, kv_heads, d, bt = 8, 2, 64, 16
+    lanes_spec = [(3, 5), (20, 1)]
+    tables, k_pool, v_pool, q, k, v = _attn_case(rng, lanes_spec, q_heads, kv_heads, d, bt, 1, 0, np.float32)
+    res = ops.attention_step(q, k, v, k_pool, v_pool, tables, [3, 20], [5, 1], q_heads=q_heads, kv_heads=kv_heads,
+                             head_dim=d, block_tokens=bt, layers=1, layer=0, scale=0.125)
+    assert np.array_equal(res["q_rot"], q)
