@@ -13,8 +13,8 @@ using namespace mk;
 namespace {
 
 struct ActBufs {
-    DevBuf qs, d, bs;
-    ActQ view(int T, int K, int kind) {
+    DevBuf qs, d, bs, xh;
+    ActQ view(int T, int K, int kind, bool want_f16 = false) {
         qs.ensure((size_t)T * K);
         d.ensure((size_t)T * (kind == ACT_Q8K ? K / 256 : K / 32) * 4);
         bs.ensure((size_t)T * (K / 16) * 2 + 16);
@@ -22,6 +22,10 @@ struct ActBufs {
         a.qs = qs.as<int8_t>();
         a.d = d.as<float>();
         a.bsums = bs.as<int16_t>();
+        if (want_f16) {
+            xh.ensure((size_t)T * K * 2);
+            a.xh = xh.as<__half>();
+        }
         return a;
     }
 };
@@ -91,7 +95,8 @@ int32_t mk_k_qmatmul(int32_t type, const void* w, int64_t rows, int64_t cols, co
         DevBuf dx((size_t)T * cols * 4), dy((size_t)T * rows * 4);
         dx.upload(x, (size_t)T * cols * 4);
         ActBufs ab;
-        ActQ a = ab.view(T, (int)cols, kind);
+        bool tensor = path == MK_PATH_TENSOR || (path == MK_PATH_AUTO && qgemm_tc_preferred(dw.w, T));
+        ActQ a = ab.view(T, (int)cols, kind, tensor);
         NormQuantArgs na;
         na.h = dx.as<float>();
         na.rows = T;
@@ -99,9 +104,14 @@ int32_t mk_k_qmatmul(int32_t type, const void* w, int64_t rows, int64_t cols, co
         na.act_kind = kind;
         na.out = a;
         launch_add_norm_quant(na, nullptr);
-        if (path == MK_PATH_TENSOR || (path == MK_PATH_AUTO && qgemm_tc_preferred(dw.w, T))) {
+        if (tensor) {
             QgemmWorkspace ws;
             launch_qgemm_tc(dw.w, a, kind, T, dy.as<float>(), (int)rows, 1.0f, 0.f, ws, nullptr);
+            MK_CUDA(cudaDeviceSynchronize());
+            int32_t st = 0;
+            ws.status.download(&st, 4);
+            MK_CUDA(cudaDeviceSynchronize());
+            if (st != 0) throw std::runtime_error("qgemm_tc: a bounded wait inside the kernel gave up (status " + std::to_string(st) + ")");
         } else {
             launch_qgemv(dw.w, a, T, dy.as<float>(), (int)rows, 1.0f, 0.f, nullptr);
         }

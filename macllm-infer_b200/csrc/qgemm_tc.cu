@@ -101,7 +101,7 @@ __device__ __forceinline__ void q4k_scale_min_reg(uint32_t y, uint32_t z, uint32
 }
 
 // Four bytes b0..b3 (each < 64) -> two half2 holding (b0, b1) and (b2, b3) minus `bias`, times `scale`,
-// minus `offset`, rounded once per element.
+// plus `neg_offset`, rounded once per element.
 __device__ __forceinline__ void bytes_to_half4(uint32_t bytes, __half2 bias, __half2 scale, __half2 neg_offset, uint32_t& o01,
                                                uint32_t& o23) {
     uint32_t p01 = __byte_perm(bytes, 0x64646464u, 0x4140);
@@ -110,6 +110,32 @@ __device__ __forceinline__ void bytes_to_half4(uint32_t bytes, __half2 bias, __h
     __half2 h23 = __hsub2(*reinterpret_cast<__half2*>(&p23), bias);
     h01 = __hfma2(h01, scale, neg_offset);
     h23 = __hfma2(h23, scale, neg_offset);
+    o01 = *reinterpret_cast<uint32_t*>(&h01);
+    o23 = *reinterpret_cast<uint32_t*>(&h23);
+}
+
+// Same for w = q * s - o where s and o are f32 values split into an f16 head and an f16 tail, so the
+// f16 result carries one rounding relative to w itself instead of the (larger) roundings of s and o:
+// w = fma(q, s_hi, -o_hi) + fma(q, s_lo, -o_lo).
+struct SplitScale {
+    __half2 s_hi, s_lo, o_hi, o_lo;  // o_* hold the negated offset
+};
+__device__ __forceinline__ SplitScale make_split(float s, float o) {
+    SplitScale r;
+    __half sh = __float2half_rn(s), oh = __float2half_rn(-o);
+    r.s_hi = __half2half2(sh);
+    r.o_hi = __half2half2(oh);
+    r.s_lo = __float2half2_rn(s - __half2float(sh));
+    r.o_lo = __float2half2_rn(-o - __half2float(oh));
+    return r;
+}
+__device__ __forceinline__ void nibbles_to_half4(uint32_t bytes, __half2 bias, const SplitScale& sp, uint32_t& o01, uint32_t& o23) {
+    uint32_t p01 = __byte_perm(bytes, 0x64646464u, 0x4140);
+    uint32_t p23 = __byte_perm(bytes, 0x64646464u, 0x4342);
+    __half2 q01 = __hsub2(*reinterpret_cast<__half2*>(&p01), bias);
+    __half2 q23 = __hsub2(*reinterpret_cast<__half2*>(&p23), bias);
+    __half2 h01 = __hadd2(__hfma2(q01, sp.s_hi, sp.o_hi), __hfma2(q01, sp.s_lo, sp.o_lo));
+    __half2 h23 = __hadd2(__hfma2(q23, sp.s_hi, sp.o_hi), __hfma2(q23, sp.s_lo, sp.o_lo));
     o01 = *reinterpret_cast<uint32_t*>(&h01);
     o23 = *reinterpret_cast<uint32_t*>(&h23);
 }
@@ -149,17 +175,17 @@ __device__ __forceinline__ void dequant_store_a(const TcParams& p, int row_globa
         int sc0, m0, sc1, m1;
         q4k_scale_min_reg(hdr.y, hdr.z, hdr.w, 2 * j, sc0, m0);
         q4k_scale_min_reg(hdr.y, hdr.z, hdr.w, 2 * j + 1, sc1, m1);
-        __half2 s0 = __float2half2_rn(d * (float)sc0), o0 = __float2half2_rn(-(dmin * (float)m0));
-        __half2 s1 = __float2half2_rn(d * (float)sc1), o1 = __float2half2_rn(-(dmin * (float)m1));
+        SplitScale sp0 = make_split(d * (float)sc0, dmin * (float)m0);
+        SplitScale sp1 = make_split(d * (float)sc1, dmin * (float)m1);
         __half2 bias = __float2half2_rn(1024.f);
         uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             uint4 lo, hi;
-            bytes_to_half4(words[2 * i] & 0x0F0F0F0Fu, bias, s0, o0, lo.x, lo.y);
-            bytes_to_half4(words[2 * i + 1] & 0x0F0F0F0Fu, bias, s0, o0, lo.z, lo.w);
-            bytes_to_half4((words[2 * i] >> 4) & 0x0F0F0F0Fu, bias, s1, o1, hi.x, hi.y);
-            bytes_to_half4((words[2 * i + 1] >> 4) & 0x0F0F0F0Fu, bias, s1, o1, hi.z, hi.w);
+            nibbles_to_half4(words[2 * i] & 0x0F0F0F0Fu, bias, sp0, lo.x, lo.y);
+            nibbles_to_half4(words[2 * i + 1] & 0x0F0F0F0Fu, bias, sp0, lo.z, lo.w);
+            nibbles_to_half4((words[2 * i] >> 4) & 0x0F0F0F0Fu, bias, sp1, hi.x, hi.y);
+            nibbles_to_half4((words[2 * i + 1] >> 4) & 0x0F0F0F0Fu, bias, sp1, hi.z, hi.w);
             *chunk_ptr(8 * c + i) = lo;
             *chunk_ptr(8 * c + 4 + i) = hi;
         }
