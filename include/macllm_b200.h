@@ -122,6 +122,11 @@ typedef struct mk_prefix_diagnostics {
 
 /* LoadedRuntime::load (src/runtime.rs:104-145) for a GGUF file. */
 int32_t mk_model_load_gguf(const char* path, const mk_load_config* cfg, mk_model** out);
+/* A host-only model with deterministic one-hot logits (next token after feeding token t at position p
+ * is (31 t + 7 p + 3) mod vocab): drives the scheduler, the KV pool and the prefix cache without a GPU,
+ * like FakeModel in the reference's scheduler tests (src/engine.rs:3107-3300).  fail_forward_at >= 0
+ * makes that forward (0-based) fail, to exercise rollback. */
+int32_t mk_model_new_fake(int32_t vocab, int32_t max_context, const mk_load_config* cfg, int64_t fail_forward_at, mk_model** out);
 int32_t mk_model_free(mk_model* m);
 int32_t mk_model_spec(mk_model* m, mk_runtime_spec* out);
 

@@ -105,6 +105,7 @@ SIGNATURES = {
     "mk_version": (C.c_char_p, []),
     "mk_device_count": (_i32, []),
     "mk_model_load_gguf": (_i32, [C.c_char_p, C.POINTER(LoadConfig), C.POINTER(P)]),
+    "mk_model_new_fake": (_i32, [_i32, _i32, C.POINTER(LoadConfig), _i64, C.POINTER(P)]),
     "mk_model_free": (_i32, [P]),
     "mk_model_spec": (_i32, [P, C.POINTER(RuntimeSpec)]),
     "mk_session_new": (_i32, [P, C.POINTER(P)]),

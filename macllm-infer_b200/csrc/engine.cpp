@@ -1,0 +1,445 @@
+// See engine.h.  Line references are into the reference's src/engine.rs and src/generation.rs.
+#include "engine.h"
+#include "host_sampler.h"
+#include <algorithm>
+#include <cmath>
+#include <numeric>
+
+namespace mk {
+
+Engine::Engine(PagedLm& model, const EngineConfig& cfg) : model_(model), cfg_(cfg) {
+    if (cfg.max_active_sequences <= 0 || cfg.scheduler_token_budget <= 0 || cfg.prefill_token_quantum <= 0 || cfg.queue_capacity <= 0)
+        throw std::runtime_error("engine configuration values must be positive");  // EngineConfig validation, engine.rs:350-384
+    // worker_main creates every reusable session up front (engine.rs:1336-1360)
+    for (int i = 0; i < cfg.max_active_sequences; ++i) sessions_.push_back(model_.new_session());
+}
+
+Engine::~Engine() {
+    // sequences release their pages before the sessions' tables go away
+    active_.clear();
+    sessions_.clear();
+}
+
+std::vector<int> Engine::submit(const std::vector<EngineRequest>& reqs, bool atomic_batch) {
+    if (reqs.empty()) throw std::runtime_error("submission is empty");
+    if ((int)(queue_.size() + reqs.size()) > cfg_.queue_capacity) throw std::runtime_error("inference queue is full");
+    if (atomic_batch && (int)reqs.size() > cfg_.max_active_sequences)
+        throw std::runtime_error("atomic batch exceeds the active sequence limit");  // engine.rs:976-1053
+    std::vector<int> ids;
+    int batch = atomic_batch ? next_batch_++ : -1;
+    for (const EngineRequest& r : reqs) {
+        Job j;
+        j.id = next_id_++;
+        j.req = r;
+        j.batch = batch;
+        j.batch_size = atomic_batch ? (int)reqs.size() : 0;
+        results_[j.id] = EngineResult{};
+        ids.push_back(j.id);
+        queue_.push_back(std::move(j));
+    }
+    return ids;
+}
+
+const EngineResult& Engine::result(int id) const {
+    auto it = results_.find(id);
+    if (it == results_.end()) throw std::runtime_error("unknown request id " + std::to_string(id));
+    return it->second;
+}
+
+void Engine::fail_request(int id, const std::string& message) {
+    EngineResult& r = results_[id];
+    r.state = FinishState::Failed;
+    r.message = message;
+    ++stats_.failed;
+}
+
+void Engine::admit(Job job) {  // admit_with_diagnostic_refresh, engine.rs:1654-1808
+    if ((int)active_.size() >= cfg_.max_active_sequences) throw std::runtime_error("scheduler attempted to exceed the active sequence limit");
+    const EngineRequest& rq = job.req;
+    const LmRuntimeSpec& spec = model_.spec();
+    // prepare_request / validate_request (generation.rs:1308-1337)
+    if (rq.prompt.empty()) return fail_request(job.id, "prompt must contain at least one token");
+    int64_t required = (int64_t)rq.prompt.size() + std::max(rq.max_new_tokens - 1, 0);
+    if (required > spec.max_context) return fail_request(job.id, "prompt plus requested output exceeds model context limit");
+    for (uint32_t t : rq.prompt)
+        if ((int64_t)t >= spec.vocab) return fail_request(job.id, "input contains a token ID outside the model vocabulary");
+    if (!(rq.temperature >= 0.f) || !(rq.top_p > 0.f && rq.top_p <= 1.f) || !(rq.repetition_penalty > 0.f))
+        return fail_request(job.id, "invalid sampling configuration");  // Sampler::new, sampling.rs:43-62
+    // kv_capacity_rejection (engine.rs:2839-2863)
+    {
+        KvPoolStats st = model_.pool_stats();
+        int64_t max_cached = rq.max_new_tokens == 0 ? 0 : (int64_t)rq.prompt.size() + rq.max_new_tokens - 1;
+        if (max_cached > st.max_blocks * st.block_tokens)
+            return fail_request(job.id, "request requires up to " + std::to_string(max_cached) +
+                                            " cached tokens, exceeding the configured shared KV capacity");
+    }
+    if (sessions_.empty()) throw std::runtime_error("active slot has no reusable inference session");
+    auto seq = std::make_unique<Sequence>();
+    seq->id = job.id;
+    seq->req = rq;
+    seq->session = std::move(sessions_.back());  // LIFO (engine.rs:1719-1722)
+    sessions_.pop_back();
+    seq->history = rq.prompt;
+    seq->prompt_tokens = (int)rq.prompt.size();
+    seq->rng = rq.seed * 0x9E3779B97F4A7C15ull + 0xD1B54A32D192ED03ull;
+    // GenerationCore::new (generation.rs:787-832): prefix lookup + block-table attach happen at admission
+    int64_t cached = model_.reset_session_for_prompt(*seq->session, seq->history.data(), seq->history.size());
+    if (cached >= (int64_t)seq->history.size())
+        throw std::runtime_error("prefix cache must leave at least one prompt token for first-token logits");
+    seq->cursor = (int)cached;
+    results_[job.id].cached_tokens = cached;
+    active_.push_back(std::move(seq));
+}
+
+bool Engine::admit_pending_atomic() {  // engine.rs:1886-1936
+    if (pending_atomic_.empty()) return false;
+    int available = cfg_.max_active_sequences - (int)active_.size();
+    if ((int)pending_atomic_.size() > available) return false;
+    std::vector<Job> batch = std::move(pending_atomic_);
+    pending_atomic_.clear();
+    for (Job& j : batch) admit(std::move(j));
+    return true;
+}
+
+bool Engine::try_admit_available() {  // engine.rs:1810-1881
+    bool admitted = admit_pending_atomic();
+    if (!pending_atomic_.empty()) return admitted;
+    while ((int)active_.size() < cfg_.max_active_sequences && !queue_.empty()) {
+        Job job = std::move(queue_.front());
+        queue_.pop_front();
+        if (job.batch < 0) {
+            admit(std::move(job));
+            admitted = true;
+            continue;
+        }
+        int batch = job.batch, size = job.batch_size;
+        pending_atomic_.push_back(std::move(job));
+        while ((int)pending_atomic_.size() < size) {
+            if (queue_.empty() || queue_.front().batch != batch)
+                throw std::runtime_error("atomic batch jobs were not contiguous in the inference queue");
+            pending_atomic_.push_back(std::move(queue_.front()));
+            queue_.pop_front();
+        }
+        admit_pending_atomic();
+        admitted = true;
+        if (!pending_atomic_.empty()) break;
+    }
+    return admitted;
+}
+
+void Engine::reclaim(Sequence& s) {  // reclaim_slot_sequence_after_completion_barrier, engine.rs:2676-2690
+    if (s.reclaimed) return;
+    model_.clear_session(*s.session);
+    s.reclaimed = std::move(s.session);
+}
+
+static inline uint64_t next_u64(uint64_t& state) {
+    state += 0x9E3779B97F4A7C15ull;
+    uint64_t z = state;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+uint32_t Engine::sample(Sequence& s, float* row) {  // Sampler::sample_with_generated, sampling.rs:95-169
+    const int vocab = model_.spec().vocab;
+    const EngineRequest& rq = s.req;
+    const uint32_t* generated = s.history.data() + (s.history.size() - (size_t)s.generated);
+    apply_penalties(row, vocab, s.history.data(), (int64_t)s.history.size(), rq.repetition_penalty, generated, s.generated,
+                    rq.presence_penalty, rq.frequency_penalty);
+    if (rq.temperature <= 0.f) return (uint32_t)argmax_first(row, vocab);
+    // temperature / top-k / top-p (sampling.rs:145-169,337-390).  The draw uses this library's own
+    // counter-based generator: the reference's ChaCha8 stream is a third-party detail that is not
+    // restated, so stochastic sampling is not token-comparable with the reference.
+    std::vector<float> values(row, row + vocab);
+    for (float& v : values) v /= rq.temperature;
+    std::vector<int> ranked((size_t)vocab);
+    std::iota(ranked.begin(), ranked.end(), 0);
+    auto desc = [&](int a, int b) {
+        int ka = float_total_key(values[(size_t)a]), kb = float_total_key(values[(size_t)b]);
+        return ka != kb ? ka > kb : a < b;
+    };
+    std::sort(ranked.begin(), ranked.end(), desc);
+    if (rq.top_k > 0 && rq.top_k < vocab) {
+        for (size_t i = (size_t)rq.top_k; i < ranked.size(); ++i) values[(size_t)ranked[i]] = -INFINITY;
+        ranked.resize((size_t)rq.top_k);
+    }
+    float mx = -INFINITY;
+    for (float v : values) mx = std::max(mx, v);
+    std::vector<float> prob((size_t)vocab);
+    float sum = 0.f;
+    for (int i = 0; i < vocab; ++i) { prob[(size_t)i] = std::exp(values[(size_t)i] - mx); sum += prob[(size_t)i]; }
+    if (!(sum > 0.f) || !std::isfinite(sum)) throw std::runtime_error("sampling distribution is empty");
+    for (float& p : prob) p /= sum;
+    std::sort(ranked.begin(), ranked.end(), [&](int a, int b) {
+        int ka = float_total_key(prob[(size_t)a]), kb = float_total_key(prob[(size_t)b]);
+        return ka != kb ? ka > kb : a < b;
+    });
+    if (rq.top_p < 1.f) {
+        float cumulative = 0.f;
+        size_t keep = 0;
+        for (int idx : ranked) {
+            cumulative += prob[(size_t)idx];
+            ++keep;
+            if (cumulative >= rq.top_p) break;
+        }
+        for (size_t i = keep; i < ranked.size(); ++i) prob[(size_t)ranked[i]] = 0.f;
+    }
+    float total = 0.f;
+    for (float p : prob) total += p;
+    float u = (float)(next_u64(s.rng) >> 40) * (1.0f / 16777216.0f);
+    float target = u * total, cumulative = 0.f;
+    for (int i = 0; i < vocab; ++i) {
+        if (prob[(size_t)i] <= 0.f) continue;
+        cumulative += prob[(size_t)i];
+        if (target < cumulative) return (uint32_t)i;
+    }
+    return (uint32_t)argmax_first(prob.data(), vocab);
+}
+
+int Engine::step() {  // drive_once, engine.rs:1938-1964
+    try_admit_available();
+    if (active_.empty()) return 0;
+    if (round_visits_remaining_ == 0 || round_budget_remaining_ == 0) {
+        round_visits_remaining_ = (int)active_.size();
+        round_budget_remaining_ = cfg_.scheduler_token_budget;
+    }
+
+    // ---- collect_visits (engine.rs:2005-2095)
+    const int visit_limit = std::min(round_visits_remaining_, (int)active_.size());
+    std::vector<Visit> actions;
+    int token_budget = round_budget_remaining_;
+    for (int index = 0; index < visit_limit; ++index) {
+        if (token_budget == 0) break;
+        Sequence& s = *active_[(size_t)index];
+        Visit v;
+        if (s.delivering) {
+            v.kind = Visit::Remove;
+            actions.push_back(v);
+            continue;
+        }
+        const int step_budget = std::min(cfg_.prefill_token_quantum, token_budget);
+        // GenerationCore::preview (generation.rs:876-943)
+        if (s.phase == Phase::Finished || s.req.max_new_tokens == 0) {
+            v.kind = Visit::Complete;
+            v.finished = true;
+            actions.push_back(v);
+            continue;
+        }
+        if (s.phase == Phase::Failed) throw std::runtime_error("generation sequence cannot resume after a failed step");
+        if (s.phase == Phase::Prefill) {
+            int remaining = s.prompt_tokens - s.cursor;
+            if (remaining <= 0) throw std::runtime_error("generation prefill cursor is already complete");
+            v.start_pos = s.cursor;
+            v.n_tokens = std::min(remaining, step_budget);
+            v.was_prefill = true;
+        } else {
+            v.start_pos = s.prompt_tokens + std::max(s.generated - 1, 0);
+            v.n_tokens = 1;
+        }
+        if (s.session->logical_len != v.start_pos)
+            throw std::runtime_error("generation session cache length " + std::to_string(s.session->logical_len) +
+                                     " does not match expected position " + std::to_string(v.start_pos));
+        v.kind = Visit::Preview;
+        token_budget -= v.n_tokens;
+        actions.push_back(v);
+    }
+    const int visits = (int)actions.size();
+    for (int i = 0; i < visits; ++i)  // reclaim_collected_removals (engine.rs:1995-2003)
+        if (actions[(size_t)i].kind == Visit::Remove) reclaim(*active_[(size_t)i]);
+
+    // ---- reserve_and_prepare_visits (engine.rs:2097-2167)
+    std::vector<int> candidates;
+    for (int i = 0; i < visits; ++i)
+        if (actions[(size_t)i].kind == Visit::Preview) candidates.push_back(i);
+    std::unique_ptr<LmReservation> reservation;
+    int input_tokens = 0;
+    size_t selected = candidates.size();
+    if (!candidates.empty()) {
+        for (;;) {
+            std::vector<LmLane> lanes;
+            for (size_t c = 0; c < selected; ++c) {
+                Sequence& s = *active_[(size_t)candidates[c]];
+                const Visit& v = actions[(size_t)candidates[c]];
+                lanes.push_back(LmLane{s.session.get(), nullptr, v.n_tokens, v.start_pos});
+            }
+            try {
+                reservation = model_.reserve_batch(lanes);
+                break;
+            } catch (const KvPoolExhausted& e) {
+                if (selected > 1) {  // drop the LAST candidate and retry (engine.rs:2145-2149)
+                    --selected;
+                    ++stats_.kv_shrinks;
+                    continue;
+                }
+                // one irreducible lane fails only that request (fail_kv_exhausted_visit, engine.rs:2205-2231)
+                for (int idx : candidates) actions[(size_t)idx].kind = Visit::Keep;
+                Sequence& s = *active_[(size_t)candidates[0]];
+                fail_request(s.id, e.what());
+                s.delivering = true;
+                reclaim(s);
+                selected = 0;
+                break;
+            }
+        }
+        for (size_t c = selected; c < candidates.size(); ++c) actions[(size_t)candidates[c]].kind = Visit::Keep;
+        // prepare_reserved_visits (engine.rs:2169-2203): GenerationCore::prepare (generation.rs:1003-1102)
+        for (size_t c = 0; c < selected; ++c) {
+            Visit& v = actions[(size_t)candidates[c]];
+            Sequence& s = *active_[(size_t)candidates[c]];
+            v.ready_to_sample = !v.was_prefill || v.start_pos + v.n_tokens == s.prompt_tokens;
+            v.kind = Visit::Forward;
+            input_tokens += v.n_tokens;
+        }
+    }
+
+    // ---- execute_prepared_visits (engine.rs:2233-2269)
+    int lane_count = 0;
+    for (const Visit& v : actions) lane_count += v.kind == Visit::Forward;
+    if (lane_count > 0) {
+        std::vector<LmLane> lanes;
+        std::vector<TickLaneTrace> tick;
+        bool device_greedy = !cfg_.host_sampling && !cfg_.record_logits;
+        for (int i = 0; i < visits; ++i) {
+            const Visit& v = actions[(size_t)i];
+            if (v.kind != Visit::Forward) continue;
+            Sequence& s = *active_[(size_t)i];
+            const uint32_t* ids = v.was_prefill ? s.history.data() + v.start_pos : &s.decode_token;
+            lanes.push_back(LmLane{s.session.get(), ids, v.n_tokens, v.start_pos});
+            tick.push_back(TickLaneTrace{s.id, v.start_pos, v.n_tokens});
+            const EngineRequest& rq = s.req;
+            if (v.ready_to_sample && (rq.temperature > 0.f || std::fabs(rq.repetition_penalty - 1.f) >= 1.1920929e-07f ||
+                                      rq.presence_penalty != 0.f || rq.frequency_penalty != 0.f))
+                device_greedy = false;
+            if (v.was_prefill) stats_.prefill_tokens += v.n_tokens; else stats_.decode_tokens += v.n_tokens;
+        }
+        uint32_t flags = device_greedy ? FWD_WANT_TOKENS : FWD_WANT_LOGITS;
+        model_.forward_batch_reserved(lanes, std::move(reservation), flags);
+        // validate every lane's cache length BEFORE sampling (engine.rs:2258-2265)
+        for (const LmLane& l : lanes)
+            if (l.session->logical_len != (int64_t)l.start_pos + l.n_tokens)
+                throw std::runtime_error("model advanced generation cache to an unexpected length");
+        // complete_mixed_forward (engine.rs:2378-2409): the completion barrier
+        const int vocab = model_.spec().vocab;
+        if (device_greedy) {
+            tokens_host_.resize((size_t)lane_count);
+            model_.read_output(nullptr, tokens_host_.data());
+        } else {
+            logits_host_.resize((size_t)lane_count * vocab);
+            model_.read_output(logits_host_.data(), nullptr);
+        }
+        stats_.device_ms += model_.last_forward_ms();
+        ++stats_.ticks;
+        trace_.push_back(std::move(tick));
+        // complete_mixed_rows (engine.rs:2411-2523)
+        int row = 0;
+        for (int i = 0; i < visits; ++i) {
+            Visit& v = actions[(size_t)i];
+            if (v.kind != Visit::Forward) continue;
+            Sequence& s = *active_[(size_t)i];
+            const int next_cache_len = v.start_pos + v.n_tokens;
+            // publish after every completed prefill chunk that ends inside the prompt, before sampling
+            // (generation.rs:505-509,768-773)
+            if (s.req.publish_prompt_prefix && v.was_prefill && next_cache_len > 0 && next_cache_len <= s.prompt_tokens)
+                model_.publish_prompt_prefix(*s.session, s.history.data(), (size_t)next_cache_len);
+            v.kind = Visit::Complete;
+            v.finished = false;
+            // GenerationCore::complete (generation.rs:1159-1266)
+            if (!v.ready_to_sample) {
+                s.phase = Phase::Prefill;
+                s.cursor = next_cache_len;
+                ++row;
+                continue;
+            }
+            uint32_t token;
+            if (device_greedy) {
+                token = tokens_host_[(size_t)row];
+            } else {
+                float* lrow = logits_host_.data() + (size_t)row * vocab;
+                if (cfg_.record_logits) {
+                    EngineResult& r = results_[s.id];
+                    r.logits.insert(r.logits.end(), lrow, lrow + vocab);
+                    ++r.logit_rows;
+                }
+                token = sample(s, lrow);
+            }
+            ++row;
+            EngineResult& res = results_[s.id];
+            const std::vector<uint32_t>& stops = model_.spec().stop_ids;
+            if (!s.req.ignore_stop_tokens && std::find(stops.begin(), stops.end(), token) != stops.end()) {
+                s.phase = Phase::Finished;
+                res.finish_reason = "stop";
+                v.finished = true;
+                continue;
+            }
+            bool reaches_budget = s.generated + 1 == s.req.max_new_tokens;
+            ++s.generated;
+            s.history.push_back(token);
+            res.tokens.push_back(token);
+            if (reaches_budget) {
+                s.phase = Phase::Finished;
+                res.finish_reason = "length";
+                v.finished = true;
+                continue;
+            }
+            s.phase = Phase::Decode;
+            s.decode_token = token;
+        }
+    } else {
+        reservation.reset();
+    }
+
+    // ---- finalize_visits (engine.rs:2525-2614)
+    for (int i = 0; i < visits; ++i) {
+        Visit& v = actions[(size_t)i];
+        Sequence& s = *active_[(size_t)i];
+        if (v.kind == Visit::Complete) {
+            if (v.finished) {  // apply_slot_step with final metrics (engine.rs:2618-2671)
+                EngineResult& res = results_[s.id];
+                if (res.state == FinishState::Running) {
+                    res.state = FinishState::Done;
+                    if (res.finish_reason.empty()) res.finish_reason = "length";
+                    ++stats_.completed;
+                }
+                reclaim(s);
+                s.delivering = true;
+            }
+            v.kind = Visit::Keep;
+        }
+    }
+    for (int i = 0; i < visits; ++i) {
+        Visit& v = actions[(size_t)i];
+        Sequence& s = *active_[(size_t)i];
+        if (v.kind == Visit::Remove) continue;
+        // events drain immediately here, so a delivering slot leaves in the same tick
+        if (s.delivering) { reclaim(s); v.kind = Visit::Remove; }
+    }
+    for (int i = 0; i < visits; ++i) {
+        std::unique_ptr<Sequence> slot = std::move(active_.front());
+        active_.pop_front();
+        if (actions[(size_t)i].kind == Visit::Remove) {
+            if (!slot->reclaimed) throw std::runtime_error("removed slot has no reclaimed session");
+            sessions_.push_back(std::move(slot->reclaimed));
+        } else {
+            active_.push_back(std::move(slot));
+        }
+    }
+    round_visits_remaining_ -= visits;
+    round_budget_remaining_ -= input_tokens;
+    if (active_.empty()) {
+        round_visits_remaining_ = 0;
+        round_budget_remaining_ = 0;
+    }
+    return lane_count;
+}
+
+void Engine::run() {
+    int idle = 0;
+    while (pending() > 0) {
+        int lanes = step();
+        idle = lanes > 0 ? 0 : idle + 1;
+        if (idle > 4 * (cfg_.max_active_sequences + 4)) throw std::runtime_error("scheduler made no progress");
+    }
+}
+
+}  // namespace mk

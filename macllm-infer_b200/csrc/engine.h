@@ -1,0 +1,125 @@
+// The continuous-batching engine: FIFO admission (with atomic batches), the round-robin scheduler
+// tick with its token budget and prefill quantum, KV-pressure batch shrinking, and the per-sequence
+// prefill/decode phase machine.  Restates ServingScheduler (src/engine.rs:1578-2770) and
+// GenerationCore (src/generation.rs:787-1266) of the reference, minus the HTTP-facing event plumbing:
+// results are collected per request instead of streamed.
+#pragma once
+#include "paged_lm.h"
+#include <deque>
+#include <map>
+#include <memory>
+#include <vector>
+
+namespace mk {
+
+struct EngineConfig {  // src/engine.rs:309-384
+    int max_active_sequences = 2;
+    int scheduler_token_budget = 256;
+    int prefill_token_quantum = 128;
+    int queue_capacity = 8;
+    bool record_logits = false;
+    bool host_sampling = false;
+};
+
+struct EngineRequest {
+    std::vector<uint32_t> prompt;
+    int max_new_tokens = 0;
+    bool ignore_stop_tokens = false;
+    float temperature = 0.f;
+    int top_k = 0;
+    float top_p = 1.f;
+    float repetition_penalty = 1.f, presence_penalty = 0.f, frequency_penalty = 0.f;
+    uint64_t seed = 0;
+    bool publish_prompt_prefix = true;
+};
+
+enum class FinishState : int { Running = 0, Done = 1, Failed = 2 };
+
+struct EngineResult {
+    std::vector<uint32_t> tokens;
+    FinishState state = FinishState::Running;
+    std::string message;        // failure message
+    std::string finish_reason;  // "length", "stop"
+    int64_t cached_tokens = 0;
+    std::vector<float> logits;  // record_logits: one row per sampled position
+    int logit_rows = 0;
+};
+
+struct TickLaneTrace {
+    int32_t request_id, start_pos, n_tokens;
+};
+
+struct EngineStats {
+    int64_t ticks = 0, prefill_tokens = 0, decode_tokens = 0, completed = 0, failed = 0, kv_shrinks = 0;
+    double device_ms = 0.0;
+};
+
+class Engine {
+public:
+    Engine(PagedLm& model, const EngineConfig& cfg);
+    ~Engine();
+
+    // EngineHandle::submit / submit_batch: returns request ids.  An atomic batch is admitted only when
+    // every member fits into the active set at once.  Throws when the queue is full.
+    std::vector<int> submit(const std::vector<EngineRequest>& reqs, bool atomic_batch);
+    // ServingScheduler::drive_once.  Returns the number of lanes of the packed forward (0 when none ran).
+    int step();
+    void run();
+    int pending() const { return (int)(queue_.size() + pending_atomic_.size() + active_.size()); }
+    const EngineResult& result(int id) const;
+    const std::vector<std::vector<TickLaneTrace>>& trace() const { return trace_; }
+    const EngineStats& stats() const { return stats_; }
+
+private:
+    enum class Phase { Prefill, Decode, Finished, Failed };
+    struct Job {
+        int id;
+        EngineRequest req;
+        int batch = -1;       // atomic batch id
+        int batch_size = 0;
+    };
+    struct Sequence {
+        int id = 0;
+        EngineRequest req;
+        std::unique_ptr<LmSession> session;
+        std::unique_ptr<LmSession> reclaimed;
+        std::vector<uint32_t> history;
+        int prompt_tokens = 0;
+        Phase phase = Phase::Prefill;
+        int cursor = 0;
+        uint32_t decode_token = 0;
+        int generated = 0;
+        bool delivering = false;
+        uint64_t rng = 0;
+    };
+    struct Visit {
+        enum Kind { Keep, Remove, Preview, Forward, Complete } kind = Keep;
+        int start_pos = 0, n_tokens = 0;
+        bool ready_to_sample = false;
+        bool was_prefill = false;
+        bool finished = false;  // Complete: the step carried final metrics
+    };
+
+    bool try_admit_available();
+    bool admit_pending_atomic();
+    void admit(Job job);
+    void fail_request(int id, const std::string& message);
+    void reclaim(Sequence& s);
+    uint32_t sample(Sequence& s, float* row);
+
+    PagedLm& model_;
+    EngineConfig cfg_;
+    std::deque<Job> queue_;
+    std::vector<Job> pending_atomic_;
+    std::deque<std::unique_ptr<Sequence>> active_;
+    std::vector<std::unique_ptr<LmSession>> sessions_;
+    std::map<int, EngineResult> results_;
+    std::vector<std::vector<TickLaneTrace>> trace_;
+    EngineStats stats_;
+    int next_id_ = 0, next_batch_ = 0;
+    int round_visits_remaining_ = 0, round_budget_remaining_ = 0;
+    std::vector<float> logits_host_;
+    std::vector<uint32_t> tokens_host_;
+};
+
+}  // namespace mk

@@ -1,0 +1,52 @@
+// Minimal GGUF v3 reader (memory-mapped): metadata key/values and tensor descriptors.
+// Format facts follow the reference's loader (src/gguf.rs:32-46,2155-2220): little-endian, default
+// alignment 32, dims stored innermost-first, tensor data contiguous after the aligned header.
+#pragma once
+#include <cstdint>
+#include <map>
+#include <string>
+#include <variant>
+#include <vector>
+
+namespace mk {
+
+struct GgufTensor {
+    std::string name;
+    std::vector<int64_t> dims;  // logical order: outermost first (reversed from the file)
+    int type = 0;
+    uint64_t offset = 0;        // from the start of the data section
+    const uint8_t* data = nullptr;
+    int64_t elements() const { int64_t n = 1; for (int64_t d : dims) n *= d; return n; }
+};
+
+struct GgufValue {
+    std::variant<std::monostate, int64_t, double, bool, std::string, std::vector<int64_t>, std::vector<double>, std::vector<std::string>> v;
+};
+
+class GgufFile {
+public:
+    explicit GgufFile(const std::string& path);
+    ~GgufFile();
+    GgufFile(const GgufFile&) = delete;
+    GgufFile& operator=(const GgufFile&) = delete;
+
+    bool has(const std::string& key) const { return meta_.count(key) != 0; }
+    int64_t get_int(const std::string& key) const;
+    int64_t get_int_or(const std::string& key, int64_t def) const { return has(key) ? get_int(key) : def; }
+    double get_float(const std::string& key) const;
+    double get_float_or(const std::string& key, double def) const { return has(key) ? get_float(key) : def; }
+    std::string get_string(const std::string& key) const;
+    const GgufTensor* tensor(const std::string& name) const;
+    const GgufTensor& require(const std::string& name) const;
+    const std::vector<GgufTensor>& tensors() const { return tensors_; }
+    int64_t array_len(const std::string& key) const;
+
+private:
+    void* map_ = nullptr;
+    size_t map_len_ = 0;
+    std::map<std::string, GgufValue> meta_;
+    std::vector<GgufTensor> tensors_;
+    std::map<std::string, size_t> by_name_;
+};
+
+}  // namespace mk

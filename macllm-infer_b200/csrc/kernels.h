@@ -36,6 +36,11 @@ void launch_actmul_quant(const float* gate, const float* up, int ld, int T, int 
 // against 8-bit activation blocks (CUDA-core path, any T; best for T <= 8).
 void launch_qgemv(const QWeight& W, const ActQ& x, int T, float* y, int ldy, float out_scale, float softcap,
                   cudaStream_t s);
+// Expert-grouped form: W holds `experts` matrices of W.rows x W.cols back to back; output rows
+// [offsets[e], offsets[e+1]) are computed with expert e's matrix.  Output row p reads activation row
+// src_row[p] (identity when src_row is null).
+void launch_qgemv_grouped(const QWeight& W, int experts, const int32_t* offsets, const int32_t* src_row, const ActQ& x,
+                          float* y, int ldy, cudaStream_t s);
 // F32 weight matrix (MoE router): y[t][n] = sum_k x[t][k] W[n][k], f32 activations.
 void launch_f32_gemv(const float* W, int out, int in, const float* x, int T, float* y, cudaStream_t s);
 
@@ -115,6 +120,15 @@ void launch_argmax(const float* logits, int B, int vocab, uint32_t* out, cudaStr
 // Top-k routing with (logit desc, index asc) order and softmax over the selected k.
 void launch_moe_route(const float* logits, int T, int experts, int k, int32_t* sel_experts, float* sel_weights,
                       cudaStream_t s);
+
+// Groups the (token, choice) pairs of a routed batch by expert: offsets [experts+1], pos_of_pair [T*k],
+// token_of_pos [T*k] (the activation row each grouped position reads).
+void launch_moe_group(const int32_t* sel_experts, int T, int k, int experts, int32_t* offsets, int32_t* pos_of_pair,
+                      int32_t* token_of_pos, cudaStream_t s);
+// out[t] = sum over the token's k choices in ascending expert order of weight * expert_out[pos]
+// (the index_add order of SparseMoeFeedForward::forward, src/decoder.rs:424-439).
+void launch_moe_combine(const float* expert_out, const int32_t* sel_experts, const float* sel_weights,
+                        const int32_t* pos_of_pair, int T, int k, int hidden, float* out, cudaStream_t s);
 
 // Small helpers
 void launch_add_inplace(float* h, const float* a, float scale, int64_t n, cudaStream_t s);

@@ -1,0 +1,601 @@
+// See model.h.  Line references are into the reference's sources.
+#include "model.h"
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+namespace mk {
+
+namespace {
+
+bool starts_with(const std::string& s, const std::string& p) { return s.compare(0, p.size(), p) == 0; }
+
+}  // namespace
+
+ModelSpec model_spec_from_gguf(const GgufFile& f) {
+    ModelSpec s;
+    s.arch = f.get_string("general.architecture");
+    const std::string a = s.arch;
+    if (a != "llama" && a != "smollm3" && a != "qwen3" && a != "qwen3moe" && a != "gemma2")
+        throw std::runtime_error("GGUF architecture `" + a + "` is not supported on this path");
+    s.layers = (int)f.get_int(a + ".block_count");
+    s.hidden = (int)f.get_int(a + ".embedding_length");
+    s.q_heads = (int)f.get_int(a + ".attention.head_count");
+    s.kv_heads = (int)f.get_int_or(a + ".attention.head_count_kv", s.q_heads);
+    s.head_dim = (int)f.get_int_or(a + ".attention.key_length", s.hidden / s.q_heads);
+    if (f.has(a + ".attention.value_length") && f.get_int(a + ".attention.value_length") != s.head_dim)
+        throw std::runtime_error("different key/value head widths are not supported");
+    s.ffn = (int)f.get_int_or(a + ".feed_forward_length", 0);
+    s.eps = (float)f.get_float(a + ".attention.layer_norm_rms_epsilon");
+    s.max_context = (int)f.get_int(a + ".context_length");
+    if (s.max_context <= 0 || s.max_context > (1 << 20)) throw std::runtime_error("GGUF context length is out of range");  // gguf_model.rs:63
+    const GgufTensor& emb = f.require("token_embd.weight");
+    s.vocab = (int)f.get_int_or(a + ".vocab_size", emb.dims[0]);
+    if (emb.dims.size() != 2 || emb.dims[0] != s.vocab || emb.dims[1] != s.hidden)
+        throw std::runtime_error("token_embd.weight shape does not match the model spec");
+    s.tied = f.tensor("output.weight") == nullptr;  // gguf.rs:1203-1210
+    s.rotary_dim = (int)f.get_int_or(a + ".rope.dimension_count", s.head_dim);
+    double theta = f.get_float_or(a + ".rope.freq_base", 10000.0);
+    s.permute_qk = (a == "llama" || a == "smollm3");  // gguf_model.rs:454-460
+    if (a == "smollm3" && s.layers != 36 && !f.has("macllm.allow_scaled_layers"))
+        throw std::runtime_error("GGUF SmolLM3 must have exactly 36 layers");  // gguf_model.rs:2251-2254
+    if (a == "qwen3moe") {
+        s.experts = (int)f.get_int("qwen3moe.expert_count");
+        s.experts_used = (int)f.get_int("qwen3moe.expert_used_count");
+        s.expert_ffn = (int)f.get_int("qwen3moe.expert_feed_forward_length");
+    }
+    if (a == "gemma2") {
+        if (!s.tied) throw std::runtime_error("Gemma 2 requires a tied output head and does not support `output.weight`");
+        s.embedding_scale = (float)std::sqrt((double)s.hidden);  // gguf_model.rs:1345
+        s.final_softcap = (float)f.get_float_or("gemma2.final_logit_softcapping", 0.0);
+        s.rotary_dim = s.head_dim;
+    }
+    s.layer.resize((size_t)s.layers);
+    for (int l = 0; l < s.layers; ++l) {
+        LayerSpec& ls = s.layer[(size_t)l];
+        ls.theta = theta;
+        ls.scale = (float)(1.0 / std::sqrt((double)s.head_dim));
+        ls.qk_norm = (a == "qwen3" || a == "qwen3moe");
+        ls.moe = (a == "qwen3moe");
+        if (a == "smollm3") ls.rope = ((l + 1) % 4) != 0;  // gguf_model.rs:2313-2324
+        if (a == "gemma2") {                                 // gguf_model.rs:1400-1461
+            int window = (int)f.get_int_or("gemma2.attention.sliding_window", 4096);
+            ls.sliding = (l % 2 == 0);                       // gguf_model.rs:1491-1494
+            ls.window = ls.sliding ? window : 0;
+            ls.theta = ls.sliding ? f.get_float_or("gemma2.rope.freq_base_swa", theta) : theta;
+            ls.softcap = (float)f.get_float("gemma2.attn_logit_softcapping");
+            ls.act = 1;
+            ls.sandwich = true;
+            if (s.layers == 46) ls.scale = (float)(1.0 / std::sqrt((double)(s.hidden / s.q_heads)));
+        }
+    }
+    return s;
+}
+
+// ---------------------------------------------------------------------------- load
+
+Model::Model(const std::string& gguf_path, const ModelConfig& cfg) : cfg_(cfg) {
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev <= 0) {
+        cudaGetLastError();
+        throw std::runtime_error("no usable CUDA device: this library has no CPU fallback");
+    }
+    if (cfg.device < 0 || cfg.device >= ndev) throw std::runtime_error("device ordinal out of range");
+    MK_CUDA(cudaSetDevice(cfg.device));
+    GgufFile f(gguf_path);
+    ms_ = model_spec_from_gguf(f);
+    if (ms_.head_dim > 256 || ms_.head_dim % 4 != 0) throw std::runtime_error("head_dim must be a multiple of 4, at most 256");
+    spec_.vocab = ms_.vocab;
+    spec_.max_context = ms_.max_context;
+    spec_.layers = ms_.layers;
+    spec_.hidden = ms_.hidden;
+    if (f.has("tokenizer.ggml.eos_token_id")) spec_.stop_ids.push_back((uint32_t)f.get_int("tokenizer.ggml.eos_token_id"));
+    bool any_sliding = false;
+    for (const LayerSpec& l : ms_.layer) any_sliding |= l.sliding;
+    init_pool(cfg.block_tokens, cfg.slab_blocks, cfg.kv_capacity_tokens, cfg.prefix_capacity_tokens, !any_sliding);
+
+    MK_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+    MK_CUDA(cudaEventCreate(&ev_start_));
+    MK_CUDA(cudaEventCreate(&ev_stop_));
+    load_weights(f);
+
+    const int64_t esz = cfg.kv_f16 ? 2 : 4;
+    const int64_t block_elems = (int64_t)ms_.layers * ms_.kv_heads * cfg.block_tokens * ms_.head_dim;
+    const int64_t pool_bytes = pool_->max_blocks() * block_elems * esz;
+    k_pool_.alloc((size_t)pool_bytes);
+    v_pool_.alloc((size_t)pool_bytes);
+    k_pool_.zero(stream_);
+    v_pool_.zero(stream_);
+    spec_.kv_bytes_per_token = 2 * (int64_t)ms_.layers * ms_.kv_heads * ms_.head_dim * esz;
+
+    const int T = cfg.max_batch_tokens, B = cfg.max_batch_lanes;
+    const int AW = ms_.q_heads * ms_.head_dim, KW = ms_.kv_heads * ms_.head_dim;
+    const int aw = std::max(ms_.hidden, AW);
+    const bool moe = ms_.experts > 0;
+    const int64_t P = moe ? (int64_t)T * ms_.experts_used : 0;
+    const int fw = moe ? ms_.expert_ffn : ms_.ffn;
+    const int64_t frows = moe ? P : T;
+    cu_.alloc((size_t)(B + 1) * 4);
+    pos_.alloc((size_t)T * 4);
+    tok_lane_.alloc((size_t)T * 4);
+    slots_.alloc((size_t)T * 8);
+    last_.alloc((size_t)B * 4);
+    tile_lane_.alloc((size_t)(T + B) * 4);
+    tile_row_.alloc((size_t)(T + B) * 4);
+    ntiles_.alloc(4);
+    err_.alloc(4);
+    err_.zero(stream_);
+    h_.alloc((size_t)T * ms_.hidden * 4);
+    q_.alloc((size_t)T * AW * 4);
+    k_.alloc((size_t)T * KW * 4);
+    v_.alloc((size_t)T * KW * 4);
+    attn_.alloc((size_t)T * AW * 4);
+    proj_.alloc((size_t)T * ms_.hidden * 4);
+    down_.alloc((size_t)T * ms_.hidden * 4);
+    if (!moe) {
+        gate_.alloc((size_t)T * ms_.ffn * 4);
+        up_.alloc((size_t)T * ms_.ffn * 4);
+    } else {
+        normed_.alloc((size_t)T * ms_.hidden * 4);
+        router_logits_.alloc((size_t)T * ms_.experts * 4);
+        sel_e_.alloc((size_t)P * 4);
+        sel_w_.alloc((size_t)P * 4);
+        grp_off_.alloc((size_t)(ms_.experts + 1) * 4);
+        pos_of_pair_.alloc((size_t)P * 4);
+        tok_of_pos_.alloc((size_t)P * 4);
+        e_gate_.alloc((size_t)P * fw * 4);
+        e_up_.alloc((size_t)P * fw * 4);
+        e_down_.alloc((size_t)P * ms_.hidden * 4);
+    }
+    logits_.alloc((size_t)B * ms_.vocab * 4);
+    tokens_.alloc((size_t)B * 4);
+    a_qs_.alloc((size_t)T * aw);
+    a_d_.alloc((size_t)T * (aw / 32 + 1) * 4);
+    a_bs_.alloc((size_t)T * (aw / 16 + 1) * 2);
+    a_xh_.alloc((size_t)T * aw * 2);
+    f_qs_.alloc((size_t)frows * fw);
+    f_d_.alloc((size_t)frows * (fw / 32 + 1) * 4);
+    f_bs_.alloc((size_t)frows * (fw / 16 + 1) * 2);
+    f_xh_.alloc((size_t)frows * fw * 2);
+    l_qs_.alloc((size_t)B * ms_.hidden);
+    l_d_.alloc((size_t)B * (ms_.hidden / 32 + 1) * 4);
+    l_bs_.alloc((size_t)B * (ms_.hidden / 16 + 1) * 2);
+    l_xh_.alloc((size_t)B * ms_.hidden * 2);
+    tc_ws_.status.alloc(4);
+    tc_ws_.status.zero(stream_);
+    // the largest split-K scratch any matmul of this model can ask for
+    size_t partial = 0;
+    auto consider = [&](const QWeight& w, int rows_t) {
+        if (w.type == QT_Q4_K || w.type == QT_Q6_K || w.type == QT_Q8_0)
+            for (int t : {9, 32, 64, 128, rows_t}) if (t <= rows_t && t > 0) partial = std::max(partial, qgemm_tc_partial_floats(w, t));
+    };
+    for (const LayerWeights& lw : lw_) {
+        consider(lw.wq.w, T); consider(lw.wk.w, T); consider(lw.wv.w, T); consider(lw.wo.w, T);
+        if (!moe) { consider(lw.gate.w, T); consider(lw.up.w, T); consider(lw.down.w, T); }
+    }
+    consider(ms_.tied ? token_embd_.w : output_.w, B);
+    tc_ws_.partial.alloc(std::max<size_t>(partial, 1) * 4);
+    size_t stage_bytes = (size_t)B * sizeof(LaneHeader) + (size_t)(pool_->max_blocks() + B) * 4 + (size_t)T * 4 + 64;
+    stage_host_.ensure(stage_bytes);
+    stage_dev_.alloc(stage_bytes);
+    out_host_.ensure((size_t)B * ms_.vocab * 4 + (size_t)B * 4 + 16);
+    MK_CUDA(cudaStreamSynchronize(stream_));
+}
+
+Model::~Model() {
+    if (stream_) cudaStreamSynchronize(stream_);
+    if (ev_start_) cudaEventDestroy(ev_start_);
+    if (ev_stop_) cudaEventDestroy(ev_stop_);
+    if (stream_) cudaStreamDestroy(stream_);
+}
+
+void Model::upload_f32(const GgufFile& f, const std::string& name, int64_t n, DevBuf& out) {
+    const GgufTensor& t = f.require(name);
+    if (t.type != QT_F32 || t.elements() != n) throw std::runtime_error("tensor `" + name + "` must be F32 with " + std::to_string(n) + " elements");
+    out.upload(t.data, (size_t)n * 4, stream_);
+    MK_CUDA(cudaStreamSynchronize(stream_));
+}
+
+void Model::upload_matrix(const GgufFile& f, const std::string& name, int64_t rows, int64_t cols, DeviceWeight& out,
+                          bool permute_heads, int heads) {
+    const GgufTensor& t = f.require(name);
+    int64_t total_rows = t.elements() / t.dims.back();
+    if (t.dims.back() != cols || total_rows != rows)
+        throw std::runtime_error("tensor `" + name + "` has shape that does not match the model spec");  // validate_decoder_tensors, gguf_model.rs:3388-3420
+    if (!permute_heads) {
+        upload_weight(t.type, t.data, rows, cols, out, stream_);
+    } else {
+        // llama.cpp stores Q/K rows pair-interleaved; undo it so the half-split rotation applies
+        // (src/gguf.rs:1888-1924): source row head*d + 2*pair + lane -> dest head*d + lane*d/2 + pair.
+        int64_t rb = gguf_row_bytes(t.type, cols);
+        int d = (int)(rows / heads);
+        std::vector<uint8_t> tmp((size_t)(rb * rows));
+        for (int h = 0; h < heads; ++h)
+            for (int lane = 0; lane < 2; ++lane)
+                for (int pair = 0; pair < d / 2; ++pair)
+                    memcpy(&tmp[(size_t)((h * d + lane * (d / 2) + pair) * rb)], t.data + (int64_t)(h * d + 2 * pair + lane) * rb, (size_t)rb);
+        upload_weight(t.type, tmp.data(), rows, cols, out, stream_);
+    }
+    spec_.weight_bytes += out.w.bytes;
+}
+
+void Model::load_weights(const GgufFile& f) {
+    const int H = ms_.hidden, AW = ms_.q_heads * ms_.head_dim, KW = ms_.kv_heads * ms_.head_dim;
+    upload_matrix(f, "token_embd.weight", ms_.vocab, H, token_embd_, false, 0);
+    if (!ms_.tied) upload_matrix(f, "output.weight", ms_.vocab, H, output_, false, 0);
+    upload_f32(f, "output_norm.weight", H, output_norm_);
+    int64_t per_token = (ms_.tied ? token_embd_.w.bytes : output_.w.bytes);
+    lw_.resize((size_t)ms_.layers);
+    for (int l = 0; l < ms_.layers; ++l) {
+        LayerWeights& w = lw_[(size_t)l];
+        const LayerSpec& ls = ms_.layer[(size_t)l];
+        std::string p = "blk." + std::to_string(l) + ".";
+        upload_f32(f, p + "attn_norm.weight", H, w.attn_norm);
+        upload_matrix(f, p + "attn_q.weight", AW, H, w.wq, ms_.permute_qk, ms_.q_heads);
+        upload_matrix(f, p + "attn_k.weight", KW, H, w.wk, ms_.permute_qk, ms_.kv_heads);
+        upload_matrix(f, p + "attn_v.weight", KW, H, w.wv, false, 0);
+        upload_matrix(f, p + "attn_output.weight", H, AW, w.wo, false, 0);
+        per_token += w.wq.w.bytes + w.wk.w.bytes + w.wv.w.bytes + w.wo.w.bytes;
+        if (ls.qk_norm) {
+            upload_f32(f, p + "attn_q_norm.weight", ms_.head_dim, w.q_norm);
+            upload_f32(f, p + "attn_k_norm.weight", ms_.head_dim, w.k_norm);
+        }
+        upload_f32(f, p + "ffn_norm.weight", H, w.ffn_norm);
+        if (ls.sandwich) {
+            upload_f32(f, p + "post_attention_norm.weight", H, w.post_attn_norm);
+            upload_f32(f, p + "post_ffw_norm.weight", H, w.post_ffn_norm);
+        }
+        if (!ls.moe) {
+            upload_matrix(f, p + "ffn_gate.weight", ms_.ffn, H, w.gate, false, 0);
+            upload_matrix(f, p + "ffn_up.weight", ms_.ffn, H, w.up, false, 0);
+            upload_matrix(f, p + "ffn_down.weight", H, ms_.ffn, w.down, false, 0);
+            per_token += w.gate.w.bytes + w.up.w.bytes + w.down.w.bytes;
+        } else {
+            const int E = ms_.experts, F = ms_.expert_ffn;
+            upload_f32(f, p + "ffn_gate_inp.weight", (int64_t)E * H, w.router);
+            upload_matrix(f, p + "ffn_gate_exps.weight", (int64_t)E * F, H, w.gate, false, 0);
+            upload_matrix(f, p + "ffn_up_exps.weight", (int64_t)E * F, H, w.up, false, 0);
+            upload_matrix(f, p + "ffn_down_exps.weight", (int64_t)E * H, F, w.down, false, 0);
+            per_token += (w.gate.w.bytes + w.up.w.bytes + w.down.w.bytes) / E * ms_.experts_used + (int64_t)E * H * 4;
+            // the grouped kernels address one expert's matrix at a time
+            w.gate.w.rows = F;
+            w.up.w.rows = F;
+            w.down.w.rows = H;
+        }
+    }
+    spec_.weight_bytes_per_token = per_token;
+}
+
+void Model::rope_tables_for(double theta, const float*& cos_t, const float*& sin_t) {
+    for (auto& r : rope_)
+        if (r->theta == theta) { cos_t = r->cos_t.as<float>(); sin_t = r->sin_t.as<float>(); return; }
+    // RotaryEmbedding::new / tables (src/decoder.rs:136-201): inverse frequencies in f64 then f32,
+    // angle = f32(position) * inv_freq, cos/sin in f32.
+    int half = ms_.rotary_dim / 2;
+    int64_t capacity = std::min<int64_t>(ms_.max_context, std::max<int64_t>(pool_->max_blocks() * pool_->block_tokens(), 256));
+    std::vector<float> inv((size_t)half), c((size_t)(capacity * half)), s((size_t)(capacity * half));
+    for (int i = 0; i < half; ++i) inv[(size_t)i] = (float)(1.0 / std::pow(theta, (double)(2 * i) / (double)ms_.rotary_dim));
+    for (int64_t p = 0; p < capacity; ++p)
+        for (int i = 0; i < half; ++i) {
+            float a = (float)p * inv[(size_t)i];
+            c[(size_t)(p * half + i)] = cosf(a);
+            s[(size_t)(p * half + i)] = sinf(a);
+        }
+    auto t = std::make_unique<RopeTable>();
+    t->theta = theta;
+    t->cos_t.upload(c.data(), c.size() * 4, stream_);
+    t->sin_t.upload(s.data(), s.size() * 4, stream_);
+    MK_CUDA(cudaStreamSynchronize(stream_));
+    cos_t = t->cos_t.as<float>();
+    sin_t = t->sin_t.as<float>();
+    rope_.push_back(std::move(t));
+}
+
+// ---------------------------------------------------------------------------- forward
+
+bool Model::tensor_path(const QWeight& W, int T) const {
+    if (cfg_.matmul_path == 1) return false;
+    if (W.type != QT_Q4_K && W.type != QT_Q6_K && W.type != QT_Q8_0) return false;
+    if (W.cols % 256 != 0) return false;
+    return cfg_.matmul_path == 2 ? true : T > 8;
+}
+
+ActQ Model::act_view(DevBuf& qs, DevBuf& d, DevBuf& bs, DevBuf& xh, int, int, int, bool want_f16) {
+    ActQ a;
+    a.qs = qs.as<int8_t>();
+    a.d = d.as<float>();
+    a.bsums = bs.as<int16_t>();
+    a.xh = want_f16 ? xh.as<__half>() : nullptr;
+    return a;
+}
+
+void Model::matmul(const QWeight& W, const ActQ& x, int T, float* y, int ldy, float scale, float softcap) {
+    if (tensor_path(W, T) && x.xh != nullptr) {
+        size_t need = qgemm_tc_partial_floats(W, T);
+        tc_ws_.partial.ensure(need * 4);
+        launch_qgemm_tc_scratch(W, x, T, y, ldy, scale, softcap, tc_ws_.partial.as<float>(), tc_ws_.status.as<int32_t>(), stream_);
+        launches_ += need > 0 ? 2 : 1;
+    } else {
+        launch_qgemv(W, x, T, y, ldy, scale, softcap, stream_);
+        ++launches_;
+    }
+}
+
+static int act_kind_of(const QWeight& w) { return w.type == QT_Q8_0 ? ACT_Q80 : ACT_Q8K; }
+
+void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint32_t flags) {
+    MK_CUDA(cudaSetDevice(cfg_.device));
+    const int B = (int)lanes.size();
+    int T = 0;
+    for (const LmLane& l : lanes) T += l.n_tokens;
+    if (B > cfg_.max_batch_lanes) throw std::runtime_error("batch has more lanes than max_batch_lanes");
+    if (T > cfg_.max_batch_tokens) throw std::runtime_error("batch has more tokens than max_batch_tokens");
+    const int H = ms_.hidden, AW = ms_.q_heads * ms_.head_dim, KW = ms_.kv_heads * ms_.head_dim, d = ms_.head_dim;
+    const int bt = pool_->block_tokens();
+    const int q_tile = attention_q_tile(ms_.q_heads, ms_.kv_heads);
+
+    // ---- stage the per-lane headers, block tables and token ids in one pinned buffer, one copy
+    uint8_t* hp = stage_host_.as<uint8_t>();
+    LaneHeader* hdr = reinterpret_cast<LaneHeader*>(hp);
+    size_t off_tables = (size_t)B * sizeof(LaneHeader);
+    uint32_t* tab = reinterpret_cast<uint32_t*>(hp + off_tables);
+    int n_tab = 0, tiles = 0;
+    for (int i = 0; i < B; ++i) {
+        const std::vector<KvBlockId>& blocks = r.lane_blocks((size_t)i);
+        hdr[i].start_pos = lanes[(size_t)i].start_pos;
+        hdr[i].n_tokens = lanes[(size_t)i].n_tokens;
+        hdr[i].table_off = n_tab;
+        hdr[i].n_blocks = (int32_t)blocks.size();
+        for (const KvBlockId& b : blocks) tab[n_tab++] = b.slot;
+        tiles += (lanes[(size_t)i].n_tokens + q_tile - 1) / q_tile;
+    }
+    size_t off_ids = off_tables + (size_t)n_tab * 4;
+    uint32_t* ids = reinterpret_cast<uint32_t*>(hp + off_ids);
+    int tpos = 0;
+    for (const LmLane& l : lanes) {
+        memcpy(ids + tpos, l.ids, (size_t)l.n_tokens * 4);
+        tpos += l.n_tokens;
+    }
+    size_t stage_bytes = off_ids + (size_t)T * 4;
+    if (stage_bytes > stage_dev_.size()) throw std::runtime_error("tick staging buffer is too small");
+    MK_CUDA(cudaEventRecord(ev_start_, stream_));
+    MK_CUDA(cudaMemcpyAsync(stage_dev_.ptr(), hp, stage_bytes, cudaMemcpyHostToDevice, stream_));
+    uint8_t* dp = stage_dev_.as<uint8_t>();
+
+    BatchDesc bd;
+    bd.lanes = B;
+    bd.T = T;
+    bd.max_tiles = tiles;
+    bd.hdr = reinterpret_cast<const LaneHeader*>(dp);
+    bd.tables = reinterpret_cast<const uint32_t*>(dp + off_tables);
+    bd.cu_seqlens = cu_.as<int32_t>();
+    bd.positions = pos_.as<int32_t>();
+    bd.token_lane = tok_lane_.as<int32_t>();
+    bd.slots = slots_.as<int64_t>();
+    bd.last_index = last_.as<int32_t>();
+    bd.tile_lane = tile_lane_.as<int32_t>();
+    bd.tile_row0 = tile_row_.as<int32_t>();
+    bd.n_tiles = ntiles_.as<int32_t>();
+    bd.error_flag = err_.as<int32_t>();
+    launch_build_batch(bd, bt, q_tile, stream_);
+    ++launches_;
+    const uint32_t* ids_dev = reinterpret_cast<const uint32_t*>(dp + off_ids);
+
+    // ---- copy-on-write page copies of shared partial tails (cache.rs:3042-3089)
+    for (const KvCowCopy& c : r.cow_copies()) {
+        launch_cow_copy(k_pool_.ptr(), v_pool_.ptr(), cfg_.kv_f16 ? 1 : 0, c.src_slot, c.dst_slot, c.rows, ms_.layers, ms_.kv_heads, bt,
+                        d, stream_);
+        ++launches_;
+    }
+
+    // ---- embedding (src/decoder.rs:3194-3197)
+    launch_embed(token_embd_.w, ids_dev, T, ms_.embedding_scale, h_.as<float>(), stream_);
+    ++launches_;
+
+    const bool f16_T = cfg_.matmul_path != 1 && (cfg_.matmul_path == 2 || T > 8);
+    const float* pending = nullptr;        // branch output not yet added to the residual stream
+    const float* pending_post = nullptr;   // its sandwich post-norm weight, if any
+    for (int l = 0; l < ms_.layers; ++l) {
+        LayerWeights& w = lw_[(size_t)l];
+        const LayerSpec& ls = ms_.layer[(size_t)l];
+        // residual add of the previous layer's FFN + attention norm + quantise
+        int kind = act_kind_of(w.wq.w);
+        ActQ xa = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, H, kind, f16_T);
+        NormQuantArgs na;
+        na.h = h_.as<float>();
+        na.a = pending;
+        na.post_w = pending_post;
+        na.norm_w = w.attn_norm.as<float>();
+        na.eps = ms_.eps;
+        na.rows = T;
+        na.dim = H;
+        na.act_kind = kind;
+        na.out = xa;
+        launch_add_norm_quant(na, stream_);
+        ++launches_;
+        // projections (src/decoder.rs:1099-1161)
+        matmul(w.wq.w, xa, T, q_.as<float>(), AW, 1.f, 0.f);
+        matmul(w.wk.w, xa, T, k_.as<float>(), KW, 1.f, 0.f);
+        matmul(w.wv.w, xa, T, v_.as<float>(), KW, 1.f, 0.f);
+        // per-head norms, rotation, paged write
+        RopeKvArgs ra;
+        ra.q = q_.as<float>();
+        ra.k = k_.as<float>();
+        ra.v = v_.as<float>();
+        ra.ldq = AW;
+        ra.ldk = ra.ldv = KW;
+        if (ls.qk_norm) { ra.q_norm_w = w.q_norm.as<float>(); ra.k_norm_w = w.k_norm.as<float>(); }
+        ra.norm_eps = ms_.eps;
+        if (ls.rope) { rope_tables_for(ls.theta, ra.cos_t, ra.sin_t); ra.rotary_dim = ms_.rotary_dim; }
+        ra.positions = bd.positions;
+        ra.slots = bd.slots;
+        ra.k_pool = k_pool_.ptr();
+        ra.v_pool = v_pool_.ptr();
+        ra.kv_f16 = cfg_.kv_f16 ? 1 : 0;
+        ra.T = T;
+        ra.q_heads = ms_.q_heads;
+        ra.kv_heads = ms_.kv_heads;
+        ra.d = d;
+        ra.block_tokens = bt;
+        ra.layers = ms_.layers;
+        ra.layer = l;
+        launch_rope_kv(ra, stream_);
+        ++launches_;
+        AttnArgs at;
+        at.q = q_.as<float>();
+        at.out = attn_.as<float>();
+        at.k_pool = k_pool_.ptr();
+        at.v_pool = v_pool_.ptr();
+        at.kv_f16 = ra.kv_f16;
+        at.batch = bd;
+        at.q_heads = ms_.q_heads;
+        at.kv_heads = ms_.kv_heads;
+        at.d = d;
+        at.block_tokens = bt;
+        at.layers = ms_.layers;
+        at.layer = l;
+        at.scale = ls.scale;
+        at.softcap = ls.softcap;
+        at.window = ls.window;
+        at.q_tile = q_tile;
+        launch_paged_attention(at, stream_);
+        ++launches_;
+        // output projection
+        int okind = act_kind_of(w.wo.w);
+        ActQ xo = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, AW, okind, f16_T);
+        NormQuantArgs no;
+        no.h = attn_.as<float>();
+        no.rows = T;
+        no.dim = AW;
+        no.act_kind = okind;
+        no.out = xo;
+        launch_add_norm_quant(no, stream_);
+        ++launches_;
+        matmul(w.wo.w, xo, T, proj_.as<float>(), H, 1.f, 0.f);
+        // residual add + FFN norm + quantise (finish_mixer, src/decoder.rs:2684-2699)
+        int fkind = act_kind_of(w.gate.w);
+        ActQ xf = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, H, fkind, f16_T);
+        NormQuantArgs nf;
+        nf.h = h_.as<float>();
+        nf.a = proj_.as<float>();
+        nf.post_w = ls.sandwich ? w.post_attn_norm.as<float>() : nullptr;
+        nf.norm_w = w.ffn_norm.as<float>();
+        nf.eps = ms_.eps;
+        nf.rows = T;
+        nf.dim = H;
+        nf.act_kind = fkind;
+        nf.out = xf;
+        nf.normed_out = ls.moe ? normed_.as<float>() : nullptr;
+        launch_add_norm_quant(nf, stream_);
+        ++launches_;
+        if (!ls.moe) {
+            // dense feed-forward (src/decoder.rs:298-305)
+            matmul(w.gate.w, xf, T, gate_.as<float>(), ms_.ffn, 1.f, 0.f);
+            matmul(w.up.w, xf, T, up_.as<float>(), ms_.ffn, 1.f, 0.f);
+            int dkind = act_kind_of(w.down.w);
+            ActQ xd = act_view(f_qs_, f_d_, f_bs_, f_xh_, T, ms_.ffn, dkind, f16_T);
+            launch_actmul_quant(gate_.as<float>(), up_.as<float>(), ms_.ffn, T, ms_.ffn, ls.act, dkind, xd, nullptr, stream_);
+            ++launches_;
+            matmul(w.down.w, xd, T, down_.as<float>(), H, 1.f, 0.f);
+        } else {
+            // sparse MoE (src/decoder.rs:394-554)
+            const int E = ms_.experts, K = ms_.experts_used, F = ms_.expert_ffn, P = T * K;
+            launch_f32_gemv(w.router.as<float>(), E, H, normed_.as<float>(), T, router_logits_.as<float>(), stream_);
+            launch_moe_route(router_logits_.as<float>(), T, E, K, sel_e_.as<int32_t>(), sel_w_.as<float>(), stream_);
+            launch_moe_group(sel_e_.as<int32_t>(), T, K, E, grp_off_.as<int32_t>(), pos_of_pair_.as<int32_t>(), tok_of_pos_.as<int32_t>(),
+                             stream_);
+            ActQ xq = xf;
+            xq.xh = nullptr;
+            launch_qgemv_grouped(w.gate.w, E, grp_off_.as<int32_t>(), tok_of_pos_.as<int32_t>(), xq, e_gate_.as<float>(), F, stream_);
+            launch_qgemv_grouped(w.up.w, E, grp_off_.as<int32_t>(), tok_of_pos_.as<int32_t>(), xq, e_up_.as<float>(), F, stream_);
+            int dkind = act_kind_of(w.down.w);
+            ActQ xd = act_view(f_qs_, f_d_, f_bs_, f_xh_, P, F, dkind, false);
+            launch_actmul_quant(e_gate_.as<float>(), e_up_.as<float>(), F, P, F, ls.act, dkind, xd, nullptr, stream_);
+            launch_qgemv_grouped(w.down.w, E, grp_off_.as<int32_t>(), nullptr, xd, e_down_.as<float>(), H, stream_);
+            launch_moe_combine(e_down_.as<float>(), sel_e_.as<int32_t>(), sel_w_.as<float>(), pos_of_pair_.as<int32_t>(), T, K, H,
+                               down_.as<float>(), stream_);
+            launches_ += 8;
+        }
+        pending = down_.as<float>();
+        pending_post = ls.sandwich ? w.post_ffn_norm.as<float>() : nullptr;
+    }
+    // last residual add
+    {
+        NormQuantArgs nl;
+        nl.h = h_.as<float>();
+        nl.a = pending;
+        nl.post_w = pending_post;
+        nl.eps = ms_.eps;
+        nl.rows = T;
+        nl.dim = H;
+        launch_add_norm_quant(nl, stream_);
+        ++launches_;
+    }
+    // logits tail (src/decoder.rs:3333-3356): last rows -> final norm -> output projection -> scale -> softcap
+    const QWeight& head = ms_.tied ? token_embd_.w : output_.w;
+    {
+        const bool f16_B = cfg_.matmul_path != 1 && (cfg_.matmul_path == 2 || B > 8);
+        int kind = act_kind_of(head);
+        ActQ xl = act_view(l_qs_, l_d_, l_bs_, l_xh_, B, H, kind, f16_B);
+        NormQuantArgs ng;
+        ng.h = h_.as<float>();
+        ng.norm_w = output_norm_.as<float>();
+        ng.eps = ms_.eps;
+        ng.rows = B;
+        ng.dim = H;
+        ng.row_index = bd.last_index;
+        ng.act_kind = kind;
+        ng.out = xl;
+        launch_add_norm_quant(ng, stream_);
+        ++launches_;
+        matmul(head, xl, B, logits_.as<float>(), ms_.vocab, ms_.final_logit_scale, ms_.final_softcap);
+    }
+    if (flags & FWD_WANT_TOKENS) {
+        launch_argmax(logits_.as<float>(), B, ms_.vocab, tokens_.as<uint32_t>(), stream_);
+        ++launches_;
+    }
+    // results travel to pinned host memory on the same stream; the barrier is in fetch_output
+    uint8_t* oh = out_host_.as<uint8_t>();
+    size_t tok_off = (size_t)B * ms_.vocab * 4;
+    if (flags & FWD_WANT_LOGITS) MK_CUDA(cudaMemcpyAsync(oh, logits_.ptr(), tok_off, cudaMemcpyDeviceToHost, stream_));
+    if (flags & FWD_WANT_TOKENS) MK_CUDA(cudaMemcpyAsync(oh + tok_off, tokens_.ptr(), (size_t)B * 4, cudaMemcpyDeviceToHost, stream_));
+    MK_CUDA(cudaMemcpyAsync(oh + tok_off + (size_t)B * 4, err_.ptr(), 4, cudaMemcpyDeviceToHost, stream_));
+    MK_CUDA(cudaMemcpyAsync(oh + tok_off + (size_t)B * 4 + 4, tc_ws_.status.ptr(), 4, cudaMemcpyDeviceToHost, stream_));
+    MK_CUDA(cudaEventRecord(ev_stop_, stream_));
+    timed_ = true;
+    out_lanes_ = B;
+    out_flags_ = flags;
+}
+
+void Model::fetch_output(float* logits, uint32_t* tokens) {
+    MK_CUDA(cudaStreamSynchronize(stream_));
+    const int B = out_lanes_;
+    uint8_t* oh = out_host_.as<uint8_t>();
+    size_t tok_off = (size_t)B * ms_.vocab * 4;
+    int32_t flags[2];
+    memcpy(flags, oh + tok_off + (size_t)B * 4, 8);
+    if (flags[0] != 0) throw std::runtime_error("batch descriptor index out of range on the device (flag " + std::to_string(flags[0]) + ")");
+    if (flags[1] != 0) throw std::runtime_error("a bounded wait inside the tensor-core matmul gave up (status " + std::to_string(flags[1]) + ")");
+    if (logits) {
+        if (!(out_flags_ & FWD_WANT_LOGITS)) throw std::runtime_error("logits were not requested for this forward");
+        memcpy(logits, oh, tok_off);
+    }
+    if (tokens) {
+        if (!(out_flags_ & FWD_WANT_TOKENS)) throw std::runtime_error("tokens were not requested for this forward");
+        memcpy(tokens, oh + tok_off, (size_t)B * 4);
+    }
+}
+
+void Model::device_synchronize() { MK_CUDA(cudaStreamSynchronize(stream_)); }
+
+float Model::last_forward_ms() const {
+    if (!timed_) return 0.f;
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, ev_start_, ev_stop_) != cudaSuccess) {
+        cudaGetLastError();
+        return 0.f;
+    }
+    return ms;
+}
+
+}  // namespace mk

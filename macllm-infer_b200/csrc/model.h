@@ -1,0 +1,107 @@
+// The decoder on the B200: GGUF weights resident in HBM in the layouts the kernels read, one
+// contiguous paged K/V arena, and the per-tick graph of kernel launches on one CUDA stream.
+// Mirrors DecoderModel of the reference (src/decoder.rs: load :2980-3105, forward_inner_batch
+// :3146-3358) for the attention-only families llama, smollm3, qwen3, qwen3moe and gemma2.
+#pragma once
+#include "device_util.h"
+#include "gguf_file.h"
+#include "kernels.h"
+#include "paged_lm.h"
+#include "qgemm_tc.h"
+
+namespace mk {
+
+struct LayerSpec {
+    bool sliding = false;
+    int window = 0;
+    bool rope = true;
+    double theta = 10000.0;
+    bool qk_norm = false;
+    int act = 0;           // 0 SiLU, 1 tanh-GELU
+    bool sandwich = false; // Gemma-style post norms
+    bool moe = false;
+    float scale = 1.f;
+    float softcap = 0.f;
+};
+
+struct ModelSpec {
+    std::string arch;
+    int vocab = 0, max_context = 0, layers = 0, hidden = 0, q_heads = 0, kv_heads = 0, head_dim = 0, ffn = 0, rotary_dim = 0;
+    float eps = 1e-5f, embedding_scale = 1.f, final_logit_scale = 1.f, final_softcap = 0.f;
+    bool tied = false, permute_qk = false;
+    int experts = 0, experts_used = 0, expert_ffn = 0;
+    std::vector<LayerSpec> layer;
+};
+
+// Reads the family spec from GGUF metadata (the reference's src/gguf_model.rs:1298-1461,1816-2533).
+ModelSpec model_spec_from_gguf(const GgufFile& f);
+
+struct ModelConfig {
+    int device = 0;
+    int block_tokens = 16, slab_blocks = 8;
+    int64_t kv_capacity_tokens = 4096, prefix_capacity_tokens = 0;
+    bool kv_f16 = true;
+    int max_batch_tokens = 2048, max_batch_lanes = 64;
+    int matmul_path = 0;  // 0 auto, 1 integer GEMV only, 2 tensor cores whenever the shape allows
+};
+
+class Model : public PagedLm {
+public:
+    Model(const std::string& gguf_path, const ModelConfig& cfg);
+    ~Model() override;
+
+    const ModelSpec& model_spec() const { return ms_; }
+    float last_forward_ms() const override;
+    int64_t launch_count() const override { return launches_; }
+
+protected:
+    void run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint32_t flags) override;
+    void fetch_output(float* logits, uint32_t* tokens) override;
+    void device_synchronize() override;
+
+private:
+    struct LayerWeights {
+        DevBuf attn_norm, ffn_norm, post_attn_norm, post_ffn_norm, q_norm, k_norm, router;
+        DeviceWeight wq, wk, wv, wo, gate, up, down;  // dense FFN, or expert banks for MoE layers
+    };
+    void load_weights(const GgufFile& f);
+    void upload_matrix(const GgufFile& f, const std::string& name, int64_t rows, int64_t cols, DeviceWeight& out, bool permute_heads,
+                       int heads);
+    void upload_f32(const GgufFile& f, const std::string& name, int64_t n, DevBuf& out);
+    void matmul(const QWeight& W, const ActQ& x, int T, float* y, int ldy, float scale, float softcap);
+    ActQ act_view(DevBuf& qs, DevBuf& d, DevBuf& bs, DevBuf& xh, int T, int dim, int kind, bool want_f16);
+    bool tensor_path(const QWeight& W, int T) const;
+    void rope_tables_for(double theta, const float*& cos_t, const float*& sin_t);
+
+    ModelSpec ms_;
+    ModelConfig cfg_;
+    cudaStream_t stream_ = nullptr;
+    cudaEvent_t ev_start_ = nullptr, ev_stop_ = nullptr;
+    bool timed_ = false;
+    int64_t launches_ = 0;
+
+    std::vector<LayerWeights> lw_;
+    DeviceWeight token_embd_, output_;
+    DevBuf output_norm_;
+    struct RopeTable { double theta; DevBuf cos_t, sin_t; };
+    std::vector<std::unique_ptr<RopeTable>> rope_;
+
+    DevBuf k_pool_, v_pool_;
+    // per-tick staging
+    PinnedBuf stage_host_;
+    DevBuf stage_dev_;
+    DevBuf cu_, pos_, tok_lane_, slots_, last_, tile_lane_, tile_row_, ntiles_, err_;
+    // activations
+    DevBuf h_, q_, k_, v_, attn_, proj_, gate_, up_, down_, normed_, logits_, tokens_;
+    DevBuf a_qs_, a_d_, a_bs_, a_xh_;   // quantised activations of width hidden / attention width
+    DevBuf f_qs_, f_d_, f_bs_, f_xh_;   // quantised activations of width ffn
+    DevBuf l_qs_, l_d_, l_bs_, l_xh_;   // last-token rows for the output projection
+    // MoE
+    DevBuf router_logits_, sel_e_, sel_w_, grp_off_, pos_of_pair_, tok_of_pos_, e_gate_, e_up_, e_down_;
+    QgemmWorkspace tc_ws_;
+    PinnedBuf out_host_;
+    int out_lanes_ = 0;
+    uint32_t out_flags_ = 0;
+};
+
+}  // namespace mk

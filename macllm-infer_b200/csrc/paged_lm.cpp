@@ -1,0 +1,190 @@
+// See paged_lm.h.  Line references are into the reference's src/decoder.rs unless noted.
+#include "paged_lm.h"
+#include <algorithm>
+
+namespace mk {
+
+void PagedLm::init_pool(int block_tokens, int slab_blocks, int64_t capacity_tokens, int64_t prefix_capacity_tokens,
+                        bool allow_prefix_cache) {
+    if (block_tokens <= 0 || slab_blocks <= 0 || capacity_tokens <= 0)
+        throw std::runtime_error("KV pool configuration must be positive");
+    int64_t max_blocks = (capacity_tokens + block_tokens - 1) / block_tokens;  // src/runtime.rs:194
+    pool_ = std::make_shared<KvPool>(block_tokens, slab_blocks, max_blocks);
+    if (prefix_capacity_tokens > 0) {
+        if (!allow_prefix_cache)  // :4352-4372: rejected for models with a sliding-window layer
+            throw std::runtime_error("the automatic prefix cache is not supported for models with sliding-window layers");
+        int64_t budget = std::min((prefix_capacity_tokens + block_tokens - 1) / block_tokens, max_blocks);  // :3403-3412
+        prefix_cache_ = std::make_unique<TokenPrefixCache<Snapshot>>((size_t)block_tokens, (size_t)budget);
+    }
+}
+
+std::unique_ptr<LmSession> PagedLm::new_session() {  // :3433-3477
+    auto s = std::make_unique<LmSession>();
+    s->owner = this;
+    s->table = std::make_unique<KvTable>(pool_, spec_.max_context);
+    return s;
+}
+
+void PagedLm::validate_session(const LmSession& s) const {  // :3479-3492
+    if (s.owner != this) throw std::runtime_error("decoder session belongs to a different model instance");
+}
+
+void PagedLm::clear_session(LmSession& s) {  // :3804-3818
+    int64_t old_len = s.table->logical_len();
+    s.table->clear();
+    if (old_len != 0 && s.table->logical_len() != 0) return;  // a reservation keeps the table locked
+    s.logical_len = 0;
+}
+
+int64_t PagedLm::reset_session_for_prompt(LmSession& s, const uint32_t* tokens, size_t n) {  // :3494-3532
+    validate_session(s);
+    clear_session(s);
+    if (s.logical_len != 0 || s.table->logical_len() != 0)
+        throw std::runtime_error("decoder session did not become empty before prompt admission");
+    if (!prefix_cache_) return 0;
+    auto hit = prefix_cache_->lookup_aligned_common_prefix(tokens, n, n);
+    if (!hit) return 0;
+    s.table->attach_prefix(**hit->snapshot, (int64_t)hit->matched_tokens);  // restore_into
+    s.logical_len = (int64_t)hit->matched_tokens;
+    return s.logical_len;
+}
+
+void PagedLm::publish_prompt_prefix(LmSession& s, const uint32_t* tokens, size_t n) {  // :3534-3603
+    if (!prefix_cache_ || s.owner != this) return;
+    size_t bt = prefix_cache_->block_tokens();
+    size_t snapshot_tokens = n / bt * bt;
+    if (snapshot_tokens == 0 || (size_t)s.logical_len < snapshot_tokens) return;
+    Snapshot fork;
+    try {
+        fork = s.table->fork_prefix((int64_t)snapshot_tokens);
+    } catch (...) {
+        return;
+    }
+    size_t cost = std::max<size_t>((size_t)fork->owned_blocks(), 1);
+    std::vector<uint32_t> key(tokens, tokens + snapshot_tokens);
+    prefix_cache_->insert(std::move(key), std::move(fork), cost);
+}
+
+std::optional<LmPrefixDiagnostics> PagedLm::prefix_diagnostics() const {  // :3605-3632
+    if (!prefix_cache_) return std::nullopt;
+    PrefixCacheStats st = prefix_cache_->stats();
+    LmPrefixDiagnostics d;
+    d.entries = (int64_t)st.entries;
+    d.cached_blocks = (int64_t)st.cost;
+    d.capacity_blocks = (int64_t)st.max_cost;
+    d.hits = (int64_t)st.hits;
+    d.misses = (int64_t)st.misses;
+    d.matched_tokens = (int64_t)st.matched_tokens;
+    d.insertions = (int64_t)st.insertions;
+    d.evictions = (int64_t)st.evictions;
+    return d;
+}
+
+std::unique_ptr<LmReservation> PagedLm::reserve_batch(const std::vector<LmLane>& lanes) {  // :3696-3758
+    if (lanes.empty()) throw std::runtime_error("paged KV reservation batch cannot be empty");
+    std::vector<KvTable*> tables;
+    std::vector<int64_t> counts;
+    auto r = std::make_unique<LmReservation>();
+    r->owner = this;
+    for (const LmLane& l : lanes) {
+        if (l.session == nullptr) throw std::runtime_error("reservation lane has no session");
+        validate_session(*l.session);
+        if (l.n_tokens <= 0) throw std::runtime_error("input sequence cannot be empty");  // validate_session_geometry :3878-3899
+        if (l.session->logical_len != l.start_pos)
+            throw std::runtime_error("start_pos " + std::to_string(l.start_pos) + " does not match decoder sequence length " +
+                                     std::to_string(l.session->logical_len));
+        if (l.session->table->logical_len() != l.session->logical_len)
+            throw std::runtime_error("decoder session block table disagrees with its sequence length");
+        tables.push_back(l.session->table.get());
+        counts.push_back(l.n_tokens);
+        r->sessions.push_back(l.session);
+        r->start_pos.push_back(l.start_pos);
+        r->n_tokens.push_back(l.n_tokens);
+    }
+    for (;;) {
+        try {
+            r->paged = pool_->reserve_batch(tables, counts);
+            break;
+        } catch (const KvPoolExhausted&) {
+            if (!prefix_cache_) throw;
+            auto evicted = prefix_cache_->evict_lru();  // dropping the snapshot releases its pages
+            if (!evicted) throw;
+        }
+    }
+    return r;
+}
+
+void PagedLm::forward_batch_reserved(const std::vector<LmLane>& lanes, std::unique_ptr<LmReservation> reservation,
+                                     uint32_t flags) {  // :4203-4269, :4125-4201
+    if (lanes.empty()) throw std::runtime_error("mixed-sequence batch cannot be empty");
+    if (!reservation || reservation->owner != this || !reservation->paged)
+        throw std::runtime_error("forward needs a KV reservation made by this model");
+    if (reservation->sessions.size() != lanes.size())
+        throw std::runtime_error("KV reservation covers " + std::to_string(reservation->sessions.size()) + " lanes, forward has " +
+                                 std::to_string(lanes.size()));
+    for (size_t i = 0; i < lanes.size(); ++i) {
+        const LmLane& l = lanes[i];
+        if (l.session == nullptr || l.ids == nullptr) throw std::runtime_error("forward lane is missing its session or tokens");
+        validate_session(*l.session);
+        if (l.n_tokens <= 0) throw std::runtime_error("input sequence cannot be empty");
+        for (int t = 0; t < l.n_tokens; ++t)
+            if ((int64_t)l.ids[t] >= spec_.vocab) throw std::runtime_error("input contains a token ID outside the model vocabulary");
+        if (l.session->logical_len != l.start_pos)
+            throw std::runtime_error("start_pos " + std::to_string(l.start_pos) + " does not match decoder sequence length " +
+                                     std::to_string(l.session->logical_len));
+        if (reservation->sessions[i] != l.session || reservation->start_pos[i] != l.start_pos ||
+            reservation->n_tokens[i] != l.n_tokens)
+            throw std::runtime_error("KV reservation lane " + std::to_string(i) + " does not match the forward lane");
+    }
+    KvReservation& paged = *reservation->paged;
+    paged.mark_all_used();
+    run_forward(lanes, paged, flags);  // a throw leaves every session untouched; the reservation rolls back
+    paged.commit();
+    for (const LmLane& l : lanes) l.session->logical_len = (int64_t)l.start_pos + l.n_tokens;
+    last_lanes_ = (int)lanes.size();
+    last_flags_ = flags;
+}
+
+void PagedLm::read_output(float* logits, uint32_t* tokens) {  // :3779-3783
+    fetch_output(logits, tokens);
+    pool_->mark_completed_through(pool_->submitted_epoch());
+}
+
+void PagedLm::synchronize() {  // :3785-3788
+    device_synchronize();
+    pool_->mark_completed_through(pool_->submitted_epoch());
+}
+
+// ---------------------------------------------------------------------------- FakeLm
+
+FakeLm::FakeLm(int vocab, int max_context, int block_tokens, int slab_blocks, int64_t capacity_tokens,
+               int64_t prefix_capacity_tokens) {
+    spec_.vocab = vocab;
+    spec_.max_context = max_context;
+    spec_.layers = 1;
+    spec_.hidden = 1;
+    init_pool(block_tokens, slab_blocks, capacity_tokens, prefix_capacity_tokens, true);
+}
+
+void FakeLm::run_forward(const std::vector<LmLane>& lanes, KvReservation&, uint32_t) {
+    if (forwards_++ == fail_at_) throw std::runtime_error("injected forward failure");
+    next_.clear();
+    for (const LmLane& l : lanes) {
+        uint64_t t = l.ids[l.n_tokens - 1];
+        uint64_t p = (uint64_t)(l.start_pos + l.n_tokens - 1);
+        next_.push_back((uint32_t)((31 * t + 7 * p + 3) % (uint64_t)spec_.vocab));
+    }
+}
+
+void FakeLm::fetch_output(float* logits, uint32_t* tokens) {
+    for (size_t i = 0; i < next_.size(); ++i) {
+        if (tokens) tokens[i] = next_[i];
+        if (logits) {
+            float* row = logits + i * (size_t)spec_.vocab;
+            std::fill(row, row + spec_.vocab, 0.f);
+            row[next_[i]] = 1.f;
+        }
+    }
+}
+
+}  // namespace mk

@@ -1,0 +1,120 @@
+// The model/session/KV-reservation boundary the scheduler talks to, shaped like the reference's
+// CausalLm / CausalLmSession / CausalLmKvReservation traits (src/architecture.rs:803-1246), with the
+// shared host-side glue of the reference's DecoderModel: sessions over one paged KV pool, the
+// exact-token prefix cache (src/decoder.rs:3392-3431,3494-3603) and transactional reservations
+// (src/decoder.rs:3696-3758,4125-4201).  Device work is supplied by the subclass.
+#pragma once
+#include "kv_pool.h"
+#include "prefix_cache.h"
+#include <memory>
+#include <optional>
+#include <string>
+#include <vector>
+
+namespace mk {
+
+class PagedLm;
+
+struct LmSession {
+    PagedLm* owner = nullptr;
+    std::unique_ptr<KvTable> table;
+    int64_t logical_len = 0;
+};
+
+struct LmLane {
+    LmSession* session = nullptr;
+    const uint32_t* ids = nullptr;
+    int32_t n_tokens = 0;
+    int32_t start_pos = 0;
+};
+
+struct LmReservation {
+    PagedLm* owner = nullptr;
+    std::vector<LmSession*> sessions;
+    std::vector<int32_t> start_pos, n_tokens;
+    std::unique_ptr<KvReservation> paged;
+};
+
+struct LmRuntimeSpec {
+    int vocab = 0, max_context = 0, layers = 0, hidden = 0;
+    std::vector<uint32_t> stop_ids;
+    int64_t weight_bytes = 0, weight_bytes_per_token = 0, kv_bytes_per_token = 0;
+};
+
+struct LmPrefixDiagnostics {
+    int64_t entries = 0, cached_blocks = 0, capacity_blocks = 0, hits = 0, misses = 0, matched_tokens = 0, insertions = 0,
+            evictions = 0;
+};
+
+constexpr uint32_t FWD_WANT_LOGITS = 1u, FWD_WANT_TOKENS = 2u;
+
+class PagedLm {
+public:
+    virtual ~PagedLm() = default;
+
+    const LmRuntimeSpec& spec() const { return spec_; }
+    KvPool& pool() { return *pool_; }
+
+    // CausalLm::new_session
+    std::unique_ptr<LmSession> new_session();
+    // CausalLm::reset_session_for_prompt: clears the session, then attaches the longest cached
+    // block-aligned prefix strictly shorter than the prompt.  Returns the cached token count.
+    int64_t reset_session_for_prompt(LmSession& s, const uint32_t* tokens, size_t n);
+    // CausalLm::publish_prompt_prefix: best effort, never fails the request.
+    void publish_prompt_prefix(LmSession& s, const uint32_t* tokens, size_t n);
+    // CausalLmSession::clear_cache
+    void clear_session(LmSession& s);
+    // CausalLm::reserve_batch_kv: host only.  Throws KvPoolExhausted after evicting every prefix
+    // snapshot that could have relieved the pressure.
+    std::unique_ptr<LmReservation> reserve_batch(const std::vector<LmLane>& lanes);
+    // CausalLm::forward_batch_tokens_reserved: validates every lane before any mutation, consumes the
+    // reservation, enqueues the tick and commits the block tables.
+    void forward_batch_reserved(const std::vector<LmLane>& lanes, std::unique_ptr<LmReservation> reservation, uint32_t flags);
+    // CausalLm::read_output_to_cpu: completion barrier; retired pages become free.
+    void read_output(float* logits, uint32_t* tokens);
+    // CausalLm::synchronize
+    void synchronize();
+
+    KvPoolStats pool_stats() const { return pool_->stats(); }
+    std::optional<LmPrefixDiagnostics> prefix_diagnostics() const;
+    int last_lanes() const { return last_lanes_; }
+    virtual float last_forward_ms() const { return 0.f; }
+    virtual int64_t launch_count() const { return 0; }
+    void validate_session(const LmSession& s) const;
+
+protected:
+    void init_pool(int block_tokens, int slab_blocks, int64_t capacity_tokens, int64_t prefix_capacity_tokens, bool allow_prefix_cache);
+    // Enqueue the device work of one tick.  `r` holds the provisional block tables of every lane.
+    virtual void run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint32_t flags) = 0;
+    // Wait for the tick and copy the requested outputs to the host.
+    virtual void fetch_output(float* logits, uint32_t* tokens) = 0;
+    virtual void device_synchronize() {}
+
+    LmRuntimeSpec spec_;
+    std::shared_ptr<KvPool> pool_;
+    using Snapshot = std::unique_ptr<KvTable>;
+    std::unique_ptr<TokenPrefixCache<Snapshot>> prefix_cache_;
+    int last_lanes_ = 0;
+    uint32_t last_flags_ = 0;
+};
+
+// Host-only model with deterministic one-hot logits, used to exercise the scheduler, the KV pool and
+// the prefix cache without a GPU (the role of FakeModel in the reference's tests,
+// src/engine.rs:3107-3300).  The next token after feeding token t at position p is
+// (31 * t + 7 * p + 3) mod vocab.
+class FakeLm : public PagedLm {
+public:
+    FakeLm(int vocab, int max_context, int block_tokens, int slab_blocks, int64_t capacity_tokens, int64_t prefix_capacity_tokens);
+    // Fail the forward numbered `index` (0-based) with an exception, to test rollback.
+    void fail_forward_at(int64_t index) { fail_at_ = index; }
+
+protected:
+    void run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint32_t flags) override;
+    void fetch_output(float* logits, uint32_t* tokens) override;
+
+private:
+    std::vector<uint32_t> next_;
+    int64_t forwards_ = 0, fail_at_ = -1;
+};
+
+}  // namespace mk

@@ -18,6 +18,17 @@ namespace {
 constexpr int GEMV_WARPS = 4;
 constexpr int NT = 8;  // activation rows per pass
 
+// Optional expert grouping: blockIdx.y selects the expert, whose output rows are [offsets[e], offsets[e+1]).
+struct Group {
+    const int32_t* offsets = nullptr;
+    const int32_t* src_row = nullptr;
+};
+__device__ __forceinline__ void group_range(const Group& g, int T, int& t_begin, int& t_end) {
+    if (g.offsets != nullptr) { t_begin = g.offsets[blockIdx.y]; t_end = g.offsets[blockIdx.y + 1]; }
+    else { t_begin = 0; t_end = T; }
+}
+__device__ __forceinline__ int src_of(const Group& g, int t) { return g.src_row != nullptr ? g.src_row[t] : t; }
+
 __device__ __forceinline__ void q4k_scale_min(const uint8_t* s, int j, int& sc, int& mn) {
     if (j < 4) {
         sc = s[j] & 63;
@@ -48,7 +59,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) qgemv_q4k_kernel(const uint8_
                                                                     const float* __restrict__ xd,
                                                                     const int16_t* __restrict__ xbs, int T,
                                                                     float* __restrict__ y, int ldy, float out_scale,
-                                                                    float softcap) {
+                                                                    float softcap, Group grp) {
     int n = blockIdx.x * GEMV_WARPS + (threadIdx.x >> 5);
     if (n >= out) return;
     int lane = threadIdx.x & 31;
@@ -56,9 +67,11 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) qgemv_q4k_kernel(const uint8_
     int j = part >> 1;         // 64-weight chunk
     int h = part & 1;          // half of the chunk's 32 bytes
     const int K = nb * 256;
-    const uint8_t* wrow = W + (int64_t)n * nb * 144;
+    const uint8_t* wrow = W + ((int64_t)blockIdx.y * out + n) * nb * 144;
+    int t_first;
+    group_range(grp, T, t_first, T);
 
-    for (int t0 = 0; t0 < T; t0 += NT) {
+    for (int t0 = t_first; t0 < T; t0 += NT) {
         float acc[NT];
 #pragma unroll
         for (int t = 0; t < NT; ++t) acc[t] = 0.f;
@@ -78,7 +91,8 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) qgemv_q4k_kernel(const uint8_
 #pragma unroll
             for (int t = 0; t < NT; ++t) {
                 if (t < rows) {
-                    const int8_t* xr = xq + (int64_t)(t0 + t) * K + ib * 256 + 64 * j + 16 * h;
+                    const int64_t xrow = src_of(grp, t0 + t);
+                    const int8_t* xr = xq + xrow * K + ib * 256 + 64 * j + 16 * h;
                     int4 xl = *reinterpret_cast<const int4*>(xr);
                     int4 xh = *reinterpret_cast<const int4*>(xr + 32);
                     int s_lo = __dp4a((int)ql[0], xl.x, 0);
@@ -89,10 +103,10 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) qgemv_q4k_kernel(const uint8_
                     s_hi = __dp4a((int)qh[1], xh.y, s_hi);
                     s_hi = __dp4a((int)qh[2], xh.z, s_hi);
                     s_hi = __dp4a((int)qh[3], xh.w, s_hi);
-                    const int16_t* bs = xbs + (int64_t)(t0 + t) * (K / 16) + ib * 16 + 4 * j + h;
+                    const int16_t* bs = xbs + xrow * (K / 16) + ib * 16 + 4 * j + h;
                     int isum = sc_lo * s_lo + sc_hi * s_hi;
                     int msum = m_lo * (int)bs[0] + m_hi * (int)bs[2];
-                    acc[t] += xd[(int64_t)(t0 + t) * nb + ib] * (d * (float)isum - dmin * (float)msum);
+                    acc[t] += xd[xrow * nb + ib] * (d * (float)isum - dmin * (float)msum);
                 }
             }
         }
@@ -108,7 +122,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) qgemv_q6k_kernel(const uint8_
                                                                     const int8_t* __restrict__ xq,
                                                                     const float* __restrict__ xd, int T,
                                                                     float* __restrict__ y, int ldy, float out_scale,
-                                                                    float softcap) {
+                                                                    float softcap, Group grp) {
     int n = blockIdx.x * GEMV_WARPS + (threadIdx.x >> 5);
     if (n >= out) return;
     int lane = threadIdx.x & 31;
@@ -116,9 +130,11 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) qgemv_q6k_kernel(const uint8_
     int half = part >> 2;          // 128-weight half of the block
     int l0 = (part & 3) * 8;       // eight consecutive positions inside the half
     const int K = nb * 256;
-    int64_t row_blk = (int64_t)n * nb;
+    int64_t row_blk = ((int64_t)blockIdx.y * out + n) * nb;
+    int t_first;
+    group_range(grp, T, t_first, T);
 
-    for (int t0 = 0; t0 < T; t0 += NT) {
+    for (int t0 = t_first; t0 < T; t0 += NT) {
         float acc[NT];
 #pragma unroll
         for (int t = 0; t < NT; ++t) acc[t] = 0.f;
@@ -144,7 +160,8 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) qgemv_q6k_kernel(const uint8_
 #pragma unroll
             for (int t = 0; t < NT; ++t) {
                 if (t < rows) {
-                    const int8_t* xr = xq + (int64_t)(t0 + t) * K + ib * 256 + half * 128 + l0;
+                    const int64_t xrow = src_of(grp, t0 + t);
+                    const int8_t* xr = xq + xrow * K + ib * 256 + half * 128 + l0;
                     int2 x0 = *reinterpret_cast<const int2*>(xr);
                     int2 x1 = *reinterpret_cast<const int2*>(xr + 32);
                     int2 x2 = *reinterpret_cast<const int2*>(xr + 64);
@@ -154,7 +171,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) qgemv_q6k_kernel(const uint8_
                     int i2 = __dp4a((int)g[2][1], x2.y, __dp4a((int)g[2][0], x2.x, 0));
                     int i3 = __dp4a((int)g[3][1], x3.y, __dp4a((int)g[3][0], x3.x, 0));
                     int isum = s0 * i0 + s1 * i1 + s2 * i2 + s3 * i3;
-                    acc[t] += xd[(int64_t)(t0 + t) * nb + ib] * (d * (float)isum);
+                    acc[t] += xd[xrow * nb + ib] * (d * (float)isum);
                 }
             }
         }
@@ -168,14 +185,16 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) qgemv_q80_kernel(const int8_t
                                                                     const int8_t* __restrict__ xq,
                                                                     const float* __restrict__ xd, int T,
                                                                     float* __restrict__ y, int ldy, float out_scale,
-                                                                    float softcap) {
+                                                                    float softcap, Group grp) {
     int n = blockIdx.x * GEMV_WARPS + (threadIdx.x >> 5);
     if (n >= out) return;
     int lane = threadIdx.x & 31;
     int nb = K / 32;
-    const int8_t* wq = qs_p + (int64_t)n * K;
-    const __half* wd = d_p + (int64_t)n * nb;
-    for (int t0 = 0; t0 < T; t0 += NT) {
+    const int8_t* wq = qs_p + ((int64_t)blockIdx.y * out + n) * K;
+    const __half* wd = d_p + ((int64_t)blockIdx.y * out + n) * nb;
+    int t_first;
+    group_range(grp, T, t_first, T);
+    for (int t0 = t_first; t0 < T; t0 += NT) {
         float acc[NT];
 #pragma unroll
         for (int t = 0; t < NT; ++t) acc[t] = 0.f;
@@ -187,7 +206,8 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) qgemv_q80_kernel(const int8_t
 #pragma unroll
             for (int t = 0; t < NT; ++t) {
                 if (t < rows) {
-                    const int8_t* xr = xq + (int64_t)(t0 + t) * K + b * 32;
+                    const int64_t xrow = src_of(grp, t0 + t);
+                    const int8_t* xr = xq + xrow * K + b * 32;
                     int4 x0 = *reinterpret_cast<const int4*>(xr);
                     int4 x1 = *reinterpret_cast<const int4*>(xr + 16);
                     int s = __dp4a(w0.x, x0.x, 0);
@@ -198,7 +218,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) qgemv_q80_kernel(const int8_t
                     s = __dp4a(w1.y, x1.y, s);
                     s = __dp4a(w1.z, x1.z, s);
                     s = __dp4a(w1.w, x1.w, s);
-                    acc[t] += (float)s * (d * xd[(int64_t)(t0 + t) * nb + b]);
+                    acc[t] += (float)s * (d * xd[xrow * nb + b]);
                 }
             }
         }
@@ -225,29 +245,43 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) f32_gemv_kernel(const float* 
 
 }  // namespace
 
-void launch_qgemv(const QWeight& W, const ActQ& x, int T, float* y, int ldy, float out_scale, float softcap,
-                  cudaStream_t s) {
-    if (T <= 0 || W.rows <= 0) return;
-    unsigned grid = (unsigned)((W.rows + GEMV_WARPS - 1) / GEMV_WARPS);
+static void launch_qgemv_impl(const QWeight& W, const ActQ& x, int T, float* y, int ldy, float out_scale, float softcap,
+                              int experts, Group grp, cudaStream_t s) {
+    dim3 grid((unsigned)((W.rows + GEMV_WARPS - 1) / GEMV_WARPS), (unsigned)experts);
     switch (W.type) {
         case QT_Q4_K:
             qgemv_q4k_kernel<<<grid, GEMV_WARPS * 32, 0, s>>>((const uint8_t*)W.p0, (int)(W.cols / 256), (int)W.rows, x.qs,
-                                                              x.d, x.bsums, T, y, ldy, out_scale, softcap);
+                                                              x.d, x.bsums, T, y, ldy, out_scale, softcap, grp);
             break;
         case QT_Q6_K:
             qgemv_q6k_kernel<<<grid, GEMV_WARPS * 32, 0, s>>>((const uint8_t*)W.p0, (const uint8_t*)W.p1,
                                                               (const int8_t*)W.p2, (const __half*)W.p3,
                                                               (int)(W.cols / 256), (int)W.rows, x.qs, x.d, T, y, ldy,
-                                                              out_scale, softcap);
+                                                              out_scale, softcap, grp);
             break;
         case QT_Q8_0:
             qgemv_q80_kernel<<<grid, GEMV_WARPS * 32, 0, s>>>((const int8_t*)W.p0, (const __half*)W.p1, (int)W.cols,
-                                                              (int)W.rows, x.qs, x.d, T, y, ldy, out_scale, softcap);
+                                                              (int)W.rows, x.qs, x.d, T, y, ldy, out_scale, softcap, grp);
             break;
         default:
             throw std::runtime_error("launch_qgemv: unsupported weight type");
     }
     MK_LAUNCH_CHECK();
+}
+
+void launch_qgemv(const QWeight& W, const ActQ& x, int T, float* y, int ldy, float out_scale, float softcap,
+                  cudaStream_t s) {
+    if (T <= 0 || W.rows <= 0) return;
+    launch_qgemv_impl(W, x, T, y, ldy, out_scale, softcap, 1, Group{}, s);
+}
+
+void launch_qgemv_grouped(const QWeight& W, int experts, const int32_t* offsets, const int32_t* src_row, const ActQ& x,
+                          float* y, int ldy, cudaStream_t s) {
+    if (experts <= 0 || W.rows <= 0) return;
+    Group g;
+    g.offsets = offsets;
+    g.src_row = src_row;
+    launch_qgemv_impl(W, x, 0, y, ldy, 1.0f, 0.f, experts, g, s);
 }
 
 void launch_f32_gemv(const float* W, int out, int in, const float* x, int T, float* y, cudaStream_t s) {

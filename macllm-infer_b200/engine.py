@@ -1,0 +1,288 @@
+"""Python mirror of the reference's model / session / engine surface over the C ABI.
+
+`Model` follows the CausalLm trait (src/architecture.rs:1038-1246 of the reference): sessions,
+prompt-prefix reset/publish, KV reservation, packed ragged forward, completion barrier.  `Engine`
+follows EngineHandle / ServingScheduler (src/engine.rs): submit requests of raw token ids, drive
+scheduler ticks, read back generated tokens.  Everything runs in libmacllm_b200.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _capi as capi
+
+
+@dataclass
+class Request:
+    prompt: list | np.ndarray
+    max_new_tokens: int
+    ignore_stop_tokens: bool = True
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    repetition_penalty: float = 1.0
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    seed: int = 0
+
+
+class Session:
+    def __init__(self, model: "Model"):
+        self.model = model
+        h = C.c_void_p()
+        capi.check(capi.lib().mk_session_new(model._h, C.byref(h)))
+        self._h = h
+
+    def __len__(self) -> int:
+        n = C.c_int64()
+        capi.check(capi.lib().mk_session_len(self._h, C.byref(n)))
+        return int(n.value)
+
+    def clear(self) -> None:
+        capi.check(capi.lib().mk_session_clear(self._h))
+
+    def block_table(self):
+        cap = 1 << 16
+        slots = np.empty(cap, np.uint32)
+        gens = np.empty(cap, np.uint64)
+        n = C.c_int32(cap)
+        capi.check(capi.lib().mk_session_block_table(self._h, slots.ctypes.data, gens.ctypes.data, C.byref(n)))
+        return slots[: n.value].copy(), gens[: n.value].copy()
+
+    def close(self) -> None:
+        if self._h:
+            capi.lib().mk_session_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Model:
+    """A decoder resident on one GPU (or the host-only fake used for scheduler tests)."""
+
+    def __init__(self, handle, keep=None):
+        self._h = handle
+        self._keep = keep
+
+    @staticmethod
+    def _config(device=0, block_tokens=16, slab_blocks=8, kv_capacity_tokens=4096, prefix_capacity_tokens=0, kv_dtype="f16",
+                max_batch_tokens=2048, max_batch_lanes=64, matmul_path=capi.PATH_AUTO) -> capi.LoadConfig:
+        cfg = capi.LoadConfig()
+        cfg.device_ordinal = device
+        cfg.block_tokens = block_tokens
+        cfg.slab_blocks = slab_blocks
+        cfg.kv_capacity_tokens = kv_capacity_tokens
+        cfg.prefix_capacity_tokens = prefix_capacity_tokens
+        cfg.kv_dtype = capi.TYPE_F16 if kv_dtype == "f16" else capi.TYPE_F32
+        cfg.max_batch_tokens = max_batch_tokens
+        cfg.max_batch_lanes = max_batch_lanes
+        cfg.matmul_path = matmul_path
+        return cfg
+
+    @classmethod
+    def load_gguf(cls, path, **kw) -> "Model":
+        cfg = cls._config(**kw)
+        h = C.c_void_p()
+        capi.check(capi.lib().mk_model_load_gguf(str(path).encode(), C.byref(cfg), C.byref(h)))
+        return cls(h)
+
+    @classmethod
+    def fake(cls, vocab=32, max_context=4096, fail_forward_at=-1, **kw) -> "Model":
+        cfg = cls._config(**kw)
+        h = C.c_void_p()
+        capi.check(capi.lib().mk_model_new_fake(vocab, max_context, C.byref(cfg), fail_forward_at, C.byref(h)))
+        return cls(h)
+
+    def spec(self) -> capi.RuntimeSpec:
+        s = capi.RuntimeSpec()
+        capi.check(capi.lib().mk_model_spec(self._h, C.byref(s)))
+        return s
+
+    def new_session(self) -> Session:
+        return Session(self)
+
+    def reset_session_for_prompt(self, session: Session, tokens) -> int:
+        t = np.ascontiguousarray(tokens, dtype=np.uint32)
+        cached = C.c_int64()
+        capi.check(capi.lib().mk_reset_session_for_prompt(self._h, session._h, t.ctypes.data, len(t), C.byref(cached)))
+        return int(cached.value)
+
+    def publish_prompt_prefix(self, session: Session, tokens) -> None:
+        t = np.ascontiguousarray(tokens, dtype=np.uint32)
+        capi.check(capi.lib().mk_publish_prompt_prefix(self._h, session._h, t.ctypes.data, len(t)))
+
+    def pool_stats(self) -> dict:
+        s = capi.PoolStats()
+        capi.check(capi.lib().mk_pool_stats_query(self._h, C.byref(s)))
+        return s.as_dict()
+
+    def kv_capacity(self) -> dict:
+        c = capi.KvCapacity()
+        capi.check(capi.lib().mk_kv_capacity_query(self._h, C.byref(c)))
+        return {n: getattr(c, n) for n, _ in c._fields_}
+
+    def prefix_diagnostics(self) -> dict:
+        d = capi.PrefixDiagnostics()
+        capi.check(capi.lib().mk_prefix_diagnostics_query(self._h, C.byref(d)))
+        return d.as_dict()
+
+    def _lanes(self, lanes):
+        """lanes: list of (session, token ids, start_pos).  Returns (ctypes array, keep-alive list)."""
+        arr = (capi.Lane * len(lanes))()
+        keep = []
+        for i, (session, ids, start_pos) in enumerate(lanes):
+            t = np.ascontiguousarray(ids, dtype=np.uint32)
+            keep.append(t)
+            arr[i].session = session._h
+            arr[i].input_ids = t.ctypes.data_as(C.POINTER(C.c_uint32))
+            arr[i].n_tokens = len(t)
+            arr[i].start_pos = start_pos
+        return arr, keep
+
+    def forward_batch(self, lanes, want_logits=True, want_tokens=True):
+        """reserve_batch_kv + forward_batch_tokens_reserved + read_output_to_cpu for one packed ragged
+        batch.  Returns (logits [lanes, vocab] or None, tokens [lanes] or None)."""
+        arr, keep = self._lanes(lanes)
+        r = C.c_void_p()
+        capi.check(capi.lib().mk_reserve_batch(self._h, arr, len(lanes), C.byref(r)))
+        flags = (capi.FWD_WANT_LOGITS if want_logits else 0) | (capi.FWD_WANT_TOKENS if want_tokens else 0)
+        capi.check(capi.lib().mk_forward_batch_reserved(self._h, arr, len(lanes), r, flags))
+        vocab = self.spec().vocab_size
+        logits = np.empty((len(lanes), vocab), np.float32) if want_logits else None
+        tokens = np.empty(len(lanes), np.uint32) if want_tokens else None
+        capi.check(capi.lib().mk_read_output(self._h, None if logits is None else logits.ctypes.data,
+                                             None if tokens is None else tokens.ctypes.data))
+        del keep
+        return logits, tokens
+
+    def last_forward_ms(self) -> float:
+        v = C.c_float()
+        capi.check(capi.lib().mk_last_forward_ms(self._h, C.byref(v)))
+        return float(v.value)
+
+    def launch_count(self) -> int:
+        v = C.c_int64()
+        capi.check(capi.lib().mk_launch_count(self._h, C.byref(v)))
+        return int(v.value)
+
+    def synchronize(self) -> None:
+        capi.check(capi.lib().mk_synchronize(self._h))
+
+    def close(self) -> None:
+        if self._h:
+            capi.lib().mk_model_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Engine:
+    """The continuous-batching scheduler over one model."""
+
+    def __init__(self, model: Model, max_active_sequences=2, scheduler_token_budget=256, prefill_token_quantum=128,
+                 queue_capacity=8, record_logits=False, host_sampling=False):
+        self.model = model
+        cfg = capi.EngineConfig(max_active_sequences, scheduler_token_budget, prefill_token_quantum, queue_capacity,
+                                1 if record_logits else 0, 1 if host_sampling else 0)
+        h = C.c_void_p()
+        capi.check(capi.lib().mk_engine_new(model._h, C.byref(cfg), C.byref(h)))
+        self._h = h
+
+    def submit(self, requests, atomic_batch=False) -> list[int]:
+        n = len(requests)
+        arr = (capi.Request * n)()
+        keep = []
+        for i, r in enumerate(requests):
+            t = np.ascontiguousarray(r.prompt, dtype=np.uint32)
+            keep.append(t)
+            arr[i].prompt = t.ctypes.data_as(C.POINTER(C.c_uint32))
+            arr[i].n_prompt = len(t)
+            arr[i].max_new_tokens = r.max_new_tokens
+            arr[i].ignore_stop_tokens = 1 if r.ignore_stop_tokens else 0
+            arr[i].temperature = r.temperature
+            arr[i].top_k = r.top_k
+            arr[i].top_p = r.top_p
+            arr[i].repetition_penalty = r.repetition_penalty
+            arr[i].presence_penalty = r.presence_penalty
+            arr[i].frequency_penalty = r.frequency_penalty
+            arr[i].seed = r.seed
+        ids = np.empty(n, np.int32)
+        capi.check(capi.lib().mk_engine_submit(self._h, arr, n, 1 if atomic_batch else 0, ids.ctypes.data))
+        return [int(x) for x in ids]
+
+    def step(self) -> int:
+        lanes = C.c_int32()
+        capi.check(capi.lib().mk_engine_step(self._h, C.byref(lanes)))
+        return int(lanes.value)
+
+    def run(self) -> None:
+        capi.check(capi.lib().mk_engine_run(self._h))
+
+    def pending(self) -> int:
+        n = C.c_int32()
+        capi.check(capi.lib().mk_engine_pending(self._h, C.byref(n)))
+        return int(n.value)
+
+    def result(self, request_id: int):
+        """Returns dict(tokens, state ('running' | 'done' | 'failed'), cached_tokens, message)."""
+        cap = 1 << 16
+        toks = np.empty(cap, np.uint32)
+        n = C.c_int32(cap)
+        fin = C.c_int32()
+        cached = C.c_int64()
+        capi.check(capi.lib().mk_engine_result(self._h, request_id, toks.ctypes.data, C.byref(n), C.byref(fin), C.byref(cached)))
+        state = ("running", "done", "failed")[fin.value]
+        msg = capi.lib().mk_last_error().decode() if state == "failed" else ""
+        return dict(tokens=toks[: n.value].copy(), state=state, cached_tokens=int(cached.value), message=msg)
+
+    def logits(self, request_id: int) -> np.ndarray:
+        rows = C.c_int32()
+        capi.check(capi.lib().mk_engine_logits(self._h, request_id, None, C.byref(rows)))
+        vocab = self.model.spec().vocab_size
+        out = np.empty((rows.value, vocab), np.float32)
+        if rows.value:
+            capi.check(capi.lib().mk_engine_logits(self._h, request_id, out.ctypes.data, C.byref(rows)))
+        return out
+
+    def trace(self) -> list[list[tuple[int, int, int]]]:
+        """Every packed forward so far: [(request id, start position, token count), ...] per tick."""
+        out = []
+        tick = 0
+        while True:
+            n = C.c_int32(0)
+            st = capi.lib().mk_engine_trace(self._h, tick, None, C.byref(n))
+            if st != 0:
+                break
+            arr = (capi.TickLane * max(n.value, 1))()
+            m = C.c_int32(n.value)
+            capi.check(capi.lib().mk_engine_trace(self._h, tick, arr, C.byref(m)))
+            out.append([(arr[i].request_id, arr[i].start_pos, arr[i].n_tokens) for i in range(m.value)])
+            tick += 1
+        return out
+
+    def stats(self) -> dict:
+        s = capi.EngineStats()
+        capi.check(capi.lib().mk_engine_stats_query(self._h, C.byref(s)))
+        return {n: getattr(s, n) for n, _ in s._fields_}
+
+    def close(self) -> None:
+        if self._h:
+            capi.lib().mk_engine_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

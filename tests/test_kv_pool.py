@@ -1,0 +1,172 @@
+"""Paged-KV pool parity: the reference's own known-answer cases (crates/macllm-kv/src/cache.rs tests)
+run against BOTH the oracle restatement and the product's host library, then a randomised differential
+between the two.  CPU only."""
+import random
+
+import pytest
+
+from kvadapters import OraclePool, ProductPool
+
+IMPLS = {"oracle": OraclePool, "product": ProductPool}
+
+
+@pytest.fixture(params=list(IMPLS))
+def Pool(request, mk):
+    return IMPLS[request.param]
+
+
+def sub(stats, *keys):
+    return tuple(stats[k] for k in keys)
+
+
+def test_compact_page_table_of_two_lanes(Pool):
+    """cache.rs:4898-4977: pool(block_tokens 2, slab_blocks 2, max 4), lanes of 3 and 1 tokens."""
+    pool = Pool(2, 2, 4)
+    first, second = pool.new_table(), pool.new_table()
+    pages, offsets, counts, lens = pool.page_table([first, second], [3, 1])
+    assert [list(p) for p in pages] == [[0, 0], [0, 1], [1, 0]]
+    assert list(offsets) == [0, 2] and list(counts) == [2, 1] and list(lens) == [3, 1]
+
+
+def test_shared_full_prefix_appends_on_a_fresh_page(Pool):
+    """cache.rs:4585-4630."""
+    pool = Pool(4, 2, 2)
+    source = pool.new_table()
+    assert pool.append([source], [4]) == []
+    pool.complete(pool.submitted())
+    source_id = source.blocks()[0]
+    fork = source.fork_prefix(4)
+    assert pool.append([fork], [1]) == []          # no copy-on-write: the shared page is full
+    assert source.blocks() == [source_id]
+    assert fork.blocks()[0] == source_id and fork.blocks()[1] != source_id
+    assert sub(pool.stats(), "live_blocks", "live_references", "shared_blocks") == (2, 3, 1)
+
+
+def test_shared_partial_prefix_copies_on_write(Pool):
+    """cache.rs:4632-4693."""
+    pool = Pool(4, 2, 2)
+    source = pool.new_table()
+    pool.append([source], [4])
+    pool.complete(pool.submitted())
+    source_id = source.blocks()[0]
+    fork = source.fork_prefix(2)
+    cows = pool.append([fork], [1])
+    assert len(cows) == 1 and cows[0][0] == source_id[0] and cows[0][2] == 2
+    assert source.blocks() == [source_id]
+    assert fork.blocks()[0] != source_id and fork.blocks()[0][0] == cows[0][1]
+    assert sub(pool.stats(), "live_blocks", "live_references", "shared_blocks") == (2, 2, 0)
+
+
+def test_batch_cows_two_lanes_sharing_one_partial_tail(Pool):
+    """cache.rs:4695-4747."""
+    pool = Pool(4, 3, 3)
+    source = pool.new_table()
+    pool.append([source], [2])
+    pool.complete(pool.submitted())
+    source_id = source.blocks()[0]
+    first, second = source.fork_prefix(2), source.fork_prefix(2)
+    assert pool.stats()["live_references"] == 3
+    cows = pool.append([first, second], [1, 1])
+    assert [c[0] for c in cows] == [source_id[0]] * 2 and [c[2] for c in cows] == [2, 2]
+    assert source.blocks() == [source_id]
+    assert first.blocks()[0] != source_id and second.blocks()[0] != source_id and first.blocks()[0] != second.blocks()[0]
+    assert sub(pool.stats(), "live_blocks", "live_references", "shared_blocks") == (3, 3, 0)
+
+
+def test_exhaustion_mutates_nothing(Pool):
+    """cache.rs:4802-4830, 5130-5156: a batch that does not fit leaves stats and epochs untouched."""
+    pool = Pool(2, 2, 3)
+    a, b = pool.new_table(), pool.new_table()
+    assert pool.append([a], [4]) == []
+    before = pool.stats()
+    assert pool.append([a, b], [1, 4]) is None
+    assert pool.stats() == before
+    assert len(a) == 4 and len(b) == 0
+
+
+def test_clear_retires_until_completion_then_reuses_with_new_generation(Pool):
+    """cache.rs:5404-5449."""
+    pool = Pool(2, 2, 2)
+    t = pool.new_table()
+    pool.append([t], [3])
+    first_ids = t.blocks()
+    epoch = pool.submitted()
+    t.clear()                                        # device work of `epoch` may still read the pages
+    assert sub(pool.stats(), "retired_blocks", "free_blocks", "live_blocks") == (2, 0, 0)
+    u = pool.new_table()
+    assert pool.append([u], [1]) is None            # nothing is free while the pages are quarantined
+    pool.complete(epoch)
+    assert sub(pool.stats(), "retired_blocks", "free_blocks") == (0, 2)
+    assert pool.append([u], [1]) == []
+    (slot, gen), = u.blocks()
+    assert slot == first_ids[0][0] and gen == first_ids[0][1] + 1
+
+
+def test_fork_retains_pages_until_last_owner_releases(Pool):
+    """cache.rs:4443-4474."""
+    pool = Pool(2, 4, 4)
+    source = pool.new_table()
+    pool.append([source], [4])
+    pool.complete(pool.submitted())
+    fork = source.fork_prefix(3)
+    assert sub(pool.stats(), "live_blocks", "live_references", "shared_blocks") == (2, 4, 2)
+    source.clear()
+    assert sub(pool.stats(), "live_blocks", "live_references", "shared_blocks", "free_blocks") == (2, 2, 0, 2)
+    fork.clear()
+    assert sub(pool.stats(), "live_blocks", "free_blocks") == (0, 4)
+
+
+def test_zero_growth_batch_still_takes_an_epoch(Pool):
+    """cache.rs:5010-5043: appending into a partial page reserves nothing but opens a transaction."""
+    pool = Pool(4, 2, 2)
+    t = pool.new_table()
+    pool.append([t], [1])
+    e1 = pool.submitted()
+    pool.complete(e1)
+    assert pool.append([t], [2]) == []
+    assert pool.submitted() == e1 + 1
+    assert len(t.blocks()) == 1 and len(t) == 3
+
+
+def test_randomised_differential_oracle_vs_product(mk):
+    """Same random operation sequence on both implementations: block ids (slot, generation), stats,
+    copy-on-write plans and exhaustion decisions must agree at every step."""
+    for seed in range(6):
+        rng = random.Random(seed)
+        bt, slab, mx = rng.choice([(2, 2, 9), (4, 3, 12), (16, 8, 24)])
+        pools = [OraclePool(bt, slab, mx), ProductPool(bt, slab, mx)]
+        tables = [[], []]
+        for step in range(300):
+            op = rng.random()
+            n_tab = len(tables[0])
+            if op < 0.15 or n_tab == 0:
+                for i, p in enumerate(pools):
+                    tables[i].append(p.new_table())
+            elif op < 0.55:
+                k = rng.randint(1, min(3, n_tab))
+                idx = rng.sample(range(n_tab), k)
+                ns = [rng.randint(1, 2 * bt + 1) for _ in idx]
+                commit = rng.random() < 0.85
+                outs = [p.append([tables[i][j] for j in idx], ns, commit) for i, p in enumerate(pools)]
+                assert outs[0] == outs[1], (seed, step)
+            elif op < 0.7:
+                j = rng.randrange(n_tab)
+                length = len(tables[0][j])
+                if length:
+                    n = rng.randint(0, length)
+                    for i in range(2):
+                        tables[i].append(tables[i][j].fork_prefix(n))
+            elif op < 0.85:
+                j = rng.randrange(n_tab)
+                for i in range(2):
+                    tables[i][j].clear()
+            else:
+                e = pools[0].submitted()
+                for p in pools:
+                    p.complete(e)
+            assert pools[0].stats() == pools[1].stats(), (seed, step)
+            for a, b in zip(tables[0], tables[1]):
+                assert a.blocks() == b.blocks() and len(a) == len(b), (seed, step)
+        for i in range(2):
+            for t in tables[i]:
+                t.free()

@@ -1,0 +1,159 @@
+"""Exact-token prefix cache parity: the reference's known answers (crates/macllm-kv/src/prefix_cache.rs
+tests) against the oracle restatement and the product's host library, plus a randomised differential."""
+import hashlib
+import importlib
+import random
+
+import pytest
+
+GOLDEN = bytes([234, 223, 154, 217, 54, 25, 155, 93, 168, 35, 250, 114, 218, 228, 3, 17, 159, 115, 165, 90, 62, 133, 54, 226,
+                28, 250, 17, 165, 115, 7, 250, 146])
+
+
+@pytest.fixture(scope="module")
+def pkv(mk):
+    return importlib.import_module("macllm_infer_b200.kv")
+
+
+def test_sha256_known_answers(pkv):
+    for msg in (b"", b"abc", b"abcdbcdecdefdefgefghfghighijhijkijkljklmklmnlmnomnopnopq", bytes(range(256)) * 5):
+        assert pkv.sha256(msg) == hashlib.sha256(msg).digest()
+    assert pkv.sha256(b"abc").hex() == "ba7816bf8f01cfea414140de5dae2223b00361a396177a9cb410ff61f20015ad"
+
+
+def test_hash_has_the_reference_golden_value():
+    """prefix_cache.rs:1010-1018: hash_endpoint([0x01020304, 5, 6, 7, 8], 4)."""
+    from oracle import kv
+    assert kv.endpoint_digest([0x01020304, 5, 6, 7, 8], 5, 4) == GOLDEN
+
+
+def test_product_block_digests_chain_like_the_oracle(pkv):
+    from oracle import kv
+    toks = [0x01020304, 5, 6, 7, 8, 9, 10, 11, 12]
+    assert pkv.block_digests(4, toks) == kv.full_block_digests(toks, 4)
+    # the golden endpoint is a partial block chained on the first full block
+    first = pkv.block_digests(4, toks)[0]
+    assert kv.hash_block(first, 4, 1, [8]) == GOLDEN
+
+
+class OracleCache:
+    def __init__(self, bt, cap):
+        from oracle import kv
+        self.c = kv.PrefixCache(bt, cap)
+
+    def insert(self, tokens, value, cost):
+        ev = self.c.insert(tokens, value, cost)
+        return None if ev is None else list(ev)
+
+    def lookup(self, tokens):
+        return self.c.lookup_aligned_common_prefix(tokens, len(tokens))
+
+    def evict(self):
+        return self.c.evict_lru()
+
+    def stats(self):
+        return self.c.stats()
+
+
+class ProductCache:
+    def __init__(self, bt, cap):
+        self.kv = importlib.import_module("macllm_infer_b200.kv")
+        self.capi = importlib.import_module("macllm_infer_b200._capi")
+        self.c = self.kv.PrefixCache(bt, cap)
+
+    def insert(self, tokens, value, cost):
+        try:
+            return self.c.insert(tokens, value, cost)
+        except self.capi.MkError:
+            return None
+
+    def lookup(self, tokens):
+        return self.c.lookup(tokens)
+
+    def evict(self):
+        return self.c.evict_lru()
+
+    def stats(self):
+        return self.c.stats()
+
+
+@pytest.fixture(params=["oracle", "product"])
+def Cache(request, mk):
+    return {"oracle": OracleCache, "product": ProductCache}[request.param]
+
+
+def test_aligned_lookup_reuses_a_long_snapshot_before_a_divergent_suffix(Cache):
+    """prefix_cache.rs:773-792."""
+    c = Cache(4, 20)
+    c.insert(list(range(1, 13)), 7, 7)
+    assert c.lookup([1, 2, 3, 4, 5, 6, 99, 100]) == (4, 7)
+    assert c.lookup([1, 2, 3, 4, 5, 6, 7, 8, 9, 77, 78]) == (8, 7)
+
+
+def test_aligned_lookup_strict_bounds(Cache):
+    """prefix_cache.rs:795-821."""
+    c = Cache(4, 20)
+    c.insert(list(range(1, 13)), 1, 1)
+    assert c.lookup([1, 2, 3, 4, 5, 6]) == (4, 1)
+    assert c.lookup([1, 2, 3, 4]) is None          # an aligned endpoint equal to the prompt is not reusable
+    assert c.lookup([0, 1, 2, 3, 4, 5, 6]) is None  # a substring is not a prefix
+    s = c.stats()
+    assert (s["hits"], s["misses"], s["matched_tokens"]) == (1, 2, 4)
+
+
+def test_aligned_block_indexes_follow_replacement_and_lru_eviction(Cache):
+    """prefix_cache.rs:932-957."""
+    c = Cache(4, 2)
+    c.insert([1] * 5, 10, 1)
+    c.insert([2] * 5, 20, 1)
+    assert c.lookup([1, 1, 1, 1, 9]) == (4, 10)
+    assert c.insert([3] * 5, 30, 1) == [20]         # LRU is "second": "first" was just touched
+    assert c.lookup([2, 2, 2, 2, 9]) is None
+    assert c.insert([1] * 5, 11, 1) == []           # replacement is not an eviction
+    assert c.lookup([1, 1, 1, 1, 9]) == (4, 11)
+    assert c.evict() == 30
+    assert c.lookup([3, 3, 3, 3, 9]) is None
+    assert c.stats()["evictions"] == 2
+
+
+def test_insert_evicts_lru_until_the_budget_fits_and_rejects_oversize(Cache):
+    """prefix_cache.rs:915-929,181-195."""
+    c = Cache(1, 5)
+    c.insert([1, 7], 1, 2)
+    c.insert([2, 7], 2, 2)
+    assert c.lookup([1, 7, 0]) == (2, 1)
+    assert c.insert([3, 7], 3, 3) == [2]
+    s = c.stats()
+    assert (s["entries"], s["cached_blocks"], s["evictions"]) == (2, 5, 1)
+    assert c.insert([4, 7], 4, 6) is None           # cost above the budget
+    assert c.stats()["entries"] == 2
+
+
+def test_most_recently_used_enclosing_snapshot_wins(Cache):
+    """prefix_cache.rs:341-351."""
+    c = Cache(2, 10)
+    c.insert([1, 2, 3, 4, 5, 6], 100, 1)
+    c.insert([1, 2, 3, 4, 9, 9], 200, 1)
+    assert c.lookup([1, 2, 3, 4, 0]) == (4, 200)
+    assert c.lookup([1, 2, 3, 4, 5, 6, 0]) == (6, 100)
+    assert c.lookup([1, 2, 3, 4, 0]) == (4, 100)   # the last hit made 100 the most recent
+
+
+def test_randomised_differential(mk):
+    for seed in range(5):
+        rng = random.Random(seed)
+        bt = rng.choice([2, 4, 16])
+        a, b = OracleCache(bt, 12), ProductCache(bt, 12)
+        stems = [[rng.randrange(5) for _ in range(rng.randint(1, 6 * bt))] for _ in range(6)]
+        for step in range(400):
+            stem = rng.choice(stems)
+            toks = stem[: rng.randint(1, len(stem))] + [rng.randrange(5) for _ in range(rng.randint(0, 3))]
+            op = rng.random()
+            if op < 0.4:
+                cost = rng.randint(0, 5)
+                assert a.insert(toks, step, cost) == b.insert(toks, step, cost), (seed, step)
+            elif op < 0.9:
+                assert a.lookup(toks) == b.lookup(toks), (seed, step)
+            else:
+                assert a.evict() == b.evict(), (seed, step)
+            assert a.stats() == b.stats(), (seed, step)

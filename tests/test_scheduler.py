@@ -1,0 +1,196 @@
+"""Scheduler-tick parity on the host-only fake model: the schedules the reference's own tests assert
+(src/engine.rs:4701-5014) and a randomised differential of traces, tokens, block tables, prefix-cache
+counters and pool stats between the product's C++ engine and the oracle's Python restatement."""
+import importlib
+import random
+
+import pytest
+
+
+@pytest.fixture(scope="module")
+def eng(mk):
+    return importlib.import_module("macllm_infer_b200.engine")
+
+
+def product_engine(eng, model_kw, engine_kw):
+    model = eng.Model.fake(**model_kw)
+    return model, eng.Engine(model, **engine_kw)
+
+
+def oracle_engine(model_kw, engine_kw):
+    from oracle import engine as oe
+    m = oe.OracleModel(model_kw.get("vocab", 32), model_kw.get("max_context", 4096), model_kw.get("block_tokens", 16),
+                       model_kw.get("slab_blocks", 8), model_kw.get("kv_capacity_tokens", 4096),
+                       model_kw.get("prefix_capacity_tokens", 0))
+    return m, oe.OracleEngine(m, **engine_kw)
+
+
+def both(eng, model_kw, engine_kw):
+    return product_engine(eng, model_kw, engine_kw), oracle_engine(model_kw, engine_kw)
+
+
+def submit_both(eng, pe, oe_, prompts, max_new, atomic=False):
+    from oracle import engine as oe
+    ids_p = pe.submit([eng.Request(p, n) for p, n in zip(prompts, max_new)], atomic)
+    ids_o = oe_.submit([oe.Req(list(p), n) for p, n in zip(prompts, max_new)], atomic)
+    assert ids_p == ids_o
+    return ids_p
+
+
+def test_ragged_prefill_and_decode_schedule(eng):
+    """engine.rs:4701-4765: budget 4, quantum 2, two active; a 6-token prompt with 1 new token and a
+    1-token prompt with 2 new tokens."""
+    (pm, pe), (om, oe_) = both(eng, dict(vocab=32), dict(max_active_sequences=2, scheduler_token_budget=4, prefill_token_quantum=2))
+    submit_both(eng, pe, oe_, [[1, 2, 3, 4, 1, 2], [2]], [1, 2])
+    for e in (pe, oe_):
+        for _ in range(3):
+            e.step()
+    want = [[(0, 0, 2), (1, 0, 1)], [(0, 2, 2), (1, 1, 1)], [(0, 4, 2)]]
+    assert pe.trace() == want
+    assert [[tuple(l) for l in t] for t in oe_.trace] == want
+    assert pe.pending() == 0 and oe_.pending() == 0
+    assert len(pe.result(0)["tokens"]) == 1 and len(pe.result(1)["tokens"]) == 2
+    assert list(pe.result(1)["tokens"]) == oe_.results[1].tokens
+
+
+def test_budget_smaller_than_active_count_keeps_the_round_robin_cursor(eng):
+    """engine.rs:4968-5014: three 4-token prompts, budget 2, quantum 1 -> lanes [a,b], [c,a], [b,c]."""
+    (pm, pe), (om, oe_) = both(eng, dict(vocab=32), dict(max_active_sequences=3, scheduler_token_budget=2, prefill_token_quantum=1))
+    submit_both(eng, pe, oe_, [[1] * 4, [2] * 4, [4] * 4], [1, 1, 1])
+    for e in (pe, oe_):
+        for _ in range(3):
+            e.step()
+    assert [[l[0] for l in t] for t in pe.trace()] == [[0, 1], [2, 0], [1, 2]]
+    assert [[l[0] for l in t] for t in oe_.trace] == [[0, 1], [2, 0], [1, 2]]
+
+
+def test_kv_pressure_shrinks_the_batch_from_the_back(eng):
+    """engine.rs:4845-4895: three one-token requests, room for two blocks."""
+    mkw = dict(vocab=32, block_tokens=16, slab_blocks=2, kv_capacity_tokens=32)
+    (pm, pe), (om, oe_) = both(eng, mkw, dict(max_active_sequences=3, scheduler_token_budget=3, prefill_token_quantum=1))
+    submit_both(eng, pe, oe_, [[1], [2], [3]], [1, 1, 1])
+    for e in (pe, oe_):
+        e.step()
+    assert [len(t) for t in pe.trace()] == [2] and pe.pending() == 1
+    assert pe.stats()["kv_shrinks"] == 1 and oe_.kv_shrinks == 1
+    for e in (pe, oe_):
+        e.step()
+    assert [[l[0] for l in t] for t in pe.trace()] == [[0, 1], [2]]
+    assert all(pe.result(i)["state"] == "done" for i in range(3))
+
+
+def test_irreducible_kv_pressure_fails_only_that_request(eng):
+    """engine.rs:4898-4966: a lane that can never be served fails alone; its peers continue."""
+    mkw = dict(vocab=32, block_tokens=2, slab_blocks=2, kv_capacity_tokens=4)
+    (pm, pe), (om, oe_) = both(eng, mkw, dict(max_active_sequences=2, scheduler_token_budget=8, prefill_token_quantum=4))
+    # each request fits the pool on its own (4 cached tokens), but after the first tick each holds one of the
+    # two blocks and the first lane's decode needs a third: not even a one-lane batch can be reserved
+    submit_both(eng, pe, oe_, [[1, 2], [4, 5]], [3, 3])
+    for e in (pe, oe_):
+        e.run()
+    states = [pe.result(i)["state"] for i in range(2)]
+    assert states == [oe_.results[i].state for i in range(2)]
+    assert states == ["failed", "done"]
+    assert "exhausted" in pe.result(0)["message"]
+    assert len(pe.result(1)["tokens"]) == 3
+    assert pm.pool_stats()["live_blocks"] == 0
+
+
+def test_atomic_batch_waits_until_every_member_fits(eng):
+    """engine.rs:1886-1936."""
+    (pm, pe), (om, oe_) = both(eng, dict(vocab=32), dict(max_active_sequences=3, scheduler_token_budget=16, prefill_token_quantum=8,
+                                                        queue_capacity=8))
+    submit_both(eng, pe, oe_, [[1, 2, 3]], [6])
+    for e in (pe, oe_):
+        e.step()
+    submit_both(eng, pe, oe_, [[4], [5], [6]], [2, 2, 2], atomic=True)
+    for e in (pe, oe_):
+        e.run()
+    tr = pe.trace()
+    assert tr == [[tuple(l) for l in t] for t in oe_.trace]
+    # no member of the batch runs before request 0 has left and all three fit
+    first_batch_tick = next(i for i, t in enumerate(tr) if any(l[0] in (1, 2, 3) for l in t))
+    assert sorted(l[0] for l in tr[first_batch_tick]) == [1, 2, 3]
+    assert all(all(l[0] == 0 for l in t) for t in tr[:first_batch_tick])
+
+
+def test_requests_that_can_never_fit_are_rejected_at_admission(eng):
+    """kv_capacity_rejection, engine.rs:2839-2863, and validate_request, generation.rs:1308-1337."""
+    model, e = product_engine(eng, dict(vocab=32, max_context=64, block_tokens=16, kv_capacity_tokens=32),
+                              dict(max_active_sequences=2, queue_capacity=8))
+    ids = e.submit([eng.Request(list(range(1, 30)), 8), eng.Request([1, 2], 100), eng.Request([40], 1), eng.Request([], 1),
+                    eng.Request([3], 2)])
+    e.run()
+    assert [e.result(i)["state"] for i in ids] == ["failed", "failed", "failed", "failed", "done"]
+    assert "KV capacity" in e.result(ids[0])["message"]
+    assert "context limit" in e.result(ids[1])["message"]
+
+
+def test_forward_failure_rolls_back_every_lane(eng):
+    """decoder.rs:4146-4162 / cache.rs:3001-3005: a failed forward leaves sessions and pool untouched."""
+    capi = importlib.import_module("macllm_infer_b200._capi")
+    model = eng.Model.fake(vocab=32, fail_forward_at=1)
+    a, b = model.new_session(), model.new_session()
+    model.forward_batch([(a, [1, 2, 3], 0), (b, [4], 0)])
+    before = model.pool_stats()
+    with pytest.raises(capi.MkError, match="injected"):
+        model.forward_batch([(a, [5], 3), (b, [6, 7], 1)])
+    after = model.pool_stats()
+    assert len(a) == 3 and len(b) == 1
+    assert after["live_blocks"] == before["live_blocks"] and after["reserved_blocks"] == 0
+    logits, toks = model.forward_batch([(a, [5], 3), (b, [6, 7], 1)])
+    assert list(toks) == [(31 * 5 + 7 * 3 + 3) % 32, (31 * 7 + 7 * 2 + 3) % 32]
+
+
+def test_lane_validation_happens_before_any_mutation(eng):
+    capi = importlib.import_module("macllm_infer_b200._capi")
+    model = eng.Model.fake(vocab=32)
+    a, b = model.new_session(), model.new_session()
+    with pytest.raises(capi.MkError, match="start_pos"):
+        model.forward_batch([(a, [1], 0), (b, [2], 5)])
+    with pytest.raises(capi.MkError):
+        model.forward_batch([(a, [1], 0), (b, [99], 0)])     # token outside the vocabulary
+    with pytest.raises(capi.MkError, match="duplicates"):
+        model.forward_batch([(a, [1], 0), (a, [2], 0)])
+    assert len(a) == 0 and len(b) == 0 and model.pool_stats()["live_blocks"] == 0
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_randomised_differential_with_prefix_cache(eng, seed):
+    """Shared-prefix workloads under KV pressure: schedules, tokens, cached-token counts, block tables
+    (through pool stats) and prefix-cache counters agree tick by tick."""
+    rng = random.Random(seed)
+    bt = rng.choice([4, 16])
+    mkw = dict(vocab=64, max_context=2048, block_tokens=bt, slab_blocks=rng.choice([2, 8]),
+               kv_capacity_tokens=rng.choice([40 * bt, 200 * bt]), prefix_capacity_tokens=rng.choice([0, 12 * bt, 64 * bt]))
+    ekw = dict(max_active_sequences=rng.choice([2, 4, 7]), scheduler_token_budget=rng.choice([8, 48, 256]),
+               prefill_token_quantum=rng.choice([3, 16, 64]), queue_capacity=64)
+    (pm, pe), (om, oe_) = both(eng, mkw, ekw)
+    stems = [[rng.randrange(3, 64) for _ in range(rng.randint(bt, 6 * bt))] for _ in range(3)]
+    submitted = 0
+    for wave in range(4):
+        prompts, max_new = [], []
+        for _ in range(rng.randint(1, 6)):
+            stem = rng.choice(stems)
+            prompts.append(stem[: rng.randint(1, len(stem))] + [rng.randrange(3, 64) for _ in range(rng.randint(1, 2 * bt))])
+            max_new.append(rng.randint(1, 12))
+        submit_both(eng, pe, oe_, prompts, max_new, atomic=rng.random() < 0.3 and len(prompts) <= ekw["max_active_sequences"])
+        submitted += len(prompts)
+        for _ in range(rng.randint(1, 30)):
+            lp, lo = pe.step(), oe_.step()
+            assert lp == lo
+            assert pm.pool_stats() == om.pool.stats()
+            if mkw["prefix_capacity_tokens"]:
+                assert pm.prefix_diagnostics() == om.prefix.stats()
+    pe.run()
+    oe_.run()
+    assert pe.trace() == [[tuple(l) for l in t] for t in oe_.trace]
+    for rid in range(submitted):
+        rp, ro = pe.result(rid), oe_.results[rid]
+        assert rp["state"] == ro.state
+        assert list(rp["tokens"]) == ro.tokens
+        assert rp["cached_tokens"] == ro.cached_tokens
+    assert pm.pool_stats() == om.pool.stats()
+    if mkw["prefix_capacity_tokens"]:
+        assert pm.prefix_diagnostics() == om.prefix.stats()
+        assert pm.prefix_diagnostics()["hits"] + pm.prefix_diagnostics()["misses"] > 0
