@@ -178,6 +178,24 @@ int32_t mk_synchronize(mk_model* m);
 int32_t mk_last_forward_ms(mk_model* m, float* out);
 /* Kernel launches issued by this model since load. */
 int32_t mk_launch_count(mk_model* m, int64_t* out);
+/* Host-to-device and device-to-host bytes moved by forwards since load (per-tick staging in, tokens or
+ * logits out). */
+int32_t mk_transfer_bytes(mk_model* m, int64_t* h2d, int64_t* d2h);
+
+/* Per-kernel-class device timing, the measurement behind the roofline figures: while enabled, every
+ * launch group is bracketed by CUDA events on the model's stream; mk_profile_query returns, per class,
+ * launches, summed milliseconds and the algorithmic bytes / flops of those launches.  The reference
+ * has no counterpart beyond its ignored Metal micro-profile test
+ * (crates/macllm-kernels/src/paged_attention.rs:1910-2054). */
+typedef struct mk_kernel_profile {
+    char name[32];
+    int64_t launches;
+    double ms;
+    double bytes;
+    double flops;
+} mk_kernel_profile;
+int32_t mk_profile_enable(mk_model* m, int32_t on);
+int32_t mk_profile_query(mk_model* m, mk_kernel_profile* out, int32_t* n);
 
 /* ------------------------------------------------------------------------------------------------
  * Engine: the scheduler tick  (ServingScheduler, src/engine.rs:1578-2770; GenerationCore,

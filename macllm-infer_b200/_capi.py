@@ -85,6 +85,10 @@ class EngineStats(C.Structure):
                 ("device_ms", C.c_double)]
 
 
+class KernelProfile(C.Structure):
+    _fields_ = [("name", C.c_char * 32), ("launches", C.c_int64), ("ms", C.c_double), ("bytes", C.c_double), ("flops", C.c_double)]
+
+
 class AttnCase(C.Structure):
     _fields_ = [("lanes", C.c_int32), ("total_tokens", C.c_int32), ("q_heads", C.c_int32), ("kv_heads", C.c_int32),
                 ("head_dim", C.c_int32), ("block_tokens", C.c_int32), ("layers", C.c_int32), ("layer", C.c_int32),
@@ -125,6 +129,9 @@ SIGNATURES = {
     "mk_synchronize": (_i32, [P]),
     "mk_last_forward_ms": (_i32, [P, C.POINTER(_f32)]),
     "mk_launch_count": (_i32, [P, C.POINTER(_i64)]),
+    "mk_transfer_bytes": (_i32, [P, C.POINTER(_i64), C.POINTER(_i64)]),
+    "mk_profile_enable": (_i32, [P, _i32]),
+    "mk_profile_query": (_i32, [P, P, C.POINTER(_i32)]),
     "mk_engine_new": (_i32, [P, C.POINTER(EngineConfig), C.POINTER(P)]),
     "mk_engine_free": (_i32, [P]),
     "mk_engine_submit": (_i32, [P, C.POINTER(Request), _i32, _i32, P]),

@@ -229,6 +229,35 @@ int32_t mk_launch_count(mk_model* m, int64_t* out) {
     return guarded([&] { *out = m->lm->launch_count(); });
 }
 
+int32_t mk_transfer_bytes(mk_model* m, int64_t* h2d, int64_t* d2h) {
+    return guarded([&] {
+        if (h2d) *h2d = m->lm->h2d_bytes();
+        if (d2h) *d2h = m->lm->d2h_bytes();
+    });
+}
+
+int32_t mk_profile_enable(mk_model* m, int32_t on) {
+    return guarded([&] { m->lm->profile_enable(on != 0); });
+}
+
+int32_t mk_profile_query(mk_model* m, mk_kernel_profile* out, int32_t* n) {
+    return guarded([&] {
+        auto v = m->lm->profile_query();
+        if (out != nullptr) {
+            if ((int32_t)v.size() > *n) throw std::runtime_error("profile buffer is too small");
+            for (size_t i = 0; i < v.size(); ++i) {
+                memset(&out[i], 0, sizeof out[i]);
+                strncpy(out[i].name, v[i].name.c_str(), sizeof out[i].name - 1);
+                out[i].launches = v[i].launches;
+                out[i].ms = v[i].ms;
+                out[i].bytes = v[i].bytes;
+                out[i].flops = v[i].flops;
+            }
+        }
+        *n = (int32_t)v.size();
+    });
+}
+
 // ------------------------------------------------------------------------------------------ engine
 
 int32_t mk_engine_new(mk_model* m, const mk_engine_config* cfg, mk_engine** out) {

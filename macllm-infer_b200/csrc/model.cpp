@@ -291,6 +291,63 @@ void Model::rope_tables_for(double theta, const float*& cos_t, const float*& sin
     rope_.push_back(std::move(t));
 }
 
+// ---------------------------------------------------------------------------- profiling
+
+static const char* kclass_names[] = {"qgemm_tc", "qgemv", "paged_attention", "add_norm_quant", "rope_kv_scatter", "actmul_quant",
+                                     "embed", "build_batch", "argmax", "moe"};
+
+void Model::profile_enable(bool on) {
+    profiling_ = on;
+    if (on) for (int i = 0; i < KC_COUNT; ++i) { prof_[i] = KernelProfile{}; prof_[i].name = kclass_names[i]; }
+}
+
+void Model::prof_begin(int cls, double bytes, double flops) {
+    if (!profiling_) return;
+    ProfSpan sp;
+    sp.cls = cls;
+    sp.bytes = bytes;
+    sp.flops = flops;
+    for (cudaEvent_t* e : {&sp.a, &sp.b}) {
+        if (event_pool_.empty()) {
+            MK_CUDA(cudaEventCreate(e));
+        } else {
+            *e = event_pool_.back();
+            event_pool_.pop_back();
+        }
+    }
+    MK_CUDA(cudaEventRecord(sp.a, stream_));
+    spans_.push_back(sp);
+}
+
+void Model::prof_end() {
+    if (!profiling_ || spans_.empty()) return;
+    MK_CUDA(cudaEventRecord(spans_.back().b, stream_));
+}
+
+void Model::prof_resolve() {
+    for (ProfSpan& sp : spans_) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, sp.a, sp.b) == cudaSuccess) {
+            KernelProfile& k = prof_[sp.cls];
+            ++k.launches;
+            k.ms += ms;
+            k.bytes += sp.bytes;
+            k.flops += sp.flops;
+        } else {
+            cudaGetLastError();
+        }
+        event_pool_.push_back(sp.a);
+        event_pool_.push_back(sp.b);
+    }
+    spans_.clear();
+}
+
+std::vector<PagedLm::KernelProfile> Model::profile_query() {
+    std::vector<KernelProfile> out;
+    for (int i = 0; i < KC_COUNT; ++i) if (prof_[i].launches > 0) out.push_back(prof_[i]);
+    return out;
+}
+
 // ---------------------------------------------------------------------------- forward
 
 bool Model::tensor_path(const QWeight& W, int T) const {
@@ -310,7 +367,12 @@ ActQ Model::act_view(DevBuf& qs, DevBuf& d, DevBuf& bs, DevBuf& xh, int, int, in
 }
 
 void Model::matmul(const QWeight& W, const ActQ& x, int T, float* y, int ldy, float scale, float softcap) {
-    if (tensor_path(W, T) && x.xh != nullptr) {
+    const bool tc = tensor_path(W, T) && x.xh != nullptr;
+    // algorithmic traffic of one call: the matrix as stored, the activation rows as consumed, the f32 result
+    const double act_bytes = tc ? 2.0 * T * W.cols : 1.0 * T * W.cols;
+    prof_begin(tc ? KC_GEMM_TC : KC_GEMV, (double)W.bytes + act_bytes + 4.0 * T * W.rows, 2.0 * T * (double)W.rows * (double)W.cols);
+    struct End { Model* m; ~End() { m->prof_end(); } } end{this};
+    if (tc) {
         size_t need = qgemm_tc_partial_floats(W, T);
         tc_ws_.partial.ensure(need * 4);
         launch_qgemm_tc_scratch(W, x, T, y, ldy, scale, softcap, tc_ws_.partial.as<float>(), tc_ws_.status.as<int32_t>(), stream_);
@@ -360,6 +422,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
     if (stage_bytes > stage_dev_.size()) throw std::runtime_error("tick staging buffer is too small");
     MK_CUDA(cudaEventRecord(ev_start_, stream_));
     MK_CUDA(cudaMemcpyAsync(stage_dev_.ptr(), hp, stage_bytes, cudaMemcpyHostToDevice, stream_));
+    h2d_bytes_ += (int64_t)stage_bytes;
     uint8_t* dp = stage_dev_.as<uint8_t>();
 
     BatchDesc bd;
@@ -377,7 +440,9 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
     bd.tile_row0 = tile_row_.as<int32_t>();
     bd.n_tiles = ntiles_.as<int32_t>();
     bd.error_flag = err_.as<int32_t>();
-    launch_build_batch(bd, bt, q_tile, stream_);
+    prof_begin(KC_BATCH, 0, 0);
+        launch_build_batch(bd, bt, q_tile, stream_);
+        prof_end();
     ++launches_;
     const uint32_t* ids_dev = reinterpret_cast<const uint32_t*>(dp + off_ids);
 
@@ -389,7 +454,9 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
     }
 
     // ---- embedding (src/decoder.rs:3194-3197)
-    launch_embed(token_embd_.w, ids_dev, T, ms_.embedding_scale, h_.as<float>(), stream_);
+    prof_begin(KC_EMBED, 4.0 * T * H, 0);
+        launch_embed(token_embd_.w, ids_dev, T, ms_.embedding_scale, h_.as<float>(), stream_);
+        prof_end();
     ++launches_;
 
     const bool f16_T = cfg_.matmul_path != 1 && (cfg_.matmul_path == 2 || T > 8);
@@ -411,7 +478,9 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         na.dim = H;
         na.act_kind = kind;
         na.out = xa;
+        prof_begin(KC_NORM_QUANT, 9.0 * T * H, 0);
         launch_add_norm_quant(na, stream_);
+        prof_end();
         ++launches_;
         // projections (src/decoder.rs:1099-1161)
         matmul(w.wq.w, xa, T, q_.as<float>(), AW, 1.f, 0.f);
@@ -439,7 +508,9 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         ra.block_tokens = bt;
         ra.layers = ms_.layers;
         ra.layer = l;
+        prof_begin(KC_ROPE_KV, 4.0 * T * (2 * AW + 2 * KW) + (cfg_.kv_f16 ? 2.0 : 4.0) * 2 * T * KW, 0);
         launch_rope_kv(ra, stream_);
+        prof_end();
         ++launches_;
         AttnArgs at;
         at.q = q_.as<float>();
@@ -458,7 +529,20 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         at.softcap = ls.softcap;
         at.window = ls.window;
         at.q_tile = q_tile;
+        {
+            // algorithmic traffic: each lane's visible K/V history once, plus queries and outputs
+            double kv_tokens = 0;
+            for (const LmLane& ln : lanes) {
+                double ctx = (double)ln.start_pos + ln.n_tokens;
+                kv_tokens += ls.window > 0 ? std::min<double>(ctx, (double)ls.window + ln.n_tokens) : ctx;
+            }
+            double esz = cfg_.kv_f16 ? 2.0 : 4.0;
+            double flops = 0;
+            for (const LmLane& ln : lanes) flops += 4.0 * ms_.q_heads * d * ((double)ln.n_tokens * ln.start_pos + 0.5 * ln.n_tokens * ln.n_tokens);
+            prof_begin(KC_ATTN, kv_tokens * 2 * KW * esz + 8.0 * T * AW, flops);
+        }
         launch_paged_attention(at, stream_);
+        prof_end();
         ++launches_;
         // output projection
         int okind = act_kind_of(w.wo.w);
@@ -469,7 +553,9 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         no.dim = AW;
         no.act_kind = okind;
         no.out = xo;
+        prof_begin(KC_NORM_QUANT, 5.0 * T * AW, 0);
         launch_add_norm_quant(no, stream_);
+        prof_end();
         ++launches_;
         matmul(w.wo.w, xo, T, proj_.as<float>(), H, 1.f, 0.f);
         // residual add + FFN norm + quantise (finish_mixer, src/decoder.rs:2684-2699)
@@ -486,7 +572,9 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         nf.act_kind = fkind;
         nf.out = xf;
         nf.normed_out = ls.moe ? normed_.as<float>() : nullptr;
+        prof_begin(KC_NORM_QUANT, 13.0 * T * H, 0);
         launch_add_norm_quant(nf, stream_);
+        prof_end();
         ++launches_;
         if (!ls.moe) {
             // dense feed-forward (src/decoder.rs:298-305)
@@ -494,7 +582,9 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
             matmul(w.up.w, xf, T, up_.as<float>(), ms_.ffn, 1.f, 0.f);
             int dkind = act_kind_of(w.down.w);
             ActQ xd = act_view(f_qs_, f_d_, f_bs_, f_xh_, T, ms_.ffn, dkind, f16_T);
-            launch_actmul_quant(gate_.as<float>(), up_.as<float>(), ms_.ffn, T, ms_.ffn, ls.act, dkind, xd, nullptr, stream_);
+            prof_begin(KC_ACTMUL, 9.0 * T * ms_.ffn, 0);
+        launch_actmul_quant(gate_.as<float>(), up_.as<float>(), ms_.ffn, T, ms_.ffn, ls.act, dkind, xd, nullptr, stream_);
+        prof_end();
             ++launches_;
             matmul(w.down.w, xd, T, down_.as<float>(), H, 1.f, 0.f);
         } else {
@@ -528,7 +618,9 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         nl.eps = ms_.eps;
         nl.rows = T;
         nl.dim = H;
+        prof_begin(KC_NORM_QUANT, 12.0 * T * H, 0);
         launch_add_norm_quant(nl, stream_);
+        prof_end();
         ++launches_;
     }
     // logits tail (src/decoder.rs:3333-3356): last rows -> final norm -> output projection -> scale -> softcap
@@ -546,12 +638,16 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         ng.row_index = bd.last_index;
         ng.act_kind = kind;
         ng.out = xl;
+        prof_begin(KC_NORM_QUANT, 5.0 * B * H, 0);
         launch_add_norm_quant(ng, stream_);
+        prof_end();
         ++launches_;
         matmul(head, xl, B, logits_.as<float>(), ms_.vocab, ms_.final_logit_scale, ms_.final_softcap);
     }
     if (flags & FWD_WANT_TOKENS) {
+        prof_begin(KC_SAMPLE, 4.0 * B * ms_.vocab, 0);
         launch_argmax(logits_.as<float>(), B, ms_.vocab, tokens_.as<uint32_t>(), stream_);
+        prof_end();
         ++launches_;
     }
     // results travel to pinned host memory on the same stream; the barrier is in fetch_output
@@ -561,6 +657,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
     if (flags & FWD_WANT_TOKENS) MK_CUDA(cudaMemcpyAsync(oh + tok_off, tokens_.ptr(), (size_t)B * 4, cudaMemcpyDeviceToHost, stream_));
     MK_CUDA(cudaMemcpyAsync(oh + tok_off + (size_t)B * 4, err_.ptr(), 4, cudaMemcpyDeviceToHost, stream_));
     MK_CUDA(cudaMemcpyAsync(oh + tok_off + (size_t)B * 4 + 4, tc_ws_.status.ptr(), 4, cudaMemcpyDeviceToHost, stream_));
+    d2h_bytes_ += 8 + ((flags & FWD_WANT_LOGITS) ? (int64_t)tok_off : 0) + ((flags & FWD_WANT_TOKENS) ? (int64_t)B * 4 : 0);
     MK_CUDA(cudaEventRecord(ev_stop_, stream_));
     timed_ = true;
     out_lanes_ = B;
@@ -569,6 +666,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
 
 void Model::fetch_output(float* logits, uint32_t* tokens) {
     MK_CUDA(cudaStreamSynchronize(stream_));
+    if (profiling_) prof_resolve();
     const int B = out_lanes_;
     uint8_t* oh = out_host_.as<uint8_t>();
     size_t tok_off = (size_t)B * ms_.vocab * 4;

@@ -53,6 +53,10 @@ public:
     const ModelSpec& model_spec() const { return ms_; }
     float last_forward_ms() const override;
     int64_t launch_count() const override { return launches_; }
+    int64_t h2d_bytes() const override { return h2d_bytes_; }
+    int64_t d2h_bytes() const override { return d2h_bytes_; }
+    void profile_enable(bool on) override;
+    std::vector<KernelProfile> profile_query() override;
 
 protected:
     void run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint32_t flags) override;
@@ -78,7 +82,17 @@ private:
     cudaStream_t stream_ = nullptr;
     cudaEvent_t ev_start_ = nullptr, ev_stop_ = nullptr;
     bool timed_ = false;
-    int64_t launches_ = 0;
+    int64_t launches_ = 0, h2d_bytes_ = 0, d2h_bytes_ = 0;
+    // profiling: one event pair per launch group, resolved after the tick's barrier
+    enum KClass { KC_GEMM_TC = 0, KC_GEMV, KC_ATTN, KC_NORM_QUANT, KC_ROPE_KV, KC_ACTMUL, KC_EMBED, KC_BATCH, KC_SAMPLE, KC_MOE, KC_COUNT };
+    struct ProfSpan { int cls; double bytes, flops; cudaEvent_t a, b; };
+    bool profiling_ = false;
+    std::vector<ProfSpan> spans_;
+    std::vector<cudaEvent_t> event_pool_;
+    KernelProfile prof_[KC_COUNT];
+    void prof_begin(int cls, double bytes, double flops);
+    void prof_end();
+    void prof_resolve();
 
     std::vector<LayerWeights> lw_;
     DeviceWeight token_embd_, output_;

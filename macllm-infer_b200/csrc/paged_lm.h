@@ -80,6 +80,17 @@ public:
     int last_lanes() const { return last_lanes_; }
     virtual float last_forward_ms() const { return 0.f; }
     virtual int64_t launch_count() const { return 0; }
+    // Host<->device bytes moved by forwards since load.
+    virtual int64_t h2d_bytes() const { return 0; }
+    virtual int64_t d2h_bytes() const { return 0; }
+    // Per-kernel-class device timing (CUDA events on the launching stream); off by default.
+    struct KernelProfile {
+        std::string name;
+        int64_t launches = 0;
+        double ms = 0, bytes = 0, flops = 0;
+    };
+    virtual void profile_enable(bool) {}
+    virtual std::vector<KernelProfile> profile_query() { return {}; }
     void validate_session(const LmSession& s) const;
 
 protected:

