@@ -346,6 +346,27 @@ int32_t mk_k_add_norm(float* h, const float* a, float a_scale, const float* post
  * W given as GGUF block bytes of `type`. */
 int32_t mk_k_qmatmul(int32_t type, const void* w, int64_t rows, int64_t cols, const float* x, int32_t T, float* y, int32_t path);
 
+/* Allocation-free tensor-core matmul for Q4_K weights.  This entry point has no counterpart in the
+ * reference; it exists for hosts that may not allocate GPU memory on the request path - a serving
+ * process that owns the whole device arena and forbids cudaMalloc there, or a sandboxed plugin whose
+ * allocations are rejected.  All pointers are DEVICE pointers supplied by the caller: w_q4k_dev is the
+ * matrix in GGUF Q4_K block bytes (144 bytes per 256 weights, row-major [rows][cols/256], 16-byte
+ * aligned), x_dev is [T][cols] f32, y_dev receives [T][rows] f32.  The kernel's working storage
+ * (quantised activations, split-K partial sums, status word) sits in fixed device arrays inside the
+ * library image, about 10 MiB on every GPU that loads the library, kept until the process exits.
+ * Limits: T * cols <= MK_NOALLOC_MAX_ACT_ELEMS and the split-K partial sums (at most 8 * T * rows
+ * floats) <= MK_NOALLOC_MAX_PARTIAL; anything larger is refused with a message.  The arrays are
+ * shared by every call and keep the previous call's contents (what must start at zero is cleared by
+ * the call itself), so calls that overlap on the GPU - other streams or other threads - race and must
+ * be serialised by the caller.  The first call on a device also looks up the arrays' device addresses;
+ * issue it before any stream capture begins.  The call returns after the result is complete on
+ * cuda_stream (a cudaStream_t, or NULL for the default stream).  It never calls cudaMalloc, cudaFree
+ * or any allocating library routine.  Same arithmetic as mk_k_qmatmul(MK_TYPE_Q4_K, ..., MK_PATH_TENSOR). */
+#define MK_NOALLOC_MAX_ACT_ELEMS 524288
+#define MK_NOALLOC_MAX_PARTIAL 2097152
+int32_t mk_k_q4k_matmul_tc_noalloc_dev(const void* w_q4k_dev, int64_t rows, int64_t cols, const float* x_dev, int32_t T, float* y_dev,
+                                       void* cuda_stream);
+
 /* TokenEmbedding::forward_validated (src/model_weights.rs:489-502). */
 int32_t mk_k_embed(int32_t type, const void* w, int64_t rows, int64_t cols, const uint32_t* ids, int32_t T, float scale, float* out);
 
