@@ -407,6 +407,8 @@ typedef struct mk_attn_case {
     int32_t* positions_out;       /* optional [T] */
     int32_t* last_index_out;      /* optional [lanes] */
     int32_t* cu_seqlens_out;      /* optional [lanes+1] */
+    int32_t kernel;               /* 0: what the model path would pick; 1: the scalar f32 kernel; 2: the tensor-core
+                                   * kernel (f16 pools, head_dim 64/128/256, group 1/2/4/8), refused otherwise */
 } mk_attn_case;
 int32_t mk_k_attention_step(const mk_attn_case* c);
 

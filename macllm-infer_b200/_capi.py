@@ -98,7 +98,8 @@ class AttnCase(C.Structure):
                 ("tables", C.c_void_p), ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("q_norm_w", C.c_void_p),
                 ("k_norm_w", C.c_void_p), ("cos_table", C.c_void_p), ("sin_table", C.c_void_p), ("k_pool", C.c_void_p),
                 ("v_pool", C.c_void_p), ("out", C.c_void_p), ("q_rot_out", C.c_void_p), ("slots_out", C.c_void_p),
-                ("positions_out", C.c_void_p), ("last_index_out", C.c_void_p), ("cu_seqlens_out", C.c_void_p)]
+                ("positions_out", C.c_void_p), ("last_index_out", C.c_void_p), ("cu_seqlens_out", C.c_void_p),
+                ("kernel", C.c_int32)]
 
 
 # Every symbol include/macllm_b200.h declares, with its ctypes signature (restype is int32 unless noted).

@@ -1,0 +1,386 @@
+// Tensor-core varlen paged GQA attention for f16 KV pools: prefill chunks and (split over the keys)
+// decode lanes.
+//
+// Same operator as attention.cu (the replacement of macllm_kernels::paged_attention_batch,
+// crates/macllm-kernels/src/paged_attention.rs:614-709, and of dense_causal_attention,
+// src/decoder.rs:4580-4670; visibility rule src/decoder.rs:4515-4532), restructured for bandwidth:
+// one CTA owns 16*WARPS (query row, query head) items that all read ONE KV head, so every K/V page
+// is fetched once for the whole query group; pages travel global -> shared with 16-byte cp.async in a
+// two-stage pipeline; Q.K^T and P.V run on the tensor cores (mma.sync m16n8k16, f16 operands, f32
+// accumulators) and the online softmax stays in f32 registers.  Decode lanes use one warp per CTA and
+// split the key range over CTAs (scratch: unnormalised partial outputs + running max / sum per item),
+// merged by attn_combine_kernel.  Queries are rounded to f16 once; K/V are read as stored.
+#include "kernels.h"
+#include "attention_tc.h"
+#include <algorithm>
+
+namespace mk {
+
+namespace {
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    int bytes = valid ? 16 : 0;  // src-size 0 zero-fills the 16 destination bytes
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_half2(float x, float y) {
+    __half2 h = __floats2half2_rn(x, y);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// One CTA.  D = head_dim, WARPS warps of 16 items each, KT keys per shared-memory tile.
+// SPLIT = false: work item = tiles[blockIdx.x] = (lane, first query row); the CTA walks every visible key
+//                and writes normalised outputs.
+// SPLIT = true : work item = entries[blockIdx.x] = (lane, split, n_splits) of a one-token lane; the CTA walks
+//                its share of the keys and writes an unnormalised partial.
+template <int D, int WARPS, int KT, bool SPLIT>
+__global__ void __launch_bounds__(WARPS * 32) attn_tc_kernel(AttnTcArgs a) {
+    constexpr int DP = D + 8;              // padded row (halves): conflict-free ldmatrix
+    constexpr int M = 16 * WARPS;
+    constexpr int NT_S = KT / 8;           // score n-tiles per warp
+    constexpr int NT_O = D / 8;            // output n-tiles per warp
+    constexpr int CHUNKS = D / 8;          // 16-byte chunks per K or V row
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __half* Qs = reinterpret_cast<__half*>(smem_raw);          // [M][DP]
+    __half* Ks = Qs + M * DP;                                   // [2][KT][DP]
+    __half* Vs = Ks + 2 * KT * DP;                              // [2][KT][DP]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int gid = lane >> 2, tq = lane & 3;
+    const int kvh = blockIdx.y;
+    const int g = a.q_heads / a.kv_heads;
+
+    int lane_id, row0, rows_per_head, split = 0, n_splits = 1;
+    if (SPLIT) {
+        lane_id = a.entries[3 * blockIdx.x];
+        split = a.entries[3 * blockIdx.x + 1];
+        n_splits = a.entries[3 * blockIdx.x + 2];
+        row0 = 0;
+        rows_per_head = 1;
+    } else {
+        lane_id = a.tiles[2 * blockIdx.x];
+        row0 = a.tiles[2 * blockIdx.x + 1];
+        rows_per_head = M / g;
+    }
+    const LaneHeader hdr = a.hdr[lane_id];
+    const int q_off = a.cu_seqlens[lane_id];
+    const int n_rows = SPLIT ? 1 : min(rows_per_head, hdr.n_tokens - row0);
+    const int ldq = a.q_heads * D;
+
+    // item i of the CTA: head-in-group i / rows_per_head, query row i % rows_per_head
+    for (int i = tid; i < M * CHUNKS; i += WARPS * 32) {
+        int item = i / CHUNKS, c = (i - item * CHUNKS) * 8;
+        int hq = item / rows_per_head, r = item - hq * rows_per_head;
+        __half2 h[4];
+        if (hq < g && r < n_rows) {
+            const float* src = a.q + (int64_t)(q_off + row0 + r) * ldq + (kvh * g + hq) * D + c;
+            float4 x0 = *reinterpret_cast<const float4*>(src), x1 = *reinterpret_cast<const float4*>(src + 4);
+            h[0] = __floats2half2_rn(x0.x, x0.y);
+            h[1] = __floats2half2_rn(x0.z, x0.w);
+            h[2] = __floats2half2_rn(x1.x, x1.y);
+            h[3] = __floats2half2_rn(x1.z, x1.w);
+        } else {
+            h[0] = h[1] = h[2] = h[3] = __floats2half2_rn(0.f, 0.f);
+        }
+        *reinterpret_cast<uint4*>(Qs + item * DP + c) = *reinterpret_cast<uint4*>(h);
+    }
+
+    // key range of this CTA
+    const int p_first = hdr.start_pos + row0, p_last = p_first + n_rows - 1;
+    int k_lo = a.window > 0 ? max(0, p_first - a.window + 1) : 0;
+    int k_hi = p_last + 1;
+    if (SPLIT) {
+        int len = k_hi - k_lo;
+        int chunk = ((len + n_splits - 1) / n_splits + 15) / 16 * 16;
+        k_lo = k_lo + split * chunk;
+        k_hi = min(k_hi, k_lo + chunk);
+    }
+    const int k_begin = k_lo / 16 * 16;  // page aligned
+    const int n_tiles = k_hi > k_begin ? (k_hi - k_begin + KT - 1) / KT : 0;
+
+    const __half* kp = reinterpret_cast<const __half*>(a.k_pool);
+    const __half* vp = reinterpret_cast<const __half*>(a.v_pool);
+    auto load_tile = [&](int t, int stage) {
+        __half* kd = Ks + stage * KT * DP;
+        __half* vd = Vs + stage * KT * DP;
+        for (int i = tid; i < KT * CHUNKS; i += WARPS * 32) {
+            int key = i / CHUNKS, c = (i - key * CHUNKS) * 8;
+            int pos = k_begin + t * KT + key;
+            bool valid = pos < k_hi;
+            int64_t base = 0;
+            if (valid) {
+                int64_t blk = a.tables[hdr.table_off + pos / a.block_tokens];
+                base = (((blk * a.layers + a.layer) * a.kv_heads + kvh) * a.block_tokens + pos % a.block_tokens) * (int64_t)D + c;
+            }
+            cp_async16(kd + key * DP + c, kp + base, valid);
+            cp_async16(vd + key * DP + c, vp + base, valid);
+        }
+    };
+
+    float o_acc[NT_O][4];
+#pragma unroll
+    for (int j = 0; j < NT_O; ++j) o_acc[j][0] = o_acc[j][1] = o_acc[j][2] = o_acc[j][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    // the two accumulator rows of this thread: items warp*16 + gid and + 8
+    int item_r[2] = {warp * 16 + gid, warp * 16 + gid + 8};
+    int pos_r[2];
+    bool live_r[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        int hq = item_r[h] / rows_per_head, r = item_r[h] - hq * rows_per_head;
+        live_r[h] = hq < g && r < n_rows;
+        pos_r[h] = p_first + r;
+    }
+
+    if (n_tiles > 0) load_tile(0, 0);
+    cp_async_commit();
+    for (int t = 0; t < n_tiles; ++t) {
+        if (t + 1 < n_tiles) load_tile(t + 1, (t + 1) & 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const __half* kt = Ks + (t & 1) * KT * DP;
+        const __half* vt = Vs + (t & 1) * KT * DP;
+
+        // S = Q K^T
+        float s[NT_S][4];
+#pragma unroll
+        for (int j = 0; j < NT_S; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            uint32_t af[4];
+            ldmatrix_x4(af, Qs + (warp * 16 + (lane & 15)) * DP + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int j = 0; j < NT_S; j += 2) {
+                uint32_t bf[4];
+                ldmatrix_x4(bf, kt + (j * 8 + (lane & 7) + (lane >> 4) * 8) * DP + kk * 16 + ((lane >> 3) & 1) * 8);
+                mma16816(s[j], af, bf[0], bf[1]);
+                mma16816(s[j + 1], af, bf[2], bf[3]);
+            }
+        }
+        // scale, softcap, mask, online softmax (f32)
+        const int tile_pos = k_begin + t * KT;
+        float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < NT_S; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                int h = e >> 1;
+                int pos = tile_pos + j * 8 + 2 * tq + (e & 1);
+                float v = s[j][e] * a.scale;
+                if (a.softcap != 0.f) v = tanhf(v / a.softcap) * a.softcap;
+                bool vis = live_r[h] && pos >= k_lo && pos < k_hi && pos <= pos_r[h] && (a.window == 0 || pos_r[h] - pos < a.window);
+                v = vis ? v : -INFINITY;
+                s[j][e] = v;
+                tmax[h] = fmaxf(tmax[h], v);
+            }
+        }
+        float alpha[2], m_use[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 1));
+            tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 2));
+            float m_new = fmaxf(m_run[h], tmax[h]);
+            m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+            alpha[h] = m_run[h] == -INFINITY ? 0.f : expf(m_run[h] - m_use[h]);
+            m_run[h] = m_new;
+        }
+        float psum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < NT_S; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                int h = e >> 1;
+                float p = s[j][e] == -INFINITY ? 0.f : expf(s[j][e] - m_use[h]);
+                s[j][e] = p;
+                psum[h] += p;
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], 1);
+            psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], 2);
+            l_run[h] = l_run[h] * alpha[h] + psum[h];
+        }
+#pragma unroll
+        for (int j = 0; j < NT_O; ++j) {
+            o_acc[j][0] *= alpha[0];
+            o_acc[j][1] *= alpha[0];
+            o_acc[j][2] *= alpha[1];
+            o_acc[j][3] *= alpha[1];
+        }
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < KT / 16; ++kk) {
+            uint32_t pf[4] = {pack_half2(s[2 * kk][0], s[2 * kk][1]), pack_half2(s[2 * kk][2], s[2 * kk][3]),
+                              pack_half2(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack_half2(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+#pragma unroll
+            for (int j = 0; j < NT_O; j += 2) {
+                uint32_t bf[4];
+                ldmatrix_x4_trans(bf, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * DP + j * 8 + (lane >> 4) * 8);
+                mma16816(o_acc[j], pf, bf[0], bf[1]);
+                mma16816(o_acc[j + 1], pf, bf[2], bf[3]);
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+
+    if (!SPLIT) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            if (!live_r[h]) continue;
+            int hq = item_r[h] / rows_per_head, r = item_r[h] - hq * rows_per_head;
+            float inv = 1.0f / l_run[h];
+            float* o = a.out + (int64_t)(q_off + row0 + r) * ldq + (kvh * g + hq) * D;
+#pragma unroll
+            for (int j = 0; j < NT_O; ++j)
+                *reinterpret_cast<float2*>(o + j * 8 + 2 * tq) = make_float2(o_acc[j][2 * h] * inv, o_acc[j][2 * h + 1] * inv);
+        }
+    } else {
+        // unnormalised partial of this key share: [entry][kv head][16 items][D], plus (max, sum) per item
+        int64_t slot = ((int64_t)blockIdx.x * a.kv_heads + kvh) * 16;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            int item = gid + 8 * h;
+            if (item >= g) continue;  // only the group's heads are live in a one-token lane
+            float* o = a.part_o + (slot + item) * D;
+#pragma unroll
+            for (int j = 0; j < NT_O; ++j)
+                *reinterpret_cast<float2*>(o + j * 8 + 2 * tq) = make_float2(o_acc[j][2 * h], o_acc[j][2 * h + 1]);
+            if (tq == 0) {
+                a.part_ml[(slot + item) * 2] = m_run[h];
+                a.part_ml[(slot + item) * 2 + 1] = l_run[h];
+            }
+        }
+    }
+}
+
+// Merge the key shares of one-token lanes: grid (decode lane, kv head), one warp per query head of the group.
+__global__ void attn_combine_kernel(AttnTcArgs a, int D) {
+    const int dl = blockIdx.x, kvh = blockIdx.y;
+    const int lane_id = a.dec_lanes[3 * dl], first = a.dec_lanes[3 * dl + 1], n_splits = a.dec_lanes[3 * dl + 2];
+    const int g = a.q_heads / a.kv_heads;
+    const int hq = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (hq >= g) return;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, a.part_ml[(((int64_t)(first + s) * a.kv_heads + kvh) * 16 + hq) * 2]);
+    float l = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float* ml = a.part_ml + (((int64_t)(first + s) * a.kv_heads + kvh) * 16 + hq) * 2;
+        if (ml[0] != -INFINITY) l += ml[1] * expf(ml[0] - m);
+    }
+    const int q_off = a.cu_seqlens[lane_id];
+    float* o = a.out + (int64_t)q_off * a.q_heads * D + (kvh * g + hq) * D;
+    for (int c = lane; c < D; c += 32) {
+        float acc = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            int64_t slot = ((int64_t)(first + s) * a.kv_heads + kvh) * 16 + hq;
+            float ms = a.part_ml[slot * 2];
+            if (ms != -INFINITY) acc += a.part_o[slot * D + c] * expf(ms - m);
+        }
+        o[c] = acc / l;
+    }
+}
+
+template <int D, int WARPS, int KT, bool SPLIT>
+void launch_variant(const AttnTcArgs& a, int n_work, cudaStream_t s) {
+    constexpr size_t smem = (size_t)(16 * WARPS + 4 * KT) * (D + 8) * sizeof(__half);
+    static bool configured = false;
+    if (!configured) {
+        MK_CUDA(cudaFuncSetAttribute(attn_tc_kernel<D, WARPS, KT, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    dim3 grid((unsigned)n_work, (unsigned)a.kv_heads);
+    attn_tc_kernel<D, WARPS, KT, SPLIT><<<grid, WARPS * 32, smem, s>>>(a);
+    MK_LAUNCH_CHECK();
+}
+
+template <int D>
+void launch_for_dim(const AttnTcArgs& a, int warps, cudaStream_t s) {
+    if (a.n_tiles > 0) {
+        if (warps == 8) launch_variant<D, 8, 64, false>(a, a.n_tiles, s);
+        else launch_variant<D, 4, 64, false>(a, a.n_tiles, s);
+    }
+    if (a.n_entries > 0) {
+        launch_variant<D, 1, 16, true>(a, a.n_entries, s);
+        dim3 grid((unsigned)a.n_dec_lanes, (unsigned)a.kv_heads);
+        attn_combine_kernel<<<grid, 32 * (a.q_heads / a.kv_heads), 0, s>>>(a, D);
+        MK_LAUNCH_CHECK();
+    }
+}
+
+}  // namespace
+
+bool attention_tc_supported(int q_heads, int kv_heads, int head_dim, bool kv_f16) {
+    int g = kv_heads > 0 ? q_heads / kv_heads : 0;
+    return kv_f16 && (head_dim == 64 || head_dim == 128 || head_dim == 256) && (g == 1 || g == 2 || g == 4 || g == 8) &&
+           q_heads == g * kv_heads;
+}
+
+int attention_tc_warps(int q_heads, int kv_heads) { return q_heads / kv_heads >= 4 ? (q_heads / kv_heads == 8 ? 8 : 4) : 4; }
+
+int attention_tc_tile_rows(int q_heads, int kv_heads) { return 16 * attention_tc_warps(q_heads, kv_heads) / (q_heads / kv_heads); }
+
+int attention_tc_max_entries(int lanes, int kv_heads) { return lanes + kAttnTargetCtas / kv_heads + 1; }
+
+void plan_attention_tc(const int32_t* start_pos, const int32_t* n_tokens, int lanes, int q_heads, int kv_heads, AttnTcPlan& plan) {
+    plan.tiles.clear();
+    plan.entries.clear();
+    plan.dec_lanes.clear();
+    const int tile_rows = attention_tc_tile_rows(q_heads, kv_heads);
+    int n_dec = 0;
+    for (int i = 0; i < lanes; ++i) n_dec += n_tokens[i] == 1 ? 1 : 0;
+    const int budget = std::max(1, kAttnTargetCtas / kv_heads / std::max(1, n_dec));
+    for (int i = 0; i < lanes; ++i) {
+        if (n_tokens[i] == 1) {
+            int ctx = start_pos[i] + 1;
+            int splits = std::max(1, std::min(std::min(budget, kAttnMaxSplits), (ctx + kAttnMinSplitKeys - 1) / kAttnMinSplitKeys));
+            plan.dec_lanes.push_back(i);
+            plan.dec_lanes.push_back(plan.n_entries());
+            plan.dec_lanes.push_back(splits);
+            for (int sidx = 0; sidx < splits; ++sidx) {
+                plan.entries.push_back(i);
+                plan.entries.push_back(sidx);
+                plan.entries.push_back(splits);
+            }
+        } else {
+            for (int r0 = 0; r0 < n_tokens[i]; r0 += tile_rows) {
+                plan.tiles.push_back(i);
+                plan.tiles.push_back(r0);
+            }
+        }
+    }
+}
+
+int launch_paged_attention_tc(const AttnTcArgs& a, cudaStream_t s) {
+    int warps = attention_tc_warps(a.q_heads, a.kv_heads);
+    switch (a.d) {
+        case 64: launch_for_dim<64>(a, warps, s); break;
+        case 128: launch_for_dim<128>(a, warps, s); break;
+        case 256: launch_for_dim<256>(a, warps, s); break;
+        default: throw std::runtime_error("launch_paged_attention_tc: unsupported head_dim");
+    }
+    return (a.n_tiles > 0 ? 1 : 0) + (a.n_entries > 0 ? 2 : 0);
+}
+
+}  // namespace mk

@@ -1,0 +1,53 @@
+// Tensor-core paged attention (see attention_tc.cu).
+#pragma once
+#include "kernels.h"
+#include <vector>
+
+namespace mk {
+
+struct AttnTcArgs {
+    const float* q = nullptr;   // [T][q_heads*d] f32
+    float* out = nullptr;       // [T][q_heads*d] f32
+    const void* k_pool = nullptr;  // f16 [blocks][layers][kv_heads][block_tokens][d]
+    const void* v_pool = nullptr;
+    const LaneHeader* hdr = nullptr;
+    const uint32_t* tables = nullptr;
+    const int32_t* cu_seqlens = nullptr;
+    // work lists (device): prefill tiles (lane, first row); decode entries (lane, split, n_splits);
+    // decode lanes (lane, first entry, n_splits)
+    const int32_t* tiles = nullptr;
+    const int32_t* entries = nullptr;
+    const int32_t* dec_lanes = nullptr;
+    int n_tiles = 0, n_entries = 0, n_dec_lanes = 0;
+    float* part_o = nullptr;    // [n_entries][kv_heads][16][d]
+    float* part_ml = nullptr;   // [n_entries][kv_heads][16][2]
+    int q_heads = 0, kv_heads = 0, d = 0, block_tokens = 16, layers = 0, layer = 0;
+    float scale = 1.f, softcap = 0.f;
+    int window = 0;
+};
+
+bool attention_tc_supported(int q_heads, int kv_heads, int head_dim, bool kv_f16);
+// Query rows of one prefill tile (the CTA covers rows x group heads = 16 * warps items).
+int attention_tc_tile_rows(int q_heads, int kv_heads);
+int attention_tc_warps(int q_heads, int kv_heads);
+
+// Host-side work lists of one tick (the same for every layer): lanes with more than one token are cut
+// into query tiles; one-token lanes split their keys over up to kAttnMaxSplits CTAs, at least
+// kAttnMinSplitKeys keys each, until about kAttnTargetCtas CTAs are in flight.
+constexpr int kAttnTargetCtas = 148 * 8;
+constexpr int kAttnMaxSplits = 16;
+constexpr int kAttnMinSplitKeys = 64;
+struct AttnTcPlan {
+    std::vector<int32_t> tiles, entries, dec_lanes;
+    int n_tiles() const { return (int)tiles.size() / 2; }
+    int n_entries() const { return (int)entries.size() / 3; }
+    int n_dec_lanes() const { return (int)dec_lanes.size() / 3; }
+};
+void plan_attention_tc(const int32_t* start_pos, const int32_t* n_tokens, int lanes, int q_heads, int kv_heads, AttnTcPlan& plan);
+// Upper bound of plan.n_entries() for a tick of at most `lanes` lanes.
+int attention_tc_max_entries(int lanes, int kv_heads);
+
+// Returns the number of kernels launched.
+int launch_paged_attention_tc(const AttnTcArgs& a, cudaStream_t s);
+
+}  // namespace mk

@@ -4,6 +4,7 @@
 #include "c_api_util.h"
 #include "device_util.h"
 #include "kernels.h"
+#include "attention_tc.h"
 #include "qgemm_tc.h"
 #include <vector>
 #include <cstring>
@@ -250,7 +251,50 @@ int32_t mk_k_attention_step(const mk_attn_case* c) {
         at.softcap = c->softcap;
         at.window = c->window;
         at.q_tile = q_tile;
-        launch_paged_attention(at, nullptr);
+        const bool tc_ok = attention_tc_supported(c->q_heads, c->kv_heads, d, c->kv_f16 != 0);
+        if (c->kernel == 2 && !tc_ok) throw std::runtime_error("mk_k_attention_step: the tensor-core kernel does not cover this shape");
+        if (c->kernel < 0 || c->kernel > 2) throw std::runtime_error("mk_k_attention_step: unknown kernel selector");
+        DevBuf work, part_o, part_ml;
+        if (tc_ok && c->kernel != 1) {
+            AttnTcPlan plan;
+            plan_attention_tc(c->start_pos, c->lane_len, lanes, c->q_heads, c->kv_heads, plan);
+            std::vector<int32_t> lists;
+            lists.insert(lists.end(), plan.tiles.begin(), plan.tiles.end());
+            lists.insert(lists.end(), plan.entries.begin(), plan.entries.end());
+            lists.insert(lists.end(), plan.dec_lanes.begin(), plan.dec_lanes.end());
+            work.alloc(std::max<size_t>(lists.size(), 1) * 4);
+            if (!lists.empty()) work.upload(lists.data(), lists.size() * 4);
+            part_o.alloc(std::max<size_t>((size_t)plan.n_entries() * c->kv_heads * 16 * d, 1) * 4);
+            part_ml.alloc(std::max<size_t>((size_t)plan.n_entries() * c->kv_heads * 32, 1) * 4);
+            AttnTcArgs ta;
+            ta.q = at.q;
+            ta.out = at.out;
+            ta.k_pool = at.k_pool;
+            ta.v_pool = at.v_pool;
+            ta.hdr = b.hdr;
+            ta.tables = b.tables;
+            ta.cu_seqlens = b.cu_seqlens;
+            ta.tiles = work.as<int32_t>();
+            ta.entries = ta.tiles + plan.tiles.size();
+            ta.dec_lanes = ta.entries + plan.entries.size();
+            ta.n_tiles = plan.n_tiles();
+            ta.n_entries = plan.n_entries();
+            ta.n_dec_lanes = plan.n_dec_lanes();
+            ta.part_o = part_o.as<float>();
+            ta.part_ml = part_ml.as<float>();
+            ta.q_heads = c->q_heads;
+            ta.kv_heads = c->kv_heads;
+            ta.d = d;
+            ta.block_tokens = c->block_tokens;
+            ta.layers = c->layers;
+            ta.layer = c->layer;
+            ta.scale = c->scale;
+            ta.softcap = c->softcap;
+            ta.window = c->window;
+            launch_paged_attention_tc(ta, nullptr);
+        } else {
+            launch_paged_attention(at, nullptr);
+        }
         MK_CUDA(cudaDeviceSynchronize());
 
         int32_t flag = 0;

@@ -6,6 +6,7 @@
 
 namespace mk {
 
+
 namespace {
 
 bool starts_with(const std::string& s, const std::string& p) { return s.compare(0, p.size(), p) == 0; }
@@ -176,6 +177,14 @@ Model::Model(const std::string& gguf_path, const ModelConfig& cfg) : cfg_(cfg) {
     consider(ms_.tied ? token_embd_.w : output_.w, B);
     tc_ws_.partial.alloc(std::max<size_t>(partial, 1) * 4);
     size_t stage_bytes = (size_t)B * sizeof(LaneHeader) + (size_t)(pool_->max_blocks() + B) * 4 + (size_t)T * 4 + 64;
+    attn_tc_ = attention_tc_supported(ms_.q_heads, ms_.kv_heads, ms_.head_dim, cfg_.kv_f16);
+    if (attn_tc_) {
+        attn_max_entries_ = attention_tc_max_entries(B, ms_.kv_heads);
+        attn_part_o_.alloc((size_t)attn_max_entries_ * ms_.kv_heads * 16 * ms_.head_dim * 4);
+        attn_part_ml_.alloc((size_t)attn_max_entries_ * ms_.kv_heads * 16 * 2 * 4);
+        // work lists: prefill tiles (2 ints), key-share entries (3 ints), one-token lanes (3 ints)
+        stage_bytes += ((size_t)(T + B) * 2 + (size_t)attn_max_entries_ * 3 + (size_t)B * 3) * 4;
+    }
     stage_host_.ensure(stage_bytes);
     stage_dev_.alloc(stage_bytes);
     out_host_.ensure((size_t)B * ms_.vocab * 4 + (size_t)B * 4 + 16);
@@ -419,6 +428,27 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         tpos += l.n_tokens;
     }
     size_t stage_bytes = off_ids + (size_t)T * 4;
+    // work lists of the tensor-core attention (the same for every layer of the tick)
+    size_t off_tiles = 0, off_entries = 0, off_dec = 0;
+    int n_attn_tiles = 0, n_attn_entries = 0, n_attn_dec = 0;
+    if (attn_tc_) {
+        plan_sp_.resize((size_t)B);
+        plan_nt_.resize((size_t)B);
+        for (int i = 0; i < B; ++i) { plan_sp_[(size_t)i] = lanes[(size_t)i].start_pos; plan_nt_[(size_t)i] = lanes[(size_t)i].n_tokens; }
+        plan_attention_tc(plan_sp_.data(), plan_nt_.data(), B, ms_.q_heads, ms_.kv_heads, attn_plan_);
+        n_attn_tiles = attn_plan_.n_tiles();
+        n_attn_entries = attn_plan_.n_entries();
+        n_attn_dec = attn_plan_.n_dec_lanes();
+        if (n_attn_entries > attn_max_entries_) throw std::runtime_error("attention work list exceeds its scratch");
+        off_tiles = (stage_bytes + 15) / 16 * 16;
+        off_entries = off_tiles + attn_plan_.tiles.size() * 4;
+        off_dec = off_entries + attn_plan_.entries.size() * 4;
+        stage_bytes = off_dec + attn_plan_.dec_lanes.size() * 4;
+        if (stage_bytes > stage_host_.size()) throw std::runtime_error("tick staging buffer is too small");
+        if (n_attn_tiles) memcpy(hp + off_tiles, attn_plan_.tiles.data(), attn_plan_.tiles.size() * 4);
+        if (n_attn_entries) memcpy(hp + off_entries, attn_plan_.entries.data(), attn_plan_.entries.size() * 4);
+        if (n_attn_dec) memcpy(hp + off_dec, attn_plan_.dec_lanes.data(), attn_plan_.dec_lanes.size() * 4);
+    }
     if (stage_bytes > stage_dev_.size()) throw std::runtime_error("tick staging buffer is too small");
     MK_CUDA(cudaEventRecord(ev_start_, stream_));
     MK_CUDA(cudaMemcpyAsync(stage_dev_.ptr(), hp, stage_bytes, cudaMemcpyHostToDevice, stream_));
@@ -541,9 +571,38 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
             for (const LmLane& ln : lanes) flops += 4.0 * ms_.q_heads * d * ((double)ln.n_tokens * ln.start_pos + 0.5 * ln.n_tokens * ln.n_tokens);
             prof_begin(KC_ATTN, kv_tokens * 2 * KW * esz + 8.0 * T * AW, flops);
         }
-        launch_paged_attention(at, stream_);
+        if (attn_tc_) {
+            AttnTcArgs ta;
+            ta.q = at.q;
+            ta.out = at.out;
+            ta.k_pool = at.k_pool;
+            ta.v_pool = at.v_pool;
+            ta.hdr = bd.hdr;
+            ta.tables = bd.tables;
+            ta.cu_seqlens = bd.cu_seqlens;
+            ta.tiles = reinterpret_cast<const int32_t*>(dp + off_tiles);
+            ta.entries = reinterpret_cast<const int32_t*>(dp + off_entries);
+            ta.dec_lanes = reinterpret_cast<const int32_t*>(dp + off_dec);
+            ta.n_tiles = n_attn_tiles;
+            ta.n_entries = n_attn_entries;
+            ta.n_dec_lanes = n_attn_dec;
+            ta.part_o = attn_part_o_.as<float>();
+            ta.part_ml = attn_part_ml_.as<float>();
+            ta.q_heads = ms_.q_heads;
+            ta.kv_heads = ms_.kv_heads;
+            ta.d = d;
+            ta.block_tokens = bt;
+            ta.layers = ms_.layers;
+            ta.layer = l;
+            ta.scale = ls.scale;
+            ta.softcap = ls.softcap;
+            ta.window = ls.window;
+            launches_ += launch_paged_attention_tc(ta, stream_);
+        } else {
+            launch_paged_attention(at, stream_);
+            ++launches_;
+        }
         prof_end();
-        ++launches_;
         // output projection
         int okind = act_kind_of(w.wo.w);
         ActQ xo = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, AW, okind, f16_T);

@@ -8,6 +8,7 @@
 #include "kernels.h"
 #include "paged_lm.h"
 #include "qgemm_tc.h"
+#include "attention_tc.h"
 
 namespace mk {
 
@@ -105,6 +106,12 @@ private:
     PinnedBuf stage_host_;
     DevBuf stage_dev_;
     DevBuf cu_, pos_, tok_lane_, slots_, last_, tile_lane_, tile_row_, ntiles_, err_;
+    // tensor-core attention: split-KV partials of one-token lanes
+    DevBuf attn_part_o_, attn_part_ml_;
+    bool attn_tc_ = false;
+    int attn_max_entries_ = 0;
+    AttnTcPlan attn_plan_;
+    std::vector<int32_t> plan_sp_, plan_nt_;
     // activations
     DevBuf h_, q_, k_, v_, attn_, proj_, gate_, up_, down_, normed_, logits_, tokens_;
     DevBuf a_qs_, a_d_, a_bs_, a_xh_;   // quantised activations of width hidden / attention width

@@ -100,7 +100,7 @@ def moe_route(logits, k: int):
 
 def attention_step(q, k, v, k_pool, v_pool, tables, start_pos, lane_len, *, q_heads, kv_heads, head_dim, block_tokens,
                    layers, layer, scale, softcap=0.0, window=0, cos_table=None, sin_table=None, rotary_dim=0,
-                   q_norm_w=None, k_norm_w=None, norm_eps=1e-6):
+                   q_norm_w=None, k_norm_w=None, norm_eps=1e-6, kernel=0):
     """One attention layer step of a ragged batch.  `tables` is a list of per-lane block-id lists.
     k_pool / v_pool ([blocks, layers, kv_heads, block_tokens, head_dim], f16 or f32) are updated in place.
     Returns dict(out, q_rot, slots, positions, last_index, cu_seqlens)."""
@@ -138,6 +138,7 @@ def attention_step(q, k, v, k_pool, v_pool, tables, start_pos, lane_len, *, q_he
     c.rotary_dim = rotary_dim if cos_table is not None else 0
     c.rope_capacity = 0 if cos_table is None else cos_table.shape[0]
     c.norm_eps = norm_eps
+    c.kernel = kernel  # 0 auto, 1 scalar f32 kernel, 2 tensor-core kernel
     for name, arr in (("start_pos", sp), ("lane_len", ll), ("table_off", to), ("table_len", tl), ("tables", tab), ("q", q),
                       ("k", k), ("v", v), ("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w), ("cos_table", cos_table),
                       ("sin_table", sin_table), ("k_pool", k_pool), ("v_pool", v_pool), ("out", out), ("q_rot_out", q_rot),

@@ -202,6 +202,44 @@ def test_attention_step_matches_oracle(ops, orc, kv_dtype, geom, window, softcap
         assert np.max(np.abs(res["out"] - want)) < (2e-5 if kv_dtype == np.float32 else 2e-3)
 
 
+@pytest.mark.parametrize("geom", [(32, 4, 64), (16, 4, 128), (8, 4, 128), (4, 4, 64), (16, 8, 256)])
+@pytest.mark.parametrize("window,softcap,bt", [(0, 0.0, 16), (100, 0.0, 16), (0, 30.0, 32)])
+def test_tensor_core_attention_long_contexts(ops, orc, geom, window, softcap, bt):
+    """The tensor-core kernel on its own (kernel=2): prefill chunks that span several query tiles and key
+    tiles, one-token lanes long enough to be split over several CTAs, against the oracle and against
+    the scalar kernel (kernel=1) on the same pools."""
+    q_heads, kv_heads, d = geom
+    layers, layer = 2, 1
+    rng = np.random.default_rng(q_heads * 77 + d + window + bt)
+    lanes_spec = [(0, 150), (700, 1), (333, 200), (1500, 1), (63, 1), (64, 1), (0, 1), (129, 67), (2047, 1)]
+    tables, k_pool, v_pool, q, k, v = _attn_case(rng, lanes_spec, q_heads, kv_heads, d, bt, layers, layer, np.float16)
+    scale = 1.0 / np.sqrt(d)
+    outs = {}
+    for kernel in (1, 2):
+        kp, vp = k_pool.copy(), v_pool.copy()
+        res = ops.attention_step(q, k, v, kp, vp, tables, [s for s, _ in lanes_spec], [n for _, n in lanes_spec],
+                                 q_heads=q_heads, kv_heads=kv_heads, head_dim=d, block_tokens=bt, layers=layers, layer=layer,
+                                 scale=scale, softcap=softcap, window=window, kernel=kernel)
+        outs[kernel] = res["out"]
+    flat = np.concatenate(tables).astype(np.uint32)
+    page_off = np.concatenate([[0], np.cumsum([len(t) for t in tables])[:-1]]).astype(np.int32)
+    want = orc.paged_attention(q, kp, vp, flat, page_off, [s for s, _ in lanes_spec], [n for _, n in lanes_spec],
+                               q_heads=q_heads, kv_heads=kv_heads, d=d, block_tokens=bt, layers=layers, layer=layer,
+                               scale=scale, softcap=softcap, window=window, mode=0)
+    assert np.isfinite(outs[2]).all()
+    assert np.max(np.abs(outs[1] - want)) < 2e-5
+    # queries and probabilities are rounded to f16 for the tensor cores: 2^-11 relative on operands of size <= 1
+    assert np.max(np.abs(outs[2] - want)) < 2e-3
+
+
+def test_tensor_core_attention_is_refused_for_f32_pools(ops):
+    rng = np.random.default_rng(3)
+    tables, k_pool, v_pool, q, k, v = _attn_case(rng, [(0, 4)], 4, 2, 64, 16, 1, 0, np.float32)
+    with pytest.raises(RuntimeError, match="does not cover"):
+        ops.attention_step(q, k, v, k_pool, v_pool, tables, [0], [4], q_heads=4, kv_heads=2, head_dim=64, block_tokens=16,
+                           layers=1, layer=0, scale=0.125, kernel=2)
+
+
 def test_attention_nope_layer_leaves_queries_unrotated(ops, orc):
     rng = np.random.default_rng(9)
     q_heads, kv_heads, d, bt = 8, 2, 64, 16
