@@ -42,7 +42,8 @@ extern "C" {
 /* Matmul path selection for mk_k_qmatmul. */
 #define MK_PATH_AUTO 0
 #define MK_PATH_GEMV 1   /* integer dp4a kernel */
-#define MK_PATH_TENSOR 2 /* tcgen05 kernel */
+#define MK_PATH_TENSOR 2 /* tcgen05 kernel, GGUF blocks dequantised inside the kernel */
+#define MK_PATH_HALF 3   /* tcgen05 kernel over an f16 image of the matrix built at load time (wide batches) */
 
 typedef struct mk_model mk_model;
 typedef struct mk_session mk_session;
@@ -70,7 +71,7 @@ typedef struct mk_load_config {
     int32_t kv_dtype;                /* MK_TYPE_F16 or MK_TYPE_F32 */
     int32_t max_batch_tokens;        /* largest packed token count of one forward */
     int32_t max_batch_lanes;         /* largest lane count of one forward */
-    int32_t matmul_path;             /* MK_PATH_AUTO / MK_PATH_GEMV / MK_PATH_TENSOR */
+    int32_t matmul_path;             /* MK_PATH_AUTO / MK_PATH_GEMV / MK_PATH_TENSOR / MK_PATH_HALF */
 } mk_load_config;
 
 /* CausalLm::runtime_spec (src/architecture.rs:312-316,1039). */
@@ -345,6 +346,12 @@ int32_t mk_k_add_norm(float* h, const float* a, float a_scale, const float* post
 /* LinearOp::forward for a quantised matrix (src/model_weights.rs:346-377): y [T][rows] = x [T][cols] . W^T,
  * W given as GGUF block bytes of `type`. */
 int32_t mk_k_qmatmul(int32_t type, const void* w, int64_t rows, int64_t cols, const float* x, int32_t T, float* y, int32_t path);
+
+/* The same matmul left on the device and launched `iters` times after two untimed launches, each timed with
+ * CUDA events and the L2 flushed before it; avg_ms is the mean launch duration.  A measuring aid for
+ * choosing between the paths; it has no counterpart in the reference. */
+int32_t mk_k_qmatmul_time(int32_t type, const void* w, int64_t rows, int64_t cols, const float* x, int32_t T, int32_t path,
+                          int32_t iters, float* avg_ms);
 
 /* Allocation-free tensor-core matmul for Q4_K weights.  This entry point has no counterpart in the
  * reference; it exists for hosts that may not allocate GPU memory on the request path - a serving

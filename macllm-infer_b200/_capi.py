@@ -14,7 +14,7 @@ LIB_PATH = HERE / "libmacllm_b200.so"
 
 MK_OK, MK_KV_EXHAUSTED = 0, 1
 TYPE_F32, TYPE_F16, TYPE_Q8_0, TYPE_Q4_K, TYPE_Q6_K = 0, 1, 8, 12, 14
-PATH_AUTO, PATH_GEMV, PATH_TENSOR = 0, 1, 2
+PATH_AUTO, PATH_GEMV, PATH_TENSOR, PATH_HALF = 0, 1, 2, 3
 FWD_WANT_LOGITS, FWD_WANT_TOKENS = 1, 2
 
 
@@ -171,6 +171,7 @@ SIGNATURES = {
     "mk_k_quantize": (_i32, [_i32, P, _i32, _i32, P, P, P]),
     "mk_k_add_norm": (_i32, [P, P, _f32, P, P, _f32, _i32, _i32, P]),
     "mk_k_qmatmul": (_i32, [_i32, P, _i64, _i64, P, _i32, P, _i32]),
+    "mk_k_qmatmul_time": (_i32, [_i32, P, _i64, _i64, P, _i32, _i32, _i32, C.POINTER(_f32)]),
     "mk_k_q4k_matmul_tc_noalloc_dev": (_i32, [P, _i64, _i64, P, _i32, P, P]),
     "mk_k_embed": (_i32, [_i32, P, _i64, _i64, P, _i32, _f32, P]),
     "mk_k_actmul": (_i32, [P, P, _i32, _i32, _i32, P]),

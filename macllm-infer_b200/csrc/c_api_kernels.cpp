@@ -4,6 +4,7 @@
 #include "c_api_util.h"
 #include "device_util.h"
 #include "kernels.h"
+#include "hgemm_tc.h"
 #include "attention_tc.h"
 #include "qgemm_tc.h"
 #include <vector>
@@ -86,39 +87,85 @@ int32_t mk_k_add_norm(float* h, const float* a, float a_scale, const float* post
     });
 }
 
+namespace {
+
+// Shared body of mk_k_qmatmul and mk_k_qmatmul_time: upload, quantise the activations once, then run the
+// chosen matmul `iters` times (timed one by one with the L2 flushed in between when avg_ms is wanted).
+void qmatmul_case(int32_t type, const void* w, int64_t rows, int64_t cols, const float* x, int32_t T, float* y, int32_t path,
+                  int iters, float* avg_ms) {
+    require_device();
+    if (path < MK_PATH_AUTO || path > MK_PATH_HALF) throw std::runtime_error("mk_k_qmatmul: unknown path selector");
+    DeviceWeight dw;
+    upload_weight(type, w, rows, cols, dw);
+    int kind = act_kind_for(type);
+    DevBuf dx((size_t)T * cols * 4), dy((size_t)T * rows * 4);
+    dx.upload(x, (size_t)T * cols * 4);
+    ActBufs ab;
+    const bool half = path == MK_PATH_HALF;
+    if (half) {
+        if (!hgemm_tc_supported(dw.w)) throw std::runtime_error("mk_k_qmatmul: the f16-image GEMM does not cover this matrix");
+        build_half_weight(dw.w, dw.half, nullptr);
+    }
+    const bool tensor = !half && (path == MK_PATH_TENSOR || (path == MK_PATH_AUTO && qgemm_tc_preferred(dw.w, T)));
+    ActQ a = ab.view(T, (int)cols, kind, tensor || half);
+    NormQuantArgs na;
+    na.h = dx.as<float>();
+    na.rows = T;
+    na.dim = (int)cols;
+    na.act_kind = kind;
+    na.out = a;
+    launch_add_norm_quant(na, nullptr);
+    QgemmWorkspace ws;
+    ws.status.alloc(sizeof(int32_t));
+    ws.status.zero(nullptr);
+    auto run = [&] {
+        if (half) launch_hgemm_tc(dw.half, a.xh, T, dy.as<float>(), (int)rows, 1.0f, 0.f, ws.status.as<int32_t>(), nullptr);
+        else if (tensor) launch_qgemm_tc(dw.w, a, kind, T, dy.as<float>(), (int)rows, 1.0f, 0.f, ws, nullptr);
+        else launch_qgemv(dw.w, a, T, dy.as<float>(), (int)rows, 1.0f, 0.f, nullptr);
+    };
+    if (avg_ms == nullptr) {
+        run();
+    } else {
+        DevBuf flush((size_t)256 << 20);  // larger than the L2
+        cudaEvent_t e0, e1;
+        MK_CUDA(cudaEventCreate(&e0));
+        MK_CUDA(cudaEventCreate(&e1));
+        double total = 0;
+        for (int i = 0; i < iters + 2; ++i) {
+            flush.zero(nullptr);
+            MK_CUDA(cudaEventRecord(e0, nullptr));
+            run();
+            MK_CUDA(cudaEventRecord(e1, nullptr));
+            MK_CUDA(cudaEventSynchronize(e1));
+            float ms = 0;
+            MK_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+            if (i >= 2) total += ms;
+        }
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        *avg_ms = (float)(total / iters);
+    }
+    MK_CUDA(cudaDeviceSynchronize());
+    int32_t st = 0;
+    ws.status.download(&st, 4);
+    MK_CUDA(cudaDeviceSynchronize());
+    if (st != 0) throw std::runtime_error("tensor-core matmul: a bounded wait inside the kernel gave up (status " + std::to_string(st) + ")");
+    if (y != nullptr) dy.download(y, (size_t)T * rows * 4);
+    MK_CUDA(cudaDeviceSynchronize());
+}
+
+}  // namespace
+
 int32_t mk_k_qmatmul(int32_t type, const void* w, int64_t rows, int64_t cols, const float* x, int32_t T, float* y,
                      int32_t path) {
+    return guarded([&] { qmatmul_case(type, w, rows, cols, x, T, y, path, 1, nullptr); });
+}
+
+int32_t mk_k_qmatmul_time(int32_t type, const void* w, int64_t rows, int64_t cols, const float* x, int32_t T, int32_t path,
+                          int32_t iters, float* avg_ms) {
     return guarded([&] {
-        require_device();
-        DeviceWeight dw;
-        upload_weight(type, w, rows, cols, dw);
-        int kind = act_kind_for(type);
-        DevBuf dx((size_t)T * cols * 4), dy((size_t)T * rows * 4);
-        dx.upload(x, (size_t)T * cols * 4);
-        ActBufs ab;
-        bool tensor = path == MK_PATH_TENSOR || (path == MK_PATH_AUTO && qgemm_tc_preferred(dw.w, T));
-        ActQ a = ab.view(T, (int)cols, kind, tensor);
-        NormQuantArgs na;
-        na.h = dx.as<float>();
-        na.rows = T;
-        na.dim = (int)cols;
-        na.act_kind = kind;
-        na.out = a;
-        launch_add_norm_quant(na, nullptr);
-        if (tensor) {
-            QgemmWorkspace ws;
-            launch_qgemm_tc(dw.w, a, kind, T, dy.as<float>(), (int)rows, 1.0f, 0.f, ws, nullptr);
-            MK_CUDA(cudaDeviceSynchronize());
-            int32_t st = 0;
-            ws.status.download(&st, 4);
-            MK_CUDA(cudaDeviceSynchronize());
-            if (st != 0) throw std::runtime_error("qgemm_tc: a bounded wait inside the kernel gave up (status " + std::to_string(st) + ")");
-        } else {
-            launch_qgemv(dw.w, a, T, dy.as<float>(), (int)rows, 1.0f, 0.f, nullptr);
-        }
-        MK_CUDA(cudaDeviceSynchronize());
-        dy.download(y, (size_t)T * rows * 4);
-        MK_CUDA(cudaDeviceSynchronize());
+        if (iters <= 0 || avg_ms == nullptr) throw std::runtime_error("mk_k_qmatmul_time: iters must be positive and avg_ms non-null");
+        qmatmul_case(type, w, rows, cols, x, T, nullptr, path, iters, avg_ms);
     });
 }
 

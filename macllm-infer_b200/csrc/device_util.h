@@ -61,10 +61,20 @@ private:
     size_t n_ = 0;
 };
 
+// The f16 image of one weight matrix [rows][cols] plus the TMA descriptor of its 128-row x 64-column
+// boxes (see hgemm_tc.h).  Built once at load time from the device copy of the quantised matrix.
+struct HalfWeight {
+    DevBuf values;               // rows * cols halves, row-major
+    int64_t rows = 0, cols = 0;
+    alignas(64) unsigned char tmap[128] = {};  // CUtensorMap (opaque here, 64-byte aligned)
+    bool ready = false;
+};
+
 // A weight matrix uploaded to HBM in the layout the kernels read (see QWeight).
 struct DeviceWeight {
     QWeight w;
     DevBuf b0, b1, b2, b3;
+    HalfWeight half;  // optional second copy for wide batches
 };
 
 // Upload `rows` x `cols` weights stored in GGUF block format `type` at host pointer `src`.

@@ -1,0 +1,426 @@
+// Wide-batch matmul on the tcgen05 tensor cores over an f16 image of the weights.
+//
+// Replaces LinearOp::Quantized forward (src/model_weights.rs:346-377 of the reference) for prefill
+// chunks: when hundreds of activation rows share one pass over a matrix, dequantising the GGUF blocks
+// inside the GEMM repeats that work once per 128 tokens and the CUDA cores, not the tensor cores,
+// set the pace.  A B200 has room to keep a second, f16 copy of every matrix (2 bytes per weight), made
+// once at load time: w = f16(dequant(block)), one rounding per weight.  The GEMM is then the plain
+// y[t][n] = sum_k xh[t][k] * wh[n][k] with f32 accumulation in tensor memory.
+//
+// One persistent CTA per SM, 192 threads in three roles:
+//   warp 0   - one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of a 128 x 64 weight
+//              box and a BN x 64 activation box per stage into a ring of shared-memory stages;
+//   warp 1   - one lane issues the MMAs (tcgen05.mma kind::f16, M = 128 weight rows, N = BN tokens,
+//              four K = 16 steps per stage), commits each stage back to the loader, and commits the tile
+//              to the epilogue; two accumulators in tensor memory alternate so the next tile's main
+//              loop runs under the previous tile's epilogue;
+//   warps 2-5 - read the accumulator (tcgen05.ld, one lane per weight row), apply scale / soft cap and
+//              store f32 results (32 consecutive rows of one token per store instruction).
+// Every mbarrier wait is bounded; a wait that gives up records a status word and the role leaves its
+// loop, the other roles run into their own limits, and tensor memory is always released.
+#include "hgemm_tc.h"
+#include "kernels.h"
+#include <cuda.h>
+#include <mutex>
+
+namespace mk {
+
+namespace {
+
+constexpr int HG_BM = 128;
+constexpr int HG_BK = 64;  // 64 halves = 128 bytes = one swizzle row
+constexpr int HG_THREADS = 192;
+constexpr uint32_t HG_SPIN_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit) {
+    uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i <= limit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// One 2-D box, no multicast: lands in this CTA's shared memory and completes bytes on its mbarrier.
+__device__ __forceinline__ void tma_load_2d(void* dst, const void* tmap, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+// K-major operand tile with 128-byte rows and the 128-byte swizzle: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;                    // leading byte offset: unused for swizzled K-major tiles
+    d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset
+    d |= (uint64_t)1 << 46;                    // descriptor version for sm_100
+    d |= (uint64_t)2 << 61;                    // layout type: 128-byte swizzle
+    return d;
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+// ---- load-time dequantisation to f16 (values as the reference's dequantize: crates candle k_quants
+// to_float order of operations: (d * scale) * q - (dmin * min) in f32, then one rounding to f16) -------
+
+__device__ __forceinline__ void q4k_scale_min(const uint8_t* sc, int j, int& s, int& m) {
+    if (j < 4) {
+        s = sc[j] & 63;
+        m = sc[j + 4] & 63;
+    } else {
+        s = (sc[j + 4] & 0xF) | ((sc[j - 4] >> 6) << 4);
+        m = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4);
+    }
+}
+
+// One warp per 256-element block; lane l produces elements 8l .. 8l+7.
+__global__ void dequant_f16_kernel(QWeight W, __half* out) {
+    const int64_t nb = W.cols / 256;
+    const int64_t b = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (b >= W.rows * nb) return;
+    const int lane = threadIdx.x & 31;
+    __half h[8];
+    if (W.type == QT_Q4_K) {
+        const uint8_t* blk = (const uint8_t*)W.p0 + b * 144;
+        float d = __half2float(*reinterpret_cast<const __half*>(blk));
+        float dmin = __half2float(*reinterpret_cast<const __half*>(blk + 2));
+        int j = lane >> 2;  // 32-element group
+        int s, m;
+        q4k_scale_min(blk + 4, j, s, m);
+        float d1 = __fmul_rn(d, (float)s), m1 = __fmul_rn(dmin, (float)m);
+        const uint8_t* qs = blk + 16 + (j >> 1) * 32 + (lane & 3) * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            int q = (j & 1) ? (qs[i] >> 4) : (qs[i] & 0xF);
+            h[i] = __float2half_rn(__fsub_rn(__fmul_rn(d1, (float)q), m1));
+        }
+    } else if (W.type == QT_Q6_K) {
+        const uint8_t* ql = (const uint8_t*)W.p0 + b * 128;
+        const uint8_t* qh = (const uint8_t*)W.p1 + b * 64;
+        const int8_t* sc = (const int8_t*)W.p2 + b * 16;
+        float d = __half2float(((const __half*)W.p3)[b]);
+        int e0 = lane * 8;
+        int hf = e0 >> 7, r = e0 & 127;     // 128-element half, offset inside it
+        int grp = r >> 5, l0 = r & 31;       // which of the four 32-element quarters, first l
+        float ds = __fmul_rn(d, (float)sc[hf * 8 + (l0 >> 4) + 2 * grp]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            int l = l0 + i;
+            uint8_t lo = ql[hf * 64 + (grp & 1) * 32 + l];
+            int nib = (grp >> 1) ? (lo >> 4) : (lo & 0xF);
+            int q = (nib | (((qh[hf * 32 + l] >> (2 * grp)) & 3) << 4)) - 32;
+            h[i] = __float2half_rn(__fmul_rn(ds, (float)q));
+        }
+    } else if (W.type == QT_Q8_0) {
+        int64_t row = b / nb, ib = b - row * nb;
+        const int8_t* qs = (const int8_t*)W.p0 + row * W.cols + ib * 256 + lane * 8;
+        float d = __half2float(((const __half*)W.p1)[row * (W.cols / 32) + ib * 8 + (lane >> 2)]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] = __float2half_rn(__fmul_rn(d, (float)qs[i]));
+    } else {  // QT_F32
+        const float* src = (const float*)W.p0 + b * 256 + lane * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] = __float2half_rn(src[i]);
+    }
+    *reinterpret_cast<uint4*>(out + b * 256 + lane * 8) = *reinterpret_cast<uint4*>(h);
+}
+
+// ---- the GEMM ------------------------------------------------------------------------------------
+
+struct HgParams {
+    int T, K, rows;
+    float* y;
+    int ldy;
+    float out_scale, softcap;
+    int row_tiles, n_tiles;
+    int32_t* status;
+};
+
+template <int BN, int STAGES>
+struct HgSmem {
+    static constexpr int A_BYTES = HG_BM * HG_BK * 2;   // 16 KiB
+    static constexpr int B_BYTES = BN * HG_BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr size_t TOTAL = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(HG_THREADS, 1)
+hgemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, HgParams p) {
+    using L = HgSmem<BN, STAGES>;
+    extern __shared__ uint8_t hg_smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(hg_smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + (size_t)STAGES * L::STAGE_BYTES);
+    uint64_t* full = bars;                  // [STAGES]  loader -> MMA
+    uint64_t* empty = bars + STAGES;        // [STAGES]  MMA -> loader
+    uint64_t* acc_full = bars + 2 * STAGES; // [2]       MMA -> epilogue
+    uint64_t* acc_empty = acc_full + 2;     // [2]       epilogue -> MMA
+    __shared__ uint32_t tmem_base_slot;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_blocks = p.K / HG_BK;
+    const int total_tiles = p.row_tiles * p.n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], 128);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                     "r"((uint32_t)(2 * BN))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ---- loader
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m_tile = tile % p.row_tiles, n_tile = tile / p.row_tiles;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t st = it % STAGES, ph = (it / STAGES) & 1;
+                    if (!mbar_wait(&empty[st], ph ^ 1, HG_SPIN_LIMIT)) {
+                        atomicExch(p.status, 11);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* a_dst = tiles + (size_t)st * L::STAGE_BYTES;
+                    uint8_t* b_dst = a_dst + L::A_BYTES;
+                    mbar_expect_tx(&full[st], (uint32_t)L::STAGE_BYTES);
+                    tma_load_2d(a_dst, &tm_w, kb * HG_BK, m_tile * HG_BM, &full[st]);
+                    tma_load_2d(b_dst, &tm_x, kb * HG_BK, n_tile * BN, &full[st]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(HG_BM >> 4) << 24);
+            uint32_t it = 0, tile_it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_it) {
+                const uint32_t acc = tile_it & 1, acc_ph = (tile_it >> 1) & 1;
+                if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1, HG_SPIN_LIMIT)) {
+                    atomicExch(p.status, 12);
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t st = it % STAGES, ph = (it / STAGES) & 1;
+                    if (!mbar_wait(&full[st], ph, HG_SPIN_LIMIT)) {
+                        atomicExch(p.status, 13);
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(tiles + (size_t)st * L::STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + L::A_BYTES;
+                    const uint64_t adesc = make_sw128_desc(a_addr), bdesc = make_sw128_desc(b_addr);
+#pragma unroll
+                    for (int k = 0; k < HG_BK / 16; ++k) {
+                        // 16 halves = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
+                        umma_f16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty[st]);
+                }
+                if (ok) umma_commit(&acc_full[acc]);
+            }
+        }
+    } else {
+        // ---- epilogue: warps 2..5 own TMEM lane quadrants (warp % 4)
+        const int quad = warp & 3;
+        uint32_t tile_it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tile_it) {
+            const int m_tile = tile % p.row_tiles, n_tile = tile / p.row_tiles;
+            const uint32_t acc = tile_it & 1, acc_ph = (tile_it >> 1) & 1;
+            if (!mbar_wait(&acc_full[acc], acc_ph, HG_SPIN_LIMIT)) {
+                if (lane == 0) atomicExch(p.status, 14);
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = m_tile * HG_BM + quad * 32 + lane;
+            const int tok0 = n_tile * BN;
+#pragma unroll 1
+            for (int cb = 0; cb < BN; cb += 32) {
+                if (tok0 + cb >= p.T) break;  // uniform over the CTA: nothing but padding from here on
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + (uint32_t)cb, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < p.rows) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        int tok = tok0 + cb + i;
+                        if (tok < p.T) {
+                            float v = __uint_as_float(r[i]) * p.out_scale;
+                            if (p.softcap != 0.f) v = tanhf(v * (1.0f / p.softcap)) * p.softcap;
+                            p.y[(int64_t)tok * p.ldy + row] = v;
+                        }
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&acc_empty[acc]);
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q);
+        if (e == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    if (fn == nullptr) throw std::runtime_error("the CUDA driver does not provide cuTensorMapEncodeTiled");
+    return fn;
+}
+
+// f16 matrix [n_rows][cols] row-major, boxes of box_rows x 64 columns, 128-byte swizzle, zero fill.
+void encode_half_matrix(CUtensorMap* out, const void* base, int64_t n_rows, int64_t cols, int box_rows) {
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) throw std::runtime_error("hgemm: matrix base must be 16-byte aligned");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)n_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)HG_BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = encode_fn()(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+}
+
+template <int BN, int STAGES>
+void launch_hg(const CUtensorMap& tw, const CUtensorMap& tx, const HgParams& p, int grid, cudaStream_t s) {
+    constexpr size_t smem = HgSmem<BN, STAGES>::TOTAL;
+    static bool configured = false;
+    if (!configured) {
+        MK_CUDA(cudaFuncSetAttribute(hgemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    hgemm_tc_kernel<BN, STAGES><<<grid, HG_THREADS, smem, s>>>(tw, tx, p);
+    MK_LAUNCH_CHECK();
+}
+
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        MK_CUDA(cudaGetDevice(&dev));
+        MK_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    }
+    return n;
+}
+
+}  // namespace
+
+bool hgemm_tc_supported(const QWeight& W) {
+    if (W.type != QT_Q4_K && W.type != QT_Q6_K && W.type != QT_Q8_0 && W.type != QT_F32) return false;
+    return W.cols % 256 == 0 && W.rows > 0;
+}
+
+void build_half_weight(const QWeight& W, HalfWeight& out, cudaStream_t s) {
+    if (!hgemm_tc_supported(W)) throw std::runtime_error("build_half_weight: unsupported matrix");
+    out.rows = W.rows;
+    out.cols = W.cols;
+    out.values.alloc(half_weight_bytes(W));
+    const int64_t blocks = W.rows * (W.cols / 256);
+    const int warps_per_cta = 8;
+    dequant_f16_kernel<<<(unsigned)((blocks + warps_per_cta - 1) / warps_per_cta), warps_per_cta * 32, 0, s>>>(W, out.values.as<__half>());
+    MK_LAUNCH_CHECK();
+    static_assert(sizeof(CUtensorMap) <= sizeof(out.tmap), "descriptor storage too small");
+    encode_half_matrix(reinterpret_cast<CUtensorMap*>(out.tmap), out.values.ptr(), W.rows, W.cols, HG_BM);
+    out.ready = true;
+}
+
+void launch_hgemm_tc(const HalfWeight& W, const __half* xh, int T, float* y, int ldy, float out_scale, float softcap,
+                     int32_t* status, cudaStream_t s) {
+    if (T <= 0) return;
+    if (!W.ready) throw std::runtime_error("launch_hgemm_tc: the f16 image of the matrix was not built");
+    if (xh == nullptr) throw std::runtime_error("launch_hgemm_tc: f16 activations missing");
+    const int bn = T > 128 ? 256 : 128;
+    alignas(64) CUtensorMap tx;
+    encode_half_matrix(&tx, xh, T, W.cols, bn);
+    HgParams p;
+    p.T = T;
+    p.K = (int)W.cols;
+    p.rows = (int)W.rows;
+    p.y = y;
+    p.ldy = ldy;
+    p.out_scale = out_scale;
+    p.softcap = softcap;
+    p.row_tiles = (int)((W.rows + HG_BM - 1) / HG_BM);
+    p.n_tiles = (T + bn - 1) / bn;
+    p.status = status;
+    const int grid = std::min(sm_count(), p.row_tiles * p.n_tiles);
+    const CUtensorMap& tw = *reinterpret_cast<const CUtensorMap*>(W.tmap);
+    if (bn == 256) launch_hg<256, 4>(tw, tx, p, grid, s);
+    else launch_hg<128, 6>(tw, tx, p, grid, s);
+}
+
+}  // namespace mk

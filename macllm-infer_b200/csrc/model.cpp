@@ -189,6 +189,7 @@ Model::Model(const std::string& gguf_path, const ModelConfig& cfg) : cfg_(cfg) {
     stage_dev_.alloc(stage_bytes);
     out_host_.ensure((size_t)B * ms_.vocab * 4 + (size_t)B * 4 + 16);
     MK_CUDA(cudaStreamSynchronize(stream_));
+    build_half_cache();
 }
 
 Model::~Model() {
@@ -302,7 +303,7 @@ void Model::rope_tables_for(double theta, const float*& cos_t, const float*& sin
 
 // ---------------------------------------------------------------------------- profiling
 
-static const char* kclass_names[] = {"qgemm_tc", "qgemv", "paged_attention", "add_norm_quant", "rope_kv_scatter", "actmul_quant",
+static const char* kclass_names[] = {"qgemm_tc", "hgemm_tc", "qgemv", "paged_attention", "add_norm_quant", "rope_kv_scatter", "actmul_quant",
                                      "embed", "build_batch", "argmax", "moe"};
 
 void Model::profile_enable(bool on) {
@@ -375,13 +376,19 @@ ActQ Model::act_view(DevBuf& qs, DevBuf& d, DevBuf& bs, DevBuf& xh, int, int, in
     return a;
 }
 
-void Model::matmul(const QWeight& W, const ActQ& x, int T, float* y, int ldy, float scale, float softcap) {
-    const bool tc = tensor_path(W, T) && x.xh != nullptr;
-    // algorithmic traffic of one call: the matrix as stored, the activation rows as consumed, the f32 result
-    const double act_bytes = tc ? 2.0 * T * W.cols : 1.0 * T * W.cols;
-    prof_begin(tc ? KC_GEMM_TC : KC_GEMV, (double)W.bytes + act_bytes + 4.0 * T * W.rows, 2.0 * T * (double)W.rows * (double)W.cols);
+void Model::matmul(const DeviceWeight& DW, const ActQ& x, int T, float* y, int ldy, float scale, float softcap) {
+    const QWeight& W = DW.w;
+    const bool hg = DW.half.ready && T >= hgemm_min_rows_ && x.xh != nullptr;
+    const bool tc = !hg && tensor_path(W, T) && x.xh != nullptr;
+    // algorithmic traffic of one call: the matrix as read, the activation rows as consumed, the f32 result
+    const double act_bytes = (hg || tc) ? 2.0 * T * W.cols : 1.0 * T * W.cols;
+    const double w_bytes = hg ? 2.0 * (double)W.rows * (double)W.cols : (double)W.bytes;
+    prof_begin(hg ? KC_HGEMM : (tc ? KC_GEMM_TC : KC_GEMV), w_bytes + act_bytes + 4.0 * T * W.rows, 2.0 * T * (double)W.rows * (double)W.cols);
     struct End { Model* m; ~End() { m->prof_end(); } } end{this};
-    if (tc) {
+    if (hg) {
+        launch_hgemm_tc(DW.half, x.xh, T, y, ldy, scale, softcap, tc_ws_.status.as<int32_t>(), stream_);
+        ++launches_;
+    } else if (tc) {
         size_t need = qgemm_tc_partial_floats(W, T);
         tc_ws_.partial.ensure(need * 4);
         launch_qgemm_tc_scratch(W, x, T, y, ldy, scale, softcap, tc_ws_.partial.as<float>(), tc_ws_.status.as<int32_t>(), stream_);
@@ -390,6 +397,31 @@ void Model::matmul(const QWeight& W, const ActQ& x, int T, float* y, int ldy, fl
         launch_qgemv(W, x, T, y, ldy, scale, softcap, stream_);
         ++launches_;
     }
+}
+
+// The f16 images of the dense layer matrices (2 bytes per weight), built when the configuration asks for
+// them and, in automatic mode, only when they fit beside everything else with room to spare.
+void Model::build_half_cache() {
+    if (cfg_.matmul_path != 0 && cfg_.matmul_path != 3) return;
+    hgemm_min_rows_ = cfg_.matmul_path == 3 ? 9 : 33;
+    std::vector<DeviceWeight*> all;
+    for (size_t l = 0; l < lw_.size(); ++l) {
+        LayerWeights& w = lw_[l];
+        for (DeviceWeight* dw : {&w.wq, &w.wk, &w.wv, &w.wo}) all.push_back(dw);
+        if (!ms_.layer[l].moe) for (DeviceWeight* dw : {&w.gate, &w.up, &w.down}) all.push_back(dw);
+    }
+    size_t total = 0;
+    for (DeviceWeight* dw : all) if (hgemm_tc_supported(dw->w)) total += half_weight_bytes(dw->w);
+    if (cfg_.matmul_path == 0) {
+        if (cfg_.max_batch_tokens < hgemm_min_rows_) return;
+        size_t free_b = 0, total_b = 0;
+        MK_CUDA(cudaMemGetInfo(&free_b, &total_b));
+        if (total + (size_t(4) << 30) > free_b) return;  // keep 4 GiB of headroom
+    }
+    for (DeviceWeight* dw : all) if (hgemm_tc_supported(dw->w)) build_half_weight(dw->w, dw->half, stream_);
+    MK_CUDA(cudaStreamSynchronize(stream_));
+    half_cache_ = true;
+    half_cache_bytes_ = (int64_t)total;
 }
 
 static int act_kind_of(const QWeight& w) { return w.type == QT_Q8_0 ? ACT_Q80 : ACT_Q8K; }
@@ -513,9 +545,9 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         prof_end();
         ++launches_;
         // projections (src/decoder.rs:1099-1161)
-        matmul(w.wq.w, xa, T, q_.as<float>(), AW, 1.f, 0.f);
-        matmul(w.wk.w, xa, T, k_.as<float>(), KW, 1.f, 0.f);
-        matmul(w.wv.w, xa, T, v_.as<float>(), KW, 1.f, 0.f);
+        matmul(w.wq, xa, T, q_.as<float>(), AW, 1.f, 0.f);
+        matmul(w.wk, xa, T, k_.as<float>(), KW, 1.f, 0.f);
+        matmul(w.wv, xa, T, v_.as<float>(), KW, 1.f, 0.f);
         // per-head norms, rotation, paged write
         RopeKvArgs ra;
         ra.q = q_.as<float>();
@@ -616,7 +648,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         launch_add_norm_quant(no, stream_);
         prof_end();
         ++launches_;
-        matmul(w.wo.w, xo, T, proj_.as<float>(), H, 1.f, 0.f);
+        matmul(w.wo, xo, T, proj_.as<float>(), H, 1.f, 0.f);
         // residual add + FFN norm + quantise (finish_mixer, src/decoder.rs:2684-2699)
         int fkind = act_kind_of(w.gate.w);
         ActQ xf = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, H, fkind, f16_T);
@@ -637,15 +669,15 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         ++launches_;
         if (!ls.moe) {
             // dense feed-forward (src/decoder.rs:298-305)
-            matmul(w.gate.w, xf, T, gate_.as<float>(), ms_.ffn, 1.f, 0.f);
-            matmul(w.up.w, xf, T, up_.as<float>(), ms_.ffn, 1.f, 0.f);
+            matmul(w.gate, xf, T, gate_.as<float>(), ms_.ffn, 1.f, 0.f);
+            matmul(w.up, xf, T, up_.as<float>(), ms_.ffn, 1.f, 0.f);
             int dkind = act_kind_of(w.down.w);
             ActQ xd = act_view(f_qs_, f_d_, f_bs_, f_xh_, T, ms_.ffn, dkind, f16_T);
             prof_begin(KC_ACTMUL, 9.0 * T * ms_.ffn, 0);
         launch_actmul_quant(gate_.as<float>(), up_.as<float>(), ms_.ffn, T, ms_.ffn, ls.act, dkind, xd, nullptr, stream_);
         prof_end();
             ++launches_;
-            matmul(w.down.w, xd, T, down_.as<float>(), H, 1.f, 0.f);
+            matmul(w.down, xd, T, down_.as<float>(), H, 1.f, 0.f);
         } else {
             // sparse MoE (src/decoder.rs:394-554)
             const int E = ms_.experts, K = ms_.experts_used, F = ms_.expert_ffn, P = T * K;
@@ -683,7 +715,8 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         ++launches_;
     }
     // logits tail (src/decoder.rs:3333-3356): last rows -> final norm -> output projection -> scale -> softcap
-    const QWeight& head = ms_.tied ? token_embd_.w : output_.w;
+    const DeviceWeight& head_dw = ms_.tied ? token_embd_ : output_;
+    const QWeight& head = head_dw.w;
     {
         const bool f16_B = cfg_.matmul_path != 1 && (cfg_.matmul_path == 2 || B > 8);
         int kind = act_kind_of(head);
@@ -701,7 +734,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         launch_add_norm_quant(ng, stream_);
         prof_end();
         ++launches_;
-        matmul(head, xl, B, logits_.as<float>(), ms_.vocab, ms_.final_logit_scale, ms_.final_softcap);
+        matmul(head_dw, xl, B, logits_.as<float>(), ms_.vocab, ms_.final_logit_scale, ms_.final_softcap);
     }
     if (flags & FWD_WANT_TOKENS) {
         prof_begin(KC_SAMPLE, 4.0 * B * ms_.vocab, 0);

@@ -8,6 +8,7 @@
 #include "kernels.h"
 #include "paged_lm.h"
 #include "qgemm_tc.h"
+#include "hgemm_tc.h"
 #include "attention_tc.h"
 
 namespace mk {
@@ -43,7 +44,10 @@ struct ModelConfig {
     int64_t kv_capacity_tokens = 4096, prefix_capacity_tokens = 0;
     bool kv_f16 = true;
     int max_batch_tokens = 2048, max_batch_lanes = 64;
-    int matmul_path = 0;  // 0 auto, 1 integer GEMV only, 2 tensor cores whenever the shape allows
+    // 0 auto (integer GEMV for a few rows, in-kernel dequant GEMM for tens of rows, f16-image GEMM for wide
+    // ticks when the image fits), 1 integer GEMV only, 2 in-kernel dequant GEMM whenever the shape allows,
+    // 3 f16-image GEMM whenever more than 8 rows share a matrix
+    int matmul_path = 0;
 };
 
 class Model : public PagedLm {
@@ -73,7 +77,7 @@ private:
     void upload_matrix(const GgufFile& f, const std::string& name, int64_t rows, int64_t cols, DeviceWeight& out, bool permute_heads,
                        int heads);
     void upload_f32(const GgufFile& f, const std::string& name, int64_t n, DevBuf& out);
-    void matmul(const QWeight& W, const ActQ& x, int T, float* y, int ldy, float scale, float softcap);
+    void matmul(const DeviceWeight& DW, const ActQ& x, int T, float* y, int ldy, float scale, float softcap);
     ActQ act_view(DevBuf& qs, DevBuf& d, DevBuf& bs, DevBuf& xh, int T, int dim, int kind, bool want_f16);
     bool tensor_path(const QWeight& W, int T) const;
     void rope_tables_for(double theta, const float*& cos_t, const float*& sin_t);
@@ -85,7 +89,7 @@ private:
     bool timed_ = false;
     int64_t launches_ = 0, h2d_bytes_ = 0, d2h_bytes_ = 0;
     // profiling: one event pair per launch group, resolved after the tick's barrier
-    enum KClass { KC_GEMM_TC = 0, KC_GEMV, KC_ATTN, KC_NORM_QUANT, KC_ROPE_KV, KC_ACTMUL, KC_EMBED, KC_BATCH, KC_SAMPLE, KC_MOE, KC_COUNT };
+    enum KClass { KC_GEMM_TC = 0, KC_HGEMM, KC_GEMV, KC_ATTN, KC_NORM_QUANT, KC_ROPE_KV, KC_ACTMUL, KC_EMBED, KC_BATCH, KC_SAMPLE, KC_MOE, KC_COUNT };
     struct ProfSpan { int cls; double bytes, flops; cudaEvent_t a, b; };
     bool profiling_ = false;
     std::vector<ProfSpan> spans_;
@@ -109,6 +113,11 @@ private:
     // tensor-core attention: split-KV partials of one-token lanes
     DevBuf attn_part_o_, attn_part_ml_;
     bool attn_tc_ = false;
+    // f16 weight images for wide ticks
+    bool half_cache_ = false;
+    int hgemm_min_rows_ = 33;
+    int64_t half_cache_bytes_ = 0;
+    void build_half_cache();
     int attn_max_entries_ = 0;
     AttnTcPlan attn_plan_;
     std::vector<int32_t> plan_sp_, plan_nt_;

@@ -65,6 +65,15 @@ def qmatmul(qtype: int, w_bytes: np.ndarray, rows: int, cols: int, x: np.ndarray
     return y
 
 
+def qmatmul_time(qtype: int, w_bytes: np.ndarray, rows: int, cols: int, x: np.ndarray, path: int, iters: int = 10) -> float:
+    """Mean launch duration (ms) of the matmul on the chosen path, operands resident, L2 flushed per launch."""
+    x = _f32(x)
+    w_bytes = np.ascontiguousarray(w_bytes)
+    ms = C.c_float(0)
+    capi.check(capi.lib().mk_k_qmatmul_time(qtype, _p(w_bytes), rows, cols, _p(x), x.shape[0], path, iters, C.byref(ms)))
+    return float(ms.value)
+
+
 def embed(qtype: int, w_bytes: np.ndarray, rows: int, cols: int, ids, scale: float = 1.0) -> np.ndarray:
     ids = np.ascontiguousarray(ids, dtype=np.uint32)
     out = np.empty((len(ids), cols), dtype=np.float32)

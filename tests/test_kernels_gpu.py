@@ -65,6 +65,28 @@ def test_qgemm_tensor_matches_oracle(ops, orc, name, T, rows, cols):
     assert cos >= 0.999999
 
 
+@pytest.mark.parametrize("name", list(QTYPES))
+@pytest.mark.parametrize("T,rows,cols", [(9, 128, 256), (130, 300, 1024), (257, 2048, 2048), (700, 512, 5632), (2048, 1152, 768)])
+def test_f16_image_gemm_matches_oracle(ops, orc, name, T, rows, cols):
+    """The wide-batch path: weights rounded once to f16 at load time, TMA-fed tcgen05 GEMM.  Ragged edges on
+    purpose: T and rows that are not multiples of the tile, several K blocks, more tiles than SMs."""
+    qtype = QTYPES[name]
+    w = _weights(ops, qtype, rows, cols, stream=4)
+    rng = np.random.default_rng(T + rows)
+    x = rng.standard_normal((T, cols)).astype(np.float32)
+    got = ops.qmatmul(qtype, w, rows, cols, x, 3)
+    want = orc.qmatmul(qtype, w, rows, cols, x, 1)
+    assert np.isfinite(got).all()
+    # both operands rounded once to f16 (rel 2^-11 each), f32 accumulation
+    scale = np.sqrt(cols) * 0.02
+    assert np.max(np.abs(got - want)) <= 2e-3 * scale
+    cos = float((got * want).sum() / np.sqrt((got * got).sum() * (want * want).sum()))
+    assert cos >= 0.999999
+    # against the in-kernel dequant path the only difference is how the weight was rounded
+    other = ops.qmatmul(qtype, w, rows, cols, x, 2)
+    assert np.max(np.abs(got - other)) <= 2e-3 * scale
+
+
 @pytest.mark.parametrize("name", ["q4_k", "q6_k", "q8_0", "f32"])
 def test_embed_rows_exact(ops, orc, name):
     qtype = {"f32": 0, **QTYPES}[name]
