@@ -47,7 +47,8 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_tile_kernel(AttnArgs a) {
     const int n_rows = min(a.q_tile, hdr.n_tokens - row0);
     const int g = a.q_heads / a.kv_heads;
     const int items = n_rows * g;
-    const int ldq = a.q_heads * d;
+    const int ldq = a.ldq > 0 ? a.ldq : a.q_heads * d;
+    const int ldo = a.q_heads * d;
 
     for (int i = threadIdx.x; i < items * d; i += blockDim.x) {
         int item = i / d, k = i - item * d;
@@ -146,7 +147,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_tile_kernel(AttnArgs a) {
         int item = warp + AT_WARPS * ii;
         if (item >= items) continue;
         int r = item / g, hq = item - r * g;
-        float* o = a.out + (int64_t)(q_off + row0 + r) * ldq + (kvh * g + hq) * d;
+        float* o = a.out + (int64_t)(q_off + row0 + r) * ldo + (kvh * g + hq) * d;
         float inv = 1.0f / l_run[ii];
 #pragma unroll
         for (int j = 0; j < AT_DPL; ++j) {

@@ -83,7 +83,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tc_kernel(AttnTcArgs a) {
     const LaneHeader hdr = a.hdr[lane_id];
     const int q_off = a.cu_seqlens[lane_id];
     const int n_rows = SPLIT ? 1 : min(rows_per_head, hdr.n_tokens - row0);
-    const int ldq = a.q_heads * D;
+    const int ldq = a.ldq > 0 ? a.ldq : a.q_heads * D;
+    const int ldo = a.q_heads * D;
 
     // item i of the CTA: head-in-group i / rows_per_head, query row i % rows_per_head
     for (int i = tid; i < M * CHUNKS; i += WARPS * 32) {
@@ -251,7 +252,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tc_kernel(AttnTcArgs a) {
             if (!live_r[h]) continue;
             int hq = item_r[h] / rows_per_head, r = item_r[h] - hq * rows_per_head;
             float inv = 1.0f / l_run[h];
-            float* o = a.out + (int64_t)(q_off + row0 + r) * ldq + (kvh * g + hq) * D;
+            float* o = a.out + (int64_t)(q_off + row0 + r) * ldo + (kvh * g + hq) * D;
 #pragma unroll
             for (int j = 0; j < NT_O; ++j)
                 *reinterpret_cast<float2*>(o + j * 8 + 2 * tq) = make_float2(o_acc[j][2 * h] * inv, o_acc[j][2 * h + 1] * inv);

@@ -6,7 +6,8 @@
 namespace mk {
 
 struct AttnTcArgs {
-    const float* q = nullptr;   // [T][q_heads*d] f32
+    const float* q = nullptr;   // [T] rows of q_heads*d f32 values, row stride ldq
+    int ldq = 0;                // 0 = q_heads*d
     float* out = nullptr;       // [T][q_heads*d] f32
     const void* k_pool = nullptr;  // f16 [blocks][layers][kv_heads][block_tokens][d]
     const void* v_pool = nullptr;

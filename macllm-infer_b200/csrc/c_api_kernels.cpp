@@ -118,8 +118,10 @@ void qmatmul_case(int32_t type, const void* w, int64_t rows, int64_t cols, const
     QgemmWorkspace ws;
     ws.status.alloc(sizeof(int32_t));
     ws.status.zero(nullptr);
+    HgemmScratch hs;
+    hs.status = ws.status.as<int32_t>();
     auto run = [&] {
-        if (half) launch_hgemm_tc(dw.half, a.xh, T, dy.as<float>(), (int)rows, 1.0f, 0.f, ws.status.as<int32_t>(), nullptr);
+        if (half) launch_hgemm_tc(dw.half, a.xh, T, dy.as<float>(), (int)rows, 1.0f, 0.f, hs, nullptr, 1);
         else if (tensor) launch_qgemm_tc(dw.w, a, kind, T, dy.as<float>(), (int)rows, 1.0f, 0.f, ws, nullptr);
         else launch_qgemv(dw.w, a, T, dy.as<float>(), (int)rows, 1.0f, 0.f, nullptr);
     };

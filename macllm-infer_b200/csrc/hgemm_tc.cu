@@ -171,6 +171,11 @@ struct HgParams {
     int ldy;
     float out_scale, softcap;
     int row_tiles, n_tiles;
+    // split-K (narrow batches, long K): work item = (output tile, K share); every share writes its f32
+    // partial sums to partial[share][T][rows] and the kernel that consumes the result adds the shares in
+    // share order, so the value does not depend on scheduling and no extra pass over the output is needed
+    int splits, kb_per_split;
+    float* partial;
     int32_t* status;
 };
 
@@ -182,10 +187,17 @@ struct HgSmem {
     static constexpr size_t TOTAL = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
+__device__ __forceinline__ float finish_value(float v, const HgParams& p) {
+    v *= p.out_scale;
+    if (p.softcap != 0.f) v = tanhf(v * (1.0f / p.softcap)) * p.softcap;
+    return v;
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(HG_THREADS, 1)
 hgemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, HgParams p) {
     using L = HgSmem<BN, STAGES>;
+    constexpr int LD_COLS = BN >= 32 ? 32 : BN;
     extern __shared__ uint8_t hg_smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(hg_smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + (size_t)STAGES * L::STAGE_BYTES);
@@ -197,7 +209,9 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_blocks = p.K / HG_BK;
-    const int total_tiles = p.row_tiles * p.n_tiles;
+    const int mn_tiles = p.row_tiles * p.n_tiles;
+    const int total_items = mn_tiles * p.splits;
+    constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) {
@@ -212,7 +226,7 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
-                     "r"((uint32_t)(2 * BN))
+                     "r"(TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -221,14 +235,24 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
 
+    // work item -> (row tile, token tile, K share); row tiles vary fastest so concurrent CTAs share activations
+    auto decode = [&](int item, int& m_tile, int& n_tile, int& kb0, int& kb1) {
+        int mn = item % mn_tiles, split = item / mn_tiles;
+        m_tile = mn % p.row_tiles;
+        n_tile = mn / p.row_tiles;
+        kb0 = split * p.kb_per_split;
+        kb1 = min(k_blocks, kb0 + p.kb_per_split);
+    };
+
     if (warp == 0) {
         // ---- loader
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int m_tile = tile % p.row_tiles, n_tile = tile / p.row_tiles;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+                int m_tile, n_tile, kb0, kb1;
+                decode(item, m_tile, n_tile, kb0, kb1);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t st = it % STAGES, ph = (it / STAGES) & 1;
                     if (!mbar_wait(&empty[st], ph ^ 1, HG_SPIN_LIMIT)) {
                         atomicExch(p.status, 11);
@@ -249,7 +273,9 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(HG_BM >> 4) << 24);
             uint32_t it = 0, tile_it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_it) {
+            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++tile_it) {
+                int m_tile, n_tile, kb0, kb1;
+                decode(item, m_tile, n_tile, kb0, kb1);
                 const uint32_t acc = tile_it & 1, acc_ph = (tile_it >> 1) & 1;
                 if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1, HG_SPIN_LIMIT)) {
                     atomicExch(p.status, 12);
@@ -257,7 +283,7 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t st = it % STAGES, ph = (it / STAGES) & 1;
                     if (!mbar_wait(&full[st], ph, HG_SPIN_LIMIT)) {
                         atomicExch(p.status, 13);
@@ -271,7 +297,7 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
 #pragma unroll
                     for (int k = 0; k < HG_BK / 16; ++k) {
                         // 16 halves = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
-                        umma_f16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_f16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit(&empty[st]);
                 }
@@ -281,19 +307,36 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     } else {
         // ---- epilogue: warps 2..5 own TMEM lane quadrants (warp % 4)
         const int quad = warp & 3;
+        const int etid = (int)threadIdx.x - 64;  // 0..127 among the epilogue threads
         uint32_t tile_it = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tile_it) {
-            const int m_tile = tile % p.row_tiles, n_tile = tile / p.row_tiles;
+        for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++tile_it) {
+            int m_tile, n_tile, kb0, kb1;
+            decode(item, m_tile, n_tile, kb0, kb1);
+            const int split = item / mn_tiles;
             const uint32_t acc = tile_it & 1, acc_ph = (tile_it >> 1) & 1;
-            if (!mbar_wait(&acc_full[acc], acc_ph, HG_SPIN_LIMIT)) {
-                if (lane == 0) atomicExch(p.status, 14);
+            // every epilogue warp waits for itself, then the four agree on the outcome, so that a wait that
+            // gave up takes all of them out of the loop together (they meet again at named barrier 1)
+            const uint32_t got = mbar_wait(&acc_full[acc], acc_ph, HG_SPIN_LIMIT) ? 1u : 0u;
+            uint32_t all_got;
+            asm volatile(
+                "{\n\t.reg .pred p, q;\n\t"
+                "setp.ne.u32 q, %1, 0;\n\t"
+                "bar.red.and.pred p, 1, 128, q;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(all_got)
+                : "r"(got)
+                : "memory");
+            if (!all_got) {
+                if (etid == 0) atomicExch(p.status, 14);
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int row = m_tile * HG_BM + quad * 32 + lane;
             const int tok0 = n_tile * BN;
+            float* dst = p.splits > 1 ? p.partial + (int64_t)split * p.T * p.rows : p.y;
+            const int ld = p.splits > 1 ? p.rows : p.ldy;
 #pragma unroll 1
-            for (int cb = 0; cb < BN; cb += 32) {
+            for (int cb = 0; cb < BN; cb += LD_COLS) {
                 if (tok0 + cb >= p.T) break;  // uniform over the CTA: nothing but padding from here on
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + (uint32_t)cb, r);
@@ -303,9 +346,9 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     for (int i = 0; i < 32; ++i) {
                         int tok = tok0 + cb + i;
                         if (tok < p.T) {
-                            float v = __uint_as_float(r[i]) * p.out_scale;
-                            if (p.softcap != 0.f) v = tanhf(v * (1.0f / p.softcap)) * p.softcap;
-                            p.y[(int64_t)tok * p.ldy + row] = v;
+                            float v = __uint_as_float(r[i]);
+                            if (p.splits == 1) v = finish_value(v, p);
+                            dst[(int64_t)tok * ld + row] = v;
                         }
                     }
                 }
@@ -319,7 +362,7 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     __syncthreads();
     if (warp == 0) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -384,28 +427,76 @@ bool hgemm_tc_supported(const QWeight& W) {
     return W.cols % 256 == 0 && W.rows > 0;
 }
 
-void build_half_weight(const QWeight& W, HalfWeight& out, cudaStream_t s) {
-    if (!hgemm_tc_supported(W)) throw std::runtime_error("build_half_weight: unsupported matrix");
-    out.rows = W.rows;
-    out.cols = W.cols;
-    out.values.alloc(half_weight_bytes(W));
-    const int64_t blocks = W.rows * (W.cols / 256);
-    const int warps_per_cta = 8;
-    dequant_f16_kernel<<<(unsigned)((blocks + warps_per_cta - 1) / warps_per_cta), warps_per_cta * 32, 0, s>>>(W, out.values.as<__half>());
-    MK_LAUNCH_CHECK();
+void build_half_weight_stacked(const QWeight* const* parts, int n_parts, HalfWeight& out, cudaStream_t s) {
+    if (n_parts <= 0) throw std::runtime_error("build_half_weight: nothing to build");
+    int64_t rows = 0;
+    const int64_t cols = parts[0]->cols;
+    for (int i = 0; i < n_parts; ++i) {
+        if (!hgemm_tc_supported(*parts[i]) || parts[i]->cols != cols) throw std::runtime_error("build_half_weight: unsupported matrix");
+        rows += parts[i]->rows;
+    }
+    out.rows = rows;
+    out.cols = cols;
+    out.values.alloc((size_t)rows * (size_t)cols * 2);
+    int64_t row0 = 0;
+    for (int i = 0; i < n_parts; ++i) {
+        const QWeight& W = *parts[i];
+        const int64_t blocks = W.rows * (W.cols / 256);
+        const int warps_per_cta = 8;
+        dequant_f16_kernel<<<(unsigned)((blocks + warps_per_cta - 1) / warps_per_cta), warps_per_cta * 32, 0, s>>>(
+            W, out.values.as<__half>() + row0 * cols);
+        MK_LAUNCH_CHECK();
+        row0 += W.rows;
+    }
     static_assert(sizeof(CUtensorMap) <= sizeof(out.tmap), "descriptor storage too small");
-    encode_half_matrix(reinterpret_cast<CUtensorMap*>(out.tmap), out.values.ptr(), W.rows, W.cols, HG_BM);
+    encode_half_matrix(reinterpret_cast<CUtensorMap*>(out.tmap), out.values.ptr(), rows, cols, HG_BM);
     out.ready = true;
 }
 
-void launch_hgemm_tc(const HalfWeight& W, const __half* xh, int T, float* y, int ldy, float out_scale, float softcap,
-                     int32_t* status, cudaStream_t s) {
-    if (T <= 0) return;
+void build_half_weight(const QWeight& W, HalfWeight& out, cudaStream_t s) {
+    const QWeight* one = &W;
+    build_half_weight_stacked(&one, 1, out, s);
+}
+
+HgemmPlan hgemm_tc_plan(int64_t rows, int64_t cols, int T, int max_splits) {
+    HgemmPlan pl;
+    pl.bn = T <= 64 ? 64 : (T <= 128 ? 128 : 256);
+    pl.row_tiles = (int)((rows + HG_BM - 1) / HG_BM);
+    pl.n_tiles = (T + pl.bn - 1) / pl.bn;
+    const int kb = (int)(cols / HG_BK);
+    const int tiles = pl.row_tiles * pl.n_tiles;
+    const int sms = 148;
+    // shares of K per output tile: fewest "waves x (K blocks per share + fixed cost)" with shares of at least
+    // four K blocks and at most 16 MiB of partial sums
+    int best = 1;
+    long best_cost = -1;
+    for (int s = 1; s <= std::max(1, std::min(max_splits, 16)); ++s) {
+        int per = (kb + s - 1) / s;
+        if (s > 1 && (per < 4 || (size_t)s * T * rows * 4 > ((size_t)16 << 20))) break;
+        if ((kb + per - 1) / per != s) continue;  // not a distinct split
+        long waves = ((long)tiles * s + sms - 1) / sms;
+        long cost = waves * (per + 3) + (s > 1 ? 1 : 0);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
+    }
+    pl.splits = best;
+    pl.kb_per_split = (kb + best - 1) / best;
+    pl.partial_floats = best > 1 ? (size_t)best * T * rows : 0;
+    return pl;
+}
+
+int launch_hgemm_tc(const HalfWeight& W, const __half* xh, int T, float* y, int ldy, float out_scale, float softcap,
+                    const HgemmScratch& ws, cudaStream_t s, int max_splits) {
+    if (T <= 0) return 1;
     if (!W.ready) throw std::runtime_error("launch_hgemm_tc: the f16 image of the matrix was not built");
     if (xh == nullptr) throw std::runtime_error("launch_hgemm_tc: f16 activations missing");
-    const int bn = T > 128 ? 256 : 128;
+    if (out_scale != 1.0f || softcap != 0.f || ws.partial == nullptr) max_splits = 1;
+    HgemmPlan pl = hgemm_tc_plan(W.rows, W.cols, T, max_splits);
+    if (pl.splits > 1 && pl.partial_floats > ws.partial_floats) {
+        pl.splits = 1;
+        pl.kb_per_split = (int)(W.cols / HG_BK);
+    }
     alignas(64) CUtensorMap tx;
-    encode_half_matrix(&tx, xh, T, W.cols, bn);
+    encode_half_matrix(&tx, xh, T, W.cols, pl.bn);
     HgParams p;
     p.T = T;
     p.K = (int)W.cols;
@@ -414,13 +505,18 @@ void launch_hgemm_tc(const HalfWeight& W, const __half* xh, int T, float* y, int
     p.ldy = ldy;
     p.out_scale = out_scale;
     p.softcap = softcap;
-    p.row_tiles = (int)((W.rows + HG_BM - 1) / HG_BM);
-    p.n_tiles = (T + bn - 1) / bn;
-    p.status = status;
-    const int grid = std::min(sm_count(), p.row_tiles * p.n_tiles);
+    p.row_tiles = pl.row_tiles;
+    p.n_tiles = pl.n_tiles;
+    p.splits = pl.splits;
+    p.kb_per_split = pl.kb_per_split;
+    p.partial = ws.partial;
+    p.status = ws.status;
+    const int grid = std::min(sm_count(), p.row_tiles * p.n_tiles * p.splits);
     const CUtensorMap& tw = *reinterpret_cast<const CUtensorMap*>(W.tmap);
-    if (bn == 256) launch_hg<256, 4>(tw, tx, p, grid, s);
-    else launch_hg<128, 6>(tw, tx, p, grid, s);
+    if (pl.bn == 256) launch_hg<256, 4>(tw, tx, p, grid, s);
+    else if (pl.bn == 128) launch_hg<128, 6>(tw, tx, p, grid, s);
+    else launch_hg<64, 8>(tw, tx, p, grid, s);
+    return pl.splits;
 }
 
 }  // namespace mk

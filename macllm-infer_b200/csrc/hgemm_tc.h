@@ -14,9 +14,30 @@ bool hgemm_tc_supported(const QWeight& W);
 // Dequantise W (device layout of QWeight) into out.values and encode its descriptor.
 void build_half_weight(const QWeight& W, HalfWeight& out, cudaStream_t s);
 
+// Dequantise several matrices with the same number of columns into one image, stacked by rows (fused
+// projections: one GEMM then produces the concatenated outputs).
+void build_half_weight_stacked(const QWeight* const* parts, int n_parts, HalfWeight& out, cudaStream_t s);
+
+// How a call is cut into work items (see hgemm_tc.cu); partial_floats is the scratch a split call needs.
+struct HgemmPlan {
+    int bn = 0, row_tiles = 0, n_tiles = 0, splits = 1, kb_per_split = 0;
+    size_t partial_floats = 0;
+};
+HgemmPlan hgemm_tc_plan(int64_t rows, int64_t cols, int T, int max_splits);
+
+// Device scratch of the GEMM: split-K partial sums and the status word that receives a non-zero code when
+// a bounded wait gave up.
+struct HgemmScratch {
+    float* partial = nullptr;
+    size_t partial_floats = 0;
+    int32_t* status = nullptr;
+};
+
 // y[t][n] = scale * sum_k xh[t][k] * Wh[n][k] (then the optional soft cap), t < T, n < rows.
-// xh is [T][cols] f16, 16-byte aligned.  `status` receives a non-zero code when a bounded wait gave up.
-void launch_hgemm_tc(const HalfWeight& W, const __half* xh, int T, float* y, int ldy, float out_scale, float softcap,
-                     int32_t* status, cudaStream_t s);
+// xh is [T][cols] f16, 16-byte aligned.  Returns the number of K shares S the call was cut into.  S = 1: y holds
+// the result.  S > 1 (only when max_splits > 1, scale = 1 and no soft cap): y is NOT written; share s left its
+// partial sums at ws.partial[(s * T + t) * rows + n] and the consumer adds them for s = 0 .. S-1 in that order.
+int launch_hgemm_tc(const HalfWeight& W, const __half* xh, int T, float* y, int ldy, float out_scale, float softcap,
+                    const HgemmScratch& ws, cudaStream_t s, int max_splits = 1);
 
 }  // namespace mk

@@ -15,6 +15,10 @@ namespace mk {
 struct NormQuantArgs {
     float* h = nullptr;
     const float* a = nullptr;
+    // a may arrive as a_splits partial sums a_split_stride floats apart (split-K matmul output); they are
+    // added in index order before anything else
+    int a_splits = 1;
+    int64_t a_split_stride = 0;
     float a_scale = 1.f;
     const float* post_w = nullptr;
     const float* norm_w = nullptr;
@@ -98,7 +102,8 @@ void launch_cow_copy(void* k_pool, void* v_pool, int kv_f16, int64_t src_block, 
 
 // ---- attention ---------------------------------------------------------------------------------
 struct AttnArgs {
-    const float* q = nullptr;  // [T][q_heads*d]
+    const float* q = nullptr;  // [T] rows of q_heads*d values, row stride ldq
+    int ldq = 0;               // 0 = q_heads*d
     float* out = nullptr;      // [T][q_heads*d]
     const void* k_pool = nullptr;
     const void* v_pool = nullptr;

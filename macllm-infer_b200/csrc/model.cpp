@@ -127,15 +127,12 @@ Model::Model(const std::string& gguf_path, const ModelConfig& cfg) : cfg_(cfg) {
     err_.alloc(4);
     err_.zero(stream_);
     h_.alloc((size_t)T * ms_.hidden * 4);
-    q_.alloc((size_t)T * AW * 4);
-    k_.alloc((size_t)T * KW * 4);
-    v_.alloc((size_t)T * KW * 4);
+    qkv_.alloc((size_t)T * (AW + 2 * KW) * 4);
     attn_.alloc((size_t)T * AW * 4);
     proj_.alloc((size_t)T * ms_.hidden * 4);
     down_.alloc((size_t)T * ms_.hidden * 4);
     if (!moe) {
-        gate_.alloc((size_t)T * ms_.ffn * 4);
-        up_.alloc((size_t)T * ms_.ffn * 4);
+        gu_.alloc((size_t)T * 2 * ms_.ffn * 4);
     } else {
         normed_.alloc((size_t)T * ms_.hidden * 4);
         router_logits_.alloc((size_t)T * ms_.experts * 4);
@@ -376,19 +373,34 @@ ActQ Model::act_view(DevBuf& qs, DevBuf& d, DevBuf& bs, DevBuf& xh, int, int, in
     return a;
 }
 
+HgemmScratch Model::hgemm_scratch() const {
+    HgemmScratch ws;
+    ws.partial = tc_ws_.partial.as<float>();
+    ws.partial_floats = tc_ws_.partial.size() / 4;
+    ws.status = tc_ws_.status.as<int32_t>();
+    return ws;
+}
+
+int Model::matmul_half(const HalfWeight& W, const ActQ& x, int T, float* y, int ldy, float scale, float softcap, int max_splits) {
+    prof_begin(KC_HGEMM, 2.0 * (double)W.rows * (double)W.cols + 2.0 * T * W.cols + 4.0 * T * W.rows, 2.0 * T * (double)W.rows * (double)W.cols);
+    int splits = launch_hgemm_tc(W, x.xh, T, y, ldy, scale, softcap, hgemm_scratch(), stream_, max_splits);
+    prof_end();
+    ++launches_;
+    return splits;
+}
+
 void Model::matmul(const DeviceWeight& DW, const ActQ& x, int T, float* y, int ldy, float scale, float softcap) {
     const QWeight& W = DW.w;
-    const bool hg = DW.half.ready && T >= hgemm_min_rows_ && x.xh != nullptr;
-    const bool tc = !hg && tensor_path(W, T) && x.xh != nullptr;
-    // algorithmic traffic of one call: the matrix as read, the activation rows as consumed, the f32 result
-    const double act_bytes = (hg || tc) ? 2.0 * T * W.cols : 1.0 * T * W.cols;
-    const double w_bytes = hg ? 2.0 * (double)W.rows * (double)W.cols : (double)W.bytes;
-    prof_begin(hg ? KC_HGEMM : (tc ? KC_GEMM_TC : KC_GEMV), w_bytes + act_bytes + 4.0 * T * W.rows, 2.0 * T * (double)W.rows * (double)W.cols);
+    if (DW.half.ready && T >= hgemm_min_rows_ && x.xh != nullptr) {
+        matmul_half(DW.half, x, T, y, ldy, scale, softcap);
+        return;
+    }
+    const bool tc = tensor_path(W, T) && x.xh != nullptr;
+    // algorithmic traffic of one call: the matrix as stored, the activation rows as consumed, the f32 result
+    const double act_bytes = tc ? 2.0 * T * W.cols : 1.0 * T * W.cols;
+    prof_begin(tc ? KC_GEMM_TC : KC_GEMV, (double)W.bytes + act_bytes + 4.0 * T * W.rows, 2.0 * T * (double)W.rows * (double)W.cols);
     struct End { Model* m; ~End() { m->prof_end(); } } end{this};
-    if (hg) {
-        launch_hgemm_tc(DW.half, x.xh, T, y, ldy, scale, softcap, tc_ws_.status.as<int32_t>(), stream_);
-        ++launches_;
-    } else if (tc) {
+    if (tc) {
         size_t need = qgemm_tc_partial_floats(W, T);
         tc_ws_.partial.ensure(need * 4);
         launch_qgemm_tc_scratch(W, x, T, y, ldy, scale, softcap, tc_ws_.partial.as<float>(), tc_ws_.status.as<int32_t>(), stream_);
@@ -404,21 +416,37 @@ void Model::matmul(const DeviceWeight& DW, const ActQ& x, int T, float* y, int l
 void Model::build_half_cache() {
     if (cfg_.matmul_path != 0 && cfg_.matmul_path != 3) return;
     hgemm_min_rows_ = cfg_.matmul_path == 3 ? 9 : 33;
-    std::vector<DeviceWeight*> all;
+    size_t total = 0;
     for (size_t l = 0; l < lw_.size(); ++l) {
         LayerWeights& w = lw_[l];
-        for (DeviceWeight* dw : {&w.wq, &w.wk, &w.wv, &w.wo}) all.push_back(dw);
-        if (!ms_.layer[l].moe) for (DeviceWeight* dw : {&w.gate, &w.up, &w.down}) all.push_back(dw);
+        for (DeviceWeight* dw : {&w.wq, &w.wk, &w.wv, &w.wo}) {
+            if (!hgemm_tc_supported(dw->w)) return;  // all or nothing: the forward pass takes one route per tick
+            total += half_weight_bytes(dw->w);
+        }
+        if (!ms_.layer[l].moe)
+            for (DeviceWeight* dw : {&w.gate, &w.up, &w.down}) {
+                if (!hgemm_tc_supported(dw->w)) return;
+                total += half_weight_bytes(dw->w);
+            }
     }
-    size_t total = 0;
-    for (DeviceWeight* dw : all) if (hgemm_tc_supported(dw->w)) total += half_weight_bytes(dw->w);
     if (cfg_.matmul_path == 0) {
         if (cfg_.max_batch_tokens < hgemm_min_rows_) return;
         size_t free_b = 0, total_b = 0;
         MK_CUDA(cudaMemGetInfo(&free_b, &total_b));
         if (total + (size_t(4) << 30) > free_b) return;  // keep 4 GiB of headroom
     }
-    for (DeviceWeight* dw : all) if (hgemm_tc_supported(dw->w)) build_half_weight(dw->w, dw->half, stream_);
+    for (size_t l = 0; l < lw_.size(); ++l) {
+        LayerWeights& w = lw_[l];
+        const QWeight* qkv[3] = {&w.wq.w, &w.wk.w, &w.wv.w};
+        build_half_weight_stacked(qkv, 3, w.qkv_half, stream_);
+        build_half_weight(w.wo.w, w.wo.half, stream_);
+        if (!ms_.layer[l].moe) {
+            const QWeight* gu[2] = {&w.gate.w, &w.up.w};
+            build_half_weight_stacked(gu, 2, w.gu_half, stream_);
+            build_half_weight(w.down.w, w.down.half, stream_);
+        }
+    }
+    tc_ws_.partial.ensure((size_t)16 << 20);
     MK_CUDA(cudaStreamSynchronize(stream_));
     half_cache_ = true;
     half_cache_bytes_ = (int64_t)total;
@@ -434,6 +462,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
     if (B > cfg_.max_batch_lanes) throw std::runtime_error("batch has more lanes than max_batch_lanes");
     if (T > cfg_.max_batch_tokens) throw std::runtime_error("batch has more tokens than max_batch_tokens");
     const int H = ms_.hidden, AW = ms_.q_heads * ms_.head_dim, KW = ms_.kv_heads * ms_.head_dim, d = ms_.head_dim;
+    const int QKVW = AW + 2 * KW;
     const int bt = pool_->block_tokens();
     const int q_tile = attention_q_tile(ms_.q_heads, ms_.kv_heads);
 
@@ -524,6 +553,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
     const bool f16_T = cfg_.matmul_path != 1 && (cfg_.matmul_path == 2 || T > 8);
     const float* pending = nullptr;        // branch output not yet added to the residual stream
     const float* pending_post = nullptr;   // its sandwich post-norm weight, if any
+    int pending_splits = 1;                // > 1: `pending` is that many split-K partials, T * H floats apart
     for (int l = 0; l < ms_.layers; ++l) {
         LayerWeights& w = lw_[(size_t)l];
         const LayerSpec& ls = ms_.layer[(size_t)l];
@@ -533,6 +563,8 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         NormQuantArgs na;
         na.h = h_.as<float>();
         na.a = pending;
+        na.a_splits = pending_splits;
+        na.a_split_stride = (int64_t)T * H;
         na.post_w = pending_post;
         na.norm_w = w.attn_norm.as<float>();
         na.eps = ms_.eps;
@@ -545,16 +577,22 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         prof_end();
         ++launches_;
         // projections (src/decoder.rs:1099-1161)
-        matmul(w.wq, xa, T, q_.as<float>(), AW, 1.f, 0.f);
-        matmul(w.wk, xa, T, k_.as<float>(), KW, 1.f, 0.f);
-        matmul(w.wv, xa, T, v_.as<float>(), KW, 1.f, 0.f);
+        float* qp = qkv_.as<float>();
+        float* kp = qp + AW;
+        float* vp = kp + KW;
+        if (w.qkv_half.ready && T >= hgemm_min_rows_ && xa.xh != nullptr) {
+            matmul_half(w.qkv_half, xa, T, qp, QKVW, 1.f, 0.f);
+        } else {
+            matmul(w.wq, xa, T, qp, QKVW, 1.f, 0.f);
+            matmul(w.wk, xa, T, kp, QKVW, 1.f, 0.f);
+            matmul(w.wv, xa, T, vp, QKVW, 1.f, 0.f);
+        }
         // per-head norms, rotation, paged write
         RopeKvArgs ra;
-        ra.q = q_.as<float>();
-        ra.k = k_.as<float>();
-        ra.v = v_.as<float>();
-        ra.ldq = AW;
-        ra.ldk = ra.ldv = KW;
+        ra.q = qp;
+        ra.k = kp;
+        ra.v = vp;
+        ra.ldq = ra.ldk = ra.ldv = QKVW;
         if (ls.qk_norm) { ra.q_norm_w = w.q_norm.as<float>(); ra.k_norm_w = w.k_norm.as<float>(); }
         ra.norm_eps = ms_.eps;
         if (ls.rope) { rope_tables_for(ls.theta, ra.cos_t, ra.sin_t); ra.rotary_dim = ms_.rotary_dim; }
@@ -575,7 +613,8 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         prof_end();
         ++launches_;
         AttnArgs at;
-        at.q = q_.as<float>();
+        at.q = qp;
+        at.ldq = QKVW;
         at.out = attn_.as<float>();
         at.k_pool = k_pool_.ptr();
         at.v_pool = v_pool_.ptr();
@@ -606,6 +645,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         if (attn_tc_) {
             AttnTcArgs ta;
             ta.q = at.q;
+            ta.ldq = at.ldq;
             ta.out = at.out;
             ta.k_pool = at.k_pool;
             ta.v_pool = at.v_pool;
@@ -648,13 +688,19 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         launch_add_norm_quant(no, stream_);
         prof_end();
         ++launches_;
-        matmul(w.wo, xo, T, proj_.as<float>(), H, 1.f, 0.f);
+        // split-K shares of the two long-K projections are summed by the residual kernel that consumes them
+        const int kMaxShares = 16;
+        int wo_splits = 1;
+        if (w.wo.half.ready && T >= hgemm_min_rows_ && xo.xh != nullptr) wo_splits = matmul_half(w.wo.half, xo, T, proj_.as<float>(), H, 1.f, 0.f, kMaxShares);
+        else matmul(w.wo, xo, T, proj_.as<float>(), H, 1.f, 0.f);
         // residual add + FFN norm + quantise (finish_mixer, src/decoder.rs:2684-2699)
         int fkind = act_kind_of(w.gate.w);
         ActQ xf = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, H, fkind, f16_T);
         NormQuantArgs nf;
         nf.h = h_.as<float>();
-        nf.a = proj_.as<float>();
+        nf.a = wo_splits > 1 ? tc_ws_.partial.as<float>() : proj_.as<float>();
+        nf.a_splits = wo_splits;
+        nf.a_split_stride = (int64_t)T * H;
         nf.post_w = ls.sandwich ? w.post_attn_norm.as<float>() : nullptr;
         nf.norm_w = w.ffn_norm.as<float>();
         nf.eps = ms_.eps;
@@ -669,15 +715,22 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         ++launches_;
         if (!ls.moe) {
             // dense feed-forward (src/decoder.rs:298-305)
-            matmul(w.gate, xf, T, gate_.as<float>(), ms_.ffn, 1.f, 0.f);
-            matmul(w.up, xf, T, up_.as<float>(), ms_.ffn, 1.f, 0.f);
+            float* gp = gu_.as<float>();
+            float* up = gp + ms_.ffn;
+            if (w.gu_half.ready && T >= hgemm_min_rows_ && xf.xh != nullptr) {
+                matmul_half(w.gu_half, xf, T, gp, 2 * ms_.ffn, 1.f, 0.f);
+            } else {
+                matmul(w.gate, xf, T, gp, 2 * ms_.ffn, 1.f, 0.f);
+                matmul(w.up, xf, T, up, 2 * ms_.ffn, 1.f, 0.f);
+            }
             int dkind = act_kind_of(w.down.w);
             ActQ xd = act_view(f_qs_, f_d_, f_bs_, f_xh_, T, ms_.ffn, dkind, f16_T);
             prof_begin(KC_ACTMUL, 9.0 * T * ms_.ffn, 0);
-        launch_actmul_quant(gate_.as<float>(), up_.as<float>(), ms_.ffn, T, ms_.ffn, ls.act, dkind, xd, nullptr, stream_);
+        launch_actmul_quant(gp, up, 2 * ms_.ffn, T, ms_.ffn, ls.act, dkind, xd, nullptr, stream_);
         prof_end();
             ++launches_;
-            matmul(w.down, xd, T, down_.as<float>(), H, 1.f, 0.f);
+            if (w.down.half.ready && T >= hgemm_min_rows_ && xd.xh != nullptr) pending_splits = matmul_half(w.down.half, xd, T, down_.as<float>(), H, 1.f, 0.f, kMaxShares);
+            else { matmul(w.down, xd, T, down_.as<float>(), H, 1.f, 0.f); pending_splits = 1; }
         } else {
             // sparse MoE (src/decoder.rs:394-554)
             const int E = ms_.experts, K = ms_.experts_used, F = ms_.expert_ffn, P = T * K;
@@ -697,7 +750,8 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
                                down_.as<float>(), stream_);
             launches_ += 8;
         }
-        pending = down_.as<float>();
+        if (ls.moe) pending_splits = 1;
+        pending = pending_splits > 1 ? tc_ws_.partial.as<float>() : down_.as<float>();
         pending_post = ls.sandwich ? w.post_ffn_norm.as<float>() : nullptr;
     }
     // last residual add
@@ -705,6 +759,8 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         NormQuantArgs nl;
         nl.h = h_.as<float>();
         nl.a = pending;
+        nl.a_splits = pending_splits;
+        nl.a_split_stride = (int64_t)T * H;
         nl.post_w = pending_post;
         nl.eps = ms_.eps;
         nl.rows = T;

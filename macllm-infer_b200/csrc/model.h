@@ -71,6 +71,7 @@ protected:
 private:
     struct LayerWeights {
         DevBuf attn_norm, ffn_norm, post_attn_norm, post_ffn_norm, q_norm, k_norm, router;
+        HalfWeight qkv_half, gu_half;  // f16 images of [wq; wk; wv] and [gate; up] stacked by rows
         DeviceWeight wq, wk, wv, wo, gate, up, down;  // dense FFN, or expert banks for MoE layers
     };
     void load_weights(const GgufFile& f);
@@ -118,11 +119,16 @@ private:
     int hgemm_min_rows_ = 33;
     int64_t half_cache_bytes_ = 0;
     void build_half_cache();
+    HgemmScratch hgemm_scratch() const;
+    // Returns the number of K shares; more than one means the result is the sum of that many partials in the
+    // split-K scratch (see launch_hgemm_tc) and y was not written.
+    int matmul_half(const HalfWeight& W, const ActQ& x, int T, float* y, int ldy, float scale, float softcap, int max_splits = 1);
     int attn_max_entries_ = 0;
     AttnTcPlan attn_plan_;
     std::vector<int32_t> plan_sp_, plan_nt_;
     // activations
-    DevBuf h_, q_, k_, v_, attn_, proj_, gate_, up_, down_, normed_, logits_, tokens_;
+    // qkv_: [T][AW + 2 KW] (q | k | v per row); gu_: [T][2 ffn] (gate | up per row)
+    DevBuf h_, qkv_, attn_, proj_, gu_, down_, normed_, logits_, tokens_;
     DevBuf a_qs_, a_d_, a_bs_, a_xh_;   // quantised activations of width hidden / attention width
     DevBuf f_qs_, f_d_, f_bs_, f_xh_;   // quantised activations of width ffn
     DevBuf l_qs_, l_d_, l_bs_, l_xh_;   // last-token rows for the output projection

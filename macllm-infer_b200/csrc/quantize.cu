@@ -125,15 +125,20 @@ __global__ void __launch_bounds__(NQ_THREADS) add_norm_quant_kernel(NormQuantArg
 
     if (a.a != nullptr) {
         const float* av = a.a + (int64_t)src * dim;
+        auto a_at = [&](int k) {
+            float x = av[k];
+            for (int sp = 1; sp < a.a_splits; ++sp) x += av[(int64_t)sp * a.a_split_stride + k];
+            return x;
+        };
         float post_m = 1.f;
         if (a.post_w != nullptr) {
             float ss = 0.f;
-            for (int k = threadIdx.x; k < dim; k += blockDim.x) { float x = av[k]; ss += x * x; }
+            for (int k = threadIdx.x; k < dim; k += blockDim.x) { float x = a_at(k); ss += x * x; }
             ss = block_sum(ss, red);
             post_m = sqrtf(ss / (float)dim + a.eps);
         }
         for (int k = threadIdx.x; k < dim; k += blockDim.x) {
-            float x = av[k];
+            float x = a_at(k);
             if (a.post_w != nullptr) x = x / post_m * a.post_w[k];
             float hv = h[k] + x * a.a_scale;
             row[k] = hv;
@@ -184,10 +189,238 @@ __global__ void add_inplace_kernel(float* h, const float* a, float scale, int64_
     if (i < n) h[i] = h[i] + a[i] * scale;
 }
 
+
+// ---- fast path: rows whose width is a multiple of 256 ------------------------------------------------
+// One warp owns one 256-element group at a time and each lane eight consecutive values of it, so a K-quant
+// activation block (256) or eight Q8_0 blocks (32 = four lanes) are quantised from registers with
+// shuffles only.  Same arithmetic as quantize_row_q8k / quantize_row_q80 above.
+
+__device__ __forceinline__ void quant8_q8k(const float (&v)[8], int lane, int8_t* qs, float* d, int16_t* bsums, __half* xh) {
+    float amax = 0.f, mx = 0.f;
+    int idx = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float ax = fabsf(v[i]);
+        if (ax > amax) { amax = ax; idx = lane * 8 + i; mx = v[i]; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float oa = __shfl_xor_sync(0xffffffffu, amax, o);
+        int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        float om = __shfl_xor_sync(0xffffffffu, mx, o);
+        if (oa > amax || (oa == amax && oi < idx)) { amax = oa; idx = oi; mx = om; }
+    }
+    int8_t q[8];
+    int sum = 0;
+    float dd = 0.f;
+    if (amax == 0.f) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = 0;
+    } else {
+        float iscale = -128.f / mx;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float r = roundf(iscale * v[i]);
+            q[i] = (int8_t)(r > 127.f ? 127.f : r);
+            sum += q[i];
+        }
+        dd = 1.0f / iscale;
+    }
+    int2 packed;
+    packed.x = (uint8_t)q[0] | ((uint8_t)q[1] << 8) | ((uint8_t)q[2] << 16) | ((uint32_t)(uint8_t)q[3] << 24);
+    packed.y = (uint8_t)q[4] | ((uint8_t)q[5] << 8) | ((uint8_t)q[6] << 16) | ((uint32_t)(uint8_t)q[7] << 24);
+    *reinterpret_cast<int2*>(qs + lane * 8) = packed;
+    if (xh != nullptr) {
+        __half2 hv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) hv[i] = __floats2half2_rn(__fmul_rn(dd, (float)q[2 * i]), __fmul_rn(dd, (float)q[2 * i + 1]));
+        *reinterpret_cast<uint4*>(xh + lane * 8) = *reinterpret_cast<uint4*>(hv);
+    }
+    int pair = sum + __shfl_xor_sync(0xffffffffu, sum, 1);
+    if ((lane & 1) == 0) bsums[lane >> 1] = (int16_t)pair;
+    if (lane == 0) *d = dd;
+}
+
+__device__ __forceinline__ void quant8_q80(const float (&v)[8], int lane, int8_t* qs, float* d, __half* xh) {
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    float dd = amax / 127.f;
+    float id = dd != 0.f ? 1.0f / dd : 0.f;
+    float ddh = __half2float(__float2half_rn(dd));
+    int8_t q[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] = (int8_t)roundf(v[i] * id);
+    int2 packed;
+    packed.x = (uint8_t)q[0] | ((uint8_t)q[1] << 8) | ((uint8_t)q[2] << 16) | ((uint32_t)(uint8_t)q[3] << 24);
+    packed.y = (uint8_t)q[4] | ((uint8_t)q[5] << 8) | ((uint8_t)q[6] << 16) | ((uint32_t)(uint8_t)q[7] << 24);
+    *reinterpret_cast<int2*>(qs + lane * 8) = packed;
+    if (xh != nullptr) {
+        __half2 hv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) hv[i] = __floats2half2_rn(__fmul_rn(ddh, (float)q[2 * i]), __fmul_rn(ddh, (float)q[2 * i + 1]));
+        *reinterpret_cast<uint4*>(xh + lane * 8) = *reinterpret_cast<uint4*>(hv);
+    }
+    if ((lane & 3) == 0) d[lane >> 2] = ddh;
+}
+
+// Quantise group `grp` (256 values, eight per lane) of output row r.
+__device__ __forceinline__ void quant_group(const float (&v)[8], int lane, int kind, const ActQ& out, int64_t r, int dim, int grp) {
+    if (out.qs == nullptr) return;
+    int8_t* qs = out.qs + r * dim + grp * 256;
+    __half* xh = out.xh ? out.xh + r * dim + grp * 256 : nullptr;
+    if (kind == ACT_Q8K) quant8_q8k(v, lane, qs, out.d + r * (dim / 256) + grp, out.bsums + r * (dim / 16) + grp * 16, xh);
+    else quant8_q80(v, lane, qs, out.d + r * (dim / 32) + grp * 8, xh);
+}
+
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+// One CTA per row, NG groups of 256 per warp held in registers (dim <= 8 warps * NG * 256).
+template <int NG>
+__global__ void __launch_bounds__(NQ_THREADS) add_norm_quant_fast_kernel(NormQuantArgs a) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const int src = a.row_index ? a.row_index[r] : r;
+    const int dim = a.dim, groups = dim / 256;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* h = a.h + (int64_t)src * dim;
+    float x[NG][8];
+    bool live[NG];
+#pragma unroll
+    for (int g = 0; g < NG; ++g) {
+        int grp = warp + g * 8;
+        live[g] = grp < groups;
+        if (live[g]) load8(h + grp * 256 + lane * 8, x[g]);
+        else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[g][i] = 0.f;
+        }
+    }
+    if (a.a != nullptr) {
+        const float* av = a.a + (int64_t)src * dim;
+        float y[NG][8];
+        float ss = 0.f;
+#pragma unroll
+        for (int g = 0; g < NG; ++g) {
+            if (live[g]) {
+                load8(av + (warp + g * 8) * 256 + lane * 8, y[g]);
+                for (int sp = 1; sp < a.a_splits; ++sp) {
+                    float part[8];
+                    load8(av + (int64_t)sp * a.a_split_stride + (warp + g * 8) * 256 + lane * 8, part);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) y[g][i] += part[i];
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) y[g][i] = 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += y[g][i] * y[g][i];
+        }
+        float post_m = 1.f;
+        if (a.post_w != nullptr) {
+            ss = block_sum(ss, red);
+            post_m = sqrtf(ss / (float)dim + a.eps);
+        }
+#pragma unroll
+        for (int g = 0; g < NG; ++g) {
+            if (!live[g]) continue;
+            int base = (warp + g * 8) * 256 + lane * 8;
+            if (a.post_w != nullptr) {
+                float pw[8];
+                load8(a.post_w + base, pw);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) y[g][i] = y[g][i] / post_m * pw[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[g][i] = x[g][i] + y[g][i] * a.a_scale;
+            if (a.row_index == nullptr) store8(h + base, x[g]);
+        }
+    }
+    if (a.norm_w != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int g = 0; g < NG; ++g)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += x[g][i] * x[g][i];
+        ss = block_sum(ss, red);
+        float m = sqrtf(ss / (float)dim + a.eps);
+#pragma unroll
+        for (int g = 0; g < NG; ++g) {
+            if (!live[g]) continue;
+            float nw[8];
+            load8(a.norm_w + (warp + g * 8) * 256 + lane * 8, nw);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[g][i] = x[g][i] / m * nw[i];
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < NG; ++g) {
+        if (!live[g]) continue;  // uniform per warp
+        int grp = warp + g * 8;
+        if (a.normed_out != nullptr) store8(a.normed_out + (int64_t)r * dim + grp * 256 + lane * 8, x[g]);
+        quant_group(x[g], lane, a.act_kind, a.out, r, dim, grp);
+    }
+}
+
+// Rows that need no row-wide statistic: one warp per (row, 256-value group), any number of rows.
+__global__ void __launch_bounds__(NQ_THREADS) quant_groups_kernel(const float* x, int ld, int rows, int dim, int kind, ActQ out) {
+    const int groups = dim / 256;
+    const int64_t wid = (int64_t)blockIdx.x * (NQ_THREADS / 32) + (threadIdx.x >> 5);
+    if (wid >= (int64_t)rows * groups) return;
+    const int r = (int)(wid / groups), grp = (int)(wid - (int64_t)r * groups), lane = threadIdx.x & 31;
+    float v[8];
+    load8(x + (int64_t)r * ld + grp * 256 + lane * 8, v);
+    quant_group(v, lane, kind, out, r, dim, grp);
+}
+
+__global__ void __launch_bounds__(NQ_THREADS) actmul_quant_groups_kernel(const float* gate, const float* up, int ld, int rows, int F,
+                                                                          int act, int kind, ActQ out, float* f32_out) {
+    const int groups = F / 256;
+    const int64_t wid = (int64_t)blockIdx.x * (NQ_THREADS / 32) + (threadIdx.x >> 5);
+    if (wid >= (int64_t)rows * groups) return;
+    const int r = (int)(wid / groups), grp = (int)(wid - (int64_t)r * groups), lane = threadIdx.x & 31;
+    float g[8], u[8], v[8];
+    load8(gate + (int64_t)r * ld + grp * 256 + lane * 8, g);
+    load8(up + (int64_t)r * ld + grp * 256 + lane * 8, u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = (act == 0 ? silu_f(g[i]) : gelu_tanh_f(g[i])) * u[i];
+    if (f32_out) store8(f32_out + (int64_t)r * F + grp * 256 + lane * 8, v);
+    quant_group(v, lane, kind, out, r, F, grp);
+}
+
 }  // namespace
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 void launch_add_norm_quant(const NormQuantArgs& a, cudaStream_t s) {
     if (a.rows <= 0) return;
+    const bool vec_ok = a.dim % 256 == 0 && aligned16(a.h) && aligned16(a.a) && aligned16(a.post_w) && aligned16(a.norm_w) &&
+                        aligned16(a.normed_out) && aligned16(a.out.xh) && (reinterpret_cast<uintptr_t>(a.out.qs) & 7) == 0;
+    if (vec_ok && a.a == nullptr && a.norm_w == nullptr && a.row_index == nullptr && a.normed_out == nullptr) {
+        // plain quantisation: no row-wide dependency
+        int64_t warps = (int64_t)a.rows * (a.dim / 256);
+        quant_groups_kernel<<<(unsigned)((warps + 7) / 8), NQ_THREADS, 0, s>>>(a.h, a.dim, a.rows, a.dim, a.act_kind, a.out);
+        MK_LAUNCH_CHECK();
+        return;
+    }
+    if (vec_ok && a.dim <= 8 * 4 * 256) {
+        int ng = (a.dim / 256 + 7) / 8;
+        if (ng == 1) add_norm_quant_fast_kernel<1><<<a.rows, NQ_THREADS, 0, s>>>(a);
+        else if (ng == 2) add_norm_quant_fast_kernel<2><<<a.rows, NQ_THREADS, 0, s>>>(a);
+        else add_norm_quant_fast_kernel<4><<<a.rows, NQ_THREADS, 0, s>>>(a);
+        MK_LAUNCH_CHECK();
+        return;
+    }
     size_t smem = (size_t)a.dim * sizeof(float);
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
@@ -201,6 +434,13 @@ void launch_add_norm_quant(const NormQuantArgs& a, cudaStream_t s) {
 void launch_actmul_quant(const float* gate, const float* up, int ld, int T, int F, int act, int act_kind, ActQ out,
                          float* f32_out, cudaStream_t s) {
     if (T <= 0) return;
+    if (F % 256 == 0 && ld % 4 == 0 && aligned16(gate) && aligned16(up) && aligned16(f32_out) && aligned16(out.xh) &&
+        (reinterpret_cast<uintptr_t>(out.qs) & 7) == 0) {
+        int64_t warps = (int64_t)T * (F / 256);
+        actmul_quant_groups_kernel<<<(unsigned)((warps + 7) / 8), NQ_THREADS, 0, s>>>(gate, up, ld, T, F, act, act_kind, out, f32_out);
+        MK_LAUNCH_CHECK();
+        return;
+    }
     size_t smem = (size_t)F * sizeof(float);
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {

@@ -66,7 +66,8 @@ def test_qgemm_tensor_matches_oracle(ops, orc, name, T, rows, cols):
 
 
 @pytest.mark.parametrize("name", list(QTYPES))
-@pytest.mark.parametrize("T,rows,cols", [(9, 128, 256), (130, 300, 1024), (257, 2048, 2048), (700, 512, 5632), (2048, 1152, 768)])
+@pytest.mark.parametrize("T,rows,cols", [(9, 128, 256), (40, 2048, 2048), (64, 512, 5632), (100, 300, 1024), (130, 300, 1024),
+                                          (257, 2048, 2048), (700, 512, 5632), (2048, 1152, 768)])
 def test_f16_image_gemm_matches_oracle(ops, orc, name, T, rows, cols):
     """The wide-batch path: weights rounded once to f16 at load time, TMA-fed tcgen05 GEMM.  Ragged edges on
     purpose: T and rows that are not multiples of the tile, several K blocks, more tiles than SMs."""

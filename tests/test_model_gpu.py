@@ -147,12 +147,15 @@ def test_single_layer_models_match_tightly(pk, tmp_path_factory, fam):
 
 
 @pytest.mark.parametrize("fam", ["llama", "qwen3", "gemma2"])
-def test_family_matches_oracle_on_the_tensor_core_path_with_f16_kv(pk, tmp_path_factory, fam):
-    """The B200 configuration: f16 KV and tcgen05 matmuls; the oracle keeps f32 KV like the reference."""
+@pytest.mark.parametrize("matmul_path", [2, 3, 0])
+def test_family_matches_oracle_on_the_tensor_core_path_with_f16_kv(pk, tmp_path_factory, fam, matmul_path):
+    """The B200 configuration: f16 KV and tcgen05 matmuls (2: GGUF blocks dequantised in the kernel; 3: the f16
+    weight images with fused projections and split-K shares; 0: the automatic mix); the oracle keeps f32 KV
+    like the reference."""
     path, spec = make_checkpoint(pk, tmp_path_factory, fam)
     rng = np.random.default_rng(2)
     prompts = [rng.integers(3, spec.vocab, size=n) for n in (50, 19, 70)]
-    model, pe, om, oe_, alt = run_pair(pk, path, prompts, [5, 5, 5], kv_dtype="f16", matmul_path=2, oracle_kv="f32")
+    model, pe, om, oe_, alt = run_pair(pk, path, prompts, [5, 5, 5], kv_dtype="f16", matmul_path=matmul_path, oracle_kv="f32")
     print(fam, compare(pe, oe_, alt, 3))
     assert model.pool_stats() == om.pool.stats()
 
