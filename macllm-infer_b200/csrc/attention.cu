@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_tile_kernel(AttnArgs a) {
             float4 kv4 = make_float4(0.f, 0.f, 0.f, 0.f), vv4 = kv4;
             if (pos < k_end) {
                 int64_t blk = a.batch.tables[hdr.table_off + pos / a.block_tokens];
-                int64_t base = (((blk * a.layers + a.layer) * a.kv_heads + kvh) * a.block_tokens + pos % a.block_tokens) *
+                int64_t base = ((kv_page_index(blk, a.layer, a.layers, a.pool_blocks) * a.kv_heads + kvh) * a.block_tokens + pos % a.block_tokens) *
                                    (int64_t)d + c;
                 kv4 = make_float4(kv_to_float<KV>(kp[base]), kv_to_float<KV>(kp[base + 1]), kv_to_float<KV>(kp[base + 2]),
                                   kv_to_float<KV>(kp[base + 3]));

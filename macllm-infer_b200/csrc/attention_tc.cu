@@ -7,9 +7,11 @@
 // one CTA owns 16*WARPS (query row, query head) items that all read ONE KV head, so every K/V page
 // is fetched once for the whole query group; pages travel global -> shared with 16-byte cp.async in a
 // two-stage pipeline; Q.K^T and P.V run on the tensor cores (mma.sync m16n8k16, f16 operands, f32
-// accumulators) and the online softmax stays in f32 registers.  Decode lanes use one warp per CTA and
-// split the key range over CTAs (scratch: unnormalised partial outputs + running max / sum per item),
-// merged by attn_combine_kernel.  Queries are rounded to f16 once; K/V are read as stored.
+// accumulators) and the online softmax stays in f32 registers.  One-token lanes run attn_decode_kernel: the
+// keys are shared out over the four warps of a CTA (warp-private cp.async rings, merge in shared memory) and,
+// when few lanes have long histories, over several CTAs as well (scratch: unnormalised partial outputs +
+// running max / sum per head, merged by attn_combine_kernel).  Queries are rounded to f16 once; K/V are read
+// as stored.
 #include "kernels.h"
 #include "attention_tc.h"
 #include <algorithm>
@@ -128,8 +130,9 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tc_kernel(AttnTcArgs a) {
             bool valid = pos < k_hi;
             int64_t base = 0;
             if (valid) {
-                int64_t blk = a.tables[hdr.table_off + pos / a.block_tokens];
-                base = (((blk * a.layers + a.layer) * a.kv_heads + kvh) * a.block_tokens + pos % a.block_tokens) * (int64_t)D + c;
+                int64_t blk = a.tables[hdr.table_off + (pos >> a.bt_shift)];
+                base = ((kv_page_index(blk, a.layer, a.layers, a.pool_blocks) * a.kv_heads + kvh) * a.block_tokens +
+                        (pos & (a.block_tokens - 1))) * (int64_t)D + c;
             }
             cp_async16(kd + key * DP + c, kp + base, valid);
             cp_async16(vd + key * DP + c, vp + base, valid);
@@ -202,7 +205,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tc_kernel(AttnTcArgs a) {
             tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 2));
             float m_new = fmaxf(m_run[h], tmax[h]);
             m_use[h] = m_new == -INFINITY ? 0.f : m_new;
-            alpha[h] = m_run[h] == -INFINITY ? 0.f : expf(m_run[h] - m_use[h]);
+            alpha[h] = m_run[h] == -INFINITY ? 0.f : __expf(m_run[h] - m_use[h]);
             m_run[h] = m_new;
         }
         float psum[2] = {0.f, 0.f};
@@ -211,7 +214,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tc_kernel(AttnTcArgs a) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 int h = e >> 1;
-                float p = s[j][e] == -INFINITY ? 0.f : expf(s[j][e] - m_use[h]);
+                float p = s[j][e] == -INFINITY ? 0.f : __expf(s[j][e] - m_use[h]);
                 s[j][e] = p;
                 psum[h] += p;
             }
@@ -276,6 +279,227 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tc_kernel(AttnTcArgs a) {
     }
 }
 
+// One-token lanes.  Work item = entries[blockIdx.x] = (lane, share, n_shares) x KV head.  The four warps of the
+// CTA take the 16-key tiles of the share round-robin, each through its own ring of cp.async stages (no
+// block-wide barrier inside the loop), keep their own running max / sum / output, and merge through shared
+// memory at the end.  n_shares == 1: the CTA writes the normalised output.  Otherwise it writes the
+// unnormalised partial for attn_combine_kernel.
+template <int D, int STAGES>
+__global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
+    constexpr int DP = D + 8;
+    constexpr int KT = 16;
+    constexpr int NT_O = D / 8;
+    constexpr int CHUNKS = D / 8;
+    constexpr int RING_HALVES = STAGES * 2 * KT * DP;  // per warp: STAGES x (K tile + V tile)
+    static_assert(RING_HALVES * 2 >= 16 * D * 4 + 16 * 2 * 4, "a warp's ring must hold its partial result");
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __half* Qs = reinterpret_cast<__half*>(smem_raw);  // [16][DP]
+    __half* rings = Qs + 16 * DP;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int gid = lane >> 2, tq = lane & 3;
+    const int kvh = blockIdx.y;
+    const int g = a.q_heads / a.kv_heads;
+    // one 32-byte record per work item, so that nothing but the block table and the queries is a dependent load
+    const int4 e0 = reinterpret_cast<const int4*>(a.entries)[2 * blockIdx.x];
+    const int4 e1 = reinterpret_cast<const int4*>(a.entries)[2 * blockIdx.x + 1];
+    const int split = e0.y, n_splits = e0.z, start_pos = e0.w, table_off = e1.x, q_off = e1.y;
+    const int ldq = a.ldq > 0 ? a.ldq : a.q_heads * D;
+
+    // the group's query heads -> rows 0..g-1 of the A operand, the rest zero
+    for (int i = tid; i < 16 * CHUNKS; i += 128) {
+        int item = i / CHUNKS, c = (i - item * CHUNKS) * 8;
+        __half2 h[4];
+        if (item < g) {
+            const float* src = a.q + (int64_t)q_off * ldq + (kvh * g + item) * D + c;
+            float4 x0 = *reinterpret_cast<const float4*>(src), x1 = *reinterpret_cast<const float4*>(src + 4);
+            h[0] = __floats2half2_rn(x0.x, x0.y);
+            h[1] = __floats2half2_rn(x0.z, x0.w);
+            h[2] = __floats2half2_rn(x1.x, x1.y);
+            h[3] = __floats2half2_rn(x1.z, x1.w);
+        } else {
+            h[0] = h[1] = h[2] = h[3] = __floats2half2_rn(0.f, 0.f);
+        }
+        *reinterpret_cast<uint4*>(Qs + item * DP + c) = *reinterpret_cast<uint4*>(h);
+    }
+
+    const int p = start_pos;  // the query's position
+    int k_lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+    int k_hi = p + 1;
+    {
+        int len = k_hi - k_lo;
+        int chunk = ((len + n_splits - 1) / n_splits + 15) / 16 * 16;
+        k_lo = k_lo + split * chunk;
+        k_hi = min(k_hi, k_lo + chunk);
+    }
+    const int k_begin = k_lo / 16 * 16;
+    const int n_tiles = k_hi > k_begin ? (k_hi - k_begin + KT - 1) / KT : 0;
+    const int my_tiles = n_tiles > warp ? (n_tiles - warp + 3) / 4 : 0;  // tiles warp, warp + 4, ...
+
+    const __half* kp = reinterpret_cast<const __half*>(a.k_pool);
+    const __half* vp = reinterpret_cast<const __half*>(a.v_pool);
+    __half* ring = rings + warp * RING_HALVES;
+    auto load_tile = [&](int i) {  // the warp's i-th tile into stage i % STAGES
+        __half* kd = ring + (i % STAGES) * 2 * KT * DP;
+        __half* vd = kd + KT * DP;
+        // 16 keys starting at a multiple of 16 lie in one page (block_tokens is a multiple of 16): one table
+        // lookup, then the tile is one contiguous run of 16 * D halves in each pool
+        const int pos0 = k_begin + (warp + 4 * i) * KT;
+        const int64_t blk = a.tables[table_off + (pos0 >> a.bt_shift)];
+        const int64_t src0 = ((kv_page_index(blk, a.layer, a.layers, a.pool_blocks) * a.kv_heads + kvh) * a.block_tokens +
+                              (pos0 & (a.block_tokens - 1))) * (int64_t)D;
+        const int n_valid = k_hi - pos0;  // keys of the tile inside the share
+#pragma unroll
+        for (int j = lane; j < KT * CHUNKS; j += 32) {
+            const int key = j / CHUNKS, c = (j % CHUNKS) * 8;
+            const bool valid = key < n_valid;
+            const int64_t src = valid ? src0 + (int64_t)j * 8 : 0;
+            cp_async16(kd + key * DP + c, kp + src, valid);
+            cp_async16(vd + key * DP + c, vp + src, valid);
+        }
+    };
+
+    float o_acc[NT_O][4];
+#pragma unroll
+    for (int j = 0; j < NT_O; ++j) o_acc[j][0] = o_acc[j][1] = o_acc[j][2] = o_acc[j][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const bool live_r[2] = {gid < g, gid + 8 < g};
+
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) {
+        if (i < my_tiles) load_tile(i);
+        cp_async_commit();
+    }
+    __syncthreads();  // Qs complete
+
+    for (int i = 0; i < my_tiles; ++i) {
+        if (i + STAGES - 1 < my_tiles) load_tile(i + STAGES - 1);
+        cp_async_commit();
+        cp_async_wait<STAGES - 1>();
+        __syncwarp();
+        const __half* kt = ring + (i % STAGES) * 2 * KT * DP;
+        const __half* vt = kt + KT * DP;
+
+        float sc[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            uint32_t af[4], bf[4];
+            ldmatrix_x4(af, Qs + (lane & 15) * DP + kk * 16 + (lane >> 4) * 8);
+            ldmatrix_x4(bf, kt + ((lane & 7) + (lane >> 4) * 8) * DP + kk * 16 + ((lane >> 3) & 1) * 8);
+            mma16816(sc[0], af, bf[0], bf[1]);
+            mma16816(sc[1], af, bf[2], bf[3]);
+        }
+        const int tile_pos = k_begin + (warp + 4 * i) * KT;
+        float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                int h = e >> 1;
+                int pos = tile_pos + j * 8 + 2 * tq + (e & 1);
+                float v = sc[j][e] * a.scale;
+                if (a.softcap != 0.f) v = tanhf(v / a.softcap) * a.softcap;
+                bool vis = live_r[h] && pos >= k_lo && pos < k_hi;  // k_lo / k_hi already carry causality and the window
+                v = vis ? v : -INFINITY;
+                sc[j][e] = v;
+                tmax[h] = fmaxf(tmax[h], v);
+            }
+        }
+        float alpha[2], m_use[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 1));
+            tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 2));
+            float m_new = fmaxf(m_run[h], tmax[h]);
+            m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+            alpha[h] = m_run[h] == -INFINITY ? 0.f : __expf(m_run[h] - m_use[h]);
+            m_run[h] = m_new;
+        }
+        float psum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                int h = e >> 1;
+                float pe = sc[j][e] == -INFINITY ? 0.f : __expf(sc[j][e] - m_use[h]);
+                sc[j][e] = pe;
+                psum[h] += pe;
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], 1);
+            psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], 2);
+            l_run[h] = l_run[h] * alpha[h] + psum[h];
+        }
+#pragma unroll
+        for (int j = 0; j < NT_O; ++j) {
+            o_acc[j][0] *= alpha[0];
+            o_acc[j][1] *= alpha[0];
+            o_acc[j][2] *= alpha[1];
+            o_acc[j][3] *= alpha[1];
+        }
+        uint32_t pf[4] = {pack_half2(sc[0][0], sc[0][1]), pack_half2(sc[0][2], sc[0][3]), pack_half2(sc[1][0], sc[1][1]),
+                          pack_half2(sc[1][2], sc[1][3])};
+#pragma unroll
+        for (int j = 0; j < NT_O; j += 2) {
+            uint32_t bf[4];
+            ldmatrix_x4_trans(bf, vt + ((lane & 7) + ((lane >> 3) & 1) * 8) * DP + j * 8 + (lane >> 4) * 8);
+            mma16816(o_acc[j], pf, bf[0], bf[1]);
+            mma16816(o_acc[j + 1], pf, bf[2], bf[3]);
+        }
+        __syncwarp();  // the stage is refilled by the next iteration's load
+    }
+    cp_async_wait<0>();
+    __syncwarp();
+
+    // each warp leaves (max, sum, output) of its live rows in its own ring, then everyone merges
+    float* w_o = reinterpret_cast<float*>(ring);            // [16][D]
+    float* w_ml = w_o + 16 * D;                              // [16][2]
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        int item = gid + 8 * h;
+        if (item >= g) continue;
+#pragma unroll
+        for (int j = 0; j < NT_O; ++j)
+            *reinterpret_cast<float2*>(w_o + item * D + j * 8 + 2 * tq) = make_float2(o_acc[j][2 * h], o_acc[j][2 * h + 1]);
+        if (tq == 0) {
+            w_ml[item * 2] = m_run[h];
+            w_ml[item * 2 + 1] = l_run[h];
+        }
+    }
+    __syncthreads();
+    const int64_t slot = ((int64_t)blockIdx.x * a.kv_heads + kvh) * 16;
+    for (int idx = tid; idx < g * D; idx += 128) {
+        int item = idx / D, c = idx - item * D;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, reinterpret_cast<const float*>(rings + w * RING_HALVES)[16 * D + item * 2]);
+        float l = 0.f, o = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float* ro = reinterpret_cast<const float*>(rings + w * RING_HALVES);
+            float mw = ro[16 * D + item * 2];
+            if (mw != -INFINITY) {
+                float f = __expf(mw - m);
+                l += ro[16 * D + item * 2 + 1] * f;
+                o += ro[item * D + c] * f;
+            }
+        }
+        if (n_splits == 1) {
+            a.out[(int64_t)q_off * a.q_heads * D + (kvh * g + item) * D + c] = o / l;
+        } else {
+            a.part_o[(slot + item) * D + c] = o;
+            if (c == 0) {
+                a.part_ml[(slot + item) * 2] = m;
+                a.part_ml[(slot + item) * 2 + 1] = l;
+            }
+        }
+    }
+}
+
 // Merge the key shares of one-token lanes: grid (decode lane, kv head), one warp per query head of the group.
 __global__ void attn_combine_kernel(AttnTcArgs a, int D) {
     const int dl = blockIdx.x, kvh = blockIdx.y;
@@ -288,7 +512,7 @@ __global__ void attn_combine_kernel(AttnTcArgs a, int D) {
     float l = 0.f;
     for (int s = 0; s < n_splits; ++s) {
         const float* ml = a.part_ml + (((int64_t)(first + s) * a.kv_heads + kvh) * 16 + hq) * 2;
-        if (ml[0] != -INFINITY) l += ml[1] * expf(ml[0] - m);
+        if (ml[0] != -INFINITY) l += ml[1] * __expf(ml[0] - m);
     }
     const int q_off = a.cu_seqlens[lane_id];
     float* o = a.out + (int64_t)q_off * a.q_heads * D + (kvh * g + hq) * D;
@@ -297,7 +521,7 @@ __global__ void attn_combine_kernel(AttnTcArgs a, int D) {
         for (int s = 0; s < n_splits; ++s) {
             int64_t slot = ((int64_t)(first + s) * a.kv_heads + kvh) * 16 + hq;
             float ms = a.part_ml[slot * 2];
-            if (ms != -INFINITY) acc += a.part_o[slot * D + c] * expf(ms - m);
+            if (ms != -INFINITY) acc += a.part_o[slot * D + c] * __expf(ms - m);
         }
         o[c] = acc / l;
     }
@@ -323,7 +547,18 @@ void launch_for_dim(const AttnTcArgs& a, int warps, cudaStream_t s) {
         else launch_variant<D, 4, 64, false>(a, a.n_tiles, s);
     }
     if (a.n_entries > 0) {
-        launch_variant<D, 1, 16, true>(a, a.n_entries, s);
+        constexpr int STAGES = D >= 256 ? 2 : 3;
+        constexpr size_t smem = (size_t)(16 + 4 * STAGES * 2 * 16) * (D + 8) * sizeof(__half);
+        static bool configured = false;
+        if (!configured) {
+            MK_CUDA(cudaFuncSetAttribute(attn_decode_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            configured = true;
+        }
+        dim3 grid((unsigned)a.n_entries, (unsigned)a.kv_heads);
+        attn_decode_kernel<D, STAGES><<<grid, 128, smem, s>>>(a);
+        MK_LAUNCH_CHECK();
+    }
+    if (a.n_dec_lanes > 0) {  // lanes whose keys were shared out over several CTAs
         dim3 grid((unsigned)a.n_dec_lanes, (unsigned)a.kv_heads);
         attn_combine_kernel<<<grid, 32 * (a.q_heads / a.kv_heads), 0, s>>>(a, D);
         MK_LAUNCH_CHECK();
@@ -332,8 +567,9 @@ void launch_for_dim(const AttnTcArgs& a, int warps, cudaStream_t s) {
 
 }  // namespace
 
-bool attention_tc_supported(int q_heads, int kv_heads, int head_dim, bool kv_f16) {
+bool attention_tc_supported(int q_heads, int kv_heads, int head_dim, int block_tokens, bool kv_f16) {
     int g = kv_heads > 0 ? q_heads / kv_heads : 0;
+    if (block_tokens < 16 || (block_tokens & (block_tokens - 1)) != 0) return false;  // pages hold whole 16-key tiles
     return kv_f16 && (head_dim == 64 || head_dim == 128 || head_dim == 256) && (g == 1 || g == 2 || g == 4 || g == 8) &&
            q_heads == g * kv_heads;
 }
@@ -344,7 +580,8 @@ int attention_tc_tile_rows(int q_heads, int kv_heads) { return 16 * attention_tc
 
 int attention_tc_max_entries(int lanes, int kv_heads) { return lanes + kAttnTargetCtas / kv_heads + 1; }
 
-void plan_attention_tc(const int32_t* start_pos, const int32_t* n_tokens, int lanes, int q_heads, int kv_heads, AttnTcPlan& plan) {
+void plan_attention_tc(const int32_t* start_pos, const int32_t* n_tokens, const int32_t* n_blocks, int lanes, int q_heads,
+                       int kv_heads, AttnTcPlan& plan) {
     plan.tiles.clear();
     plan.entries.clear();
     plan.dec_lanes.clear();
@@ -352,17 +589,19 @@ void plan_attention_tc(const int32_t* start_pos, const int32_t* n_tokens, int la
     int n_dec = 0;
     for (int i = 0; i < lanes; ++i) n_dec += n_tokens[i] == 1 ? 1 : 0;
     const int budget = std::max(1, kAttnTargetCtas / kv_heads / std::max(1, n_dec));
-    for (int i = 0; i < lanes; ++i) {
+    int q_off = 0, table_off = 0;
+    for (int i = 0; i < lanes; q_off += n_tokens[i], table_off += n_blocks[i], ++i) {
         if (n_tokens[i] == 1) {
             int ctx = start_pos[i] + 1;
             int splits = std::max(1, std::min(std::min(budget, kAttnMaxSplits), (ctx + kAttnMinSplitKeys - 1) / kAttnMinSplitKeys));
-            plan.dec_lanes.push_back(i);
-            plan.dec_lanes.push_back(plan.n_entries());
-            plan.dec_lanes.push_back(splits);
+            if (splits > 1) {  // merged by the combine kernel
+                plan.dec_lanes.push_back(i);
+                plan.dec_lanes.push_back(plan.n_entries());
+                plan.dec_lanes.push_back(splits);
+            }
             for (int sidx = 0; sidx < splits; ++sidx) {
-                plan.entries.push_back(i);
-                plan.entries.push_back(sidx);
-                plan.entries.push_back(splits);
+                const int32_t rec[8] = {i, sidx, splits, start_pos[i], table_off, q_off, 0, 0};
+                plan.entries.insert(plan.entries.end(), rec, rec + 8);
             }
         } else {
             for (int r0 = 0; r0 < n_tokens[i]; r0 += tile_rows) {
@@ -373,7 +612,12 @@ void plan_attention_tc(const int32_t* start_pos, const int32_t* n_tokens, int la
     }
 }
 
-int launch_paged_attention_tc(const AttnTcArgs& a, cudaStream_t s) {
+int launch_paged_attention_tc(const AttnTcArgs& a_in, cudaStream_t s) {
+    AttnTcArgs a = a_in;
+    if (!attention_tc_supported(a.q_heads, a.kv_heads, a.d, a.block_tokens, true))
+        throw std::runtime_error("launch_paged_attention_tc: unsupported shape");
+    a.bt_shift = 0;
+    while ((1 << a.bt_shift) < a.block_tokens) ++a.bt_shift;
     int warps = attention_tc_warps(a.q_heads, a.kv_heads);
     switch (a.d) {
         case 64: launch_for_dim<64>(a, warps, s); break;
@@ -381,7 +625,7 @@ int launch_paged_attention_tc(const AttnTcArgs& a, cudaStream_t s) {
         case 256: launch_for_dim<256>(a, warps, s); break;
         default: throw std::runtime_error("launch_paged_attention_tc: unsupported head_dim");
     }
-    return (a.n_tiles > 0 ? 1 : 0) + (a.n_entries > 0 ? 2 : 0);
+    return (a.n_tiles > 0 ? 1 : 0) + (a.n_entries > 0 ? 1 : 0) + (a.n_dec_lanes > 0 ? 1 : 0);
 }
 
 }  // namespace mk

@@ -300,16 +300,19 @@ int32_t mk_k_attention_step(const mk_attn_case* c) {
         at.softcap = c->softcap;
         at.window = c->window;
         at.q_tile = q_tile;
-        const bool tc_ok = attention_tc_supported(c->q_heads, c->kv_heads, d, c->kv_f16 != 0);
+        const bool tc_ok = attention_tc_supported(c->q_heads, c->kv_heads, d, c->block_tokens, c->kv_f16 != 0);
         if (c->kernel == 2 && !tc_ok) throw std::runtime_error("mk_k_attention_step: the tensor-core kernel does not cover this shape");
         if (c->kernel < 0 || c->kernel > 2) throw std::runtime_error("mk_k_attention_step: unknown kernel selector");
         DevBuf work, part_o, part_ml;
         if (tc_ok && c->kernel != 1) {
             AttnTcPlan plan;
-            plan_attention_tc(c->start_pos, c->lane_len, lanes, c->q_heads, c->kv_heads, plan);
+            // the kernels address block tables through LaneHeader::table_off; the plan assumes tables packed in lane order
+            for (int l = 0, off = 0; l < lanes; off += c->table_len[l], ++l)
+                if (c->table_off[l] != off) throw std::runtime_error("mk_k_attention_step: block tables must be packed in lane order");
+            plan_attention_tc(c->start_pos, c->lane_len, c->table_len, lanes, c->q_heads, c->kv_heads, plan);
             std::vector<int32_t> lists;
-            lists.insert(lists.end(), plan.tiles.begin(), plan.tiles.end());
             lists.insert(lists.end(), plan.entries.begin(), plan.entries.end());
+            lists.insert(lists.end(), plan.tiles.begin(), plan.tiles.end());
             lists.insert(lists.end(), plan.dec_lanes.begin(), plan.dec_lanes.end());
             work.alloc(std::max<size_t>(lists.size(), 1) * 4);
             if (!lists.empty()) work.upload(lists.data(), lists.size() * 4);
@@ -323,9 +326,9 @@ int32_t mk_k_attention_step(const mk_attn_case* c) {
             ta.hdr = b.hdr;
             ta.tables = b.tables;
             ta.cu_seqlens = b.cu_seqlens;
-            ta.tiles = work.as<int32_t>();
-            ta.entries = ta.tiles + plan.tiles.size();
-            ta.dec_lanes = ta.entries + plan.entries.size();
+            ta.entries = work.as<int32_t>();
+            ta.tiles = ta.entries + plan.entries.size();
+            ta.dec_lanes = ta.tiles + plan.tiles.size();
             ta.n_tiles = plan.n_tiles();
             ta.n_entries = plan.n_entries();
             ta.n_dec_lanes = plan.n_dec_lanes();

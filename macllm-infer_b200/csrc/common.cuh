@@ -57,6 +57,14 @@ inline void cuda_check(cudaError_t e, const char* what, const char* file, int li
 #define MK_CUDA(x) ::mk::cuda_check((x), #x, __FILE__, __LINE__)
 #define MK_LAUNCH_CHECK() ::mk::cuda_check(cudaGetLastError(), "kernel launch", __FILE__, __LINE__)
 
+// Index of the (block, layer) page of a paged KV pool whose pages are [kv_heads][block_tokens][head_dim].
+// pool_blocks > 0: layer-major pool [layers][pool_blocks] - one layer's pages are contiguous, so the attention
+// of a layer walks one compact region (this is how the model lays its pools out); pool_blocks == 0: block-major
+// pool [blocks][layers] (the layout of host-provided pools in the kernel-level entry points).
+__host__ __device__ __forceinline__ int64_t kv_page_index(int64_t blk, int layer, int layers, int64_t pool_blocks) {
+    return pool_blocks > 0 ? (int64_t)layer * pool_blocks + blk : blk * layers + layer;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -93,12 +93,13 @@ struct RopeKvArgs {
     void* v_pool = nullptr;
     int kv_f16 = 1;
     int T = 0, q_heads = 0, kv_heads = 0, d = 0, block_tokens = 16, layers = 0, layer = 0;
+    int64_t pool_blocks = 0;  // see kv_page_index
 };
 void launch_rope_kv(const RopeKvArgs& a, cudaStream_t s);
 
 // Copy `rows` token rows of every layer and head from block src to block dst (copy-on-write).
 void launch_cow_copy(void* k_pool, void* v_pool, int kv_f16, int64_t src_block, int64_t dst_block, int rows,
-                     int layers, int kv_heads, int block_tokens, int d, cudaStream_t s);
+                     int layers, int64_t pool_blocks, int kv_heads, int block_tokens, int d, cudaStream_t s);
 
 // ---- attention ---------------------------------------------------------------------------------
 struct AttnArgs {
@@ -110,6 +111,7 @@ struct AttnArgs {
     int kv_f16 = 1;
     BatchDesc batch;
     int q_heads = 0, kv_heads = 0, d = 0, block_tokens = 16, layers = 0, layer = 0;
+    int64_t pool_blocks = 0;  // see kv_page_index
     float scale = 1.f, softcap = 0.f;
     int window = 0;  // 0 = full causal
     int q_tile = 0;

@@ -174,13 +174,13 @@ Model::Model(const std::string& gguf_path, const ModelConfig& cfg) : cfg_(cfg) {
     consider(ms_.tied ? token_embd_.w : output_.w, B);
     tc_ws_.partial.alloc(std::max<size_t>(partial, 1) * 4);
     size_t stage_bytes = (size_t)B * sizeof(LaneHeader) + (size_t)(pool_->max_blocks() + B) * 4 + (size_t)T * 4 + 64;
-    attn_tc_ = attention_tc_supported(ms_.q_heads, ms_.kv_heads, ms_.head_dim, cfg_.kv_f16);
+    attn_tc_ = attention_tc_supported(ms_.q_heads, ms_.kv_heads, ms_.head_dim, cfg_.block_tokens, cfg_.kv_f16);
     if (attn_tc_) {
         attn_max_entries_ = attention_tc_max_entries(B, ms_.kv_heads);
         attn_part_o_.alloc((size_t)attn_max_entries_ * ms_.kv_heads * 16 * ms_.head_dim * 4);
         attn_part_ml_.alloc((size_t)attn_max_entries_ * ms_.kv_heads * 16 * 2 * 4);
-        // work lists: prefill tiles (2 ints), key-share entries (3 ints), one-token lanes (3 ints)
-        stage_bytes += ((size_t)(T + B) * 2 + (size_t)attn_max_entries_ * 3 + (size_t)B * 3) * 4;
+        // work lists: key-share entries (8 ints), prefill tiles (2 ints), split one-token lanes (3 ints)
+        stage_bytes += ((size_t)(T + B) * 2 + (size_t)attn_max_entries_ * 8 + (size_t)B * 3) * 4 + 16;
     }
     stage_host_.ensure(stage_bytes);
     stage_dev_.alloc(stage_bytes);
@@ -495,15 +495,20 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
     if (attn_tc_) {
         plan_sp_.resize((size_t)B);
         plan_nt_.resize((size_t)B);
-        for (int i = 0; i < B; ++i) { plan_sp_[(size_t)i] = lanes[(size_t)i].start_pos; plan_nt_[(size_t)i] = lanes[(size_t)i].n_tokens; }
-        plan_attention_tc(plan_sp_.data(), plan_nt_.data(), B, ms_.q_heads, ms_.kv_heads, attn_plan_);
+        plan_nb_.resize((size_t)B);
+        for (int i = 0; i < B; ++i) {
+            plan_sp_[(size_t)i] = lanes[(size_t)i].start_pos;
+            plan_nt_[(size_t)i] = lanes[(size_t)i].n_tokens;
+            plan_nb_[(size_t)i] = hdr[i].n_blocks;
+        }
+        plan_attention_tc(plan_sp_.data(), plan_nt_.data(), plan_nb_.data(), B, ms_.q_heads, ms_.kv_heads, attn_plan_);
         n_attn_tiles = attn_plan_.n_tiles();
         n_attn_entries = attn_plan_.n_entries();
         n_attn_dec = attn_plan_.n_dec_lanes();
         if (n_attn_entries > attn_max_entries_) throw std::runtime_error("attention work list exceeds its scratch");
-        off_tiles = (stage_bytes + 15) / 16 * 16;
-        off_entries = off_tiles + attn_plan_.tiles.size() * 4;
-        off_dec = off_entries + attn_plan_.entries.size() * 4;
+        off_entries = (stage_bytes + 15) / 16 * 16;  // 32-byte records read as two 16-byte loads
+        off_tiles = off_entries + attn_plan_.entries.size() * 4;
+        off_dec = off_tiles + attn_plan_.tiles.size() * 4;
         stage_bytes = off_dec + attn_plan_.dec_lanes.size() * 4;
         if (stage_bytes > stage_host_.size()) throw std::runtime_error("tick staging buffer is too small");
         if (n_attn_tiles) memcpy(hp + off_tiles, attn_plan_.tiles.data(), attn_plan_.tiles.size() * 4);
@@ -539,7 +544,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
 
     // ---- copy-on-write page copies of shared partial tails (cache.rs:3042-3089)
     for (const KvCowCopy& c : r.cow_copies()) {
-        launch_cow_copy(k_pool_.ptr(), v_pool_.ptr(), cfg_.kv_f16 ? 1 : 0, c.src_slot, c.dst_slot, c.rows, ms_.layers, ms_.kv_heads, bt,
+        launch_cow_copy(k_pool_.ptr(), v_pool_.ptr(), cfg_.kv_f16 ? 1 : 0, c.src_slot, c.dst_slot, c.rows, ms_.layers, pool_->max_blocks(), ms_.kv_heads, bt,
                         d, stream_);
         ++launches_;
     }
@@ -607,6 +612,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         ra.d = d;
         ra.block_tokens = bt;
         ra.layers = ms_.layers;
+        ra.pool_blocks = pool_->max_blocks();
         ra.layer = l;
         prof_begin(KC_ROPE_KV, 4.0 * T * (2 * AW + 2 * KW) + (cfg_.kv_f16 ? 2.0 : 4.0) * 2 * T * KW, 0);
         launch_rope_kv(ra, stream_);
@@ -625,6 +631,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         at.d = d;
         at.block_tokens = bt;
         at.layers = ms_.layers;
+        at.pool_blocks = pool_->max_blocks();
         at.layer = l;
         at.scale = ls.scale;
         at.softcap = ls.softcap;
@@ -665,6 +672,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
             ta.d = d;
             ta.block_tokens = bt;
             ta.layers = ms_.layers;
+            ta.pool_blocks = at.pool_blocks;
             ta.layer = l;
             ta.scale = ls.scale;
             ta.softcap = ls.softcap;

@@ -125,7 +125,7 @@ private:
     int matmul_half(const HalfWeight& W, const ActQ& x, int T, float* y, int ldy, float scale, float softcap, int max_splits = 1);
     int attn_max_entries_ = 0;
     AttnTcPlan attn_plan_;
-    std::vector<int32_t> plan_sp_, plan_nt_;
+    std::vector<int32_t> plan_sp_, plan_nt_, plan_nb_;
     // activations
     // qkv_: [T][AW + 2 KW] (q | k | v per row); gu_: [T][2 ffn] (gate | up per row)
     DevBuf h_, qkv_, attn_, proj_, gu_, down_, normed_, logits_, tokens_;

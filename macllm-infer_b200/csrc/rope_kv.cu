@@ -74,19 +74,19 @@ __global__ void __launch_bounds__(RK_WARPS * 32) rope_kv_kernel(RopeKvArgs a) {
     } else {
         int64_t slot = a.slots[t];
         int64_t blk = slot / a.block_tokens, row = slot % a.block_tokens;
-        int64_t base = (((blk * a.layers + a.layer) * a.kv_heads + hh) * a.block_tokens + row) * (int64_t)d;
+        int64_t base = ((kv_page_index(blk, a.layer, a.layers, a.pool_blocks) * a.kv_heads + hh) * a.block_tokens + row) * (int64_t)d;
         KV* pool = reinterpret_cast<KV*>(kind == 1 ? a.k_pool : a.v_pool);
         for (int i = lane; i < d; i += 32) pool[base + i] = to_kv<KV>(x[i]);
     }
 }
 
 template <typename KV>
-__global__ void cow_copy_kernel(KV* k_pool, KV* v_pool, int64_t src_block, int64_t dst_block, int rows, int layers,
+__global__ void cow_copy_kernel(KV* k_pool, KV* v_pool, int64_t src_block, int64_t dst_block, int rows, int layers, int64_t pool_blocks,
                                 int kv_heads, int block_tokens, int d) {
     // one CTA per (layer, kv_head)
     int layer = blockIdx.x / kv_heads, h = blockIdx.x % kv_heads;
-    int64_t s = (((src_block * layers + layer) * kv_heads + h) * block_tokens) * (int64_t)d;
-    int64_t t = (((dst_block * layers + layer) * kv_heads + h) * block_tokens) * (int64_t)d;
+    int64_t s = ((kv_page_index(src_block, layer, layers, pool_blocks) * kv_heads + h) * block_tokens) * (int64_t)d;
+    int64_t t = ((kv_page_index(dst_block, layer, layers, pool_blocks) * kv_heads + h) * block_tokens) * (int64_t)d;
     for (int i = threadIdx.x; i < rows * d; i += blockDim.x) {
         k_pool[t + i] = k_pool[s + i];
         v_pool[t + i] = v_pool[s + i];
@@ -108,15 +108,15 @@ void launch_rope_kv(const RopeKvArgs& a, cudaStream_t s) {
 }
 
 void launch_cow_copy(void* k_pool, void* v_pool, int kv_f16, int64_t src_block, int64_t dst_block, int rows, int layers,
-                     int kv_heads, int block_tokens, int d, cudaStream_t s) {
+                     int64_t pool_blocks, int kv_heads, int block_tokens, int d, cudaStream_t s) {
     if (rows <= 0) return;
     unsigned grid = (unsigned)(layers * kv_heads);
     if (kv_f16)
         cow_copy_kernel<__half><<<grid, 128, 0, s>>>((__half*)k_pool, (__half*)v_pool, src_block, dst_block, rows,
-                                                     layers, kv_heads, block_tokens, d);
+                                                     layers, pool_blocks, kv_heads, block_tokens, d);
     else
         cow_copy_kernel<float><<<grid, 128, 0, s>>>((float*)k_pool, (float*)v_pool, src_block, dst_block, rows, layers,
-                                                    kv_heads, block_tokens, d);
+                                                    pool_blocks, kv_heads, block_tokens, d);
     MK_LAUNCH_CHECK();
 }
 

@@ -255,6 +255,24 @@ def test_tensor_core_attention_long_contexts(ops, orc, geom, window, softcap, bt
     assert np.max(np.abs(outs[2] - want)) < 2e-3
 
 
+def test_decode_attention_at_the_benchmark_shape(ops, orc):
+    """64 one-token lanes with 100..1000 tokens of history each, 16 query heads over 4 KV heads of 128: the
+    decode tick of the headline workload, one layer of it."""
+    q_heads, kv_heads, d, bt = 16, 4, 128, 16
+    rng = np.random.default_rng(64)
+    lanes_spec = [(int(c), 1) for c in rng.integers(100, 1000, size=64)]
+    tables, k_pool, v_pool, q, k, v = _attn_case(rng, lanes_spec, q_heads, kv_heads, d, bt, 1, 0, np.float16)
+    scale = 1.0 / np.sqrt(d)
+    kp, vp = k_pool.copy(), v_pool.copy()
+    res = ops.attention_step(q, k, v, kp, vp, tables, [s for s, _ in lanes_spec], [n for _, n in lanes_spec], q_heads=q_heads,
+                             kv_heads=kv_heads, head_dim=d, block_tokens=bt, layers=1, layer=0, scale=scale, kernel=2)
+    flat = np.concatenate(tables).astype(np.uint32)
+    page_off = np.concatenate([[0], np.cumsum([len(t) for t in tables])[:-1]]).astype(np.int32)
+    want = orc.paged_attention(q, kp, vp, flat, page_off, [s for s, _ in lanes_spec], [n for _, n in lanes_spec], q_heads=q_heads,
+                               kv_heads=kv_heads, d=d, block_tokens=bt, layers=1, layer=0, scale=scale, softcap=0.0, window=0, mode=0)
+    assert np.max(np.abs(res["out"] - want)) < 2e-3
+
+
 def test_tensor_core_attention_is_refused_for_f32_pools(ops):
     rng = np.random.default_rng(3)
     tables, k_pool, v_pool, q, k, v = _attn_case(rng, [(0, 4)], 4, 2, 64, 16, 1, 0, np.float32)
