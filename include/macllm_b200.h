@@ -44,6 +44,8 @@ extern "C" {
 #define MK_PATH_GEMV 1   /* integer dp4a kernel */
 #define MK_PATH_TENSOR 2 /* tcgen05 kernel, GGUF blocks dequantised inside the kernel */
 #define MK_PATH_HALF 3   /* tcgen05 kernel over an f16 image of the matrix built at load time (wide batches) */
+#define MK_PATH_STREAM 4 /* tcgen05 kernel that streams raw Q4_K blocks once (at most 64 rows; in a model: 9..64 rows,
+                          * f16 images above that) */
 
 typedef struct mk_model mk_model;
 typedef struct mk_session mk_session;
@@ -71,7 +73,7 @@ typedef struct mk_load_config {
     int32_t kv_dtype;                /* MK_TYPE_F16 or MK_TYPE_F32 */
     int32_t max_batch_tokens;        /* largest packed token count of one forward */
     int32_t max_batch_lanes;         /* largest lane count of one forward */
-    int32_t matmul_path;             /* MK_PATH_AUTO / MK_PATH_GEMV / MK_PATH_TENSOR / MK_PATH_HALF */
+    int32_t matmul_path;             /* MK_PATH_AUTO / MK_PATH_GEMV / MK_PATH_TENSOR / MK_PATH_HALF / MK_PATH_STREAM */
 } mk_load_config;
 
 /* CausalLm::runtime_spec (src/architecture.rs:312-316,1039). */

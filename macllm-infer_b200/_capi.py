@@ -14,7 +14,7 @@ LIB_PATH = HERE / "libmacllm_b200.so"
 
 MK_OK, MK_KV_EXHAUSTED = 0, 1
 TYPE_F32, TYPE_F16, TYPE_Q8_0, TYPE_Q4_K, TYPE_Q6_K = 0, 1, 8, 12, 14
-PATH_AUTO, PATH_GEMV, PATH_TENSOR, PATH_HALF = 0, 1, 2, 3
+PATH_AUTO, PATH_GEMV, PATH_TENSOR, PATH_HALF, PATH_STREAM = 0, 1, 2, 3, 4
 FWD_WANT_LOGITS, FWD_WANT_TOKENS = 1, 2
 
 

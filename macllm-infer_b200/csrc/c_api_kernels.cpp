@@ -5,6 +5,7 @@
 #include "device_util.h"
 #include "kernels.h"
 #include "hgemm_tc.h"
+#include "qstream_tc.h"
 #include "attention_tc.h"
 #include "qgemm_tc.h"
 #include <vector>
@@ -94,7 +95,7 @@ namespace {
 void qmatmul_case(int32_t type, const void* w, int64_t rows, int64_t cols, const float* x, int32_t T, float* y, int32_t path,
                   int iters, float* avg_ms) {
     require_device();
-    if (path < MK_PATH_AUTO || path > MK_PATH_HALF) throw std::runtime_error("mk_k_qmatmul: unknown path selector");
+    if (path < MK_PATH_AUTO || path > MK_PATH_STREAM) throw std::runtime_error("mk_k_qmatmul: unknown path selector");
     DeviceWeight dw;
     upload_weight(type, w, rows, cols, dw);
     int kind = act_kind_for(type);
@@ -102,12 +103,21 @@ void qmatmul_case(int32_t type, const void* w, int64_t rows, int64_t cols, const
     dx.upload(x, (size_t)T * cols * 4);
     ActBufs ab;
     const bool half = path == MK_PATH_HALF;
+    const bool stream = path == MK_PATH_STREAM;
+    QStreamWeight qsw;
+    DevBuf qs_partial;
+    int qs_splits = 1;
+    if (stream) {
+        if (type != MK_TYPE_Q4_K || T > kQStreamMaxRows) throw std::runtime_error("mk_k_qmatmul: the streamed matmul covers Q4_K matrices and at most 64 rows");
+        build_qstream_weight(dw.w.p0, rows, cols, qsw);
+        qs_partial.alloc((size_t)16 << 20);
+    }
     if (half) {
         if (!hgemm_tc_supported(dw.w)) throw std::runtime_error("mk_k_qmatmul: the f16-image GEMM does not cover this matrix");
         build_half_weight(dw.w, dw.half, nullptr);
     }
-    const bool tensor = !half && (path == MK_PATH_TENSOR || (path == MK_PATH_AUTO && qgemm_tc_preferred(dw.w, T)));
-    ActQ a = ab.view(T, (int)cols, kind, tensor || half);
+    const bool tensor = !half && !stream && (path == MK_PATH_TENSOR || (path == MK_PATH_AUTO && qgemm_tc_preferred(dw.w, T)));
+    ActQ a = ab.view(T, (int)cols, kind, tensor || half || stream);
     NormQuantArgs na;
     na.h = dx.as<float>();
     na.rows = T;
@@ -121,7 +131,9 @@ void qmatmul_case(int32_t type, const void* w, int64_t rows, int64_t cols, const
     HgemmScratch hs;
     hs.status = ws.status.as<int32_t>();
     auto run = [&] {
-        if (half) launch_hgemm_tc(dw.half, a.xh, T, dy.as<float>(), (int)rows, 1.0f, 0.f, hs, nullptr, 1);
+        if (stream) qs_splits = launch_qstream_tc(qsw, a.xh, T, dy.as<float>(), (int)rows, qs_partial.as<float>(), qs_partial.size() / 4,
+                                                  ws.status.as<int32_t>(), nullptr, 16);
+        else if (half) launch_hgemm_tc(dw.half, a.xh, T, dy.as<float>(), (int)rows, 1.0f, 0.f, hs, nullptr, 1);
         else if (tensor) launch_qgemm_tc(dw.w, a, kind, T, dy.as<float>(), (int)rows, 1.0f, 0.f, ws, nullptr);
         else launch_qgemv(dw.w, a, T, dy.as<float>(), (int)rows, 1.0f, 0.f, nullptr);
     };
@@ -152,7 +164,18 @@ void qmatmul_case(int32_t type, const void* w, int64_t rows, int64_t cols, const
     ws.status.download(&st, 4);
     MK_CUDA(cudaDeviceSynchronize());
     if (st != 0) throw std::runtime_error("tensor-core matmul: a bounded wait inside the kernel gave up (status " + std::to_string(st) + ")");
-    if (y != nullptr) dy.download(y, (size_t)T * rows * 4);
+    if (y != nullptr && stream && qs_splits > 1) {
+        // the shares are added in share order, as the consumer kernels of the model do
+        std::vector<float> parts((size_t)qs_splits * T * rows);
+        qs_partial.download(parts.data(), parts.size() * 4);
+        MK_CUDA(cudaDeviceSynchronize());
+        const size_t n = (size_t)T * rows;
+        for (size_t i = 0; i < n; ++i) {
+            float v = parts[i];
+            for (int sp = 1; sp < qs_splits; ++sp) v += parts[(size_t)sp * n + i];
+            y[i] = v;
+        }
+    } else if (y != nullptr) dy.download(y, (size_t)T * rows * 4);
     MK_CUDA(cudaDeviceSynchronize());
 }
 
@@ -369,7 +392,9 @@ int32_t mk_k_argmax(const float* logits, int32_t B, int32_t vocab, uint32_t* out
         require_device();
         DevBuf dl((size_t)B * vocab * 4), dout((size_t)B * 4);
         dl.upload(logits, (size_t)B * vocab * 4);
-        launch_argmax(dl.as<float>(), B, vocab, dout.as<uint32_t>(), nullptr);
+        DevBuf scratch(argmax_scratch_bytes(B));
+        scratch.zero(nullptr);
+        launch_argmax(dl.as<float>(), B, vocab, dout.as<uint32_t>(), scratch.ptr(), nullptr);
         MK_CUDA(cudaDeviceSynchronize());
         dout.download(out, (size_t)B * 4);
         MK_CUDA(cudaDeviceSynchronize());

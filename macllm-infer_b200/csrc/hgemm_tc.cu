@@ -410,6 +410,26 @@ void launch_hg(const CUtensorMap& tw, const CUtensorMap& tx, const HgParams& p, 
     MK_LAUNCH_CHECK();
 }
 
+}  // namespace
+
+void encode_tma_2d(void* out_map, bool bytes_not_halves, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                   uint32_t box_inner, uint32_t box_outer, bool swizzle_128b) {
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || row_stride_bytes % 16 != 0)
+        throw std::runtime_error("TMA descriptor: base and row stride must be multiples of 16 bytes");
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[1] = {(cuuint64_t)row_stride_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = encode_fn()(reinterpret_cast<CUtensorMap*>(out_map),
+                             bytes_not_halves ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                             const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             swizzle_128b ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+}
+
+namespace {
+
 int sm_count() {
     static int n = 0;
     if (n == 0) {

@@ -5,6 +5,12 @@
 
 namespace mk {
 
+// Encodes a 2-D tiled TMA descriptor (128 bytes at out_map, 64-byte aligned) over a row-major matrix of bytes or
+// halves: `inner` elements per row, `outer` rows, boxes of box_inner x box_outer, optional 128-byte swizzle, zero
+// fill outside the matrix.
+void encode_tma_2d(void* out_map, bool bytes_not_halves, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                   uint32_t box_inner, uint32_t box_outer, bool swizzle_128b);
+
 // Bytes an f16 image of W takes.
 inline size_t half_weight_bytes(const QWeight& W) { return (size_t)W.rows * (size_t)W.cols * 2; }
 

@@ -32,8 +32,10 @@ struct NormQuantArgs {
 void launch_add_norm_quant(const NormQuantArgs& a, cudaStream_t s);
 
 // out = quantise(act(gate) * up) ; act 0 = SiLU, 1 = tanh-GELU.  gate/up are [T][F] with row stride ld.
+// gate/up may arrive as `splits` partial sums `split_stride` floats apart (split-K matmul output), added in index
+// order on the way in.
 void launch_actmul_quant(const float* gate, const float* up, int ld, int T, int F, int act, int act_kind,
-                         ActQ out, float* f32_out, cudaStream_t s);
+                         ActQ out, float* f32_out, cudaStream_t s, int splits = 1, int64_t split_stride = 0);
 
 // ---- quantised matmul ---------------------------------------------------------------------
 // y[t][n] = (sum_k x[t][k] W[n][k]) * out_scale, then optional tanh softcap; integer block dots
@@ -81,6 +83,12 @@ struct RopeKvArgs {
     const float* k = nullptr;      // [T][kv_heads*d]
     const float* v = nullptr;      // [T][kv_heads*d]
     int ldq = 0, ldk = 0, ldv = 0;
+    // q and k may arrive as qk_splits partial sums qk_split_stride floats apart (split-K matmul output), added in
+    // index order on the way in; the rotated q is then written to q_out (row stride ldq_out) instead of in place
+    int qk_splits = 1;
+    int64_t qk_split_stride = 0;
+    float* q_out = nullptr;
+    int ldq_out = 0;
     const float* q_norm_w = nullptr;  // [d] or null
     const float* k_norm_w = nullptr;  // [d] or null
     float norm_eps = 1e-6f;
@@ -120,8 +128,10 @@ void launch_paged_attention(const AttnArgs& a, cudaStream_t s);
 int attention_q_tile(int q_heads, int kv_heads);
 
 // ---- sampling ------------------------------------------------------------------------------------
-// First-index argmax of each row of logits [B][vocab].
-void launch_argmax(const float* logits, int B, int vocab, uint32_t* out, cudaStream_t s);
+// First-index argmax of each row of logits [B][vocab].  `scratch` is argmax_scratch_bytes(B) bytes of device
+// memory that is zero before the first call; every call leaves it zero again.
+size_t argmax_scratch_bytes(int B);
+void launch_argmax(const float* logits, int B, int vocab, uint32_t* out, void* scratch, cudaStream_t s);
 
 // ---- MoE -------------------------------------------------------------------------------------------
 // Top-k routing with (logit desc, index asc) order and softmax over the selected k.

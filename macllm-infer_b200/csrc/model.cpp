@@ -147,6 +147,8 @@ Model::Model(const std::string& gguf_path, const ModelConfig& cfg) : cfg_(cfg) {
     }
     logits_.alloc((size_t)B * ms_.vocab * 4);
     tokens_.alloc((size_t)B * 4);
+    argmax_scratch_.alloc(argmax_scratch_bytes(B));
+    argmax_scratch_.zero(stream_);
     a_qs_.alloc((size_t)T * aw);
     a_d_.alloc((size_t)T * (aw / 32 + 1) * 4);
     a_bs_.alloc((size_t)T * (aw / 16 + 1) * 2);
@@ -187,6 +189,7 @@ Model::Model(const std::string& gguf_path, const ModelConfig& cfg) : cfg_(cfg) {
     out_host_.ensure((size_t)B * ms_.vocab * 4 + (size_t)B * 4 + 16);
     MK_CUDA(cudaStreamSynchronize(stream_));
     build_half_cache();
+    build_qstream();
 }
 
 Model::~Model() {
@@ -300,7 +303,7 @@ void Model::rope_tables_for(double theta, const float*& cos_t, const float*& sin
 
 // ---------------------------------------------------------------------------- profiling
 
-static const char* kclass_names[] = {"qgemm_tc", "hgemm_tc", "qgemv", "paged_attention", "add_norm_quant", "rope_kv_scatter", "actmul_quant",
+static const char* kclass_names[] = {"qgemm_tc", "hgemm_tc", "qstream_tc", "qgemv", "paged_attention", "add_norm_quant", "rope_kv_scatter", "actmul_quant",
                                      "embed", "build_batch", "argmax", "moe"};
 
 void Model::profile_enable(bool on) {
@@ -414,8 +417,8 @@ void Model::matmul(const DeviceWeight& DW, const ActQ& x, int T, float* y, int l
 // The f16 images of the dense layer matrices (2 bytes per weight), built when the configuration asks for
 // them and, in automatic mode, only when they fit beside everything else with room to spare.
 void Model::build_half_cache() {
-    if (cfg_.matmul_path != 0 && cfg_.matmul_path != 3) return;
-    hgemm_min_rows_ = cfg_.matmul_path == 3 ? 9 : 33;
+    if (cfg_.matmul_path != 0 && cfg_.matmul_path != 3 && cfg_.matmul_path != 4) return;
+    hgemm_min_rows_ = cfg_.matmul_path == 0 ? 33 : 9;
     size_t total = 0;
     for (size_t l = 0; l < lw_.size(); ++l) {
         LayerWeights& w = lw_[l];
@@ -429,17 +432,23 @@ void Model::build_half_cache() {
                 total += half_weight_bytes(dw->w);
             }
     }
+    // the output head joins when batches of lanes can be wide enough to use it
+    DeviceWeight& head_dw = ms_.tied ? token_embd_ : output_;
+    const bool head_half = hgemm_tc_supported(head_dw.w) && cfg_.max_batch_lanes >= hgemm_min_rows_;
+    if (head_half) total += half_weight_bytes(head_dw.w);
     if (cfg_.matmul_path == 0) {
         if (cfg_.max_batch_tokens < hgemm_min_rows_) return;
         size_t free_b = 0, total_b = 0;
         MK_CUDA(cudaMemGetInfo(&free_b, &total_b));
         if (total + (size_t(4) << 30) > free_b) return;  // keep 4 GiB of headroom
     }
+    if (head_half) build_half_weight(head_dw.w, head_dw.half, stream_);
     for (size_t l = 0; l < lw_.size(); ++l) {
         LayerWeights& w = lw_[l];
         const QWeight* qkv[3] = {&w.wq.w, &w.wk.w, &w.wv.w};
         build_half_weight_stacked(qkv, 3, w.qkv_half, stream_);
         build_half_weight(w.wo.w, w.wo.half, stream_);
+        build_half_weight(w.wv.w, w.wv.half, stream_);  // V alone, for ticks whose Q and K come from the streamed matmul
         if (!ms_.layer[l].moe) {
             const QWeight* gu[2] = {&w.gate.w, &w.up.w};
             build_half_weight_stacked(gu, 2, w.gu_half, stream_);
@@ -450,6 +459,50 @@ void Model::build_half_cache() {
     MK_CUDA(cudaStreamSynchronize(stream_));
     half_cache_ = true;
     half_cache_bytes_ = (int64_t)total;
+}
+
+// Descriptors for the narrow-batch matmul over raw Q4_K blocks.  [wq; wk] and [gate; up] are moved into one
+// buffer each (rows stacked) so that one launch covers both; nothing is duplicated.
+void Model::build_qstream() {
+    if (cfg_.matmul_path != 0 && cfg_.matmul_path != 4) return;
+    if (!half_cache_) return;  // V and wide ticks ride on the f16 images
+    auto q4k = [](const DeviceWeight& d) { return d.w.type == QT_Q4_K && d.w.cols % 256 == 0; };
+    auto stack = [&](DeviceWeight& a, DeviceWeight& b, DevBuf& out) {
+        out.alloc((size_t)(a.w.bytes + b.w.bytes));
+        MK_CUDA(cudaMemcpyAsync(out.ptr(), a.w.p0, (size_t)a.w.bytes, cudaMemcpyDeviceToDevice, stream_));
+        MK_CUDA(cudaMemcpyAsync(out.as<uint8_t>() + a.w.bytes, b.w.p0, (size_t)b.w.bytes, cudaMemcpyDeviceToDevice, stream_));
+        MK_CUDA(cudaStreamSynchronize(stream_));
+        a.b0.release();
+        b.b0.release();
+        a.w.p0 = out.ptr();
+        b.w.p0 = out.as<uint8_t>() + a.w.bytes;
+    };
+    for (size_t l = 0; l < lw_.size(); ++l) {
+        LayerWeights& w = lw_[l];
+        if (ms_.layer[l].moe) return;
+        if (!q4k(w.wq) || !q4k(w.wk) || !q4k(w.wo) || !q4k(w.gate) || !q4k(w.up) || !q4k(w.down)) return;
+        if (!w.wv.half.ready) return;
+    }
+    for (size_t l = 0; l < lw_.size(); ++l) {
+        LayerWeights& w = lw_[l];
+        stack(w.wq, w.wk, w.qk_raw);
+        stack(w.gate, w.up, w.gu_raw);
+        build_qstream_weight(w.qk_raw.ptr(), w.wq.w.rows + w.wk.w.rows, w.wq.w.cols, w.qs_qk);
+        build_qstream_weight(w.wo.w.p0, w.wo.w.rows, w.wo.w.cols, w.qs_o);
+        build_qstream_weight(w.gu_raw.ptr(), w.gate.w.rows + w.up.w.rows, w.gate.w.cols, w.qs_gu);
+        build_qstream_weight(w.down.w.p0, w.down.w.rows, w.down.w.cols, w.qs_down);
+    }
+    qstream_ = true;
+}
+
+int Model::matmul_stream(const QStreamWeight& W, const ActQ& x, int T, float* y, int ldy, int max_splits) {
+    prof_begin(KC_QSTREAM, (double)W.rows * (double)(W.cols / 256) * 144.0 + 2.0 * T * W.cols + 4.0 * T * W.rows,
+               2.0 * T * (double)W.rows * (double)W.cols);
+    int splits = launch_qstream_tc(W, x.xh, T, y, ldy, tc_ws_.partial.as<float>(), tc_ws_.partial.size() / 4,
+                                   tc_ws_.status.as<int32_t>(), stream_, max_splits);
+    prof_end();
+    ++launches_;
+    return splits;
 }
 
 static int act_kind_of(const QWeight& w) { return w.type == QT_Q8_0 ? ACT_Q80 : ACT_Q8K; }
@@ -585,7 +638,13 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         float* qp = qkv_.as<float>();
         float* kp = qp + AW;
         float* vp = kp + KW;
-        if (w.qkv_half.ready && T >= hgemm_min_rows_ && xa.xh != nullptr) {
+        const bool stream = qstream_ && T >= qstream_min_rows_ && T <= kQStreamMaxRows && xa.xh != nullptr;
+        const int kMaxShares = 16;
+        int qk_splits = 1;
+        if (stream) {
+            qk_splits = matmul_stream(w.qs_qk, xa, T, qp, QKVW, kMaxShares);
+            matmul_half(w.wv.half, xa, T, vp, QKVW, 1.f, 0.f);
+        } else if (w.qkv_half.ready && T >= hgemm_min_rows_ && xa.xh != nullptr) {
             matmul_half(w.qkv_half, xa, T, qp, QKVW, 1.f, 0.f);
         } else {
             matmul(w.wq, xa, T, qp, QKVW, 1.f, 0.f);
@@ -598,6 +657,16 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         ra.k = kp;
         ra.v = vp;
         ra.ldq = ra.ldk = ra.ldv = QKVW;
+        if (qk_splits > 1) {
+            // shares of [q | k] rows of width AW + KW in the split-K scratch; the rotated q goes to its usual place
+            ra.q = tc_ws_.partial.as<float>();
+            ra.k = ra.q + AW;
+            ra.ldq = ra.ldk = AW + KW;
+            ra.qk_splits = qk_splits;
+            ra.qk_split_stride = (int64_t)T * (AW + KW);
+            ra.q_out = qp;
+            ra.ldq_out = QKVW;
+        }
         if (ls.qk_norm) { ra.q_norm_w = w.q_norm.as<float>(); ra.k_norm_w = w.k_norm.as<float>(); }
         ra.norm_eps = ms_.eps;
         if (ls.rope) { rope_tables_for(ls.theta, ra.cos_t, ra.sin_t); ra.rotary_dim = ms_.rotary_dim; }
@@ -697,9 +766,9 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         prof_end();
         ++launches_;
         // split-K shares of the two long-K projections are summed by the residual kernel that consumes them
-        const int kMaxShares = 16;
         int wo_splits = 1;
-        if (w.wo.half.ready && T >= hgemm_min_rows_ && xo.xh != nullptr) wo_splits = matmul_half(w.wo.half, xo, T, proj_.as<float>(), H, 1.f, 0.f, kMaxShares);
+        if (stream && xo.xh != nullptr) wo_splits = matmul_stream(w.qs_o, xo, T, proj_.as<float>(), H, kMaxShares);
+        else if (w.wo.half.ready && T >= hgemm_min_rows_ && xo.xh != nullptr) wo_splits = matmul_half(w.wo.half, xo, T, proj_.as<float>(), H, 1.f, 0.f, kMaxShares);
         else matmul(w.wo, xo, T, proj_.as<float>(), H, 1.f, 0.f);
         // residual add + FFN norm + quantise (finish_mixer, src/decoder.rs:2684-2699)
         int fkind = act_kind_of(w.gate.w);
@@ -725,7 +794,10 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
             // dense feed-forward (src/decoder.rs:298-305)
             float* gp = gu_.as<float>();
             float* up = gp + ms_.ffn;
-            if (w.gu_half.ready && T >= hgemm_min_rows_ && xf.xh != nullptr) {
+            int gu_splits = 1;
+            if (stream && xf.xh != nullptr) {
+                gu_splits = matmul_stream(w.qs_gu, xf, T, gp, 2 * ms_.ffn, kMaxShares);
+            } else if (w.gu_half.ready && T >= hgemm_min_rows_ && xf.xh != nullptr) {
                 matmul_half(w.gu_half, xf, T, gp, 2 * ms_.ffn, 1.f, 0.f);
             } else {
                 matmul(w.gate, xf, T, gp, 2 * ms_.ffn, 1.f, 0.f);
@@ -734,10 +806,17 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
             int dkind = act_kind_of(w.down.w);
             ActQ xd = act_view(f_qs_, f_d_, f_bs_, f_xh_, T, ms_.ffn, dkind, f16_T);
             prof_begin(KC_ACTMUL, 9.0 * T * ms_.ffn, 0);
-        launch_actmul_quant(gp, up, 2 * ms_.ffn, T, ms_.ffn, ls.act, dkind, xd, nullptr, stream_);
+        if (gu_splits > 1) {
+            const float* pg = tc_ws_.partial.as<float>();
+            launch_actmul_quant(pg, pg + ms_.ffn, 2 * ms_.ffn, T, ms_.ffn, ls.act, dkind, xd, nullptr, stream_, gu_splits,
+                                (int64_t)T * 2 * ms_.ffn);
+        } else {
+            launch_actmul_quant(gp, up, 2 * ms_.ffn, T, ms_.ffn, ls.act, dkind, xd, nullptr, stream_);
+        }
         prof_end();
             ++launches_;
-            if (w.down.half.ready && T >= hgemm_min_rows_ && xd.xh != nullptr) pending_splits = matmul_half(w.down.half, xd, T, down_.as<float>(), H, 1.f, 0.f, kMaxShares);
+            if (stream && xd.xh != nullptr) pending_splits = matmul_stream(w.qs_down, xd, T, down_.as<float>(), H, kMaxShares);
+            else if (w.down.half.ready && T >= hgemm_min_rows_ && xd.xh != nullptr) pending_splits = matmul_half(w.down.half, xd, T, down_.as<float>(), H, 1.f, 0.f, kMaxShares);
             else { matmul(w.down, xd, T, down_.as<float>(), H, 1.f, 0.f); pending_splits = 1; }
         } else {
             // sparse MoE (src/decoder.rs:394-554)
@@ -802,7 +881,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
     }
     if (flags & FWD_WANT_TOKENS) {
         prof_begin(KC_SAMPLE, 4.0 * B * ms_.vocab, 0);
-        launch_argmax(logits_.as<float>(), B, ms_.vocab, tokens_.as<uint32_t>(), stream_);
+        launch_argmax(logits_.as<float>(), B, ms_.vocab, tokens_.as<uint32_t>(), argmax_scratch_.ptr(), stream_);
         prof_end();
         ++launches_;
     }

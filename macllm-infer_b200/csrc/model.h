@@ -9,6 +9,7 @@
 #include "paged_lm.h"
 #include "qgemm_tc.h"
 #include "hgemm_tc.h"
+#include "qstream_tc.h"
 #include "attention_tc.h"
 
 namespace mk {
@@ -46,7 +47,8 @@ struct ModelConfig {
     int max_batch_tokens = 2048, max_batch_lanes = 64;
     // 0 auto (integer GEMV for a few rows, in-kernel dequant GEMM for tens of rows, f16-image GEMM for wide
     // ticks when the image fits), 1 integer GEMV only, 2 in-kernel dequant GEMM whenever the shape allows,
-    // 3 f16-image GEMM whenever more than 8 rows share a matrix
+    // 3 f16-image GEMM whenever more than 8 rows share a matrix, 4 like 0 but nothing falls back to the in-kernel
+    // dequant GEMM (f16 images for wide ticks, streamed Q4_K blocks for 9..64 rows)
     int matmul_path = 0;
 };
 
@@ -72,6 +74,9 @@ private:
     struct LayerWeights {
         DevBuf attn_norm, ffn_norm, post_attn_norm, post_ffn_norm, q_norm, k_norm, router;
         HalfWeight qkv_half, gu_half;  // f16 images of [wq; wk; wv] and [gate; up] stacked by rows
+        // Q4_K matrices streamed by the narrow-batch matmul: [wq; wk] and [gate; up] share one buffer each
+        DevBuf qk_raw, gu_raw;
+        QStreamWeight qs_qk, qs_o, qs_gu, qs_down;
         DeviceWeight wq, wk, wv, wo, gate, up, down;  // dense FFN, or expert banks for MoE layers
     };
     void load_weights(const GgufFile& f);
@@ -90,7 +95,7 @@ private:
     bool timed_ = false;
     int64_t launches_ = 0, h2d_bytes_ = 0, d2h_bytes_ = 0;
     // profiling: one event pair per launch group, resolved after the tick's barrier
-    enum KClass { KC_GEMM_TC = 0, KC_HGEMM, KC_GEMV, KC_ATTN, KC_NORM_QUANT, KC_ROPE_KV, KC_ACTMUL, KC_EMBED, KC_BATCH, KC_SAMPLE, KC_MOE, KC_COUNT };
+    enum KClass { KC_GEMM_TC = 0, KC_HGEMM, KC_QSTREAM, KC_GEMV, KC_ATTN, KC_NORM_QUANT, KC_ROPE_KV, KC_ACTMUL, KC_EMBED, KC_BATCH, KC_SAMPLE, KC_MOE, KC_COUNT };
     struct ProfSpan { int cls; double bytes, flops; cudaEvent_t a, b; };
     bool profiling_ = false;
     std::vector<ProfSpan> spans_;
@@ -115,10 +120,15 @@ private:
     DevBuf attn_part_o_, attn_part_ml_;
     bool attn_tc_ = false;
     // f16 weight images for wide ticks
+    DevBuf argmax_scratch_;
     bool half_cache_ = false;
     int hgemm_min_rows_ = 33;
     int64_t half_cache_bytes_ = 0;
     void build_half_cache();
+    void build_qstream();
+    bool qstream_ = false;
+    int qstream_min_rows_ = 9;
+    int matmul_stream(const QStreamWeight& W, const ActQ& x, int T, float* y, int ldy, int max_splits);
     HgemmScratch hgemm_scratch() const;
     // Returns the number of K shares; more than one means the result is the sum of that many partials in the
     // split-K scratch (see launch_hgemm_tc) and y was not written.

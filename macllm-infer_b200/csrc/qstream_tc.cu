@@ -1,0 +1,426 @@
+// Narrow-batch matmul for decode ticks: y[t][n] = sum_k xh[t][k] * dequant(W)[n][k] with W in GGUF Q4_K blocks,
+// read from HBM exactly once per call.
+//
+// Replaces LinearOp::Quantized forward (src/model_weights.rs:346-377 of the reference) when at most 64 activation
+// rows share a matrix - the decode tick of a continuous batch, where the matmuls are bound by the bytes of the
+// weights.  Keeping the weights in their 4.5-bit block format makes those bytes 3.5x fewer than an f16 image.
+//
+// One CTA per (128 weight rows, share of K); 192 threads in three roles:
+//   warp 0    - one lane issues TMA loads into a ring of stages, each holding one 256-wide block column of the
+//               weights (128 rows x 144 raw bytes, no swizzle) and the matching 256 columns of the f16 activations
+//               (four 64-column boxes, 128-byte swizzle);
+//   warps 2-5 - thread r dequantises row r of the stage, 128 columns at a time, into one of two f16 operand
+//               slots in the K-major no-swizzle core-matrix layout (8 rows x 16 bytes), with the same
+//               split-precision arithmetic as the in-kernel dequantisation of the wide GEMM;
+//   warp 1    - one lane issues eight K = 16 tcgen05 MMAs per slot (M = 128 rows, N = BN tokens, accumulator in
+//               tensor memory), commits the slot back to the dequantisers and, after the second slot of a stage,
+//               the stage back to the loader.
+// After the last MMA the dequantising warps read the accumulator and store either the result or, when K was
+// shared out over several CTAs, this share's partial sums (added later, in share order, by the consumer kernel).
+// Every mbarrier wait is bounded; a wait that gives up records a status word and the role leaves its loop.
+#include "qstream_tc.h"
+#include "hgemm_tc.h"
+#include "kernels.h"
+#include <cuda.h>
+#include <algorithm>
+
+namespace mk {
+
+namespace {
+
+constexpr int QS_BM = 128;
+constexpr int QS_THREADS = 192;
+constexpr int QS_STAGES = 3;
+constexpr int QS_RAW_BYTES = QS_BM * 144;         // one block column of 128 rows
+constexpr int QS_A_SLOT_BYTES = QS_BM * 128 * 2;  // 128 rows x 128 columns f16
+constexpr int QS_A_LBO = QS_BM / 8 * 128;         // bytes between consecutive 16-byte K chunks
+constexpr uint32_t QS_SPIN_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit) {
+    uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i <= limit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const void* tmap, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+// K-major, no swizzle: core matrices of 8 rows x 16 bytes; lbo = bytes between K chunks, sbo = between 8-row groups.
+__device__ __forceinline__ uint64_t make_nosw_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    return d;
+}
+// K-major, 128-byte rows, 128-byte swizzle: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+// ---- Q4_K block -> f16, split precision (w = q * s - o with s and o carried as f16 head + f16 tail, so the
+// result has one f16 rounding relative to the f32 value d*sc*q - dmin*m)
+
+__device__ __forceinline__ uint32_t scale_byte(uint32_t y, uint32_t z, uint32_t w, int i) {
+    uint32_t word = (i >> 2) == 0 ? y : ((i >> 2) == 1 ? z : w);
+    return (word >> ((i & 3) * 8)) & 0xFFu;
+}
+__device__ __forceinline__ void q4k_scale_min_reg(uint32_t y, uint32_t z, uint32_t w, int j, int& sc, int& mn) {
+    if (j < 4) {
+        sc = scale_byte(y, z, w, j) & 63;
+        mn = scale_byte(y, z, w, j + 4) & 63;
+    } else {
+        uint32_t a = scale_byte(y, z, w, j + 4);
+        sc = (a & 0xF) | ((scale_byte(y, z, w, j - 4) >> 6) << 4);
+        mn = (a >> 4) | ((scale_byte(y, z, w, j) >> 6) << 4);
+    }
+}
+struct SplitScale {
+    __half2 s_hi, s_lo, o_hi, o_lo;  // o_* hold the negated offset
+};
+__device__ __forceinline__ SplitScale make_split(float s, float o) {
+    SplitScale r;
+    __half sh = __float2half_rn(s), oh = __float2half_rn(-o);
+    r.s_hi = __half2half2(sh);
+    r.o_hi = __half2half2(oh);
+    r.s_lo = __float2half2_rn(s - __half2float(sh));
+    r.o_lo = __float2half2_rn(-o - __half2float(oh));
+    return r;
+}
+__device__ __forceinline__ void nibbles_to_half4(uint32_t bytes, __half2 bias, const SplitScale& sp, uint32_t& o01, uint32_t& o23) {
+    uint32_t p01 = __byte_perm(bytes, 0x64646464u, 0x4140);
+    uint32_t p23 = __byte_perm(bytes, 0x64646464u, 0x4342);
+    __half2 q01 = __hsub2(*reinterpret_cast<__half2*>(&p01), bias);
+    __half2 q23 = __hsub2(*reinterpret_cast<__half2*>(&p23), bias);
+    __half2 h01 = __hadd2(__hfma2(q01, sp.s_hi, sp.o_hi), __hfma2(q01, sp.s_lo, sp.o_lo));
+    __half2 h23 = __hadd2(__hfma2(q23, sp.s_hi, sp.o_hi), __hfma2(q23, sp.s_lo, sp.o_lo));
+    o01 = *reinterpret_cast<uint32_t*>(&h01);
+    o23 = *reinterpret_cast<uint32_t*>(&h23);
+}
+
+// Row `row` of the stage, columns [128 * half, 128 * half + 128) of its 256-wide block, into operand slot `a_slot`.
+__device__ __forceinline__ void dequant_half_block(const uint8_t* raw, int row, int half, uint8_t* a_slot) {
+    const uint8_t* blk = raw + row * 144;
+    const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
+    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFF)));
+    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+    const __half2 bias = __float2half2_rn(1024.f);
+    uint8_t* dst_row = a_slot + (row >> 3) * 128 + (row & 7) * 16;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const int j = half * 2 + c;  // 64-column chunk of the block: low nibbles = group 2j, high nibbles = 2j + 1
+        const uint4 q0 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * j);
+        const uint4 q1 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * j + 16);
+        int sc0, m0, sc1, m1;
+        q4k_scale_min_reg(hdr.y, hdr.z, hdr.w, 2 * j, sc0, m0);
+        q4k_scale_min_reg(hdr.y, hdr.z, hdr.w, 2 * j + 1, sc1, m1);
+        const SplitScale sp0 = make_split(d * (float)sc0, dmin * (float)m0);
+        const SplitScale sp1 = make_split(d * (float)sc1, dmin * (float)m1);
+        const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint4 lo, hi;
+            nibbles_to_half4(words[2 * i] & 0x0F0F0F0Fu, bias, sp0, lo.x, lo.y);
+            nibbles_to_half4(words[2 * i + 1] & 0x0F0F0F0Fu, bias, sp0, lo.z, lo.w);
+            nibbles_to_half4((words[2 * i] >> 4) & 0x0F0F0F0Fu, bias, sp1, hi.x, hi.y);
+            nibbles_to_half4((words[2 * i + 1] >> 4) & 0x0F0F0F0Fu, bias, sp1, hi.z, hi.w);
+            *reinterpret_cast<uint4*>(dst_row + (8 * c + i) * QS_A_LBO) = lo;
+            *reinterpret_cast<uint4*>(dst_row + (8 * c + 4 + i) * QS_A_LBO) = hi;
+        }
+    }
+}
+
+struct QsParams {
+    int T, rows, n_blocks;        // n_blocks = cols / 256
+    float* y;
+    int ldy;
+    int row_tiles, splits, blocks_per_split;
+    float* partial;               // [splits][T][rows] when splits > 1
+    int32_t* status;
+};
+
+template <int BN>
+struct QsSmem {
+    static constexpr int B_BYTES = 4 * BN * 128;                 // four 64-column boxes of BN rows
+    static constexpr int STAGE_BYTES = QS_RAW_BYTES + B_BYTES;   // both multiples of 1024
+    static constexpr size_t TOTAL = (size_t)QS_STAGES * STAGE_BYTES + 2 * QS_A_SLOT_BYTES + 1024 + 256;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(QS_THREADS, 1)
+qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, QsParams p) {
+    using L = QsSmem<BN>;
+    extern __shared__ uint8_t qs_smem_raw[];
+    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(qs_smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* a_slots = ring + (size_t)QS_STAGES * L::STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(a_slots + 2 * QS_A_SLOT_BYTES);
+    uint64_t* raw_full = bars;                   // [QS_STAGES] loader -> dequantisers, MMA
+    uint64_t* raw_empty = bars + QS_STAGES;      // [QS_STAGES] MMA -> loader
+    uint64_t* a_full = bars + 2 * QS_STAGES;     // [2] dequantisers -> MMA
+    uint64_t* a_empty = a_full + 2;              // [2] MMA -> dequantisers
+    uint64_t* acc_full = a_empty + 2;            // [1] MMA -> epilogue
+    __shared__ uint32_t tmem_base_slot;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tile = blockIdx.x % p.row_tiles, split = blockIdx.x / p.row_tiles;
+    const int b0 = split * p.blocks_per_split, b1 = min(p.n_blocks, b0 + p.blocks_per_split);
+    const int n_local = b1 - b0;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < QS_STAGES; ++i) {
+            mbar_init(&raw_full[i], 1);
+            mbar_init(&raw_empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&a_full[i], 128);
+            mbar_init(&a_empty[i], 1);
+        }
+        mbar_init(acc_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ---- loader
+        if (lane == 0) {
+            for (int i = 0; i < n_local; ++i) {
+                const uint32_t st = i % QS_STAGES, ph = (i / QS_STAGES) & 1;
+                if (!mbar_wait(&raw_empty[st], ph ^ 1, QS_SPIN_LIMIT)) {
+                    atomicExch(p.status, 21);
+                    break;
+                }
+                uint8_t* raw = ring + (size_t)st * L::STAGE_BYTES;
+                uint8_t* xb = raw + QS_RAW_BYTES;
+                mbar_expect_tx(&raw_full[st], (uint32_t)L::STAGE_BYTES);
+                tma_load_2d(raw, &tm_w, (b0 + i) * 144, m_tile * QS_BM, &raw_full[st]);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) tma_load_2d(xb + q * BN * 128, &tm_x, (b0 + i) * 256 + q * 64, 0, &raw_full[st]);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(QS_BM >> 4) << 24);
+            bool ok = true;
+            for (int i = 0; i < n_local && ok; ++i) {
+                const uint32_t st = i % QS_STAGES, ph = (i / QS_STAGES) & 1;
+                if (!mbar_wait(&raw_full[st], ph, QS_SPIN_LIMIT)) {  // the activation boxes of the stage have landed
+                    atomicExch(p.status, 22);
+                    break;
+                }
+                const uint32_t xb_addr = smem_u32(ring + (size_t)st * L::STAGE_BYTES + QS_RAW_BYTES);
+                for (int half = 0; half < 2; ++half) {
+                    const uint32_t use = 2 * i + half, slot = use & 1, sph = (use >> 1) & 1;
+                    if (!mbar_wait(&a_full[slot], sph, QS_SPIN_LIMIT)) {
+                        atomicExch(p.status, 23);
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(a_slots + slot * QS_A_SLOT_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const uint64_t adesc = make_nosw_desc(a_addr + k * 2 * QS_A_LBO, QS_A_LBO, 128);
+                        const uint64_t bdesc = make_sw128_desc(xb_addr + (half * 2 + (k >> 2)) * BN * 128) + (uint64_t)(2 * (k & 3));
+                        umma_f16(tmem_base, adesc, bdesc, idesc, (use > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&a_empty[slot]);
+                }
+                if (ok) umma_commit(&raw_empty[st]);
+            }
+            if (ok) umma_commit(acc_full);
+        }
+    } else {
+        // ---- dequantisers (thread r <-> weight row r of the tile), then the epilogue
+        const int r = (int)threadIdx.x - 64;
+        bool ok = true;
+        for (int i = 0; i < n_local && ok; ++i) {
+            const uint32_t st = i % QS_STAGES, ph = (i / QS_STAGES) & 1;
+            if (!mbar_wait(&raw_full[st], ph, QS_SPIN_LIMIT)) {
+                if (lane == 0) atomicExch(p.status, 24);
+                break;
+            }
+            const uint8_t* raw = ring + (size_t)st * L::STAGE_BYTES;
+            for (int half = 0; half < 2; ++half) {
+                const uint32_t use = 2 * i + half, slot = use & 1, sph = (use >> 1) & 1;
+                if (!mbar_wait(&a_empty[slot], sph ^ 1, QS_SPIN_LIMIT)) {
+                    if (lane == 0) atomicExch(p.status, 25);
+                    ok = false;
+                    break;
+                }
+                dequant_half_block(raw, r, half, a_slots + slot * QS_A_SLOT_BYTES);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(&a_full[slot]);
+            }
+        }
+        if (ok && n_local > 0 && mbar_wait(acc_full, 0, QS_SPIN_LIMIT)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int quad = warp & 3;
+            const int row = m_tile * QS_BM + quad * 32 + lane;
+            float* dst = p.splits > 1 ? p.partial + (int64_t)split * p.T * p.rows : p.y;
+            const int ld = p.splits > 1 ? p.rows : p.ldy;
+#pragma unroll 1
+            for (int cb = 0; cb < BN; cb += 32) {
+                if (cb >= p.T) break;
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)cb, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < p.rows) {
+#pragma unroll
+                    for (int t = 0; t < 32; ++t)
+                        if (cb + t < p.T) dst[(int64_t)(cb + t) * ld + row] = __uint_as_float(v[t]);
+                }
+            }
+        } else if (ok && n_local > 0) {
+            if (lane == 0) atomicExch(p.status, 26);
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+template <int BN>
+void launch_qs(const CUtensorMap& tw, const CUtensorMap& tx, const QsParams& p, cudaStream_t s) {
+    constexpr size_t smem = QsSmem<BN>::TOTAL;
+    static bool configured = false;
+    if (!configured) {
+        MK_CUDA(cudaFuncSetAttribute(qstream_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    qstream_tc_kernel<BN><<<p.row_tiles * p.splits, QS_THREADS, smem, s>>>(tw, tx, p);
+    MK_LAUNCH_CHECK();
+}
+
+}  // namespace
+
+void build_qstream_weight(const void* q4k_blocks, int64_t rows, int64_t cols, QStreamWeight& out) {
+    if (cols <= 0 || cols % 256 != 0 || rows <= 0) throw std::runtime_error("build_qstream_weight: cols must be a positive multiple of 256");
+    out.base = q4k_blocks;
+    out.rows = rows;
+    out.cols = cols;
+    const uint64_t row_bytes = (uint64_t)(cols / 256) * 144;
+    encode_tma_2d(out.tmap, true, q4k_blocks, row_bytes, (uint64_t)rows, row_bytes, 144, QS_BM, false);
+    out.ready = true;
+}
+
+QStreamPlan qstream_plan(int64_t rows, int64_t cols, int T, int max_splits) {
+    QStreamPlan pl;
+    pl.bn = T <= 32 ? 32 : 64;
+    pl.row_tiles = (int)((rows + QS_BM - 1) / QS_BM);
+    const int nb = (int)(cols / 256);
+    const int sms = 148;
+    // K shares: fewest "waves x (blocks per share + fixed cost)", at most 16 MiB of partial sums
+    int best = 1;
+    long best_cost = -1;
+    for (int s = 1; s <= std::max(1, std::min(max_splits, nb)); ++s) {
+        int per = (nb + s - 1) / s;
+        if (s > 1 && (size_t)s * T * rows * 4 > ((size_t)16 << 20)) break;
+        if ((nb + per - 1) / per != s) continue;
+        long waves = ((long)pl.row_tiles * s + sms - 1) / sms;
+        long cost = waves * (2 * per + 3) + (s > 1 ? 1 : 0);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
+    }
+    pl.splits = best;
+    pl.blocks_per_split = (nb + best - 1) / best;
+    pl.partial_floats = best > 1 ? (size_t)best * T * rows : 0;
+    return pl;
+}
+
+int launch_qstream_tc(const QStreamWeight& W, const __half* xh, int T, float* y, int ldy, float* partial, size_t partial_floats,
+                      int32_t* status, cudaStream_t s, int max_splits) {
+    if (T <= 0) return 1;
+    if (!W.ready) throw std::runtime_error("launch_qstream_tc: the matrix descriptor was not built");
+    if (T > kQStreamMaxRows) throw std::runtime_error("launch_qstream_tc: more activation rows than the kernel covers");
+    if (xh == nullptr) throw std::runtime_error("launch_qstream_tc: f16 activations missing");
+    if (partial == nullptr) max_splits = 1;
+    QStreamPlan pl = qstream_plan(W.rows, W.cols, T, max_splits);
+    if (pl.splits > 1 && pl.partial_floats > partial_floats) {
+        pl.splits = 1;
+        pl.blocks_per_split = (int)(W.cols / 256);
+    }
+    alignas(64) CUtensorMap tx;
+    encode_tma_2d(&tx, false, xh, (uint64_t)W.cols, (uint64_t)T, (uint64_t)W.cols * 2, 64, (uint32_t)pl.bn, true);
+    QsParams p;
+    p.T = T;
+    p.rows = (int)W.rows;
+    p.n_blocks = (int)(W.cols / 256);
+    p.y = y;
+    p.ldy = ldy;
+    p.row_tiles = pl.row_tiles;
+    p.splits = pl.splits;
+    p.blocks_per_split = pl.blocks_per_split;
+    p.partial = partial;
+    p.status = status;
+    const CUtensorMap& tw = *reinterpret_cast<const CUtensorMap*>(W.tmap);
+    if (pl.bn == 32) launch_qs<32>(tw, tx, p, s);
+    else launch_qs<64>(tw, tx, p, s);
+    return pl.splits;
+}
+
+}  // namespace mk

@@ -384,7 +384,8 @@ __global__ void __launch_bounds__(NQ_THREADS) quant_groups_kernel(const float* x
 }
 
 __global__ void __launch_bounds__(NQ_THREADS) actmul_quant_groups_kernel(const float* gate, const float* up, int ld, int rows, int F,
-                                                                          int act, int kind, ActQ out, float* f32_out) {
+                                                                          int act, int kind, ActQ out, float* f32_out, int splits,
+                                                                          int64_t split_stride) {
     const int groups = F / 256;
     const int64_t wid = (int64_t)blockIdx.x * (NQ_THREADS / 32) + (threadIdx.x >> 5);
     if (wid >= (int64_t)rows * groups) return;
@@ -392,6 +393,13 @@ __global__ void __launch_bounds__(NQ_THREADS) actmul_quant_groups_kernel(const f
     float g[8], u[8], v[8];
     load8(gate + (int64_t)r * ld + grp * 256 + lane * 8, g);
     load8(up + (int64_t)r * ld + grp * 256 + lane * 8, u);
+    for (int sp = 1; sp < splits; ++sp) {
+        float pg[8], pu[8];
+        load8(gate + sp * split_stride + (int64_t)r * ld + grp * 256 + lane * 8, pg);
+        load8(up + sp * split_stride + (int64_t)r * ld + grp * 256 + lane * 8, pu);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { g[i] += pg[i]; u[i] += pu[i]; }
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = (act == 0 ? silu_f(g[i]) : gelu_tanh_f(g[i])) * u[i];
     if (f32_out) store8(f32_out + (int64_t)r * F + grp * 256 + lane * 8, v);
@@ -432,12 +440,15 @@ void launch_add_norm_quant(const NormQuantArgs& a, cudaStream_t s) {
 }
 
 void launch_actmul_quant(const float* gate, const float* up, int ld, int T, int F, int act, int act_kind, ActQ out,
-                         float* f32_out, cudaStream_t s) {
+                         float* f32_out, cudaStream_t s, int splits, int64_t split_stride) {
     if (T <= 0) return;
+    if (splits > 1 && !(F % 256 == 0 && ld % 4 == 0 && split_stride % 4 == 0 && aligned16(gate) && aligned16(up)))
+        throw std::runtime_error("launch_actmul_quant: split inputs need 256-wide, 16-byte aligned rows");
     if (F % 256 == 0 && ld % 4 == 0 && aligned16(gate) && aligned16(up) && aligned16(f32_out) && aligned16(out.xh) &&
         (reinterpret_cast<uintptr_t>(out.qs) & 7) == 0) {
         int64_t warps = (int64_t)T * (F / 256);
-        actmul_quant_groups_kernel<<<(unsigned)((warps + 7) / 8), NQ_THREADS, 0, s>>>(gate, up, ld, T, F, act, act_kind, out, f32_out);
+        actmul_quant_groups_kernel<<<(unsigned)((warps + 7) / 8), NQ_THREADS, 0, s>>>(gate, up, ld, T, F, act, act_kind, out, f32_out, splits,
+                                                                                       split_stride);
         MK_LAUNCH_CHECK();
         return;
     }

@@ -40,7 +40,12 @@ __global__ void __launch_bounds__(RK_WARPS * 32) rope_kv_kernel(RopeKvArgs a) {
     else if (head < a.q_heads + a.kv_heads) { kind = 1; hh = head - a.q_heads; src = a.k + (int64_t)t * a.ldk + hh * d; }
     else { kind = 2; hh = head - a.q_heads - a.kv_heads; src = a.v + (int64_t)t * a.ldv + hh * d; }
 
-    for (int i = lane; i < d; i += 32) x[i] = src[i];
+    const int n_parts = kind == 2 ? 1 : a.qk_splits;
+    for (int i = lane; i < d; i += 32) {
+        float v = src[i];
+        for (int sp = 1; sp < n_parts; ++sp) v += src[(int64_t)sp * a.qk_split_stride + i];
+        x[i] = v;
+    }
     __syncwarp();
 
     const float* nw = kind == 0 ? a.q_norm_w : (kind == 1 ? a.k_norm_w : nullptr);
@@ -69,7 +74,7 @@ __global__ void __launch_bounds__(RK_WARPS * 32) rope_kv_kernel(RopeKvArgs a) {
         __syncwarp();
     }
     if (kind == 0) {
-        float* dst = a.q + (int64_t)t * a.ldq + hh * d;
+        float* dst = a.q_out != nullptr ? a.q_out + (int64_t)t * a.ldq_out + hh * d : a.q + (int64_t)t * a.ldq + hh * d;
         for (int i = lane; i < d; i += 32) dst[i] = x[i];
     } else {
         int64_t slot = a.slots[t];

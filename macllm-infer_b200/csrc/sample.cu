@@ -16,36 +16,57 @@ __device__ __forceinline__ int total_key(float f) {
     return b ^ (int)(((unsigned)(b >> 31)) >> 1);
 }
 
-__global__ void __launch_bounds__(1024) argmax_kernel(const float* logits, int vocab, uint32_t* out) {
-    __shared__ int s_key[32];
-    __shared__ int s_idx[32];
-    const float* row = logits + (int64_t)blockIdx.x * vocab;
-    int best_key = INT_MIN, best_idx = INT_MAX;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        int k = total_key(row[i]);
-        if (k > best_key || (k == best_key && i < best_idx)) { best_key = k; best_idx = i; }
+// grid (rows, chunks): every CTA scans one chunk of one row, folds its best (key, index) into the row's packed
+// 64-bit slot with atomicMax (key in the high word, 2^32-1 - index in the low word, so the larger packed value
+// is the larger key and, among equal keys, the lower index - an order-independent reduction), and the CTA that
+// arrives last at the row's counter writes the token and restores slot and counter to zero for the next call.
+constexpr int ARGMAX_THREADS = 256;
+constexpr int ARGMAX_CHUNKS = 16;
+
+__global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(const float* logits, int vocab, uint32_t* out,
+                                                                unsigned long long* slots, int32_t* counters) {
+    __shared__ unsigned long long s_best[ARGMAX_THREADS / 32];
+    const int r = blockIdx.x;
+    const float* row = logits + (int64_t)r * vocab;
+    const int per = ((vocab + gridDim.y - 1) / gridDim.y + 3) / 4 * 4;
+    const int lo = blockIdx.y * per, hi = min(vocab, lo + per);
+    unsigned long long best = 0;
+    auto consider = [&](float f, int i) {
+        unsigned long long p = ((unsigned long long)((uint32_t)total_key(f) ^ 0x80000000u) << 32) | (0xFFFFFFFFu - (uint32_t)i);
+        best = p > best ? p : best;
+    };
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        int i = lo + threadIdx.x * 4;
+        for (; i + 3 < hi; i += ARGMAX_THREADS * 4) {
+            float4 v = *reinterpret_cast<const float4*>(row + i);
+            consider(v.x, i);
+            consider(v.y, i + 1);
+            consider(v.z, i + 2);
+            consider(v.w, i + 3);
+        }
+        for (; i < hi; ++i) consider(row[i], i);  // at most one ragged group per row, in the last chunk
+    } else {
+        for (int i = lo + threadIdx.x; i < hi; i += ARGMAX_THREADS) consider(row[i], i);
     }
-    auto better = [](int k1, int i1, int k2, int i2) { return k1 > k2 || (k1 == k2 && i1 < i2); };
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-        int ok = __shfl_xor_sync(0xffffffffu, best_key, o);
-        int oi = __shfl_xor_sync(0xffffffffu, best_idx, o);
-        if (better(ok, oi, best_key, best_idx)) { best_key = ok; best_idx = oi; }
+        unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
     }
-    int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    if (lane == 0) { s_key[w] = best_key; s_idx[w] = best_idx; }
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    if (lane == 0) s_best[w] = best;
     __syncthreads();
-    if (w == 0) {
-        int nw = blockDim.x >> 5;
-        best_key = lane < nw ? s_key[lane] : INT_MIN;
-        best_idx = lane < nw ? s_idx[lane] : INT_MAX;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            int ok = __shfl_xor_sync(0xffffffffu, best_key, o);
-            int oi = __shfl_xor_sync(0xffffffffu, best_idx, o);
-            if (better(ok, oi, best_key, best_idx)) { best_key = ok; best_idx = oi; }
+    if (threadIdx.x == 0) {
+        for (int k = 1; k < ARGMAX_THREADS / 32; ++k) best = s_best[k] > best ? s_best[k] : best;
+        atomicMax(&slots[r], best);
+        __threadfence();
+        int prev = atomicAdd(&counters[r], 1);
+        if (prev == (int)gridDim.y - 1) {
+            __threadfence();
+            unsigned long long win = atomicExch(&slots[r], 0ull);
+            counters[r] = 0;
+            out[r] = 0xFFFFFFFFu - (uint32_t)(win & 0xFFFFFFFFull);
         }
-        if (lane == 0) out[blockIdx.x] = (uint32_t)best_idx;
     }
 }
 
@@ -91,9 +112,15 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* logits, int
 
 }  // namespace
 
-void launch_argmax(const float* logits, int B, int vocab, uint32_t* out, cudaStream_t s) {
+size_t argmax_scratch_bytes(int B) { return (size_t)B * 16; }
+
+void launch_argmax(const float* logits, int B, int vocab, uint32_t* out, void* scratch, cudaStream_t s) {
     if (B <= 0) return;
-    argmax_kernel<<<B, 1024, 0, s>>>(logits, vocab, out);
+    unsigned long long* slots = reinterpret_cast<unsigned long long*>(scratch);
+    int32_t* counters = reinterpret_cast<int32_t*>(slots + B);
+    int chunks = vocab >= 4096 ? ARGMAX_CHUNKS : 1;
+    dim3 grid((unsigned)B, (unsigned)chunks);
+    argmax_kernel<<<grid, ARGMAX_THREADS, 0, s>>>(logits, vocab, out, slots, counters);
     MK_LAUNCH_CHECK();
 }
 

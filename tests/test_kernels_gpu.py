@@ -88,6 +88,26 @@ def test_f16_image_gemm_matches_oracle(ops, orc, name, T, rows, cols):
     assert np.max(np.abs(got - other)) <= 2e-3 * scale
 
 
+@pytest.mark.parametrize("T,rows,cols", [(9, 128, 256), (33, 300, 1024), (64, 2048, 2048), (64, 512, 5632), (40, 2560, 2048),
+                                          (64, 1000, 11008), (17, 22016, 2048)])
+def test_streamed_q4k_matmul_matches_oracle(ops, orc, T, rows, cols):
+    """The decode-tick path: raw Q4_K blocks through TMA, dequantised in shared memory, tcgen05 MMA, K shared out
+    over CTAs.  Ragged row counts, one to 43 block columns, with and without shares."""
+    w = _weights(ops, 12, rows, cols, stream=6)
+    rng = np.random.default_rng(T + rows)
+    x = rng.standard_normal((T, cols)).astype(np.float32)
+    got = ops.qmatmul(12, w, rows, cols, x, 4)
+    want = orc.qmatmul(12, w, rows, cols, x, 1)
+    assert np.isfinite(got).all()
+    scale = np.sqrt(cols) * 0.02
+    assert np.max(np.abs(got - want)) <= 2e-3 * scale
+    cos = float((got * want).sum() / np.sqrt((got * got).sum() * (want * want).sum()))
+    assert cos >= 0.999999
+    # same operand rounding as the in-kernel dequant GEMM: only the summation order differs
+    other = ops.qmatmul(12, w, rows, cols, x, 2)
+    assert np.max(np.abs(got - other)) <= 2e-5 * scale * np.sqrt(cols / 256)
+
+
 @pytest.mark.parametrize("name", ["q4_k", "q6_k", "q8_0", "f32"])
 def test_embed_rows_exact(ops, orc, name):
     qtype = {"f32": 0, **QTYPES}[name]
