@@ -69,6 +69,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tc_kernel(AttnTcArgs a) {
     const int gid = lane >> 2, tq = lane & 3;
     const int kvh = blockIdx.y;
     const int g = a.q_heads / a.kv_heads;
+    pdl_trigger();
+    pdl_wait();
 
     int lane_id, row0, rows_per_head, split = 0, n_splits = 1;
     if (SPLIT) {
@@ -300,6 +302,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
     const int gid = lane >> 2, tq = lane & 3;
     const int kvh = blockIdx.y;
     const int g = a.q_heads / a.kv_heads;
+    pdl_trigger();
+    pdl_wait();
     // one 32-byte record per work item, so that nothing but the block table and the queries is a dependent load
     const int4 e0 = reinterpret_cast<const int4*>(a.entries)[2 * blockIdx.x];
     const int4 e1 = reinterpret_cast<const int4*>(a.entries)[2 * blockIdx.x + 1];
@@ -502,6 +506,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
 
 // Merge the key shares of one-token lanes: grid (decode lane, kv head), one warp per query head of the group.
 __global__ void attn_combine_kernel(AttnTcArgs a, int D) {
+    pdl_trigger();
+    pdl_wait();
     const int dl = blockIdx.x, kvh = blockIdx.y;
     const int lane_id = a.dec_lanes[3 * dl], first = a.dec_lanes[3 * dl + 1], n_splits = a.dec_lanes[3 * dl + 2];
     const int g = a.q_heads / a.kv_heads;
@@ -536,7 +542,7 @@ void launch_variant(const AttnTcArgs& a, int n_work, cudaStream_t s) {
         configured = true;
     }
     dim3 grid((unsigned)n_work, (unsigned)a.kv_heads);
-    attn_tc_kernel<D, WARPS, KT, SPLIT><<<grid, WARPS * 32, smem, s>>>(a);
+    launch_pdl(attn_tc_kernel<D, WARPS, KT, SPLIT>, grid, dim3(WARPS * 32), smem, s, a);
     MK_LAUNCH_CHECK();
 }
 
@@ -555,12 +561,12 @@ void launch_for_dim(const AttnTcArgs& a, int warps, cudaStream_t s) {
             configured = true;
         }
         dim3 grid((unsigned)a.n_entries, (unsigned)a.kv_heads);
-        attn_decode_kernel<D, STAGES><<<grid, 128, smem, s>>>(a);
+        launch_pdl(attn_decode_kernel<D, STAGES>, grid, dim3(128), smem, s, a);
         MK_LAUNCH_CHECK();
     }
     if (a.n_dec_lanes > 0) {  // lanes whose keys were shared out over several CTAs
         dim3 grid((unsigned)a.n_dec_lanes, (unsigned)a.kv_heads);
-        attn_combine_kernel<<<grid, 32 * (a.q_heads / a.kv_heads), 0, s>>>(a, D);
+        launch_pdl(attn_combine_kernel, grid, dim3(32 * (a.q_heads / a.kv_heads)), 0, s, a, (int)D);
         MK_LAUNCH_CHECK();
     }
 }

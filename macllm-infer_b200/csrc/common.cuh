@@ -6,6 +6,8 @@
 #include <cstdio>
 #include <string>
 #include <stdexcept>
+#include <cstdlib>
+#include <utility>
 
 namespace mk {
 
@@ -64,6 +66,36 @@ inline void cuda_check(cudaError_t e, const char* what, const char* file, int li
 __host__ __device__ __forceinline__ int64_t kv_page_index(int64_t blk, int layer, int layers, int64_t pool_blocks) {
     return pool_blocks > 0 ? (int64_t)layer * pool_blocks + blk : blk * layers + layer;
 }
+
+// Programmatic dependent launch: a kernel launched through launch_pdl may start (be scheduled, run its
+// prologue) while the previous kernel of the stream is still running; pdl_wait() blocks until that kernel has
+// completed and its writes are visible, so it must precede the first access to anything the predecessor wrote
+// or still reads.  pdl_trigger() lets the next kernel of the stream begin its own launch early.  Both are no-ops
+// for kernels launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#ifdef __CUDACC__
+inline bool pdl_enabled() {
+    static const bool on = [] { const char* e = std::getenv("MACLLM_B200_PDL"); return e == nullptr || e[0] != '0'; }();
+    return on;
+}
+// Launch `kernel`, which calls pdl_wait() before it touches global memory, with programmatic stream serialisation.
+template <typename... Params, typename... Args>
+inline void launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cuda_check(cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...), "kernel launch", __FILE__, __LINE__);
+}
+#endif
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

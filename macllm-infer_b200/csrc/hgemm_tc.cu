@@ -234,6 +234,9 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
+    // everything above is private to the CTA; from here on the kernel reads what its predecessor wrote
+    pdl_trigger();
+    pdl_wait();
 
     // work item -> (row tile, token tile, K share); row tiles vary fastest so concurrent CTAs share activations
     auto decode = [&](int item, int& m_tile, int& n_tile, int& kb0, int& kb1) {
@@ -406,7 +409,7 @@ void launch_hg(const CUtensorMap& tw, const CUtensorMap& tx, const HgParams& p, 
         MK_CUDA(cudaFuncSetAttribute(hgemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
-    hgemm_tc_kernel<BN, STAGES><<<grid, HG_THREADS, smem, s>>>(tw, tx, p);
+    launch_pdl(hgemm_tc_kernel<BN, STAGES>, dim3(grid), dim3(HG_THREADS), smem, s, tw, tx, p);
     MK_LAUNCH_CHECK();
 }
 

@@ -240,6 +240,9 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
+    // everything above is private to the CTA; from here on the kernel reads what its predecessor wrote
+    pdl_trigger();
+    pdl_wait();
 
     if (warp == 0) {
         // ---- loader
@@ -353,7 +356,7 @@ void launch_qs(const CUtensorMap& tw, const CUtensorMap& tx, const QsParams& p, 
         MK_CUDA(cudaFuncSetAttribute(qstream_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
-    qstream_tc_kernel<BN><<<p.row_tiles * p.splits, QS_THREADS, smem, s>>>(tw, tx, p);
+    launch_pdl(qstream_tc_kernel<BN>, dim3(p.row_tiles * p.splits), dim3(QS_THREADS), smem, s, tw, tx, p);
     MK_LAUNCH_CHECK();
 }
 

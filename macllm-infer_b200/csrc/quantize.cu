@@ -288,6 +288,8 @@ __device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
 template <int NG>
 __global__ void __launch_bounds__(NQ_THREADS) add_norm_quant_fast_kernel(NormQuantArgs a) {
     __shared__ float red[32];
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     const int src = a.row_index ? a.row_index[r] : r;
     const int dim = a.dim, groups = dim / 256;
@@ -375,6 +377,8 @@ __global__ void __launch_bounds__(NQ_THREADS) add_norm_quant_fast_kernel(NormQua
 // Rows that need no row-wide statistic: one warp per (row, 256-value group), any number of rows.
 __global__ void __launch_bounds__(NQ_THREADS) quant_groups_kernel(const float* x, int ld, int rows, int dim, int kind, ActQ out) {
     const int groups = dim / 256;
+    pdl_trigger();
+    pdl_wait();
     const int64_t wid = (int64_t)blockIdx.x * (NQ_THREADS / 32) + (threadIdx.x >> 5);
     if (wid >= (int64_t)rows * groups) return;
     const int r = (int)(wid / groups), grp = (int)(wid - (int64_t)r * groups), lane = threadIdx.x & 31;
@@ -387,6 +391,8 @@ __global__ void __launch_bounds__(NQ_THREADS) actmul_quant_groups_kernel(const f
                                                                           int act, int kind, ActQ out, float* f32_out, int splits,
                                                                           int64_t split_stride) {
     const int groups = F / 256;
+    pdl_trigger();
+    pdl_wait();
     const int64_t wid = (int64_t)blockIdx.x * (NQ_THREADS / 32) + (threadIdx.x >> 5);
     if (wid >= (int64_t)rows * groups) return;
     const int r = (int)(wid / groups), grp = (int)(wid - (int64_t)r * groups), lane = threadIdx.x & 31;
@@ -417,15 +423,15 @@ void launch_add_norm_quant(const NormQuantArgs& a, cudaStream_t s) {
     if (vec_ok && a.a == nullptr && a.norm_w == nullptr && a.row_index == nullptr && a.normed_out == nullptr) {
         // plain quantisation: no row-wide dependency
         int64_t warps = (int64_t)a.rows * (a.dim / 256);
-        quant_groups_kernel<<<(unsigned)((warps + 7) / 8), NQ_THREADS, 0, s>>>(a.h, a.dim, a.rows, a.dim, a.act_kind, a.out);
+        launch_pdl(quant_groups_kernel, dim3((unsigned)((warps + 7) / 8)), dim3(NQ_THREADS), 0, s, (const float*)a.h, a.dim, a.rows, a.dim, a.act_kind, a.out);
         MK_LAUNCH_CHECK();
         return;
     }
     if (vec_ok && a.dim <= 8 * 4 * 256) {
         int ng = (a.dim / 256 + 7) / 8;
-        if (ng == 1) add_norm_quant_fast_kernel<1><<<a.rows, NQ_THREADS, 0, s>>>(a);
-        else if (ng == 2) add_norm_quant_fast_kernel<2><<<a.rows, NQ_THREADS, 0, s>>>(a);
-        else add_norm_quant_fast_kernel<4><<<a.rows, NQ_THREADS, 0, s>>>(a);
+        if (ng == 1) launch_pdl(add_norm_quant_fast_kernel<1>, dim3(a.rows), dim3(NQ_THREADS), 0, s, a);
+        else if (ng == 2) launch_pdl(add_norm_quant_fast_kernel<2>, dim3(a.rows), dim3(NQ_THREADS), 0, s, a);
+        else launch_pdl(add_norm_quant_fast_kernel<4>, dim3(a.rows), dim3(NQ_THREADS), 0, s, a);
         MK_LAUNCH_CHECK();
         return;
     }
@@ -447,8 +453,8 @@ void launch_actmul_quant(const float* gate, const float* up, int ld, int T, int 
     if (F % 256 == 0 && ld % 4 == 0 && aligned16(gate) && aligned16(up) && aligned16(f32_out) && aligned16(out.xh) &&
         (reinterpret_cast<uintptr_t>(out.qs) & 7) == 0) {
         int64_t warps = (int64_t)T * (F / 256);
-        actmul_quant_groups_kernel<<<(unsigned)((warps + 7) / 8), NQ_THREADS, 0, s>>>(gate, up, ld, T, F, act, act_kind, out, f32_out, splits,
-                                                                                       split_stride);
+        launch_pdl(actmul_quant_groups_kernel, dim3((unsigned)((warps + 7) / 8)), dim3(NQ_THREADS), 0, s, gate, up, ld, T, F, act, act_kind, out,
+                   f32_out, splits, split_stride);
         MK_LAUNCH_CHECK();
         return;
     }

@@ -25,6 +25,8 @@ __device__ __forceinline__ __half to_kv<__half>(float v) { return __float2half_r
 template <typename KV>
 __global__ void __launch_bounds__(RK_WARPS * 32) rope_kv_kernel(RopeKvArgs a) {
     __shared__ float buf[RK_WARPS][RK_MAX_D];
+    pdl_trigger();
+    pdl_wait();
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int heads_total = a.q_heads + 2 * a.kv_heads;
     int head = blockIdx.y * RK_WARPS + warp;
@@ -106,9 +108,9 @@ void launch_rope_kv(const RopeKvArgs& a, cudaStream_t s) {
     int heads_total = a.q_heads + 2 * a.kv_heads;
     dim3 grid((unsigned)a.T, (unsigned)((heads_total + RK_WARPS - 1) / RK_WARPS));
     if (a.kv_f16)
-        rope_kv_kernel<__half><<<grid, RK_WARPS * 32, 0, s>>>(a);
+        launch_pdl(rope_kv_kernel<__half>, grid, dim3(RK_WARPS * 32), 0, s, a);
     else
-        rope_kv_kernel<float><<<grid, RK_WARPS * 32, 0, s>>>(a);
+        launch_pdl(rope_kv_kernel<float>, grid, dim3(RK_WARPS * 32), 0, s, a);
     MK_LAUNCH_CHECK();
 }
 

@@ -26,6 +26,8 @@ constexpr int ARGMAX_CHUNKS = 16;
 __global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(const float* logits, int vocab, uint32_t* out,
                                                                 unsigned long long* slots, int32_t* counters) {
     __shared__ unsigned long long s_best[ARGMAX_THREADS / 32];
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* row = logits + (int64_t)r * vocab;
     const int per = ((vocab + gridDim.y - 1) / gridDim.y + 3) / 4 * 4;
@@ -120,7 +122,7 @@ void launch_argmax(const float* logits, int B, int vocab, uint32_t* out, void* s
     int32_t* counters = reinterpret_cast<int32_t*>(slots + B);
     int chunks = vocab >= 4096 ? ARGMAX_CHUNKS : 1;
     dim3 grid((unsigned)B, (unsigned)chunks);
-    argmax_kernel<<<grid, ARGMAX_THREADS, 0, s>>>(logits, vocab, out, slots, counters);
+    launch_pdl(argmax_kernel, grid, dim3(ARGMAX_THREADS), 0, s, logits, vocab, out, slots, counters);
     MK_LAUNCH_CHECK();
 }
 
