@@ -234,9 +234,11 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
-    // everything above is private to the CTA; from here on the kernel reads what its predecessor wrote
+    // Everything above is private to the CTA.  The weights do not depend on the predecessor kernel either, so
+    // the loader fills the ring with weight boxes first and only then waits for the predecessor, whose output
+    // (the activations) it loads next.  Every other access to global memory of this kernel (the epilogue's
+    // stores) is ordered after those loads through the mbarriers.
     pdl_trigger();
-    pdl_wait();
 
     // work item -> (row tile, token tile, K share); row tiles vary fastest so concurrent CTAs share activations
     auto decode = [&](int item, int& m_tile, int& n_tile, int& kb0, int& kb1) {
@@ -251,12 +253,19 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         // ---- loader
         if (lane == 0) {
             uint32_t it = 0;
-            bool ok = true;
+            bool ok = true, waited = false;
+            int held_x[STAGES], held_y[STAGES];  // activation boxes of the stages filled before the wait
             for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
                 int m_tile, n_tile, kb0, kb1;
                 decode(item, m_tile, n_tile, kb0, kb1);
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t st = it % STAGES, ph = (it / STAGES) & 1;
+                    if (it == STAGES && !waited) {  // the ring is full of weights: now the activations
+                        pdl_wait();
+                        waited = true;
+                        for (int h = 0; h < STAGES; ++h)
+                            tma_load_2d(tiles + (size_t)h * L::STAGE_BYTES + L::A_BYTES, &tm_x, held_x[h], held_y[h], &full[h]);
+                    }
                     if (!mbar_wait(&empty[st], ph ^ 1, HG_SPIN_LIMIT)) {
                         atomicExch(p.status, 11);
                         ok = false;
@@ -266,8 +275,18 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     uint8_t* b_dst = a_dst + L::A_BYTES;
                     mbar_expect_tx(&full[st], (uint32_t)L::STAGE_BYTES);
                     tma_load_2d(a_dst, &tm_w, kb * HG_BK, m_tile * HG_BM, &full[st]);
-                    tma_load_2d(b_dst, &tm_x, kb * HG_BK, n_tile * BN, &full[st]);
+                    if (waited) {
+                        tma_load_2d(b_dst, &tm_x, kb * HG_BK, n_tile * BN, &full[st]);
+                    } else {
+                        held_x[st] = kb * HG_BK;
+                        held_y[st] = n_tile * BN;
+                    }
                 }
+            }
+            if (!waited) {  // fewer stages of work than the ring holds
+                pdl_wait();
+                for (uint32_t h = 0; h < it && h < (uint32_t)STAGES; ++h)
+                    tma_load_2d(tiles + (size_t)h * L::STAGE_BYTES + L::A_BYTES, &tm_x, held_x[h], held_y[h], &full[h]);
             }
         }
     } else if (warp == 1) {

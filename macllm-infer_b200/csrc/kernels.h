@@ -87,6 +87,8 @@ struct RopeKvArgs {
     // index order on the way in; the rotated q is then written to q_out (row stride ldq_out) instead of in place
     int qk_splits = 1;
     int64_t qk_split_stride = 0;
+    int v_splits = 1;              // the same for v
+    int64_t v_split_stride = 0;
     float* q_out = nullptr;
     int ldq_out = 0;
     const float* q_norm_w = nullptr;  // [d] or null

@@ -384,9 +384,15 @@ HgemmScratch Model::hgemm_scratch() const {
     return ws;
 }
 
-int Model::matmul_half(const HalfWeight& W, const ActQ& x, int T, float* y, int ldy, float scale, float softcap, int max_splits) {
+int Model::matmul_half(const HalfWeight& W, const ActQ& x, int T, float* y, int ldy, float scale, float softcap, int max_splits,
+                       float* partial, size_t partial_floats) {
     prof_begin(KC_HGEMM, 2.0 * (double)W.rows * (double)W.cols + 2.0 * T * W.cols + 4.0 * T * W.rows, 2.0 * T * (double)W.rows * (double)W.cols);
-    int splits = launch_hgemm_tc(W, x.xh, T, y, ldy, scale, softcap, hgemm_scratch(), stream_, max_splits);
+    HgemmScratch ws = hgemm_scratch();
+    if (partial != nullptr) {
+        ws.partial = partial;
+        ws.partial_floats = partial_floats;
+    }
+    int splits = launch_hgemm_tc(W, x.xh, T, y, ldy, scale, softcap, ws, stream_, max_splits);
     prof_end();
     ++launches_;
     return splits;
@@ -492,6 +498,7 @@ void Model::build_qstream() {
         build_qstream_weight(w.gu_raw.ptr(), w.gate.w.rows + w.up.w.rows, w.gate.w.cols, w.qs_gu);
         build_qstream_weight(w.down.w.p0, w.down.w.rows, w.down.w.cols, w.qs_down);
     }
+    v_partial_.alloc((size_t)16 * kQStreamMaxRows * ms_.kv_heads * ms_.head_dim * 4);
     qstream_ = true;
 }
 
@@ -640,10 +647,10 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         float* vp = kp + KW;
         const bool stream = qstream_ && T >= qstream_min_rows_ && T <= kQStreamMaxRows && xa.xh != nullptr;
         const int kMaxShares = 16;
-        int qk_splits = 1;
+        int qk_splits = 1, v_splits = 1;
         if (stream) {
             qk_splits = matmul_stream(w.qs_qk, xa, T, qp, QKVW, kMaxShares);
-            matmul_half(w.wv.half, xa, T, vp, QKVW, 1.f, 0.f);
+            v_splits = matmul_half(w.wv.half, xa, T, vp, QKVW, 1.f, 0.f, kMaxShares, v_partial_.as<float>(), v_partial_.size() / 4);
         } else if (w.qkv_half.ready && T >= hgemm_min_rows_ && xa.xh != nullptr) {
             matmul_half(w.qkv_half, xa, T, qp, QKVW, 1.f, 0.f);
         } else {
@@ -666,6 +673,12 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
             ra.qk_split_stride = (int64_t)T * (AW + KW);
             ra.q_out = qp;
             ra.ldq_out = QKVW;
+        }
+        if (v_splits > 1) {
+            ra.v = v_partial_.as<float>();
+            ra.ldv = KW;
+            ra.v_splits = v_splits;
+            ra.v_split_stride = (int64_t)T * KW;
         }
         if (ls.qk_norm) { ra.q_norm_w = w.q_norm.as<float>(); ra.k_norm_w = w.k_norm.as<float>(); }
         ra.norm_eps = ms_.eps;

@@ -127,12 +127,14 @@ private:
     void build_half_cache();
     void build_qstream();
     bool qstream_ = false;
+    DevBuf v_partial_;  // split-K shares of the V projection on streamed ticks
     int qstream_min_rows_ = 9;
     int matmul_stream(const QStreamWeight& W, const ActQ& x, int T, float* y, int ldy, int max_splits);
     HgemmScratch hgemm_scratch() const;
     // Returns the number of K shares; more than one means the result is the sum of that many partials in the
     // split-K scratch (see launch_hgemm_tc) and y was not written.
-    int matmul_half(const HalfWeight& W, const ActQ& x, int T, float* y, int ldy, float scale, float softcap, int max_splits = 1);
+    int matmul_half(const HalfWeight& W, const ActQ& x, int T, float* y, int ldy, float scale, float softcap, int max_splits = 1,
+                    float* partial = nullptr, size_t partial_floats = 0);
     int attn_max_entries_ = 0;
     AttnTcPlan attn_plan_;
     std::vector<int32_t> plan_sp_, plan_nt_, plan_nb_;

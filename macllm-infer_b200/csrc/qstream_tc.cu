@@ -5,17 +5,17 @@
 // rows share a matrix - the decode tick of a continuous batch, where the matmuls are bound by the bytes of the
 // weights.  Keeping the weights in their 4.5-bit block format makes those bytes 3.5x fewer than an f16 image.
 //
-// One CTA per (128 weight rows, share of K); 192 threads in three roles:
+// One CTA per (128 weight rows, share of K); 320 threads in three roles:
 //   warp 0    - one lane issues TMA loads into a ring of stages, each holding one 256-wide block column of the
 //               weights (128 rows x 144 raw bytes, no swizzle) and the matching 256 columns of the f16 activations
 //               (four 64-column boxes, 128-byte swizzle);
-//   warps 2-5 - thread r dequantises row r of the stage, 128 columns at a time, into one of two f16 operand
+//   warps 2-9 - two threads per weight row dequantise the stage, 128 columns at a time, into one of two f16 operand
 //               slots in the K-major no-swizzle core-matrix layout (8 rows x 16 bytes), with the same
 //               split-precision arithmetic as the in-kernel dequantisation of the wide GEMM;
 //   warp 1    - one lane issues eight K = 16 tcgen05 MMAs per slot (M = 128 rows, N = BN tokens, accumulator in
 //               tensor memory), commits the slot back to the dequantisers and, after the second slot of a stage,
 //               the stage back to the loader.
-// After the last MMA the dequantising warps read the accumulator and store either the result or, when K was
+// After the last MMA four of the dequantising warps read the accumulator and store either the result or, when K was
 // shared out over several CTAs, this share's partial sums (added later, in share order, by the consumer kernel).
 // Every mbarrier wait is bounded; a wait that gives up records a status word and the role leaves its loop.
 #include "qstream_tc.h"
@@ -29,7 +29,7 @@ namespace mk {
 namespace {
 
 constexpr int QS_BM = 128;
-constexpr int QS_THREADS = 192;
+constexpr int QS_THREADS = 320;  // loader warp, MMA warp, eight dequantising warps
 constexpr int QS_STAGES = 3;
 constexpr int QS_RAW_BYTES = QS_BM * 144;         // one block column of 128 rows
 constexpr int QS_A_SLOT_BYTES = QS_BM * 128 * 2;  // 128 rows x 128 columns f16
@@ -149,16 +149,15 @@ __device__ __forceinline__ void nibbles_to_half4(uint32_t bytes, __half2 bias, c
     o23 = *reinterpret_cast<uint32_t*>(&h23);
 }
 
-// Row `row` of the stage, columns [128 * half, 128 * half + 128) of its 256-wide block, into operand slot `a_slot`.
-__device__ __forceinline__ void dequant_half_block(const uint8_t* raw, int row, int half, uint8_t* a_slot) {
+// Row `row` of the stage, columns [128 * half + 64 * c, + 64) of its 256-wide block, into operand slot `a_slot`.
+__device__ __forceinline__ void dequant_half_block(const uint8_t* raw, int row, int half, int c, uint8_t* a_slot) {
     const uint8_t* blk = raw + row * 144;
     const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
     const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFF)));
     const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
     const __half2 bias = __float2half2_rn(1024.f);
     uint8_t* dst_row = a_slot + (row >> 3) * 128 + (row & 7) * 16;
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
+    {
         const int j = half * 2 + c;  // 64-column chunk of the block: low nibbles = group 2j, high nibbles = 2j + 1
         const uint4 q0 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * j);
         const uint4 q1 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * j + 16);
@@ -224,7 +223,7 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             mbar_init(&raw_empty[i], 1);
         }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&a_full[i], 128);
+            mbar_init(&a_full[i], 256);
             mbar_init(&a_empty[i], 1);
         }
         mbar_init(acc_full, 1);
@@ -240,14 +239,27 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
-    // everything above is private to the CTA; from here on the kernel reads what its predecessor wrote
+    // Everything above is private to the CTA.  The weights do not depend on the predecessor kernel either, so
+    // the loader fills the ring with weight blocks first and only then waits for the predecessor, whose output
+    // (the activations) it loads next.  Every other access to global memory of this kernel (the epilogue's
+    // stores) is ordered after those loads through the mbarriers.
     pdl_trigger();
-    pdl_wait();
 
     if (warp == 0) {
         // ---- loader
         if (lane == 0) {
-            for (int i = 0; i < n_local; ++i) {
+            const int pre = min(n_local, QS_STAGES);
+            for (int i = 0; i < pre; ++i) {  // first use of each stage: nothing to wait for
+                mbar_expect_tx(&raw_full[i], (uint32_t)L::STAGE_BYTES);
+                tma_load_2d(ring + (size_t)i * L::STAGE_BYTES, &tm_w, (b0 + i) * 144, m_tile * QS_BM, &raw_full[i]);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i) {
+                uint8_t* xb = ring + (size_t)i * L::STAGE_BYTES + QS_RAW_BYTES;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) tma_load_2d(xb + q * BN * 128, &tm_x, (b0 + i) * 256 + q * 64, 0, &raw_full[i]);
+            }
+            for (int i = pre; i < n_local; ++i) {
                 const uint32_t st = i % QS_STAGES, ph = (i / QS_STAGES) & 1;
                 if (!mbar_wait(&raw_empty[st], ph ^ 1, QS_SPIN_LIMIT)) {
                     atomicExch(p.status, 21);
@@ -295,8 +307,9 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             if (ok) umma_commit(acc_full);
         }
     } else {
-        // ---- dequantisers (thread r <-> weight row r of the tile), then the epilogue
-        const int r = (int)threadIdx.x - 64;
+        // ---- dequantisers (two threads per weight row of the tile, 64 columns each), then four of the warps
+        // run the epilogue
+        const int r = ((int)threadIdx.x - 64) & 127, csel = ((int)threadIdx.x - 64) >> 7;
         bool ok = true;
         for (int i = 0; i < n_local && ok; ++i) {
             const uint32_t st = i % QS_STAGES, ph = (i / QS_STAGES) & 1;
@@ -312,12 +325,14 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                     ok = false;
                     break;
                 }
-                dequant_half_block(raw, r, half, a_slots + slot * QS_A_SLOT_BYTES);
+                dequant_half_block(raw, r, half, csel, a_slots + slot * QS_A_SLOT_BYTES);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 mbar_arrive(&a_full[slot]);
             }
         }
-        if (ok && n_local > 0 && mbar_wait(acc_full, 0, QS_SPIN_LIMIT)) {
+        if (warp >= 6) {
+            // warps 6-9 only dequantise
+        } else if (ok && n_local > 0 && mbar_wait(acc_full, 0, QS_SPIN_LIMIT)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int quad = warp & 3;
             const int row = m_tile * QS_BM + quad * 32 + lane;

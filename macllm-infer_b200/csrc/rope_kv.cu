@@ -42,11 +42,23 @@ __global__ void __launch_bounds__(RK_WARPS * 32) rope_kv_kernel(RopeKvArgs a) {
     else if (head < a.q_heads + a.kv_heads) { kind = 1; hh = head - a.q_heads; src = a.k + (int64_t)t * a.ldk + hh * d; }
     else { kind = 2; hh = head - a.q_heads - a.kv_heads; src = a.v + (int64_t)t * a.ldv + hh * d; }
 
-    const int n_parts = kind == 2 ? 1 : a.qk_splits;
-    for (int i = lane; i < d; i += 32) {
-        float v = src[i];
-        for (int sp = 1; sp < n_parts; ++sp) v += src[(int64_t)sp * a.qk_split_stride + i];
-        x[i] = v;
+    const int n_parts = kind == 2 ? a.v_splits : a.qk_splits;
+    const int64_t part_stride = kind == 2 ? a.v_split_stride : a.qk_split_stride;
+    if ((d & 127) == 0 && ((reinterpret_cast<uintptr_t>(src) | (uintptr_t)(part_stride * 4)) & 15) == 0) {
+        for (int i = lane * 4; i < d; i += 128) {
+            float4 v = *reinterpret_cast<const float4*>(src + i);
+            for (int sp = 1; sp < n_parts; ++sp) {
+                float4 w = *reinterpret_cast<const float4*>(src + (int64_t)sp * part_stride + i);
+                v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+            }
+            *reinterpret_cast<float4*>(x + i) = v;
+        }
+    } else {
+        for (int i = lane; i < d; i += 32) {
+            float v = src[i];
+            for (int sp = 1; sp < n_parts; ++sp) v += src[(int64_t)sp * part_stride + i];
+            x[i] = v;
+        }
     }
     __syncwarp();
 
