@@ -229,8 +229,13 @@ def main():
     ap.add_argument("--workload", default="smollm3-3b-ragged64", choices=list(WORKLOADS))
     ap.add_argument("--matmul-path", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    # a shorter slice of the same workload for profiler captures (a number printed by such a run is not a bench value)
+    ap.add_argument("--new-tokens", type=int, default=0, help="override the generated tokens per sequence")
+    ap.add_argument("--no-profiled-step", action="store_true", help="skip the extra step that times every launch")
     args = ap.parse_args()
-    w = WORKLOADS[args.workload]
+    w = dict(WORKLOADS[args.workload])
+    if args.new_tokens > 0:
+        w["new_tokens"] = args.new_tokens
 
     rank, local, world, dist = dist_setup(args.gpus)
     entry.load_package()
@@ -239,7 +244,7 @@ def main():
     barrier(dist)
     seed = importlib.import_module("macllm_infer_b200.seed_gguf")
     spec = seed.CONFIGS[w["config"]]
-    config = dict(workload=args.workload, model_shape=w["config"], sequences_per_gpu=w["seqs"], new_tokens=w["new_tokens"],
+    config = dict(workload=args.workload + (f" (slice: {w['new_tokens']} new tokens)" if args.new_tokens > 0 else ""), model_shape=w["config"], sequences_per_gpu=w["seqs"], new_tokens=w["new_tokens"],
                   prefill_quantum=w["quantum"], scheduler_token_budget=w["budget"], kv="f16 paged, 16-token blocks",
                   quant="Q4_K_M-shaped GGUF (Q4_K, Q6_K for attn_v and output)", parallelism=f"replicas x{world}",
                   l2="inputs larger than L2 (weights %.2f GB per pass)" % (seed.weight_bytes(spec)["per_token"] / 1e9))
@@ -309,7 +314,7 @@ def main():
     # one extra profiled step: CUDA events around every launch, per kernel class
     roof = None
     prof_rows = []
-    if rank == 0:
+    if rank == 0 and not args.no_profiled_step:
         model.profile_enable(True)
         run_step(eng_mod, model, w, prompts)
         prof_rows = model.profile_query()

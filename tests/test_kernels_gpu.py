@@ -108,6 +108,19 @@ def test_streamed_q4k_matmul_matches_oracle(ops, orc, T, rows, cols):
     assert np.max(np.abs(got - other)) <= 2e-5 * scale * np.sqrt(cols / 256)
 
 
+@pytest.mark.parametrize("label,T,rows,cols,path", [("decode_gate_up", 64, 22016, 2048, 4), ("decode_down", 64, 2048, 11008, 4),
+                                                     ("prefill_gate_up", 2048, 22016, 2048, 3), ("prefill_down", 2048, 2048, 11008, 3)])
+def test_matmul_timing_entry_on_the_benchmark_shapes(ops, label, T, rows, cols, path):
+    """mk_k_qmatmul_time on the feed-forward matrices of the headline workload (device-resident operands, L2
+    flushed before every launch): the launch must take a sane, positive time.  Also the command the profiler
+    captures of these two GEMM kernels run."""
+    w = _weights(ops, 12, rows, cols, stream=8)
+    x = np.random.default_rng(1).standard_normal((T, cols)).astype(np.float32)
+    ms = ops.qmatmul_time(12, w, rows, cols, x, path, 3)
+    assert 0.0 < ms < 50.0
+    print(label, "ms per launch", ms, "TFLOP/s", 2.0 * T * rows * cols / ms / 1e9)
+
+
 @pytest.mark.parametrize("name", ["q4_k", "q6_k", "q8_0", "f32"])
 def test_embed_rows_exact(ops, orc, name):
     qtype = {"f32": 0, **QTYPES}[name]
