@@ -16,8 +16,8 @@ using namespace mk;
 namespace {
 
 struct ActBufs {
-    DevBuf qs, d, bs, xh;
-    ActQ view(int T, int K, int kind, bool want_f16 = false) {
+    DevBuf qs, d, bs, xh, gs;
+    ActQ view(int T, int K, int kind, bool want_f16 = false, bool want_group_sums = false) {
         qs.ensure((size_t)T * K);
         d.ensure((size_t)T * (kind == ACT_Q8K ? K / 256 : K / 32) * 4);
         bs.ensure((size_t)T * (K / 16) * 2 + 16);
@@ -28,6 +28,10 @@ struct ActBufs {
         if (want_f16) {
             xh.ensure((size_t)T * K * 2);
             a.xh = xh.as<__half>();
+        }
+        if (want_f16 && want_group_sums && kind == ACT_Q8K) {
+            gs.ensure((size_t)T * (K / 16) * 2);
+            a.gs = gs.as<__half>();
         }
         return a;
     }
@@ -117,7 +121,7 @@ void qmatmul_case(int32_t type, const void* w, int64_t rows, int64_t cols, const
         build_half_weight(dw.w, dw.half, nullptr);
     }
     const bool tensor = !half && !stream && (path == MK_PATH_TENSOR || (path == MK_PATH_AUTO && qgemm_tc_preferred(dw.w, T)));
-    ActQ a = ab.view(T, (int)cols, kind, tensor || half || stream);
+    ActQ a = ab.view(T, (int)cols, kind, tensor || half || stream, stream);
     NormQuantArgs na;
     na.h = dx.as<float>();
     na.rows = T;
@@ -131,7 +135,7 @@ void qmatmul_case(int32_t type, const void* w, int64_t rows, int64_t cols, const
     HgemmScratch hs;
     hs.status = ws.status.as<int32_t>();
     auto run = [&] {
-        if (stream) qs_splits = launch_qstream_tc(qsw, a.xh, T, dy.as<float>(), (int)rows, qs_partial.as<float>(), qs_partial.size() / 4,
+        if (stream) qs_splits = launch_qstream_tc(qsw, a.xh, a.gs, T, dy.as<float>(), (int)rows, qs_partial.as<float>(), qs_partial.size() / 4,
                                                   ws.status.as<int32_t>(), nullptr, 16);
         else if (half) launch_hgemm_tc(dw.half, a.xh, T, dy.as<float>(), (int)rows, 1.0f, 0.f, hs, nullptr, 1);
         else if (tensor) launch_qgemm_tc(dw.w, a, kind, T, dy.as<float>(), (int)rows, 1.0f, 0.f, ws, nullptr);

@@ -240,11 +240,12 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     // stores) is ordered after those loads through the mbarriers.
     pdl_trigger();
 
-    // work item -> (row tile, token tile, K share); row tiles vary fastest so concurrent CTAs share activations
+    // work item -> (row tile, token tile, K share); token tiles vary fastest, so the CTAs that run side by side cover
+    // a few row tiles across every token tile: each weight box comes from HBM once and the activations stay in L2
     auto decode = [&](int item, int& m_tile, int& n_tile, int& kb0, int& kb1) {
         int mn = item % mn_tiles, split = item / mn_tiles;
-        m_tile = mn % p.row_tiles;
-        n_tile = mn / p.row_tiles;
+        m_tile = mn / p.n_tiles;
+        n_tile = mn % p.n_tiles;
         kb0 = split * p.kb_per_split;
         kb1 = min(k_blocks, kb0 + p.kb_per_split);
     };

@@ -367,8 +367,9 @@ bool Model::tensor_path(const QWeight& W, int T) const {
     return cfg_.matmul_path == 2 ? true : T > 8;
 }
 
-ActQ Model::act_view(DevBuf& qs, DevBuf& d, DevBuf& bs, DevBuf& xh, int, int, int, bool want_f16) {
+ActQ Model::act_view(DevBuf& qs, DevBuf& d, DevBuf& bs, DevBuf& xh, int, int, int kind, bool want_f16, DevBuf* gs) {
     ActQ a;
+    if (gs != nullptr && want_f16 && kind == ACT_Q8K && gs->size() > 0) a.gs = gs->as<__half>();
     a.qs = qs.as<int8_t>();
     a.d = d.as<float>();
     a.bsums = bs.as<int16_t>();
@@ -499,13 +500,16 @@ void Model::build_qstream() {
         build_qstream_weight(w.down.w.p0, w.down.w.rows, w.down.w.cols, w.qs_down);
     }
     v_partial_.alloc((size_t)16 * kQStreamMaxRows * ms_.kv_heads * ms_.head_dim * 4);
+    // group sums of the streamed ticks' activations (at most kQStreamMaxRows rows)
+    a_gs_.alloc((size_t)kQStreamMaxRows * (std::max(ms_.hidden, ms_.q_heads * ms_.head_dim) / 16) * 2);
+    f_gs_.alloc((size_t)kQStreamMaxRows * (ms_.ffn / 16) * 2);
     qstream_ = true;
 }
 
 int Model::matmul_stream(const QStreamWeight& W, const ActQ& x, int T, float* y, int ldy, int max_splits) {
     prof_begin(KC_QSTREAM, (double)W.rows * (double)(W.cols / 256) * 144.0 + 2.0 * T * W.cols + 4.0 * T * W.rows,
                2.0 * T * (double)W.rows * (double)W.cols);
-    int splits = launch_qstream_tc(W, x.xh, T, y, ldy, tc_ws_.partial.as<float>(), tc_ws_.partial.size() / 4,
+    int splits = launch_qstream_tc(W, x.xh, x.gs, T, y, ldy, tc_ws_.partial.as<float>(), tc_ws_.partial.size() / 4,
                                    tc_ws_.status.as<int32_t>(), stream_, max_splits);
     prof_end();
     ++launches_;
@@ -624,7 +628,8 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         const LayerSpec& ls = ms_.layer[(size_t)l];
         // residual add of the previous layer's FFN + attention norm + quantise
         int kind = act_kind_of(w.wq.w);
-        ActQ xa = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, H, kind, f16_T);
+        const bool stream_T = qstream_ && T >= qstream_min_rows_ && T <= kQStreamMaxRows && f16_T;
+        ActQ xa = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, H, kind, f16_T, stream_T ? &a_gs_ : nullptr);
         NormQuantArgs na;
         na.h = h_.as<float>();
         na.a = pending;
@@ -645,7 +650,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         float* qp = qkv_.as<float>();
         float* kp = qp + AW;
         float* vp = kp + KW;
-        const bool stream = qstream_ && T >= qstream_min_rows_ && T <= kQStreamMaxRows && xa.xh != nullptr;
+        const bool stream = stream_T && xa.gs != nullptr;
         const int kMaxShares = 16;
         int qk_splits = 1, v_splits = 1;
         if (stream) {
@@ -767,7 +772,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         prof_end();
         // output projection
         int okind = act_kind_of(w.wo.w);
-        ActQ xo = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, AW, okind, f16_T);
+        ActQ xo = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, AW, okind, f16_T, stream_T ? &a_gs_ : nullptr);
         NormQuantArgs no;
         no.h = attn_.as<float>();
         no.rows = T;
@@ -780,12 +785,12 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         ++launches_;
         // split-K shares of the two long-K projections are summed by the residual kernel that consumes them
         int wo_splits = 1;
-        if (stream && xo.xh != nullptr) wo_splits = matmul_stream(w.qs_o, xo, T, proj_.as<float>(), H, kMaxShares);
+        if (stream && xo.gs != nullptr) wo_splits = matmul_stream(w.qs_o, xo, T, proj_.as<float>(), H, kMaxShares);
         else if (w.wo.half.ready && T >= hgemm_min_rows_ && xo.xh != nullptr) wo_splits = matmul_half(w.wo.half, xo, T, proj_.as<float>(), H, 1.f, 0.f, kMaxShares);
         else matmul(w.wo, xo, T, proj_.as<float>(), H, 1.f, 0.f);
         // residual add + FFN norm + quantise (finish_mixer, src/decoder.rs:2684-2699)
         int fkind = act_kind_of(w.gate.w);
-        ActQ xf = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, H, fkind, f16_T);
+        ActQ xf = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, H, fkind, f16_T, stream_T ? &a_gs_ : nullptr);
         NormQuantArgs nf;
         nf.h = h_.as<float>();
         nf.a = wo_splits > 1 ? tc_ws_.partial.as<float>() : proj_.as<float>();
@@ -808,7 +813,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
             float* gp = gu_.as<float>();
             float* up = gp + ms_.ffn;
             int gu_splits = 1;
-            if (stream && xf.xh != nullptr) {
+            if (stream && xf.gs != nullptr) {
                 gu_splits = matmul_stream(w.qs_gu, xf, T, gp, 2 * ms_.ffn, kMaxShares);
             } else if (w.gu_half.ready && T >= hgemm_min_rows_ && xf.xh != nullptr) {
                 matmul_half(w.gu_half, xf, T, gp, 2 * ms_.ffn, 1.f, 0.f);
@@ -817,7 +822,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
                 matmul(w.up, xf, T, up, 2 * ms_.ffn, 1.f, 0.f);
             }
             int dkind = act_kind_of(w.down.w);
-            ActQ xd = act_view(f_qs_, f_d_, f_bs_, f_xh_, T, ms_.ffn, dkind, f16_T);
+            ActQ xd = act_view(f_qs_, f_d_, f_bs_, f_xh_, T, ms_.ffn, dkind, f16_T, stream_T ? &f_gs_ : nullptr);
             prof_begin(KC_ACTMUL, 9.0 * T * ms_.ffn, 0);
         if (gu_splits > 1) {
             const float* pg = tc_ws_.partial.as<float>();
@@ -828,7 +833,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         }
         prof_end();
             ++launches_;
-            if (stream && xd.xh != nullptr) pending_splits = matmul_stream(w.qs_down, xd, T, down_.as<float>(), H, kMaxShares);
+            if (stream && xd.gs != nullptr) pending_splits = matmul_stream(w.qs_down, xd, T, down_.as<float>(), H, kMaxShares);
             else if (w.down.half.ready && T >= hgemm_min_rows_ && xd.xh != nullptr) pending_splits = matmul_half(w.down.half, xd, T, down_.as<float>(), H, 1.f, 0.f, kMaxShares);
             else { matmul(w.down, xd, T, down_.as<float>(), H, 1.f, 0.f); pending_splits = 1; }
         } else {

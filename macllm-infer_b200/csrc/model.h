@@ -84,7 +84,7 @@ private:
                        int heads);
     void upload_f32(const GgufFile& f, const std::string& name, int64_t n, DevBuf& out);
     void matmul(const DeviceWeight& DW, const ActQ& x, int T, float* y, int ldy, float scale, float softcap);
-    ActQ act_view(DevBuf& qs, DevBuf& d, DevBuf& bs, DevBuf& xh, int T, int dim, int kind, bool want_f16);
+    ActQ act_view(DevBuf& qs, DevBuf& d, DevBuf& bs, DevBuf& xh, int T, int dim, int kind, bool want_f16, DevBuf* gs = nullptr);
     bool tensor_path(const QWeight& W, int T) const;
     void rope_tables_for(double theta, const float*& cos_t, const float*& sin_t);
 
@@ -127,6 +127,7 @@ private:
     void build_half_cache();
     void build_qstream();
     bool qstream_ = false;
+    DevBuf a_gs_, f_gs_;  // per-group activation sums for the streamed matmul
     DevBuf v_partial_;  // split-K shares of the V projection on streamed ticks
     int qstream_min_rows_ = 9;
     int matmul_stream(const QStreamWeight& W, const ActQ& x, int T, float* y, int ldy, int max_splits);

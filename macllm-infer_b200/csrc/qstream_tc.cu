@@ -29,8 +29,9 @@ namespace mk {
 namespace {
 
 constexpr int QS_BM = 128;
-constexpr int QS_THREADS = 320;  // loader warp, MMA warp, eight dequantising warps
-constexpr int QS_STAGES = 3;
+constexpr int QS_THREADS = 448;  // loader warp, MMA warp, eight converting warps, four epilogue warps
+constexpr int QS_RAW_STAGES = 4;  // weight blocks in flight (HBM latency)
+constexpr int QS_X_STAGES = 2;    // activation blocks in flight (L2 latency)
 constexpr int QS_RAW_BYTES = QS_BM * 144;         // one block column of 128 rows
 constexpr int QS_A_SLOT_BYTES = QS_BM * 128 * 2;  // 128 rows x 128 columns f16
 constexpr int QS_A_LBO = QS_BM / 8 * 128;         // bytes between consecutive 16-byte K chunks
@@ -109,8 +110,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "memory");
 }
 
-// ---- Q4_K block -> f16, split precision (w = q * s - o with s and o carried as f16 head + f16 tail, so the
-// result has one f16 rounding relative to the f32 value d*sc*q - dmin*m)
+// ---- Q4_K block -> tensor-core operands -----------------------------------------------------------------------
+// A 256-wide block of row n is d * (sc_g * q) - dmin * m_g over its eight groups g of 32.  sc_g * q is an integer
+// below 1024 and m_g one below 64: both are exact in f16.  So the MMA multiplies the activations by sc_g * q (main
+// accumulator) and the per-group sums of the activations by m_g (second accumulator); d and dmin, which are f16 in
+// the file, scale the two accumulators in f32 once per block.  No weight is ever rounded.
 
 __device__ __forceinline__ uint32_t scale_byte(uint32_t y, uint32_t z, uint32_t w, int i) {
     uint32_t word = (i >> 2) == 0 ? y : ((i >> 2) == 1 ? z : w);
@@ -126,58 +130,58 @@ __device__ __forceinline__ void q4k_scale_min_reg(uint32_t y, uint32_t z, uint32
         mn = (a >> 4) | ((scale_byte(y, z, w, j) >> 6) << 4);
     }
 }
-struct SplitScale {
-    __half2 s_hi, s_lo, o_hi, o_lo;  // o_* hold the negated offset
-};
-__device__ __forceinline__ SplitScale make_split(float s, float o) {
-    SplitScale r;
-    __half sh = __float2half_rn(s), oh = __float2half_rn(-o);
-    r.s_hi = __half2half2(sh);
-    r.o_hi = __half2half2(oh);
-    r.s_lo = __float2half2_rn(s - __half2float(sh));
-    r.o_lo = __float2half2_rn(-o - __half2float(oh));
-    return r;
-}
-__device__ __forceinline__ void nibbles_to_half4(uint32_t bytes, __half2 bias, const SplitScale& sp, uint32_t& o01, uint32_t& o23) {
+// Four nibbles in the low halves of four bytes -> (1024 + q) as f16 by byte permutation, then
+// fma(1024 + q, sc, -1024 sc) = sc * q: the product is exact and the result has at most 10 bits.
+__device__ __forceinline__ void nibbles_times_scale(uint32_t bytes, __half2 sc, __half2 nbias, uint32_t& o01, uint32_t& o23) {
     uint32_t p01 = __byte_perm(bytes, 0x64646464u, 0x4140);
     uint32_t p23 = __byte_perm(bytes, 0x64646464u, 0x4342);
-    __half2 q01 = __hsub2(*reinterpret_cast<__half2*>(&p01), bias);
-    __half2 q23 = __hsub2(*reinterpret_cast<__half2*>(&p23), bias);
-    __half2 h01 = __hadd2(__hfma2(q01, sp.s_hi, sp.o_hi), __hfma2(q01, sp.s_lo, sp.o_lo));
-    __half2 h23 = __hadd2(__hfma2(q23, sp.s_hi, sp.o_hi), __hfma2(q23, sp.s_lo, sp.o_lo));
+    __half2 h01 = __hfma2(*reinterpret_cast<__half2*>(&p01), sc, nbias);
+    __half2 h23 = __hfma2(*reinterpret_cast<__half2*>(&p23), sc, nbias);
     o01 = *reinterpret_cast<uint32_t*>(&h01);
     o23 = *reinterpret_cast<uint32_t*>(&h23);
 }
 
 // Row `row` of the stage, columns [128 * half + 64 * c, + 64) of its 256-wide block, into operand slot `a_slot`.
-__device__ __forceinline__ void dequant_half_block(const uint8_t* raw, int row, int half, int c, uint8_t* a_slot) {
-    const uint8_t* blk = raw + row * 144;
+__device__ __forceinline__ void convert_chunk(const uint8_t* blk, int row, int half, int c, uint8_t* a_slot) {
     const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
-    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFF)));
-    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
-    const __half2 bias = __float2half2_rn(1024.f);
     uint8_t* dst_row = a_slot + (row >> 3) * 128 + (row & 7) * 16;
-    {
-        const int j = half * 2 + c;  // 64-column chunk of the block: low nibbles = group 2j, high nibbles = 2j + 1
-        const uint4 q0 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * j);
-        const uint4 q1 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * j + 16);
-        int sc0, m0, sc1, m1;
-        q4k_scale_min_reg(hdr.y, hdr.z, hdr.w, 2 * j, sc0, m0);
-        q4k_scale_min_reg(hdr.y, hdr.z, hdr.w, 2 * j + 1, sc1, m1);
-        const SplitScale sp0 = make_split(d * (float)sc0, dmin * (float)m0);
-        const SplitScale sp1 = make_split(d * (float)sc1, dmin * (float)m1);
-        const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    const int j = half * 2 + c;  // 64-column chunk of the block: low nibbles = group 2j, high nibbles = 2j + 1
+    const uint4 q0 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * j);
+    const uint4 q1 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * j + 16);
+    int sc0, m0, sc1, m1;
+    q4k_scale_min_reg(hdr.y, hdr.z, hdr.w, 2 * j, sc0, m0);
+    q4k_scale_min_reg(hdr.y, hdr.z, hdr.w, 2 * j + 1, sc1, m1);
+    const __half2 s0 = __float2half2_rn((float)sc0), s1 = __float2half2_rn((float)sc1);
+    const __half2 nb0 = __float2half2_rn(-1024.f * (float)sc0), nb1 = __float2half2_rn(-1024.f * (float)sc1);
+    const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint4 lo, hi;
-            nibbles_to_half4(words[2 * i] & 0x0F0F0F0Fu, bias, sp0, lo.x, lo.y);
-            nibbles_to_half4(words[2 * i + 1] & 0x0F0F0F0Fu, bias, sp0, lo.z, lo.w);
-            nibbles_to_half4((words[2 * i] >> 4) & 0x0F0F0F0Fu, bias, sp1, hi.x, hi.y);
-            nibbles_to_half4((words[2 * i + 1] >> 4) & 0x0F0F0F0Fu, bias, sp1, hi.z, hi.w);
-            *reinterpret_cast<uint4*>(dst_row + (8 * c + i) * QS_A_LBO) = lo;
-            *reinterpret_cast<uint4*>(dst_row + (8 * c + 4 + i) * QS_A_LBO) = hi;
-        }
+    for (int i = 0; i < 4; ++i) {
+        uint4 lo, hi;
+        nibbles_times_scale(words[2 * i] & 0x0F0F0F0Fu, s0, nb0, lo.x, lo.y);
+        nibbles_times_scale(words[2 * i + 1] & 0x0F0F0F0Fu, s0, nb0, lo.z, lo.w);
+        nibbles_times_scale((words[2 * i] >> 4) & 0x0F0F0F0Fu, s1, nb1, hi.x, hi.y);
+        nibbles_times_scale((words[2 * i + 1] >> 4) & 0x0F0F0F0Fu, s1, nb1, hi.z, hi.w);
+        *reinterpret_cast<uint4*>(dst_row + (8 * c + i) * QS_A_LBO) = lo;
+        *reinterpret_cast<uint4*>(dst_row + (8 * c + 4 + i) * QS_A_LBO) = hi;
     }
+}
+
+// The eight group minimums of the block as f16, twice (once for the head, once for the tail of the activation sums),
+// and d, dmin as f32 for the epilogue.
+__device__ __forceinline__ void write_mins(const uint8_t* blk, int row, uint8_t* extra, float2* dd) {
+    const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
+    __half m[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        int sc, mn;
+        q4k_scale_min_reg(hdr.y, hdr.z, hdr.w, g, sc, mn);
+        m[g] = __float2half_rn((float)mn);
+    }
+    uint8_t* dst = extra + (row >> 3) * 128 + (row & 7) * 16;
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(m);
+    *reinterpret_cast<uint4*>(dst + QS_A_LBO) = *reinterpret_cast<uint4*>(m);
+    dd[row] = make_float2(__half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFF))),
+                          __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16))));
 }
 
 struct QsParams {
@@ -191,42 +195,55 @@ struct QsParams {
 
 template <int BN>
 struct QsSmem {
-    static constexpr int B_BYTES = 4 * BN * 128;                 // four 64-column boxes of BN rows
-    static constexpr int STAGE_BYTES = QS_RAW_BYTES + B_BYTES;   // both multiples of 1024
-    static constexpr size_t TOTAL = (size_t)QS_STAGES * STAGE_BYTES + 2 * QS_A_SLOT_BYTES + 1024 + 256;
+    static constexpr int X_BYTES = 4 * BN * 128 + 2 * BN * 16;   // four 64-column boxes + the group sums (head, tail)
+    static constexpr int EXTRA_BYTES = 2 * QS_BM * 16;           // the group minimums, twice
+    static constexpr size_t TOTAL = (size_t)QS_RAW_STAGES * QS_RAW_BYTES + (size_t)QS_X_STAGES * X_BYTES + 2 * QS_A_SLOT_BYTES +
+                                    2 * EXTRA_BYTES + 4 * QS_BM * sizeof(float2) + 1024 + 256;
 };
 
 template <int BN>
 __global__ void __launch_bounds__(QS_THREADS, 1)
-qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, QsParams p) {
+qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                  const __grid_constant__ CUtensorMap tm_gs, QsParams p) {
     using L = QsSmem<BN>;
     extern __shared__ uint8_t qs_smem_raw[];
-    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(qs_smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t* a_slots = ring + (size_t)QS_STAGES * L::STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(a_slots + 2 * QS_A_SLOT_BYTES);
-    uint64_t* raw_full = bars;                   // [QS_STAGES] loader -> dequantisers, MMA
-    uint64_t* raw_empty = bars + QS_STAGES;      // [QS_STAGES] MMA -> loader
-    uint64_t* a_full = bars + 2 * QS_STAGES;     // [2] dequantisers -> MMA
-    uint64_t* a_empty = a_full + 2;              // [2] MMA -> dequantisers
-    uint64_t* acc_full = a_empty + 2;            // [1] MMA -> epilogue
+    uint8_t* raw_ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(qs_smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* x_ring = raw_ring + (size_t)QS_RAW_STAGES * QS_RAW_BYTES;
+    uint8_t* a_slots = x_ring + (size_t)QS_X_STAGES * L::X_BYTES;
+    uint8_t* extras = a_slots + 2 * QS_A_SLOT_BYTES;
+    float2* dd = reinterpret_cast<float2*>(extras + 2 * L::EXTRA_BYTES);  // [4][128] (d, dmin)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(dd + 4 * QS_BM);
+    uint64_t* raw_full = bars;                              // [RAW] loader -> converters
+    uint64_t* raw_empty = raw_full + QS_RAW_STAGES;         // [RAW] converters -> loader
+    uint64_t* x_full = raw_empty + QS_RAW_STAGES;           // [X]   loader -> MMA
+    uint64_t* x_empty = x_full + QS_X_STAGES;               // [X]   MMA -> loader
+    uint64_t* a_full = x_empty + QS_X_STAGES;               // [2]   converters -> MMA
+    uint64_t* a_empty = a_full + 2;                         // [2]   MMA -> converters
+    uint64_t* acc_full = a_empty + 2;                       // [2]   MMA -> epilogue
+    uint64_t* acc_empty = acc_full + 2;                     // [2]   epilogue -> MMA
     __shared__ uint32_t tmem_base_slot;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tile = blockIdx.x % p.row_tiles, split = blockIdx.x / p.row_tiles;
     const int b0 = split * p.blocks_per_split, b1 = min(p.n_blocks, b0 + p.blocks_per_split);
     const int n_local = b1 - b0;
-    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr uint32_t TMEM_COLS = 4 * BN;  // two sets of (main, minimums) accumulators
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < QS_STAGES; ++i) {
+        for (int i = 0; i < QS_RAW_STAGES; ++i) {
             mbar_init(&raw_full[i], 1);
-            mbar_init(&raw_empty[i], 1);
+            mbar_init(&raw_empty[i], 256);
+        }
+        for (int i = 0; i < QS_X_STAGES; ++i) {
+            mbar_init(&x_full[i], 1);
+            mbar_init(&x_empty[i], 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&a_full[i], 256);
             mbar_init(&a_empty[i], 1);
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], 128);
         }
-        mbar_init(acc_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -239,38 +256,44 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
-    // Everything above is private to the CTA.  The weights do not depend on the predecessor kernel either, so
-    // the loader fills the ring with weight blocks first and only then waits for the predecessor, whose output
-    // (the activations) it loads next.  Every other access to global memory of this kernel (the epilogue's
-    // stores) is ordered after those loads through the mbarriers.
+    // Everything above is private to the CTA.  The weights do not depend on the predecessor kernel either, so the
+    // loader fills the weight ring first and only then waits for the predecessor, whose output (the activations) it
+    // loads next.  Every other access to global memory of this kernel (the epilogue's stores) is ordered after
+    // those loads through the mbarriers.
     pdl_trigger();
 
     if (warp == 0) {
         // ---- loader
         if (lane == 0) {
-            const int pre = min(n_local, QS_STAGES);
-            for (int i = 0; i < pre; ++i) {  // first use of each stage: nothing to wait for
-                mbar_expect_tx(&raw_full[i], (uint32_t)L::STAGE_BYTES);
-                tma_load_2d(ring + (size_t)i * L::STAGE_BYTES, &tm_w, (b0 + i) * 144, m_tile * QS_BM, &raw_full[i]);
-            }
+            auto load_raw = [&](int i) {
+                const int st = i % QS_RAW_STAGES;
+                mbar_expect_tx(&raw_full[st], (uint32_t)QS_RAW_BYTES);
+                tma_load_2d(raw_ring + (size_t)st * QS_RAW_BYTES, &tm_w, (b0 + i) * 144, m_tile * QS_BM, &raw_full[st]);
+            };
+            auto load_x = [&](int i) {
+                const int st = i % QS_X_STAGES;
+                uint8_t* xb = x_ring + (size_t)st * L::X_BYTES;
+                mbar_expect_tx(&x_full[st], (uint32_t)L::X_BYTES);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) tma_load_2d(xb + q * BN * 128, &tm_x, (b0 + i) * 256 + q * 64, 0, &x_full[st]);
+                tma_load_2d(xb + 4 * BN * 128, &tm_gs, (b0 + i) * 8, 0, &x_full[st]);
+                tma_load_2d(xb + 4 * BN * 128 + BN * 16, &tm_gs, p.n_blocks * 8 + (b0 + i) * 8, 0, &x_full[st]);
+            };
+            int ri = 0, xi = 0;
+            for (; ri < n_local && ri < QS_RAW_STAGES; ++ri) load_raw(ri);  // first use of each stage: nothing to wait for
             pdl_wait();
-            for (int i = 0; i < pre; ++i) {
-                uint8_t* xb = ring + (size_t)i * L::STAGE_BYTES + QS_RAW_BYTES;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) tma_load_2d(xb + q * BN * 128, &tm_x, (b0 + i) * 256 + q * 64, 0, &raw_full[i]);
-            }
-            for (int i = pre; i < n_local; ++i) {
-                const uint32_t st = i % QS_STAGES, ph = (i / QS_STAGES) & 1;
-                if (!mbar_wait(&raw_empty[st], ph ^ 1, QS_SPIN_LIMIT)) {
-                    atomicExch(p.status, 21);
-                    break;
+            bool ok = true;
+            while (ok && (xi < n_local || ri < n_local)) {
+                if (xi < n_local) {
+                    const uint32_t st = xi % QS_X_STAGES, ph = (xi / QS_X_STAGES) & 1;
+                    if (!mbar_wait(&x_empty[st], ph ^ 1, QS_SPIN_LIMIT)) { atomicExch(p.status, 21); ok = false; break; }
+                    load_x(xi++);
                 }
-                uint8_t* raw = ring + (size_t)st * L::STAGE_BYTES;
-                uint8_t* xb = raw + QS_RAW_BYTES;
-                mbar_expect_tx(&raw_full[st], (uint32_t)L::STAGE_BYTES);
-                tma_load_2d(raw, &tm_w, (b0 + i) * 144, m_tile * QS_BM, &raw_full[st]);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) tma_load_2d(xb + q * BN * 128, &tm_x, (b0 + i) * 256 + q * 64, 0, &raw_full[st]);
+                if (ri < n_local) {
+                    const uint32_t st = ri % QS_RAW_STAGES, ph = (ri / QS_RAW_STAGES) & 1;
+                    if (!mbar_wait(&raw_empty[st], ph ^ 1, QS_SPIN_LIMIT)) { atomicExch(p.status, 22); ok = false; break; }
+                    load_raw(ri++);
+                }
             }
         }
     } else if (warp == 1) {
@@ -279,79 +302,100 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(QS_BM >> 4) << 24);
             bool ok = true;
             for (int i = 0; i < n_local && ok; ++i) {
-                const uint32_t st = i % QS_STAGES, ph = (i / QS_STAGES) & 1;
-                if (!mbar_wait(&raw_full[st], ph, QS_SPIN_LIMIT)) {  // the activation boxes of the stage have landed
-                    atomicExch(p.status, 22);
-                    break;
-                }
-                const uint32_t xb_addr = smem_u32(ring + (size_t)st * L::STAGE_BYTES + QS_RAW_BYTES);
+                const uint32_t set = i & 1, aph = (i >> 1) & 1;
+                const uint32_t xs = i % QS_X_STAGES, xph = (i / QS_X_STAGES) & 1;
+                if (!mbar_wait(&acc_empty[set], aph ^ 1, QS_SPIN_LIMIT)) { atomicExch(p.status, 23); break; }
+                if (!mbar_wait(&x_full[xs], xph, QS_SPIN_LIMIT)) { atomicExch(p.status, 24); break; }
+                const uint32_t xb_addr = smem_u32(x_ring + (size_t)xs * L::X_BYTES);
+                const uint32_t d_main = tmem_base + set * 2 * BN, d_mins = d_main + BN;
                 for (int half = 0; half < 2; ++half) {
-                    const uint32_t use = 2 * i + half, slot = use & 1, sph = (use >> 1) & 1;
-                    if (!mbar_wait(&a_full[slot], sph, QS_SPIN_LIMIT)) {
-                        atomicExch(p.status, 23);
-                        ok = false;
-                        break;
-                    }
+                    if (!mbar_wait(&a_full[half], (uint32_t)(i & 1), QS_SPIN_LIMIT)) { atomicExch(p.status, 25); ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_addr = smem_u32(a_slots + slot * QS_A_SLOT_BYTES);
+                    const uint32_t a_addr = smem_u32(a_slots + half * QS_A_SLOT_BYTES);
 #pragma unroll
                     for (int k = 0; k < 8; ++k) {
                         const uint64_t adesc = make_nosw_desc(a_addr + k * 2 * QS_A_LBO, QS_A_LBO, 128);
                         const uint64_t bdesc = make_sw128_desc(xb_addr + (half * 2 + (k >> 2)) * BN * 128) + (uint64_t)(2 * (k & 3));
-                        umma_f16(tmem_base, adesc, bdesc, idesc, (use > 0 || k > 0) ? 1u : 0u);
+                        umma_f16(d_main, adesc, bdesc, idesc, (half > 0 || k > 0) ? 1u : 0u);
                     }
-                    umma_commit(&a_empty[slot]);
+                    if (half == 0) {
+                        // the group minimums against the group sums of the activations (head and tail): one K = 16 step
+                        const uint64_t adesc = make_nosw_desc(smem_u32(extras + (i & 1) * L::EXTRA_BYTES), QS_A_LBO, 128);
+                        const uint64_t bdesc = make_nosw_desc(xb_addr + 4 * BN * 128, BN * 16, 128);
+                        umma_f16(d_mins, adesc, bdesc, idesc, 0u);
+                    }
+                    umma_commit(&a_empty[half]);
                 }
-                if (ok) umma_commit(&raw_empty[st]);
+                if (ok) {
+                    umma_commit(&x_empty[xs]);
+                    umma_commit(&acc_full[set]);
+                }
             }
-            if (ok) umma_commit(acc_full);
         }
-    } else {
-        // ---- dequantisers (two threads per weight row of the tile, 64 columns each), then four of the warps
-        // run the epilogue
+    } else if (warp < 10) {
+        // ---- converters: two threads per weight row of the tile, 64 columns each per half block
         const int r = ((int)threadIdx.x - 64) & 127, csel = ((int)threadIdx.x - 64) >> 7;
         bool ok = true;
         for (int i = 0; i < n_local && ok; ++i) {
-            const uint32_t st = i % QS_STAGES, ph = (i / QS_STAGES) & 1;
+            const uint32_t st = i % QS_RAW_STAGES, ph = (i / QS_RAW_STAGES) & 1;
             if (!mbar_wait(&raw_full[st], ph, QS_SPIN_LIMIT)) {
-                if (lane == 0) atomicExch(p.status, 24);
+                if (lane == 0) atomicExch(p.status, 26);
                 break;
             }
-            const uint8_t* raw = ring + (size_t)st * L::STAGE_BYTES;
+            const uint8_t* blk = raw_ring + (size_t)st * QS_RAW_BYTES + r * 144;
             for (int half = 0; half < 2; ++half) {
-                const uint32_t use = 2 * i + half, slot = use & 1, sph = (use >> 1) & 1;
-                if (!mbar_wait(&a_empty[slot], sph ^ 1, QS_SPIN_LIMIT)) {
-                    if (lane == 0) atomicExch(p.status, 25);
+                if (!mbar_wait(&a_empty[half], (uint32_t)((i & 1) ^ 1), QS_SPIN_LIMIT)) {
+                    if (lane == 0) atomicExch(p.status, 27);
                     ok = false;
                     break;
                 }
-                dequant_half_block(raw, r, half, csel, a_slots + slot * QS_A_SLOT_BYTES);
+                convert_chunk(blk, r, half, csel, a_slots + half * QS_A_SLOT_BYTES);
+                if (half == 0 && csel == 0) write_mins(blk, r, extras + (i & 1) * L::EXTRA_BYTES, dd + (i & 3) * QS_BM);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive(&a_full[slot]);
+                mbar_arrive(&a_full[half]);
             }
+            if (ok) mbar_arrive(&raw_empty[st]);
         }
-        if (warp >= 6) {
-            // warps 6-9 only dequantise
-        } else if (ok && n_local > 0 && mbar_wait(acc_full, 0, QS_SPIN_LIMIT)) {
+    } else {
+        // ---- epilogue warps 10-13: per block, y += d * main - dmin * minimums, running sums in registers
+        const int quad = warp & 3;
+        const int row_in_tile = quad * 32 + lane;
+        float acc[BN];
+#pragma unroll
+        for (int t = 0; t < BN; ++t) acc[t] = 0.f;
+        bool ok = true;
+        for (int i = 0; i < n_local; ++i) {
+            const uint32_t set = i & 1, aph = (i >> 1) & 1;
+            if (!mbar_wait(&acc_full[set], aph, QS_SPIN_LIMIT)) {
+                if (lane == 0) atomicExch(p.status, 28);
+                ok = false;
+                break;
+            }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int quad = warp & 3;
-            const int row = m_tile * QS_BM + quad * 32 + lane;
+            const float2 dm = dd[(i & 3) * QS_BM + row_in_tile];
+            const uint32_t t_main = tmem_base + ((uint32_t)(quad * 32) << 16) + set * 2 * BN;
+#pragma unroll
+            for (int cb = 0; cb < BN; cb += 32) {
+                uint32_t vm[32], vn[32];
+                tmem_ld32(t_main + (uint32_t)cb, vm);
+                tmem_ld32(t_main + BN + (uint32_t)cb, vn);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int t = 0; t < 32; ++t)
+                    acc[cb + t] = __fmaf_rn(-dm.y, __uint_as_float(vn[t]), __fmaf_rn(dm.x, __uint_as_float(vm[t]), acc[cb + t]));
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&acc_empty[set]);
+        }
+        if (ok && n_local > 0) {
+            const int row = m_tile * QS_BM + row_in_tile;
             float* dst = p.splits > 1 ? p.partial + (int64_t)split * p.T * p.rows : p.y;
             const int ld = p.splits > 1 ? p.rows : p.ldy;
-#pragma unroll 1
-            for (int cb = 0; cb < BN; cb += 32) {
-                if (cb >= p.T) break;
-                uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)cb, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row < p.rows) {
+            if (row < p.rows) {
 #pragma unroll
-                    for (int t = 0; t < 32; ++t)
-                        if (cb + t < p.T) dst[(int64_t)(cb + t) * ld + row] = __uint_as_float(v[t]);
-                }
+                for (int t = 0; t < BN; ++t)
+                    if (t < p.T) dst[(int64_t)t * ld + row] = acc[t];
             }
-        } else if (ok && n_local > 0) {
-            if (lane == 0) atomicExch(p.status, 26);
         }
     }
 
@@ -364,14 +408,14 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
 }
 
 template <int BN>
-void launch_qs(const CUtensorMap& tw, const CUtensorMap& tx, const QsParams& p, cudaStream_t s) {
+void launch_qs(const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& tg, const QsParams& p, cudaStream_t s) {
     constexpr size_t smem = QsSmem<BN>::TOTAL;
     static bool configured = false;
     if (!configured) {
         MK_CUDA(cudaFuncSetAttribute(qstream_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
-    launch_pdl(qstream_tc_kernel<BN>, dim3(p.row_tiles * p.splits), dim3(QS_THREADS), smem, s, tw, tx, p);
+    launch_pdl(qstream_tc_kernel<BN>, dim3(p.row_tiles * p.splits), dim3(QS_THREADS), smem, s, tw, tx, tg, p);
     MK_LAUNCH_CHECK();
 }
 
@@ -410,12 +454,12 @@ QStreamPlan qstream_plan(int64_t rows, int64_t cols, int T, int max_splits) {
     return pl;
 }
 
-int launch_qstream_tc(const QStreamWeight& W, const __half* xh, int T, float* y, int ldy, float* partial, size_t partial_floats,
-                      int32_t* status, cudaStream_t s, int max_splits) {
+int launch_qstream_tc(const QStreamWeight& W, const __half* xh, const __half* gs, int T, float* y, int ldy, float* partial,
+                      size_t partial_floats, int32_t* status, cudaStream_t s, int max_splits) {
     if (T <= 0) return 1;
     if (!W.ready) throw std::runtime_error("launch_qstream_tc: the matrix descriptor was not built");
     if (T > kQStreamMaxRows) throw std::runtime_error("launch_qstream_tc: more activation rows than the kernel covers");
-    if (xh == nullptr) throw std::runtime_error("launch_qstream_tc: f16 activations missing");
+    if (xh == nullptr || gs == nullptr) throw std::runtime_error("launch_qstream_tc: f16 activations or their group sums missing");
     if (partial == nullptr) max_splits = 1;
     QStreamPlan pl = qstream_plan(W.rows, W.cols, T, max_splits);
     if (pl.splits > 1 && pl.partial_floats > partial_floats) {
@@ -424,6 +468,10 @@ int launch_qstream_tc(const QStreamWeight& W, const __half* xh, int T, float* y,
     }
     alignas(64) CUtensorMap tx;
     encode_tma_2d(&tx, false, xh, (uint64_t)W.cols, (uint64_t)T, (uint64_t)W.cols * 2, 64, (uint32_t)pl.bn, true);
+    // group sums [T][2 * cols/32] f16: boxes of 8 halves (the eight groups of one block) x BN rows land as one
+    // 16-byte K chunk of the no-swizzle operand layout
+    alignas(64) CUtensorMap tg;
+    encode_tma_2d(&tg, false, gs, (uint64_t)W.cols / 16, (uint64_t)T, (uint64_t)W.cols / 16 * 2, 8, (uint32_t)pl.bn, false);
     QsParams p;
     p.T = T;
     p.rows = (int)W.rows;
@@ -436,8 +484,8 @@ int launch_qstream_tc(const QStreamWeight& W, const __half* xh, int T, float* y,
     p.partial = partial;
     p.status = status;
     const CUtensorMap& tw = *reinterpret_cast<const CUtensorMap*>(W.tmap);
-    if (pl.bn == 32) launch_qs<32>(tw, tx, p, s);
-    else launch_qs<64>(tw, tx, p, s);
+    if (pl.bn == 32) launch_qs<32>(tw, tx, tg, p, s);
+    else launch_qs<64>(tw, tx, tg, p, s);
     return pl.splits;
 }
 

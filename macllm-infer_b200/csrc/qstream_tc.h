@@ -25,11 +25,12 @@ struct QStreamPlan {
 };
 QStreamPlan qstream_plan(int64_t rows, int64_t cols, int T, int max_splits);
 
-// y[t][n] = sum_k xh[t][k] * dequant(W)[n][k] for T <= kQStreamMaxRows rows of f16 activations [T][cols].
+// y[t][n] = sum_k xh[t][k] * dequant(W)[n][k] for T <= kQStreamMaxRows rows of f16 activations [T][cols]; gs holds the
+// per-group sums of those activations (ActQ::gs).
 // Returns the number of K shares S.  S = 1: y (row stride ldy) holds the result.  S > 1 (only when max_splits > 1):
 // y is not written; share s left its partial sums at partial[(s * T + t) * rows + n] and the consumer adds them
 // for s = 0 .. S-1 in that order.  `status` receives a non-zero code when a bounded wait gave up.
-int launch_qstream_tc(const QStreamWeight& W, const __half* xh, int T, float* y, int ldy, float* partial, size_t partial_floats,
-                      int32_t* status, cudaStream_t s, int max_splits);
+int launch_qstream_tc(const QStreamWeight& W, const __half* xh, const __half* gs, int T, float* y, int ldy, float* partial,
+                      size_t partial_floats, int32_t* status, cudaStream_t s, int max_splits);
 
 }  // namespace mk

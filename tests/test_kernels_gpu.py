@@ -103,9 +103,10 @@ def test_streamed_q4k_matmul_matches_oracle(ops, orc, T, rows, cols):
     assert np.max(np.abs(got - want)) <= 2e-3 * scale
     cos = float((got * want).sum() / np.sqrt((got * got).sum() * (want * want).sum()))
     assert cos >= 0.999999
-    # same operand rounding as the in-kernel dequant GEMM: only the summation order differs
+    # the weights enter the MMA as exact integers (sc * q, m) and d / dmin are applied in f32, so the only rounding left
+    # is the f16 image of the activations: closer to the oracle than the in-kernel dequant GEMM, which also rounds weights
     other = ops.qmatmul(12, w, rows, cols, x, 2)
-    assert np.max(np.abs(got - other)) <= 2e-5 * scale * np.sqrt(cols / 256)
+    assert np.max(np.abs(got - want)) <= np.max(np.abs(other - want)) * 1.5 + 1e-6
 
 
 @pytest.mark.parametrize("label,T,rows,cols,path", [("decode_gate_up", 64, 22016, 2048, 4), ("decode_down", 64, 2048, 11008, 4),
