@@ -113,7 +113,7 @@ void qmatmul_case(int32_t type, const void* w, int64_t rows, int64_t cols, const
     int qs_splits = 1;
     if (stream) {
         if (type != MK_TYPE_Q4_K || T > kQStreamMaxRows) throw std::runtime_error("mk_k_qmatmul: the streamed matmul covers Q4_K matrices and at most 64 rows");
-        build_qstream_weight(dw.w.p0, rows, cols, qsw);
+        build_qstream_weight(dw.w.p0, rows, cols, qsw, nullptr);
         qs_partial.alloc((size_t)16 << 20);
     }
     if (half) {

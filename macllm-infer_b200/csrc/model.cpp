@@ -494,15 +494,16 @@ void Model::build_qstream() {
         LayerWeights& w = lw_[l];
         stack(w.wq, w.wk, w.qk_raw);
         stack(w.gate, w.up, w.gu_raw);
-        build_qstream_weight(w.qk_raw.ptr(), w.wq.w.rows + w.wk.w.rows, w.wq.w.cols, w.qs_qk);
-        build_qstream_weight(w.wo.w.p0, w.wo.w.rows, w.wo.w.cols, w.qs_o);
-        build_qstream_weight(w.gu_raw.ptr(), w.gate.w.rows + w.up.w.rows, w.gate.w.cols, w.qs_gu);
-        build_qstream_weight(w.down.w.p0, w.down.w.rows, w.down.w.cols, w.qs_down);
+        build_qstream_weight(w.qk_raw.ptr(), w.wq.w.rows + w.wk.w.rows, w.wq.w.cols, w.qs_qk, stream_);
+        build_qstream_weight(w.wo.w.p0, w.wo.w.rows, w.wo.w.cols, w.qs_o, stream_);
+        build_qstream_weight(w.gu_raw.ptr(), w.gate.w.rows + w.up.w.rows, w.gate.w.cols, w.qs_gu, stream_);
+        build_qstream_weight(w.down.w.p0, w.down.w.rows, w.down.w.cols, w.qs_down, stream_);
     }
     v_partial_.alloc((size_t)16 * kQStreamMaxRows * ms_.kv_heads * ms_.head_dim * 4);
     // group sums of the streamed ticks' activations (at most kQStreamMaxRows rows)
     a_gs_.alloc((size_t)kQStreamMaxRows * (std::max(ms_.hidden, ms_.q_heads * ms_.head_dim) / 16) * 2);
     f_gs_.alloc((size_t)kQStreamMaxRows * (ms_.ffn / 16) * 2);
+    MK_CUDA(cudaStreamSynchronize(stream_));
     qstream_ = true;
 }
 

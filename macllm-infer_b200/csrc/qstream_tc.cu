@@ -5,18 +5,23 @@
 // rows share a matrix - the decode tick of a continuous batch, where the matmuls are bound by the bytes of the
 // weights.  Keeping the weights in their 4.5-bit block format makes those bytes 3.5x fewer than an f16 image.
 //
-// One CTA per (128 weight rows, share of K); 320 threads in three roles:
-//   warp 0    - one lane issues TMA loads into a ring of stages, each holding one 256-wide block column of the
-//               weights (128 rows x 144 raw bytes, no swizzle) and the matching 256 columns of the f16 activations
-//               (four 64-column boxes, 128-byte swizzle);
-//   warps 2-9 - two threads per weight row dequantise the stage, 128 columns at a time, into one of two f16 operand
-//               slots in the K-major no-swizzle core-matrix layout (8 rows x 16 bytes), with the same
-//               split-precision arithmetic as the in-kernel dequantisation of the wide GEMM;
-//   warp 1    - one lane issues eight K = 16 tcgen05 MMAs per slot (M = 128 rows, N = BN tokens, accumulator in
-//               tensor memory), commits the slot back to the dequantisers and, after the second slot of a stage,
-//               the stage back to the loader.
-// After the last MMA four of the dequantising warps read the accumulator and store either the result or, when K was
-// shared out over several CTAs, this share's partial sums (added later, in share order, by the consumer kernel).
+// The work is cut into (128-row tile, 256-column block) units, shared out evenly over at most one persistent CTA per
+// SM; a CTA's contiguous range of units usually covers the tail of one row tile, some whole row tiles and the head
+// of another.  448 threads in four roles:
+//   warp 0      - one lane issues TMA loads: the raw blocks of a unit (128 rows x 144 bytes, no swizzle) into a
+//                 four-deep ring, and the matching 256 columns of the f16 activations (four 64-column boxes,
+//                 128-byte swizzle) plus their per-group sums into a two-deep ring;
+//   warps 2-9   - two threads per weight row turn the nibbles of the block, 128 columns at a time, into one of two
+//                 f16 operand slots in the K-major no-swizzle core-matrix layout (8 rows x 16 bytes) - as the exact
+//                 integers sc * q - and the eight group minimums into a small second operand;
+//   warp 1      - one lane issues, per unit, sixteen K = 16 tcgen05 MMAs of sc * q against the activations and one of
+//                 the minimums against the activation group sums, into two of four accumulators in tensor memory
+//                 (M = 128 rows, N = BN tokens), and commits slots, stages and accumulators back to their producers;
+//   warps 10-13 - per unit, read both accumulators and add d * main - dmin * minimums (d and dmin are f16 in the
+//                 file, the arithmetic here is f32) to running sums in registers; at the end of the CTA's piece of a
+//                 row tile they store the sums - to the result when every row tile has one piece, else to that
+//                 piece's slot of the partial-sum scratch, whose slots the consumer kernel adds in slot order.
+// No weight is ever rounded: the only rounding left is the f16 image of the activations.
 // Every mbarrier wait is bounded; a wait that gives up records a status word and the role leaves its loop.
 #include "qstream_tc.h"
 #include "hgemm_tc.h"
@@ -68,6 +73,12 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const void* tmap, int x, 
         ::"r"(smem_u32(dst)), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
 }
+// One contiguous run of bytes (a multiple of 16, both ends 16-byte aligned) into this CTA's shared memory.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
 // K-major, no swizzle: core matrices of 8 rows x 16 bytes; lbo = bytes between K chunks, sbo = between 8-row groups.
 __device__ __forceinline__ uint64_t make_nosw_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     uint64_t d = 0;
@@ -97,6 +108,14 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -188,8 +207,10 @@ struct QsParams {
     int T, rows, n_blocks;        // n_blocks = cols / 256
     float* y;
     int ldy;
-    int row_tiles, splits, blocks_per_split;
-    float* partial;               // [splits][T][rows] when splits > 1
+    int row_tiles;
+    int units;                    // row_tiles * n_blocks (row tile, block) units, shared out evenly over the CTAs
+    int slots;                    // most pieces any row tile is cut into; > 1: pieces go to partial[slot][T][rows]
+    float* partial;
     int32_t* status;
 };
 
@@ -203,7 +224,7 @@ struct QsSmem {
 
 template <int BN>
 __global__ void __launch_bounds__(QS_THREADS, 1)
-qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+qstream_tc_kernel(const uint8_t* __restrict__ w_tiled, const __grid_constant__ CUtensorMap tm_x,
                   const __grid_constant__ CUtensorMap tm_gs, QsParams p) {
     using L = QsSmem<BN>;
     extern __shared__ uint8_t qs_smem_raw[];
@@ -224,9 +245,16 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     __shared__ uint32_t tmem_base_slot;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m_tile = blockIdx.x % p.row_tiles, split = blockIdx.x / p.row_tiles;
-    const int b0 = split * p.blocks_per_split, b1 = min(p.n_blocks, b0 + p.blocks_per_split);
-    const int n_local = b1 - b0;
+    // this CTA's share of the units: a contiguous range, usually the tail of one row tile, some whole row tiles and
+    // the head of another; a "piece" is the part of a row tile one CTA covers
+    const int u0 = (int)((int64_t)blockIdx.x * p.units / gridDim.x), u1 = (int)((int64_t)(blockIdx.x + 1) * p.units / gridDim.x);
+    const int n_local = u1 - u0;
+    auto cta_of_unit = [&](int u) {
+        int c = (int)((int64_t)u * gridDim.x / p.units);
+        while ((int64_t)(c + 1) * p.units / gridDim.x <= u) ++c;
+        while ((int64_t)c * p.units / gridDim.x > u) --c;
+        return c;
+    };
     constexpr uint32_t TMEM_COLS = 4 * BN;  // two sets of (main, minimums) accumulators
 
     if (threadIdx.x == 0) {
@@ -268,16 +296,18 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             auto load_raw = [&](int i) {
                 const int st = i % QS_RAW_STAGES;
                 mbar_expect_tx(&raw_full[st], (uint32_t)QS_RAW_BYTES);
-                tma_load_2d(raw_ring + (size_t)st * QS_RAW_BYTES, &tm_w, (b0 + i) * 144, m_tile * QS_BM, &raw_full[st]);
+                // units are stored one after the other, 128 rows x 144 bytes each: one contiguous copy
+                bulk_load(raw_ring + (size_t)st * QS_RAW_BYTES, w_tiled + (size_t)(u0 + i) * QS_RAW_BYTES, (uint32_t)QS_RAW_BYTES, &raw_full[st]);
             };
             auto load_x = [&](int i) {
                 const int st = i % QS_X_STAGES;
                 uint8_t* xb = x_ring + (size_t)st * L::X_BYTES;
+                const int blk = (u0 + i) % p.n_blocks;
                 mbar_expect_tx(&x_full[st], (uint32_t)L::X_BYTES);
 #pragma unroll
-                for (int q = 0; q < 4; ++q) tma_load_2d(xb + q * BN * 128, &tm_x, (b0 + i) * 256 + q * 64, 0, &x_full[st]);
-                tma_load_2d(xb + 4 * BN * 128, &tm_gs, (b0 + i) * 8, 0, &x_full[st]);
-                tma_load_2d(xb + 4 * BN * 128 + BN * 16, &tm_gs, p.n_blocks * 8 + (b0 + i) * 8, 0, &x_full[st]);
+                for (int q = 0; q < 4; ++q) tma_load_2d(xb + q * BN * 128, &tm_x, blk * 256 + q * 64, 0, &x_full[st]);
+                tma_load_2d(xb + 4 * BN * 128, &tm_gs, blk * 8, 0, &x_full[st]);
+                tma_load_2d(xb + 4 * BN * 128 + BN * 16, &tm_gs, p.n_blocks * 8 + blk * 8, 0, &x_full[st]);
             };
             int ri = 0, xi = 0;
             for (; ri < n_local && ri < QS_RAW_STAGES; ++ri) load_raw(ri);  // first use of each stage: nothing to wait for
@@ -375,28 +405,47 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             const float2 dm = dd[(i & 3) * QS_BM + row_in_tile];
             const uint32_t t_main = tmem_base + ((uint32_t)(quad * 32) << 16) + set * 2 * BN;
 #pragma unroll
-            for (int cb = 0; cb < BN; cb += 32) {
-                uint32_t vm[32], vn[32];
-                tmem_ld32(t_main + (uint32_t)cb, vm);
-                tmem_ld32(t_main + BN + (uint32_t)cb, vn);
+            for (int cb = 0; cb < BN; cb += 16) {
+                uint32_t vm[16], vn[16];
+                tmem_ld16(t_main + (uint32_t)cb, vm);
+                tmem_ld16(t_main + BN + (uint32_t)cb, vn);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int t = 0; t < 32; ++t)
+                for (int t = 0; t < 16; ++t)
                     acc[cb + t] = __fmaf_rn(-dm.y, __uint_as_float(vn[t]), __fmaf_rn(dm.x, __uint_as_float(vm[t]), acc[cb + t]));
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(&acc_empty[set]);
-        }
-        if (ok && n_local > 0) {
-            const int row = m_tile * QS_BM + row_in_tile;
-            float* dst = p.splits > 1 ? p.partial + (int64_t)split * p.T * p.rows : p.y;
-            const int ld = p.splits > 1 ? p.rows : p.ldy;
-            if (row < p.rows) {
+            // end of this CTA's piece of the row tile: store it and start the next piece from zero
+            const int u = u0 + i, tile = u / p.n_blocks;
+            if (i + 1 == n_local || (u + 1) / p.n_blocks != tile) {
+                const int row = tile * QS_BM + row_in_tile;
+                if (p.slots == 1) {
+                    if (row < p.rows) {
 #pragma unroll
-                for (int t = 0; t < BN; ++t)
-                    if (t < p.T) dst[(int64_t)t * ld + row] = acc[t];
+                        for (int t = 0; t < BN; ++t)
+                            if (t < p.T) p.y[(int64_t)t * p.ldy + row] = acc[t];
+                    }
+                } else {
+                    const int first = cta_of_unit(tile * p.n_blocks);
+                    const int64_t slot_stride = (int64_t)p.T * p.rows;
+                    float* dst = p.partial + (int64_t)((int)blockIdx.x - first) * slot_stride;
+                    const bool last_piece = u + 1 == (tile + 1) * p.n_blocks;
+                    if (row < p.rows) {
+#pragma unroll
+                        for (int t = 0; t < BN; ++t)
+                            if (t < p.T) dst[(int64_t)t * p.rows + row] = acc[t];
+                        if (last_piece) {  // the slots this row tile does not use read as zero
+                            for (int sl = (int)blockIdx.x - first + 1; sl < p.slots; ++sl)
+                                for (int t = 0; t < p.T; ++t) p.partial[sl * slot_stride + (int64_t)t * p.rows + row] = 0.f;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int t = 0; t < BN; ++t) acc[t] = 0.f;
             }
         }
+        (void)ok;
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -407,27 +456,44 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     }
 }
 
+// Row-major Q4_K blocks [rows][nb][144 bytes] -> unit-major [row tile][block][128 rows][144 bytes], rows past the end
+// zero (a zero block dequantises to zero).  16 bytes per thread.
+__global__ void retile_q4k_kernel(const uint4* src, int64_t rows, int nb, uint4* dst, int64_t chunks) {
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= chunks) return;
+    const int64_t unit = c / (QS_RAW_BYTES / 16);
+    const int in_unit = (int)(c - unit * (QS_RAW_BYTES / 16));
+    const int r = in_unit / 9, part = in_unit - r * 9;  // 144 bytes = 9 chunks
+    const int64_t tile = unit / nb, blk = unit - tile * nb;
+    const int64_t row = tile * QS_BM + r;
+    dst[c] = row < rows ? src[(row * nb + blk) * 9 + part] : make_uint4(0, 0, 0, 0);
+}
+
 template <int BN>
-void launch_qs(const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& tg, const QsParams& p, cudaStream_t s) {
+void launch_qs(const uint8_t* w_tiled, const CUtensorMap& tx, const CUtensorMap& tg, const QsParams& p, int ctas, cudaStream_t s) {
     constexpr size_t smem = QsSmem<BN>::TOTAL;
     static bool configured = false;
     if (!configured) {
         MK_CUDA(cudaFuncSetAttribute(qstream_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
-    launch_pdl(qstream_tc_kernel<BN>, dim3(p.row_tiles * p.splits), dim3(QS_THREADS), smem, s, tw, tx, tg, p);
+    launch_pdl(qstream_tc_kernel<BN>, dim3(ctas), dim3(QS_THREADS), smem, s, w_tiled, tx, tg, p);
     MK_LAUNCH_CHECK();
 }
 
 }  // namespace
 
-void build_qstream_weight(const void* q4k_blocks, int64_t rows, int64_t cols, QStreamWeight& out) {
+void build_qstream_weight(const void* q4k_blocks, int64_t rows, int64_t cols, QStreamWeight& out, cudaStream_t s) {
     if (cols <= 0 || cols % 256 != 0 || rows <= 0) throw std::runtime_error("build_qstream_weight: cols must be a positive multiple of 256");
-    out.base = q4k_blocks;
     out.rows = rows;
     out.cols = cols;
-    const uint64_t row_bytes = (uint64_t)(cols / 256) * 144;
-    encode_tma_2d(out.tmap, true, q4k_blocks, row_bytes, (uint64_t)rows, row_bytes, 144, QS_BM, false);
+    const int nb = (int)(cols / 256);
+    const int64_t row_tiles = (rows + QS_BM - 1) / QS_BM;
+    out.tiled.alloc((size_t)row_tiles * nb * QS_RAW_BYTES);
+    const int64_t chunks = row_tiles * nb * (QS_RAW_BYTES / 16);
+    retile_q4k_kernel<<<(unsigned)((chunks + 255) / 256), 256, 0, s>>>(reinterpret_cast<const uint4*>(q4k_blocks), rows, nb,
+                                                                        out.tiled.as<uint4>(), chunks);
+    MK_LAUNCH_CHECK();
     out.ready = true;
 }
 
@@ -436,21 +502,35 @@ QStreamPlan qstream_plan(int64_t rows, int64_t cols, int T, int max_splits) {
     pl.bn = T <= 32 ? 32 : 64;
     pl.row_tiles = (int)((rows + QS_BM - 1) / QS_BM);
     const int nb = (int)(cols / 256);
+    pl.units = pl.row_tiles * nb;
     const int sms = 148;
-    // K shares: fewest "waves x (blocks per share + fixed cost)", at most 16 MiB of partial sums
-    int best = 1;
-    long best_cost = -1;
-    for (int s = 1; s <= std::max(1, std::min(max_splits, nb)); ++s) {
-        int per = (nb + s - 1) / s;
-        if (s > 1 && (size_t)s * T * rows * 4 > ((size_t)16 << 20)) break;
-        if ((nb + per - 1) / per != s) continue;
-        long waves = ((long)pl.row_tiles * s + sms - 1) / sms;
-        long cost = waves * (2 * per + 3) + (s > 1 ? 1 : 0);
-        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
+    auto pieces = [&](int ctas) {  // most CTAs any row tile is spread over
+        int worst = 1;
+        auto cta_of = [&](int64_t u) {
+            int64_t c = u * ctas / pl.units;
+            while ((c + 1) * pl.units / ctas <= u) ++c;
+            while (c * pl.units / ctas > u) --c;
+            return (int)c;
+        };
+        for (int t = 0; t < pl.row_tiles; ++t) worst = std::max(worst, cta_of((int64_t)t * nb + nb - 1) - cta_of((int64_t)t * nb) + 1);
+        return worst;
+    };
+    if (max_splits <= 1) {
+        pl.ctas = pl.row_tiles;  // whole row tiles only: the result is complete in y
+        pl.slots = 1;
+    } else {
+        // as many CTAs as there are SMs, at least two blocks each; fewer while a row tile would be cut into more
+        // pieces than the consumer may add or the pieces would not fit in 16 MiB
+        int ctas = std::max(1, std::min(sms, pl.units));
+        while (ctas > 1) {
+            int s = pieces(ctas);
+            if (s <= std::min(max_splits, 16) && (size_t)s * T * rows * 4 <= ((size_t)16 << 20)) break;
+            ctas = ctas * 3 / 4;
+        }
+        pl.ctas = ctas;
+        pl.slots = pieces(ctas);
     }
-    pl.splits = best;
-    pl.blocks_per_split = (nb + best - 1) / best;
-    pl.partial_floats = best > 1 ? (size_t)best * T * rows : 0;
+    pl.partial_floats = pl.slots > 1 ? (size_t)pl.slots * T * rows : 0;
     return pl;
 }
 
@@ -462,10 +542,7 @@ int launch_qstream_tc(const QStreamWeight& W, const __half* xh, const __half* gs
     if (xh == nullptr || gs == nullptr) throw std::runtime_error("launch_qstream_tc: f16 activations or their group sums missing");
     if (partial == nullptr) max_splits = 1;
     QStreamPlan pl = qstream_plan(W.rows, W.cols, T, max_splits);
-    if (pl.splits > 1 && pl.partial_floats > partial_floats) {
-        pl.splits = 1;
-        pl.blocks_per_split = (int)(W.cols / 256);
-    }
+    if (pl.slots > 1 && pl.partial_floats > partial_floats) pl = qstream_plan(W.rows, W.cols, T, 1);
     alignas(64) CUtensorMap tx;
     encode_tma_2d(&tx, false, xh, (uint64_t)W.cols, (uint64_t)T, (uint64_t)W.cols * 2, 64, (uint32_t)pl.bn, true);
     // group sums [T][2 * cols/32] f16: boxes of 8 halves (the eight groups of one block) x BN rows land as one
@@ -479,14 +556,13 @@ int launch_qstream_tc(const QStreamWeight& W, const __half* xh, const __half* gs
     p.y = y;
     p.ldy = ldy;
     p.row_tiles = pl.row_tiles;
-    p.splits = pl.splits;
-    p.blocks_per_split = pl.blocks_per_split;
+    p.units = pl.units;
+    p.slots = pl.slots;
     p.partial = partial;
     p.status = status;
-    const CUtensorMap& tw = *reinterpret_cast<const CUtensorMap*>(W.tmap);
-    if (pl.bn == 32) launch_qs<32>(tw, tx, tg, p, s);
-    else launch_qs<64>(tw, tx, tg, p, s);
-    return pl.splits;
+    if (pl.bn == 32) launch_qs<32>(W.tiled.as<uint8_t>(), tx, tg, p, pl.ctas, s);
+    else launch_qs<64>(W.tiled.as<uint8_t>(), tx, tg, p, pl.ctas, s);
+    return pl.slots;
 }
 
 }  // namespace mk
