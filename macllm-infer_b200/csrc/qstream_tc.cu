@@ -7,7 +7,7 @@
 //
 // The work is cut into (128-row tile, 256-column block) units, shared out evenly over at most one persistent CTA per
 // SM; a CTA's contiguous range of units usually covers the tail of one row tile, some whole row tiles and the head
-// of another.  448 threads in four roles:
+// of another.  576 threads in four roles:
 //   warp 0      - one lane issues TMA loads: the raw blocks of a unit (128 rows x 144 bytes, no swizzle) into a
 //                 four-deep ring, and the matching 256 columns of the f16 activations (four 64-column boxes,
 //                 128-byte swizzle) plus their per-group sums into a two-deep ring;
@@ -17,7 +17,7 @@
 //   warp 1      - one lane issues, per unit, sixteen K = 16 tcgen05 MMAs of sc * q against the activations and one of
 //                 the minimums against the activation group sums, into two of four accumulators in tensor memory
 //                 (M = 128 rows, N = BN tokens), and commits slots, stages and accumulators back to their producers;
-//   warps 10-13 - per unit, read both accumulators and add d * main - dmin * minimums (d and dmin are f16 in the
+//   warps 10-17 - per unit, read both accumulators (one TMEM lane quadrant and one half of the token columns each) and add d * main - dmin * minimums (d and dmin are f16 in the
 //                 file, the arithmetic here is f32) to running sums in registers; at the end of the CTA's piece of a
 //                 row tile they store the sums - to the result when every row tile has one piece, else to that
 //                 piece's slot of the partial-sum scratch, whose slots the consumer kernel adds in slot order.
@@ -34,7 +34,7 @@ namespace mk {
 namespace {
 
 constexpr int QS_BM = 128;
-constexpr int QS_THREADS = 448;  // loader warp, MMA warp, eight converting warps, four epilogue warps
+constexpr int QS_THREADS = 576;  // loader warp, MMA warp, eight converting warps, eight epilogue warps
 constexpr int QS_RAW_STAGES = 4;  // weight blocks in flight (HBM latency)
 constexpr int QS_X_STAGES = 2;    // activation blocks in flight (L2 latency)
 constexpr int QS_RAW_BYTES = QS_BM * 144;         // one block column of 128 rows
@@ -117,6 +117,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr)
         : "memory");
 }
+template <int N>
+__device__ __forceinline__ void tmem_ld_n(uint32_t taddr, uint32_t (&r)[N]);
+template <>
+__device__ __forceinline__ void tmem_ld_n<16>(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld16(taddr, r); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]);
+template <>
+__device__ __forceinline__ void tmem_ld_n<32>(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
@@ -270,7 +277,7 @@ qstream_tc_kernel(const uint8_t* __restrict__ w_tiled, const __grid_constant__ C
             mbar_init(&a_full[i], 256);
             mbar_init(&a_empty[i], 1);
             mbar_init(&acc_full[i], 1);
-            mbar_init(&acc_empty[i], 128);
+            mbar_init(&acc_empty[i], 256);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -387,12 +394,14 @@ qstream_tc_kernel(const uint8_t* __restrict__ w_tiled, const __grid_constant__ C
             if (ok) mbar_arrive(&raw_empty[st]);
         }
     } else {
-        // ---- epilogue warps 10-13: per block, y += d * main - dmin * minimums, running sums in registers
-        const int quad = warp & 3;
+        // ---- epilogue warps 10-17: warp w reads TMEM lanes 32 (w % 4) .. + 31 (weight rows) and one half of the
+        // token columns; per block, y += d * main - dmin * minimums, running sums in registers
+        constexpr int HN = BN / 2;  // token columns per warp
+        const int quad = warp & 3, chalf = (warp - 10) >> 2;
         const int row_in_tile = quad * 32 + lane;
-        float acc[BN];
+        float acc[HN];
 #pragma unroll
-        for (int t = 0; t < BN; ++t) acc[t] = 0.f;
+        for (int t = 0; t < HN; ++t) acc[t] = 0.f;
         bool ok = true;
         for (int i = 0; i < n_local; ++i) {
             const uint32_t set = i & 1, aph = (i >> 1) & 1;
@@ -403,16 +412,15 @@ qstream_tc_kernel(const uint8_t* __restrict__ w_tiled, const __grid_constant__ C
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float2 dm = dd[(i & 3) * QS_BM + row_in_tile];
-            const uint32_t t_main = tmem_base + ((uint32_t)(quad * 32) << 16) + set * 2 * BN;
-#pragma unroll
-            for (int cb = 0; cb < BN; cb += 16) {
-                uint32_t vm[16], vn[16];
-                tmem_ld16(t_main + (uint32_t)cb, vm);
-                tmem_ld16(t_main + BN + (uint32_t)cb, vn);
+            const uint32_t t_main = tmem_base + ((uint32_t)(quad * 32) << 16) + set * 2 * BN + chalf * HN;
+            {
+                uint32_t vm[HN], vn[HN];
+                tmem_ld_n<HN>(t_main, vm);
+                tmem_ld_n<HN>(t_main + BN, vn);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int t = 0; t < 16; ++t)
-                    acc[cb + t] = __fmaf_rn(-dm.y, __uint_as_float(vn[t]), __fmaf_rn(dm.x, __uint_as_float(vm[t]), acc[cb + t]));
+                for (int t = 0; t < HN; ++t)
+                    acc[t] = __fmaf_rn(-dm.y, __uint_as_float(vn[t]), __fmaf_rn(dm.x, __uint_as_float(vm[t]), acc[t]));
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(&acc_empty[set]);
@@ -420,11 +428,12 @@ qstream_tc_kernel(const uint8_t* __restrict__ w_tiled, const __grid_constant__ C
             const int u = u0 + i, tile = u / p.n_blocks;
             if (i + 1 == n_local || (u + 1) / p.n_blocks != tile) {
                 const int row = tile * QS_BM + row_in_tile;
+                const int t0 = chalf * HN;
                 if (p.slots == 1) {
                     if (row < p.rows) {
 #pragma unroll
-                        for (int t = 0; t < BN; ++t)
-                            if (t < p.T) p.y[(int64_t)t * p.ldy + row] = acc[t];
+                        for (int t = 0; t < HN; ++t)
+                            if (t0 + t < p.T) p.y[(int64_t)(t0 + t) * p.ldy + row] = acc[t];
                     }
                 } else {
                     const int first = cta_of_unit(tile * p.n_blocks);
@@ -433,16 +442,16 @@ qstream_tc_kernel(const uint8_t* __restrict__ w_tiled, const __grid_constant__ C
                     const bool last_piece = u + 1 == (tile + 1) * p.n_blocks;
                     if (row < p.rows) {
 #pragma unroll
-                        for (int t = 0; t < BN; ++t)
-                            if (t < p.T) dst[(int64_t)t * p.rows + row] = acc[t];
+                        for (int t = 0; t < HN; ++t)
+                            if (t0 + t < p.T) dst[(int64_t)(t0 + t) * p.rows + row] = acc[t];
                         if (last_piece) {  // the slots this row tile does not use read as zero
                             for (int sl = (int)blockIdx.x - first + 1; sl < p.slots; ++sl)
-                                for (int t = 0; t < p.T; ++t) p.partial[sl * slot_stride + (int64_t)t * p.rows + row] = 0.f;
+                                for (int t = t0; t < min(p.T, t0 + HN); ++t) p.partial[sl * slot_stride + (int64_t)t * p.rows + row] = 0.f;
                         }
                     }
                 }
 #pragma unroll
-                for (int t = 0; t < BN; ++t) acc[t] = 0.f;
+                for (int t = 0; t < HN; ++t) acc[t] = 0.f;
             }
         }
         (void)ok;
