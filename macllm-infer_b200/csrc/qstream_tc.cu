@@ -7,17 +7,17 @@
 //
 // The work is cut into (128-row tile, 256-column block) units, shared out evenly over at most one persistent CTA per
 // SM; a CTA's contiguous range of units usually covers the tail of one row tile, some whole row tiles and the head
-// of another.  576 threads in four roles:
-//   warp 0      - one lane issues TMA loads: the raw blocks of a unit (128 rows x 144 bytes, no swizzle) into a
-//                 four-deep ring, and the matching 256 columns of the f16 activations (four 64-column boxes,
+// of another.  608 threads in five roles:
+//   warp 0      - one lane streams the raw blocks of the units (18 KiB bulk copies) into a four-deep ring;
+//   warp 2      - one lane loads the matching 256 columns of the f16 activations (four 64-column TMA boxes,
 //                 128-byte swizzle) plus their per-group sums into a two-deep ring;
-//   warps 2-9   - two threads per weight row turn the nibbles of the block, 128 columns at a time, into one of two
+//   warps 3-10  - two threads per weight row turn the nibbles of the block, 128 columns at a time, into one of two
 //                 f16 operand slots in the K-major no-swizzle core-matrix layout (8 rows x 16 bytes) - as the exact
 //                 integers sc * q - and the eight group minimums into a small second operand;
 //   warp 1      - one lane issues, per unit, sixteen K = 16 tcgen05 MMAs of sc * q against the activations and one of
 //                 the minimums against the activation group sums, into two of four accumulators in tensor memory
 //                 (M = 128 rows, N = BN tokens), and commits slots, stages and accumulators back to their producers;
-//   warps 10-17 - per unit, read both accumulators (one TMEM lane quadrant and one half of the token columns each) and add d * main - dmin * minimums (d and dmin are f16 in the
+//   warps 11-18 - per unit, read both accumulators (one TMEM lane quadrant and one half of the token columns each) and add d * main - dmin * minimums (d and dmin are f16 in the
 //                 file, the arithmetic here is f32) to running sums in registers; at the end of the CTA's piece of a
 //                 row tile they store the sums - to the result when every row tile has one piece, else to that
 //                 piece's slot of the partial-sum scratch, whose slots the consumer kernel adds in slot order.
@@ -34,7 +34,7 @@ namespace mk {
 namespace {
 
 constexpr int QS_BM = 128;
-constexpr int QS_THREADS = 576;  // loader warp, MMA warp, eight converting warps, eight epilogue warps
+constexpr int QS_THREADS = 608;  // weight loader, MMA, activation loader warps; eight converting, eight epilogue warps
 constexpr int QS_RAW_STAGES = 4;  // weight blocks in flight (HBM latency)
 constexpr int QS_X_STAGES = 2;    // activation blocks in flight (L2 latency)
 constexpr int QS_RAW_BYTES = QS_BM * 144;         // one block column of 128 rows
@@ -267,17 +267,17 @@ qstream_tc_kernel(const uint8_t* __restrict__ w_tiled, const __grid_constant__ C
     if (threadIdx.x == 0) {
         for (int i = 0; i < QS_RAW_STAGES; ++i) {
             mbar_init(&raw_full[i], 1);
-            mbar_init(&raw_empty[i], 256);
+            mbar_init(&raw_empty[i], 8);   // one arrival per converting warp
         }
         for (int i = 0; i < QS_X_STAGES; ++i) {
             mbar_init(&x_full[i], 1);
             mbar_init(&x_empty[i], 1);
         }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&a_full[i], 256);
+            mbar_init(&a_full[i], 8);
             mbar_init(&a_empty[i], 1);
             mbar_init(&acc_full[i], 1);
-            mbar_init(&acc_empty[i], 256);
+            mbar_init(&acc_empty[i], 8);   // one arrival per epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -298,16 +298,23 @@ qstream_tc_kernel(const uint8_t* __restrict__ w_tiled, const __grid_constant__ C
     pdl_trigger();
 
     if (warp == 0) {
-        // ---- loader
+        // ---- weight loader: the weights depend on no predecessor kernel, so this lane never waits for one
         if (lane == 0) {
-            auto load_raw = [&](int i) {
-                const int st = i % QS_RAW_STAGES;
+            for (int i = 0; i < n_local; ++i) {
+                const uint32_t st = i % QS_RAW_STAGES, ph = (i / QS_RAW_STAGES) & 1;
+                if (!mbar_wait(&raw_empty[st], ph ^ 1, QS_SPIN_LIMIT)) { atomicExch(p.status, 22); break; }
                 mbar_expect_tx(&raw_full[st], (uint32_t)QS_RAW_BYTES);
                 // units are stored one after the other, 128 rows x 144 bytes each: one contiguous copy
                 bulk_load(raw_ring + (size_t)st * QS_RAW_BYTES, w_tiled + (size_t)(u0 + i) * QS_RAW_BYTES, (uint32_t)QS_RAW_BYTES, &raw_full[st]);
-            };
-            auto load_x = [&](int i) {
-                const int st = i % QS_X_STAGES;
+            }
+        }
+    } else if (warp == 2) {
+        // ---- activation loader (its own warp, so that a full activation ring never holds back the weight stream)
+        if (lane == 0) {
+            pdl_wait();
+            for (int i = 0; i < n_local; ++i) {
+                const uint32_t st = i % QS_X_STAGES, ph = (i / QS_X_STAGES) & 1;
+                if (!mbar_wait(&x_empty[st], ph ^ 1, QS_SPIN_LIMIT)) { atomicExch(p.status, 21); break; }
                 uint8_t* xb = x_ring + (size_t)st * L::X_BYTES;
                 const int blk = (u0 + i) % p.n_blocks;
                 mbar_expect_tx(&x_full[st], (uint32_t)L::X_BYTES);
@@ -315,22 +322,6 @@ qstream_tc_kernel(const uint8_t* __restrict__ w_tiled, const __grid_constant__ C
                 for (int q = 0; q < 4; ++q) tma_load_2d(xb + q * BN * 128, &tm_x, blk * 256 + q * 64, 0, &x_full[st]);
                 tma_load_2d(xb + 4 * BN * 128, &tm_gs, blk * 8, 0, &x_full[st]);
                 tma_load_2d(xb + 4 * BN * 128 + BN * 16, &tm_gs, p.n_blocks * 8 + blk * 8, 0, &x_full[st]);
-            };
-            int ri = 0, xi = 0;
-            for (; ri < n_local && ri < QS_RAW_STAGES; ++ri) load_raw(ri);  // first use of each stage: nothing to wait for
-            pdl_wait();
-            bool ok = true;
-            while (ok && (xi < n_local || ri < n_local)) {
-                if (xi < n_local) {
-                    const uint32_t st = xi % QS_X_STAGES, ph = (xi / QS_X_STAGES) & 1;
-                    if (!mbar_wait(&x_empty[st], ph ^ 1, QS_SPIN_LIMIT)) { atomicExch(p.status, 21); ok = false; break; }
-                    load_x(xi++);
-                }
-                if (ri < n_local) {
-                    const uint32_t st = ri % QS_RAW_STAGES, ph = (ri / QS_RAW_STAGES) & 1;
-                    if (!mbar_wait(&raw_empty[st], ph ^ 1, QS_SPIN_LIMIT)) { atomicExch(p.status, 22); ok = false; break; }
-                    load_raw(ri++);
-                }
             }
         }
     } else if (warp == 1) {
@@ -369,9 +360,9 @@ qstream_tc_kernel(const uint8_t* __restrict__ w_tiled, const __grid_constant__ C
                 }
             }
         }
-    } else if (warp < 10) {
-        // ---- converters: two threads per weight row of the tile, 64 columns each per half block
-        const int r = ((int)threadIdx.x - 64) & 127, csel = ((int)threadIdx.x - 64) >> 7;
+    } else if (warp < 11) {
+        // ---- converters (warps 3-10): two threads per weight row of the tile, 64 columns each per half block
+        const int r = ((int)threadIdx.x - 96) & 127, csel = ((int)threadIdx.x - 96) >> 7;
         bool ok = true;
         for (int i = 0; i < n_local && ok; ++i) {
             const uint32_t st = i % QS_RAW_STAGES, ph = (i / QS_RAW_STAGES) & 1;
@@ -388,16 +379,21 @@ qstream_tc_kernel(const uint8_t* __restrict__ w_tiled, const __grid_constant__ C
                 }
                 convert_chunk(blk, r, half, csel, a_slots + half * QS_A_SLOT_BYTES);
                 if (half == 0 && csel == 0) write_mins(blk, r, extras + (i & 1) * L::EXTRA_BYTES, dd + (i & 3) * QS_BM);
+                // every lane makes its stores visible to the async proxy, then one lane arrives for the warp
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive(&a_full[half]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&a_full[half]);
             }
-            if (ok) mbar_arrive(&raw_empty[st]);
+            if (ok) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&raw_empty[st]);
+            }
         }
     } else {
-        // ---- epilogue warps 10-17: warp w reads TMEM lanes 32 (w % 4) .. + 31 (weight rows) and one half of the
+        // ---- epilogue warps 11-18: warp w reads TMEM lanes 32 (w % 4) .. + 31 (weight rows) and one half of the
         // token columns; per block, y += d * main - dmin * minimums, running sums in registers
         constexpr int HN = BN / 2;  // token columns per warp
-        const int quad = warp & 3, chalf = (warp - 10) >> 2;
+        const int quad = warp & 3, chalf = (warp - 11) >> 2;
         const int row_in_tile = quad * 32 + lane;
         float acc[HN];
 #pragma unroll
@@ -423,7 +419,8 @@ qstream_tc_kernel(const uint8_t* __restrict__ w_tiled, const __grid_constant__ C
                     acc[t] = __fmaf_rn(-dm.y, __uint_as_float(vn[t]), __fmaf_rn(dm.x, __uint_as_float(vm[t]), acc[t]));
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(&acc_empty[set]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[set]);
             // end of this CTA's piece of the row tile: store it and start the next piece from zero
             const int u = u0 + i, tile = u / p.n_blocks;
             if (i + 1 == n_local || (u + 1) / p.n_blocks != tile) {
