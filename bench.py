@@ -51,6 +51,17 @@ WORKLOADS = {
 }
 
 
+# DRAM traffic of the three dominant kernels relative to their algorithmic bytes, from one `ncu --set full` capture
+# each on the benchmark's shapes (dram__bytes_read.sum + dram__bytes_write.sum over the bytes counted here; the
+# summaries with the commands are profiles/hgemm_tc_kernel_prefill_gate_up.md, qstream_tc_kernel_decode_gate_up.md and
+# attn_decode_kernel_64_lanes.md).  The roofline block scales the live per-launch algorithmic bytes by these ratios.
+NCU_TRAFFIC_RATIO = {
+    "hgemm_tc": (498.9 + 145.5) / (90.2 + 8.4 + 180.4),   # the weight image is re-read about five times, outputs partly stay in L2
+    "qstream_tc": 25.69 / (25.36 + 0.26 + 5.64),          # weights once; the partial sums never leave L2
+    "paged_attention": (76.97 + 2.64) / (72.4 + 4.2),
+}
+
+
 def peaks() -> dict:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -133,7 +144,10 @@ class ClockSampler:
                     samples=len(sm))
 
 
-def dist_setup(n_gpus: int):
+def dist_setup(n_gpus: int, backend: str = "nccl"):
+    """One process per GPU (torchrun sets RANK / LOCAL_RANK / WORLD_SIZE / MASTER_*).  Replicas share nothing on
+    the data path; the process group only carries the barrier and the two scalar reductions of the report.
+    backend "gloo" keeps everything on the CPU (used by the CPU tests of this plumbing)."""
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -141,35 +155,49 @@ def dist_setup(n_gpus: int):
     if world > 1:
         import torch
         import torch.distributed as dist_mod
-        torch.cuda.set_device(local)
-        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        if backend == "nccl":
+            torch.cuda.set_device(local)
+            dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        else:
+            dist_mod.init_process_group(backend)
         dist = dist_mod
     return rank, local, world, dist
 
 
+def _on_gpu(dist) -> bool:
+    return dist.get_backend() == "nccl"
+
+
 def barrier(dist):
     if dist is not None:
-        import torch
         dist.barrier()
-        torch.cuda.synchronize()
+        if _on_gpu(dist):
+            import torch
+            torch.cuda.synchronize()
+
+
+def _all_reduce(dist, x: float, op_name: str) -> float:
+    if dist is None:
+        return x
+    import torch
+    t = torch.tensor([x], dtype=torch.float64, device="cuda" if _on_gpu(dist) else "cpu")
+    dist.all_reduce(t, op=getattr(dist.ReduceOp, op_name))
+    return float(t.item())
 
 
 def all_max(dist, x: float) -> float:
-    if dist is None:
-        return x
-    import torch
-    t = torch.tensor([x], dtype=torch.float64, device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
+    return _all_reduce(dist, x, "MAX")
 
 
 def all_sum(dist, x: float) -> float:
-    if dist is None:
-        return x
-    import torch
-    t = torch.tensor([x], dtype=torch.float64, device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.SUM)
-    return float(t.item())
+    return _all_reduce(dist, x, "SUM")
+
+
+def aggregate(dist, tokens: float, seconds: float) -> tuple[float, float, float]:
+    """Whole-job figures of N replicas: (tokens of all ranks, slowest rank's time, tokens / that time)."""
+    total = all_sum(dist, float(tokens))
+    slowest = all_max(dist, float(seconds))
+    return total, slowest, total / max(slowest, 1e-12)
 
 
 def run_step(eng_mod, model, w, prompts):
@@ -330,6 +358,10 @@ def main():
         else:
             achieved = top["bytes"] / (top["ms"] / 1e3) / 1e9
             roof = dict(bound="hbm", achieved=achieved, peak=pk["hbm_gbs"], unit="GB/s", frac=achieved / pk["hbm_gbs"], traffic=None)
+        ratio = NCU_TRAFFIC_RATIO.get(top["name"])
+        if ratio is not None:
+            roof["traffic"] = ratio * top["bytes"] / max(top["launches"], 1)
+            roof["traffic_unit"] = "bytes per launch (ncu ratio x live algorithmic bytes)"
         roof.update(kernel=top["name"], launches=top["launches"], avg_launch_ms=top["ms"] / max(top["launches"], 1),
                     time_share=top["ms"] / total_ms, peak_source=pk["source"],
                     classes={r["name"]: dict(launches=r["launches"], ms=round(r["ms"], 3), share=round(r["ms"] / total_ms, 4),
@@ -346,7 +378,7 @@ def main():
     if rank == 0:
         out = dict(metric=METRIC, value=tokens_all / dev_max, unit=UNIT, n_gpus=world, steps=args.steps, warmup=args.warmup,
                    ms_per_step=wall_max * 1e3 / max(args.steps, 1), higher_is_better=True, scaling="weak", vs_baseline=None,
-                   dtype="int8 x int4/6 block dots (decode rows) / f16 tensor cores (wide batches), f32 accumulate, f16 KV",
+                   dtype="f16 tensor cores over exact Q4_K integers or f16 weight images (>= 9 rows), int8 x int4/6 block dots (<= 8 rows), f32 accumulate, f16 KV",
                    data="synthetic", config=config, clocks=clocks,
                    e2e=dict(value=tokens_all / wall_max, unit=UNIT, h2d_bytes_per_step=(h2d1 - h2d0) // max(args.steps, 1),
                             d2h_bytes_per_step=(d2h1 - d2h0) // max(args.steps, 1)),

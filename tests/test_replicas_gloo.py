@@ -1,0 +1,68 @@
+"""The multi-GPU form of the benchmark is N independent replicas (one process per GPU, no data-path collective):
+this exercises its plumbing - rendezvous, per-rank request streams, barrier, sum of tokens over ranks, time of the
+slowest rank - with two CPU processes over gloo, each running the real engine (scheduler, paged KV pool, prefix
+cache) on the host-only fake model."""
+import json
+import os
+import socket
+import subprocess
+import sys
+import textwrap
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+
+CHILD = textwrap.dedent("""
+    import importlib, json, sys, time
+    sys.path.insert(0, %r)
+    import bench
+    import __graft_entry__ as entry
+    entry.load_package()
+    eng = importlib.import_module("macllm_infer_b200.engine")
+    rank, local, world, dist = bench.dist_setup(2, backend="gloo")
+    w = dict(seed=77, seqs=6, prompt=(5, 40), new_tokens=7)
+    prompts = bench.make_prompts(w, 32, rank)
+    model = eng.Model.fake(vocab=32, max_context=256, kv_capacity_tokens=1024)
+    e = eng.Engine(model, max_active_sequences=6, scheduler_token_budget=64, prefill_token_quantum=16, queue_capacity=16)
+    bench.barrier(dist)
+    t0 = time.perf_counter()
+    ids = e.submit([eng.Request(p, w["new_tokens"]) for p in prompts], atomic_batch=True)
+    e.run()
+    seconds = time.perf_counter() - t0 + 0.01 * (rank + 1)   # rank 1 is the slowest by construction
+    tokens = sum(len(p) for p in prompts) + sum(len(e.result(i)["tokens"]) for i in ids)
+    bench.barrier(dist)
+    total, slowest, rate = bench.aggregate(dist, tokens, seconds)
+    print(json.dumps(dict(rank=rank, world=world, tokens=tokens, seconds=seconds, total=total, slowest=slowest, rate=rate,
+                          first_prompt=[int(x) for x in prompts[0][:4]])), flush=True)
+    dist.destroy_process_group()
+""") % str(ROOT)
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_two_replicas_aggregate_over_gloo():
+    port = _free_port()
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        procs.append(subprocess.Popen([sys.executable, "-c", CHILD], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    outs = []
+    for p in procs:
+        out, err = p.communicate(timeout=240)
+        assert p.returncode == 0, err[-2000:]
+        outs.append(json.loads(out.strip().splitlines()[-1]))
+    outs.sort(key=lambda o: o["rank"])
+    assert [o["world"] for o in outs] == [2, 2]
+    # per-rank request streams differ, every rank reports the same whole-job figures
+    assert outs[0]["first_prompt"] != outs[1]["first_prompt"]
+    want_total = outs[0]["tokens"] + outs[1]["tokens"]
+    want_slowest = max(outs[0]["seconds"], outs[1]["seconds"])
+    for o in outs:
+        assert o["total"] == want_total
+        assert abs(o["slowest"] - want_slowest) < 1e-9
+        assert abs(o["rate"] - want_total / want_slowest) < 1e-6 * o["rate"]
+    assert outs[1]["seconds"] == want_slowest
