@@ -284,8 +284,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tc_kernel(AttnTcArgs a) {
 // One-token lanes.  Work item = entries[blockIdx.x] = (lane, share, n_shares) x KV head.  The four warps of the
 // CTA take the 16-key tiles of the share round-robin, each through its own ring of cp.async stages (no
 // block-wide barrier inside the loop), keep their own running max / sum / output, and merge through shared
-// memory at the end.  n_shares == 1: the CTA writes the normalised output.  Otherwise it writes the
-// unnormalised partial for attn_combine_kernel.
+// memory at the end.  n_shares == 1: the CTA writes the normalised output.  Otherwise it writes its unnormalised
+// partial, and the CTA that arrives last at the lane's counter merges the shares.
 template <int D, int STAGES>
 __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
     constexpr int DP = D + 8;
@@ -307,7 +307,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
     // one 32-byte record per work item, so that nothing but the block table and the queries is a dependent load
     const int4 e0 = reinterpret_cast<const int4*>(a.entries)[2 * blockIdx.x];
     const int4 e1 = reinterpret_cast<const int4*>(a.entries)[2 * blockIdx.x + 1];
-    const int split = e0.y, n_splits = e0.z, start_pos = e0.w, table_off = e1.x, q_off = e1.y;
+    const int lane_id = e0.x, split = e0.y, n_splits = e0.z, start_pos = e0.w, table_off = e1.x, q_off = e1.y, first_entry = e1.z;
     const int ldq = a.ldq > 0 ? a.ldq : a.q_heads * D;
 
     // the group's query heads -> rows 0..g-1 of the A operand, the rest zero
@@ -502,6 +502,39 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
             }
         }
     }
+    if (n_splits > 1) {
+        // The lane's keys were shared out over several CTAs: the CTA that arrives last at the lane's counter adds
+        // the shares in share order (so the result does not depend on which one that is) and resets the counter.
+        __shared__ int s_last;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            int prev = atomicAdd(&a.counters[lane_id * a.kv_heads + kvh], 1);
+            s_last = prev == n_splits - 1 ? 1 : 0;
+            if (prev == n_splits - 1) a.counters[lane_id * a.kv_heads + kvh] = 0;
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            for (int idx = tid; idx < g * D; idx += 128) {
+                int item = idx / D, c = idx - item * D;
+                float m = -INFINITY;
+                for (int sp = 0; sp < n_splits; ++sp)
+                    m = fmaxf(m, __ldcg(a.part_ml + (((int64_t)(first_entry + sp) * a.kv_heads + kvh) * 16 + item) * 2));
+                float l = 0.f, o = 0.f;
+                for (int sp = 0; sp < n_splits; ++sp) {
+                    const int64_t ps = ((int64_t)(first_entry + sp) * a.kv_heads + kvh) * 16 + item;
+                    float ms = __ldcg(a.part_ml + ps * 2);
+                    if (ms != -INFINITY) {
+                        float f = __expf(ms - m);
+                        l += __ldcg(a.part_ml + ps * 2 + 1) * f;
+                        o += __ldcg(a.part_o + ps * D + c) * f;
+                    }
+                }
+                a.out[(int64_t)q_off * a.q_heads * D + (kvh * g + item) * D + c] = o / l;
+            }
+        }
+    }
 }
 
 // Merge the key shares of one-token lanes: grid (decode lane, kv head), one warp per query head of the group.
@@ -584,7 +617,7 @@ int attention_tc_warps(int q_heads, int kv_heads) { return q_heads / kv_heads >=
 
 int attention_tc_tile_rows(int q_heads, int kv_heads) { return 16 * attention_tc_warps(q_heads, kv_heads) / (q_heads / kv_heads); }
 
-int attention_tc_max_entries(int lanes, int kv_heads) { return lanes + kAttnTargetCtas / kv_heads + 1; }
+int attention_tc_max_entries(int lanes, int kv_heads) { return std::max(lanes, kAttnTargetCtas / std::max(1, kv_heads)) + 1; }
 
 void plan_attention_tc(const int32_t* start_pos, const int32_t* n_tokens, const int32_t* n_blocks, int lanes, int q_heads,
                        int kv_heads, AttnTcPlan& plan) {
@@ -592,21 +625,30 @@ void plan_attention_tc(const int32_t* start_pos, const int32_t* n_tokens, const 
     plan.entries.clear();
     plan.dec_lanes.clear();
     const int tile_rows = attention_tc_tile_rows(q_heads, kv_heads);
+    // One-token lanes: every CTA should walk about the same number of keys, and all CTAs should fit on the GPU at
+    // once.  Share size = total keys / CTA slots per KV head, raised until the shares of all lanes fit.
     int n_dec = 0;
-    for (int i = 0; i < lanes; ++i) n_dec += n_tokens[i] == 1 ? 1 : 0;
-    const int budget = std::max(1, kAttnTargetCtas / kv_heads / std::max(1, n_dec));
+    int64_t total_keys = 0;
+    for (int i = 0; i < lanes; ++i)
+        if (n_tokens[i] == 1) { ++n_dec; total_keys += start_pos[i] + 1; }
+    const int slots = std::max(n_dec, kAttnTargetCtas / std::max(1, kv_heads));
+    int share = (int)std::max<int64_t>(kAttnMinSplitKeys, (total_keys + slots - 1) / std::max(1, slots));
+    share = (share + 63) / 64 * 64;
+    auto shares_of = [&](int ctx) { return std::max(1, std::min(kAttnMaxSplits, (ctx + share - 1) / share)); };
+    for (;;) {
+        int64_t ctas = 0;
+        for (int i = 0; i < lanes; ++i)
+            if (n_tokens[i] == 1) ctas += shares_of(start_pos[i] + 1);
+        if (ctas <= slots || share > (1 << 20)) break;
+        share += 64;
+    }
     int q_off = 0, table_off = 0;
     for (int i = 0; i < lanes; q_off += n_tokens[i], table_off += n_blocks[i], ++i) {
         if (n_tokens[i] == 1) {
-            int ctx = start_pos[i] + 1;
-            int splits = std::max(1, std::min(std::min(budget, kAttnMaxSplits), (ctx + kAttnMinSplitKeys - 1) / kAttnMinSplitKeys));
-            if (splits > 1) {  // merged by the combine kernel
-                plan.dec_lanes.push_back(i);
-                plan.dec_lanes.push_back(plan.n_entries());
-                plan.dec_lanes.push_back(splits);
-            }
+            const int splits = shares_of(start_pos[i] + 1);
+            const int first = plan.n_entries();
             for (int sidx = 0; sidx < splits; ++sidx) {
-                const int32_t rec[8] = {i, sidx, splits, start_pos[i], table_off, q_off, 0, 0};
+                const int32_t rec[8] = {i, sidx, splits, start_pos[i], table_off, q_off, first, 0};
                 plan.entries.insert(plan.entries.end(), rec, rec + 8);
             }
         } else {

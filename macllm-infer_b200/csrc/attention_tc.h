@@ -15,7 +15,7 @@ struct AttnTcArgs {
     const uint32_t* tables = nullptr;
     const int32_t* cu_seqlens = nullptr;
     // work lists (device): prefill tiles (lane, first row); decode entries, 8 ints each, 32-byte aligned
-    // (lane, share, n_shares, start_pos, table offset, first packed row, 0, 0);
+    // (lane, share, n_shares, start_pos, table offset, first packed row, first entry of the lane, 0);
     // one-token lanes with more than one share (lane, first entry, n_splits)
     const int32_t* tiles = nullptr;
     const int32_t* entries = nullptr;
@@ -23,6 +23,7 @@ struct AttnTcArgs {
     int n_tiles = 0, n_entries = 0, n_dec_lanes = 0;
     float* part_o = nullptr;    // [n_entries][kv_heads][16][d]
     float* part_ml = nullptr;   // [n_entries][kv_heads][16][2]
+    int32_t* counters = nullptr;  // [lanes][kv_heads], zero before the first call; every call leaves them zero
     int q_heads = 0, kv_heads = 0, d = 0, block_tokens = 16, layers = 0, layer = 0;
     int64_t pool_blocks = 0;  // see kv_page_index
     int bt_shift = 0;         // log2(block_tokens), filled in by the launcher
@@ -41,7 +42,7 @@ int attention_tc_warps(int q_heads, int kv_heads);
 // least kAttnMinSplitKeys keys each, until about kAttnTargetCtas CTAs are in flight.
 constexpr int kAttnTargetCtas = 148 * 2;
 constexpr int kAttnMaxSplits = 16;
-constexpr int kAttnMinSplitKeys = 256;
+constexpr int kAttnMinSplitKeys = 128;
 struct AttnTcPlan {
     std::vector<int32_t> tiles, entries, dec_lanes;
     int n_tiles() const { return (int)tiles.size() / 2; }

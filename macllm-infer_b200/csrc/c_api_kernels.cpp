@@ -361,6 +361,9 @@ int32_t mk_k_attention_step(const mk_attn_case* c) {
             ta.n_dec_lanes = plan.n_dec_lanes();
             ta.part_o = part_o.as<float>();
             ta.part_ml = part_ml.as<float>();
+            DevBuf counters((size_t)std::max(lanes, 1) * c->kv_heads * 4);
+            counters.zero(nullptr);
+            ta.counters = counters.as<int32_t>();
             ta.q_heads = c->q_heads;
             ta.kv_heads = c->kv_heads;
             ta.d = d;

@@ -181,6 +181,8 @@ Model::Model(const std::string& gguf_path, const ModelConfig& cfg) : cfg_(cfg) {
         attn_max_entries_ = attention_tc_max_entries(B, ms_.kv_heads);
         attn_part_o_.alloc((size_t)attn_max_entries_ * ms_.kv_heads * 16 * ms_.head_dim * 4);
         attn_part_ml_.alloc((size_t)attn_max_entries_ * ms_.kv_heads * 16 * 2 * 4);
+        attn_counters_.alloc((size_t)B * ms_.kv_heads * 4);
+        attn_counters_.zero(stream_);
         // work lists: key-share entries (8 ints), prefill tiles (2 ints), split one-token lanes (3 ints)
         stage_bytes += ((size_t)(T + B) * 2 + (size_t)attn_max_entries_ * 8 + (size_t)B * 3) * 4 + 16;
     }
@@ -755,6 +757,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
             ta.n_dec_lanes = n_attn_dec;
             ta.part_o = attn_part_o_.as<float>();
             ta.part_ml = attn_part_ml_.as<float>();
+            ta.counters = attn_counters_.as<int32_t>();
             ta.q_heads = ms_.q_heads;
             ta.kv_heads = ms_.kv_heads;
             ta.d = d;

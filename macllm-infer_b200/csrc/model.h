@@ -117,7 +117,7 @@ private:
     DevBuf stage_dev_;
     DevBuf cu_, pos_, tok_lane_, slots_, last_, tile_lane_, tile_row_, ntiles_, err_;
     // tensor-core attention: split-KV partials of one-token lanes
-    DevBuf attn_part_o_, attn_part_ml_;
+    DevBuf attn_part_o_, attn_part_ml_, attn_counters_;
     bool attn_tc_ = false;
     // f16 weight images for wide ticks
     DevBuf argmax_scratch_;
