@@ -223,6 +223,66 @@ def run_step(eng_mod, model, w, prompts):
     return toks + gen, wall, st
 
 
+def tick_classes(eng_mod, model, w, prompts, weight_bytes_per_pass: float, kv_bytes_per_token: float, hbm_gbs: float) -> dict:
+    """One more (untimed) step driven tick by tick: device time and algorithmic HBM bytes per tick class.
+    A tick's algorithmic bytes = the weight bytes one pass touches + the K/V history its lanes attend to;
+    `hbm_frac` = those bytes / device time / measured copy bandwidth (the decode roofline of the metric)."""
+    eng = eng_mod.Engine(model, max_active_sequences=w["seqs"], scheduler_token_budget=w["budget"],
+                         prefill_token_quantum=w["quantum"], queue_capacity=w["seqs"] + 8)
+    eng.submit([eng_mod.Request(p, w["new_tokens"]) for p in prompts], atomic_batch=True)
+    ms = []
+    while eng.pending() > 0:
+        before = model.launch_count()
+        eng.step()
+        if model.launch_count() != before:  # a step that only delivers events runs no forward pass
+            ms.append(model.last_forward_ms())
+    trace = eng.trace()
+    eng.close()
+    out = {}
+    for t, dev_ms in zip(trace, ms):
+        toks = sum(n for _, _, n in t)
+        if toks == 0:
+            continue
+        cls = "decode" if toks == len(t) else ("mixed" if any(n == 1 for _, _, n in t) else "prefill")
+        kv = sum(sp + n for _, sp, n in t) * kv_bytes_per_token
+        a = out.setdefault(cls, dict(ticks=0, tokens=0, ms=0.0, bytes=0.0))
+        a["ticks"] += 1
+        a["tokens"] += toks
+        a["ms"] += dev_ms
+        a["bytes"] += weight_bytes_per_pass + kv
+    for a in out.values():
+        a["tokens_per_s"] = round(a["tokens"] / max(a["ms"], 1e-9) * 1e3, 1)
+        a["ms_per_tick"] = round(a["ms"] / a["ticks"], 3)
+        a["hbm_frac"] = round(a["bytes"] / max(a["ms"], 1e-9) / 1e6 / hbm_gbs, 4)
+        a["ms"] = round(a["ms"], 2)
+        del a["bytes"]
+    return out
+
+
+Q4K_SHAPES = [(2048, 2048), (256, 2048), (5632, 2048), (2048, 5632), (11008, 2048), (2048, 11008), (12288, 4096)]
+
+
+def microbench() -> None:
+    """Q4_K matmul micro-benchmark: achieved GB/s on the algorithmic bytes of the matrix (rows * cols * 144/256) for
+    the decode shapes of the first three configurations at 1, 4, 16 and 64 activation rows, on the path the model
+    picks for that many rows (integer GEMV up to 8 rows, streamed blocks above).  Operands resident, L2 flushed
+    before every launch, CUDA events around the launch.  One JSON line per shape."""
+    ops = importlib.import_module("macllm_infer_b200.ops")
+    capi = importlib.import_module("macllm_infer_b200._capi")
+    pk = peaks()
+    rng = np.random.default_rng(0)
+    for rows, cols in Q4K_SHAPES:
+        wq = ops.seed_tensor(0, 1, 0.02, capi.TYPE_Q4_K, rows, cols)
+        nbytes = rows * cols * 144 // 256
+        line = dict(kernel="q4k_matmul", rows=rows, cols=cols, weight_mb=round(nbytes / 1e6, 2), peak_gbs=pk["hbm_gbs"], peak_source=pk["source"])
+        for T in (1, 4, 16, 64):
+            x = rng.standard_normal((T, cols)).astype(np.float32)
+            path = capi.PATH_GEMV if T <= 8 else capi.PATH_STREAM
+            ms = ops.qmatmul_time(capi.TYPE_Q4_K, wq, rows, cols, x, path, 20)
+            line[f"T{T}"] = dict(us=round(ms * 1e3, 1), gbs=round(nbytes / ms / 1e6, 1), frac=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
+        print(json.dumps(line), flush=True)
+
+
 def cpu_baseline(w, path, budget_s: float, seqs_sample: int = 4) -> dict:
     """The oracle (a port of the reference's CPU path) on a bounded sample of the same workload: the
     first prefill tokens of the first sequences, one scheduler tick, all host threads."""
@@ -260,6 +320,7 @@ def main():
     # a shorter slice of the same workload for profiler captures (a number printed by such a run is not a bench value)
     ap.add_argument("--new-tokens", type=int, default=0, help="override the generated tokens per sequence")
     ap.add_argument("--no-profiled-step", action="store_true", help="skip the extra step that times every launch")
+    ap.add_argument("--microbench", action="store_true", help="Q4_K matmul GB/s on the decode shapes instead of the workload")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
     if args.new_tokens > 0:
@@ -276,6 +337,11 @@ def main():
                   prefill_quantum=w["quantum"], scheduler_token_budget=w["budget"], kv="f16 paged, 16-token blocks",
                   quant="Q4_K_M-shaped GGUF (Q4_K, Q6_K for attn_v and output)", parallelism=f"replicas x{world}",
                   l2="inputs larger than L2 (weights %.2f GB per pass)" % (seed.weight_bytes(spec)["per_token"] / 1e9))
+
+    if args.microbench:
+        if rank == 0:
+            microbench()
+        return
 
     if args.impl == "reference":
         # The reference is Rust on candle and cannot be built here (no cargo/rustc): the reference arm
@@ -368,6 +434,12 @@ def main():
                                              gbs=round(r["bytes"] / max(r["ms"], 1e-9) / 1e6, 1),
                                              tflops=round(r["flops"] / max(r["ms"], 1e-9) / 1e9, 2)) for r in prof_rows})
 
+    classes = None
+    if rank == 0 and not args.no_profiled_step:
+        wb = seed.weight_bytes(spec)
+        classes = tick_classes(eng_mod, model, w, prompts, float(wb["per_token"]), float(model.spec().kv_bytes_per_token),
+                               peaks()["hbm_gbs"])
+
     base = None
     if rank == 0 and not args.no_cpu_baseline:
         try:
@@ -382,7 +454,8 @@ def main():
                    data="synthetic", config=config, clocks=clocks,
                    e2e=dict(value=tokens_all / wall_max, unit=UNIT, h2d_bytes_per_step=(h2d1 - h2d0) // max(args.steps, 1),
                             d2h_bytes_per_step=(d2h1 - d2h0) // max(args.steps, 1)),
-                   gpu_launches=launches, ticks_per_step=ticks // max(args.steps, 1), roofline=roof, cpu_baseline=base)
+                   gpu_launches=launches, ticks_per_step=ticks // max(args.steps, 1), roofline=roof, tick_classes=classes,
+                   cpu_baseline=base)
         print(json.dumps(out))
     model.close()
     if dist is not None:

@@ -286,8 +286,11 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tc_kernel(AttnTcArgs a) {
 // block-wide barrier inside the loop), keep their own running max / sum / output, and merge through shared
 // memory at the end.  n_shares == 1: the CTA writes the normalised output.  Otherwise it writes its unnormalised
 // partial, and the CTA that arrives last at the lane's counter merges the shares.
-template <int D, int STAGES>
+// LOW8: at most eight query heads per KV head, so rows 8-15 of the A operand are zero and everything that concerns
+// them (half of the softmax and of the accumulator rescaling) is skipped.
+template <int D, int STAGES, bool LOW8>
 __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
+    constexpr int NH = LOW8 ? 1 : 2;  // accumulator row halves that can hold live rows
     constexpr int DP = D + 8;
     constexpr int KT = 16;
     constexpr int NT_O = D / 8;
@@ -343,13 +346,19 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
     const __half* kp = reinterpret_cast<const __half*>(a.k_pool);
     const __half* vp = reinterpret_cast<const __half*>(a.v_pool);
     __half* ring = rings + warp * RING_HALVES;
-    auto load_tile = [&](int i) {  // the warp's i-th tile into stage i % STAGES
+    uint32_t tile_blk = 0;
+    auto load_tile = [&](int i) {  // the warp's i-th tile into stage i % STAGES (called with i = 0, 1, 2, ... in order)
         __half* kd = ring + (i % STAGES) * 2 * KT * DP;
         __half* vd = kd + KT * DP;
         // 16 keys starting at a multiple of 16 lie in one page (block_tokens is a multiple of 16): one table
         // lookup, then the tile is one contiguous run of 16 * D halves in each pool
         const int pos0 = k_begin + (warp + 4 * i) * KT;
-        const int64_t blk = a.tables[table_off + (pos0 >> a.bt_shift)];
+        // the page ids of the warp's next 32 tiles sit in the lanes (fetched together, off the critical path)
+        if ((i & 31) == 0) {
+            const int t = i + lane;
+            tile_blk = t < my_tiles ? a.tables[table_off + ((k_begin + (warp + 4 * t) * KT) >> a.bt_shift)] : 0u;
+        }
+        const int64_t blk = __shfl_sync(0xffffffffu, tile_blk, i & 31);
         const int64_t src0 = ((kv_page_index(blk, a.layer, a.layers, a.pool_blocks) * a.kv_heads + kvh) * a.block_tokens +
                               (pos0 & (a.block_tokens - 1))) * (int64_t)D;
         const int n_valid = k_hi - pos0;  // keys of the tile inside the share
@@ -375,6 +384,12 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
         cp_async_commit();
     }
     __syncthreads();  // Qs complete
+    constexpr bool Q_IN_REGS = D <= 128;
+    uint32_t qf[Q_IN_REGS ? D / 16 : 1][4];
+    if (Q_IN_REGS) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) ldmatrix_x4(qf[Q_IN_REGS ? kk : 0], Qs + (lane & 15) * DP + kk * 16 + (lane >> 4) * 8);
+    }
 
     for (int i = 0; i < my_tiles; ++i) {
         if (i + STAGES - 1 < my_tiles) load_tile(i + STAGES - 1);
@@ -390,30 +405,33 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
             uint32_t af[4], bf[4];
-            ldmatrix_x4(af, Qs + (lane & 15) * DP + kk * 16 + (lane >> 4) * 8);
+            if (!Q_IN_REGS) ldmatrix_x4(af, Qs + (lane & 15) * DP + kk * 16 + (lane >> 4) * 8);
             ldmatrix_x4(bf, kt + ((lane & 7) + (lane >> 4) * 8) * DP + kk * 16 + ((lane >> 3) & 1) * 8);
-            mma16816(sc[0], af, bf[0], bf[1]);
-            mma16816(sc[1], af, bf[2], bf[3]);
+            mma16816(sc[0], Q_IN_REGS ? qf[Q_IN_REGS ? kk : 0] : af, bf[0], bf[1]);
+            mma16816(sc[1], Q_IN_REGS ? qf[Q_IN_REGS ? kk : 0] : af, bf[2], bf[3]);
         }
         const int tile_pos = k_begin + (warp + 4 * i) * KT;
+        // a tile that lies wholly inside the share needs no masking (rows without a query head hold zeros and are
+        // never stored)
+        const bool full_tile = tile_pos >= k_lo && tile_pos + KT <= k_hi;
         float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
+            for (int e = 0; e < 2 * NH; ++e) {
                 int h = e >> 1;
                 int pos = tile_pos + j * 8 + 2 * tq + (e & 1);
                 float v = sc[j][e] * a.scale;
                 if (a.softcap != 0.f) v = tanhf(v / a.softcap) * a.softcap;
-                bool vis = live_r[h] && pos >= k_lo && pos < k_hi;  // k_lo / k_hi already carry causality and the window
+                bool vis = full_tile || (live_r[h] && pos >= k_lo && pos < k_hi);  // k_lo / k_hi carry causality and the window
                 v = vis ? v : -INFINITY;
                 sc[j][e] = v;
                 tmax[h] = fmaxf(tmax[h], v);
             }
         }
-        float alpha[2], m_use[2];
+        float alpha[2] = {1.f, 1.f}, m_use[2] = {0.f, 0.f};
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < NH; ++h) {
             tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 1));
             tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 2));
             float m_new = fmaxf(m_run[h], tmax[h]);
@@ -425,15 +443,16 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
+            for (int e = 0; e < 2 * NH; ++e) {
                 int h = e >> 1;
                 float pe = sc[j][e] == -INFINITY ? 0.f : __expf(sc[j][e] - m_use[h]);
                 sc[j][e] = pe;
                 psum[h] += pe;
             }
+            if (LOW8) sc[j][2] = sc[j][3] = 0.f;
         }
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < NH; ++h) {
             psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], 1);
             psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], 2);
             l_run[h] = l_run[h] * alpha[h] + psum[h];
@@ -442,11 +461,13 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
         for (int j = 0; j < NT_O; ++j) {
             o_acc[j][0] *= alpha[0];
             o_acc[j][1] *= alpha[0];
-            o_acc[j][2] *= alpha[1];
-            o_acc[j][3] *= alpha[1];
+            if (!LOW8) {
+                o_acc[j][2] *= alpha[1];
+                o_acc[j][3] *= alpha[1];
+            }
         }
-        uint32_t pf[4] = {pack_half2(sc[0][0], sc[0][1]), pack_half2(sc[0][2], sc[0][3]), pack_half2(sc[1][0], sc[1][1]),
-                          pack_half2(sc[1][2], sc[1][3])};
+        uint32_t pf[4] = {pack_half2(sc[0][0], sc[0][1]), LOW8 ? 0u : pack_half2(sc[0][2], sc[0][3]), pack_half2(sc[1][0], sc[1][1]),
+                          LOW8 ? 0u : pack_half2(sc[1][2], sc[1][3])};
 #pragma unroll
         for (int j = 0; j < NT_O; j += 2) {
             uint32_t bf[4];
@@ -590,11 +611,13 @@ void launch_for_dim(const AttnTcArgs& a, int warps, cudaStream_t s) {
         constexpr size_t smem = (size_t)(16 + 4 * STAGES * 2 * 16) * (D + 8) * sizeof(__half);
         static bool configured = false;
         if (!configured) {
-            MK_CUDA(cudaFuncSetAttribute(attn_decode_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            MK_CUDA(cudaFuncSetAttribute(attn_decode_kernel<D, STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            MK_CUDA(cudaFuncSetAttribute(attn_decode_kernel<D, STAGES, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             configured = true;
         }
         dim3 grid((unsigned)a.n_entries, (unsigned)a.kv_heads);
-        launch_pdl(attn_decode_kernel<D, STAGES>, grid, dim3(128), smem, s, a);
+        if (a.q_heads / a.kv_heads <= 8) launch_pdl(attn_decode_kernel<D, STAGES, true>, grid, dim3(128), smem, s, a);
+        else launch_pdl(attn_decode_kernel<D, STAGES, false>, grid, dim3(128), smem, s, a);
         MK_LAUNCH_CHECK();
     }
     if (a.n_dec_lanes > 0) {  // lanes whose keys were shared out over several CTAs

@@ -506,6 +506,7 @@ void Model::build_qstream() {
     a_gs_.alloc((size_t)kQStreamMaxRows * (std::max(ms_.hidden, ms_.q_heads * ms_.head_dim) / 16) * 2);
     f_gs_.alloc((size_t)kQStreamMaxRows * (ms_.ffn / 16) * 2);
     MK_CUDA(cudaStreamSynchronize(stream_));
+    if (const char* e = std::getenv("MACLLM_B200_STREAM_MIN_ROWS")) qstream_min_rows_ = std::max(1, atoi(e));
     qstream_ = true;
 }
 
@@ -622,7 +623,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         prof_end();
     ++launches_;
 
-    const bool f16_T = cfg_.matmul_path != 1 && (cfg_.matmul_path == 2 || T > 8);
+    const bool f16_T = cfg_.matmul_path != 1 && (cfg_.matmul_path == 2 || T > 8 || (qstream_ && T >= qstream_min_rows_));
     const float* pending = nullptr;        // branch output not yet added to the residual stream
     const float* pending_post = nullptr;   // its sandwich post-norm weight, if any
     int pending_splits = 1;                // > 1: `pending` is that many split-K partials, T * H floats apart
@@ -661,6 +662,14 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
             v_splits = matmul_half(w.wv.half, xa, T, vp, QKVW, 1.f, 0.f, kMaxShares, v_partial_.as<float>(), v_partial_.size() / 4);
         } else if (w.qkv_half.ready && T >= hgemm_min_rows_ && xa.xh != nullptr) {
             matmul_half(w.qkv_half, xa, T, qp, QKVW, 1.f, 0.f);
+        } else if (w.qk_raw.size() > 0) {
+            // [wq; wk] share one buffer: one launch for both (their outputs are adjacent columns of the row)
+            DeviceWeight qk;
+            qk.w = w.wq.w;
+            qk.w.rows = w.wq.w.rows + w.wk.w.rows;
+            qk.w.bytes = w.wq.w.bytes + w.wk.w.bytes;
+            matmul(qk, xa, T, qp, QKVW, 1.f, 0.f);
+            matmul(w.wv, xa, T, vp, QKVW, 1.f, 0.f);
         } else {
             matmul(w.wq, xa, T, qp, QKVW, 1.f, 0.f);
             matmul(w.wk, xa, T, kp, QKVW, 1.f, 0.f);
@@ -821,6 +830,12 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
                 gu_splits = matmul_stream(w.qs_gu, xf, T, gp, 2 * ms_.ffn, kMaxShares);
             } else if (w.gu_half.ready && T >= hgemm_min_rows_ && xf.xh != nullptr) {
                 matmul_half(w.gu_half, xf, T, gp, 2 * ms_.ffn, 1.f, 0.f);
+            } else if (w.gu_raw.size() > 0) {
+                DeviceWeight gu;  // [gate; up] share one buffer: one launch for both
+                gu.w = w.gate.w;
+                gu.w.rows = w.gate.w.rows + w.up.w.rows;
+                gu.w.bytes = w.gate.w.bytes + w.up.w.bytes;
+                matmul(gu, xf, T, gp, 2 * ms_.ffn, 1.f, 0.f);
             } else {
                 matmul(w.gate, xf, T, gp, 2 * ms_.ffn, 1.f, 0.f);
                 matmul(w.up, xf, T, up, 2 * ms_.ffn, 1.f, 0.f);

@@ -48,7 +48,7 @@ struct ModelConfig {
     // 0 auto (integer GEMV for a few rows, in-kernel dequant GEMM for tens of rows, f16-image GEMM for wide
     // ticks when the image fits), 1 integer GEMV only, 2 in-kernel dequant GEMM whenever the shape allows,
     // 3 f16-image GEMM whenever more than 8 rows share a matrix, 4 like 0 but nothing falls back to the in-kernel
-    // dequant GEMM (f16 images for wide ticks, streamed Q4_K blocks for 9..64 rows)
+    // dequant GEMM (f16 images for wide ticks, streamed Q4_K blocks for 2..64 rows)
     int matmul_path = 0;
 };
 
@@ -129,7 +129,7 @@ private:
     bool qstream_ = false;
     DevBuf a_gs_, f_gs_;  // per-group activation sums for the streamed matmul
     DevBuf v_partial_;  // split-K shares of the V projection on streamed ticks
-    int qstream_min_rows_ = 9;
+    int qstream_min_rows_ = 2;  // one row stays on the integer GEMV
     int matmul_stream(const QStreamWeight& W, const ActQ& x, int T, float* y, int ldy, int max_splits);
     HgemmScratch hgemm_scratch() const;
     // Returns the number of K shares; more than one means the result is the sum of that many partials in the

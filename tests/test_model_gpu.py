@@ -150,7 +150,7 @@ def test_single_layer_models_match_tightly(pk, tmp_path_factory, fam):
 @pytest.mark.parametrize("matmul_path", [2, 3, 4, 0])
 def test_family_matches_oracle_on_the_tensor_core_path_with_f16_kv(pk, tmp_path_factory, fam, matmul_path):
     """The B200 configuration: f16 KV and tcgen05 matmuls (2: GGUF blocks dequantised in the kernel; 3: the f16
-    weight images with fused projections and split-K shares; 4: those plus streamed Q4_K blocks for 9..64 rows;
+    weight images with fused projections and split-K shares; 4: those plus streamed Q4_K blocks for 2..64 rows;
     0: the automatic mix); the oracle keeps f32 KV
     like the reference."""
     path, spec = make_checkpoint(pk, tmp_path_factory, fam)
