@@ -14,6 +14,7 @@
 // as stored.
 #include "kernels.h"
 #include "attention_tc.h"
+#include "quant_blocks.cuh"
 #include <algorithm>
 
 namespace mk {
@@ -497,7 +498,25 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
     }
     __syncthreads();
     const int64_t slot = ((int64_t)blockIdx.x * a.kv_heads + kvh) * 16;
-    for (int idx = tid; idx < g * D; idx += 128) {
+    // merged, normalised outputs of this (lane, KV head): g * D consecutive values of the lane's output row
+    auto finish = [&](auto&& value_of) {
+        const int64_t row = q_off;
+        const int col0 = kvh * g * D;
+        const bool fuse_quant = a.qout.qs != nullptr;  // uniform
+        if (!fuse_quant || a.out != nullptr) {
+            for (int idx = tid; idx < g * D; idx += 128) a.out[row * a.q_heads * D + col0 + idx] = value_of(idx);
+        }
+        if (fuse_quant) {
+            // one warp per 256-wide group, eight consecutive values per lane (g * D is a multiple of 256 here)
+            for (int grp = warp; grp < g * D / 256; grp += 4) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = value_of(grp * 256 + lane * 8 + i);
+                quant_group(v, lane, a.qkind, a.qout, row, a.q_heads * D, col0 / 256 + grp);
+            }
+        }
+    };
+    auto merged_local = [&](int idx, float& m_out, float& l_out) {
         int item = idx / D, c = idx - item * D;
         float m = -INFINITY;
 #pragma unroll
@@ -513,17 +532,27 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
                 o += ro[item * D + c] * f;
             }
         }
-        if (n_splits == 1) {
-            a.out[(int64_t)q_off * a.q_heads * D + (kvh * g + item) * D + c] = o / l;
-        } else {
+        m_out = m;
+        l_out = l;
+        return o;
+    };
+    if (n_splits == 1) {
+        finish([&](int idx) {
+            float m, l;
+            float o = merged_local(idx, m, l);
+            return o / l;
+        });
+    } else {
+        for (int idx = tid; idx < g * D; idx += 128) {
+            int item = idx / D, c = idx - item * D;
+            float m, l;
+            float o = merged_local(idx, m, l);
             a.part_o[(slot + item) * D + c] = o;
             if (c == 0) {
                 a.part_ml[(slot + item) * 2] = m;
                 a.part_ml[(slot + item) * 2 + 1] = l;
             }
         }
-    }
-    if (n_splits > 1) {
         // The lane's keys were shared out over several CTAs: the CTA that arrives last at the lane's counter adds
         // the shares in share order (so the result does not depend on which one that is) and resets the counter.
         __shared__ int s_last;
@@ -537,7 +566,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
         __syncthreads();
         if (s_last) {
             __threadfence();
-            for (int idx = tid; idx < g * D; idx += 128) {
+            finish([&](int idx) {
                 int item = idx / D, c = idx - item * D;
                 float m = -INFINITY;
                 for (int sp = 0; sp < n_splits; ++sp)
@@ -552,8 +581,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
                         o += __ldcg(a.part_o + ps * D + c) * f;
                     }
                 }
-                a.out[(int64_t)q_off * a.q_heads * D + (kvh * g + item) * D + c] = o / l;
-            }
+                return o / l;
+            });
         }
     }
 }

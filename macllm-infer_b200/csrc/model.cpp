@@ -717,6 +717,11 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         launch_rope_kv(ra, stream_);
         prof_end();
         ++launches_;
+        // the quantised image of the attention output feeds the output projection; on a tick of one-token lanes only,
+        // the attention kernel writes it itself
+        const int okind = act_kind_of(w.wo.w);
+        ActQ xo = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, AW, okind, f16_T, stream_T ? &a_gs_ : nullptr);
+        const bool fuse_attn_quant = attn_tc_ && n_attn_tiles == 0 && n_attn_entries > 0 && (AW / ms_.kv_heads) % 256 == 0;
         AttnArgs at;
         at.q = qp;
         at.ldq = QKVW;
@@ -777,6 +782,11 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
             ta.scale = ls.scale;
             ta.softcap = ls.softcap;
             ta.window = ls.window;
+            if (fuse_attn_quant) {
+                ta.qout = xo;
+                ta.qkind = okind;
+                ta.out = nullptr;  // nothing reads the f32 rows of a pure decode tick
+            }
             launches_ += launch_paged_attention_tc(ta, stream_);
         } else {
             launch_paged_attention(at, stream_);
@@ -784,18 +794,18 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         }
         prof_end();
         // output projection
-        int okind = act_kind_of(w.wo.w);
-        ActQ xo = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, AW, okind, f16_T, stream_T ? &a_gs_ : nullptr);
-        NormQuantArgs no;
-        no.h = attn_.as<float>();
-        no.rows = T;
-        no.dim = AW;
-        no.act_kind = okind;
-        no.out = xo;
-        prof_begin(KC_NORM_QUANT, 5.0 * T * AW, 0);
-        launch_add_norm_quant(no, stream_);
-        prof_end();
-        ++launches_;
+        if (!fuse_attn_quant) {
+            NormQuantArgs no;
+            no.h = attn_.as<float>();
+            no.rows = T;
+            no.dim = AW;
+            no.act_kind = okind;
+            no.out = xo;
+            prof_begin(KC_NORM_QUANT, 5.0 * T * AW, 0);
+            launch_add_norm_quant(no, stream_);
+            prof_end();
+            ++launches_;
+        }
         // split-K shares of the two long-K projections are summed by the residual kernel that consumes them
         int wo_splits = 1;
         if (stream && xo.gs != nullptr) wo_splits = matmul_stream(w.qs_o, xo, T, proj_.as<float>(), H, kMaxShares);

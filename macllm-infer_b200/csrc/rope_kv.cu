@@ -47,6 +47,7 @@ __global__ void __launch_bounds__(RK_WARPS * 32) rope_kv_kernel(RopeKvArgs a) {
     if ((d & 127) == 0 && ((reinterpret_cast<uintptr_t>(src) | (uintptr_t)(part_stride * 4)) & 15) == 0) {
         for (int i = lane * 4; i < d; i += 128) {
             float4 v = *reinterpret_cast<const float4*>(src + i);
+#pragma unroll 4
             for (int sp = 1; sp < n_parts; ++sp) {
                 float4 w = *reinterpret_cast<const float4*>(src + (int64_t)sp * part_stride + i);
                 v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
