@@ -499,21 +499,29 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
     __syncthreads();
     const int64_t slot = ((int64_t)blockIdx.x * a.kv_heads + kvh) * 16;
     // merged, normalised outputs of this (lane, KV head): g * D consecutive values of the lane's output row
+    // (all threads of the CTA call this together; the query tile is dead by now and lends its shared memory: g * D
+    // floats fit in it for up to eight query heads per KV head)
+    float* stage = reinterpret_cast<float*>(Qs);
     auto finish = [&](auto&& value_of) {
         const int64_t row = q_off;
         const int col0 = kvh * g * D;
         const bool fuse_quant = a.qout.qs != nullptr;  // uniform
-        if (!fuse_quant || a.out != nullptr) {
+        if (!fuse_quant) {
             for (int idx = tid; idx < g * D; idx += 128) a.out[row * a.q_heads * D + col0 + idx] = value_of(idx);
+            return;
         }
-        if (fuse_quant) {
-            // one warp per 256-wide group, eight consecutive values per lane (g * D is a multiple of 256 here)
-            for (int grp = warp; grp < g * D / 256; grp += 4) {
-                float v[8];
+        for (int idx = tid; idx < g * D; idx += 128) {
+            float v = value_of(idx);
+            stage[idx] = v;
+            if (a.out != nullptr) a.out[row * a.q_heads * D + col0 + idx] = v;
+        }
+        __syncthreads();
+        // one warp per 256-wide group, eight consecutive values per lane (g * D is a multiple of 256 here)
+        for (int grp = warp; grp < g * D / 256; grp += 4) {
+            float v[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = value_of(grp * 256 + lane * 8 + i);
-                quant_group(v, lane, a.qkind, a.qout, row, a.q_heads * D, col0 / 256 + grp);
-            }
+            for (int i = 0; i < 8; ++i) v[i] = stage[grp * 256 + lane * 8 + i];
+            quant_group(v, lane, a.qkind, a.qout, row, a.q_heads * D, col0 / 256 + grp);
         }
     };
     auto merged_local = [&](int idx, float& m_out, float& l_out) {

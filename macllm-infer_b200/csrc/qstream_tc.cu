@@ -58,7 +58,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
-        __nanosleep(40);  // many warps wait at once here: leave the issue slots to the ones that have work
     }
     return false;
 }
