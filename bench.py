@@ -56,9 +56,9 @@ WORKLOADS = {
 # summaries with the commands are profiles/hgemm_tc_kernel_prefill_gate_up.md, qstream_tc_kernel_decode_gate_up.md and
 # attn_decode_kernel_64_lanes.md).  The roofline block scales the live per-launch algorithmic bytes by these ratios.
 NCU_TRAFFIC_RATIO = {
-    "hgemm_tc": (498.9 + 145.5) / (90.2 + 8.4 + 180.4),   # the weight image is re-read about five times, outputs partly stay in L2
+    "hgemm_tc": (98.7 + 132.9) / (90.2 + 8.4 + 180.4),    # every operand once; part of the f32 output is still in L2 at kernel end
     "qstream_tc": 25.69 / (25.36 + 0.26 + 5.64),          # weights once; the partial sums never leave L2
-    "paged_attention": (76.97 + 2.64) / (72.4 + 4.2),
+    "paged_attention": (77.0 + 2.4) / (72.4 + 4.2),
 }
 
 
