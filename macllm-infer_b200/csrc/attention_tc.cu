@@ -673,7 +673,9 @@ bool attention_tc_supported(int q_heads, int kv_heads, int head_dim, int block_t
            q_heads == g * kv_heads;
 }
 
-int attention_tc_warps(int q_heads, int kv_heads) { return q_heads / kv_heads >= 4 ? (q_heads / kv_heads == 8 ? 8 : 4) : 4; }
+// Eight warps (128 (row, head) items per CTA) for groups of eight query heads, else four: with four heads per group
+// eight warps measured slower (fewer, longer CTAs) than four.
+int attention_tc_warps(int q_heads, int kv_heads) { return q_heads / kv_heads == 8 ? 8 : 4; }
 
 int attention_tc_tile_rows(int q_heads, int kv_heads) { return 16 * attention_tc_warps(q_heads, kv_heads) / (q_heads / kv_heads); }
 
