@@ -231,7 +231,7 @@ struct QsSmem {
 
 template <int BN>
 __global__ void __launch_bounds__(QS_THREADS, 1)
-qstream_tc_kernel(const uint8_t* __restrict__ w_tiled, const __grid_constant__ CUtensorMap tm_x,
+qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                   const __grid_constant__ CUtensorMap tm_gs, QsParams p) {
     using L = QsSmem<BN>;
     extern __shared__ uint8_t qs_smem_raw[];
@@ -304,8 +304,8 @@ qstream_tc_kernel(const uint8_t* __restrict__ w_tiled, const __grid_constant__ C
                 const uint32_t st = i % QS_RAW_STAGES, ph = (i / QS_RAW_STAGES) & 1;
                 if (!mbar_wait(&raw_empty[st], ph ^ 1, QS_SPIN_LIMIT)) { atomicExch(p.status, 22); break; }
                 mbar_expect_tx(&raw_full[st], (uint32_t)QS_RAW_BYTES);
-                // units are stored one after the other, 128 rows x 144 bytes each: one contiguous copy
-                bulk_load(raw_ring + (size_t)st * QS_RAW_BYTES, w_tiled + (size_t)(u0 + i) * QS_RAW_BYTES, (uint32_t)QS_RAW_BYTES, &raw_full[st]);
+                // units are stored one after the other, 18 KiB each: fetched as one box of 144 full 128-byte lines
+                tma_load_2d(raw_ring + (size_t)st * QS_RAW_BYTES, &tm_w, 0, (u0 + i) * (QS_RAW_BYTES / 128), &raw_full[st]);
             }
         }
     } else if (warp == 2) {
@@ -476,14 +476,14 @@ __global__ void retile_q4k_kernel(const uint4* src, int64_t rows, int nb, uint4*
 }
 
 template <int BN>
-void launch_qs(const uint8_t* w_tiled, const CUtensorMap& tx, const CUtensorMap& tg, const QsParams& p, int ctas, cudaStream_t s) {
+void launch_qs(const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& tg, const QsParams& p, int ctas, cudaStream_t s) {
     constexpr size_t smem = QsSmem<BN>::TOTAL;
     static bool configured = false;
     if (!configured) {
         MK_CUDA(cudaFuncSetAttribute(qstream_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
-    launch_pdl(qstream_tc_kernel<BN>, dim3(ctas), dim3(QS_THREADS), smem, s, w_tiled, tx, tg, p);
+    launch_pdl(qstream_tc_kernel<BN>, dim3(ctas), dim3(QS_THREADS), smem, s, tw, tx, tg, p);
     MK_LAUNCH_CHECK();
 }
 
@@ -500,6 +500,8 @@ void build_qstream_weight(const void* q4k_blocks, int64_t rows, int64_t cols, QS
     retile_q4k_kernel<<<(unsigned)((chunks + 255) / 256), 256, 0, s>>>(reinterpret_cast<const uint4*>(q4k_blocks), rows, nb,
                                                                         out.tiled.as<uint4>(), chunks);
     MK_LAUNCH_CHECK();
+    // the unit-major copy seen as rows of 128 bytes: one unit = one box of 144 rows
+    encode_tma_2d(out.tmap, true, out.tiled.ptr(), 128, (uint64_t)row_tiles * nb * (QS_RAW_BYTES / 128), 128, 128, QS_RAW_BYTES / 128, false);
     out.ready = true;
 }
 
@@ -566,8 +568,9 @@ int launch_qstream_tc(const QStreamWeight& W, const __half* xh, const __half* gs
     p.slots = pl.slots;
     p.partial = partial;
     p.status = status;
-    if (pl.bn == 32) launch_qs<32>(W.tiled.as<uint8_t>(), tx, tg, p, pl.ctas, s);
-    else launch_qs<64>(W.tiled.as<uint8_t>(), tx, tg, p, pl.ctas, s);
+    const CUtensorMap& tw = *reinterpret_cast<const CUtensorMap*>(W.tmap);
+    if (pl.bn == 32) launch_qs<32>(tw, tx, tg, p, pl.ctas, s);
+    else launch_qs<64>(tw, tx, tg, p, pl.ctas, s);
     return pl.slots;
 }
 

@@ -11,6 +11,7 @@ namespace mk {
 struct QStreamWeight {
     DevBuf tiled;
     int64_t rows = 0, cols = 0;
+    alignas(64) unsigned char tmap[128] = {};  // TMA descriptor of the copy as rows of 128 bytes, boxes of one unit
     bool ready = false;
 };
 

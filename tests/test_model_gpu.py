@@ -228,5 +228,71 @@ def test_prefix_cache_restore_equals_cold_prefill(pk, tmp_path_factory):
     del s3
 
 
+def test_full_size_smollm3_properties(pk, tmp_path_factory):
+    """The headline configuration at its real size (SmolLM3-3B shape: 36 layers, 2048 wide, 16/4 heads of 128, vocabulary
+    128 256, Q4_K_M-shaped mix, f16 KV, automatic matmul paths), where the oracle is too slow to run: properties that
+    need no oracle.  (1) Determinism: the same batch twice gives bit-identical logits and tokens - no atomics or
+    scheduling-dependent reduction order anywhere on the path.  (2) Chunking a prompt at a block boundary or inside a
+    block changes the last-token logits only within the reassociation envelope of the arithmetic.  (3) A lane computed
+    inside a ragged batch (streamed matmul, decode attention) agrees with the same lane computed alone (integer GEMV)
+    within that envelope, and the KV pool ends where it started."""
+    seed, eng = pk["seed"], pk["eng"]
+    spec = seed.CONFIGS["smollm3-3b"]
+    path = tmp_path_factory.mktemp("full") / "smollm3-3b.gguf"
+    seed.write_seed_gguf(path, spec, seed=0)
+    model = eng.Model.load_gguf(path, kv_dtype="f16", matmul_path=0, max_batch_tokens=512, max_batch_lanes=8, kv_capacity_tokens=8192)
+    rng = np.random.default_rng(11)
+    prompts = [rng.integers(3, spec.vocab, size=n) for n in (200, 33, 1, 120)]
+    free0 = model.pool_stats()
+
+    def run_batch():
+        ss = [model.new_session() for _ in prompts]
+        logits, toks = model.forward_batch([(s, p, 0) for s, p in zip(ss, prompts)])
+        # two decode ticks on top, all four lanes one token each
+        outs = [logits.copy()]
+        cur = [int(t) for t in toks]
+        for step in range(2):
+            logits, toks = model.forward_batch([(s, [c], len(p) + step) for s, p, c in zip(ss, prompts, cur)])
+            outs.append(logits.copy())
+            cur = [int(t) for t in toks]
+        for s in ss:
+            s.clear()
+            s.close()
+        return outs, cur
+
+    a, ta = run_batch()
+    b, tb = run_batch()
+    assert ta == tb
+    for x, y in zip(a, b):
+        assert np.array_equal(x, y)
+    assert np.isfinite(a[0]).all() and float(np.abs(a[0]).max()) > 0.0
+
+    # (2) chunked prefill of the 200-token prompt: 512-wide one shot vs 64 + 136 vs 50 + 150
+    ref = a[0][0]
+    scale = float(np.abs(ref).max())
+    for first in (64, 50):
+        s = model.new_session()
+        model.forward_batch([(s, prompts[0][:first], 0)], want_logits=False)
+        logits, _ = model.forward_batch([(s, prompts[0][first:], first)])
+        cos = float(logits[0] @ ref / np.sqrt((logits[0] @ logits[0]) * (ref @ ref)))
+        # 36 layers of 8-bit re-quantisation: two valid evaluation orders of the reference arithmetic itself drift to
+        # cosine 0.9995 at 8 layers (1 - cos grows with depth); hold the chunked run to 0.985
+        assert cos > 0.985 and np.max(np.abs(logits[0] - ref)) < 0.25 * max(scale, 1.0), (first, cos)
+        s.clear()
+        s.close()
+
+    # (3) the 33-token lane alone
+    s = model.new_session()
+    logits, _ = model.forward_batch([(s, prompts[1], 0)])
+    cos = float(logits[0] @ a[0][1] / np.sqrt((logits[0] @ logits[0]) * (a[0][1] @ a[0][1])))
+    assert cos > 0.985, cos
+    s.clear()
+    s.close()
+    model.synchronize()
+    after = model.pool_stats()
+    for key in ("live_blocks", "reserved_blocks", "retired_blocks", "shared_blocks", "live_references"):
+        assert after[key] == free0[key] == 0, (key, after)
+
+
 def test_no_cpu_fallback_symbols_are_loaded(pk):
     assert pk["capi"].lib().mk_device_count() >= 1
