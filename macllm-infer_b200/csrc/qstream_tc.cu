@@ -328,30 +328,38 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         // ---- MMA issuer
         if (lane == 0) {
             const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(QS_BM >> 4) << 24);
+            // every descriptor this lane will ever need, built once: the issue loop below is a single thread's
+            // dependent instruction stream, and anything computed per MMA there delays the tensor cores
+            uint64_t a_desc[2], e_adesc[2], b_desc[QS_X_STAGES][4], e_bdesc[QS_X_STAGES];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                a_desc[h] = make_nosw_desc(smem_u32(a_slots + h * QS_A_SLOT_BYTES), QS_A_LBO, 128);
+                e_adesc[h] = make_nosw_desc(smem_u32(extras + h * L::EXTRA_BYTES), QS_A_LBO, 128);
+            }
+#pragma unroll
+            for (int xs = 0; xs < QS_X_STAGES; ++xs) {
+                const uint32_t xb_addr = smem_u32(x_ring + (size_t)xs * L::X_BYTES);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) b_desc[xs][q] = make_sw128_desc(xb_addr + q * BN * 128);
+                e_bdesc[xs] = make_nosw_desc(xb_addr + 4 * BN * 128, BN * 16, 128);
+            }
+            constexpr uint64_t A_K_STEP = (2 * QS_A_LBO) >> 4;  // two 16-byte K chunks further, in descriptor units
             bool ok = true;
             for (int i = 0; i < n_local && ok; ++i) {
                 const uint32_t set = i & 1, aph = (i >> 1) & 1;
                 const uint32_t xs = i % QS_X_STAGES, xph = (i / QS_X_STAGES) & 1;
                 if (!mbar_wait(&acc_empty[set], aph ^ 1, QS_SPIN_LIMIT)) { atomicExch(p.status, 23); break; }
                 if (!mbar_wait(&x_full[xs], xph, QS_SPIN_LIMIT)) { atomicExch(p.status, 24); break; }
-                const uint32_t xb_addr = smem_u32(x_ring + (size_t)xs * L::X_BYTES);
                 const uint32_t d_main = tmem_base + set * 2 * BN, d_mins = d_main + BN;
                 for (int half = 0; half < 2; ++half) {
                     if (!mbar_wait(&a_full[half], (uint32_t)(i & 1), QS_SPIN_LIMIT)) { atomicExch(p.status, 25); ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_addr = smem_u32(a_slots + half * QS_A_SLOT_BYTES);
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        const uint64_t adesc = make_nosw_desc(a_addr + k * 2 * QS_A_LBO, QS_A_LBO, 128);
-                        const uint64_t bdesc = make_sw128_desc(xb_addr + (half * 2 + (k >> 2)) * BN * 128) + (uint64_t)(2 * (k & 3));
-                        umma_f16(d_main, adesc, bdesc, idesc, (half > 0 || k > 0) ? 1u : 0u);
-                    }
-                    if (half == 0) {
-                        // the group minimums against the group sums of the activations (head and tail): one K = 16 step
-                        const uint64_t adesc = make_nosw_desc(smem_u32(extras + (i & 1) * L::EXTRA_BYTES), QS_A_LBO, 128);
-                        const uint64_t bdesc = make_nosw_desc(xb_addr + 4 * BN * 128, BN * 16, 128);
-                        umma_f16(d_mins, adesc, bdesc, idesc, 0u);
-                    }
+                    for (int k = 0; k < 8; ++k)
+                        umma_f16(d_main, a_desc[half] + A_K_STEP * k, b_desc[xs][half * 2 + (k >> 2)] + (uint64_t)(2 * (k & 3)), idesc,
+                                 (half > 0 || k > 0) ? 1u : 0u);
+                    // the group minimums against the group sums of the activations (head and tail): one K = 16 step
+                    if (half == 0) umma_f16(d_mins, e_adesc[i & 1], e_bdesc[xs], idesc, 0u);
                     umma_commit(&a_empty[half]);
                 }
                 if (ok) {
