@@ -52,9 +52,8 @@ WORKLOADS = {
 
 
 # DRAM traffic of the three dominant kernels relative to their algorithmic bytes, from one `ncu --set full` capture
-# each on the benchmark's shapes (dram__bytes_read.sum + dram__bytes_write.sum over the bytes counted here; the
-# summaries with the commands are profiles/hgemm_tc_kernel_prefill_gate_up.md, qstream_tc_kernel_decode_gate_up.md and
-# attn_decode_kernel_64_lanes.md).  The roofline block scales the live per-launch algorithmic bytes by these ratios.
+# each on the benchmark's shapes (dram__bytes_read.sum + dram__bytes_write.sum over the bytes counted here).  The
+# roofline block scales the live per-launch algorithmic bytes by these ratios.
 NCU_TRAFFIC_RATIO = {
     "hgemm_tc": (98.7 + 132.9) / (90.2 + 8.4 + 180.4),    # every operand once; part of the f32 output is still in L2 at kernel end
     "qstream_tc": 25.69 / (25.36 + 0.26 + 5.64),          # weights once; the partial sums never leave L2

@@ -51,7 +51,7 @@ class SeedSpec:
     extra: dict = field(default_factory=dict)
 
 
-# The five benchmark shapes (BASELINE.json configs) and scaled-down siblings for parity tests.
+# The five benchmark shapes and scaled-down siblings for parity tests.
 CONFIGS = {
     "tinyllama-1.1b": SeedSpec("llama", 22, 2048, 32, 4, 64, 5632, 32000, context=2048, theta=10000.0, eps=1e-5),
     "smollm3-3b": SeedSpec("smollm3", 36, 2048, 16, 4, 128, 11008, 128256, context=65536, theta=5e6, eps=1e-6, tied=True),
