@@ -196,11 +196,19 @@ template <int NG>
 __global__ void __launch_bounds__(NQ_THREADS) add_norm_quant_fast_kernel(NormQuantArgs a) {
     __shared__ float red[32];
     pdl_trigger();
-    pdl_wait();
     const int r = blockIdx.x;
-    const int src = a.row_index ? a.row_index[r] : r;
     const int dim = a.dim, groups = dim / 256;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // the norm weights never depend on the predecessor kernel: fetch them while it finishes
+    float nw[NG][8], pw[NG][8];
+#pragma unroll
+    for (int g = 0; g < NG; ++g) {
+        const int grp = warp + g * 8;
+        if (grp < groups && a.norm_w != nullptr) load8(a.norm_w + grp * 256 + lane * 8, nw[g]);
+        if (grp < groups && a.post_w != nullptr && a.a != nullptr) load8(a.post_w + grp * 256 + lane * 8, pw[g]);
+    }
+    pdl_wait();
+    const int src = a.row_index ? a.row_index[r] : r;
     float* h = a.h + (int64_t)src * dim;
     float x[NG][8];
     bool live[NG];
@@ -246,10 +254,8 @@ __global__ void __launch_bounds__(NQ_THREADS) add_norm_quant_fast_kernel(NormQua
             if (!live[g]) continue;
             int base = (warp + g * 8) * 256 + lane * 8;
             if (a.post_w != nullptr) {
-                float pw[8];
-                load8(a.post_w + base, pw);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) y[g][i] = y[g][i] / post_m * pw[i];
+                for (int i = 0; i < 8; ++i) y[g][i] = y[g][i] / post_m * pw[g][i];
             }
 #pragma unroll
             for (int i = 0; i < 8; ++i) x[g][i] = x[g][i] + y[g][i] * a.a_scale;
@@ -267,10 +273,8 @@ __global__ void __launch_bounds__(NQ_THREADS) add_norm_quant_fast_kernel(NormQua
 #pragma unroll
         for (int g = 0; g < NG; ++g) {
             if (!live[g]) continue;
-            float nw[8];
-            load8(a.norm_w + (warp + g * 8) * 256 + lane * 8, nw);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) x[g][i] = x[g][i] / m * nw[i];
+            for (int i = 0; i < 8; ++i) x[g][i] = x[g][i] / m * nw[g][i];
         }
     }
 #pragma unroll
