@@ -74,6 +74,11 @@ typedef struct mk_load_config {
     int32_t max_batch_tokens;        /* largest packed token count of one forward */
     int32_t max_batch_lanes;         /* largest lane count of one forward */
     int32_t matmul_path;             /* MK_PATH_AUTO / MK_PATH_GEMV / MK_PATH_TENSOR / MK_PATH_HALF / MK_PATH_STREAM */
+    /* Expert parallelism of a sparse-MoE model (no counterpart in the reference, which runs every expert of
+     * SparseMoeFeedForward::forward, src/decoder.rs:394-441, on one device): this process loads experts
+     * [ep_rank, ep_rank + 1) * expert_count / ep_size.  ep_size 0 or 1: every expert is loaded here. */
+    int32_t ep_rank;
+    int32_t ep_size;
 } mk_load_config;
 
 /* CausalLm::runtime_spec (src/architecture.rs:312-316,1039). */
@@ -131,6 +136,14 @@ int32_t mk_model_load_gguf(const char* path, const mk_load_config* cfg, mk_model
  * makes that forward (0-based) fail, to exercise rollback. */
 int32_t mk_model_new_fake(int32_t vocab, int32_t max_context, const mk_load_config* cfg, int64_t fail_forward_at, mk_model** out);
 int32_t mk_model_free(mk_model* m);
+/* Expert parallelism, one process per GPU.  Rank 0 calls mk_ep_unique_id (MK_EP_ID_BYTES bytes out) and passes the
+ * id to the other ranks out of band; then every rank calls mk_model_ep_init on its model (loaded with the same
+ * ep_size and its own ep_rank) - a collective that returns once all ranks have joined.  From then on every rank must
+ * run the same forwards on the same lanes and tokens, in the same order: each MoE layer exchanges the ranks' partial
+ * sums (one NCCL all-gather over NVLink) and adds them in rank order, so all ranks hold the same logits. */
+#define MK_EP_ID_BYTES 128
+int32_t mk_ep_unique_id(uint8_t* id_out);
+int32_t mk_model_ep_init(mk_model* m, const uint8_t* id);
 int32_t mk_model_spec(mk_model* m, mk_runtime_spec* out);
 
 /* CausalLm::new_session / CausalLmSession::{clear_cache, cache_len} (src/architecture.rs:803-833,1074). */

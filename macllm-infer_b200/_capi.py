@@ -29,7 +29,8 @@ class KvExhausted(MkError):
 class LoadConfig(C.Structure):
     _fields_ = [("device_ordinal", C.c_int32), ("block_tokens", C.c_int32), ("slab_blocks", C.c_int32),
                 ("kv_capacity_tokens", C.c_int64), ("prefix_capacity_tokens", C.c_int64), ("kv_dtype", C.c_int32),
-                ("max_batch_tokens", C.c_int32), ("max_batch_lanes", C.c_int32), ("matmul_path", C.c_int32)]
+                ("max_batch_tokens", C.c_int32), ("max_batch_lanes", C.c_int32), ("matmul_path", C.c_int32),
+                ("ep_rank", C.c_int32), ("ep_size", C.c_int32)]
 
 
 class RuntimeSpec(C.Structure):
@@ -112,6 +113,8 @@ SIGNATURES = {
     "mk_model_load_gguf": (_i32, [C.c_char_p, C.POINTER(LoadConfig), C.POINTER(P)]),
     "mk_model_new_fake": (_i32, [_i32, _i32, C.POINTER(LoadConfig), _i64, C.POINTER(P)]),
     "mk_model_free": (_i32, [P]),
+    "mk_ep_unique_id": (_i32, [P]),
+    "mk_model_ep_init": (_i32, [P, P]),
     "mk_model_spec": (_i32, [P, C.POINTER(RuntimeSpec)]),
     "mk_session_new": (_i32, [P, C.POINTER(P)]),
     "mk_session_free": (_i32, [P]),

@@ -72,6 +72,10 @@ ModelConfig to_model_config(const mk_load_config* cfg) {
     if (cfg->max_batch_tokens > 0) c.max_batch_tokens = cfg->max_batch_tokens;
     if (cfg->max_batch_lanes > 0) c.max_batch_lanes = cfg->max_batch_lanes;
     c.matmul_path = cfg->matmul_path;
+    if (cfg->ep_size > 1) {
+        c.ep_size = cfg->ep_size;
+        c.ep_rank = cfg->ep_rank;
+    }
     return c;
 }
 
@@ -104,6 +108,21 @@ int32_t mk_model_new_fake(int32_t vocab, int32_t max_context, const mk_load_conf
 
 int32_t mk_model_free(mk_model* m) {
     return guarded([&] { delete m; });
+}
+
+int32_t mk_ep_unique_id(uint8_t* id_out) {
+    return guarded([&] {
+        require_device();
+        EpComm::unique_id(id_out);
+    });
+}
+
+int32_t mk_model_ep_init(mk_model* m, const uint8_t* id) {
+    return guarded([&] {
+        Model* model = dynamic_cast<Model*>(m->lm.get());
+        if (model == nullptr) throw std::runtime_error("mk_model_ep_init needs a GGUF model");
+        model->ep_init(id);
+    });
 }
 
 int32_t mk_model_spec(mk_model* m, mk_runtime_spec* out) {

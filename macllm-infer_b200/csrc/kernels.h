@@ -145,9 +145,12 @@ void launch_moe_route(const float* logits, int T, int experts, int k, int32_t* s
 void launch_moe_group(const int32_t* sel_experts, int T, int k, int experts, int32_t* offsets, int32_t* pos_of_pair,
                       int32_t* token_of_pos, cudaStream_t s);
 // out[t] = sum over the token's k choices in ascending expert order of weight * expert_out[pos]
-// (the index_add order of SparseMoeFeedForward::forward, src/decoder.rs:424-439).
+// (the index_add order of SparseMoeFeedForward::forward, src/decoder.rs:424-439).  Only experts in [e_lo, e_hi) are
+// read and added: the whole range on one GPU, one rank's experts under expert parallelism.
 void launch_moe_combine(const float* expert_out, const int32_t* sel_experts, const float* sel_weights,
-                        const int32_t* pos_of_pair, int T, int k, int hidden, float* out, cudaStream_t s);
+                        const int32_t* pos_of_pair, int T, int k, int hidden, int e_lo, int e_hi, float* out, cudaStream_t s);
+// Expert parallelism: out[i] = sum over ranks r = 0, 1, ... (in that order) of gathered[r * count + i].
+void launch_ep_sum(const float* gathered, int ranks, int64_t count, float* out, cudaStream_t s);
 
 // Small helpers
 void launch_add_inplace(float* h, const float* a, float scale, int64_t n, cudaStream_t s);

@@ -85,6 +85,11 @@ Model::Model(const std::string& gguf_path, const ModelConfig& cfg) : cfg_(cfg) {
     MK_CUDA(cudaSetDevice(cfg.device));
     GgufFile f(gguf_path);
     ms_ = model_spec_from_gguf(f);
+    if (cfg.ep_size > 1) {
+        if (ms_.experts <= 0) throw std::runtime_error("expert parallelism asked for a model without experts");
+        if (cfg.ep_rank < 0 || cfg.ep_rank >= cfg.ep_size) throw std::runtime_error("ep_rank out of range");
+        if (ms_.experts % cfg.ep_size != 0) throw std::runtime_error("expert count is not a multiple of ep_size");
+    }
     if (ms_.head_dim > 256 || ms_.head_dim % 4 != 0) throw std::runtime_error("head_dim must be a multiple of 4, at most 256");
     spec_.vocab = ms_.vocab;
     spec_.max_context = ms_.max_context;
@@ -144,6 +149,13 @@ Model::Model(const std::string& gguf_path, const ModelConfig& cfg) : cfg_(cfg) {
         e_gate_.alloc((size_t)P * fw * 4);
         e_up_.alloc((size_t)P * fw * 4);
         e_down_.alloc((size_t)P * ms_.hidden * 4);
+        if (cfg_.ep_size > 1) {
+            // rows of experts held elsewhere are never written here; keep them finite for the row-wise kernels
+            e_gate_.zero(stream_);
+            e_up_.zero(stream_);
+            ep_partial_.alloc((size_t)T * ms_.hidden * 4);
+            ep_gather_.alloc((size_t)cfg_.ep_size * T * ms_.hidden * 4);
+        }
     }
     logits_.alloc((size_t)B * ms_.vocab * 4);
     tokens_.alloc((size_t)B * 4);
@@ -231,6 +243,25 @@ void Model::upload_matrix(const GgufFile& f, const std::string& name, int64_t ro
     spec_.weight_bytes += out.w.bytes;
 }
 
+// An expert bank [experts * rows][cols]; with expert parallelism only this rank's contiguous share of the experts
+// is uploaded (expert e lives on rank e / (experts / ep_size)).
+void Model::upload_expert_bank(const GgufFile& f, const std::string& name, int experts, int64_t rows, int64_t cols, DeviceWeight& out) {
+    const GgufTensor& t = f.require(name);
+    int64_t total_rows = t.elements() / t.dims.back();
+    if (t.dims.back() != cols || total_rows != rows * experts)
+        throw std::runtime_error("tensor `" + name + "` has shape that does not match the model spec");
+    int64_t rb = gguf_row_bytes(t.type, cols);
+    int local = ep_local_experts();
+    upload_weight(t.type, t.data + (int64_t)ep_first_expert() * rows * rb, rows * local, cols, out, stream_);
+    spec_.weight_bytes += out.w.bytes;
+}
+
+void Model::ep_init(const uint8_t* id) {
+    if (cfg_.ep_size <= 1) throw std::runtime_error("mk_model_ep_init on a model loaded without expert parallelism");
+    MK_CUDA(cudaSetDevice(cfg_.device));
+    ep_ = std::make_unique<EpComm>(cfg_.ep_rank, cfg_.ep_size, id);
+}
+
 void Model::load_weights(const GgufFile& f) {
     const int H = ms_.hidden, AW = ms_.q_heads * ms_.head_dim, KW = ms_.kv_heads * ms_.head_dim;
     upload_matrix(f, "token_embd.weight", ms_.vocab, H, token_embd_, false, 0);
@@ -265,10 +296,10 @@ void Model::load_weights(const GgufFile& f) {
         } else {
             const int E = ms_.experts, F = ms_.expert_ffn;
             upload_f32(f, p + "ffn_gate_inp.weight", (int64_t)E * H, w.router);
-            upload_matrix(f, p + "ffn_gate_exps.weight", (int64_t)E * F, H, w.gate, false, 0);
-            upload_matrix(f, p + "ffn_up_exps.weight", (int64_t)E * F, H, w.up, false, 0);
-            upload_matrix(f, p + "ffn_down_exps.weight", (int64_t)E * H, F, w.down, false, 0);
-            per_token += (w.gate.w.bytes + w.up.w.bytes + w.down.w.bytes) / E * ms_.experts_used + (int64_t)E * H * 4;
+            upload_expert_bank(f, p + "ffn_gate_exps.weight", E, F, H, w.gate);
+            upload_expert_bank(f, p + "ffn_up_exps.weight", E, F, H, w.up);
+            upload_expert_bank(f, p + "ffn_down_exps.weight", E, H, F, w.down);
+            per_token += (w.gate.w.bytes + w.up.w.bytes + w.down.w.bytes) / ep_local_experts() * ms_.experts_used + (int64_t)E * H * 4;
             // the grouped kernels address one expert's matrix at a time
             w.gate.w.rows = F;
             w.up.w.rows = F;
@@ -874,14 +905,25 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
                              stream_);
             ActQ xq = xf;
             xq.xh = nullptr;
-            launch_qgemv_grouped(w.gate.w, E, grp_off_.as<int32_t>(), tok_of_pos_.as<int32_t>(), xq, e_gate_.as<float>(), F, stream_);
-            launch_qgemv_grouped(w.up.w, E, grp_off_.as<int32_t>(), tok_of_pos_.as<int32_t>(), xq, e_up_.as<float>(), F, stream_);
+            // expert parallelism: only the experts [e0, e0 + EL) live here; their rows of the grouped layout are
+            // computed and combined into a partial sum, and the partials of all ranks are added in rank order
+            const bool ep = cfg_.ep_size > 1;
+            if (ep && !ep_) throw std::runtime_error("expert-parallel model used before mk_model_ep_init");
+            const int e0 = ep_first_expert(), EL = ep_local_experts();
+            const int32_t* off = grp_off_.as<int32_t>() + e0;
+            launch_qgemv_grouped(w.gate.w, EL, off, tok_of_pos_.as<int32_t>(), xq, e_gate_.as<float>(), F, stream_);
+            launch_qgemv_grouped(w.up.w, EL, off, tok_of_pos_.as<int32_t>(), xq, e_up_.as<float>(), F, stream_);
             int dkind = act_kind_of(w.down.w);
             ActQ xd = act_view(f_qs_, f_d_, f_bs_, f_xh_, P, F, dkind, false);
             launch_actmul_quant(e_gate_.as<float>(), e_up_.as<float>(), F, P, F, ls.act, dkind, xd, nullptr, stream_);
-            launch_qgemv_grouped(w.down.w, E, grp_off_.as<int32_t>(), nullptr, xd, e_down_.as<float>(), H, stream_);
+            launch_qgemv_grouped(w.down.w, EL, off, nullptr, xd, e_down_.as<float>(), H, stream_);
             launch_moe_combine(e_down_.as<float>(), sel_e_.as<int32_t>(), sel_w_.as<float>(), pos_of_pair_.as<int32_t>(), T, K, H,
-                               down_.as<float>(), stream_);
+                               e0, e0 + EL, ep ? ep_partial_.as<float>() : down_.as<float>(), stream_);
+            if (ep) {
+                ep_->all_gather_f32(ep_partial_.as<float>(), ep_gather_.as<float>(), (size_t)T * H, stream_);
+                launch_ep_sum(ep_gather_.as<float>(), cfg_.ep_size, (int64_t)T * H, down_.as<float>(), stream_);
+                launches_ += 2;
+            }
             launches_ += 8;
         }
         if (ls.moe) pending_splits = 1;

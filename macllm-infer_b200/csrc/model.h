@@ -11,6 +11,7 @@
 #include "hgemm_tc.h"
 #include "qstream_tc.h"
 #include "attention_tc.h"
+#include "ep_comm.h"
 
 namespace mk {
 
@@ -50,6 +51,9 @@ struct ModelConfig {
     // 3 f16-image GEMM whenever more than 8 rows share a matrix, 4 like 0 but nothing falls back to the in-kernel
     // dequant GEMM (f16 images for wide ticks, streamed Q4_K blocks for 2..64 rows)
     int matmul_path = 0;
+    // expert parallelism of a sparse-MoE model: this process holds experts [ep_rank, ep_rank + 1) * experts / ep_size
+    // and exchanges per-layer partial sums with the other ranks; ep_size <= 1 keeps every expert here
+    int ep_rank = 0, ep_size = 1;
 };
 
 class Model : public PagedLm {
@@ -58,6 +62,8 @@ public:
     ~Model() override;
 
     const ModelSpec& model_spec() const { return ms_; }
+    // Joins the expert-parallel group (collective over all ep_size ranks; `id` is EpComm::unique_id from rank 0).
+    void ep_init(const uint8_t* id);
     float last_forward_ms() const override;
     int64_t launch_count() const override { return launches_; }
     int64_t h2d_bytes() const override { return h2d_bytes_; }
@@ -80,6 +86,9 @@ private:
         DeviceWeight wq, wk, wv, wo, gate, up, down;  // dense FFN, or expert banks for MoE layers
     };
     void load_weights(const GgufFile& f);
+    int ep_local_experts() const { return ms_.experts / std::max(cfg_.ep_size, 1); }
+    int ep_first_expert() const { return cfg_.ep_size > 1 ? cfg_.ep_rank * ep_local_experts() : 0; }
+    void upload_expert_bank(const GgufFile& f, const std::string& name, int experts, int64_t rows, int64_t cols, DeviceWeight& out);
     void upload_matrix(const GgufFile& f, const std::string& name, int64_t rows, int64_t cols, DeviceWeight& out, bool permute_heads,
                        int heads);
     void upload_f32(const GgufFile& f, const std::string& name, int64_t n, DevBuf& out);
@@ -147,6 +156,9 @@ private:
     DevBuf l_qs_, l_d_, l_bs_, l_xh_;   // last-token rows for the output projection
     // MoE
     DevBuf router_logits_, sel_e_, sel_w_, grp_off_, pos_of_pair_, tok_of_pos_, e_gate_, e_up_, e_down_;
+    // expert parallelism: this rank's partial layer output [T][hidden] and all ranks' partials [ep_size][T][hidden]
+    std::unique_ptr<EpComm> ep_;
+    DevBuf ep_partial_, ep_gather_;
     QgemmWorkspace tc_ws_;
     PinnedBuf out_host_;
     int out_lanes_ = 0;

@@ -43,8 +43,10 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t* sel, int
     }
 }
 
+// Only choices whose expert lies in [e_lo, e_hi) contribute (the whole range on one GPU, a rank's share under
+// expert parallelism).
 __global__ void moe_combine_kernel(const float* expert_out, const int32_t* sel, const float* w, const int32_t* pos_of_pair, int k,
-                                   int hidden, float* out) {
+                                   int hidden, int e_lo, int e_hi, float* out) {
     int t = blockIdx.x;
     // choices sorted by expert index (k <= 32)
     __shared__ int order[32];
@@ -61,10 +63,27 @@ __global__ void moe_combine_kernel(const float* expert_out, const int32_t* sel, 
         float acc = 0.f;
         for (int i = 0; i < k; ++i) {
             int choice = order[i];
+            int e = sel[t * k + choice];
+            if (e < e_lo || e >= e_hi) continue;
             float v = expert_out[(int64_t)pos_of_pair[t * k + choice] * hidden + c];
             acc = __fadd_rn(acc, __fmul_rn(v, w[t * k + choice]));
         }
         out[(int64_t)t * hidden + c] = acc;
+    }
+}
+
+// out[i] = ((g[0][i] + g[1][i]) + g[2][i]) + ... : the same order on every rank, so every rank gets the same bits.
+__global__ void ep_sum_kernel(const float4* gathered, int ranks, int64_t count4, float4* out) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count4; i += (int64_t)gridDim.x * blockDim.x) {
+        float4 a = gathered[i];
+        for (int r = 1; r < ranks; ++r) {
+            float4 b = gathered[(int64_t)r * count4 + i];
+            a.x = __fadd_rn(a.x, b.x);
+            a.y = __fadd_rn(a.y, b.y);
+            a.z = __fadd_rn(a.z, b.z);
+            a.w = __fadd_rn(a.w, b.w);
+        }
+        out[i] = a;
     }
 }
 
@@ -79,10 +98,19 @@ void launch_moe_group(const int32_t* sel_experts, int T, int k, int experts, int
 }
 
 void launch_moe_combine(const float* expert_out, const int32_t* sel_experts, const float* sel_weights,
-                        const int32_t* pos_of_pair, int T, int k, int hidden, float* out, cudaStream_t s) {
+                        const int32_t* pos_of_pair, int T, int k, int hidden, int e_lo, int e_hi, float* out, cudaStream_t s) {
     if (T <= 0) return;
     if (k > 32) throw std::runtime_error("launch_moe_combine: more than 32 experts per token");
-    moe_combine_kernel<<<T, 256, 0, s>>>(expert_out, sel_experts, sel_weights, pos_of_pair, k, hidden, out);
+    moe_combine_kernel<<<T, 256, 0, s>>>(expert_out, sel_experts, sel_weights, pos_of_pair, k, hidden, e_lo, e_hi, out);
+    MK_LAUNCH_CHECK();
+}
+
+void launch_ep_sum(const float* gathered, int ranks, int64_t count, float* out, cudaStream_t s) {
+    if (count <= 0) return;
+    if (count % 4 != 0) throw std::runtime_error("launch_ep_sum: count must be a multiple of 4");
+    int64_t c4 = count / 4;
+    int grid = (int)std::min<int64_t>((c4 + 255) / 256, 148 * 8);
+    ep_sum_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const float4*>(gathered), ranks, c4, reinterpret_cast<float4*>(out));
     MK_LAUNCH_CHECK();
 }
 

@@ -73,7 +73,7 @@ class Model:
 
     @staticmethod
     def _config(device=0, block_tokens=16, slab_blocks=8, kv_capacity_tokens=4096, prefix_capacity_tokens=0, kv_dtype="f16",
-                max_batch_tokens=2048, max_batch_lanes=64, matmul_path=capi.PATH_AUTO) -> capi.LoadConfig:
+                max_batch_tokens=2048, max_batch_lanes=64, matmul_path=capi.PATH_AUTO, ep_rank=0, ep_size=1) -> capi.LoadConfig:
         cfg = capi.LoadConfig()
         cfg.device_ordinal = device
         cfg.block_tokens = block_tokens
@@ -84,7 +84,25 @@ class Model:
         cfg.max_batch_tokens = max_batch_tokens
         cfg.max_batch_lanes = max_batch_lanes
         cfg.matmul_path = matmul_path
+        cfg.ep_rank = ep_rank
+        cfg.ep_size = ep_size
         return cfg
+
+    EP_ID_BYTES = 128
+
+    @staticmethod
+    def ep_unique_id() -> bytes:
+        """Rank 0's id of a new expert-parallel group; hand it to the other ranks (file, store, socket)."""
+        buf = (C.c_uint8 * Model.EP_ID_BYTES)()
+        capi.check(capi.lib().mk_ep_unique_id(buf))
+        return bytes(buf)
+
+    def ep_init(self, unique_id: bytes) -> None:
+        """Joins the expert-parallel group (collective: returns once all ep_size ranks have called it)."""
+        if len(unique_id) != Model.EP_ID_BYTES:
+            raise ValueError("expert-parallel id must be 128 bytes")
+        buf = (C.c_uint8 * Model.EP_ID_BYTES).from_buffer_copy(unique_id)
+        capi.check(capi.lib().mk_model_ep_init(self._h, buf))
 
     @classmethod
     def load_gguf(cls, path, **kw) -> "Model":

@@ -1,0 +1,116 @@
+"""Expert parallelism of the sparse-MoE family over two GPUs (one process per GPU, NCCL): both ranks run the same
+ragged batches on half of the experts each and must end every forward with the same bits; against the same
+checkpoint served from one GPU the schedule is identical and the logits differ only by the association of the
+per-token sum over experts.  Needs two CUDA devices."""
+import importlib
+import os
+import subprocess
+import sys
+import textwrap
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = Path(__file__).resolve().parent.parent
+
+PROMPT_SEED, N_PROMPTS, NEW_TOKENS = 5, 5, 6
+ENGINE_KW = dict(max_active_sequences=4, scheduler_token_budget=96, prefill_token_quantum=48, queue_capacity=16)
+
+
+def make_prompts(vocab):
+    rng = np.random.default_rng(PROMPT_SEED)
+    return [rng.integers(0, vocab, int(n)).tolist() for n in rng.integers(3, 70, N_PROMPTS)]
+
+
+def serve(eng, model, vocab):
+    e = eng.Engine(model, record_logits=True, **ENGINE_KW)
+    ids = e.submit([eng.Request(p, NEW_TOKENS) for p in make_prompts(vocab)], atomic_batch=False)
+    e.run()
+    return (e.trace(), [list(map(int, e.result(i)["tokens"])) for i in ids], [np.asarray(e.logits(i), dtype=np.float32) for i in ids])
+
+
+CHILD = textwrap.dedent("""
+    import importlib, pickle, sys, time
+    sys.path.insert(0, %r)
+    sys.path.insert(0, %r)
+    import __graft_entry__ as entry
+    entry.load_package()
+    eng = importlib.import_module("macllm_infer_b200.engine")
+    import test_expert_parallel_gpu as t
+    rank, size, gguf, id_file, out_file, vocab = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4], sys.argv[5], int(sys.argv[6])
+    model = eng.Model.load_gguf(gguf, device=rank, kv_dtype="f32", matmul_path=1, max_batch_tokens=256, max_batch_lanes=8,
+                                kv_capacity_tokens=2048, ep_rank=rank, ep_size=size)
+    if rank == 0:
+        uid = eng.Model.ep_unique_id()
+        with open(id_file + ".tmp", "wb") as f:
+            f.write(uid)
+        import os
+        os.replace(id_file + ".tmp", id_file)
+    else:
+        import os
+        deadline = time.time() + 120
+        while not os.path.exists(id_file):
+            if time.time() > deadline:
+                raise SystemExit("rank 0 never published the group id")
+            time.sleep(0.05)
+        uid = open(id_file, "rb").read()
+    model.ep_init(uid)
+    trace, tokens, logits = t.serve(eng, model, vocab)
+    with open(out_file, "wb") as f:
+        pickle.dump(dict(trace=trace, tokens=tokens, logits=logits, weight_bytes=model.spec().weight_bytes), f)
+""") % (str(ROOT), str(ROOT / "tests"))
+
+
+def test_two_ranks_hold_half_the_experts_and_agree(mk, tmp_path):
+    import pickle
+    capi = importlib.import_module("macllm_infer_b200._capi")
+    eng = importlib.import_module("macllm_infer_b200.engine")
+    seed = importlib.import_module("macllm_infer_b200.seed_gguf")
+    if capi.lib().mk_device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    spec = seed.scaled("qwen3-30b-a3b", layers=2, vocab=2048, hidden=1024, experts=16)
+    gguf = tmp_path / "moe.gguf"
+    seed.write_seed_gguf(gguf, spec, seed=0)
+
+    whole = eng.Model.load_gguf(gguf, device=0, kv_dtype="f32", matmul_path=1, max_batch_tokens=256, max_batch_lanes=8,
+                                kv_capacity_tokens=2048)
+    ref_trace, ref_tokens, ref_logits = serve(eng, whole, spec.vocab)
+    whole_bytes = whole.spec().weight_bytes
+    del whole
+
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, "-c", CHILD, str(r), "2", str(gguf), str(tmp_path / "ep.id"), str(tmp_path / f"out{r}.pkl"),
+                               str(spec.vocab)], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(2)]
+    try:
+        for p in procs:
+            _, err = p.communicate(timeout=300)
+            assert p.returncode == 0, err[-3000:]
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+    out = [pickle.load(open(tmp_path / f"out{r}.pkl", "rb")) for r in range(2)]
+
+    # both ranks: the same schedule, tokens and logit bits
+    assert out[0]["trace"] == out[1]["trace"] == ref_trace
+    assert out[0]["tokens"] == out[1]["tokens"]
+    for a, b in zip(out[0]["logits"], out[1]["logits"]):
+        assert np.array_equal(a, b)
+    # each rank holds half of the expert banks
+    expert_bytes = sum(seed._tensor_bytes(dims, qtype) for name, dims, qtype, _ in seed.tensor_plan(spec) if "_exps" in name)
+    assert out[0]["weight_bytes"] == out[1]["weight_bytes"] == whole_bytes - expert_bytes // 2
+    # against one GPU: rows computed from the same inputs agree up to the reassociated expert sum
+    worst = 0.0
+    for toks, lg, rtoks, rlg in zip(out[0]["tokens"], out[0]["logits"], ref_tokens, ref_logits):
+        same = 0
+        while same < min(len(toks), len(rtoks)) and toks[same] == rtoks[same]:
+            same += 1
+        rows = min(same + 1, len(lg), len(rlg))
+        worst = max(worst, float(np.abs(lg[:rows] - rlg[:rows]).max()))
+        if same < len(rtoks):
+            top2 = np.sort(rlg[same])[-2:]
+            assert top2[1] - top2[0] <= 2 * max(worst, 1e-3)
+    assert worst <= 2e-2, worst
