@@ -69,7 +69,73 @@ EpComm::EpComm(int rank, int size, const uint8_t id_bytes[kEpUniqueIdBytes]) : r
 }
 
 EpComm::~EpComm() {
+    for (void* p : mapped_)
+        if (p != nullptr) cudaIpcCloseMemHandle(p);
+    if (exchange_ != nullptr) cudaFree(exchange_);
     if (comm_ != nullptr) nccl().CommDestroy(static_cast<ncclComm_t>(comm_));
+}
+
+namespace {
+void cuda_check(cudaError_t e, const char* what) {
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+    }
+}
+}  // namespace
+
+void EpComm::open_exchange(int max_tokens, int row_floats, cudaStream_t s) {
+    if (size_ > kEpMaxRanks) throw std::runtime_error("the fused expert exchange serves at most 8 ranks");
+    if (exchange_ != nullptr) throw std::runtime_error("expert exchange opened twice");
+    const int64_t slot_floats = (int64_t)max_tokens * row_floats;
+    const size_t gather_bytes = (size_t)2 * size_ * slot_floats * 4;
+    const size_t flag_bytes = (size_t)2 * size_ * max_tokens * 4;
+    cuda_check(cudaMalloc(&exchange_, gather_bytes + flag_bytes), "cudaMalloc of the expert exchange block");
+    cuda_check(cudaMemsetAsync(exchange_, 0, gather_bytes + flag_bytes, s), "cudaMemsetAsync");
+    // the handles travel through the communicator itself; nobody can store into a block before its owner has
+    // zeroed it, because the owner's all-gather is ordered after the memset on the same stream
+    cudaIpcMemHandle_t mine;
+    cuda_check(cudaIpcGetMemHandle(&mine, exchange_), "cudaIpcGetMemHandle");
+    static_assert(sizeof(cudaIpcMemHandle_t) % 4 == 0, "handle size");
+    constexpr size_t HF = sizeof(cudaIpcMemHandle_t) / 4;
+    float* stage = nullptr;
+    cuda_check(cudaMalloc(&stage, (size_t)(size_ + 1) * HF * 4), "cudaMalloc");
+    cudaIpcMemHandle_t all[kEpMaxRanks];
+    try {
+        cuda_check(cudaMemcpyAsync(stage, &mine, sizeof mine, cudaMemcpyHostToDevice, s), "cudaMemcpyAsync");
+        all_gather_f32(stage, stage + HF, HF, s);
+        cuda_check(cudaMemcpyAsync(all, stage + HF, (size_t)size_ * sizeof mine, cudaMemcpyDeviceToHost, s), "cudaMemcpyAsync");
+        cuda_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+    } catch (...) {
+        cudaFree(stage);
+        throw;
+    }
+    cudaFree(stage);
+    peers_ = EpPeers{};
+    peers_.rank = rank_;
+    peers_.ranks = size_;
+    peers_.max_tokens = max_tokens;
+    peers_.slot_floats = slot_floats;
+    for (int p = 0; p < size_; ++p) {
+        void* base = exchange_;
+        if (p != rank_) {
+            cuda_check(cudaIpcOpenMemHandle(&base, all[p], cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle of a peer's expert exchange block");
+            mapped_[p] = base;
+        }
+        peers_.gather[p] = static_cast<float*>(base);
+        peers_.flags[p] = reinterpret_cast<uint32_t*>(static_cast<char*>(base) + gather_bytes);
+    }
+    // leave together: once this returns, every rank has mapped every block
+    float* fence = nullptr;
+    cuda_check(cudaMalloc(&fence, (size_t)(size_ + 1) * 4), "cudaMalloc");
+    try {
+        all_gather_f32(fence, fence + 1, 1, s);
+        cuda_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+    } catch (...) {
+        cudaFree(fence);
+        throw;
+    }
+    cudaFree(fence);
 }
 
 void EpComm::all_gather_f32(const float* send, float* recv, size_t count, cudaStream_t s) {

@@ -17,6 +17,19 @@
 namespace mk {
 
 constexpr int kEpUniqueIdBytes = 128;
+constexpr int kEpMaxRanks = 8;
+
+// The exchange area of the fused combine kernel, as every rank sees it.  Each rank owns one cudaMalloc'd block, mapped
+// into the other processes through CUDA IPC (NVLink peer stores land in it):
+//   gather[p]: rank p's block viewed as floats [2][ranks][slot_floats]: buffer b, slot q holds rank q's partial rows
+//   flags[p]:  rank p's block viewed as u32    [2][ranks][max_tokens]:  the epoch in which slot q's row t was filled
+// gather[rank] / flags[rank] are this process's own block.
+struct EpPeers {
+    float* gather[kEpMaxRanks] = {};
+    uint32_t* flags[kEpMaxRanks] = {};
+    int rank = 0, ranks = 1, max_tokens = 0;
+    int64_t slot_floats = 0;
+};
 
 class EpComm {
 public:
@@ -33,9 +46,21 @@ public:
     // recv[r * count + i] = rank r's send[i], enqueued on `s`.
     void all_gather_f32(const float* send, float* recv, size_t count, cudaStream_t s);
 
+    // Collective: allocates this rank's exchange block for `max_tokens` rows of `row_floats` floats, publishes its IPC
+    // handle to the other ranks (through an all-gather) and maps theirs.  Throws when a peer's block cannot be mapped.
+    void open_exchange(int max_tokens, int row_floats, cudaStream_t s);
+    bool has_exchange() const { return exchange_ != nullptr; }
+    const EpPeers& peers() const { return peers_; }
+    // Every rank calls this once per exchange, in the same order: the epoch names the exchange, its parity the buffer.
+    uint32_t next_epoch() { return ++epoch_; }
+
 private:
     void* comm_ = nullptr;
     int rank_ = 0, size_ = 1;
+    void* exchange_ = nullptr;
+    void* mapped_[kEpMaxRanks] = {};
+    EpPeers peers_;
+    uint32_t epoch_ = 0;
 };
 
 }  // namespace mk

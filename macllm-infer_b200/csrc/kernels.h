@@ -1,6 +1,7 @@
 // Host-side launchers of the sm_100a kernels.  All pointers are device pointers unless noted.
 #pragma once
 #include "common.cuh"
+#include "ep_comm.h"
 
 namespace mk {
 
@@ -151,6 +152,13 @@ void launch_moe_combine(const float* expert_out, const int32_t* sel_experts, con
                         const int32_t* pos_of_pair, int T, int k, int hidden, int e_lo, int e_hi, float* out, cudaStream_t s);
 // Expert parallelism: out[i] = sum over ranks r = 0, 1, ... (in that order) of gathered[r * count + i].
 void launch_ep_sum(const float* gathered, int ranks, int64_t count, float* out, cudaStream_t s);
+// Expert parallelism, fused: launch_moe_combine of this rank's experts, the exchange of the partial rows with the other
+// ranks through peer stores into their exchange blocks (EpComm::open_exchange), and the sum in rank order, in one
+// kernel.  All ranks call it with the same epoch.  A peer that does not deliver within a few seconds leaves a non-zero
+// code in *status and the forward's result is not to be used.
+void launch_moe_combine_exchange(const float* expert_out, const int32_t* sel_experts, const float* sel_weights,
+                                 const int32_t* pos_of_pair, int T, int k, int hidden, int e_lo, int e_hi, const EpPeers& peers,
+                                 uint32_t epoch, float* out, int32_t* status, cudaStream_t s);
 
 // Small helpers
 void launch_add_inplace(float* h, const float* a, float scale, int64_t n, cudaStream_t s);

@@ -260,6 +260,10 @@ void Model::ep_init(const uint8_t* id) {
     if (cfg_.ep_size <= 1) throw std::runtime_error("mk_model_ep_init on a model loaded without expert parallelism");
     MK_CUDA(cudaSetDevice(cfg_.device));
     ep_ = std::make_unique<EpComm>(cfg_.ep_rank, cfg_.ep_size, id);
+    // MACLLM_B200_EP_FUSED=0 keeps the exchange on NCCL (all-gather + a sum kernel) instead of the fused kernel
+    const char* fused = getenv("MACLLM_B200_EP_FUSED");
+    if ((fused == nullptr || strcmp(fused, "0") != 0) && cfg_.ep_size <= kEpMaxRanks)
+        ep_->open_exchange(cfg_.max_batch_tokens, ms_.hidden, stream_);
 }
 
 void Model::load_weights(const GgufFile& f) {
@@ -917,9 +921,15 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
             ActQ xd = act_view(f_qs_, f_d_, f_bs_, f_xh_, P, F, dkind, false);
             launch_actmul_quant(e_gate_.as<float>(), e_up_.as<float>(), F, P, F, ls.act, dkind, xd, nullptr, stream_);
             launch_qgemv_grouped(w.down.w, EL, off, nullptr, xd, e_down_.as<float>(), H, stream_);
-            launch_moe_combine(e_down_.as<float>(), sel_e_.as<int32_t>(), sel_w_.as<float>(), pos_of_pair_.as<int32_t>(), T, K, H,
-                               e0, e0 + EL, ep ? ep_partial_.as<float>() : down_.as<float>(), stream_);
-            if (ep) {
+            if (ep && ep_->has_exchange()) {
+                launch_moe_combine_exchange(e_down_.as<float>(), sel_e_.as<int32_t>(), sel_w_.as<float>(), pos_of_pair_.as<int32_t>(), T, K,
+                                            H, e0, e0 + EL, ep_->peers(), ep_->next_epoch(), down_.as<float>(),
+                                            tc_ws_.status.as<int32_t>(), stream_);
+            } else {
+                launch_moe_combine(e_down_.as<float>(), sel_e_.as<int32_t>(), sel_w_.as<float>(), pos_of_pair_.as<int32_t>(), T, K, H,
+                                   e0, e0 + EL, ep ? ep_partial_.as<float>() : down_.as<float>(), stream_);
+            }
+            if (ep && !ep_->has_exchange()) {
                 ep_->all_gather_f32(ep_partial_.as<float>(), ep_gather_.as<float>(), (size_t)T * H, stream_);
                 launch_ep_sum(ep_gather_.as<float>(), cfg_.ep_size, (int64_t)T * H, down_.as<float>(), stream_);
                 launches_ += 2;
@@ -997,7 +1007,7 @@ void Model::fetch_output(float* logits, uint32_t* tokens) {
     int32_t flags[2];
     memcpy(flags, oh + tok_off + (size_t)B * 4, 8);
     if (flags[0] != 0) throw std::runtime_error("batch descriptor index out of range on the device (flag " + std::to_string(flags[0]) + ")");
-    if (flags[1] != 0) throw std::runtime_error("a bounded wait inside the tensor-core matmul gave up (status " + std::to_string(flags[1]) + ")");
+    if (flags[1] != 0) throw std::runtime_error("a bounded wait inside a kernel gave up (tensor-core matmul pipeline or expert exchange; status " + std::to_string(flags[1]) + ")");
     if (logits) {
         if (!(out_flags_ & FWD_WANT_LOGITS)) throw std::runtime_error("logits were not requested for this forward");
         memcpy(logits, oh, tok_off);

@@ -87,7 +87,116 @@ __global__ void ep_sum_kernel(const float4* gathered, int ranks, int64_t count4,
     }
 }
 
+constexpr uint64_t kEpWaitNs = 5ull * 1000 * 1000 * 1000;  // a peer that is 5 s late counts as lost
+
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Expert-parallel combine and exchange in one kernel (ranks run it at the same point of the same forward, one per
+// GPU).  Pass 1, for each of the CTA's tokens: the weighted sum of the token's choices held by this rank, in ascending
+// expert order, is stored into slot `rank` of buffer `buf` in this GPU's block AND, with peer stores over NVLink, in
+// every other rank's block; after a system-scope fence the row's flag in each block is set to `epoch`.  Pass 2: wait
+// (bounded) until the flags of all other ranks' rows carry `epoch`, then add the slots in rank order - all local
+// reads.  No CTA waits before it has published all of its rows, so two GPUs can never wait on each other's
+// unscheduled CTAs.  Buffers alternate with the epoch: a rank can reach exchange e+2 only after every peer has set
+// its flags of exchange e+1, which a peer does only after it has finished reading exchange e.
+__global__ void __launch_bounds__(256) moe_combine_exchange_kernel(const float* __restrict__ expert_out, const int32_t* __restrict__ sel,
+                                                                   const float* __restrict__ w, const int32_t* __restrict__ pos_of_pair,
+                                                                   int T, int k, int hidden, int e_lo, int e_hi, EpPeers P, uint32_t epoch,
+                                                                   float* __restrict__ out, int32_t* status) {
+    __shared__ int order[32];
+    __shared__ int lost;
+    const int R = P.ranks, me = P.rank, buf = (int)(epoch & 1u);
+    const int h4 = hidden / 4;
+    if (threadIdx.x == 0) lost = 0;
+    for (int t = blockIdx.x; t < T; t += gridDim.x) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int i = 0; i < k; ++i) order[i] = i;
+            for (int i = 1; i < k; ++i) {
+                int o = order[i], j = i - 1;
+                while (j >= 0 && sel[t * k + order[j]] > sel[t * k + o]) { order[j + 1] = order[j]; --j; }
+                order[j + 1] = o;
+            }
+        }
+        __syncthreads();
+        const int64_t row4 = ((int64_t)(buf * R + me) * P.slot_floats + (int64_t)t * hidden) / 4;
+        for (int c = threadIdx.x; c < h4; c += blockDim.x) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int i = 0; i < k; ++i) {
+                int choice = order[i];
+                int e = sel[t * k + choice];
+                if (e < e_lo || e >= e_hi) continue;
+                float wt = w[t * k + choice];
+                float4 v = reinterpret_cast<const float4*>(expert_out + (int64_t)pos_of_pair[t * k + choice] * hidden)[c];
+                acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, wt));
+                acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, wt));
+                acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, wt));
+                acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, wt));
+            }
+            for (int p = 0; p < R; ++p) reinterpret_cast<float4*>(P.gather[p])[row4 + c] = acc;
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x < R && threadIdx.x != me)
+            st_release_sys(P.flags[threadIdx.x] + (int64_t)(buf * R + me) * P.max_tokens + t, epoch);
+    }
+    for (int t = blockIdx.x; t < T; t += gridDim.x) {
+        if (threadIdx.x < R && threadIdx.x != me) {
+            const uint32_t* f = P.flags[me] + (int64_t)(buf * R + threadIdx.x) * P.max_tokens + t;
+            const uint64_t t0 = global_ns();
+            while (ld_acquire_sys(f) != epoch) {
+                if (global_ns() - t0 > kEpWaitNs) {
+                    atomicExch(status, 0x4550000 | (int)threadIdx.x);
+                    lost = 1;
+                    break;
+                }
+                __nanosleep(200);
+            }
+        }
+        __syncthreads();
+        if (lost) return;  // the host reads the status word and fails the forward
+        const float4* g = reinterpret_cast<const float4*>(P.gather[me]);
+        for (int c = threadIdx.x; c < h4; c += blockDim.x) {
+            float4 a = __ldcg(g + ((int64_t)(buf * R) * P.slot_floats + (int64_t)t * hidden) / 4 + c);
+            for (int r = 1; r < R; ++r) {
+                float4 b = __ldcg(g + ((int64_t)(buf * R + r) * P.slot_floats + (int64_t)t * hidden) / 4 + c);
+                a.x = __fadd_rn(a.x, b.x);
+                a.y = __fadd_rn(a.y, b.y);
+                a.z = __fadd_rn(a.z, b.z);
+                a.w = __fadd_rn(a.w, b.w);
+            }
+            reinterpret_cast<float4*>(out + (int64_t)t * hidden)[c] = a;
+        }
+    }
+}
+
 }  // namespace
+
+void launch_moe_combine_exchange(const float* expert_out, const int32_t* sel_experts, const float* sel_weights,
+                                 const int32_t* pos_of_pair, int T, int k, int hidden, int e_lo, int e_hi, const EpPeers& peers,
+                                 uint32_t epoch, float* out, int32_t* status, cudaStream_t s) {
+    if (T <= 0) return;
+    if (k > 32) throw std::runtime_error("launch_moe_combine_exchange: more than 32 experts per token");
+    if (hidden % 4 != 0 || (int64_t)T * hidden > peers.slot_floats || T > peers.max_tokens)
+        throw std::runtime_error("launch_moe_combine_exchange: batch does not fit the exchange block");
+    // one CTA per SM at most: every CTA is resident, so pass 1 of all tokens runs without waiting on anything
+    int grid = std::min(T, 148);
+    moe_combine_exchange_kernel<<<grid, 256, 0, s>>>(expert_out, sel_experts, sel_weights, pos_of_pair, T, k, hidden, e_lo, e_hi, peers,
+                                                     epoch, out, status);
+    MK_LAUNCH_CHECK();
+}
 
 void launch_moe_group(const int32_t* sel_experts, int T, int k, int experts, int32_t* offsets, int32_t* pos_of_pair,
                       int32_t* token_of_pos, cudaStream_t s) {

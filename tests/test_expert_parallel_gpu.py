@@ -60,11 +60,15 @@ CHILD = textwrap.dedent("""
     model.ep_init(uid)
     trace, tokens, logits = t.serve(eng, model, vocab)
     with open(out_file, "wb") as f:
-        pickle.dump(dict(trace=trace, tokens=tokens, logits=logits, weight_bytes=model.spec().weight_bytes), f)
+        pickle.dump(dict(trace=trace, tokens=tokens, logits=logits, weight_bytes=model.spec().weight_bytes,
+                         launches=model.launch_count()), f)
 """) % (str(ROOT), str(ROOT / "tests"))
 
 
-def test_two_ranks_hold_half_the_experts_and_agree(mk, tmp_path):
+@pytest.mark.parametrize("exchange", ["fused", "nccl"])
+def test_two_ranks_hold_half_the_experts_and_agree(mk, tmp_path, exchange):
+    """exchange = fused: one kernel combines this rank's experts, stores the partial rows into the peers' memory over
+    NVLink and adds all ranks' rows; nccl: combine kernel, ncclAllGather, sum kernel."""
     import pickle
     capi = importlib.import_module("macllm_infer_b200._capi")
     eng = importlib.import_module("macllm_infer_b200.engine")
@@ -79,9 +83,10 @@ def test_two_ranks_hold_half_the_experts_and_agree(mk, tmp_path):
                                 kv_capacity_tokens=2048)
     ref_trace, ref_tokens, ref_logits = serve(eng, whole, spec.vocab)
     whole_bytes = whole.spec().weight_bytes
+    whole_launches = whole.launch_count()
     del whole
 
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MACLLM_B200_EP_FUSED="1" if exchange == "fused" else "0")
     procs = [subprocess.Popen([sys.executable, "-c", CHILD, str(r), "2", str(gguf), str(tmp_path / "ep.id"), str(tmp_path / f"out{r}.pkl"),
                                str(spec.vocab)], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(2)]
     try:
@@ -99,6 +104,10 @@ def test_two_ranks_hold_half_the_experts_and_agree(mk, tmp_path):
     assert out[0]["tokens"] == out[1]["tokens"]
     for a, b in zip(out[0]["logits"], out[1]["logits"]):
         assert np.array_equal(a, b)
+    # the fused exchange adds no launch to the single-GPU sequence; the NCCL form adds two per MoE layer and forward
+    moe_layer_forwards = spec.layers * len(ref_trace)
+    extra = 0 if exchange == "fused" else 2 * moe_layer_forwards
+    assert out[0]["launches"] == out[1]["launches"] == whole_launches + extra
     # each rank holds half of the expert banks
     expert_bytes = sum(seed._tensor_bytes(dims, qtype) for name, dims, qtype, _ in seed.tensor_plan(spec) if "_exps" in name)
     assert out[0]["weight_bytes"] == out[1]["weight_bytes"] == whole_bytes - expert_bytes // 2
