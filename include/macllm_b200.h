@@ -394,6 +394,11 @@ int32_t mk_k_embed(int32_t type, const void* w, int64_t rows, int64_t cols, cons
 
 /* DenseFeedForward gate (src/decoder.rs:298-305): out = act(gate) * up, act 0 = SiLU, 1 = tanh-GELU. */
 int32_t mk_k_actmul(const float* gate, const float* up, int32_t T, int32_t F, int32_t act, float* out);
+/* The front half of DenseFeedForward::forward (src/decoder.rs:298-305) as ONE tensor-core GEMM: gate_w and up_w are
+ * F x cols matrices in GGUF block format `type`, x is [T][cols]; out[t][j] = f16(act(x . gate_j) * (x . up_j)) widened
+ * to f32.  With iters > 0 and avg_ms non-null the GEMM is also timed (L2 flushed between runs). */
+int32_t mk_k_gated_ffn(int32_t type, const void* gate_w, const void* up_w, int64_t F, int64_t cols, const float* x, int32_t T,
+                       int32_t act, float* out, int32_t iters, float* avg_ms);
 
 /* One attention layer step of a ragged batch: builds the batch descriptor on the device, applies the
  * optional per-head RMSNorm and RoPE, scatters K/V into the paged pool and runs paged attention

@@ -229,6 +229,68 @@ int32_t mk_k_actmul(const float* gate, const float* up, int32_t T, int32_t F, in
     });
 }
 
+int32_t mk_k_gated_ffn(int32_t type, const void* gate_w, const void* up_w, int64_t F, int64_t cols, const float* x, int32_t T,
+                       int32_t act, float* out, int32_t iters, float* avg_ms) {
+    return guarded([&] {
+        require_device();
+        DeviceWeight dg, du;
+        upload_weight(type, gate_w, F, cols, dg);
+        upload_weight(type, up_w, F, cols, du);
+        if (!hgemm_tc_supported(dg.w)) throw std::runtime_error("mk_k_gated_ffn: the f16-image GEMM does not cover this matrix");
+        HalfWeight image;
+        build_half_weight_interleaved(dg.w, du.w, image, nullptr);
+        int kind = act_kind_for(type);
+        DevBuf dx((size_t)T * cols * 4), dy((size_t)T * F * 2);
+        dx.upload(x, (size_t)T * cols * 4);
+        ActBufs ab;
+        ActQ a = ab.view(T, (int)cols, kind, true, false);
+        NormQuantArgs na;
+        na.h = dx.as<float>();
+        na.rows = T;
+        na.dim = (int)cols;
+        na.act_kind = kind;
+        na.out = a;
+        launch_add_norm_quant(na, nullptr);
+        DevBuf status(4);
+        status.zero(nullptr);
+        HgemmScratch hs;
+        hs.status = status.as<int32_t>();
+        auto run = [&] { launch_hgemm_tc_gated(image, a.xh, T, act, dy.as<__half>(), (int)F, hs, nullptr); };
+        run();
+        if (iters > 0 && avg_ms != nullptr) {
+            DevBuf flush((size_t)256 << 20);  // larger than the L2
+            cudaEvent_t e0, e1;
+            MK_CUDA(cudaEventCreate(&e0));
+            MK_CUDA(cudaEventCreate(&e1));
+            double total = 0;
+            for (int i = 0; i < iters + 2; ++i) {
+                flush.zero(nullptr);
+                MK_CUDA(cudaEventRecord(e0, nullptr));
+                run();
+                MK_CUDA(cudaEventRecord(e1, nullptr));
+                MK_CUDA(cudaEventSynchronize(e1));
+                float ms = 0;
+                MK_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+                if (i >= 2) total += ms;
+            }
+            cudaEventDestroy(e0);
+            cudaEventDestroy(e1);
+            *avg_ms = (float)(total / iters);
+        }
+        MK_CUDA(cudaDeviceSynchronize());
+        int32_t st = 0;
+        status.download(&st, 4);
+        MK_CUDA(cudaDeviceSynchronize());
+        if (st != 0) throw std::runtime_error("tensor-core matmul: a bounded wait inside the kernel gave up (status " + std::to_string(st) + ")");
+        if (out != nullptr) {
+            std::vector<__half> h((size_t)T * F);
+            dy.download(h.data(), h.size() * 2);
+            MK_CUDA(cudaDeviceSynchronize());
+            for (size_t i = 0; i < h.size(); ++i) out[i] = __half2float(h[i]);
+        }
+    });
+}
+
 int32_t mk_k_attention_step(const mk_attn_case* c) {
     return guarded([&] {
         require_device();

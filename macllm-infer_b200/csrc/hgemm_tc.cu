@@ -111,8 +111,8 @@ __device__ __forceinline__ void q4k_scale_min(const uint8_t* sc, int j, int& s, 
     }
 }
 
-// One warp per 256-element block; lane l produces elements 8l .. 8l+7.
-__global__ void dequant_f16_kernel(QWeight W, __half* out) {
+// One warp per 256-element block; lane l produces elements 8l .. 8l+7.  Row r of W goes to out + r * row_stride.
+__global__ void dequant_f16_kernel(QWeight W, __half* out, int64_t row_stride) {
     const int64_t nb = W.cols / 256;
     const int64_t b = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (b >= W.rows * nb) return;
@@ -160,7 +160,8 @@ __global__ void dequant_f16_kernel(QWeight W, __half* out) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) h[i] = __float2half_rn(src[i]);
     }
-    *reinterpret_cast<uint4*>(out + b * 256 + lane * 8) = *reinterpret_cast<uint4*>(h);
+    const int64_t out_row = b / nb, out_blk = b - out_row * nb;
+    *reinterpret_cast<uint4*>(out + out_row * row_stride + out_blk * 256 + lane * 8) = *reinterpret_cast<uint4*>(h);
 }
 
 // ---- the GEMM ------------------------------------------------------------------------------------
@@ -177,6 +178,11 @@ struct HgParams {
     int splits, kb_per_split;
     float* partial;
     int32_t* status;
+    // gated epilogue (splits == 1): weight rows 2j / 2j+1 are the gate / up projections of feature j and the kernel
+    // writes yh[t][j] = f16(act(gate) * up) instead of y; 0 = off, 1 = SiLU, 2 = tanh GELU
+    int gated;
+    __half* yh;
+    int ldyh;
 };
 
 template <int BN, int STAGES>
@@ -191,6 +197,12 @@ __device__ __forceinline__ float finish_value(float v, const HgParams& p) {
     v *= p.out_scale;
     if (p.softcap != 0.f) v = tanhf(v * (1.0f / p.softcap)) * p.softcap;
     return v;
+}
+
+// The activations of the gated feed-forward, as the SwiGLU kernel of quantize.cu computes them.
+__device__ __forceinline__ float hg_silu(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float hg_gelu_tanh(float x) {
+    return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * x * (1.0f + 0.044715f * x * x)));
 }
 
 template <int BN, int STAGES>
@@ -364,7 +376,24 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + (uint32_t)cb, r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row < p.rows) {
+                if (p.gated != 0) {
+                    // lanes 2i / 2i+1 hold gate / up of one feature: the even lane finishes the even token columns,
+                    // the odd lane the odd ones, after one exchange per pair of columns
+                    const bool odd = (lane & 1) != 0;
+                    const int feature = row >> 1;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        float mine = __uint_as_float(odd ? r[i] : r[i + 1]);       // what the partner needs
+                        float theirs = __shfl_xor_sync(0xffffffffu, mine, 1);
+                        float g = odd ? theirs : __uint_as_float(r[i]);
+                        float u = odd ? __uint_as_float(r[i + 1]) : theirs;
+                        int tok = tok0 + cb + i + (odd ? 1 : 0);
+                        if (row < p.rows && tok < p.T) {
+                            float a = p.gated == 1 ? hg_silu(g) : hg_gelu_tanh(g);
+                            p.yh[(int64_t)tok * p.ldyh + feature] = __float2half_rn(a * u);
+                        }
+                    }
+                } else if (row < p.rows) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         int tok = tok0 + cb + i;
@@ -487,12 +516,31 @@ void build_half_weight_stacked(const QWeight* const* parts, int n_parts, HalfWei
         const int64_t blocks = W.rows * (W.cols / 256);
         const int warps_per_cta = 8;
         dequant_f16_kernel<<<(unsigned)((blocks + warps_per_cta - 1) / warps_per_cta), warps_per_cta * 32, 0, s>>>(
-            W, out.values.as<__half>() + row0 * cols);
+            W, out.values.as<__half>() + row0 * cols, cols);
         MK_LAUNCH_CHECK();
         row0 += W.rows;
     }
     static_assert(sizeof(CUtensorMap) <= sizeof(out.tmap), "descriptor storage too small");
     encode_half_matrix(reinterpret_cast<CUtensorMap*>(out.tmap), out.values.ptr(), rows, cols, HG_BM);
+    out.ready = true;
+}
+
+void build_half_weight_interleaved(const QWeight& gate, const QWeight& up, HalfWeight& out, cudaStream_t s) {
+    if (!hgemm_tc_supported(gate) || !hgemm_tc_supported(up) || gate.cols != up.cols || gate.rows != up.rows)
+        throw std::runtime_error("build_half_weight_interleaved: unsupported pair of matrices");
+    const int64_t cols = gate.cols;
+    out.rows = 2 * gate.rows;
+    out.cols = cols;
+    out.values.alloc((size_t)out.rows * (size_t)cols * 2);
+    const QWeight* parts[2] = {&gate, &up};
+    for (int i = 0; i < 2; ++i) {
+        const int64_t blocks = parts[i]->rows * (cols / 256);
+        const int warps_per_cta = 8;
+        dequant_f16_kernel<<<(unsigned)((blocks + warps_per_cta - 1) / warps_per_cta), warps_per_cta * 32, 0, s>>>(
+            *parts[i], out.values.as<__half>() + i * cols, 2 * cols);
+        MK_LAUNCH_CHECK();
+    }
+    encode_half_matrix(reinterpret_cast<CUtensorMap*>(out.tmap), out.values.ptr(), out.rows, cols, HG_BM);
     out.ready = true;
 }
 
@@ -535,8 +583,25 @@ HgemmPlan hgemm_tc_plan(int64_t rows, int64_t cols, int T, int max_splits) {
     return pl;
 }
 
+namespace {
+int launch_hgemm_any(const HalfWeight& W, const __half* xh, int T, float* y, int ldy, float out_scale, float softcap,
+                     const HgemmScratch& ws, cudaStream_t s, int max_splits, int gated, __half* yh, int ldyh);
+}
+
 int launch_hgemm_tc(const HalfWeight& W, const __half* xh, int T, float* y, int ldy, float out_scale, float softcap,
                     const HgemmScratch& ws, cudaStream_t s, int max_splits) {
+    return launch_hgemm_any(W, xh, T, y, ldy, out_scale, softcap, ws, s, max_splits, 0, nullptr, 0);
+}
+
+void launch_hgemm_tc_gated(const HalfWeight& W, const __half* xh, int T, int act, __half* yh, int ldyh, const HgemmScratch& ws,
+                           cudaStream_t s) {
+    if (W.rows % 2 != 0 || yh == nullptr) throw std::runtime_error("launch_hgemm_tc_gated: needs an interleaved gate/up image and an output");
+    launch_hgemm_any(W, xh, T, nullptr, 0, 1.0f, 0.f, ws, s, 1, act == 0 ? 1 : 2, yh, ldyh);
+}
+
+namespace {
+int launch_hgemm_any(const HalfWeight& W, const __half* xh, int T, float* y, int ldy, float out_scale, float softcap,
+                     const HgemmScratch& ws, cudaStream_t s, int max_splits, int gated, __half* yh, int ldyh) {
     if (T <= 0) return 1;
     if (!W.ready) throw std::runtime_error("launch_hgemm_tc: the f16 image of the matrix was not built");
     if (xh == nullptr) throw std::runtime_error("launch_hgemm_tc: f16 activations missing");
@@ -562,6 +627,9 @@ int launch_hgemm_tc(const HalfWeight& W, const __half* xh, int T, float* y, int 
     p.kb_per_split = pl.kb_per_split;
     p.partial = ws.partial;
     p.status = ws.status;
+    p.gated = gated;
+    p.yh = yh;
+    p.ldyh = ldyh;
     const int grid = std::min(sm_count(), p.row_tiles * p.n_tiles * p.splits);
     const CUtensorMap& tw = *reinterpret_cast<const CUtensorMap*>(W.tmap);
     if (pl.bn == 256) launch_hg<256, 4>(tw, tx, p, grid, s);
@@ -569,5 +637,6 @@ int launch_hgemm_tc(const HalfWeight& W, const __half* xh, int T, float* y, int 
     else launch_hg<64, 8>(tw, tx, p, grid, s);
     return pl.splits;
 }
+}  // namespace
 
 }  // namespace mk

@@ -24,6 +24,10 @@ void build_half_weight(const QWeight& W, HalfWeight& out, cudaStream_t s);
 // projections: one GEMM then produces the concatenated outputs).
 void build_half_weight_stacked(const QWeight* const* parts, int n_parts, HalfWeight& out, cudaStream_t s);
 
+// The gate and up projections of a gated feed-forward in one image with their rows interleaved (row 2j = gate row j,
+// row 2j+1 = up row j), for launch_hgemm_tc_gated.
+void build_half_weight_interleaved(const QWeight& gate, const QWeight& up, HalfWeight& out, cudaStream_t s);
+
 // How a call is cut into work items (see hgemm_tc.cu); partial_floats is the scratch a split call needs.
 struct HgemmPlan {
     int bn = 0, row_tiles = 0, n_tiles = 0, splits = 1, kb_per_split = 0;
@@ -45,5 +49,12 @@ struct HgemmScratch {
 // partial sums at ws.partial[(s * T + t) * rows + n] and the consumer adds them for s = 0 .. S-1 in that order.
 int launch_hgemm_tc(const HalfWeight& W, const __half* xh, int T, float* y, int ldy, float out_scale, float softcap,
                     const HgemmScratch& ws, cudaStream_t s, int max_splits = 1);
+
+// Gated feed-forward front half in one kernel: with W an interleaved gate/up image (2F rows),
+// yh[t][j] = f16(act(sum_k xh[t][k] gate[j][k]) * sum_k xh[t][k] up[j][k]), j < F; act 0 = SiLU, otherwise tanh GELU.
+// The two sums are the f32 accumulators of the plain GEMM and the activation is evaluated like the separate SwiGLU
+// kernel does, so the halves written equal the ones that kernel derives from the plain GEMM's output.
+void launch_hgemm_tc_gated(const HalfWeight& W, const __half* xh, int T, int act, __half* yh, int ldyh, const HgemmScratch& ws,
+                           cudaStream_t s);
 
 }  // namespace mk

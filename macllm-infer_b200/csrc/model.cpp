@@ -494,8 +494,8 @@ void Model::build_half_cache() {
         build_half_weight(w.wo.w, w.wo.half, stream_);
         build_half_weight(w.wv.w, w.wv.half, stream_);  // V alone, for ticks whose Q and K come from the streamed matmul
         if (!ms_.layer[l].moe) {
-            const QWeight* gu[2] = {&w.gate.w, &w.up.w};
-            build_half_weight_stacked(gu, 2, w.gu_half, stream_);
+            // gate and up rows interleaved: the GEMM that uses this image finishes the gated activation itself
+            build_half_weight_interleaved(w.gate.w, w.up.w, w.gu_half, stream_);
             build_half_weight(w.down.w, w.down.half, stream_);
         }
     }
@@ -871,10 +871,18 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
             float* gp = gu_.as<float>();
             float* up = gp + ms_.ffn;
             int gu_splits = 1;
-            if (stream && xf.gs != nullptr) {
+            // wide ticks: one GEMM over the interleaved gate/up image writes act(gate) * up as f16, which is all the
+            // f16 GEMM of the down projection reads; no f32 gate|up round trip and no separate activation kernel
+            const bool gated_gemm = !(stream && xf.gs != nullptr) && w.gu_half.ready && w.down.half.ready && T >= hgemm_min_rows_ &&
+                                    xf.xh != nullptr && f16_T;
+            if (gated_gemm) {
+                prof_begin(KC_HGEMM, 2.0 * (double)w.gu_half.rows * (double)w.gu_half.cols + 2.0 * T * H + 2.0 * T * ms_.ffn,
+                           2.0 * T * (double)w.gu_half.rows * (double)w.gu_half.cols);
+                launch_hgemm_tc_gated(w.gu_half, xf.xh, T, ls.act, f_xh_.as<__half>(), ms_.ffn, hgemm_scratch(), stream_);
+                prof_end();
+                ++launches_;
+            } else if (stream && xf.gs != nullptr) {
                 gu_splits = matmul_stream(w.qs_gu, xf, T, gp, 2 * ms_.ffn, kMaxShares);
-            } else if (w.gu_half.ready && T >= hgemm_min_rows_ && xf.xh != nullptr) {
-                matmul_half(w.gu_half, xf, T, gp, 2 * ms_.ffn, 1.f, 0.f);
             } else if (w.gu_raw.size() > 0) {
                 DeviceWeight gu;  // [gate; up] share one buffer: one launch for both
                 gu.w = w.gate.w;
@@ -887,16 +895,18 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
             }
             int dkind = act_kind_of(w.down.w);
             ActQ xd = act_view(f_qs_, f_d_, f_bs_, f_xh_, T, ms_.ffn, dkind, f16_T, stream_T ? &f_gs_ : nullptr);
-            prof_begin(KC_ACTMUL, 9.0 * T * ms_.ffn, 0);
-        if (gu_splits > 1) {
-            const float* pg = tc_ws_.partial.as<float>();
-            launch_actmul_quant(pg, pg + ms_.ffn, 2 * ms_.ffn, T, ms_.ffn, ls.act, dkind, xd, nullptr, stream_, gu_splits,
-                                (int64_t)T * 2 * ms_.ffn);
-        } else {
-            launch_actmul_quant(gp, up, 2 * ms_.ffn, T, ms_.ffn, ls.act, dkind, xd, nullptr, stream_);
-        }
-        prof_end();
-            ++launches_;
+            if (!gated_gemm) {
+                prof_begin(KC_ACTMUL, 9.0 * T * ms_.ffn, 0);
+                if (gu_splits > 1) {
+                    const float* pg = tc_ws_.partial.as<float>();
+                    launch_actmul_quant(pg, pg + ms_.ffn, 2 * ms_.ffn, T, ms_.ffn, ls.act, dkind, xd, nullptr, stream_, gu_splits,
+                                        (int64_t)T * 2 * ms_.ffn);
+                } else {
+                    launch_actmul_quant(gp, up, 2 * ms_.ffn, T, ms_.ffn, ls.act, dkind, xd, nullptr, stream_);
+                }
+                prof_end();
+                ++launches_;
+            }
             if (stream && xd.gs != nullptr) pending_splits = matmul_stream(w.qs_down, xd, T, down_.as<float>(), H, kMaxShares);
             else if (w.down.half.ready && T >= hgemm_min_rows_ && xd.xh != nullptr) pending_splits = matmul_half(w.down.half, xd, T, down_.as<float>(), H, 1.f, 0.f, kMaxShares);
             else { matmul(w.down, xd, T, down_.as<float>(), H, 1.f, 0.f); pending_splits = 1; }

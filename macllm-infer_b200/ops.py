@@ -90,6 +90,18 @@ def actmul(gate, up, act: int = 0) -> np.ndarray:
     return out
 
 
+def gated_ffn(qtype: int, gate_w, up_w, F: int, cols: int, x, act: int = 0, iters: int = 0):
+    """f16(act(x @ gate.T) * (x @ up.T)) from one tensor-core GEMM over the interleaved gate/up image, as f32 [T][F];
+    with iters > 0 also the average milliseconds of the GEMM."""
+    x = _f32(x)
+    T = x.shape[0]
+    out = np.empty((T, F), dtype=np.float32)
+    ms = C.c_float(0)
+    capi.check(capi.lib().mk_k_gated_ffn(qtype, _p(gate_w), _p(up_w), F, cols, _p(x), T, act, _p(out), iters,
+                                         C.byref(ms) if iters > 0 else None))
+    return (out, float(ms.value)) if iters > 0 else out
+
+
 def argmax(logits) -> np.ndarray:
     logits = _f32(logits)
     B, V = logits.shape

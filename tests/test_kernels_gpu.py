@@ -88,6 +88,32 @@ def test_f16_image_gemm_matches_oracle(ops, orc, name, T, rows, cols):
     assert np.max(np.abs(got - other)) <= 2e-3 * scale
 
 
+@pytest.mark.parametrize("name", list(QTYPES))
+@pytest.mark.parametrize("act", [0, 1])
+@pytest.mark.parametrize("T,F,cols", [(9, 64, 256), (40, 96, 1024), (100, 1024, 2048), (257, 300, 1024), (301, 2048, 512), (2048, 672, 768)])
+def test_gated_gemm_equals_gemm_then_activation(ops, orc, name, act, T, F, cols):
+    """The wide-tick feed-forward front: gate and up rows interleaved in one f16 image, the activation and the product
+    finished in the GEMM's epilogue and written as f16.  Against the separate kernels (plain f16-image GEMM of each
+    matrix, then the SwiGLU kernel) the accumulators and the activation arithmetic are the same, so the halves must
+    be identical; against the oracle the usual f16-operand tolerance applies.  Odd T, F with a partial last tile."""
+    qtype = QTYPES[name]
+    gate_w = _weights(ops, qtype, F, cols, stream=7)
+    up_w = _weights(ops, qtype, F, cols, stream=8)
+    rng = np.random.default_rng(T + F)
+    x = rng.standard_normal((T, cols)).astype(np.float32)
+    got = ops.gated_ffn(qtype, gate_w, up_w, F, cols, x, act)
+    g = ops.qmatmul(qtype, gate_w, F, cols, x, 3)
+    u = ops.qmatmul(qtype, up_w, F, cols, x, 3)
+    want = ops.actmul(g, u, act).astype(np.float16).astype(np.float32)
+    assert np.array_equal(got, want)
+    og = orc.qmatmul(qtype, gate_w, F, cols, x, 1)
+    ou = orc.qmatmul(qtype, up_w, F, cols, x, 1)
+    ref = orc.act_mul(og, ou, act)
+    # gate and up each carry the f16-operand error of the GEMM (2e-3 * scale); the product adds them, then one f16 rounding
+    scale = np.sqrt(cols) * 0.02
+    assert np.max(np.abs(got - ref)) <= 2e-3 * scale * (2 * np.max(np.abs(og)) + np.max(np.abs(ou)) + 1)
+
+
 @pytest.mark.parametrize("T,rows,cols", [(9, 128, 256), (33, 300, 1024), (64, 2048, 2048), (64, 512, 5632), (40, 2560, 2048),
                                           (64, 1000, 11008), (17, 22016, 2048)])
 def test_streamed_q4k_matmul_matches_oracle(ops, orc, T, rows, cols):
