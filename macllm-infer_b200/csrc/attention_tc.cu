@@ -258,10 +258,18 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tc_kernel(AttnTcArgs a) {
             if (!live_r[h]) continue;
             int hq = item_r[h] / rows_per_head, r = item_r[h] - hq * rows_per_head;
             float inv = 1.0f / l_run[h];
-            float* o = a.out + (int64_t)(q_off + row0 + r) * ldo + (kvh * g + hq) * D;
+            const int64_t at = (int64_t)(q_off + row0 + r) * ldo + (kvh * g + hq) * D;
+            if (a.out != nullptr) {
 #pragma unroll
-            for (int j = 0; j < NT_O; ++j)
-                *reinterpret_cast<float2*>(o + j * 8 + 2 * tq) = make_float2(o_acc[j][2 * h] * inv, o_acc[j][2 * h + 1] * inv);
+                for (int j = 0; j < NT_O; ++j)
+                    *reinterpret_cast<float2*>(a.out + at + j * 8 + 2 * tq) = make_float2(o_acc[j][2 * h] * inv, o_acc[j][2 * h + 1] * inv);
+            }
+            if (a.out_h != nullptr) {
+#pragma unroll
+                for (int j = 0; j < NT_O; ++j)
+                    *reinterpret_cast<__half2*>(a.out_h + at + j * 8 + 2 * tq) =
+                        __floats2half2_rn(o_acc[j][2 * h] * inv, o_acc[j][2 * h + 1] * inv);
+            }
         }
     } else {
         // unnormalised partial of this key share: [entry][kv head][16 items][D], plus (max, sum) per item
@@ -507,7 +515,11 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
         const int col0 = kvh * g * D;
         const bool fuse_quant = a.qout.qs != nullptr;  // uniform
         if (!fuse_quant) {
-            for (int idx = tid; idx < g * D; idx += 128) a.out[row * a.q_heads * D + col0 + idx] = value_of(idx);
+            for (int idx = tid; idx < g * D; idx += 128) {
+                float v = value_of(idx);
+                if (a.out != nullptr) a.out[row * a.q_heads * D + col0 + idx] = v;
+                if (a.out_h != nullptr) a.out_h[row * a.q_heads * D + col0 + idx] = __float2half_rn(v);
+            }
             return;
         }
         for (int idx = tid; idx < g * D; idx += 128) {
@@ -726,6 +738,8 @@ int launch_paged_attention_tc(const AttnTcArgs& a_in, cudaStream_t s) {
     AttnTcArgs a = a_in;
     if (!attention_tc_supported(a.q_heads, a.kv_heads, a.d, a.block_tokens, true))
         throw std::runtime_error("launch_paged_attention_tc: unsupported shape");
+    if (a.out == nullptr && a.out_h == nullptr && a.qout.qs == nullptr) throw std::runtime_error("launch_paged_attention_tc: no output");
+    if (a.out == nullptr && a.n_dec_lanes > 0) throw std::runtime_error("launch_paged_attention_tc: the separate merge pass writes f32 rows");
     a.bt_shift = 0;
     while ((1 << a.bt_shift) < a.block_tokens) ++a.bt_shift;
     int warps = attention_tc_warps(a.q_heads, a.kv_heads);

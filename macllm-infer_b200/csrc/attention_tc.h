@@ -9,6 +9,8 @@ struct AttnTcArgs {
     const float* q = nullptr;   // [T] rows of q_heads*d f32 values, row stride ldq
     int ldq = 0;                // 0 = q_heads*d
     float* out = nullptr;       // [T][q_heads*d] f32
+    __half* out_h = nullptr;    // optional: the same rows rounded to f16 (what an f16 GEMM of the output projection reads);
+                                // with out_h set, `out` may be null
     const void* k_pool = nullptr;  // f16 pages [kv_heads][block_tokens][d], page order per kv_page_index
     const void* v_pool = nullptr;
     const LaneHeader* hdr = nullptr;

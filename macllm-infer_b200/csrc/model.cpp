@@ -692,7 +692,22 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         const bool stream = stream_T && xa.gs != nullptr;
         const int kMaxShares = 16;
         int qk_splits = 1, v_splits = 1;
-        if (stream) {
+        bool qkv_joint = false;
+        // Narrow ticks: which projections leave the streamed Q4_K matmul for the f16 images with split-K.  Measured on
+        // 64-lane decode ticks of the 3 B shape: [q; k; v] as ONE launch over the stacked image beats the streamed
+        // Q|K launch plus a separate V launch, and the long-K down projection is a little faster on its image; the
+        // output projection and gate|up stay on the streamed blocks (a quarter of the bytes).
+        // MACLLM_B200_DECODE_HALF_MASK overrides: 1 q|k|v, 2 attention output, 4 gate|up (implies 8), 8 down.
+        static const int half_mask = [] {
+            const char* e = getenv("MACLLM_B200_DECODE_HALF_MASK");
+            int m = e != nullptr ? atoi(e) : 9;
+            return (m & 4) ? (m | 8) : m;
+        }();
+        const bool stream_o = stream && !(half_mask & 2), stream_gu = stream && !(half_mask & 4), stream_down = stream && !(half_mask & 8);
+        if (stream && (half_mask & 1) && w.qkv_half.ready) {
+            qk_splits = v_splits = matmul_half(w.qkv_half, xa, T, qp, QKVW, 1.f, 0.f, kMaxShares);
+            qkv_joint = qk_splits > 1;
+        } else if (stream) {
             qk_splits = matmul_stream(w.qs_qk, xa, T, qp, QKVW, kMaxShares);
             v_splits = matmul_half(w.wv.half, xa, T, vp, QKVW, 1.f, 0.f, kMaxShares, v_partial_.as<float>(), v_partial_.size() / 4);
         } else if (w.qkv_half.ready && T >= hgemm_min_rows_ && xa.xh != nullptr) {
@@ -716,7 +731,16 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         ra.k = kp;
         ra.v = vp;
         ra.ldq = ra.ldk = ra.ldv = QKVW;
-        if (qk_splits > 1) {
+        if (qkv_joint) {
+            // shares of whole [q | k | v] rows in the split-K scratch
+            ra.q = tc_ws_.partial.as<float>();
+            ra.k = ra.q + AW;
+            ra.v = ra.k + KW;
+            ra.qk_splits = ra.v_splits = qk_splits;
+            ra.qk_split_stride = ra.v_split_stride = (int64_t)T * QKVW;
+            ra.q_out = qp;
+            ra.ldq_out = QKVW;
+        } else if (qk_splits > 1) {
             // shares of [q | k] rows of width AW + KW in the split-K scratch; the rotated q goes to its usual place
             ra.q = tc_ws_.partial.as<float>();
             ra.k = ra.q + AW;
@@ -726,7 +750,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
             ra.q_out = qp;
             ra.ldq_out = QKVW;
         }
-        if (v_splits > 1) {
+        if (!qkv_joint && v_splits > 1) {
             ra.v = v_partial_.as<float>();
             ra.ldv = KW;
             ra.v_splits = v_splits;
@@ -757,6 +781,10 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         const int okind = act_kind_of(w.wo.w);
         ActQ xo = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, AW, okind, f16_T, stream_T ? &a_gs_ : nullptr);
         const bool fuse_attn_quant = attn_tc_ && n_attn_tiles == 0 && n_attn_entries > 0 && (AW / ms_.kv_heads) % 256 == 0;
+        // wide ticks: the output projection is an f16 GEMM that reads nothing but the f16 rows, so the attention kernels
+        // write those and the separate quantisation pass is dropped
+        const bool attn_half_out = attn_tc_ && !fuse_attn_quant && !(stream_o && xo.gs != nullptr) && w.wo.half.ready &&
+                                   T >= hgemm_min_rows_ && xo.xh != nullptr && n_attn_dec == 0;
         AttnArgs at;
         at.q = qp;
         at.ldq = QKVW;
@@ -821,6 +849,9 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
                 ta.qout = xo;
                 ta.qkind = okind;
                 ta.out = nullptr;  // nothing reads the f32 rows of a pure decode tick
+            } else if (attn_half_out) {
+                ta.out_h = xo.xh;
+                ta.out = nullptr;
             }
             launches_ += launch_paged_attention_tc(ta, stream_);
         } else {
@@ -829,7 +860,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         }
         prof_end();
         // output projection
-        if (!fuse_attn_quant) {
+        if (!fuse_attn_quant && !attn_half_out) {
             NormQuantArgs no;
             no.h = attn_.as<float>();
             no.rows = T;
@@ -843,7 +874,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         }
         // split-K shares of the two long-K projections are summed by the residual kernel that consumes them
         int wo_splits = 1;
-        if (stream && xo.gs != nullptr) wo_splits = matmul_stream(w.qs_o, xo, T, proj_.as<float>(), H, kMaxShares);
+        if (stream_o && xo.gs != nullptr) wo_splits = matmul_stream(w.qs_o, xo, T, proj_.as<float>(), H, kMaxShares);
         else if (w.wo.half.ready && T >= hgemm_min_rows_ && xo.xh != nullptr) wo_splits = matmul_half(w.wo.half, xo, T, proj_.as<float>(), H, 1.f, 0.f, kMaxShares);
         else matmul(w.wo, xo, T, proj_.as<float>(), H, 1.f, 0.f);
         // residual add + FFN norm + quantise (finish_mixer, src/decoder.rs:2684-2699)
@@ -873,7 +904,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
             int gu_splits = 1;
             // wide ticks: one GEMM over the interleaved gate/up image writes act(gate) * up as f16, which is all the
             // f16 GEMM of the down projection reads; no f32 gate|up round trip and no separate activation kernel
-            const bool gated_gemm = !(stream && xf.gs != nullptr) && w.gu_half.ready && w.down.half.ready && T >= hgemm_min_rows_ &&
+            const bool gated_gemm = !(stream_gu && xf.gs != nullptr) && w.gu_half.ready && w.down.half.ready && T >= hgemm_min_rows_ &&
                                     xf.xh != nullptr && f16_T;
             if (gated_gemm) {
                 prof_begin(KC_HGEMM, 2.0 * (double)w.gu_half.rows * (double)w.gu_half.cols + 2.0 * T * H + 2.0 * T * ms_.ffn,
@@ -881,7 +912,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
                 launch_hgemm_tc_gated(w.gu_half, xf.xh, T, ls.act, f_xh_.as<__half>(), ms_.ffn, hgemm_scratch(), stream_);
                 prof_end();
                 ++launches_;
-            } else if (stream && xf.gs != nullptr) {
+            } else if (stream_gu && xf.gs != nullptr) {
                 gu_splits = matmul_stream(w.qs_gu, xf, T, gp, 2 * ms_.ffn, kMaxShares);
             } else if (w.gu_raw.size() > 0) {
                 DeviceWeight gu;  // [gate; up] share one buffer: one launch for both
@@ -907,7 +938,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
                 prof_end();
                 ++launches_;
             }
-            if (stream && xd.gs != nullptr) pending_splits = matmul_stream(w.qs_down, xd, T, down_.as<float>(), H, kMaxShares);
+            if (stream_down && xd.gs != nullptr) pending_splits = matmul_stream(w.qs_down, xd, T, down_.as<float>(), H, kMaxShares);
             else if (w.down.half.ready && T >= hgemm_min_rows_ && xd.xh != nullptr) pending_splits = matmul_half(w.down.half, xd, T, down_.as<float>(), H, 1.f, 0.f, kMaxShares);
             else { matmul(w.down, xd, T, down_.as<float>(), H, 1.f, 0.f); pending_splits = 1; }
         } else {
