@@ -341,7 +341,7 @@ void Model::rope_tables_for(double theta, const float*& cos_t, const float*& sin
 // ---------------------------------------------------------------------------- profiling
 
 static const char* kclass_names[] = {"qgemm_tc", "hgemm_tc", "qstream_tc", "qgemv", "paged_attention", "add_norm_quant", "rope_kv_scatter", "actmul_quant",
-                                     "embed", "build_batch", "argmax", "moe"};
+                                     "embed", "build_batch", "argmax", "moe", "hgemm_tc_splitk"};
 
 void Model::profile_enable(bool on) {
     profiling_ = on;
@@ -424,7 +424,9 @@ HgemmScratch Model::hgemm_scratch() const {
 
 int Model::matmul_half(const HalfWeight& W, const ActQ& x, int T, float* y, int ldy, float scale, float softcap, int max_splits,
                        float* partial, size_t partial_floats) {
-    prof_begin(KC_HGEMM, 2.0 * (double)W.rows * (double)W.cols + 2.0 * T * W.cols + 4.0 * T * W.rows, 2.0 * T * (double)W.rows * (double)W.cols);
+    // narrow ticks run the 64-token instantiation with K shared out over CTAs: a weight-streaming kernel, accounted apart
+    prof_begin(T <= 64 ? KC_HGEMM_NARROW : KC_HGEMM, 2.0 * (double)W.rows * (double)W.cols + 2.0 * T * W.cols + 4.0 * T * W.rows,
+               2.0 * T * (double)W.rows * (double)W.cols);
     HgemmScratch ws = hgemm_scratch();
     if (partial != nullptr) {
         ws.partial = partial;

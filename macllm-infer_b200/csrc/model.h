@@ -104,7 +104,7 @@ private:
     bool timed_ = false;
     int64_t launches_ = 0, h2d_bytes_ = 0, d2h_bytes_ = 0;
     // profiling: one event pair per launch group, resolved after the tick's barrier
-    enum KClass { KC_GEMM_TC = 0, KC_HGEMM, KC_QSTREAM, KC_GEMV, KC_ATTN, KC_NORM_QUANT, KC_ROPE_KV, KC_ACTMUL, KC_EMBED, KC_BATCH, KC_SAMPLE, KC_MOE, KC_COUNT };
+    enum KClass { KC_GEMM_TC = 0, KC_HGEMM, KC_QSTREAM, KC_GEMV, KC_ATTN, KC_NORM_QUANT, KC_ROPE_KV, KC_ACTMUL, KC_EMBED, KC_BATCH, KC_SAMPLE, KC_MOE, KC_HGEMM_NARROW, KC_COUNT };
     struct ProfSpan { int cls; double bytes, flops; cudaEvent_t a, b; };
     bool profiling_ = false;
     std::vector<ProfSpan> spans_;

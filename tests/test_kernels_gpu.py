@@ -148,6 +148,18 @@ def test_matmul_timing_entry_on_the_benchmark_shapes(ops, label, T, rows, cols, 
     print(label, "ms per launch", ms, "TFLOP/s", 2.0 * T * rows * cols / ms / 1e9)
 
 
+def test_gated_gemm_timing_entry_on_the_benchmark_shape(ops):
+    """The gate|up GEMM of one 2048-token tick of the headline workload with the activation in its epilogue (operands
+    resident, L2 flushed before every launch).  Also the command the profiler captures of this kernel run."""
+    F, cols, T = 11008, 2048, 2048
+    gate_w = _weights(ops, 12, F, cols, stream=8)
+    up_w = _weights(ops, 12, F, cols, stream=9)
+    x = np.random.default_rng(1).standard_normal((T, cols)).astype(np.float32)
+    out, ms = ops.gated_ffn(12, gate_w, up_w, F, cols, x, 0, iters=3)
+    assert ms > 0.0 and np.isfinite(out).all()
+    print("gated prefill_gate_up ms per launch", ms, "TFLOP/s", 2.0 * T * 2 * F * cols / ms / 1e9)
+
+
 @pytest.mark.parametrize("name", ["q4_k", "q6_k", "q8_0", "f32"])
 def test_embed_rows_exact(ops, orc, name):
     qtype = {"f32": 0, **QTYPES}[name]
