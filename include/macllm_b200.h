@@ -445,6 +445,18 @@ int32_t mk_k_argmax(const float* logits, int32_t B, int32_t vocab, uint32_t* out
 /* selected_softmax_routes (src/decoder.rs:448-554): sel_experts / sel_weights are [T][k], best first. */
 int32_t mk_k_moe_route(const float* logits, int32_t T, int32_t experts, int32_t k, int32_t* sel_experts, float* sel_weights);
 
+/* One rank's launch of the expert-parallel combine + exchange kernel (the fused form behind mk_model_ep_init) with the
+ * exchange blocks of all `ranks` ranks allocated on ONE GPU, so that its data path and its bounded wait can be checked
+ * without peers.  expert_out is [T*k][hidden] with pair p = (token p / k, choice p % k) at row p; sel and weights are
+ * [T][k]; this rank holds experts [e_lo, e_hi).  With deliver != 0 the rows peer_rows[r] ([ranks][T][hidden], row
+ * `rank` ignored) and the flags of every other rank are placed in this rank's block before each of the `epochs`
+ * launches (epoch numbers 1, 2, ...: the two buffers alternate); with deliver == 0 nothing sets the flags and the
+ * kernel gives up after wait_ms.  out is [T][hidden]; pushed is [ranks][T][hidden], the rows the last launch stored
+ * into each rank's block; *status_out is the kernel's status word (0, or 0x4550000 | peer after a wait ran out). */
+int32_t mk_k_moe_combine_exchange(const float* expert_out, const int32_t* sel, const float* weights, int32_t T, int32_t k,
+                                  int32_t hidden, int32_t e_lo, int32_t e_hi, int32_t ranks, int32_t rank, const float* peer_rows,
+                                  int32_t deliver, int32_t wait_ms, int32_t epochs, float* out, float* pushed, int32_t* status_out);
+
 #ifdef __cplusplus
 }
 #endif

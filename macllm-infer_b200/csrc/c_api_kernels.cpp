@@ -483,4 +483,61 @@ int32_t mk_k_moe_route(const float* logits, int32_t T, int32_t experts, int32_t 
     });
 }
 
+int32_t mk_k_moe_combine_exchange(const float* expert_out, const int32_t* sel, const float* weights, int32_t T, int32_t k,
+                                  int32_t hidden, int32_t e_lo, int32_t e_hi, int32_t ranks, int32_t rank, const float* peer_rows,
+                                  int32_t deliver, int32_t wait_ms, int32_t epochs, float* out, float* pushed, int32_t* status_out) {
+    return guarded([&] {
+        require_device();
+        if (ranks < 2 || ranks > kEpMaxRanks || rank < 0 || rank >= ranks || T <= 0 || epochs <= 0 || wait_ms <= 0 || wait_ms > 2000)
+            throw std::runtime_error("mk_k_moe_combine_exchange: arguments out of range");
+        const size_t pairs = (size_t)T * k, row_floats = (size_t)T * hidden;
+        DevBuf d_eo(pairs * hidden * 4), d_sel(pairs * 4), d_w(pairs * 4), d_pos(pairs * 4), d_out(row_floats * 4), d_status(4);
+        d_eo.upload(expert_out, pairs * hidden * 4);
+        d_sel.upload(sel, pairs * 4);
+        d_w.upload(weights, pairs * 4);
+        std::vector<int32_t> pos(pairs);
+        for (size_t i = 0; i < pairs; ++i) pos[i] = (int32_t)i;
+        d_pos.upload(pos.data(), pairs * 4);
+        d_status.zero(nullptr);
+        // every rank's block, laid out as EpComm::open_exchange does: gather [2][ranks][T*hidden] floats, then flags [2][ranks][T]
+        const size_t gather_bytes = (size_t)2 * ranks * row_floats * 4, flag_bytes = (size_t)2 * ranks * T * 4;
+        std::vector<DevBuf> blocks((size_t)ranks);
+        EpPeers peers;
+        peers.rank = rank;
+        peers.ranks = ranks;
+        peers.max_tokens = T;
+        peers.slot_floats = (int64_t)row_floats;
+        for (int r = 0; r < ranks; ++r) {
+            blocks[(size_t)r].alloc(gather_bytes + flag_bytes);
+            blocks[(size_t)r].zero(nullptr);
+            peers.gather[r] = blocks[(size_t)r].as<float>();
+            peers.flags[r] = reinterpret_cast<uint32_t*>(static_cast<char*>(blocks[(size_t)r].ptr()) + gather_bytes);
+        }
+        MK_CUDA(cudaDeviceSynchronize());
+        for (int e = 1; e <= epochs; ++e) {
+            const int buf = e & 1;
+            if (deliver != 0) {
+                std::vector<uint32_t> flags((size_t)T, (uint32_t)e);
+                for (int r = 0; r < ranks; ++r) {
+                    if (r == rank) continue;
+                    MK_CUDA(cudaMemcpy(peers.gather[rank] + ((size_t)buf * ranks + r) * row_floats, peer_rows + (size_t)r * row_floats,
+                                       row_floats * 4, cudaMemcpyHostToDevice));
+                    MK_CUDA(cudaMemcpy(peers.flags[rank] + ((size_t)buf * ranks + r) * T, flags.data(), (size_t)T * 4, cudaMemcpyHostToDevice));
+                }
+            }
+            launch_moe_combine_exchange(d_eo.as<float>(), d_sel.as<int32_t>(), d_w.as<float>(), d_pos.as<int32_t>(), T, k, hidden, e_lo,
+                                        e_hi, peers, (uint32_t)e, d_out.as<float>(), d_status.as<int32_t>(), nullptr,
+                                        (uint64_t)wait_ms * 1000000ull);
+            MK_CUDA(cudaDeviceSynchronize());
+        }
+        d_out.download(out, row_floats * 4);
+        d_status.download(status_out, 4);
+        const int buf = epochs & 1;
+        for (int r = 0; r < ranks; ++r)
+            MK_CUDA(cudaMemcpy(pushed + (size_t)r * row_floats, peers.gather[r] + ((size_t)buf * ranks + rank) * row_floats, row_floats * 4,
+                               cudaMemcpyDeviceToHost));
+        MK_CUDA(cudaDeviceSynchronize());
+    });
+}
+
 }  // extern "C"

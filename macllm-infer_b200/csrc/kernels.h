@@ -154,11 +154,12 @@ void launch_moe_combine(const float* expert_out, const int32_t* sel_experts, con
 void launch_ep_sum(const float* gathered, int ranks, int64_t count, float* out, cudaStream_t s);
 // Expert parallelism, fused: launch_moe_combine of this rank's experts, the exchange of the partial rows with the other
 // ranks through peer stores into their exchange blocks (EpComm::open_exchange), and the sum in rank order, in one
-// kernel.  All ranks call it with the same epoch.  A peer that does not deliver within a few seconds leaves a non-zero
-// code in *status and the forward's result is not to be used.
+// kernel.  All ranks call it with the same epoch.  A peer that does not deliver within wait_ns (5 s unless told
+// otherwise) leaves a non-zero code (0x4550000 | peer) in *status and the forward's result is not to be used.
+constexpr uint64_t kEpWaitNs = 5ull * 1000 * 1000 * 1000;
 void launch_moe_combine_exchange(const float* expert_out, const int32_t* sel_experts, const float* sel_weights,
                                  const int32_t* pos_of_pair, int T, int k, int hidden, int e_lo, int e_hi, const EpPeers& peers,
-                                 uint32_t epoch, float* out, int32_t* status, cudaStream_t s);
+                                 uint32_t epoch, float* out, int32_t* status, cudaStream_t s, uint64_t wait_ns = kEpWaitNs);
 
 // Small helpers
 void launch_add_inplace(float* h, const float* a, float scale, int64_t n, cudaStream_t s);

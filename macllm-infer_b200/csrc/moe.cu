@@ -87,7 +87,6 @@ __global__ void ep_sum_kernel(const float4* gathered, int ranks, int64_t count4,
     }
 }
 
-constexpr uint64_t kEpWaitNs = 5ull * 1000 * 1000 * 1000;  // a peer that is 5 s late counts as lost
 
 __device__ __forceinline__ uint64_t global_ns() {
     uint64_t t;
@@ -114,7 +113,7 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 __global__ void __launch_bounds__(256) moe_combine_exchange_kernel(const float* __restrict__ expert_out, const int32_t* __restrict__ sel,
                                                                    const float* __restrict__ w, const int32_t* __restrict__ pos_of_pair,
                                                                    int T, int k, int hidden, int e_lo, int e_hi, EpPeers P, uint32_t epoch,
-                                                                   float* __restrict__ out, int32_t* status) {
+                                                                   uint64_t wait_ns, float* __restrict__ out, int32_t* status) {
     __shared__ int order[32];
     __shared__ int lost;
     const int R = P.ranks, me = P.rank, buf = (int)(epoch & 1u);
@@ -157,7 +156,7 @@ __global__ void __launch_bounds__(256) moe_combine_exchange_kernel(const float* 
             const uint32_t* f = P.flags[me] + (int64_t)(buf * R + threadIdx.x) * P.max_tokens + t;
             const uint64_t t0 = global_ns();
             while (ld_acquire_sys(f) != epoch) {
-                if (global_ns() - t0 > kEpWaitNs) {
+                if (global_ns() - t0 > wait_ns) {
                     atomicExch(status, 0x4550000 | (int)threadIdx.x);
                     lost = 1;
                     break;
@@ -186,7 +185,7 @@ __global__ void __launch_bounds__(256) moe_combine_exchange_kernel(const float* 
 
 void launch_moe_combine_exchange(const float* expert_out, const int32_t* sel_experts, const float* sel_weights,
                                  const int32_t* pos_of_pair, int T, int k, int hidden, int e_lo, int e_hi, const EpPeers& peers,
-                                 uint32_t epoch, float* out, int32_t* status, cudaStream_t s) {
+                                 uint32_t epoch, float* out, int32_t* status, cudaStream_t s, uint64_t wait_ns) {
     if (T <= 0) return;
     if (k > 32) throw std::runtime_error("launch_moe_combine_exchange: more than 32 experts per token");
     if (hidden % 4 != 0 || (int64_t)T * hidden > peers.slot_floats || T > peers.max_tokens)
@@ -194,7 +193,7 @@ void launch_moe_combine_exchange(const float* expert_out, const int32_t* sel_exp
     // one CTA per SM at most: every CTA is resident, so pass 1 of all tokens runs without waiting on anything
     int grid = std::min(T, 148);
     moe_combine_exchange_kernel<<<grid, 256, 0, s>>>(expert_out, sel_experts, sel_weights, pos_of_pair, T, k, hidden, e_lo, e_hi, peers,
-                                                     epoch, out, status);
+                                                     epoch, wait_ns, out, status);
     MK_LAUNCH_CHECK();
 }
 

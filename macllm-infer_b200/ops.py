@@ -119,6 +119,26 @@ def moe_route(logits, k: int):
     return sel, w
 
 
+def moe_combine_exchange(expert_out, sel, weights, e_lo: int, e_hi: int, ranks: int, rank: int, peer_rows=None, wait_ms: int = 50,
+                         epochs: int = 1):
+    """One rank's launch(es) of the fused expert-parallel combine + exchange kernel with every rank's exchange block on
+    this GPU.  peer_rows [ranks][T][hidden] plays the other ranks' deliveries; None leaves their flags unset, so the
+    kernel's bounded wait runs out.  Returns (out [T][hidden], pushed [ranks][T][hidden], status word)."""
+    sel = np.ascontiguousarray(sel, dtype=np.int32)
+    weights = _f32(weights)
+    T, k = sel.shape
+    expert_out = _f32(expert_out)
+    hidden = expert_out.shape[1]
+    out = np.empty((T, hidden), dtype=np.float32)
+    pushed = np.empty((ranks, T, hidden), dtype=np.float32)
+    status = C.c_int32(0)
+    rows = _f32(peer_rows) if peer_rows is not None else None
+    capi.check(capi.lib().mk_k_moe_combine_exchange(_p(expert_out), _p(sel), _p(weights), T, k, hidden, e_lo, e_hi, ranks, rank,
+                                                    _p(rows) if rows is not None else None, 1 if rows is not None else 0, wait_ms,
+                                                    epochs, _p(out), _p(pushed), C.byref(status)))
+    return out, pushed, int(status.value)
+
+
 def attention_step(q, k, v, k_pool, v_pool, tables, start_pos, lane_len, *, q_heads, kv_heads, head_dim, block_tokens,
                    layers, layer, scale, softcap=0.0, window=0, cos_table=None, sin_table=None, rotary_dim=0,
                    q_norm_w=None, k_norm_w=None, norm_eps=1e-6, kernel=0):

@@ -361,3 +361,55 @@ def test_attention_nope_layer_leaves_queries_unrotated(ops, orc):
     res = ops.attention_step(q, k, v, k_pool, v_pool, tables, [3, 20], [5, 1], q_heads=q_heads, kv_heads=kv_heads,
                              head_dim=d, block_tokens=bt, layers=1, layer=0, scale=0.125)
     assert np.array_equal(res["q_rot"], q)
+
+
+def _expert_partial(expert_out, sel, weights, e_lo, e_hi):
+    """A token's choices held by one rank, weighted and added in ascending expert order, in f32."""
+    T, k = sel.shape
+    out = np.zeros((T, expert_out.shape[1]), dtype=np.float32)
+    for t in range(T):
+        for c in np.argsort(sel[t], kind="stable"):
+            if e_lo <= sel[t, c] < e_hi:
+                out[t] = out[t] + expert_out[t * k + c] * weights[t, c]
+    return out
+
+
+@pytest.mark.parametrize("T,ranks,rank,epochs", [(1, 2, 0, 1), (37, 4, 2, 3), (300, 2, 1, 2)])
+def test_expert_exchange_kernel_combines_pushes_and_adds_in_rank_order(ops, T, ranks, rank, epochs):
+    """The fused expert-parallel kernel from one rank's side, every rank's exchange block on this GPU: its own partial
+    rows must land in all blocks, and the result must be the ranks' rows added in rank order, bit for bit; more than
+    148 tokens (several rows per CTA) and several epochs (alternating buffers) included."""
+    k, hidden, experts = 4, 512, 16
+    rng = np.random.default_rng(T)
+    sel = np.stack([rng.choice(experts, k, replace=False) for _ in range(T)]).astype(np.int32)
+    weights = rng.random((T, k)).astype(np.float32)
+    expert_out = rng.standard_normal((T * k, hidden)).astype(np.float32)
+    per = experts // ranks
+    e_lo, e_hi = rank * per, (rank + 1) * per
+    peer_rows = rng.standard_normal((ranks, T, hidden)).astype(np.float32)
+    out, pushed, status = ops.moe_combine_exchange(expert_out, sel, weights, e_lo, e_hi, ranks, rank, peer_rows, epochs=epochs)
+    assert status == 0
+    partial = _expert_partial(expert_out, sel, weights, e_lo, e_hi)
+    for r in range(ranks):
+        assert np.array_equal(pushed[r], partial)
+    rows = peer_rows.copy()
+    rows[rank] = partial
+    want = rows[0]
+    for r in range(1, ranks):
+        want = want + rows[r]
+    assert np.array_equal(out, want)
+
+
+def test_expert_exchange_kernel_gives_up_when_a_peer_never_delivers(ops):
+    """Nothing sets the other rank's flags: the wait is bounded (50 ms here), the kernel returns, the status word names
+    the missing peer and the context stays usable."""
+    T, k, hidden = 5, 2, 256
+    rng = np.random.default_rng(0)
+    sel = np.stack([rng.choice(8, k, replace=False) for _ in range(T)]).astype(np.int32)
+    weights = rng.random((T, k)).astype(np.float32)
+    expert_out = rng.standard_normal((T * k, hidden)).astype(np.float32)
+    out, pushed, status = ops.moe_combine_exchange(expert_out, sel, weights, 0, 4, 2, 0, None, wait_ms=50)
+    assert status == (0x4550000 | 1)
+    assert np.array_equal(pushed[1], _expert_partial(expert_out, sel, weights, 0, 4))
+    # the device still answers
+    assert ops.argmax(np.eye(3, dtype=np.float32)).tolist() == [0, 1, 2]
