@@ -14,6 +14,7 @@
 // as stored.
 #include "kernels.h"
 #include "attention_tc.h"
+#include "rope_head.cuh"
 #include "quant_blocks.cuh"
 #include <algorithm>
 
@@ -322,6 +323,33 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
     const int lane_id = e0.x, split = e0.y, n_splits = e0.z, start_pos = e0.w, table_off = e1.x, q_off = e1.y, first_entry = e1.z;
     const int ldq = a.ldq > 0 ? a.ldq : a.q_heads * D;
 
+    // Rows straight from the projection's output (see AttnTcArgs::fused_rope): one warp per head, the head vector staged
+    // in f32; the group's query heads, and in the CTA that walks the lane's newest keys also the new K and V rows, which
+    // reach the pool before any tile is requested (block-wide barrier below).
+    __shared__ __align__(16) float head_stage[4][D];
+    auto prepare_head = [&](int kind, int item) {  // kind 0: query head `item` of the group; 1 / 2: the new K / V row
+        float* xs = head_stage[warp];
+        rope_head_prepare(a.rk, kind, kind == 0 ? kvh * g + item : kvh, q_off, start_pos, xs, lane);
+        if (kind == 0) {
+            for (int i = lane; i < D; i += 32) Qs[item * DP + i] = __float2half_rn(xs[i]);
+        } else {
+            const int64_t blk = a.tables[table_off + (start_pos >> a.bt_shift)];
+            const int64_t base = ((kv_page_index(blk, a.layer, a.layers, a.pool_blocks) * a.kv_heads + kvh) * a.block_tokens +
+                                  (start_pos & (a.block_tokens - 1))) * (int64_t)D;
+            __half* pool = reinterpret_cast<__half*>(kind == 1 ? a.rk.k_pool : a.rk.v_pool);
+            for (int i = lane; i < D; i += 32) pool[base + i] = __float2half_rn(xs[i]);
+        }
+        __syncwarp();
+    };
+    if (a.fused_rope) {
+        for (int i = tid; i < (16 - g) * CHUNKS; i += 128) {
+            int item = g + i / CHUNKS, c = (i % CHUNKS) * 8;
+            *reinterpret_cast<uint4*>(Qs + item * DP + c) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        const int n_heads = g + (split == n_splits - 1 ? 2 : 0);
+        for (int h = warp; h < n_heads; h += 4) prepare_head(h < g ? 0 : (h == g ? 1 : 2), h);
+        __syncthreads();  // the new K / V rows are visible to every tile load of this CTA
+    } else {
     // the group's query heads -> rows 0..g-1 of the A operand, the rest zero
     for (int i = tid; i < 16 * CHUNKS; i += 128) {
         int item = i / CHUNKS, c = (i - item * CHUNKS) * 8;
@@ -337,6 +365,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnTcArgs a) {
             h[0] = h[1] = h[2] = h[3] = __floats2half2_rn(0.f, 0.f);
         }
         *reinterpret_cast<uint4*>(Qs + item * DP + c) = *reinterpret_cast<uint4*>(h);
+    }
     }
 
     const int p = start_pos;  // the query's position

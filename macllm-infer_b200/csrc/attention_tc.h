@@ -29,6 +29,12 @@ struct AttnTcArgs {
     // matmul that follows; needs (q_heads / kv_heads) * d to be a multiple of 256.  With qout set, `out` may be null.
     ActQ qout;
     int qkind = ACT_Q8K;
+    // optional (ticks of one-token lanes only): the kernel prepares its own rows from the projection's output - share
+    // summation, per-head norm and rotation of the group's query heads, and, in the CTA that walks the lane's last keys,
+    // of the new K and V rows, which it writes to the pools (rk.k_pool / rk.v_pool) before it fetches any tile - so no
+    // separate RoPE + scatter launch is needed.  `q` is not read then.
+    int fused_rope = 0;
+    RopeKvArgs rk;
     int32_t* counters = nullptr;  // [lanes][kv_heads], zero before the first call; every call leaves them zero
     int q_heads = 0, kv_heads = 0, d = 0, block_tokens = 16, layers = 0, layer = 0;
     int64_t pool_blocks = 0;  // see kv_page_index

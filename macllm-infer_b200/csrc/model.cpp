@@ -664,6 +664,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
     const float* pending = nullptr;        // branch output not yet added to the residual stream
     const float* pending_post = nullptr;   // its sandwich post-norm weight, if any
     int pending_splits = 1;                // > 1: `pending` is that many split-K partials, T * H floats apart
+    const bool fuse_rope_enabled = [] { const char* e = getenv("MACLLM_B200_FUSE_ROPE"); return e == nullptr || strcmp(e, "0") != 0; }();
     for (int l = 0; l < ms_.layers; ++l) {
         LayerWeights& w = lw_[(size_t)l];
         const LayerSpec& ls = ms_.layer[(size_t)l];
@@ -774,10 +775,15 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         ra.layers = ms_.layers;
         ra.pool_blocks = pool_->max_blocks();
         ra.layer = l;
-        prof_begin(KC_ROPE_KV, 4.0 * T * (2 * AW + 2 * KW) + (cfg_.kv_f16 ? 2.0 : 4.0) * 2 * T * KW, 0);
-        launch_rope_kv(ra, stream_);
-        prof_end();
-        ++launches_;
+        // ticks of one-token lanes only: the attention kernel prepares its own query rows and writes the new K / V rows
+        // itself (same arithmetic, see rope_head.cuh), so the separate launch is dropped.  MACLLM_B200_FUSE_ROPE=0 keeps it.
+        const bool fuse_rope = attn_tc_ && cfg_.kv_f16 && n_attn_tiles == 0 && n_attn_entries > 0 && n_attn_dec == 0 && fuse_rope_enabled;
+        if (!fuse_rope) {
+            prof_begin(KC_ROPE_KV, 4.0 * T * (2 * AW + 2 * KW) + (cfg_.kv_f16 ? 2.0 : 4.0) * 2 * T * KW, 0);
+            launch_rope_kv(ra, stream_);
+            prof_end();
+            ++launches_;
+        }
         // the quantised image of the attention output feeds the output projection; on a tick of one-token lanes only,
         // the attention kernel writes it itself
         const int okind = act_kind_of(w.wo.w);
@@ -847,6 +853,10 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
             ta.scale = ls.scale;
             ta.softcap = ls.softcap;
             ta.window = ls.window;
+            if (fuse_rope) {
+                ta.fused_rope = 1;
+                ta.rk = ra;
+            }
             if (fuse_attn_quant) {
                 ta.qout = xo;
                 ta.qkind = okind;

@@ -7,13 +7,13 @@
 // KV-head cardinality, token at slot block*block_tokens + row.
 // One warp per (token, head); the head vector is staged in shared memory so any head_dim works.
 #include "kernels.h"
+#include "rope_head.cuh"
 
 namespace mk {
 
 namespace {
 
 constexpr int RK_WARPS = 4;
-constexpr int RK_MAX_D = 256;
 
 template <typename KV>
 __device__ __forceinline__ KV to_kv(float v);
@@ -35,59 +35,11 @@ __global__ void __launch_bounds__(RK_WARPS * 32) rope_kv_kernel(RopeKvArgs a) {
     const int d = a.d;
     float* x = buf[warp];
 
-    int kind;  // 0 = q, 1 = k, 2 = v
-    const float* src;
-    int hh;
-    if (head < a.q_heads) { kind = 0; hh = head; src = a.q + (int64_t)t * a.ldq + hh * d; }
-    else if (head < a.q_heads + a.kv_heads) { kind = 1; hh = head - a.q_heads; src = a.k + (int64_t)t * a.ldk + hh * d; }
-    else { kind = 2; hh = head - a.q_heads - a.kv_heads; src = a.v + (int64_t)t * a.ldv + hh * d; }
-
-    const int n_parts = kind == 2 ? a.v_splits : a.qk_splits;
-    const int64_t part_stride = kind == 2 ? a.v_split_stride : a.qk_split_stride;
-    if ((d & 127) == 0 && ((reinterpret_cast<uintptr_t>(src) | (uintptr_t)(part_stride * 4)) & 15) == 0) {
-        for (int i = lane * 4; i < d; i += 128) {
-            float4 v = *reinterpret_cast<const float4*>(src + i);
-#pragma unroll 4
-            for (int sp = 1; sp < n_parts; ++sp) {
-                float4 w = *reinterpret_cast<const float4*>(src + (int64_t)sp * part_stride + i);
-                v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
-            }
-            *reinterpret_cast<float4*>(x + i) = v;
-        }
-    } else {
-        for (int i = lane; i < d; i += 32) {
-            float v = src[i];
-            for (int sp = 1; sp < n_parts; ++sp) v += src[(int64_t)sp * part_stride + i];
-            x[i] = v;
-        }
-    }
-    __syncwarp();
-
-    const float* nw = kind == 0 ? a.q_norm_w : (kind == 1 ? a.k_norm_w : nullptr);
-    if (nw != nullptr) {
-        float ss = 0.f;
-        for (int i = lane; i < d; i += 32) ss += x[i] * x[i];
-        ss = warp_sum(ss);
-        float m = sqrtf(ss / (float)d + a.norm_eps);
-        for (int i = lane; i < d; i += 32) x[i] = x[i] / m * nw[i];
-        __syncwarp();
-    }
-    if (kind != 2 && a.cos_t != nullptr) {
-        int half = a.rotary_dim / 2;
-        const float* c = a.cos_t + (int64_t)a.positions[t] * half;
-        const float* s = a.sin_t + (int64_t)a.positions[t] * half;
-        float r1[RK_MAX_D / 64], r2[RK_MAX_D / 64];
-        int cnt = 0;
-        for (int i = lane; i < half; i += 32, ++cnt) {
-            float x1 = x[i], x2 = x[i + half];
-            r1[cnt] = __fsub_rn(__fmul_rn(x1, c[i]), __fmul_rn(x2, s[i]));
-            r2[cnt] = __fadd_rn(__fmul_rn(x1, s[i]), __fmul_rn(x2, c[i]));
-        }
-        __syncwarp();
-        cnt = 0;
-        for (int i = lane; i < half; i += 32, ++cnt) { x[i] = r1[cnt]; x[i + half] = r2[cnt]; }
-        __syncwarp();
-    }
+    int kind, hh;  // 0 = q, 1 = k, 2 = v
+    if (head < a.q_heads) { kind = 0; hh = head; }
+    else if (head < a.q_heads + a.kv_heads) { kind = 1; hh = head - a.q_heads; }
+    else { kind = 2; hh = head - a.q_heads - a.kv_heads; }
+    rope_head_prepare(a, kind, hh, t, kind != 2 && a.cos_t != nullptr ? a.positions[t] : 0, x, lane);
     if (kind == 0) {
         float* dst = a.q_out != nullptr ? a.q_out + (int64_t)t * a.ldq_out + hh * d : a.q + (int64_t)t * a.ldq + hh * d;
         for (int i = lane; i < d; i += 32) dst[i] = x[i];

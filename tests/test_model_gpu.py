@@ -161,6 +161,31 @@ def test_family_matches_oracle_on_the_tensor_core_path_with_f16_kv(pk, tmp_path_
     assert model.pool_stats() == om.pool.stats()
 
 
+@pytest.mark.parametrize("fam", ["smollm3", "qwen3", "gemma2"])
+def test_attention_that_prepares_its_own_rows_equals_the_separate_rope_kernel(pk, tmp_path_factory, fam, monkeypatch):
+    """On ticks of one-token lanes the decode attention kernel sums the projection's shares, applies the per-head norm
+    and the rotation and writes the new K / V rows itself; with MACLLM_B200_FUSE_ROPE=0 the separate kernel does.
+    Same arithmetic in the same order: tokens, logits and the pool's later contents (seen through further decoding)
+    must be identical bit for bit.  NoPE layers (smollm3), QK-norm (qwen3), windows and head_dim 256 (gemma2);
+    contexts long enough for several key shares per lane."""
+    path, spec = make_checkpoint(pk, tmp_path_factory, fam)
+    eng = pk["eng"]
+    rng = np.random.default_rng(9)
+    prompts = [rng.integers(3, spec.vocab, size=n) for n in (300, 7, 41, 129)]
+    runs = []
+    for flag in ("0", "1"):
+        monkeypatch.setenv("MACLLM_B200_FUSE_ROPE", flag)
+        model = eng.Model.load_gguf(path, kv_dtype="f16", matmul_path=0, max_batch_tokens=512, max_batch_lanes=8, kv_capacity_tokens=4096)
+        e = eng.Engine(model, record_logits=True, max_active_sequences=4, scheduler_token_budget=512, prefill_token_quantum=512, queue_capacity=8)
+        ids = e.submit([eng.Request(p, 12) for p in prompts], atomic_batch=True)
+        e.run()
+        runs.append(([list(e.result(i)["tokens"]) for i in ids], [np.asarray(e.logits(i)) for i in ids], model.launch_count()))
+    assert runs[0][0] == runs[1][0]
+    for a, b in zip(runs[0][1], runs[1][1]):
+        assert np.array_equal(a, b)
+    assert runs[1][2] < runs[0][2]  # the fused form really ran: fewer launches
+
+
 def test_chunk_boundaries_15_16_17_agree_with_one_shot_prefill(pk, tmp_path_factory):
     """src/decoder.rs:8970-9013: chunking a prompt across a 16-token block boundary changes nothing."""
     path, spec = make_checkpoint(pk, tmp_path_factory, "llama")
