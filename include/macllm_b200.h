@@ -128,6 +128,20 @@ typedef struct mk_prefix_diagnostics {
     int64_t evictions;
 } mk_prefix_diagnostics;
 
+/* Host-only audit of a GGUF checkpoint, the step LoadedRuntime::load runs before it builds the model: the container
+ * (src/gguf.rs:2155-2220), the family spec from the metadata (src/gguf_model.rs:1298-2533) and every decoder tensor's
+ * presence, shape and block format (validate_decoder_tensors, src/gguf_model.rs:3388-3776).  Needs no GPU.  A file
+ * that mk_model_load_gguf would refuse is refused here with the same message. */
+typedef struct mk_gguf_summary {
+    char architecture[32];
+    int32_t n_layers, hidden_size, q_heads, kv_heads, head_dim, rotary_dim;
+    int32_t ffn_size, vocab_size, max_context;
+    int32_t experts, experts_used, expert_ffn_size;
+    int32_t tied_embeddings, sliding_layers, nope_layers, qk_norm;
+    int64_t tensors_in_file, matrices, vectors, matrix_bytes;
+} mk_gguf_summary;
+int32_t mk_gguf_inspect(const char* path, mk_gguf_summary* out);
+
 /* LoadedRuntime::load (src/runtime.rs:104-145) for a GGUF file. */
 int32_t mk_model_load_gguf(const char* path, const mk_load_config* cfg, mk_model** out);
 /* A host-only model with deterministic one-hot logits (next token after feeding token t at position p

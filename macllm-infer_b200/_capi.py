@@ -33,6 +33,15 @@ class LoadConfig(C.Structure):
                 ("ep_rank", C.c_int32), ("ep_size", C.c_int32)]
 
 
+class GgufSummary(C.Structure):
+    _fields_ = [("architecture", C.c_char * 32), ("n_layers", C.c_int32), ("hidden_size", C.c_int32), ("q_heads", C.c_int32),
+                ("kv_heads", C.c_int32), ("head_dim", C.c_int32), ("rotary_dim", C.c_int32), ("ffn_size", C.c_int32),
+                ("vocab_size", C.c_int32), ("max_context", C.c_int32), ("experts", C.c_int32), ("experts_used", C.c_int32),
+                ("expert_ffn_size", C.c_int32), ("tied_embeddings", C.c_int32), ("sliding_layers", C.c_int32),
+                ("nope_layers", C.c_int32), ("qk_norm", C.c_int32), ("tensors_in_file", C.c_int64), ("matrices", C.c_int64),
+                ("vectors", C.c_int64), ("matrix_bytes", C.c_int64)]
+
+
 class RuntimeSpec(C.Structure):
     _fields_ = [("vocab_size", C.c_int32), ("max_context", C.c_int32), ("n_layers", C.c_int32), ("hidden_size", C.c_int32),
                 ("n_stop_tokens", C.c_int32), ("stop_token_ids", C.c_uint32 * 8), ("weight_bytes", C.c_int64),
@@ -113,6 +122,7 @@ SIGNATURES = {
     "mk_model_load_gguf": (_i32, [C.c_char_p, C.POINTER(LoadConfig), C.POINTER(P)]),
     "mk_model_new_fake": (_i32, [_i32, _i32, C.POINTER(LoadConfig), _i64, C.POINTER(P)]),
     "mk_model_free": (_i32, [P]),
+    "mk_gguf_inspect": (_i32, [C.c_char_p, C.POINTER(GgufSummary)]),
     "mk_ep_unique_id": (_i32, [P]),
     "mk_model_ep_init": (_i32, [P, P]),
     "mk_model_spec": (_i32, [P, C.POINTER(RuntimeSpec)]),

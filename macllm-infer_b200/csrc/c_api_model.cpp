@@ -85,6 +85,39 @@ extern "C" {
 
 // ------------------------------------------------------------------------------------------ model
 
+int32_t mk_gguf_inspect(const char* path, mk_gguf_summary* out) {
+    return guarded([&] {
+        if (path == nullptr || out == nullptr) throw std::runtime_error("mk_gguf_inspect: null argument");
+        GgufFile f(path);
+        ModelSpec s = model_spec_from_gguf(f);
+        GgufAudit a = validate_decoder_tensors(f, s);
+        memset(out, 0, sizeof *out);
+        strncpy(out->architecture, s.arch.c_str(), sizeof out->architecture - 1);
+        out->n_layers = s.layers;
+        out->hidden_size = s.hidden;
+        out->q_heads = s.q_heads;
+        out->kv_heads = s.kv_heads;
+        out->head_dim = s.head_dim;
+        out->rotary_dim = s.rotary_dim;
+        out->ffn_size = s.ffn;
+        out->vocab_size = s.vocab;
+        out->max_context = s.max_context;
+        out->experts = s.experts;
+        out->experts_used = s.experts_used;
+        out->expert_ffn_size = s.expert_ffn;
+        out->tied_embeddings = s.tied ? 1 : 0;
+        for (const LayerSpec& l : s.layer) {
+            out->sliding_layers += l.sliding ? 1 : 0;
+            out->nope_layers += l.rope ? 0 : 1;
+            out->qk_norm |= l.qk_norm ? 1 : 0;
+        }
+        out->tensors_in_file = a.tensors_in_file;
+        out->matrices = a.matrices;
+        out->vectors = a.vectors;
+        out->matrix_bytes = a.matrix_bytes;
+    });
+}
+
 int32_t mk_model_load_gguf(const char* path, const mk_load_config* cfg, mk_model** out) {
     return guarded([&] {
         require_device();

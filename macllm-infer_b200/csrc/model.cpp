@@ -85,6 +85,7 @@ Model::Model(const std::string& gguf_path, const ModelConfig& cfg) : cfg_(cfg) {
     MK_CUDA(cudaSetDevice(cfg.device));
     GgufFile f(gguf_path);
     ms_ = model_spec_from_gguf(f);
+    validate_decoder_tensors(f, ms_);  // before any device memory is touched
     if (cfg.ep_size > 1) {
         if (ms_.experts <= 0) throw std::runtime_error("expert parallelism asked for a model without experts");
         if (cfg.ep_rank < 0 || cfg.ep_rank >= cfg.ep_size) throw std::runtime_error("ep_rank out of range");

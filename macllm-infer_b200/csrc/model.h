@@ -40,6 +40,14 @@ struct ModelSpec {
 // Reads the family spec from GGUF metadata (the reference's src/gguf_model.rs:1298-1461,1816-2533).
 ModelSpec model_spec_from_gguf(const GgufFile& f);
 
+// What validate_decoder_tensors found: the matrices and vectors the forward pass uploads.
+struct GgufAudit {
+    int64_t tensors_in_file = 0, matrices = 0, vectors = 0, matrix_bytes = 0;
+};
+// Every tensor of the spec present with the expected shape and a readable block format, nothing of another layer kind
+// (src/gguf_model.rs:3388-3776); throws with the reference's wording on the first violation.  Host only.
+GgufAudit validate_decoder_tensors(const GgufFile& f, const ModelSpec& s);
+
 struct ModelConfig {
     int device = 0;
     int block_tokens = 16, slab_blocks = 8;

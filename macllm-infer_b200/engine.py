@@ -104,6 +104,16 @@ class Model:
         buf = (C.c_uint8 * Model.EP_ID_BYTES).from_buffer_copy(unique_id)
         capi.check(capi.lib().mk_model_ep_init(self._h, buf))
 
+    @staticmethod
+    def inspect_gguf(path) -> dict:
+        """Host-only audit of a checkpoint (container, family spec, every decoder tensor); raises MkError with the
+        loader's message when load_gguf would refuse the file.  Needs no GPU."""
+        s = capi.GgufSummary()
+        capi.check(capi.lib().mk_gguf_inspect(str(path).encode(), C.byref(s)))
+        out = {name: getattr(s, name) for name, _ in capi.GgufSummary._fields_}
+        out["architecture"] = s.architecture.decode()
+        return out
+
     @classmethod
     def load_gguf(cls, path, **kw) -> "Model":
         cfg = cls._config(**kw)

@@ -1,0 +1,145 @@
+"""The loader's audit of a checkpoint, on a machine without a GPU: container, family spec and every decoder tensor
+(presence, shape, block format, nothing of another layer kind), as the reference checks them before it builds a model
+(src/gguf.rs:2155-2220, src/gguf_model.rs:3388-3776).  Valid seed checkpoints of the five families must pass with the
+right summary; files broken in one place each must be refused with a message that names the place."""
+import importlib
+import struct
+
+import numpy as np
+import pytest
+
+
+@pytest.fixture(scope="module")
+def pk(mk):
+    return dict(eng=importlib.import_module("macllm_infer_b200.engine"), seed=importlib.import_module("macllm_infer_b200.seed_gguf"),
+                capi=importlib.import_module("macllm_infer_b200._capi"))
+
+
+FAMILIES = {
+    "llama": dict(name="tinyllama-1.1b", layers=2, vocab=512, hidden=256, ffn=512),
+    "smollm3": dict(name="smollm3-3b", layers=4, vocab=512, hidden=256, ffn=512),
+    "qwen3": dict(name="qwen3-8b", layers=2, vocab=512, hidden=256, ffn=512),
+    "gemma2": dict(name="gemma2-9b", layers=2, vocab=512, hidden=256, ffn=512, window=24),
+    "qwen3moe": dict(name="qwen3-30b-a3b", layers=2, vocab=512, hidden=256, experts=8),
+}
+
+
+def spec_of(pk, fam):
+    kw = dict(FAMILIES[fam])
+    return pk["seed"].scaled(kw.pop("name"), **kw)
+
+
+def write_structure(pk, path, metas, plan, magic=None, version=3, truncate=0):
+    """A GGUF file with the given metadata records and tensor descriptors and zero-filled data."""
+    seed = pk["seed"]
+    sizes = {13: 176}  # Q5_K, a format this path does not read
+    def nbytes(dims, qtype):
+        return int(np.prod(dims)) // 256 * sizes[qtype] if qtype in sizes else seed._tensor_bytes(dims, qtype)
+    head = struct.pack("<IIQQ", seed.GGUF_MAGIC if magic is None else magic, version, len(plan), len(metas)) + b"".join(metas)
+    offset = 0
+    for name, dims, qtype, _ in plan:
+        head += seed._s(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in reversed(dims)) + struct.pack("<IQ", qtype, offset)
+        offset += (nbytes(dims, qtype) + seed.ALIGN - 1) // seed.ALIGN * seed.ALIGN
+    head += b"\0" * ((-len(head)) % seed.ALIGN)
+    with open(path, "wb") as f:
+        f.write(head + b"\0" * max(0, offset - truncate))
+    return path
+
+
+@pytest.mark.parametrize("fam", list(FAMILIES))
+def test_seed_checkpoints_pass_with_the_right_summary(pk, tmp_path, fam):
+    seed = pk["seed"]
+    spec = spec_of(pk, fam)
+    path = seed.write_seed_gguf(tmp_path / f"{fam}.gguf", spec, seed=0)
+    s = pk["eng"].Model.inspect_gguf(path)
+    assert s["architecture"] == spec.arch
+    assert (s["n_layers"], s["hidden_size"], s["q_heads"], s["kv_heads"], s["head_dim"]) == (spec.layers, spec.hidden, spec.q_heads, spec.kv_heads, spec.head_dim)
+    assert s["vocab_size"] == spec.vocab and s["max_context"] == spec.context and s["tied_embeddings"] == int(spec.tied)
+    assert (s["experts"], s["experts_used"], s["expert_ffn_size"]) == (spec.experts, spec.experts_used, spec.expert_ffn)
+    plan = seed.tensor_plan(spec)
+    assert s["tensors_in_file"] == len(plan) == s["matrices"] + s["vectors"]
+    # the seed module counts every 2-D tensor; the audit files the F32 router under the vectors
+    assert s["matrix_bytes"] == seed.weight_bytes(spec)["total"] - spec.experts * spec.hidden * 4 * spec.layers
+    assert s["sliding_layers"] == (spec.layers // 2 if fam == "gemma2" else 0)
+    assert s["nope_layers"] == (spec.layers // 4 if fam == "smollm3" else 0)
+    assert s["qk_norm"] == int(fam in ("qwen3", "qwen3moe"))
+
+
+def broken(pk, tmp_path, fam, edit, **kw):
+    seed = pk["seed"]
+    spec = spec_of(pk, fam)
+    metas, plan = seed._meta(spec), list(seed.tensor_plan(spec))
+    metas, plan = edit(spec, metas, plan) or (metas, plan)
+    return write_structure(pk, tmp_path / "broken.gguf", metas, plan, **kw)
+
+
+def refused(pk, path, fragment):
+    with pytest.raises(pk["capi"].MkError) as e:
+        pk["eng"].Model.inspect_gguf(path)
+    assert fragment in str(e.value), str(e.value)
+
+
+def test_structural_copy_of_a_valid_file_passes(pk, tmp_path):
+    path = broken(pk, tmp_path, "qwen3", lambda spec, m, p: None)
+    assert pk["eng"].Model.inspect_gguf(path)["n_layers"] == 2
+
+
+def test_missing_tensor_is_named(pk, tmp_path):
+    path = broken(pk, tmp_path, "llama", lambda s, m, p: (m, [t for t in p if t[0] != "blk.1.ffn_up.weight"]))
+    refused(pk, path, "required GGUF tensor `blk.1.ffn_up.weight` is missing")
+
+
+def test_wrong_shape_reports_found_and_expected(pk, tmp_path):
+    def edit(spec, m, p):
+        return m, [(n, (d[0], d[1] * 2) if n == "blk.0.attn_k.weight" else d, q, s) for n, d, q, s in p]
+    refused(pk, broken(pk, tmp_path, "qwen3", edit), "GGUF tensor `blk.0.attn_k.weight` has shape [1024, 512], expected [1024, 256]")
+
+
+def test_bias_tensors_are_refused_not_ignored(pk, tmp_path):
+    f32 = pk["capi"].TYPE_F32
+    path = broken(pk, tmp_path, "qwen3", lambda spec, m, p: (m, p + [("blk.0.attn_q.bias", (spec.q_heads * spec.head_dim,), f32, 0.0)]))
+    refused(pk, path, "carries a bias tensor")
+
+
+def test_dense_layer_with_expert_tensors_and_moe_layer_with_dense_tensors(pk, tmp_path):
+    f32 = pk["capi"].TYPE_F32
+    refused(pk, broken(pk, tmp_path, "llama", lambda spec, m, p: (m, p + [("blk.0.ffn_gate_inp.weight", (8, spec.hidden), f32, 0.0)])),
+            "dense layer 0 contains incompatible sparse-MoE tensor `ffn_gate_inp.weight`")
+    q4 = pk["capi"].TYPE_Q4_K
+    refused(pk, broken(pk, tmp_path, "qwen3moe", lambda spec, m, p: (m, p + [("blk.1.ffn_up.weight", (512, spec.hidden), q4, 0.0)])),
+            "sparse-MoE layer 1 contains unsupported dense tensor `ffn_up.weight`")
+
+
+def test_tensor_of_another_sequence_mixer(pk, tmp_path):
+    f32 = pk["capi"].TYPE_F32
+    path = broken(pk, tmp_path, "llama", lambda spec, m, p: (m, p + [("blk.0.ssm_a", (4,), f32, 0.0)]))
+    refused(pk, path, "attention layer 0 contains a tensor of another sequence mixer: `ssm_a`")
+
+
+def test_block_formats(pk, tmp_path):
+    def retype(name, qtype):
+        return lambda spec, m, p: (m, [(n, d, qtype if n == name else q, s) for n, d, q, s in p])
+    refused(pk, broken(pk, tmp_path, "llama", retype("blk.0.ffn_down.weight", 13)), "GGML type 13")
+    refused(pk, broken(pk, tmp_path, "llama", retype("blk.0.attn_norm.weight", pk["capi"].TYPE_F16)), "`blk.0.attn_norm.weight` must be F32")
+
+
+def test_container_errors(pk, tmp_path):
+    same = lambda spec, m, p: None
+    refused(pk, broken(pk, tmp_path, "llama", same, magic=0x12345678), "is not a GGUF file")
+    refused(pk, broken(pk, tmp_path, "llama", same, version=1), "unsupported GGUF version 1")
+    refused(pk, broken(pk, tmp_path, "llama", same, truncate=4096), "extends past the end of the file")
+    refused(pk, tmp_path / "nothing-here.gguf", "cannot open GGUF file")
+
+
+def test_metadata_errors(pk, tmp_path):
+    seed = pk["seed"]
+    def drop(key):
+        return lambda spec, m, p: ([r for r in m if not r.startswith(seed._s(key))], p)
+    refused(pk, broken(pk, tmp_path, "llama", drop("llama.block_count")), "GGUF metadata key `llama.block_count` is missing")
+    def other_arch(spec, m, p):
+        return [seed._kv("general.architecture", seed.T_STR, seed._s("mamba2")) if r.startswith(seed._s("general.architecture")) else r for r in m], p
+    refused(pk, broken(pk, tmp_path, "llama", other_arch), "architecture `mamba2` is not supported on this path")
+    def heads(spec, m, p):
+        key = "qwen3.attention.head_count_kv"
+        return [seed._kv(key, seed.T_U32, struct.pack("<I", 3)) if r.startswith(seed._s(key)) else r for r in m], p
+    refused(pk, broken(pk, tmp_path, "qwen3", heads), "query heads must be a multiple of KV heads")
