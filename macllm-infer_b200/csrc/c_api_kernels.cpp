@@ -119,6 +119,8 @@ void qmatmul_case(int32_t type, const void* w, int64_t rows, int64_t cols, const
     if (half) {
         if (!hgemm_tc_supported(dw.w)) throw std::runtime_error("mk_k_qmatmul: the f16-image GEMM does not cover this matrix");
         build_half_weight(dw.w, dw.half, nullptr);
+        // narrow batches share K out over CTAs, as the model's decode ticks do; the shares are added below
+        if (T <= kQStreamMaxRows) qs_partial.alloc((size_t)16 << 20);
     }
     const bool tensor = !half && !stream && (path == MK_PATH_TENSOR || (path == MK_PATH_AUTO && qgemm_tc_preferred(dw.w, T)));
     ActQ a = ab.view(T, (int)cols, kind, tensor || half || stream, stream);
@@ -134,10 +136,14 @@ void qmatmul_case(int32_t type, const void* w, int64_t rows, int64_t cols, const
     ws.status.zero(nullptr);
     HgemmScratch hs;
     hs.status = ws.status.as<int32_t>();
+    if (half && qs_partial.size() > 0) {
+        hs.partial = qs_partial.as<float>();
+        hs.partial_floats = qs_partial.size() / 4;
+    }
     auto run = [&] {
         if (stream) qs_splits = launch_qstream_tc(qsw, a.xh, a.gs, T, dy.as<float>(), (int)rows, qs_partial.as<float>(), qs_partial.size() / 4,
                                                   ws.status.as<int32_t>(), nullptr, 16);
-        else if (half) launch_hgemm_tc(dw.half, a.xh, T, dy.as<float>(), (int)rows, 1.0f, 0.f, hs, nullptr, 1);
+        else if (half) qs_splits = launch_hgemm_tc(dw.half, a.xh, T, dy.as<float>(), (int)rows, 1.0f, 0.f, hs, nullptr, hs.partial ? 16 : 1);
         else if (tensor) launch_qgemm_tc(dw.w, a, kind, T, dy.as<float>(), (int)rows, 1.0f, 0.f, ws, nullptr);
         else launch_qgemv(dw.w, a, T, dy.as<float>(), (int)rows, 1.0f, 0.f, nullptr);
     };
@@ -168,7 +174,7 @@ void qmatmul_case(int32_t type, const void* w, int64_t rows, int64_t cols, const
     ws.status.download(&st, 4);
     MK_CUDA(cudaDeviceSynchronize());
     if (st != 0) throw std::runtime_error("tensor-core matmul: a bounded wait inside the kernel gave up (status " + std::to_string(st) + ")");
-    if (y != nullptr && stream && qs_splits > 1) {
+    if (y != nullptr && (stream || half) && qs_splits > 1) {
         // the shares are added in share order, as the consumer kernels of the model do
         std::vector<float> parts((size_t)qs_splits * T * rows);
         qs_partial.download(parts.data(), parts.size() * 4);

@@ -136,6 +136,7 @@ def test_streamed_q4k_matmul_matches_oracle(ops, orc, T, rows, cols):
 
 
 @pytest.mark.parametrize("label,T,rows,cols,path", [("decode_gate_up", 64, 22016, 2048, 4), ("decode_down", 64, 2048, 11008, 4),
+                                                     ("decode_qkv_image", 64, 3072, 2048, 3), ("decode_down_image", 64, 2048, 11008, 3),
                                                      ("prefill_gate_up", 2048, 22016, 2048, 3), ("prefill_down", 2048, 2048, 11008, 3)])
 def test_matmul_timing_entry_on_the_benchmark_shapes(ops, label, T, rows, cols, path):
     """mk_k_qmatmul_time on the feed-forward matrices of the headline workload (device-resident operands, L2
