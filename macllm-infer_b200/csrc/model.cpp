@@ -700,14 +700,14 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         // Narrow ticks: which projections leave the streamed Q4_K matmul for the f16 images with split-K.  Measured on
         // 64-lane decode ticks of the 3 B shape: [q; k; v] as ONE launch over the stacked image beats the streamed
         // Q|K launch plus a separate V launch, and the long-K down projection is a little faster on its image; the
-        // output projection and gate|up stay on the streamed blocks (a quarter of the bytes).
+        // output projection and gate|up stay on the streamed blocks (a quarter of the bytes).  Bit 8 applies from 33 rows.
         // MACLLM_B200_DECODE_HALF_MASK overrides: 1 q|k|v, 2 attention output, 4 gate|up (implies 8), 8 down.
         static const int half_mask = [] {
             const char* e = getenv("MACLLM_B200_DECODE_HALF_MASK");
             int m = e != nullptr ? atoi(e) : 9;
             return (m & 4) ? (m | 8) : m;
         }();
-        const bool stream_o = stream && !(half_mask & 2), stream_gu = stream && !(half_mask & 4), stream_down = stream && !(half_mask & 8);
+        const bool stream_o = stream && !(half_mask & 2), stream_gu = stream && !(half_mask & 4), stream_down = stream && !((half_mask & 8) && T >= 33);  // with a handful of lanes the streamed blocks win (measured at 4 lanes)
         if (stream && (half_mask & 1) && w.qkv_half.ready) {
             qk_splits = v_splits = matmul_half(w.qkv_half, xa, T, qp, QKVW, 1.f, 0.f, kMaxShares);
             qkv_joint = qk_splits > 1;
