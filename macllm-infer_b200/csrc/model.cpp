@@ -38,6 +38,21 @@ ModelSpec model_spec_from_gguf(const GgufFile& f) {
     s.rotary_dim = (int)f.get_int_or(a + ".rope.dimension_count", s.head_dim);
     double theta = f.get_float_or(a + ".rope.freq_base", 10000.0);
     s.permute_qk = (a == "llama" || a == "smollm3");  // gguf_model.rs:454-460
+    if (const GgufTensor* rf = f.tensor("rope_freqs.weight")) {
+        // only the Llama profile reads frequency factors (gguf_model.rs:1855,2015-2033); the others refuse the tensor
+        // (gguf_model.rs:1302,2138,2244,2402)
+        if (a == "gemma2") throw std::runtime_error("GGUF Gemma 2 RoPE frequency-factor tensors are not supported");
+        if (a != "llama") throw std::runtime_error("GGUF " + a + " rope frequency factors are not supported yet");
+        if (rf->type != QT_F32) throw std::runtime_error("GGUF `rope_freqs.weight` must be F32");
+        if (rf->elements() != s.head_dim / 2)
+            throw std::runtime_error("GGUF `rope_freqs.weight` has " + std::to_string(rf->elements()) + " factors, expected " +
+                                     std::to_string(s.head_dim / 2) + " for head dimension " + std::to_string(s.head_dim));
+        s.rope_factors.resize((size_t)rf->elements());
+        memcpy(s.rope_factors.data(), rf->data, s.rope_factors.size() * 4);
+        for (float v : s.rope_factors)
+            if (!std::isfinite(v) || !(v > 0.f)) throw std::runtime_error("GGUF `rope_freqs.weight` factors must be finite and positive");
+        if (s.rotary_dim != s.head_dim) throw std::runtime_error("partial Llama RoPE is not supported");  // gguf_model.rs:1851-1854
+    }
     if (a == "smollm3" && s.layers != 36 && !f.has("macllm.allow_scaled_layers"))
         throw std::runtime_error("GGUF SmolLM3 must have exactly 36 layers");  // gguf_model.rs:2251-2254
     if (a == "qwen3moe") {
@@ -322,7 +337,10 @@ void Model::rope_tables_for(double theta, const float*& cos_t, const float*& sin
     int half = ms_.rotary_dim / 2;
     int64_t capacity = std::min<int64_t>(ms_.max_context, std::max<int64_t>(pool_->max_blocks() * pool_->block_tokens(), 256));
     std::vector<float> inv((size_t)half), c((size_t)(capacity * half)), s((size_t)(capacity * half));
-    for (int i = 0; i < half; ++i) inv[(size_t)i] = (float)(1.0 / std::pow(theta, (double)(2 * i) / (double)ms_.rotary_dim));
+    for (int i = 0; i < half; ++i) {
+        double base = 1.0 / std::pow(theta, (double)(2 * i) / (double)ms_.rotary_dim);
+        inv[(size_t)i] = ms_.rope_factors.empty() ? (float)base : (float)(base / (double)ms_.rope_factors[(size_t)i]);
+    }
     for (int64_t p = 0; p < capacity; ++p)
         for (int i = 0; i < half; ++i) {
             float a = (float)p * inv[(size_t)i];

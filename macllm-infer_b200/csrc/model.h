@@ -34,6 +34,7 @@ struct ModelSpec {
     float eps = 1e-5f, embedding_scale = 1.f, final_logit_scale = 1.f, final_softcap = 0.f;
     bool tied = false, permute_qk = false;
     int experts = 0, experts_used = 0, expert_ffn = 0;
+    std::vector<float> rope_factors;  // GGUF `rope_freqs.weight`: per-frequency divisors (Llama profile only), else empty
     std::vector<LayerSpec> layer;
 };
 

@@ -122,7 +122,8 @@ def _meta(spec: SeedSpec) -> list[bytes]:
             _kv("qwen3moe.expert_feed_forward_length", T_U32, struct.pack("<I", spec.expert_ffn)),
         ]
     for k, v in spec.extra.items():
-        out.append(_kv(k, T_BOOL, struct.pack("<B", 1 if v else 0)))
+        if k != "rope_factors":  # a tensor's payload, not a metadata key (see tensor_plan)
+            out.append(_kv(k, T_BOOL, struct.pack("<B", 1 if v else 0)))
     # a minimal embedded tokenizer: the reference's loader requires these keys (gguf_model.rs:3233-3262)
     toks = b"".join(_s(f"t{i}") for i in range(spec.vocab))
     out += [
@@ -168,6 +169,8 @@ def tensor_plan(spec: SeedSpec) -> list[tuple[str, tuple[int, ...], int, float]]
             t.append((p + "ffn_down.weight", (H, spec.ffn), m, 0.02))
         if spec.arch == "gemma2":
             t.append((p + "post_ffw_norm.weight", (H,), F32, 0.0))
+    if spec.extra.get("rope_factors") is not None:
+        t.append(("rope_freqs.weight", (len(spec.extra["rope_factors"]),), F32, -1.0))  # payload from spec.extra
     t.append(("output_norm.weight", (H,), F32, 0.0))
     if not spec.tied:
         t.append(("output.weight", (spec.vocab, H), hi, 0.02))
@@ -205,7 +208,9 @@ def write_seed_gguf(path: str | Path, spec: SeedSpec, seed: int = 0) -> Path:
         f.write(head + b"\0" * pad)
         for (name, dims, qtype, std), off in zip(plan, offsets):
             n = _tensor_bytes(dims, qtype)
-            if std == 0.0:
+            if name == "rope_freqs.weight":
+                data = np.asarray(spec.extra["rope_factors"], dtype=np.float32).tobytes()
+            elif std == 0.0:
                 data = np.ones(int(np.prod(dims)), dtype=np.float32).tobytes()
             else:
                 cols = dims[-1]

@@ -118,6 +118,14 @@ class Decoder:
         self.rotary = int(m.get(f"{a}.rope.dimension_count", self.d))
         theta = float(m.get(f"{a}.rope.freq_base", 10000.0))
         self.permute = a in ("llama", "smollm3")
+        # RoPE frequency factors: the Llama profile reads them (src/gguf_model.rs:1855,2015-2033), the others refuse the tensor
+        self.rope_factors = None
+        if "rope_freqs.weight" in g.tensors:
+            if a != "llama":
+                raise ValueError(f"GGUF {a} rope frequency factors are not supported")
+            self.rope_factors = g.f32("rope_freqs.weight")
+            if len(self.rope_factors) != self.d // 2 or not (np.isfinite(self.rope_factors).all() and (self.rope_factors > 0).all()):
+                raise ValueError("GGUF `rope_freqs.weight` factors must be head_dim / 2 finite positive values")
         self.embedding_scale = 1.0
         self.final_softcap = 0.0
         self.experts = int(m.get("qwen3moe.expert_count", 0))
@@ -176,7 +184,7 @@ class Decoder:
     def _rope(self, theta):
         if theta not in self.rope_tables:
             cap = min(self.max_context, max(self.pool.max_blocks * self.pool.block_tokens, 256))
-            self.rope_tables[theta] = M.rope_tables(theta, self.rotary, cap)
+            self.rope_tables[theta] = M.rope_tables(theta, self.rotary, cap, self.rope_factors)
         return self.rope_tables[theta]
 
     def forward(self, lanes, reservation):

@@ -135,10 +135,11 @@ def softcap(x: np.ndarray, cap: float) -> np.ndarray:
     return x
 
 
-def rope_tables(theta: float, rotary_dim: int, capacity: int):
+def rope_tables(theta: float, rotary_dim: int, capacity: int, factors=None):
     cos = np.empty((capacity, rotary_dim // 2), np.float32)
     sin = np.empty_like(cos)
-    lib().orc_rope_tables(C.c_double(theta), rotary_dim, C.c_int64(capacity), _p(cos), _p(sin))
+    f = _f32(factors) if factors is not None else None
+    lib().orc_rope_tables(C.c_double(theta), rotary_dim, C.c_int64(capacity), _p(f) if f is not None else None, _p(cos), _p(sin))
     return cos, sin
 
 

@@ -369,10 +369,15 @@ void orc_softcap(float* x, int64_t n, float cap) {
 }
 
 // RoPE tables (src/decoder.rs:136-201): inv_freq in f64 then f32; angle = f32(pos) * inv_freq.
-void orc_rope_tables(double theta, int rotary_dim, int64_t capacity, float* cos_t, float* sin_t) {
+// factors (may be null): per-frequency divisors, f32(base / f64(factor)) as RotaryEmbedding::new does for GGUF
+// `rope_freqs.weight` (src/decoder.rs:136-152).
+void orc_rope_tables(double theta, int rotary_dim, int64_t capacity, const float* factors, float* cos_t, float* sin_t) {
     int half = rotary_dim / 2;
     std::vector<float> inv((size_t)half);
-    for (int i = 0; i < half; ++i) inv[i] = (float)(1.0 / pow(theta, (double)(2 * i) / (double)rotary_dim));
+    for (int i = 0; i < half; ++i) {
+        double base = 1.0 / pow(theta, (double)(2 * i) / (double)rotary_dim);
+        inv[i] = factors ? (float)(base / (double)factors[i]) : (float)base;
+    }
     for (int64_t p = 0; p < capacity; ++p)
         for (int i = 0; i < half; ++i) { float a = (float)p * inv[i]; cos_t[p * half + i] = cosf(a); sin_t[p * half + i] = sinf(a); }
 }

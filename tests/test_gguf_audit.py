@@ -143,3 +143,21 @@ def test_metadata_errors(pk, tmp_path):
         key = "qwen3.attention.head_count_kv"
         return [seed._kv(key, seed.T_U32, struct.pack("<I", 3)) if r.startswith(seed._s(key)) else r for r in m], p
     refused(pk, broken(pk, tmp_path, "qwen3", heads), "query heads must be a multiple of KV heads")
+
+
+def test_rope_frequency_factors_are_read_for_llama_only(pk, tmp_path):
+    """src/gguf_model.rs:1855,2015-2033 (Llama reads head_dim / 2 finite positive factors) and :1302,2138 (the other
+    profiles refuse the tensor)."""
+    seed, f32 = pk["seed"], pk["capi"].TYPE_F32
+    def with_factors(n):
+        return lambda spec, m, p: (m, p + [("rope_freqs.weight", (n,), f32, 0.0)])
+    spec = spec_of(pk, "llama")
+    # zero-filled payload: the right length but not positive
+    refused(pk, broken(pk, tmp_path, "llama", with_factors(spec.head_dim // 2)), "factors must be finite and positive")
+    refused(pk, broken(pk, tmp_path, "llama", with_factors(3)), f"`rope_freqs.weight` has 3 factors, expected {spec.head_dim // 2} for head dimension {spec.head_dim}")
+    refused(pk, broken(pk, tmp_path, "qwen3", with_factors(64)), "GGUF qwen3 rope frequency factors are not supported yet")
+    refused(pk, broken(pk, tmp_path, "gemma2", with_factors(128)), "GGUF Gemma 2 RoPE frequency-factor tensors are not supported")
+    good = seed.scaled("tinyllama-1.1b", layers=2, vocab=512, hidden=256, ffn=512)
+    good.extra = dict(good.extra, rope_factors=np.linspace(1.0, 8.0, good.head_dim // 2))
+    s = pk["eng"].Model.inspect_gguf(seed.write_seed_gguf(tmp_path / "factors.gguf", good, seed=0))
+    assert s["tensors_in_file"] == s["matrices"] + s["vectors"] + 1

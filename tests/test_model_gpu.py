@@ -186,6 +186,24 @@ def test_attention_that_prepares_its_own_rows_equals_the_separate_rope_kernel(pk
     assert runs[1][2] < runs[0][2]  # the fused form really ran: fewer launches
 
 
+def test_llama_rope_frequency_factors_match_oracle(pk, tmp_path_factory):
+    """GGUF `rope_freqs.weight` (src/gguf_model.rs:2015-2033): inverse frequencies f32(base / f64(factor))
+    (src/decoder.rs:136-152).  Same bar as the other integer-path runs, and the factors must matter."""
+    spec0 = pk["seed"].scaled("tinyllama-1.1b", layers=2, vocab=2048)
+    factors = np.concatenate([np.ones(spec0.head_dim // 4), np.linspace(1.5, 8.0, spec0.head_dim // 4)]).astype(np.float32)
+    path, spec = make_checkpoint(pk, tmp_path_factory, "llama", extra=dict(rope_factors=factors))
+    rng = np.random.default_rng(11)
+    prompts = [rng.integers(3, spec.vocab, size=n) for n in (33, 9, 50)]
+    model, pe, om, oe_, alt = run_pair(pk, path, prompts, [4, 4, 4])
+    print(compare(pe, oe_, alt, 3))
+    plain_path, _ = make_checkpoint(pk, tmp_path_factory, "llama")
+    plain = pk["eng"].Model.load_gguf(plain_path, kv_dtype="f32", matmul_path=1, max_batch_tokens=512, max_batch_lanes=8)
+    s1, s2 = model.new_session(), plain.new_session()
+    a, _ = model.forward_batch([(s1, prompts[0], 0)])
+    b, _ = plain.forward_batch([(s2, prompts[0], 0)])
+    assert np.max(np.abs(a - b)) > 1e-3
+
+
 def test_chunk_boundaries_15_16_17_agree_with_one_shot_prefill(pk, tmp_path_factory):
     """src/decoder.rs:8970-9013: chunking a prompt across a 16-token block boundary changes nothing."""
     path, spec = make_checkpoint(pk, tmp_path_factory, "llama")
