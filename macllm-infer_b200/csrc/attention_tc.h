@@ -51,7 +51,8 @@ int attention_tc_warps(int q_heads, int kv_heads);
 
 // Host-side work lists of one tick (the same for every layer): lanes with more than one token are cut
 // into query tiles; one-token lanes split their keys over up to kAttnMaxSplits CTAs (four warps each), at
-// least kAttnMinSplitKeys keys each, until about kAttnTargetCtas CTAs are in flight.
+// least kAttnMinSplitKeys keys each, until about kAttnTargetCtas CTAs are in flight - unless the lanes alone already
+// give every SM a CTA, in which case no lane is split.
 constexpr int kAttnTargetCtas = 148 * 2;
 constexpr int kAttnMaxSplits = 16;
 constexpr int kAttnMinSplitKeys = 128;

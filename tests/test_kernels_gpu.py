@@ -95,7 +95,7 @@ def test_gated_gemm_equals_gemm_then_activation(ops, orc, name, act, T, F, cols)
     """The wide-tick feed-forward front: gate and up rows interleaved in one f16 image, the activation and the product
     finished in the GEMM's epilogue and written as f16.  Against the separate kernels (plain f16-image GEMM of each
     matrix, then the SwiGLU kernel) the accumulators and the activation arithmetic are the same, so the halves must
-    be identical; against the oracle the usual f16-operand tolerance applies.  Odd T, F with a partial last tile."""
+    be identical (above 64 rows, where neither side splits K); against the oracle the usual f16-operand tolerance applies.  Odd T, F with a partial last tile."""
     qtype = QTYPES[name]
     gate_w = _weights(ops, qtype, F, cols, stream=7)
     up_w = _weights(ops, qtype, F, cols, stream=8)
@@ -105,7 +105,11 @@ def test_gated_gemm_equals_gemm_then_activation(ops, orc, name, act, T, F, cols)
     g = ops.qmatmul(qtype, gate_w, F, cols, x, 3)
     u = ops.qmatmul(qtype, up_w, F, cols, x, 3)
     want = ops.actmul(g, u, act).astype(np.float16).astype(np.float32)
-    assert np.array_equal(got, want)
+    if T > 64:
+        assert np.array_equal(got, want)
+    else:
+        # up to 64 rows the plain GEMM shares K out over CTAs and adds the shares afterwards: another association
+        assert np.allclose(got, want, rtol=4e-3, atol=2e-4)
     og = orc.qmatmul(qtype, gate_w, F, cols, x, 1)
     ou = orc.qmatmul(qtype, up_w, F, cols, x, 1)
     ref = orc.act_mul(og, ou, act)
