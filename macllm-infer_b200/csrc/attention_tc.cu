@@ -720,7 +720,7 @@ int attention_tc_warps(int q_heads, int kv_heads) { return q_heads / kv_heads ==
 
 int attention_tc_tile_rows(int q_heads, int kv_heads) { return 16 * attention_tc_warps(q_heads, kv_heads) / (q_heads / kv_heads); }
 
-int attention_tc_max_entries(int lanes, int kv_heads) { return std::max(lanes, kAttnTargetCtas / std::max(1, kv_heads)) + 1; }
+int attention_tc_max_entries(int lanes, int kv_heads) { return std::max(lanes + lanes / 2, kAttnTargetCtas / std::max(1, kv_heads)) + 1; }
 
 void plan_attention_tc(const int32_t* start_pos, const int32_t* n_tokens, const int32_t* n_blocks, int lanes, int q_heads,
                        int kv_heads, AttnTcPlan& plan) {
@@ -734,10 +734,13 @@ void plan_attention_tc(const int32_t* start_pos, const int32_t* n_tokens, const 
     int64_t total_keys = 0;
     for (int i = 0; i < lanes; ++i)
         if (n_tokens[i] == 1) { ++n_dec; total_keys += start_pos[i] + 1; }
-    // once the lanes alone give every SM a CTA, sharing keys out only adds merge work and repeated query preparation
-    // (measured at 64 lanes x 4 KV heads: +1.4 % on the whole benchmark without shares)
-    const int slots = n_dec * kv_heads >= 148 ? n_dec : std::max(n_dec, kAttnTargetCtas / std::max(1, kv_heads));
-    int share = (int)std::max<int64_t>(kAttnMinSplitKeys, (total_keys + slots - 1) / std::max(1, slots));
+    // Once the lanes alone give every SM a CTA, sharing keys out only adds merge work and repeated query preparation
+    // (measured at 64 lanes x 4 KV heads with histories within twice their mean: +1.4 % on the whole benchmark
+    // without shares).  Then only a lane more than twice as long as the mean is cut, so that one long history among
+    // many short ones does not set the length of the launch.
+    const bool filled = n_dec * kv_heads >= 148;
+    const int slots = filled ? n_dec + n_dec / 2 : std::max(n_dec, kAttnTargetCtas / std::max(1, kv_heads));
+    int share = (int)std::max<int64_t>(kAttnMinSplitKeys, filled ? 2 * (total_keys / std::max(1, n_dec)) : (total_keys + slots - 1) / std::max(1, slots));
     share = (share + 63) / 64 * 64;
     auto shares_of = [&](int ctx) { return std::max(1, std::min(kAttnMaxSplits, (ctx + share - 1) / share)); };
     for (;;) {

@@ -350,6 +350,24 @@ def test_decode_attention_at_the_benchmark_shape(ops, orc):
     assert np.max(np.abs(res["out"] - want)) < 2e-3
 
 
+def test_decode_attention_with_one_long_history_among_many_short_ones(ops, orc):
+    """48 one-token lanes x 4 KV heads fill the GPU by themselves, so lanes are not cut - except the one whose history is
+    many times the mean, which is shared out over several CTAs and merged; every lane must still match the oracle."""
+    q_heads, kv_heads, d, bt = 16, 4, 128, 16
+    rng = np.random.default_rng(65)
+    lanes_spec = [(int(c), 1) for c in rng.integers(40, 300, size=47)] + [(5000, 1)]
+    tables, k_pool, v_pool, q, k, v = _attn_case(rng, lanes_spec, q_heads, kv_heads, d, bt, 1, 0, np.float16)
+    scale = 1.0 / np.sqrt(d)
+    kp, vp = k_pool.copy(), v_pool.copy()
+    res = ops.attention_step(q, k, v, kp, vp, tables, [s for s, _ in lanes_spec], [n for _, n in lanes_spec], q_heads=q_heads,
+                             kv_heads=kv_heads, head_dim=d, block_tokens=bt, layers=1, layer=0, scale=scale, kernel=2)
+    flat = np.concatenate(tables).astype(np.uint32)
+    page_off = np.concatenate([[0], np.cumsum([len(t) for t in tables])[:-1]]).astype(np.int32)
+    want = orc.paged_attention(q, kp, vp, flat, page_off, [s for s, _ in lanes_spec], [n for _, n in lanes_spec], q_heads=q_heads,
+                               kv_heads=kv_heads, d=d, block_tokens=bt, layers=1, layer=0, scale=scale, softcap=0.0, window=0, mode=0)
+    assert np.max(np.abs(res["out"] - want)) < 2e-3
+
+
 def test_tensor_core_attention_is_refused_for_f32_pools(ops):
     rng = np.random.default_rng(3)
     tables, k_pool, v_pool, q, k, v = _attn_case(rng, [(0, 4)], 4, 2, 64, 16, 1, 0, np.float32)
