@@ -553,11 +553,11 @@ HgemmPlan hgemm_tc_plan(int64_t rows, int64_t cols, int T, int max_splits) {
     HgemmPlan pl;
     pl.bn = T <= 64 ? 64 : 128;
     if (T > 128) {
-        // 256-token tiles do about 5 % more per byte of shared memory, 128-token tiles fill the last round of CTAs
-        // better: take the one with fewer (rounds x tile time)
+        // 256-token tiles do about 10 % more per unit of time (less shared-memory traffic per MMA, half the epilogue
+        // hand-offs), 128-token tiles fill the last round of CTAs better: take the one with fewer (rounds x tile time)
         const int64_t mt = (rows + HG_BM - 1) / HG_BM;
         const double cost256 = (double)((mt * ((T + 255) / 256) + 147) / 148) * 2.0;
-        const double cost128 = (double)((mt * ((T + 127) / 128) + 147) / 148) * 1.05;
+        const double cost128 = (double)((mt * ((T + 127) / 128) + 147) / 148) * 1.1;
         pl.bn = cost128 < cost256 ? 128 : 256;
     }
     pl.row_tiles = (int)((rows + HG_BM - 1) / HG_BM);
