@@ -1,5 +1,6 @@
 // See gguf_file.h.
 #include "gguf_file.h"
+#include <cstdio>
 #include <cstring>
 #include <fcntl.h>
 #include <stdexcept>
@@ -61,7 +62,11 @@ int64_t row_bytes_of(int type, int64_t cols) {
 
 }  // namespace
 
-GgufFile::GgufFile(const std::string& path) {
+// One file of a checkpoint: mapped, header parsed, tensor payloads bounds-checked.
+GgufFile::Shard GgufFile::open_shard(const std::string& path, std::map<std::string, GgufValue>& meta_, std::vector<GgufTensor>& tensors_) {
+    Shard sh;
+    void*& map_ = sh.map;
+    size_t& map_len_ = sh.len;
     int fd = open(path.c_str(), O_RDONLY);
     if (fd < 0) throw std::runtime_error("cannot open GGUF file " + path);
     struct stat st;
@@ -112,7 +117,8 @@ GgufFile::GgufFile(const std::string& path) {
         }
         meta_[key] = std::move(val);
     }
-    tensors_.reserve((size_t)n_tensors);
+    const size_t first_tensor = tensors_.size();  // earlier shards' tensors stay as they are
+    tensors_.reserve(first_tensor + (size_t)n_tensors);
     for (uint64_t i = 0; i < n_tensors; ++i) {
         GgufTensor t;
         t.name = c.read_string();
@@ -123,13 +129,16 @@ GgufFile::GgufFile(const std::string& path) {
         t.dims.assign(file_dims.rbegin(), file_dims.rend());
         t.type = (int)c.read<uint32_t>();
         t.offset = c.read<uint64_t>();
-        by_name_[t.name] = tensors_.size();
         tensors_.push_back(std::move(t));
     }
-    uint64_t alignment = (uint64_t)get_int_or("general.alignment", 32);
+    uint64_t alignment = 32;
+    if (auto it = meta_.find("general.alignment"); it != meta_.end())
+        if (auto pv = std::get_if<int64_t>(&it->second.v)) alignment = (uint64_t)*pv;
+    if (alignment == 0 || (alignment & (alignment - 1)) != 0) throw std::runtime_error("GGUF alignment must be a power of two");
     uint64_t header = (uint64_t)(c.p - base);
     uint64_t data_start = (header + alignment - 1) / alignment * alignment;
-    for (GgufTensor& t : tensors_) {
+    for (size_t ti = first_tensor; ti < tensors_.size(); ++ti) {
+        GgufTensor& t = tensors_[ti];
         int64_t cols = t.dims.back();
         int64_t rows = t.elements() / cols;
         int64_t rb = row_bytes_of(t.type, cols);
@@ -138,11 +147,120 @@ GgufFile::GgufFile(const std::string& path) {
             throw std::runtime_error("tensor " + t.name + " extends past the end of the file");
         t.data = base + data_start + t.offset;
     }
+    return sh;
 }
 
-GgufFile::~GgufFile() {
-    if (map_) munmap(map_, map_len_);
+GgufFile::Shard::Shard(Shard&& o) noexcept : map(o.map), len(o.len) { o.map = nullptr; o.len = 0; }
+GgufFile::Shard::~Shard() { if (map) munmap(map, len); }
+
+namespace {
+
+// `<prefix>-00001-of-00003.gguf` -> (prefix, 0-based index, count); false when the name is not of that form
+// (the reference's parse_gguf_split_filename, src/gguf.rs:492-514).
+bool parse_split_name(const std::string& filename, std::string& prefix, int& index, int& count) {
+    const std::string suffix = ".gguf";
+    if (filename.size() <= suffix.size() || filename.compare(filename.size() - suffix.size(), suffix.size(), suffix) != 0) return false;
+    std::string stem = filename.substr(0, filename.size() - suffix.size());
+    size_t of = stem.rfind("-of-");
+    if (of == std::string::npos) return false;
+    std::string count_text = stem.substr(of + 4), indexed = stem.substr(0, of);
+    size_t dash = indexed.rfind('-');
+    if (dash == std::string::npos || dash == 0) return false;
+    std::string index_text = indexed.substr(dash + 1);
+    auto digits5 = [](const std::string& t) { return t.size() == 5 && t.find_first_not_of("0123456789") == std::string::npos; };
+    if (!digits5(index_text) || !digits5(count_text)) return false;
+    int file_index = std::stoi(index_text);
+    count = std::stoi(count_text);
+    if (file_index == 0 || count == 0 || file_index > count || count > 65535) return false;
+    prefix = indexed.substr(0, dash);
+    index = file_index - 1;
+    return true;
 }
+
+struct SplitInfo { bool present = false; int64_t index = 0, count = 0, tensors = 0; };
+
+// split.no / split.count / split.tensors.count (src/gguf.rs:956-993)
+SplitInfo split_info(const std::map<std::string, GgufValue>& meta) {
+    SplitInfo s;
+    for (const auto& kv : meta)
+        if (kv.first.compare(0, 6, "split.") == 0) s.present = true;
+    if (!s.present) return s;
+    auto need = [&](const char* key) {
+        auto it = meta.find(key);
+        if (it == meta.end()) throw std::runtime_error(std::string("required GGUF metadata `") + key + "` is missing");
+        auto p = std::get_if<int64_t>(&it->second.v);
+        if (p == nullptr || *p < 0) throw std::runtime_error(std::string("GGUF metadata `") + key + "` must be a non-negative integer");
+        return *p;
+    };
+    s.index = need("split.no");
+    s.count = need("split.count");
+    s.tensors = need("split.tensors.count");
+    if (s.count == 0 ? s.index != 0 : s.index >= s.count)
+        throw std::runtime_error("GGUF metadata `split.no`=" + std::to_string(s.index) + " is outside split.count=" + std::to_string(s.count));
+    return s;
+}
+
+constexpr int kMaxShards = 128;  // the reference's safety limit (src/gguf.rs:50)
+
+}  // namespace
+
+// A checkpoint is one file or a family `<prefix>-00001-of-000NN.gguf` opened through its first member
+// (GgufFile::open, src/gguf.rs:576-660): siblings are found by name, must declare their own place in the same family,
+// and contribute tensors only - the metadata of the first shard is the checkpoint's.
+GgufFile::GgufFile(const std::string& path) {
+    shards_.push_back(open_shard(path, meta_, tensors_));
+    const SplitInfo first = split_info(meta_);
+    const size_t slash = path.find_last_of('/');
+    const std::string dir = slash == std::string::npos ? "" : path.substr(0, slash + 1);
+    const std::string filename = slash == std::string::npos ? path : path.substr(slash + 1);
+    std::string prefix;
+    int name_index = 0, name_count = 0;
+    const bool named = parse_split_name(filename, prefix, name_index, name_count);
+    if ((!first.present || first.count <= 1) && named && name_count > 1)
+        throw std::runtime_error("GGUF filename " + path + " declares an active shard family, but its metadata does not");
+    if (first.present && first.count > 1) {
+        if (first.index != 0) throw std::runtime_error("GGUF split " + path + " has split.no=" + std::to_string(first.index) + "; load the first shard instead");
+        if (first.count > kMaxShards)
+            throw std::runtime_error("GGUF declares " + std::to_string(first.count) + " shards, exceeding the supported safety limit " + std::to_string(kMaxShards));
+        if (!named || name_index != 0 || name_count != first.count)
+            throw std::runtime_error("GGUF first shard filename `" + filename + "` does not match split.no=0 and split.count=" + std::to_string(first.count));
+        if ((int64_t)tensors_.size() > first.tensors) throw std::runtime_error("GGUF shard holds more tensors than split.tensors.count declares");
+        for (int i = 1; i < (int)first.count; ++i) {
+            char name[64];
+            snprintf(name, sizeof name, "-%05d-of-%05d.gguf", i + 1, (int)first.count);
+            const std::string shard_path = dir + prefix + name;
+            std::map<std::string, GgufValue> shard_meta;
+            try {
+                shards_.push_back(open_shard(shard_path, shard_meta, tensors_));
+            } catch (const std::exception& e) {
+                throw std::runtime_error("failed to load GGUF shard " + std::to_string(i + 1) + " of " + std::to_string(first.count) + ": " + e.what());
+            }
+            const SplitInfo s = split_info(shard_meta);
+            if (!s.present) throw std::runtime_error("GGUF shard " + shard_path + " is missing required split metadata");
+            if (s.index != i) throw std::runtime_error("GGUF shard " + shard_path + " declares split.no=" + std::to_string(s.index) + ", expected " + std::to_string(i));
+            if (s.count != first.count)
+                throw std::runtime_error("GGUF shard " + shard_path + " declares split.count=" + std::to_string(s.count) + ", expected " + std::to_string(first.count));
+            if (s.tensors != first.tensors)
+                throw std::runtime_error("GGUF shard " + shard_path + " declares split.tensors.count=" + std::to_string(s.tensors) + ", expected " +
+                                         std::to_string(first.tensors));
+            // a later shard may repeat metadata of the first, never add or change any (src/gguf.rs:995-1017)
+            for (const auto& kv : shard_meta) {
+                if (kv.first.compare(0, 6, "split.") == 0 || kv.first == "general.alignment") continue;
+                auto it = meta_.find(kv.first);
+                if (it == meta_.end())
+                    throw std::runtime_error("GGUF subsidiary shard " + shard_path + " contains metadata `" + kv.first + "` absent from the first shard");
+                if (!(it->second.v == kv.second.v)) throw std::runtime_error("GGUF subsidiary shard " + shard_path + " has conflicting metadata `" + kv.first + "`");
+            }
+            if ((int64_t)tensors_.size() > first.tensors) throw std::runtime_error("GGUF shards hold more tensors than split.tensors.count declares");
+        }
+    }
+    for (size_t i = 0; i < tensors_.size(); ++i)
+        if (!by_name_.emplace(tensors_[i].name, i).second) throw std::runtime_error("GGUF tensor `" + tensors_[i].name + "` appears more than once");
+    if (first.present && first.count > 1 && (int64_t)tensors_.size() != first.tensors)
+        throw std::runtime_error("GGUF split checkpoint declares " + std::to_string(first.tensors) + " tensors, but " + std::to_string(tensors_.size()) +
+                                 " unique tensors were loaded");
+}
+GgufFile::~GgufFile() = default;
 
 int64_t GgufFile::get_int(const std::string& key) const {
     auto it = meta_.find(key);

@@ -1,4 +1,5 @@
-// Minimal GGUF v3 reader (memory-mapped): metadata key/values and tensor descriptors.
+// Minimal GGUF v3 reader (memory-mapped): metadata key/values and tensor descriptors of one file or of a shard family
+// `<prefix>-00001-of-000NN.gguf` opened through its first member (src/gguf.rs:576-660).
 // Format facts follow the reference's loader (src/gguf.rs:32-46,2155-2220): little-endian, default
 // alignment 32, dims stored innermost-first, tensor data contiguous after the aligned header.
 #pragma once
@@ -40,10 +41,20 @@ public:
     const GgufTensor& require(const std::string& name) const;
     const std::vector<GgufTensor>& tensors() const { return tensors_; }
     int64_t array_len(const std::string& key) const;
+    int shard_count() const { return (int)shards_.size(); }
 
 private:
-    void* map_ = nullptr;
-    size_t map_len_ = 0;
+    struct Shard {  // one mapped file; tensors point into it
+        void* map = nullptr;
+        size_t len = 0;
+        Shard() = default;
+        Shard(Shard&& o) noexcept;
+        Shard(const Shard&) = delete;
+        Shard& operator=(const Shard&) = delete;
+        ~Shard();
+    };
+    static Shard open_shard(const std::string& path, std::map<std::string, GgufValue>& meta, std::vector<GgufTensor>& tensors);
+    std::vector<Shard> shards_;
     std::map<std::string, GgufValue> meta_;
     std::vector<GgufTensor> tensors_;
     std::map<std::string, size_t> by_name_;

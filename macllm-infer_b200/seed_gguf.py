@@ -187,11 +187,8 @@ def stream_of(name: str) -> int:
     return zlib.crc32(name.encode("utf-8")) & 0xFFFFFFFF
 
 
-def write_seed_gguf(path: str | Path, spec: SeedSpec, seed: int = 0) -> Path:
-    """Write the checkpoint; returns the path.  Deterministic in (spec, seed)."""
-    path = Path(path)
-    plan = tensor_plan(spec)
-    metas = _meta(spec)
+def _write_file(path: Path, metas: list[bytes], plan, spec: SeedSpec, seed: int) -> Path:
+    """One GGUF file holding the given metadata records and the tensors of `plan` with their seeded payloads."""
     header = struct.pack("<IIQQ", GGUF_MAGIC, 3, len(plan), len(metas)) + b"".join(metas)
     infos = []
     offset = 0
@@ -220,6 +217,35 @@ def write_seed_gguf(path: str | Path, spec: SeedSpec, seed: int = 0) -> Path:
             f.write(data)
             f.write(b"\0" * ((-n) % ALIGN))
     return path
+
+
+def write_seed_gguf(path: str | Path, spec: SeedSpec, seed: int = 0) -> Path:
+    """Write the checkpoint; returns the path.  Deterministic in (spec, seed)."""
+    return _write_file(Path(path), _meta(spec), tensor_plan(spec), spec, seed)
+
+
+T_U16 = 2
+
+
+def split_metas(index: int, count: int, tensors: int) -> list[bytes]:
+    """The split.* records of shard `index` (src/gguf.rs:52-54,956-993: UINT16 index and count, INT32 tensor total)."""
+    return [_kv("split.no", T_U16, struct.pack("<H", index)), _kv("split.count", T_U16, struct.pack("<H", count)),
+            _kv("split.tensors.count", T_I32, struct.pack("<i", tensors))]
+
+
+def write_seed_gguf_shards(directory: str | Path, prefix: str, spec: SeedSpec, shards: int, seed: int = 0) -> Path:
+    """The same checkpoint as write_seed_gguf cut into `shards` files `<prefix>-0000i-of-0000n.gguf`: the tensors in
+    file order in contiguous groups, the whole metadata in the first file, the architecture and the split records in
+    the others.  Returns the path of the first shard, which is the one to load."""
+    directory = Path(directory)
+    plan = tensor_plan(spec)
+    per = -(-len(plan) // shards)
+    first = None
+    for i in range(shards):
+        metas = (_meta(spec) if i == 0 else [_kv("general.architecture", T_STR, _s(spec.arch))]) + split_metas(i, shards, len(plan))
+        path = _write_file(directory / f"{prefix}-{i + 1:05d}-of-{shards:05d}.gguf", metas, plan[i * per:(i + 1) * per], spec, seed)
+        first = first or path
+    return first
 
 
 def weight_bytes(spec: SeedSpec) -> dict:

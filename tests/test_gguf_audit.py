@@ -161,3 +161,49 @@ def test_rope_frequency_factors_are_read_for_llama_only(pk, tmp_path):
     good.extra = dict(good.extra, rope_factors=np.linspace(1.0, 8.0, good.head_dim // 2))
     s = pk["eng"].Model.inspect_gguf(seed.write_seed_gguf(tmp_path / "factors.gguf", good, seed=0))
     assert s["tensors_in_file"] == s["matrices"] + s["vectors"] + 1
+
+
+def test_shard_family_is_one_checkpoint(pk, tmp_path):
+    """src/gguf.rs:576-660: a family `<prefix>-00001-of-0000n.gguf` opened through its first member holds the tensors of
+    all members and the metadata of the first."""
+    seed = pk["seed"]
+    spec = spec_of(pk, "qwen3")
+    whole = pk["eng"].Model.inspect_gguf(seed.write_seed_gguf(tmp_path / "whole.gguf", spec, seed=0))
+    first = seed.write_seed_gguf_shards(tmp_path / "fam", "model", spec, 3, seed=0)
+    assert first.name == "model-00001-of-00003.gguf"
+    assert pk["eng"].Model.inspect_gguf(first) == whole
+
+
+def test_shard_family_rules(pk, tmp_path):
+    seed = pk["seed"]
+    spec = spec_of(pk, "llama")
+    plan, n = seed.tensor_plan(spec), len(seed.tensor_plan(spec))
+    half = n // 2
+    def family(d, first_metas=None, second_metas=None, first_plan=None, second_plan=None, names=("m-00001-of-00002.gguf", "m-00002-of-00002.gguf")):
+        d.mkdir()
+        arch = [seed._kv("general.architecture", seed.T_STR, seed._s(spec.arch))]
+        write_structure(pk, d / names[0], first_metas if first_metas is not None else seed._meta(spec) + seed.split_metas(0, 2, n),
+                        plan[:half] if first_plan is None else first_plan)
+        if names[1] is not None:
+            write_structure(pk, d / names[1], second_metas if second_metas is not None else arch + seed.split_metas(1, 2, n),
+                            plan[half:] if second_plan is None else second_plan)
+        return d / names[0]
+    arch = [seed._kv("general.architecture", seed.T_STR, seed._s(spec.arch))]
+    assert pk["eng"].Model.inspect_gguf(family(tmp_path / "ok"))["tensors_in_file"] == n
+    refused(pk, family(tmp_path / "gone", names=("m-00001-of-00002.gguf", None)), "failed to load GGUF shard 2 of 2")
+    refused(pk, family(tmp_path / "no", second_metas=arch + seed.split_metas(0, 2, n)), "declares split.no=0, expected 1")
+    refused(pk, family(tmp_path / "count", second_metas=arch + seed.split_metas(1, 3, n)), "declares split.count=3, expected 2")
+    refused(pk, family(tmp_path / "total", second_metas=arch + seed.split_metas(1, 2, n + 1)), f"declares split.tensors.count={n + 1}, expected {n}")
+    refused(pk, family(tmp_path / "nosplit", second_metas=arch), "is missing required split metadata")
+    refused(pk, family(tmp_path / "short", second_plan=plan[half:-1]), f"declares {n} tensors, but {n - 1} unique tensors were loaded")
+    refused(pk, family(tmp_path / "twice", second_plan=plan[half - 1:-1]), "appears more than once")
+    extra = arch + [seed._kv("llama.block_count", seed.T_U32, struct.pack("<I", 99))] + seed.split_metas(1, 2, n)
+    refused(pk, family(tmp_path / "conflict", second_metas=extra), "has conflicting metadata `llama.block_count`")
+    added = arch + [seed._kv("general.note", seed.T_STR, seed._s("x"))] + seed.split_metas(1, 2, n)
+    refused(pk, family(tmp_path / "added", second_metas=added), "contains metadata `general.note` absent from the first shard")
+    # the family must be entered through its first member, and names and metadata must tell the same story
+    ok_second = tmp_path / "ok" / "m-00002-of-00002.gguf"
+    refused(pk, ok_second, "has split.no=1; load the first shard instead")
+    refused(pk, family(tmp_path / "name", names=("plain.gguf", "m-00002-of-00002.gguf")), "does not match split.no=0 and split.count=2")
+    refused(pk, family(tmp_path / "meta", first_metas=seed._meta(spec), first_plan=plan, names=("m-00001-of-00002.gguf", None)),
+            "declares an active shard family, but its metadata does not")

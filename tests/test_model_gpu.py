@@ -204,6 +204,23 @@ def test_llama_rope_frequency_factors_match_oracle(pk, tmp_path_factory):
     assert np.max(np.abs(a - b)) > 1e-3
 
 
+def test_sharded_checkpoint_loads_to_the_same_model(pk, tmp_path_factory):
+    """A shard family (src/gguf.rs:576-660) and the single file with the same tensors give the same logits bit for bit."""
+    seed, eng = pk["seed"], pk["eng"]
+    spec = seed.scaled("qwen3-8b", layers=2, vocab=2048, hidden=1024, ffn=2048)
+    d = tmp_path_factory.mktemp("shards")
+    whole = seed.write_seed_gguf(d / "whole.gguf", spec, seed=0)
+    first = seed.write_seed_gguf_shards(d, "model", spec, 3, seed=0)
+    prompt = np.random.default_rng(12).integers(3, spec.vocab, size=45)
+    rows = []
+    for path in (whole, first):
+        model = eng.Model.load_gguf(path, kv_dtype="f16", matmul_path=0, max_batch_tokens=128, max_batch_lanes=4)
+        s = model.new_session()
+        logits, _ = model.forward_batch([(s, prompt, 0)])
+        rows.append(np.array(logits))
+    assert np.array_equal(rows[0], rows[1])
+
+
 def test_chunk_boundaries_15_16_17_agree_with_one_shot_prefill(pk, tmp_path_factory):
     """src/decoder.rs:8970-9013: chunking a prompt across a 16-token block boundary changes nothing."""
     path, spec = make_checkpoint(pk, tmp_path_factory, "llama")
