@@ -120,6 +120,14 @@ GgufAudit validate_decoder_tensors(const GgufFile& f, const ModelSpec& s) {
                           "sparse-MoE " + where + " contains unsupported dense tensor");
         }
     }
+    // quantised payloads are only defined for quantisation version 2 (validate_quantization_metadata, src/gguf.rs:1019-1037)
+    bool quantised = false;
+    for (const GgufTensor& t : f.tensors()) quantised |= (t.type != QT_F32 && t.type != QT_F16);
+    if (quantised) {
+        if (!f.has("general.quantization_version")) throw std::runtime_error("quantized GGUF tensors require general.quantization_version");
+        const int64_t v = f.get_int("general.quantization_version");
+        if (v != 2) throw std::runtime_error("unsupported GGUF quantization version " + std::to_string(v) + "; expected version 2");
+    }
     audit.tensors_in_file = (int64_t)f.tensors().size();
     return audit;
 }

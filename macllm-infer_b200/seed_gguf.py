@@ -95,6 +95,7 @@ def _meta(spec: SeedSpec) -> list[bytes]:
         _kv("general.architecture", T_STR, _s(a)),
         _kv("general.name", T_STR, _s(spec.name)),
         _kv("general.alignment", T_U32, struct.pack("<I", ALIGN)),
+        _kv("general.quantization_version", T_U32, struct.pack("<I", 2)),  # required beside quantised tensors (src/gguf.rs:1019-1037)
         _kv(f"{a}.block_count", T_U32, struct.pack("<I", spec.layers)),
         _kv(f"{a}.context_length", T_U32, struct.pack("<I", spec.context)),
         _kv(f"{a}.embedding_length", T_U32, struct.pack("<I", spec.hidden)),

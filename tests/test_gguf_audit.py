@@ -139,6 +139,11 @@ def test_metadata_errors(pk, tmp_path):
     def other_arch(spec, m, p):
         return [seed._kv("general.architecture", seed.T_STR, seed._s("mamba2")) if r.startswith(seed._s("general.architecture")) else r for r in m], p
     refused(pk, broken(pk, tmp_path, "llama", other_arch), "architecture `mamba2` is not supported on this path")
+    refused(pk, broken(pk, tmp_path, "llama", drop("general.quantization_version")), "quantized GGUF tensors require general.quantization_version")
+    def old_quant(spec, m, p):
+        key = "general.quantization_version"
+        return [seed._kv(key, seed.T_U32, struct.pack("<I", 1)) if r.startswith(seed._s(key)) else r for r in m], p
+    refused(pk, broken(pk, tmp_path, "llama", old_quant), "unsupported GGUF quantization version 1; expected version 2")
     def heads(spec, m, p):
         key = "qwen3.attention.head_count_kv"
         return [seed._kv(key, seed.T_U32, struct.pack("<I", 3)) if r.startswith(seed._s(key)) else r for r in m], p
