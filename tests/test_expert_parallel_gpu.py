@@ -1,7 +1,7 @@
-"""Expert parallelism of the sparse-MoE family over two GPUs (one process per GPU, NCCL): both ranks run the same
-ragged batches on half of the experts each and must end every forward with the same bits; against the same
+"""Expert parallelism of the sparse-MoE family over two and four GPUs (one process per GPU, NCCL): all ranks run the same
+ragged batches on their share of the experts and must end every forward with the same bits; against the same
 checkpoint served from one GPU the schedule is identical and the logits differ only by the association of the
-per-token sum over experts.  Needs two CUDA devices."""
+per-token sum over experts.  Needs as many CUDA devices as ranks."""
 import importlib
 import os
 import subprocess
@@ -65,16 +65,17 @@ CHILD = textwrap.dedent("""
 """) % (str(ROOT), str(ROOT / "tests"))
 
 
+@pytest.mark.parametrize("ranks", [2, 4])
 @pytest.mark.parametrize("exchange", ["fused", "nccl"])
-def test_two_ranks_hold_half_the_experts_and_agree(mk, tmp_path, exchange):
+def test_ranks_hold_their_share_of_the_experts_and_agree(mk, tmp_path, exchange, ranks):
     """exchange = fused: one kernel combines this rank's experts, stores the partial rows into the peers' memory over
     NVLink and adds all ranks' rows; nccl: combine kernel, ncclAllGather, sum kernel."""
     import pickle
     capi = importlib.import_module("macllm_infer_b200._capi")
     eng = importlib.import_module("macllm_infer_b200.engine")
     seed = importlib.import_module("macllm_infer_b200.seed_gguf")
-    if capi.lib().mk_device_count() < 2:
-        pytest.skip("needs two CUDA devices")
+    if capi.lib().mk_device_count() < ranks:
+        pytest.skip(f"needs {ranks} CUDA devices")
     spec = seed.scaled("qwen3-30b-a3b", layers=2, vocab=2048, hidden=1024, experts=16)
     gguf = tmp_path / "moe.gguf"
     seed.write_seed_gguf(gguf, spec, seed=0)
@@ -87,8 +88,8 @@ def test_two_ranks_hold_half_the_experts_and_agree(mk, tmp_path, exchange):
     del whole
 
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MACLLM_B200_EP_FUSED="1" if exchange == "fused" else "0")
-    procs = [subprocess.Popen([sys.executable, "-c", CHILD, str(r), "2", str(gguf), str(tmp_path / "ep.id"), str(tmp_path / f"out{r}.pkl"),
-                               str(spec.vocab)], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(2)]
+    procs = [subprocess.Popen([sys.executable, "-c", CHILD, str(r), str(ranks), str(gguf), str(tmp_path / "ep.id"), str(tmp_path / f"out{r}.pkl"),
+                               str(spec.vocab)], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(ranks)]
     try:
         for p in procs:
             _, err = p.communicate(timeout=300)
@@ -97,20 +98,21 @@ def test_two_ranks_hold_half_the_experts_and_agree(mk, tmp_path, exchange):
         for p in procs:
             if p.poll() is None:
                 p.kill()
-    out = [pickle.load(open(tmp_path / f"out{r}.pkl", "rb")) for r in range(2)]
+    out = [pickle.load(open(tmp_path / f"out{r}.pkl", "rb")) for r in range(ranks)]
 
-    # both ranks: the same schedule, tokens and logit bits
-    assert out[0]["trace"] == out[1]["trace"] == ref_trace
-    assert out[0]["tokens"] == out[1]["tokens"]
-    for a, b in zip(out[0]["logits"], out[1]["logits"]):
-        assert np.array_equal(a, b)
+    # all ranks: the same schedule, tokens and logit bits
+    for o in out[1:]:
+        assert out[0]["trace"] == o["trace"] == ref_trace
+        assert out[0]["tokens"] == o["tokens"]
+        for a, b in zip(out[0]["logits"], o["logits"]):
+            assert np.array_equal(a, b)
     # the fused exchange adds no launch to the single-GPU sequence; the NCCL form adds two per MoE layer and forward
     moe_layer_forwards = spec.layers * len(ref_trace)
     extra = 0 if exchange == "fused" else 2 * moe_layer_forwards
-    assert out[0]["launches"] == out[1]["launches"] == whole_launches + extra
-    # each rank holds half of the expert banks
+    assert all(o["launches"] == whole_launches + extra for o in out)
+    # each rank holds its share of the expert banks
     expert_bytes = sum(seed._tensor_bytes(dims, qtype) for name, dims, qtype, _ in seed.tensor_plan(spec) if "_exps" in name)
-    assert out[0]["weight_bytes"] == out[1]["weight_bytes"] == whole_bytes - expert_bytes // 2
+    assert all(o["weight_bytes"] == whole_bytes - expert_bytes * (ranks - 1) // ranks for o in out)
     # against one GPU: rows computed from the same inputs agree up to the reassociated expert sum
     worst = 0.0
     for toks, lg, rtoks, rlg in zip(out[0]["tokens"], out[0]["logits"], ref_tokens, ref_logits):
