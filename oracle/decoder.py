@@ -25,7 +25,10 @@ _SCALAR = {0: "<B", 1: "<b", 2: "<H", 3: "<h", 4: "<I", 5: "<i", 6: "<f", 7: "<B
 
 
 class Gguf:
-    def __init__(self, path):
+    """One GGUF file, or a shard family `<prefix>-00001-of-000NN.gguf` entered through its first member
+    (src/gguf.rs:576-660): later members add tensors, the metadata is the first member's."""
+
+    def __init__(self, path, _member=False):
         self.f = open(path, "rb")
         self.mm = mmap.mmap(self.f.fileno(), 0, access=mmap.ACCESS_READ)
         self.buf = np.frombuffer(self.mm, dtype=np.uint8)
@@ -48,6 +51,22 @@ class Gguf:
             order.append(name)
         align = self.meta.get("general.alignment", 32)
         self.data_start = (self.p + align - 1) // align * align
+        for t in self.tensors.values():
+            t["file"] = self
+        self.members = [self]
+        count = int(self.meta.get("split.count", 0))
+        if not _member and count > 1:
+            path = Path(path)
+            stem = path.name[:-len(".gguf")]
+            prefix, index = stem.rsplit("-of-", 1)[0].rsplit("-", 1)
+            assert int(index) == 1 and int(self.meta["split.no"]) == 0, "a shard family is entered through its first member"
+            for i in range(1, count):
+                g = Gguf(path.with_name(f"{prefix}-{i + 1:05d}-of-{count:05d}.gguf"), _member=True)
+                assert int(g.meta["split.no"]) == i and int(g.meta["split.count"]) == count
+                assert not set(g.tensors) & set(self.tensors), "a tensor appears in two shards"
+                self.tensors.update(g.tensors)
+                self.members.append(g)
+            assert len(self.tensors) == int(self.meta["split.tensors.count"])
 
     def _unpack(self, fmt):
         n = struct.calcsize(fmt)
@@ -83,8 +102,9 @@ class Gguf:
         cols = t["dims"][-1]
         rows = int(np.prod(t["dims"][:-1])) if len(t["dims"]) > 1 else 1
         n = rows * M.row_bytes(t["type"], cols)
-        start = self.data_start + t["offset"]
-        return self.buf[start:start + n], t["type"], rows, cols
+        src = t["file"]
+        start = src.data_start + t["offset"]
+        return src.buf[start:start + n], t["type"], rows, cols
 
     def f32(self, name):
         raw, qtype, rows, cols = self.raw(name)

@@ -212,3 +212,16 @@ def test_shard_family_rules(pk, tmp_path):
     refused(pk, family(tmp_path / "name", names=("plain.gguf", "m-00002-of-00002.gguf")), "does not match split.no=0 and split.count=2")
     refused(pk, family(tmp_path / "meta", first_metas=seed._meta(spec), first_plan=plan, names=("m-00001-of-00002.gguf", None)),
             "declares an active shard family, but its metadata does not")
+
+
+def test_oracle_reads_a_shard_family_like_the_single_file(pk, tmp_path):
+    """The oracle's reader follows the same family rule, so sharded checkpoints can be compared with the product."""
+    from oracle import decoder
+    seed = pk["seed"]
+    spec = spec_of(pk, "qwen3")
+    whole = decoder.Gguf(seed.write_seed_gguf(tmp_path / "whole.gguf", spec, seed=0))
+    family = decoder.Gguf(seed.write_seed_gguf_shards(tmp_path / "fam", "model", spec, 3, seed=0))
+    assert len(family.members) == 3 and set(family.tensors) == set(whole.tensors)
+    for name in whole.tensors:
+        a, b = whole.raw(name), family.raw(name)
+        assert a[1:] == b[1:] and np.array_equal(a[0], b[0]), name
