@@ -453,6 +453,13 @@ typedef struct mk_attn_case {
 } mk_attn_case;
 int32_t mk_k_attention_step(const mk_attn_case* c);
 
+/* Host-only: how one tick's attention work is cut (the plan the model builds before every forward).  Lanes with more
+ * than one token become query tiles; one-token lanes become one CTA per KV head, or several key shares when that pays.
+ * shares_out[i] = key shares of lane i (0 for lanes with more than one token); *tiles_out = query tiles;
+ * *max_entries_out = the bound buffers are sized for.  Needs no GPU. */
+int32_t mk_k_attention_plan(const int32_t* start_pos, const int32_t* n_tokens, int32_t lanes, int32_t q_heads, int32_t kv_heads,
+                            int32_t block_tokens, int32_t* shares_out, int32_t* tiles_out, int32_t* max_entries_out);
+
 /* argmax of src/sampling.rs:425-433 for each row of logits [B][vocab]. */
 int32_t mk_k_argmax(const float* logits, int32_t B, int32_t vocab, uint32_t* out);
 

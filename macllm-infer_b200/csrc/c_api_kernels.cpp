@@ -489,6 +489,23 @@ int32_t mk_k_moe_route(const float* logits, int32_t T, int32_t experts, int32_t 
     });
 }
 
+int32_t mk_k_attention_plan(const int32_t* start_pos, const int32_t* n_tokens, int32_t lanes, int32_t q_heads, int32_t kv_heads,
+                            int32_t block_tokens, int32_t* shares_out, int32_t* tiles_out, int32_t* max_entries_out) {
+    return guarded([&] {
+        if (lanes <= 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || block_tokens <= 0)
+            throw std::runtime_error("mk_k_attention_plan: arguments out of range");
+        std::vector<int32_t> n_blocks((size_t)lanes);
+        for (int i = 0; i < lanes; ++i) n_blocks[(size_t)i] = (start_pos[i] + n_tokens[i] + block_tokens - 1) / block_tokens;
+        AttnTcPlan plan;
+        plan_attention_tc(start_pos, n_tokens, n_blocks.data(), lanes, q_heads, kv_heads, plan);
+        for (int i = 0; i < lanes; ++i) shares_out[i] = 0;
+        for (int e = 0; e < plan.n_entries(); ++e) shares_out[plan.entries[(size_t)e * 8]] = plan.entries[(size_t)e * 8 + 2];
+        *tiles_out = plan.n_tiles();
+        *max_entries_out = attention_tc_max_entries(lanes, kv_heads);
+        if (plan.n_entries() > *max_entries_out) throw std::runtime_error("mk_k_attention_plan: the plan exceeds its own bound");
+    });
+}
+
 int32_t mk_k_moe_combine_exchange(const float* expert_out, const int32_t* sel, const float* weights, int32_t T, int32_t k,
                                   int32_t hidden, int32_t e_lo, int32_t e_hi, int32_t ranks, int32_t rank, const float* peer_rows,
                                   int32_t deliver, int32_t wait_ms, int32_t epochs, float* out, float* pushed, int32_t* status_out) {

@@ -119,6 +119,17 @@ def moe_route(logits, k: int):
     return sel, w
 
 
+def attention_plan(start_pos, n_tokens, q_heads: int, kv_heads: int, block_tokens: int = 16):
+    """Host-only: (key shares per lane, query tiles, entry bound) of one tick's attention plan."""
+    sp = np.ascontiguousarray(start_pos, dtype=np.int32)
+    nt = np.ascontiguousarray(n_tokens, dtype=np.int32)
+    shares = np.zeros(len(sp), dtype=np.int32)
+    tiles, bound = C.c_int32(0), C.c_int32(0)
+    capi.check(capi.lib().mk_k_attention_plan(_p(sp), _p(nt), len(sp), q_heads, kv_heads, block_tokens, _p(shares), C.byref(tiles),
+                                              C.byref(bound)))
+    return shares, int(tiles.value), int(bound.value)
+
+
 def moe_combine_exchange(expert_out, sel, weights, e_lo: int, e_hi: int, ranks: int, rank: int, peer_rows=None, wait_ms: int = 50,
                          epochs: int = 1):
     """One rank's launch(es) of the fused expert-parallel combine + exchange kernel with every rank's exchange block on
