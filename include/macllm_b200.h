@@ -453,6 +453,12 @@ typedef struct mk_attn_case {
 } mk_attn_case;
 int32_t mk_k_attention_step(const mk_attn_case* c);
 
+/* Host-only: how one matmul launch is cut into work items.  path MK_PATH_HALF: out = {token-tile width, row tiles, token
+ * tiles, K shares, K blocks (of 64) per share, floats of partial sums}; path MK_PATH_STREAM (T <= 64): out = {token-tile
+ * width, row tiles, (row tile, 256-column block) units, persistent CTAs, partial-sum slots, floats of partial sums}.
+ * Needs no GPU. */
+int32_t mk_k_matmul_plan(int32_t path, int64_t rows, int64_t cols, int32_t T, int32_t max_splits, int64_t* out6);
+
 /* Host-only: how one tick's attention work is cut (the plan the model builds before every forward).  Lanes with more
  * than one token become query tiles; one-token lanes become one CTA per KV head, or several key shares when that pays.
  * shares_out[i] = key shares of lane i (0 for lanes with more than one token); *tiles_out = query tiles;

@@ -189,6 +189,7 @@ SIGNATURES = {
     "mk_k_embed": (_i32, [_i32, P, _i64, _i64, P, _i32, _f32, P]),
     "mk_k_actmul": (_i32, [P, P, _i32, _i32, _i32, P]),
     "mk_k_moe_combine_exchange": (_i32, [P, P, P, _i32, _i32, _i32, _i32, _i32, _i32, _i32, P, _i32, _i32, _i32, P, P, P]),
+    "mk_k_matmul_plan": (_i32, [_i32, _i64, _i64, _i32, _i32, P]),
     "mk_k_attention_plan": (_i32, [P, P, _i32, _i32, _i32, _i32, P, P, P]),
     "mk_k_gated_ffn": (_i32, [_i32, P, P, _i64, _i64, P, _i32, _i32, P, _i32, P]),
     "mk_k_attention_step": (_i32, [C.POINTER(AttnCase)]),

@@ -489,6 +489,25 @@ int32_t mk_k_moe_route(const float* logits, int32_t T, int32_t experts, int32_t 
     });
 }
 
+int32_t mk_k_matmul_plan(int32_t path, int64_t rows, int64_t cols, int32_t T, int32_t max_splits, int64_t* out6) {
+    return guarded([&] {
+        if (rows <= 0 || cols <= 0 || T <= 0 || out6 == nullptr) throw std::runtime_error("mk_k_matmul_plan: arguments out of range");
+        if (path == MK_PATH_HALF) {
+            if (cols % 64 != 0) throw std::runtime_error("mk_k_matmul_plan: the f16-image GEMM needs columns in multiples of 64");
+            HgemmPlan p = hgemm_tc_plan(rows, cols, T, max_splits);
+            const int64_t v[6] = {p.bn, p.row_tiles, p.n_tiles, p.splits, p.kb_per_split, (int64_t)p.partial_floats};
+            memcpy(out6, v, sizeof v);
+        } else if (path == MK_PATH_STREAM) {
+            if (cols % 256 != 0 || T > kQStreamMaxRows) throw std::runtime_error("mk_k_matmul_plan: the streamed matmul covers 256-wide blocks and at most 64 rows");
+            QStreamPlan p = qstream_plan(rows, cols, T, max_splits);
+            const int64_t v[6] = {p.bn, p.row_tiles, p.units, p.ctas, p.slots, (int64_t)p.partial_floats};
+            memcpy(out6, v, sizeof v);
+        } else {
+            throw std::runtime_error("mk_k_matmul_plan: only the f16-image and the streamed path are planned on the host");
+        }
+    });
+}
+
 int32_t mk_k_attention_plan(const int32_t* start_pos, const int32_t* n_tokens, int32_t lanes, int32_t q_heads, int32_t kv_heads,
                             int32_t block_tokens, int32_t* shares_out, int32_t* tiles_out, int32_t* max_entries_out) {
     return guarded([&] {

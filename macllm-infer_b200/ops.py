@@ -119,6 +119,15 @@ def moe_route(logits, k: int):
     return sel, w
 
 
+def matmul_plan(path: int, rows: int, cols: int, T: int, max_splits: int = 16) -> dict:
+    """Host-only: how a launch of the f16-image GEMM (PATH_HALF) or the streamed matmul (PATH_STREAM) is cut."""
+    out = np.zeros(6, dtype=np.int64)
+    capi.check(capi.lib().mk_k_matmul_plan(path, rows, cols, T, max_splits, _p(out)))
+    names = ("bn", "row_tiles", "n_tiles", "splits", "kb_per_split", "partial_floats") if path == capi.PATH_HALF else \
+        ("bn", "row_tiles", "units", "ctas", "slots", "partial_floats")
+    return dict(zip(names, map(int, out)))
+
+
 def attention_plan(start_pos, n_tokens, q_heads: int, kv_heads: int, block_tokens: int = 16):
     """Host-only: (key shares per lane, query tiles, entry bound) of one tick's attention plan."""
     sp = np.ascontiguousarray(start_pos, dtype=np.int32)
