@@ -149,6 +149,11 @@ int32_t mk_model_load_gguf(const char* path, const mk_load_config* cfg, mk_model
  * like FakeModel in the reference's scheduler tests (src/engine.rs:3107-3300).  fail_forward_at >= 0
  * makes that forward (0-based) fail, to exercise rollback. */
 int32_t mk_model_new_fake(int32_t vocab, int32_t max_context, const mk_load_config* cfg, int64_t fail_forward_at, mk_model** out);
+/* More injection sites of the fake model, like FakeModel's fail_completion_barrier_at and friends (src/engine.rs:
+ * 3107-3300): the call numbered `index` (0-based) at `site` fails.  site 0 forward, 1 completion barrier
+ * (mk_read_output), 2 prompt admission (mk_reset_session_for_prompt), 3 cleanup drain (mk_synchronize).  Refused for
+ * a model loaded from a file. */
+int32_t mk_model_fake_inject(mk_model* m, int32_t site, int64_t index);
 int32_t mk_model_free(mk_model* m);
 /* Expert parallelism, one process per GPU.  Rank 0 calls mk_ep_unique_id (MK_EP_ID_BYTES bytes out) and passes the
  * id to the other ranks out of band; then every rank calls mk_model_ep_init on its model (loaded with the same
@@ -197,7 +202,9 @@ int32_t mk_reservation_drop(mk_reservation* r);
 
 /* CausalLm::forward_batch_tokens_reserved (src/architecture.rs:1218-1227; src/decoder.rs:4203-4269):
  * validates every lane before any mutation, consumes the reservation, enqueues the whole tick on the
- * model's stream and returns without waiting. */
+ * model's stream and returns without waiting.  One tick may be in flight: the tick's staging and result buffers are
+ * reused by the next one, so a second forward before mk_read_output or mk_synchronize is refused ("previous forward
+ * was not read") and changes nothing. */
 int32_t mk_forward_batch_reserved(mk_model* m, const mk_lane* lanes, int32_t n_lanes, mk_reservation* r, uint32_t flags);
 /* CausalLm::read_output_to_cpu (src/architecture.rs:1229-1235; src/decoder.rs:3779-3783): the
  * completion barrier; also releases KV pages retired before this tick.  logits may be NULL. */
@@ -273,6 +280,7 @@ typedef struct mk_engine_stats {
     int64_t failed_requests;
     int64_t kv_shrinks;          /* candidate lanes dropped because the pool was exhausted */
     double device_ms;            /* sum of per-tick device times */
+    int64_t cleanup_drains;      /* mk_synchronize calls made while poisoning (src/engine.rs:2723-2736) */
 } mk_engine_stats;
 
 int32_t mk_engine_new(mk_model* m, const mk_engine_config* cfg, mk_engine** out);
@@ -293,6 +301,15 @@ int32_t mk_engine_logits(mk_engine* e, int32_t request_id, float* out, int32_t* 
 /* Lanes of tick `tick` (0-based); capacity in *n. */
 int32_t mk_engine_trace(mk_engine* e, int64_t tick, mk_tick_lane* lanes, int32_t* n);
 int32_t mk_engine_stats_query(mk_engine* e, mk_engine_stats* out);
+/* EngineStatus (src/engine.rs:281-288): 1 Ready, 2 Busy, 3 Poisoned.  An error that escapes a tick (a failed forward, a
+ * failed completion barrier, a broken scheduler invariant) poisons the engine like ServingScheduler::run / poison
+ * (src/engine.rs:1577-1647,2719-2770): what was submitted is drained once with mk_synchronize, every active, pending
+ * and queued request fails with kind 4 (Fatal) and the message "inference worker failed: ...", the sessions are
+ * dropped, mk_engine_step becomes a no-op and mk_engine_submit answers "inference worker is unavailable (Poisoned)". */
+int32_t mk_engine_status(mk_engine* e, int32_t* status);
+/* EngineFailureKind of a failed request (src/engine.rs:268-273): 0 none, 1 InvalidRequest, 2 ResourceExhausted,
+ * 3 Internal, 4 Fatal. */
+int32_t mk_engine_failure_kind(mk_engine* e, int32_t request_id, int32_t* kind);
 
 /* ------------------------------------------------------------------------------------------------
  * Host-only paged-KV pool and prefix cache, exposed for parity tests of block tables, refcounts and

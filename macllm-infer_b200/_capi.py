@@ -92,7 +92,7 @@ class TickLane(C.Structure):
 class EngineStats(C.Structure):
     _fields_ = [("ticks", C.c_int64), ("prefill_tokens", C.c_int64), ("decode_tokens", C.c_int64),
                 ("completed_requests", C.c_int64), ("failed_requests", C.c_int64), ("kv_shrinks", C.c_int64),
-                ("device_ms", C.c_double)]
+                ("device_ms", C.c_double), ("cleanup_drains", C.c_int64)]
 
 
 class KernelProfile(C.Structure):
@@ -121,6 +121,7 @@ SIGNATURES = {
     "mk_device_count": (_i32, []),
     "mk_model_load_gguf": (_i32, [C.c_char_p, C.POINTER(LoadConfig), C.POINTER(P)]),
     "mk_model_new_fake": (_i32, [_i32, _i32, C.POINTER(LoadConfig), _i64, C.POINTER(P)]),
+    "mk_model_fake_inject": (_i32, [P, _i32, _i64]),
     "mk_model_free": (_i32, [P]),
     "mk_gguf_inspect": (_i32, [C.c_char_p, C.POINTER(GgufSummary)]),
     "mk_ep_unique_id": (_i32, [P]),
@@ -156,6 +157,8 @@ SIGNATURES = {
     "mk_engine_logits": (_i32, [P, _i32, P, C.POINTER(_i32)]),
     "mk_engine_trace": (_i32, [P, _i64, C.POINTER(TickLane), C.POINTER(_i32)]),
     "mk_engine_stats_query": (_i32, [P, C.POINTER(EngineStats)]),
+    "mk_engine_status": (_i32, [P, C.POINTER(_i32)]),
+    "mk_engine_failure_kind": (_i32, [P, _i32, C.POINTER(_i32)]),
     "mk_kvpool_new": (_i32, [_i32, _i32, _i64, C.POINTER(P)]),
     "mk_kvpool_free": (_i32, [P]),
     "mk_kvpool_stats": (_i32, [P, C.POINTER(PoolStats)]),

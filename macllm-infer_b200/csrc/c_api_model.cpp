@@ -139,6 +139,14 @@ int32_t mk_model_new_fake(int32_t vocab, int32_t max_context, const mk_load_conf
     });
 }
 
+int32_t mk_model_fake_inject(mk_model* m, int32_t site, int64_t index) {
+    return guarded([&] {
+        FakeLm* fake = dynamic_cast<FakeLm*>(m->lm.get());
+        if (fake == nullptr) throw std::runtime_error("failure injection is only available on the host-only fake model");
+        fake->inject_failure(site, index);
+    });
+}
+
 int32_t mk_model_free(mk_model* m) {
     return guarded([&] { delete m; });
 }
@@ -414,7 +422,16 @@ int32_t mk_engine_stats_query(mk_engine* e, mk_engine_stats* out) {
         out->failed_requests = s.failed;
         out->kv_shrinks = s.kv_shrinks;
         out->device_ms = s.device_ms;
+        out->cleanup_drains = s.cleanup_drains;
     });
+}
+
+int32_t mk_engine_status(mk_engine* e, int32_t* status) {
+    return guarded([&] { *status = (int32_t)e->e->status(); });
+}
+
+int32_t mk_engine_failure_kind(mk_engine* e, int32_t request_id, int32_t* kind) {
+    return guarded([&] { *kind = (int32_t)e->e->result(request_id).kind; });
 }
 
 // ------------------------------------------------------------------------------------------ host-only pool

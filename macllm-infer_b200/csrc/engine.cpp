@@ -21,6 +21,7 @@ Engine::~Engine() {
 }
 
 std::vector<int> Engine::submit(const std::vector<EngineRequest>& reqs, bool atomic_batch) {
+    if (poisoned_) throw std::runtime_error("inference worker is unavailable (Poisoned)");  // SubmitError::Unavailable, engine.rs:394-402,923
     if (reqs.empty()) throw std::runtime_error("submission is empty");
     if ((int)(queue_.size() + reqs.size()) > cfg_.queue_capacity) throw std::runtime_error("inference queue is full");
     if (atomic_batch && (int)reqs.size() > cfg_.max_active_sequences)
@@ -46,11 +47,39 @@ const EngineResult& Engine::result(int id) const {
     return it->second;
 }
 
-void Engine::fail_request(int id, const std::string& message) {
+void Engine::fail_request(int id, const std::string& message, FailureKind kind) {
     EngineResult& r = results_[id];
+    if (r.state != FinishState::Running) return;  // a terminal event is delivered once
     r.state = FinishState::Failed;
     r.message = message;
+    r.kind = kind;
     ++stats_.failed;
+}
+
+// ServingScheduler::poison (engine.rs:2719-2770): drain what was submitted, fail every active slot, every member of
+// a pending atomic batch and every queued job with kind Fatal, drop the sequences and all reusable sessions.
+void Engine::poison(std::string message) {
+    poisoned_ = true;
+    if (forward_needs_drain_) {
+        forward_needs_drain_ = false;
+        ++stats_.cleanup_drains;
+        try {
+            model_.synchronize();
+        } catch (const std::exception& e) {
+            message += std::string("; forward-error cleanup synchronization also failed: ") + e.what();
+        }
+    }
+    if (orphan_ >= 0) fail_request(orphan_, message, FailureKind::Fatal);
+    orphan_ = -1;
+    for (auto& slot : active_) fail_request(slot->id, message, FailureKind::Fatal);
+    active_.clear();    // sequences go without a completion barrier of their own (discard_session_without_synchronize)
+    sessions_.clear();
+    for (Job& j : pending_atomic_) fail_request(j.id, message, FailureKind::Fatal);
+    pending_atomic_.clear();
+    for (Job& j : queue_) fail_request(j.id, message, FailureKind::Fatal);
+    queue_.clear();
+    round_visits_remaining_ = round_budget_remaining_ = 0;
+    poison_message_ = std::move(message);
 }
 
 void Engine::admit(Job job) {  // admit_with_diagnostic_refresh, engine.rs:1654-1808
@@ -83,9 +112,16 @@ void Engine::admit(Job job) {  // admit_with_diagnostic_refresh, engine.rs:1654-
     seq->prompt_tokens = (int)rq.prompt.size();
     seq->rng = rq.seed * 0x9E3779B97F4A7C15ull + 0xD1B54A32D192ED03ull;
     // GenerationCore::new (generation.rs:787-832): prefix lookup + block-table attach happen at admission
-    int64_t cached = model_.reset_session_for_prompt(*seq->session, seq->history.data(), seq->history.size());
-    if (cached >= (int64_t)seq->history.size())
-        throw std::runtime_error("prefix cache must leave at least one prompt token for first-token logits");
+    int64_t cached = 0;
+    try {
+        cached = model_.reset_session_for_prompt(*seq->session, seq->history.data(), seq->history.size());
+        if (cached >= (int64_t)seq->history.size())
+            throw std::runtime_error("prefix cache must leave at least one prompt token for first-token logits");
+    } catch (...) {
+        sessions_.push_back(std::move(seq->session));  // the slot's session is not lost with the failed admission
+        orphan_ = job.id;                              // neither queued nor active any more: poison() answers it
+        throw;
+    }
     seq->cursor = (int)cached;
     results_[job.id].cached_tokens = cached;
     active_.push_back(std::move(seq));
@@ -197,7 +233,19 @@ uint32_t Engine::sample(Sequence& s, float* row) {  // Sampler::sample_with_gene
     return (uint32_t)argmax_first(prob.data(), vocab);
 }
 
-int Engine::step() {  // drive_once, engine.rs:1938-1964
+int Engine::step() {  // one turn of ServingScheduler::run, engine.rs:1577-1647
+    if (poisoned_) return 0;
+    try {
+        return drive_once();
+    } catch (const std::exception& e) {
+        poison(std::string("inference worker failed: ") + e.what());
+    } catch (...) {
+        poison("inference worker panicked and was poisoned");
+    }
+    return 0;
+}
+
+int Engine::drive_once() {  // engine.rs:1938-1964
     try_admit_available();
     if (active_.empty()) return 0;
     if (round_visits_remaining_ == 0 || round_budget_remaining_ == 0) {
@@ -264,9 +312,13 @@ int Engine::step() {  // drive_once, engine.rs:1938-1964
                 lanes.push_back(LmLane{s.session.get(), nullptr, v.n_tokens, v.start_pos});
             }
             try {
+                // a failed allocation may leave storage initialisation work behind; Exhausted and success reset the
+                // obligation to drain (engine.rs:2131-2152)
+                forward_needs_drain_ = true;
                 reservation = model_.reserve_batch(lanes);
                 break;
             } catch (const KvPoolExhausted& e) {
+                forward_needs_drain_ = false;
                 if (selected > 1) {  // drop the LAST candidate and retry (engine.rs:2145-2149)
                     --selected;
                     ++stats_.kv_shrinks;
@@ -275,7 +327,7 @@ int Engine::step() {  // drive_once, engine.rs:1938-1964
                 // one irreducible lane fails only that request (fail_kv_exhausted_visit, engine.rs:2205-2231)
                 for (int idx : candidates) actions[(size_t)idx].kind = Visit::Keep;
                 Sequence& s = *active_[(size_t)candidates[0]];
-                fail_request(s.id, e.what());
+                fail_request(s.id, e.what(), FailureKind::ResourceExhausted);
                 s.delivering = true;
                 reclaim(s);
                 selected = 0;
@@ -314,6 +366,7 @@ int Engine::step() {  // drive_once, engine.rs:1938-1964
             if (v.was_prefill) stats_.prefill_tokens += v.n_tokens; else stats_.decode_tokens += v.n_tokens;
         }
         uint32_t flags = device_greedy ? FWD_WANT_TOKENS : FWD_WANT_LOGITS;
+        forward_needs_drain_ = true;  // engine.rs:2294
         model_.forward_batch_reserved(lanes, std::move(reservation), flags);
         // validate every lane's cache length BEFORE sampling (engine.rs:2258-2265)
         for (const LmLane& l : lanes)
@@ -321,6 +374,7 @@ int Engine::step() {  // drive_once, engine.rs:1938-1964
                 throw std::runtime_error("model advanced generation cache to an unexpected length");
         // complete_mixed_forward (engine.rs:2378-2409): the completion barrier
         const int vocab = model_.spec().vocab;
+        forward_needs_drain_ = false;  // the read-back is the barrier; a failure inside it is not drained again (engine.rs:2388-2391)
         if (device_greedy) {
             tokens_host_.resize((size_t)lane_count);
             model_.read_output(nullptr, tokens_host_.data());
@@ -387,6 +441,7 @@ int Engine::step() {  // drive_once, engine.rs:1938-1964
         }
     } else {
         reservation.reset();
+        forward_needs_drain_ = false;
     }
 
     // ---- finalize_visits (engine.rs:2525-2614)
@@ -435,7 +490,7 @@ int Engine::step() {  // drive_once, engine.rs:1938-1964
 
 void Engine::run() {
     int idle = 0;
-    while (pending() > 0) {
+    while (pending() > 0 && !poisoned_) {
         int lanes = step();
         idle = lanes > 0 ? 0 : idle + 1;
         if (idle > 4 * (cfg_.max_active_sequences + 4)) throw std::runtime_error("scheduler made no progress");

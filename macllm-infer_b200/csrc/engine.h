@@ -34,11 +34,16 @@ struct EngineRequest {
 };
 
 enum class FinishState : int { Running = 0, Done = 1, Failed = 2 };
+// EngineFailureKind (src/engine.rs:268-273)
+enum class FailureKind : int { None = 0, InvalidRequest = 1, ResourceExhausted = 2, Internal = 3, Fatal = 4 };
+// EngineStatus (src/engine.rs:281-288); this engine is driven by its caller's thread, so Starting never shows
+enum class EngineStatus : int { Starting = 0, Ready = 1, Busy = 2, Poisoned = 3, Stopped = 4 };
 
 struct EngineResult {
     std::vector<uint32_t> tokens;
     FinishState state = FinishState::Running;
     std::string message;        // failure message
+    FailureKind kind = FailureKind::None;
     std::string finish_reason;  // "length", "stop"
     int64_t cached_tokens = 0;
     std::vector<float> logits;  // record_logits: one row per sampled position
@@ -50,7 +55,7 @@ struct TickLaneTrace {
 };
 
 struct EngineStats {
-    int64_t ticks = 0, prefill_tokens = 0, decode_tokens = 0, completed = 0, failed = 0, kv_shrinks = 0;
+    int64_t ticks = 0, prefill_tokens = 0, decode_tokens = 0, completed = 0, failed = 0, kv_shrinks = 0, cleanup_drains = 0;
     double device_ms = 0.0;
 };
 
@@ -62,8 +67,12 @@ public:
     // EngineHandle::submit / submit_batch: returns request ids.  An atomic batch is admitted only when
     // every member fits into the active set at once.  Throws when the queue is full.
     std::vector<int> submit(const std::vector<EngineRequest>& reqs, bool atomic_batch);
-    // ServingScheduler::drive_once.  Returns the number of lanes of the packed forward (0 when none ran).
+    // One turn of ServingScheduler::run (src/engine.rs:1577-1647): admission and drive_once.  Returns the number of
+    // lanes of the packed forward (0 when none ran).  Any error that escapes the tick poisons the engine: every active,
+    // pending and queued request fails with kind Fatal, the sessions are dropped, later submissions are refused.
     int step();
+    EngineStatus status() const { return poisoned_ ? EngineStatus::Poisoned : (pending() > 0 ? EngineStatus::Busy : EngineStatus::Ready); }
+    const std::string& poison_message() const { return poison_message_; }
     void run();
     int pending() const { return (int)(queue_.size() + pending_atomic_.size() + active_.size()); }
     const EngineResult& result(int id) const;
@@ -103,7 +112,9 @@ private:
     bool try_admit_available();
     bool admit_pending_atomic();
     void admit(Job job);
-    void fail_request(int id, const std::string& message);
+    int drive_once();
+    void poison(std::string message);
+    void fail_request(int id, const std::string& message, FailureKind kind = FailureKind::InvalidRequest);
     void reclaim(Sequence& s);
     uint32_t sample(Sequence& s, float* row);
 
@@ -120,6 +131,10 @@ private:
     int round_visits_remaining_ = 0, round_budget_remaining_ = 0;
     std::vector<float> logits_host_;
     std::vector<uint32_t> tokens_host_;
+    bool poisoned_ = false;
+    int orphan_ = -1;                   // request whose admission threw
+    bool forward_needs_drain_ = false;  // a reservation or forward was submitted and no completion barrier ran yet
+    std::string poison_message_;
 };
 
 }  // namespace mk

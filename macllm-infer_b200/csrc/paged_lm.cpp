@@ -38,6 +38,7 @@ void PagedLm::clear_session(LmSession& s) {  // :3804-3818
 
 int64_t PagedLm::reset_session_for_prompt(LmSession& s, const uint32_t* tokens, size_t n) {  // :3494-3532
     validate_session(s);
+    on_reset_session();
     clear_session(s);
     if (s.logical_len != 0 || s.table->logical_len() != 0)
         throw std::runtime_error("decoder session did not become empty before prompt admission");
@@ -117,6 +118,9 @@ std::unique_ptr<LmReservation> PagedLm::reserve_batch(const std::vector<LmLane>&
 void PagedLm::forward_batch_reserved(const std::vector<LmLane>& lanes, std::unique_ptr<LmReservation> reservation,
                                      uint32_t flags) {  // :4203-4269, :4125-4201
     if (lanes.empty()) throw std::runtime_error("mixed-sequence batch cannot be empty");
+    // one tick in flight: the staging buffers and the output buffer of a tick are reused by the next one
+    if (forward_unread_)
+        throw std::runtime_error("previous forward was not read: call read_output or synchronize before the next forward");
     if (!reservation || reservation->owner != this || !reservation->paged)
         throw std::runtime_error("forward needs a KV reservation made by this model");
     if (reservation->sessions.size() != lanes.size())
@@ -139,6 +143,7 @@ void PagedLm::forward_batch_reserved(const std::vector<LmLane>& lanes, std::uniq
     KvReservation& paged = *reservation->paged;
     paged.mark_all_used();
     run_forward(lanes, paged, flags);  // a throw leaves every session untouched; the reservation rolls back
+    forward_unread_ = true;
     paged.commit();
     for (const LmLane& l : lanes) l.session->logical_len = (int64_t)l.start_pos + l.n_tokens;
     last_lanes_ = (int)lanes.size();
@@ -146,11 +151,14 @@ void PagedLm::forward_batch_reserved(const std::vector<LmLane>& lanes, std::uniq
 }
 
 void PagedLm::read_output(float* logits, uint32_t* tokens) {  // :3779-3783
+    if (!forward_unread_) throw std::runtime_error("no forward is waiting to be read");
+    forward_unread_ = false;  // a failed barrier is not retried (src/engine.rs:2388-2391)
     fetch_output(logits, tokens);
     pool_->mark_completed_through(pool_->submitted_epoch());
 }
 
 void PagedLm::synchronize() {  // :3785-3788
+    forward_unread_ = false;
     device_synchronize();
     pool_->mark_completed_through(pool_->submitted_epoch());
 }
@@ -176,7 +184,26 @@ void FakeLm::run_forward(const std::vector<LmLane>& lanes, KvReservation&, uint3
     }
 }
 
+void FakeLm::inject_failure(int site, int64_t index) {
+    switch (site) {
+        case 0: fail_at_ = index; break;
+        case 1: fail_read_at_ = index; break;
+        case 2: fail_reset_at_ = index; break;
+        case 3: fail_drain_at_ = index; break;
+        default: throw std::runtime_error("unknown failure site");
+    }
+}
+
+void FakeLm::device_synchronize() {
+    if (drains_++ == fail_drain_at_) throw std::runtime_error("injected synchronize failure");
+}
+
+void FakeLm::on_reset_session() {
+    if (resets_++ == fail_reset_at_) throw std::runtime_error("injected admission failure");
+}
+
 void FakeLm::fetch_output(float* logits, uint32_t* tokens) {
+    if (reads_++ == fail_read_at_) throw std::runtime_error("injected completion barrier failure");
     for (size_t i = 0; i < next_.size(); ++i) {
         if (tokens) tokens[i] = next_[i];
         if (logits) {

@@ -100,6 +100,7 @@ protected:
     // Wait for the tick and copy the requested outputs to the host.
     virtual void fetch_output(float* logits, uint32_t* tokens) = 0;
     virtual void device_synchronize() {}
+    virtual void on_reset_session() {}  // test hook: the fake model injects admission failures here
 
     LmRuntimeSpec spec_;
     std::shared_ptr<KvPool> pool_;
@@ -107,6 +108,7 @@ protected:
     std::unique_ptr<TokenPrefixCache<Snapshot>> prefix_cache_;
     int last_lanes_ = 0;
     uint32_t last_flags_ = 0;
+    bool forward_unread_ = false;  // a forward was enqueued and neither read_output nor synchronize has run since
 };
 
 // Host-only model with deterministic one-hot logits, used to exercise the scheduler, the KV pool and
@@ -118,14 +120,21 @@ public:
     FakeLm(int vocab, int max_context, int block_tokens, int slab_blocks, int64_t capacity_tokens, int64_t prefix_capacity_tokens);
     // Fail the forward numbered `index` (0-based) with an exception, to test rollback.
     void fail_forward_at(int64_t index) { fail_at_ = index; }
+    // The same for the completion barrier (site 1), prompt admission (site 2) and the cleanup drain (site 3), like
+    // fail_completion_barrier_at and friends of the reference's FakeModel (src/engine.rs:3107-3300).
+    void inject_failure(int site, int64_t index);
+    int64_t drains() const { return drains_; }
 
 protected:
     void run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint32_t flags) override;
     void fetch_output(float* logits, uint32_t* tokens) override;
+    void device_synchronize() override;
+    void on_reset_session() override;
 
 private:
     std::vector<uint32_t> next_;
     int64_t forwards_ = 0, fail_at_ = -1;
+    int64_t reads_ = 0, fail_read_at_ = -1, resets_ = 0, fail_reset_at_ = -1, drains_ = 0, fail_drain_at_ = -1;
 };
 
 }  // namespace mk

@@ -128,6 +128,11 @@ class Model:
         capi.check(capi.lib().mk_model_new_fake(vocab, max_context, C.byref(cfg), fail_forward_at, C.byref(h)))
         return cls(h)
 
+    def inject_failure(self, site: str, index: int) -> None:
+        """Fake model only: make call number `index` at 'forward' | 'read_output' | 'admission' | 'synchronize' fail."""
+        sites = {"forward": 0, "read_output": 1, "admission": 2, "synchronize": 3}
+        capi.check(capi.lib().mk_model_fake_inject(self._h, sites[site], index))
+
     def spec(self) -> capi.RuntimeSpec:
         s = capi.RuntimeSpec()
         capi.check(capi.lib().mk_model_spec(self._h, C.byref(s)))
@@ -289,7 +294,16 @@ class Engine:
         capi.check(capi.lib().mk_engine_result(self._h, request_id, toks.ctypes.data, C.byref(n), C.byref(fin), C.byref(cached)))
         state = ("running", "done", "failed")[fin.value]
         msg = capi.lib().mk_last_error().decode() if state == "failed" else ""
-        return dict(tokens=toks[: n.value].copy(), state=state, cached_tokens=int(cached.value), message=msg)
+        kind = C.c_int32()
+        capi.check(capi.lib().mk_engine_failure_kind(self._h, request_id, C.byref(kind)))
+        return dict(tokens=toks[: n.value].copy(), state=state, cached_tokens=int(cached.value), message=msg,
+                    kind=("none", "invalid_request", "resource_exhausted", "internal", "fatal")[kind.value])
+
+    def status(self) -> str:
+        """EngineStatus of the reference: 'ready', 'busy' or 'poisoned'."""
+        st = C.c_int32()
+        capi.check(capi.lib().mk_engine_status(self._h, C.byref(st)))
+        return {1: "ready", 2: "busy", 3: "poisoned"}.get(st.value, "stopped")
 
     def logits(self, request_id: int) -> np.ndarray:
         rows = C.c_int32()

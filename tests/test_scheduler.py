@@ -194,3 +194,108 @@ def test_randomised_differential_with_prefix_cache(eng, seed):
     if mkw["prefix_capacity_tokens"]:
         assert pm.prefix_diagnostics() == om.prefix.stats()
         assert pm.prefix_diagnostics()["hits"] + pm.prefix_diagnostics()["misses"] > 0
+
+
+# ---- worker poisoning (src/engine.rs:1577-1647,2719-2770; tests at src/engine.rs:5603-5760) ----------------------
+
+def test_forward_failure_poisons_the_engine_and_fans_out_fatal(eng):
+    """scheduler_panic_is_caught_and_fanned_out_as_fatal (src/engine.rs:5603-5637): the tick that fails had both
+    requests packed; both, and the one still queued, end Fatal; one cleanup drain, no completion barrier; the sessions
+    are gone and later submissions are refused."""
+    capi = importlib.import_module("macllm_infer_b200._capi")
+    model = eng.Model.fake(vocab=32, fail_forward_at=1)
+    e = eng.Engine(model, max_active_sequences=2, scheduler_token_budget=8, prefill_token_quantum=2, queue_capacity=8)
+    ids = e.submit([eng.Request([1, 2, 3], 4), eng.Request([4, 5], 4), eng.Request([6], 2)])
+    assert e.step() == 2            # tick 0 runs
+    assert e.status() == "busy"
+    assert e.step() == 0            # tick 1: the injected failure escapes the tick
+    assert e.status() == "poisoned"
+    for i in ids:
+        r = e.result(i)
+        assert r["state"] == "failed" and r["kind"] == "fatal"
+        assert r["message"].startswith("inference worker failed: ") and "injected forward failure" in r["message"]
+    assert e.pending() == 0
+    assert e.stats()["cleanup_drains"] == 1 and e.stats()["failed_requests"] == 3
+    assert len(e.trace()) == 1      # the failed tick never completed
+    assert e.step() == 0            # a poisoned engine does nothing more
+    with pytest.raises(capi.MkError, match=r"inference worker is unavailable \(Poisoned\)"):
+        e.submit([eng.Request([1], 1)])
+    # the model rolled the failed tick back (src/decoder.rs:4146-4162): nothing is reserved, the sessions' pages
+    # were released with the sessions
+    st = model.pool_stats()
+    assert st["reserved_blocks"] == 0 and st["live_blocks"] == 0
+
+
+def test_completion_barrier_failure_poisons_without_a_second_drain(eng):
+    """shared_completion_failure_poison_is_atomic_and_not_retried (src/engine.rs:5687-5760): once the read-back has
+    been entered a failure poisons the engine and no cleanup drain follows."""
+    model = eng.Model.fake(vocab=32)
+    model.inject_failure("read_output", 0)
+    e = eng.Engine(model, max_active_sequences=2, scheduler_token_budget=8, prefill_token_quantum=4, queue_capacity=8)
+    ids = e.submit([eng.Request([1], 1), eng.Request([2], 1), eng.Request([1, 2], 1)])
+    e.run()
+    assert e.status() == "poisoned"
+    assert [e.result(i)["kind"] for i in ids] == ["fatal"] * 3
+    assert "injected completion barrier failure" in e.result(ids[2])["message"]
+    assert e.stats()["cleanup_drains"] == 0
+
+
+def test_cleanup_drain_failure_is_appended_to_the_fatal_message(eng):
+    """src/engine.rs:2723-2736."""
+    model = eng.Model.fake(vocab=32, fail_forward_at=0)
+    model.inject_failure("synchronize", 0)
+    e = eng.Engine(model, max_active_sequences=2, queue_capacity=4)
+    (i,) = e.submit([eng.Request([1, 2], 2)])
+    e.run()
+    msg = e.result(i)["message"]
+    assert "injected forward failure" in msg and "forward-error cleanup synchronization also failed" in msg
+
+
+def test_admission_failure_poisons_and_loses_no_session(eng):
+    """An error during request admission poisons the worker too (src/engine.rs:1607-1621); with the engine alive
+    the slot's session goes back to the reusable list before the error travels on."""
+    model = eng.Model.fake(vocab=32)
+    model.inject_failure("admission", 1)
+    e = eng.Engine(model, max_active_sequences=2, queue_capacity=4)
+    ids = e.submit([eng.Request([1], 1), eng.Request([2], 1)])
+    e.run()
+    assert e.status() == "poisoned"
+    assert [e.result(i)["kind"] for i in ids] == ["fatal", "fatal"]
+    assert "injected admission failure" in e.result(ids[0])["message"]
+
+
+def test_kv_exhaustion_fails_one_request_with_resource_exhausted_not_fatal(eng):
+    """fail_kv_exhausted_visit (src/engine.rs:2205-2231): request-local, the engine stays healthy."""
+    model = eng.Model.fake(vocab=32, kv_capacity_tokens=64, block_tokens=16)
+    e = eng.Engine(model, max_active_sequences=2, scheduler_token_budget=64, prefill_token_quantum=64, queue_capacity=4)
+    ids = e.submit([eng.Request(list(range(1, 31)) * 2, 2), eng.Request(list(range(1, 31)), 8)])
+    e.run()
+    kinds = sorted(e.result(i)["kind"] for i in ids)
+    assert e.status() == "ready"
+    assert "fatal" not in kinds
+
+
+def test_second_forward_before_the_read_is_refused(eng):
+    """One tick in flight: the staging and result buffers of a tick are reused by the next one."""
+    import ctypes as C
+    capi = importlib.import_module("macllm_infer_b200._capi")
+    model = eng.Model.fake(vocab=32)
+    a, b = model.new_session(), model.new_session()
+    def enqueue(lanes):
+        arr, keep = model._lanes(lanes)
+        r = C.c_void_p()
+        capi.check(capi.lib().mk_reserve_batch(model._h, arr, len(lanes), C.byref(r)))
+        st = capi.lib().mk_forward_batch_reserved(model._h, arr, len(lanes), r, capi.FWD_WANT_TOKENS)
+        return st, keep
+    st, _ = enqueue([(a, [1, 2], 0)])
+    assert st == 0
+    st, _ = enqueue([(b, [3], 0)])
+    assert st != 0 and "previous forward was not read" in capi.lib().mk_last_error().decode()
+    assert len(b) == 0 and len(a) == 2      # the refused forward changed nothing
+    toks = (C.c_uint32 * 1)()
+    capi.check(capi.lib().mk_read_output(model._h, None, toks))
+    assert toks[0] == (31 * 2 + 7 * 1 + 3) % 32
+    st, _ = enqueue([(b, [3], 0)])          # after the read the next tick goes through
+    assert st == 0
+    model.synchronize()
+    assert capi.lib().mk_read_output(model._h, None, toks) != 0   # nothing left to read
