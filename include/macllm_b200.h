@@ -168,6 +168,12 @@ int32_t mk_model_spec(mk_model* m, mk_runtime_spec* out);
 /* CausalLm::new_session / CausalLmSession::{clear_cache, cache_len} (src/architecture.rs:803-833,1074). */
 int32_t mk_session_new(mk_model* m, mk_session** out);
 int32_t mk_session_free(mk_session* s);
+/* PagedKvBlockTable::fork_prefix (crates/macllm-kv/src/cache.rs:1565-1571) at session level: a new session of the same
+ * model whose table shares the first logical_len tokens of src (every block retained once more; logical_len need not
+ * be block-aligned).  The first append of either session to a shared partial tail block replaces that block by a
+ * private copy of its valid rows (copy-on-write, cache.rs:2252-2280,3042-3089).  Refused while src has a reservation
+ * in flight or when logical_len exceeds its length. */
+int32_t mk_session_fork_prefix(mk_model* m, mk_session* src, int64_t logical_len, mk_session** out);
 int32_t mk_session_clear(mk_session* s);
 int32_t mk_session_len(mk_session* s, int64_t* out);
 /* Block table of a session: slot indices and generations (PagedKvBlockTable, cache.rs:1434-1865).
@@ -407,13 +413,16 @@ int32_t mk_k_qmatmul_time(int32_t type, const void* w, int64_t rows, int64_t col
  * aligned), x_dev is [T][cols] f32, y_dev receives [T][rows] f32.  The kernel's working storage
  * (quantised activations, split-K partial sums, status word) sits in fixed device arrays inside the
  * library image, about 10 MiB on every GPU that loads the library, kept until the process exits.
- * Limits: T * cols <= MK_NOALLOC_MAX_ACT_ELEMS and the split-K partial sums (at most 8 * T * rows
- * floats) <= MK_NOALLOC_MAX_PARTIAL; anything larger is refused with a message.  The arrays are
+ * Limits: T * cols <= MK_NOALLOC_MAX_ACT_ELEMS, rows <= INT32_MAX, and the split-K partial sums
+ * (shares * T * rows floats, where a matrix of few row tiles is cut into up to
+ * min(ceil(148 / tiles), cols / 256) K shares - e.g. 64 shares for 128 x 16384) <= MK_NOALLOC_MAX_PARTIAL;
+ * anything larger is refused with a message.  The arrays are
  * shared by every call and keep the previous call's contents (what must start at zero is cleared by
  * the call itself), so calls that overlap on the GPU - other streams or other threads - race and must
  * be serialised by the caller.  The first call on a device also looks up the arrays' device addresses;
- * issue it before any stream capture begins.  The call returns after the result is complete on
- * cuda_stream (a cudaStream_t, or NULL for the default stream).  It never calls cudaMalloc, cudaFree
+ * make that first call before any stream capture begins.  Every call waits for its own result: it
+ * synchronises cuda_stream (a cudaStream_t, or NULL for the default stream) and reads a status word back
+ * before it returns.  It never calls cudaMalloc, cudaFree
  * or any allocating library routine.  Same arithmetic as mk_k_qmatmul(MK_TYPE_Q4_K, ..., MK_PATH_TENSOR). */
 #define MK_NOALLOC_MAX_ACT_ELEMS 524288
 #define MK_NOALLOC_MAX_PARTIAL 2097152
@@ -471,10 +480,10 @@ typedef struct mk_attn_case {
 int32_t mk_k_attention_step(const mk_attn_case* c);
 
 /* Host-only: how one matmul launch is cut into work items.  path MK_PATH_HALF: out = {token-tile width, row tiles, token
- * tiles, K shares, K blocks (of 64) per share, floats of partial sums}; path MK_PATH_STREAM (T <= 64): out = {token-tile
- * width, row tiles, (row tile, 256-column block) units, persistent CTAs, partial-sum slots, floats of partial sums}.
- * Needs no GPU. */
-int32_t mk_k_matmul_plan(int32_t path, int64_t rows, int64_t cols, int32_t T, int32_t max_splits, int64_t* out6);
+ * tiles, K shares, K blocks (of 64) per share, floats of partial sums, 0, 0}; path MK_PATH_STREAM (T <= 64): out =
+ * {token-tile width, row tiles, (group of row tiles, 256-column block) items, persistent CTAs, partial-sum slots, floats
+ * of partial sums, row tiles per group, groups}.  Needs no GPU. */
+int32_t mk_k_matmul_plan(int32_t path, int64_t rows, int64_t cols, int32_t T, int32_t max_splits, int64_t* out8);
 
 /* Host-only: how one tick's attention work is cut (the plan the model builds before every forward).  Lanes with more
  * than one token become query tiles; one-token lanes become one CTA per KV head, or several key shares when that pays.

@@ -129,6 +129,7 @@ SIGNATURES = {
     "mk_model_spec": (_i32, [P, C.POINTER(RuntimeSpec)]),
     "mk_session_new": (_i32, [P, C.POINTER(P)]),
     "mk_session_free": (_i32, [P]),
+    "mk_session_fork_prefix": (_i32, [P, P, _i64, C.POINTER(P)]),
     "mk_session_clear": (_i32, [P]),
     "mk_session_len": (_i32, [P, C.POINTER(_i64)]),
     "mk_session_block_table": (_i32, [P, P, P, C.POINTER(_i32)]),

@@ -172,18 +172,11 @@ void launch_paged_attention(const AttnArgs& a, cudaStream_t s) {
         throw std::runtime_error("launch_paged_attention: unsupported query group size");
     size_t smem = (size_t)(AT_MAX_ITEMS * a.d + AT_KEYS * (a.d + 4) + AT_KEYS * a.d) * sizeof(float);
     dim3 grid((unsigned)a.batch.max_tiles, (unsigned)a.kv_heads);
-    static size_t conf16 = 0, conf32 = 0;
     if (a.kv_f16) {
-        if (smem > 48 * 1024 && smem > conf16) {
-            MK_CUDA(cudaFuncSetAttribute(attn_tile_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            conf16 = smem;
-        }
+        ensure_dynamic_smem(reinterpret_cast<const void*>(&attn_tile_kernel<__half>), smem);
         attn_tile_kernel<__half><<<grid, AT_WARPS * 32, smem, s>>>(a);
     } else {
-        if (smem > 48 * 1024 && smem > conf32) {
-            MK_CUDA(cudaFuncSetAttribute(attn_tile_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            conf32 = smem;
-        }
+        ensure_dynamic_smem(reinterpret_cast<const void*>(&attn_tile_kernel<float>), smem);
         attn_tile_kernel<float><<<grid, AT_WARPS * 32, smem, s>>>(a);
     }
     MK_LAUNCH_CHECK();

@@ -668,11 +668,7 @@ __global__ void attn_combine_kernel(AttnTcArgs a, int D) {
 template <int D, int WARPS, int KT, bool SPLIT>
 void launch_variant(const AttnTcArgs& a, int n_work, cudaStream_t s) {
     constexpr size_t smem = (size_t)(16 * WARPS + 4 * KT) * (D + 8) * sizeof(__half);
-    static bool configured = false;
-    if (!configured) {
-        MK_CUDA(cudaFuncSetAttribute(attn_tc_kernel<D, WARPS, KT, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
-    }
+    ensure_dynamic_smem(reinterpret_cast<const void*>(&attn_tc_kernel<D, WARPS, KT, SPLIT>), smem);
     dim3 grid((unsigned)n_work, (unsigned)a.kv_heads);
     launch_pdl(attn_tc_kernel<D, WARPS, KT, SPLIT>, grid, dim3(WARPS * 32), smem, s, a);
     MK_LAUNCH_CHECK();
@@ -687,12 +683,8 @@ void launch_for_dim(const AttnTcArgs& a, int warps, cudaStream_t s) {
     if (a.n_entries > 0) {
         constexpr int STAGES = D >= 256 ? 2 : 3;
         constexpr size_t smem = (size_t)(16 + 4 * STAGES * 2 * 16) * (D + 8) * sizeof(__half);
-        static bool configured = false;
-        if (!configured) {
-            MK_CUDA(cudaFuncSetAttribute(attn_decode_kernel<D, STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            MK_CUDA(cudaFuncSetAttribute(attn_decode_kernel<D, STAGES, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            configured = true;
-        }
+        ensure_dynamic_smem(reinterpret_cast<const void*>(&attn_decode_kernel<D, STAGES, true>), smem);
+        ensure_dynamic_smem(reinterpret_cast<const void*>(&attn_decode_kernel<D, STAGES, false>), smem);
         dim3 grid((unsigned)a.n_entries, (unsigned)a.kv_heads);
         if (a.q_heads / a.kv_heads <= 8) launch_pdl(attn_decode_kernel<D, STAGES, true>, grid, dim3(128), smem, s, a);
         else launch_pdl(attn_decode_kernel<D, STAGES, false>, grid, dim3(128), smem, s, a);
@@ -738,7 +730,7 @@ void plan_attention_tc(const int32_t* start_pos, const int32_t* n_tokens, const 
     // (measured at 64 lanes x 4 KV heads with histories within twice their mean: +1.4 % on the whole benchmark
     // without shares).  Then only a lane more than twice as long as the mean is cut, so that one long history among
     // many short ones does not set the length of the launch.
-    const bool filled = n_dec * kv_heads >= 148;
+    const bool filled = n_dec * kv_heads >= kPlanSms;
     const int slots = filled ? n_dec + n_dec / 2 : std::max(n_dec, kAttnTargetCtas / std::max(1, kv_heads));
     int share = (int)std::max<int64_t>(kAttnMinSplitKeys, filled ? 2 * (total_keys / std::max(1, n_dec)) : (total_keys + slots - 1) / std::max(1, slots));
     share = (share + 63) / 64 * 64;

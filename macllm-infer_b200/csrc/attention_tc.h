@@ -53,7 +53,8 @@ int attention_tc_warps(int q_heads, int kv_heads);
 // into query tiles; one-token lanes split their keys over up to kAttnMaxSplits CTAs (four warps each), at
 // least kAttnMinSplitKeys keys each, until about kAttnTargetCtas CTAs are in flight - unless the lanes alone already
 // give every SM a CTA, in which case no lane is split.
-constexpr int kAttnTargetCtas = 148 * 2;
+constexpr int kPlanSms = 148;  // the work lists are planned on the host, without a device, for a B200's SM count
+constexpr int kAttnTargetCtas = kPlanSms * 2;
 constexpr int kAttnMaxSplits = 16;
 constexpr int kAttnMinSplitKeys = 512;  // a share costs a partial write, a counter and a merge: below this a lane stays whole (measured at 4 lanes x 333 keys: +8 % without shares)
 struct AttnTcPlan {

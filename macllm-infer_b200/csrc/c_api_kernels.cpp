@@ -109,18 +109,22 @@ void qmatmul_case(int32_t type, const void* w, int64_t rows, int64_t cols, const
     const bool half = path == MK_PATH_HALF;
     const bool stream = path == MK_PATH_STREAM;
     QStreamWeight qsw;
+    // MACLLM_B200_QS_SPLITS=1 keeps whole groups of row tiles in one CTA (no partial sums), for tests of that form
+    const int stream_splits = [] { const char* e = getenv("MACLLM_B200_QS_SPLITS"); return e != nullptr ? std::max(1, atoi(e)) : 16; }();  // read per call
     DevBuf qs_partial;
     int qs_splits = 1;
     if (stream) {
-        if (type != MK_TYPE_Q4_K || T > kQStreamMaxRows) throw std::runtime_error("mk_k_qmatmul: the streamed matmul covers Q4_K matrices and at most 64 rows");
-        build_qstream_weight(dw.w.p0, rows, cols, qsw, nullptr);
-        qs_partial.alloc((size_t)16 << 20);
+        if ((type != MK_TYPE_Q4_K && type != MK_TYPE_Q6_K) || T > kQStreamMaxRows)
+            throw std::runtime_error("mk_k_qmatmul: the streamed matmul covers Q4_K and Q6_K matrices and at most 64 rows");
+        if (type == MK_TYPE_Q4_K) build_qstream_weight(dw.w.p0, rows, cols, qsw, nullptr);
+        else build_qstream_weight_q6k(dw.w, qsw, nullptr);
+        qs_partial.alloc(kSplitScratchBytes);
     }
     if (half) {
         if (!hgemm_tc_supported(dw.w)) throw std::runtime_error("mk_k_qmatmul: the f16-image GEMM does not cover this matrix");
         build_half_weight(dw.w, dw.half, nullptr);
         // narrow batches share K out over CTAs, as the model's decode ticks do; the shares are added below
-        if (T <= kQStreamMaxRows) qs_partial.alloc((size_t)16 << 20);
+        if (T <= kQStreamMaxRows) qs_partial.alloc(kSplitScratchBytes);
     }
     const bool tensor = !half && !stream && (path == MK_PATH_TENSOR || (path == MK_PATH_AUTO && qgemm_tc_preferred(dw.w, T)));
     ActQ a = ab.view(T, (int)cols, kind, tensor || half || stream, stream);
@@ -141,8 +145,8 @@ void qmatmul_case(int32_t type, const void* w, int64_t rows, int64_t cols, const
         hs.partial_floats = qs_partial.size() / 4;
     }
     auto run = [&] {
-        if (stream) qs_splits = launch_qstream_tc(qsw, a.xh, a.gs, T, dy.as<float>(), (int)rows, qs_partial.as<float>(), qs_partial.size() / 4,
-                                                  ws.status.as<int32_t>(), nullptr, 16);
+        if (stream) qs_splits = launch_qstream_tc(qsw, a.xh, T, dy.as<float>(), (int)rows, qs_partial.as<float>(), qs_partial.size() / 4,
+                                                  ws.status.as<int32_t>(), nullptr, stream_splits);
         else if (half) qs_splits = launch_hgemm_tc(dw.half, a.xh, T, dy.as<float>(), (int)rows, 1.0f, 0.f, hs, nullptr, hs.partial ? 16 : 1);
         else if (tensor) launch_qgemm_tc(dw.w, a, kind, T, dy.as<float>(), (int)rows, 1.0f, 0.f, ws, nullptr);
         else launch_qgemv(dw.w, a, T, dy.as<float>(), (int)rows, 1.0f, 0.f, nullptr);
@@ -170,6 +174,30 @@ void qmatmul_case(int32_t type, const void* w, int64_t rows, int64_t cols, const
         *avg_ms = (float)(total / iters);
     }
     MK_CUDA(cudaDeviceSynchronize());
+    if (stream && getenv("MACLLM_B200_QS_PROF") != nullptr) {
+        // one more launch with CTA 0 recording where each of its roles waited (printed to stderr)
+        DevBuf prof((41 + 2000) * sizeof(long long));
+        prof.zero(nullptr);
+        qstream_set_profile_buffer(prof.as<long long>());
+        run();
+        qstream_set_profile_buffer(nullptr);
+        MK_CUDA(cudaDeviceSynchronize());
+        std::vector<long long> hv(41 + 2000);
+        prof.download(hv.data(), hv.size() * sizeof(long long));
+        MK_CUDA(cudaDeviceSynchronize());
+        const long long* h = hv.data();
+        if (getenv("MACLLM_B200_QS_TRACE") != nullptr) {
+            for (int role = 0; role < 5; ++role)
+                for (long long k = 0; k < h[role * 8 + 6]; ++k) {
+                    const long long e = h[41 + role * 400 + k];
+                    fprintf(stderr, "[qstream trace] role %d ev %lld t %lld\n", role, (e >> 28) & 0xF, e & 0x0FFFFFFF);
+                }
+        }
+        static const char* role[5] = {"weight loader", "mma issuer", "activation loader", "converter", "epilogue"};
+        for (int r = 0; r < 5; ++r)
+            fprintf(stderr, "[qstream prof] %-18s total %8lld  wait0 %8lld  wait1 %8lld  wait2 %8lld  wait3 %8lld  items %lld\n", role[r], h[r * 8],
+                    h[r * 8 + 1], h[r * 8 + 2], h[r * 8 + 3], h[r * 8 + 4], h[r * 8 + 5]);
+    }
     int32_t st = 0;
     ws.status.download(&st, 4);
     MK_CUDA(cudaDeviceSynchronize());
@@ -481,27 +509,33 @@ int32_t mk_k_moe_route(const float* logits, int32_t T, int32_t experts, int32_t 
         require_device();
         DevBuf dl((size_t)T * experts * 4), de((size_t)T * k * 4), dw((size_t)T * k * 4);
         dl.upload(logits, (size_t)T * experts * 4);
-        launch_moe_route(dl.as<float>(), T, experts, k, de.as<int32_t>(), dw.as<float>(), nullptr);
+        DevBuf status(4);
+        status.zero(nullptr);
+        launch_moe_route(dl.as<float>(), T, experts, k, de.as<int32_t>(), dw.as<float>(), status.as<int32_t>(), nullptr);
         MK_CUDA(cudaDeviceSynchronize());
         de.download(sel_experts, (size_t)T * k * 4);
         dw.download(sel_weights, (size_t)T * k * 4);
+        int32_t st = 0;
+        status.download(&st, 4);
         MK_CUDA(cudaDeviceSynchronize());
+        // the choices are written (in range) even for a refused row, so a caller can inspect them
+        if ((st & 0xFFFF0000) == kMoeRouteStatus) throw std::runtime_error("router produced non-finite logits for token row " + std::to_string(st & 0xFFFF));
     });
 }
 
-int32_t mk_k_matmul_plan(int32_t path, int64_t rows, int64_t cols, int32_t T, int32_t max_splits, int64_t* out6) {
+int32_t mk_k_matmul_plan(int32_t path, int64_t rows, int64_t cols, int32_t T, int32_t max_splits, int64_t* out8) {
     return guarded([&] {
-        if (rows <= 0 || cols <= 0 || T <= 0 || out6 == nullptr) throw std::runtime_error("mk_k_matmul_plan: arguments out of range");
+        if (rows <= 0 || cols <= 0 || T <= 0 || out8 == nullptr) throw std::runtime_error("mk_k_matmul_plan: arguments out of range");
         if (path == MK_PATH_HALF) {
             if (cols % 64 != 0) throw std::runtime_error("mk_k_matmul_plan: the f16-image GEMM needs columns in multiples of 64");
             HgemmPlan p = hgemm_tc_plan(rows, cols, T, max_splits);
-            const int64_t v[6] = {p.bn, p.row_tiles, p.n_tiles, p.splits, p.kb_per_split, (int64_t)p.partial_floats};
-            memcpy(out6, v, sizeof v);
+            const int64_t v[8] = {p.bn, p.row_tiles, p.n_tiles, p.splits, p.kb_per_split, (int64_t)p.partial_floats, 0, 0};
+            memcpy(out8, v, sizeof v);
         } else if (path == MK_PATH_STREAM) {
             if (cols % 256 != 0 || T > kQStreamMaxRows) throw std::runtime_error("mk_k_matmul_plan: the streamed matmul covers 256-wide blocks and at most 64 rows");
-            QStreamPlan p = qstream_plan(rows, cols, T, max_splits);
-            const int64_t v[6] = {p.bn, p.row_tiles, p.units, p.ctas, p.slots, (int64_t)p.partial_floats};
-            memcpy(out6, v, sizeof v);
+            QStreamPlan p = qstream_plan((int)((rows + 127) / 128), (int)(cols / 256), rows, T, max_splits, false);
+            const int64_t v[8] = {p.bn, p.row_tiles, p.items, p.ctas, p.slots, (int64_t)p.partial_floats, p.R, p.groups};
+            memcpy(out8, v, sizeof v);
         } else {
             throw std::runtime_error("mk_k_matmul_plan: only the f16-image and the streamed path are planned on the host");
         }

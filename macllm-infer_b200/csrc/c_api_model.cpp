@@ -190,6 +190,14 @@ int32_t mk_session_new(mk_model* m, mk_session** out) {
     });
 }
 
+int32_t mk_session_fork_prefix(mk_model* m, mk_session* src, int64_t logical_len, mk_session** out) {
+    return guarded([&] {
+        auto s = std::make_unique<mk_session>();
+        s->s = m->lm->fork_session_prefix(*src->s, logical_len);
+        *out = s.release();
+    });
+}
+
 int32_t mk_session_free(mk_session* s) {
     return guarded([&] { delete s; });
 }

@@ -79,6 +79,13 @@ __host__ __device__ __forceinline__ int64_t kv_page_index(int64_t blk, int layer
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device attribute of a kernel: opt `func` in for `bytes` of
+// dynamic shared memory on the current device, once per (kernel, device) and again only when more is asked for.
+// Safe to call from several host threads.
+void ensure_dynamic_smem(const void* func, size_t bytes);
+// Streaming multiprocessors of the current device (cached per device).
+int device_sm_count();
+
 #ifdef __CUDACC__
 inline bool pdl_enabled() {
     static const bool on = [] { const char* e = std::getenv("MACLLM_B200_PDL"); return e == nullptr || e[0] != '0'; }();

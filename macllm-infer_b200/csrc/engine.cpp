@@ -177,6 +177,9 @@ static inline uint64_t next_u64(uint64_t& state) {
     return z ^ (z >> 31);
 }
 
+// One uniform draw in [0, 1) per sampled token, the same stream whether the token is picked on the host or on the device.
+static inline float next_uniform(uint64_t& state) { return (float)(next_u64(state) >> 40) * (1.0f / 16777216.0f); }
+
 uint32_t Engine::sample(Sequence& s, float* row) {  // Sampler::sample_with_generated, sampling.rs:95-169
     const int vocab = model_.spec().vocab;
     const EngineRequest& rq = s.req;
@@ -187,50 +190,7 @@ uint32_t Engine::sample(Sequence& s, float* row) {  // Sampler::sample_with_gene
     // temperature / top-k / top-p (sampling.rs:145-169,337-390).  The draw uses this library's own
     // counter-based generator: the reference's ChaCha8 stream is a third-party detail that is not
     // restated, so stochastic sampling is not token-comparable with the reference.
-    std::vector<float> values(row, row + vocab);
-    for (float& v : values) v /= rq.temperature;
-    std::vector<int> ranked((size_t)vocab);
-    std::iota(ranked.begin(), ranked.end(), 0);
-    auto desc = [&](int a, int b) {
-        int ka = float_total_key(values[(size_t)a]), kb = float_total_key(values[(size_t)b]);
-        return ka != kb ? ka > kb : a < b;
-    };
-    std::sort(ranked.begin(), ranked.end(), desc);
-    if (rq.top_k > 0 && rq.top_k < vocab) {
-        for (size_t i = (size_t)rq.top_k; i < ranked.size(); ++i) values[(size_t)ranked[i]] = -INFINITY;
-        ranked.resize((size_t)rq.top_k);
-    }
-    float mx = -INFINITY;
-    for (float v : values) mx = std::max(mx, v);
-    std::vector<float> prob((size_t)vocab);
-    float sum = 0.f;
-    for (int i = 0; i < vocab; ++i) { prob[(size_t)i] = std::exp(values[(size_t)i] - mx); sum += prob[(size_t)i]; }
-    if (!(sum > 0.f) || !std::isfinite(sum)) throw std::runtime_error("sampling distribution is empty");
-    for (float& p : prob) p /= sum;
-    std::sort(ranked.begin(), ranked.end(), [&](int a, int b) {
-        int ka = float_total_key(prob[(size_t)a]), kb = float_total_key(prob[(size_t)b]);
-        return ka != kb ? ka > kb : a < b;
-    });
-    if (rq.top_p < 1.f) {
-        float cumulative = 0.f;
-        size_t keep = 0;
-        for (int idx : ranked) {
-            cumulative += prob[(size_t)idx];
-            ++keep;
-            if (cumulative >= rq.top_p) break;
-        }
-        for (size_t i = keep; i < ranked.size(); ++i) prob[(size_t)ranked[i]] = 0.f;
-    }
-    float total = 0.f;
-    for (float p : prob) total += p;
-    float u = (float)(next_u64(s.rng) >> 40) * (1.0f / 16777216.0f);
-    float target = u * total, cumulative = 0.f;
-    for (int i = 0; i < vocab; ++i) {
-        if (prob[(size_t)i] <= 0.f) continue;
-        cumulative += prob[(size_t)i];
-        if (target < cumulative) return (uint32_t)i;
-    }
-    return (uint32_t)argmax_first(prob.data(), vocab);
+    return sample_top_k_top_p(row, vocab, rq.temperature, rq.top_k, rq.top_p, next_uniform(s.rng));
 }
 
 int Engine::step() {  // one turn of ServingScheduler::run, engine.rs:1577-1647

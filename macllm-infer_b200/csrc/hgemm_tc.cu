@@ -453,11 +453,7 @@ void encode_half_matrix(CUtensorMap* out, const void* base, int64_t n_rows, int6
 template <int BN, int STAGES>
 void launch_hg(const CUtensorMap& tw, const CUtensorMap& tx, const HgParams& p, int grid, cudaStream_t s) {
     constexpr size_t smem = HgSmem<BN, STAGES>::TOTAL;
-    static bool configured = false;
-    if (!configured) {
-        MK_CUDA(cudaFuncSetAttribute(hgemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
-    }
+    ensure_dynamic_smem(reinterpret_cast<const void*>(&hgemm_tc_kernel<BN, STAGES>), smem);
     launch_pdl(hgemm_tc_kernel<BN, STAGES>, dim3(grid), dim3(HG_THREADS), smem, s, tw, tx, p);
     MK_LAUNCH_CHECK();
 }
@@ -480,19 +476,7 @@ void encode_tma_2d(void* out_map, bool bytes_not_halves, const void* base, uint6
     if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
 }
 
-namespace {
 
-int sm_count() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        MK_CUDA(cudaGetDevice(&dev));
-        MK_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
-    }
-    return n;
-}
-
-}  // namespace
 
 bool hgemm_tc_supported(const QWeight& W) {
     if (W.type != QT_Q4_K && W.type != QT_Q6_K && W.type != QT_Q8_0 && W.type != QT_F32) return false;
@@ -630,7 +614,7 @@ int launch_hgemm_any(const HalfWeight& W, const __half* xh, int T, float* y, int
     p.gated = gated;
     p.yh = yh;
     p.ldyh = ldyh;
-    const int grid = std::min(sm_count(), p.row_tiles * p.n_tiles * p.splits);
+    const int grid = std::min(device_sm_count(), p.row_tiles * p.n_tiles * p.splits);
     const CUtensorMap& tw = *reinterpret_cast<const CUtensorMap*>(W.tmap);
     if (pl.bn == 256) launch_hg<256, 4>(tw, tx, p, grid, s);
     else if (pl.bn == 128) launch_hg<128, 6>(tw, tx, p, grid, s);

@@ -136,10 +136,27 @@ int attention_q_tile(int q_heads, int kv_heads);
 size_t argmax_scratch_bytes(int B);
 void launch_argmax(const float* logits, int B, int vocab, uint32_t* out, void* scratch, cudaStream_t s);
 
+// Per-lane sampling of one tick: temperature <= 0 selects the first-index argmax; otherwise temperature / top-k / top-p
+// with the uniform draw u in [0, 1) supplied by the host (Sampler::sample_stochastic, src/sampling.rs:145-169,337-390).
+struct LaneSampling {
+    float temperature;
+    int32_t top_k;
+    float top_p;
+    float u;
+};
+// Whether the device kernel covers these settings (greedy, or 1 <= top_k <= 1024); the rest is sampled on the host.
+bool device_sampling_covers(float temperature, int top_k, int vocab);
+// One token per row of logits [B][vocab].  A row whose kept candidates add up to nothing leaves
+// kSampleEmptyStatus | (row & 0xFFFF) in *status ("sampling distribution is empty", src/sampling.rs:352-355).
+constexpr int32_t kSampleEmptyStatus = 0x534D0000;
+void launch_sample(const float* logits, int B, int vocab, const LaneSampling* params_dev, uint32_t* out, int32_t* status, cudaStream_t s);
+
 // ---- MoE -------------------------------------------------------------------------------------------
-// Top-k routing with (logit desc, index asc) order and softmax over the selected k.
+// Top-k routing with (logit desc, index asc) order and softmax over the selected k.  A row with a non-finite logit
+// leaves kMoeRouteStatus | (row & 0xFFFF) in *status (when it is still zero); the choices written stay in range.
+constexpr int32_t kMoeRouteStatus = 0x524F0000;
 void launch_moe_route(const float* logits, int T, int experts, int k, int32_t* sel_experts, float* sel_weights,
-                      cudaStream_t s);
+                      int32_t* status, cudaStream_t s);
 
 // Groups the (token, choice) pairs of a routed batch by expert: offsets [experts+1], pos_of_pair [T*k],
 // token_of_pos [T*k] (the activation row each grouped position reads).

@@ -423,9 +423,8 @@ bool Model::tensor_path(const QWeight& W, int T) const {
     return cfg_.matmul_path == 2 ? true : T > 8;
 }
 
-ActQ Model::act_view(DevBuf& qs, DevBuf& d, DevBuf& bs, DevBuf& xh, int, int, int kind, bool want_f16, DevBuf* gs) {
+ActQ Model::act_view(DevBuf& qs, DevBuf& d, DevBuf& bs, DevBuf& xh, int, int, int, bool want_f16) {
     ActQ a;
-    if (gs != nullptr && want_f16 && kind == ACT_Q8K && gs->size() > 0) a.gs = gs->as<__half>();
     a.qs = qs.as<int8_t>();
     a.d = d.as<float>();
     a.bsums = bs.as<int16_t>();
@@ -520,18 +519,19 @@ void Model::build_half_cache() {
             build_half_weight(w.down.w, w.down.half, stream_);
         }
     }
-    tc_ws_.partial.ensure((size_t)16 << 20);
+    tc_ws_.partial.ensure(kSplitScratchBytes);
     MK_CUDA(cudaStreamSynchronize(stream_));
     half_cache_ = true;
     half_cache_bytes_ = (int64_t)total;
 }
 
-// Descriptors for the narrow-batch matmul over raw Q4_K blocks.  [wq; wk] and [gate; up] are moved into one
-// buffer each (rows stacked) so that one launch covers both; nothing is duplicated.
+// Re-tiled copies for the narrow-batch matmul over raw Q4_K / Q6_K blocks.  [wq; wk] and [gate; up] are moved into one
+// buffer each (rows stacked) so that one launch covers both; nothing of the row-major blocks is duplicated.
 void Model::build_qstream() {
     if (cfg_.matmul_path != 0 && cfg_.matmul_path != 4) return;
-    if (!half_cache_) return;  // V and wide ticks ride on the f16 images
+    if (!half_cache_) return;  // wide ticks ride on the f16 images
     auto q4k = [](const DeviceWeight& d) { return d.w.type == QT_Q4_K && d.w.cols % 256 == 0; };
+    auto kq = [](const DeviceWeight& d) { return (d.w.type == QT_Q4_K || d.w.type == QT_Q6_K) && d.w.cols % 256 == 0; };
     auto stack = [&](DeviceWeight& a, DeviceWeight& b, DevBuf& out) {
         out.alloc((size_t)(a.w.bytes + b.w.bytes));
         MK_CUDA(cudaMemcpyAsync(out.ptr(), a.w.p0, (size_t)a.w.bytes, cudaMemcpyDeviceToDevice, stream_));
@@ -542,35 +542,49 @@ void Model::build_qstream() {
         a.w.p0 = out.ptr();
         b.w.p0 = out.as<uint8_t>() + a.w.bytes;
     };
+    auto retile = [&](const QWeight& w, QStreamWeight& out) {
+        if (w.type == QT_Q4_K) build_qstream_weight(w.p0, w.rows, w.cols, out, stream_);
+        else build_qstream_weight_q6k(w, out, stream_);
+    };
+    bool qkv_one = true;
     for (size_t l = 0; l < lw_.size(); ++l) {
         LayerWeights& w = lw_[l];
         if (ms_.layer[l].moe) return;
-        if (!q4k(w.wq) || !q4k(w.wk) || !q4k(w.wo) || !q4k(w.gate) || !q4k(w.up) || !q4k(w.down)) return;
+        if (!q4k(w.wq) || !q4k(w.wk) || !kq(w.wo) || !q4k(w.gate) || !q4k(w.up) || !kq(w.down)) return;
         if (!w.wv.half.ready) return;
+        // one launch for q | k | v needs the Q4_K part to end on a row-tile boundary
+        if (!kq(w.wv) || (w.wq.w.rows + w.wk.w.rows) % 128 != 0) qkv_one = false;
     }
+    // act(gate) * up in the epilogue of the streamed gate|up matmul (rows interleaved); MACLLM_B200_QS_GATED=0 keeps the
+    // plain form with the separate activation kernel
+    { const char* e = std::getenv("MACLLM_B200_QS_GATED"); qstream_gated_ = e == nullptr || e[0] != '0'; }
     for (size_t l = 0; l < lw_.size(); ++l) {
         LayerWeights& w = lw_[l];
         stack(w.wq, w.wk, w.qk_raw);
         stack(w.gate, w.up, w.gu_raw);
         build_qstream_weight(w.qk_raw.ptr(), w.wq.w.rows + w.wk.w.rows, w.wq.w.cols, w.qs_qk, stream_);
-        build_qstream_weight(w.wo.w.p0, w.wo.w.rows, w.wo.w.cols, w.qs_o, stream_);
-        build_qstream_weight(w.gu_raw.ptr(), w.gate.w.rows + w.up.w.rows, w.gate.w.cols, w.qs_gu, stream_);
-        build_qstream_weight(w.down.w.p0, w.down.w.rows, w.down.w.cols, w.qs_down, stream_);
+        if (qkv_one) retile(w.wv.w, w.qs_v);
+        retile(w.wo.w, w.qs_o);
+        build_qstream_weight(w.gu_raw.ptr(), w.gate.w.rows + w.up.w.rows, w.gate.w.cols, w.qs_gu, stream_, qstream_gated_ ? w.gate.w.rows : 0);
+        retile(w.down.w, w.qs_down);
     }
+    qstream_qkv_ = qkv_one;
+    // the output projection of narrow batches (no scale, no soft cap: those stay on the other paths)
+    DeviceWeight& head = ms_.tied ? token_embd_ : output_;
+    if (kq(head) && ms_.final_logit_scale == 1.f && ms_.final_softcap == 0.f) retile(head.w, qs_head_);
     v_partial_.alloc((size_t)16 * kQStreamMaxRows * ms_.kv_heads * ms_.head_dim * 4);
-    // group sums of the streamed ticks' activations (at most kQStreamMaxRows rows)
-    a_gs_.alloc((size_t)kQStreamMaxRows * (std::max(ms_.hidden, ms_.q_heads * ms_.head_dim) / 16) * 2);
-    f_gs_.alloc((size_t)kQStreamMaxRows * (ms_.ffn / 16) * 2);
     MK_CUDA(cudaStreamSynchronize(stream_));
     if (const char* e = std::getenv("MACLLM_B200_STREAM_MIN_ROWS")) qstream_min_rows_ = std::max(1, atoi(e));
     qstream_ = true;
 }
 
-int Model::matmul_stream(const QStreamWeight& W, const ActQ& x, int T, float* y, int ldy, int max_splits) {
-    prof_begin(KC_QSTREAM, (double)W.rows * (double)(W.cols / 256) * 144.0 + 2.0 * T * W.cols + 4.0 * T * W.rows,
-               2.0 * T * (double)W.rows * (double)W.cols);
-    int splits = launch_qstream_tc(W, x.xh, x.gs, T, y, ldy, tc_ws_.partial.as<float>(), tc_ws_.partial.size() / 4,
-                                   tc_ws_.status.as<int32_t>(), stream_, max_splits);
+int Model::matmul_stream(const QStreamWeight& W, const ActQ& x, int T, float* y, int ldy, int max_splits, const QStreamWeight* W2) {
+    const double rows = (double)W.rows + (W2 ? (double)W2->rows : 0.0);
+    const double wbytes = (double)W.rows * (double)(W.cols / 256) * (W.fmt ? 210.0 : 144.0) +
+                          (W2 ? (double)W2->rows * (double)(W2->cols / 256) * (W2->fmt ? 210.0 : 144.0) : 0.0);
+    prof_begin(KC_QSTREAM, wbytes + 2.0 * T * W.cols + 4.0 * T * rows, 2.0 * T * rows * (double)W.cols);
+    int splits = launch_qstream_tc(W, x.xh, T, y, ldy, tc_ws_.partial.as<float>(), tc_ws_.partial.size() / 4,
+                                   tc_ws_.status.as<int32_t>(), stream_, max_splits, W2);
     prof_end();
     ++launches_;
     return splits;
@@ -690,7 +704,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         // residual add of the previous layer's FFN + attention norm + quantise
         int kind = act_kind_of(w.wq.w);
         const bool stream_T = qstream_ && T >= qstream_min_rows_ && T <= kQStreamMaxRows && f16_T;
-        ActQ xa = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, H, kind, f16_T, stream_T ? &a_gs_ : nullptr);
+        ActQ xa = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, H, kind, f16_T);
         NormQuantArgs na;
         na.h = h_.as<float>();
         na.a = pending;
@@ -711,7 +725,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         float* qp = qkv_.as<float>();
         float* kp = qp + AW;
         float* vp = kp + KW;
-        const bool stream = stream_T && xa.gs != nullptr;
+        const bool stream = stream_T;
         const int kMaxShares = 16;
         int qk_splits = 1, v_splits = 1;
         bool qkv_joint = false;
@@ -722,12 +736,16 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         // MACLLM_B200_DECODE_HALF_MASK overrides: 1 q|k|v, 2 attention output, 4 gate|up (implies 8), 8 down.
         static const int half_mask = [] {
             const char* e = getenv("MACLLM_B200_DECODE_HALF_MASK");
-            int m = e != nullptr ? atoi(e) : 9;
+            int m = e != nullptr ? atoi(e) : 0;
             return (m & 4) ? (m | 8) : m;
         }();
         const bool stream_o = stream && !(half_mask & 2), stream_gu = stream && !(half_mask & 4), stream_down = stream && !((half_mask & 8) && T >= 33);  // with a handful of lanes the streamed blocks win (measured at 4 lanes)
         if (stream && (half_mask & 1) && w.qkv_half.ready) {
             qk_splits = v_splits = matmul_half(w.qkv_half, xa, T, qp, QKVW, 1.f, 0.f, kMaxShares);
+            qkv_joint = qk_splits > 1;
+        } else if (stream && qstream_qkv_) {
+            // [wq; wk] in Q4_K and wv in its own format, one launch: the rows of q | k | v side by side
+            qk_splits = v_splits = matmul_stream(w.qs_qk, xa, T, qp, QKVW, kMaxShares, &w.qs_v);
             qkv_joint = qk_splits > 1;
         } else if (stream) {
             qk_splits = matmul_stream(w.qs_qk, xa, T, qp, QKVW, kMaxShares);
@@ -806,11 +824,11 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         // the quantised image of the attention output feeds the output projection; on a tick of one-token lanes only,
         // the attention kernel writes it itself
         const int okind = act_kind_of(w.wo.w);
-        ActQ xo = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, AW, okind, f16_T, stream_T ? &a_gs_ : nullptr);
+        ActQ xo = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, AW, okind, f16_T);
         const bool fuse_attn_quant = attn_tc_ && n_attn_tiles == 0 && n_attn_entries > 0 && (AW / ms_.kv_heads) % 256 == 0;
         // wide ticks: the output projection is an f16 GEMM that reads nothing but the f16 rows, so the attention kernels
         // write those and the separate quantisation pass is dropped
-        const bool attn_half_out = attn_tc_ && !fuse_attn_quant && !(stream_o && xo.gs != nullptr) && w.wo.half.ready &&
+        const bool attn_half_out = attn_tc_ && !fuse_attn_quant && !stream_o && w.wo.half.ready &&
                                    T >= hgemm_min_rows_ && xo.xh != nullptr && n_attn_dec == 0;
         AttnArgs at;
         at.q = qp;
@@ -905,12 +923,12 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         }
         // split-K shares of the two long-K projections are summed by the residual kernel that consumes them
         int wo_splits = 1;
-        if (stream_o && xo.gs != nullptr) wo_splits = matmul_stream(w.qs_o, xo, T, proj_.as<float>(), H, kMaxShares);
+        if (stream_o) wo_splits = matmul_stream(w.qs_o, xo, T, proj_.as<float>(), H, kMaxShares);
         else if (w.wo.half.ready && T >= hgemm_min_rows_ && xo.xh != nullptr) wo_splits = matmul_half(w.wo.half, xo, T, proj_.as<float>(), H, 1.f, 0.f, kMaxShares);
         else matmul(w.wo, xo, T, proj_.as<float>(), H, 1.f, 0.f);
         // residual add + FFN norm + quantise (finish_mixer, src/decoder.rs:2684-2699)
         int fkind = act_kind_of(w.gate.w);
-        ActQ xf = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, H, fkind, f16_T, stream_T ? &a_gs_ : nullptr);
+        ActQ xf = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, H, fkind, f16_T);
         NormQuantArgs nf;
         nf.h = h_.as<float>();
         nf.a = wo_splits > 1 ? tc_ws_.partial.as<float>() : proj_.as<float>();
@@ -935,15 +953,26 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
             int gu_splits = 1;
             // wide ticks: one GEMM over the interleaved gate/up image writes act(gate) * up as f16, which is all the
             // f16 GEMM of the down projection reads; no f32 gate|up round trip and no separate activation kernel
-            const bool gated_gemm = !(stream_gu && xf.gs != nullptr) && w.gu_half.ready && w.down.half.ready && T >= hgemm_min_rows_ &&
-                                    xf.xh != nullptr && f16_T;
-            if (gated_gemm) {
+            const bool gated_gemm = !stream_gu && w.gu_half.ready && w.down.half.ready && T >= hgemm_min_rows_ && xf.xh != nullptr && f16_T;
+            // narrow ticks, gated form: act(gate) * up leaves the streamed matmul as f16, which is what the streamed down
+            // projection reads (the activation is the f16 rounding of the f32 value, not an 8-bit block image)
+            const bool gated_stream = stream_gu && qstream_gated_ && stream_down;
+            if (gated_stream) {
+                const QStreamWeight& W = w.qs_gu;
+                prof_begin(KC_QSTREAM, (double)W.rows * (double)(W.cols / 256) * 144.0 + 2.0 * T * W.cols + 2.0 * T * ms_.ffn,
+                           2.0 * T * (double)W.rows * (double)W.cols);
+                launch_qstream_tc(W, xf.xh, T, nullptr, 0, nullptr, 0, tc_ws_.status.as<int32_t>(), stream_, 1, nullptr, ls.act,
+                                  f_xh_.as<__half>(), ms_.ffn);
+                prof_end();
+                ++launches_;
+            } else if (gated_gemm) {
                 prof_begin(KC_HGEMM, 2.0 * (double)w.gu_half.rows * (double)w.gu_half.cols + 2.0 * T * H + 2.0 * T * ms_.ffn,
                            2.0 * T * (double)w.gu_half.rows * (double)w.gu_half.cols);
                 launch_hgemm_tc_gated(w.gu_half, xf.xh, T, ls.act, f_xh_.as<__half>(), ms_.ffn, hgemm_scratch(), stream_);
                 prof_end();
                 ++launches_;
-            } else if (stream_gu && xf.gs != nullptr) {
+            } else if (stream_gu) {
+                if (qstream_gated_) throw std::runtime_error("the interleaved gate|up copy serves the gated form only");
                 gu_splits = matmul_stream(w.qs_gu, xf, T, gp, 2 * ms_.ffn, kMaxShares);
             } else if (w.gu_raw.size() > 0) {
                 DeviceWeight gu;  // [gate; up] share one buffer: one launch for both
@@ -956,8 +985,8 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
                 matmul(w.up, xf, T, up, 2 * ms_.ffn, 1.f, 0.f);
             }
             int dkind = act_kind_of(w.down.w);
-            ActQ xd = act_view(f_qs_, f_d_, f_bs_, f_xh_, T, ms_.ffn, dkind, f16_T, stream_T ? &f_gs_ : nullptr);
-            if (!gated_gemm) {
+            ActQ xd = act_view(f_qs_, f_d_, f_bs_, f_xh_, T, ms_.ffn, dkind, f16_T);
+            if (!gated_gemm && !gated_stream) {
                 prof_begin(KC_ACTMUL, 9.0 * T * ms_.ffn, 0);
                 if (gu_splits > 1) {
                     const float* pg = tc_ws_.partial.as<float>();
@@ -969,14 +998,14 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
                 prof_end();
                 ++launches_;
             }
-            if (stream_down && xd.gs != nullptr) pending_splits = matmul_stream(w.qs_down, xd, T, down_.as<float>(), H, kMaxShares);
+            if (stream_down) pending_splits = matmul_stream(w.qs_down, xd, T, down_.as<float>(), H, kMaxShares);
             else if (w.down.half.ready && T >= hgemm_min_rows_ && xd.xh != nullptr) pending_splits = matmul_half(w.down.half, xd, T, down_.as<float>(), H, 1.f, 0.f, kMaxShares);
             else { matmul(w.down, xd, T, down_.as<float>(), H, 1.f, 0.f); pending_splits = 1; }
         } else {
             // sparse MoE (src/decoder.rs:394-554)
             const int E = ms_.experts, K = ms_.experts_used, F = ms_.expert_ffn, P = T * K;
             launch_f32_gemv(w.router.as<float>(), E, H, normed_.as<float>(), T, router_logits_.as<float>(), stream_);
-            launch_moe_route(router_logits_.as<float>(), T, E, K, sel_e_.as<int32_t>(), sel_w_.as<float>(), stream_);
+            launch_moe_route(router_logits_.as<float>(), T, E, K, sel_e_.as<int32_t>(), sel_w_.as<float>(), tc_ws_.status.as<int32_t>(), stream_);
             launch_moe_group(sel_e_.as<int32_t>(), T, K, E, grp_off_.as<int32_t>(), pos_of_pair_.as<int32_t>(), tok_of_pos_.as<int32_t>(),
                              stream_);
             ActQ xq = xf;
@@ -1048,7 +1077,10 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         launch_add_norm_quant(ng, stream_);
         prof_end();
         ++launches_;
-        matmul(head_dw, xl, B, logits_.as<float>(), ms_.vocab, ms_.final_logit_scale, ms_.final_softcap);
+        if (qs_head_.ready && f16_B && B >= qstream_min_rows_ && B <= kQStreamMaxRows && xl.xh != nullptr)
+            matmul_stream(qs_head_, xl, B, logits_.as<float>(), ms_.vocab, 1);
+        else
+            matmul(head_dw, xl, B, logits_.as<float>(), ms_.vocab, ms_.final_logit_scale, ms_.final_softcap);
     }
     if (flags & FWD_WANT_TOKENS) {
         prof_begin(KC_SAMPLE, 4.0 * B * ms_.vocab, 0);
@@ -1079,7 +1111,13 @@ void Model::fetch_output(float* logits, uint32_t* tokens) {
     int32_t flags[2];
     memcpy(flags, oh + tok_off + (size_t)B * 4, 8);
     if (flags[0] != 0) throw std::runtime_error("batch descriptor index out of range on the device (flag " + std::to_string(flags[0]) + ")");
-    if (flags[1] != 0) throw std::runtime_error("a bounded wait inside a kernel gave up (tensor-core matmul pipeline or expert exchange; status " + std::to_string(flags[1]) + ")");
+    if (flags[1] != 0) {
+        // the status word is sticky on the device: clear it so that the next forward starts clean
+        cudaMemsetAsync(tc_ws_.status.ptr(), 0, 4, stream_);
+        if ((flags[1] & 0xFFFF0000) == kMoeRouteStatus)
+            throw std::runtime_error("router produced non-finite logits for token row " + std::to_string(flags[1] & 0xFFFF));  // src/decoder.rs:474-483
+        throw std::runtime_error("a bounded wait inside a kernel gave up (tensor-core matmul pipeline or expert exchange; status " + std::to_string(flags[1]) + ")");
+    }
     if (logits) {
         if (!(out_flags_ & FWD_WANT_LOGITS)) throw std::runtime_error("logits were not requested for this forward");
         memcpy(logits, oh, tok_off);

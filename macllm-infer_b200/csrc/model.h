@@ -91,7 +91,7 @@ private:
         HalfWeight qkv_half, gu_half;  // f16 images of [wq; wk; wv] and [gate; up] stacked by rows
         // Q4_K matrices streamed by the narrow-batch matmul: [wq; wk] and [gate; up] share one buffer each
         DevBuf qk_raw, gu_raw;
-        QStreamWeight qs_qk, qs_o, qs_gu, qs_down;
+        QStreamWeight qs_qk, qs_v, qs_o, qs_gu, qs_down;  // qs_gu: rows interleaved when the gated form is on
         DeviceWeight wq, wk, wv, wo, gate, up, down;  // dense FFN, or expert banks for MoE layers
     };
     void load_weights(const GgufFile& f);
@@ -102,7 +102,7 @@ private:
                        int heads);
     void upload_f32(const GgufFile& f, const std::string& name, int64_t n, DevBuf& out);
     void matmul(const DeviceWeight& DW, const ActQ& x, int T, float* y, int ldy, float scale, float softcap);
-    ActQ act_view(DevBuf& qs, DevBuf& d, DevBuf& bs, DevBuf& xh, int T, int dim, int kind, bool want_f16, DevBuf* gs = nullptr);
+    ActQ act_view(DevBuf& qs, DevBuf& d, DevBuf& bs, DevBuf& xh, int T, int dim, int kind, bool want_f16);
     bool tensor_path(const QWeight& W, int T) const;
     void rope_tables_for(double theta, const float*& cos_t, const float*& sin_t);
 
@@ -145,10 +145,12 @@ private:
     void build_half_cache();
     void build_qstream();
     bool qstream_ = false;
-    DevBuf a_gs_, f_gs_;  // per-group activation sums for the streamed matmul
+    bool qstream_gated_ = false;   // gate|up streamed with act(gate) * up in its epilogue
+    bool qstream_qkv_ = false;     // [wq; wk] and wv go in one streamed launch
+    QStreamWeight qs_head_;        // output projection for narrow batches
     DevBuf v_partial_;  // split-K shares of the V projection on streamed ticks
     int qstream_min_rows_ = 2;  // one row stays on the integer GEMV
-    int matmul_stream(const QStreamWeight& W, const ActQ& x, int T, float* y, int ldy, int max_splits);
+    int matmul_stream(const QStreamWeight& W, const ActQ& x, int T, float* y, int ldy, int max_splits, const QStreamWeight* W2 = nullptr);
     HgemmScratch hgemm_scratch() const;
     // Returns the number of K shares; more than one means the result is the sum of that many partials in the
     // split-K scratch (see launch_hgemm_tc) and y was not written.

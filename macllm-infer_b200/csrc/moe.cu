@@ -20,7 +20,12 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t* sel, int
     __shared__ int32_t start[MAX_EXPERTS + 1];
     for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
     __syncthreads();
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&count[sel[p]], 1);
+    // a choice outside [0, experts) cannot come from the routing kernel; if one ever does it is left out of every group
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = sel[p];
+        if (e >= 0 && e < experts) atomicAdd(&count[e], 1);
+        else pos_of_pair[p] = -1;
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
         int acc = 0;

@@ -16,7 +16,8 @@
 //   * two calls that overlap on the GPU (different streams, or different host threads) race on the
 //     arrays and corrupt each other's results - serialise them;
 //   * the first call on a device resolves the arrays' device addresses (cudaGetSymbolAddress with that
-//     device current); make that first call before starting any stream capture.
+//     device current); make that first call before starting any stream capture;
+//   * every call synchronises its stream and copies a status word back to the host before it returns.
 #include "../../include/macllm_b200.h"
 #include "c_api_util.h"
 #include "kernels.h"
@@ -81,6 +82,7 @@ extern "C" int32_t mk_k_q4k_matmul_tc_noalloc_dev(const void* w_q4k_dev, int64_t
         if (w_q4k_dev == nullptr || x_dev == nullptr || y_dev == nullptr) throw std::runtime_error("mk_k_q4k_matmul_tc_noalloc_dev: null pointer");
         if (rows <= 0 || T <= 0 || cols <= 0 || cols % 256 != 0)
             throw std::runtime_error("mk_k_q4k_matmul_tc_noalloc_dev: rows and T must be positive and cols a positive multiple of 256");
+        if (rows > INT32_MAX) throw std::runtime_error("mk_k_q4k_matmul_tc_noalloc_dev: rows must fit a 32-bit integer");
         if (((uintptr_t)w_q4k_dev & 15) != 0) throw std::runtime_error("mk_k_q4k_matmul_tc_noalloc_dev: weights must be 16-byte aligned");
         if ((size_t)T * (size_t)cols > ACT_ELEMS)
             throw std::runtime_error("mk_k_q4k_matmul_tc_noalloc_dev: T * cols = " + std::to_string((size_t)T * cols) +

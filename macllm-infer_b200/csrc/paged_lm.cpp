@@ -25,6 +25,16 @@ std::unique_ptr<LmSession> PagedLm::new_session() {  // :3433-3477
     return s;
 }
 
+std::unique_ptr<LmSession> PagedLm::fork_session_prefix(LmSession& s, int64_t logical_len) {
+    validate_session(s);
+    if (s.table->logical_len() != s.logical_len) throw std::runtime_error("decoder session block table disagrees with its sequence length");
+    auto f = std::make_unique<LmSession>();
+    f->owner = this;
+    f->table = s.table->fork_prefix(logical_len);
+    f->logical_len = logical_len;
+    return f;
+}
+
 void PagedLm::validate_session(const LmSession& s) const {  // :3479-3492
     if (s.owner != this) throw std::runtime_error("decoder session belongs to a different model instance");
 }

@@ -57,6 +57,8 @@ public:
 
     // CausalLm::new_session
     std::unique_ptr<LmSession> new_session();
+    // A new session sharing the first logical_len tokens of s (PagedKvBlockTable::fork_prefix, cache.rs:1565-1571).
+    std::unique_ptr<LmSession> fork_session_prefix(LmSession& s, int64_t logical_len);
     // CausalLm::reset_session_for_prompt: clears the session, then attaches the longest cached
     // block-aligned prefix strictly shorter than the prompt.  Returns the cached token count.
     int64_t reset_session_for_prompt(LmSession& s, const uint32_t* tokens, size_t n);

@@ -407,11 +407,7 @@ TcPlan make_plan(const QWeight& W, int T) {
 
 template <int BN, int STAGES>
 void launch_variant(const TcParams& p, const TcPlan& pl, cudaStream_t s) {
-    static bool configured = false;
-    if (!configured) {
-        MK_CUDA(cudaFuncSetAttribute(qgemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
-        configured = true;
-    }
+    ensure_dynamic_smem(reinterpret_cast<const void*>(&qgemm_tc_kernel<BN, STAGES>), pl.smem);
     dim3 grid((unsigned)pl.row_tiles, (unsigned)pl.n_tiles, (unsigned)pl.splits);
     qgemm_tc_kernel<BN, STAGES><<<grid, TC_THREADS, pl.smem, s>>>(p);
     MK_LAUNCH_CHECK();

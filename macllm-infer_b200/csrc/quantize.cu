@@ -350,11 +350,7 @@ void launch_add_norm_quant(const NormQuantArgs& a, cudaStream_t s) {
     }
     if (a.out.gs != nullptr) throw std::runtime_error("launch_add_norm_quant: group sums need 256-wide, 16-byte aligned rows");
     size_t smem = (size_t)a.dim * sizeof(float);
-    static size_t configured = 0;
-    if (smem > 48 * 1024 && smem > configured) {
-        MK_CUDA(cudaFuncSetAttribute(add_norm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
-    }
+    ensure_dynamic_smem(reinterpret_cast<const void*>(&add_norm_quant_kernel), smem);
     add_norm_quant_kernel<<<a.rows, NQ_THREADS, smem, s>>>(a);
     MK_LAUNCH_CHECK();
 }
@@ -374,11 +370,7 @@ void launch_actmul_quant(const float* gate, const float* up, int ld, int T, int 
     }
     if (out.gs != nullptr) throw std::runtime_error("launch_actmul_quant: group sums need 256-wide, 16-byte aligned rows");
     size_t smem = (size_t)F * sizeof(float);
-    static size_t configured = 0;
-    if (smem > 48 * 1024 && smem > configured) {
-        MK_CUDA(cudaFuncSetAttribute(actmul_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
-    }
+    ensure_dynamic_smem(reinterpret_cast<const void*>(&actmul_quant_kernel), smem);
     actmul_quant_kernel<<<T, NQ_THREADS, smem, s>>>(gate, up, ld, F, act, act_kind, out, f32_out);
     MK_LAUNCH_CHECK();
 }

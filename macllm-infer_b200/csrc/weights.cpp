@@ -1,9 +1,35 @@
 // Weight upload: GGUF block bytes -> HBM layouts read by the kernels.
 #include "device_util.h"
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <vector>
 
 namespace mk {
+
+void ensure_dynamic_smem(const void* func, size_t bytes) {
+    if (bytes <= 48 * 1024) return;
+    static std::mutex mu;
+    static std::map<std::pair<const void*, int>, size_t> done;
+    int dev = 0;
+    MK_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    size_t& have = done[{func, dev}];
+    if (have >= bytes) return;
+    MK_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    have = bytes;
+}
+
+int device_sm_count() {
+    static std::mutex mu;
+    static std::map<int, int> cached;
+    int dev = 0;
+    MK_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    int& n = cached[dev];
+    if (n == 0) MK_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    return n;
+}
 
 int64_t gguf_row_bytes(int type, int64_t cols) {
     switch (type) {

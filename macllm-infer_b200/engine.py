@@ -30,11 +30,20 @@ class Request:
 
 
 class Session:
-    def __init__(self, model: "Model"):
+    def __init__(self, model: "Model", _handle=None):
         self.model = model
+        if _handle is not None:
+            self._h = _handle
+            return
         h = C.c_void_p()
         capi.check(capi.lib().mk_session_new(model._h, C.byref(h)))
         self._h = h
+
+    def fork_prefix(self, logical_len: int) -> "Session":
+        """A new session sharing this one's first logical_len tokens (copy-on-write on a shared partial tail)."""
+        h = C.c_void_p()
+        capi.check(capi.lib().mk_session_fork_prefix(self.model._h, self._h, logical_len, C.byref(h)))
+        return Session(self.model, _handle=h)
 
     def __len__(self) -> int:
         n = C.c_int64()

@@ -121,10 +121,10 @@ def moe_route(logits, k: int):
 
 def matmul_plan(path: int, rows: int, cols: int, T: int, max_splits: int = 16) -> dict:
     """Host-only: how a launch of the f16-image GEMM (PATH_HALF) or the streamed matmul (PATH_STREAM) is cut."""
-    out = np.zeros(6, dtype=np.int64)
+    out = np.zeros(8, dtype=np.int64)
     capi.check(capi.lib().mk_k_matmul_plan(path, rows, cols, T, max_splits, _p(out)))
     names = ("bn", "row_tiles", "n_tiles", "splits", "kb_per_split", "partial_floats") if path == capi.PATH_HALF else \
-        ("bn", "row_tiles", "units", "ctas", "slots", "partial_floats")
+        ("bn", "row_tiles", "items", "ctas", "slots", "partial_floats", "tiles_per_group", "groups")
     return dict(zip(names, map(int, out)))
 
 

@@ -43,19 +43,32 @@ def test_f16_gemm_plan_invariants(env, rows, cols, T):
     assert ops.matmul_plan(capi.PATH_HALF, rows, cols, T, max_splits=1)["splits"] == 1
 
 
-@pytest.mark.parametrize("rows,cols", [(2560, 2048), (2048, 2048), (22016, 2048), (2048, 11008), (1000, 11008), (128, 256)])
+@pytest.mark.parametrize("rows,cols", [(2560, 2048), (2048, 2048), (22016, 2048), (2048, 11008), (1000, 11008), (128, 256), (128256, 2048)])
 @pytest.mark.parametrize("T", [2, 17, 33, 64])
 def test_streamed_matmul_plan_invariants(env, rows, cols, T):
     ops, capi = env
     p = ops.matmul_plan(capi.PATH_STREAM, rows, cols, T)
-    assert p["row_tiles"] == -(-rows // 128) and p["units"] == p["row_tiles"] * (cols // 256)
-    assert 1 <= p["ctas"] <= min(SMS, p["units"])   # one persistent CTA per SM, fewer when the cap on slots bites
-    if p["ctas"] < min(SMS, p["units"]):
-        assert p["slots"] >= 12
-    assert 1 <= p["slots"] <= 16 and p["bn"] >= T
+    nb = cols // 256
+    assert p["row_tiles"] == -(-rows // 128) and p["tiles_per_group"] in (1, 2, 4)
+    assert p["groups"] == -(-p["row_tiles"] // p["tiles_per_group"]) and p["items"] == p["groups"] * nb
+    assert 1 <= p["ctas"] <= min(SMS, p["items"])   # at most one persistent CTA per SM
+    assert 1 <= p["slots"] <= 16 and p["bn"] >= T and p["bn"] in (16, 32, 64)
     assert p["partial_floats"] == (p["slots"] * T * rows if p["slots"] > 1 else 0)
+    assert p["partial_floats"] * 4 <= 24 << 20
+    if p["slots"] == 1:
+        assert p["ctas"] <= p["groups"]             # whole groups: every result is complete in one CTA
     whole = ops.matmul_plan(capi.PATH_STREAM, rows, cols, T, max_splits=1)
-    assert whole["slots"] == 1 and whole["ctas"] == whole["row_tiles"]  # without shares a CTA owns whole row tiles
+    assert whole["slots"] == 1 and whole["ctas"] == min(SMS, whole["groups"])
+
+
+def test_streamed_matmul_plans_of_the_benchmark_shapes(env):
+    ops, capi = env
+    gate_up = ops.matmul_plan(capi.PATH_STREAM, 22016, 2048, 64)
+    assert (gate_up["ctas"], gate_up["tiles_per_group"], gate_up["slots"]) == (148, 2, 3)   # 4.6 items of two units per CTA
+    down = ops.matmul_plan(capi.PATH_STREAM, 2048, 11008, 64)
+    assert (down["ctas"], down["tiles_per_group"]) == (148, 1) and down["slots"] <= 11
+    head = ops.matmul_plan(capi.PATH_STREAM, 128256, 2048, 64)
+    assert head["slots"] == 1 and head["ctas"] == 148                                          # 32 MB per slot: never cut
 
 
 def test_plans_refuse_what_the_kernels_do_not_cover(env):

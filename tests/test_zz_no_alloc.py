@@ -34,10 +34,12 @@ def call_noalloc(torch, capi, w_bytes, rows, cols, x):
     x_dev = torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32)).to(dev)
     y_dev = torch.full((x.shape[0], rows), float("nan"), dtype=torch.float32, device=dev)
     torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
     status = capi.lib().mk_k_q4k_matmul_tc_noalloc_dev(C.c_void_p(w_dev.data_ptr()), rows, cols, C.c_void_p(x_dev.data_ptr()),
                                                       x.shape[0], C.c_void_p(y_dev.data_ptr()), None)
     capi.check(status)
-    return y_dev.cpu().numpy()
+    free_after, _ = torch.cuda.mem_get_info()
+    return y_dev.cpu().numpy(), free_before - free_after
 
 
 def test_two_calls_in_a_row_match_the_allocating_entry_point(env):
@@ -45,12 +47,16 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point(env):
     rng = np.random.default_rng(11)
     # different shapes on purpose: the second call must not see anything the first one left behind
     cases = [(40, 768, 2048, 5), (64, 2048, 1024, 6)]
-    for T, rows, cols, stream in cases:
+    for call, (T, rows, cols, stream) in enumerate(cases):
         w = ops.seed_tensor(0, stream, 0.02, capi.TYPE_Q4_K, rows, cols)
         x = rng.standard_normal((T, cols)).astype(np.float32)
         want = ops.qmatmul(capi.TYPE_Q4_K, w, rows, cols, x, capi.PATH_TENSOR)
-        got = call_noalloc(torch, capi, w, rows, cols, x)
+        got, taken = call_noalloc(torch, capi, w, rows, cols, x)
         assert np.isfinite(got).all()
+        # the first call on a device may load the library's kernels (module loading is lazy); from the second call
+        # on, the device's free memory is the same before and after: nothing was allocated
+        if call > 0:
+            assert taken == 0
         # same kernels, same operands, same split order: the tolerance of the tensor-core tests, and in
         # practice bit-identical
         scale = np.sqrt(cols) * 0.02
