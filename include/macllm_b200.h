@@ -203,6 +203,20 @@ int32_t mk_reserve_batch(mk_model* m, const mk_lane* lanes, int32_t n_lanes, mk_
 /* Dropping a reservation rolls it back (cache.rs:3001-3005). */
 int32_t mk_reservation_drop(mk_reservation* r);
 
+/* Per-lane token selection of the NEXT forward with MK_FWD_WANT_TOKENS: temperature <= 0 selects the first-index
+ * argmax (the default for every lane); otherwise Sampler::sample_stochastic (src/sampling.rs:145-169,337-390) runs on
+ * the device - scale by 1 / temperature, keep the top_k best, softmax, keep the head that adds up to top_p, then pick
+ * by the uniform draw u in [0, 1), which the caller supplies so that the random stream stays on the host.  The device
+ * covers 1 <= top_k <= 1024; other settings are refused (read logits back and sample on the host).  The settings
+ * apply to one forward and are forgotten after it. */
+typedef struct mk_lane_sampling {
+    float temperature;
+    int32_t top_k;
+    float top_p;
+    float u;
+} mk_lane_sampling;
+int32_t mk_forward_set_sampling(mk_model* m, const mk_lane_sampling* lanes, int32_t n_lanes);
+
 #define MK_FWD_WANT_LOGITS 1u  /* copy [lanes, vocab] f32 logits to the host at the barrier */
 #define MK_FWD_WANT_TOKENS 2u  /* on-device greedy selection, one u32 per lane */
 
@@ -287,6 +301,7 @@ typedef struct mk_engine_stats {
     int64_t kv_shrinks;          /* candidate lanes dropped because the pool was exhausted */
     double device_ms;            /* sum of per-tick device times */
     int64_t cleanup_drains;      /* mk_synchronize calls made while poisoning (src/engine.rs:2723-2736) */
+    int64_t device_sampled;      /* stochastic tokens picked by the device sampler */
 } mk_engine_stats;
 
 int32_t mk_engine_new(mk_model* m, const mk_engine_config* cfg, mk_engine** out);
@@ -494,6 +509,13 @@ int32_t mk_k_attention_plan(const int32_t* start_pos, const int32_t* n_tokens, i
 
 /* argmax of src/sampling.rs:425-433 for each row of logits [B][vocab]. */
 int32_t mk_k_argmax(const float* logits, int32_t B, int32_t vocab, uint32_t* out);
+/* Sampler::sample_with_generated without penalties (src/sampling.rs:95-169,337-390) on rows of logits [B][vocab] (host
+ * memory), one setting per row.  where = 0: this library's host sampler (any top_k; needs no GPU); where = 1: the device
+ * kernel (greedy rows, or 1 <= top_k <= 1024).  Both use the same arithmetic and return the same tokens. */
+/* apply_repetition_penalty + apply_openai_penalties (src/sampling.rs:392-423) on one row, in place (host only). */
+int32_t mk_k_penalties(float* logits, int32_t vocab, const uint32_t* history, int32_t n_history, float repetition_penalty,
+                       const uint32_t* generated, int32_t n_generated, float presence_penalty, float frequency_penalty);
+int32_t mk_k_sample(const float* logits, int32_t B, int32_t vocab, const mk_lane_sampling* settings, int32_t where, uint32_t* out);
 
 /* selected_softmax_routes (src/decoder.rs:448-554): sel_experts / sel_weights are [T][k], best first. */
 int32_t mk_k_moe_route(const float* logits, int32_t T, int32_t experts, int32_t k, int32_t* sel_experts, float* sel_weights);

@@ -92,7 +92,11 @@ class TickLane(C.Structure):
 class EngineStats(C.Structure):
     _fields_ = [("ticks", C.c_int64), ("prefill_tokens", C.c_int64), ("decode_tokens", C.c_int64),
                 ("completed_requests", C.c_int64), ("failed_requests", C.c_int64), ("kv_shrinks", C.c_int64),
-                ("device_ms", C.c_double), ("cleanup_drains", C.c_int64)]
+                ("device_ms", C.c_double), ("cleanup_drains", C.c_int64), ("device_sampled", C.c_int64)]
+
+
+class LaneSampling(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_k", C.c_int32), ("top_p", C.c_float), ("u", C.c_float)]
 
 
 class KernelProfile(C.Structure):
@@ -198,6 +202,9 @@ SIGNATURES = {
     "mk_k_gated_ffn": (_i32, [_i32, P, P, _i64, _i64, P, _i32, _i32, P, _i32, P]),
     "mk_k_attention_step": (_i32, [C.POINTER(AttnCase)]),
     "mk_k_argmax": (_i32, [P, _i32, _i32, P]),
+    "mk_k_sample": (_i32, [P, _i32, _i32, P, _i32, P]),
+    "mk_k_penalties": (_i32, [P, _i32, P, _i32, C.c_float, P, _i32, C.c_float, C.c_float]),
+    "mk_forward_set_sampling": (_i32, [P, P, _i32]),
     "mk_k_moe_route": (_i32, [P, _i32, _i32, _i32, P, P]),
 }
 

@@ -6,6 +6,7 @@
 #include "kernels.h"
 #include "hgemm_tc.h"
 #include "qstream_tc.h"
+#include "host_sampler.h"
 #include "attention_tc.h"
 #include "qgemm_tc.h"
 #include <vector>
@@ -501,6 +502,45 @@ int32_t mk_k_argmax(const float* logits, int32_t B, int32_t vocab, uint32_t* out
         MK_CUDA(cudaDeviceSynchronize());
         dout.download(out, (size_t)B * 4);
         MK_CUDA(cudaDeviceSynchronize());
+    });
+}
+
+int32_t mk_k_penalties(float* logits, int32_t vocab, const uint32_t* history, int32_t n_history, float repetition_penalty,
+                       const uint32_t* generated, int32_t n_generated, float presence_penalty, float frequency_penalty) {
+    return guarded([&] {
+        apply_penalties(logits, vocab, history, n_history, repetition_penalty, generated, n_generated, presence_penalty, frequency_penalty);
+    });
+}
+
+int32_t mk_k_sample(const float* logits, int32_t B, int32_t vocab, const mk_lane_sampling* settings, int32_t where, uint32_t* out) {
+    return guarded([&] {
+        if (B <= 0 || vocab <= 0 || logits == nullptr || settings == nullptr || out == nullptr) throw std::runtime_error("mk_k_sample: bad arguments");
+        if (where == 0) {
+            for (int32_t r = 0; r < B; ++r) {
+                const float* row = logits + (int64_t)r * vocab;
+                const mk_lane_sampling& s = settings[r];
+                out[r] = s.temperature > 0.f ? sample_top_k_top_p(row, vocab, s.temperature, s.top_k, s.top_p, s.u) : (uint32_t)argmax_first(row, vocab);
+            }
+            return;
+        }
+        require_device();
+        std::vector<LaneSampling> ls((size_t)B);
+        for (int32_t r = 0; r < B; ++r) {
+            if (!device_sampling_covers(settings[r].temperature, settings[r].top_k, vocab))
+                throw std::runtime_error("mk_k_sample: the device sampler covers greedy selection and 1 <= top_k <= 1024");
+            ls[(size_t)r] = LaneSampling{settings[r].temperature, settings[r].top_k, settings[r].top_p, settings[r].u};
+        }
+        DevBuf dl((size_t)B * vocab * 4), dp((size_t)B * sizeof(LaneSampling)), dout((size_t)B * 4), status(4);
+        dl.upload(logits, (size_t)B * vocab * 4);
+        dp.upload(ls.data(), ls.size() * sizeof(LaneSampling));
+        status.zero(nullptr);
+        launch_sample(dl.as<float>(), B, vocab, dp.as<LaneSampling>(), dout.as<uint32_t>(), status.as<int32_t>(), nullptr);
+        MK_CUDA(cudaDeviceSynchronize());
+        dout.download(out, (size_t)B * 4);
+        int32_t st = 0;
+        status.download(&st, 4);
+        MK_CUDA(cudaDeviceSynchronize());
+        if ((st & 0xFFFF0000) == kSampleEmptyStatus) throw std::runtime_error("sampling distribution is empty (row " + std::to_string(st & 0xFFFF) + ")");
     });
 }
 

@@ -9,7 +9,10 @@
 
 using namespace mk;
 
-struct mk_model { std::unique_ptr<PagedLm> lm; };
+struct mk_model {
+    std::unique_ptr<PagedLm> lm;
+    std::vector<mk_lane_sampling> sampling;  // settings of the next forward (mk_forward_set_sampling)
+};
 struct mk_session { std::unique_ptr<LmSession> s; };
 struct mk_reservation { std::unique_ptr<LmReservation> r; };
 struct mk_engine { std::unique_ptr<Engine> e; };
@@ -272,12 +275,38 @@ int32_t mk_reservation_drop(mk_reservation* r) {
     return guarded([&] { delete r; });
 }
 
+int32_t mk_forward_set_sampling(mk_model* m, const mk_lane_sampling* lanes, int32_t n_lanes) {
+    return guarded([&] {
+        if (n_lanes < 0 || (n_lanes > 0 && lanes == nullptr)) throw std::runtime_error("mk_forward_set_sampling: bad arguments");
+        for (int32_t i = 0; i < n_lanes; ++i) {
+            if (!m->lm->device_sampling_covers(lanes[i].temperature, lanes[i].top_k))
+                throw std::runtime_error("mk_forward_set_sampling: the device sampler covers greedy selection and 1 <= top_k <= 1024");
+            if (lanes[i].temperature > 0.f && !(lanes[i].top_p > 0.f && lanes[i].top_p <= 1.f))
+                throw std::runtime_error("mk_forward_set_sampling: top_p must be in (0, 1]");
+            if (!(lanes[i].u >= 0.f && lanes[i].u < 1.f)) throw std::runtime_error("mk_forward_set_sampling: the draw must be in [0, 1)");
+        }
+        m->sampling.assign(lanes, lanes + n_lanes);
+    });
+}
+
 int32_t mk_forward_batch_reserved(mk_model* m, const mk_lane* lanes, int32_t n_lanes, mk_reservation* r, uint32_t flags) {
     return guarded([&] {
         if (r == nullptr) throw std::runtime_error("forward needs a KV reservation");
         std::unique_ptr<LmReservation> res = std::move(r->r);
         delete r;  // consumed
-        m->lm->forward_batch_reserved(to_lanes(lanes, n_lanes), std::move(res), flags);
+        std::vector<LmLane> ll = to_lanes(lanes, n_lanes);
+        std::vector<mk_lane_sampling> sampling = std::move(m->sampling);  // one forward only
+        m->sampling.clear();
+        if (!sampling.empty()) {
+            if ((int32_t)sampling.size() != n_lanes) throw std::runtime_error("sampling settings cover another number of lanes than the forward");
+            for (int32_t i = 0; i < n_lanes; ++i) {
+                ll[(size_t)i].temperature = sampling[(size_t)i].temperature;
+                ll[(size_t)i].top_k = sampling[(size_t)i].top_k;
+                ll[(size_t)i].top_p = sampling[(size_t)i].top_p;
+                ll[(size_t)i].u = sampling[(size_t)i].u;
+            }
+        }
+        m->lm->forward_batch_reserved(ll, std::move(res), flags);
     });
 }
 
@@ -431,6 +460,7 @@ int32_t mk_engine_stats_query(mk_engine* e, mk_engine_stats* out) {
         out->kv_shrinks = s.kv_shrinks;
         out->device_ms = s.device_ms;
         out->cleanup_drains = s.cleanup_drains;
+        out->device_sampled = s.device_sampled;
     });
 }
 

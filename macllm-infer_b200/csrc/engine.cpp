@@ -311,6 +311,8 @@ int Engine::drive_once() {  // engine.rs:1938-1964
     if (lane_count > 0) {
         std::vector<LmLane> lanes;
         std::vector<TickLaneTrace> tick;
+        // tokens are picked on the device unless some lane needs what only the host sampler has: penalties (they read
+        // the request's history), an unbounded or very wide top-k, or recorded logits
         bool device_greedy = !cfg_.host_sampling && !cfg_.record_logits;
         for (int i = 0; i < visits; ++i) {
             const Visit& v = actions[(size_t)i];
@@ -320,10 +322,27 @@ int Engine::drive_once() {  // engine.rs:1938-1964
             lanes.push_back(LmLane{s.session.get(), ids, v.n_tokens, v.start_pos});
             tick.push_back(TickLaneTrace{s.id, v.start_pos, v.n_tokens});
             const EngineRequest& rq = s.req;
-            if (v.ready_to_sample && (rq.temperature > 0.f || std::fabs(rq.repetition_penalty - 1.f) >= 1.1920929e-07f ||
-                                      rq.presence_penalty != 0.f || rq.frequency_penalty != 0.f))
+            if (v.ready_to_sample && (std::fabs(rq.repetition_penalty - 1.f) >= 1.1920929e-07f || rq.presence_penalty != 0.f ||
+                                      rq.frequency_penalty != 0.f || !model_.device_sampling_covers(rq.temperature, rq.top_k)))
                 device_greedy = false;
             if (v.was_prefill) stats_.prefill_tokens += v.n_tokens; else stats_.decode_tokens += v.n_tokens;
+        }
+        if (device_greedy) {
+            // one uniform draw per stochastic token, taken from the request's stream exactly as the host sampler would
+            size_t li = 0;
+            for (int i = 0; i < visits; ++i) {
+                const Visit& v = actions[(size_t)i];
+                if (v.kind != Visit::Forward) continue;
+                Sequence& s = *active_[(size_t)i];
+                LmLane& l = lanes[li++];
+                if (v.ready_to_sample && s.req.temperature > 0.f) {
+                    l.temperature = s.req.temperature;
+                    l.top_k = s.req.top_k;
+                    l.top_p = s.req.top_p;
+                    l.u = next_uniform(s.rng);
+                    ++stats_.device_sampled;
+                }
+            }
         }
         uint32_t flags = device_greedy ? FWD_WANT_TOKENS : FWD_WANT_LOGITS;
         forward_needs_drain_ = true;  // engine.rs:2294

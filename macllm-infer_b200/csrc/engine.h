@@ -55,7 +55,7 @@ struct TickLaneTrace {
 };
 
 struct EngineStats {
-    int64_t ticks = 0, prefill_tokens = 0, decode_tokens = 0, completed = 0, failed = 0, kv_shrinks = 0, cleanup_drains = 0;
+    int64_t ticks = 0, prefill_tokens = 0, decode_tokens = 0, completed = 0, failed = 0, kv_shrinks = 0, cleanup_drains = 0, device_sampled = 0;
     double device_ms = 0.0;
 };
 

@@ -203,7 +203,8 @@ Model::Model(const std::string& gguf_path, const ModelConfig& cfg) : cfg_(cfg) {
     }
     consider(ms_.tied ? token_embd_.w : output_.w, B);
     tc_ws_.partial.alloc(std::max<size_t>(partial, 1) * 4);
-    size_t stage_bytes = (size_t)B * sizeof(LaneHeader) + (size_t)(pool_->max_blocks() + B) * 4 + (size_t)T * 4 + 64;
+    size_t stage_bytes = (size_t)B * sizeof(LaneHeader) + (size_t)(pool_->max_blocks() + B) * 4 + (size_t)T * 4 + 64 +
+                         (size_t)B * sizeof(LaneSampling) + 16;
     attn_tc_ = attention_tc_supported(ms_.q_heads, ms_.kv_heads, ms_.head_dim, cfg_.block_tokens, cfg_.kv_f16);
     if (attn_tc_) {
         attn_max_entries_ = attention_tc_max_entries(B, ms_.kv_heads);
@@ -627,6 +628,21 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         tpos += l.n_tokens;
     }
     size_t stage_bytes = off_ids + (size_t)T * 4;
+    // per-lane sampling settings, only when some lane does not take the plain argmax
+    bool any_stochastic = false;
+    for (const LmLane& l : lanes) any_stochastic |= l.temperature > 0.f;
+    size_t off_sampling = 0;
+    if (any_stochastic && (flags & FWD_WANT_TOKENS)) {
+        off_sampling = (stage_bytes + 15) / 16 * 16;
+        LaneSampling* sp = reinterpret_cast<LaneSampling*>(hp + off_sampling);
+        for (int i = 0; i < B; ++i) {
+            const LmLane& l = lanes[(size_t)i];
+            if (!mk::device_sampling_covers(l.temperature, l.top_k, ms_.vocab))
+                throw std::runtime_error("the device sampler covers greedy selection and 1 <= top_k <= 1024");
+            sp[i] = LaneSampling{l.temperature, l.top_k, l.top_p, l.u};
+        }
+        stage_bytes = off_sampling + (size_t)B * sizeof(LaneSampling);
+    }
     // work lists of the tensor-core attention (the same for every layer of the tick)
     size_t off_tiles = 0, off_entries = 0, off_dec = 0;
     int n_attn_tiles = 0, n_attn_entries = 0, n_attn_dec = 0;
@@ -1084,7 +1100,11 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
     }
     if (flags & FWD_WANT_TOKENS) {
         prof_begin(KC_SAMPLE, 4.0 * B * ms_.vocab, 0);
-        launch_argmax(logits_.as<float>(), B, ms_.vocab, tokens_.as<uint32_t>(), argmax_scratch_.ptr(), stream_);
+        if (off_sampling != 0)
+            launch_sample(logits_.as<float>(), B, ms_.vocab, reinterpret_cast<const LaneSampling*>(dp + off_sampling), tokens_.as<uint32_t>(),
+                          tc_ws_.status.as<int32_t>(), stream_);
+        else
+            launch_argmax(logits_.as<float>(), B, ms_.vocab, tokens_.as<uint32_t>(), argmax_scratch_.ptr(), stream_);
         prof_end();
         ++launches_;
     }
@@ -1114,6 +1134,8 @@ void Model::fetch_output(float* logits, uint32_t* tokens) {
     if (flags[1] != 0) {
         // the status word is sticky on the device: clear it so that the next forward starts clean
         cudaMemsetAsync(tc_ws_.status.ptr(), 0, 4, stream_);
+        if ((flags[1] & 0xFFFF0000) == kSampleEmptyStatus)
+            throw std::runtime_error("sampling distribution is empty (lane " + std::to_string(flags[1] & 0xFFFF) + ")");  // src/sampling.rs:352-355
         if ((flags[1] & 0xFFFF0000) == kMoeRouteStatus)
             throw std::runtime_error("router produced non-finite logits for token row " + std::to_string(flags[1] & 0xFFFF));  // src/decoder.rs:474-483
         throw std::runtime_error("a bounded wait inside a kernel gave up (tensor-core matmul pipeline or expert exchange; status " + std::to_string(flags[1]) + ")");

@@ -73,6 +73,7 @@ public:
     const ModelSpec& model_spec() const { return ms_; }
     // Joins the expert-parallel group (collective over all ep_size ranks; `id` is EpComm::unique_id from rank 0).
     void ep_init(const uint8_t* id);
+    bool device_sampling_covers(float temperature, int top_k) const override { return mk::device_sampling_covers(temperature, top_k, ms_.vocab); }
     float last_forward_ms() const override;
     int64_t launch_count() const override { return launches_; }
     int64_t h2d_bytes() const override { return h2d_bytes_; }

@@ -26,6 +26,12 @@ struct LmLane {
     const uint32_t* ids = nullptr;
     int32_t n_tokens = 0;
     int32_t start_pos = 0;
+    // how FWD_WANT_TOKENS picks this lane's token: temperature <= 0 = first-index argmax; otherwise temperature /
+    // top-k / top-p with the uniform draw u supplied by the caller (see LaneSampling in kernels.h)
+    float temperature = 0.f;
+    int32_t top_k = 0;
+    float top_p = 1.f;
+    float u = 0.f;
 };
 
 struct LmReservation {
@@ -80,6 +86,8 @@ public:
     KvPoolStats pool_stats() const { return pool_->stats(); }
     std::optional<LmPrefixDiagnostics> prefix_diagnostics() const;
     int last_lanes() const { return last_lanes_; }
+    // Whether FWD_WANT_TOKENS can pick a token with these settings on the device (else the caller reads logits back).
+    virtual bool device_sampling_covers(float temperature, int top_k) const { return !(temperature > 0.f) && top_k >= 0; }
     virtual float last_forward_ms() const { return 0.f; }
     virtual int64_t launch_count() const { return 0; }
     // Host<->device bytes moved by forwards since load.

@@ -119,6 +119,25 @@ def moe_route(logits, k: int):
     return sel, w
 
 
+def penalties(logits, history, repetition, generated, presence, frequency) -> np.ndarray:
+    """Repetition penalty over the set of history tokens, then presence / frequency penalties over generated counts."""
+    row = np.array(logits, dtype=np.float32)
+    h = np.ascontiguousarray(history, dtype=np.uint32)
+    g = np.ascontiguousarray(generated, dtype=np.uint32)
+    capi.check(capi.lib().mk_k_penalties(_p(row), len(row), _p(h), len(h), repetition, _p(g), len(g), presence, frequency))
+    return row
+
+
+def sample(logits: np.ndarray, settings, where: int) -> np.ndarray:
+    """settings: one (temperature, top_k, top_p, u) per row.  where 0 = host sampler, 1 = device kernel."""
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    B, V = logits.shape
+    arr = (capi.LaneSampling * B)(*[capi.LaneSampling(float(t), int(k), float(p), float(u)) for t, k, p, u in settings])
+    out = np.zeros(B, dtype=np.uint32)
+    capi.check(capi.lib().mk_k_sample(_p(logits), B, V, arr, where, _p(out)))
+    return out
+
+
 def matmul_plan(path: int, rows: int, cols: int, T: int, max_splits: int = 16) -> dict:
     """Host-only: how a launch of the f16-image GEMM (PATH_HALF) or the streamed matmul (PATH_STREAM) is cut."""
     out = np.zeros(8, dtype=np.int64)

@@ -188,9 +188,21 @@ def argmax(v: np.ndarray) -> int:
 
 
 def apply_penalties(logits, history, rep, generated, presence, frequency) -> np.ndarray:
-    logits = _f32(logits).copy()
-    h = np.ascontiguousarray(history, dtype=np.uint32)
-    g = np.ascontiguousarray(generated, dtype=np.uint32)
-    lib().orc_apply_penalties(_p(logits), C.c_int64(logits.size), _p(h), C.c_int64(len(h)), C.c_float(rep), _p(g),
-                              C.c_int64(len(g)), C.c_float(presence), C.c_float(frequency))
-    return logits
+    """apply_repetition_penalty then apply_openai_penalties (src/sampling.rs:392-423), in numpy f32: the repetition
+    penalty touches every distinct history token once (negative logits are multiplied, the others divided); the
+    presence / frequency penalties subtract frequency * count + presence per distinct generated token.  Tokens outside
+    the row are ignored.  Written apart from the product's host sampler on purpose."""
+    out = _f32(logits).copy()
+    rep = np.float32(rep)
+    if rep > 0 and abs(rep - np.float32(1.0)) >= np.finfo(np.float32).eps:
+        for t in sorted({int(t) for t in history}):
+            if t < out.size:
+                out[t] = out[t] * rep if out[t] < 0 else out[t] / rep
+    if (presence != 0 or frequency != 0) and len(generated) > 0:
+        counts = {}
+        for t in generated:
+            counts[int(t)] = counts.get(int(t), 0) + 1
+        for t, c in counts.items():
+            if t < out.size:
+                out[t] = out[t] - (np.float32(frequency) * np.float32(c) + np.float32(presence))
+    return out

@@ -530,25 +530,6 @@ int64_t orc_argmax(const float* v, int64_t n) {
     return best;
 }
 
-// Repetition penalty over the set of history tokens, then OpenAI penalties over generated counts
-// (src/sampling.rs:392-423).
-void orc_apply_penalties(float* logits, int64_t vocab, const uint32_t* history, int64_t nh, float rep,
-                         const uint32_t* generated, int64_t ng, float presence, float frequency) {
-    if (rep > 0.f && fabsf(rep - 1.0f) >= 1.1920929e-07f) {
-        std::vector<uint32_t> seen(history, history + nh);
-        std::sort(seen.begin(), seen.end()); seen.erase(std::unique(seen.begin(), seen.end()), seen.end());
-        for (uint32_t t : seen) if ((int64_t)t < vocab) logits[t] = logits[t] < 0.f ? logits[t] * rep : logits[t] / rep;
-    }
-    if ((presence != 0.f || frequency != 0.f) && ng > 0) {
-        std::vector<uint32_t> g(generated, generated + ng); std::sort(g.begin(), g.end());
-        for (size_t i = 0; i < g.size();) {
-            size_t j = i; while (j < g.size() && g[j] == g[i]) ++j;
-            if ((int64_t)g[i] < vocab) logits[g[i]] -= frequency * (float)(j - i) + presence;
-            i = j;
-        }
-    }
-}
-
 int orc_num_threads() {
 #ifdef _OPENMP
     return omp_get_max_threads();
