@@ -43,20 +43,15 @@ import __graft_entry__ as entry  # noqa: E402
 METRIC = "ragged-batch tokens/s (prefill+decode)"
 UNIT = "tokens/s"
 
-WORKLOADS = {
-    # name: (seed config, sequences, prompt range, new tokens, quantum, budget)
-    "smollm3-3b-ragged64": dict(config="smollm3-3b", seqs=64, prompt=(32, 1024), new_tokens=128, quantum=512, budget=2048, seed=1002),
-    "tinyllama-1.1b-batch4": dict(config="tinyllama-1.1b", seqs=4, prompt_list=[17, 64, 128, 301], new_tokens=32, quantum=128,
-                                  budget=256, seed=1001),
-}
+DEFAULT_WORKLOAD = "smollm3-3b-ragged64"
+WORKLOAD_NAMES = ["tinyllama-1.1b-batch4", "smollm3-3b-ragged64", "qwen3-8b-prefix32", "gemma2-9b-long128", "qwen3-30b-a3b-poisson"]
 
 
-# DRAM traffic of the three dominant kernels relative to their algorithmic bytes, from one `ncu --set full` capture
-# each on the benchmark's shapes (dram__bytes_read.sum + dram__bytes_write.sum over the bytes counted here).  The
+# DRAM traffic of the dominant kernels relative to their algorithmic bytes, from one `ncu` capture each on the
+# benchmark's shapes (dram__bytes_read.sum + dram__bytes_write.sum over the bytes counted here; profiles/).  The
 # roofline block scales the live per-launch algorithmic bytes by these ratios.
 NCU_TRAFFIC_RATIO = {
     "hgemm_tc": (98.8 + 21.4) / (90.2 + 8.4 + 45.1),      # gate|up with the activation in the epilogue: every operand once; part of the f16 output is still in L2 at kernel end
-    "qstream_tc": 25.69 / (25.36 + 0.26 + 5.64),          # weights once; the partial sums never leave L2
     "paged_attention": (77.0 + 1.9) / (72.4 + 4.2),
 }
 
@@ -69,28 +64,24 @@ def peaks() -> dict:
     return dict(hbm_gbs=6650.0, tflops=1400.0, source="fallback")
 
 
-def make_prompts(w: dict, vocab: int, rank: int):
-    rng = np.random.default_rng(w["seed"] + 7919 * rank)
-    if "prompt_list" in w:
-        lens = list(w["prompt_list"])
-    else:
-        lens = [int(x) for x in rng.integers(w["prompt"][0], w["prompt"][1] + 1, size=w["seqs"])]
-    return [rng.integers(3, vocab, size=n).astype(np.uint32) for n in lens]
+def workloads_module():
+    entry.load_package()
+    return importlib.import_module("macllm_infer_b200.workloads")
 
 
-def checkpoint_path(w: dict) -> Path:
+def checkpoint_path(config: str) -> Path:
     d = Path(os.environ.get("MACLLM_SEED_DIR", tempfile.gettempdir())) / "macllm_b200_seed"
     d.mkdir(parents=True, exist_ok=True)
-    return d / f"{w['config']}.gguf"
+    return d / f"{config}.gguf"
 
 
-def ensure_checkpoint(w: dict) -> Path:
+def ensure_checkpoint(config: str) -> Path:
     seed = importlib.import_module("macllm_infer_b200.seed_gguf")
-    path = checkpoint_path(w)
+    path = checkpoint_path(config)
     done = path.with_suffix(".done")
     if not done.exists():
         t0 = time.time()
-        seed.write_seed_gguf(path, seed.CONFIGS[w["config"]], seed=0)
+        seed.write_seed_gguf(path, seed.CONFIGS[config], seed=0)
         done.write_text("ok")
         print(f"[bench] wrote {path} ({path.stat().st_size / 1e9:.2f} GB) in {time.time() - t0:.1f}s", file=sys.stderr)
     return path
@@ -199,62 +190,114 @@ def aggregate(dist, tokens: float, seconds: float) -> tuple[float, float, float]
     return total, slowest, total / max(slowest, 1e-12)
 
 
-def run_step(eng_mod, model, w, prompts):
-    """One step: the whole continuous batch through a fresh engine.  Returns (tokens, wall s, stats)."""
-    eng = eng_mod.Engine(model, max_active_sequences=w["seqs"], scheduler_token_budget=w["budget"],
-                         prefill_token_quantum=w["quantum"], queue_capacity=w["seqs"] + 8)
-    reqs = [eng_mod.Request(p, w["new_tokens"]) for p in prompts]
+def new_engine(eng_mod, model, w, active: int, n_requests: int):
+    return eng_mod.Engine(model, max_active_sequences=active, scheduler_token_budget=w.budget, prefill_token_quantum=w.quantum,
+                          queue_capacity=n_requests + 8)
+
+
+def drive(eng_mod, model, eng, w, reqs):
+    """Submits the requests the way the workload says and yields after every scheduler tick.
+    - one atomic batch (configurations 1, 2, 4);
+    - prefix reuse (configuration 3): request 0 alone until it has finished, then the others in submission order;
+    - Poisson arrivals (configuration 5): a request is submitted once the step's clock has passed its arrival time; the
+      clock is the wall time since the step began, and it jumps to the next arrival whenever the engine would idle, so
+      that a step measures service, not waiting."""
+    prompts, new, arrivals = reqs
+    mk = lambda i: eng_mod.Request(prompts[i], new[i])
+    ids = []
+    if w.arrival_rate > 0:
+        t0, skipped, nxt = time.perf_counter(), 0.0, 0
+        while nxt < len(prompts) or eng.pending() > 0:
+            now = time.perf_counter() - t0 + skipped
+            if eng.pending() == 0 and nxt < len(prompts) and arrivals[nxt] > now:
+                skipped += arrivals[nxt] - now
+                now = arrivals[nxt]
+            wave = []
+            while nxt < len(prompts) and arrivals[nxt] <= now:
+                wave.append(mk(nxt))
+                nxt += 1
+            if wave:
+                ids += eng.submit(wave)
+            yield eng.step()
+    else:
+        waves = [(0, 1, False), (1, len(prompts), False)] if w.shared_prefix else [(0, len(prompts), True)]
+        for lo, hi, atomic in waves:
+            if hi <= lo:
+                continue
+            ids += eng.submit([mk(i) for i in range(lo, hi)], atomic_batch=atomic)
+            while eng.pending() > 0:
+                yield eng.step()
+    drive.last_ids = ids
+
+
+def run_step(eng_mod, model, w, reqs, active: int):
+    """One step: the whole workload through a fresh engine.  Returns (tokens, wall s, engine stats, prefix diagnostics)."""
+    prompts, new, _ = reqs
+    eng = new_engine(eng_mod, model, w, active, len(prompts))
     model.synchronize()
     t0 = time.perf_counter()
-    ids = eng.submit(reqs, atomic_batch=True)
-    eng.run()
+    for _ in drive(eng_mod, model, eng, w, reqs):
+        pass
     model.synchronize()
     wall = time.perf_counter() - t0
     st = eng.stats()
     toks = sum(len(p) for p in prompts)
     gen = 0
-    for i in ids:
+    for i in drive.last_ids:
         r = eng.result(i)
         if r["state"] != "done":
             raise RuntimeError(f"request {i} ended in state {r['state']}: {r['message']}")
         gen += len(r["tokens"])
+        toks -= r["cached_tokens"]          # prompt tokens served from the prefix cache were not computed
+    diag = model.prefix_diagnostics() if w.prefix_capacity_tokens else None
     eng.close()
-    return toks + gen, wall, st
+    return toks + gen, wall, st, diag
 
 
-def tick_classes(eng_mod, model, w, prompts, weight_bytes_per_pass: float, kv_bytes_per_token: float, hbm_gbs: float) -> dict:
+def tick_classes(eng_mod, model, w, reqs, active: int, weight_bytes_per_pass: float, kv_bytes_per_token: float, hbm_gbs: float,
+                 window_layers: tuple = (0, 0, 0)) -> dict:
     """One more (untimed) step driven tick by tick: device time and algorithmic HBM bytes per tick class.
-    A tick's algorithmic bytes = the weight bytes one pass touches + the K/V history its lanes attend to;
-    `hbm_frac` = those bytes / device time / measured copy bandwidth (the decode roofline of the metric)."""
-    eng = eng_mod.Engine(model, max_active_sequences=w["seqs"], scheduler_token_budget=w["budget"],
-                         prefill_token_quantum=w["quantum"], queue_capacity=w["seqs"] + 8)
-    eng.submit([eng_mod.Request(p, w["new_tokens"]) for p in prompts], atomic_batch=True)
+    A tick's algorithmic bytes = the weight bytes one pass touches + the K/V history its lanes attend to (sliding-window
+    layers count at most `window` tokens); `hbm_frac` = those bytes / device time / measured copy bandwidth - the decode
+    roofline of the metric."""
+    prompts, new, _ = reqs
+    eng = new_engine(eng_mod, model, w, active, len(prompts))
     ms = []
-    while eng.pending() > 0:
-        before = model.launch_count()
-        eng.step()
+    before = model.launch_count()
+    for _ in drive(eng_mod, model, eng, w, reqs):
         if model.launch_count() != before:  # a step that only delivers events runs no forward pass
             ms.append(model.last_forward_ms())
+        before = model.launch_count()
     trace = eng.trace()
     eng.close()
+    n_sliding, n_layers, window = window_layers
     out = {}
     for t, dev_ms in zip(trace, ms):
         toks = sum(n for _, _, n in t)
         if toks == 0:
             continue
         cls = "decode" if toks == len(t) else ("mixed" if any(n == 1 for _, _, n in t) else "prefill")
-        kv = sum(sp + n for _, sp, n in t) * kv_bytes_per_token
-        a = out.setdefault(cls, dict(ticks=0, tokens=0, ms=0.0, bytes=0.0))
+        kv = 0.0
+        for _, sp, n in t:
+            ctx = sp + n
+            if n_sliding:
+                kv += kv_bytes_per_token / n_layers * ((n_layers - n_sliding) * ctx + n_sliding * min(ctx, window + n))
+            else:
+                kv += kv_bytes_per_token * ctx
+        a = out.setdefault(cls, dict(ticks=0, tokens=0, lanes=0, ms=0.0, bytes=0.0))
         a["ticks"] += 1
         a["tokens"] += toks
+        a["lanes"] += len(t)
         a["ms"] += dev_ms
         a["bytes"] += weight_bytes_per_pass + kv
     for a in out.values():
         a["tokens_per_s"] = round(a["tokens"] / max(a["ms"], 1e-9) * 1e3, 1)
         a["ms_per_tick"] = round(a["ms"] / a["ticks"], 3)
+        a["lanes_per_tick"] = round(a["lanes"] / a["ticks"], 1)
+        a["gbs"] = round(a["bytes"] / max(a["ms"], 1e-9) / 1e6, 1)
         a["hbm_frac"] = round(a["bytes"] / max(a["ms"], 1e-9) / 1e6 / hbm_gbs, 4)
         a["ms"] = round(a["ms"], 2)
-        del a["bytes"]
+        del a["bytes"], a["lanes"]
     return out
 
 
@@ -282,29 +325,84 @@ def microbench() -> None:
         print(json.dumps(line), flush=True)
 
 
-def cpu_baseline(w, path, budget_s: float, seqs_sample: int = 4) -> dict:
-    """The oracle (a port of the reference's CPU path) on a bounded sample of the same workload: the
-    first prefill tokens of the first sequences, one scheduler tick, all host threads."""
+def cpu_model_name() -> str:
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("model name"):
+                return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown CPU"
+
+
+def cpu_baseline(w, path, budget_s: float, threads: int) -> dict:
+    """The oracle (a port of the reference's CPU path: no Rust toolchain here to build the reference itself) on a bounded
+    sample of the same workload: the first S sequences with 4 new tokens each through the oracle's own scheduler with the
+    workload's quantum and budget - prefill ticks, mixed ticks and at least three decode ticks - on `threads` OpenMP
+    threads.  S is the largest number of sequences whose prompts fit the time budget at the rate of a short probe."""
     from oracle import decoder, engine as oe, mathlib
     mathlib.build()
+    mathlib.set_num_threads(threads)
+    wl = workloads_module()
     t0 = time.time()
     dec = decoder.Decoder(path, kv_dtype="f32", matmul_mode=1)
     load_s = time.time() - t0
-    prompts = make_prompts(w, dec.vocab, 0)
-    # calibrate on a short tick, then size the sample to the time budget
-    def tick(n_tokens: int) -> float:
-        om = oe.OracleModel(dec.vocab, dec.max_context, 16, 8, max(n_tokens + 64, 1024), 0, decoder=dec)
-        s = om.new_session()
-        ids = [int(x) for x in np.concatenate(prompts)[:n_tokens]]
-        r = om.reserve_batch([(s, 0, len(ids))])
-        t = time.time()
-        om.forward([(s, ids, 0)], r)
-        return time.time() - t
-    probe = tick(8)
-    n = int(max(8, min(512, budget_s / max(probe / 8, 1e-6))))
-    dt = tick(n)
-    return dict(value=n / dt, unit=UNIT, cores=mathlib.num_threads(), kind="port",
-                sample=f"one prefill tick of {n} tokens of sequence 0 ({dt:.1f}s; checkpoint load {load_s:.1f}s not counted)")
+    prompts, _, _ = wl.make_requests(w, dec.vocab, 0)
+    # probe: a 16-token prefill
+    om = oe.OracleModel(dec.vocab, dec.max_context, 16, 8, 1024, 0, decoder=dec)
+    s = om.new_session()
+    ids = [int(x) for x in prompts[0][:16]]
+    t = time.time()
+    om.forward([(s, ids, 0)], om.reserve_batch([(s, 0, len(ids))]))
+    rate = len(ids) / max(time.time() - t, 1e-6)
+    S, total = 0, 0
+    order = sorted(range(len(prompts)), key=lambda i: len(prompts[i])) if w.shared_prefix == 0 else list(range(len(prompts)))
+    chosen = []
+    for i in order:
+        if chosen and (total + len(prompts[i])) / rate > budget_s:
+            break
+        chosen.append(i)
+        total += len(prompts[i])
+        if len(chosen) >= 8:
+            break
+    sample = [[int(x) for x in prompts[i]] for i in chosen]
+    if total / rate > 2.5 * budget_s:   # even one prompt is too long for the budget: its head
+        keep = max(32, int(budget_s * rate))
+        sample = [sample[0][:keep]]
+    new = 4
+    cap = sum(len(p) + new + 32 for p in sample)
+    om = oe.OracleModel(dec.vocab, dec.max_context, 16, 8, cap, 0, decoder=dec)
+    e = oe.OracleEngine(om, max_active_sequences=max(len(sample), 1), scheduler_token_budget=w.budget, prefill_token_quantum=w.quantum,
+                        queue_capacity=len(sample) + 8)
+    e.submit([oe.Req(p, new) for p in sample], atomic_batch=True)
+    t = time.time()
+    e.run()
+    dt = time.time() - t
+    ticks = e.trace
+    decode_ticks = sum(1 for tk in ticks if all(n == 1 for _, _, n in tk))
+    tokens = sum(len(p) for p in sample) + new * len(sample)
+    return dict(value=tokens / dt, unit=UNIT, cores=mathlib.num_threads(), kind="port", cpu=cpu_model_name(),
+                sample=f"the {len(sample)} shortest sequences of the workload ({sum(len(p) for p in sample)} prompt tokens), {new} new tokens each, "
+                       f"quantum {w.quantum}, budget {w.budget}: {len(ticks)} ticks of which {decode_ticks} decode ticks, {dt:.1f}s "
+                       f"(checkpoint load {load_s:.1f}s not counted)")
+
+
+def q4k_gemv_block(hbm_gbs: float) -> dict:
+    """The metric's second half: Q4_K matrix-vector products of the decode path (integer block dots, 1 and 8 activation
+    rows) on the gate/up shape of configuration 2 and the feed-forward shape of configuration 3: achieved GB/s on the
+    bytes of the matrix, operands resident, L2 flushed before every launch, CUDA events around the launch."""
+    ops = importlib.import_module("macllm_infer_b200.ops")
+    capi = importlib.import_module("macllm_infer_b200._capi")
+    rng = np.random.default_rng(0)
+    out = {}
+    for rows, cols in ((11008, 2048), (12288, 4096)):
+        wq = ops.seed_tensor(0, 1, 0.02, capi.TYPE_Q4_K, rows, cols)
+        nbytes = rows * cols * 144 // 256
+        for T in (1, 8):
+            x = rng.standard_normal((T, cols)).astype(np.float32)
+            ms = ops.qmatmul_time(capi.TYPE_Q4_K, wq, rows, cols, x, capi.PATH_GEMV, 10)
+            out[f"{rows}x{cols}_T{T}"] = dict(us=round(ms * 1e3, 1), gbs=round(nbytes / ms / 1e6, 1), frac=round(nbytes / ms / 1e6 / hbm_gbs, 4))
+    return out
 
 
 def main():
@@ -313,29 +411,39 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="smollm3-3b-ragged64", choices=list(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=WORKLOAD_NAMES)
     ap.add_argument("--matmul-path", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     # a shorter slice of the same workload for profiler captures (a number printed by such a run is not a bench value)
     ap.add_argument("--new-tokens", type=int, default=0, help="override the generated tokens per sequence")
+    ap.add_argument("--limit-requests", type=int, default=0, help="only the first N requests of the workload (per replica)")
+    ap.add_argument("--kv-budget-gb", type=float, default=110.0, help="largest KV arena; the active set shrinks until it fits")
     ap.add_argument("--no-profiled-step", action="store_true", help="skip the extra step that times every launch")
     ap.add_argument("--microbench", action="store_true", help="Q4_K matmul GB/s on the decode shapes instead of the workload")
     args = ap.parse_args()
-    w = dict(WORKLOADS[args.workload])
-    if args.new_tokens > 0:
-        w["new_tokens"] = args.new_tokens
 
     rank, local, world, dist = dist_setup(args.gpus)
-    entry.load_package()
+    wl = workloads_module()
+    w = wl.WORKLOADS[args.workload]
+    if args.new_tokens > 0:
+        from dataclasses import replace
+        w = replace(w, new_tokens=args.new_tokens)
     if rank == 0:
         entry.ensure_built()
     barrier(dist)
     seed = importlib.import_module("macllm_infer_b200.seed_gguf")
-    spec = seed.CONFIGS[w["config"]]
-    config = dict(workload=args.workload + (f" (slice: {w['new_tokens']} new tokens)" if args.new_tokens > 0 else ""), model_shape=w["config"], sequences_per_gpu=w["seqs"], new_tokens=w["new_tokens"],
-                  prefill_quantum=w["quantum"], scheduler_token_budget=w["budget"], kv="f16 paged, 16-token blocks",
+    spec = seed.CONFIGS[w.config]
+    wb = seed.weight_bytes(spec)
+    kv_per_token = 2 * spec.layers * spec.kv_heads * spec.head_dim * 2
+    sliced = args.new_tokens > 0 or args.limit_requests > 0
+    config = dict(workload=args.workload + (" (slice)" if sliced else ""), model_shape=w.config, requests_per_gpu=w.seqs if args.limit_requests <= 0 else min(w.seqs, args.limit_requests),
+                  new_tokens=w.new_tokens, prefill_quantum=w.quantum, scheduler_token_budget=w.budget, kv="f16 paged, 16-token blocks",
                   quant="Q4_K_M-shaped GGUF (Q4_K, Q6_K for attn_v and output)", parallelism=f"replicas x{world}",
-                  l2="inputs larger than L2 (weights %.2f GB per pass)" % (seed.weight_bytes(spec)["per_token"] / 1e9))
+                  l2="inputs larger than L2 (weights %.2f GB per pass)" % (wb["per_token"] / 1e9))
+    if w.shared_prefix:
+        config.update(shared_prefix_tokens=w.shared_prefix, prefix_capacity_tokens=w.prefix_capacity_tokens)
+    if w.arrival_rate:
+        config.update(arrivals=f"Poisson {w.arrival_rate:g} requests/s, replayed from a seeded list; the clock skips idle time")
 
     if args.microbench:
         if rank == 0:
@@ -343,23 +451,25 @@ def main():
         return
 
     if args.impl == "reference":
-        # The reference is Rust on candle and cannot be built here (no cargo/rustc): the reference arm
-        # is the CPU oracle, the port of its CPU path, on a bounded sample per step.
+        # The reference is Rust on candle and cannot be built here (no cargo/rustc): the reference arm is the CPU oracle,
+        # the port of its CPU path, on a bounded sample per step, on every host core (rank 0 alone runs under torchrun,
+        # which exports OMP_NUM_THREADS=1: the thread count is set explicitly).
         if rank != 0:
             return
-        path = ensure_checkpoint(w)
+        path = ensure_checkpoint(w.config)
+        threads = os.cpu_count() or 1
         budget = max(4.0, 150.0 / max(args.steps + args.warmup, 1))
         vals = []
         for i in range(args.warmup + args.steps):
-            b = cpu_baseline(w, path, budget)
+            b = cpu_baseline(w, path, budget, threads)
             if i >= args.warmup:
                 vals.append(b)
         v = float(np.mean([b["value"] for b in vals])) if vals else 0.0
-        b = vals[-1] if vals else dict(cores=0, sample="none", kind="port")
+        b = vals[-1] if vals else dict(cores=0, sample="none", kind="port", cpu=cpu_model_name())
         out = dict(metric=METRIC, value=v, unit=UNIT, n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
                    ms_per_step=None, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="int8 x int4/6 block dots, f32 accumulate",
                    data="synthetic", config=config, impl="reference",
-                   cpu_baseline=dict(value=v, unit=UNIT, cores=b["cores"], kind=b["kind"], sample=b["sample"]),
+                   cpu_baseline=dict(value=v, unit=UNIT, cores=b["cores"], kind=b["kind"], cpu=b["cpu"], sample=b["sample"]),
                    e2e=dict(value=v, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0))
         print(json.dumps(out))
         return
@@ -369,16 +479,25 @@ def main():
     if capi.lib().mk_device_count() <= 0:
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU fallback")
     if rank == 0:
-        path = ensure_checkpoint(w)
+        ensure_checkpoint(w.config)
     barrier(dist)
-    path = checkpoint_path(w)
+    path = checkpoint_path(w.config)
 
-    prompts = make_prompts(w, spec.vocab, rank)
-    max_len = max(len(p) for p in prompts) + w["new_tokens"]
-    model = eng_mod.Model.load_gguf(path, device=local, kv_capacity_tokens=w["seqs"] * ((max_len + 15) // 16 * 16 + 16), kv_dtype="f16",
-                                    max_batch_tokens=w["budget"], max_batch_lanes=w["seqs"], matmul_path=args.matmul_path)
+    reqs = wl.make_requests(w, spec.vocab, rank, args.limit_requests)
+    prompts, new, _ = reqs
+    # the KV arena holds the active set at its longest; when that exceeds the budget the active set shrinks
+    active = min(w.max_active(), len(prompts))
+    def arena_tokens(a):
+        longest = sorted(((len(p) + k + 31) // 16 * 16 + 16 for p, k in zip(prompts, new)), reverse=True)
+        return sum(longest[:a]) + w.prefix_capacity_tokens
+    while active > 1 and arena_tokens(active) * kv_per_token > args.kv_budget_gb * 1e9:
+        active = active * 3 // 4
+    cap = arena_tokens(active)
+    config.update(active_sequences=active, kv_arena_gb=round(cap * kv_per_token / 1e9, 2))
+    model = eng_mod.Model.load_gguf(path, device=local, kv_capacity_tokens=cap, kv_dtype="f16", prefix_capacity_tokens=w.prefix_capacity_tokens,
+                                    max_batch_tokens=w.budget, max_batch_lanes=active, matmul_path=args.matmul_path)
     for _ in range(args.warmup):
-        run_step(eng_mod, model, w, prompts)
+        run_step(eng_mod, model, w, reqs, active)
     sampler = ClockSampler(local)
     barrier(dist)
     if rank == 0:
@@ -388,9 +507,10 @@ def main():
     tokens = 0
     dev_ms = 0.0
     ticks = 0
+    diag = None
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        n, wall, st = run_step(eng_mod, model, w, prompts)
+        n, wall, st, diag = run_step(eng_mod, model, w, reqs, active)
         tokens += n
         dev_ms += st["device_ms"]
         ticks += st["ticks"]
@@ -403,16 +523,15 @@ def main():
     wall_max = all_max(dist, wall_total)
     dev_max = all_max(dist, dev_ms / 1e3)
     tokens_all = all_sum(dist, float(tokens))
+    pk = peaks()
 
     # one extra profiled step: CUDA events around every launch, per kernel class
     roof = None
-    prof_rows = []
     if rank == 0 and not args.no_profiled_step:
         model.profile_enable(True)
-        run_step(eng_mod, model, w, prompts)
+        run_step(eng_mod, model, w, reqs, active)
         prof_rows = model.profile_query()
         model.profile_enable(False)
-        pk = peaks()
         total_ms = sum(r["ms"] for r in prof_rows) or 1.0
         top = max(prof_rows, key=lambda r: r["ms"])
         intensity = top["flops"] / max(top["bytes"], 1.0)
@@ -435,26 +554,35 @@ def main():
 
     classes = None
     if rank == 0 and not args.no_profiled_step:
-        wb = seed.weight_bytes(spec)
-        classes = tick_classes(eng_mod, model, w, prompts, float(wb["per_token"]), float(model.spec().kv_bytes_per_token),
-                               peaks()["hbm_gbs"])
+        sliding = (spec.layers // 2, spec.layers, spec.window) if spec.arch == "gemma2" else (0, 0, 0)
+        weights_pass = float(wb["per_token"]) if spec.experts == 0 else float(wb.get("all_experts", wb["per_token"]))
+        classes = tick_classes(eng_mod, model, w, reqs, active, weights_pass, float(model.spec().kv_bytes_per_token), pk["hbm_gbs"], sliding)
+        if roof is not None and "decode" in classes:
+            # the decode roofline of the metric: weight + K/V bytes of a tick over its device time
+            d = classes["decode"]
+            roof["decode_tick"] = dict(achieved=d["gbs"], peak=pk["hbm_gbs"], unit="GB/s", frac=d["hbm_frac"], ms_per_tick=d["ms_per_tick"],
+                                       lanes_per_tick=d["lanes_per_tick"])
+        if roof is not None:
+            roof["q4k_gemv"] = q4k_gemv_block(pk["hbm_gbs"])
 
     base = None
     if rank == 0 and not args.no_cpu_baseline:
         try:
-            base = cpu_baseline(w, path, 15.0)
+            base = cpu_baseline(w, path, 15.0, max(1, (os.cpu_count() or 1)))
         except Exception as e:  # the baseline is a report, never a reason to lose the measurement
             base = dict(value=None, unit=UNIT, cores=None, kind="port", sample=f"failed: {e}")
 
     if rank == 0:
         out = dict(metric=METRIC, value=tokens_all / dev_max, unit=UNIT, n_gpus=world, steps=args.steps, warmup=args.warmup,
                    ms_per_step=wall_max * 1e3 / max(args.steps, 1), higher_is_better=True, scaling="weak", vs_baseline=None,
-                   dtype="f16 tensor cores over exact Q4_K integers or f16 weight images (>= 9 rows), int8 x int4/6 block dots (<= 8 rows), f32 accumulate, f16 KV",
+                   dtype="f16 tensor cores over f16 weights dequantised in flight (2..64 rows) or f16 weight images (wider ticks), int8 x int4/6 block dots (1 row), f32 accumulate, f16 KV",
                    data="synthetic", config=config, clocks=clocks,
                    e2e=dict(value=tokens_all / wall_max, unit=UNIT, h2d_bytes_per_step=(h2d1 - h2d0) // max(args.steps, 1),
                             d2h_bytes_per_step=(d2h1 - d2h0) // max(args.steps, 1)),
                    gpu_launches=launches, ticks_per_step=ticks // max(args.steps, 1), roofline=roof, tick_classes=classes,
                    cpu_baseline=base)
+        if diag is not None:
+            out["prefix_cache"] = diag
         print(json.dumps(out))
     model.close()
     if dist is not None:

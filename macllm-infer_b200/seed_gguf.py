@@ -252,7 +252,7 @@ def write_seed_gguf_shards(directory: str | Path, prefix: str, spec: SeedSpec, s
 
 def weight_bytes(spec: SeedSpec) -> dict:
     """Algorithmic byte counts of the checkpoint: all matrices, and what one decode row touches."""
-    total = per_token = 0
+    total = per_token = all_experts = 0
     for name, dims, qtype, std in tensor_plan(spec):
         if len(dims) < 2:
             continue
@@ -260,9 +260,12 @@ def weight_bytes(spec: SeedSpec) -> dict:
         total += n
         if "_exps" in name:
             per_token += n // spec.experts * spec.experts_used
+            all_experts += n
         elif name == "token_embd.weight" and not spec.tied:
             pass  # only a row gather touches it
         else:
             per_token += n
+            all_experts += n
     kv_per_token = 2 * spec.layers * spec.kv_heads * spec.head_dim * 2
-    return {"total": total, "per_token": per_token, "kv_f16_per_token": kv_per_token}
+    # all_experts: what a decode tick touches once its lanes hit every expert (a batch of some 64 lanes and more)
+    return {"total": total, "per_token": per_token, "all_experts": all_experts, "kv_f16_per_token": kv_per_token}

@@ -60,6 +60,11 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def set_num_threads(n: int) -> None:
+    """Threads of the oracle's OpenMP loops from now on (torchrun exports OMP_NUM_THREADS=1)."""
+    lib().orc_set_num_threads(int(n))
+
+
 def dequant(t: int, w: np.ndarray, rows: int, cols: int) -> np.ndarray:
     w = np.ascontiguousarray(w)
     out = np.empty((rows, cols), dtype=np.float32)

@@ -530,6 +530,15 @@ int64_t orc_argmax(const float* v, int64_t n) {
     return best;
 }
 
+// Threads the OpenMP loops of this library use from now on (launchers such as torchrun export OMP_NUM_THREADS=1).
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int orc_num_threads() {
 #ifdef _OPENMP
     return omp_get_max_threads();

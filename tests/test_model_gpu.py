@@ -1,6 +1,9 @@
 """End-to-end parity of the B200 model + engine against the CPU oracle on seed checkpoints of every
-supported family (needs a GPU).  Block tables, prefix-cache counters and schedules must be identical;
-greedy tokens are compared and logits are held to max-abs 2e-2 / cosine 0.9995."""
+supported family (needs a GPU).  Block tables, prefix-cache counters and schedules must be identical.
+Logits are held to the bound compare() asserts: max-abs within 3x the envelope measured on the same inputs (the
+distance between two evaluation orders of the reference arithmetic itself, oracle mode 1 against mode 3), never above
+0.25, cosine >= 0.999; a divergence of greedy tokens must be a near-tie of the oracle's own logits.  One-layer models,
+where no rounding flip can avalanche, must agree to 2e-5."""
 import importlib
 
 import numpy as np

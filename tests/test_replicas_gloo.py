@@ -20,16 +20,15 @@ CHILD = textwrap.dedent("""
     entry.load_package()
     eng = importlib.import_module("macllm_infer_b200.engine")
     rank, local, world, dist = bench.dist_setup(2, backend="gloo")
-    w = dict(seed=77, seqs=6, prompt=(5, 40), new_tokens=7)
-    prompts = bench.make_prompts(w, 32, rank)
+    wl = bench.workloads_module()
+    w = wl.Workload("gloo-test", "none", 6, 7, 16, 64, 77, prompt=(5, 40))
+    reqs = wl.make_requests(w, 32, rank)
+    prompts = reqs[0]
     model = eng.Model.fake(vocab=32, max_context=256, kv_capacity_tokens=1024)
-    e = eng.Engine(model, max_active_sequences=6, scheduler_token_budget=64, prefill_token_quantum=16, queue_capacity=16)
     bench.barrier(dist)
-    t0 = time.perf_counter()
-    ids = e.submit([eng.Request(p, w["new_tokens"]) for p in prompts], atomic_batch=True)
-    e.run()
-    seconds = time.perf_counter() - t0 + 0.01 * (rank + 1)   # rank 1 is the slowest by construction
-    tokens = sum(len(p) for p in prompts) + sum(len(e.result(i)["tokens"]) for i in ids)
+    tokens, seconds, st, _ = bench.run_step(eng, model, w, reqs, 6)   # the benchmark's own step driver
+    seconds += 0.01 * (rank + 1)   # rank 1 is the slowest by construction
+    assert tokens == sum(len(p) for p in prompts) + 6 * 7 and st["completed_requests"] == 6
     bench.barrier(dist)
     total, slowest, rate = bench.aggregate(dist, tokens, seconds)
     print(json.dumps(dict(rank=rank, world=world, tokens=tokens, seconds=seconds, total=total, slowest=slowest, rate=rate,
