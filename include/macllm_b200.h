@@ -79,6 +79,10 @@ typedef struct mk_load_config {
      * [ep_rank, ep_rank + 1) * expert_count / ep_size.  ep_size 0 or 1: every expert is loaded here. */
     int32_t ep_rank;
     int32_t ep_size;
+    /* 0: every rank runs the same ticks on the same tokens and the per-layer partial sums are exchanged; 1: every rank
+     * schedules its own sequences (data-parallel lanes) and each MoE layer sends the routed token rows to the rank that
+     * holds the expert and the outputs back (dispatch / combine all-to-all over NVLink peer memory). */
+    int32_t ep_mode;
 } mk_load_config;
 
 /* CausalLm::runtime_spec (src/architecture.rs:312-316,1039). */
@@ -155,6 +159,11 @@ int32_t mk_model_new_fake(int32_t vocab, int32_t max_context, const mk_load_conf
  * a model loaded from a file. */
 int32_t mk_model_fake_inject(mk_model* m, int32_t site, int64_t index);
 int32_t mk_model_free(mk_model* m);
+/* ep_mode 1 only.  The ranks of an expert-parallel group tick in lock step: each MoE layer of each forward is one
+ * exchange that all ranks take part in.  A rank whose scheduler has no lane to run in a tick calls this instead of a
+ * forward: it serves the other ranks' rows on its experts and contributes none of its own.  Returns without waiting
+ * (the work is queued on the model's stream; the next mk_read_output / mk_synchronize covers it). */
+int32_t mk_model_ep_idle_tick(mk_model* m);
 /* Expert parallelism, one process per GPU.  Rank 0 calls mk_ep_unique_id (MK_EP_ID_BYTES bytes out) and passes the
  * id to the other ranks out of band; then every rank calls mk_model_ep_init on its model (loaded with the same
  * ep_size and its own ep_rank) - a collective that returns once all ranks have joined.  From then on every rank must
@@ -494,6 +503,15 @@ typedef struct mk_attn_case {
 } mk_attn_case;
 int32_t mk_k_attention_step(const mk_attn_case* c);
 
+/* The expert matmuls of SparseMoeFeedForward::forward (src/decoder.rs:394-441): w is a bank of `experts` matrices
+ * [rows_pe][cols] of GGUF blocks of `type`, back to back; x [P][cols] holds the routed rows grouped by expert, rows
+ * [offsets[e], offsets[e + 1]) going to expert e (offsets: experts + 1 ints); y [P][rows_pe].  path MK_PATH_GEMV: the
+ * integer block dots; MK_PATH_STREAM: the tensor-core kernel of the decode ticks in its expert-grouped form (Q4_K / Q6_K,
+ * rows_pe a multiple of 128).  up_w non-NULL (MK_PATH_STREAM only): w holds the gate matrices, up_w the up matrices, and
+ * y [P][rows_pe] receives act(gate . x) * (up . x), act 0 SiLU / 1 tanh GELU, rounded through f16. */
+int32_t mk_k_grouped_qmatmul(int32_t type, const void* w, const void* up_w, int32_t experts, int64_t rows_pe, int64_t cols, const float* x,
+                             const int32_t* offsets, float* y, int32_t path, int32_t act);
+
 /* Host-only: how one matmul launch is cut into work items.  path MK_PATH_HALF: out = {token-tile width, row tiles, token
  * tiles, K shares, K blocks (of 64) per share, floats of partial sums, 0, 0}; path MK_PATH_STREAM (T <= 64): out =
  * {token-tile width, row tiles, (group of row tiles, 256-column block) items, persistent CTAs, partial-sum slots, floats
@@ -509,12 +527,23 @@ int32_t mk_k_attention_plan(const int32_t* start_pos, const int32_t* n_tokens, i
 
 /* argmax of src/sampling.rs:425-433 for each row of logits [B][vocab]. */
 int32_t mk_k_argmax(const float* logits, int32_t B, int32_t vocab, uint32_t* out);
-/* Sampler::sample_with_generated without penalties (src/sampling.rs:95-169,337-390) on rows of logits [B][vocab] (host
- * memory), one setting per row.  where = 0: this library's host sampler (any top_k; needs no GPU); where = 1: the device
- * kernel (greedy rows, or 1 <= top_k <= 1024).  Both use the same arithmetic and return the same tokens. */
+/* Test support for expert parallelism with data-parallel lanes: the dispatch / regroup / return / wait kernels of all
+ * `ranks` ranks run on ONE device, stage by stage on one stream (every flag a kernel waits for was published by an earlier
+ * launch), with `out = row * (global expert + 1)` standing in for the expert matmuls.  rows: f16 [ranks][cap_rows][hidden],
+ * each rank's routed rows grouped by expert; offsets: [ranks][ranks * local_experts + 1].  results: f32
+ * [ranks][cap_rows][hidden], each rank's result area after the last of `exchanges` consecutive exchanges;
+ * merged_ranges [ranks][local_experts + 1]; status [ranks].  silent_rank >= 0: that rank takes no part, the others' waits
+ * run out after wait_ns nanoseconds and report 0x4550000 | silent_rank in their status (nothing is returned). */
+int32_t mk_k_ep_exchange_emulated(int32_t ranks, int32_t local_experts, int32_t hidden, int32_t cap_rows, const uint16_t* rows,
+                                  const int32_t* offsets, int32_t exchanges, int32_t silent_rank, int64_t wait_ns, float* results,
+                                  int32_t* merged_ranges, int32_t* status);
+
 /* apply_repetition_penalty + apply_openai_penalties (src/sampling.rs:392-423) on one row, in place (host only). */
 int32_t mk_k_penalties(float* logits, int32_t vocab, const uint32_t* history, int32_t n_history, float repetition_penalty,
                        const uint32_t* generated, int32_t n_generated, float presence_penalty, float frequency_penalty);
+/* Sampler::sample_with_generated without penalties (src/sampling.rs:95-169,337-390) on rows of logits [B][vocab] (host
+ * memory), one setting per row.  where = 0: this library's host sampler (any top_k; needs no GPU); where = 1: the device
+ * kernel (greedy rows, or 1 <= top_k <= 1024).  Both use the same arithmetic and return the same tokens. */
 int32_t mk_k_sample(const float* logits, int32_t B, int32_t vocab, const mk_lane_sampling* settings, int32_t where, uint32_t* out);
 
 /* selected_softmax_routes (src/decoder.rs:448-554): sel_experts / sel_weights are [T][k], best first. */

@@ -30,7 +30,7 @@ class LoadConfig(C.Structure):
     _fields_ = [("device_ordinal", C.c_int32), ("block_tokens", C.c_int32), ("slab_blocks", C.c_int32),
                 ("kv_capacity_tokens", C.c_int64), ("prefix_capacity_tokens", C.c_int64), ("kv_dtype", C.c_int32),
                 ("max_batch_tokens", C.c_int32), ("max_batch_lanes", C.c_int32), ("matmul_path", C.c_int32),
-                ("ep_rank", C.c_int32), ("ep_size", C.c_int32)]
+                ("ep_rank", C.c_int32), ("ep_size", C.c_int32), ("ep_mode", C.c_int32)]
 
 
 class GgufSummary(C.Structure):
@@ -126,6 +126,8 @@ SIGNATURES = {
     "mk_model_load_gguf": (_i32, [C.c_char_p, C.POINTER(LoadConfig), C.POINTER(P)]),
     "mk_model_new_fake": (_i32, [_i32, _i32, C.POINTER(LoadConfig), _i64, C.POINTER(P)]),
     "mk_model_fake_inject": (_i32, [P, _i32, _i64]),
+    "mk_model_ep_idle_tick": (_i32, [P]),
+    "mk_k_ep_exchange_emulated": (_i32, [_i32, _i32, _i32, _i32, P, P, _i32, _i32, _i64, P, P, P]),
     "mk_model_free": (_i32, [P]),
     "mk_gguf_inspect": (_i32, [C.c_char_p, C.POINTER(GgufSummary)]),
     "mk_ep_unique_id": (_i32, [P]),
@@ -202,6 +204,7 @@ SIGNATURES = {
     "mk_k_gated_ffn": (_i32, [_i32, P, P, _i64, _i64, P, _i32, _i32, P, _i32, P]),
     "mk_k_attention_step": (_i32, [C.POINTER(AttnCase)]),
     "mk_k_argmax": (_i32, [P, _i32, _i32, P]),
+    "mk_k_grouped_qmatmul": (_i32, [_i32, P, P, _i32, _i64, _i64, P, P, P, _i32, _i32]),
     "mk_k_sample": (_i32, [P, _i32, _i32, P, _i32, P]),
     "mk_k_penalties": (_i32, [P, _i32, P, _i32, C.c_float, P, _i32, C.c_float, C.c_float]),
     "mk_forward_set_sampling": (_i32, [P, P, _i32]),

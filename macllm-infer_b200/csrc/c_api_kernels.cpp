@@ -505,6 +505,161 @@ int32_t mk_k_argmax(const float* logits, int32_t B, int32_t vocab, uint32_t* out
     });
 }
 
+int32_t mk_k_grouped_qmatmul(int32_t type, const void* w, const void* up_w, int32_t experts, int64_t rows_pe, int64_t cols, const float* x,
+                             const int32_t* offsets, float* y, int32_t path, int32_t act) {
+    return guarded([&] {
+        require_device();
+        if (experts <= 0 || rows_pe <= 0 || cols <= 0 || offsets == nullptr) throw std::runtime_error("mk_k_grouped_qmatmul: bad arguments");
+        const int P = offsets[experts];
+        int most = 0;
+        for (int e = 0; e < experts; ++e) {
+            if (offsets[e + 1] < offsets[e]) throw std::runtime_error("mk_k_grouped_qmatmul: row ranges must not decrease");
+            most = std::max(most, offsets[e + 1] - offsets[e]);
+        }
+        if (P <= 0) return;
+        const bool gated = up_w != nullptr;
+        if (gated && path != MK_PATH_STREAM) throw std::runtime_error("mk_k_grouped_qmatmul: the gated form exists on the streamed path only");
+        const int64_t rb = gguf_row_bytes(type, cols);
+        DeviceWeight bank;
+        if (!gated) {
+            upload_weight(type, w, rows_pe * experts, cols, bank);
+        } else {
+            // [gate bank; up bank] in one buffer, as the model stacks them
+            std::vector<uint8_t> both((size_t)(2 * rows_pe * experts * rb));
+            memcpy(both.data(), w, both.size() / 2);
+            memcpy(both.data() + both.size() / 2, up_w, both.size() / 2);
+            upload_weight(type, both.data(), 2 * rows_pe * experts, cols, bank);
+        }
+        int kind = act_kind_for(type);
+        DevBuf dx((size_t)P * cols * 4), dy((size_t)P * rows_pe * 4), doff((size_t)(experts + 1) * 4), status(4);
+        dx.upload(x, (size_t)P * cols * 4);
+        doff.upload(offsets, (size_t)(experts + 1) * 4);
+        status.zero(nullptr);
+        ActBufs ab;
+        ActQ a = ab.view(P, (int)cols, kind, path == MK_PATH_STREAM, false);
+        NormQuantArgs na;
+        na.h = dx.as<float>();
+        na.rows = P;
+        na.dim = (int)cols;
+        na.act_kind = kind;
+        na.out = a;
+        launch_add_norm_quant(na, nullptr);
+        if (path == MK_PATH_GEMV) {
+            QWeight one = bank.w;
+            one.rows = rows_pe;
+            launch_qgemv_grouped(one, experts, doff.as<int32_t>(), nullptr, a, dy.as<float>(), (int)rows_pe, nullptr);
+        } else if (path == MK_PATH_STREAM) {
+            if (type != MK_TYPE_Q4_K && !(type == MK_TYPE_Q6_K && !gated)) throw std::runtime_error("mk_k_grouped_qmatmul: the streamed path covers Q4_K (and Q6_K when not gated)");
+            QStreamWeight qsw;
+            if (type == MK_TYPE_Q4_K) build_qstream_weight(bank.w.p0, bank.w.rows, cols, qsw, nullptr, gated ? rows_pe * experts : 0);
+            else build_qstream_weight_q6k(bank.w, qsw, nullptr);
+            DevBuf yh;
+            if (gated) yh.alloc((size_t)P * rows_pe * 2);
+            launch_qstream_tc_grouped(qsw, experts, doff.as<int32_t>(), a.xh, P, most, dy.as<float>(), (int)rows_pe, status.as<int32_t>(), nullptr,
+                                      gated ? act : -1, gated ? yh.as<__half>() : nullptr, (int)rows_pe);
+            MK_CUDA(cudaDeviceSynchronize());
+            if (gated) {
+                std::vector<uint16_t> h((size_t)P * rows_pe);
+                yh.download(h.data(), h.size() * 2);
+                MK_CUDA(cudaDeviceSynchronize());
+                for (size_t i = 0; i < h.size(); ++i) y[i] = __half2float(__ushort_as_half(h[i]));
+            }
+        } else {
+            throw std::runtime_error("mk_k_grouped_qmatmul: path must be the integer GEMV or the streamed kernel");
+        }
+        MK_CUDA(cudaDeviceSynchronize());
+        int32_t st = 0;
+        status.download(&st, 4);
+        if (!(gated && path == MK_PATH_STREAM)) dy.download(y, (size_t)P * rows_pe * 4);
+        MK_CUDA(cudaDeviceSynchronize());
+        if (st != 0) throw std::runtime_error("grouped matmul: a bounded wait inside the kernel gave up (status " + std::to_string(st) + ")");
+    });
+}
+
+int32_t mk_k_ep_exchange_emulated(int32_t ranks, int32_t local_experts, int32_t hidden, int32_t cap_rows, const uint16_t* rows,
+                                  const int32_t* offsets, int32_t exchanges, int32_t silent_rank, int64_t wait_ns, float* results,
+                                  int32_t* merged_ranges, int32_t* status) {
+    return guarded([&] {
+        require_device();
+        if (ranks < 1 || ranks > kEpMaxRanks || local_experts < 1 || local_experts > 128 || hidden <= 0 || hidden % 8 != 0 || cap_rows <= 0 ||
+            exchanges < 1 || rows == nullptr || offsets == nullptr || results == nullptr || merged_ranges == nullptr || status == nullptr)
+            throw std::runtime_error("mk_k_ep_exchange_emulated: bad arguments");
+        const int N = ranks, EL = local_experts, E = N * EL;
+        for (int r = 0; r < N; ++r) {
+            const int32_t* o = offsets + (size_t)r * (E + 1);
+            if (o[0] != 0 || o[E] > cap_rows) throw std::runtime_error("mk_k_ep_exchange_emulated: row ranges start at 0 and fit cap_rows");
+            for (int e = 0; e < E; ++e)
+                if (o[e + 1] < o[e]) throw std::runtime_error("mk_k_ep_exchange_emulated: row ranges must not decrease");
+        }
+        // the blocks of all ranks live on this device; every rank's view of them is the same table with its own rank
+        auto up = [](int64_t v) { return (v + 255) / 256 * 256; };
+        EpDispatch d0;
+        d0.ranks = N;
+        d0.local_experts = EL;
+        d0.hidden = hidden;
+        d0.cap_rows = cap_rows;
+        int64_t at = 0;
+        d0.rows_in_off = at;
+        at = up(at + (int64_t)2 * N * cap_rows * hidden * 2);
+        d0.off_in_off = at;
+        at = up(at + (int64_t)2 * N * (EL + 1) * 4);
+        d0.flag_in_off = at;
+        at = up(at + (int64_t)2 * N * 4);
+        d0.out_back_off = at;
+        at = up(at + (int64_t)2 * cap_rows * hidden * 4);
+        d0.flag_back_off = at;
+        at = up(at + (int64_t)2 * N * 4);
+        std::vector<DevBuf> block((size_t)N), x((size_t)N), off((size_t)N), merged((size_t)N), out((size_t)N), comb((size_t)N), start((size_t)N),
+            done((size_t)N), st((size_t)N);
+        for (int r = 0; r < N; ++r) {
+            block[(size_t)r].alloc((size_t)at);
+            block[(size_t)r].zero(nullptr);
+            d0.base[r] = block[(size_t)r].as<uint8_t>();
+            x[(size_t)r].alloc((size_t)cap_rows * hidden * 2);
+            x[(size_t)r].upload(rows + (size_t)r * cap_rows * hidden, (size_t)cap_rows * hidden * 2);
+            off[(size_t)r].alloc((size_t)(E + 1) * 4);
+            off[(size_t)r].upload(offsets + (size_t)r * (E + 1), (size_t)(E + 1) * 4);
+            merged[(size_t)r].alloc((size_t)N * cap_rows * hidden * 2);
+            out[(size_t)r].alloc((size_t)N * cap_rows * hidden * 4);
+            comb[(size_t)r].alloc((size_t)(EL + 1) * 4);
+            comb[(size_t)r].zero(nullptr);
+            start[(size_t)r].alloc((size_t)N * EL * 4);
+            start[(size_t)r].zero(nullptr);
+            done[(size_t)r].alloc((size_t)2 * kEpMaxRanks * 4);
+            done[(size_t)r].zero(nullptr);
+            st[(size_t)r].alloc(4);
+            st[(size_t)r].zero(nullptr);
+        }
+        MK_CUDA(cudaDeviceSynchronize());
+        auto view = [&](int r) { EpDispatch d = d0; d.rank = r; return d; };
+        // one stream, stage by stage over all ranks: every flag a kernel waits for was published by an earlier launch (or,
+        // for the silent rank, never is - those waits run out after wait_ns and leave their status code)
+        const uint64_t wns = wait_ns > 0 ? (uint64_t)wait_ns : kEpWaitNs;
+        for (uint32_t epoch = 1; epoch <= (uint32_t)exchanges; ++epoch) {
+            for (int r = 0; r < N; ++r)
+                if (r != silent_rank) launch_ep_dispatch(x[(size_t)r].as<__half>(), off[(size_t)r].as<int32_t>(), view(r), epoch, done[(size_t)r].as<int32_t>(), st[(size_t)r].as<int32_t>(), nullptr);
+            for (int r = 0; r < N; ++r)
+                if (r != silent_rank)
+                    launch_ep_regroup(view(r), epoch, merged[(size_t)r].as<__half>(), comb[(size_t)r].as<int32_t>(), start[(size_t)r].as<int32_t>(), st[(size_t)r].as<int32_t>(), nullptr, wns);
+            if (silent_rank >= 0) break;  // the ranks that waited hold empty ranges and their status; nothing to return
+            for (int r = 0; r < N; ++r)
+                launch_ep_scale_rows(merged[(size_t)r].as<__half>(), comb[(size_t)r].as<int32_t>(), EL, r * EL, hidden, out[(size_t)r].as<float>(), nullptr);
+            for (int r = 0; r < N; ++r)
+                launch_ep_return(out[(size_t)r].as<float>(), start[(size_t)r].as<int32_t>(), view(r), epoch, done[(size_t)r].as<int32_t>() + kEpMaxRanks, nullptr);
+            for (int r = 0; r < N; ++r) launch_ep_wait_back(view(r), epoch, st[(size_t)r].as<int32_t>(), nullptr, wns);
+        }
+        MK_CUDA(cudaDeviceSynchronize());
+        const uint32_t last = silent_rank >= 0 ? 1u : (uint32_t)exchanges;
+        for (int r = 0; r < N; ++r) {
+            EpDispatch d = view(r);
+            MK_CUDA(cudaMemcpy(results + (size_t)r * cap_rows * hidden, ep_result_area(d, last), (size_t)cap_rows * hidden * 4, cudaMemcpyDeviceToHost));
+            comb[(size_t)r].download(merged_ranges + (size_t)r * (EL + 1), (size_t)(EL + 1) * 4);
+            st[(size_t)r].download(status + r, 4);
+        }
+        MK_CUDA(cudaDeviceSynchronize());
+    });
+}
+
 int32_t mk_k_penalties(float* logits, int32_t vocab, const uint32_t* history, int32_t n_history, float repetition_penalty,
                        const uint32_t* generated, int32_t n_generated, float presence_penalty, float frequency_penalty) {
     return guarded([&] {

@@ -78,6 +78,8 @@ ModelConfig to_model_config(const mk_load_config* cfg) {
     if (cfg->ep_size > 1) {
         c.ep_size = cfg->ep_size;
         c.ep_rank = cfg->ep_rank;
+        c.ep_mode = cfg->ep_mode;
+        if (c.ep_mode != 0 && c.ep_mode != 1) throw std::runtime_error("ep_mode must be 0 or 1");
     }
     return c;
 }
@@ -166,6 +168,14 @@ int32_t mk_model_ep_init(mk_model* m, const uint8_t* id) {
         Model* model = dynamic_cast<Model*>(m->lm.get());
         if (model == nullptr) throw std::runtime_error("mk_model_ep_init needs a GGUF model");
         model->ep_init(id);
+    });
+}
+
+int32_t mk_model_ep_idle_tick(mk_model* m) {
+    return guarded([&] {
+        Model* model = dynamic_cast<Model*>(m->lm.get());
+        if (model == nullptr) throw std::runtime_error("mk_model_ep_idle_tick needs a GGUF model");
+        model->ep_idle_tick();
     });
 }
 

@@ -71,7 +71,10 @@ EpComm::EpComm(int rank, int size, const uint8_t id_bytes[kEpUniqueIdBytes]) : r
 EpComm::~EpComm() {
     for (void* p : mapped_)
         if (p != nullptr) cudaIpcCloseMemHandle(p);
+    for (void* p : dispatch_mapped_)
+        if (p != nullptr) cudaIpcCloseMemHandle(p);
     if (exchange_ != nullptr) cudaFree(exchange_);
+    if (dispatch_block_ != nullptr) cudaFree(dispatch_block_);
     if (comm_ != nullptr) nccl().CommDestroy(static_cast<ncclComm_t>(comm_));
 }
 
@@ -84,18 +87,15 @@ void cuda_check(cudaError_t e, const char* what) {
 }
 }  // namespace
 
-void EpComm::open_exchange(int max_tokens, int row_floats, cudaStream_t s) {
-    if (size_ > kEpMaxRanks) throw std::runtime_error("the fused expert exchange serves at most 8 ranks");
-    if (exchange_ != nullptr) throw std::runtime_error("expert exchange opened twice");
-    const int64_t slot_floats = (int64_t)max_tokens * row_floats;
-    const size_t gather_bytes = (size_t)2 * size_ * slot_floats * 4;
-    const size_t flag_bytes = (size_t)2 * size_ * max_tokens * 4;
-    cuda_check(cudaMalloc(&exchange_, gather_bytes + flag_bytes), "cudaMalloc of the expert exchange block");
-    cuda_check(cudaMemsetAsync(exchange_, 0, gather_bytes + flag_bytes, s), "cudaMemsetAsync");
+void* EpComm::open_block(size_t bytes, cudaStream_t s, void* (&bases)[kEpMaxRanks], void* (&mapped)[kEpMaxRanks]) {
+    if (size_ > kEpMaxRanks) throw std::runtime_error("the expert exchange serves at most 8 ranks");
+    void* block = nullptr;
+    cuda_check(cudaMalloc(&block, bytes), "cudaMalloc of an expert exchange block");
+    cuda_check(cudaMemsetAsync(block, 0, bytes, s), "cudaMemsetAsync");
     // the handles travel through the communicator itself; nobody can store into a block before its owner has
     // zeroed it, because the owner's all-gather is ordered after the memset on the same stream
     cudaIpcMemHandle_t mine;
-    cuda_check(cudaIpcGetMemHandle(&mine, exchange_), "cudaIpcGetMemHandle");
+    cuda_check(cudaIpcGetMemHandle(&mine, block), "cudaIpcGetMemHandle");
     static_assert(sizeof(cudaIpcMemHandle_t) % 4 == 0, "handle size");
     constexpr size_t HF = sizeof(cudaIpcMemHandle_t) / 4;
     float* stage = nullptr;
@@ -111,19 +111,13 @@ void EpComm::open_exchange(int max_tokens, int row_floats, cudaStream_t s) {
         throw;
     }
     cudaFree(stage);
-    peers_ = EpPeers{};
-    peers_.rank = rank_;
-    peers_.ranks = size_;
-    peers_.max_tokens = max_tokens;
-    peers_.slot_floats = slot_floats;
     for (int p = 0; p < size_; ++p) {
-        void* base = exchange_;
+        void* base = block;
         if (p != rank_) {
             cuda_check(cudaIpcOpenMemHandle(&base, all[p], cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle of a peer's expert exchange block");
-            mapped_[p] = base;
+            mapped[p] = base;
         }
-        peers_.gather[p] = static_cast<float*>(base);
-        peers_.flags[p] = reinterpret_cast<uint32_t*>(static_cast<char*>(base) + gather_bytes);
+        bases[p] = base;
     }
     // leave together: once this returns, every rank has mapped every block
     float* fence = nullptr;
@@ -136,6 +130,52 @@ void EpComm::open_exchange(int max_tokens, int row_floats, cudaStream_t s) {
         throw;
     }
     cudaFree(fence);
+    return block;
+}
+
+void EpComm::open_exchange(int max_tokens, int row_floats, cudaStream_t s) {
+    if (exchange_ != nullptr) throw std::runtime_error("expert exchange opened twice");
+    const int64_t slot_floats = (int64_t)max_tokens * row_floats;
+    const size_t gather_bytes = (size_t)2 * size_ * slot_floats * 4;
+    const size_t flag_bytes = (size_t)2 * size_ * max_tokens * 4;
+    void* bases[kEpMaxRanks] = {};
+    exchange_ = open_block(gather_bytes + flag_bytes, s, bases, mapped_);
+    peers_ = EpPeers{};
+    peers_.rank = rank_;
+    peers_.ranks = size_;
+    peers_.max_tokens = max_tokens;
+    peers_.slot_floats = slot_floats;
+    for (int p = 0; p < size_; ++p) {
+        peers_.gather[p] = static_cast<float*>(bases[p]);
+        peers_.flags[p] = reinterpret_cast<uint32_t*>(static_cast<char*>(bases[p]) + gather_bytes);
+    }
+}
+
+void EpComm::open_dispatch(int64_t cap_rows, int hidden, int local_experts, cudaStream_t s) {
+    if (dispatch_block_ != nullptr) throw std::runtime_error("expert dispatch exchange opened twice");
+    if (hidden % 8 != 0 || cap_rows <= 0 || local_experts <= 0) throw std::runtime_error("expert dispatch exchange: bad geometry");
+    auto up = [](int64_t v) { return (v + 255) / 256 * 256; };
+    EpDispatch d;
+    d.rank = rank_;
+    d.ranks = size_;
+    d.local_experts = local_experts;
+    d.hidden = hidden;
+    d.cap_rows = cap_rows;
+    int64_t at = 0;
+    d.rows_in_off = at;
+    at = up(at + (int64_t)2 * size_ * cap_rows * hidden * 2);
+    d.off_in_off = at;
+    at = up(at + (int64_t)2 * size_ * (local_experts + 1) * 4);
+    d.flag_in_off = at;
+    at = up(at + (int64_t)2 * size_ * 4);
+    d.out_back_off = at;
+    at = up(at + (int64_t)2 * cap_rows * hidden * 4);
+    d.flag_back_off = at;
+    at = up(at + (int64_t)2 * size_ * 4);
+    void* bases[kEpMaxRanks] = {};
+    dispatch_block_ = open_block((size_t)at, s, bases, dispatch_mapped_);
+    for (int p = 0; p < size_; ++p) d.base[p] = static_cast<uint8_t*>(bases[p]);
+    dispatch_ = d;
 }
 
 void EpComm::all_gather_f32(const float* send, float* recv, size_t count, cudaStream_t s) {

@@ -31,6 +31,21 @@ struct EpPeers {
     int64_t slot_floats = 0;
 };
 
+// The exchange area of expert parallelism with data-parallel lanes (see ep_dispatch.cu), as every rank sees it: base[p]
+// is rank p's block (this rank's own for p = rank; the others mapped through CUDA IPC).  Inside a block, for buffer
+// b = epoch & 1:
+//   rows_in   f16 [2][ranks][cap_rows][hidden]  rows sent by each source for this rank's experts
+//   off_in    i32 [2][ranks][local_experts + 1] the source's own positions of those rows, per local expert
+//   flag_in   u32 [2][ranks]                    epoch in which the source's rows were complete
+//   out_back  f32 [2][cap_rows][hidden]         expert outputs of this rank's routed rows, in its own grouped order
+//   flag_back u32 [2][ranks]                    epoch in which a destination's outputs were complete
+struct EpDispatch {
+    uint8_t* base[kEpMaxRanks] = {};
+    int rank = 0, ranks = 1, local_experts = 0, hidden = 0;
+    int64_t cap_rows = 0;
+    int64_t rows_in_off = 0, off_in_off = 0, flag_in_off = 0, out_back_off = 0, flag_back_off = 0;
+};
+
 class EpComm {
 public:
     // Rank 0 creates the id and hands it to the other ranks out of band (a file, a store, a socket).
@@ -50,6 +65,11 @@ public:
     // handle to the other ranks (through an all-gather) and maps theirs.  Throws when a peer's block cannot be mapped.
     void open_exchange(int max_tokens, int row_floats, cudaStream_t s);
     bool has_exchange() const { return exchange_ != nullptr; }
+    // Collective: the same for the dispatch / return exchange of data-parallel lanes: every source may send up to cap_rows
+    // rows of `hidden` halves to every destination per exchange.
+    void open_dispatch(int64_t cap_rows, int hidden, int local_experts, cudaStream_t s);
+    bool has_dispatch() const { return dispatch_block_ != nullptr; }
+    const EpDispatch& dispatch() const { return dispatch_; }
     const EpPeers& peers() const { return peers_; }
     // Every rank calls this once per exchange, in the same order: the epoch names the exchange, its parity the buffer.
     uint32_t next_epoch() { return ++epoch_; }
@@ -57,8 +77,14 @@ public:
 private:
     void* comm_ = nullptr;
     int rank_ = 0, size_ = 1;
+    // Collective: allocates and zeroes `bytes` on this rank, exchanges the IPC handles, maps the peers' blocks and
+    // returns once every rank has mapped every block.
+    void* open_block(size_t bytes, cudaStream_t s, void* (&bases)[kEpMaxRanks], void* (&mapped)[kEpMaxRanks]);
     void* exchange_ = nullptr;
     void* mapped_[kEpMaxRanks] = {};
+    void* dispatch_block_ = nullptr;
+    void* dispatch_mapped_[kEpMaxRanks] = {};
+    EpDispatch dispatch_;
     EpPeers peers_;
     uint32_t epoch_ = 0;
 };

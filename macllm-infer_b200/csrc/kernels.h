@@ -178,6 +178,23 @@ void launch_moe_combine_exchange(const float* expert_out, const int32_t* sel_exp
                                  const int32_t* pos_of_pair, int T, int k, int hidden, int e_lo, int e_hi, const EpPeers& peers,
                                  uint32_t epoch, float* out, int32_t* status, cudaStream_t s, uint64_t wait_ns = kEpWaitNs);
 
+// Expert parallelism with data-parallel lanes (ep_dispatch.cu): the four steps around the expert matmuls of one MoE layer.
+// `done` is ranks ints of device memory, zero before the first call (every call leaves it zero).  All ranks call these
+// with the same epoch, in the same order.
+void launch_ep_dispatch(const __half* grouped_rows, const int32_t* offsets, const EpDispatch& D, uint32_t epoch, int32_t* done, int32_t* status,
+                        cudaStream_t s);
+void launch_ep_regroup(const EpDispatch& D, uint32_t epoch, __half* merged, int32_t* comb_off, int32_t* src_start, int32_t* status, cudaStream_t s,
+                       uint64_t wait_ns = kEpWaitNs);
+void launch_ep_return(const float* expert_out, const int32_t* src_start, const EpDispatch& D, uint32_t epoch, int32_t* done, cudaStream_t s);
+void launch_ep_wait_back(const EpDispatch& D, uint32_t epoch, int32_t* status, cudaStream_t s, uint64_t wait_ns = kEpWaitNs);
+// Test stand-in for the expert matmuls: out[row] = merged[row] * (first_expert + local expert of the row + 1).
+void launch_ep_scale_rows(const __half* merged, const int32_t* comb_off, int local_experts, int first_expert, int hidden, float* out, cudaStream_t s);
+// This rank's result area of the exchange `epoch`: expert outputs of its routed rows in its own grouped order.
+const float* ep_result_area(const EpDispatch& D, uint32_t epoch);
+
+// out[p] = x[token_of_pos[p]] for p < P: rows of `width` halves (a multiple of 8) gathered into grouped order.
+void launch_gather_rows_half(const __half* x, const int32_t* token_of_pos, int P, int width, __half* out, cudaStream_t s);
+
 // Small helpers
 void launch_add_inplace(float* h, const float* a, float scale, int64_t n, cudaStream_t s);
 

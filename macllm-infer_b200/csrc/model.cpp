@@ -279,8 +279,55 @@ void Model::ep_init(const uint8_t* id) {
     ep_ = std::make_unique<EpComm>(cfg_.ep_rank, cfg_.ep_size, id);
     // MACLLM_B200_EP_FUSED=0 keeps the exchange on NCCL (all-gather + a sum kernel) instead of the fused kernel
     const char* fused = getenv("MACLLM_B200_EP_FUSED");
+    if (cfg_.ep_mode == 1) {
+        if (!qstream_moe_) throw std::runtime_error("expert parallelism with data-parallel lanes needs Q4_K / Q6_K expert banks of whole 128-row tiles");
+        if (cfg_.ep_size > kEpMaxRanks) throw std::runtime_error("expert parallelism with data-parallel lanes: at most 8 ranks");
+        const int EL = ep_local_experts(), N = cfg_.ep_size;
+        const int64_t cap = (int64_t)cfg_.max_batch_tokens * ms_.experts_used;
+        ep_->open_dispatch(cap, ms_.hidden, EL, stream_);
+        ep_merged_xh_.alloc((size_t)N * cap * ms_.hidden * 2);
+        ep_merged_act_.alloc((size_t)N * cap * ms_.expert_ffn * 2);
+        ep_merged_out_.alloc((size_t)N * cap * ms_.hidden * 4);
+        ep_comb_off_.alloc((size_t)(EL + 1) * 4);
+        ep_src_start_.alloc((size_t)N * EL * 4);
+        ep_done_.alloc((size_t)2 * kEpMaxRanks * 4);
+        ep_zero_off_.alloc((size_t)(ms_.experts + 1) * 4);
+        MK_CUDA(cudaMemsetAsync(ep_done_.ptr(), 0, (size_t)2 * kEpMaxRanks * 4, stream_));
+        MK_CUDA(cudaMemsetAsync(ep_zero_off_.ptr(), 0, (size_t)(ms_.experts + 1) * 4, stream_));
+        MK_CUDA(cudaMemsetAsync(ep_comb_off_.ptr(), 0, (size_t)(EL + 1) * 4, stream_));
+        MK_CUDA(cudaStreamSynchronize(stream_));
+        return;
+    }
     if ((fused == nullptr || strcmp(fused, "0") != 0) && cfg_.ep_size <= kEpMaxRanks)
         ep_->open_exchange(cfg_.max_batch_tokens, ms_.hidden, stream_);
+}
+
+// One MoE layer's experts under data-parallel expert parallelism: this rank's routed rows (grouped by expert, f16) go to
+// the ranks that hold the experts, the rows this rank received run through its expert banks, and the outputs go back.
+// Returns the area that holds the outputs of this rank's own rows in its own grouped order.
+const float* Model::ep_exchange_layer(LayerWeights& w, const LayerSpec& ls, const __half* grouped_rows, const int32_t* offsets) {
+    const EpDispatch& D = ep_->dispatch();
+    const int EL = ep_local_experts(), H = ms_.hidden, F = ms_.expert_ffn;
+    const int capacity = (int)std::min<int64_t>((int64_t)D.ranks * D.cap_rows, INT32_MAX);
+    const uint32_t epoch = ep_->next_epoch();
+    int32_t* status = tc_ws_.status.as<int32_t>();
+    launch_ep_dispatch(grouped_rows, offsets, D, epoch, ep_done_.as<int32_t>(), status, stream_);
+    launch_ep_regroup(D, epoch, ep_merged_xh_.as<__half>(), ep_comb_off_.as<int32_t>(), ep_src_start_.as<int32_t>(), status, stream_);
+    launch_qstream_tc_grouped(w.qs_gu, EL, ep_comb_off_.as<int32_t>(), ep_merged_xh_.as<__half>(), capacity, kQStreamMaxRows, nullptr, 0, status,
+                              stream_, ls.act, ep_merged_act_.as<__half>(), F);
+    launch_qstream_tc_grouped(w.qs_down, EL, ep_comb_off_.as<int32_t>(), ep_merged_act_.as<__half>(), capacity, kQStreamMaxRows,
+                              ep_merged_out_.as<float>(), H, status, stream_);
+    launch_ep_return(ep_merged_out_.as<float>(), ep_src_start_.as<int32_t>(), D, epoch, ep_done_.as<int32_t>() + kEpMaxRanks, stream_);
+    launch_ep_wait_back(D, epoch, status, stream_);
+    launches_ += 6;
+    return ep_result_area(D, epoch);
+}
+
+void Model::ep_idle_tick() {
+    if (cfg_.ep_mode != 1 || !ep_ || !ep_->has_dispatch()) throw std::runtime_error("ep_idle_tick needs a model in data-parallel expert parallelism after mk_model_ep_init");
+    MK_CUDA(cudaSetDevice(cfg_.device));
+    for (int l = 0; l < ms_.layers; ++l)
+        if (ms_.layer[(size_t)l].moe) ep_exchange_layer(lw_[(size_t)l], ms_.layer[(size_t)l], e_xh_.as<__half>(), ep_zero_off_.as<int32_t>());
 }
 
 void Model::load_weights(const GgufFile& f) {
@@ -548,9 +595,11 @@ void Model::build_qstream() {
         else build_qstream_weight_q6k(w, out, stream_);
     };
     bool qkv_one = true;
+    const bool moe = ms_.experts > 0;
+    if (moe && ((2 * ms_.expert_ffn) % 128 != 0 || ms_.hidden % 128 != 0)) return;  // experts are whole row tiles
     for (size_t l = 0; l < lw_.size(); ++l) {
         LayerWeights& w = lw_[l];
-        if (ms_.layer[l].moe) return;
+        if (ms_.layer[l].moe != moe) return;
         if (!q4k(w.wq) || !q4k(w.wk) || !kq(w.wo) || !q4k(w.gate) || !q4k(w.up) || !kq(w.down)) return;
         if (!w.wv.half.ready) return;
         // one launch for q | k | v needs the Q4_K part to end on a row-tile boundary
@@ -558,7 +607,7 @@ void Model::build_qstream() {
     }
     // act(gate) * up in the epilogue of the streamed gate|up matmul (rows interleaved); MACLLM_B200_QS_GATED=0 keeps the
     // plain form with the separate activation kernel
-    { const char* e = std::getenv("MACLLM_B200_QS_GATED"); qstream_gated_ = e == nullptr || e[0] != '0'; }
+    { const char* e = std::getenv("MACLLM_B200_QS_GATED"); qstream_gated_ = moe || e == nullptr || e[0] != '0'; }
     for (size_t l = 0; l < lw_.size(); ++l) {
         LayerWeights& w = lw_[l];
         stack(w.wq, w.wk, w.qk_raw);
@@ -566,8 +615,22 @@ void Model::build_qstream() {
         build_qstream_weight(w.qk_raw.ptr(), w.wq.w.rows + w.wk.w.rows, w.wq.w.cols, w.qs_qk, stream_);
         if (qkv_one) retile(w.wv.w, w.qs_v);
         retile(w.wo.w, w.qs_o);
-        build_qstream_weight(w.gu_raw.ptr(), w.gate.w.rows + w.up.w.rows, w.gate.w.cols, w.qs_gu, stream_, qstream_gated_ ? w.gate.w.rows : 0);
-        retile(w.down.w, w.qs_down);
+        if (!moe) {
+            build_qstream_weight(w.gu_raw.ptr(), w.gate.w.rows + w.up.w.rows, w.gate.w.cols, w.qs_gu, stream_, qstream_gated_ ? w.gate.w.rows : 0);
+            retile(w.down.w, w.qs_down);
+        } else {
+            // expert banks (this rank's experts): [gate bank; up bank] with the rows of every expert interleaved, and the
+            // down bank; w.rows holds the rows of ONE expert
+            const int64_t EL = ep_local_experts();
+            build_qstream_weight(w.gu_raw.ptr(), 2 * EL * w.gate.w.rows, w.gate.w.cols, w.qs_gu, stream_, EL * w.gate.w.rows);
+            QWeight bank = w.down.w;
+            bank.rows = EL * w.down.w.rows;
+            retile(bank, w.qs_down);
+        }
+    }
+    if (moe) {
+        e_xh_.alloc((size_t)cfg_.max_batch_tokens * ms_.experts_used * ms_.hidden * 2);
+        qstream_moe_ = true;
     }
     qstream_qkv_ = qkv_one;
     // the output projection of narrow batches (no scale, no soft cap: those stay on the other paths)
@@ -944,7 +1007,8 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         else matmul(w.wo, xo, T, proj_.as<float>(), H, 1.f, 0.f);
         // residual add + FFN norm + quantise (finish_mixer, src/decoder.rs:2684-2699)
         int fkind = act_kind_of(w.gate.w);
-        ActQ xf = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, H, fkind, f16_T);
+        const bool ep_dp = cfg_.ep_size > 1 && cfg_.ep_mode == 1 && ls.moe;  // the exchange moves f16 rows at every width
+        ActQ xf = act_view(a_qs_, a_d_, a_bs_, a_xh_, T, H, fkind, f16_T || ep_dp);
         NormQuantArgs nf;
         nf.h = h_.as<float>();
         nf.a = wo_splits > 1 ? tc_ws_.partial.as<float>() : proj_.as<float>();
@@ -1026,18 +1090,47 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
                              stream_);
             ActQ xq = xf;
             xq.xh = nullptr;
+            const bool moe_stream = qstream_moe_ && xf.xh != nullptr && (ep_dp || (f16_T && T >= qstream_min_rows_));
             // expert parallelism: only the experts [e0, e0 + EL) live here; their rows of the grouped layout are
             // computed and combined into a partial sum, and the partials of all ranks are added in rank order
             const bool ep = cfg_.ep_size > 1;
             if (ep && !ep_) throw std::runtime_error("expert-parallel model used before mk_model_ep_init");
             const int e0 = ep_first_expert(), EL = ep_local_experts();
             const int32_t* off = grp_off_.as<int32_t>() + e0;
-            launch_qgemv_grouped(w.gate.w, EL, off, tok_of_pos_.as<int32_t>(), xq, e_gate_.as<float>(), F, stream_);
-            launch_qgemv_grouped(w.up.w, EL, off, tok_of_pos_.as<int32_t>(), xq, e_up_.as<float>(), F, stream_);
-            int dkind = act_kind_of(w.down.w);
-            ActQ xd = act_view(f_qs_, f_d_, f_bs_, f_xh_, P, F, dkind, false);
-            launch_actmul_quant(e_gate_.as<float>(), e_up_.as<float>(), F, P, F, ls.act, dkind, xd, nullptr, stream_);
-            launch_qgemv_grouped(w.down.w, EL, off, nullptr, xd, e_down_.as<float>(), H, stream_);
+            if (ep_dp) {
+                if (!ep_->has_dispatch() || !moe_stream) throw std::runtime_error("data-parallel expert parallelism: the dispatch exchange is not open");
+                prof_begin(KC_MOE, 4.0 * P * H, 0);
+                launch_gather_rows_half(xf.xh, tok_of_pos_.as<int32_t>(), P, H, e_xh_.as<__half>(), stream_);
+                prof_end();
+                const float* back = ep_exchange_layer(w, ls, e_xh_.as<__half>(), grp_off_.as<int32_t>());
+                launch_moe_combine(back, sel_e_.as<int32_t>(), sel_w_.as<float>(), pos_of_pair_.as<int32_t>(), T, K, H, 0, E, down_.as<float>(),
+                                   stream_);
+            } else {
+            if (moe_stream) {
+                // the routed rows grouped by expert as f16, then the expert-grouped tensor-core matmuls: gate|up with the
+                // activation in its epilogue (f16 out), down on those rows.  Every expert's weights are read once per 64
+                // of its rows; the row ranges stay on the device.
+                prof_begin(KC_MOE, 4.0 * P * H, 0);
+                launch_gather_rows_half(xf.xh, tok_of_pos_.as<int32_t>(), P, H, e_xh_.as<__half>(), stream_);
+                prof_end();
+                const double gu_bytes = (double)w.qs_gu.rows * (double)(w.qs_gu.cols / 256) * 144.0;
+                prof_begin(KC_QSTREAM, gu_bytes + 2.0 * P * H + 2.0 * P * F, 2.0 * P * 2.0 * F * H);
+                launch_qstream_tc_grouped(w.qs_gu, EL, off, e_xh_.as<__half>(), P, std::min(T, kQStreamMaxRows), nullptr, 0, tc_ws_.status.as<int32_t>(), stream_,
+                                          ls.act, f_xh_.as<__half>(), F);
+                prof_end();
+                const double dn_bytes = (double)w.qs_down.rows * (double)(w.qs_down.cols / 256) * (w.qs_down.fmt ? 210.0 : 144.0);
+                prof_begin(KC_QSTREAM, dn_bytes + 2.0 * P * F + 4.0 * P * H, 2.0 * P * (double)F * H);
+                launch_qstream_tc_grouped(w.qs_down, EL, off, f_xh_.as<__half>(), P, std::min(T, kQStreamMaxRows), e_down_.as<float>(), H,
+                                          tc_ws_.status.as<int32_t>(), stream_);
+                prof_end();
+            } else {
+                launch_qgemv_grouped(w.gate.w, EL, off, tok_of_pos_.as<int32_t>(), xq, e_gate_.as<float>(), F, stream_);
+                launch_qgemv_grouped(w.up.w, EL, off, tok_of_pos_.as<int32_t>(), xq, e_up_.as<float>(), F, stream_);
+                int dkind = act_kind_of(w.down.w);
+                ActQ xd = act_view(f_qs_, f_d_, f_bs_, f_xh_, P, F, dkind, false);
+                launch_actmul_quant(e_gate_.as<float>(), e_up_.as<float>(), F, P, F, ls.act, dkind, xd, nullptr, stream_);
+                launch_qgemv_grouped(w.down.w, EL, off, nullptr, xd, e_down_.as<float>(), H, stream_);
+            }
             if (ep && ep_->has_exchange()) {
                 launch_moe_combine_exchange(e_down_.as<float>(), sel_e_.as<int32_t>(), sel_w_.as<float>(), pos_of_pair_.as<int32_t>(), T, K,
                                             H, e0, e0 + EL, ep_->peers(), ep_->next_epoch(), down_.as<float>(),
@@ -1050,6 +1143,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
                 ep_->all_gather_f32(ep_partial_.as<float>(), ep_gather_.as<float>(), (size_t)T * H, stream_);
                 launch_ep_sum(ep_gather_.as<float>(), cfg_.ep_size, (int64_t)T * H, down_.as<float>(), stream_);
                 launches_ += 2;
+            }
             }
             launches_ += 8;
         }

@@ -63,6 +63,9 @@ struct ModelConfig {
     // expert parallelism of a sparse-MoE model: this process holds experts [ep_rank, ep_rank + 1) * experts / ep_size
     // and exchanges per-layer partial sums with the other ranks; ep_size <= 1 keeps every expert here
     int ep_rank = 0, ep_size = 1;
+    // 0: all ranks run the same ticks on the same tokens (partial sums exchanged); 1: every rank schedules its own
+    // sequences and each MoE layer sends the routed rows to the experts' ranks and the outputs back (ep_dispatch.cu)
+    int ep_mode = 0;
 };
 
 class Model : public PagedLm {
@@ -73,6 +76,8 @@ public:
     const ModelSpec& model_spec() const { return ms_; }
     // Joins the expert-parallel group (collective over all ep_size ranks; `id` is EpComm::unique_id from rank 0).
     void ep_init(const uint8_t* id);
+    // ep_mode 1: the exchanges of one tick for a rank that has no lane to run (it serves the other ranks' rows).
+    void ep_idle_tick();
     bool device_sampling_covers(float temperature, int top_k) const override { return mk::device_sampling_covers(temperature, top_k, ms_.vocab); }
     float last_forward_ms() const override;
     int64_t launch_count() const override { return launches_; }
@@ -148,6 +153,8 @@ private:
     bool qstream_ = false;
     bool qstream_gated_ = false;   // gate|up streamed with act(gate) * up in its epilogue
     bool qstream_qkv_ = false;     // [wq; wk] and wv go in one streamed launch
+    bool qstream_moe_ = false;     // expert banks re-tiled for the expert-grouped form of the streamed matmul
+    DevBuf e_xh_;                  // routed rows grouped by expert, f16 [T * experts_used][hidden]
     QStreamWeight qs_head_;        // output projection for narrow batches
     DevBuf v_partial_;  // split-K shares of the V projection on streamed ticks
     int qstream_min_rows_ = 2;  // one row stays on the integer GEMV
@@ -171,6 +178,11 @@ private:
     // expert parallelism: this rank's partial layer output [T][hidden] and all ranks' partials [ep_size][T][hidden]
     std::unique_ptr<EpComm> ep_;
     DevBuf ep_partial_, ep_gather_;
+    // ep_mode 1: rows of all sources merged per local expert (f16 inputs, f16 gated activations, f32 outputs), their row
+    // ranges, where each source's rows start, the completion counters of the two exchange kernels, and an all-zero
+    // range table for a tick without rows
+    DevBuf ep_merged_xh_, ep_merged_act_, ep_merged_out_, ep_comb_off_, ep_src_start_, ep_done_, ep_zero_off_;
+    const float* ep_exchange_layer(LayerWeights& w, const LayerSpec& ls, const __half* grouped_rows, const int32_t* offsets);
     QgemmWorkspace tc_ws_;
     PinnedBuf out_host_;
     int out_lanes_ = 0;

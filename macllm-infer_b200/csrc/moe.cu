@@ -202,6 +202,26 @@ void launch_moe_combine_exchange(const float* expert_out, const int32_t* sel_exp
     MK_LAUNCH_CHECK();
 }
 
+namespace {
+
+__global__ void gather_rows_half_kernel(const uint4* x, const int32_t* token_of_pos, int P, int chunks, uint4* out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t)P * chunks) return;
+    const int p = (int)(i / chunks), c = (int)(i - (int64_t)p * chunks);
+    out[i] = x[(int64_t)token_of_pos[p] * chunks + c];
+}
+
+}  // namespace
+
+void launch_gather_rows_half(const __half* x, const int32_t* token_of_pos, int P, int width, __half* out, cudaStream_t s) {
+    if (P <= 0) return;
+    if (width % 8 != 0) throw std::runtime_error("launch_gather_rows_half: rows must be multiples of 16 bytes");
+    const int chunks = width / 8;
+    const int64_t n = (int64_t)P * chunks;
+    gather_rows_half_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(reinterpret_cast<const uint4*>(x), token_of_pos, P, chunks, reinterpret_cast<uint4*>(out));
+    MK_LAUNCH_CHECK();
+}
+
 void launch_moe_group(const int32_t* sel_experts, int T, int k, int experts, int32_t* offsets, int32_t* pos_of_pair,
                       int32_t* token_of_pos, cudaStream_t s) {
     if (T <= 0) return;

@@ -49,6 +49,7 @@ constexpr int QS_ACC = 4;                                        // accumulators
 constexpr uint32_t QS_SPIN_LIMIT = 1u << 22;
 constexpr uint32_t QS_TMEM_COLS = 512;
 constexpr uint32_t QS_A_COL0 = 256;                              // two A buffers of 128 columns
+constexpr int QS_MAX_JOBS = 320;                                 // jobs one CTA can be handed in the expert-grouped form
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -248,6 +249,11 @@ struct QsParams {
     int tiles_a;                  // row tiles of the first segment (Q4_K); the rest are Q6_K
     int fmt_a, fmt_b;             // 0 = Q4_K, 1 = Q6_K
     int stage_bytes, n_stages;
+    // expert-grouped form: the matrix is `experts` matrices of tiles_pe row tiles back to back; the activation rows
+    // [offsets[e], offsets[e + 1]) belong to expert e and are multiplied by its matrix only.  A job is (expert, chunk of
+    // BN rows, group of R row tiles); jobs are shared out evenly over the CTAs, whole jobs only.  rows = rows per expert.
+    int grouped, experts, tiles_pe, groups_pe;
+    const int32_t* offsets;
     int mode;                     // 0 plain, 1 gated (rows interleaved gate/up; writes f16 act(gate) * up)
     int act;                      // gated: 0 SiLU, 1 tanh GELU
     const uint8_t* w_a;           // units of segment a, then of segment b
@@ -319,9 +325,63 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_x, QsParams p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int C = (int)gridDim.x, c = (int)blockIdx.x;
     const int R = p.R, nb = p.n_blocks;
+    // expert-grouped form: this CTA's jobs, looked up by the roles as "group" g = 0, 1, ...
+    __shared__ int16_t job_expert[QS_MAX_JOBS], job_rows[QS_MAX_JOBS], job_group[QS_MAX_JOBS];
+    __shared__ int32_t job_row0[QS_MAX_JOBS];
+    __shared__ int32_t job_range[2];
+    if (p.grouped) {
+        // the row ranges come from the routing kernels: nothing of this launch can start before they are final
+        pdl_wait();
+        if (warp == 0) {
+            // jobs of expert e: ceil(rows_e / BN) chunks x groups_pe; two passes over the experts, 32 at a time: the
+            // total first, then the entries of this CTA's share
+            int total = 0;
+            for (int base = 0; base < p.experts; base += 32) {
+                const int e = base + lane;
+                int cnt = e < p.experts ? (p.offsets[e + 1] - p.offsets[e] + BN - 1) / BN * p.groups_pe : 0;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+                total += cnt;
+            }
+            const int j0 = (int)((int64_t)c * total / C), j1 = (int)((int64_t)(c + 1) * total / C);
+            int running = 0;
+            for (int base = 0; base < p.experts; base += 32) {
+                const int e = base + lane;
+                const int n_e = e < p.experts ? p.offsets[e + 1] - p.offsets[e] : 0;
+                const int cnt = (n_e + BN - 1) / BN * p.groups_pe;
+                int incl = cnt;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += t;
+                }
+                const int start = running + incl - cnt;
+                for (int j = max(start, j0); j < min(start + cnt, j1); ++j) {
+                    const int idx = j - j0;
+                    if (idx < QS_MAX_JOBS) {
+                        const int q = j - start, chunk = q / p.groups_pe;
+                        job_expert[idx] = (int16_t)e;
+                        job_group[idx] = (int16_t)(q - chunk * p.groups_pe);
+                        job_row0[idx] = p.offsets[e] + chunk * BN;
+                        job_rows[idx] = (int16_t)min(BN, n_e - chunk * BN);
+                    }
+                }
+                running += __shfl_sync(0xffffffffu, incl, 31);
+            }
+            if (lane == 0) {
+                job_range[0] = j0;
+                job_range[1] = j1;
+                if (j1 - j0 > QS_MAX_JOBS) atomicExch(p.status, 30);
+            }
+        }
+        __syncthreads();
+    }
     // this CTA's contiguous range of items
     int i0, i1;
-    if (p.whole_groups) {
+    if (p.grouped) {
+        i0 = 0;
+        i1 = min(job_range[1] - job_range[0], QS_MAX_JOBS) * nb;
+    } else if (p.whole_groups) {
         i0 = (int)((int64_t)c * p.groups / C) * nb;
         i1 = (int)((int64_t)(c + 1) * p.groups / C) * nb;
     } else {
@@ -331,6 +391,10 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_x, QsParams p) {
     const int g0 = i0 / nb, b0 = i0 - g0 * nb;       // the only division of the item walk: (g, b) advance by counting
     const int acc_shift = R == 1 ? 2 : (R == 2 ? 1 : 0);  // QS_ACC / R accumulator sets
     const int n_stages = p.n_stages;
+    // row tile r of group g: its index inside its matrix, whether it exists, and the index of its first unit
+    const int tiles_limit = p.grouped ? p.tiles_pe : p.row_tiles;
+    auto tile_of = [&](int g, int r) { return (p.grouped ? (int)job_group[g] : g) * R + r; };
+    auto unit_tile = [&](int g, int tile) { return p.grouped ? (int64_t)job_expert[g] * p.tiles_pe + tile : (int64_t)tile; };
 
     if (warp == 0) {
         // one barrier per lane
@@ -360,12 +424,12 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_x, QsParams p) {
         uint32_t st = 0, use = 0;
         for (int it = i0; it < i1; ++it) {
             for (int r = 0; r < R; ++r) {
-                const int tile = g * R + r;
-                if (tile >= p.row_tiles) break;
+                const int tile = tile_of(g, r);
+                if (tile >= tiles_limit) break;
                 if (!QS_WAIT(0, &raw_empty[st], (use & 1) ^ 1)) { if (lane == 0) atomicExch(p.status, 22); it = i1; break; }
-                const bool seg_b = tile >= p.tiles_a;
+                const bool seg_b = !p.grouped && tile >= p.tiles_a;
                 const uint32_t bytes = (uint32_t)((seg_b ? p.fmt_b : p.fmt_a) ? QS_Q6K_UNIT : QS_Q4K_UNIT);
-                const uint8_t* src = seg_b ? p.w_b + ((int64_t)(tile - p.tiles_a) * nb + b) * bytes : p.w_a + ((int64_t)tile * nb + b) * bytes;
+                const uint8_t* src = seg_b ? p.w_b + ((int64_t)(tile - p.tiles_a) * nb + b) * bytes : p.w_a + (unit_tile(g, tile) * nb + b) * bytes;
                 if (elect_one()) {
                     mbar_expect_tx(&raw_full[st], bytes);
                     bulk_load(raw_ring + (size_t)st * p.stage_bytes, src, bytes, &raw_full[st]);
@@ -380,7 +444,7 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_x, QsParams p) {
         // ---- activation loader: one block of 256 columns per item
         pdl_wait();
         QS_LOG(2, 1);
-        int b = b0;
+        int g = g0, b = b0;
         uint32_t st = 0, ph = 0;
         for (int it = i0; it < i1; ++it) {
             if (!QS_WAIT(0, &x_empty[st], ph ^ 1)) { if (lane == 0) atomicExch(p.status, 21); break; }
@@ -388,11 +452,11 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_x, QsParams p) {
             if (elect_one()) {
                 mbar_expect_tx(&x_full[st], (uint32_t)L::X_BYTES);
 #pragma unroll
-                for (int q = 0; q < 4; ++q) tma_load_2d(xb + q * BN * 128, &tm_x, b * 256 + q * 64, 0, &x_full[st]);
+                for (int q = 0; q < 4; ++q) tma_load_2d(xb + q * BN * 128, &tm_x, b * 256 + q * 64, p.grouped ? job_row0[g] : 0, &x_full[st]);
             }
             __syncwarp();
             QS_LOG(2, 2);
-            if (++b == nb) b = 0;
+            if (++b == nb) { b = 0; ++g; }
             if (++st == QS_X_STAGES) { st = 0; ph ^= 1; }
         }
     } else if (warp == 1) {
@@ -421,7 +485,7 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_x, QsParams p) {
             const int set = piece & ((QS_ACC >> (2 - acc_shift)) - 1), set_use = piece >> acc_shift;
             const uint64_t b_stage = b_desc0 + (uint64_t)((xs * L::X_BYTES) >> 4);
             for (int r = 0; r < R; ++r) {
-                if (g * R + r >= p.row_tiles) break;
+                if (tile_of(g, r) >= tiles_limit) break;
                 const int slot = set * R + r;
                 if (first && !QS_WAIT(1, &acc_empty[slot], (uint32_t)(set_use & 1) ^ 1)) { if (lane == 0) atomicExch(p.status, 23); ok = false; break; }
                 const uint32_t buf = n & 1;
@@ -463,8 +527,8 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_x, QsParams p) {
         bool ok = true;
         for (int it = i0; it < i1 && ok; ++it) {
             for (int r = 0; r < R; ++r) {
-                const int tile = g * R + r;
-                if (tile >= p.row_tiles) break;
+                const int tile = tile_of(g, r);
+                if (tile >= tiles_limit) break;
                 if ((n & 1) == buf) {
                     if (!QS_WAIT(0, &raw_full[st], use & 1)) {
                         if (lane == 0) atomicExch(p.status, 26);
@@ -485,7 +549,7 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_x, QsParams p) {
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     if (warp == 3) QS_LOG(3, 3);
                     const uint32_t t_dst = tmem_base + ((uint32_t)(quad * 32) << 16) + QS_A_COL0 + buf * 128 + 64 * h;
-                    const bool q6 = (tile >= p.tiles_a ? p.fmt_b : p.fmt_a) != 0;
+                    const bool q6 = ((!p.grouped && tile >= p.tiles_a) ? p.fmt_b : p.fmt_a) != 0;
                     uint32_t w[16];
                     if (PROF && (p.dbg & 1)) {
 #pragma unroll
@@ -555,9 +619,11 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_x, QsParams p) {
                 // split results: this piece's slot of the scratch
                 int my_slot = 0;
                 if (p.mode == 0 && p.slots > 1) my_slot = c - cta_of_item(g * nb);
+                // token rows of this piece: the call's rows, or the chunk of one expert's rows
+                const int tok0 = p.grouped ? job_row0[g] : 0, T_here = p.grouped ? (int)job_rows[g] : p.T;
                 for (int r = 0; r < R && ok; ++r) {
-                    const int tile = g * R + r;
-                    if (tile >= p.row_tiles) break;
+                    const int tile = tile_of(g, r);
+                    if (tile >= tiles_limit) break;
                     const int slot = set * R + r;
                     if (!QS_WAIT(0, &acc_full[slot], (uint32_t)(set_use & 1))) {
                         if (lane == 0) atomicExch(p.status, 28);
@@ -586,15 +652,15 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_x, QsParams p) {
                                 const float gate = (lane & 1) ? recv : a0;
                                 const float up = (lane & 1) ? a1 : recv;
                                 const int tok = c0 + t + (lane & 1);
-                                if (row < p.rows && tok < p.T) p.yh[(int64_t)tok * p.ldyh + (row >> 1)] = __float2half_rn(act_fn(gate, p.act) * up);
+                                if (row < p.rows && tok < T_here) p.yh[(int64_t)(tok0 + tok) * p.ldyh + (row >> 1)] = __float2half_rn(act_fn(gate, p.act) * up);
                             }
                         } else if (row < p.rows) {
                             const bool direct = p.slots == 1;
                             const int64_t ld = direct ? p.ldy : p.rows;
-                            float* dst = (direct ? p.y : p.partial + (int64_t)my_slot * p.T * p.rows) + (int64_t)c0 * ld + row;
+                            float* dst = (direct ? p.y : p.partial + (int64_t)my_slot * p.T * p.rows) + (int64_t)(tok0 + c0) * ld + row;
 #pragma unroll
                             for (int t = 0; t < CH; ++t)
-                                if (c0 + t < p.T) dst[(int64_t)t * ld] = __uint_as_float(v[t]);
+                                if (c0 + t < T_here) dst[(int64_t)t * ld] = __uint_as_float(v[t]);
                             if (!direct && b + 1 == nb) {  // the group's last piece: the slots this group does not use read as zero
                                 for (int sl = my_slot + 1; sl < p.slots; ++sl) {
                                     float* z = p.partial + (int64_t)sl * p.T * p.rows + (int64_t)c0 * ld + row;
@@ -855,6 +921,62 @@ int launch_qstream_tc(const QStreamWeight& W, const __half* xh, int T, float* y,
     else if (pl.bn == 32) launch_qs<32>(tx, p, pl.ctas, s);
     else launch_qs<64>(tx, p, pl.ctas, s);
     return pl.slots;
+}
+
+// Expert-grouped form (SparseMoeFeedForward::forward, src/decoder.rs:394-441: every expert multiplies the rows routed to it).
+int launch_qstream_tc_grouped(const QStreamWeight& W, int experts, const int32_t* offsets_dev, const __half* xh, int rows_total,
+                              int max_rows_per_expert, float* y, int ldy, int32_t* status, cudaStream_t s, int gated_act, __half* yh, int ldyh) {
+    if (rows_total <= 0) return 1;
+    if (!W.ready) throw std::runtime_error("launch_qstream_tc_grouped: the matrix was not re-tiled");
+    if (experts <= 0 || W.rows % experts != 0 || (W.rows / experts) % QS_BM != 0)
+        throw std::runtime_error("launch_qstream_tc_grouped: every expert needs a whole number of 128-row tiles");
+    if (xh == nullptr || offsets_dev == nullptr) throw std::runtime_error("launch_qstream_tc_grouped: activations or row ranges missing");
+    const bool gated = gated_act >= 0;
+    if (gated && (!W.gated || yh == nullptr)) throw std::runtime_error("launch_qstream_tc_grouped: the gated form needs an interleaved gate|up bank and an f16 output");
+    const int nb = (int)(W.cols / 256);
+    const int tiles_pe = (int)(W.rows / experts / QS_BM);
+    const int bound = std::max(1, std::min(max_rows_per_expert, kQStreamMaxRows));
+    const int bn = bound <= 16 ? 16 : (bound <= 32 ? 32 : 64);
+    const int R = tiles_pe % 2 == 0 ? 2 : 1;
+    const int sms = device_sm_count();
+    // a bound on the jobs any CTA is handed: every expert may add one partly filled chunk
+    const int64_t max_jobs = ((int64_t)rows_total / bn + experts) * (tiles_pe / R);
+    if ((max_jobs + sms - 1) / sms + 1 > QS_MAX_JOBS) throw std::runtime_error("launch_qstream_tc_grouped: more jobs per CTA than the kernel's table holds");
+    alignas(64) CUtensorMap tx;
+    encode_tma_2d(&tx, false, xh, (uint64_t)W.cols, (uint64_t)rows_total, (uint64_t)W.cols * 2, 64, (uint32_t)bn, true);
+    QsParams p{};
+    p.T = rows_total;
+    p.rows = (int)(W.rows / experts);
+    p.n_blocks = nb;
+    p.row_tiles = W.row_tiles;
+    p.R = R;
+    p.groups = 0;
+    p.items = 0;
+    p.whole_groups = 1;
+    p.slots = 1;
+    p.tiles_a = W.row_tiles;
+    p.fmt_a = p.fmt_b = W.fmt;
+    p.stage_bytes = W.fmt ? QS_Q6K_UNIT : QS_Q4K_UNIT;
+    const size_t x_bytes = (size_t)QS_X_STAGES * 4 * bn * 128;
+    p.n_stages = (int)std::min<size_t>(QS_MAX_STAGES, ((size_t)200 * 1024 - x_bytes) / (size_t)p.stage_bytes);
+    p.grouped = 1;
+    p.experts = experts;
+    p.tiles_pe = tiles_pe;
+    p.groups_pe = tiles_pe / R;
+    p.offsets = offsets_dev;
+    p.mode = gated ? 1 : 0;
+    p.act = gated ? gated_act : 0;
+    p.w_a = W.tiled.as<uint8_t>();
+    p.y = y;
+    p.ldy = ldy;
+    p.yh = yh;
+    p.ldyh = ldyh;
+    p.status = status;
+    p.prof = nullptr;
+    if (bn == 16) launch_qs<16>(tx, p, sms, s);
+    else if (bn == 32) launch_qs<32>(tx, p, sms, s);
+    else launch_qs<64>(tx, p, sms, s);
+    return 1;
 }
 
 }  // namespace mk

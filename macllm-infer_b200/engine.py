@@ -82,7 +82,7 @@ class Model:
 
     @staticmethod
     def _config(device=0, block_tokens=16, slab_blocks=8, kv_capacity_tokens=4096, prefix_capacity_tokens=0, kv_dtype="f16",
-                max_batch_tokens=2048, max_batch_lanes=64, matmul_path=capi.PATH_AUTO, ep_rank=0, ep_size=1) -> capi.LoadConfig:
+                max_batch_tokens=2048, max_batch_lanes=64, matmul_path=capi.PATH_AUTO, ep_rank=0, ep_size=1, ep_mode=0) -> capi.LoadConfig:
         cfg = capi.LoadConfig()
         cfg.device_ordinal = device
         cfg.block_tokens = block_tokens
@@ -95,6 +95,7 @@ class Model:
         cfg.matmul_path = matmul_path
         cfg.ep_rank = ep_rank
         cfg.ep_size = ep_size
+        cfg.ep_mode = ep_mode
         return cfg
 
     EP_ID_BYTES = 128
@@ -112,6 +113,10 @@ class Model:
             raise ValueError("expert-parallel id must be 128 bytes")
         buf = (C.c_uint8 * Model.EP_ID_BYTES).from_buffer_copy(unique_id)
         capi.check(capi.lib().mk_model_ep_init(self._h, buf))
+
+    def ep_idle_tick(self) -> None:
+        """Data-parallel expert parallelism: take part in this tick's exchanges without lanes of one's own."""
+        capi.check(capi.lib().mk_model_ep_idle_tick(self._h))
 
     @staticmethod
     def inspect_gguf(path) -> dict:
@@ -354,3 +359,23 @@ class Engine:
             self.close()
         except Exception:
             pass
+
+
+def run_expert_parallel(engine: Engine, model: Model, all_reduce_sum, outstanding=None, on_tick=None) -> int:
+    """Drives `engine` in lock step with the other ranks of an expert-parallel group with data-parallel lanes
+    (ep_mode=1): every rank schedules its own sequences, and every MoE layer of every tick is one exchange that all ranks
+    take part in, so a rank without a lane to run takes the tick idle.  `all_reduce_sum(n)` returns the sum of n over all
+    ranks (torch.distributed, MPI, a socket: the library does not care); `outstanding()` is this rank's count of requests
+    not yet finished, including ones it has yet to submit (default: the engine's pending count); `on_tick()` runs before
+    each tick (a place to submit arrivals).  Returns the number of ticks."""
+    ticks = 0
+    while True:
+        if on_tick is not None:
+            on_tick()
+        if all_reduce_sum(engine.pending() if outstanding is None else outstanding()) <= 0:
+            break
+        if engine.step() == 0:
+            model.ep_idle_tick()
+        ticks += 1
+    model.synchronize()
+    return ticks

@@ -119,6 +119,32 @@ def moe_route(logits, k: int):
     return sel, w
 
 
+def grouped_qmatmul(qtype: int, w_bank, experts: int, rows_pe: int, cols: int, x: np.ndarray, offsets, path: int, up_bank=None, act: int = 0):
+    """Expert-grouped matmul: rows [offsets[e], offsets[e+1]) of x go through expert e's matrix of the bank."""
+    x = _f32(x)
+    off = np.ascontiguousarray(offsets, dtype=np.int32)
+    y = np.zeros((x.shape[0], rows_pe), dtype=np.float32)
+    w_bank = np.ascontiguousarray(w_bank)
+    up = None if up_bank is None else np.ascontiguousarray(up_bank)
+    capi.check(capi.lib().mk_k_grouped_qmatmul(qtype, _p(w_bank), None if up is None else _p(up), experts, rows_pe, cols, _p(x), _p(off), _p(y), path, act))
+    return y
+
+
+def ep_exchange_emulated(rows: np.ndarray, offsets: np.ndarray, local_experts: int, exchanges: int = 1, silent_rank: int = -1, wait_ns: int = 0):
+    """The dispatch / return exchange of data-parallel expert parallelism with all ranks on one device.  rows: f16
+    [ranks][cap_rows][hidden]; offsets: [ranks][ranks * local_experts + 1].  Returns (results f32 like rows, merged
+    ranges [ranks][local_experts + 1], status [ranks])."""
+    rows = np.ascontiguousarray(rows, dtype=np.float16)
+    off = np.ascontiguousarray(offsets, dtype=np.int32)
+    ranks, cap, hidden = rows.shape
+    results = np.zeros((ranks, cap, hidden), dtype=np.float32)
+    ranges = np.zeros((ranks, local_experts + 1), dtype=np.int32)
+    status = np.zeros(ranks, dtype=np.int32)
+    capi.check(capi.lib().mk_k_ep_exchange_emulated(ranks, local_experts, hidden, cap, _p(rows), _p(off), exchanges, silent_rank, wait_ns,
+                                                    _p(results), _p(ranges), _p(status)))
+    return results, ranges, status
+
+
 def penalties(logits, history, repetition, generated, presence, frequency) -> np.ndarray:
     """Repetition penalty over the set of history tokens, then presence / frequency penalties over generated counts."""
     row = np.array(logits, dtype=np.float32)

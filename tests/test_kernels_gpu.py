@@ -440,3 +440,58 @@ def test_expert_exchange_kernel_gives_up_when_a_peer_never_delivers(ops):
     assert np.array_equal(pushed[1], _expert_partial(expert_out, sel, weights, 0, 4))
     # the device still answers
     assert ops.argmax(np.eye(3, dtype=np.float32)).tolist() == [0, 1, 2]
+
+
+@pytest.mark.parametrize("name", ["q4_k", "q6_k"])
+@pytest.mark.parametrize("case", ["decode", "ragged", "wide"])
+def test_expert_grouped_streamed_matmul_matches_oracle(ops, orc, name, case):
+    """The expert-grouped form of the decode matmul (the row ranges are read on the device): experts with no rows, with a
+    handful, and with more than one 64-row chunk; against the oracle's integer arithmetic per expert and against the
+    grouped integer GEMV."""
+    qtype = QTYPES[name]
+    experts, rows_pe, cols = 8, 256, 512
+    counts = {"decode": [1, 0, 3, 2, 0, 1, 4, 1], "ragged": [0, 17, 64, 5, 33, 0, 1, 40], "wide": [130, 0, 64, 65, 7, 200, 1, 0]}[case]
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    P = int(offsets[-1])
+    rng = np.random.default_rng(len(case))
+    x = rng.standard_normal((P, cols)).astype(np.float32)
+    w = _weights(ops, qtype, experts * rows_pe, cols, stream=11)
+    rb = len(w) // (experts * rows_pe)
+    want = np.zeros((P, rows_pe), np.float32)
+    for e in range(experts):
+        lo, hi = offsets[e], offsets[e + 1]
+        if hi > lo:
+            want[lo:hi] = orc.qmatmul(qtype, w[e * rows_pe * rb:(e + 1) * rows_pe * rb], rows_pe, cols, x[lo:hi], 1)
+    got = ops.grouped_qmatmul(qtype, w, experts, rows_pe, cols, x, offsets, 4)
+    scale = np.sqrt(cols) * 0.02
+    assert np.isfinite(got).all() and np.max(np.abs(got - want)) <= 3e-3 * scale
+    gemv = ops.grouped_qmatmul(qtype, w, experts, rows_pe, cols, x, offsets, 1)
+    assert np.max(np.abs(gemv - want)) <= 2e-5 * max(1.0, np.max(np.abs(want)))
+
+
+@pytest.mark.parametrize("act", [0, 1])
+def test_expert_grouped_gated_matmul_matches_oracle(ops, orc, act):
+    """gate and up banks interleaved per expert, act(gate) * up in the epilogue, f16 out."""
+    experts, F, cols = 4, 384, 512
+    counts = [5, 0, 70, 12]
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    P = int(offsets[-1])
+    rng = np.random.default_rng(act)
+    x = rng.standard_normal((P, cols)).astype(np.float32)
+    gate = _weights(ops, 12, experts * F, cols, stream=12)
+    up = _weights(ops, 12, experts * F, cols, stream=13)
+    rb = len(gate) // (experts * F)
+    want = np.zeros((P, F), np.float32)
+    gmax = umax = 0.0
+    for e in range(experts):
+        lo, hi = offsets[e], offsets[e + 1]
+        if hi > lo:
+            g = orc.qmatmul(12, gate[e * F * rb:(e + 1) * F * rb], F, cols, x[lo:hi], 1)
+            u = orc.qmatmul(12, up[e * F * rb:(e + 1) * F * rb], F, cols, x[lo:hi], 1)
+            gmax, umax = max(gmax, float(np.abs(g).max())), max(umax, float(np.abs(u).max()))
+            want[lo:hi] = orc.act_mul(g, u, act)
+    got = ops.grouped_qmatmul(12, gate, experts, F, cols, x, offsets, 4, up_bank=up, act=act)
+    scale = np.sqrt(cols) * 0.02
+    assert np.isfinite(got).all()
+    # gate and up each carry the f16-operand error of the matmul; the product adds them, then one f16 rounding
+    assert np.max(np.abs(got - want)) <= 3e-3 * scale * (2 * gmax + umax + 1)

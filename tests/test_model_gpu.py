@@ -149,13 +149,14 @@ def test_single_layer_models_match_tightly(pk, tmp_path_factory, fam):
     assert max(errs) < 5e-2, errs
 
 
-@pytest.mark.parametrize("fam", ["llama", "qwen3", "gemma2"])
+@pytest.mark.parametrize("fam", ["llama", "qwen3", "gemma2", "qwen3moe"])
 @pytest.mark.parametrize("matmul_path", [2, 3, 4, 0])
 def test_family_matches_oracle_on_the_tensor_core_path_with_f16_kv(pk, tmp_path_factory, fam, matmul_path):
     """The B200 configuration: f16 KV and tcgen05 matmuls (2: GGUF blocks dequantised in the kernel; 3: the f16
-    weight images with fused projections and split-K shares; 4: those plus streamed Q4_K blocks for 2..64 rows;
-    0: the automatic mix); the oracle keeps f32 KV
-    like the reference."""
+    weight images with fused projections and split-K shares; 4: those plus Q4_K / Q6_K blocks streamed and dequantised
+    into tensor memory for 2..64 rows; 0: the automatic mix); the oracle keeps f32 KV like the reference.  For the
+    sparse-MoE family paths 4 and 0 run the experts on the expert-grouped form of the streamed matmul (gate|up with the
+    activation in its epilogue), on prefill chunks and decode ticks alike."""
     path, spec = make_checkpoint(pk, tmp_path_factory, fam)
     rng = np.random.default_rng(2)
     prompts = [rng.integers(3, spec.vocab, size=n) for n in (50, 19, 70)]
