@@ -195,19 +195,30 @@ def new_engine(eng_mod, model, w, active: int, n_requests: int):
                           queue_capacity=n_requests + 8)
 
 
-def drive(eng_mod, model, eng, w, reqs):
+def drive(eng_mod, model, eng, w, reqs, lockstep=None):
     """Submits the requests the way the workload says and yields after every scheduler tick.
     - one atomic batch (configurations 1, 2, 4);
     - prefix reuse (configuration 3): request 0 alone until it has finished, then the others in submission order;
     - Poisson arrivals (configuration 5): a request is submitted once the step's clock has passed its arrival time; the
       clock is the wall time since the step began, and it jumps to the next arrival whenever the engine would idle, so
-      that a step measures service, not waiting."""
+      that a step measures service, not waiting.
+    lockstep (expert parallelism with data-parallel lanes): a function that sums a count over all ranks.  Every rank then
+    ticks until no rank has work left, and a rank with no lane to run takes the tick idle (it serves the others' rows)."""
     prompts, new, arrivals = reqs
     mk = lambda i: eng_mod.Request(prompts[i], new[i])
     ids = []
+    drive.idle_s = 0.0
     if w.arrival_rate > 0:
-        t0, skipped, nxt = time.perf_counter(), 0.0, 0
-        while nxt < len(prompts) or eng.pending() > 0:
+        waves = None
+    else:
+        waves = [(0, 1, False), (1, len(prompts), False)] if w.shared_prefix else [(0, len(prompts), True)]
+        waves = [x for x in waves if x[1] > x[0]]
+    t0, skipped, nxt = time.perf_counter(), 0.0, 0
+    while True:
+        outstanding = (len(prompts) - nxt) + eng.pending()
+        if (outstanding if lockstep is None else lockstep(outstanding)) <= 0:
+            break
+        if waves is None:
             now = time.perf_counter() - t0 + skipped
             if eng.pending() == 0 and nxt < len(prompts) and arrivals[nxt] > now:
                 skipped += arrivals[nxt] - now
@@ -218,29 +229,34 @@ def drive(eng_mod, model, eng, w, reqs):
                 nxt += 1
             if wave:
                 ids += eng.submit(wave)
-            yield eng.step()
-    else:
-        waves = [(0, 1, False), (1, len(prompts), False)] if w.shared_prefix else [(0, len(prompts), True)]
-        for lo, hi, atomic in waves:
-            if hi <= lo:
-                continue
+        elif eng.pending() == 0 and waves:
+            lo, hi, atomic = waves.pop(0)
             ids += eng.submit([mk(i) for i in range(lo, hi)], atomic_batch=atomic)
-            while eng.pending() > 0:
-                yield eng.step()
+            nxt = hi
+        lanes = eng.step()
+        if lanes == 0 and lockstep is not None:
+            t_idle = time.perf_counter()
+            model.ep_idle_tick()
+            model.synchronize()
+            drive.idle_s += time.perf_counter() - t_idle
+        yield lanes
     drive.last_ids = ids
 
 
-def run_step(eng_mod, model, w, reqs, active: int):
-    """One step: the whole workload through a fresh engine.  Returns (tokens, wall s, engine stats, prefix diagnostics)."""
+def run_step(eng_mod, model, w, reqs, active: int, lockstep=None):
+    """One step: the whole workload through a fresh engine.  Returns (tokens, wall s, engine stats, prefix diagnostics).
+    Under lock step the device time of the stats also counts the ticks this rank idled through (timed on the host around
+    the idle exchange and a synchronize)."""
     prompts, new, _ = reqs
     eng = new_engine(eng_mod, model, w, active, len(prompts))
     model.synchronize()
     t0 = time.perf_counter()
-    for _ in drive(eng_mod, model, eng, w, reqs):
+    for _ in drive(eng_mod, model, eng, w, reqs, lockstep):
         pass
     model.synchronize()
     wall = time.perf_counter() - t0
     st = eng.stats()
+    st["device_ms"] += drive.idle_s * 1e3
     toks = sum(len(p) for p in prompts)
     gen = 0
     for i in drive.last_ids:
@@ -255,7 +271,7 @@ def run_step(eng_mod, model, w, reqs, active: int):
 
 
 def tick_classes(eng_mod, model, w, reqs, active: int, weight_bytes_per_pass: float, kv_bytes_per_token: float, hbm_gbs: float,
-                 window_layers: tuple = (0, 0, 0)) -> dict:
+                 window_layers: tuple = (0, 0, 0), lockstep=None) -> dict:
     """One more (untimed) step driven tick by tick: device time and algorithmic HBM bytes per tick class.
     A tick's algorithmic bytes = the weight bytes one pass touches + the K/V history its lanes attend to (sliding-window
     layers count at most `window` tokens); `hbm_frac` = those bytes / device time / measured copy bandwidth - the decode
@@ -264,8 +280,8 @@ def tick_classes(eng_mod, model, w, reqs, active: int, weight_bytes_per_pass: fl
     eng = new_engine(eng_mod, model, w, active, len(prompts))
     ms = []
     before = model.launch_count()
-    for _ in drive(eng_mod, model, eng, w, reqs):
-        if model.launch_count() != before:  # a step that only delivers events runs no forward pass
+    for lanes in drive(eng_mod, model, eng, w, reqs, lockstep):
+        if lanes > 0 and model.launch_count() != before:  # a step that only delivers events runs no forward pass
             ms.append(model.last_forward_ms())
         before = model.launch_count()
     trace = eng.trace()
@@ -418,6 +434,8 @@ def main():
     ap.add_argument("--new-tokens", type=int, default=0, help="override the generated tokens per sequence")
     ap.add_argument("--limit-requests", type=int, default=0, help="only the first N requests of the workload (per replica)")
     ap.add_argument("--kv-budget-gb", type=float, default=110.0, help="largest KV arena; the active set shrinks until it fits")
+    ap.add_argument("--ep", default="auto", choices=["auto", "on", "off"],
+                    help="N > 1 and a sparse-MoE workload: expert parallelism with data-parallel lanes (auto = on) instead of replicas")
     ap.add_argument("--no-profiled-step", action="store_true", help="skip the extra step that times every launch")
     ap.add_argument("--microbench", action="store_true", help="Q4_K matmul GB/s on the decode shapes instead of the workload")
     args = ap.parse_args()
@@ -474,6 +492,16 @@ def main():
         print(json.dumps(out))
         return
 
+    ep = world > 1 and spec.experts > 0 and args.ep != "off"
+    if args.ep == "on" and not ep:
+        raise SystemExit("--ep on needs more than one GPU and a sparse-MoE workload")
+    if ep:
+        if spec.experts % world != 0:
+            raise SystemExit(f"{spec.experts} experts do not split over {world} ranks")
+        config["parallelism"] = f"dp{world} lanes x ep{world} experts"
+        config["ep"] = dict(ranks=world, local_experts=spec.experts // world, lanes="data-parallel: every rank schedules its own requests",
+                            exchange="per MoE layer: routed rows to the experts' ranks and outputs back, peer stores over NVLink",
+                            lockstep="one scalar all-reduce per tick; a rank without lanes serves the others' rows")
     capi = importlib.import_module("macllm_infer_b200._capi")
     eng_mod = importlib.import_module("macllm_infer_b200.engine")
     if capi.lib().mk_device_count() <= 0:
@@ -495,9 +523,16 @@ def main():
     cap = arena_tokens(active)
     config.update(active_sequences=active, kv_arena_gb=round(cap * kv_per_token / 1e9, 2))
     model = eng_mod.Model.load_gguf(path, device=local, kv_capacity_tokens=cap, kv_dtype="f16", prefix_capacity_tokens=w.prefix_capacity_tokens,
-                                    max_batch_tokens=w.budget, max_batch_lanes=active, matmul_path=args.matmul_path)
+                                    max_batch_tokens=w.budget, max_batch_lanes=active, matmul_path=args.matmul_path,
+                                    **(dict(ep_rank=rank, ep_size=world, ep_mode=1) if ep else {}))
+    lockstep = None
+    if ep:
+        box = [eng_mod.Model.ep_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        model.ep_init(box[0])
+        lockstep = lambda n: int(round(all_sum(dist, float(n))))
     for _ in range(args.warmup):
-        run_step(eng_mod, model, w, reqs, active)
+        run_step(eng_mod, model, w, reqs, active, lockstep)
     sampler = ClockSampler(local)
     barrier(dist)
     if rank == 0:
@@ -510,7 +545,7 @@ def main():
     diag = None
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        n, wall, st, diag = run_step(eng_mod, model, w, reqs, active)
+        n, wall, st, diag = run_step(eng_mod, model, w, reqs, active, lockstep)
         tokens += n
         dev_ms += st["device_ms"]
         ticks += st["ticks"]
@@ -527,9 +562,9 @@ def main():
 
     # one extra profiled step: CUDA events around every launch, per kernel class
     roof = None
-    if rank == 0 and not args.no_profiled_step:
+    if (rank == 0 or ep) and not args.no_profiled_step:  # under expert parallelism every forward needs all ranks
         model.profile_enable(True)
-        run_step(eng_mod, model, w, reqs, active)
+        run_step(eng_mod, model, w, reqs, active, lockstep)
         prof_rows = model.profile_query()
         model.profile_enable(False)
         total_ms = sum(r["ms"] for r in prof_rows) or 1.0
@@ -553,10 +588,13 @@ def main():
                                              tflops=round(r["flops"] / max(r["ms"], 1e-9) / 1e9, 2)) for r in prof_rows})
 
     classes = None
-    if rank == 0 and not args.no_profiled_step:
+    if (rank == 0 or ep) and not args.no_profiled_step:
         sliding = (spec.layers // 2, spec.layers, spec.window) if spec.arch == "gemma2" else (0, 0, 0)
         weights_pass = float(wb["per_token"]) if spec.experts == 0 else float(wb.get("all_experts", wb["per_token"]))
-        classes = tick_classes(eng_mod, model, w, reqs, active, weights_pass, float(model.spec().kv_bytes_per_token), pk["hbm_gbs"], sliding)
+        if ep:  # this rank's share: everything but the expert banks, plus its experts
+            expert_part = float(wb.get("experts_only", 0.0))
+            weights_pass = weights_pass - expert_part + expert_part / world
+        classes = tick_classes(eng_mod, model, w, reqs, active, weights_pass, float(model.spec().kv_bytes_per_token), pk["hbm_gbs"], sliding, lockstep)
         if roof is not None and "decode" in classes:
             # the decode roofline of the metric: weight + K/V bytes of a tick over its device time
             d = classes["decode"]

@@ -302,23 +302,47 @@ void Model::ep_init(const uint8_t* id) {
         ep_->open_exchange(cfg_.max_batch_tokens, ms_.hidden, stream_);
 }
 
+// The column width the expert-grouped matmuls are launched with: rows of one expert are processed in chunks of that many,
+// and a chunk costs the same whether it is full or not, so a tick whose experts see a handful of rows each runs narrow
+// chunks (an expert with more rows than one chunk takes a second pass over its weights), a wide tick runs full ones.
+// MACLLM_B200_MOE_CHUNK=16|32|64 pins it.
+static int moe_chunk_rows(int T, int k, int experts) {
+    static const int pinned = [] { const char* e = std::getenv("MACLLM_B200_MOE_CHUNK"); return e ? atoi(e) : 0; }();
+    if (pinned == 16 || pinned == 32 || pinned == 64) return pinned;
+    const double avg = (double)T * k / std::max(experts, 1);
+    return avg <= 6.0 ? 16 : (avg <= 14.0 ? 32 : 64);
+}
+
 // One MoE layer's experts under data-parallel expert parallelism: this rank's routed rows (grouped by expert, f16) go to
 // the ranks that hold the experts, the rows this rank received run through its expert banks, and the outputs go back.
 // Returns the area that holds the outputs of this rank's own rows in its own grouped order.
-const float* Model::ep_exchange_layer(LayerWeights& w, const LayerSpec& ls, const __half* grouped_rows, const int32_t* offsets) {
+const float* Model::ep_exchange_layer(LayerWeights& w, const LayerSpec& ls, const __half* grouped_rows, const int32_t* offsets, int T) {
     const EpDispatch& D = ep_->dispatch();
     const int EL = ep_local_experts(), H = ms_.hidden, F = ms_.expert_ffn;
     const int capacity = (int)std::min<int64_t>((int64_t)D.ranks * D.cap_rows, INT32_MAX);
     const uint32_t epoch = ep_->next_epoch();
     int32_t* status = tc_ws_.status.as<int32_t>();
+    // the other ranks' row counts are not known on the host: the chunk width follows this rank's own tick (ranks that
+    // serve similar traffic run similar ticks); any width is correct for any row count
+    const int chunk = moe_chunk_rows(std::max(T, 1) * D.ranks, ms_.experts_used, ms_.experts);
+    // the time of the two exchange halves includes waiting for the slowest peer; rows are not known on the host, so the
+    // profile's byte counts are the weights alone
+    prof_begin(KC_EP, 0, 0);
     launch_ep_dispatch(grouped_rows, offsets, D, epoch, ep_done_.as<int32_t>(), status, stream_);
     launch_ep_regroup(D, epoch, ep_merged_xh_.as<__half>(), ep_comb_off_.as<int32_t>(), ep_src_start_.as<int32_t>(), status, stream_);
-    launch_qstream_tc_grouped(w.qs_gu, EL, ep_comb_off_.as<int32_t>(), ep_merged_xh_.as<__half>(), capacity, kQStreamMaxRows, nullptr, 0, status,
-                              stream_, ls.act, ep_merged_act_.as<__half>(), F);
-    launch_qstream_tc_grouped(w.qs_down, EL, ep_comb_off_.as<int32_t>(), ep_merged_act_.as<__half>(), capacity, kQStreamMaxRows,
-                              ep_merged_out_.as<float>(), H, status, stream_);
+    prof_end();
+    prof_begin(KC_QSTREAM, (double)w.qs_gu.rows * (double)(w.qs_gu.cols / 256) * 144.0, 0);
+    launch_qstream_tc_grouped(w.qs_gu, EL, ep_comb_off_.as<int32_t>(), ep_merged_xh_.as<__half>(), capacity, chunk, nullptr, 0, status,
+                              stream_, ls.act, ep_merged_act_.as<__half>(), F, false);
+    prof_end();
+    prof_begin(KC_QSTREAM, (double)w.qs_down.rows * (double)(w.qs_down.cols / 256) * (w.qs_down.fmt ? 210.0 : 144.0), 0);
+    launch_qstream_tc_grouped(w.qs_down, EL, ep_comb_off_.as<int32_t>(), ep_merged_act_.as<__half>(), capacity, chunk,
+                              ep_merged_out_.as<float>(), H, status, stream_, -1, nullptr, 0, false);
+    prof_end();
+    prof_begin(KC_EP, 0, 0);
     launch_ep_return(ep_merged_out_.as<float>(), ep_src_start_.as<int32_t>(), D, epoch, ep_done_.as<int32_t>() + kEpMaxRanks, stream_);
     launch_ep_wait_back(D, epoch, status, stream_);
+    prof_end();
     launches_ += 6;
     return ep_result_area(D, epoch);
 }
@@ -327,7 +351,7 @@ void Model::ep_idle_tick() {
     if (cfg_.ep_mode != 1 || !ep_ || !ep_->has_dispatch()) throw std::runtime_error("ep_idle_tick needs a model in data-parallel expert parallelism after mk_model_ep_init");
     MK_CUDA(cudaSetDevice(cfg_.device));
     for (int l = 0; l < ms_.layers; ++l)
-        if (ms_.layer[(size_t)l].moe) ep_exchange_layer(lw_[(size_t)l], ms_.layer[(size_t)l], e_xh_.as<__half>(), ep_zero_off_.as<int32_t>());
+        if (ms_.layer[(size_t)l].moe) ep_exchange_layer(lw_[(size_t)l], ms_.layer[(size_t)l], e_xh_.as<__half>(), ep_zero_off_.as<int32_t>(), 0);
 }
 
 void Model::load_weights(const GgufFile& f) {
@@ -408,7 +432,7 @@ void Model::rope_tables_for(double theta, const float*& cos_t, const float*& sin
 // ---------------------------------------------------------------------------- profiling
 
 static const char* kclass_names[] = {"qgemm_tc", "hgemm_tc", "qstream_tc", "qgemv", "paged_attention", "add_norm_quant", "rope_kv_scatter", "actmul_quant",
-                                     "embed", "build_batch", "argmax", "moe", "hgemm_tc_splitk"};
+                                     "embed", "build_batch", "argmax", "moe", "hgemm_tc_splitk", "ep_exchange"};
 
 void Model::profile_enable(bool on) {
     profiling_ = on;
@@ -1084,10 +1108,16 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         } else {
             // sparse MoE (src/decoder.rs:394-554)
             const int E = ms_.experts, K = ms_.experts_used, F = ms_.expert_ffn, P = T * K;
+            prof_begin(KC_MOE, 4.0 * E * H + 4.0 * T * H + 4.0 * T * E, 2.0 * T * E * H);
             launch_f32_gemv(w.router.as<float>(), E, H, normed_.as<float>(), T, router_logits_.as<float>(), stream_);
+            prof_end();
+            prof_begin(KC_MOE, 4.0 * T * E + 8.0 * P, 0);
             launch_moe_route(router_logits_.as<float>(), T, E, K, sel_e_.as<int32_t>(), sel_w_.as<float>(), tc_ws_.status.as<int32_t>(), stream_);
+            prof_end();
+            prof_begin(KC_MOE, 12.0 * P, 0);
             launch_moe_group(sel_e_.as<int32_t>(), T, K, E, grp_off_.as<int32_t>(), pos_of_pair_.as<int32_t>(), tok_of_pos_.as<int32_t>(),
                              stream_);
+            prof_end();
             ActQ xq = xf;
             xq.xh = nullptr;
             const bool moe_stream = qstream_moe_ && xf.xh != nullptr && (ep_dp || (f16_T && T >= qstream_min_rows_));
@@ -1102,7 +1132,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
                 prof_begin(KC_MOE, 4.0 * P * H, 0);
                 launch_gather_rows_half(xf.xh, tok_of_pos_.as<int32_t>(), P, H, e_xh_.as<__half>(), stream_);
                 prof_end();
-                const float* back = ep_exchange_layer(w, ls, e_xh_.as<__half>(), grp_off_.as<int32_t>());
+                const float* back = ep_exchange_layer(w, ls, e_xh_.as<__half>(), grp_off_.as<int32_t>(), T);
                 launch_moe_combine(back, sel_e_.as<int32_t>(), sel_w_.as<float>(), pos_of_pair_.as<int32_t>(), T, K, H, 0, E, down_.as<float>(),
                                    stream_);
             } else {
@@ -1115,12 +1145,12 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
                 prof_end();
                 const double gu_bytes = (double)w.qs_gu.rows * (double)(w.qs_gu.cols / 256) * 144.0;
                 prof_begin(KC_QSTREAM, gu_bytes + 2.0 * P * H + 2.0 * P * F, 2.0 * P * 2.0 * F * H);
-                launch_qstream_tc_grouped(w.qs_gu, EL, off, e_xh_.as<__half>(), P, std::min(T, kQStreamMaxRows), nullptr, 0, tc_ws_.status.as<int32_t>(), stream_,
+                launch_qstream_tc_grouped(w.qs_gu, EL, off, e_xh_.as<__half>(), P, moe_chunk_rows(T, K, E), nullptr, 0, tc_ws_.status.as<int32_t>(), stream_,
                                           ls.act, f_xh_.as<__half>(), F);
                 prof_end();
                 const double dn_bytes = (double)w.qs_down.rows * (double)(w.qs_down.cols / 256) * (w.qs_down.fmt ? 210.0 : 144.0);
                 prof_begin(KC_QSTREAM, dn_bytes + 2.0 * P * F + 4.0 * P * H, 2.0 * P * (double)F * H);
-                launch_qstream_tc_grouped(w.qs_down, EL, off, f_xh_.as<__half>(), P, std::min(T, kQStreamMaxRows), e_down_.as<float>(), H,
+                launch_qstream_tc_grouped(w.qs_down, EL, off, f_xh_.as<__half>(), P, moe_chunk_rows(T, K, E), e_down_.as<float>(), H,
                                           tc_ws_.status.as<int32_t>(), stream_);
                 prof_end();
             } else {
@@ -1136,8 +1166,10 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
                                             H, e0, e0 + EL, ep_->peers(), ep_->next_epoch(), down_.as<float>(),
                                             tc_ws_.status.as<int32_t>(), stream_);
             } else {
+                prof_begin(KC_MOE, 4.0 * P * H + 4.0 * T * H, 2.0 * P * H);
                 launch_moe_combine(e_down_.as<float>(), sel_e_.as<int32_t>(), sel_w_.as<float>(), pos_of_pair_.as<int32_t>(), T, K, H,
                                    e0, e0 + EL, ep ? ep_partial_.as<float>() : down_.as<float>(), stream_);
+                prof_end();
             }
             if (ep && !ep_->has_exchange()) {
                 ep_->all_gather_f32(ep_partial_.as<float>(), ep_gather_.as<float>(), (size_t)T * H, stream_);

@@ -119,7 +119,7 @@ private:
     bool timed_ = false;
     int64_t launches_ = 0, h2d_bytes_ = 0, d2h_bytes_ = 0;
     // profiling: one event pair per launch group, resolved after the tick's barrier
-    enum KClass { KC_GEMM_TC = 0, KC_HGEMM, KC_QSTREAM, KC_GEMV, KC_ATTN, KC_NORM_QUANT, KC_ROPE_KV, KC_ACTMUL, KC_EMBED, KC_BATCH, KC_SAMPLE, KC_MOE, KC_HGEMM_NARROW, KC_COUNT };
+    enum KClass { KC_GEMM_TC = 0, KC_HGEMM, KC_QSTREAM, KC_GEMV, KC_ATTN, KC_NORM_QUANT, KC_ROPE_KV, KC_ACTMUL, KC_EMBED, KC_BATCH, KC_SAMPLE, KC_MOE, KC_HGEMM_NARROW, KC_EP, KC_COUNT };
     struct ProfSpan { int cls; double bytes, flops; cudaEvent_t a, b; };
     bool profiling_ = false;
     std::vector<ProfSpan> spans_;
@@ -182,7 +182,7 @@ private:
     // ranges, where each source's rows start, the completion counters of the two exchange kernels, and an all-zero
     // range table for a tick without rows
     DevBuf ep_merged_xh_, ep_merged_act_, ep_merged_out_, ep_comb_off_, ep_src_start_, ep_done_, ep_zero_off_;
-    const float* ep_exchange_layer(LayerWeights& w, const LayerSpec& ls, const __half* grouped_rows, const int32_t* offsets);
+    const float* ep_exchange_layer(LayerWeights& w, const LayerSpec& ls, const __half* grouped_rows, const int32_t* offsets, int T);
     QgemmWorkspace tc_ws_;
     PinnedBuf out_host_;
     int out_lanes_ = 0;

@@ -7,14 +7,19 @@
 // order - the order index_add produces - so the sum is bit-identical for identical contributions.
 #include "kernels.h"
 
+#include <climits>
+
 namespace mk {
 
 namespace {
 
 constexpr int MAX_EXPERTS = 1024;
 
-// One CTA.  Counting sort of pairs by expert; positions inside an expert follow pair order.
-__global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t* sel, int pairs, int k, int experts, int32_t* offsets,
+// Counting sort of the (token, choice) pairs by expert; positions inside an expert follow pair order.  CTA b owns the
+// experts [32 b, 32 b + 32), one warp each.  Every CTA counts all experts for itself (the start of its own experts needs
+// the counts of all earlier ones); then each warp walks the pairs 32 at a time and gives the pairs of its expert their
+// positions from a ballot: the rank of a pair among its expert's pairs is the number of earlier pairs of that expert.
+__global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t* __restrict__ sel, int pairs, int k, int experts, int32_t* offsets,
                                                          int32_t* pos_of_pair, int32_t* token_of_pos) {
     __shared__ int32_t count[MAX_EXPERTS];
     __shared__ int32_t start[MAX_EXPERTS + 1];
@@ -24,56 +29,109 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t* sel, int
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
         const int e = sel[p];
         if (e >= 0 && e < experts) atomicAdd(&count[e], 1);
-        else pos_of_pair[p] = -1;
+        else if (blockIdx.x == 0) pos_of_pair[p] = -1;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int acc = 0;
-        for (int e = 0; e < experts; ++e) { start[e] = acc; acc += count[e]; }
-        start[experts] = acc;
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = start[e];
-    // deterministic placement: expert e's positions are assigned in increasing pair order by one thread per expert
-    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-        if (count[e] == 0) continue;
-        int pos = start[e];
-        for (int p = 0; p < pairs; ++p) {
-            if (sel[p] == e) {
-                pos_of_pair[p] = pos;
-                token_of_pos[pos] = p / k;
-                ++pos;
+    if (threadIdx.x < 32) {  // exclusive scan of the counts by one warp, 32 experts at a time
+        int carry = 0;
+        for (int base = 0; base < experts; base += 32) {
+            const int e = base + (int)threadIdx.x;
+            const int c = e < experts ? count[e] : 0;
+            int inc = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, inc, o);
+                if ((int)threadIdx.x >= o) inc += v;
             }
+            if (e < experts) start[e] = carry + inc - c;
+            carry += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (threadIdx.x == 0) start[experts] = carry;
+    }
+    __syncthreads();
+    if (blockIdx.x == 0)
+        for (int e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = start[e];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = (int)blockIdx.x * 32 + warp;
+    if (e >= experts || count[e] == 0) return;
+    int pos = start[e];
+    const unsigned below = (1u << lane) - 1u;
+    for (int base = 0; base < pairs; base += 128) {  // four independent loads in flight per lane
+        int mine[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int p = base + 32 * j + lane;
+            mine[j] = p < pairs ? sel[p] : -1;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const unsigned m = __ballot_sync(0xffffffffu, mine[j] == e);
+            if (mine[j] == e) {
+                const int p = base + 32 * j + lane, at = pos + __popc(m & below);
+                pos_of_pair[p] = at;
+                token_of_pos[at] = p / k;
+            }
+            pos += __popc(m);
         }
     }
 }
 
 // Only choices whose expert lies in [e_lo, e_hi) contribute (the whole range on one GPU, a rank's share under
 // expert parallelism).
-__global__ void moe_combine_kernel(const float* expert_out, const int32_t* sel, const float* w, const int32_t* pos_of_pair, int k,
-                                   int hidden, int e_lo, int e_hi, float* out) {
-    int t = blockIdx.x;
-    // choices sorted by expert index (k <= 32)
-    __shared__ int order[32];
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < k; ++i) order[i] = i;
-        for (int i = 1; i < k; ++i) {
-            int o = order[i], j = i - 1;
-            while (j >= 0 && sel[t * k + order[j]] > sel[t * k + o]) { order[j + 1] = order[j]; --j; }
-            order[j + 1] = o;
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ expert_out, const int32_t* __restrict__ sel,
+                                                          const float* __restrict__ w, const int32_t* __restrict__ pos_of_pair, int k,
+                                                          int hidden, int e_lo, int e_hi, float* __restrict__ out) {
+    const int t = blockIdx.x;
+    // the token's choices held here, sorted by expert index (k <= 32): row position and weight of each
+    __shared__ int s_pos[32], n_here;
+    __shared__ float s_w[32];
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        const int e = lane < k ? sel[t * k + lane] : INT_MAX;
+        const bool here = lane < k && e >= e_lo && e < e_hi;
+        // rank among the choices held here: experts of one token are distinct, so the expert index orders them
+        int rank = 0;
+        for (int j = 0; j < k; ++j) {
+            const int ej = __shfl_sync(0xffffffffu, e, j);
+            const bool hj = ej >= e_lo && ej < e_hi;
+            if (hj && (ej < e || (ej == e && j < lane))) ++rank;
         }
+        if (here) {
+            s_pos[rank] = pos_of_pair[t * k + lane];
+            s_w[rank] = w[t * k + lane];
+        }
+        const unsigned m = __ballot_sync(0xffffffffu, here);
+        if (lane == 0) n_here = __popc(m);
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        float acc = 0.f;
-        for (int i = 0; i < k; ++i) {
-            int choice = order[i];
-            int e = sel[t * k + choice];
-            if (e < e_lo || e >= e_hi) continue;
-            float v = expert_out[(int64_t)pos_of_pair[t * k + choice] * hidden + c];
-            acc = __fadd_rn(acc, __fmul_rn(v, w[t * k + choice]));
+    const int n = n_here;
+    if (hidden % 4 == 0) {
+        const int h4 = hidden / 4;
+        for (int c = threadIdx.x; c < h4; c += blockDim.x) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int base = 0; base < n; base += 8) {  // eight rows in flight, then added in order
+                float4 v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (base + i < n) v[i] = reinterpret_cast<const float4*>(expert_out + (int64_t)s_pos[base + i] * hidden)[c];
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (base + i < n) {
+                        const float wt = s_w[base + i];
+                        acc.x = __fadd_rn(acc.x, __fmul_rn(v[i].x, wt));
+                        acc.y = __fadd_rn(acc.y, __fmul_rn(v[i].y, wt));
+                        acc.z = __fadd_rn(acc.z, __fmul_rn(v[i].z, wt));
+                        acc.w = __fadd_rn(acc.w, __fmul_rn(v[i].w, wt));
+                    }
+            }
+            reinterpret_cast<float4*>(out + (int64_t)t * hidden)[c] = acc;
         }
-        out[(int64_t)t * hidden + c] = acc;
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            float acc = 0.f;
+            for (int i = 0; i < n; ++i) acc = __fadd_rn(acc, __fmul_rn(expert_out[(int64_t)s_pos[i] * hidden + c], s_w[i]));
+            out[(int64_t)t * hidden + c] = acc;
+        }
     }
 }
 
@@ -226,7 +284,7 @@ void launch_moe_group(const int32_t* sel_experts, int T, int k, int experts, int
                       int32_t* token_of_pos, cudaStream_t s) {
     if (T <= 0) return;
     if (experts > MAX_EXPERTS) throw std::runtime_error("launch_moe_group: more than 1024 experts");
-    moe_group_kernel<<<1, 1024, 0, s>>>(sel_experts, T * k, k, experts, offsets, pos_of_pair, token_of_pos);
+    moe_group_kernel<<<(experts + 31) / 32, 1024, 0, s>>>(sel_experts, T * k, k, experts, offsets, pos_of_pair, token_of_pos);
     MK_LAUNCH_CHECK();
 }
 

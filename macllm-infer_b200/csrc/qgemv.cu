@@ -227,6 +227,11 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) qgemv_q80_kernel(const int8_t
 }
 
 // ---------------------------------------------------------------- F32 (router)
+constexpr int F32_GEMV_ROWS = 8;
+// y[t][n] = sum_k x[t][k] * W[n][k] for a small f32 matrix (the MoE router).  One warp per output n and run of
+// F32_GEMV_ROWS rows of x (blockIdx.y): the rows' sums advance side by side, so a warp has a row's worth of independent
+// loads in flight per step instead of one chain.  The sum of one (row, output) pair is always formed the same way -
+// lane-strided partial sums in ascending k, then the warp tree - whatever the grid or the number of rows.
 __global__ void __launch_bounds__(GEMV_WARPS * 32) f32_gemv_kernel(const float* __restrict__ W, int out, int in,
                                                                    const float* __restrict__ x, int T,
                                                                    float* __restrict__ y) {
@@ -234,12 +239,31 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) f32_gemv_kernel(const float* 
     if (n >= out) return;
     int lane = threadIdx.x & 31;
     const float* w = W + (int64_t)n * in;
-    for (int t = 0; t < T; ++t) {
-        const float* xr = x + (int64_t)t * in;
-        float acc = 0.f;
-        for (int k = lane; k < in; k += 32) acc += xr[k] * w[k];
-        acc = warp_sum(acc);
-        if (lane == 0) y[(int64_t)t * out + n] = acc;
+    const int t0 = (int)blockIdx.y * F32_GEMV_ROWS;
+    const int rows = min(F32_GEMV_ROWS, T - t0);
+    const float* xr = x + (int64_t)t0 * in;
+    float acc[F32_GEMV_ROWS];
+#pragma unroll
+    for (int r = 0; r < F32_GEMV_ROWS; ++r) acc[r] = 0.f;
+    if (rows == F32_GEMV_ROWS) {
+#pragma unroll 4
+        for (int k = lane; k < in; k += 32) {
+            const float wv = w[k];
+#pragma unroll
+            for (int r = 0; r < F32_GEMV_ROWS; ++r) acc[r] += xr[(int64_t)r * in + k] * wv;
+        }
+    } else {
+        for (int k = lane; k < in; k += 32) {
+            const float wv = w[k];
+#pragma unroll
+            for (int r = 0; r < F32_GEMV_ROWS; ++r)
+                if (r < rows) acc[r] += xr[(int64_t)r * in + k] * wv;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < F32_GEMV_ROWS; ++r) {
+        const float v = warp_sum(acc[r]);
+        if (lane == 0 && r < rows) y[(int64_t)(t0 + r) * out + n] = v;
     }
 }
 
@@ -286,7 +310,7 @@ void launch_qgemv_grouped(const QWeight& W, int experts, const int32_t* offsets,
 
 void launch_f32_gemv(const float* W, int out, int in, const float* x, int T, float* y, cudaStream_t s) {
     if (T <= 0) return;
-    unsigned grid = (unsigned)((out + GEMV_WARPS - 1) / GEMV_WARPS);
+    dim3 grid((unsigned)((out + GEMV_WARPS - 1) / GEMV_WARPS), (unsigned)((T + F32_GEMV_ROWS - 1) / F32_GEMV_ROWS));
     f32_gemv_kernel<<<grid, GEMV_WARPS * 32, 0, s>>>(W, out, in, x, T, y);
     MK_LAUNCH_CHECK();
 }

@@ -925,7 +925,7 @@ int launch_qstream_tc(const QStreamWeight& W, const __half* xh, int T, float* y,
 
 // Expert-grouped form (SparseMoeFeedForward::forward, src/decoder.rs:394-441: every expert multiplies the rows routed to it).
 int launch_qstream_tc_grouped(const QStreamWeight& W, int experts, const int32_t* offsets_dev, const __half* xh, int rows_total,
-                              int max_rows_per_expert, float* y, int ldy, int32_t* status, cudaStream_t s, int gated_act, __half* yh, int ldyh) {
+                              int max_rows_per_expert, float* y, int ldy, int32_t* status, cudaStream_t s, int gated_act, __half* yh, int ldyh, bool rows_known) {
     if (rows_total <= 0) return 1;
     if (!W.ready) throw std::runtime_error("launch_qstream_tc_grouped: the matrix was not re-tiled");
     if (experts <= 0 || W.rows % experts != 0 || (W.rows / experts) % QS_BM != 0)
@@ -941,7 +941,7 @@ int launch_qstream_tc_grouped(const QStreamWeight& W, int experts, const int32_t
     const int sms = device_sm_count();
     // a bound on the jobs any CTA is handed: every expert may add one partly filled chunk
     const int64_t max_jobs = ((int64_t)rows_total / bn + experts) * (tiles_pe / R);
-    if ((max_jobs + sms - 1) / sms + 1 > QS_MAX_JOBS) throw std::runtime_error("launch_qstream_tc_grouped: more jobs per CTA than the kernel's table holds");
+    if (rows_known && (max_jobs + sms - 1) / sms + 1 > QS_MAX_JOBS) throw std::runtime_error("launch_qstream_tc_grouped: more jobs per CTA than the kernel's table holds");
     alignas(64) CUtensorMap tx;
     encode_tma_2d(&tx, false, xh, (uint64_t)W.cols, (uint64_t)rows_total, (uint64_t)W.cols * 2, 64, (uint32_t)bn, true);
     QsParams p{};

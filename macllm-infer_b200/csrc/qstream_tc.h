@@ -52,11 +52,14 @@ int launch_qstream_tc(const QStreamWeight& W, const __half* xh, int T, float* y,
 // Expert-grouped form: W is a bank of `experts` matrices stacked by rows (each a whole number of 128-row tiles);
 // activation rows [offsets[e], offsets[e + 1]) of xh [rows_total][cols] (grouped by expert, device array of experts + 1
 // row numbers) are multiplied by expert e's matrix: y[r][n] for those rows r and n < rows per expert, or, gated,
-// yh[r][f].  max_rows_per_expert bounds any expert's row count (it picks the token-tile width); experts with more rows
-// than 64 take several passes over their matrix.  The kernel reads the row ranges on the device: no host round trip.
+// yh[r][f].  max_rows_per_expert picks the chunk width (16, 32 or 64 rows): an expert's rows are processed a chunk at a
+// time, each chunk one pass over the expert's matrix, so any width is correct for any row count.  The kernel reads the
+// row ranges on the device: no host round trip.  rows_known = false: rows_total is only the extent of xh (the true row
+// count lives on the device); the host then cannot bound the jobs per CTA, and a launch that overflows the kernel's job
+// table reports status 30 instead of an exception here.
 int launch_qstream_tc_grouped(const QStreamWeight& W, int experts, const int32_t* offsets_dev, const __half* xh, int rows_total,
                               int max_rows_per_expert, float* y, int ldy, int32_t* status, cudaStream_t s, int gated_act = -1,
-                              __half* yh = nullptr, int ldyh = 0);
+                              __half* yh = nullptr, int ldyh = 0, bool rows_known = true);
 
 // Measuring aid: when set (a device buffer of 40 int64), CTA 0 of every following launch records the cycles its roles
 // spent waiting: rows weight loader, MMA issuer, activation loader, first converter warp, first epilogue warp; columns

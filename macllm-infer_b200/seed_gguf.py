@@ -252,7 +252,7 @@ def write_seed_gguf_shards(directory: str | Path, prefix: str, spec: SeedSpec, s
 
 def weight_bytes(spec: SeedSpec) -> dict:
     """Algorithmic byte counts of the checkpoint: all matrices, and what one decode row touches."""
-    total = per_token = all_experts = 0
+    total = per_token = all_experts = experts_only = 0
     for name, dims, qtype, std in tensor_plan(spec):
         if len(dims) < 2:
             continue
@@ -261,6 +261,7 @@ def weight_bytes(spec: SeedSpec) -> dict:
         if "_exps" in name:
             per_token += n // spec.experts * spec.experts_used
             all_experts += n
+            experts_only += n
         elif name == "token_embd.weight" and not spec.tied:
             pass  # only a row gather touches it
         else:
@@ -268,4 +269,4 @@ def weight_bytes(spec: SeedSpec) -> dict:
             all_experts += n
     kv_per_token = 2 * spec.layers * spec.kv_heads * spec.head_dim * 2
     # all_experts: what a decode tick touches once its lanes hit every expert (a batch of some 64 lanes and more)
-    return {"total": total, "per_token": per_token, "all_experts": all_experts, "kv_f16_per_token": kv_per_token}
+    return {"total": total, "per_token": per_token, "all_experts": all_experts, "experts_only": experts_only, "kv_f16_per_token": kv_per_token}
