@@ -38,10 +38,12 @@ __device__ __forceinline__ uint64_t now_ns() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-__device__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint64_t wait_ns) {
+// Once a wait of this forward has given up (the status word is set) the later ones do not wait again: a broken exchange
+// costs one limit, not one per layer.
+__device__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint64_t wait_ns, const int32_t* status) {
     const uint64_t t0 = now_ns();
     while (ld_acquire_sys(flag) != epoch) {
-        if (now_ns() - t0 > wait_ns) return false;
+        if (*reinterpret_cast<const volatile int32_t*>(status) != 0 || now_ns() - t0 > wait_ns) return false;
         __nanosleep(100);
     }
     return true;
@@ -104,7 +106,7 @@ __global__ void __launch_bounds__(256) ep_regroup_kernel(EpDispatch D, uint32_t 
     const int EL = D.local_experts, N = D.ranks, me = D.rank, buf = (int)(epoch & 1u);
     if (threadIdx.x == 0) ok = 1;
     __syncthreads();
-    if ((int)threadIdx.x < N && !wait_flag(flag_in(D, me, buf, threadIdx.x), epoch, wait_ns)) {
+    if ((int)threadIdx.x < N && !wait_flag(flag_in(D, me, buf, threadIdx.x), epoch, wait_ns, status)) {
         atomicCAS(status, 0, 0x4550000 | (int)threadIdx.x);
         ok = 0;
     }
@@ -182,7 +184,7 @@ __global__ void ep_scale_rows_kernel(const __half* __restrict__ x, const int32_t
 
 __global__ void ep_wait_back_kernel(EpDispatch D, uint32_t epoch, uint64_t wait_ns, int32_t* status) {
     const int buf = (int)(epoch & 1u);
-    if ((int)threadIdx.x < D.ranks && !wait_flag(flag_back(D, D.rank, buf, threadIdx.x), epoch, wait_ns)) atomicCAS(status, 0, 0x4550000 | (int)threadIdx.x);
+    if ((int)threadIdx.x < D.ranks && !wait_flag(flag_back(D, D.rank, buf, threadIdx.x), epoch, wait_ns, status)) atomicCAS(status, 0, 0x4550000 | (int)threadIdx.x);
 }
 
 }  // namespace

@@ -285,6 +285,8 @@ void Model::ep_init(const uint8_t* id) {
         const int EL = ep_local_experts(), N = cfg_.ep_size;
         const int64_t cap = (int64_t)cfg_.max_batch_tokens * ms_.experts_used;
         ep_->open_dispatch(cap, ms_.hidden, EL, stream_);
+        // how long a rank waits for a peer's rows before it reports the peer missing (MACLLM_B200_EP_WAIT_MS, default 5 s)
+        if (const char* e = std::getenv("MACLLM_B200_EP_WAIT_MS")) ep_wait_ns_ = (uint64_t)std::max(1, atoi(e)) * 1000000ull;
         ep_merged_xh_.alloc((size_t)N * cap * ms_.hidden * 2);
         ep_merged_act_.alloc((size_t)N * cap * ms_.expert_ffn * 2);
         ep_merged_out_.alloc((size_t)N * cap * ms_.hidden * 4);
@@ -322,14 +324,15 @@ const float* Model::ep_exchange_layer(LayerWeights& w, const LayerSpec& ls, cons
     const int capacity = (int)std::min<int64_t>((int64_t)D.ranks * D.cap_rows, INT32_MAX);
     const uint32_t epoch = ep_->next_epoch();
     int32_t* status = tc_ws_.status.as<int32_t>();
-    // the other ranks' row counts are not known on the host: the chunk width follows this rank's own tick (ranks that
-    // serve similar traffic run similar ticks); any width is correct for any row count
-    const int chunk = moe_chunk_rows(std::max(T, 1) * D.ranks, ms_.experts_used, ms_.experts);
+    // the other ranks' row counts are not known on the host (a peer may run a prefill chunk while this rank decodes), and
+    // a narrow chunk under many rows costs a pass over the expert's weights per chunk: always the full width
+    (void)T;
+    const int chunk = kQStreamMaxRows;
     // the time of the two exchange halves includes waiting for the slowest peer; rows are not known on the host, so the
     // profile's byte counts are the weights alone
     prof_begin(KC_EP, 0, 0);
     launch_ep_dispatch(grouped_rows, offsets, D, epoch, ep_done_.as<int32_t>(), status, stream_);
-    launch_ep_regroup(D, epoch, ep_merged_xh_.as<__half>(), ep_comb_off_.as<int32_t>(), ep_src_start_.as<int32_t>(), status, stream_);
+    launch_ep_regroup(D, epoch, ep_merged_xh_.as<__half>(), ep_comb_off_.as<int32_t>(), ep_src_start_.as<int32_t>(), status, stream_, ep_wait_ns_);
     prof_end();
     prof_begin(KC_QSTREAM, (double)w.qs_gu.rows * (double)(w.qs_gu.cols / 256) * 144.0, 0);
     launch_qstream_tc_grouped(w.qs_gu, EL, ep_comb_off_.as<int32_t>(), ep_merged_xh_.as<__half>(), capacity, chunk, nullptr, 0, status,
@@ -341,7 +344,7 @@ const float* Model::ep_exchange_layer(LayerWeights& w, const LayerSpec& ls, cons
     prof_end();
     prof_begin(KC_EP, 0, 0);
     launch_ep_return(ep_merged_out_.as<float>(), ep_src_start_.as<int32_t>(), D, epoch, ep_done_.as<int32_t>() + kEpMaxRanks, stream_);
-    launch_ep_wait_back(D, epoch, status, stream_);
+    launch_ep_wait_back(D, epoch, status, stream_, ep_wait_ns_);
     prof_end();
     launches_ += 6;
     return ep_result_area(D, epoch);

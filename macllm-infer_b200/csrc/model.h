@@ -182,6 +182,7 @@ private:
     // ranges, where each source's rows start, the completion counters of the two exchange kernels, and an all-zero
     // range table for a tick without rows
     DevBuf ep_merged_xh_, ep_merged_act_, ep_merged_out_, ep_comb_off_, ep_src_start_, ep_done_, ep_zero_off_;
+    uint64_t ep_wait_ns_ = kEpWaitNs;
     const float* ep_exchange_layer(LayerWeights& w, const LayerSpec& ls, const __half* grouped_rows, const int32_t* offsets, int T);
     QgemmWorkspace tc_ws_;
     PinnedBuf out_host_;

@@ -8,6 +8,7 @@
 #include <cmath>
 #include <cstring>
 #include <algorithm>
+#include <thread>
 #include <vector>
 #include <stdexcept>
 
@@ -187,7 +188,10 @@ void seed_tensor(uint64_t seed, uint64_t stream, float std_dev, int type, int64_
     if (rb < 0) throw std::runtime_error("seed_tensor: unsupported type or column count");
     uint64_t key = splitmix64(seed * 0x100000001B3ull + splitmix64(stream));
     uint8_t* o = static_cast<uint8_t*>(out);
-#pragma omp parallel
+    // every host core, whatever OMP_NUM_THREADS says: launchers of multi-process jobs export 1, which would turn the
+    // seconds a seeded checkpoint takes into many minutes.  Rows are independent, so the bytes do not depend on it.
+    const int threads = std::max(1, (int)std::thread::hardware_concurrency());
+#pragma omp parallel num_threads(threads)
     {
         std::vector<float> row((size_t)cols);
 #pragma omp for schedule(static)

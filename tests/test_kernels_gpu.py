@@ -495,3 +495,28 @@ def test_expert_grouped_gated_matmul_matches_oracle(ops, orc, act):
     assert np.isfinite(got).all()
     # gate and up each carry the f16-operand error of the matmul; the product adds them, then one f16 rounding
     assert np.max(np.abs(got - want)) <= 3e-3 * scale * (2 * gmax + umax + 1)
+
+
+def test_expert_grouped_gated_matmul_on_the_moe_decode_shape(ops, orc):
+    """One MoE layer's gate|up bank of the 30B-A3B shape (128 experts of 768 x 2048 Q4_K each for gate and for up) with the
+    routed rows of a 72-lane decode tick (576 rows, a few per expert, some experts idle); checked against the oracle on
+    every eighth expert.  Also the launch the profiler capture of the expert-grouped kernel runs."""
+    experts, F, cols, P = 128, 768, 2048, 576
+    rng = np.random.default_rng(30)
+    counts = np.bincount(rng.integers(0, experts, P), minlength=experts)
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    x = rng.standard_normal((P, cols)).astype(np.float32)
+    gate = _weights(ops, 12, experts * F, cols, stream=14)
+    up = _weights(ops, 12, experts * F, cols, stream=15)
+    rb = len(gate) // (experts * F)
+    got = ops.grouped_qmatmul(12, gate, experts, F, cols, x, offsets, 4, up_bank=up, act=0)
+    assert np.isfinite(got).all()
+    scale = np.sqrt(cols) * 0.02
+    for e in range(0, experts, 8):
+        lo, hi = offsets[e], offsets[e + 1]
+        if hi == lo:
+            continue
+        g = orc.qmatmul(12, gate[e * F * rb:(e + 1) * F * rb], F, cols, x[lo:hi], 1)
+        u = orc.qmatmul(12, up[e * F * rb:(e + 1) * F * rb], F, cols, x[lo:hi], 1)
+        want = orc.act_mul(g, u, 0)
+        assert np.max(np.abs(got[lo:hi] - want)) <= 3e-3 * scale * (2 * float(np.abs(g).max()) + float(np.abs(u).max()) + 1), e
