@@ -12,7 +12,7 @@
 //               contiguous run per local expert and writes the row ranges the grouped matmuls read;
 //   (the two expert-grouped matmuls run on those rows)
 //   return    - every output row goes back into its source's result area at the position the source's own grouping gave
-//               it; the last CTA publishes the epoch in the source's return flag;
+//               it, one CTA per (source, local expert); the last CTA of a source publishes the epoch in its return flag;
 //   wait_back - waits (bounded) for the return flags of all destinations; the ordinary combine kernel then adds a token's
 //               choices in ascending expert order from the result area.
 // Buffers alternate with the epoch's parity: a rank can reach exchange e + 2 only after every peer has returned its rows
@@ -65,7 +65,25 @@ __device__ __forceinline__ uint32_t* flag_back(const EpDispatch& D, int p, int b
     return reinterpret_cast<uint32_t*>(D.base[p] + D.flag_back_off) + buf * D.ranks + dst;
 }
 
-constexpr int EPD_SLICES = 16;  // CTAs per destination / source
+constexpr int EPD_SLICES = 64;  // CTAs per destination of the dispatch copy
+constexpr int EPD_PARTS = 1;    // CTAs per (source, local expert) segment of the regroup and return copies
+constexpr int EPD_COPY_THREADS = 1024;  // threads of those CTAs: few CTAs poll the flags, many threads carry the copies
+
+// Part `part` of `parts` of a copy of n 16-byte pieces by one CTA, four loads in flight per thread (a wide tick moves
+// hundreds of megabytes per layer through these copies; one load at a time would leave them latency-bound).
+template <typename V>
+__device__ __forceinline__ void copy_part(V* __restrict__ to, const V* __restrict__ from, int64_t n, int part, int parts) {
+    const int64_t stride = (int64_t)parts * blockDim.x;
+    int64_t i = (int64_t)part * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < n; i += 4 * stride) {
+        const V a = from[i], b = from[i + stride], c = from[i + 2 * stride], d = from[i + 3 * stride];
+        to[i] = a;
+        to[i + stride] = b;
+        to[i + 2 * stride] = c;
+        to[i + 3 * stride] = d;
+    }
+    for (; i < n; i += stride) to[i] = from[i];
+}
 
 // grid (ranks * EPD_SLICES).  x: this rank's routed rows grouped by expert, f16 [P][hidden]; off: [experts + 1].
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ off, EpDispatch D, uint32_t epoch,
@@ -81,8 +99,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const uint4* __restric
     const int chunks = D.hidden / 8;  // 16-byte pieces per row
     uint4* dst = reinterpret_cast<uint4*>(rows_in(D, d, buf, me));
     const uint4* src = x + (int64_t)r0 * chunks;
-    const int64_t total = (int64_t)n * chunks;
-    for (int64_t i = (int64_t)slice * blockDim.x + threadIdx.x; i < total; i += (int64_t)EPD_SLICES * blockDim.x) dst[i] = src[i];
+    copy_part(dst, src, (int64_t)n * chunks, slice, EPD_SLICES);
     if (slice == 0)
         for (int le = threadIdx.x; le <= EL; le += blockDim.x) off_in(D, d, buf, me)[le] = off[d * EL + le];
     __threadfence_system();
@@ -96,10 +113,10 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const uint4* __restric
     }
 }
 
-// grid (ranks * local_experts): CTA (src, le) moves that source's rows for local expert le to their place in the merged
-// run.  comb_off [EL + 1]: row ranges per local expert in the merged run; src_start [ranks][EL]: where each source's
+// grid (ranks * local_experts * EPD_PARTS): the CTAs (src, le, part) move that source's rows for local expert le to their
+// place in the merged run.  comb_off [EL + 1]: row ranges per local expert in the merged run; src_start [ranks][EL]: where each source's
 // rows of an expert begin in it.
-__global__ void __launch_bounds__(256) ep_regroup_kernel(EpDispatch D, uint32_t epoch, uint64_t wait_ns, uint4* __restrict__ merged,
+__global__ void __launch_bounds__(EPD_COPY_THREADS) ep_regroup_kernel(EpDispatch D, uint32_t epoch, uint64_t wait_ns, uint4* __restrict__ merged,
                                                          int32_t* __restrict__ comb_off, int32_t* __restrict__ src_start, int32_t* status) {
     __shared__ int ok;
     __shared__ int32_t s_n[kEpMaxRanks * 128], s_start[kEpMaxRanks * 128], s_comb[129];
@@ -138,34 +155,35 @@ __global__ void __launch_bounds__(256) ep_regroup_kernel(EpDispatch D, uint32_t 
         for (int le = threadIdx.x; le <= EL; le += blockDim.x) comb_off[le] = s_comb[le];
         for (int i = threadIdx.x; i < N * EL; i += blockDim.x) src_start[i] = s_start[i];
     }
-    const int seg = blockIdx.x, src = seg / EL, le = seg - src * EL;
+    const int seg = blockIdx.x / EPD_PARTS, part = blockIdx.x % EPD_PARTS, src = seg / EL, le = seg - src * EL;
     const int n = s_n[seg];
     if (n <= 0) return;
     const int chunks = D.hidden / 8;
     const int32_t* o = off_in(D, me, buf, src);
     const uint4* from = reinterpret_cast<const uint4*>(rows_in(D, me, buf, src)) + (int64_t)(o[le] - o[0]) * chunks;
     uint4* to = merged + (int64_t)s_start[seg] * chunks;
-    for (int64_t i = threadIdx.x; i < (int64_t)n * chunks; i += blockDim.x) to[i] = from[i];
+    copy_part(to, from, (int64_t)n * chunks, part, EPD_PARTS);
 }
 
-// grid (ranks * EPD_SLICES).  out: expert outputs of the merged run, f32 [rows][hidden].
-__global__ void __launch_bounds__(256) ep_return_kernel(const float4* __restrict__ out, const int32_t* __restrict__ src_start, EpDispatch D,
+// grid (ranks * local_experts * EPD_PARTS): the CTAs (src, le, part) send the outputs of that source's rows of local expert le back to the
+// positions the source's own grouping gave them.  out: expert outputs of the merged run, f32 [rows][hidden].  The CTA
+// that finishes last among a source's CTAs publishes the epoch in the source's return flag.
+__global__ void __launch_bounds__(EPD_COPY_THREADS) ep_return_kernel(const float4* __restrict__ out, const int32_t* __restrict__ src_start, EpDispatch D,
                                                         uint32_t epoch, int32_t* done) {
-    const int src = blockIdx.x / EPD_SLICES, slice = blockIdx.x % EPD_SLICES;
     const int EL = D.local_experts, me = D.rank, buf = (int)(epoch & 1u);
+    const int seg = blockIdx.x / EPD_PARTS, part = blockIdx.x % EPD_PARTS, src = seg / EL, le = seg - src * EL;
     const int chunks = D.hidden / 4;
     const int32_t* o = off_in(D, me, buf, src);  // the source's own positions of its rows for my experts
-    float4* back = reinterpret_cast<float4*>(out_back(D, src, buf));
-    for (int le = 0; le < EL; ++le) {
-        const int n = o[le + 1] - o[le];
+    const int at = o[le], n = o[le + 1] - at;
+    if (n > 0) {
         const float4* from = out + (int64_t)src_start[src * EL + le] * chunks;
-        float4* to = back + (int64_t)o[le] * chunks;
-        for (int64_t i = (int64_t)slice * blockDim.x + threadIdx.x; i < (int64_t)n * chunks; i += (int64_t)EPD_SLICES * blockDim.x) to[i] = from[i];
+        float4* to = reinterpret_cast<float4*>(out_back(D, src, buf)) + (int64_t)at * chunks;
+        copy_part(to, from, (int64_t)n * chunks, part, EPD_PARTS);
     }
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
-        if (atomicAdd(&done[src], 1) == EPD_SLICES - 1) {
+        if (atomicAdd(&done[src], 1) == EL * EPD_PARTS - 1) {
             done[src] = 0;
             __threadfence_system();
             st_release_sys(flag_back(D, src, buf, me), epoch);
@@ -198,12 +216,12 @@ void launch_ep_dispatch(const __half* grouped_rows, const int32_t* offsets, cons
 void launch_ep_regroup(const EpDispatch& D, uint32_t epoch, __half* merged, int32_t* comb_off, int32_t* src_start, int32_t* status, cudaStream_t s,
                        uint64_t wait_ns) {
     if (D.ranks * D.local_experts > kEpMaxRanks * 128 || D.local_experts > 128) throw std::runtime_error("expert dispatch: more than 128 local experts");
-    ep_regroup_kernel<<<D.ranks * D.local_experts, 256, 0, s>>>(D, epoch, wait_ns, reinterpret_cast<uint4*>(merged), comb_off, src_start, status);
+    ep_regroup_kernel<<<D.ranks * D.local_experts * EPD_PARTS, EPD_COPY_THREADS, 0, s>>>(D, epoch, wait_ns, reinterpret_cast<uint4*>(merged), comb_off, src_start, status);
     MK_LAUNCH_CHECK();
 }
 
 void launch_ep_return(const float* expert_out, const int32_t* src_start, const EpDispatch& D, uint32_t epoch, int32_t* done, cudaStream_t s) {
-    ep_return_kernel<<<D.ranks * EPD_SLICES, 256, 0, s>>>(reinterpret_cast<const float4*>(expert_out), src_start, D, epoch, done);
+    ep_return_kernel<<<D.ranks * D.local_experts * EPD_PARTS, EPD_COPY_THREADS, 0, s>>>(reinterpret_cast<const float4*>(expert_out), src_start, D, epoch, done);
     MK_LAUNCH_CHECK();
 }
 

@@ -9,21 +9,29 @@
 // The matrix is cut into (128-row tile, 256-column block) units, stored one after the other so that a unit is one
 // contiguous bulk copy.  R row tiles that follow one another form a group; an item is (group, block): the R units
 // that multiply the same 256 activation columns.  Items are shared out evenly over at most one persistent CTA per
-// SM; the part of a group one CTA covers is a piece.  736 threads in five roles:
-//   warp 0       - one lane streams the raw units into a ring of shared-memory stages (up to 7 x 18 KiB in flight);
-//                  the weights depend on no predecessor kernel, so this lane never waits for one;
-//   warp 2       - one lane loads the 256 columns of the f16 activations of an item (four 64-column TMA boxes,
-//                  128-byte swizzle) into a two-deep ring, once per item, whatever R is;
-//   warps 3-18   - converters: thread (row, 64-column chunk) turns its nibbles into f16 weights in registers and writes
-//                  them with one tcgen05.st into the A operand buffer in TENSOR memory (row = TMEM lane, two weights
-//                  per 32-bit column), two buffers of 128 columns alternating.  Shared memory carries the raw bytes
-//                  only; the dequantised operand never touches it;
-//   warp 1       - one lane issues, per unit, sixteen K = 16 tcgen05.mma with A from tensor memory and B (the
-//                  activations) from shared memory into the accumulator of the unit's row tile (M = 128, N = BN
-//                  tokens, up to four accumulators), and commits buffers, stages and accumulators back;
-//   warps 19-22  - at the end of a piece read its accumulators and store them: to the result when every group has one
-//                  piece, else to that piece's slot of the partial-sum scratch, whose slots the consumer kernel adds
-//                  in slot order; or, for an interleaved gate|up matrix, act(gate) * up as f16.
+// SM; the part of a group one CTA covers is a piece.  864 threads in five roles:
+//   warp 0       - streams the raw units into a ring of shared-memory stages (up to 8 x 18 KiB in flight; one elected
+//                  lane issues, the warp walks the item list together so that ring counters stay warp-uniform); the
+//                  weights depend on no predecessor kernel, so this role never waits for one;
+//   warp 2       - loads the 256 columns of the f16 activations of an item (four 64-column TMA boxes, 128-byte swizzle)
+//                  into a three-deep ring, once per item, whatever R is;
+//   warps 3-18   - converters, two groups of eight warps: group i owns A buffer i and the units of parity i, so one
+//                  group converts while the MMAs of the other group's buffer run.  Thread (row, 64-column chunk) turns
+//                  its nibbles into f16 weights in registers, sixteen at a time, and writes them with tcgen05.st into the
+//                  A operand buffer in TENSOR memory (row = TMEM lane, two weights per 32-bit column).  Shared memory
+//                  carries the raw bytes only; the dequantised operand never touches it;
+//   warp 1       - allocates tensor memory (overlapped with the first weight copies) and issues, per unit, sixteen
+//                  K = 16 tcgen05.mma with A from tensor memory and B (the activations) from shared memory into the
+//                  accumulator of the unit's row tile (M = 128, N = BN tokens, up to four accumulators), and commits
+//                  buffers, stages and accumulators back;
+//   warps 19-26  - at the end of a piece read its accumulators (each warp a lane quadrant and a column half) and store
+//                  them: to the result when every group has one piece, else to that piece's slot of the partial-sum
+//                  scratch, whose slots the consumer kernel adds in slot order; or, for an interleaved gate|up matrix,
+//                  act(gate) * up as f16.
+// Expert-grouped form (sparse-MoE layers): the matrix is a bank of experts, the activation rows are grouped by expert,
+// and the row ranges live on the device (they come from the routing kernels of the same forward).  Warp 0 first builds
+// this CTA's share of the job list - (expert, chunk of up to BN of its rows, group of row tiles) - from the ranges, with
+// no host round trip; a job then runs like a whole group of the plain form.
 // Q4_K arithmetic: sc * q (an integer below 1024) is formed exactly, then w = fma(sc * q, d, -f16(dmin * m)): the f16
 // weight carries the rounding of the product and that of dmin * m.  Q6_K: w = (q - 32) * f16(d * sc).
 // Every mbarrier wait is bounded; a wait that gives up records a status word and the role leaves its loop.
