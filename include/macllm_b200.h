@@ -443,10 +443,10 @@ int32_t mk_k_qmatmul_time(int32_t type, const void* w, int64_t rows, int64_t col
  * anything larger is refused with a message.  The arrays are
  * shared by every call and keep the previous call's contents (what must start at zero is cleared by
  * the call itself), so calls that overlap on the GPU - other streams or other threads - race and must
- * be serialised by the caller.  The first call on a device also looks up the arrays' device addresses;
- * make that first call before any stream capture begins.  Every call waits for its own result: it
- * synchronises cuda_stream (a cudaStream_t, or NULL for the default stream) and reads a status word back
- * before it returns.  It never calls cudaMalloc, cudaFree
+ * be serialised by the caller.  The first call on a device also looks up the arrays' device addresses.
+ * Every call waits for its own result: it synchronises cuda_stream (a cudaStream_t, or NULL for the default
+ * stream) and reads a status word back before it returns, so it cannot be used on a stream that is being
+ * captured into a graph.  It never calls cudaMalloc, cudaFree
  * or any allocating library routine.  Same arithmetic as mk_k_qmatmul(MK_TYPE_Q4_K, ..., MK_PATH_TENSOR). */
 #define MK_NOALLOC_MAX_ACT_ELEMS 524288
 #define MK_NOALLOC_MAX_PARTIAL 2097152

@@ -305,7 +305,8 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
-template <int BN, bool PROF>
+// GROUPED is a template parameter so that the plain form carries none of the job-table lookups.
+template <int BN, bool PROF, bool GROUPED>
 __global__ void __launch_bounds__(QS_THREADS, 1)
 qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_x, QsParams p) {
     using L = QsSmem<BN>;
@@ -334,10 +335,11 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_x, QsParams p) {
     const int C = (int)gridDim.x, c = (int)blockIdx.x;
     const int R = p.R, nb = p.n_blocks;
     // expert-grouped form: this CTA's jobs, looked up by the roles as "group" g = 0, 1, ...
-    __shared__ int16_t job_expert[QS_MAX_JOBS], job_rows[QS_MAX_JOBS], job_group[QS_MAX_JOBS];
-    __shared__ int32_t job_row0[QS_MAX_JOBS];
+    constexpr int JOBS = GROUPED ? QS_MAX_JOBS : 1;
+    __shared__ int16_t job_expert[JOBS], job_rows[JOBS], job_group[JOBS];
+    __shared__ int32_t job_row0[JOBS];
     __shared__ int32_t job_range[2];
-    if (p.grouped) {
+    if (GROUPED) {
         // the row ranges come from the routing kernels: nothing of this launch can start before they are final
         pdl_wait();
         if (warp == 0) {
@@ -386,7 +388,7 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_x, QsParams p) {
     }
     // this CTA's contiguous range of items
     int i0, i1;
-    if (p.grouped) {
+    if (GROUPED) {
         i0 = 0;
         i1 = min(job_range[1] - job_range[0], QS_MAX_JOBS) * nb;
     } else if (p.whole_groups) {
@@ -400,9 +402,9 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_x, QsParams p) {
     const int acc_shift = R == 1 ? 2 : (R == 2 ? 1 : 0);  // QS_ACC / R accumulator sets
     const int n_stages = p.n_stages;
     // row tile r of group g: its index inside its matrix, whether it exists, and the index of its first unit
-    const int tiles_limit = p.grouped ? p.tiles_pe : p.row_tiles;
-    auto tile_of = [&](int g, int r) { return (p.grouped ? (int)job_group[g] : g) * R + r; };
-    auto unit_tile = [&](int g, int tile) { return p.grouped ? (int64_t)job_expert[g] * p.tiles_pe + tile : (int64_t)tile; };
+    const int tiles_limit = GROUPED ? p.tiles_pe : p.row_tiles;
+    auto tile_of = [&](int g, int r) { return (GROUPED ? (int)job_group[g] : g) * R + r; };
+    auto unit_tile = [&](int g, int tile) { return GROUPED ? (int64_t)job_expert[g] * p.tiles_pe + tile : (int64_t)tile; };
 
     if (warp == 0) {
         // one barrier per lane
@@ -435,7 +437,7 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_x, QsParams p) {
                 const int tile = tile_of(g, r);
                 if (tile >= tiles_limit) break;
                 if (!QS_WAIT(0, &raw_empty[st], (use & 1) ^ 1)) { if (lane == 0) atomicExch(p.status, 22); it = i1; break; }
-                const bool seg_b = !p.grouped && tile >= p.tiles_a;
+                const bool seg_b = !GROUPED && tile >= p.tiles_a;
                 const uint32_t bytes = (uint32_t)((seg_b ? p.fmt_b : p.fmt_a) ? QS_Q6K_UNIT : QS_Q4K_UNIT);
                 const uint8_t* src = seg_b ? p.w_b + ((int64_t)(tile - p.tiles_a) * nb + b) * bytes : p.w_a + (unit_tile(g, tile) * nb + b) * bytes;
                 if (elect_one()) {
@@ -460,7 +462,7 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_x, QsParams p) {
             if (elect_one()) {
                 mbar_expect_tx(&x_full[st], (uint32_t)L::X_BYTES);
 #pragma unroll
-                for (int q = 0; q < 4; ++q) tma_load_2d(xb + q * BN * 128, &tm_x, b * 256 + q * 64, p.grouped ? job_row0[g] : 0, &x_full[st]);
+                for (int q = 0; q < 4; ++q) tma_load_2d(xb + q * BN * 128, &tm_x, b * 256 + q * 64, GROUPED ? job_row0[g] : 0, &x_full[st]);
             }
             __syncwarp();
             QS_LOG(2, 2);
@@ -557,7 +559,7 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_x, QsParams p) {
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     if (warp == 3) QS_LOG(3, 3);
                     const uint32_t t_dst = tmem_base + ((uint32_t)(quad * 32) << 16) + QS_A_COL0 + buf * 128 + 64 * h;
-                    const bool q6 = ((!p.grouped && tile >= p.tiles_a) ? p.fmt_b : p.fmt_a) != 0;
+                    const bool q6 = ((!GROUPED && tile >= p.tiles_a) ? p.fmt_b : p.fmt_a) != 0;
                     uint32_t w[16];
                     if (PROF && (p.dbg & 1)) {
 #pragma unroll
@@ -628,7 +630,7 @@ qstream_tc_kernel(const __grid_constant__ CUtensorMap tm_x, QsParams p) {
                 int my_slot = 0;
                 if (p.mode == 0 && p.slots > 1) my_slot = c - cta_of_item(g * nb);
                 // token rows of this piece: the call's rows, or the chunk of one expert's rows
-                const int tok0 = p.grouped ? job_row0[g] : 0, T_here = p.grouped ? (int)job_rows[g] : p.T;
+                const int tok0 = GROUPED ? job_row0[g] : 0, T_here = GROUPED ? (int)job_rows[g] : p.T;
                 for (int r = 0; r < R && ok; ++r) {
                     const int tile = tile_of(g, r);
                     if (tile >= tiles_limit) break;
@@ -768,12 +770,15 @@ size_t qs_smem_bytes(int n_stages, int stage_bytes) {
 template <int BN>
 void launch_qs(const CUtensorMap& tx, const QsParams& p, int ctas, cudaStream_t s) {
     const size_t smem = qs_smem_bytes<BN>(p.n_stages, p.stage_bytes);
-    if (p.prof != nullptr) {
-        ensure_dynamic_smem(reinterpret_cast<const void*>(&qstream_tc_kernel<BN, true>), smem);
-        launch_pdl(qstream_tc_kernel<BN, true>, dim3(ctas), dim3(QS_THREADS), smem, s, tx, p);
+    if (p.grouped) {
+        ensure_dynamic_smem(reinterpret_cast<const void*>(&qstream_tc_kernel<BN, false, true>), smem);
+        launch_pdl(qstream_tc_kernel<BN, false, true>, dim3(ctas), dim3(QS_THREADS), smem, s, tx, p);
+    } else if (p.prof != nullptr) {
+        ensure_dynamic_smem(reinterpret_cast<const void*>(&qstream_tc_kernel<BN, true, false>), smem);
+        launch_pdl(qstream_tc_kernel<BN, true, false>, dim3(ctas), dim3(QS_THREADS), smem, s, tx, p);
     } else {
-        ensure_dynamic_smem(reinterpret_cast<const void*>(&qstream_tc_kernel<BN, false>), smem);
-        launch_pdl(qstream_tc_kernel<BN, false>, dim3(ctas), dim3(QS_THREADS), smem, s, tx, p);
+        ensure_dynamic_smem(reinterpret_cast<const void*>(&qstream_tc_kernel<BN, false, false>), smem);
+        launch_pdl(qstream_tc_kernel<BN, false, false>, dim3(ctas), dim3(QS_THREADS), smem, s, tx, p);
     }
     MK_LAUNCH_CHECK();
 }
