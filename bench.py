@@ -53,6 +53,7 @@ WORKLOAD_NAMES = ["tinyllama-1.1b-batch4", "smollm3-3b-ragged64", "qwen3-8b-pref
 NCU_TRAFFIC_RATIO = {
     "hgemm_tc": (98.8 + 21.4) / (90.2 + 8.4 + 45.1),      # gate|up with the activation in the epilogue: every operand once; part of the f16 output is still in L2 at kernel end
     "paged_attention": (77.0 + 1.9) / (72.4 + 4.2),
+    "qstream_tc": (25.70 + 0.004) / (25.36 + 0.26),         # streamed gate|up of a decode tick: every weight block once, the partial sums stay in L2
 }
 
 
@@ -270,6 +271,49 @@ def run_step(eng_mod, model, w, reqs, active: int, lockstep=None):
     return toks + gen, wall, st, diag
 
 
+def http_step(eng_mod, model, w, reqs, active: int, clients: int) -> dict:
+    """The same workload through the raw `/completion` endpoint (macllm_infer_b200.server, the reference's benchmark
+    surface src/server.rs:633-666) on 127.0.0.1: `clients` threads each post their share of the requests one after the
+    other (non-streamed, token-id prompts) and the step ends with the last response - the reference's own throughput
+    definition, total tokens / wall time from the first submission to the last completion (src/benchmark/serving.rs:301-328)."""
+    import http.client
+    import threading
+    srv_mod = importlib.import_module("macllm_infer_b200.server")
+    prompts, new, _ = reqs
+    server = srv_mod.CompletionServer(lambda: (new_engine(eng_mod, model, w, active, len(prompts)), model)).start()
+    done = [0] * clients
+    errors = []
+
+    def client(c):
+        conn = http.client.HTTPConnection("127.0.0.1", server.port, timeout=600)
+        for i in range(c, len(prompts), clients):
+            body = {"prompt": [int(t) for t in prompts[i]], "n_predict": int(new[i]), "temperature": 0.0, "top_k": 1, "top_p": 1.0, "seed": 0,
+                    "cache_prompt": True, "stream": False, "return_tokens": True, "id_slot": 0, "ignore_eos": True, "repeat_penalty": 1.0,
+                    "response_fields": srv_mod.RAW_COMPLETION_RESPONSE_FIELDS}
+            conn.request("POST", "/completion", body=json.dumps(body), headers={"Content-Type": "application/json"})
+            r = conn.getresponse()
+            out = json.loads(r.read())
+            if r.status != 200:
+                errors.append(out)
+                return
+            done[c] += out["tokens_predicted"] + out["timings/prompt_n"]
+        conn.close()
+    try:
+        threads = [threading.Thread(target=client, args=(c,)) for c in range(clients)]
+        t0 = time.perf_counter()
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        wall = time.perf_counter() - t0
+    finally:
+        server.stop()
+    if errors:
+        raise RuntimeError(f"/completion answered an error: {errors[0]}")
+    return dict(value=sum(done) / wall, unit=UNIT, clients=clients, requests=len(prompts), wall_s=round(wall, 3),
+                surface="POST /completion on 127.0.0.1, non-streamed, token-id prompts, one connection per client")
+
+
 def tick_classes(eng_mod, model, w, reqs, active: int, weight_bytes_per_pass: float, kv_bytes_per_token: float, hbm_gbs: float,
                  window_layers: tuple = (0, 0, 0), lockstep=None) -> dict:
     """One more (untimed) step driven tick by tick: device time and algorithmic HBM bytes per tick class.
@@ -436,6 +480,8 @@ def main():
     ap.add_argument("--kv-budget-gb", type=float, default=110.0, help="largest KV arena; the active set shrinks until it fits")
     ap.add_argument("--ep", default="auto", choices=["auto", "on", "off"],
                     help="N > 1 and a sparse-MoE workload: expert parallelism with data-parallel lanes (auto = on) instead of replicas")
+    ap.add_argument("--http-clients", type=int, default=0,
+                    help="also run one step through the /completion endpoint with this many concurrent clients (adds an `http` key)")
     ap.add_argument("--no-profiled-step", action="store_true", help="skip the extra step that times every launch")
     ap.add_argument("--microbench", action="store_true", help="Q4_K matmul GB/s on the decode shapes instead of the workload")
     args = ap.parse_args()
@@ -603,6 +649,10 @@ def main():
         if roof is not None:
             roof["q4k_gemv"] = q4k_gemv_block(pk["hbm_gbs"])
 
+    http = None
+    if rank == 0 and args.http_clients > 0 and not ep:
+        http = http_step(eng_mod, model, w, reqs, active, args.http_clients)
+
     base = None
     if rank == 0 and not args.no_cpu_baseline:
         try:
@@ -621,6 +671,8 @@ def main():
                    cpu_baseline=base)
         if diag is not None:
             out["prefix_cache"] = diag
+        if http is not None:
+            out["http"] = http
         print(json.dumps(out))
     model.close()
     if dist is not None:

@@ -291,6 +291,10 @@ typedef struct mk_request {
     float presence_penalty;
     float frequency_penalty;
     uint64_t seed;
+    /* EngineRequestPolicy (src/engine.rs:222-241): 0 = the request publishes its prompt prefix after every completed
+     * prefill chunk (the default policy); 1 = benchmark_measured(): it may hit the prefix cache but publishes nothing. */
+    int32_t no_prefix_publication;
+    int32_t reserved_;
 } mk_request;
 
 /* One packed forward of the schedule: which request ran which token range (the shape the reference's

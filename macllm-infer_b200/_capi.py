@@ -82,7 +82,7 @@ class Request(C.Structure):
     _fields_ = [("prompt", C.POINTER(C.c_uint32)), ("n_prompt", C.c_int32), ("max_new_tokens", C.c_int32),
                 ("ignore_stop_tokens", C.c_int32), ("temperature", C.c_float), ("top_k", C.c_int32), ("top_p", C.c_float),
                 ("repetition_penalty", C.c_float), ("presence_penalty", C.c_float), ("frequency_penalty", C.c_float),
-                ("seed", C.c_uint64)]
+                ("seed", C.c_uint64), ("no_prefix_publication", C.c_int32), ("reserved_", C.c_int32)]
 
 
 class TickLane(C.Structure):

@@ -394,6 +394,7 @@ int32_t mk_engine_submit(mk_engine* e, const mk_request* reqs, int32_t n, int32_
             r.prompt.assign(reqs[i].prompt, reqs[i].prompt + reqs[i].n_prompt);
             r.max_new_tokens = reqs[i].max_new_tokens;
             r.ignore_stop_tokens = reqs[i].ignore_stop_tokens != 0;
+            r.publish_prompt_prefix = reqs[i].no_prefix_publication == 0;
             r.temperature = reqs[i].temperature;
             r.top_k = reqs[i].top_k;
             r.top_p = reqs[i].top_p;

@@ -27,6 +27,7 @@ class Request:
     presence_penalty: float = 0.0
     frequency_penalty: float = 0.0
     seed: int = 0
+    publish_prompt_prefix: bool = True
 
 
 class Session:
@@ -281,6 +282,7 @@ class Engine:
             arr[i].presence_penalty = r.presence_penalty
             arr[i].frequency_penalty = r.frequency_penalty
             arr[i].seed = r.seed
+            arr[i].no_prefix_publication = 0 if r.publish_prompt_prefix else 1
         ids = np.empty(n, np.int32)
         capi.check(capi.lib().mk_engine_submit(self._h, arr, n, 1 if atomic_batch else 0, ids.ctypes.data))
         return [int(x) for x in ids]
@@ -298,11 +300,19 @@ class Engine:
         capi.check(capi.lib().mk_engine_pending(self._h, C.byref(n)))
         return int(n.value)
 
+    def progress(self, request_id: int):
+        """(generated tokens so far, state, prompt tokens served from the prefix cache) without copying the tokens."""
+        n = C.c_int32(0)
+        fin = C.c_int32()
+        cached = C.c_int64()
+        capi.check(capi.lib().mk_engine_result(self._h, request_id, None, C.byref(n), C.byref(fin), C.byref(cached)))
+        return int(n.value), ("running", "done", "failed")[fin.value], int(cached.value)
+
     def result(self, request_id: int):
-        """Returns dict(tokens, state ('running' | 'done' | 'failed'), cached_tokens, message)."""
-        cap = 1 << 16
-        toks = np.empty(cap, np.uint32)
-        n = C.c_int32(cap)
+        """Returns dict(tokens, state ('running' | 'done' | 'failed'), cached_tokens, message, kind)."""
+        count, _, _ = self.progress(request_id)
+        toks = np.empty(max(count, 1), np.uint32)
+        n = C.c_int32(len(toks))
         fin = C.c_int32()
         cached = C.c_int64()
         capi.check(capi.lib().mk_engine_result(self._h, request_id, toks.ctypes.data, C.byref(n), C.byref(fin), C.byref(cached)))

@@ -151,8 +151,8 @@ def terminal_event(content: str, settings: dict, m: dict) -> dict:
 
 
 class _Job:
-    def __init__(self, tokens, settings):
-        self.tokens, self.settings = tokens, settings
+    def __init__(self, tokens, settings, publish_prefix=True):
+        self.tokens, self.settings, self.publish_prefix = tokens, settings, publish_prefix
         self.events: queue.Queue = queue.Queue()
         self.request_id = None
         self.seen = 0
@@ -213,7 +213,8 @@ class CompletionServer:
                 try:
                     v = parse_raw_request(body)
                     tokens, settings = validate_raw_request(v, server._max_context, server._tokenizer)
-                    job = server._submit(tokens, settings)
+                    # cache_prompt = false selects EngineRequestPolicy::benchmark_measured() (src/server.rs:434-438)
+                    job = server._submit(tokens, settings, publish_prefix=bool(v["cache_prompt"]))
                 except ApiError as e:
                     self._json(e.status, e.body())
                     return
@@ -303,11 +304,11 @@ class CompletionServer:
         return self._status
 
     # ------------------------------------------------------------------ handler side
-    def _submit(self, tokens, settings) -> _Job:
+    def _submit(self, tokens, settings, publish_prefix=True) -> _Job:
         if self._status in ("poisoned", "stopped", "starting"):
             label = self._status.capitalize()
             raise ApiError.server_error(f"inference worker is unavailable ({label})", 503)
-        job = _Job(tokens, settings)
+        job = _Job(tokens, settings, publish_prefix)
         reply: queue.Queue = queue.Queue()
         self._inbox.put((job, reply))
         err = reply.get()
@@ -339,7 +340,8 @@ class CompletionServer:
                 try:
                     s = job.settings
                     (rid,) = engine.submit([_engine.Request(job.tokens, s["n_predict"], ignore_stop_tokens=True, temperature=s["temperature"],
-                                                            top_k=s["top_k"], top_p=s["top_p"], seed=s["seed"])])
+                                                            top_k=s["top_k"], top_p=s["top_p"], seed=s["seed"],
+                                                            publish_prompt_prefix=job.publish_prefix)])
                     job.request_id = rid
                     active[rid] = job
                     reply.put(None)

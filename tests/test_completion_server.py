@@ -1,0 +1,230 @@
+"""The raw `/completion` surface over the engine, on the host-only model (no GPU): the request contract, the response
+projection, the streamed form and the error mapping of the reference's endpoint (src/server.rs:326-841; its own tests
+`raw_completion_uses_the_untemplated_fixed_length_contract`, `raw_completion_streams_visible_text_then_exact_terminal_evidence`,
+`health_and_models_report_the_single_loaded_runtime`, src/server.rs:5085-5230)."""
+import http.client
+import importlib
+import json
+import threading
+
+import pytest
+
+
+@pytest.fixture()
+def srv_mod(mk):
+    return importlib.import_module("macllm_infer_b200.server")
+
+
+def body(srv_mod, **over):
+    b = {"prompt": [5, 6, 7], "n_predict": 2, "temperature": 0.0, "top_k": 1, "top_p": 1.0, "seed": 7, "cache_prompt": True,
+         "stream": False, "return_tokens": True, "id_slot": 3, "ignore_eos": True, "repeat_penalty": 1.0,
+         "response_fields": list(srv_mod.RAW_COMPLETION_RESPONSE_FIELDS)}
+    b.update(over)
+    return b
+
+
+def start(mk, srv_mod, tokenizer=None, queue_capacity=8, max_active=4, inject=None, **model_kw):
+    eng = importlib.import_module("macllm_infer_b200.engine")
+
+    def factory():
+        model = eng.Model.fake(vocab=64, max_context=256, kv_capacity_tokens=2048, **model_kw)
+        if inject is not None:
+            model.inject_failure(*inject)
+        return eng.Engine(model, max_active_sequences=max_active, scheduler_token_budget=64, prefill_token_quantum=32, queue_capacity=queue_capacity), model
+    return srv_mod.CompletionServer(factory, tokenizer=tokenizer, metadata=dict(served_model="test-model", device="cpu", dtype="f32")).start()
+
+
+def call(server, method, path, payload=None, raw=None):
+    conn = http.client.HTTPConnection("127.0.0.1", server.port, timeout=30)
+    data = raw if raw is not None else (json.dumps(payload).encode() if payload is not None else None)
+    conn.request(method, path, body=data, headers={"Content-Type": "application/json"} if data is not None else {})
+    r = conn.getresponse()
+    out = r.read()
+    conn.close()
+    return r.status, r.getheader("Content-Type"), out
+
+
+def test_health_and_models_report_the_single_loaded_runtime(mk, srv_mod):
+    s = start(mk, srv_mod)
+    try:
+        st, _, b = call(s, "GET", "/healthz")
+        h = json.loads(b)
+        assert st == 200 and h["status"] == "ok" and h["worker"] == "ready" and h["device"] == "cpu" and h["dtype"] == "f32"
+        st, _, b = call(s, "GET", "/v1/models")
+        assert st == 200 and json.loads(b)["data"][0]["id"] == "test-model" and json.loads(b)["data"][0]["owned_by"] == "macllm-infer"
+    finally:
+        s.stop()
+
+
+def test_completion_uses_the_fixed_length_contract(mk, srv_mod):
+    s = start(mk, srv_mod)
+    try:
+        st, ctype, b = call(s, "POST", "/completion", body(srv_mod))
+        assert st == 200 and ctype == "application/json"
+        r = json.loads(b)
+        # exactly the projected fields: no token list, no prompt echo
+        assert list(r.keys()) == srv_mod.RAW_COMPLETION_RESPONSE_FIELDS
+        assert r["stop"] is True and r["stop_type"] == "limit" and r["truncated"] is False and r["index"] == 0
+        assert r["tokens_predicted"] == 2 and r["tokens_evaluated"] == 3
+        assert r["generation_settings/ignore_eos"] is True and r["generation_settings/repeat_penalty"] == 1.0
+        assert r["generation_settings/n_predict"] == 2 and r["generation_settings/max_tokens"] == 2 and r["generation_settings/n_keep"] == 0
+        assert r["generation_settings/seed"] == 7 and r["generation_settings/top_k"] == 1
+        assert r["timings/cache_n"] == 0 and r["timings/prompt_n"] == 3 and r["timings/predicted_n"] == 2
+        assert r["timings/prompt_ms"] >= 0.0 and r["timings/predicted_ms"] >= 0.0
+    finally:
+        s.stop()
+
+
+def test_completion_streams_token_evidence_then_the_terminal_event(mk, srv_mod):
+    s = start(mk, srv_mod)
+    try:
+        # what the engine generates for this prompt, from the non-streamed path's sibling: run it through the engine directly
+        eng = importlib.import_module("macllm_infer_b200.engine")
+        model = eng.Model.fake(vocab=64, max_context=256, kv_capacity_tokens=2048)
+        e = eng.Engine(model, max_active_sequences=4, scheduler_token_budget=64, prefill_token_quantum=32)
+        (rid,) = e.submit([eng.Request([5, 6, 7], 3)])
+        e.run()
+        want = [int(t) for t in e.result(rid)["tokens"]]
+        e.close()
+
+        st, ctype, b = call(s, "POST", "/completion", body(srv_mod, stream=True, n_predict=3, cache_prompt=False))
+        assert st == 200 and ctype == "text/event-stream"
+        text = b.decode()
+        assert "[DONE]" not in text and "keep-alive" not in text
+        events = [json.loads(line[len("data: "):]) for line in text.split("\n\n") if line.startswith("data: ")]
+        assert len(events) == 4
+        for i, ev in enumerate(events[:3]):
+            assert ev["tokens"] == [want[i]] and ev["stop"] is False and ev["id_slot"] == -1
+            assert ev["tokens_predicted"] == i + 1 and ev["tokens_evaluated"] == 3 and ev["index"] == 0
+        last = events[3]
+        assert list(last.keys()) == srv_mod.RAW_COMPLETION_RESPONSE_FIELDS
+        assert last["content"] == "" and last["stop"] is True and last["tokens_predicted"] == 3 and last["stop_type"] == "limit"
+        assert last["generation_settings/stream"] is True
+    finally:
+        s.stop()
+
+
+def test_text_prompts_need_a_tokenizer_and_content_is_decoded_text(mk, srv_mod):
+    class Toy:
+        def encode(self, text):
+            return [ord(c) % 60 + 1 for c in text]
+
+        def decode(self, ids):
+            return "".join(chr(97 + i % 26) for i in ids)
+    s = start(mk, srv_mod)
+    try:
+        st, _, b = call(s, "POST", "/completion", body(srv_mod, prompt="a b"))
+        err = json.loads(b)["error"]
+        assert st == 400 and err["param"] == "prompt" and err["type"] == "invalid_request_error"
+    finally:
+        s.stop()
+    s = start(mk, srv_mod, tokenizer=Toy())
+    try:
+        st, _, b = call(s, "POST", "/completion", body(srv_mod, prompt="a b"))
+        r = json.loads(b)
+        assert st == 200 and r["tokens_evaluated"] == 3 and len(r["content"]) == 2 and r["content"].isalpha()
+    finally:
+        s.stop()
+
+
+@pytest.mark.parametrize("change,param,code,message", [
+    (dict(prompt=[]), "prompt", "invalid_value", "prompt must not be empty"),
+    (dict(n_predict=0), "n_predict", "invalid_value", "n_predict must be in 1..=256"),
+    (dict(n_predict=257), "n_predict", "invalid_value", "n_predict must be in 1..=256"),
+    (dict(temperature=-0.5), "temperature", "invalid_value", "temperature must be finite and non-negative"),
+    (dict(top_p=0.0), "top_p", "invalid_value", "top_p must be finite and in (0, 1]"),
+    (dict(top_p=1.5), "top_p", "invalid_value", "top_p must be finite and in (0, 1]"),
+    (dict(id_slot=8), "id_slot", "invalid_value", "id_slot must be in 0..8"),
+    (dict(ignore_eos=False), "ignore_eos", "unsupported_value", "ignore_eos must be true for fixed-length benchmark completions"),
+    (dict(return_tokens=False), "return_tokens", "unsupported_value", "return_tokens must be true for benchmark token-parity evidence"),
+    (dict(repeat_penalty=1.1), "repeat_penalty", "unsupported_value", "repeat_penalty must be 1.0 for the shared benchmark contract"),
+    (dict(response_fields=["content"]), "response_fields", "unsupported_value", "response_fields must exactly match the benchmark response projection"),
+])
+def test_requests_outside_the_contract_are_refused_with_the_reference_wording(mk, srv_mod, change, param, code, message):
+    s = start(mk, srv_mod)
+    try:
+        st, _, b = call(s, "POST", "/completion", body(srv_mod, **change))
+        err = json.loads(b)["error"]
+        assert st == 400
+        assert err == {"message": message, "type": "invalid_request_error", "param": param, "code": code}
+    finally:
+        s.stop()
+
+
+def test_malformed_unknown_and_missing_fields_fail_closed(mk, srv_mod):
+    s = start(mk, srv_mod)
+    try:
+        for raw in (b"{not json", json.dumps({**body(srv_mod), "extra": 1}).encode(),
+                    json.dumps({k: v for k, v in body(srv_mod).items() if k != "seed"}).encode(),
+                    json.dumps(body(srv_mod, n_predict="2")).encode(), json.dumps(body(srv_mod, stream=1)).encode()):
+            st, _, b = call(s, "POST", "/completion", raw=raw)
+            err = json.loads(b)["error"]
+            assert st == 400 and err["code"] == "invalid_json" and err["message"].startswith("invalid /completion request: ")
+        assert call(s, "POST", "/v1/chat/completions", {"model": "x"})[0] == 404
+    finally:
+        s.stop()
+
+
+def test_concurrent_requests_share_the_batch_and_each_gets_its_own_tokens(mk, srv_mod):
+    eng = importlib.import_module("macllm_infer_b200.engine")
+    prompts = [[3 + i, 9, 4 + 2 * i, 11] for i in range(6)]
+    model = eng.Model.fake(vocab=64, max_context=256, kv_capacity_tokens=2048)
+    e = eng.Engine(model, max_active_sequences=4, scheduler_token_budget=64, prefill_token_quantum=32, queue_capacity=8)
+    want = []
+    for p in prompts:  # one at a time: the host-only model's tokens depend only on the sequence
+        (rid,) = e.submit([eng.Request(p, 5)])
+        e.run()
+        want.append([int(t) for t in e.result(rid)["tokens"]])
+    e.close()
+    s = start(mk, srv_mod)
+    got = [None] * len(prompts)
+
+    def one(i):
+        st, _, b = call(s, "POST", "/completion", body(srv_mod, prompt=prompts[i], n_predict=5, stream=True))
+        evs = [json.loads(line[6:]) for line in b.decode().split("\n\n") if line.startswith("data: ")]
+        got[i] = (st, [ev["tokens"][0] for ev in evs[:-1]], evs[-1])
+    try:
+        threads = [threading.Thread(target=one, args=(i,)) for i in range(len(prompts))]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join(60)
+        for i, (st, toks, last) in enumerate(got):
+            assert st == 200 and toks == want[i] and last["tokens_predicted"] == 5 and last["tokens_evaluated"] == 4
+    finally:
+        s.stop()
+
+
+def test_a_poisoned_worker_fails_the_request_and_turns_health_red(mk, srv_mod):
+    """A forward that fails poisons the engine (src/engine.rs:1577-1647): the request in flight gets a server error, later
+    submissions answer 503 `inference worker is unavailable (Poisoned)`, `/healthz` reports the worker poisoned."""
+    s = start(mk, srv_mod, inject=("forward", 1))
+    try:
+        st, _, b = call(s, "POST", "/completion", body(srv_mod, n_predict=4))
+        err = json.loads(b)["error"]
+        assert st == 500 and err["type"] == "server_error" and err["code"] == "internal_error" and "inference worker failed" in err["message"]
+        st, _, b = call(s, "GET", "/healthz")
+        assert st == 503 and json.loads(b)["worker"] == "poisoned" and json.loads(b)["status"] == "error"
+        st, _, b = call(s, "POST", "/completion", body(srv_mod))
+        assert st == 503 and "unavailable (Poisoned)" in json.loads(b)["error"]["message"]
+    finally:
+        s.stop()
+
+
+def test_cache_prompt_false_hits_the_prefix_cache_but_publishes_nothing(mk, srv_mod):
+    """EngineRequestPolicy::benchmark_measured (src/engine.rs:222-241, selected by cache_prompt = false,
+    src/server.rs:434-438): measured requests leave the cache as they found it."""
+    prompt = list(range(3, 3 + 48))
+    s = start(mk, srv_mod, prefix_capacity_tokens=1024)
+    try:
+        def cached(cache_prompt):
+            st, _, b = call(s, "POST", "/completion", body(srv_mod, prompt=prompt, cache_prompt=cache_prompt))
+            assert st == 200
+            return json.loads(b)["timings/cache_n"]
+        assert cached(False) == 0 and cached(False) == 0      # nothing was published by the measured requests
+        assert cached(True) == 0                               # this one publishes its prompt prefix ...
+        hit = cached(False)
+        assert hit > 0 and hit % 16 == 0 and hit < len(prompt)  # ... which a measured request may use (whole blocks, not the last token)
+        assert cached(True) == hit
+    finally:
+        s.stop()
