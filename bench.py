@@ -361,14 +361,14 @@ def tick_classes(eng_mod, model, w, reqs, active: int, weight_bytes_per_pass: fl
     return out
 
 
-Q4K_SHAPES = [(2048, 2048), (256, 2048), (5632, 2048), (2048, 5632), (11008, 2048), (2048, 11008), (12288, 4096)]
+Q4K_SHAPES = [(2048, 2048), (256, 2048), (5632, 2048), (2048, 5632), (11008, 2048), (2048, 11008), (12288, 4096), (24576, 4096), (4096, 12288)]
 
 
 def microbench() -> None:
     """Q4_K matmul micro-benchmark: achieved GB/s on the algorithmic bytes of the matrix (rows * cols * 144/256) for
-    the decode shapes of the first three configurations at 1, 4, 16 and 64 activation rows, on the path the model
-    picks for that many rows (integer GEMV up to 8 rows, streamed blocks above).  Operands resident, L2 flushed
-    before every launch, CUDA events around the launch.  One JSON line per shape."""
+    the decode shapes of the first three configurations at 1, 4, 8, 16 and 64 activation rows: the integer GEMV (up to 8
+    rows) and the streamed tensor-core kernel side by side.  Operands resident, L2 flushed before every launch, CUDA
+    events around the launch.  One JSON line per shape."""
     ops = importlib.import_module("macllm_infer_b200.ops")
     capi = importlib.import_module("macllm_infer_b200._capi")
     pk = peaks()
@@ -377,11 +377,13 @@ def microbench() -> None:
         wq = ops.seed_tensor(0, 1, 0.02, capi.TYPE_Q4_K, rows, cols)
         nbytes = rows * cols * 144 // 256
         line = dict(kernel="q4k_matmul", rows=rows, cols=cols, weight_mb=round(nbytes / 1e6, 2), peak_gbs=pk["hbm_gbs"], peak_source=pk["source"])
-        for T in (1, 4, 16, 64):
+        for T in (1, 4, 8, 16, 64):
             x = rng.standard_normal((T, cols)).astype(np.float32)
-            path = capi.PATH_GEMV if T <= 8 else capi.PATH_STREAM
-            ms = ops.qmatmul_time(capi.TYPE_Q4_K, wq, rows, cols, x, path, 20)
-            line[f"T{T}"] = dict(us=round(ms * 1e3, 1), gbs=round(nbytes / ms / 1e6, 1), frac=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
+            for label, path in (("gemv", capi.PATH_GEMV), ("stream", capi.PATH_STREAM)):
+                if label == "gemv" and T > 8:
+                    continue
+                ms = ops.qmatmul_time(capi.TYPE_Q4_K, wq, rows, cols, x, path, 20)
+                line[f"T{T}_{label}"] = dict(us=round(ms * 1e3, 1), gbs=round(nbytes / ms / 1e6, 1), frac=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
         print(json.dumps(line), flush=True)
 
 
@@ -663,7 +665,7 @@ def main():
     if rank == 0:
         out = dict(metric=METRIC, value=tokens_all / dev_max, unit=UNIT, n_gpus=world, steps=args.steps, warmup=args.warmup,
                    ms_per_step=wall_max * 1e3 / max(args.steps, 1), higher_is_better=True, scaling="weak", vs_baseline=None,
-                   dtype="f16 tensor cores over f16 weights dequantised in flight (2..64 rows) or f16 weight images (wider ticks), int8 x int4/6 block dots (1 row), f32 accumulate, f16 KV",
+                   dtype="f16 tensor cores over f16 weights dequantised in flight (1..64 rows) or f16 weight images (wider ticks), f32 accumulate, f16 KV",
                    data="synthetic", config=config, clocks=clocks,
                    e2e=dict(value=tokens_all / wall_max, unit=UNIT, h2d_bytes_per_step=(h2d1 - h2d0) // max(args.steps, 1),
                             d2h_bytes_per_step=(d2h1 - d2h0) // max(args.steps, 1)),

@@ -44,7 +44,7 @@ extern "C" {
 #define MK_PATH_GEMV 1   /* integer dp4a kernel */
 #define MK_PATH_TENSOR 2 /* tcgen05 kernel, GGUF blocks dequantised inside the kernel */
 #define MK_PATH_HALF 3   /* tcgen05 kernel over an f16 image of the matrix built at load time (wide batches) */
-#define MK_PATH_STREAM 4 /* tcgen05 kernel that streams raw Q4_K blocks once (at most 64 rows; in a model: 2..64 rows,
+#define MK_PATH_STREAM 4 /* tcgen05 kernel that streams raw Q4_K blocks once (at most 64 rows; in a model: 1..64 rows,
                           * f16 images above that) */
 
 typedef struct mk_model mk_model;

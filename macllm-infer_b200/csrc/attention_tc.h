@@ -25,7 +25,7 @@ struct AttnTcArgs {
     int n_tiles = 0, n_entries = 0, n_dec_lanes = 0;
     float* part_o = nullptr;    // [n_entries][kv_heads][16][d]
     float* part_ml = nullptr;   // [n_entries][kv_heads][16][2]
-    // optional: one-token lanes also leave their output rows quantised (8-bit blocks, f16 image, group sums) for the
+    // optional: one-token lanes also leave their output rows quantised (8-bit blocks, f16 image) for the
     // matmul that follows; needs (q_heads / kv_heads) * d to be a multiple of 256.  With qout set, `out` may be null.
     ActQ qout;
     int qkind = ACT_Q8K;

@@ -17,8 +17,8 @@ using namespace mk;
 namespace {
 
 struct ActBufs {
-    DevBuf qs, d, bs, xh, gs;
-    ActQ view(int T, int K, int kind, bool want_f16 = false, bool want_group_sums = false) {
+    DevBuf qs, d, bs, xh;
+    ActQ view(int T, int K, int kind, bool want_f16 = false) {
         qs.ensure((size_t)T * K);
         d.ensure((size_t)T * (kind == ACT_Q8K ? K / 256 : K / 32) * 4);
         bs.ensure((size_t)T * (K / 16) * 2 + 16);
@@ -29,10 +29,6 @@ struct ActBufs {
         if (want_f16) {
             xh.ensure((size_t)T * K * 2);
             a.xh = xh.as<__half>();
-        }
-        if (want_f16 && want_group_sums && kind == ACT_Q8K) {
-            gs.ensure((size_t)T * (K / 16) * 2);
-            a.gs = gs.as<__half>();
         }
         return a;
     }
@@ -128,7 +124,7 @@ void qmatmul_case(int32_t type, const void* w, int64_t rows, int64_t cols, const
         if (T <= kQStreamMaxRows) qs_partial.alloc(kSplitScratchBytes);
     }
     const bool tensor = !half && !stream && (path == MK_PATH_TENSOR || (path == MK_PATH_AUTO && qgemm_tc_preferred(dw.w, T)));
-    ActQ a = ab.view(T, (int)cols, kind, tensor || half || stream, stream);
+    ActQ a = ab.view(T, (int)cols, kind, tensor || half || stream);
     NormQuantArgs na;
     na.h = dx.as<float>();
     na.rows = T;
@@ -278,7 +274,7 @@ int32_t mk_k_gated_ffn(int32_t type, const void* gate_w, const void* up_w, int64
         DevBuf dx((size_t)T * cols * 4), dy((size_t)T * F * 2);
         dx.upload(x, (size_t)T * cols * 4);
         ActBufs ab;
-        ActQ a = ab.view(T, (int)cols, kind, true, false);
+        ActQ a = ab.view(T, (int)cols, kind, true);
         NormQuantArgs na;
         na.h = dx.as<float>();
         na.rows = T;
@@ -536,7 +532,7 @@ int32_t mk_k_grouped_qmatmul(int32_t type, const void* w, const void* up_w, int3
         doff.upload(offsets, (size_t)(experts + 1) * 4);
         status.zero(nullptr);
         ActBufs ab;
-        ActQ a = ab.view(P, (int)cols, kind, path == MK_PATH_STREAM, false);
+        ActQ a = ab.view(P, (int)cols, kind, path == MK_PATH_STREAM);
         NormQuantArgs na;
         na.h = dx.as<float>();
         na.rows = P;

@@ -43,10 +43,6 @@ struct ActQ {
     float* d = nullptr;
     int16_t* bsums = nullptr;
     __half* xh = nullptr;
-    // gs (optional, with xh, K-quant rows only): [T][2 * K/32] f16 - the sum of the 32 xh values of every group as an
-    // f16 head (first K/32 entries of a row) and an f16 tail (last K/32), for kernels that apply the Q4_K group
-    // minimums to sums of activations instead of to every weight
-    __half* gs = nullptr;
 };
 
 struct CudaError : std::runtime_error {

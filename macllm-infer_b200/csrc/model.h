@@ -58,7 +58,7 @@ struct ModelConfig {
     // 0 auto (integer GEMV for a few rows, in-kernel dequant GEMM for tens of rows, f16-image GEMM for wide
     // ticks when the image fits), 1 integer GEMV only, 2 in-kernel dequant GEMM whenever the shape allows,
     // 3 f16-image GEMM whenever more than 8 rows share a matrix, 4 like 0 but nothing falls back to the in-kernel
-    // dequant GEMM (f16 images for wide ticks, streamed Q4_K blocks for 2..64 rows)
+    // dequant GEMM (f16 images for wide ticks, streamed Q4_K / Q6_K blocks for 1..64 rows)
     int matmul_path = 0;
     // expert parallelism of a sparse-MoE model: this process holds experts [ep_rank, ep_rank + 1) * experts / ep_size
     // and exchanges per-layer partial sums with the other ranks; ep_size <= 1 keeps every expert here
@@ -157,7 +157,7 @@ private:
     DevBuf e_xh_;                  // routed rows grouped by expert, f16 [T * experts_used][hidden]
     QStreamWeight qs_head_;        // output projection for narrow batches
     DevBuf v_partial_;  // split-K shares of the V projection on streamed ticks
-    int qstream_min_rows_ = 2;  // one row stays on the integer GEMV
+    int qstream_min_rows_ = 1;  // measured: from one row up the streamed kernel is level with the integer GEMV on 2-6 MB matrices and ahead above
     int matmul_stream(const QStreamWeight& W, const ActQ& x, int T, float* y, int ldy, int max_splits, const QStreamWeight* W2 = nullptr);
     HgemmScratch hgemm_scratch() const;
     // Returns the number of K shares; more than one means the result is the sum of that many partials in the

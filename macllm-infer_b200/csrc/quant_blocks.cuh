@@ -12,8 +12,7 @@ namespace mk {
 // activation block (256) or eight Q8_0 blocks (32 = four lanes) are quantised from registers with
 // shuffles only.  Same arithmetic as quantize_row_q8k / quantize_row_q80 in quantize.cu.
 
-__device__ __forceinline__ void quant8_q8k(const float (&v)[8], int lane, int8_t* qs, float* d, int16_t* bsums, __half* xh,
-                                           __half* gs_hi, __half* gs_lo) {
+__device__ __forceinline__ void quant8_q8k(const float (&v)[8], int lane, int8_t* qs, float* d, int16_t* bsums, __half* xh) {
     float amax = 0.f, mx = 0.f;
     int idx = 0;
 #pragma unroll
@@ -53,19 +52,6 @@ __device__ __forceinline__ void quant8_q8k(const float (&v)[8], int lane, int8_t
 #pragma unroll
         for (int i = 0; i < 4; ++i) hv[i] = __floats2half2_rn(__fmul_rn(dd, (float)q[2 * i]), __fmul_rn(dd, (float)q[2 * i + 1]));
         *reinterpret_cast<uint4*>(xh + lane * 8) = *reinterpret_cast<uint4*>(hv);
-        if (gs_hi != nullptr) {  // warp-uniform
-            // sum of the 32 f16 values of the group (four lanes), in a fixed order, as f16 head + tail
-            float part = 0.f;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) part += __low2float(hv[i]) + __high2float(hv[i]);
-            part += __shfl_xor_sync(0xffffffffu, part, 1);
-            part += __shfl_xor_sync(0xffffffffu, part, 2);
-            if ((lane & 3) == 0) {
-                __half hi = __float2half_rn(part);
-                gs_hi[lane >> 2] = hi;
-                gs_lo[lane >> 2] = __float2half_rn(part - __half2float(hi));
-            }
-        }
     }
     int pair = sum + __shfl_xor_sync(0xffffffffu, sum, 1);
     if ((lane & 1) == 0) bsums[lane >> 1] = (int16_t)pair;
@@ -103,8 +89,7 @@ __device__ __forceinline__ void quant_group(const float (&v)[8], int lane, int k
     int8_t* qs = out.qs + r * dim + grp * 256;
     __half* xh = out.xh ? out.xh + r * dim + grp * 256 : nullptr;
     if (kind == ACT_Q8K) {
-        __half* gs = (out.gs && out.xh) ? out.gs + r * (dim / 16) + grp * 8 : nullptr;
-        quant8_q8k(v, lane, qs, out.d + r * (dim / 256) + grp, out.bsums + r * (dim / 16) + grp * 16, xh, gs, gs ? gs + dim / 32 : nullptr);
+        quant8_q8k(v, lane, qs, out.d + r * (dim / 256) + grp, out.bsums + r * (dim / 16) + grp * 16, xh);
     }
     else quant8_q80(v, lane, qs, out.d + r * (dim / 32) + grp * 8, xh);
 }

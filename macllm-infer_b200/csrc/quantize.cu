@@ -348,7 +348,6 @@ void launch_add_norm_quant(const NormQuantArgs& a, cudaStream_t s) {
         MK_LAUNCH_CHECK();
         return;
     }
-    if (a.out.gs != nullptr) throw std::runtime_error("launch_add_norm_quant: group sums need 256-wide, 16-byte aligned rows");
     size_t smem = (size_t)a.dim * sizeof(float);
     ensure_dynamic_smem(reinterpret_cast<const void*>(&add_norm_quant_kernel), smem);
     add_norm_quant_kernel<<<a.rows, NQ_THREADS, smem, s>>>(a);
@@ -368,7 +367,6 @@ void launch_actmul_quant(const float* gate, const float* up, int ld, int T, int 
         MK_LAUNCH_CHECK();
         return;
     }
-    if (out.gs != nullptr) throw std::runtime_error("launch_actmul_quant: group sums need 256-wide, 16-byte aligned rows");
     size_t smem = (size_t)F * sizeof(float);
     ensure_dynamic_smem(reinterpret_cast<const void*>(&actmul_quant_kernel), smem);
     actmul_quant_kernel<<<T, NQ_THREADS, smem, s>>>(gate, up, ld, F, act, act_kind, out, f32_out);

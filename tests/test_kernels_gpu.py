@@ -122,7 +122,7 @@ def test_gated_gemm_equals_gemm_then_activation(ops, orc, name, act, T, F, cols)
 @pytest.mark.parametrize("name,T,rows,cols", [("q4_k", 9, 128, 256), ("q4_k", 33, 300, 1024), ("q4_k", 64, 2048, 2048), ("q4_k", 64, 512, 5632),
                                                ("q4_k", 40, 2560, 2048), ("q4_k", 64, 1000, 11008), ("q4_k", 17, 22016, 2048), ("q4_k", 4, 2048, 2048),
                                                ("q4_k", 16, 3000, 2048), ("q6_k", 9, 128, 256), ("q6_k", 64, 512, 2048), ("q6_k", 33, 1000, 1024),
-                                               ("q6_k", 2, 3072, 2048)])
+                                               ("q6_k", 2, 3072, 2048), ("q4_k", 1, 2048, 2048), ("q4_k", 1, 12288, 4096), ("q6_k", 1, 1000, 1024)])
 def test_streamed_matmul_matches_oracle(ops, orc, monkeypatch, name, T, rows, cols, splits):
     """The decode-tick path: raw Q4_K / Q6_K units by bulk copy, dequantised by the converter warps straight into tensor
     memory, tcgen05 MMA with A from tensor memory.  Ragged row counts, one to 43 block columns, token tiles of 16 / 32 /

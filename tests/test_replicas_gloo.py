@@ -65,3 +65,62 @@ def test_two_replicas_aggregate_over_gloo():
         assert abs(o["slowest"] - want_slowest) < 1e-9
         assert abs(o["rate"] - want_total / want_slowest) < 1e-6 * o["rate"]
     assert outs[1]["seconds"] == want_slowest
+
+
+LOCKSTEP_CHILD = textwrap.dedent("""
+    import importlib, json, sys
+    sys.path.insert(0, %r)
+    import bench
+    import __graft_entry__ as entry
+    entry.load_package()
+    eng = importlib.import_module("macllm_infer_b200.engine")
+    rank, local, world, dist = bench.dist_setup(2, backend="gloo")
+    wl = bench.workloads_module()
+    # rank 0 has twice the requests of rank 1, and Poisson arrivals: the ranks run out of lanes at different ticks
+    w = wl.Workload("lockstep-test", "none", 8 if rank == 0 else 4, (3, 9), 16, 64, 78, prompt=(5, 40), arrival_rate=200.0)
+    reqs = wl.make_requests(w, 32, rank)
+
+    class Counting:
+        # the host-only model with the expert-parallel idle tick of a GGUF model stubbed: counts the ticks this rank idles
+        def __init__(self, inner):
+            self.inner, self.idle = inner, 0
+        def ep_idle_tick(self):
+            self.idle += 1
+        def __getattr__(self, name):
+            return getattr(self.inner, name)
+
+    model = Counting(eng.Model.fake(vocab=32, max_context=256, kv_capacity_tokens=2048))
+    calls = [0]
+    def lockstep(n):
+        calls[0] += 1
+        return int(round(bench.all_sum(dist, float(n))))
+    e = bench.new_engine(eng, model.inner, w, 4, len(reqs[0]))
+    lanes = [n for n in bench.drive(eng, model, e, w, reqs, lockstep)]
+    done = [e.result(i)["state"] for i in bench.drive.last_ids]
+    print(json.dumps(dict(rank=rank, iterations=len(lanes), forwards=sum(1 for n in lanes if n > 0), idle=model.idle, calls=calls[0],
+                          done=done, generated=sum(len(e.result(i)["tokens"]) for i in bench.drive.last_ids), want=int(sum(reqs[1])))), flush=True)
+    dist.destroy_process_group()
+""") % str(ROOT)
+
+
+def test_lock_step_drive_keeps_two_ranks_on_the_same_tick_count():
+    """The host loop of expert parallelism with data-parallel lanes (bench.drive with a lock-step sum, the same loop as
+    engine.run_expert_parallel): every rank ticks until no rank has work left, a rank whose scheduler ran no lane takes the
+    tick idle, and every request still finishes with its own token count."""
+    port = _free_port()
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        procs.append(subprocess.Popen([sys.executable, "-c", LOCKSTEP_CHILD], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    outs = []
+    for p in procs:
+        out, err = p.communicate(timeout=240)
+        assert p.returncode == 0, err[-2000:]
+        outs.append(json.loads(out.strip().splitlines()[-1]))
+    outs.sort(key=lambda o: o["rank"])
+    a, b = outs
+    assert a["iterations"] == b["iterations"] and a["calls"] == b["calls"] == a["iterations"] + 1
+    for o in outs:
+        assert o["forwards"] + o["idle"] == o["iterations"]          # exactly one forward or one idle tick per iteration
+        assert set(o["done"]) == {"done"} and o["generated"] == o["want"]
+    assert b["idle"] > 0 and b["forwards"] < a["forwards"] + a["idle"]  # the rank with fewer requests idled through the tail
