@@ -12,7 +12,10 @@
 namespace mk {
 
 // GGML tensor type ids as stored in GGUF files (the reference's src/gguf.rs:283-297 table).
-enum QType : int { QT_F32 = 0, QT_F16 = 1, QT_Q8_0 = 8, QT_Q4_K = 12, QT_Q6_K = 14 };
+// GGML tensor types (src/gguf.rs:283-345 of the reference).  The kernels read F32, Q8_0, Q4_K and Q6_K in place; the other
+// block formats are decoded once at load into a dense matrix (weights.cpp) and served by the dense f16 GEMM.
+enum QType : int { QT_F32 = 0, QT_F16 = 1, QT_Q4_0 = 2, QT_Q5_0 = 6, QT_Q5_1 = 7, QT_Q8_0 = 8, QT_Q2_K = 10, QT_Q3_K = 11, QT_Q4_K = 12,
+                   QT_Q5_K = 13, QT_Q6_K = 14, QT_BF16 = 30 };
 
 // Activation block formats produced by the quantising kernels.
 enum ActKind : int { ACT_Q8K = 0, ACT_Q80 = 1 };

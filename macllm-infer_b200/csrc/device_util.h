@@ -75,6 +75,7 @@ struct DeviceWeight {
     QWeight w;
     DevBuf b0, b1, b2, b3;
     HalfWeight half;  // optional second copy for wide batches
+    int file_type = -1;  // the GGML type in the file when the matrix was decoded at load (w.type is then F32), else -1
 };
 
 // Upload `rows` x `cols` weights stored in GGUF block format `type` at host pointer `src`.
@@ -84,5 +85,9 @@ void upload_weight(int type, const void* src, int64_t rows, int64_t cols, Device
 
 // Bytes of one row of `cols` weights in GGUF storage (src/gguf.rs:386-408 of the reference).
 int64_t gguf_row_bytes(int type, int64_t cols);
+// Block formats without a kernel of their own (Q4_0, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K, BF16): upload_weight decodes them on the
+// host into a dense f32 matrix.  decode_rows_host is that decoder (host only, no GPU).
+bool decoded_at_load(int type);
+void decode_rows_host(int type, const void* src, int64_t rows, int64_t cols, float* out);
 
 }  // namespace mk

@@ -32,22 +32,32 @@ void expect_f32(const GgufTensor& t) {
     if (t.type != QT_F32) throw std::runtime_error("GGUF tensor `" + t.name + "` must be F32 (norm and router weights are not quantised)");
 }
 
-// Matrices go through the quantised kernels: Q4_K / Q6_K need rows of whole 256-blocks, Q8_0 of whole 32-blocks.
+// Matrices: Q4_K / Q6_K / Q8_0 go through the quantised kernels; the other block formats of the reference's loader
+// (src/gguf.rs:283-345) are decoded at load.  K-quants need rows of whole 256-blocks, the others of whole 32-blocks.
 void expect_matrix_type(const GgufTensor& t) {
     const int64_t cols = t.dims.back();
     switch (t.type) {
         case QT_F32:
-        case QT_F16: return;
+        case QT_F16:
+        case QT_BF16: return;
         case QT_Q8_0:
-            if (cols % 32 != 0) throw std::runtime_error("GGUF tensor `" + t.name + "`: Q8_0 rows must be a multiple of 32 wide");
+        case QT_Q4_0:
+        case QT_Q5_0:
+        case QT_Q5_1:
+            if (cols % 32 != 0) throw std::runtime_error("GGUF tensor `" + t.name + "`: rows of 32-weight blocks must be a multiple of 32 wide");
             return;
         case QT_Q4_K:
         case QT_Q6_K:
+        case QT_Q2_K:
+        case QT_Q3_K:
+        case QT_Q5_K:
             if (cols % 256 != 0) throw std::runtime_error("GGUF tensor `" + t.name + "`: K-quant rows must be a multiple of 256 wide");
             return;
         default:
-            throw std::runtime_error("GGUF tensor `" + t.name + "` uses GGML type " + std::to_string(t.type) +
-                                     ", which this path does not read (F32, F16, Q8_0, Q4_K, Q6_K)");
+            // the wording of GgmlType::from_tag (src/gguf.rs:345-349)
+            throw std::runtime_error("GGUF tensor `" + t.name + "`: unsupported GGML tensor type " + std::to_string(t.type) +
+                                     "; this runtime currently supports F32 (0), F16 (1), Q4_0 (2), Q5_0 (6), Q5_1 (7), Q8_0 (8), Q2_K (10), "
+                                     "Q3_K (11), Q4_K (12), Q5_K (13), Q6_K (14), and BF16 (30)");
     }
 }
 
@@ -63,6 +73,10 @@ GgufAudit validate_decoder_tensors(const GgufFile& f, const ModelSpec& s) {
     auto matrix = [&](const std::string& name, const std::vector<int64_t>& shape) {
         const GgufTensor& t = expect_shape(f, name, shape);
         expect_matrix_type(t);
+        // expert banks are read in place by the expert-grouped kernels; the formats decoded at load have no grouped form
+        if (shape.size() == 3 && t.type != QT_Q4_K && t.type != QT_Q6_K && t.type != QT_Q8_0)
+            throw std::runtime_error("GGUF tensor `" + t.name + "`: expert banks must be Q4_K, Q6_K or Q8_0 (GGML type " + std::to_string(t.type) +
+                                     " has no expert-grouped kernel)");
         ++audit.matrices;
         audit.matrix_bytes += gguf_row_bytes(t.type, t.dims.back()) * (t.elements() / t.dims.back());
     };
@@ -122,7 +136,7 @@ GgufAudit validate_decoder_tensors(const GgufFile& f, const ModelSpec& s) {
     }
     // quantised payloads are only defined for quantisation version 2 (validate_quantization_metadata, src/gguf.rs:1019-1037)
     bool quantised = false;
-    for (const GgufTensor& t : f.tensors()) quantised |= (t.type != QT_F32 && t.type != QT_F16);
+    for (const GgufTensor& t : f.tensors()) quantised |= (t.type != QT_F32 && t.type != QT_F16 && t.type != QT_BF16);
     if (quantised) {
         if (!f.has("general.quantization_version")) throw std::runtime_error("quantized GGUF tensors require general.quantization_version");
         const int64_t v = f.get_int("general.quantization_version");

@@ -179,8 +179,46 @@ int64_t seed_row_bytes(int type, int64_t cols) {
         case 8: return cols % 32 ? -1 : cols / 32 * 34;
         case 12: return cols % 256 ? -1 : cols / 256 * 144;
         case 14: return cols % 256 ? -1 : cols / 256 * 210;
+        // formats written as random block bytes (see random_blocks below)
+        case 2: return cols % 32 ? -1 : cols / 32 * 18;
+        case 6: return cols % 32 ? -1 : cols / 32 * 22;
+        case 7: return cols % 32 ? -1 : cols / 32 * 24;
+        case 10: return cols % 256 ? -1 : cols / 256 * 84;
+        case 11: return cols % 256 ? -1 : cols / 256 * 110;
+        case 13: return cols % 256 ? -1 : cols / 256 * 176;
+        case 30: return cols * 2;
         default: return -1;
     }
+}
+
+// The formats without a quantiser here (Q4_0, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K) are written as seeded random block bytes: any
+// bit pattern is a valid block once its f16 scale fields are finite, and the product and the oracle both read the bytes.
+// The scale fields are set so that the decoded weights have about the asked standard deviation and zero mean (the
+// divisors are the standard deviations of the decoded values of uniformly random bytes with unit scales).
+struct RandomBlock { int type, bytes, d_at, m_at; float d_div, m_per_d; };
+constexpr RandomBlock kRandomBlocks[] = {
+    {2, 18, 0, -1, 4.612f, 0.f},  {6, 22, 0, -1, 9.227f, 0.f},   {7, 24, 0, 2, 9.231f, -15.5f},
+    {10, 84, 80, 82, 13.873f, 1.5f}, {11, 110, 108, -1, 43.331f, 0.f}, {13, 176, 0, 2, 526.319f, 15.5f},
+};
+
+static bool random_blocks(int type, uint64_t key, float std_dev, int64_t n_bytes, uint8_t* o, int threads) {
+    const RandomBlock* rb = nullptr;
+    for (const RandomBlock& b : kRandomBlocks)
+        if (b.type == type) rb = &b;
+    if (rb == nullptr) return false;
+    const int64_t blocks = n_bytes / rb->bytes;
+    const uint16_t dh = f2h(std_dev / rb->d_div), mh = f2h(std_dev / rb->d_div * rb->m_per_d);
+#pragma omp parallel for schedule(static) num_threads(threads)
+    for (int64_t b = 0; b < blocks; ++b) {
+        uint8_t* dst = o + b * rb->bytes;
+        for (int i = 0; i < rb->bytes; i += 8) {
+            const uint64_t w = splitmix64(key ^ splitmix64((uint64_t)(b * 32 + i / 8 + 1)));
+            memcpy(dst + i, &w, (size_t)std::min(8, rb->bytes - i));
+        }
+        memcpy(dst + rb->d_at, &dh, 2);
+        if (rb->m_at >= 0) memcpy(dst + rb->m_at, &mh, 2);
+    }
+    return true;
 }
 
 void seed_tensor(uint64_t seed, uint64_t stream, float std_dev, int type, int64_t rows, int64_t cols, void* out) {
@@ -188,6 +226,7 @@ void seed_tensor(uint64_t seed, uint64_t stream, float std_dev, int type, int64_
     if (rb < 0) throw std::runtime_error("seed_tensor: unsupported type or column count");
     uint64_t key = splitmix64(seed * 0x100000001B3ull + splitmix64(stream));
     uint8_t* o = static_cast<uint8_t*>(out);
+    if (random_blocks(type, key, std_dev, rows * rb, o, std::max(1, (int)std::thread::hardware_concurrency()))) return;
     // every host core, whatever OMP_NUM_THREADS says: launchers of multi-process jobs export 1, which would turn the
     // seconds a seeded checkpoint takes into many minutes.  Rows are independent, so the bytes do not depend on it.
     const int threads = std::max(1, (int)std::thread::hardware_concurrency());
@@ -201,6 +240,7 @@ void seed_tensor(uint64_t seed, uint64_t stream, float std_dev, int type, int64_
             switch (type) {
                 case 0: memcpy(dst, row.data(), (size_t)cols * 4); break;
                 case 1: for (int64_t c = 0; c < cols; ++c) { uint16_t h = f2h(row[c]); memcpy(dst + 2 * c, &h, 2); } break;
+                case 30: for (int64_t c = 0; c < cols; ++c) { uint32_t u; memcpy(&u, &row[c], 4); uint16_t h = (uint16_t)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16); memcpy(dst + 2 * c, &h, 2); } break;
                 case 8: quantize_q8_0(row.data(), cols, dst); break;
                 case 12: quantize_q4_k(row.data(), cols, dst); break;
                 case 14: quantize_q6_k(row.data(), cols, dst); break;

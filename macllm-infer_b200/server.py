@@ -275,8 +275,11 @@ class CompletionServer:
                     pass
                 self.close_connection = True
 
-        self._httpd = ThreadingHTTPServer(bind, Handler)
-        self._httpd.daemon_threads = True
+        class Httpd(ThreadingHTTPServer):
+            request_queue_size = 1024   # the listen backlog: a wave of clients connecting at once must not wait for SYN retries
+            daemon_threads = True
+
+        self._httpd = Httpd(bind, Handler)
         self._http_thread = threading.Thread(target=self._httpd.serve_forever, name="http", daemon=True)
 
     # ------------------------------------------------------------------ lifecycle

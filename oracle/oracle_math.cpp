@@ -42,7 +42,8 @@
 
 extern "C" {
 
-enum { ORC_F32 = 0, ORC_F16 = 1, ORC_Q8_0 = 8, ORC_Q4_K = 12, ORC_Q6_K = 14 };
+enum { ORC_F32 = 0, ORC_F16 = 1, ORC_Q4_0 = 2, ORC_Q5_0 = 6, ORC_Q5_1 = 7, ORC_Q8_0 = 8, ORC_Q2_K = 10, ORC_Q3_K = 11, ORC_Q4_K = 12,
+       ORC_Q5_K = 13, ORC_Q6_K = 14, ORC_BF16 = 30 };
 
 // ---------------------------------------------------------------- f16 helpers
 static inline float h2f(uint16_t h) {
@@ -114,13 +115,110 @@ int64_t orc_row_bytes(int type, int64_t cols) {
         case ORC_Q8_0: return cols / 32 * 34;
         case ORC_Q4_K: return cols / 256 * 144;
         case ORC_Q6_K: return cols / 256 * 210;
+        // the other block formats the reference's loader accepts (src/gguf.rs:283-297, sizes :386-408)
+        case ORC_Q4_0: return cols / 32 * 18;
+        case ORC_Q5_0: return cols / 32 * 22;
+        case ORC_Q5_1: return cols / 32 * 24;
+        case ORC_Q2_K: return cols / 256 * 84;
+        case ORC_Q3_K: return cols / 256 * 110;
+        case ORC_Q5_K: return cols / 256 * 176;
+        case ORC_BF16: return cols * 2;
     }
     return -1;
 }
 
+// The block formats below follow the published GGML layouts; the decoders are pinned against the `gguf` Python package on
+// random block bytes (tests/test_oracle_formats.py).
+static uint16_t rd16(const uint8_t* p) { return (uint16_t)(p[0] | (p[1] << 8)); }
+static uint32_t rd32(const uint8_t* p) { return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24); }
+
+// Q4_0: [d f16][16 bytes]; weight j = low nibble of byte j, weight j + 16 = its high nibble, both offset by 8.
+static void dq_q4_0(const uint8_t* b, float* y) {
+    float d = h2f(rd16(b));
+    for (int j = 0; j < 16; ++j) { y[j] = d * ((b[2 + j] & 0xF) - 8); y[j + 16] = d * ((b[2 + j] >> 4) - 8); }
+}
+// Q5_0 / Q5_1: a fifth bit per weight in a 32-bit word: bit j for weight j, bit j + 16 for weight j + 16.
+static void dq_q5_0(const uint8_t* b, float* y) {
+    float d = h2f(rd16(b));
+    uint32_t hi = rd32(b + 2);
+    for (int j = 0; j < 16; ++j) {
+        int lo0 = b[6 + j] & 0xF, lo1 = b[6 + j] >> 4;
+        y[j] = d * ((lo0 | (((hi >> j) & 1) << 4)) - 16);
+        y[j + 16] = d * ((lo1 | (((hi >> (j + 16)) & 1) << 4)) - 16);
+    }
+}
+static void dq_q5_1(const uint8_t* b, float* y) {
+    float d = h2f(rd16(b)), m = h2f(rd16(b + 2));
+    uint32_t hi = rd32(b + 4);
+    for (int j = 0; j < 16; ++j) {
+        int lo0 = b[8 + j] & 0xF, lo1 = b[8 + j] >> 4;
+        y[j] = d * (float)(lo0 | (((hi >> j) & 1) << 4)) + m;
+        y[j + 16] = d * (float)(lo1 | (((hi >> (j + 16)) & 1) << 4)) + m;
+    }
+}
+// Q2_K: [16 scale bytes: low nibble scale, high nibble min][64 bytes of 2-bit values][d f16][dmin f16]; sixteen groups of 16
+// weights; group g of half n (128 weights) reads bit pair (g / 2) of bytes [32 n + 16 (g % 2), + 16).
+static void dq_q2_k(const uint8_t* b, float* y) {
+    const uint8_t* sc = b; const uint8_t* q = b + 16;
+    float d = h2f(rd16(b + 80)), dmin = h2f(rd16(b + 82));
+    for (int g = 0; g < 16; ++g) {
+        int n = g / 8, gi = g % 8, shift = 2 * (gi / 2);
+        const uint8_t* src = q + 32 * n + 16 * (gi % 2);
+        float dl = d * (sc[g] & 0xF), ml = dmin * (sc[g] >> 4);
+        for (int l = 0; l < 16; ++l) y[16 * g + l] = dl * ((src[l] >> shift) & 3) - ml;
+    }
+}
+// Q3_K: [32 bytes: one high bit per weight][64 bytes of 2-bit values][12 bytes: sixteen 6-bit scales][d f16].
+static void dq_q3_k(const uint8_t* b, float* y) {
+    const uint8_t* hm = b; const uint8_t* q = b + 32; const uint8_t* s = b + 96;
+    float d = h2f(rd16(b + 108));
+    int scale[16];
+    for (int i = 0; i < 16; ++i) {
+        // low 4 bits: nibbles of bytes 0..7; high 2 bits: bit pairs of bytes 8..11
+        int lo = i < 8 ? (s[i] & 0xF) : (s[i - 8] >> 4);
+        int hi2 = (s[8 + (i % 4)] >> (2 * (i / 4))) & 3;
+        scale[i] = (lo | (hi2 << 4)) - 32;
+    }
+    for (int g = 0; g < 16; ++g) {
+        int n = g / 8, gi = g % 8, shift = 2 * (gi / 2), bit = 4 * n + gi / 2;
+        const uint8_t* src = q + 32 * n + 16 * (gi % 2);
+        const uint8_t* hsrc = hm + 16 * (gi % 2);
+        float dl = d * scale[g];
+        for (int l = 0; l < 16; ++l) {
+            int v = (src[l] >> shift) & 3;
+            if (!((hsrc[l] >> bit) & 1)) v -= 4;
+            y[16 * g + l] = dl * v;
+        }
+    }
+}
+// Q5_K: [d f16][dmin f16][12 bytes: eight 6-bit scale / min pairs as in Q4_K][32 bytes: a fifth bit per weight][128 nibble bytes].
+static void dq_q5_k(const uint8_t* b, float* y) {
+    float d = h2f(rd16(b)), dmin = h2f(rd16(b + 2));
+    const uint8_t* scales = b + 4; const uint8_t* qh = b + 16; const uint8_t* ql = b + 48;
+    for (int j = 0; j < 4; ++j) {
+        int sc0, m0, sc1, m1;
+        q4k_scale_min(2 * j, scales, &sc0, &m0);
+        q4k_scale_min(2 * j + 1, scales, &sc1, &m1);
+        float d0 = d * sc0, mm0 = dmin * m0, d1 = d * sc1, mm1 = dmin * m1;
+        for (int l = 0; l < 32; ++l) {
+            int lo = ql[32 * j + l] & 0xF, hi = ql[32 * j + l] >> 4;
+            y[64 * j + l] = d0 * (lo + (((qh[l] >> (2 * j)) & 1) << 4)) - mm0;
+            y[64 * j + 32 + l] = d1 * (hi + (((qh[l] >> (2 * j + 1)) & 1) << 4)) - mm1;
+        }
+    }
+}
+
 // Dequantise one row of `cols` weights.
 void orc_dequant_row(int type, const void* src, int64_t cols, float* dst) {
+    const uint8_t* raw = (const uint8_t*)src;
     switch (type) {
+        case ORC_Q4_0: for (int64_t i = 0; i < cols / 32; ++i) dq_q4_0(raw + i * 18, dst + i * 32); break;
+        case ORC_Q5_0: for (int64_t i = 0; i < cols / 32; ++i) dq_q5_0(raw + i * 22, dst + i * 32); break;
+        case ORC_Q5_1: for (int64_t i = 0; i < cols / 32; ++i) dq_q5_1(raw + i * 24, dst + i * 32); break;
+        case ORC_Q2_K: for (int64_t i = 0; i < cols / 256; ++i) dq_q2_k(raw + i * 84, dst + i * 256); break;
+        case ORC_Q3_K: for (int64_t i = 0; i < cols / 256; ++i) dq_q3_k(raw + i * 110, dst + i * 256); break;
+        case ORC_Q5_K: for (int64_t i = 0; i < cols / 256; ++i) dq_q5_k(raw + i * 176, dst + i * 256); break;
+        case ORC_BF16: for (int64_t i = 0; i < cols; ++i) { uint32_t u = (uint32_t)rd16(raw + 2 * i) << 16; memcpy(dst + i, &u, 4); } break;
         case ORC_F32: memcpy(dst, src, cols * 4); break;
         case ORC_F16: { const uint16_t* h = (const uint16_t*)src; for (int64_t i = 0; i < cols; ++i) dst[i] = h2f(h[i]); break; }
         case ORC_Q8_0: {

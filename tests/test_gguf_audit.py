@@ -32,7 +32,7 @@ def spec_of(pk, fam):
 def write_structure(pk, path, metas, plan, magic=None, version=3, truncate=0):
     """A GGUF file with the given metadata records and tensor descriptors and zero-filled data."""
     seed = pk["seed"]
-    sizes = {13: 176}  # Q5_K, a format this path does not read
+    sizes = {16: 66}  # IQ2_XXS, a format neither the reference's loader nor this path reads
     def nbytes(dims, qtype):
         return int(np.prod(dims)) // 256 * sizes[qtype] if qtype in sizes else seed._tensor_bytes(dims, qtype)
     head = struct.pack("<IIQQ", seed.GGUF_MAGIC if magic is None else magic, version, len(plan), len(metas)) + b"".join(metas)
@@ -119,7 +119,7 @@ def test_tensor_of_another_sequence_mixer(pk, tmp_path):
 def test_block_formats(pk, tmp_path):
     def retype(name, qtype):
         return lambda spec, m, p: (m, [(n, d, qtype if n == name else q, s) for n, d, q, s in p])
-    refused(pk, broken(pk, tmp_path, "llama", retype("blk.0.ffn_down.weight", 13)), "GGML type 13")
+    refused(pk, broken(pk, tmp_path, "llama", retype("blk.0.ffn_down.weight", 16)), "unsupported GGML tensor type 16")
     refused(pk, broken(pk, tmp_path, "llama", retype("blk.0.attn_norm.weight", pk["capi"].TYPE_F16)), "`blk.0.attn_norm.weight` must be F32")
 
 
