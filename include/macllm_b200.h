@@ -38,6 +38,14 @@ extern "C" {
 #define MK_TYPE_Q8_0 8
 #define MK_TYPE_Q4_K 12
 #define MK_TYPE_Q6_K 14
+/* decoded once at load into a dense matrix and served by the dense f16 GEMM (no kernel reads them in place) */
+#define MK_TYPE_Q4_0 2
+#define MK_TYPE_Q5_0 6
+#define MK_TYPE_Q5_1 7
+#define MK_TYPE_Q2_K 10
+#define MK_TYPE_Q3_K 11
+#define MK_TYPE_Q5_K 13
+#define MK_TYPE_BF16 30
 
 /* Matmul path selection for mk_k_qmatmul. */
 #define MK_PATH_AUTO 0
@@ -407,6 +415,9 @@ int32_t mk_host_sample_greedy(float* logits, int32_t vocab, const uint32_t* hist
  * Used to build the synthetic GGUF checkpoints both this library and the CPU oracle load. */
 int32_t mk_seed_tensor(uint64_t seed, uint64_t stream, float std, int32_t type, int64_t rows, int64_t cols, void* out);
 int64_t mk_row_bytes(int32_t type, int64_t cols);
+/* Host only: the load-time decoder of the block formats no kernel reads in place (MK_TYPE_Q4_0, Q5_0, Q5_1, Q2_K, Q3_K,
+ * Q5_K, BF16): `rows` rows of mk_row_bytes(type, cols) bytes each -> out[rows][cols] f32.  Needs no GPU. */
+int32_t mk_decode_rows(int32_t type, const void* src, int64_t rows, int64_t cols, float* out);
 
 /* ------------------------------------------------------------------------------------------------
  * Kernel-level entry points (unit parity).  Host buffers in and out; each call stages its operands

@@ -14,6 +14,7 @@ LIB_PATH = HERE / "libmacllm_b200.so"
 
 MK_OK, MK_KV_EXHAUSTED = 0, 1
 TYPE_F32, TYPE_F16, TYPE_Q8_0, TYPE_Q4_K, TYPE_Q6_K = 0, 1, 8, 12, 14
+TYPE_Q4_0, TYPE_Q5_0, TYPE_Q5_1, TYPE_Q2_K, TYPE_Q3_K, TYPE_Q5_K, TYPE_BF16 = 2, 6, 7, 10, 11, 13, 30
 PATH_AUTO, PATH_GEMV, PATH_TENSOR, PATH_HALF, PATH_STREAM = 0, 1, 2, 3, 4
 FWD_WANT_LOGITS, FWD_WANT_TOKENS = 1, 2
 
@@ -191,6 +192,7 @@ SIGNATURES = {
     "mk_host_sample_greedy": (_i32, [P, _i32, P, _i32, _f32, P, _i32, _f32, _f32, C.POINTER(_u32)]),
     "mk_seed_tensor": (_i32, [_u64, _u64, _f32, _i32, _i64, _i64, P]),
     "mk_row_bytes": (_i64, [_i32, _i64]),
+    "mk_decode_rows": (_i32, [_i32, P, _i64, _i64, P]),
     "mk_k_quantize": (_i32, [_i32, P, _i32, _i32, P, P, P]),
     "mk_k_add_norm": (_i32, [P, P, _f32, P, P, _f32, _i32, _i32, P]),
     "mk_k_qmatmul": (_i32, [_i32, P, _i64, _i64, P, _i32, P, _i32]),

@@ -2,6 +2,7 @@
 #include "../../include/macllm_b200.h"
 #include "c_api_util.h"
 #include "seed_model.h"
+#include "device_util.h"
 #include "sha256.h"
 #include "host_sampler.h"
 #include <cstring>
@@ -55,6 +56,13 @@ int32_t mk_seed_tensor(uint64_t seed, uint64_t stream, float std_dev, int32_t ty
 }
 
 int64_t mk_row_bytes(int32_t type, int64_t cols) { return seed_row_bytes(type, cols); }
+
+int32_t mk_decode_rows(int32_t type, const void* src, int64_t rows, int64_t cols, float* out) {
+    return guarded([&] {
+        if (src == nullptr || out == nullptr || rows <= 0 || cols <= 0) throw std::runtime_error("mk_decode_rows: bad arguments");
+        decode_rows_host(type, src, rows, cols, out);
+    });
+}
 
 int32_t mk_host_sample_greedy(float* logits, int32_t vocab, const uint32_t* history, int32_t n_history, float repetition_penalty,
                               const uint32_t* generated, int32_t n_generated, float presence_penalty, float frequency_penalty,

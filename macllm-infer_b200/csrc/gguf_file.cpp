@@ -56,6 +56,13 @@ int64_t row_bytes_of(int type, int64_t cols) {
         case 8: return cols / 32 * 34;
         case 12: return cols / 256 * 144;
         case 14: return cols / 256 * 210;
+        case 2: return cols / 32 * 18;     // Q4_0
+        case 6: return cols / 32 * 22;     // Q5_0
+        case 7: return cols / 32 * 24;     // Q5_1
+        case 10: return cols / 256 * 84;   // Q2_K
+        case 11: return cols / 256 * 110;  // Q3_K
+        case 13: return cols / 256 * 176;  // Q5_K
+        case 30: return cols * 2;          // BF16
         default: return -1;
     }
 }

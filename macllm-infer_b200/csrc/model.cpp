@@ -537,6 +537,7 @@ void Model::matmul(const DeviceWeight& DW, const ActQ& x, int T, float* y, int l
         matmul_half(DW.half, x, T, y, ldy, scale, softcap);
         return;
     }
+    if (W.type == QT_F32) throw std::runtime_error("a dense matrix reached the quantised matmul paths (its f16 image is missing)");
     const bool tc = tensor_path(W, T) && x.xh != nullptr;
     // algorithmic traffic of one call: the matrix as stored, the activation rows as consumed, the f32 result
     const double act_bytes = tc ? 2.0 * T * W.cols : 1.0 * T * W.cols;
@@ -556,18 +557,32 @@ void Model::matmul(const DeviceWeight& DW, const ActQ& x, int T, float* y, int l
 // The f16 images of the dense layer matrices (2 bytes per weight), built when the configuration asks for
 // them and, in automatic mode, only when they fit beside everything else with room to spare.
 void Model::build_half_cache() {
+    // Matrices without a quantised kernel - F32 / F16 / BF16 in the file, or a block format decoded at load - are dense
+    // (the reference multiplies them without quantising the activations, src/model_weights.rs:346-377): the f16 GEMM
+    // serves them at every row count, so their images are not optional and every matmul of the model takes that route.
+    DeviceWeight& head_first = ms_.tied ? token_embd_ : output_;
+    dense_matrices_ = head_first.w.type == QT_F32;
+    for (size_t l = 0; l < lw_.size(); ++l) {
+        LayerWeights& w = lw_[l];
+        for (DeviceWeight* dw : {&w.wq, &w.wk, &w.wv, &w.wo}) dense_matrices_ |= dw->w.type == QT_F32;
+        if (!ms_.layer[l].moe)
+            for (DeviceWeight* dw : {&w.gate, &w.up, &w.down}) dense_matrices_ |= dw->w.type == QT_F32;
+    }
+    if (dense_matrices_ && cfg_.matmul_path != 0 && cfg_.matmul_path != 3 && cfg_.matmul_path != 4)
+        throw std::runtime_error("this checkpoint has dense matrices (F32 / F16 / BF16, or a block format decoded at load): they need the f16 "
+                                 "images, which matmul_path " + std::to_string(cfg_.matmul_path) + " does not build");
     if (cfg_.matmul_path != 0 && cfg_.matmul_path != 3 && cfg_.matmul_path != 4) return;
-    hgemm_min_rows_ = cfg_.matmul_path == 0 ? 33 : 9;
+    hgemm_min_rows_ = dense_matrices_ ? 1 : (cfg_.matmul_path == 0 ? 33 : 9);
     size_t total = 0;
     for (size_t l = 0; l < lw_.size(); ++l) {
         LayerWeights& w = lw_[l];
         for (DeviceWeight* dw : {&w.wq, &w.wk, &w.wv, &w.wo}) {
-            if (!hgemm_tc_supported(dw->w)) return;  // all or nothing: the forward pass takes one route per tick
+            if (!hgemm_tc_supported(dw->w)) { half_cache_refused("a layer matrix the f16 GEMM does not take"); return; }  // all or nothing: the forward pass takes one route per tick
             total += half_weight_bytes(dw->w);
         }
         if (!ms_.layer[l].moe)
             for (DeviceWeight* dw : {&w.gate, &w.up, &w.down}) {
-                if (!hgemm_tc_supported(dw->w)) return;
+                if (!hgemm_tc_supported(dw->w)) { half_cache_refused("a layer matrix the f16 GEMM does not take"); return; }
                 total += half_weight_bytes(dw->w);
             }
     }
@@ -579,8 +594,9 @@ void Model::build_half_cache() {
         if (cfg_.max_batch_tokens < hgemm_min_rows_) return;
         size_t free_b = 0, total_b = 0;
         MK_CUDA(cudaMemGetInfo(&free_b, &total_b));
-        if (total + (size_t(4) << 30) > free_b) return;  // keep 4 GiB of headroom
+        if (total + (size_t(4) << 30) > free_b) { half_cache_refused("not enough free device memory for the f16 images"); return; }  // keep 4 GiB of headroom
     }
+    if (dense_matrices_ && !head_half) half_cache_refused("an output matrix the f16 GEMM does not take");
     if (head_half) build_half_weight(head_dw.w, head_dw.half, stream_);
     for (size_t l = 0; l < lw_.size(); ++l) {
         LayerWeights& w = lw_[l];
@@ -598,6 +614,11 @@ void Model::build_half_cache() {
     MK_CUDA(cudaStreamSynchronize(stream_));
     half_cache_ = true;
     half_cache_bytes_ = (int64_t)total;
+}
+
+// Quantised models simply stay on the integer paths without the images; a model with dense matrices cannot run.
+void Model::half_cache_refused(const char* why) const {
+    if (dense_matrices_) throw std::runtime_error(std::string("this checkpoint has dense matrices, which need the f16 images: ") + why);
 }
 
 // Re-tiled copies for the narrow-batch matmul over raw Q4_K / Q6_K blocks.  [wq; wk] and [gate; up] are moved into one
@@ -799,7 +820,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
         prof_end();
     ++launches_;
 
-    const bool f16_T = cfg_.matmul_path != 1 && (cfg_.matmul_path == 2 || T > 8 || (qstream_ && T >= qstream_min_rows_));
+    const bool f16_T = dense_matrices_ || (cfg_.matmul_path != 1 && (cfg_.matmul_path == 2 || T > 8 || (qstream_ && T >= qstream_min_rows_)));
     const float* pending = nullptr;        // branch output not yet added to the residual stream
     const float* pending_post = nullptr;   // its sandwich post-norm weight, if any
     int pending_splits = 1;                // > 1: `pending` is that many split-K partials, T * H floats apart
@@ -1206,7 +1227,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
     const DeviceWeight& head_dw = ms_.tied ? token_embd_ : output_;
     const QWeight& head = head_dw.w;
     {
-        const bool f16_B = cfg_.matmul_path != 1 && (cfg_.matmul_path == 2 || B > 8);
+        const bool f16_B = dense_matrices_ || (cfg_.matmul_path != 1 && (cfg_.matmul_path == 2 || B > 8));
         int kind = act_kind_of(head);
         ActQ xl = act_view(l_qs_, l_d_, l_bs_, l_xh_, B, H, kind, f16_B);
         NormQuantArgs ng;

@@ -157,6 +157,8 @@ private:
     DevBuf e_xh_;                  // routed rows grouped by expert, f16 [T * experts_used][hidden]
     QStreamWeight qs_head_;        // output projection for narrow batches
     DevBuf v_partial_;  // split-K shares of the V projection on streamed ticks
+    bool dense_matrices_ = false;  // some matrix is F32 / F16 / BF16 or was decoded at load: the f16 GEMM serves every row count
+    void half_cache_refused(const char* why) const;
     int qstream_min_rows_ = 1;  // measured: from one row up the streamed kernel is level with the integer GEMV on 2-6 MB matrices and ahead above
     int matmul_stream(const QStreamWeight& W, const ActQ& x, int T, float* y, int ldy, int max_splits, const QStreamWeight* W2 = nullptr);
     HgemmScratch hgemm_scratch() const;

@@ -24,6 +24,14 @@ def row_bytes(qtype: int, cols: int) -> int:
     return int(capi.lib().mk_row_bytes(qtype, cols))
 
 
+def decode_rows(qtype: int, w: np.ndarray, rows: int, cols: int) -> np.ndarray:
+    """The load-time host decoder of the block formats no kernel reads in place (Q4_0, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K, BF16)."""
+    w = np.ascontiguousarray(w)
+    out = np.empty((rows, cols), dtype=np.float32)
+    capi.check(capi.lib().mk_decode_rows(qtype, _p(w), rows, cols, _p(out)))
+    return out
+
+
 def seed_tensor(seed: int, stream: int, std: float, qtype: int, rows: int, cols: int) -> np.ndarray:
     """N(0, std) weights from the counter-based generator, quantised to `qtype`; returns raw block bytes."""
     rb = row_bytes(qtype, cols)

@@ -143,8 +143,8 @@ static void dq_q5_0(const uint8_t* b, float* y) {
     uint32_t hi = rd32(b + 2);
     for (int j = 0; j < 16; ++j) {
         int lo0 = b[6 + j] & 0xF, lo1 = b[6 + j] >> 4;
-        y[j] = d * ((lo0 | (((hi >> j) & 1) << 4)) - 16);
-        y[j + 16] = d * ((lo1 | (((hi >> (j + 16)) & 1) << 4)) - 16);
+        y[j] = d * ((lo0 | (int)(((hi >> j) & 1) << 4)) - 16);
+        y[j + 16] = d * ((lo1 | (int)(((hi >> (j + 16)) & 1) << 4)) - 16);
     }
 }
 static void dq_q5_1(const uint8_t* b, float* y) {
@@ -152,8 +152,8 @@ static void dq_q5_1(const uint8_t* b, float* y) {
     uint32_t hi = rd32(b + 4);
     for (int j = 0; j < 16; ++j) {
         int lo0 = b[8 + j] & 0xF, lo1 = b[8 + j] >> 4;
-        y[j] = d * (float)(lo0 | (((hi >> j) & 1) << 4)) + m;
-        y[j + 16] = d * (float)(lo1 | (((hi >> (j + 16)) & 1) << 4)) + m;
+        y[j] = d * (float)(lo0 | (int)(((hi >> j) & 1) << 4)) + m;
+        y[j + 16] = d * (float)(lo1 | (int)(((hi >> (j + 16)) & 1) << 4)) + m;
     }
 }
 // Q2_K: [16 scale bytes: low nibble scale, high nibble min][64 bytes of 2-bit values][d f16][dmin f16]; sixteen groups of 16

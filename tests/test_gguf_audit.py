@@ -119,7 +119,7 @@ def test_tensor_of_another_sequence_mixer(pk, tmp_path):
 def test_block_formats(pk, tmp_path):
     def retype(name, qtype):
         return lambda spec, m, p: (m, [(n, d, qtype if n == name else q, s) for n, d, q, s in p])
-    refused(pk, broken(pk, tmp_path, "llama", retype("blk.0.ffn_down.weight", 16)), "unsupported GGML tensor type 16")
+    refused(pk, broken(pk, tmp_path, "llama", retype("blk.0.ffn_down.weight", 16)), "unsupported GGML type 16")
     refused(pk, broken(pk, tmp_path, "llama", retype("blk.0.attn_norm.weight", pk["capi"].TYPE_F16)), "`blk.0.attn_norm.weight` must be F32")
 
 

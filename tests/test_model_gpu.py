@@ -360,3 +360,36 @@ def test_full_size_smollm3_properties(pk, tmp_path_factory):
 
 def test_no_cpu_fallback_symbols_are_loaded(pk):
     assert pk["capi"].lib().mk_device_count() >= 1
+
+
+@pytest.mark.parametrize("matrix_type,high_type", [(2, 13), (6, 11), (7, 10), (30, 1), (12, 13)])
+def test_block_formats_decoded_at_load_match_oracle(pk, tmp_path_factory, matrix_type, high_type):
+    """Checkpoints in the block formats no kernel reads in place - Q4_0 with Q5_K, Q5_0 with Q3_K, Q5_1 with Q2_K, BF16
+    with F16, and Q4_K layers with Q5_K for attn_v and the output matrix - are decoded at load and served by the dense f16
+    GEMM at every row count (prefill chunks and one-token ticks alike).  The oracle multiplies such matrices in f32 without
+    quantising the activations, like the reference's dense path; the product's operands are their f16 roundings and its KV
+    is f16, so the logits agree to a few 2^-10 of their magnitude per layer (bound: 2.5 % of the largest logit, cosine
+    0.9995), schedules and pool counters exactly."""
+    path, spec = make_checkpoint(pk, tmp_path_factory, "llama", matrix_type=matrix_type, high_type=high_type)
+    rng = np.random.default_rng(4)
+    prompts = [rng.integers(3, spec.vocab, size=n) for n in (37, 9, 64)]
+    model, pe, om, oe_, alt = run_pair(pk, path, prompts, [6, 4, 5], kv_dtype="f16", matmul_path=0, oracle_kv="f32",
+                                       engine_kw=dict(scheduler_token_budget=64, prefill_token_quantum=32))
+    assert pe.trace() == [[tuple(l) for l in t] for t in oe_.trace]
+    assert model.pool_stats() == om.pool.stats()
+    worst = env = scale = 0.0
+    cos = 1.0
+    for rid in range(3):
+        rp, ro, ra = pe.result(rid), oe_.results[rid], alt.results[rid]
+        assert rp["state"] == ro.state == "done"
+        lo = np.array(ro.logits)
+        same, rows = agreeing_rows(list(rp["tokens"]), ro.tokens, pe.logits(rid), lo)
+        w, c = drift(pe.logits(rid)[:rows], lo[:rows])
+        worst, cos, scale = max(worst, w), min(cos, c), max(scale, float(np.abs(lo[:rows]).max()))
+        _, rows_e = agreeing_rows(ra.tokens, ro.tokens, ra.logits, lo)
+        env = max(env, drift(np.array(ra.logits)[:rows_e], lo[:rows_e])[0])
+        if same < len(ro.tokens):
+            top2 = np.sort(lo[same])[-2:]
+            assert top2[1] - top2[0] <= 2 * max(worst, 1e-3), f"request {rid} diverged at step {same} without a near-tie"
+    print(matrix_type, high_type, dict(worst=worst, cos=cos, envelope=env, scale=scale))
+    assert worst <= 0.025 * scale + 3 * env and cos >= 0.9995, (worst, cos, env, scale)

@@ -83,3 +83,44 @@ def test_embedding_rows_equal_dequantised_rows(ops, orc):
         w = ops.seed_tensor(1, 9, 0.02, qtype, rows, cols)
         ids = [3, 39, 0]
         assert np.array_equal(orc.embed(qtype, w, cols, ids), orc.dequant(qtype, w, rows, cols)[ids])
+
+
+# The block formats no kernel reads in place: the oracle's decoder and the product's load-time host decoder are two
+# independent restatements of the public layouts; both are pinned against the `gguf` package on seeded random blocks
+# (any bit pattern is a valid block once its f16 scale fields are finite) and on arbitrary bytes.
+LOAD_DECODED = [("q4_0", 2, gguf.GGMLQuantizationType.Q4_0, 18, 32), ("q5_0", 6, gguf.GGMLQuantizationType.Q5_0, 22, 32),
+                ("q5_1", 7, gguf.GGMLQuantizationType.Q5_1, 24, 32), ("q2_k", 10, gguf.GGMLQuantizationType.Q2_K, 84, 256),
+                ("q3_k", 11, gguf.GGMLQuantizationType.Q3_K, 110, 256), ("q5_k", 13, gguf.GGMLQuantizationType.Q5_K, 176, 256)]
+F16_FIELDS = {2: [0], 6: [0], 7: [0, 2], 10: [80, 82], 11: [108], 13: [0, 2]}
+
+
+@pytest.mark.parametrize("name,qtype,gtype,block_bytes,block_weights", LOAD_DECODED)
+def test_load_decoded_formats_match_gguf_package(ops, orc, name, qtype, gtype, block_bytes, block_weights):
+    rows, cols = 6, 1024
+    rb = ops.row_bytes(qtype, cols)
+    assert rb == cols // block_weights * block_bytes == orc.row_bytes(qtype, cols)
+    # seeded blocks as the checkpoint writer makes them: decoded weights of about the asked spread, zero mean
+    w = ops.seed_tensor(5, 9, 0.02, qtype, rows, cols)
+    want = quants.dequantize(w.reshape(rows, rb), gtype)
+    assert np.isfinite(want).all() and 0.012 < want.std() < 0.03 and abs(want.mean()) < 0.004
+    assert np.array_equal(orc.dequant(qtype, w, rows, cols), want.astype(np.float32))
+    assert np.array_equal(ops.decode_rows(qtype, w, rows, cols), want.astype(np.float32))
+    # arbitrary bytes, scale fields kept finite
+    raw = np.random.default_rng(qtype).integers(0, 256, size=(rows, rb), dtype=np.uint8)
+    view = raw.reshape(rows, rb // block_bytes, block_bytes)
+    for off in F16_FIELDS[qtype]:
+        view[:, :, off + 1] &= 0x3B
+    want = quants.dequantize(raw, gtype).astype(np.float32)
+    assert np.allclose(orc.dequant(qtype, raw, rows, cols), want, rtol=1e-6, atol=1e-7)
+    assert np.allclose(ops.decode_rows(qtype, raw, rows, cols), want, rtol=1e-6, atol=1e-7)
+
+
+def test_bf16_rows_decode_exactly(ops, orc):
+    rows, cols = 3, 64
+    w = ops.seed_tensor(1, 2, 0.02, 30, rows, cols)
+    assert w.size == rows * cols * 2
+    want = (w.view(np.uint16).astype(np.uint32) << 16).view(np.float32).reshape(rows, cols)
+    ref = np.frombuffer(ops.seed_tensor(1, 2, 0.02, 0, rows, cols).tobytes(), dtype=np.float32).reshape(rows, cols)
+    assert np.max(np.abs(want - ref)) <= np.max(np.abs(ref)) * 2 ** -8       # round-to-nearest-even truncation to 8 bits of mantissa
+    assert np.array_equal(orc.dequant(30, w, rows, cols), want)
+    assert np.array_equal(ops.decode_rows(30, w, rows, cols), want)
