@@ -378,7 +378,7 @@ def test_block_formats_decoded_at_load_match_oracle(pk, tmp_path_factory, matrix
     assert pe.trace() == [[tuple(l) for l in t] for t in oe_.trace]
     assert model.pool_stats() == om.pool.stats()
     worst = env = scale = 0.0
-    cos = 1.0
+    cos = env_cos = 1.0
     for rid in range(3):
         rp, ro, ra = pe.result(rid), oe_.results[rid], alt.results[rid]
         assert rp["state"] == ro.state == "done"
@@ -387,9 +387,11 @@ def test_block_formats_decoded_at_load_match_oracle(pk, tmp_path_factory, matrix
         w, c = drift(pe.logits(rid)[:rows], lo[:rows])
         worst, cos, scale = max(worst, w), min(cos, c), max(scale, float(np.abs(lo[:rows]).max()))
         _, rows_e = agreeing_rows(ra.tokens, ro.tokens, ra.logits, lo)
-        env = max(env, drift(np.array(ra.logits)[:rows_e], lo[:rows_e])[0])
+        w_e, c_e = drift(np.array(ra.logits)[:rows_e], lo[:rows_e])
+        env, env_cos = max(env, w_e), min(env_cos, c_e)
         if same < len(ro.tokens):
             top2 = np.sort(lo[same])[-2:]
             assert top2[1] - top2[0] <= 2 * max(worst, 1e-3), f"request {rid} diverged at step {same} without a near-tie"
-    print(matrix_type, high_type, dict(worst=worst, cos=cos, envelope=env, scale=scale))
-    assert worst <= 0.025 * scale + 3 * env and cos >= 0.9995, (worst, cos, env, scale)
+    print(matrix_type, high_type, dict(worst=worst, cos=cos, envelope=env, envelope_cos=env_cos, scale=scale))
+    # the mixed checkpoint keeps Q4_K matrices, whose integer arithmetic in the oracle has its own order-to-order envelope
+    assert worst <= 0.025 * scale + 3 * env and cos >= min(0.9995, 1 - 3 * (1 - env_cos)), (worst, cos, env, env_cos, scale)
