@@ -878,7 +878,9 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
             qk_splits = matmul_stream(w.qs_qk, xa, T, qp, QKVW, kMaxShares);
             v_splits = matmul_half(w.wv.half, xa, T, vp, QKVW, 1.f, 0.f, kMaxShares, v_partial_.as<float>(), v_partial_.size() / 4);
         } else if (w.qkv_half.ready && T >= hgemm_min_rows_ && xa.xh != nullptr) {
-            matmul_half(w.qkv_half, xa, T, qp, QKVW, 1.f, 0.f);
+            // a tick of a hundred rows has fewer output tiles than SMs: the plan may share K out, the consumer adds the shares
+            qk_splits = v_splits = matmul_half(w.qkv_half, xa, T, qp, QKVW, 1.f, 0.f, kMaxShares);
+            qkv_joint = qk_splits > 1;
         } else if (w.qk_raw.size() > 0) {
             // [wq; wk] share one buffer: one launch for both (their outputs are adjacent columns of the row)
             DeviceWeight qk;
