@@ -367,9 +367,10 @@ def test_block_formats_decoded_at_load_match_oracle(pk, tmp_path_factory, matrix
     """Checkpoints in the block formats no kernel reads in place - Q4_0 with Q5_K, Q5_0 with Q3_K, Q5_1 with Q2_K, BF16
     with F16, and Q4_K layers with Q5_K for attn_v and the output matrix - are decoded at load and served by the dense f16
     GEMM at every row count (prefill chunks and one-token ticks alike).  The oracle multiplies such matrices in f32 without
-    quantising the activations, like the reference's dense path; the product's operands are their f16 roundings and its KV
-    is f16, so the logits agree to a few 2^-10 of their magnitude per layer (bound: 2.5 % of the largest logit, cosine
-    0.9995), schedules and pool counters exactly."""
+    quantising the activations, like the reference's dense path; the product feeds every matmul the f16 image of the 8-bit
+    activation blocks (one activation buffer serves all matrices of a layer) and keeps f16 KV, so the logits differ by
+    that quantisation noise: bound 2.5 % of the largest logit for the all-dense checkpoints, 5 % for the mixed one (whose
+    Q4_K matrices add the integer arithmetic's own order-to-order envelope); schedules and pool counters exactly."""
     path, spec = make_checkpoint(pk, tmp_path_factory, "llama", matrix_type=matrix_type, high_type=high_type)
     rng = np.random.default_rng(4)
     prompts = [rng.integers(3, spec.vocab, size=n) for n in (37, 9, 64)]
@@ -393,5 +394,6 @@ def test_block_formats_decoded_at_load_match_oracle(pk, tmp_path_factory, matrix
             top2 = np.sort(lo[same])[-2:]
             assert top2[1] - top2[0] <= 2 * max(worst, 1e-3), f"request {rid} diverged at step {same} without a near-tie"
     print(matrix_type, high_type, dict(worst=worst, cos=cos, envelope=env, envelope_cos=env_cos, scale=scale))
-    # the mixed checkpoint keeps Q4_K matrices, whose integer arithmetic in the oracle has its own order-to-order envelope
-    assert worst <= 0.025 * scale + 3 * env and cos >= min(0.9995, 1 - 3 * (1 - env_cos)), (worst, cos, env, env_cos, scale)
+    mixed = matrix_type in (8, 12, 14)
+    assert worst <= (0.05 if mixed else 0.025) * scale + 3 * env, (worst, env, scale)
+    assert cos >= (min(0.999, 1 - 3 * (1 - env_cos)) if mixed else 0.9995), (cos, env_cos)
