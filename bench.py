@@ -18,8 +18,15 @@ blocks.  One "step" is that whole batch, admission to last token.  The metric is
   roofline  the dominant kernel class of one extra profiled step (CUDA events around every launch)
   cpu_baseline  the CPU oracle (a port of the reference's CPU path) timed on a bounded sample
 
-N > 1 (torchrun) runs N independent replicas, one per GPU, each with its own request stream (the path
-has no exchange step for dense models); the reported time is the max over ranks.
+The other four workloads of the metric (`--workload`: tinyllama-1.1b-batch4, qwen3-8b-prefix32 with a shared prefix and
+the prefix cache, gemma2-9b-long128, qwen3-30b-a3b-poisson with seeded Poisson arrivals) run the same way on their own
+shapes; `--limit-requests` / `--new-tokens` cut slices of them.
+
+N > 1 (torchrun): dense workloads run N independent replicas, one per GPU, each with its own request stream (the path
+has no exchange step for them); the sparse-MoE workload runs expert parallelism with data-parallel lanes - every rank
+serves its own requests and each MoE layer exchanges the routed rows (`config.ep`; `--ep off` for replicas).  The
+reported time is the max over ranks.  `--http-clients N` adds a step through the `/completion` endpoint (`http` key),
+`--microbench` prints the Q4_K matmul GB/s of the decode shapes instead.
 """
 from __future__ import annotations
 
