@@ -228,3 +228,18 @@ def test_cache_prompt_false_hits_the_prefix_cache_but_publishes_nothing(mk, srv_
         assert cached(True) == hit
     finally:
         s.stop()
+
+
+def test_the_benchmark_step_through_the_endpoint_counts_every_token(mk):
+    """bench.http_step on the host-only model: every request of a workload goes through POST /completion from concurrent
+    clients and the step's token count is prompt + generated tokens of all of them."""
+    import bench
+    eng = importlib.import_module("macllm_infer_b200.engine")
+    wl = bench.workloads_module()
+    w = wl.Workload("http-test", "none", 10, (2, 6), 16, 64, 91, prompt=(4, 30))
+    reqs = wl.make_requests(w, 64, 0, 0)
+    model = eng.Model.fake(vocab=64, max_context=512, kv_capacity_tokens=4096)
+    out = bench.http_step(eng, model, w, reqs, 4, 3)
+    want = sum(len(p) for p in reqs[0]) + int(sum(reqs[1]))
+    assert out["requests"] == 10 and out["clients"] == 3
+    assert abs(out["value"] * out["wall_s"] - want) <= 0.02 * want          # wall_s is rounded to a millisecond

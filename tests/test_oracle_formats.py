@@ -124,3 +124,14 @@ def test_bf16_rows_decode_exactly(ops, orc):
     assert np.max(np.abs(want - ref)) <= np.max(np.abs(ref)) * 2 ** -8       # round-to-nearest-even truncation to 8 bits of mantissa
     assert np.array_equal(orc.dequant(30, w, rows, cols), want)
     assert np.array_equal(ops.decode_rows(30, w, rows, cols), want)
+
+
+def test_host_decoder_refuses_what_it_does_not_decode(ops, mk):
+    import importlib
+    capi = importlib.import_module("macllm_infer_b200._capi")
+    raw = np.zeros(144 * 4, dtype=np.uint8)
+    for qtype, cols in ((12, 256), (8, 32), (99, 32)):     # formats the kernels read in place, and an unknown id
+        with pytest.raises(capi.MkError):
+            ops.decode_rows(qtype, raw, 1, cols)
+    with pytest.raises(capi.MkError):
+        ops.decode_rows(13, raw, 1, 300)                    # not a whole number of 256-weight blocks
