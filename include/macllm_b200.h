@@ -374,7 +374,9 @@ int32_t mk_kvtable_fork_prefix(mk_kvtable* t, int64_t tokens, mk_kvtable** out);
 int32_t mk_kvtable_attach_prefix(mk_kvtable* t, mk_kvtable* src, int64_t tokens);
 /* SharedPagedKvPool::reserve_batch + commit in one step (cache.rs:2331-2445,2947-2979): append
  * n_tokens[i] tokens to tables[i]; MK_KV_EXHAUSTED mutates nothing.  When commit == 0 the reservation
- * is rolled back instead.  copies_out (optional, capacity in *n_copies as triples) receives the
+ * is rolled back untouched (its blocks return to the free list directly); commit == 2 rolls it back after marking its
+ * pages as touched by the device, the path of a forward that failed midway (cache.rs:1214-1276): they stay retired
+ * until the epoch completes.  copies_out (optional, capacity in *n_copies as triples) receives the
  * copy-on-write (src_slot, dst_slot, rows) triples. */
 int32_t mk_kvpool_append_batch(mk_kvpool* p, mk_kvtable** tables, const int32_t* n_tokens, int32_t n, int32_t commit,
                                int64_t* copies_out, int32_t* n_copies);

@@ -564,9 +564,14 @@ int32_t mk_kvpool_append_batch(mk_kvpool* p, mk_kvtable** tables, const int32_t*
             }
             *n_copies = (int32_t)cows.size();
         }
-        if (commit) {
+        if (commit == 1) {
             r->mark_all_used();
             r->commit();
+        } else if (commit == 2) {
+            // a forward that failed after it had touched its pages: what it wrote or read stays quarantined until the epoch
+            // completes (cache.rs:1214-1276)
+            r->mark_all_used();
+            r->rollback();
         } else {
             r->rollback();
         }

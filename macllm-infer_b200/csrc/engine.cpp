@@ -8,8 +8,12 @@
 namespace mk {
 
 Engine::Engine(PagedLm& model, const EngineConfig& cfg) : model_(model), cfg_(cfg) {
-    if (cfg.max_active_sequences <= 0 || cfg.scheduler_token_budget <= 0 || cfg.prefill_token_quantum <= 0 || cfg.queue_capacity <= 0)
-        throw std::runtime_error("engine configuration values must be positive");  // EngineConfig validation, engine.rs:350-384
+    // EngineConfig::validate (engine.rs:350-367): the same checks in the same order with the same wording
+    if (cfg.queue_capacity <= 0) throw std::runtime_error("queue capacity must be positive");
+    if (cfg.max_active_sequences <= 0) throw std::runtime_error("maximum active sequences must be positive");
+    if (cfg.scheduler_token_budget <= 0) throw std::runtime_error("scheduler token budget must be positive");
+    if (cfg.prefill_token_quantum <= 0) throw std::runtime_error("prefill token quantum must be positive");
+    if (cfg.prefill_token_quantum > cfg.scheduler_token_budget) throw std::runtime_error("prefill token quantum cannot exceed the scheduler token budget");
     // worker_main creates every reusable session up front (engine.rs:1336-1360)
     for (int i = 0; i < cfg.max_active_sequences; ++i) sessions_.push_back(model_.new_session());
 }
@@ -86,12 +90,18 @@ void Engine::admit(Job job) {  // admit_with_diagnostic_refresh, engine.rs:1654-
     if ((int)active_.size() >= cfg_.max_active_sequences) throw std::runtime_error("scheduler attempted to exceed the active sequence limit");
     const EngineRequest& rq = job.req;
     const LmRuntimeSpec& spec = model_.spec();
-    // prepare_request / validate_request (generation.rs:1308-1337)
-    if (rq.prompt.empty()) return fail_request(job.id, "prompt must contain at least one token");
+    // prepare_request for EngineInput::TokenIds (engine.rs:2976-3021): empty prompt, vocabulary, context - in that order,
+    // with the reference's wording (the context message leads with the phrase clients recognise an overflow by)
+    if (rq.prompt.empty()) return fail_request(job.id, "raw token prompt must not be empty");
+    for (size_t i = 0; i < rq.prompt.size(); ++i)
+        if ((int64_t)rq.prompt[i] >= spec.vocab)
+            return fail_request(job.id, "raw prompt token " + std::to_string(rq.prompt[i]) + " at index " + std::to_string(i) +
+                                            " exceeds model vocabulary " + std::to_string(spec.vocab));
     int64_t required = (int64_t)rq.prompt.size() + std::max(rq.max_new_tokens - 1, 0);
-    if (required > spec.max_context) return fail_request(job.id, "prompt plus requested output exceeds model context limit");
-    for (uint32_t t : rq.prompt)
-        if ((int64_t)t >= spec.vocab) return fail_request(job.id, "input contains a token ID outside the model vocabulary");
+    if (required > spec.max_context)
+        return fail_request(job.id, "This model's maximum context length is " + std::to_string(spec.max_context) + " tokens; the prompt (" +
+                                        std::to_string(rq.prompt.size()) + " tokens) plus requested output (" +
+                                        std::to_string(rq.max_new_tokens) + " tokens) exceeds it");
     if (!(rq.temperature >= 0.f) || !(rq.top_p > 0.f && rq.top_p <= 1.f) || !(rq.repetition_penalty > 0.f))
         return fail_request(job.id, "invalid sampling configuration");  // Sampler::new, sampling.rs:43-62
     // kv_capacity_rejection (engine.rs:2839-2863)

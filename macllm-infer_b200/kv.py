@@ -41,6 +41,14 @@ class KvPool:
                                                      copies.ctypes.data, C.byref(nc)))
         return [tuple(int(x) for x in copies[3 * i:3 * i + 3]) for i in range(nc.value)]
 
+    def append_touch_rollback(self, tables, n_tokens) -> int:
+        """reserve_batch, mark every page of the reservation as touched by the device, roll back: what a forward that
+        failed midway leaves behind.  Returns the epoch the reservation had taken."""
+        arr = self._tables(tables)
+        n = np.ascontiguousarray(n_tokens, dtype=np.int32)
+        capi.check(capi.lib().mk_kvpool_append_batch(self._h, arr, n.ctypes.data, len(tables), 2, None, None))
+        return self.submitted_epoch()
+
     def page_table(self, tables, n_tokens):
         """The compact page table a reservation of this batch would expose (then rolls it back)."""
         arr = self._tables(tables)

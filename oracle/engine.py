@@ -141,6 +141,13 @@ class Result:
 class OracleEngine:
     def __init__(self, model: OracleModel, max_active_sequences=2, scheduler_token_budget=256, prefill_token_quantum=128,
                  queue_capacity=8, record_logits=False, sampler=None):
+        # EngineConfig::validate, engine.rs:350-367
+        for value, what in ((queue_capacity, "queue capacity"), (max_active_sequences, "maximum active sequences"),
+                            (scheduler_token_budget, "scheduler token budget"), (prefill_token_quantum, "prefill token quantum")):
+            if value <= 0:
+                raise ValueError(f"{what} must be positive")
+        if prefill_token_quantum > scheduler_token_budget:
+            raise ValueError("prefill token quantum cannot exceed the scheduler token budget")
         self.m = model
         self.max_active, self.budget, self.quantum, self.queue_capacity = (max_active_sequences, scheduler_token_budget,
                                                                             prefill_token_quantum, queue_capacity)
@@ -179,12 +186,15 @@ class OracleEngine:
         self.results[rid].state, self.results[rid].message = "failed", msg
 
     def _admit(self, rid, r: Req):  # engine.rs:1654-1808
+        # prepare_request for token-id input, engine.rs:2976-3021
         if not r.prompt:
-            return self._fail(rid, "prompt must contain at least one token")
+            return self._fail(rid, "raw token prompt must not be empty")
+        for i, t in enumerate(r.prompt):
+            if t >= self.m.vocab:
+                return self._fail(rid, f"raw prompt token {t} at index {i} exceeds model vocabulary {self.m.vocab}")
         if len(r.prompt) + max(r.max_new_tokens - 1, 0) > self.m.max_context:
-            return self._fail(rid, "prompt plus requested output exceeds model context limit")
-        if any(t >= self.m.vocab for t in r.prompt):
-            return self._fail(rid, "input contains a token ID outside the model vocabulary")
+            return self._fail(rid, f"This model's maximum context length is {self.m.max_context} tokens; the prompt ({len(r.prompt)} tokens) "
+                                   f"plus requested output ({r.max_new_tokens} tokens) exceeds it")
         max_cached = 0 if r.max_new_tokens == 0 else len(r.prompt) + r.max_new_tokens - 1  # engine.rs:2839-2863
         if max_cached > self.m.pool.max_blocks * self.m.pool.block_tokens:
             return self._fail(rid, "request exceeds the configured shared KV capacity")

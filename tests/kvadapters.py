@@ -85,6 +85,9 @@ class ProductPool:
         except self.capi.KvExhausted:
             return None
 
+    def append_touch_rollback(self, tables, ns):
+        return self.p.append_touch_rollback([t.t for t in tables], list(ns))
+
     def page_table(self, tables, ns):
         return self.p.page_table([t.t for t in tables], list(ns))
 

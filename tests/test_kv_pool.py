@@ -170,3 +170,95 @@ def test_randomised_differential_oracle_vs_product(mk):
         for i in range(2):
             for t in tables[i]:
                 t.free()
+
+
+# ---- further known answers of the reference's pool tests (cache.rs; pool(layers, heads, dim, block_tokens, slab_blocks,
+# max_blocks) there = Pool(block_tokens, slab_blocks, max_blocks) here)
+
+def test_partial_tail_cow_rollback_quarantines_only_the_replacement(Pool):
+    """cache.rs:4750-4799: a fork that shares a partial tail reserves a replacement page, the forward touches it and
+    fails: source and fork keep the shared page, only the replacement waits for its epoch."""
+    pool = Pool(4, 2, 2)
+    source = pool.new_table()
+    pool.append([source], [4])
+    pool.complete(pool.submitted())
+    source_id = source.blocks()[0]
+    fork = source.fork_prefix(2)
+    failed = pool.append_touch_rollback([fork], [1])
+    assert source.blocks() == [source_id] and fork.blocks() == [source_id]
+    assert len(source) == 4 and len(fork) == 2
+    assert sub(pool.stats(), "live_blocks", "live_references", "shared_blocks", "retired_blocks", "free_blocks") == (1, 2, 1, 1, 0)
+    pool.complete(failed)
+    assert sub(pool.stats(), "live_blocks", "free_blocks", "retired_blocks") == (1, 1, 0)
+
+
+def test_second_lane_exhaustion_is_atomic(Pool):
+    """cache.rs:5130-5155: two lanes that together need three blocks of a two-block pool: nothing is taken."""
+    pool = Pool(2, 1, 2)
+    first, second = pool.new_table(), pool.new_table()
+    before = pool.stats()
+    assert pool.append([first, second], [2, 3]) is None
+    assert pool.stats() == before
+    assert len(first) == 0 and first.blocks() == [] and len(second) == 0 and second.blocks() == []
+
+
+def test_exhaustion_does_not_publish_an_epoch(Pool):
+    """cache.rs:5334-5355."""
+    pool = Pool(2, 1, 1)
+    owner, waiter = pool.new_table(), pool.new_table()
+    pool.append([owner], [1])
+    before = pool.stats()
+    assert before["submitted_epoch"] == pool.submitted() == 1
+    assert pool.append([waiter], [1]) is None
+    assert pool.stats() == before and len(waiter) == 0 and waiter.blocks() == []
+
+
+def test_two_lanes_commit_in_one_epoch(Pool):
+    """cache.rs:4832-4896: one reservation, one epoch, both tables advance."""
+    pool = Pool(2, 2, 4)
+    first, second = pool.new_table(), pool.new_table()
+    assert pool.append([first, second], [3, 1]) == []
+    assert pool.submitted() == 1 and len(first) == 3 and len(second) == 1
+    assert len(first.blocks()) == 2 and len(second.blocks()) == 1
+    assert sub(pool.stats(), "live_blocks", "live_references", "reserved_blocks") == (3, 3, 0)
+
+
+def test_partial_tail_rollback_stays_private_and_retry_reuses_the_page(Pool):
+    """cache.rs:5226-5296: growth inside the table's own partial page needs no new block; a failed attempt leaves the table
+    as it was, retires nothing, and still publishes its epoch; the retry lands on the same page."""
+    pool = Pool(4, 1, 1)
+    table = pool.new_table()
+    pool.append([table], [2])
+    pool.complete(pool.submitted())
+    page = table.blocks()
+    failed = pool.append_touch_rollback([table], [1])
+    assert len(table) == 2 and table.blocks() == page
+    s = pool.stats()
+    assert sub(s, "live_blocks", "retired_blocks") == (1, 0) and s["submitted_epoch"] == failed
+    assert pool.append([table], [1]) == []
+    assert len(table) == 3 and table.blocks() == page
+
+
+def test_touched_history_is_quarantined_when_the_table_is_cleared_after_a_failed_forward(Pool):
+    """cache.rs:5045-5070: the failed forward read the table's history; clearing the table afterwards may not hand those
+    pages out before the failed epoch completes."""
+    pool = Pool(2, 2, 2)
+    table = pool.new_table()
+    pool.append([table], [3])
+    pool.complete(pool.submitted())
+    failed = pool.append_touch_rollback([table], [1])
+    table.clear()
+    assert sub(pool.stats(), "free_blocks", "live_blocks", "retired_blocks") == (0, 0, 2)
+    pool.complete(failed)
+    assert pool.stats()["free_blocks"] == 2
+
+
+def test_a_table_twice_in_one_batch_is_refused_without_pool_mutation(Pool):
+    """cache.rs:5186-5200."""
+    pool = Pool(2, 1, 2)
+    table = pool.new_table()
+    before = pool.stats()
+    with pytest.raises(Exception):
+        pool.append([table, table], [1, 1])
+    assert pool.stats() == before and len(table) == 0
+    assert pool.append([table], [1]) == []          # the table is not left locked

@@ -157,3 +157,37 @@ def test_randomised_differential(mk):
             else:
                 assert a.evict() == b.evict(), (seed, step)
             assert a.stats() == b.stats(), (seed, step)
+
+
+def test_two_snapshots_with_different_first_blocks_are_told_apart(Cache):
+    """prefix_cache.rs:824-846 (there with every block digest forced to collide; here the digests differ, the answers are
+    the same): the aligned common prefix of each prompt is found under its own snapshot, a third prompt matches neither."""
+    c = Cache(4, 20)
+    c.insert([1, 2, 3, 4, 5, 6, 7, 8, 10], 1, 1)
+    c.insert([9, 8, 7, 6, 5, 4, 3, 2, 10], 2, 1)
+    assert c.lookup([1, 2, 3, 4, 5, 6, 7, 8, 99]) == (8, 1)
+    assert c.lookup([9, 8, 7, 6, 5, 4, 3, 2, 99]) == (8, 2)
+    assert c.lookup([4, 4, 4, 4, 4, 4, 4, 4, 0]) is None
+
+
+def test_refused_insertions_leave_the_cache_empty(Cache):
+    """prefix_cache.rs:686-702: an empty prefix and a cost above the budget are refused."""
+    c = Cache(4, 3)
+    assert c.insert([], 0, 0) is None
+    assert c.insert([1], 0, 4) is None
+    s = c.stats()
+    assert (s["entries"], s["cached_blocks"], s["evictions"]) == (0, 0, 0)
+
+
+def test_endpoint_digest_is_independent_of_how_the_prefix_is_cut(pkv):
+    """prefix_cache.rs:1001-1008: the digest of the first n tokens is the chain of the full blocks and one partial block,
+    whichever way the prompt was walked; the product's chained block digests are that chain's full-block links."""
+    from oracle import kv
+    tokens = [10, 20, 30, 40, 50, 60, 70]
+    full = kv.full_block_digests(tokens, 4)
+    assert pkv.block_digests(4, tokens) == full
+    for n in range(1, len(tokens) + 1):
+        whole, rest = divmod(n, 4)
+        chained = (b"\0" * 32 if whole == 0 else full[whole - 1]) if rest else None
+        want = full[whole - 1] if rest == 0 else kv.hash_block(chained, 4, whole, tokens[4 * whole:n])
+        assert kv.endpoint_digest(tokens, n, 4) == want, n

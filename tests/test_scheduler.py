@@ -123,7 +123,7 @@ def test_requests_that_can_never_fit_are_rejected_at_admission(eng):
     e.run()
     assert [e.result(i)["state"] for i in ids] == ["failed", "failed", "failed", "failed", "done"]
     assert "KV capacity" in e.result(ids[0])["message"]
-    assert "context limit" in e.result(ids[1])["message"]
+    assert "maximum context length is 64 tokens" in e.result(ids[1])["message"]
 
 
 def test_forward_failure_rolls_back_every_lane(eng):
@@ -299,3 +299,48 @@ def test_second_forward_before_the_read_is_refused(eng):
     assert st == 0
     model.synchronize()
     assert capi.lib().mk_read_output(model._h, None, toks) != 0   # nothing left to read
+
+
+def test_scheduler_limits_must_be_positive_and_internally_consistent(eng):
+    """engine.rs:4376-4395 with EngineConfig::validate's wording (engine.rs:350-367)."""
+    from oracle import engine as oe
+    capi = importlib.import_module("macllm_infer_b200._capi")
+    cases = [(dict(max_active_sequences=0), "maximum active sequences must be positive"),
+             (dict(scheduler_token_budget=0), "scheduler token budget must be positive"),
+             (dict(prefill_token_quantum=0), "prefill token quantum must be positive"),
+             (dict(queue_capacity=0), "queue capacity must be positive"),
+             (dict(scheduler_token_budget=4, prefill_token_quantum=5), "prefill token quantum cannot exceed the scheduler token budget")]
+    model = eng.Model.fake(vocab=8)
+    om = oe.OracleModel(8, 4096, 16, 8, 4096, 0)
+    eng.Engine(model).close()                      # the defaults are valid
+    oe.OracleEngine(om)
+    for kw, message in cases:
+        with pytest.raises(capi.MkError, match=message):
+            eng.Engine(model, **kw)
+        with pytest.raises(ValueError, match=message):
+            oe.OracleEngine(om, **kw)
+
+
+def test_token_prompts_are_validated_with_the_reference_wording(eng):
+    """engine.rs:4341-4364 (empty and out-of-vocabulary token prompts) and engine.rs:4315-4338 (context overflow leads
+    with the phrase clients recognise): each fails only its own request, as an invalid request, before any model work."""
+    (pm, pe), (om, oe_) = both(eng, dict(vocab=6, max_context=32, kv_capacity_tokens=256),
+                               dict(max_active_sequences=2, scheduler_token_budget=8, prefill_token_quantum=4))
+    prompts = [[], [1, 6], [1, 2, 3], [1] * 30, [1] * 29, [2, 3]]
+    max_new = [4, 4, 33, 4, 4, 2]
+    ids = submit_both(eng, pe, oe_, prompts, max_new)
+    pe.run()
+    oe_.run()
+    want = {0: "raw token prompt must not be empty",
+            1: "raw prompt token 6 at index 1 exceeds model vocabulary 6",
+            2: "This model's maximum context length is 32 tokens; the prompt (3 tokens) plus requested output (33 tokens) exceeds it",
+            3: "This model's maximum context length is 32 tokens; the prompt (30 tokens) plus requested output (4 tokens) exceeds it"}
+    for rid in ids:
+        rp, ro = pe.result(rid), oe_.results[rid]
+        if rid in want:
+            assert rp["state"] == ro.state == "failed" and rp["kind"] == "invalid_request"
+            assert rp["message"] == ro.message == want[rid]
+        else:   # 29 + 4 - 1 = 32 tokens of context is exactly the limit
+            assert rp["state"] == ro.state == "done" and list(rp["tokens"]) == ro.tokens
+    assert all(lane[0] in (4, 5) for tick in pe.trace() for lane in tick)     # the refused requests never reached the model
+    assert pe.trace() == [[tuple(l) for l in t] for t in oe_.trace]
