@@ -344,3 +344,16 @@ def test_token_prompts_are_validated_with_the_reference_wording(eng):
             assert rp["state"] == ro.state == "done" and list(rp["tokens"]) == ro.tokens
     assert all(lane[0] in (4, 5) for tick in pe.trace() for lane in tick)     # the refused requests never reached the model
     assert pe.trace() == [[tuple(l) for l in t] for t in oe_.trace]
+
+
+def test_scheduler_fills_available_slots_before_the_first_iteration(eng):
+    """engine.rs:4811-4842: three queued one-token requests, three slots, budget 3, quantum 1 - the first tick already packs
+    all three in submission order, with one completion barrier and no cleanup drain."""
+    (pm, pe), (om, oe_) = both(eng, dict(vocab=32), dict(max_active_sequences=3, scheduler_token_budget=3, prefill_token_quantum=1,
+                                                          queue_capacity=3))
+    submit_both(eng, pe, oe_, [[1], [2], [3]], [1, 1, 1])
+    assert pe.step() == 3
+    oe_.step()
+    assert pe.trace() == [[(0, 0, 1), (1, 0, 1), (2, 0, 1)]] == [[tuple(l) for l in t] for t in oe_.trace]
+    s = pe.stats()
+    assert s["ticks"] == 1 and s["cleanup_drains"] == 0 and s["completed_requests"] == 3
