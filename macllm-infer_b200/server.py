@@ -332,69 +332,84 @@ class CompletionServer:
         self._status = "ready"
         self._ready.set()
         active: dict[int, _Job] = {}
-        while not self._stop.is_set():
-            # admit what the handlers queued; block only when there is nothing to run
-            try:
-                item = self._inbox.get(timeout=self._idle_wait_s) if not active else self._inbox.get_nowait()
-            except queue.Empty:
-                item = False
-            while item:
-                job, reply = item
+        try:
+            while not self._stop.is_set():
+                # admit what the handlers queued; block only when there is nothing to run
                 try:
-                    s = job.settings
-                    (rid,) = engine.submit([_engine.Request(job.tokens, s["n_predict"], ignore_stop_tokens=True, temperature=s["temperature"],
-                                                            top_k=s["top_k"], top_p=s["top_p"], seed=s["seed"],
-                                                            publish_prompt_prefix=job.publish_prefix)])
-                    job.request_id = rid
-                    active[rid] = job
-                    reply.put(None)
-                except Exception as e:
-                    msg = str(e)
-                    if "queue is full" in msg:
-                        reply.put(ApiError.server_error("inference queue is full", 429))
-                    else:
-                        reply.put(ApiError.server_error(msg, 503))
-                try:
-                    item = self._inbox.get_nowait()
+                    item = self._inbox.get(timeout=self._idle_wait_s) if not active else self._inbox.get_nowait()
                 except queue.Empty:
                     item = False
-            if item is None:
-                break
-            if not active:
-                continue
-            try:
-                engine.step()
-            except Exception:
-                pass  # a failure that escapes a tick poisons the engine; the requests report it below
-            self._status = engine.status()
-            now = time.perf_counter()
-            for rid in list(active):
-                job = active[rid]
-                n, state, cached = engine.progress(rid)
-                if n > job.seen:
-                    toks = engine.result(rid)["tokens"]
-                    if job.t_first is None:
-                        job.t_first = now
-                    for i in range(job.seen, n):
-                        text = self._tokenizer.decode([int(toks[i])]) if self._tokenizer is not None else ""
-                        job.events.put(("token", int(toks[i]), i + 1, text))
-                    job.seen = n
-                if state == "done":
-                    first = job.t_first if job.t_first is not None else now
-                    job.events.put(("finished", dict(generated_tokens=n, prompt_tokens=len(job.tokens), cached_prompt_tokens=int(cached),
-                                                     stop_type="limit" if n == job.settings["n_predict"] else "stop",
-                                                     prefill_ms=(first - job.t_submit) * 1e3, ttft_ms=(first - job.t_submit) * 1e3,
-                                                     total_ms=(now - job.t_submit) * 1e3)))
-                    del active[rid]
-                elif state == "failed":
-                    r = engine.result(rid)
-                    job.events.put(("failed", r["kind"], r["message"]))
-                    del active[rid]
-            if self._status not in ("poisoned",) and not active:
-                self._status = "ready"
+                while item:
+                    job, reply = item
+                    try:
+                        s = job.settings
+                        (rid,) = engine.submit([_engine.Request(job.tokens, s["n_predict"], ignore_stop_tokens=True, temperature=s["temperature"],
+                                                                top_k=s["top_k"], top_p=s["top_p"], seed=s["seed"],
+                                                                publish_prompt_prefix=job.publish_prefix)])
+                        job.request_id = rid
+                        active[rid] = job
+                        reply.put(None)
+                    except Exception as e:
+                        msg = str(e)
+                        if "queue is full" in msg:
+                            reply.put(ApiError.server_error("inference queue is full", 429))
+                        else:
+                            reply.put(ApiError.server_error(msg, 503))
+                    try:
+                        item = self._inbox.get_nowait()
+                    except queue.Empty:
+                        item = False
+                if item is None:
+                    break
+                if not active:
+                    continue
+                try:
+                    engine.step()
+                except Exception:
+                    pass  # a failure that escapes a tick poisons the engine; the requests report it below
+                self._status = engine.status()
+                now = time.perf_counter()
+                for rid in list(active):
+                    job = active[rid]
+                    n, state, cached = engine.progress(rid)
+                    if n > job.seen:
+                        toks = engine.result(rid)["tokens"]
+                        if job.t_first is None:
+                            job.t_first = now
+                        for i in range(job.seen, n):
+                            text = self._tokenizer.decode([int(toks[i])]) if self._tokenizer is not None else ""
+                            job.events.put(("token", int(toks[i]), i + 1, text))
+                        job.seen = n
+                    if state == "done":
+                        first = job.t_first if job.t_first is not None else now
+                        job.events.put(("finished", dict(generated_tokens=n, prompt_tokens=len(job.tokens), cached_prompt_tokens=int(cached),
+                                                         stop_type="limit" if n == job.settings["n_predict"] else "stop",
+                                                         prefill_ms=(first - job.t_submit) * 1e3, ttft_ms=(first - job.t_submit) * 1e3,
+                                                         total_ms=(now - job.t_submit) * 1e3)))
+                        del active[rid]
+                    elif state == "failed":
+                        r = engine.result(rid)
+                        job.events.put(("failed", r["kind"], r["message"]))
+                        del active[rid]
+                if self._status not in ("poisoned",) and not active:
+                    self._status = "ready"
+        except Exception as e:  # a scheduler panic (src/engine.rs:1600-1647): fatal for everything in flight, the worker is gone
+            self._status = "poisoned"
+            for job in active.values():
+                job.events.put(("failed", "fatal", f"inference worker failed: {e}"))
+            active.clear()
+            while not self._stop.is_set():   # keep refusing what handlers had already queued
+                try:
+                    item = self._inbox.get(timeout=0.05)
+                except queue.Empty:
+                    continue
+                if item is None:
+                    break
+                item[1].put(ApiError.server_error("inference worker is unavailable (Poisoned)", 503))
         for job in active.values():
             job.events.put(("failed", "internal", "inference worker stopped before completing the request"))
-        self._status = "stopped"
+        if self._status != "poisoned":
+            self._status = "stopped"
         try:
             engine.close()
         except Exception:

@@ -243,3 +243,25 @@ def test_the_benchmark_step_through_the_endpoint_counts_every_token(mk):
     want = sum(len(p) for p in reqs[0]) + int(sum(reqs[1]))
     assert out["requests"] == 10 and out["clients"] == 3
     assert abs(out["value"] * out["wall_s"] - want) <= 0.02 * want          # wall_s is rounded to a millisecond
+
+
+def test_a_worker_exception_fails_everything_in_flight_and_the_server_keeps_answering(mk, srv_mod):
+    """A panic of the worker itself (src/engine.rs:1600-1647), here a tokenizer that raises while a fragment is decoded:
+    the request in flight ends with a server error naming the cause, later requests get 503, `/healthz` turns red."""
+    class Broken:
+        def encode(self, text):
+            return [1, 2, 3]
+
+        def decode(self, ids):
+            raise RuntimeError("detokeniser exploded")
+    s = start(mk, srv_mod, tokenizer=Broken())
+    try:
+        st, _, b = call(s, "POST", "/completion", body(srv_mod, prompt="abc"))
+        err = json.loads(b)["error"]
+        assert st == 500 and err["type"] == "server_error" and "inference worker failed: detokeniser exploded" in err["message"]
+        st, _, b = call(s, "POST", "/completion", body(srv_mod))
+        assert st == 503 and "unavailable (Poisoned)" in json.loads(b)["error"]["message"]
+        st, _, b = call(s, "GET", "/healthz")
+        assert st == 503 and json.loads(b)["worker"] == "poisoned"
+    finally:
+        s.stop()
