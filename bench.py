@@ -457,9 +457,10 @@ def cpu_baseline(w, path, budget_s: float, threads: int) -> dict:
 
 
 def q4k_gemv_block(hbm_gbs: float) -> dict:
-    """The metric's second half: Q4_K matrix-vector products of the decode path (integer block dots, 1 and 8 activation
-    rows) on the gate/up shape of configuration 2 and the feed-forward shape of configuration 3: achieved GB/s on the
-    bytes of the matrix, operands resident, L2 flushed before every launch, CUDA events around the launch."""
+    """The metric's second half: Q4_K matrix-vector products of the decode path at 1 and 8 activation rows on the gate/up
+    shape of configuration 2 and the feed-forward shape of configuration 3, on the integer GEMV and on the streamed
+    tensor-core kernel: achieved GB/s on the bytes of the matrix, operands resident, L2 flushed before every launch, CUDA
+    events around the launch."""
     ops = importlib.import_module("macllm_infer_b200.ops")
     capi = importlib.import_module("macllm_infer_b200._capi")
     rng = np.random.default_rng(0)
@@ -471,6 +472,10 @@ def q4k_gemv_block(hbm_gbs: float) -> dict:
             x = rng.standard_normal((T, cols)).astype(np.float32)
             ms = ops.qmatmul_time(capi.TYPE_Q4_K, wq, rows, cols, x, capi.PATH_GEMV, 10)
             out[f"{rows}x{cols}_T{T}"] = dict(us=round(ms * 1e3, 1), gbs=round(nbytes / ms / 1e6, 1), frac=round(nbytes / ms / 1e6 / hbm_gbs, 4))
+            # the same product on the streamed tensor-core kernel, which is what a tick of 1..64 rows runs in automatic mode
+            ms = ops.qmatmul_time(capi.TYPE_Q4_K, wq, rows, cols, x, capi.PATH_STREAM, 10)
+            out[f"{rows}x{cols}_T{T}_streamed"] = dict(us=round(ms * 1e3, 1), gbs=round(nbytes / ms / 1e6, 1),
+                                                      frac=round(nbytes / ms / 1e6 / hbm_gbs, 4))
     return out
 
 
