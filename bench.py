@@ -198,6 +198,17 @@ def aggregate(dist, tokens: float, seconds: float) -> tuple[float, float, float]
     return total, slowest, total / max(slowest, 1e-12)
 
 
+def make_lockstep(dist):
+    """The per-tick agreement of an expert-parallel group: (sum of the ranks' outstanding requests, did any rank fail)."""
+    import torch
+
+    def lockstep(n, failed=False):
+        t = torch.tensor([float(n), 1.0 if failed else 0.0], dtype=torch.float64, device="cuda" if _on_gpu(dist) else "cpu")
+        dist.all_reduce(t)
+        return int(round(float(t[0].item()))), float(t[1].item()) > 0.0
+    return lockstep
+
+
 def new_engine(eng_mod, model, w, active: int, n_requests: int):
     return eng_mod.Engine(model, max_active_sequences=active, scheduler_token_budget=w.budget, prefill_token_quantum=w.quantum,
                           queue_capacity=n_requests + 8)
@@ -210,8 +221,10 @@ def drive(eng_mod, model, eng, w, reqs, lockstep=None):
     - Poisson arrivals (configuration 5): a request is submitted once the step's clock has passed its arrival time; the
       clock is the wall time since the step began, and it jumps to the next arrival whenever the engine would idle, so
       that a step measures service, not waiting.
-    lockstep (expert parallelism with data-parallel lanes): a function that sums a count over all ranks.  Every rank then
-    ticks until no rank has work left, and a rank with no lane to run takes the tick idle (it serves the others' rows)."""
+    lockstep (expert parallelism with data-parallel lanes): `lockstep(n, failed)` returns (sum of n over all ranks, whether
+    any rank reported a failure).  Every rank then ticks until no rank has work left, and a rank with no lane to run takes
+    the tick idle (it serves the others' rows).  An exception on one rank is held until the next sum, where every rank
+    learns of it and all leave the loop in the same iteration - no rank is left waiting in a collective."""
     prompts, new, arrivals = reqs
     mk = lambda i: eng_mod.Request(prompts[i], new[i])
     ids = []
@@ -222,33 +235,55 @@ def drive(eng_mod, model, eng, w, reqs, lockstep=None):
         waves = [(0, 1, False), (1, len(prompts), False)] if w.shared_prefix else [(0, len(prompts), True)]
         waves = [x for x in waves if x[1] > x[0]]
     t0, skipped, nxt = time.perf_counter(), 0.0, 0
+    failure = None
     while True:
         outstanding = (len(prompts) - nxt) + eng.pending()
-        if (outstanding if lockstep is None else lockstep(outstanding)) <= 0:
-            break
-        if waves is None:
-            now = time.perf_counter() - t0 + skipped
-            if eng.pending() == 0 and nxt < len(prompts) and arrivals[nxt] > now:
-                skipped += arrivals[nxt] - now
-                now = arrivals[nxt]
-            wave = []
-            while nxt < len(prompts) and arrivals[nxt] <= now:
-                wave.append(mk(nxt))
-                nxt += 1
-            if wave:
-                ids += eng.submit(wave)
-        elif eng.pending() == 0 and waves:
-            lo, hi, atomic = waves.pop(0)
-            ids += eng.submit([mk(i) for i in range(lo, hi)], atomic_batch=atomic)
-            nxt = hi
-        lanes = eng.step()
-        if lanes == 0 and lockstep is not None:
-            t_idle = time.perf_counter()
-            model.ep_idle_tick()
-            model.synchronize()
-            drive.idle_s += time.perf_counter() - t_idle
+        if lockstep is None:
+            if outstanding <= 0:
+                break
+        else:
+            total, any_failed = lockstep(outstanding, failure is not None)
+            if any_failed:
+                raise RuntimeError(failure or "another rank of the expert-parallel group failed")
+            if total <= 0:
+                break
+        try:
+            lanes, skipped, nxt = _tick(eng_mod, model, eng, reqs, mk, waves, ids, lockstep is not None, t0, skipped, nxt)
+        except Exception as e:
+            if lockstep is None:
+                raise
+            failure = f"{type(e).__name__}: {e}"
+            continue
         yield lanes
     drive.last_ids = ids
+
+
+def _tick(eng_mod, model, eng, reqs, mk, waves, ids, in_lockstep, t0, skipped, nxt):
+    """One iteration of drive(): submit what is due (extending `ids`), run one scheduler tick or idle through it.
+    Returns (lanes, skipped, nxt)."""
+    prompts, _, arrivals = reqs
+    if waves is None:
+        now = time.perf_counter() - t0 + skipped
+        if eng.pending() == 0 and nxt < len(prompts) and arrivals[nxt] > now:
+            skipped += arrivals[nxt] - now
+            now = arrivals[nxt]
+        wave = []
+        while nxt < len(prompts) and arrivals[nxt] <= now:
+            wave.append(mk(nxt))
+            nxt += 1
+        if wave:
+            ids.extend(eng.submit(wave))
+    elif eng.pending() == 0 and waves:
+        lo, hi, atomic = waves.pop(0)
+        ids.extend(eng.submit([mk(i) for i in range(lo, hi)], atomic_batch=atomic))
+        nxt = hi
+    lanes = eng.step()
+    if lanes == 0 and in_lockstep:
+        t_idle = time.perf_counter()
+        model.ep_idle_tick()
+        model.synchronize()
+        drive.idle_s += time.perf_counter() - t_idle
+    return lanes, skipped, nxt
 
 
 def run_step(eng_mod, model, w, reqs, active: int, lockstep=None):
@@ -259,22 +294,36 @@ def run_step(eng_mod, model, w, reqs, active: int, lockstep=None):
     eng = new_engine(eng_mod, model, w, active, len(prompts))
     model.synchronize()
     t0 = time.perf_counter()
-    for _ in drive(eng_mod, model, eng, w, reqs, lockstep):
-        pass
-    model.synchronize()
+    err = None
+    try:
+        for _ in drive(eng_mod, model, eng, w, reqs, lockstep):
+            pass
+        model.synchronize()
+    except Exception as e:
+        if lockstep is None:
+            raise
+        err = str(e)
     wall = time.perf_counter() - t0
     st = eng.stats()
     st["device_ms"] += drive.idle_s * 1e3
     toks = sum(len(p) for p in prompts)
     gen = 0
-    for i in drive.last_ids:
+    for i in (drive.last_ids if err is None else []):
         r = eng.result(i)
         if r["state"] != "done":
-            raise RuntimeError(f"request {i} ended in state {r['state']}: {r['message']}")
+            err = f"request {i} ended in state {r['state']}: {r['message']}"
+            break
         gen += len(r["tokens"])
         toks -= r["cached_tokens"]          # prompt tokens served from the prefix cache were not computed
-    diag = model.prefix_diagnostics() if w.prefix_capacity_tokens else None
+    diag = model.prefix_diagnostics() if w.prefix_capacity_tokens and err is None else None
     eng.close()
+    if lockstep is not None:
+        # every rank of the group learns whether the step failed anywhere, so that all of them raise (or none does)
+        _, any_failed = lockstep(0, err is not None)
+        if any_failed:
+            raise RuntimeError(err or "the step failed on another rank of the expert-parallel group")
+    elif err is not None:
+        raise RuntimeError(err)
     return toks + gen, wall, st, diag
 
 
@@ -479,6 +528,74 @@ def q4k_gemv_block(hbm_gbs: float) -> dict:
     return out
 
 
+def plan_arena(w, prompts, new, kv_per_token: int, kv_budget_gb: float):
+    """(active sequences, KV arena tokens): the arena holds the active set at its longest; when that exceeds the budget the
+    active set shrinks."""
+    active = min(w.max_active(), len(prompts))
+
+    def arena_tokens(a):
+        longest = sorted(((len(p) + k + 31) // 16 * 16 + 16 for p, k in zip(prompts, new)), reverse=True)
+        return sum(longest[:a]) + w.prefix_capacity_tokens
+    while active > 1 and arena_tokens(active) * kv_per_token > kv_budget_gb * 1e9:
+        active = active * 3 // 4
+    return active, arena_tokens(active)
+
+
+EP_SLICE_WORKLOAD = "qwen3-30b-a3b-poisson"
+EP_SLICE_REQUESTS = 64
+
+
+def ep_slice(eng_mod, wl, seed, rank: int, local: int, world: int, dist, kv_budget_gb: float) -> dict:
+    """The sparse-MoE workload's curve beside the headline: the first EP_SLICE_REQUESTS requests per rank of the Poisson
+    workload on the full 48-layer, 128-expert shape, one warm-up step and one timed step.  One GPU serves them with every
+    expert resident; N > 1 runs expert parallelism with data-parallel lanes over the same N ranks (each rank its own
+    requests, the routed rows exchanged per MoE layer).  Every phase ends with an agreement over all ranks, so a failure on
+    one rank makes all of them report it instead of leaving the others in a collective."""
+    w = wl.WORKLOADS[EP_SLICE_WORKLOAD]
+    spec = seed.CONFIGS[w.config]
+    if spec.experts % world != 0:
+        return dict(skipped=f"{spec.experts} experts do not split over {world} ranks")
+    agree = make_lockstep(dist) if dist is not None else (lambda n, failed=False: (n, failed))
+
+    def phase(fn):
+        err, out = None, None
+        try:
+            out = fn()
+        except Exception as e:
+            err = f"{type(e).__name__}: {e}"
+        if agree(0, err is not None)[1]:
+            raise RuntimeError(err or "another rank failed")
+        return out
+    phase(lambda: ensure_checkpoint(w.config) if rank == 0 else None)
+    path = checkpoint_path(w.config)
+    reqs = wl.make_requests(w, spec.vocab, rank, EP_SLICE_REQUESTS)
+    prompts, new, _ = reqs
+    kv_per_token = 2 * spec.layers * spec.kv_heads * spec.head_dim * 2
+    active, cap = plan_arena(w, prompts, new, kv_per_token, kv_budget_gb)
+    ep_kw = dict(ep_rank=rank, ep_size=world, ep_mode=1) if world > 1 else {}
+    model = phase(lambda: eng_mod.Model.load_gguf(path, device=local, kv_capacity_tokens=cap, kv_dtype="f16", max_batch_tokens=w.budget,
+                                                  max_batch_lanes=active, **ep_kw))
+    try:
+        lockstep = None
+        if world > 1:
+            box = [eng_mod.Model.ep_unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(box, src=0)
+            phase(lambda: model.ep_init(box[0]))
+            lockstep = agree
+        run_step(eng_mod, model, w, reqs, active, lockstep)            # warm-up
+        barrier(dist)
+        tokens, wall, st, _ = run_step(eng_mod, model, w, reqs, active, lockstep)
+        tokens_all = all_sum(dist, float(tokens))
+        dev = all_max(dist, st["device_ms"] / 1e3)
+        wall = all_max(dist, wall)
+        return dict(workload=f"{EP_SLICE_WORKLOAD}, first {EP_SLICE_REQUESTS} requests per rank", ranks=world,
+                    parallelism=f"dp{world} lanes x ep{world} experts" if world > 1 else "one GPU, all experts resident",
+                    local_experts=spec.experts // world, value=tokens_all / max(dev, 1e-12), e2e=tokens_all / max(wall, 1e-12), unit=UNIT,
+                    steps=1, warmup=1, ms_per_step=wall * 1e3, ticks_per_step=int(st["ticks"]), scaling="weak")
+    finally:
+        model.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -496,6 +613,9 @@ def main():
                     help="N > 1 and a sparse-MoE workload: expert parallelism with data-parallel lanes (auto = on) instead of replicas")
     ap.add_argument("--http-clients", type=int, default=0,
                     help="also run one step through the /completion endpoint with this many concurrent clients (adds an `http` key)")
+    ap.add_argument("--no-ep-slice", action="store_true",
+                    help="default workload only: skip the slice of the sparse-MoE workload that adds the `ep` key (one GPU: all experts "
+                         "resident; N > 1: expert parallelism over the same ranks)")
     ap.add_argument("--no-profiled-step", action="store_true", help="skip the extra step that times every launch")
     ap.add_argument("--microbench", action="store_true", help="Q4_K matmul GB/s on the decode shapes instead of the workload")
     args = ap.parse_args()
@@ -573,14 +693,7 @@ def main():
 
     reqs = wl.make_requests(w, spec.vocab, rank, args.limit_requests)
     prompts, new, _ = reqs
-    # the KV arena holds the active set at its longest; when that exceeds the budget the active set shrinks
-    active = min(w.max_active(), len(prompts))
-    def arena_tokens(a):
-        longest = sorted(((len(p) + k + 31) // 16 * 16 + 16 for p, k in zip(prompts, new)), reverse=True)
-        return sum(longest[:a]) + w.prefix_capacity_tokens
-    while active > 1 and arena_tokens(active) * kv_per_token > args.kv_budget_gb * 1e9:
-        active = active * 3 // 4
-    cap = arena_tokens(active)
+    active, cap = plan_arena(w, prompts, new, kv_per_token, args.kv_budget_gb)
     config.update(active_sequences=active, kv_arena_gb=round(cap * kv_per_token / 1e9, 2))
     model = eng_mod.Model.load_gguf(path, device=local, kv_capacity_tokens=cap, kv_dtype="f16", prefix_capacity_tokens=w.prefix_capacity_tokens,
                                     max_batch_tokens=w.budget, max_batch_lanes=active, matmul_path=args.matmul_path,
@@ -590,7 +703,7 @@ def main():
         box = [eng_mod.Model.ep_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         model.ep_init(box[0])
-        lockstep = lambda n: int(round(all_sum(dist, float(n))))
+        lockstep = make_lockstep(dist)
     for _ in range(args.warmup):
         run_step(eng_mod, model, w, reqs, active, lockstep)
     sampler = ClockSampler(local)
@@ -674,6 +787,15 @@ def main():
         except Exception as e:  # the baseline is a report, never a reason to lose the measurement
             base = dict(value=None, unit=UNIT, cores=None, kind="port", sample=f"failed: {e}")
 
+    # the sparse-MoE curve beside the headline (every rank takes part; the headline model's memory is released first)
+    ep_block = None
+    if args.workload == DEFAULT_WORKLOAD and not sliced and not args.no_ep_slice and not args.no_profiled_step:
+        model.close()
+        try:
+            ep_block = ep_slice(eng_mod, wl, seed, rank, local, world, dist, args.kv_budget_gb)
+        except Exception as e:  # never a reason to lose the headline measurement
+            ep_block = dict(error=str(e)[:400])
+
     if rank == 0:
         out = dict(metric=METRIC, value=tokens_all / dev_max, unit=UNIT, n_gpus=world, steps=args.steps, warmup=args.warmup,
                    ms_per_step=wall_max * 1e3 / max(args.steps, 1), higher_is_better=True, scaling="weak", vs_baseline=None,
@@ -687,6 +809,8 @@ def main():
             out["prefix_cache"] = diag
         if http is not None:
             out["http"] = http
+        if ep_block is not None:
+            out["ep"] = ep_block
         print(json.dumps(out))
     model.close()
     if dist is not None:

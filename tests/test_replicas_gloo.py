@@ -91,9 +91,10 @@ LOCKSTEP_CHILD = textwrap.dedent("""
 
     model = Counting(eng.Model.fake(vocab=32, max_context=256, kv_capacity_tokens=2048))
     calls = [0]
-    def lockstep(n):
+    agree = bench.make_lockstep(dist)
+    def lockstep(n, failed=False):
         calls[0] += 1
-        return int(round(bench.all_sum(dist, float(n))))
+        return agree(n, failed)
     e = bench.new_engine(eng, model.inner, w, 4, len(reqs[0]))
     lanes = [n for n in bench.drive(eng, model, e, w, reqs, lockstep)]
     done = [e.result(i)["state"] for i in bench.drive.last_ids]
@@ -124,3 +125,56 @@ def test_lock_step_drive_keeps_two_ranks_on_the_same_tick_count():
         assert o["forwards"] + o["idle"] == o["iterations"]          # exactly one forward or one idle tick per iteration
         assert set(o["done"]) == {"done"} and o["generated"] == o["want"]
     assert b["idle"] > 0 and b["forwards"] < a["forwards"] + a["idle"]  # the rank with fewer requests idled through the tail
+
+
+FAILURE_CHILD = textwrap.dedent("""
+    import importlib, json, sys
+    sys.path.insert(0, %r)
+    import bench
+    import __graft_entry__ as entry
+    entry.load_package()
+    eng = importlib.import_module("macllm_infer_b200.engine")
+    rank, local, world, dist = bench.dist_setup(2, backend="gloo")
+    wl = bench.workloads_module()
+    w = wl.Workload("lockstep-failure", "none", 6, 8, 16, 64, 79, prompt=(5, 40))
+    reqs = wl.make_requests(w, 32, rank)
+
+    class Idle:
+        def __init__(self, inner):
+            self.inner = inner
+        def ep_idle_tick(self):
+            pass
+        def __getattr__(self, name):
+            return getattr(self.inner, name)
+
+    inner = eng.Model.fake(vocab=32, max_context=256, kv_capacity_tokens=2048)
+    if rank == 1:
+        inner.inject_failure("forward", 3)      # rank 1's fourth forward fails: its engine poisons, its requests fail
+    outcome = "ok"
+    try:
+        bench.run_step(eng, Idle(inner), w, reqs, 6, bench.make_lockstep(dist))
+    except RuntimeError as e:
+        outcome = str(e)
+    print(json.dumps(dict(rank=rank, outcome=outcome)), flush=True)
+    dist.barrier()          # both ranks are still in step: nobody was left inside a collective
+    dist.destroy_process_group()
+""") % str(ROOT)
+
+
+def test_a_failure_on_one_rank_ends_the_lock_step_on_all_of_them():
+    """One rank's model fails mid-run: that rank's requests end failed, it keeps ticking idle until the group is done, and
+    the agreement at the end of the step makes BOTH ranks raise - the healthy one with a message naming a peer - instead of
+    one of them waiting in a collective for ever."""
+    port = _free_port()
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        procs.append(subprocess.Popen([sys.executable, "-c", FAILURE_CHILD], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    outs = []
+    for p in procs:
+        out, err = p.communicate(timeout=120)
+        assert p.returncode == 0, err[-2000:]
+        outs.append(json.loads(out.strip().splitlines()[-1]))
+    outs.sort(key=lambda o: o["rank"])
+    assert "another rank" in outs[0]["outcome"]
+    assert "ended in state failed" in outs[1]["outcome"] and "inference worker failed" in outs[1]["outcome"]
