@@ -698,6 +698,8 @@ int32_t mk_k_sample(const float* logits, int32_t B, int32_t vocab, const mk_lane
 int32_t mk_k_moe_route(const float* logits, int32_t T, int32_t experts, int32_t k, int32_t* sel_experts, float* sel_weights) {
     return guarded([&] {
         require_device();
+        if (T <= 0 || experts <= 0) throw std::runtime_error("mk_k_moe_route: bad arguments");
+        if (k <= 0 || k > experts) throw std::runtime_error("experts per token " + std::to_string(k) + " must be in 1..=" + std::to_string(experts));  // src/decoder.rs:456-458
         DevBuf dl((size_t)T * experts * 4), de((size_t)T * k * 4), dw((size_t)T * k * 4);
         dl.upload(logits, (size_t)T * experts * 4);
         DevBuf status(4);

@@ -179,8 +179,14 @@ def paged_attention(q, k_pool, v_pool, page_table, page_off, start_pos, lane_len
 
 
 def moe_route(logits: np.ndarray, k: int):
+    """selected_softmax_routes (src/decoder.rs:448-554), with its refusals (:453-483)."""
     logits = _f32(logits)
     T, E = logits.shape
+    if k == 0 or k > E:
+        raise ValueError(f"experts per token {k} must be in 1..={E}")
+    bad = np.flatnonzero(~np.isfinite(logits).all(axis=1))
+    if bad.size:
+        raise ValueError(f"router produced non-finite logits for token row {int(bad[0])}")
     sel = np.empty((T, k), np.int32)
     w = np.empty((T, k), np.float32)
     lib().orc_moe_route(_p(logits), C.c_int64(T), E, k, _p(sel), _p(w))

@@ -187,3 +187,30 @@ def test_ragged_batch_matches_serial_attention_on_the_gpu(ops, softcap):
     want = np.concatenate([dense_gqa(qq, kk, vv, 0, 0.41, softcap) for qq, kk, vv in zip(q, k, v)])
     got = r["out"].reshape(-1, H, d4)
     assert np.abs(got[..., :d] - want).max() <= 2e-6 and np.abs(got[..., d:]).max() == 0.0
+
+
+def test_router_refuses_non_finite_logits_and_bad_counts_on_the_oracle(orc):
+    """selected_softmax_routes_rejects_invalid_or_non_finite_logits (src/decoder.rs:8620-8629)."""
+    with pytest.raises(ValueError, match="non-finite logits for token row 0"):
+        orc.moe_route(np.array([[1.0, np.nan]], np.float32), 1)
+    with pytest.raises(ValueError, match="non-finite logits for token row 1"):
+        orc.moe_route(np.array([[1.0, 2.0], [np.inf, 0.0]], np.float32), 1)
+    for k in (0, 3):
+        with pytest.raises(ValueError, match=r"experts per token \d must be in 1\.\.=2"):
+            orc.moe_route(np.array([[1.0, 2.0]], np.float32), k)
+
+
+@pytest.mark.gpu
+def test_router_refuses_non_finite_logits_and_bad_counts_on_the_gpu(ops, mk):
+    """The same refusals from the device kernel: a row with a NaN records a status that names the row (the choices written
+    for it stay in range, so nothing downstream indexes out of bounds); counts outside 1..=experts are refused before any
+    launch."""
+    import importlib
+    capi = importlib.import_module("macllm_infer_b200._capi")
+    with pytest.raises(capi.MkError, match="non-finite logits for token row 1"):
+        ops.moe_route(np.array([[1.0, 2.0, 3.0, 0.5], [0.0, np.nan, 1.0, 2.0]], np.float32), 2)
+    for k in (0, 5):
+        with pytest.raises(capi.MkError, match=r"experts per token \d must be in 1\.\.=4"):
+            ops.moe_route(np.array([[1.0, 2.0, 3.0, 0.5]], np.float32), k)
+    sel, w = ops.moe_route(np.array([[1.0, 2.0, 3.0, 0.5]], np.float32), 2)    # the device still answers
+    assert sel.tolist() == [[2, 1]]
