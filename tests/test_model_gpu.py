@@ -397,3 +397,40 @@ def test_block_formats_decoded_at_load_match_oracle(pk, tmp_path_factory, matrix
     mixed = matrix_type in (8, 12, 14)
     assert worst <= (0.05 if mixed else 0.025) * scale + 3 * env, (worst, env, scale)
     assert cos >= (min(0.999, 1 - 3 * (1 - env_cos)) if mixed else 0.9995), (cos, env_cos)
+
+
+def test_chunked_execution_matches_one_shot_across_a_block_boundary(pk, tmp_path_factory):
+    """paged_full_cache_matches_chunked_execution_at_15_16_17_tokens (src/decoder.rs:8970-9013): seventeen tokens in one
+    pass against chunks of 15, 1 and 1 - the second chunk fills the first 16-token page, the third opens the next one.
+    One layer and the reference configuration (f32 KV, integer matmuls), so no rounding flip can avalanche; the
+    reference's own bound is 1e-4.  The oracle is held to the same case."""
+    path, spec = make_checkpoint(pk, tmp_path_factory, "llama", layers=1)
+    eng = pk["eng"]
+    tokens = list(range(1, 18))
+    model = eng.Model.load_gguf(path, kv_dtype="f32", matmul_path=1, max_batch_tokens=64, max_batch_lanes=4, kv_capacity_tokens=256)
+    one = model.new_session()
+    want, _ = model.forward_batch([(one, tokens, 0)])
+    assert len(one) == 17 and len(one.block_table()[0]) == 2
+    chunked = model.new_session()
+    model.forward_batch([(chunked, tokens[:15], 0)])
+    assert len(chunked) == 15 and len(chunked.block_table()[0]) == 1
+    model.forward_batch([(chunked, tokens[15:16], 15)])
+    assert len(chunked) == 16 and len(chunked.block_table()[0]) == 1
+    got, _ = model.forward_batch([(chunked, tokens[16:], 16)])
+    assert len(chunked) == 17 and len(chunked.block_table()[0]) == 2
+    assert float(np.abs(got - want).max()) < 1e-4
+
+    from oracle import decoder, engine as oe
+    dec = decoder.Decoder(path)
+    om = oe.OracleModel(dec.vocab, dec.max_context, 16, 8, 256, 0, decoder=dec)
+
+    def oracle_pass(session, ids, start):
+        r = om.reserve_batch([(session, start, len(ids))])
+        return om.forward([(session, [int(t) for t in ids], start)], r)
+    a, b = om.new_session(), om.new_session()
+    o_want = oracle_pass(a, tokens, 0)
+    oracle_pass(b, tokens[:15], 0)
+    oracle_pass(b, tokens[15:16], 15)
+    o_got = oracle_pass(b, tokens[16:], 16)
+    assert float(np.abs(o_got - o_want).max()) < 1e-4
+    assert float(np.abs(got - o_got).max()) < 2e-5          # and the product agrees with the oracle on the chunked path
