@@ -434,3 +434,25 @@ def test_chunked_execution_matches_one_shot_across_a_block_boundary(pk, tmp_path
     o_got = oracle_pass(b, tokens[16:], 16)
     assert float(np.abs(o_got - o_want).max()) < 1e-4
     assert float(np.abs(got - o_got).max()) < 2e-5          # and the product agrees with the oracle on the chunked path
+
+
+@pytest.mark.parametrize("kv_dtype,matmul_path", [("f32", 1), ("f16", 0)])
+def test_mixed_same_start_ragged_batch_matches_serial_lanes(pk, tmp_path_factory, kv_dtype, matmul_path):
+    """mixed_same_start_ragged_batch_matches_serial_lanes (src/decoder.rs:8932-8967): lanes of three tokens and of one
+    token in one packed forward give each lane the logits it gets alone (the reference's bound is 1e-5; on the integer path
+    the rows are bit-identical, on the tensor-core path the row count of a launch picks the kernel's token tile, not the
+    arithmetic of a row)."""
+    path, spec = make_checkpoint(pk, tmp_path_factory, "llama")
+    eng = pk["eng"]
+    model = eng.Model.load_gguf(path, kv_dtype=kv_dtype, matmul_path=matmul_path, max_batch_tokens=64, max_batch_lanes=4, kv_capacity_tokens=256)
+    first_tokens, second_tokens = [1, 2, 3], [4]
+    a, b, c, d = (model.new_session() for _ in range(4))
+    mixed, _ = model.forward_batch([(a, first_tokens, 0), (b, second_tokens, 0)])
+    first, _ = model.forward_batch([(c, first_tokens, 0)])
+    second, _ = model.forward_batch([(d, second_tokens, 0)])
+    assert mixed.shape == (2, spec.vocab)
+    assert float(np.abs(first - second).max()) > 1e-5
+    assert float(np.abs(mixed[0] - first[0]).max()) < 1e-5 and float(np.abs(mixed[1] - second[0]).max()) < 1e-5
+    if matmul_path == 1:
+        assert np.array_equal(mixed[0], first[0]) and np.array_equal(mixed[1], second[0])
+    assert len(a) == 3 and len(b) == 1
