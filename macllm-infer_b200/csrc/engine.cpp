@@ -102,8 +102,16 @@ void Engine::admit(Job job) {  // admit_with_diagnostic_refresh, engine.rs:1654-
         return fail_request(job.id, "This model's maximum context length is " + std::to_string(spec.max_context) + " tokens; the prompt (" +
                                         std::to_string(rq.prompt.size()) + " tokens) plus requested output (" +
                                         std::to_string(rq.max_new_tokens) + " tokens) exceeds it");
-    if (!(rq.temperature >= 0.f) || !(rq.top_p > 0.f && rq.top_p <= 1.f) || !(rq.repetition_penalty > 0.f))
-        return fail_request(job.id, "invalid sampling configuration");  // Sampler::new, sampling.rs:43-62
+    // EngineRequest::sampler -> Sampler::new + set_penalties (sampling.rs:43-79), reported as in prepare_request (engine.rs:3022-3032)
+    {
+        const char* why = nullptr;
+        if (!(std::isfinite(rq.temperature) && rq.temperature >= 0.f)) why = "temperature must be finite and non-negative";
+        else if (!(std::isfinite(rq.top_p) && rq.top_p > 0.f && rq.top_p <= 1.f)) why = "top_p must be finite and in (0, 1]";
+        else if (!(std::isfinite(rq.repetition_penalty) && rq.repetition_penalty > 0.f)) why = "repetition_penalty must be finite and positive";
+        else if (!(std::isfinite(rq.presence_penalty) && rq.presence_penalty >= -2.f && rq.presence_penalty <= 2.f)) why = "invalid presence_penalty";
+        else if (!(std::isfinite(rq.frequency_penalty) && rq.frequency_penalty >= -2.f && rq.frequency_penalty <= 2.f)) why = "invalid frequency_penalty";
+        if (why != nullptr) return fail_request(job.id, std::string("invalid sampling parameters: ") + why);
+    }
     // kv_capacity_rejection (engine.rs:2839-2863)
     {
         KvPoolStats st = model_.pool_stats();

@@ -11,6 +11,7 @@ from __future__ import annotations
 from collections import deque
 from dataclasses import dataclass, field
 
+import math
 import numpy as np
 
 from . import kv
@@ -195,6 +196,20 @@ class OracleEngine:
         if len(r.prompt) + max(r.max_new_tokens - 1, 0) > self.m.max_context:
             return self._fail(rid, f"This model's maximum context length is {self.m.max_context} tokens; the prompt ({len(r.prompt)} tokens) "
                                    f"plus requested output ({r.max_new_tokens} tokens) exceeds it")
+        why = None  # Sampler::new + set_penalties, sampling.rs:43-79; reported as in engine.rs:3022-3032
+        top_p = getattr(r, "top_p", 1.0)
+        if not (math.isfinite(r.temperature) and r.temperature >= 0.0):
+            why = "temperature must be finite and non-negative"
+        elif not (math.isfinite(top_p) and 0.0 < top_p <= 1.0):
+            why = "top_p must be finite and in (0, 1]"
+        elif not (math.isfinite(r.repetition_penalty) and r.repetition_penalty > 0.0):
+            why = "repetition_penalty must be finite and positive"
+        elif not (math.isfinite(r.presence_penalty) and -2.0 <= r.presence_penalty <= 2.0):
+            why = "invalid presence_penalty"
+        elif not (math.isfinite(r.frequency_penalty) and -2.0 <= r.frequency_penalty <= 2.0):
+            why = "invalid frequency_penalty"
+        if why is not None:
+            return self._fail(rid, "invalid sampling parameters: " + why)
         max_cached = 0 if r.max_new_tokens == 0 else len(r.prompt) + r.max_new_tokens - 1  # engine.rs:2839-2863
         if max_cached > self.m.pool.max_blocks * self.m.pool.block_tokens:
             return self._fail(rid, "request exceeds the configured shared KV capacity")

@@ -357,3 +357,32 @@ def test_scheduler_fills_available_slots_before_the_first_iteration(eng):
     assert pe.trace() == [[(0, 0, 1), (1, 0, 1), (2, 0, 1)]] == [[tuple(l) for l in t] for t in oe_.trace]
     s = pe.stats()
     assert s["ticks"] == 1 and s["cleanup_drains"] == 0 and s["completed_requests"] == 3
+
+
+def test_invalid_sampling_parameters_fail_the_request_with_the_reference_wording(eng):
+    """rejects_invalid_sampling_parameters (src/sampling.rs:812-829) as the engine reports it (engine.rs:3022-3032):
+    Sampler::new's three checks, then set_penalties' two, each failing only its own request."""
+    from oracle import engine as oe
+    (pm, pe), (om, oe_) = both(eng, dict(vocab=16), dict(max_active_sequences=2, scheduler_token_budget=8, prefill_token_quantum=4, queue_capacity=16))
+    cases = [(dict(temperature=-1.0), "temperature must be finite and non-negative"),
+             (dict(temperature=float("nan")), "temperature must be finite and non-negative"),
+             (dict(repetition_penalty=0.0), "repetition_penalty must be finite and positive"),
+             (dict(presence_penalty=2.5), "invalid presence_penalty"),
+             (dict(frequency_penalty=-3.0), "invalid frequency_penalty"),
+             (dict(presence_penalty=2.0, frequency_penalty=-2.0), None)]
+    ids_p = pe.submit([eng.Request([1, 2], 2, **kw) for kw, _ in cases])
+    ids_o = oe_.submit([oe.Req([1, 2], 2, **kw) for kw, _ in cases])
+    assert ids_p == ids_o
+    pe.run()
+    oe_.run()
+    for rid, (_, why) in zip(ids_p, cases):
+        rp, ro = pe.result(rid), oe_.results[rid]
+        if why is None:
+            assert rp["state"] == ro.state == "done"
+        else:
+            assert rp["state"] == ro.state == "failed" and rp["kind"] == "invalid_request"
+            assert rp["message"] == ro.message == "invalid sampling parameters: " + why
+    # top_p lives on the product's request only (the oracle's engine has no stochastic sampler of its own)
+    (rid,) = pe.submit([eng.Request([1, 2], 2, top_p=0.0)])
+    pe.run()
+    assert pe.result(rid)["message"] == "invalid sampling parameters: top_p must be finite and in (0, 1]"
