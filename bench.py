@@ -315,6 +315,7 @@ def run_step(eng_mod, model, w, reqs, active: int, lockstep=None):
             break
         gen += len(r["tokens"])
         toks -= r["cached_tokens"]          # prompt tokens served from the prefix cache were not computed
+    st["generated_tokens"] = gen
     diag = model.prefix_diagnostics() if w.prefix_capacity_tokens and err is None else None
     eng.close()
     if lockstep is not None:
@@ -713,6 +714,7 @@ def main():
     launches0 = model.launch_count()
     h2d0, d2h0 = model.transfer_bytes()
     tokens = 0
+    generated = 0
     dev_ms = 0.0
     ticks = 0
     diag = None
@@ -720,6 +722,7 @@ def main():
     for _ in range(args.steps):
         n, wall, st, diag = run_step(eng_mod, model, w, reqs, active, lockstep)
         tokens += n
+        generated += st["generated_tokens"]
         dev_ms += st["device_ms"]
         ticks += st["ticks"]
     barrier(dist)
@@ -731,6 +734,7 @@ def main():
     wall_max = all_max(dist, wall_total)
     dev_max = all_max(dist, dev_ms / 1e3)
     tokens_all = all_sum(dist, float(tokens))
+    generated_all = all_sum(dist, float(generated))
     pk = peaks()
 
     # one extra profiled step: CUDA events around every launch, per kernel class
@@ -803,7 +807,9 @@ def main():
                    data="synthetic", config=config, clocks=clocks,
                    e2e=dict(value=tokens_all / wall_max, unit=UNIT, h2d_bytes_per_step=(h2d1 - h2d0) // max(args.steps, 1),
                             d2h_bytes_per_step=(d2h1 - d2h0) // max(args.steps, 1)),
-                   gpu_launches=launches, ticks_per_step=ticks // max(args.steps, 1), roofline=roof, tick_classes=classes,
+                   gpu_launches=launches, ticks_per_step=ticks // max(args.steps, 1),
+                   # the reference's scoreboard also quotes generated tokens alone (src/benchmark/serving.rs:301-328)
+                   output_tokens_per_s=generated_all / dev_max, roofline=roof, tick_classes=classes,
                    cpu_baseline=base)
         if diag is not None:
             out["prefix_cache"] = diag
