@@ -262,3 +262,90 @@ def test_a_table_twice_in_one_batch_is_refused_without_pool_mutation(Pool):
         pool.append([table, table], [1, 1])
     assert pool.stats() == before and len(table) == 0
     assert pool.append([table], [1]) == []          # the table is not left locked
+
+
+def test_pool_serialises_reservations_in_epoch_order(mk):
+    """cache.rs:5104-5127: while one reservation is open a second one is refused and no device completion can be
+    published; the next reservation takes the next epoch.  Oracle pool directly; product through the model-level ABI
+    (mk_reserve_batch / mk_reservation_drop on the host-only model), where a reservation stays open between calls."""
+    import ctypes as C
+    import importlib
+    from oracle import kv
+    p = kv.Pool(2, 2, 2)
+    t1, t2 = kv.Table(p), kv.Table(p)
+    r1 = p.reserve_batch([t1], [1])
+    with pytest.raises(kv.Invalid, match="transaction 1 is still active"):
+        p.reserve_batch([t2], [1])
+    with pytest.raises(kv.Invalid, match="cannot publish device completion"):
+        p.mark_completed_through(r1.epoch)
+    assert p.stats()["submitted_epoch"] == r1.epoch == 1
+    r1.rollback()
+    r2 = p.reserve_batch([t2], [1])
+    assert r2.epoch == 2
+    r2.rollback()
+
+    eng = importlib.import_module("macllm_infer_b200.engine")
+    capi = importlib.import_module("macllm_infer_b200._capi")
+    m = eng.Model.fake(vocab=8, block_tokens=2, slab_blocks=2, kv_capacity_tokens=4)
+    s1, s2 = m.new_session(), m.new_session()
+    lanes1, keep1 = m._lanes([(s1, [1], 0)])
+    lanes2, keep2 = m._lanes([(s2, [1], 0)])
+    first, second = C.c_void_p(), C.c_void_p()
+    assert capi.lib().mk_reserve_batch(m._h, lanes1, 1, C.byref(first)) == 0
+    assert capi.lib().mk_reserve_batch(m._h, lanes2, 1, C.byref(second)) < 0
+    assert "transaction 1 is still active" in capi.lib().mk_last_error().decode()
+    assert m.pool_stats()["submitted_epoch"] == 1
+    assert capi.lib().mk_reservation_drop(first) == 0
+    assert capi.lib().mk_reserve_batch(m._h, lanes2, 1, C.byref(second)) == 0
+    assert m.pool_stats()["submitted_epoch"] == 2
+    assert capi.lib().mk_reservation_drop(second) == 0
+    s = m.pool_stats()
+    assert (s["reserved_blocks"], s["free_blocks"], s["live_blocks"]) == (0, 2, 0)
+    del keep1, keep2
+
+
+def test_attach_prefix_failures_leave_ownership_unchanged(mk):
+    """cache.rs:4476-4526: a prefix cannot come from another pool, be longer than its source, or land in a table that
+    already owns pages; every refusal leaves the tables and the pool's counters as they were."""
+    import importlib
+    from oracle import kv
+    pkv = importlib.import_module("macllm_infer_b200.kv")
+    capi = importlib.import_module("macllm_infer_b200._capi")
+
+    # oracle
+    pool = kv.Pool(2, 2, 2)
+    source = kv.Table(pool)
+    r = pool.reserve_batch([source], [3])
+    r.mark_all_used()
+    r.commit()
+    pool.mark_completed_through(pool.submitted_epoch)
+    before = pool.stats()
+    foreign = kv.Table(kv.Pool(2, 1, 1))
+    too_long, small = kv.Table(pool), kv.Table(pool, limit=2)
+    occupied = source.fork_prefix(1)
+    shared = pool.stats()
+    for table, n in ((foreign, 2), (too_long, 4), (small, 3), (occupied, 1)):
+        kept = (table.logical_len, list(table.blocks))
+        with pytest.raises(kv.Invalid):
+            table.attach_prefix(source, n)
+        assert (table.logical_len, list(table.blocks)) == kept
+    assert pool.stats() == shared and shared["live_references"] == before["live_references"] + 1
+
+    # product
+    ppool = pkv.KvPool(2, 2, 2)
+    psource = ppool.new_table()
+    ppool.append_batch([psource], [3])
+    ppool.complete_epoch(ppool.submitted_epoch())
+    pbefore = ppool.stats()
+    assert pbefore == before
+    pforeign = pkv.KvPool(2, 1, 1).new_table()
+    ptoo_long = ppool.new_table()
+    poccupied = psource.fork_prefix(1)
+    pshared = ppool.stats()
+    assert pshared == shared
+    for table, n in ((pforeign, 2), (ptoo_long, 4), (poccupied, 1)):
+        kept = (len(table), table.blocks())
+        with pytest.raises(capi.MkError):
+            table.attach_prefix(psource, n)
+        assert (len(table), table.blocks()) == kept
+    assert ppool.stats() == pshared
