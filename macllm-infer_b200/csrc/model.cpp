@@ -1161,8 +1161,7 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
                 const float* back = ep_exchange_layer(w, ls, e_xh_.as<__half>(), grp_off_.as<int32_t>(), T);
                 launch_moe_combine(back, sel_e_.as<int32_t>(), sel_w_.as<float>(), pos_of_pair_.as<int32_t>(), T, K, H, 0, E, down_.as<float>(),
                                    stream_);
-            } else {
-            if (moe_stream) {
+            } else if (moe_stream) {
                 // the routed rows grouped by expert as f16, then the expert-grouped tensor-core matmuls: gate|up with the
                 // activation in its epilogue (f16 out), down on those rows.  Every expert's weights are read once per 64
                 // of its rows; the row ranges stay on the device.
@@ -1187,7 +1186,10 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
                 launch_actmul_quant(e_gate_.as<float>(), e_up_.as<float>(), F, P, F, ls.act, dkind, xd, nullptr, stream_);
                 launch_qgemv_grouped(w.down.w, EL, off, nullptr, xd, e_down_.as<float>(), H, stream_);
             }
-            if (ep && ep_->has_exchange()) {
+            // replicated lanes (or one GPU): this rank's expert outputs are combined here, the partial sums exchanged
+            if (ep_dp) {
+                // combined above from the result area of the exchange
+            } else if (ep && ep_->has_exchange()) {
                 launch_moe_combine_exchange(e_down_.as<float>(), sel_e_.as<int32_t>(), sel_w_.as<float>(), pos_of_pair_.as<int32_t>(), T, K,
                                             H, e0, e0 + EL, ep_->peers(), ep_->next_epoch(), down_.as<float>(),
                                             tc_ws_.status.as<int32_t>(), stream_);
@@ -1197,11 +1199,10 @@ void Model::run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint
                                    e0, e0 + EL, ep ? ep_partial_.as<float>() : down_.as<float>(), stream_);
                 prof_end();
             }
-            if (ep && !ep_->has_exchange()) {
+            if (!ep_dp && ep && !ep_->has_exchange()) {
                 ep_->all_gather_f32(ep_partial_.as<float>(), ep_gather_.as<float>(), (size_t)T * H, stream_);
                 launch_ep_sum(ep_gather_.as<float>(), cfg_.ep_size, (int64_t)T * H, down_.as<float>(), stream_);
                 launches_ += 2;
-            }
             }
             launches_ += 8;
         }
