@@ -39,6 +39,10 @@
 #ifdef _OPENMP
 #include <omp.h>
 #endif
+#if defined(__AVX2__) && !defined(ORC_NO_SIMD)
+#include <immintrin.h>
+#define ORC_AVX2 1
+#endif
 
 extern "C" {
 
@@ -300,22 +304,44 @@ void orc_quantize_q80(const float* x, int64_t n, int8_t* qs, uint16_t* d) {
 }
 
 // ---------------------------------------------------------------- quantised matmul
+#ifdef ORC_AVX2
+static inline int32_t hsum_i32(__m256i v) {
+    __m128i s = _mm_add_epi32(_mm256_castsi256_si128(v), _mm256_extracti128_si256(v, 1));
+    s = _mm_add_epi32(s, _mm_shuffle_epi32(s, 0x4E));
+    s = _mm_add_epi32(s, _mm_shuffle_epi32(s, 0xB1));
+    return _mm_cvtsi128_si32(s);
+}
+#endif
 static float dot_q4k_q8k(const BlkQ4K* w, const int8_t* qs, const float* dx, const int16_t* bs, int64_t nb, bool rev) {
     float acc = 0.f;
     for (int64_t bi = 0; bi < nb; ++bi) {
         int64_t b = rev ? nb - 1 - bi : bi;
         const int8_t* q8 = qs + b * 256;
         int32_t isum = 0, msum = 0;
+#ifdef ORC_AVX2
+        __m256i vsum = _mm256_setzero_si256();   // exact 32-bit integer sums: any order gives the same isum
+#endif
         for (int j = 0; j < 4; ++j) {
             int sc0, m0, sc1, m1;
             q4k_scale_min(2 * j, w[b].scales, &sc0, &m0);
             q4k_scale_min(2 * j + 1, w[b].scales, &sc1, &m1);
             const uint8_t* q = w[b].qs + 32 * j;
+#ifdef ORC_AVX2
+            // 4-bit x 8-bit pairs: |sum of two| <= 2*15*128 fits 16 bits; times a 6-bit scale, pairwise, fits 32 bits.
+            const __m256i qv = _mm256_loadu_si256((const __m256i*)q), nib = _mm256_set1_epi8(0xF);
+            const __m256i p0 = _mm256_maddubs_epi16(_mm256_and_si256(qv, nib), _mm256_loadu_si256((const __m256i*)(q8 + 64 * j)));
+            const __m256i p1 = _mm256_maddubs_epi16(_mm256_and_si256(_mm256_srli_epi16(qv, 4), nib), _mm256_loadu_si256((const __m256i*)(q8 + 64 * j + 32)));
+            vsum = _mm256_add_epi32(vsum, _mm256_add_epi32(_mm256_madd_epi16(p0, _mm256_set1_epi16((short)sc0)), _mm256_madd_epi16(p1, _mm256_set1_epi16((short)sc1))));
+#else
             int32_t s0 = 0, s1 = 0;
             for (int l = 0; l < 32; ++l) { s0 += (int)(q[l] & 0xF) * q8[64 * j + l]; s1 += (int)(q[l] >> 4) * q8[64 * j + 32 + l]; }
             isum += sc0 * s0 + sc1 * s1;
+#endif
             msum += m0 * ((int)bs[b * 16 + 4 * j] + bs[b * 16 + 4 * j + 1]) + m1 * ((int)bs[b * 16 + 4 * j + 2] + bs[b * 16 + 4 * j + 3]);
         }
+#ifdef ORC_AVX2
+        isum = hsum_i32(vsum);
+#endif
         float d = h2f(w[b].d), dmin = h2f(w[b].dmin);
         acc += dx[b] * (d * (float)isum - dmin * (float)msum);
     }
@@ -328,6 +354,30 @@ static float dot_q6k_q8k(const BlkQ6K* w, const int8_t* qs, const float* dx, int
         int64_t b = rev ? nb - 1 - bi : bi;
         const int8_t* q8 = qs + b * 256;
         int32_t isum = 0;
+#ifdef ORC_AVX2
+        // (q - 32) * y = q * y - 32 * y with q in 0..63: pair sums stay within 16 bits (<= 2*63*128 + 2*32*128), and
+        // the 8-bit scale of each 16-element run multiplies pairwise into exact 32-bit sums.  A 32-byte vector holds
+        // two runs: the low half takes scale 2k, the high half scale 2k+1.
+        __m256i vsum = _mm256_setzero_si256();
+        const __m256i nib = _mm256_set1_epi8(0xF), two = _mm256_set1_epi8(3), off = _mm256_set1_epi8(32);
+        for (int h = 0; h < 2; ++h) {
+            const __m256i l0 = _mm256_loadu_si256((const __m256i*)(w[b].ql + 64 * h)), l1 = _mm256_loadu_si256((const __m256i*)(w[b].ql + 64 * h + 32));
+            const __m256i hv = _mm256_loadu_si256((const __m256i*)(w[b].qh + 32 * h));
+            const int8_t* sc = w[b].scales + 8 * h; const int8_t* y = q8 + 128 * h;
+            __m256i qv[4];
+            qv[0] = _mm256_or_si256(_mm256_and_si256(l0, nib), _mm256_slli_epi16(_mm256_and_si256(hv, two), 4));
+            qv[1] = _mm256_or_si256(_mm256_and_si256(l1, nib), _mm256_slli_epi16(_mm256_and_si256(_mm256_srli_epi16(hv, 2), two), 4));
+            qv[2] = _mm256_or_si256(_mm256_and_si256(_mm256_srli_epi16(l0, 4), nib), _mm256_slli_epi16(_mm256_and_si256(_mm256_srli_epi16(hv, 4), two), 4));
+            qv[3] = _mm256_or_si256(_mm256_and_si256(_mm256_srli_epi16(l1, 4), nib), _mm256_slli_epi16(_mm256_and_si256(_mm256_srli_epi16(hv, 6), two), 4));
+            for (int k = 0; k < 4; ++k) {
+                const __m256i yv = _mm256_loadu_si256((const __m256i*)(y + 32 * k));
+                const __m256i p = _mm256_sub_epi16(_mm256_maddubs_epi16(qv[k], yv), _mm256_maddubs_epi16(off, yv));
+                const __m256i sv = _mm256_set_m128i(_mm_set1_epi16((short)sc[2 * k + 1]), _mm_set1_epi16((short)sc[2 * k]));
+                vsum = _mm256_add_epi32(vsum, _mm256_madd_epi16(p, sv));
+            }
+        }
+        isum = hsum_i32(vsum);
+#else
         for (int h = 0; h < 2; ++h) {
             const uint8_t* ql = w[b].ql + 64 * h; const uint8_t* qh = w[b].qh + 32 * h; const int8_t* sc = w[b].scales + 8 * h;
             const int8_t* y = q8 + 128 * h;
@@ -342,6 +392,7 @@ static float dot_q6k_q8k(const BlkQ6K* w, const int8_t* qs, const float* dx, int
             }
             for (int k = 0; k < 8; ++k) isum += (int)sc[k] * s[k];
         }
+#endif
         acc += dx[b] * (h2f(w[b].d) * (float)isum);
     }
     return acc;

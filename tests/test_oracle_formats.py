@@ -135,3 +135,34 @@ def test_host_decoder_refuses_what_it_does_not_decode(ops, mk):
             ops.decode_rows(qtype, raw, 1, cols)
     with pytest.raises(capi.MkError):
         ops.decode_rows(13, raw, 1, 300)                    # not a whole number of 256-weight blocks
+
+
+def test_vector_inner_sums_equal_the_scalar_loops(orc, tmp_path):
+    """The oracle's Q4_K / Q6_K dots take their integer inner sums with AVX2 where the host has it. Integer sums are
+    exact in any order, so the result must equal the scalar loops' bit for bit: the same file built without the
+    vector path is the check. Random block bytes cover every nibble, high-bit and scale pattern."""
+    import ctypes as C
+    import os
+    import subprocess
+    src = os.path.join(os.path.dirname(orc.__file__), "oracle_math.cpp")
+    so = str(tmp_path / "liboracle_scalar.so")
+    cxx = "/usr/bin/g++" if os.access("/usr/bin/g++", os.X_OK) else "g++"
+    subprocess.run([cxx, "-O2", "-std=c++17", "-fPIC", "-fopenmp", "-mavx2", "-mfma", "-ffp-contract=off", "-fno-fast-math",
+                    "-DORC_NO_SIMD", "-shared", "-o", so, src], check=True)
+    scalar = C.CDLL(so)
+    rng = np.random.default_rng(11)
+    for qtype, block_bytes, scale_at in ((12, 144, (0, 4)), (14, 210, (208, 210))):
+        for rows, cols, T in ((96, 1024, 3), (33, 256, 1)):
+            nb = cols // 256
+            w = rng.integers(0, 256, size=(rows, nb, block_bytes), dtype=np.uint8)
+            halves = rng.uniform(0.001, 0.05, size=(rows, nb, (scale_at[1] - scale_at[0]) // 2)).astype(np.float16)
+            w[:, :, scale_at[0]:scale_at[1]] = halves.view(np.uint8).reshape(rows, nb, -1)
+            w = np.ascontiguousarray(w.reshape(rows, nb * block_bytes))
+            x = (rng.standard_normal((T, cols)) * 3).astype(np.float32)
+            x[0, :40] = 0
+            for mode in (1, 3):
+                want = np.empty((T, rows), np.float32)
+                scalar.orc_qmatmul(C.c_int(qtype), C.c_void_p(w.ctypes.data), C.c_int64(rows), C.c_int64(cols),
+                                   C.c_void_p(x.ctypes.data), C.c_int64(T), C.c_void_p(want.ctypes.data), C.c_int(mode))
+                got = orc.qmatmul(qtype, w, rows, cols, x, mode)
+                assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (qtype, rows, cols, T, mode)
