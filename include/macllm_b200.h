@@ -163,9 +163,12 @@ int32_t mk_model_load_gguf(const char* path, const mk_load_config* cfg, mk_model
 int32_t mk_model_new_fake(int32_t vocab, int32_t max_context, const mk_load_config* cfg, int64_t fail_forward_at, mk_model** out);
 /* More injection sites of the fake model, like FakeModel's fail_completion_barrier_at and friends (src/engine.rs:
  * 3107-3300): the call numbered `index` (0-based) at `site` fails.  site 0 forward, 1 completion barrier
- * (mk_read_output), 2 prompt admission (mk_reset_session_for_prompt), 3 cleanup drain (mk_synchronize).  Refused for
- * a model loaded from a file. */
+ * (mk_read_output), 2 prompt admission (mk_reset_session_for_prompt), 3 cleanup drain (mk_synchronize), 4 clearing of a session (panic_clear_session,
+ * src/engine.rs:5640-5682; `index` counts from this call on).  Refused for a model loaded from a file. */
 int32_t mk_model_fake_inject(mk_model* m, int32_t site, int64_t index);
+/* Host-only fake model: call cb(user) once inside the next completion barrier - the place where the reference's FakeModel
+ * flips cancel_on_completion_barrier (src/engine.rs:3143,3575-3583), "the client gave up while the forward ran". */
+int32_t mk_model_fake_on_barrier(mk_model* m, void (*cb)(void*), void* user);
 int32_t mk_model_free(mk_model* m);
 /* ep_mode 1 only.  The ranks of an expert-parallel group tick in lock step: each MoE layer of each forward is one
  * exchange that all ranks take part in.  A rank whose scheduler has no lane to run in a tick calls this instead of a
@@ -323,6 +326,7 @@ typedef struct mk_engine_stats {
     double device_ms;            /* sum of per-tick device times */
     int64_t cleanup_drains;      /* mk_synchronize calls made while poisoning (src/engine.rs:2723-2736) */
     int64_t device_sampled;      /* stochastic tokens picked by the device sampler */
+    int64_t cancelled_requests;  /* requests that ended by mk_engine_cancel */
 } mk_engine_stats;
 
 int32_t mk_engine_new(mk_model* m, const mk_engine_config* cfg, mk_engine** out);
@@ -336,7 +340,7 @@ int32_t mk_engine_step(mk_engine* e, int32_t* ran_lanes);
 /* Run ticks until every submitted request has finished. */
 int32_t mk_engine_run(mk_engine* e);
 int32_t mk_engine_pending(mk_engine* e, int32_t* out);
-/* Generated tokens of a request (capacity in *n, count out); *finished: 0 running, 1 done, 2 failed. */
+/* Generated tokens of a request (capacity in *n, count out); *finished: 0 running, 1 done, 2 failed, 3 cancelled. */
 int32_t mk_engine_result(mk_engine* e, int32_t request_id, uint32_t* tokens, int32_t* n, int32_t* finished, int64_t* cached_tokens);
 /* Logits rows recorded for a request when record_logits is set: [n_rows][vocab]. */
 int32_t mk_engine_logits(mk_engine* e, int32_t request_id, float* out, int32_t* n_rows);
@@ -349,6 +353,13 @@ int32_t mk_engine_stats_query(mk_engine* e, mk_engine_stats* out);
  * and queued request fails with kind 4 (Fatal) and the message "inference worker failed: ...", the sessions are
  * dropped, mk_engine_step becomes a no-op and mk_engine_submit answers "inference worker is unavailable (Poisoned)". */
 int32_t mk_engine_status(mk_engine* e, int32_t* status);
+/* EngineTicket::cancel / Drop (src/engine.rs:1136-1145): a sticky flag.  A request still queued is skipped before any
+ * validation, session or model work (src/engine.rs:1671-1674); an active one leaves at its next visit and its pages are back
+ * in the pool before the peers' forward of that tick (src/engine.rs:1409-1417,2024-2029,1995-2003); one cancelled while
+ * its forward ran keeps its row in that forward and is dropped after the completion barrier without a sampled token
+ * (src/generation.rs:1201-1204).  The request's result then reads "3 cancelled" with the tokens produced so far.  The only
+ * engine entry that may be called from another thread while mk_engine_step runs. */
+int32_t mk_engine_cancel(mk_engine* e, int32_t request_id);
 /* EngineFailureKind of a failed request (src/engine.rs:268-273): 0 none, 1 InvalidRequest, 2 ResourceExhausted,
  * 3 Internal, 4 Fatal. */
 int32_t mk_engine_failure_kind(mk_engine* e, int32_t request_id, int32_t* kind);

@@ -93,7 +93,7 @@ class TickLane(C.Structure):
 class EngineStats(C.Structure):
     _fields_ = [("ticks", C.c_int64), ("prefill_tokens", C.c_int64), ("decode_tokens", C.c_int64),
                 ("completed_requests", C.c_int64), ("failed_requests", C.c_int64), ("kv_shrinks", C.c_int64),
-                ("device_ms", C.c_double), ("cleanup_drains", C.c_int64), ("device_sampled", C.c_int64)]
+                ("device_ms", C.c_double), ("cleanup_drains", C.c_int64), ("device_sampled", C.c_int64), ("cancelled_requests", C.c_int64)]
 
 
 class LaneSampling(C.Structure):
@@ -127,6 +127,7 @@ SIGNATURES = {
     "mk_model_load_gguf": (_i32, [C.c_char_p, C.POINTER(LoadConfig), C.POINTER(P)]),
     "mk_model_new_fake": (_i32, [_i32, _i32, C.POINTER(LoadConfig), _i64, C.POINTER(P)]),
     "mk_model_fake_inject": (_i32, [P, _i32, _i64]),
+    "mk_model_fake_on_barrier": (_i32, [P, C.c_void_p, C.c_void_p]),
     "mk_model_ep_idle_tick": (_i32, [P]),
     "mk_k_ep_exchange_emulated": (_i32, [_i32, _i32, _i32, _i32, P, P, _i32, _i32, _i64, P, P, P]),
     "mk_model_free": (_i32, [P]),
@@ -167,6 +168,7 @@ SIGNATURES = {
     "mk_engine_stats_query": (_i32, [P, C.POINTER(EngineStats)]),
     "mk_engine_status": (_i32, [P, C.POINTER(_i32)]),
     "mk_engine_failure_kind": (_i32, [P, _i32, C.POINTER(_i32)]),
+    "mk_engine_cancel": (_i32, [P, _i32]),
     "mk_kvpool_new": (_i32, [_i32, _i32, _i64, C.POINTER(P)]),
     "mk_kvpool_free": (_i32, [P]),
     "mk_kvpool_stats": (_i32, [P, C.POINTER(PoolStats)]),

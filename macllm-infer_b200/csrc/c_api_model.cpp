@@ -152,6 +152,14 @@ int32_t mk_model_fake_inject(mk_model* m, int32_t site, int64_t index) {
     });
 }
 
+int32_t mk_model_fake_on_barrier(mk_model* m, void (*cb)(void*), void* user) {
+    return guarded([&] {
+        FakeLm* fake = dynamic_cast<FakeLm*>(m->lm.get());
+        if (fake == nullptr) throw std::runtime_error("the barrier hook is only available on the host-only fake model");
+        fake->on_next_barrier(cb, user);
+    });
+}
+
 int32_t mk_model_free(mk_model* m) {
     return guarded([&] { delete m; });
 }
@@ -472,11 +480,16 @@ int32_t mk_engine_stats_query(mk_engine* e, mk_engine_stats* out) {
         out->device_ms = s.device_ms;
         out->cleanup_drains = s.cleanup_drains;
         out->device_sampled = s.device_sampled;
+        out->cancelled_requests = s.cancelled;
     });
 }
 
 int32_t mk_engine_status(mk_engine* e, int32_t* status) {
     return guarded([&] { *status = (int32_t)e->e->status(); });
+}
+
+int32_t mk_engine_cancel(mk_engine* e, int32_t request_id) {
+    return guarded([&] { e->e->cancel(request_id); });
 }
 
 int32_t mk_engine_failure_kind(mk_engine* e, int32_t request_id, int32_t* kind) {

@@ -60,6 +60,28 @@ void Engine::fail_request(int id, const std::string& message, FailureKind kind) 
     ++stats_.failed;
 }
 
+void Engine::cancel(int id) {
+    if (id < 0 || id >= next_id_.load()) throw std::runtime_error("unknown request id");
+    std::lock_guard<std::mutex> lock(cancel_mu_);
+    cancelled_.insert(id);
+    any_cancelled_.store(true, std::memory_order_release);
+}
+
+bool Engine::is_cancelled(int id) {
+    if (!any_cancelled_.load(std::memory_order_acquire)) return false;  // the common tick takes no lock
+    std::lock_guard<std::mutex> lock(cancel_mu_);
+    return cancelled_.count(id) != 0;
+}
+
+// A cancelled request gets no terminal event in the reference (its receiver is gone); here its result says so.
+void Engine::finish_cancelled(int id) {
+    EngineResult& r = results_[id];
+    if (r.state != FinishState::Running) return;
+    r.state = FinishState::Cancelled;
+    r.finish_reason = "cancelled";
+    ++stats_.cancelled;
+}
+
 // ServingScheduler::poison (engine.rs:2719-2770): drain what was submitted, fail every active slot, every member of
 // a pending atomic batch and every queued job with kind Fatal, drop the sequences and all reusable sessions.
 void Engine::poison(std::string message) {
@@ -88,6 +110,9 @@ void Engine::poison(std::string message) {
 
 void Engine::admit(Job job) {  // admit_with_diagnostic_refresh, engine.rs:1654-1808
     if ((int)active_.size() >= cfg_.max_active_sequences) throw std::runtime_error("scheduler attempted to exceed the active sequence limit");
+    // a request given up while it queued is skipped before preflight and model work: no validation message, no session
+    // taken, no prefix lookup (engine.rs:1671-1674,1715-1718)
+    if (is_cancelled(job.id)) return finish_cancelled(job.id);
     const EngineRequest& rq = job.req;
     const LmRuntimeSpec& spec = model_.spec();
     // prepare_request for EngineInput::TokenIds (engine.rs:2976-3021): empty prompt, vocabulary, context - in that order,
@@ -239,6 +264,11 @@ int Engine::drive_once() {  // engine.rs:1938-1964
         if (token_budget == 0) break;
         Sequence& s = *active_[(size_t)index];
         Visit v;
+        if (is_cancelled(s.id)) {  // flush_pending -> Abandoned (engine.rs:1409-1417,2024-2029): leaves before the peers' forward
+            v.kind = Visit::Remove;
+            actions.push_back(v);
+            continue;
+        }
         if (s.delivering) {
             v.kind = Visit::Remove;
             actions.push_back(v);
@@ -272,7 +302,12 @@ int Engine::drive_once() {  // engine.rs:1938-1964
     }
     const int visits = (int)actions.size();
     for (int i = 0; i < visits; ++i)  // reclaim_collected_removals (engine.rs:1995-2003)
-        if (actions[(size_t)i].kind == Visit::Remove) reclaim(*active_[(size_t)i]);
+        if (actions[(size_t)i].kind == Visit::Remove) {
+            reclaim(*active_[(size_t)i]);
+            // only now is the cancelled request answered: if clearing its session fails, it is still a slot of the
+            // scheduler and gets the fatal message with its peers (engine.rs:5640-5682)
+            if (is_cancelled(active_[(size_t)i]->id)) finish_cancelled(active_[(size_t)i]->id);
+        }
 
     // ---- reserve_and_prepare_visits (engine.rs:2097-2167)
     std::vector<int> candidates;
@@ -396,6 +431,13 @@ int Engine::drive_once() {  // engine.rs:1938-1964
             v.kind = Visit::Complete;
             v.finished = false;
             // GenerationCore::complete (generation.rs:1159-1266)
+            if (is_cancelled(s.id)) {  // given up while the forward ran: the row is dropped, the peers' rows keep their places
+                s.phase = Phase::Finished;
+                finish_cancelled(s.id);
+                v.finished = true;
+                ++row;
+                continue;
+            }
             if (!v.ready_to_sample) {
                 s.phase = Phase::Prefill;
                 s.cursor = next_cache_len;

@@ -5,9 +5,12 @@
 // results are collected per request instead of streamed.
 #pragma once
 #include "paged_lm.h"
+#include <atomic>
 #include <deque>
 #include <map>
 #include <memory>
+#include <mutex>
+#include <set>
 #include <vector>
 
 namespace mk {
@@ -33,7 +36,9 @@ struct EngineRequest {
     bool publish_prompt_prefix = true;
 };
 
-enum class FinishState : int { Running = 0, Done = 1, Failed = 2 };
+// Cancelled: the caller gave the request up (EngineTicket::cancel / a closed event channel, src/engine.rs:1136-1145); the
+// scheduler answers nothing more for it, the tokens produced so far stay readable
+enum class FinishState : int { Running = 0, Done = 1, Failed = 2, Cancelled = 3 };
 // EngineFailureKind (src/engine.rs:268-273)
 enum class FailureKind : int { None = 0, InvalidRequest = 1, ResourceExhausted = 2, Internal = 3, Fatal = 4 };
 // EngineStatus (src/engine.rs:281-288); this engine is driven by its caller's thread, so Starting never shows
@@ -44,7 +49,7 @@ struct EngineResult {
     FinishState state = FinishState::Running;
     std::string message;        // failure message
     FailureKind kind = FailureKind::None;
-    std::string finish_reason;  // "length", "stop"
+    std::string finish_reason;  // "length", "stop", "cancelled"
     int64_t cached_tokens = 0;
     std::vector<float> logits;  // record_logits: one row per sampled position
     int logit_rows = 0;
@@ -55,7 +60,7 @@ struct TickLaneTrace {
 };
 
 struct EngineStats {
-    int64_t ticks = 0, prefill_tokens = 0, decode_tokens = 0, completed = 0, failed = 0, kv_shrinks = 0, cleanup_drains = 0, device_sampled = 0;
+    int64_t ticks = 0, prefill_tokens = 0, decode_tokens = 0, completed = 0, failed = 0, kv_shrinks = 0, cleanup_drains = 0, device_sampled = 0, cancelled = 0;
     double device_ms = 0.0;
 };
 
@@ -71,6 +76,11 @@ public:
     // lanes of the packed forward (0 when none ran).  Any error that escapes the tick poisons the engine: every active,
     // pending and queued request fails with kind Fatal, the sessions are dropped, later submissions are refused.
     int step();
+    // EngineTicket::cancel (src/engine.rs:1136-1145): a sticky flag the scheduler reads - a queued request is skipped
+    // before any validation or model work, an active one leaves at its next visit (its pages are back before the peers'
+    // forward), one cancelled while its forward ran drops its row after the completion barrier.  The one entry that may be
+    // called from another thread while step() runs.
+    void cancel(int id);
     EngineStatus status() const { return poisoned_ ? EngineStatus::Poisoned : (pending() > 0 ? EngineStatus::Busy : EngineStatus::Ready); }
     const std::string& poison_message() const { return poison_message_; }
     void run();
@@ -116,6 +126,8 @@ private:
     void poison(std::string message);
     void fail_request(int id, const std::string& message, FailureKind kind = FailureKind::InvalidRequest);
     void reclaim(Sequence& s);
+    bool is_cancelled(int id);
+    void finish_cancelled(int id);
     uint32_t sample(Sequence& s, float* row);
 
     PagedLm& model_;
@@ -127,7 +139,8 @@ private:
     std::map<int, EngineResult> results_;
     std::vector<std::vector<TickLaneTrace>> trace_;
     EngineStats stats_;
-    int next_id_ = 0, next_batch_ = 0;
+    std::atomic<int> next_id_{0};
+    int next_batch_ = 0;
     int round_visits_remaining_ = 0, round_budget_remaining_ = 0;
     std::vector<float> logits_host_;
     std::vector<uint32_t> tokens_host_;
@@ -135,6 +148,9 @@ private:
     int orphan_ = -1;                   // request whose admission threw
     bool forward_needs_drain_ = false;  // a reservation or forward was submitted and no completion barrier ran yet
     std::string poison_message_;
+    std::atomic<bool> any_cancelled_{false};
+    std::mutex cancel_mu_;
+    std::set<int> cancelled_;  // sticky: ids stay until the request's result is final
 };
 
 }  // namespace mk

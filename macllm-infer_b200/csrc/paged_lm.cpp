@@ -40,6 +40,7 @@ void PagedLm::validate_session(const LmSession& s) const {  // :3479-3492
 }
 
 void PagedLm::clear_session(LmSession& s) {  // :3804-3818
+    on_clear_session();
     int64_t old_len = s.table->logical_len();
     s.table->clear();
     if (old_len != 0 && s.table->logical_len() != 0) return;  // a reservation keeps the table locked
@@ -200,6 +201,7 @@ void FakeLm::inject_failure(int site, int64_t index) {
         case 1: fail_read_at_ = index; break;
         case 2: fail_reset_at_ = index; break;
         case 3: fail_drain_at_ = index; break;
+        case 4: fail_clear_at_ = clears_ + index; break;   // counted from now: admissions clear sessions too
         default: throw std::runtime_error("unknown failure site");
     }
 }
@@ -208,12 +210,21 @@ void FakeLm::device_synchronize() {
     if (drains_++ == fail_drain_at_) throw std::runtime_error("injected synchronize failure");
 }
 
+void FakeLm::on_clear_session() {
+    if (clears_++ == fail_clear_at_) throw std::runtime_error("injected session clearing failure");
+}
+
 void FakeLm::on_reset_session() {
     if (resets_++ == fail_reset_at_) throw std::runtime_error("injected admission failure");
 }
 
 void FakeLm::fetch_output(float* logits, uint32_t* tokens) {
     if (reads_++ == fail_read_at_) throw std::runtime_error("injected completion barrier failure");
+    if (barrier_cb_ != nullptr) {
+        void (*cb)(void*) = barrier_cb_;
+        barrier_cb_ = nullptr;
+        cb(barrier_user_);
+    }
     for (size_t i = 0; i < next_.size(); ++i) {
         if (tokens) tokens[i] = next_[i];
         if (logits) {

@@ -111,6 +111,7 @@ protected:
     virtual void fetch_output(float* logits, uint32_t* tokens) = 0;
     virtual void device_synchronize() {}
     virtual void on_reset_session() {}  // test hook: the fake model injects admission failures here
+    virtual void on_clear_session() {}  // test hook: the fake model injects session-clearing failures here
 
     LmRuntimeSpec spec_;
     std::shared_ptr<KvPool> pool_;
@@ -130,21 +131,28 @@ public:
     FakeLm(int vocab, int max_context, int block_tokens, int slab_blocks, int64_t capacity_tokens, int64_t prefix_capacity_tokens);
     // Fail the forward numbered `index` (0-based) with an exception, to test rollback.
     void fail_forward_at(int64_t index) { fail_at_ = index; }
-    // The same for the completion barrier (site 1), prompt admission (site 2) and the cleanup drain (site 3), like
+    // The same for the completion barrier (site 1), prompt admission (site 2), the cleanup drain (site 3) and the clearing
+    // of a session (site 4; panic_clear_session, src/engine.rs:5640-5682), like
     // fail_completion_barrier_at and friends of the reference's FakeModel (src/engine.rs:3107-3300).
     void inject_failure(int site, int64_t index);
     int64_t drains() const { return drains_; }
+    // Calls cb(user) once, inside the next completion barrier: the place where the reference's FakeModel flips
+    // cancel_on_completion_barrier (src/engine.rs:3143,3575-3583), i.e. "the client gave up while the forward ran".
+    void on_next_barrier(void (*cb)(void*), void* user) { barrier_cb_ = cb; barrier_user_ = user; }
 
 protected:
     void run_forward(const std::vector<LmLane>& lanes, KvReservation& r, uint32_t flags) override;
     void fetch_output(float* logits, uint32_t* tokens) override;
     void device_synchronize() override;
     void on_reset_session() override;
+    void on_clear_session() override;
 
 private:
     std::vector<uint32_t> next_;
     int64_t forwards_ = 0, fail_at_ = -1;
-    int64_t reads_ = 0, fail_read_at_ = -1, resets_ = 0, fail_reset_at_ = -1, drains_ = 0, fail_drain_at_ = -1;
+    void (*barrier_cb_)(void*) = nullptr;
+    void* barrier_user_ = nullptr;
+    int64_t reads_ = 0, fail_read_at_ = -1, resets_ = 0, fail_reset_at_ = -1, drains_ = 0, fail_drain_at_ = -1, clears_ = 0, fail_clear_at_ = -1;
 };
 
 }  // namespace mk

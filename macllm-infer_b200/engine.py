@@ -144,9 +144,15 @@ class Model:
         return cls(h)
 
     def inject_failure(self, site: str, index: int) -> None:
-        """Fake model only: make call number `index` at 'forward' | 'read_output' | 'admission' | 'synchronize' fail."""
-        sites = {"forward": 0, "read_output": 1, "admission": 2, "synchronize": 3}
+        """Fake model only: make call number `index` at 'forward' | 'read_output' | 'admission' | 'synchronize' fail;
+        'clear_session' counts from this call on."""
+        sites = {"forward": 0, "read_output": 1, "admission": 2, "synchronize": 3, "clear_session": 4}
         capi.check(capi.lib().mk_model_fake_inject(self._h, sites[site], index))
+
+    def on_next_barrier(self, fn) -> None:
+        """Fake model only: call `fn()` once inside the next completion barrier (while the engine waits for a forward)."""
+        self._barrier_cb = C.CFUNCTYPE(None, C.c_void_p)(lambda _user: fn())   # kept alive until it has run
+        capi.check(capi.lib().mk_model_fake_on_barrier(self._h, C.cast(self._barrier_cb, C.c_void_p), None))
 
     def spec(self) -> capi.RuntimeSpec:
         s = capi.RuntimeSpec()
@@ -252,6 +258,9 @@ class Model:
             pass
 
 
+_STATES = ("running", "done", "failed", "cancelled")
+
+
 class Engine:
     """The continuous-batching scheduler over one model."""
 
@@ -300,23 +309,28 @@ class Engine:
         capi.check(capi.lib().mk_engine_pending(self._h, C.byref(n)))
         return int(n.value)
 
+    def cancel(self, request_id: int) -> None:
+        """EngineTicket::cancel of the reference (src/engine.rs:1136-1145): sticky; the scheduler drops the request at its
+        next look at it. May be called from another thread while `step` runs."""
+        capi.check(capi.lib().mk_engine_cancel(self._h, request_id))
+
     def progress(self, request_id: int):
         """(generated tokens so far, state, prompt tokens served from the prefix cache) without copying the tokens."""
         n = C.c_int32(0)
         fin = C.c_int32()
         cached = C.c_int64()
         capi.check(capi.lib().mk_engine_result(self._h, request_id, None, C.byref(n), C.byref(fin), C.byref(cached)))
-        return int(n.value), ("running", "done", "failed")[fin.value], int(cached.value)
+        return int(n.value), _STATES[fin.value], int(cached.value)
 
     def result(self, request_id: int):
-        """Returns dict(tokens, state ('running' | 'done' | 'failed'), cached_tokens, message, kind)."""
+        """Returns dict(tokens, state ('running' | 'done' | 'failed' | 'cancelled'), cached_tokens, message, kind)."""
         count, _, _ = self.progress(request_id)
         toks = np.empty(max(count, 1), np.uint32)
         n = C.c_int32(len(toks))
         fin = C.c_int32()
         cached = C.c_int64()
         capi.check(capi.lib().mk_engine_result(self._h, request_id, toks.ctypes.data, C.byref(n), C.byref(fin), C.byref(cached)))
-        state = ("running", "done", "failed")[fin.value]
+        state = _STATES[fin.value]
         msg = capi.lib().mk_last_error().decode() if state == "failed" else ""
         kind = C.c_int32()
         capi.check(capi.lib().mk_engine_failure_kind(self._h, request_id, C.byref(kind)))

@@ -18,6 +18,8 @@ from __future__ import annotations
 import json
 import math
 import queue
+import select
+import socket
 import threading
 import time
 from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
@@ -158,6 +160,10 @@ class _Job:
         self.seen = 0
         self.t_submit = time.perf_counter()
         self.t_first = None
+        # set by the handler when its client is gone (EngineTicket's Drop, src/engine.rs:1141-1145): sticky; the worker passes
+        # it on to the engine, which drops the request at its next look at it
+        self.cancelled = threading.Event()
+        self.cancel_sent = False
 
 
 class CompletionServer:
@@ -187,11 +193,14 @@ class CompletionServer:
 
             def _json(self, status, obj):
                 data = json.dumps(obj, separators=(",", ":")).encode()
-                self.send_response(status)
-                self.send_header("Content-Type", "application/json")
-                self.send_header("Content-Length", str(len(data)))
-                self.end_headers()
-                self.wfile.write(data)
+                try:
+                    self.send_response(status)
+                    self.send_header("Content-Type", "application/json")
+                    self.send_header("Content-Length", str(len(data)))
+                    self.end_headers()
+                    self.wfile.write(data)
+                except (BrokenPipeError, ConnectionResetError):   # the client left before its answer
+                    self.close_connection = True
 
             def do_GET(self):
                 if self.path == "/healthz":
@@ -223,10 +232,35 @@ class CompletionServer:
                 else:
                     self._collect(job)
 
+            def _client_gone(self) -> bool:
+                """True once the peer has closed its side: a readable socket that yields no byte."""
+                try:
+                    readable, _, _ = select.select([self.connection], [], [], 0)
+                    return bool(readable) and self.connection.recv(1, socket.MSG_PEEK) == b""
+                except (OSError, ValueError):
+                    return True
+
+            def _next_event(self, job):
+                """The job's next event, or None when the client went away first (the request is then given up)."""
+                while True:
+                    now = time.monotonic()
+                    if now - getattr(self, "_last_peek", 0.0) >= 0.1:   # also while events keep coming (a collected response)
+                        self._last_peek = now
+                        if self._client_gone():
+                            job.cancelled.set()
+                            return None
+                    try:
+                        return job.events.get(timeout=0.1)
+                    except queue.Empty:
+                        pass
+
             def _collect(self, job):
                 content = ""
                 while True:
-                    ev = job.events.get()
+                    ev = self._next_event(job)
+                    if ev is None:
+                        self.close_connection = True
+                        return
                     if ev[0] == "token":
                         content += ev[3]
                     elif ev[0] == "finished":
@@ -254,7 +288,9 @@ class CompletionServer:
                 last = 0
                 try:
                     while True:
-                        ev = job.events.get()
+                        ev = self._next_event(job)
+                        if ev is None:
+                            break
                         if ev[0] == "token":
                             _, token_id, n_decoded, text = ev
                             if not (last < n_decoded <= job.settings["n_predict"]):
@@ -272,7 +308,7 @@ class CompletionServer:
                             send(_engine_failure(ev[1], ev[2]).body())
                             break
                 except (BrokenPipeError, ConnectionResetError):
-                    pass
+                    job.cancelled.set()
                 self.close_connection = True
 
         class Httpd(ThreadingHTTPServer):
@@ -371,6 +407,9 @@ class CompletionServer:
                 now = time.perf_counter()
                 for rid in list(active):
                     job = active[rid]
+                    if job.cancelled.is_set() and not job.cancel_sent:
+                        engine.cancel(rid)
+                        job.cancel_sent = True
                     n, state, cached = engine.progress(rid)
                     if n > job.seen:
                         toks = engine.result(rid)["tokens"]
@@ -390,6 +429,8 @@ class CompletionServer:
                     elif state == "failed":
                         r = engine.result(rid)
                         job.events.put(("failed", r["kind"], r["message"]))
+                        del active[rid]
+                    elif state == "cancelled":   # nobody is listening any more: no event
                         del active[rid]
                 if self._status not in ("poisoned",) and not active:
                     self._status = "ready"

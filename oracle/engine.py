@@ -163,6 +163,15 @@ class OracleEngine:
         self.next_id = self.next_batch = 0
         self.round_visits = self.round_budget = 0
         self.kv_shrinks = 0
+        self.cancelled: set[int] = set()   # EngineTicket::cancel, engine.rs:1136-1145: sticky
+        self.on_barrier = None             # test hook: called once after the next forward's completion barrier
+
+    def cancel(self, rid):
+        self.cancelled.add(rid)
+
+    def _finish_cancelled(self, rid):
+        if self.results[rid].state == "running":
+            self.results[rid].state = "cancelled"
 
     def submit(self, reqs, atomic_batch=False):
         if len(self.queue) + len(reqs) > self.queue_capacity:
@@ -187,6 +196,8 @@ class OracleEngine:
         self.results[rid].state, self.results[rid].message = "failed", msg
 
     def _admit(self, rid, r: Req):  # engine.rs:1654-1808
+        if rid in self.cancelled:  # skipped before preflight and model work, engine.rs:1671-1674
+            return self._finish_cancelled(rid)
         # prepare_request for token-id input, engine.rs:2976-3021
         if not r.prompt:
             return self._fail(rid, "raw token prompt must not be empty")
@@ -267,6 +278,9 @@ class OracleEngine:
             if token_budget == 0:
                 break
             s = self.active[index]
+            if s.rid in self.cancelled:  # flush_pending -> Abandoned, engine.rs:1409-1417,2024-2029
+                actions.append(dict(kind="remove"))
+                continue
             if s.delivering:
                 actions.append(dict(kind="remove"))
                 continue
@@ -285,6 +299,8 @@ class OracleEngine:
         for i, a in enumerate(actions):
             if a["kind"] == "remove":
                 self._reclaim(self.active[i])
+                if self.active[i].rid in self.cancelled:
+                    self._finish_cancelled(self.active[i].rid)
         candidates = [i for i, a in enumerate(actions) if a["kind"] == "preview"]
         reservation = None
         input_tokens = 0
@@ -325,12 +341,19 @@ class OracleEngine:
                 tick.append((s.rid, a["start"], a["n"]))
             logits = self.m.forward(lanes, reservation)
             self.trace.append(tick)
+            if self.on_barrier is not None:
+                hook, self.on_barrier = self.on_barrier, None
+                hook()
             for row, i in enumerate(fwd):  # complete_mixed_rows, engine.rs:2411-2523
                 a, s = actions[i], self.active[i]
                 nxt = a["start"] + a["n"]
                 if s.req.publish_prompt_prefix and a["was_prefill"] and 0 < nxt <= s.prompt_tokens:
                     self.m.publish_prompt_prefix(s.session, s.history[:nxt])  # generation.rs:505-509
                 a["kind"], a["finished"] = "complete", False
+                if s.rid in self.cancelled:  # generation.rs:1201-1204: the row is consumed, nothing is sampled
+                    s.phase, a["finished"] = "finished", True
+                    self._finish_cancelled(s.rid)
+                    continue
                 if not a["ready"]:
                     s.phase, s.cursor = "prefill", nxt
                     continue

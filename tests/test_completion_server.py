@@ -265,3 +265,71 @@ def test_a_worker_exception_fails_everything_in_flight_and_the_server_keeps_answ
         assert st == 503 and json.loads(b)["worker"] == "poisoned"
     finally:
         s.stop()
+
+
+class _SlowEngine:
+    """The engine with a pause in every tick, so that a client can leave while its request runs; records the cancellations."""
+
+    def __init__(self, inner, pause_s):
+        self._inner, self._pause_s, self.cancelled = inner, pause_s, []
+
+    def step(self):
+        import time
+        time.sleep(self._pause_s)
+        return self._inner.step()
+
+    def cancel(self, rid):
+        self.cancelled.append(rid)
+        return self._inner.cancel(rid)
+
+    def __getattr__(self, name):
+        return getattr(self._inner, name)
+
+
+@pytest.mark.parametrize("stream", [True, False])
+def test_a_client_that_leaves_cancels_its_request_and_the_peer_finishes(mk, srv_mod, stream):
+    """Dropping the ticket sets the sticky cancellation flag (src/engine.rs:1141-1145,4397-4411): the request of a client that
+    closed its connection stops taking ticks, its pages return to the pool, and a peer in the same batch is served in full."""
+    import socket
+    import time
+    eng = importlib.import_module("macllm_infer_b200.engine")
+    made = {}
+
+    def factory():
+        model = eng.Model.fake(vocab=64, max_context=4096, kv_capacity_tokens=16384)
+        made["model"] = model
+        made["engine"] = _SlowEngine(eng.Engine(model, max_active_sequences=4, scheduler_token_budget=64, prefill_token_quantum=32,
+                                                queue_capacity=8), 0.004)
+        return made["engine"], model
+    s = srv_mod.CompletionServer(factory, metadata=dict(served_model="test-model", device="cpu", dtype="f32")).start()
+    try:
+        payload = json.dumps(body(srv_mod, n_predict=2000, stream=stream)).encode()
+        sock = socket.create_connection(("127.0.0.1", s.port), timeout=30)
+        sock.sendall(b"POST /completion HTTP/1.1\r\nHost: x\r\nContent-Type: application/json\r\nContent-Length: " +
+                     str(len(payload)).encode() + b"\r\n\r\n" + payload)
+        peer = {}
+        t = threading.Thread(target=lambda: peer.update(r=call(s, "POST", "/completion", body(srv_mod, prompt=[9, 8], n_predict=40))))
+        t.start()
+        if stream:
+            got = b""
+            while b"data: " not in got:              # the first fragments arrive
+                chunk = sock.recv(4096)
+                assert chunk, got
+                got += chunk
+        else:
+            time.sleep(0.1)
+        sock.close()
+        t.join(timeout=30)
+        assert peer["r"][0] == 200 and json.loads(peer["r"][2])["tokens_predicted"] == 40
+        deadline = time.time() + 20
+        while time.time() < deadline and made["engine"].pending() > 0:
+            time.sleep(0.02)
+        e = made["engine"]
+        assert e.cancelled == [0]
+        r = e.result(0)
+        assert r["state"] == "cancelled" and 0 < len(r["tokens"]) < 2000
+        assert e.pending() == 0 and made["model"].pool_stats()["live_blocks"] == 0
+        st, _, b = call(s, "GET", "/healthz")
+        assert st == 200 and json.loads(b)["worker"] == "ready"
+    finally:
+        s.stop()

@@ -386,3 +386,219 @@ def test_invalid_sampling_parameters_fail_the_request_with_the_reference_wording
     (rid,) = pe.submit([eng.Request([1, 2], 2, top_p=0.0)])
     pe.run()
     assert pe.result(rid)["message"] == "invalid sampling parameters: top_p must be finite and in (0, 1]"
+
+
+# ---- cancellation (EngineTicket::cancel, src/engine.rs:1136-1145; tests at src/engine.rs:4931-4966,5016-5131,5284-5346) --------
+
+def cancel_both(pe, oe_, rid):
+    pe.cancel(rid)
+    oe_.cancel(rid)
+
+
+def test_cancelled_queued_request_is_skipped_before_preflight_and_model_work(eng):
+    """engine.rs:5016-5058: one active slot, budget 1, quantum 1; "a a a a", "b b" and "y" queue up. After the first tick
+    the queued second request and the running first are cancelled: the first leaves without another forward, the second
+    never gets validated, a session or a forward, and the third runs once the slot is free."""
+    (pm, pe), (om, oe_) = both(eng, dict(vocab=32), dict(max_active_sequences=1, scheduler_token_budget=1, prefill_token_quantum=1))
+    submit_both(eng, pe, oe_, [[1, 1, 1, 1], [2, 2], [4]], [1, 1, 1])
+    for e in (pe, oe_):
+        assert e.step() == 1
+    cancel_both(pe, oe_, 1)
+    cancel_both(pe, oe_, 0)
+    for e in (pe, oe_):
+        assert e.step() == 0          # the first request leaves; nothing is forwarded
+    assert pm.pool_stats()["live_blocks"] == 0 and om.pool.stats()["live_blocks"] == 0
+    for e in (pe, oe_):
+        e.step()                      # the cancelled queued request is popped and skipped; the third is admitted
+        e.run()
+    trace = pe.trace()
+    assert trace == [[tuple(l) for l in t] for t in oe_.trace]
+    assert not any(l[0] == 1 for t in trace for l in t)
+    assert any(l[0] == 2 for t in trace for l in t)
+    assert [pe.result(i)["state"] for i in range(3)] == ["cancelled", "cancelled", "done"]
+    assert [oe_.results[i].state for i in range(3)] == ["cancelled", "cancelled", "done"]
+    assert pe.result(1)["message"] == "" and pe.result(1)["kind"] == "none"    # no preflight verdict of any kind
+    assert pe.stats()["cancelled_requests"] == 2 and pe.stats()["failed_requests"] == 0
+
+
+def test_a_cancelled_request_is_not_validated(eng):
+    """engine.rs:1671-1674 comes before prepare_request: a cancelled request with an invalid prompt is skipped, not refused."""
+    pm, pe = product_engine(eng, dict(vocab=32), dict(max_active_sequences=1, scheduler_token_budget=4, prefill_token_quantum=4))
+    ids = pe.submit([eng.Request([1, 2], 4), eng.Request([99], 1)])
+    pe.cancel(ids[1])
+    pe.run()
+    assert pe.result(ids[1])["state"] == "cancelled"
+    assert pe.result(ids[0])["state"] == "done"
+    with pytest.raises(RuntimeError, match="unknown request id"):
+        pe.cancel(7)
+
+
+def test_active_limit_delays_admission_until_a_cancelled_slot_is_reclaimed(eng):
+    """engine.rs:5059-5131: two active slots, three requests. The third waits; cancelling the first frees its session (cleared
+    once), the third is admitted on the next tick and reuses that slot."""
+    ekw = dict(max_active_sequences=2, scheduler_token_budget=4, prefill_token_quantum=2)
+    (pm, pe), (om, oe_) = both(eng, dict(vocab=32), ekw)
+    submit_both(eng, pe, oe_, [[1, 1, 1, 1], [2, 2, 2, 2], [4, 2]], [3, 3, 1])
+    for e in (pe, oe_):
+        e.step()
+        e.step()
+    assert pe.pending() == 3 and not any(l[0] == 2 for t in pe.trace() for l in t)
+    cancel_both(pe, oe_, 0)
+    for e in (pe, oe_):
+        e.step()
+    # the tick that sees the cancellation forwards only the peer and returns the pages before that forward
+    assert [l[0] for l in pe.trace()[-1]] == [1]
+    assert pe.result(0)["state"] == "cancelled" and oe_.results[0].state == "cancelled"
+    assert pm.pool_stats() == om.pool.stats()
+    for e in (pe, oe_):
+        e.run()
+    assert pe.trace() == [[tuple(l) for l in t] for t in oe_.trace]
+    assert pe.result(2)["state"] == "done" and list(pe.result(2)["tokens"]) == oe_.results[2].tokens
+    assert pe.result(1)["state"] == "done" and len(pe.result(1)["tokens"]) == 3
+
+
+def test_cancellation_after_the_shared_completion_barrier_drops_only_its_lane(eng):
+    """engine.rs:4931-4966: two one-token requests share a forward; the first is cancelled while the forward runs (the fake
+    model flips the flag inside the completion barrier). Both lanes were in the packed forward, the cancelled one gets no
+    token, the peer gets its own row's token, both sessions are back, one barrier, no cleanup drain."""
+    (pm, pe), (om, oe_) = both(eng, dict(vocab=32), dict(max_active_sequences=2, scheduler_token_budget=8, prefill_token_quantum=4))
+    submit_both(eng, pe, oe_, [[1], [2]], [1, 1])
+    pm.on_next_barrier(lambda: pe.cancel(0))
+    oe_.on_barrier = lambda: oe_.cancel(0)
+    for e in (pe, oe_):
+        assert e.step() == 2
+    assert pe.trace() == [[(0, 0, 1), (1, 0, 1)]] == [[tuple(l) for l in t] for t in oe_.trace]
+    assert pe.result(0)["state"] == "cancelled" and len(pe.result(0)["tokens"]) == 0
+    assert oe_.results[0].state == "cancelled" and oe_.results[0].tokens == []
+    assert pe.result(1)["state"] == "done" and list(pe.result(1)["tokens"]) == oe_.results[1].tokens
+    assert list(pe.result(1)["tokens"]) == [(31 * 2 + 3) % 32]      # row 1 of the forward, not row 0
+    assert pe.pending() == 0 and oe_.pending() == 0
+    assert pe.stats()["cleanup_drains"] == 0 and pe.stats()["ticks"] == 1
+    assert pm.pool_stats()["live_blocks"] == 0
+
+
+def test_cancelled_prefix_slot_is_removed_before_the_peers_rows_are_mapped(eng):
+    """engine.rs:5284-5346: three active one-token prompts, the first cancelled before the tick: the packed forward holds the
+    two peers at rows 0 and 1 with their own tokens, and the cancelled slot's pages were returned before that forward."""
+    mkw = dict(vocab=32, block_tokens=16, slab_blocks=2, kv_capacity_tokens=32)   # two blocks: three lanes would not fit
+    ekw = dict(max_active_sequences=3, scheduler_token_budget=3, prefill_token_quantum=1)
+    (pm, pe), (om, oe_) = both(eng, mkw, ekw)
+    submit_both(eng, pe, oe_, [[1, 1], [2], [3]], [2, 1, 1])
+    # one tick with a budget that reaches only the first slot would not do here; cancel before anything ran
+    cancel_both(pe, oe_, 0)
+    for e in (pe, oe_):
+        assert e.step() == 2
+    assert pe.trace() == [[(1, 0, 1), (2, 0, 1)]] == [[tuple(l) for l in t] for t in oe_.trace]
+    assert pe.stats()["kv_shrinks"] == 0 and oe_.kv_shrinks == 0
+    assert list(pe.result(1)["tokens"]) == [(31 * 2 + 3) % 32] and list(pe.result(2)["tokens"]) == [(31 * 3 + 3) % 32]
+    assert pe.result(0)["state"] == "cancelled"
+    assert pe.stats()["cleanup_drains"] == 0
+
+
+def test_cancellation_between_quanta_skips_the_next_decode(eng):
+    """generation.rs:2476-2516: a sequence cancelled after its first token never runs the next decode; the tokens it had stay
+    readable. generation.rs:2289-2311: one cancelled before its first prefill chunk never reaches the model."""
+    (pm, pe), (om, oe_) = both(eng, dict(vocab=32), dict(max_active_sequences=2, scheduler_token_budget=8, prefill_token_quantum=4))
+    submit_both(eng, pe, oe_, [[1, 2]], [4])
+    for e in (pe, oe_):
+        e.step()
+    assert len(pe.result(0)["tokens"]) == 1
+    cancel_both(pe, oe_, 0)
+    for e in (pe, oe_):
+        assert e.step() == 0
+        assert e.pending() == 0
+    assert pe.stats()["ticks"] == 1 and pe.stats()["decode_tokens"] == 0
+    assert pe.result(0)["state"] == "cancelled" and list(pe.result(0)["tokens"]) == oe_.results[0].tokens
+    submit_both(eng, pe, oe_, [[3, 4, 5]], [2])
+    cancel_both(pe, oe_, 1)
+    for e in (pe, oe_):
+        assert e.step() == 0
+    assert pe.stats()["ticks"] == 1 and pe.stats()["prefill_tokens"] == 2
+
+
+def test_cancelling_a_finished_request_changes_nothing(eng):
+    pm, pe = product_engine(eng, dict(vocab=32), dict(max_active_sequences=1, scheduler_token_budget=4, prefill_token_quantum=4))
+    rid = pe.submit([eng.Request([1, 2], 2)])[0]
+    pe.run()
+    before = pe.result(rid)
+    pe.cancel(rid)
+    pe.step()
+    after = pe.result(rid)
+    assert after["state"] == "done" and list(after["tokens"]) == list(before["tokens"])
+    assert pe.stats()["cancelled_requests"] == 0
+
+
+def test_a_cancelled_member_does_not_hold_back_its_atomic_batch(eng):
+    """engine.rs:1886-1936 with 1671-1674: the batch is admitted as a whole; the cancelled member is skipped at its own admission."""
+    (pm, pe), (om, oe_) = both(eng, dict(vocab=32), dict(max_active_sequences=3, scheduler_token_budget=8, prefill_token_quantum=4))
+    submit_both(eng, pe, oe_, [[1], [2], [3]], [2, 2, 2], atomic=True)
+    cancel_both(pe, oe_, 1)
+    for e in (pe, oe_):
+        e.run()
+    assert pe.trace() == [[tuple(l) for l in t] for t in oe_.trace]
+    assert [pe.result(i)["state"] for i in range(3)] == ["done", "cancelled", "done"]
+    assert [l[0] for l in pe.trace()[0]] == [0, 2]
+
+
+def test_a_failed_session_clearing_keeps_every_slot_for_the_fatal_fan_out(eng):
+    """engine.rs:5640-5682: the first of two active requests is cancelled and the clearing of its session fails: nothing was
+    forwarded, no barrier and no drain ran, and the fatal message reaches the cancelled request as well as its peer."""
+    pm, pe = product_engine(eng, dict(vocab=32), dict(max_active_sequences=2, scheduler_token_budget=8, prefill_token_quantum=4))
+    pe.submit([eng.Request([1] * 8, 1), eng.Request([2] * 8, 1)])
+    assert pe.step() == 2                     # both are active, half of each prompt is in
+    pe.cancel(0)
+    pm.inject_failure("clear_session", 0)     # the next clearing is the cancelled slot's
+    assert pe.step() == 0
+    assert pe.status() == "poisoned"
+    assert len(pe.trace()) == 1 and pe.stats()["ticks"] == 1 and pe.stats()["cleanup_drains"] == 0
+    for rid in (0, 1):
+        r = pe.result(rid)
+        assert r["state"] == "failed" and r["kind"] == "fatal"
+        assert r["message"] == "inference worker failed: injected session clearing failure"
+    with pytest.raises(RuntimeError, match=r"inference worker is unavailable \(Poisoned\)"):
+        pe.submit([eng.Request([1], 1)])
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_randomised_differential_with_cancellations(eng, seed):
+    """Requests are given up at random moments - queued, in the middle of their prefill, between decodes, after they ended:
+    schedules, tokens, states, pool statistics and prefix-cache counters agree with the oracle tick by tick."""
+    rng = random.Random(1000 + seed)
+    bt = rng.choice([4, 16])
+    mkw = dict(vocab=64, max_context=2048, block_tokens=bt, slab_blocks=rng.choice([2, 8]),
+               kv_capacity_tokens=rng.choice([40 * bt, 200 * bt]), prefix_capacity_tokens=rng.choice([0, 12 * bt, 64 * bt]))
+    ekw = dict(max_active_sequences=rng.choice([2, 4, 7]), scheduler_token_budget=rng.choice([8, 48, 256]),
+               prefill_token_quantum=rng.choice([3, 16, 64]), queue_capacity=64)
+    ekw["prefill_token_quantum"] = min(ekw["prefill_token_quantum"], ekw["scheduler_token_budget"])
+    (pm, pe), (om, oe_) = both(eng, mkw, ekw)
+    stems = [[rng.randrange(3, 64) for _ in range(rng.randint(bt, 6 * bt))] for _ in range(3)]
+    submitted = 0
+    for wave in range(4):
+        prompts, max_new = [], []
+        for _ in range(rng.randint(2, 6)):
+            stem = rng.choice(stems)
+            prompts.append(stem[: rng.randint(1, len(stem))] + [rng.randrange(3, 64) for _ in range(rng.randint(1, 2 * bt))])
+            max_new.append(rng.randint(1, 12))
+        submit_both(eng, pe, oe_, prompts, max_new, atomic=rng.random() < 0.3 and len(prompts) <= ekw["max_active_sequences"])
+        submitted += len(prompts)
+        for _ in range(rng.randint(1, 30)):
+            if rng.random() < 0.25:
+                cancel_both(pe, oe_, rng.randrange(submitted))
+            lp, lo = pe.step(), oe_.step()
+            assert lp == lo
+            assert pm.pool_stats() == om.pool.stats()
+            if mkw["prefix_capacity_tokens"]:
+                assert pm.prefix_diagnostics() == om.prefix.stats()
+    pe.run()
+    oe_.run()
+    assert pe.trace() == [[tuple(l) for l in t] for t in oe_.trace]
+    states = set()
+    for rid in range(submitted):
+        rp, ro = pe.result(rid), oe_.results[rid]
+        assert rp["state"] == ro.state
+        assert list(rp["tokens"]) == ro.tokens
+        states.add(rp["state"])
+    assert pm.pool_stats() == om.pool.stats()
+    if not mkw["prefix_capacity_tokens"]:
+        assert pm.pool_stats()["live_blocks"] == 0       # every cancelled request gave its pages back
+    assert "cancelled" in states
