@@ -314,7 +314,42 @@ typedef struct mk_tick_lane {
     int32_t request_id;
     int32_t start_pos;
     int32_t n_tokens;
+    int32_t phase;   /* MK_FWD_* of the lane (BenchmarkForwardLane::phase, src/engine.rs:441-450); never MK_FWD_MIXED */
 } mk_tick_lane;
+
+/* BenchmarkForwardKind (src/engine.rs:430-439; lanes classified as in src/generation.rs:757-766): a prefill chunk that ends
+ * inside the prompt, the chunk that ends the prompt and samples, a decode step; a packed forward whose lanes differ is
+ * MIXED and its whole time goes to that bucket. */
+enum { MK_FWD_SUFFIX_PREFILL = 0, MK_FWD_FIRST_TOKEN = 1, MK_FWD_DECODE = 2, MK_FWD_MIXED = 3 };
+
+/* BenchmarkPackedForwardRecord (src/engine.rs:452-460); model_ms is the device time of the forward. */
+typedef struct mk_tick_info {
+    int32_t kind;
+    int32_t lane_count;
+    int32_t input_tokens;
+    int32_t reserved_;
+    double model_ms;
+} mk_tick_info;
+
+/* EngineBatchTrace (src/engine.rs:462-484) of one atomic batch: member counts, the number of active sequences when its
+ * admission finished, and the device time of every packed forward that carried at least one member, by kind.  `complete`
+ * is EngineBatchTraceHandle::try_read's condition (src/engine.rs:533-543): admission ran and every member has ended
+ * (done, failed, rejected at preflight or cancelled).  The host-side wall-clock splits of the reference's trace
+ * (queue_wait, admission_exclusive, prefix_lookup_attach_time, diagnostics_time) are the caller's to take. */
+typedef struct mk_batch_trace {
+    int32_t expected_members;
+    int32_t admitted_members;
+    int32_t terminal_members;
+    int32_t rejected_members;
+    int32_t admission_active_sequences;
+    int32_t packed_forwards;
+    int32_t complete;
+    int32_t reserved_;
+    double suffix_prefill_ms;
+    double first_token_ms;
+    double decode_ms;
+    double mixed_ms;
+} mk_batch_trace;
 
 typedef struct mk_engine_stats {
     int64_t ticks;
@@ -327,6 +362,10 @@ typedef struct mk_engine_stats {
     int64_t cleanup_drains;      /* mk_synchronize calls made while poisoning (src/engine.rs:2723-2736) */
     int64_t device_sampled;      /* stochastic tokens picked by the device sampler */
     int64_t cancelled_requests;  /* requests that ended by mk_engine_cancel */
+    double suffix_prefill_ms;    /* device time by whole-forward kind: each forward is in exactly one bucket */
+    double first_token_ms;
+    double decode_ms;
+    double mixed_ms;
 } mk_engine_stats;
 
 int32_t mk_engine_new(mk_model* m, const mk_engine_config* cfg, mk_engine** out);
@@ -347,6 +386,12 @@ int32_t mk_engine_logits(mk_engine* e, int32_t request_id, float* out, int32_t* 
 /* Lanes of tick `tick` (0-based); capacity in *n. */
 int32_t mk_engine_trace(mk_engine* e, int64_t tick, mk_tick_lane* lanes, int32_t* n);
 int32_t mk_engine_stats_query(mk_engine* e, mk_engine_stats* out);
+/* Kind, geometry and device time of tick `tick` (0-based). */
+int32_t mk_engine_tick_info(mk_engine* e, int64_t tick, mk_tick_info* out);
+/* The trace of the atomic batch that `member_request_id` was submitted in (EngineBatchSubmission::benchmark_trace,
+ * src/engine.rs:1037-1053).  forward_ticks (optional, capacity in *n_forward_ticks, count out) receives the tick numbers
+ * of its packed forwards.  Fails for a request that was not part of an atomic batch. */
+int32_t mk_engine_batch_trace(mk_engine* e, int32_t member_request_id, mk_batch_trace* out, int64_t* forward_ticks, int32_t* n_forward_ticks);
 /* EngineStatus (src/engine.rs:281-288): 1 Ready, 2 Busy, 3 Poisoned.  An error that escapes a tick (a failed forward, a
  * failed completion barrier, a broken scheduler invariant) poisons the engine like ServingScheduler::run / poison
  * (src/engine.rs:1577-1647,2719-2770): what was submitted is drained once with mk_synchronize, every active, pending

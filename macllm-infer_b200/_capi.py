@@ -87,13 +87,26 @@ class Request(C.Structure):
 
 
 class TickLane(C.Structure):
-    _fields_ = [("request_id", C.c_int32), ("start_pos", C.c_int32), ("n_tokens", C.c_int32)]
+    _fields_ = [("request_id", C.c_int32), ("start_pos", C.c_int32), ("n_tokens", C.c_int32), ("phase", C.c_int32)]
+
+
+class TickInfo(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("lane_count", C.c_int32), ("input_tokens", C.c_int32), ("reserved_", C.c_int32),
+                ("model_ms", C.c_double)]
+
+
+class BatchTrace(C.Structure):
+    _fields_ = [("expected_members", C.c_int32), ("admitted_members", C.c_int32), ("terminal_members", C.c_int32),
+                ("rejected_members", C.c_int32), ("admission_active_sequences", C.c_int32), ("packed_forwards", C.c_int32),
+                ("complete", C.c_int32), ("reserved_", C.c_int32), ("suffix_prefill_ms", C.c_double), ("first_token_ms", C.c_double),
+                ("decode_ms", C.c_double), ("mixed_ms", C.c_double)]
 
 
 class EngineStats(C.Structure):
     _fields_ = [("ticks", C.c_int64), ("prefill_tokens", C.c_int64), ("decode_tokens", C.c_int64),
                 ("completed_requests", C.c_int64), ("failed_requests", C.c_int64), ("kv_shrinks", C.c_int64),
-                ("device_ms", C.c_double), ("cleanup_drains", C.c_int64), ("device_sampled", C.c_int64), ("cancelled_requests", C.c_int64)]
+                ("device_ms", C.c_double), ("cleanup_drains", C.c_int64), ("device_sampled", C.c_int64), ("cancelled_requests", C.c_int64),
+                ("suffix_prefill_ms", C.c_double), ("first_token_ms", C.c_double), ("decode_ms", C.c_double), ("mixed_ms", C.c_double)]
 
 
 class LaneSampling(C.Structure):
@@ -169,6 +182,8 @@ SIGNATURES = {
     "mk_engine_status": (_i32, [P, C.POINTER(_i32)]),
     "mk_engine_failure_kind": (_i32, [P, _i32, C.POINTER(_i32)]),
     "mk_engine_cancel": (_i32, [P, _i32]),
+    "mk_engine_tick_info": (_i32, [P, _i64, C.POINTER(TickInfo)]),
+    "mk_engine_batch_trace": (_i32, [P, _i32, C.POINTER(BatchTrace), C.POINTER(_i64), C.POINTER(_i32)]),
     "mk_kvpool_new": (_i32, [_i32, _i32, _i64, C.POINTER(P)]),
     "mk_kvpool_free": (_i32, [P]),
     "mk_kvpool_stats": (_i32, [P, C.POINTER(PoolStats)]),

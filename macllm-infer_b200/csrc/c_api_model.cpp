@@ -462,9 +462,45 @@ int32_t mk_engine_trace(mk_engine* e, int64_t tick, mk_tick_lane* lanes, int32_t
         const auto& t = tr[(size_t)tick];
         if (lanes != nullptr) {
             if ((int32_t)t.size() > *n) throw std::runtime_error("trace buffer is too small");
-            for (size_t i = 0; i < t.size(); ++i) lanes[i] = mk_tick_lane{t[i].request_id, t[i].start_pos, t[i].n_tokens};
+            for (size_t i = 0; i < t.size(); ++i) lanes[i] = mk_tick_lane{t[i].request_id, t[i].start_pos, t[i].n_tokens, t[i].phase};
         }
         *n = (int32_t)t.size();
+    });
+}
+
+int32_t mk_engine_tick_info(mk_engine* e, int64_t tick, mk_tick_info* out) {
+    return guarded([&] {
+        const TickInfo& t = e->e->tick_info(tick);
+        out->kind = (int32_t)t.kind;
+        out->lane_count = t.lane_count;
+        out->input_tokens = t.input_tokens;
+        out->reserved_ = 0;
+        out->model_ms = t.model_ms;
+    });
+}
+
+int32_t mk_engine_batch_trace(mk_engine* e, int32_t member_request_id, mk_batch_trace* out, int64_t* forward_ticks, int32_t* n_forward_ticks) {
+    return guarded([&] {
+        int terminal = 0;
+        const BatchTrace& b = e->e->batch_trace(member_request_id, &terminal);
+        out->expected_members = (int32_t)b.members.size();
+        out->admitted_members = b.admitted_members;
+        out->terminal_members = terminal;
+        out->rejected_members = b.rejected_members;
+        out->admission_active_sequences = b.admission_active_sequences;
+        out->packed_forwards = (int32_t)b.packed_forwards.size();
+        out->complete = b.admission_complete && terminal == (int)b.members.size();
+        out->reserved_ = 0;
+        out->suffix_prefill_ms = b.suffix_prefill_ms;
+        out->first_token_ms = b.first_token_ms;
+        out->decode_ms = b.decode_ms;
+        out->mixed_ms = b.mixed_ms;
+        if (forward_ticks != nullptr) {
+            if (n_forward_ticks == nullptr || *n_forward_ticks < (int32_t)b.packed_forwards.size())
+                throw std::runtime_error("forward tick buffer is too small");
+            for (size_t i = 0; i < b.packed_forwards.size(); ++i) forward_ticks[i] = b.packed_forwards[i];
+        }
+        if (n_forward_ticks != nullptr) *n_forward_ticks = (int32_t)b.packed_forwards.size();
     });
 }
 
@@ -481,6 +517,10 @@ int32_t mk_engine_stats_query(mk_engine* e, mk_engine_stats* out) {
         out->cleanup_drains = s.cleanup_drains;
         out->device_sampled = s.device_sampled;
         out->cancelled_requests = s.cancelled;
+        out->suffix_prefill_ms = s.suffix_prefill_ms;
+        out->first_token_ms = s.first_token_ms;
+        out->decode_ms = s.decode_ms;
+        out->mixed_ms = s.mixed_ms;
     });
 }
 

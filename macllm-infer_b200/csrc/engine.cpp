@@ -32,6 +32,7 @@ std::vector<int> Engine::submit(const std::vector<EngineRequest>& reqs, bool ato
         throw std::runtime_error("atomic batch exceeds the active sequence limit");  // engine.rs:976-1053
     std::vector<int> ids;
     int batch = atomic_batch ? next_batch_++ : -1;
+    if (atomic_batch) batches_.emplace_back();
     for (const EngineRequest& r : reqs) {
         Job j;
         j.id = next_id_++;
@@ -39,6 +40,10 @@ std::vector<int> Engine::submit(const std::vector<EngineRequest>& reqs, bool ato
         j.batch = batch;
         j.batch_size = atomic_batch ? (int)reqs.size() : 0;
         results_[j.id] = EngineResult{};
+        if (atomic_batch) {
+            batches_[(size_t)batch].members.push_back(j.id);
+            batch_of_request_[j.id] = batch;
+        }
         ids.push_back(j.id);
         queue_.push_back(std::move(j));
     }
@@ -49,6 +54,21 @@ const EngineResult& Engine::result(int id) const {
     auto it = results_.find(id);
     if (it == results_.end()) throw std::runtime_error("unknown request id " + std::to_string(id));
     return it->second;
+}
+
+const TickInfo& Engine::tick_info(int64_t tick) const {
+    if (tick < 0 || tick >= (int64_t)tick_info_.size()) throw std::runtime_error("tick index out of range");
+    return tick_info_[(size_t)tick];
+}
+
+const BatchTrace& Engine::batch_trace(int member_id, int* terminal) const {
+    auto it = batch_of_request_.find(member_id);
+    if (it == batch_of_request_.end()) throw std::runtime_error("request " + std::to_string(member_id) + " was not submitted in an atomic batch");
+    const BatchTrace& b = batches_[(size_t)it->second];
+    int ended = 0;
+    for (int id : b.members) ended += results_.at(id).state != FinishState::Running;
+    if (terminal != nullptr) *terminal = ended;
+    return b;
 }
 
 void Engine::fail_request(int id, const std::string& message, FailureKind kind) {
@@ -114,6 +134,11 @@ void Engine::admit(Job job) {  // admit_with_diagnostic_refresh, engine.rs:1654-
     // taken, no prefix lookup (engine.rs:1671-1674,1715-1718)
     if (is_cancelled(job.id)) return finish_cancelled(job.id);
     const EngineRequest& rq = job.req;
+    // reject_preflight (engine.rs:3027-3040): the request fails alone; a traced batch counts it as a rejected member
+    auto fail_request = [&](int id, const std::string& message, FailureKind kind = FailureKind::InvalidRequest) {
+        this->fail_request(id, message, kind);
+        if (job.batch >= 0) ++batches_[(size_t)job.batch].rejected_members;
+    };
     const LmRuntimeSpec& spec = model_.spec();
     // prepare_request for EngineInput::TokenIds (engine.rs:2976-3021): empty prompt, vocabulary, context - in that order,
     // with the reference's wording (the context message leads with the phrase clients recognise an overflow by)
@@ -142,8 +167,11 @@ void Engine::admit(Job job) {  // admit_with_diagnostic_refresh, engine.rs:1654-
         KvPoolStats st = model_.pool_stats();
         int64_t max_cached = rq.max_new_tokens == 0 ? 0 : (int64_t)rq.prompt.size() + rq.max_new_tokens - 1;
         if (max_cached > st.max_blocks * st.block_tokens)
-            return fail_request(job.id, "request requires up to " + std::to_string(max_cached) +
-                                            " cached tokens, exceeding the configured shared KV capacity");
+            return fail_request(job.id,
+                                "request requires up to " + std::to_string(max_cached) +
+                                    " cached tokens, exceeding the configured shared KV capacity of " + std::to_string(st.max_blocks) +
+                                    " blocks \xc3\x97 " + std::to_string(st.block_tokens) + " tokens",
+                                FailureKind::ResourceExhausted);
     }
     if (sessions_.empty()) throw std::runtime_error("active slot has no reusable inference session");
     auto seq = std::make_unique<Sequence>();
@@ -166,7 +194,9 @@ void Engine::admit(Job job) {  // admit_with_diagnostic_refresh, engine.rs:1654-
         throw;
     }
     seq->cursor = (int)cached;
+    seq->batch = job.batch;
     results_[job.id].cached_tokens = cached;
+    if (job.batch >= 0) ++batches_[(size_t)job.batch].admitted_members;  // record_admitted, engine.rs:1800-1803
     active_.push_back(std::move(seq));
 }
 
@@ -176,7 +206,11 @@ bool Engine::admit_pending_atomic() {  // engine.rs:1886-1936
     if ((int)pending_atomic_.size() > available) return false;
     std::vector<Job> batch = std::move(pending_atomic_);
     pending_atomic_.clear();
+    const int batch_id = batch.front().batch;
     for (Job& j : batch) admit(std::move(j));
+    BatchTrace& bt = batches_[(size_t)batch_id];  // finish_admission, engine.rs:1926-1934
+    bt.admission_active_sequences = (int)active_.size();
+    bt.admission_complete = true;
     return true;
 }
 
@@ -373,7 +407,8 @@ int Engine::drive_once() {  // engine.rs:1938-1964
             Sequence& s = *active_[(size_t)i];
             const uint32_t* ids = v.was_prefill ? s.history.data() + v.start_pos : &s.decode_token;
             lanes.push_back(LmLane{s.session.get(), ids, v.n_tokens, v.start_pos});
-            tick.push_back(TickLaneTrace{s.id, v.start_pos, v.n_tokens});
+            const ForwardKind phase = !v.was_prefill ? ForwardKind::Decode : (v.ready_to_sample ? ForwardKind::FirstToken : ForwardKind::SuffixPrefill);
+            tick.push_back(TickLaneTrace{s.id, v.start_pos, v.n_tokens, (int32_t)phase});
             const EngineRequest& rq = s.req;
             if (v.ready_to_sample && (std::fabs(rq.repetition_penalty - 1.f) >= 1.1920929e-07f || rq.presence_penalty != 0.f ||
                                       rq.frequency_penalty != 0.f || !model_.device_sampling_covers(rq.temperature, rq.top_k)))
@@ -415,6 +450,35 @@ int Engine::drive_once() {  // engine.rs:1938-1964
             model_.read_output(logits_host_.data(), nullptr);
         }
         stats_.device_ms += model_.last_forward_ms();
+        {   // collect_pending_benchmark_forwards + record_packed_forward (engine.rs:2306-2375,2394-2405,601-619)
+            TickInfo info;
+            info.kind = (ForwardKind)tick.front().phase;
+            for (const TickLaneTrace& l : tick)
+                if (l.phase != tick.front().phase) info.kind = ForwardKind::Mixed;
+            info.lane_count = lane_count;
+            info.input_tokens = input_tokens;
+            info.model_ms = model_.last_forward_ms();
+            auto bucket = [&](double& suffix, double& first, double& decode, double& mixed) -> double& {
+                switch (info.kind) {
+                    case ForwardKind::SuffixPrefill: return suffix;
+                    case ForwardKind::FirstToken: return first;
+                    case ForwardKind::Decode: return decode;
+                    default: return mixed;
+                }
+            };
+            bucket(stats_.suffix_prefill_ms, stats_.first_token_ms, stats_.decode_ms, stats_.mixed_ms) += info.model_ms;
+            std::vector<int> seen;  // every traced batch with a member in this forward records the whole forward once
+            for (int i = 0; i < visits; ++i) {
+                if (actions[(size_t)i].kind != Visit::Forward) continue;
+                const int b = active_[(size_t)i]->batch;
+                if (b < 0 || std::find(seen.begin(), seen.end(), b) != seen.end()) continue;
+                seen.push_back(b);
+                BatchTrace& bt = batches_[(size_t)b];
+                bucket(bt.suffix_prefill_ms, bt.first_token_ms, bt.decode_ms, bt.mixed_ms) += info.model_ms;
+                bt.packed_forwards.push_back(stats_.ticks);
+            }
+            tick_info_.push_back(info);
+        }
         ++stats_.ticks;
         trace_.push_back(std::move(tick));
         // complete_mixed_rows (engine.rs:2411-2523)

@@ -55,13 +55,37 @@ struct EngineResult {
     int logit_rows = 0;
 };
 
+// Whole-forward classification of the reference's benchmark traces (BenchmarkForwardKind, src/engine.rs:430-439): a lane is
+// a prefill chunk that ends inside the prompt (SuffixPrefill), the chunk that ends the prompt and samples (FirstToken) or
+// a decode step (src/generation.rs:757-766); a packed forward whose lanes differ is Mixed, and its time goes to that
+// bucket alone.
+enum class ForwardKind : int32_t { SuffixPrefill = 0, FirstToken = 1, Decode = 2, Mixed = 3 };
+
 struct TickLaneTrace {
     int32_t request_id, start_pos, n_tokens;
+    int32_t phase;  // ForwardKind of the lane, never Mixed
+};
+
+struct TickInfo {  // BenchmarkPackedForwardRecord (src/engine.rs:452-460)
+    ForwardKind kind = ForwardKind::Mixed;
+    int lane_count = 0, input_tokens = 0;
+    double model_ms = 0.0;
+};
+
+// EngineBatchTrace (src/engine.rs:462-484) of one atomic batch, minus the host-side wall-clock splits of admission.
+struct BatchTrace {
+    std::vector<int> members;
+    int admitted_members = 0, rejected_members = 0, admission_active_sequences = 0;
+    bool admission_complete = false;
+    double suffix_prefill_ms = 0.0, first_token_ms = 0.0, decode_ms = 0.0, mixed_ms = 0.0;
+    std::vector<int64_t> packed_forwards;  // tick numbers of the forwards that carried at least one member
 };
 
 struct EngineStats {
     int64_t ticks = 0, prefill_tokens = 0, decode_tokens = 0, completed = 0, failed = 0, kv_shrinks = 0, cleanup_drains = 0, device_sampled = 0, cancelled = 0;
     double device_ms = 0.0;
+    // device time by whole-forward kind: every forward's time is in exactly one bucket (src/engine.rs:601-619)
+    double suffix_prefill_ms = 0.0, first_token_ms = 0.0, decode_ms = 0.0, mixed_ms = 0.0;
 };
 
 class Engine {
@@ -87,6 +111,10 @@ public:
     int pending() const { return (int)(queue_.size() + pending_atomic_.size() + active_.size()); }
     const EngineResult& result(int id) const;
     const std::vector<std::vector<TickLaneTrace>>& trace() const { return trace_; }
+    const TickInfo& tick_info(int64_t tick) const;
+    // The trace of the atomic batch `member_id` was submitted in; *terminal receives how many of its members have ended
+    // (done, failed, rejected or cancelled).  The trace is complete once admission ran and every member is terminal.
+    const BatchTrace& batch_trace(int member_id, int* terminal) const;
     const EngineStats& stats() const { return stats_; }
 
 private:
@@ -104,6 +132,7 @@ private:
         std::unique_ptr<LmSession> reclaimed;
         std::vector<uint32_t> history;
         int prompt_tokens = 0;
+        int batch = -1;
         Phase phase = Phase::Prefill;
         int cursor = 0;
         uint32_t decode_token = 0;
@@ -138,6 +167,9 @@ private:
     std::vector<std::unique_ptr<LmSession>> sessions_;
     std::map<int, EngineResult> results_;
     std::vector<std::vector<TickLaneTrace>> trace_;
+    std::vector<TickInfo> tick_info_;
+    std::vector<BatchTrace> batches_;       // indexed by atomic batch id
+    std::map<int, int> batch_of_request_;
     EngineStats stats_;
     std::atomic<int> next_id_{0};
     int next_batch_ = 0;

@@ -188,7 +188,9 @@ FakeLm::FakeLm(int vocab, int max_context, int block_tokens, int slab_blocks, in
 void FakeLm::run_forward(const std::vector<LmLane>& lanes, KvReservation&, uint32_t) {
     if (forwards_++ == fail_at_) throw std::runtime_error("injected forward failure");
     next_.clear();
+    last_tokens_ = 0;
     for (const LmLane& l : lanes) {
+        last_tokens_ += l.n_tokens;
         uint64_t t = l.ids[l.n_tokens - 1];
         uint64_t p = (uint64_t)(l.start_pos + l.n_tokens - 1);
         next_.push_back((uint32_t)((31 * t + 7 * p + 3) % (uint64_t)spec_.vocab));

@@ -136,6 +136,8 @@ public:
     // fail_completion_barrier_at and friends of the reference's FakeModel (src/engine.rs:3107-3300).
     void inject_failure(int site, int64_t index);
     int64_t drains() const { return drains_; }
+    // A made-up, exactly representable duration (0.25 ms + tokens / 1024 ms) so that time buckets can be checked.
+    float last_forward_ms() const override { return 0.25f + (float)last_tokens_ / 1024.f; }
     // Calls cb(user) once, inside the next completion barrier: the place where the reference's FakeModel flips
     // cancel_on_completion_barrier (src/engine.rs:3143,3575-3583), i.e. "the client gave up while the forward ran".
     void on_next_barrier(void (*cb)(void*), void* user) { barrier_cb_ = cb; barrier_user_ = user; }
@@ -149,7 +151,7 @@ protected:
 
 private:
     std::vector<uint32_t> next_;
-    int64_t forwards_ = 0, fail_at_ = -1;
+    int64_t forwards_ = 0, fail_at_ = -1, last_tokens_ = 0;
     void (*barrier_cb_)(void*) = nullptr;
     void* barrier_user_ = nullptr;
     int64_t reads_ = 0, fail_read_at_ = -1, resets_ = 0, fail_reset_at_ = -1, drains_ = 0, fail_drain_at_ = -1, clears_ = 0, fail_clear_at_ = -1;

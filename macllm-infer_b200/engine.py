@@ -259,6 +259,7 @@ class Model:
 
 
 _STATES = ("running", "done", "failed", "cancelled")
+FORWARD_KINDS = ("suffix_prefill", "first_token", "decode", "mixed")
 
 
 class Engine:
@@ -366,6 +367,31 @@ class Engine:
             capi.check(capi.lib().mk_engine_trace(self._h, tick, arr, C.byref(m)))
             out.append([(arr[i].request_id, arr[i].start_pos, arr[i].n_tokens) for i in range(m.value)])
             tick += 1
+        return out
+
+    def tick_info(self, tick: int) -> dict:
+        """Kind ('suffix_prefill' | 'first_token' | 'decode' | 'mixed'), lane count, input tokens, device time and the lanes'
+        phases of one packed forward - the reference's BenchmarkPackedForwardRecord (src/engine.rs:452-460)."""
+        info = capi.TickInfo()
+        capi.check(capi.lib().mk_engine_tick_info(self._h, tick, C.byref(info)))
+        arr = (capi.TickLane * max(info.lane_count, 1))()
+        m = C.c_int32(max(info.lane_count, 1))
+        capi.check(capi.lib().mk_engine_trace(self._h, tick, arr, C.byref(m)))
+        return dict(kind=FORWARD_KINDS[info.kind], lane_count=info.lane_count, input_tokens=info.input_tokens, model_ms=info.model_ms,
+                    phases=[FORWARD_KINDS[arr[i].phase] for i in range(m.value)])
+
+    def batch_trace(self, member_request_id: int) -> dict:
+        """EngineBatchTrace of the atomic batch the request was submitted in (src/engine.rs:462-484); `complete` turns true
+        once admission ran and every member has ended."""
+        t = capi.BatchTrace()
+        n = C.c_int32(0)
+        capi.check(capi.lib().mk_engine_batch_trace(self._h, member_request_id, C.byref(t), None, C.byref(n)))
+        ticks = (C.c_int64 * max(n.value, 1))()
+        m = C.c_int32(max(n.value, 1))
+        capi.check(capi.lib().mk_engine_batch_trace(self._h, member_request_id, C.byref(t), ticks, C.byref(m)))
+        out = {name: getattr(t, name) for name, _ in t._fields_ if name != "reserved_"}
+        out["complete"] = bool(out["complete"])
+        out["forward_ticks"] = [int(ticks[i]) for i in range(m.value)]
         return out
 
     def stats(self) -> dict:

@@ -164,6 +164,7 @@ class OracleEngine:
         self.round_visits = self.round_budget = 0
         self.kv_shrinks = 0
         self.cancelled: set[int] = set()   # EngineTicket::cancel, engine.rs:1136-1145: sticky
+        self.tick_kinds: list = []
         self.on_barrier = None             # test hook: called once after the next forward's completion barrier
 
     def cancel(self, rid):
@@ -223,7 +224,8 @@ class OracleEngine:
             return self._fail(rid, "invalid sampling parameters: " + why)
         max_cached = 0 if r.max_new_tokens == 0 else len(r.prompt) + r.max_new_tokens - 1  # engine.rs:2839-2863
         if max_cached > self.m.pool.max_blocks * self.m.pool.block_tokens:
-            return self._fail(rid, "request exceeds the configured shared KV capacity")
+            return self._fail(rid, f"request requires up to {max_cached} cached tokens, exceeding the configured shared KV capacity of "
+                                   f"{self.m.pool.max_blocks} blocks \u00d7 {self.m.pool.block_tokens} tokens")
         session = self.sessions.pop()  # LIFO, engine.rs:1719-1722
         seq = _Seq(rid, r, session, list(r.prompt), len(r.prompt))
         cached = self.m.reset_session_for_prompt(session, seq.history)  # generation.rs:799
@@ -333,14 +335,18 @@ class OracleEngine:
                 input_tokens += a["n"]
         fwd = [i for i, a in enumerate(actions) if a["kind"] == "forward"]
         if fwd:  # execute_prepared_visits, engine.rs:2233-2269
-            lanes, tick = [], []
+            lanes, tick, phases = [], [], []
             for i in fwd:
                 a, s = actions[i], self.active[i]
                 ids = s.history[a["start"]:a["start"] + a["n"]] if a["was_prefill"] else [s.decode_token]
                 lanes.append((s.session, ids, a["start"]))
                 tick.append((s.rid, a["start"], a["n"]))
+                phases.append("decode" if not a["was_prefill"] else ("first_token" if a["ready"] else "suffix_prefill"))
             logits = self.m.forward(lanes, reservation)
             self.trace.append(tick)
+            # BenchmarkForwardKind of the packed forward, engine.rs:2347-2356
+            self.tick_kinds.append(dict(kind=phases[0] if all(p == phases[0] for p in phases) else "mixed", phases=phases,
+                                        lane_count=len(fwd), input_tokens=input_tokens))
             if self.on_barrier is not None:
                 hook, self.on_barrier = self.on_barrier, None
                 hook()

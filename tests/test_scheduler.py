@@ -37,6 +37,16 @@ def submit_both(eng, pe, oe_, prompts, max_new, atomic=False):
     return ids_p
 
 
+def assert_tick_kinds_agree(pe, oe_):
+    """Whole-forward kinds, lane phases, lane counts and input tokens of every tick; the device-time buckets add up."""
+    assert len(oe_.tick_kinds) == len(pe.trace())
+    for tick, want in enumerate(oe_.tick_kinds):
+        got = pe.tick_info(tick)
+        assert {k: got[k] for k in ("kind", "phases", "lane_count", "input_tokens")} == want, tick
+    st = pe.stats()
+    assert abs(st["suffix_prefill_ms"] + st["first_token_ms"] + st["decode_ms"] + st["mixed_ms"] - st["device_ms"]) < 1e-6
+
+
 def test_ragged_prefill_and_decode_schedule(eng):
     """engine.rs:4701-4765: budget 4, quantum 2, two active; a 6-token prompt with 1 new token and a
     1-token prompt with 2 new tokens."""
@@ -122,7 +132,9 @@ def test_requests_that_can_never_fit_are_rejected_at_admission(eng):
                     eng.Request([3], 2)])
     e.run()
     assert [e.result(i)["state"] for i in ids] == ["failed", "failed", "failed", "failed", "done"]
-    assert "KV capacity" in e.result(ids[0])["message"]
+    # the reference's wording and kind (reject_preflight with ResourceExhausted, engine.rs:1694-1701,2856-2861)
+    assert e.result(ids[0])["message"] == "request requires up to 36 cached tokens, exceeding the configured shared KV capacity of 2 blocks \u00d7 16 tokens"
+    assert e.result(ids[0])["kind"] == "resource_exhausted" and e.result(ids[1])["kind"] == "invalid_request"
     assert "maximum context length is 64 tokens" in e.result(ids[1])["message"]
 
 
@@ -185,6 +197,7 @@ def test_randomised_differential_with_prefix_cache(eng, seed):
     pe.run()
     oe_.run()
     assert pe.trace() == [[tuple(l) for l in t] for t in oe_.trace]
+    assert_tick_kinds_agree(pe, oe_)
     for rid in range(submitted):
         rp, ro = pe.result(rid), oe_.results[rid]
         assert rp["state"] == ro.state
@@ -592,6 +605,7 @@ def test_randomised_differential_with_cancellations(eng, seed):
     pe.run()
     oe_.run()
     assert pe.trace() == [[tuple(l) for l in t] for t in oe_.trace]
+    assert_tick_kinds_agree(pe, oe_)
     states = set()
     for rid in range(submitted):
         rp, ro = pe.result(rid), oe_.results[rid]
@@ -602,3 +616,73 @@ def test_randomised_differential_with_cancellations(eng, seed):
     if not mkw["prefix_capacity_tokens"]:
         assert pm.pool_stats()["live_blocks"] == 0       # every cancelled request gave its pages back
     assert "cancelled" in states
+
+
+# ---- benchmark traces (src/engine.rs:430-484; tests at src/engine.rs:4454-4619) ---------------------------------------
+
+def test_atomic_batch_is_fully_admitted_before_its_first_forward(eng):
+    """engine.rs:4454-4540: three one-token requests in one atomic batch, three active slots, budget 3, quantum 1 - one tick
+    admits all three and runs one packed first-token forward of three lanes; the batch's trace is complete after it."""
+    pm, pe = product_engine(eng, dict(vocab=32, max_context=8), dict(max_active_sequences=3, scheduler_token_budget=3, prefill_token_quantum=1))
+    ids = pe.submit([eng.Request([1], 1, publish_prompt_prefix=False) for _ in range(3)], True)
+    assert pe.batch_trace(ids[0])["complete"] is False
+    assert pe.step() == 3
+    t = pe.batch_trace(ids[2])
+    assert t["complete"] is True
+    assert (t["expected_members"], t["admitted_members"], t["terminal_members"], t["rejected_members"]) == (3, 3, 3, 0)
+    assert t["admission_active_sequences"] == 3
+    assert t["packed_forwards"] == 1 and t["forward_ticks"] == [0]
+    info = pe.tick_info(0)
+    assert info["kind"] == "first_token" and info["lane_count"] == 3 and info["phases"] == ["first_token"] * 3
+    assert t["first_token_ms"] == info["model_ms"]
+    assert t["suffix_prefill_ms"] == 0.0 and t["decode_ms"] == 0.0 and t["mixed_ms"] == 0.0
+
+
+def test_benchmark_trace_retains_each_packed_decode_forward(eng):
+    """engine.rs:4541-4619: two two-token requests, budget 2, quantum 1: the trace is unreadable after the first tick and holds
+    a first-token forward and a decode forward, two lanes and two input tokens each, after the second."""
+    pm, pe = product_engine(eng, dict(vocab=32, max_context=8), dict(max_active_sequences=2, scheduler_token_budget=2, prefill_token_quantum=1))
+    ids = pe.submit([eng.Request([1], 2, publish_prompt_prefix=False), eng.Request([1], 2, publish_prompt_prefix=False)], True)
+    pe.step()
+    assert pe.batch_trace(ids[0])["complete"] is False
+    pe.step()
+    t = pe.batch_trace(ids[0])
+    assert t["complete"] is True and t["forward_ticks"] == [0, 1]
+    infos = [pe.tick_info(k) for k in t["forward_ticks"]]
+    assert [i["kind"] for i in infos] == ["first_token", "decode"]
+    assert all(i["lane_count"] == 2 and i["input_tokens"] == 2 for i in infos)
+    assert t["decode_ms"] == infos[1]["model_ms"] and t["mixed_ms"] == 0.0
+
+
+def test_a_mixed_forward_is_counted_once_in_its_own_bucket(eng):
+    """engine.rs:430-439,2347-2356: a forward whose lanes differ in phase is Mixed as a whole; the lanes keep their own phases,
+    and a batch whose member shared the forward with an outsider records the whole forward."""
+    pm, pe = product_engine(eng, dict(vocab=32), dict(max_active_sequences=3, scheduler_token_budget=8, prefill_token_quantum=2))
+    outsider = pe.submit([eng.Request([1, 2, 3, 4, 5], 2)])[0]
+    batch = pe.submit([eng.Request([1], 3), eng.Request([2, 3, 4], 1)], True)
+    pe.run()
+    kinds = [pe.tick_info(k) for k in range(len(pe.trace()))]
+    # tick 0: outsider chunk 0-2 (suffix), member 0 first token, member 1 chunk 0-2 (suffix)
+    assert kinds[0]["kind"] == "mixed" and kinds[0]["phases"] == ["suffix_prefill", "first_token", "suffix_prefill"]
+    # tick 1: outsider chunk 2-4 (suffix), member 0 decode, member 1 last chunk (first token)
+    assert kinds[1]["kind"] == "mixed" and kinds[1]["phases"] == ["suffix_prefill", "decode", "first_token"]
+    t = pe.batch_trace(batch[0])
+    assert t["complete"] and (t["expected_members"], t["admitted_members"], t["rejected_members"]) == (2, 2, 0)
+    st = pe.stats()
+    assert abs(t["mixed_ms"] - sum(k["model_ms"] for i, k in enumerate(kinds) if i in t["forward_ticks"] and k["kind"] == "mixed")) < 1e-9
+    assert abs(st["suffix_prefill_ms"] + st["first_token_ms"] + st["decode_ms"] + st["mixed_ms"] - st["device_ms"]) < 1e-9
+    with pytest.raises(RuntimeError, match="was not submitted in an atomic batch"):
+        pe.batch_trace(outsider)
+
+
+def test_rejected_and_cancelled_members_end_the_trace(eng):
+    """engine.rs:517-543,3027-3040: a member refused at preflight counts as rejected and terminal, a cancelled one as terminal;
+    the trace completes without them ever running."""
+    pm, pe = product_engine(eng, dict(vocab=32), dict(max_active_sequences=3, scheduler_token_budget=8, prefill_token_quantum=4))
+    ids = pe.submit([eng.Request([1, 2], 1), eng.Request([99], 1), eng.Request([3], 1)], True)
+    pe.cancel(ids[2])
+    pe.run()
+    t = pe.batch_trace(ids[0])
+    assert t["complete"] is True
+    assert (t["expected_members"], t["admitted_members"], t["terminal_members"], t["rejected_members"]) == (3, 1, 3, 1)
+    assert t["admission_active_sequences"] == 1 and t["packed_forwards"] == 1
