@@ -169,6 +169,9 @@ int32_t mk_model_fake_inject(mk_model* m, int32_t site, int64_t index);
 /* Host-only fake model: call cb(user) once inside the next completion barrier - the place where the reference's FakeModel
  * flips cancel_on_completion_barrier (src/engine.rs:3143,3575-3583), "the client gave up while the forward ran". */
 int32_t mk_model_fake_on_barrier(mk_model* m, void (*cb)(void*), void* user);
+/* Host-only fake model: its stop token ids, and (n_logits > 0) one logits row that every lane of every forward returns in
+ * place of the one-hot row, like FakeModel::with_logits of the reference's generation tests (src/generation.rs:1633-1640). */
+int32_t mk_model_fake_script(mk_model* m, const uint32_t* stop_ids, int32_t n_stop, const float* logits_row, int32_t n_logits);
 int32_t mk_model_free(mk_model* m);
 /* ep_mode 1 only.  The ranks of an expert-parallel group tick in lock step: each MoE layer of each forward is one
  * exchange that all ranks take part in.  A rank whose scheduler has no lane to run in a tick calls this instead of a
@@ -381,6 +384,24 @@ int32_t mk_engine_run(mk_engine* e);
 int32_t mk_engine_pending(mk_engine* e, int32_t* out);
 /* Generated tokens of a request (capacity in *n, count out); *finished: 0 running, 1 done, 2 failed, 3 cancelled. */
 int32_t mk_engine_result(mk_engine* e, int32_t request_id, uint32_t* tokens, int32_t* n, int32_t* finished, int64_t* cached_tokens);
+/* GenerationMetrics (src/generation.rs:35-58), the model-side part.  Every packed forward the sequence joined adds its
+ * whole device time to the bucket of the phase its lane was in (src/generation.rs:1185-1199): chunks that end inside the
+ * prompt, the chunk that produced the first-token logits, decode steps; prefill_ms is the sum of the first two.
+ * finish_reason: 0 none yet, 1 Length, 2 Stop, 3 Cancelled.  Wall-clock figures (time to first token, total time, prefix
+ * lookup) are the caller's to take. */
+typedef struct mk_request_metrics {
+    int32_t prompt_tokens;
+    int32_t cached_prompt_tokens;
+    int32_t generated_tokens;
+    int32_t decode_steps;
+    int32_t finish_reason;
+    int32_t reserved_;
+    double suffix_prefill_ms;
+    double first_token_ms;
+    double prefill_ms;
+    double decode_ms;
+} mk_request_metrics;
+int32_t mk_engine_request_metrics(mk_engine* e, int32_t request_id, mk_request_metrics* out);
 /* Logits rows recorded for a request when record_logits is set: [n_rows][vocab]. */
 int32_t mk_engine_logits(mk_engine* e, int32_t request_id, float* out, int32_t* n_rows);
 /* Lanes of tick `tick` (0-based); capacity in *n. */

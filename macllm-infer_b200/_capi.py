@@ -90,6 +90,12 @@ class TickLane(C.Structure):
     _fields_ = [("request_id", C.c_int32), ("start_pos", C.c_int32), ("n_tokens", C.c_int32), ("phase", C.c_int32)]
 
 
+class RequestMetrics(C.Structure):
+    _fields_ = [("prompt_tokens", C.c_int32), ("cached_prompt_tokens", C.c_int32), ("generated_tokens", C.c_int32),
+                ("decode_steps", C.c_int32), ("finish_reason", C.c_int32), ("reserved_", C.c_int32), ("suffix_prefill_ms", C.c_double),
+                ("first_token_ms", C.c_double), ("prefill_ms", C.c_double), ("decode_ms", C.c_double)]
+
+
 class TickInfo(C.Structure):
     _fields_ = [("kind", C.c_int32), ("lane_count", C.c_int32), ("input_tokens", C.c_int32), ("reserved_", C.c_int32),
                 ("model_ms", C.c_double)]
@@ -182,6 +188,8 @@ SIGNATURES = {
     "mk_engine_status": (_i32, [P, C.POINTER(_i32)]),
     "mk_engine_failure_kind": (_i32, [P, _i32, C.POINTER(_i32)]),
     "mk_engine_cancel": (_i32, [P, _i32]),
+    "mk_engine_request_metrics": (_i32, [P, _i32, C.POINTER(RequestMetrics)]),
+    "mk_model_fake_script": (_i32, [P, C.c_void_p, _i32, C.c_void_p, _i32]),
     "mk_engine_tick_info": (_i32, [P, _i64, C.POINTER(TickInfo)]),
     "mk_engine_batch_trace": (_i32, [P, _i32, C.POINTER(BatchTrace), C.POINTER(_i64), C.POINTER(_i32)]),
     "mk_kvpool_new": (_i32, [_i32, _i32, _i64, C.POINTER(P)]),

@@ -446,6 +446,30 @@ int32_t mk_engine_result(mk_engine* e, int32_t request_id, uint32_t* tokens, int
     });
 }
 
+int32_t mk_engine_request_metrics(mk_engine* e, int32_t request_id, mk_request_metrics* out) {
+    return guarded([&] {
+        const EngineResult& r = e->e->result(request_id);
+        out->prompt_tokens = r.prompt_tokens;
+        out->cached_prompt_tokens = (int32_t)r.cached_tokens;
+        out->generated_tokens = (int32_t)r.tokens.size();
+        out->decode_steps = r.decode_steps;
+        out->finish_reason = r.finish_reason == "length" ? 1 : r.finish_reason == "stop" ? 2 : r.finish_reason == "cancelled" ? 3 : 0;
+        out->reserved_ = 0;
+        out->suffix_prefill_ms = r.suffix_prefill_ms;
+        out->first_token_ms = r.first_token_ms;
+        out->prefill_ms = r.suffix_prefill_ms + r.first_token_ms;
+        out->decode_ms = r.decode_ms;
+    });
+}
+
+int32_t mk_model_fake_script(mk_model* m, const uint32_t* stop_ids, int32_t n_stop, const float* logits_row, int32_t n_logits) {
+    return guarded([&] {
+        FakeLm* fake = dynamic_cast<FakeLm*>(m->lm.get());
+        if (fake == nullptr) throw std::runtime_error("scripting is only available on the host-only fake model");
+        fake->script(stop_ids, n_stop, logits_row, n_logits);
+    });
+}
+
 int32_t mk_engine_logits(mk_engine* e, int32_t request_id, float* out, int32_t* n_rows) {
     return guarded([&] {
         const EngineResult& r = e->e->result(request_id);

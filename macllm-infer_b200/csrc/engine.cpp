@@ -196,6 +196,7 @@ void Engine::admit(Job job) {  // admit_with_diagnostic_refresh, engine.rs:1654-
     seq->cursor = (int)cached;
     seq->batch = job.batch;
     results_[job.id].cached_tokens = cached;
+    results_[job.id].prompt_tokens = seq->prompt_tokens;
     if (job.batch >= 0) ++batches_[(size_t)job.batch].admitted_members;  // record_admitted, engine.rs:1800-1803
     active_.push_back(std::move(seq));
 }
@@ -494,7 +495,14 @@ int Engine::drive_once() {  // engine.rs:1938-1964
                 model_.publish_prompt_prefix(*s.session, s.history.data(), (size_t)next_cache_len);
             v.kind = Visit::Complete;
             v.finished = false;
-            // GenerationCore::complete (generation.rs:1159-1266)
+            // GenerationCore::complete (generation.rs:1159-1266): the forward's time is the sequence's before anything else
+            {
+                EngineResult& res = results_[s.id];
+                const double t = model_.last_forward_ms();
+                if (!v.was_prefill) { res.decode_ms += t; ++res.decode_steps; }
+                else if (v.ready_to_sample) res.first_token_ms += t;
+                else res.suffix_prefill_ms += t;
+            }
             if (is_cancelled(s.id)) {  // given up while the forward ran: the row is dropped, the peers' rows keep their places
                 s.phase = Phase::Finished;
                 finish_cancelled(s.id);

@@ -53,6 +53,10 @@ struct EngineResult {
     int64_t cached_tokens = 0;
     std::vector<float> logits;  // record_logits: one row per sampled position
     int logit_rows = 0;
+    // GenerationMetrics (src/generation.rs:35-58), the model-side part: every packed forward the sequence joined adds its
+    // whole device time to the sequence's bucket for the phase its lane was in (src/generation.rs:1185-1199)
+    int prompt_tokens = 0, decode_steps = 0;
+    double suffix_prefill_ms = 0.0, first_token_ms = 0.0, decode_ms = 0.0;
 };
 
 // Whole-forward classification of the reference's benchmark traces (BenchmarkForwardKind, src/engine.rs:430-439): a lane is

@@ -197,6 +197,13 @@ void FakeLm::run_forward(const std::vector<LmLane>& lanes, KvReservation&, uint3
     }
 }
 
+void FakeLm::script(const uint32_t* stop_ids, int n_stop, const float* logits_row, int n_logits) {
+    if (n_logits > spec_.vocab) throw std::runtime_error("scripted logits row is wider than the vocabulary");
+    spec_.stop_ids.assign(stop_ids, stop_ids + std::max(n_stop, 0));
+    fixed_row_.assign((size_t)(n_logits > 0 ? spec_.vocab : 0), 0.f);
+    for (int i = 0; i < n_logits; ++i) fixed_row_[(size_t)i] = logits_row[i];
+}
+
 void FakeLm::inject_failure(int site, int64_t index) {
     switch (site) {
         case 0: fail_at_ = index; break;
@@ -228,6 +235,11 @@ void FakeLm::fetch_output(float* logits, uint32_t* tokens) {
         cb(barrier_user_);
     }
     for (size_t i = 0; i < next_.size(); ++i) {
+        if (!fixed_row_.empty()) {  // scripted logits: the greedy token is the row's first maximum
+            if (tokens) tokens[i] = (uint32_t)(std::max_element(fixed_row_.begin(), fixed_row_.end()) - fixed_row_.begin());
+            if (logits) std::copy(fixed_row_.begin(), fixed_row_.end(), logits + i * (size_t)spec_.vocab);
+            continue;
+        }
         if (tokens) tokens[i] = next_[i];
         if (logits) {
             float* row = logits + i * (size_t)spec_.vocab;

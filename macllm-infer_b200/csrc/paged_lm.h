@@ -136,6 +136,9 @@ public:
     // fail_completion_barrier_at and friends of the reference's FakeModel (src/engine.rs:3107-3300).
     void inject_failure(int site, int64_t index);
     int64_t drains() const { return drains_; }
+    // Stop token ids of the runtime spec, and (n_logits > 0) one logits row that every lane of every forward returns instead
+    // of the one-hot row - FakeModel::with_logits of the reference's generation tests (src/generation.rs:1633-1640).
+    void script(const uint32_t* stop_ids, int n_stop, const float* logits_row, int n_logits);
     // A made-up, exactly representable duration (0.25 ms + tokens / 1024 ms) so that time buckets can be checked.
     float last_forward_ms() const override { return 0.25f + (float)last_tokens_ / 1024.f; }
     // Calls cb(user) once, inside the next completion barrier: the place where the reference's FakeModel flips
@@ -151,6 +154,7 @@ protected:
 
 private:
     std::vector<uint32_t> next_;
+    std::vector<float> fixed_row_;
     int64_t forwards_ = 0, fail_at_ = -1, last_tokens_ = 0;
     void (*barrier_cb_)(void*) = nullptr;
     void* barrier_user_ = nullptr;

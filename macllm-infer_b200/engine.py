@@ -149,6 +149,13 @@ class Model:
         sites = {"forward": 0, "read_output": 1, "admission": 2, "synchronize": 3, "clear_session": 4}
         capi.check(capi.lib().mk_model_fake_inject(self._h, sites[site], index))
 
+    def script(self, stop_ids=(), logits_row=()) -> None:
+        """Fake model only: stop token ids, and one logits row that every forward returns for every lane (empty: the one-hot rows)."""
+        stops = np.asarray(list(stop_ids), np.uint32)
+        row = np.asarray(list(logits_row), np.float32)
+        capi.check(capi.lib().mk_model_fake_script(self._h, stops.ctypes.data if len(stops) else None, len(stops),
+                                                   row.ctypes.data if len(row) else None, len(row)))
+
     def on_next_barrier(self, fn) -> None:
         """Fake model only: call `fn()` once inside the next completion barrier (while the engine waits for a forward)."""
         self._barrier_cb = C.CFUNCTYPE(None, C.c_void_p)(lambda _user: fn())   # kept alive until it has run
@@ -367,6 +374,15 @@ class Engine:
             capi.check(capi.lib().mk_engine_trace(self._h, tick, arr, C.byref(m)))
             out.append([(arr[i].request_id, arr[i].start_pos, arr[i].n_tokens) for i in range(m.value)])
             tick += 1
+        return out
+
+    def metrics(self, request_id: int) -> dict:
+        """The model-side GenerationMetrics of a request (src/generation.rs:35-58): token counts, decode steps, finish reason
+        and the device time of the forwards it joined, by the phase its lane was in."""
+        m = capi.RequestMetrics()
+        capi.check(capi.lib().mk_engine_request_metrics(self._h, request_id, C.byref(m)))
+        out = {name: getattr(m, name) for name, _ in m._fields_ if name != "reserved_"}
+        out["finish_reason"] = (None, "length", "stop", "cancelled")[m.finish_reason]
         return out
 
     def tick_info(self, tick: int) -> dict:

@@ -16,7 +16,7 @@ STRUCTS = {
     "mk_load_config": "LoadConfig", "mk_runtime_spec": "RuntimeSpec", "mk_kv_capacity": "KvCapacity", "mk_pool_stats": "PoolStats",
     "mk_prefix_diagnostics": "PrefixDiagnostics", "mk_lane": "Lane", "mk_engine_config": "EngineConfig", "mk_request": "Request",
     "mk_tick_lane": "TickLane", "mk_engine_stats": "EngineStats", "mk_kernel_profile": "KernelProfile", "mk_attn_case": "AttnCase",
-    "mk_gguf_summary": "GgufSummary", "mk_lane_sampling": "LaneSampling", "mk_tick_info": "TickInfo", "mk_batch_trace": "BatchTrace",
+    "mk_gguf_summary": "GgufSummary", "mk_lane_sampling": "LaneSampling", "mk_tick_info": "TickInfo", "mk_batch_trace": "BatchTrace", "mk_request_metrics": "RequestMetrics",
 }
 
 
