@@ -13,8 +13,11 @@ inline int64_t div_ceil(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 KvPool::KvPool(int block_tokens, int slab_blocks, int64_t max_blocks)
     : block_tokens_(block_tokens), slab_blocks_(slab_blocks), max_blocks_(max_blocks) {
-    if (block_tokens <= 0 || slab_blocks <= 0 || max_blocks <= 0)
-        throw KvInvalid("paged KV pool geometry must be positive");  // PagedKvPoolConfig::new, :128-148
+    // PagedKvPoolConfig::new (:126-147) with the display form of InvalidConfig (:67)
+    if (block_tokens <= 0) throw KvInvalid("invalid paged KV config: block_tokens must be positive");
+    if (slab_blocks <= 0) throw KvInvalid("invalid paged KV config: slab_blocks must be positive");
+    if (max_blocks <= 0) throw KvInvalid("invalid paged KV config: max_blocks must be positive");
+    if (max_blocks > (int64_t)UINT32_MAX) throw KvInvalid("invalid paged KV config: max_blocks exceeds the generational block-ID range");
     slots_.reserve((size_t)std::min<int64_t>(max_blocks, 1 << 20));
 }
 

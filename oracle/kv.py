@@ -42,8 +42,11 @@ def div_ceil(a, b):
 
 class Pool:
     def __init__(self, block_tokens: int, slab_blocks: int, max_blocks: int):
-        if min(block_tokens, slab_blocks, max_blocks) <= 0:
-            raise Invalid("paged KV pool geometry must be positive")
+        for value, name in ((block_tokens, "block_tokens"), (slab_blocks, "slab_blocks"), (max_blocks, "max_blocks")):  # cache.rs:126-147
+            if value <= 0:
+                raise Invalid(f"invalid paged KV config: {name} must be positive")
+        if max_blocks > 0xFFFFFFFF:
+            raise Invalid("invalid paged KV config: max_blocks exceeds the generational block-ID range")
         self.block_tokens, self.slab_blocks, self.max_blocks = block_tokens, slab_blocks, max_blocks
         self.slots: list[Slot] = []
         self.slabs = 0

@@ -349,3 +349,43 @@ def test_attach_prefix_failures_leave_ownership_unchanged(mk):
             table.attach_prefix(psource, n)
         assert (len(table), table.blocks()) == kept
     assert ppool.stats() == pshared
+
+
+def test_pool_rejects_invalid_and_overflowing_geometry(Pool):
+    """cache.rs:3940-3951 (PagedKvPoolConfig::new, cache.rs:126-147): each of the three sizes must be positive and the block
+    count must fit the 32-bit slot half of a generational block id."""
+    for args, what in (((0, 1, 1), "block_tokens"), ((1, 0, 1), "slab_blocks"), ((1, 1, 0), "max_blocks")):
+        with pytest.raises(Exception, match=f"invalid paged KV config: {what} must be positive"):
+            Pool(*args)
+    with pytest.raises(Exception, match="block-ID range"):
+        Pool(1, 1, 0xFFFFFFFF + 1)
+    Pool(1, 1, 0xFFFFFFFF)      # the largest legal pool is only a number until blocks are taken
+
+
+def test_occupancy_across_refcount_cow_and_rollback(Pool):
+    """cache.rs:3964-4054 (pool of block_tokens 2, slab_blocks 2, max 4): the occupancy figures after a commit, two forks, a
+    cleared fork, a copy-on-write append, a touched rollback on a third fork, its epoch's completion, and the release of
+    everything."""
+    pool = Pool(2, 2, 4)
+    source = pool.new_table()
+    assert pool.append([source], [3]) == []
+    assert sub(pool.stats(), "live_references", "reserved_blocks") == (2, 0)
+    pool.complete(pool.submitted())
+    first_fork, second_fork = source.fork_prefix(3), source.fork_prefix(3)
+    assert sub(pool.stats(), "live_blocks", "live_references", "shared_blocks") == (2, 6, 2)
+    first_fork.clear()
+    assert sub(pool.stats(), "live_references", "shared_blocks") == (4, 2)
+    cows = pool.append([second_fork], [1])                 # the shared half-full tail is replaced, not written
+    assert len(cows) == 1 and cows[0][2] == 1
+    cow_epoch = pool.submitted()
+    assert sub(pool.stats(), "reserved_blocks", "live_blocks", "live_references", "shared_blocks") == (0, 3, 4, 1)
+    rolled_back_fork = source.fork_prefix(3)
+    failed_epoch = pool.append_touch_rollback([rolled_back_fork], [1])
+    assert sub(pool.stats(), "reserved_blocks", "live_blocks", "live_references", "shared_blocks", "retired_blocks") == (0, 3, 6, 2, 1)
+    pool.complete(failed_epoch)
+    assert pool.stats()["retired_blocks"] == 0
+    for t in (source, second_fork, rolled_back_fork):
+        t.clear()
+    st = pool.stats()
+    assert sub(st, "live_blocks", "live_references", "shared_blocks") == (0, 0, 0)
+    assert st["free_blocks"] == st["allocated_blocks"] and st["completed_epoch"] >= cow_epoch

@@ -191,3 +191,40 @@ def test_endpoint_digest_is_independent_of_how_the_prefix_is_cut(pkv):
         chained = (b"\0" * 32 if whole == 0 else full[whole - 1]) if rest else None
         want = full[whole - 1] if rest == 0 else kv.hash_block(chained, 4, whole, tokens[4 * whole:n])
         assert kv.endpoint_digest(tokens, n, 4) == want, n
+
+
+def test_hit_refreshes_lru_and_explicit_eviction_returns_the_oldest(Cache):
+    """prefix_cache.rs:898-913 (there through the exact-endpoint lookup; one-token blocks make the aligned lookup ask the
+    same question): the hit on "one" makes "two" the oldest."""
+    c = Cache(1, 10)
+    c.insert([1], 1, 1)
+    c.insert([2], 2, 2)
+    c.insert([3], 3, 3)
+    assert c.lookup([1, 9]) == (1, 1)
+    assert c.evict() == 2
+    s = c.stats()
+    assert (s["evictions"], s["entries"], s["cached_blocks"]) == (1, 2, 4)
+
+
+def test_stats_count_each_lookup_once_and_accumulate_matched_tokens(Cache):
+    """prefix_cache.rs:975-999, asked through the aligned lookup: the two-token match is served by the most recently used
+    snapshot that encloses it (prefix_cache.rs:341-351), which is "three" after the first hit; the counters are the reference's."""
+    c = Cache(1, 10)
+    c.insert([1, 2], 2, 1)
+    c.insert([1, 2, 3], 3, 1)
+    assert c.lookup([1, 2, 3, 4]) == (3, 3)
+    assert c.lookup([1, 2, 9]) == (2, 3)
+    assert c.lookup([8, 8, 8]) is None
+    s = c.stats()
+    assert (s["hits"], s["misses"], s["matched_tokens"], s["entries"], s["cached_blocks"], s["evictions"]) == (2, 1, 5, 2, 2, 0)
+
+
+def test_empty_and_tiny_prompts_are_misses(Cache):
+    """prefix_cache.rs:1020-1030: an empty prompt and a prompt no longer than the stored prefix (at least one token must be
+    left to compute) miss, and each miss is counted."""
+    c = Cache(1, 10)
+    c.insert([1], 1, 1)
+    assert c.lookup([]) is None
+    assert c.lookup([1]) is None
+    assert c.lookup([2, 1]) is None
+    assert c.stats()["misses"] == 3 and c.stats()["hits"] == 0
