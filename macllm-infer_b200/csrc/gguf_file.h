@@ -1,5 +1,7 @@
-// Minimal GGUF v3 reader (memory-mapped): metadata key/values and tensor descriptors of one file or of a shard family
-// `<prefix>-00001-of-000NN.gguf` opened through its first member (src/gguf.rs:576-660).
+// GGUF v3 reader (memory-mapped): metadata key/values and tensor descriptors of one file or of a shard family
+// `<prefix>-00001-of-000NN.gguf` opened through its first member (src/gguf.rs:576-660).  The header is parsed with the
+// reference's rules and limits (parse_gguf, src/gguf.rs:2069-2240): bounded strings, arrays and index memory, no
+// duplicate keys or names, canonical payload offsets, overflow-checked sizes.
 // Format facts follow the reference's loader (src/gguf.rs:32-46,2155-2220): little-endian, default
 // alignment 32, dims stored innermost-first, tensor data contiguous after the aligned header.
 #pragma once
@@ -21,6 +23,7 @@ struct GgufTensor {
 };
 
 struct GgufValue {
+    uint32_t type = 0;  // the GGUF value-type tag the file gave (an array's own tag, not its elements')
     std::variant<std::monostate, int64_t, double, bool, std::string, std::vector<int64_t>, std::vector<double>, std::vector<std::string>> v;
 };
 

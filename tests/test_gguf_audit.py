@@ -119,7 +119,8 @@ def test_tensor_of_another_sequence_mixer(pk, tmp_path):
 def test_block_formats(pk, tmp_path):
     def retype(name, qtype):
         return lambda spec, m, p: (m, [(n, d, qtype if n == name else q, s) for n, d, q, s in p])
-    refused(pk, broken(pk, tmp_path, "llama", retype("blk.0.ffn_down.weight", 16)), "unsupported GGML type 16")
+    refused(pk, broken(pk, tmp_path, "llama", retype("blk.0.ffn_down.weight", 16)),
+            "unsupported GGML tensor type 16; this runtime currently supports F32 (0), F16 (1), Q4_0 (2)")
     refused(pk, broken(pk, tmp_path, "llama", retype("blk.0.attn_norm.weight", pk["capi"].TYPE_F16)), "`blk.0.attn_norm.weight` must be F32")
 
 
@@ -225,3 +226,122 @@ def test_oracle_reads_a_shard_family_like_the_single_file(pk, tmp_path):
     for name in whole.tensors:
         a, b = whole.raw(name), family.raw(name)
         assert a[1:] == b[1:] and np.array_equal(a[0], b[0]), name
+
+
+# ---- the container parser's own rules (parse_gguf, src/gguf.rs:2069-2240; its tests at src/gguf.rs:3748-3862) ---------------
+
+def raw_gguf(seed, metas=(), tensors=(), version=3, counts=None, align=32, pad_data=True):
+    """A bare GGUF file: `metas` are encoded records, `tensors` are (name, file-order dims, type tag, payload bytes, offset or
+    None for the canonical one)."""
+    n_t, n_kv = counts if counts is not None else (len(tensors), len(metas))
+    head = struct.pack("<IIQQ", seed.GGUF_MAGIC, version, n_t, n_kv) + b"".join(metas)
+    offset, data = 0, b""
+    for name, dims, tag, payload, off in tensors:
+        head += seed._s(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims) + struct.pack("<IQ", tag, offset if off is None else off)
+        padded = payload + b"\0" * ((-len(payload)) % align)
+        data += padded
+        offset += len(padded)
+    if tensors:
+        head += b"\0" * ((-len(head)) % align)
+    return head + (data if pad_data else b"")
+
+
+def refused_bytes(pk, tmp_path, blob, fragment):
+    path = tmp_path / "raw.gguf"
+    path.write_bytes(blob)
+    with pytest.raises(pk["capi"].MkError) as e:
+        pk["eng"].Model.inspect_gguf(path)
+    assert fragment in str(e.value), str(e.value)
+
+
+def f32s(*values):
+    return struct.pack(f"<{len(values)}f", *values)
+
+
+def test_rejects_bad_magic_version_and_header_counts(pk, tmp_path):
+    """src/gguf.rs:3748-3767."""
+    seed = pk["seed"]
+    valid = raw_gguf(seed)
+    refused_bytes(pk, tmp_path, b"X" + valid[1:], "bad GGUF magic")
+    refused_bytes(pk, tmp_path, valid[:4] + struct.pack("<I", 2) + valid[8:], "unsupported GGUF version 2; expected version 3")
+    refused_bytes(pk, tmp_path, valid[:4] + struct.pack(">I", 3) + valid[8:], "big-endian GGUF v3 is not supported")
+    refused_bytes(pk, tmp_path, valid[:8] + struct.pack("<Q", 2 ** 64 - 1) + valid[16:], "GGUF tensor count 18446744073709551615 exceeds limit 1048576")
+    refused_bytes(pk, tmp_path, raw_gguf(seed, counts=(1000, 1000)), "declared tensor/metadata counts need at least 37000 bytes, but only 0 remain")
+    refused_bytes(pk, tmp_path, valid[:10], "unexpected end of GGUF file at byte 8 while reading 8 bytes")
+
+
+def test_rejects_duplicate_metadata_and_tensor_names(pk, tmp_path):
+    """src/gguf.rs:3769-3786."""
+    seed = pk["seed"]
+    kv = lambda v: seed._kv("same", seed.T_U32, struct.pack("<I", v))
+    refused_bytes(pk, tmp_path, raw_gguf(seed, metas=[kv(1), kv(2)]), "duplicate GGUF metadata key 'same'")
+    t = ("same", (1,), 0, f32s(1.0), None)
+    refused_bytes(pk, tmp_path, raw_gguf(seed, tensors=[t, t]), "duplicate GGUF tensor name 'same'")
+
+
+def test_rejects_invalid_bool_unknown_type_and_nested_array(pk, tmp_path):
+    """src/gguf.rs:3788-3807."""
+    seed = pk["seed"]
+    T_BOOL, T_ARRAY, T_U8 = 7, 9, 0
+    refused_bytes(pk, tmp_path, raw_gguf(seed, metas=[seed._kv("bool", T_BOOL, b"\x02")]), "invalid GGUF boolean byte 2; expected 0 or 1")
+    refused_bytes(pk, tmp_path, raw_gguf(seed, metas=[seed._kv("value", 99, struct.pack("<I", 1))]), "unknown GGUF metadata value type 99")
+    nested = struct.pack("<IQ", T_ARRAY, 1) + struct.pack("<IQ", T_U8, 0)
+    refused_bytes(pk, tmp_path, raw_gguf(seed, metas=[seed._kv("nested", T_ARRAY, nested)]), "nested GGUF metadata arrays are not supported")
+
+
+def test_rejects_invalid_alignment_noncanonical_offsets_and_truncation(pk, tmp_path):
+    """src/gguf.rs:3809-3837; a non-power-of-two multiple of 8 is a legal alignment (src/gguf.rs:3245-3263)."""
+    seed = pk["seed"]
+    align = lambda v: seed._kv("general.alignment", seed.T_U32, struct.pack("<I", v))
+    refused_bytes(pk, tmp_path, raw_gguf(seed, metas=[align(3)]), "GGUF alignment 3 must be a multiple of 8 bytes")
+    refused_bytes(pk, tmp_path, raw_gguf(seed, metas=[seed._kv("general.alignment", seed.T_U64, struct.pack("<Q", 32))]), "general.alignment must be U32")
+    a, b = ("a", (1,), 0, f32s(1.0), 0), ("b", (1,), 0, f32s(2.0), 0)
+    refused_bytes(pk, tmp_path, raw_gguf(seed, tensors=[a, b]), "tensor 'b' has non-canonical offset 0, expected 32")
+    whole = raw_gguf(seed, tensors=[a])
+    refused_bytes(pk, tmp_path, whole[:-32], "past file length")
+    # alignment 24: accepted by the container parser (the refusal that follows is the family audit's, not the container's)
+    ok = raw_gguf(seed, metas=[align(24)], tensors=[("a", (1,), 0, f32s(1.0), None), ("b", (1,), 0, f32s(2.0), None)], align=24)
+    refused_bytes(pk, tmp_path, ok, "general.architecture")
+
+
+def test_rejects_unsupported_tensor_types_and_shape_overflow(pk, tmp_path):
+    """src/gguf.rs:3839-3861 and byte_len's rules (src/gguf.rs:427-451)."""
+    seed = pk["seed"]
+    refused_bytes(pk, tmp_path, raw_gguf(seed, tensors=[("q4_1", (32,), 3, b"\0" * 20, None)]), "unsupported GGML tensor type 3; this runtime currently supports")
+    refused_bytes(pk, tmp_path, raw_gguf(seed, tensors=[("huge", (2 ** 63 - 1, 4), 0, b"", None)]), "tensor 'huge' element count overflow")
+    refused_bytes(pk, tmp_path, raw_gguf(seed, tensors=[("huge", (2 ** 64 - 1, 2), 0, b"", None)]), "tensor 'huge' dimension does not fit usize")
+    refused_bytes(pk, tmp_path, raw_gguf(seed, tensors=[("zero", (0,), 0, b"", None)]), "tensor 'zero' has a zero-sized dimension")
+    refused_bytes(pk, tmp_path, raw_gguf(seed, tensors=[("ragged", (100,), 12, b"", None)]), "tensor 'ragged' row width 100 is not divisible by Q4K block size 256")
+    refused_bytes(pk, tmp_path, raw_gguf(seed, tensors=[("odd", (96,), 6, b"\0" * 66, None)]), "require paired 32-element blocks (a multiple of 64)")
+    refused_bytes(pk, tmp_path, raw_gguf(seed, tensors=[("r5", (1, 1, 1, 1, 1), 0, f32s(1.0), None)]), "tensor 'r5' has rank 5; supported ranks are 1..=4")
+    refused_bytes(pk, tmp_path, raw_gguf(seed, tensors=[("n" * 64, (1,), 0, f32s(1.0), None)]), "is 64 bytes; maximum is 63")
+
+
+def test_bounded_strings_arrays_and_keys(pk, tmp_path):
+    """src/gguf.rs:2040-2052,2266-2292,2326-2345,3166-3203: a length word cannot make the parser reserve what the file does not
+    hold, and the decoded metadata is charged against one cumulative budget."""
+    seed = pk["seed"]
+    T_ARRAY, T_STR = 9, seed.T_STR
+    huge_string = struct.pack("<Q", 1 << 40)
+    refused_bytes(pk, tmp_path, raw_gguf(seed, metas=[seed._s("k") + struct.pack("<I", T_STR) + huge_string]), "GGUF string length 1099511627776 exceeds limit 16777216")
+    refused_bytes(pk, tmp_path, raw_gguf(seed, metas=[seed._s("k") + struct.pack("<I", T_STR) + struct.pack("<Q", 1000)]), "GGUF string length 1000 exceeds 0 remaining bytes")
+    big_array = struct.pack("<IQ", seed.T_U32, 1 << 30)
+    refused_bytes(pk, tmp_path, raw_gguf(seed, metas=[seed._kv("k", T_ARRAY, big_array)]), "GGUF array element count 1073741824 exceeds limit 1048576")
+    short_array = struct.pack("<IQ", seed.T_U32, 1000)
+    refused_bytes(pk, tmp_path, raw_gguf(seed, metas=[seed._kv("k", T_ARRAY, short_array)]), "needs at least 4000 bytes, but only 0 remain")
+    for key, why in (("Upper.case", "is not a dot-separated lowercase identifier"), ("a..b", "is not a dot-separated lowercase identifier"),
+                     ("", "GGUF metadata key cannot be empty"), ("caf\u00e9", "is not ASCII")):
+        refused_bytes(pk, tmp_path, raw_gguf(seed, metas=[seed._kv(key, seed.T_U32, struct.pack("<I", 1))]), why)
+    # seventeen strings of 16 MiB each pass their own limit and break the cumulative 256 MiB budget
+    one = struct.pack("<Q", 16 << 20) + b"a" * (16 << 20)
+    metas = [seed._s(f"s{i}") + struct.pack("<I", T_STR) + one for i in range(17)]
+    refused_bytes(pk, tmp_path, raw_gguf(seed, metas=metas), "GGUF decoded allocation budget exceeded while reserving string storage")
+
+
+def test_a_fifo_is_refused_without_blocking(pk, tmp_path):
+    """src/gguf.rs:3073-3098."""
+    import os
+    path = tmp_path / "pipe.gguf"
+    os.mkfifo(path)
+    with pytest.raises(pk["capi"].MkError, match="is not a regular file"):
+        pk["eng"].Model.inspect_gguf(path)

@@ -166,3 +166,22 @@ def test_vector_inner_sums_equal_the_scalar_loops(orc, tmp_path):
                                    C.c_void_p(x.ctypes.data), C.c_int64(T), C.c_void_p(want.ctypes.data), C.c_int(mode))
                 got = orc.qmatmul(qtype, w, rows, cols, x, mode)
                 assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (qtype, rows, cols, T, mode)
+
+
+def test_q4_0_and_q8_0_golden_blocks_of_the_reference(ops, orc):
+    """src/gguf.rs:3882-3971: one hand-made block of each format and the weights it must decode to - Q4_0 with scale 0.125
+    walks -1.0 ... 0.875 and back; Q8_0 with scale 0.007873535 (f16 0x2008) times the signed bytes."""
+    q4 = np.array([0x00, 0x30, 0xf0, 0xe1, 0xd2, 0xc3, 0xb4, 0xa5, 0x96, 0x87, 0x78, 0x69, 0x5a, 0x4b, 0x3c, 0x2d, 0x1e, 0x0f], np.uint8)
+    q8 = np.array([0x08, 0x20, 0x81, 0xc0, 0xe0, 0xf0, 0xf3, 0xff, 0x00, 0x01, 0x0d, 0x10, 0x20, 0x40, 0x7f, 0x5f, 0xa1, 0x2a, 0xd6, 0x19,
+                   0xe7, 0x03, 0xfd, 0x72, 0x8e, 0x4c, 0xb4, 0x33, 0xcd, 0x06, 0xfa, 0x01, 0xff, 0x00], np.uint8)
+    assert ops.row_bytes(2, 32) == orc.row_bytes(2, 32) == 18 and ops.row_bytes(8, 32) == orc.row_bytes(8, 32) == 34
+    want_q4 = np.array([-1.0 + i * 0.125 for i in range(16)] + [0.875 - i * 0.125 for i in range(16)], np.float32)
+    assert np.array_equal(orc.dequant(2, q4, 1, 32)[0], want_q4)
+    assert np.array_equal(ops.decode_rows(2, q4, 1, 32)[0], want_q4)
+    signed = np.array([-127, -64, -32, -16, -13, -1, 0, 1, 13, 16, 32, 64, 127, 95, -95, 42, -42, 25, -25, 3, -3, 114, -114, 76, -76, 51,
+                       -51, 6, -6, 1, -1, 0], np.float32)
+    want_q8 = signed * np.float32(0.007873535)
+    assert np.array_equal(orc.dequant(8, q8, 1, 32)[0], want_q8)
+    assert np.float32(np.frombuffer(q8[:2].tobytes(), np.float16)[0]) == np.float32(0.007873535)
+    # the product reads Q8_0 in place: the embedding-row path decodes the same block on the host side of the oracle only;
+    # the device decoders of Q8_0 are held to the oracle in the GPU kernel tests
