@@ -497,6 +497,11 @@ int64_t mk_row_bytes(int32_t type, int64_t cols);
 /* Host only: the load-time decoder of the block formats no kernel reads in place (MK_TYPE_Q4_0, Q5_0, Q5_1, Q2_K, Q3_K,
  * Q5_K, BF16): `rows` rows of mk_row_bytes(type, cols) bytes each -> out[rows][cols] f32.  Needs no GPU. */
 int32_t mk_decode_rows(int32_t type, const void* src, int64_t rows, int64_t cols, float* out);
+/* Host only: the loader's un-permutation of Llama Q/K rows (inverse_permute_llama_qk / inverse_permute_quantized_rows,
+ * src/gguf.rs:1833-1924): rows of `row_bytes` bytes move as opaque strings, source row head*d + 2*pair + lane to
+ * destination row head*d + lane*d/2 + pair with d = rows / heads.  Refuses a row count the heads do not divide and an odd
+ * head dimension.  src and dst must not overlap. */
+int32_t mk_unpermute_qk_rows(const void* src, int64_t rows, int64_t row_bytes, int32_t heads, void* dst);
 
 /* ------------------------------------------------------------------------------------------------
  * Kernel-level entry points (unit parity).  Host buffers in and out; each call stages its operands

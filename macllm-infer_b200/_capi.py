@@ -218,6 +218,7 @@ SIGNATURES = {
     "mk_seed_tensor": (_i32, [_u64, _u64, _f32, _i32, _i64, _i64, P]),
     "mk_row_bytes": (_i64, [_i32, _i64]),
     "mk_decode_rows": (_i32, [_i32, P, _i64, _i64, P]),
+    "mk_unpermute_qk_rows": (_i32, [C.c_void_p, _i64, _i64, _i32, C.c_void_p]),
     "mk_k_quantize": (_i32, [_i32, P, _i32, _i32, P, P, P]),
     "mk_k_add_norm": (_i32, [P, P, _f32, P, P, _f32, _i32, _i32, P]),
     "mk_k_qmatmul": (_i32, [_i32, P, _i64, _i64, P, _i32, P, _i32]),

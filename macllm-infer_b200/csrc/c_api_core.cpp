@@ -64,6 +64,13 @@ int32_t mk_decode_rows(int32_t type, const void* src, int64_t rows, int64_t cols
     });
 }
 
+int32_t mk_unpermute_qk_rows(const void* src, int64_t rows, int64_t row_bytes, int32_t heads, void* dst) {
+    return guarded([&] {
+        if (src == nullptr || dst == nullptr || row_bytes <= 0) throw std::runtime_error("mk_unpermute_qk_rows: bad arguments");
+        unpermute_qk_rows_host(static_cast<const uint8_t*>(src), rows, row_bytes, heads, static_cast<uint8_t*>(dst));
+    });
+}
+
 int32_t mk_host_sample_greedy(float* logits, int32_t vocab, const uint32_t* history, int32_t n_history, float repetition_penalty,
                               const uint32_t* generated, int32_t n_generated, float presence_penalty, float frequency_penalty,
                               uint32_t* token) {

@@ -89,5 +89,9 @@ int64_t gguf_row_bytes(int type, int64_t cols);
 // host into a dense f32 matrix.  decode_rows_host is that decoder (host only, no GPU).
 bool decoded_at_load(int type);
 void decode_rows_host(int type, const void* src, int64_t rows, int64_t cols, float* out);
+// llama.cpp stores Llama Q/K rows pair-interleaved per head; the loader puts them back in half-split order so that the
+// half-split rotation applies: source row head*d + 2*pair + lane -> destination row head*d + lane*d/2 + pair, rows moved
+// as opaque byte strings so block formats stay compressed (inverse_permute_quantized_rows, src/gguf.rs:1888-1924).
+void unpermute_qk_rows_host(const uint8_t* src, int64_t rows, int64_t row_bytes, int heads, uint8_t* dst);
 
 }  // namespace mk

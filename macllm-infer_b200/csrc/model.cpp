@@ -249,12 +249,8 @@ void Model::upload_matrix(const GgufFile& f, const std::string& name, int64_t ro
         // llama.cpp stores Q/K rows pair-interleaved; undo it so the half-split rotation applies
         // (src/gguf.rs:1888-1924): source row head*d + 2*pair + lane -> dest head*d + lane*d/2 + pair.
         int64_t rb = gguf_row_bytes(t.type, cols);
-        int d = (int)(rows / heads);
         std::vector<uint8_t> tmp((size_t)(rb * rows));
-        for (int h = 0; h < heads; ++h)
-            for (int lane = 0; lane < 2; ++lane)
-                for (int pair = 0; pair < d / 2; ++pair)
-                    memcpy(&tmp[(size_t)((h * d + lane * (d / 2) + pair) * rb)], t.data + (int64_t)(h * d + 2 * pair + lane) * rb, (size_t)rb);
+        unpermute_qk_rows_host(t.data, rows, rb, heads, tmp.data());
         upload_weight(t.type, tmp.data(), rows, cols, out, stream_);
     }
     spec_.weight_bytes += out.w.bytes;

@@ -31,6 +31,18 @@ int device_sm_count() {
     return n;
 }
 
+void unpermute_qk_rows_host(const uint8_t* src, int64_t rows, int64_t row_bytes, int heads, uint8_t* dst) {
+    if (heads <= 0 || rows <= 0 || rows % heads != 0)
+        throw std::runtime_error("cannot inverse-permute compressed Llama Q/K shape [" + std::to_string(rows) + " rows] across " +
+                                 std::to_string(heads) + " heads");
+    const int64_t d = rows / heads;
+    if (d % 2 != 0) throw std::runtime_error("Llama Q/K head dimension " + std::to_string(d) + " must be even");
+    for (int64_t h = 0; h < heads; ++h)
+        for (int64_t lane = 0; lane < 2; ++lane)
+            for (int64_t pair = 0; pair < d / 2; ++pair)
+                memcpy(dst + (h * d + lane * (d / 2) + pair) * row_bytes, src + (h * d + 2 * pair + lane) * row_bytes, (size_t)row_bytes);
+}
+
 int64_t gguf_row_bytes(int type, int64_t cols) {
     switch (type) {
         case QT_F32: return cols * 4;

@@ -32,6 +32,14 @@ def decode_rows(qtype: int, w: np.ndarray, rows: int, cols: int) -> np.ndarray:
     return out
 
 
+def unpermute_qk_rows(raw: np.ndarray, rows: int, heads: int) -> np.ndarray:
+    """The loader's un-permutation of Llama Q/K rows on raw row bytes (any block format)."""
+    raw = np.ascontiguousarray(raw).reshape(-1).view(np.uint8)
+    out = np.empty_like(raw)
+    capi.check(capi.lib().mk_unpermute_qk_rows(_p(raw), rows, raw.size // max(rows, 1), heads, _p(out)))
+    return out
+
+
 def seed_tensor(seed: int, stream: int, std: float, qtype: int, rows: int, cols: int) -> np.ndarray:
     """N(0, std) weights from the counter-based generator, quantised to `qtype`; returns raw block bytes."""
     rb = row_bytes(qtype, cols)

@@ -185,3 +185,28 @@ def test_q4_0_and_q8_0_golden_blocks_of_the_reference(ops, orc):
     assert np.float32(np.frombuffer(q8[:2].tobytes(), np.float16)[0]) == np.float32(0.007873535)
     # the product reads Q8_0 in place: the embedding-row path decodes the same block on the host side of the oracle only;
     # the device decoders of Q8_0 are held to the oracle in the GPU kernel tests
+
+
+def test_llama_query_key_rows_are_unpermuted_like_the_reference(ops, orc):
+    """src/gguf.rs:3663-3683,4328-4395: eight rows across two heads go to the order 0 2 1 3 4 6 5 7; rows of Q8_0 and Q4_0
+    blocks move as whole byte strings and decode to the same first weights as the reference's."""
+    from oracle import decoder
+    import importlib
+    capi = importlib.import_module("macllm_infer_b200._capi")
+    dense = np.arange(8, dtype=np.float32)
+    want = np.array([0, 2, 1, 3, 4, 6, 5, 7], np.float32)
+    assert np.array_equal(ops.unpermute_qk_rows(dense.view(np.uint8), 8, 2).view(np.float32), want)
+    assert np.array_equal(decoder._unpermute(dense.view(np.uint8), 8, 2, 4).view(np.float32), want)
+    one = np.frombuffer(np.float16(1.0).tobytes(), np.uint8)
+    q8 = np.concatenate([np.concatenate([one, np.full(32, v, np.uint8)] * 2) for v in range(1, 9)])
+    q4 = np.concatenate([np.concatenate([one, np.full(16, c | (c << 4), np.uint8)] * 2) for c in range(8)])
+    for qtype, raw, first in ((8, q8, [1, 3, 2, 4, 5, 7, 6, 8]), (2, q4, [-8, -6, -7, -5, -4, -2, -3, -1])):
+        assert raw.size == 8 * orc.row_bytes(qtype, 64)
+        moved = ops.unpermute_qk_rows(raw, 8, 2)
+        assert np.array_equal(moved, decoder._unpermute(raw, 8, 2, raw.size // 8))
+        rows = orc.dequant(qtype, moved, 8, 64)
+        assert list(rows[:, 0]) == first and all(np.all(rows[r] == rows[r, 0]) for r in range(8))
+    with pytest.raises(capi.MkError, match="across 3 heads"):
+        ops.unpermute_qk_rows(dense.view(np.uint8), 8, 3)
+    with pytest.raises(capi.MkError, match="head dimension 1 must be even"):
+        ops.unpermute_qk_rows(dense.view(np.uint8), 8, 8)
