@@ -421,8 +421,9 @@ class CompletionServer:
                         job.seen = n
                     if state == "done":
                         first = job.t_first if job.t_first is not None else now
+                        reason = engine.metrics(rid)["finish_reason"]     # the engine's own FinishReason, not a guess from the count
                         job.events.put(("finished", dict(generated_tokens=n, prompt_tokens=len(job.tokens), cached_prompt_tokens=int(cached),
-                                                         stop_type="limit" if n == job.settings["n_predict"] else "stop",
+                                                         stop_type={"length": "limit", "stop": "stop"}.get(reason, "cancelled"),
                                                          prefill_ms=(first - job.t_submit) * 1e3, ttft_ms=(first - job.t_submit) * 1e3,
                                                          total_ms=(now - job.t_submit) * 1e3)))
                         del active[rid]

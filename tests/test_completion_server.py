@@ -333,3 +333,49 @@ def test_a_client_that_leaves_cancels_its_request_and_the_peer_finishes(mk, srv_
         assert st == 200 and json.loads(b)["worker"] == "ready"
     finally:
         s.stop()
+
+
+class _ShortEngine:
+    """An engine that ends every request after one token, whatever was asked: the endpoint must notice."""
+
+    def __init__(self, inner, eng):
+        self._inner, self._eng = inner, eng
+
+    def submit(self, requests, atomic_batch=False):
+        short = [self._eng.Request(list(r.prompt), 1, ignore_stop_tokens=True) for r in requests]
+        return self._inner.submit(short, atomic_batch)
+
+    def __getattr__(self, name):
+        return getattr(self._inner, name)
+
+
+@pytest.mark.parametrize("stream", [False, True])
+def test_completion_requires_the_exact_requested_token_boundary(mk, srv_mod, stream):
+    """validate_raw_completion_metrics (src/server.rs:808-820; its test at src/server.rs:5361-5388): a generation that ends short
+    of n_predict is an error of the server, never a shorter success - collected or streamed (src/server.rs:5250-5304: the
+    body must not carry the terminal "stop_type":"limit")."""
+    eng = importlib.import_module("macllm_infer_b200.engine")
+
+    def factory():
+        model = eng.Model.fake(vocab=64, max_context=256, kv_capacity_tokens=2048)
+        return _ShortEngine(eng.Engine(model, max_active_sequences=2, scheduler_token_budget=64, prefill_token_quantum=32), eng), model
+    s = srv_mod.CompletionServer(factory, metadata=dict(served_model="test-model", device="cpu", dtype="f32")).start()
+    try:
+        st, ctype, b = call(s, "POST", "/completion", body(srv_mod, n_predict=3, stream=stream))
+        text = b.decode()
+        assert "raw completion ended after 1 tokens with Length; expected the fixed 3-token limit" in text
+        assert '"stop_type":"limit"' not in text
+        if stream:
+            assert st == 200 and ctype == "text/event-stream"
+            events = [json.loads(line[6:]) for line in text.split("\n\n") if line.startswith("data: ")]
+            assert events[0]["tokens"] and events[-1]["error"]["type"] == "server_error"
+        else:
+            assert st == 500 and json.loads(b)["error"]["type"] == "server_error"
+        # the unit rule itself (src/server.rs:5361-5388)
+        settings = {"n_predict": 32}
+        good = dict(generated_tokens=32, stop_type="limit")
+        assert srv_mod._check_terminal(settings, good) is None
+        assert srv_mod._check_terminal(settings, dict(good, generated_tokens=31)) is not None
+        assert srv_mod._check_terminal(settings, dict(good, stop_type="stop")) is not None
+    finally:
+        s.stop()
