@@ -193,6 +193,105 @@ def moe_route(logits: np.ndarray, k: int):
     return sel, w
 
 
+def _cu(cu_seqlens, rows):
+    cu = np.ascontiguousarray(cu_seqlens, dtype=np.int32)
+    if cu.ndim != 1 or cu.size < 2 or cu[0] != 0 or cu[-1] != rows or np.any(np.diff(cu) < 0):
+        raise ValueError("lane boundaries must rise from 0 to the number of rows")
+    return cu
+
+
+def gated_delta_decay(alpha, time_bias, state_decay) -> np.ndarray:
+    """exp(softplus(alpha + time_bias) * state_decay) for alpha [tokens, heads] (crates/macllm-kernels/src/gated_delta.rs:13-60,96-104)."""
+    alpha, time_bias, state_decay = _f32(alpha), _f32(time_bias), _f32(state_decay)
+    if alpha.ndim != 2 or 0 in alpha.shape:
+        raise ValueError("Gated DeltaNet decay requires non-empty token and head dimensions")
+    if time_bias.shape != (alpha.shape[1],) or state_decay.shape != (alpha.shape[1],):
+        raise ValueError(f"Gated DeltaNet decay has alpha shape {list(alpha.shape)}, time bias {list(time_bias.shape)} and state decay {list(state_decay.shape)}")
+    out = np.empty_like(alpha)
+    lib().orc_gated_delta_decay(_p(alpha), _p(time_bias), _p(state_decay), C.c_int64(alpha.shape[0]), alpha.shape[1], _p(out))
+    return out
+
+
+def gated_delta_recurrence(query, key, value, decay, beta, state, cu_seqlens=None):
+    """query / key [rows, heads, key_dim], value [rows, heads, value_dim], decay / beta [rows, heads], state
+    [lanes, heads, key_dim, value_dim]; returns (out [rows, heads, value_dim], next state).  One lane unless `cu_seqlens`
+    says otherwise (crates/macllm-kernels/src/gated_delta.rs:139-170,236-270,396-431)."""
+    query, key, value, decay, beta, state = (_f32(t) for t in (query, key, value, decay, beta, state))
+    rows, heads, key_dim = query.shape
+    if heads == 0 or key_dim == 0 or key.shape != query.shape:
+        raise ValueError("Gated DeltaNet decode has incompatible query/key geometry")
+    value_dim = value.shape[2] if value.ndim == 3 else 0
+    cu = _cu([0, rows] if cu_seqlens is None else cu_seqlens, rows)
+    lanes = cu.size - 1
+    if (value.shape[:2] != (rows, heads) or value_dim == 0 or decay.shape != (rows, heads) or beta.shape != (rows, heads)
+            or state.shape != (lanes, heads, key_dim, value_dim)):
+        raise ValueError(f"Gated DeltaNet decode has query {list(query.shape)}, key {list(key.shape)}, value {list(value.shape)}, "
+                         f"decay {list(decay.shape)}, beta {list(beta.shape)} and state {list(state.shape)}")
+    out = np.empty((rows, heads, value_dim), np.float32)
+    nxt = np.empty_like(state)
+    lib().orc_gated_delta_recurrence(_p(query), _p(key), _p(value), _p(decay), _p(beta), _p(cu), lanes, heads, key_dim, value_dim,
+                                     _p(state), _p(nxt), _p(out))
+    return out, nxt
+
+
+def mamba2_geometry(xbc_width: int, heads: int, head_dim: int, state_size: int) -> int:
+    """The group count a projection width implies, with the refusals of ScanGeometry::validate
+    (crates/macllm-kernels/src/mamba2.rs:64-150)."""
+    if min(heads, head_dim, state_size) <= 0:
+        raise ValueError("Mamba2 scan requires non-empty dimensions")
+    inner = heads * head_dim
+    if xbc_width < inner:
+        raise ValueError(f"Mamba2 xBC width {xbc_width} is smaller than inner size {inner}")
+    bc = xbc_width - inner
+    if bc == 0 or bc % (2 * state_size) != 0:
+        raise ValueError(f"Mamba2 xBC width {xbc_width} cannot encode paired B/C states of width {state_size}")
+    groups = bc // (2 * state_size)
+    if heads % groups != 0:
+        raise ValueError(f"Mamba2 scan head count {heads} is not divisible by inferred group count {groups}")
+    return groups
+
+
+def mamba2_scan(xbc, raw_dt, dt_bias, a, d, state, cu_seqlens=None):
+    """xbc [rows, H*P + 2*G*N] laid out [x | B | C], raw_dt [rows, H], dt_bias / a / d [H], state [lanes, H, P, N]; returns
+    (out [rows, H, P], final state) (crates/macllm-kernels/src/mamba2.rs:17-150,255-289)."""
+    xbc, raw_dt, dt_bias, a, d, state = (_f32(t) for t in (xbc, raw_dt, dt_bias, a, d, state))
+    rows, width = xbc.shape
+    cu = _cu([0, rows] if cu_seqlens is None else cu_seqlens, rows)
+    lanes = cu.size - 1
+    if state.ndim != 4 or state.shape[0] != lanes:
+        raise ValueError("Mamba2 scan state must be [lanes, heads, head_dim, state_size]")
+    _, heads, head_dim, state_size = state.shape
+    if rows == 0:
+        raise ValueError("Mamba2 scan requires non-empty dimensions")
+    if raw_dt.shape != (rows, heads) or dt_bias.shape != (heads,) or a.shape != (heads,) or d.shape != (heads,):
+        raise ValueError(f"Mamba2 scan has xBC {list(xbc.shape)}, dt {list(raw_dt.shape)}, dt bias {list(dt_bias.shape)}, A {list(a.shape)}, "
+                         f"D {list(d.shape)}, and state {list(state.shape[1:])}")
+    groups = mamba2_geometry(width, heads, head_dim, state_size)
+    out = np.empty((rows, heads, head_dim), np.float32)
+    nxt = np.empty_like(state)
+    lib().orc_mamba2_scan(_p(xbc), _p(raw_dt), _p(dt_bias), _p(a), _p(d), _p(cu), lanes, heads, head_dim, state_size, groups,
+                          _p(state), _p(nxt), _p(out))
+    return out, nxt
+
+
+def short_conv(bcx, kernel, tail, cu_seqlens=None):
+    """bcx [rows, 3*hidden] laid out [B | C | x], kernel [hidden, K], tail [lanes, K-1, hidden]; returns (C * conv(B * x), new tail)
+    (src/decoder.rs:1430-1492)."""
+    bcx, kernel, tail = _f32(bcx), _f32(kernel), _f32(tail)
+    rows = bcx.shape[0]
+    hidden, K = kernel.shape
+    cu = _cu([0, rows] if cu_seqlens is None else cu_seqlens, rows)
+    lanes = cu.size - 1
+    if bcx.shape != (rows, 3 * hidden) or K < 1:
+        raise ValueError("short-convolution state geometry does not match its layer")
+    if tail.shape != (lanes, K - 1, hidden):
+        raise ValueError(f"short-convolution tail has shape {list(tail.shape)}, expected [{lanes}, {K - 1}, {hidden}]")
+    out = np.empty((rows, hidden), np.float32)
+    nxt = np.empty_like(tail)
+    lib().orc_short_conv(_p(bcx), _p(kernel), _p(cu), lanes, hidden, K, _p(tail), _p(nxt), _p(out))
+    return out, nxt
+
+
 def argmax(v: np.ndarray) -> int:
     v = _f32(v)
     return int(lib().orc_argmax(_p(v), C.c_int64(v.size)))

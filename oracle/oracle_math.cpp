@@ -670,6 +670,114 @@ void orc_moe_route(const float* logits, int64_t T, int experts, int k, int32_t* 
     }
 }
 
+// ---------------------------------------------------------------- recurrent mixers
+// Stable softplus as the reference writes it: max(x, 0) + ln(1 + exp(-|x|)).
+static inline float softplus_stable(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
+
+// Gated DeltaNet decay: exp(softplus(alpha + time_bias[h]) * state_decay[h]) for alpha [tokens][heads]
+// (crates/macllm-kernels/src/gated_delta.rs:96-104).
+void orc_gated_delta_decay(const float* alpha, const float* time_bias, const float* state_decay, int64_t tokens, int heads, float* out) {
+    for (int64_t i = 0; i < tokens * heads; ++i) {
+        int h = (int)(i % heads);
+        out[i] = expf(softplus_stable(alpha[i] + time_bias[h]) * state_decay[h]);
+    }
+}
+
+// Gated DeltaNet recurrence over ragged lanes (crates/macllm-kernels/src/gated_delta.rs:396-431).  Rows of lane l are
+// cu[l] .. cu[l+1]; query / key [rows][heads][key_dim] (already normalised, query already scaled), value / out
+// [rows][heads][value_dim], decay / beta [rows][heads]; state [lanes][heads][key_dim][value_dim], read from state_in and
+// written to state_out (the input stays as it was: a failed forward must be able to fall back to it).  Per head and value
+// column: memory = sum_k S[k] * decay * key[k]; delta = (value - memory) * beta; S[k] = S[k] * decay + key[k] * delta;
+// out = sum_k S[k] * query[k] - every product and sum rounded on its own, in this order.
+void orc_gated_delta_recurrence(const float* query, const float* key, const float* value, const float* decay, const float* beta,
+                                const int32_t* cu, int lanes, int heads, int key_dim, int value_dim, const float* state_in,
+                                float* state_out, float* out) {
+    for (int l = 0; l < lanes; ++l)
+        for (int h = 0; h < heads; ++h) {
+            const int64_t sb = ((int64_t)l * heads + h) * key_dim * value_dim;
+            for (int v = 0; v < value_dim; ++v) {
+                for (int k = 0; k < key_dim; ++k) state_out[sb + (int64_t)k * value_dim + v] = state_in[sb + (int64_t)k * value_dim + v];
+                for (int64_t r = cu[l]; r < cu[l + 1]; ++r) {
+                    const int64_t th = r * heads + h;
+                    const float* kk = key + th * key_dim; const float* qq = query + th * key_dim;
+                    float memory = 0.f;
+                    for (int k = 0; k < key_dim; ++k) memory += state_out[sb + (int64_t)k * value_dim + v] * decay[th] * kk[k];
+                    const float delta = (value[th * value_dim + v] - memory) * beta[th];
+                    float projected = 0.f;
+                    for (int k = 0; k < key_dim; ++k) {
+                        float* sp = state_out + sb + (int64_t)k * value_dim + v;
+                        const float next = *sp * decay[th] + kk[k] * delta;
+                        *sp = next;
+                        projected += next * qq[k];
+                    }
+                    out[th * value_dim + v] = projected;
+                }
+            }
+        }
+}
+
+// Mamba2 selective scan over ragged lanes (crates/macllm-kernels/src/mamba2.rs:255-289).  xbc [rows][H*P + 2*G*N] laid out
+// [x | B | C], raw_dt [rows][H], dt_bias / a / d [H], state [lanes][H][P][N]; out [rows][H][P].  Per token and head:
+// delta = softplus(dt + dt_bias), decay = exp(delta * a); per position: S[n] = decay * S[n] + delta * x * B[n],
+// out = sum_n S[n] * C[n] + d * x.  Heads are divided evenly into G contiguous groups that share B and C.
+void orc_mamba2_scan(const float* xbc, const float* raw_dt, const float* dt_bias, const float* a, const float* d, const int32_t* cu,
+                     int lanes, int heads, int head_dim, int state_size, int groups, const float* state_in, float* state_out, float* out) {
+    const int64_t inner = (int64_t)heads * head_dim, gsw = (int64_t)groups * state_size, width = inner + 2 * gsw;
+    const int hpg = heads / groups;
+    for (int l = 0; l < lanes; ++l) {
+        float* S = state_out + (int64_t)l * inner * state_size;
+        memcpy(S, state_in + (int64_t)l * inner * state_size, sizeof(float) * (size_t)(inner * state_size));
+        for (int64_t r = cu[l]; r < cu[l + 1]; ++r) {
+            const float* row = xbc + r * width;
+            for (int h = 0; h < heads; ++h) {
+                const float delta = softplus_stable(raw_dt[r * heads + h] + dt_bias[h]);
+                const float dec = expf(delta * a[h]);
+                const float* B = row + inner + (int64_t)(h / hpg) * state_size;
+                const float* Cv = row + inner + gsw + (int64_t)(h / hpg) * state_size;
+                for (int p = 0; p < head_dim; ++p) {
+                    const int64_t lane_i = (int64_t)h * head_dim + p;
+                    const float x = row[lane_i];
+                    float projected = 0.f;
+                    for (int n = 0; n < state_size; ++n) {
+                        float* sp = S + lane_i * state_size + n;
+                        const float next = dec * *sp + delta * x * B[n];
+                        *sp = next;
+                        projected += next * Cv[n];
+                    }
+                    out[r * inner + lane_i] = projected + d[h] * x;
+                }
+            }
+        }
+    }
+}
+
+// Short convolution over ragged lanes (ShortConvolution::forward_lane after the input projection and before the output
+// projection, src/decoder.rs:1436-1492): bcx [rows][3*hidden] laid out [B | C | x]; Bx = B * x; a causal depthwise
+// cross-correlation of Bx with kernel [hidden][K] (tap K-1 meets the current token) over the lane's tail of the last
+// K-1 Bx rows [lanes][K-1][hidden] followed by its new rows, summed from the oldest tap on; out = C * that.  The new
+// tail is the last K-1 rows of the window.
+void orc_short_conv(const float* bcx, const float* kernel, const int32_t* cu, int lanes, int hidden, int K, const float* tail_in,
+                    float* tail_out, float* out) {
+    const int hist = K - 1;
+    for (int l = 0; l < lanes; ++l) {
+        const int64_t n = cu[l + 1] - cu[l];
+        std::vector<float> window((size_t)((hist + n) * hidden));
+        for (int64_t i = 0; i < (int64_t)hist * hidden; ++i) window[(size_t)i] = tail_in[(int64_t)l * hist * hidden + i];
+        for (int64_t t = 0; t < n; ++t)
+            for (int c = 0; c < hidden; ++c) {
+                const float* row = bcx + (cu[l] + t) * 3 * hidden;
+                window[(size_t)((hist + t) * hidden + c)] = row[c] * row[2 * hidden + c];
+            }
+        for (int64_t t = 0; t < n; ++t)
+            for (int c = 0; c < hidden; ++c) {
+                float sum = window[(size_t)(t * hidden + c)] * kernel[(int64_t)c * K];
+                for (int j = 1; j < K; ++j) sum += window[(size_t)((t + j) * hidden + c)] * kernel[(int64_t)c * K + j];
+                out[(cu[l] + t) * hidden + c] = bcx[(cu[l] + t) * 3 * hidden + hidden + c] * sum;
+            }
+        for (int64_t i = 0; i < (int64_t)hist * hidden; ++i) tail_out[(int64_t)l * hist * hidden + i] = window[(size_t)(n * hidden + i)];
+    }
+}
+
 // ---------------------------------------------------------------- sampling
 // First-index argmax under a total order on floats (src/sampling.rs:425-433).
 static inline int32_t total_key(float f) { int32_t b; memcpy(&b, &f, 4); return b ^ (int32_t)(((uint32_t)(b >> 31)) >> 1); }

@@ -288,7 +288,8 @@ class _SlowEngine:
 
 @pytest.mark.parametrize("stream", [True, False])
 def test_a_client_that_leaves_cancels_its_request_and_the_peer_finishes(mk, srv_mod, stream):
-    """Dropping the ticket sets the sticky cancellation flag (src/engine.rs:1141-1145,4397-4411): the request of a client that
+    """Dropping the ticket sets the sticky cancellation flag (src/engine.rs:1141-1145,4397-4411; the endpoint's own case
+    `dropping_a_started_sse_body_cancels_the_worker_ticket`, src/server.rs:7192-7250): the request of a client that
     closed its connection stops taking ticks, its pages return to the pool, and a peer in the same batch is served in full."""
     import socket
     import time

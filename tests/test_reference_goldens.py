@@ -214,3 +214,19 @@ def test_router_refuses_non_finite_logits_and_bad_counts_on_the_gpu(ops, mk):
             ops.moe_route(np.array([[1.0, 2.0, 3.0, 0.5]], np.float32), k)
     sel, w = ops.moe_route(np.array([[1.0, 2.0, 3.0, 0.5]], np.float32), 2)    # the device still answers
     assert sel.tolist() == [[2, 1]]
+
+
+def test_partial_rope_rotates_only_the_configured_prefix_on_the_oracle(orc):
+    """partial_rope_rotates_only_the_configured_prefix (src/decoder.rs:8464-8500): head_dim 4, rotary_dim 2, theta 10000,
+    position 1 - the last two dimensions of every head pass through untouched, the first two turn by one radian."""
+    cos, sin = orc.rope_tables(10_000.0, 2, 8)
+    q = np.array([[1.0, 2.0, 30.0, 40.0, 3.0, 4.0, 50.0, 60.0]], np.float32)
+    k = np.array([[5.0, 6.0, 70.0, 80.0, 7.0, 8.0, 90.0, 100.0]], np.float32)
+    for x in (q, k):
+        got = orc.rope_apply(x, 2, 4, 2, [1], cos, sin).reshape(2, 4)
+        src = x.reshape(2, 4)
+        assert np.array_equal(got[:, 2:], src[:, 2:])
+        assert np.max(np.abs(got[:, :2] - src[:, :2])) > 1e-3
+        c, s = np.float32(np.cos(1.0)), np.float32(np.sin(1.0))
+        want = np.stack([src[:, 0] * c - src[:, 1] * s, src[:, 1] * c + src[:, 0] * s], axis=1)
+        assert np.allclose(got[:, :2], want, rtol=1e-6, atol=1e-6)
