@@ -625,6 +625,36 @@ int32_t mk_k_attention_plan(const int32_t* start_pos, const int32_t* n_tokens, i
                             int32_t block_tokens, int32_t* shares_out, int32_t* tiles_out, int32_t* max_entries_out);
 
 /* argmax of src/sampling.rs:425-433 for each row of logits [B][vocab]. */
+/* ------------------------------------------------------------------------------------------------
+ * Recurrent sequence mixers over ragged lanes (kernel level).  Rows of lane l are cu_seqlens[l] .. cu_seqlens[l+1] of the
+ * packed batch.  Each call reads a lane's state from *_in and writes the next state to *_out; the input is never modified,
+ * so a forward that fails later can fall back to it (crates/macllm-kernels/src/gated_delta.rs:131-137).
+ * ---------------------------------------------------------------------------------------------- */
+/* decay_factors (crates/macllm-kernels/src/gated_delta.rs:13-60,96-104): out[t][h] = exp(softplus(alpha[t][h] + time_bias[h]) *
+ * state_decay[h]), softplus in its stable form. */
+int32_t mk_k_gated_delta_decay(const float* alpha, const float* time_bias, const float* state_decay, int32_t tokens, int32_t heads, float* out);
+/* decode_recurrence / prefill_recurrence (crates/macllm-kernels/src/gated_delta.rs:139-340,396-431).  query / key
+ * [rows][heads][key_dim] (normalised; the query carries its scale), value / out [rows][heads][value_dim], decay / beta
+ * [rows][heads], state [lanes][heads][key_dim][value_dim].  Per head and value column, token by token:
+ * memory = sum_k S[k]*decay*key[k]; delta = (value - memory)*beta; S[k] = S[k]*decay + key[k]*delta; out = sum_k S[k]*query[k],
+ * every product and sum rounded on its own in that order. */
+int32_t mk_k_gated_delta_recurrence(const float* query, const float* key, const float* value, const float* decay, const float* beta,
+                                    const int32_t* cu_seqlens, int32_t lanes, int32_t heads, int32_t key_dim, int32_t value_dim,
+                                    const float* state_in, float* state_out, float* out);
+/* scan (crates/macllm-kernels/src/mamba2.rs:17-150,255-289).  xbc [rows][xbc_width] laid out [x | B | C] with
+ * xbc_width = heads*head_dim + 2*groups*state_size (the group count is derived from the width and refused like
+ * ScanGeometry::validate refuses it), raw_dt [rows][heads], dt_bias / a_decay / d_skip [heads], state
+ * [lanes][heads][head_dim][state_size], out [rows][heads][head_dim].  delta = softplus(dt + dt_bias), decay = exp(delta*a);
+ * S[n] = decay*S[n] + delta*x*B[n]; out = sum_n S[n]*C[n] + d*x. */
+int32_t mk_k_mamba2_scan(const float* xbc, int64_t xbc_width, const float* raw_dt, const float* dt_bias, const float* a_decay, const float* d_skip,
+                         const int32_t* cu_seqlens, int32_t lanes, int32_t heads, int32_t head_dim, int32_t state_size, const float* state_in,
+                         float* state_out, float* out);
+/* ShortConvolution::forward_lane between its two projections (src/decoder.rs:1436-1492).  bcx [rows][3*hidden] laid out
+ * [B | C | x], kernel [hidden][taps] (oldest tap first; the last tap meets the current row), tail [lanes][taps-1][hidden] = the
+ * lane's last taps-1 rows of B*x (zeros for a fresh lane); out [rows][hidden] = C * sum_j kernel[j] * (B*x)[row - (taps-1) + j]. */
+int32_t mk_k_short_conv(const float* bcx, const float* kernel, const int32_t* cu_seqlens, int32_t lanes, int32_t hidden, int32_t taps,
+                        const float* tail_in, float* tail_out, float* out);
+
 int32_t mk_k_argmax(const float* logits, int32_t B, int32_t vocab, uint32_t* out);
 /* Test support for expert parallelism with data-parallel lanes: the dispatch / regroup / return / wait kernels of all
  * `ranks` ranks run on ONE device, stage by stage on one stream (every flag a kernel waits for was published by an earlier

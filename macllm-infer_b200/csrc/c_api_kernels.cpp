@@ -9,6 +9,7 @@
 #include "host_sampler.h"
 #include "attention_tc.h"
 #include "qgemm_tc.h"
+#include "recurrent.h"
 #include <vector>
 #include <cstring>
 
@@ -484,6 +485,119 @@ int32_t mk_k_attention_step(const mk_attn_case* c) {
         vpool.download(c->v_pool, pool_elems * esz);
         MK_CUDA(cudaDeviceSynchronize());
         if (flag != 0) throw std::runtime_error("mk_k_attention_step: batch descriptor index out of range (flag " + std::to_string(flag) + ")");
+    });
+}
+
+namespace {
+
+// cu_seqlens as the launchers want it: on the device, rising from 0 to the number of rows
+int32_t checked_rows(const int32_t* cu, int32_t lanes, const char* what) {
+    if (cu == nullptr || lanes <= 0 || cu[0] != 0) throw std::runtime_error(std::string(what) + ": lane boundaries must rise from 0 to the number of rows");
+    for (int32_t l = 0; l < lanes; ++l)
+        if (cu[l + 1] < cu[l]) throw std::runtime_error(std::string(what) + ": lane boundaries must rise from 0 to the number of rows");
+    return cu[lanes];
+}
+
+}  // namespace
+
+int32_t mk_k_gated_delta_decay(const float* alpha, const float* time_bias, const float* state_decay, int32_t tokens, int32_t heads, float* out) {
+    return guarded([&] {
+        require_device();
+        if (tokens <= 0 || heads <= 0) throw std::runtime_error("Gated DeltaNet decay requires non-empty token and head dimensions");
+        const size_t n = (size_t)tokens * heads * 4;
+        DevBuf da(n), db((size_t)heads * 4), ds((size_t)heads * 4), dout(n);
+        da.upload(alpha, n);
+        db.upload(time_bias, (size_t)heads * 4);
+        ds.upload(state_decay, (size_t)heads * 4);
+        launch_gated_delta_decay(da.as<float>(), db.as<float>(), ds.as<float>(), tokens, heads, dout.as<float>(), nullptr);
+        MK_CUDA(cudaDeviceSynchronize());
+        dout.download(out, n);
+        MK_CUDA(cudaDeviceSynchronize());
+    });
+}
+
+int32_t mk_k_gated_delta_recurrence(const float* query, const float* key, const float* value, const float* decay, const float* beta,
+                                    const int32_t* cu_seqlens, int32_t lanes, int32_t heads, int32_t key_dim, int32_t value_dim,
+                                    const float* state_in, float* state_out, float* out) {
+    return guarded([&] {
+        require_device();
+        if (heads <= 0 || key_dim <= 0 || value_dim <= 0) throw std::runtime_error("Gated DeltaNet decode has incompatible query/key geometry");
+        const int32_t rows = checked_rows(cu_seqlens, lanes, "mk_k_gated_delta_recurrence");
+        if (rows <= 0) throw std::runtime_error("mk_k_gated_delta_recurrence: no rows");
+        const size_t qk = (size_t)rows * heads * key_dim * 4, vv = (size_t)rows * heads * value_dim * 4, ctl = (size_t)rows * heads * 4;
+        const size_t st = (size_t)lanes * heads * key_dim * value_dim * 4;
+        DevBuf dq(qk), dk(qk), dv(vv), dd(ctl), db(ctl), dcu((size_t)(lanes + 1) * 4), dsi(st), dso(st), dout(vv);
+        dq.upload(query, qk);
+        dk.upload(key, qk);
+        dv.upload(value, vv);
+        dd.upload(decay, ctl);
+        db.upload(beta, ctl);
+        dcu.upload(cu_seqlens, (size_t)(lanes + 1) * 4);
+        dsi.upload(state_in, st);
+        GatedDeltaArgs a;
+        a.query = dq.as<float>(); a.key = dk.as<float>(); a.value = dv.as<float>(); a.decay = dd.as<float>(); a.beta = db.as<float>();
+        a.cu = dcu.as<int32_t>(); a.state_in = dsi.as<float>(); a.state_out = dso.as<float>(); a.out = dout.as<float>();
+        a.lanes = lanes; a.heads = heads; a.key_dim = key_dim; a.value_dim = value_dim;
+        launch_gated_delta_recurrence(a, nullptr);
+        MK_CUDA(cudaDeviceSynchronize());
+        dso.download(state_out, st);
+        dout.download(out, vv);
+        MK_CUDA(cudaDeviceSynchronize());
+    });
+}
+
+int32_t mk_k_mamba2_scan(const float* xbc, int64_t xbc_width, const float* raw_dt, const float* dt_bias, const float* a_decay, const float* d_skip,
+                         const int32_t* cu_seqlens, int32_t lanes, int32_t heads, int32_t head_dim, int32_t state_size, const float* state_in,
+                         float* state_out, float* out) {
+    return guarded([&] {
+        require_device();
+        const int groups = mamba2_groups(xbc_width, heads, head_dim, state_size);
+        const int32_t rows = checked_rows(cu_seqlens, lanes, "mk_k_mamba2_scan");
+        if (rows <= 0) throw std::runtime_error("Mamba2 scan requires non-empty dimensions");
+        const size_t xb = (size_t)rows * xbc_width * 4, dt = (size_t)rows * heads * 4, hv = (size_t)heads * 4;
+        const size_t st = (size_t)lanes * heads * head_dim * state_size * 4, ob = (size_t)rows * heads * head_dim * 4;
+        DevBuf dx(xb), ddt(dt), dbias(hv), da(hv), dd(hv), dcu((size_t)(lanes + 1) * 4), dsi(st), dso(st), dout(ob);
+        dx.upload(xbc, xb);
+        ddt.upload(raw_dt, dt);
+        dbias.upload(dt_bias, hv);
+        da.upload(a_decay, hv);
+        dd.upload(d_skip, hv);
+        dcu.upload(cu_seqlens, (size_t)(lanes + 1) * 4);
+        dsi.upload(state_in, st);
+        Mamba2Args m;
+        m.xbc = dx.as<float>(); m.raw_dt = ddt.as<float>(); m.dt_bias = dbias.as<float>(); m.a = da.as<float>(); m.d = dd.as<float>();
+        m.cu = dcu.as<int32_t>(); m.state_in = dsi.as<float>(); m.state_out = dso.as<float>(); m.out = dout.as<float>();
+        m.lanes = lanes; m.heads = heads; m.head_dim = head_dim; m.state_size = state_size; m.groups = groups;
+        launch_mamba2_scan(m, nullptr);
+        MK_CUDA(cudaDeviceSynchronize());
+        dso.download(state_out, st);
+        dout.download(out, ob);
+        MK_CUDA(cudaDeviceSynchronize());
+    });
+}
+
+int32_t mk_k_short_conv(const float* bcx, const float* kernel, const int32_t* cu_seqlens, int32_t lanes, int32_t hidden, int32_t taps,
+                        const float* tail_in, float* tail_out, float* out) {
+    return guarded([&] {
+        require_device();
+        if (hidden <= 0 || taps < 1) throw std::runtime_error("short-convolution state geometry does not match its layer");
+        const int32_t rows = checked_rows(cu_seqlens, lanes, "mk_k_short_conv");
+        if (rows <= 0) throw std::runtime_error("mk_k_short_conv: no rows");
+        const size_t xb = (size_t)rows * 3 * hidden * 4, kb = (size_t)hidden * taps * 4, ob = (size_t)rows * hidden * 4;
+        const size_t tb = (size_t)lanes * (taps - 1) * hidden * 4;
+        DevBuf dx(xb), dk(kb), dcu((size_t)(lanes + 1) * 4), dti(std::max<size_t>(tb, 4)), dto(std::max<size_t>(tb, 4)), dout(ob);
+        dx.upload(bcx, xb);
+        dk.upload(kernel, kb);
+        dcu.upload(cu_seqlens, (size_t)(lanes + 1) * 4);
+        if (tb > 0) dti.upload(tail_in, tb);
+        ShortConvArgs c;
+        c.bcx = dx.as<float>(); c.kernel = dk.as<float>(); c.cu = dcu.as<int32_t>(); c.tail_in = dti.as<float>(); c.tail_out = dto.as<float>();
+        c.out = dout.as<float>(); c.rows = rows; c.lanes = lanes; c.hidden = hidden; c.K = taps;
+        launch_short_conv(c, nullptr);
+        MK_CUDA(cudaDeviceSynchronize());
+        if (tb > 0) dto.download(tail_out, tb);
+        dout.download(out, ob);
+        MK_CUDA(cudaDeviceSynchronize());
     });
 }
 

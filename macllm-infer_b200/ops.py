@@ -118,6 +118,77 @@ def gated_ffn(qtype: int, gate_w, up_w, F: int, cols: int, x, act: int = 0, iter
     return (out, float(ms.value)) if iters > 0 else out
 
 
+def _cu32(cu_seqlens, rows: int) -> np.ndarray:
+    return np.ascontiguousarray([0, rows] if cu_seqlens is None else cu_seqlens, dtype=np.int32)
+
+
+def gated_delta_decay(alpha, time_bias, state_decay) -> np.ndarray:
+    """exp(softplus(alpha + time_bias) * state_decay) for alpha [tokens, heads]."""
+    alpha, time_bias, state_decay = _f32(alpha), _f32(time_bias), _f32(state_decay)
+    tokens, heads = alpha.shape
+    if time_bias.shape != (heads,) or state_decay.shape != (heads,):
+        raise ValueError(f"Gated DeltaNet decay has alpha shape {list(alpha.shape)}, time bias {list(time_bias.shape)} and state decay {list(state_decay.shape)}")
+    out = np.empty_like(alpha)
+    capi.check(capi.lib().mk_k_gated_delta_decay(_p(alpha), _p(time_bias), _p(state_decay), tokens, heads, _p(out)))
+    return out
+
+
+def gated_delta_recurrence(query, key, value, decay, beta, state, cu_seqlens=None):
+    """query / key [rows, heads, key_dim], value [rows, heads, value_dim], decay / beta [rows, heads], state
+    [lanes, heads, key_dim, value_dim] -> (out [rows, heads, value_dim], next state)."""
+    query, key, value, decay, beta, state = (_f32(t) for t in (query, key, value, decay, beta, state))
+    rows, heads, key_dim = query.shape
+    cu = _cu32(cu_seqlens, rows)
+    lanes = cu.size - 1
+    value_dim = value.shape[2]
+    if (key.shape != query.shape or value.shape[:2] != (rows, heads) or decay.shape != (rows, heads) or beta.shape != (rows, heads)
+            or state.shape != (lanes, heads, key_dim, value_dim) or cu[-1] != rows):
+        raise ValueError(f"Gated DeltaNet decode has query {list(query.shape)}, key {list(key.shape)}, value {list(value.shape)}, "
+                         f"decay {list(decay.shape)}, beta {list(beta.shape)} and state {list(state.shape)}")
+    out = np.empty((rows, heads, value_dim), np.float32)
+    nxt = np.empty_like(state)
+    capi.check(capi.lib().mk_k_gated_delta_recurrence(_p(query), _p(key), _p(value), _p(decay), _p(beta), _p(cu), lanes, heads, key_dim,
+                                                      value_dim, _p(state), _p(nxt), _p(out)))
+    return out, nxt
+
+
+def mamba2_scan(xbc, raw_dt, dt_bias, a, d, state, cu_seqlens=None):
+    """xbc [rows, H*P + 2*G*N] laid out [x | B | C], raw_dt [rows, H], dt_bias / a / d [H], state [lanes, H, P, N] ->
+    (out [rows, H, P], final state)."""
+    xbc, raw_dt, dt_bias, a, d, state = (_f32(t) for t in (xbc, raw_dt, dt_bias, a, d, state))
+    rows, width = xbc.shape
+    cu = _cu32(cu_seqlens, rows)
+    lanes = cu.size - 1
+    _, heads, head_dim, state_size = state.shape
+    if (state.shape[0] != lanes or raw_dt.shape != (rows, heads) or dt_bias.shape != (heads,) or a.shape != (heads,) or d.shape != (heads,)
+            or cu[-1] != rows):
+        raise ValueError(f"Mamba2 scan has xBC {list(xbc.shape)}, dt {list(raw_dt.shape)}, dt bias {list(dt_bias.shape)}, A {list(a.shape)}, "
+                         f"D {list(d.shape)}, and state {list(state.shape[1:])}")
+    out = np.empty((rows, heads, head_dim), np.float32)
+    nxt = np.empty_like(state)
+    capi.check(capi.lib().mk_k_mamba2_scan(_p(xbc), width, _p(raw_dt), _p(dt_bias), _p(a), _p(d), _p(cu), lanes, heads, head_dim, state_size,
+                                           _p(state), _p(nxt), _p(out)))
+    return out, nxt
+
+
+def short_conv(bcx, kernel, tail, cu_seqlens=None):
+    """bcx [rows, 3*hidden] laid out [B | C | x], kernel [hidden, K], tail [lanes, K-1, hidden] -> (C * conv(B * x), new tail)."""
+    bcx, kernel, tail = _f32(bcx), _f32(kernel), _f32(tail)
+    rows = bcx.shape[0]
+    hidden, K = kernel.shape
+    cu = _cu32(cu_seqlens, rows)
+    lanes = cu.size - 1
+    if bcx.shape != (rows, 3 * hidden) or cu[-1] != rows:
+        raise ValueError("short-convolution state geometry does not match its layer")
+    if tail.shape != (lanes, K - 1, hidden):
+        raise ValueError(f"short-convolution tail has shape {list(tail.shape)}, expected [{lanes}, {K - 1}, {hidden}]")
+    out = np.empty((rows, hidden), np.float32)
+    nxt = np.empty_like(tail)
+    capi.check(capi.lib().mk_k_short_conv(_p(bcx), _p(kernel), _p(cu), lanes, hidden, K, _p(tail) if tail.size else None,
+                                          _p(nxt) if nxt.size else None, _p(out)))
+    return out, nxt
+
+
 def argmax(logits) -> np.ndarray:
     logits = _f32(logits)
     B, V = logits.shape
