@@ -654,6 +654,12 @@ int32_t mk_k_mamba2_scan(const float* xbc, int64_t xbc_width, const float* raw_d
  * lane's last taps-1 rows of B*x (zeros for a fresh lane); out [rows][hidden] = C * sum_j kernel[j] * (B*x)[row - (taps-1) + j]. */
 int32_t mk_k_short_conv(const float* bcx, const float* kernel, const int32_t* cu_seqlens, int32_t lanes, int32_t hidden, int32_t taps,
                         const float* tail_in, float* tail_out, float* out);
+/* Average device time (CUDA events around each launch, three warm-up launches first) of the recurrence kernels on zero-filled
+ * operands: `lanes` lanes of `rows_per_lane` rows each.  kind 0: Gated DeltaNet with dim_a = key_dim, dim_b = value_dim;
+ * kind 1: Mamba2 scan with dim_a = head_dim, dim_b = state_size, one group.  The two state buffers change roles every launch;
+ * *state_bytes (optional) receives the state bytes one launch reads and writes, the algorithmic traffic of a decode tick. */
+int32_t mk_k_recurrent_time(int32_t kind, int32_t lanes, int32_t rows_per_lane, int32_t heads, int32_t dim_a, int32_t dim_b, int32_t iters,
+                            float* avg_ms, double* state_bytes);
 
 int32_t mk_k_argmax(const float* logits, int32_t B, int32_t vocab, uint32_t* out);
 /* Test support for expert parallelism with data-parallel lanes: the dispatch / regroup / return / wait kernels of all

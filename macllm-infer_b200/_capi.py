@@ -236,6 +236,7 @@ SIGNATURES = {
     "mk_k_gated_delta_recurrence": (_i32, [P, P, P, P, P, P, _i32, _i32, _i32, _i32, P, P, P]),
     "mk_k_mamba2_scan": (_i32, [P, _i64, P, P, P, P, P, _i32, _i32, _i32, _i32, P, P, P]),
     "mk_k_short_conv": (_i32, [P, P, P, _i32, _i32, _i32, P, P, P]),
+    "mk_k_recurrent_time": (_i32, [_i32, _i32, _i32, _i32, _i32, _i32, _i32, C.POINTER(C.c_float), C.POINTER(C.c_double)]),
     "mk_k_grouped_qmatmul": (_i32, [_i32, P, P, _i32, _i64, _i64, P, P, P, _i32, _i32]),
     "mk_k_sample": (_i32, [P, _i32, _i32, P, _i32, P]),
     "mk_k_penalties": (_i32, [P, _i32, P, _i32, C.c_float, P, _i32, C.c_float, C.c_float]),

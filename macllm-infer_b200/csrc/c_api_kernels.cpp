@@ -601,6 +601,62 @@ int32_t mk_k_short_conv(const float* bcx, const float* kernel, const int32_t* cu
     });
 }
 
+int32_t mk_k_recurrent_time(int32_t kind, int32_t lanes, int32_t rows_per_lane, int32_t heads, int32_t dim_a, int32_t dim_b, int32_t iters,
+                            float* avg_ms, double* state_bytes) {
+    return guarded([&] {
+        require_device();
+        if (kind < 0 || kind > 1 || lanes <= 0 || rows_per_lane <= 0 || heads <= 0 || dim_a <= 0 || dim_b <= 0 || iters <= 0 || avg_ms == nullptr)
+            throw std::runtime_error("mk_k_recurrent_time: bad arguments");
+        const int64_t rows = (int64_t)lanes * rows_per_lane;
+        std::vector<int32_t> cu((size_t)lanes + 1);
+        for (int l = 0; l <= lanes; ++l) cu[(size_t)l] = l * rows_per_lane;
+        DevBuf dcu((size_t)(lanes + 1) * 4);
+        dcu.upload(cu.data(), (size_t)(lanes + 1) * 4);
+        const size_t st = (size_t)lanes * heads * dim_a * dim_b * 4;   // [key_dim][value_dim] or [head_dim][state_size] per (lane, head)
+        DevBuf s0(st), s1(st);
+        s0.zero(nullptr);
+        s1.zero(nullptr);
+        if (state_bytes != nullptr) *state_bytes = 2.0 * (double)st;   // read once, written once per launch
+        cudaEvent_t e0, e1;
+        MK_CUDA(cudaEventCreate(&e0));
+        MK_CUDA(cudaEventCreate(&e1));
+        float total = 0.f;
+        auto timed = [&](auto&& launch) {
+            for (int it = -3; it < iters; ++it) {   // three warm-up launches; the two state buffers change roles every launch
+                const bool flip = (it & 1) != 0;
+                MK_CUDA(cudaEventRecord(e0, nullptr));
+                launch(flip ? s1.as<float>() : s0.as<float>(), flip ? s0.as<float>() : s1.as<float>());
+                MK_CUDA(cudaEventRecord(e1, nullptr));
+                MK_CUDA(cudaEventSynchronize(e1));
+                float ms = 0.f;
+                MK_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+                if (it >= 0) total += ms;
+            }
+        };
+        if (kind == 0) {   // Gated DeltaNet: dim_a = key_dim, dim_b = value_dim
+            const size_t qk = (size_t)rows * heads * dim_a * 4, vv = (size_t)rows * heads * dim_b * 4, ctl = (size_t)rows * heads * 4;
+            DevBuf dq(qk), dk(qk), dv(vv), dd(ctl), db(ctl), dout(vv);
+            for (DevBuf* b : {&dq, &dk, &dv, &dd, &db}) b->zero(nullptr);
+            GatedDeltaArgs a;
+            a.query = dq.as<float>(); a.key = dk.as<float>(); a.value = dv.as<float>(); a.decay = dd.as<float>(); a.beta = db.as<float>();
+            a.cu = dcu.as<int32_t>(); a.out = dout.as<float>(); a.lanes = lanes; a.heads = heads; a.key_dim = dim_a; a.value_dim = dim_b;
+            timed([&](const float* in, float* out) { a.state_in = in; a.state_out = out; launch_gated_delta_recurrence(a, nullptr); });
+        } else {           // Mamba2: dim_a = head_dim, dim_b = state_size, one group
+            const int64_t width = (int64_t)heads * dim_a + 2 * (int64_t)dim_b;
+            const size_t xb = (size_t)rows * width * 4, dt = (size_t)rows * heads * 4, hv = (size_t)heads * 4, ob = (size_t)rows * heads * dim_a * 4;
+            DevBuf dx(xb), ddt(dt), dbias(hv), da(hv), dd(hv), dout(ob);
+            for (DevBuf* b : {&dx, &ddt, &dbias, &da, &dd}) b->zero(nullptr);
+            Mamba2Args m;
+            m.xbc = dx.as<float>(); m.raw_dt = ddt.as<float>(); m.dt_bias = dbias.as<float>(); m.a = da.as<float>(); m.d = dd.as<float>();
+            m.cu = dcu.as<int32_t>(); m.out = dout.as<float>(); m.lanes = lanes; m.heads = heads; m.head_dim = dim_a; m.state_size = dim_b; m.groups = 1;
+            timed([&](const float* in, float* out) { m.state_in = in; m.state_out = out; launch_mamba2_scan(m, nullptr); });
+        }
+        MK_CUDA(cudaEventDestroy(e0));
+        MK_CUDA(cudaEventDestroy(e1));
+        *avg_ms = total / (float)iters;
+    });
+}
+
 int32_t mk_k_argmax(const float* logits, int32_t B, int32_t vocab, uint32_t* out) {
     return guarded([&] {
         require_device();

@@ -189,6 +189,15 @@ def short_conv(bcx, kernel, tail, cu_seqlens=None):
     return out, nxt
 
 
+def recurrent_time(kind: str, lanes: int, rows_per_lane: int, heads: int, dim_a: int, dim_b: int, iters: int = 10):
+    """(average ms per launch, state bytes read + written per launch) of 'gated_delta' (dim_a key_dim, dim_b value_dim) or 'mamba2'
+    (dim_a head_dim, dim_b state_size)."""
+    ms, nbytes = C.c_float(), C.c_double()
+    capi.check(capi.lib().mk_k_recurrent_time({"gated_delta": 0, "mamba2": 1}[kind], lanes, rows_per_lane, heads, dim_a, dim_b, iters,
+                                              C.byref(ms), C.byref(nbytes)))
+    return float(ms.value), float(nbytes.value)
+
+
 def argmax(logits) -> np.ndarray:
     logits = _f32(logits)
     B, V = logits.shape

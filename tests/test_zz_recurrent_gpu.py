@@ -156,3 +156,16 @@ def test_geometry_refusals_come_back_as_errors(ops, mk):
         ops.short_conv(z(2, 6), z(2, 9), z(1, 8, 2))
     with pytest.raises(capi.MkError, match="lane boundaries must rise"):
         ops.gated_delta_recurrence(z(2, 1, 4), z(2, 1, 4), z(2, 1, 4), z(2, 1), z(2, 1), z(2, 1, 4, 4), [0, 3, 2])
+
+
+def test_launch_times_of_a_decode_tick_and_a_prefill_chunk(ops):
+    """CUDA-event time per launch at the shapes the register kernels are built for; the state is read once and written once per
+    launch, so a decode tick of 64 lanes moves 2 x 134 MB of state and little else.  Printed for the record (run with -s); the
+    assertion only says that the launches ran."""
+    cases = (("gated_delta", 64, 1, 32, 128, 128), ("gated_delta", 1, 512, 32, 128, 128),
+             ("mamba2", 64, 1, 64, 64, 128), ("mamba2", 1, 512, 64, 64, 128))
+    for kind, lanes, rows, heads, dim_a, dim_b in cases:
+        ms, nbytes = ops.recurrent_time(kind, lanes, rows, heads, dim_a, dim_b, iters=10)
+        assert ms > 0.0 and nbytes == 2.0 * lanes * heads * dim_a * dim_b * 4
+        print(f"RECURRENT_TIME {kind} lanes={lanes} rows_per_lane={rows} heads={heads} dims={dim_a}x{dim_b}: {ms * 1e3:.1f} us per launch, "
+              f"state {nbytes / 1e6:.1f} MB -> {nbytes / ms / 1e6:.0f} GB/s")
