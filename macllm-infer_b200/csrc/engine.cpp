@@ -450,7 +450,8 @@ int Engine::drive_once() {  // engine.rs:1938-1964
             logits_host_.resize((size_t)lane_count * vocab);
             model_.read_output(logits_host_.data(), nullptr);
         }
-        stats_.device_ms += model_.last_forward_ms();
+        const double tick_ms = model_.last_forward_ms();   // read once: the device time of this packed forward
+        stats_.device_ms += tick_ms;
         {   // collect_pending_benchmark_forwards + record_packed_forward (engine.rs:2306-2375,2394-2405,601-619)
             TickInfo info;
             info.kind = (ForwardKind)tick.front().phase;
@@ -458,7 +459,7 @@ int Engine::drive_once() {  // engine.rs:1938-1964
                 if (l.phase != tick.front().phase) info.kind = ForwardKind::Mixed;
             info.lane_count = lane_count;
             info.input_tokens = input_tokens;
-            info.model_ms = model_.last_forward_ms();
+            info.model_ms = tick_ms;
             auto bucket = [&](double& suffix, double& first, double& decode, double& mixed) -> double& {
                 switch (info.kind) {
                     case ForwardKind::SuffixPrefill: return suffix;
@@ -498,7 +499,7 @@ int Engine::drive_once() {  // engine.rs:1938-1964
             // GenerationCore::complete (generation.rs:1159-1266): the forward's time is the sequence's before anything else
             {
                 EngineResult& res = results_[s.id];
-                const double t = model_.last_forward_ms();
+                const double t = tick_ms;
                 if (!v.was_prefill) { res.decode_ms += t; ++res.decode_steps; }
                 else if (v.ready_to_sample) res.first_token_ms += t;
                 else res.suffix_prefill_ms += t;
