@@ -686,3 +686,26 @@ def test_rejected_and_cancelled_members_end_the_trace(eng):
     assert t["complete"] is True
     assert (t["expected_members"], t["admitted_members"], t["terminal_members"], t["rejected_members"]) == (3, 1, 3, 1)
     assert t["admission_active_sequences"] == 1 and t["packed_forwards"] == 1
+
+
+def test_a_request_local_preflight_failure_does_not_poison_the_worker(eng):
+    """engine.rs:5347-5379: an invalid request (top_p = 0) ahead of a healthy one is refused with InvalidRequest; the healthy
+    one is admitted and finishes, the engine stays usable and both reusable sessions are still there (two more requests run
+    side by side afterwards). engine.rs:4412-4453: a full queue and a poisoned engine are told apart at submission."""
+    pm, pe = product_engine(eng, dict(vocab=32), dict(max_active_sequences=2, scheduler_token_budget=8, prefill_token_quantum=4, queue_capacity=2))
+    bad, good = pe.submit([eng.Request([1], 1, top_p=0.0), eng.Request([2], 1)])
+    with pytest.raises(RuntimeError, match="inference queue is full"):
+        pe.submit([eng.Request([3], 1)])
+    pe.run()
+    assert pe.result(bad)["state"] == "failed" and pe.result(bad)["kind"] == "invalid_request"
+    assert pe.result(good)["state"] == "done" and pe.status() == "ready"
+    a, b = pe.submit([eng.Request([4, 5], 2), eng.Request([6], 2)])
+    pe.run()
+    assert all(len(t) == 2 for t in pe.trace()[1:])          # both sessions serve again
+    assert pe.result(a)["state"] == pe.result(b)["state"] == "done"
+    pm.inject_failure("forward", 3)
+    pe.submit([eng.Request([7], 1)])
+    pe.run()
+    assert pe.status() == "poisoned"
+    with pytest.raises(RuntimeError, match=r"inference worker is unavailable \(Poisoned\)"):
+        pe.submit([eng.Request([8], 1)])
