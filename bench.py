@@ -718,6 +718,7 @@ def main():
     dev_ms = 0.0
     ticks = 0
     diag = None
+    forward_kinds = dict(suffix_prefill_ms=0.0, first_token_ms=0.0, decode_ms=0.0, mixed_ms=0.0)
     t0 = time.perf_counter()
     for _ in range(args.steps):
         n, wall, st, diag = run_step(eng_mod, model, w, reqs, active, lockstep)
@@ -725,6 +726,8 @@ def main():
         generated += st["generated_tokens"]
         dev_ms += st["device_ms"]
         ticks += st["ticks"]
+        for k in forward_kinds:   # the engine's own split of the device time by whole-forward kind (src/engine.rs:430-439,601-619)
+            forward_kinds[k] += float(st.get(k, 0.0))
     barrier(dist)
     wall_total = time.perf_counter() - t0
     clocks = sampler.stop() if rank == 0 else None
@@ -811,6 +814,7 @@ def main():
                    # the reference's scoreboard also quotes generated tokens alone (src/benchmark/serving.rs:301-328)
                    output_tokens_per_s=generated_all / dev_max, roofline=roof, tick_classes=classes,
                    cpu_baseline=base)
+        out["forward_kinds_ms_per_step"] = {k: round(v / max(args.steps, 1), 3) for k, v in forward_kinds.items()}
         if diag is not None:
             out["prefix_cache"] = diag
         if http is not None:
