@@ -93,6 +93,19 @@ bool Engine::is_cancelled(int id) {
     return cancelled_.count(id) != 0;
 }
 
+// Flags of requests that have ended are dropped, so that the set stays as small as the work in flight and the common tick
+// goes back to taking no lock.  A flag set for a request that had already ended is dropped here as well.
+void Engine::forget_settled_cancellations() {
+    if (!any_cancelled_.load(std::memory_order_acquire)) return;
+    std::lock_guard<std::mutex> lock(cancel_mu_);
+    for (auto it = cancelled_.begin(); it != cancelled_.end();) {
+        auto r = results_.find(*it);
+        if (r != results_.end() && r->second.state != FinishState::Running) it = cancelled_.erase(it);
+        else ++it;
+    }
+    if (cancelled_.empty()) any_cancelled_.store(false, std::memory_order_release);
+}
+
 // A cancelled request gets no terminal event in the reference (its receiver is gone); here its result says so.
 void Engine::finish_cancelled(int id) {
     EngineResult& r = results_[id];
@@ -285,7 +298,10 @@ int Engine::step() {  // one turn of ServingScheduler::run, engine.rs:1577-1647
 
 int Engine::drive_once() {  // engine.rs:1938-1964
     try_admit_available();
-    if (active_.empty()) return 0;
+    if (active_.empty()) {
+        forget_settled_cancellations();
+        return 0;
+    }
     if (round_visits_remaining_ == 0 || round_budget_remaining_ == 0) {
         round_visits_remaining_ = (int)active_.size();
         round_budget_remaining_ = cfg_.scheduler_token_budget;
@@ -597,6 +613,7 @@ int Engine::drive_once() {  // engine.rs:1938-1964
         round_visits_remaining_ = 0;
         round_budget_remaining_ = 0;
     }
+    forget_settled_cancellations();
     return lane_count;
 }
 

@@ -161,6 +161,7 @@ private:
     void reclaim(Sequence& s);
     bool is_cancelled(int id);
     void finish_cancelled(int id);
+    void forget_settled_cancellations();
     uint32_t sample(Sequence& s, float* row);
 
     PagedLm& model_;
