@@ -426,6 +426,13 @@ int32_t mk_engine_status(mk_engine* e, int32_t* status);
  * (src/generation.rs:1201-1204).  The request's result then reads "3 cancelled" with the tokens produced so far.  The only
  * engine entry that may be called from another thread while mk_engine_step runs. */
 int32_t mk_engine_cancel(mk_engine* e, int32_t request_id);
+/* For a long-lived host.  mk_engine_keep_trace(e, 0) stops the per-tick records (mk_engine_trace, mk_engine_tick_info, the tick
+ * numbers of batch traces) and drops those kept so far: the reference captures them only for benchmark submissions
+ * (capture_benchmark_trace, src/engine.rs:1037-1053); the time buckets and counters keep running.
+ * mk_engine_release_request drops the stored result of a request that has ended (its tokens, logits rows, metrics), the
+ * counterpart of dropping the reference's ticket; a running request is refused. */
+int32_t mk_engine_keep_trace(mk_engine* e, int32_t keep);
+int32_t mk_engine_release_request(mk_engine* e, int32_t request_id);
 /* EngineFailureKind of a failed request (src/engine.rs:268-273): 0 none, 1 InvalidRequest, 2 ResourceExhausted,
  * 3 Internal, 4 Fatal. */
 int32_t mk_engine_failure_kind(mk_engine* e, int32_t request_id, int32_t* kind);

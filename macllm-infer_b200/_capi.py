@@ -188,6 +188,8 @@ SIGNATURES = {
     "mk_engine_status": (_i32, [P, C.POINTER(_i32)]),
     "mk_engine_failure_kind": (_i32, [P, _i32, C.POINTER(_i32)]),
     "mk_engine_cancel": (_i32, [P, _i32]),
+    "mk_engine_keep_trace": (_i32, [P, _i32]),
+    "mk_engine_release_request": (_i32, [P, _i32]),
     "mk_engine_request_metrics": (_i32, [P, _i32, C.POINTER(RequestMetrics)]),
     "mk_model_fake_script": (_i32, [P, C.c_void_p, _i32, C.c_void_p, _i32]),
     "mk_engine_tick_info": (_i32, [P, _i64, C.POINTER(TickInfo)]),

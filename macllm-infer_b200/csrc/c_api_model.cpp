@@ -552,6 +552,14 @@ int32_t mk_engine_status(mk_engine* e, int32_t* status) {
     return guarded([&] { *status = (int32_t)e->e->status(); });
 }
 
+int32_t mk_engine_keep_trace(mk_engine* e, int32_t keep) {
+    return guarded([&] { e->e->keep_trace(keep != 0); });
+}
+
+int32_t mk_engine_release_request(mk_engine* e, int32_t request_id) {
+    return guarded([&] { e->e->release_request(request_id); });
+}
+
 int32_t mk_engine_cancel(mk_engine* e, int32_t request_id) {
     return guarded([&] { e->e->cancel(request_id); });
 }

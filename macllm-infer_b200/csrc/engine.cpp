@@ -61,12 +61,40 @@ const TickInfo& Engine::tick_info(int64_t tick) const {
     return tick_info_[(size_t)tick];
 }
 
+void Engine::keep_trace(bool keep) {
+    keep_trace_ = keep;
+    if (!keep) {
+        trace_.clear();
+        trace_.shrink_to_fit();
+        tick_info_.clear();
+        tick_info_.shrink_to_fit();
+    }
+}
+
+void Engine::release_request(int id) {
+    auto it = results_.find(id);
+    if (it == results_.end()) throw std::runtime_error("unknown request id " + std::to_string(id));
+    if (it->second.state == FinishState::Running) throw std::runtime_error("request " + std::to_string(id) + " is still running");
+    results_.erase(it);
+    auto b = batch_of_request_.find(id);
+    if (b != batch_of_request_.end()) {   // the batch's trace goes with its last member
+        const int batch = b->second;
+        batch_of_request_.erase(b);
+        bool any = false;
+        for (int member : batches_[(size_t)batch].members) any = any || batch_of_request_.count(member) != 0;
+        if (!any) batches_[(size_t)batch] = BatchTrace{};
+    }
+}
+
 const BatchTrace& Engine::batch_trace(int member_id, int* terminal) const {
     auto it = batch_of_request_.find(member_id);
     if (it == batch_of_request_.end()) throw std::runtime_error("request " + std::to_string(member_id) + " was not submitted in an atomic batch");
     const BatchTrace& b = batches_[(size_t)it->second];
     int ended = 0;
-    for (int id : b.members) ended += results_.at(id).state != FinishState::Running;
+    for (int id : b.members) {
+        auto r = results_.find(id);
+        ended += r == results_.end() || r->second.state != FinishState::Running;   // a released result had ended
+    }
     if (terminal != nullptr) *terminal = ended;
     return b;
 }
@@ -493,12 +521,12 @@ int Engine::drive_once() {  // engine.rs:1938-1964
                 seen.push_back(b);
                 BatchTrace& bt = batches_[(size_t)b];
                 bucket(bt.suffix_prefill_ms, bt.first_token_ms, bt.decode_ms, bt.mixed_ms) += info.model_ms;
-                bt.packed_forwards.push_back(stats_.ticks);
+                if (keep_trace_) bt.packed_forwards.push_back((int64_t)trace_.size());   // the index of this forward among the kept records
             }
-            tick_info_.push_back(info);
+            if (keep_trace_) tick_info_.push_back(info);
         }
         ++stats_.ticks;
-        trace_.push_back(std::move(tick));
+        if (keep_trace_) trace_.push_back(std::move(tick));
         // complete_mixed_rows (engine.rs:2411-2523)
         int row = 0;
         for (int i = 0; i < visits; ++i) {

@@ -116,6 +116,10 @@ public:
     const EngineResult& result(int id) const;
     const std::vector<std::vector<TickLaneTrace>>& trace() const { return trace_; }
     const TickInfo& tick_info(int64_t tick) const;
+    // A long-lived host (a server) turns the per-tick records off - the reference captures them only for benchmark
+    // submissions (capture_benchmark_trace, src/engine.rs:1037-1053) - and releases each request once it has read the result.
+    void keep_trace(bool keep);
+    void release_request(int id);
     // The trace of the atomic batch `member_id` was submitted in; *terminal receives how many of its members have ended
     // (done, failed, rejected or cancelled).  The trace is complete once admission ran and every member is terminal.
     const BatchTrace& batch_trace(int member_id, int* terminal) const;
@@ -182,6 +186,7 @@ private:
     std::vector<float> logits_host_;
     std::vector<uint32_t> tokens_host_;
     bool poisoned_ = false;
+    bool keep_trace_ = true;
     int orphan_ = -1;                   // request whose admission threw
     bool forward_needs_drain_ = false;  // a reservation or forward was submitted and no completion barrier ran yet
     std::string poison_message_;

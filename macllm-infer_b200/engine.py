@@ -322,6 +322,14 @@ class Engine:
         next look at it. May be called from another thread while `step` runs."""
         capi.check(capi.lib().mk_engine_cancel(self._h, request_id))
 
+    def keep_trace(self, keep: bool) -> None:
+        """Turn the per-tick records on or off (off drops those kept so far); a server runs with them off."""
+        capi.check(capi.lib().mk_engine_keep_trace(self._h, 1 if keep else 0))
+
+    def release(self, request_id: int) -> None:
+        """Drop the stored result of a request that has ended."""
+        capi.check(capi.lib().mk_engine_release_request(self._h, request_id))
+
     def progress(self, request_id: int):
         """(generated tokens so far, state, prompt tokens served from the prefix cache) without copying the tokens."""
         n = C.c_int32(0)

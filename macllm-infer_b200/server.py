@@ -365,6 +365,8 @@ class CompletionServer:
             self._status = "stopped"
             self._ready.set()
             return
+        if hasattr(engine, "keep_trace"):
+            engine.keep_trace(False)      # a server lives long: no per-tick records, results released once delivered
         self._status = "ready"
         self._ready.set()
         active: dict[int, _Job] = {}
@@ -427,12 +429,15 @@ class CompletionServer:
                                                          prefill_ms=(first - job.t_submit) * 1e3, ttft_ms=(first - job.t_submit) * 1e3,
                                                          total_ms=(now - job.t_submit) * 1e3)))
                         del active[rid]
+                        engine.release(rid)
                     elif state == "failed":
                         r = engine.result(rid)
                         job.events.put(("failed", r["kind"], r["message"]))
                         del active[rid]
+                        engine.release(rid)
                     elif state == "cancelled":   # nobody is listening any more: no event
                         del active[rid]
+                        engine.release(rid)
                 if self._status not in ("poisoned",) and not active:
                     self._status = "ready"
         except Exception as e:  # a scheduler panic (src/engine.rs:1600-1647): fatal for everything in flight, the worker is gone

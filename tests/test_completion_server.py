@@ -271,7 +271,11 @@ class _SlowEngine:
     """The engine with a pause in every tick, so that a client can leave while its request runs; records the cancellations."""
 
     def __init__(self, inner, pause_s):
-        self._inner, self._pause_s, self.cancelled = inner, pause_s, []
+        self._inner, self._pause_s, self.cancelled, self.final = inner, pause_s, [], {}
+
+    def release(self, rid):
+        self.final[rid] = self._inner.result(rid)      # what the engine held when the server let go of the request
+        return self._inner.release(rid)
 
     def step(self):
         import time
@@ -327,8 +331,11 @@ def test_a_client_that_leaves_cancels_its_request_and_the_peer_finishes(mk, srv_
             time.sleep(0.02)
         e = made["engine"]
         assert e.cancelled == [0]
-        r = e.result(0)
+        r = e.final[0]
         assert r["state"] == "cancelled" and 0 < len(r["tokens"]) < 2000
+        with pytest.raises(RuntimeError, match="unknown request id 0"):      # delivered or given up: the engine keeps nothing
+            e.result(0)
+        assert e.trace() == []                                               # and no per-tick records in a server
         assert e.pending() == 0 and made["model"].pool_stats()["live_blocks"] == 0
         st, _, b = call(s, "GET", "/healthz")
         assert st == 200 and json.loads(b)["worker"] == "ready"

@@ -709,3 +709,38 @@ def test_a_request_local_preflight_failure_does_not_poison_the_worker(eng):
     assert pe.status() == "poisoned"
     with pytest.raises(RuntimeError, match=r"inference worker is unavailable \(Poisoned\)"):
         pe.submit([eng.Request([8], 1)])
+
+
+def test_a_long_lived_host_turns_records_off_and_releases_results(eng):
+    """The reference keeps per-forward records only for benchmark submissions (capture_benchmark_trace, engine.rs:1037-1053) and a
+    request's result lives in its ticket: here the host says so - no per-tick records, a result dropped once read."""
+    pm, pe = product_engine(eng, dict(vocab=32), dict(max_active_sequences=2, scheduler_token_budget=8, prefill_token_quantum=4))
+    a, b = pe.submit([eng.Request([1, 2], 2), eng.Request([3], 5)], True)
+    pe.step()
+    assert len(pe.trace()) == 1
+    pe.keep_trace(False)
+    assert pe.trace() == []
+    with pytest.raises(RuntimeError, match="still running"):
+        pe.release(b)
+    pe.run()
+    assert pe.trace() == [] and pe.stats()["ticks"] == 5          # counters and time buckets keep running
+    st = pe.stats()
+    assert abs(st["first_token_ms"] + st["decode_ms"] + st["mixed_ms"] + st["suffix_prefill_ms"] - st["device_ms"]) < 1e-6
+    assert pe.batch_trace(a)["complete"] and pe.batch_trace(a)["forward_ticks"] == [0]   # what was recorded before the switch stays
+    tokens = list(pe.result(a)["tokens"])
+    pe.release(a)
+    with pytest.raises(RuntimeError, match=f"unknown request id {a}"):
+        pe.result(a)
+    t = pe.batch_trace(b)                                          # the other member still reaches the batch's trace
+    assert t["complete"] and t["terminal_members"] == 2
+    pe.release(b)
+    with pytest.raises(RuntimeError, match="was not submitted in an atomic batch"):
+        pe.batch_trace(b)
+    with pytest.raises(RuntimeError, match="unknown request id 99"):
+        pe.release(99)
+    assert len(tokens) == 2
+    pe.keep_trace(True)
+    c, d = pe.submit([eng.Request([4], 1), eng.Request([5], 1)], True)
+    pe.run()
+    assert pe.trace() == [[(c, 0, 1), (d, 0, 1)]] and pe.tick_info(0)["kind"] == "first_token"
+    assert pe.batch_trace(c)["forward_ticks"] == [0]              # numbered among the records that are kept
