@@ -19,6 +19,9 @@ struct KvPoolExhausted : std::runtime_error {
         : std::runtime_error("paged KV pool exhausted: requested " + std::to_string(req) + " blocks, " + std::to_string(fr) +
                              " free and " + std::to_string(un) + " unallocated"),
           requested(req), free_blocks(fr), unallocated(un) {}
+    // the same condition with the wording of the model boundary (KvCacheExhausted, src/architecture.rs:928-953)
+    KvPoolExhausted(int64_t req, int64_t fr, int64_t un, const std::string& boundary_message)
+        : std::runtime_error(boundary_message), requested(req), free_blocks(fr), unallocated(un) {}
 };
 
 struct KvBlockId {

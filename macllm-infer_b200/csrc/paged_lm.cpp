@@ -117,10 +117,15 @@ std::unique_ptr<LmReservation> PagedLm::reserve_batch(const std::vector<LmLane>&
         try {
             r->paged = pool_->reserve_batch(tables, counts);
             break;
-        } catch (const KvPoolExhausted&) {
-            if (!prefix_cache_) throw;
-            auto evicted = prefix_cache_->evict_lru();  // dropping the snapshot releases its pages
-            if (!evicted) throw;
+        } catch (const KvPoolExhausted& e) {
+            if (prefix_cache_ && prefix_cache_->evict_lru()) continue;  // dropping the evicted snapshot releases its pages
+            // classify_reservation_error (src/decoder.rs:3970-3994): what the scheduler is told is the pool's state now
+            const KvPoolStats st = pool_->stats();
+            const int64_t free_now = st.free_blocks + (st.max_blocks - st.allocated_blocks);
+            throw KvPoolExhausted(e.requested, e.free_blocks, e.unallocated,
+                                  "KV cache requires " + std::to_string(e.requested) + " additional blocks, but only " + std::to_string(free_now) +
+                                      " of " + std::to_string(st.max_blocks) + " are free (" + std::to_string(st.retired_blocks) + " retired, " +
+                                      std::to_string(st.block_tokens) + " tokens/block)");
         }
     }
     return r;
@@ -149,7 +154,8 @@ void PagedLm::forward_batch_reserved(const std::vector<LmLane>& lanes, std::uniq
                                      std::to_string(l.session->logical_len));
         if (reservation->sessions[i] != l.session || reservation->start_pos[i] != l.start_pos ||
             reservation->n_tokens[i] != l.n_tokens)
-            throw std::runtime_error("KV reservation lane " + std::to_string(i) + " does not match the forward lane");
+            throw std::runtime_error("paged KV reservation lane " + std::to_string(i) +
+                                     " does not match session, order, start or token count");  // src/decoder.rs:4076-4090
     }
     KvReservation& paged = *reservation->paged;
     paged.mark_all_used();

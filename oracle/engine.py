@@ -79,13 +79,16 @@ class OracleModel:
         while True:
             try:
                 return self.pool.reserve_batch([s["table"] for s, _, _ in lanes], [n for _, _, n in lanes])
-            except kv.Exhausted:
-                if self.prefix is None:
-                    raise
-                snap = self.prefix.evict_lru()
-                if snap is None:
-                    raise
-                snap.drop()
+            except kv.Exhausted as e:
+                snap = self.prefix.evict_lru() if self.prefix is not None else None
+                if snap is not None:
+                    snap.drop()
+                    continue
+                st = self.pool.stats()   # classify_reservation_error, decoder.rs:3970-3994; KvCacheExhausted, architecture.rs:928-953
+                free_now = st["free_blocks"] + (self.pool.max_blocks - st["allocated_blocks"])
+                raise kv.Exhausted(e.requested, e.free_blocks, e.unallocated,
+                                   f"KV cache requires {e.requested} additional blocks, but only {free_now} of {self.pool.max_blocks} are free "
+                                   f"({st['retired_blocks']} retired, {self.pool.block_tokens} tokens/block)")
 
     def forward(self, lanes, reservation, want_logits=True):
         """lanes: (session, ids, start_pos).  Returns logits [lanes, vocab] (or next tokens for the fake)."""

@@ -17,8 +17,9 @@ FREE, RESERVED, LIVE, RETIRED = "free", "reserved", "live", "retired"
 
 
 class Exhausted(Exception):
-    def __init__(self, requested, free_blocks, unallocated):
-        super().__init__(f"paged KV pool exhausted: requested {requested} blocks, {free_blocks} free and {unallocated} unallocated")
+    def __init__(self, requested, free_blocks, unallocated, boundary_message=None):
+        super().__init__(boundary_message or
+                         f"paged KV pool exhausted: requested {requested} blocks, {free_blocks} free and {unallocated} unallocated")
         self.requested, self.free_blocks, self.unallocated = requested, free_blocks, unallocated
 
 

@@ -101,7 +101,9 @@ def test_irreducible_kv_pressure_fails_only_that_request(eng):
     states = [pe.result(i)["state"] for i in range(2)]
     assert states == [oe_.results[i].state for i in range(2)]
     assert states == ["failed", "done"]
-    assert "exhausted" in pe.result(0)["message"]
+    # KvCacheExhausted as the model boundary words it (src/architecture.rs:928-953, src/decoder.rs:3970-3994)
+    assert pe.result(0)["message"] == oe_.results[0].message == "KV cache requires 1 additional blocks, but only 0 of 2 are free (0 retired, 2 tokens/block)"
+    assert pe.result(0)["kind"] == "resource_exhausted"
     assert len(pe.result(1)["tokens"]) == 3
     assert pm.pool_stats()["live_blocks"] == 0
 
