@@ -141,7 +141,8 @@ def test_requests_that_can_never_fit_are_rejected_at_admission(eng):
 
 
 def test_forward_failure_rolls_back_every_lane(eng):
-    """decoder.rs:4146-4162 / cache.rs:3001-3005: a failed forward leaves sessions and pool untouched."""
+    """decoder.rs:4146-4162 / cache.rs:3001-3005, the case failed_mixed_batch_rolls_back_every_lane_and_retries
+    (decoder.rs:9325-9388): a failed forward leaves sessions and pool untouched, and the same batch then runs."""
     capi = importlib.import_module("macllm_infer_b200._capi")
     model = eng.Model.fake(vocab=32, fail_forward_at=1)
     a, b = model.new_session(), model.new_session()
@@ -157,6 +158,8 @@ def test_forward_failure_rolls_back_every_lane(eng):
 
 
 def test_lane_validation_happens_before_any_mutation(eng):
+    """mixed_batch_prevalidation_is_atomic_across_lanes (decoder.rs:9266-9323): a bad second lane - wrong start, a token
+    outside the vocabulary, the first lane's session again - is found before the first lane is touched."""
     capi = importlib.import_module("macllm_infer_b200._capi")
     model = eng.Model.fake(vocab=32)
     a, b = model.new_session(), model.new_session()
