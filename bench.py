@@ -544,6 +544,27 @@ def plan_arena(w, prompts, new, kv_per_token: int, kv_budget_gb: float):
 
 EP_SLICE_WORKLOAD = "qwen3-30b-a3b-poisson"
 EP_SLICE_REQUESTS = 64
+EP_SLICE_DEADLINE_S = 480.0   # one GPU takes about 100 s, most of it writing the 17 GB seeded checkpoint
+
+
+def line_emitter(out):
+    """Returns emit(ep=None): prints the JSON line once (the first call wins; later calls do nothing).  `out` is None on the
+    ranks that print nothing."""
+    lock = threading.Lock()
+    done = []
+
+    def emit(ep=None):
+        with lock:
+            if done:
+                return False
+            done.append(True)
+            if out is not None:
+                line = dict(out)
+                if ep is not None:
+                    line["ep"] = ep
+                print(json.dumps(line), flush=True)
+            return True
+    return emit
 
 
 def ep_slice(eng_mod, wl, seed, rank: int, local: int, world: int, dist, kv_budget_gb: float) -> dict:
@@ -794,15 +815,8 @@ def main():
         except Exception as e:  # the baseline is a report, never a reason to lose the measurement
             base = dict(value=None, unit=UNIT, cores=None, kind="port", sample=f"failed: {e}")
 
-    # the sparse-MoE curve beside the headline (every rank takes part; the headline model's memory is released first)
-    ep_block = None
-    if args.workload == DEFAULT_WORKLOAD and not sliced and not args.no_ep_slice and not args.no_profiled_step:
-        model.close()
-        try:
-            ep_block = ep_slice(eng_mod, wl, seed, rank, local, world, dist, args.kv_budget_gb)
-        except Exception as e:  # never a reason to lose the headline measurement
-            ep_block = dict(error=str(e)[:400])
-
+    # the headline line is complete before the sparse-MoE slice starts: whatever becomes of the slice, it is printed once
+    out = None
     if rank == 0:
         out = dict(metric=METRIC, value=tokens_all / dev_max, unit=UNIT, n_gpus=world, steps=args.steps, warmup=args.warmup,
                    ms_per_step=wall_max * 1e3 / max(args.steps, 1), higher_is_better=True, scaling="weak", vs_baseline=None,
@@ -819,9 +833,22 @@ def main():
             out["prefix_cache"] = diag
         if http is not None:
             out["http"] = http
-        if ep_block is not None:
-            out["ep"] = ep_block
-        print(json.dumps(out))
+    emit = line_emitter(out)
+
+    # the sparse-MoE curve beside the headline (every rank takes part; the headline model's memory is released first)
+    ep_block = None
+    if args.workload == DEFAULT_WORKLOAD and not sliced and not args.no_ep_slice and not args.no_profiled_step:
+        model.close()
+        # should the slice outlast its deadline (a rank stuck in a collective), rank 0 prints the headline without it
+        timer = threading.Timer(EP_SLICE_DEADLINE_S, emit, kwargs=dict(ep=dict(error=f"the slice did not finish within {EP_SLICE_DEADLINE_S:.0f} s")))
+        timer.daemon = True
+        timer.start()
+        try:
+            ep_block = ep_slice(eng_mod, wl, seed, rank, local, world, dist, args.kv_budget_gb)
+        except Exception as e:  # never a reason to lose the headline measurement
+            ep_block = dict(error=str(e)[:400])
+        timer.cancel()
+    emit(ep=ep_block)
     model.close()
     if dist is not None:
         dist.destroy_process_group()

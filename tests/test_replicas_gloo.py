@@ -178,3 +178,29 @@ def test_a_failure_on_one_rank_ends_the_lock_step_on_all_of_them():
     outs.sort(key=lambda o: o["rank"])
     assert "another rank" in outs[0]["outcome"]
     assert "ended in state failed" in outs[1]["outcome"] and "inference worker failed" in outs[1]["outcome"]
+
+
+def test_the_headline_line_is_printed_once_whatever_becomes_of_the_slice(capsys):
+    """bench.line_emitter: the headline is complete before the sparse-MoE slice starts; the first of (slice finished, slice
+    overdue) prints it, the other does nothing; ranks that print nothing still take part."""
+    import threading
+    import time
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+    import bench
+    emit = bench.line_emitter(dict(metric="m", value=1.0))
+    overdue = threading.Timer(0.05, emit, kwargs=dict(ep=dict(error="the slice did not finish")))
+    overdue.start()
+    time.sleep(0.3)
+    assert emit(ep=dict(value=2.0)) is False
+    lines = capsys.readouterr().out.strip().splitlines()
+    assert len(lines) == 1 and json.loads(lines[0]) == {"metric": "m", "value": 1.0, "ep": {"error": "the slice did not finish"}}
+    emit = bench.line_emitter(dict(metric="m", value=1.0))
+    waiting = threading.Timer(30.0, emit)
+    waiting.daemon = True
+    waiting.start()
+    waiting.cancel()
+    assert emit(ep=dict(value=2.0)) is True and emit() is False
+    lines = capsys.readouterr().out.strip().splitlines()
+    assert len(lines) == 1 and json.loads(lines[0])["ep"] == {"value": 2.0}
+    silent = bench.line_emitter(None)
+    assert silent(ep=1) is True and capsys.readouterr().out == ""
