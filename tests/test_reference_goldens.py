@@ -230,3 +230,21 @@ def test_partial_rope_rotates_only_the_configured_prefix_on_the_oracle(orc):
         c, s = np.float32(np.cos(1.0)), np.float32(np.sin(1.0))
         want = np.stack([src[:, 0] * c - src[:, 1] * s, src[:, 1] * c + src[:, 0] * s], axis=1)
         assert np.allclose(got[:, :2], want, rtol=1e-6, atol=1e-6)
+
+
+def test_grouped_attention_maps_adjacent_query_groups_on_the_oracle(orc):
+    """grouped_attention_maps_adjacent_query_groups (src/decoder.rs:7752-7776): two KV heads of width 1 with keys [1, 0] and
+    [0, 1] and values [1, 10] and [-1, -10], four query heads of 1.0 in two groups of two, one query row that sees both
+    positions: heads 0 and 1 give 0.7310586 * 1 + 0.2689414 * 10, heads 2 and 3 give -0.2689414 - 0.7310586 * 10."""
+    keys = np.array([[[1.0], [0.0]], [[0.0], [1.0]]], np.float32)          # [token][kv head][d]
+    values = np.array([[[1.0], [-1.0]], [[10.0], [-10.0]]], np.float32)
+    k_pool, v_pool = pools(1, 2, 2, 1)
+    scatter(k_pool, v_pool, [0], keys, values, 2)
+    q = np.ones((1, 4), np.float32)
+    first = np.float32(0.7310586) * 1.0 + np.float32(0.2689414) * 10.0
+    second = -np.float32(0.2689414) - np.float32(0.7310586) * 10.0
+    for mode in (1, 2):
+        got = orc.paged_attention(q, k_pool, v_pool, [0], [0], [1], [1], q_heads=4, kv_heads=2, d=1, block_tokens=2, layers=1, layer=0,
+                                  scale=1.0, softcap=0.0, mode=mode).reshape(4)
+        assert np.max(np.abs(got - np.array([first, first, second, second], np.float32))) <= 1e-4
+    assert np.max(np.abs(dense_gqa(q.reshape(1, 4, 1), keys, values, 1, 1.0)[0, :, 0] - [first, first, second, second])) <= 1e-4
