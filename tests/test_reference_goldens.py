@@ -248,3 +248,30 @@ def test_grouped_attention_maps_adjacent_query_groups_on_the_oracle(orc):
                                   scale=1.0, softcap=0.0, mode=mode).reshape(4)
         assert np.max(np.abs(got - np.array([first, first, second, second], np.float32))) <= 1e-4
     assert np.max(np.abs(dense_gqa(q.reshape(1, 4, 1), keys, values, 1, 1.0)[0, :, 0] - [first, first, second, second])) <= 1e-4
+
+
+def test_sliding_window_masks_expired_positions_in_prefill_and_decode_on_the_oracle(orc):
+    """sliding_mask_applies_during_prefill_and_single_token_decode (src/decoder.rs:9524-9585): window 2. A decode row at position
+    2 over keys 0..2 sees keys 1 and 2 only; in a three-row prefill row 0 sees key 0, row 1 keys 0-1, row 2 keys 1-2. With
+    one-hot values the output of each row is the softmax weight of every key, so the masked cells read exactly 0."""
+    d, bt, ctx = 1, 2, 3
+    keys = np.zeros((ctx, 1, d), np.float32)                    # equal scores: the weights are uniform over what is visible
+    values = np.zeros((ctx, 1, ctx), np.float32)
+    k_pool, _ = pools(2, 1, bt, d)
+    for p in range(ctx):
+        k_pool[p // bt, 0, 0, p % bt] = keys[p]
+    # the oracle's value rows have the key width, so each of the three "which key" indicators is run as its own value plane
+    def weights(rows, start):
+        out = np.zeros((rows, ctx), np.float32)
+        for key in range(ctx):
+            v_pool = np.zeros_like(k_pool)
+            v_pool[key // bt, 0, 0, key % bt] = 1.0
+            got = orc.paged_attention(np.ones((rows, 1), np.float32), k_pool, v_pool, [0, 1], [0], [start], [rows], q_heads=1, kv_heads=1, d=1,
+                                      block_tokens=bt, layers=1, layer=0, scale=1.0, softcap=0.0, window=2, mode=2)
+            out[:, key] = got[:, 0]
+        return out
+    decode = weights(1, 2)
+    assert decode[0, 0] == 0.0 and np.allclose(decode[0, 1:], [0.5, 0.5], atol=1e-6)
+    prefill = weights(3, 0)
+    assert np.allclose(prefill, [[1.0, 0.0, 0.0], [0.5, 0.5, 0.0], [0.0, 0.5, 0.5]], atol=1e-6)
+    assert prefill[0, 1] == 0.0 and prefill[2, 0] == 0.0
