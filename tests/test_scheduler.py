@@ -435,7 +435,7 @@ def test_cancelled_queued_request_is_skipped_before_preflight_and_model_work(eng
     assert any(l[0] == 2 for t in trace for l in t)
     assert [pe.result(i)["state"] for i in range(3)] == ["cancelled", "cancelled", "done"]
     assert [oe_.results[i].state for i in range(3)] == ["cancelled", "cancelled", "done"]
-    assert pe.result(1)["message"] == "" and pe.result(1)["kind"] == "none"    # no preflight verdict of any kind
+    assert pe.result(1)["message"] == "" and pe.result(1)["kind"] == "none"    # no preflight answer of any kind
     assert pe.stats()["cancelled_requests"] == 2 and pe.stats()["failed_requests"] == 0
 
 
