@@ -111,3 +111,20 @@ def test_interleaved_sessions_are_independent_and_closing_one_does_not_touch_its
     assert [list(map(int, part)) for part in b.block_table()] == before and len(b) == 1
     _, tokens = model.forward_batch([(b, [6], 1)], want_logits=False)
     assert list(tokens) == [(31 * 6 + 7 * 1 + 3) % 32]
+
+
+def test_clearing_a_session_is_a_no_op_while_its_reservation_is_open(eng, capi):
+    """PagedKvBlockTable::clear returns at once while a reservation is in flight (cache.rs:1840-1852) and the session keeps its
+    length in step with its table (decoder.rs:3804-3818): nothing is lost from under a forward that was already planned."""
+    model = eng.Model.fake(vocab=32, block_tokens=2)
+    s = model.new_session()
+    model.forward_batch([(s, [1, 2, 3], 0)])
+    table = [list(map(int, part)) for part in s.block_table()]
+    st, r, _ = reserve(capi, model, [(s, [4], 3)])
+    assert st == 0
+    s.clear()
+    assert len(s) == 3 and [list(map(int, part)) for part in s.block_table()] == table
+    capi.check(capi.lib().mk_reservation_drop(r))
+    s.clear()
+    assert len(s) == 0 and len(s.block_table()[0]) == 0
+    assert model.pool_stats()["live_blocks"] == 0
