@@ -128,3 +128,22 @@ def test_clearing_a_session_is_a_no_op_while_its_reservation_is_open(eng, capi):
     s.clear()
     assert len(s) == 0 and len(s.block_table()[0]) == 0
     assert model.pool_stats()["live_blocks"] == 0
+
+
+def test_prefill_then_decode_advances_the_cache(eng, capi):
+    """prefill_then_decode_advances_cache (decoder.rs:8906-8930): a token outside the vocabulary is refused before anything is
+    cached; three prompt tokens, then one more at position 3; the same token at position 0 again is refused; clear empties."""
+    model = eng.Model.fake(vocab=32)
+    s = model.new_session()
+    with pytest.raises(capi.MkError, match="outside the model vocabulary"):
+        model.forward_batch([(s, [32], 0)])
+    assert len(s) == 0
+    logits, _ = model.forward_batch([(s, [1, 2, 3], 0)])
+    assert logits.shape == (1, 32) and len(s) == 3
+    model.forward_batch([(s, [4], 3)])
+    assert len(s) == 4
+    with pytest.raises(capi.MkError, match="start_pos 0 does not match decoder sequence length 4"):
+        model.forward_batch([(s, [4], 0)])
+    assert len(s) == 4
+    s.clear()
+    assert len(s) == 0
