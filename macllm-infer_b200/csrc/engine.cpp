@@ -25,11 +25,16 @@ Engine::~Engine() {
 }
 
 std::vector<int> Engine::submit(const std::vector<EngineRequest>& reqs, bool atomic_batch) {
-    if (poisoned_) throw std::runtime_error("inference worker is unavailable (Poisoned)");  // SubmitError::Unavailable, engine.rs:394-402,923
-    if (reqs.empty()) throw std::runtime_error("submission is empty");
+    // submit_batch_with_policy (engine.rs:976-1053) in its order and wording (engine.rs:394-426): empty, larger than the atomic
+    // admission limit min(queue capacity, active limit) (engine.rs:876), worker unavailable, queue full - the batch is
+    // queued whole or not at all
+    if (reqs.empty()) throw std::runtime_error("inference batch must not be empty");
+    const int maximum_atomic_batch = std::min(cfg_.queue_capacity, cfg_.max_active_sequences);
+    if (atomic_batch && (int)reqs.size() > maximum_atomic_batch)
+        throw std::runtime_error("inference batch contains " + std::to_string(reqs.size()) + " requests, but the atomic admission limit is " +
+                                 std::to_string(maximum_atomic_batch));
+    if (poisoned_) throw std::runtime_error("inference worker is unavailable (Poisoned)");
     if ((int)(queue_.size() + reqs.size()) > cfg_.queue_capacity) throw std::runtime_error("inference queue is full");
-    if (atomic_batch && (int)reqs.size() > cfg_.max_active_sequences)
-        throw std::runtime_error("atomic batch exceeds the active sequence limit");  // engine.rs:976-1053
     std::vector<int> ids;
     int batch = atomic_batch ? next_batch_++ : -1;
     if (atomic_batch) batches_.emplace_back();

@@ -177,7 +177,12 @@ class OracleEngine:
         if self.results[rid].state == "running":
             self.results[rid].state = "cancelled"
 
-    def submit(self, reqs, atomic_batch=False):
+    def submit(self, reqs, atomic_batch=False):  # submit_batch_with_policy, engine.rs:976-1053 (order and wording: 394-426)
+        if not reqs:
+            raise RuntimeError("inference batch must not be empty")
+        limit = min(self.queue_capacity, self.max_active)
+        if atomic_batch and len(reqs) > limit:
+            raise RuntimeError(f"inference batch contains {len(reqs)} requests, but the atomic admission limit is {limit}")
         if len(self.queue) + len(reqs) > self.queue_capacity:
             raise RuntimeError("inference queue is full")
         batch = None

@@ -217,7 +217,8 @@ def test_randomised_differential_with_prefix_cache(eng, seed):
 # ---- worker poisoning (src/engine.rs:1577-1647,2719-2770; tests at src/engine.rs:5603-5760) ----------------------
 
 def test_forward_failure_poisons_the_engine_and_fans_out_fatal(eng):
-    """scheduler_panic_is_caught_and_fanned_out_as_fatal (src/engine.rs:5603-5637): the tick that fails had both
+    """scheduler_panic_is_caught_and_fanned_out_as_fatal (src/engine.rs:5603-5637) and
+    fatal_model_error_poisons_active_and_queued_requests (src/engine.rs:5799-5858): the tick that fails had both
     requests packed; both, and the one still queued, end Fatal; one cleanup drain, no completion barrier; the sessions
     are gone and later submissions are refused."""
     capi = importlib.import_module("macllm_infer_b200._capi")
@@ -749,3 +750,40 @@ def test_a_long_lived_host_turns_records_off_and_releases_results(eng):
     pe.run()
     assert pe.trace() == [[(c, 0, 1), (d, 0, 1)]] and pe.tick_info(0)["kind"] == "first_token"
     assert pe.batch_trace(c)["forward_ticks"] == [0]              # numbered among the records that are kept
+
+
+def test_an_atomic_batch_that_does_not_fit_the_queue_leaves_nothing_behind(eng):
+    """partial_atomic_batch_send_aborts_queued_members_without_waiting (engine.rs:4620-4662): a batch is queued whole or not at
+    all - a refused one leaves no member waiting and takes no request ids that a later submission would skip."""
+    pm, pe = product_engine(eng, dict(vocab=32), dict(max_active_sequences=3, scheduler_token_budget=8, prefill_token_quantum=4, queue_capacity=2))
+    with pytest.raises(RuntimeError, match="inference batch contains 3 requests, but the atomic admission limit is 2"):
+        pe.submit([eng.Request([1], 1), eng.Request([2], 1), eng.Request([3], 1)], True)      # the limit is min(queue, active slots)
+    with pytest.raises(RuntimeError, match="inference batch must not be empty"):
+        pe.submit([], True)
+    first = pe.submit([eng.Request([9], 1)])
+    with pytest.raises(RuntimeError, match="inference queue is full"):
+        pe.submit([eng.Request([1], 1), eng.Request([2], 1)], True)                         # one place left for two members
+    assert pe.pending() == 1
+    pe.run()
+    ids = pe.submit([eng.Request([1], 1), eng.Request([2], 1)], True)
+    assert first == [0] and ids == [1, 2]                                                  # the refused batches took no ids
+    pe.run()
+    assert all(pe.result(i)["state"] == "done" for i in ids)
+
+
+def test_a_sequence_keeps_its_own_random_stream_and_history_across_interleaved_steps(eng):
+    """resumable_steps_preserve_sampler_rng_and_history (generation.rs:2640-2693): a seeded stochastic request draws the same
+    tokens whether it runs alone or takes turns with a neighbour under a one-token budget; another seed draws others."""
+    def run(seed, with_neighbour):
+        model = eng.Model.fake(vocab=8)
+        model.script(logits_row=[1.0, 0.9, 0.8, 0.7, 0.6, 0.5, 0.4, 0.3])
+        e = eng.Engine(model, max_active_sequences=2, scheduler_token_budget=1, prefill_token_quantum=1)
+        reqs = [eng.Request([1, 2], 12, temperature=1.0, top_k=8, top_p=1.0, seed=seed)]
+        if with_neighbour:
+            reqs.append(eng.Request([3], 9, temperature=1.0, top_k=8, top_p=1.0, seed=seed + 1))
+        ids = e.submit(reqs)
+        e.run()
+        return list(e.result(ids[0])["tokens"])
+    alone, shared, other = run(7, False), run(7, True), run(8, False)
+    assert alone == shared and len(alone) == 12
+    assert alone != other and len(set(alone)) > 1
