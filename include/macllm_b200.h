@@ -483,6 +483,19 @@ int32_t mk_prefix_cache_insert(mk_prefix_cache* c, const uint32_t* tokens, int32
 /* TokenPrefixCache::lookup_aligned_common_prefix (prefix_cache.rs:316-359): longest stored
  * block-aligned prefix strictly shorter than the prompt; *value = -1 on a miss. */
 int32_t mk_prefix_cache_lookup(mk_prefix_cache* c, const uint32_t* tokens, int32_t n, int64_t* value, int64_t* matched_tokens);
+/* Both lookups with their second bound (prefix_cache.rs:250-359).  exact != 0: TokenPrefixCache::lookup, the longest stored
+ * prefix that is an exact endpoint strictly below the prompt length and below exclusive_max_tokens (negative = no bound) - the
+ * lookup of models whose state can only be restored at the very position it was saved (recurrent mixers); exact == 0: the
+ * block-aligned common prefix inside any stored snapshot, *snapshot_tokens (optional) = the length of the snapshot that serves
+ * it.  *value = -1 on a miss; every call counts one hit or one miss. */
+int32_t mk_prefix_cache_lookup_bounded(mk_prefix_cache* c, int32_t exact, const uint32_t* tokens, int32_t n, int64_t exclusive_max_tokens,
+                                       int64_t* value, int64_t* matched_tokens, int64_t* snapshot_tokens);
+/* TokenPrefixCache::set_max_cost (prefix_cache.rs:395-409): the new budget evicts least recently used snapshots until the
+ * cache fits; their values go to evicted_out (capacity in *n_evicted, count out). */
+int32_t mk_prefix_cache_set_max_cost(mk_prefix_cache* c, int64_t max_cost, int64_t* evicted_out, int32_t* n_evicted);
+/* For tests: every digest of the (still empty) index becomes the same value, so that hits can only come from the exact token
+ * comparison (force_collisions_for_tests of the reference's own collision cases, prefix_cache.rs:824-897). */
+int32_t mk_prefix_cache_force_collisions(mk_prefix_cache* c);
 int32_t mk_prefix_cache_evict_lru(mk_prefix_cache* c, int64_t* value);
 int32_t mk_prefix_cache_diagnostics(mk_prefix_cache* c, mk_prefix_diagnostics* out);
 /* Chained block digest (prefix_cache.rs:556-594): 32 bytes per full block of `tokens`. */

@@ -213,6 +213,9 @@ SIGNATURES = {
     "mk_prefix_cache_insert": (_i32, [P, P, _i32, _i64, _i64, P, C.POINTER(_i32)]),
     "mk_prefix_cache_lookup": (_i32, [P, P, _i32, C.POINTER(_i64), C.POINTER(_i64)]),
     "mk_prefix_cache_evict_lru": (_i32, [P, C.POINTER(_i64)]),
+    "mk_prefix_cache_lookup_bounded": (_i32, [P, _i32, P, _i32, _i64, C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64)]),
+    "mk_prefix_cache_set_max_cost": (_i32, [P, _i64, P, C.POINTER(_i32)]),
+    "mk_prefix_cache_force_collisions": (_i32, [P]),
     "mk_prefix_cache_diagnostics": (_i32, [P, C.POINTER(PrefixDiagnostics)]),
     "mk_prefix_block_digests": (_i32, [_i32, P, _i32, P, C.POINTER(_i32)]),
     "mk_sha256": (_i32, [P, _i64, P]),

@@ -727,6 +727,34 @@ int32_t mk_prefix_cache_lookup(mk_prefix_cache* c, const uint32_t* tokens, int32
     });
 }
 
+int32_t mk_prefix_cache_lookup_bounded(mk_prefix_cache* c, int32_t exact, const uint32_t* tokens, int32_t n, int64_t exclusive_max_tokens,
+                                       int64_t* value, int64_t* matched_tokens, int64_t* snapshot_tokens) {
+    return guarded([&] {
+        const size_t limit = exclusive_max_tokens < 0 ? SIZE_MAX : (size_t)exclusive_max_tokens;
+        auto hit = exact != 0 ? c->c->lookup(tokens, (size_t)n, limit) : c->c->lookup_aligned_common_prefix(tokens, (size_t)n, limit);
+        *value = hit ? *hit->snapshot : -1;
+        *matched_tokens = hit ? (int64_t)hit->matched_tokens : 0;
+        if (snapshot_tokens != nullptr) *snapshot_tokens = hit ? (int64_t)hit->snapshot_tokens : 0;
+    });
+}
+
+int32_t mk_prefix_cache_set_max_cost(mk_prefix_cache* c, int64_t max_cost, int64_t* evicted_out, int32_t* n_evicted) {
+    return guarded([&] {
+        if (max_cost < 0) throw std::runtime_error("prefix-cache budget must not be negative");
+        std::vector<TokenPrefixCache<int64_t>::Evicted> ev;
+        c->c->set_max_cost((size_t)max_cost, &ev);
+        if (evicted_out != nullptr && n_evicted != nullptr) {
+            if ((int32_t)ev.size() > *n_evicted) throw std::runtime_error("eviction buffer is too small");
+            for (size_t i = 0; i < ev.size(); ++i) evicted_out[i] = ev[i].snapshot;
+        }
+        if (n_evicted != nullptr) *n_evicted = (int32_t)ev.size();
+    });
+}
+
+int32_t mk_prefix_cache_force_collisions(mk_prefix_cache* c) {
+    return guarded([&] { c->c->force_collisions_for_tests(); });
+}
+
 int32_t mk_prefix_cache_evict_lru(mk_prefix_cache* c, int64_t* value) {
     return guarded([&] {
         auto ev = c->c->evict_lru();

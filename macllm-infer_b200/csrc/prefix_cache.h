@@ -11,6 +11,7 @@
 #include <map>
 #include <optional>
 #include <stdexcept>
+#include <string>
 #include <unordered_map>
 #include <vector>
 
@@ -85,8 +86,29 @@ public:
         size_t cost;
     };
 
-    TokenPrefixCache(size_t block_tokens, size_t max_cost) : bt_(block_tokens), max_cost_(max_cost) {
+    TokenPrefixCache(size_t block_tokens, size_t max_cost) : bt_(block_tokens), max_cost_(max_cost) {  // :149-175
         if (block_tokens == 0) throw std::runtime_error("prefix-cache block size must be positive");
+        if (block_tokens > (size_t)UINT32_MAX) throw std::runtime_error("prefix-cache block size " + std::to_string(block_tokens) + " does not fit the 32-bit hash domain");
+    }
+
+    // Every digest of the index becomes the same value: hits must then come from the exact token comparison alone
+    // (force_collisions_for_tests of the reference, used by its collision cases :824-897).
+    void force_collisions_for_tests() {
+        if (!entries_.empty()) throw std::runtime_error("collisions can only be forced on an empty prefix cache");
+        forced_ = true;
+    }
+
+    // set_max_cost (:395-409): the new budget evicts least recently used snapshots until the cache fits; returns how many.
+    size_t set_max_cost(size_t max_cost, std::vector<Evicted>* evicted = nullptr) {
+        max_cost_ = max_cost;
+        size_t count = 0;
+        while (resident_cost_ > max_cost_) {
+            auto ev = evict_lru();
+            if (!ev) break;
+            ++count;
+            if (evicted) evicted->push_back(std::move(*ev));
+        }
+        return count;
     }
 
     size_t block_tokens() const { return bt_; }
@@ -99,9 +121,9 @@ public:
     bool insert(std::vector<uint32_t> tokens, T snapshot, size_t cost, std::vector<Evicted>* evicted = nullptr) {
         if (tokens.empty() || cost > max_cost_) return false;
         PromptHashPlan plan(tokens.data(), tokens.size(), bt_);
-        PrefixDigest digest = plan.endpoint(tokens.size());
+        PrefixDigest digest = index(plan.endpoint(tokens.size()));
         std::vector<PrefixDigest> block_digests;
-        for (size_t b = 1; b <= tokens.size() / bt_; ++b) block_digests.push_back(plan.endpoint(b * bt_));
+        for (size_t b = 1; b <= tokens.size() / bt_; ++b) block_digests.push_back(index(plan.endpoint(b * bt_)));
         if (auto existing = exact_entry_id(digest, tokens)) remove_entry(*existing, false);
         size_t target_old = max_cost_ - cost;
         while (resident_cost_ > target_old) {
@@ -134,7 +156,7 @@ public:
         PromptHashPlan plan(prompt, candidates.back(), bt_);
         for (auto it = candidates.rbegin(); it != candidates.rend(); ++it) {
             size_t length = *it;
-            auto bucket = by_digest_.find(plan.endpoint(length));
+            auto bucket = by_digest_.find(index(plan.endpoint(length)));
             if (bucket == by_digest_.end()) continue;
             for (uint64_t id : bucket->second) {
                 auto e = entries_.find(id);
@@ -158,7 +180,7 @@ public:
         PromptHashPlan plan(prompt, candidates.back(), bt_);
         for (auto it = candidates.rbegin(); it != candidates.rend(); ++it) {
             size_t matched = *it;
-            auto bucket = by_block_digest_.find(plan.endpoint(matched));
+            auto bucket = by_block_digest_.find(index(plan.endpoint(matched)));
             if (bucket == by_block_digest_.end()) continue;
             for (auto l = lru_.rbegin(); l != lru_.rend(); ++l) {
                 uint64_t id = *l;
@@ -206,6 +228,8 @@ private:
         uint64_t entry_id;
         size_t token_count;
     };
+
+    PrefixDigest index(const PrefixDigest& d) const { return forced_ ? PrefixDigest{} : d; }
 
     std::optional<uint64_t> exact_entry_id(const PrefixDigest& digest, const std::vector<uint32_t>& tokens) const {
         auto bucket = by_digest_.find(digest);
@@ -268,6 +292,7 @@ private:
     std::map<size_t, size_t> lengths_, block_lengths_;
     std::deque<uint64_t> lru_;
     uint64_t hits_ = 0, misses_ = 0, matched_tokens_ = 0, evictions_ = 0, insertions_ = 0;
+    bool forced_ = false;
 };
 
 }  // namespace mk

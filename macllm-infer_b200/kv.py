@@ -141,6 +141,35 @@ class PrefixCache:
         capi.check(capi.lib().mk_prefix_cache_lookup(self._h, t.ctypes.data, len(t), C.byref(v), C.byref(m)))
         return None if v.value < 0 else (int(m.value), int(v.value))
 
+    def lookup_exact(self, tokens, exclusive_max=None):
+        """TokenPrefixCache::lookup: (matched tokens, value) of the longest stored prefix that is an exact endpoint strictly
+        below the prompt length and below `exclusive_max`; None on a miss."""
+        hit = self._bounded(1, tokens, exclusive_max)
+        return None if hit is None else hit[:2]
+
+    def lookup_aligned(self, tokens, exclusive_max=None):
+        """lookup_aligned_common_prefix with its bound: (matched tokens, snapshot tokens, value) or None."""
+        hit = self._bounded(0, tokens, exclusive_max)
+        return None if hit is None else (hit[0], hit[2], hit[1])
+
+    def _bounded(self, exact, tokens, exclusive_max):
+        t = np.ascontiguousarray(tokens, dtype=np.uint32)
+        v, m, s = C.c_int64(), C.c_int64(), C.c_int64()
+        capi.check(capi.lib().mk_prefix_cache_lookup_bounded(self._h, exact, t.ctypes.data if len(t) else None, len(t),
+                                                             -1 if exclusive_max is None else int(exclusive_max),
+                                                             C.byref(v), C.byref(m), C.byref(s)))
+        return None if v.value < 0 else (int(m.value), int(v.value), int(s.value))
+
+    def set_max_cost(self, max_cost: int) -> list[int]:
+        """The new budget evicts least recently used snapshots until the cache fits; returns their values."""
+        ev = np.empty(4096, np.int64)
+        n = C.c_int32(4096)
+        capi.check(capi.lib().mk_prefix_cache_set_max_cost(self._h, max_cost, ev.ctypes.data, C.byref(n)))
+        return [int(x) for x in ev[: n.value]]
+
+    def force_collisions(self) -> None:
+        capi.check(capi.lib().mk_prefix_cache_force_collisions(self._h))
+
     def evict_lru(self):
         v = C.c_int64()
         capi.check(capi.lib().mk_prefix_cache_evict_lru(self._h, C.byref(v)))

@@ -389,6 +389,7 @@ class PrefixCache:
         self.next_id = 0
         self.entries: "OrderedDict[int, _Entry]" = OrderedDict()  # order = LRU (front = least recent)
         self.hits = self.misses = self.matched_tokens = self.evictions = self.insertions = 0
+        self.forced = False
 
     def insert(self, tokens, snapshot, cost: int):  # prefix_cache.rs:181-249; returns evicted snapshots
         tokens = tuple(int(t) for t in tokens)
@@ -414,6 +415,39 @@ class PrefixCache:
         self.resident += cost
         self.entries[eid] = _Entry(tokens, snapshot, cost, digest, full_block_digests(tokens, self.bt))
         self.insertions += 1
+        return evicted
+
+    def force_collisions(self):   # force_collisions_for_tests: hits can then only come from the exact comparison
+        assert not self.entries
+        self.forced = True
+
+    def lookup(self, prompt, exclusive_max=None):  # prefix_cache.rs:250-304: the longest exact endpoint below both bounds
+        prompt = tuple(int(t) for t in prompt)
+        limit = len(prompt) if exclusive_max is None else min(len(prompt), exclusive_max)
+        best = None
+        for eid, e in self.entries.items():
+            n = len(e.tokens)
+            if n < limit and e.tokens == prompt[:n] and (best is None or n > len(self.entries[best].tokens)):
+                best = eid
+        if best is None:
+            self.misses += 1
+            return None
+        e = self.entries[best]
+        self.hits += 1
+        self.matched_tokens += len(e.tokens)
+        self.entries.move_to_end(best)
+        return len(e.tokens), e.snapshot
+
+    def set_max_cost(self, max_cost):  # prefix_cache.rs:395-409; returns the evicted snapshots
+        self.max_cost = max_cost
+        evicted = []
+        while self.resident > self.max_cost:
+            ev = self.evict_lru()
+            if ev is None:
+                break
+            evicted.append(ev)
+            if self.drop:
+                self.drop(ev)
         return evicted
 
     def lookup_aligned_common_prefix(self, prompt, exclusive_max=None):  # prefix_cache.rs:316-359

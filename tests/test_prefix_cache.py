@@ -54,6 +54,22 @@ class OracleCache:
     def stats(self):
         return self.c.stats()
 
+    def lookup_exact(self, tokens, limit=None):
+        return self.c.lookup(tokens, limit)
+
+    def lookup_aligned(self, tokens, limit=None):
+        hit = self.c.lookup_aligned_common_prefix(tokens, limit)
+        if hit is None:
+            return None
+        owner = next(e for e in self.c.entries.values() if e.snapshot == hit[1])
+        return hit[0], len(owner.tokens), hit[1]
+
+    def set_max_cost(self, cost):
+        return self.c.set_max_cost(cost)
+
+    def force_collisions(self):
+        self.c.force_collisions()
+
 
 class ProductCache:
     def __init__(self, bt, cap):
@@ -75,6 +91,18 @@ class ProductCache:
 
     def stats(self):
         return self.c.stats()
+
+    def lookup_exact(self, tokens, limit=None):
+        return self.c.lookup_exact(tokens, limit)
+
+    def lookup_aligned(self, tokens, limit=None):
+        return self.c.lookup_aligned(tokens, limit)
+
+    def set_max_cost(self, cost):
+        return self.c.set_max_cost(cost)
+
+    def force_collisions(self):
+        self.c.force_collisions()
 
 
 @pytest.fixture(params=["oracle", "product"])
@@ -228,3 +256,99 @@ def test_empty_and_tiny_prompts_are_misses(Cache):
     assert c.lookup([1]) is None
     assert c.lookup([2, 1]) is None
     assert c.stats()["misses"] == 3 and c.stats()["hits"] == 0
+
+
+# ---- the exact-endpoint lookup (prefix_cache.rs:250-304), the lookup of models whose state restores only where it was saved ----
+
+def test_returns_the_longest_exact_prefix_from_absolute_zero(Cache):
+    """prefix_cache.rs:723-739."""
+    c = Cache(4, 10)
+    c.insert([1, 2], 2, 1)
+    c.insert([1, 2, 3], 3, 1)
+    c.insert([1, 2, 3, 4], 4, 1)
+    assert c.lookup_exact([1, 2, 3, 4, 9], 5) == (4, 4)
+    assert c.lookup_exact([0, 1, 2, 3, 4, 9], 6) is None        # a matching substring is not a prefix
+
+
+def test_excludes_the_prompt_and_maximum_limit_endpoints(Cache):
+    """prefix_cache.rs:741-758."""
+    c = Cache(4, 10)
+    c.insert([1, 2, 3], 3, 1)
+    c.insert([1, 2, 3, 4], 4, 1)
+    assert c.lookup_exact([1, 2, 3, 4]) == (3, 3)               # the full prompt endpoint stays uncached
+    assert c.lookup_exact([1, 2, 3, 4, 5], 4) == (3, 3)         # the supplied maximum is exclusive too
+    assert c.lookup_exact([1, 2, 3], 3) is None
+
+
+def test_backs_off_from_a_candidate_that_fails_exact_verification(Cache):
+    """prefix_cache.rs:760-770."""
+    c = Cache(4, 10)
+    c.insert([7, 8], 1, 1)
+    c.insert([7, 8, 9, 10], 2, 1)
+    assert c.lookup_exact([7, 8, 99, 10, 11], 5) == (2, 1)
+
+
+def test_aligned_lookup_handles_shorter_prompts_and_strict_bounds(Cache):
+    """prefix_cache.rs:795-821, with the maximum-token bound."""
+    c = Cache(4, 20)
+    c.insert(list(range(1, 13)), 7, 1)
+    assert c.lookup_aligned([1, 2, 3, 4, 5, 6], 6) == (4, 12, 7)     # a shorter prompt may fork an enclosing snapshot
+    assert c.lookup_aligned([1, 2, 3, 4, 5, 6], 4) is None           # the bound is exclusive
+    assert c.lookup_aligned([1, 2, 3, 4]) is None                    # an aligned endpoint equal to the prompt is not reusable
+    assert c.lookup_aligned([0, 1, 2, 3, 4, 5, 6], 7) is None        # a substring is not a prefix
+
+
+def test_exact_tokens_defeat_injected_digest_collisions(Cache):
+    """prefix_cache.rs:824-865: with every digest forced to the same value the answers still come from the tokens."""
+    c = Cache(4, 20)
+    c.force_collisions()
+    c.insert([1, 2, 3, 4, 5, 6, 7, 8, 10], 1, 1)
+    c.insert([9, 8, 7, 6, 5, 4, 3, 2, 10], 2, 1)
+    assert c.lookup_aligned([1, 2, 3, 4, 5, 6, 7, 8, 99], 9) == (8, 9, 1)
+    assert c.lookup_aligned([9, 8, 7, 6, 5, 4, 3, 2, 99], 9) == (8, 9, 2)
+    assert c.lookup_aligned([4, 4, 4, 4, 4, 4, 4, 4, 0], 9) is None
+    c = Cache(4, 10)
+    c.force_collisions()
+    c.insert([1, 2, 3], 1, 1)
+    c.insert([9, 8, 7], 2, 1)
+    assert c.lookup_exact([1, 2, 3, 4], 4) == (3, 1)
+    assert c.lookup_exact([9, 8, 7, 6], 4) == (3, 2)
+    assert c.lookup_exact([5, 5, 5, 0], 4) is None
+
+
+def test_replacement_is_exact_even_inside_a_collision_bucket(Cache):
+    """prefix_cache.rs:866-896: the same tokens replace their own entry and nothing else; a replacement is not an eviction."""
+    c = Cache(4, 10)
+    c.force_collisions()
+    c.insert([1, 2], 1, 2)
+    c.insert([8, 9], 2, 2)
+    assert c.insert([1, 2], 3, 3) == []
+    s = c.stats()
+    assert (s["entries"], s["cached_blocks"], s["evictions"]) == (2, 5, 0)
+    assert c.lookup_exact([1, 2, 3], 3) == (2, 3)
+    assert c.lookup_exact([8, 9, 0], 3) == (2, 2)
+
+
+def test_shrinking_budget_and_zero_cost_entries_are_supported(Cache):
+    """prefix_cache.rs:959-973."""
+    c = Cache(4, 10)
+    c.insert([1], 1, 4)
+    c.insert([2], 2, 3)
+    c.insert([3], 3, 0)
+    assert len(c.set_max_cost(3)) == 1
+    s = c.stats()
+    assert (s["cached_blocks"], s["entries"]) == (3, 2)
+    assert len(c.set_max_cost(0)) == 1
+    s = c.stats()
+    assert (s["cached_blocks"], s["entries"]) == (0, 1)
+    assert c.lookup_exact([3, 0], 2) == (1, 3)
+
+
+def test_empty_and_tiny_bounds_are_misses_on_the_exact_lookup(Cache):
+    """prefix_cache.rs:1020-1030 as written there."""
+    c = Cache(4, 10)
+    c.insert([1], 1, 1)
+    assert c.lookup_exact([], 100) is None
+    assert c.lookup_exact([1, 2], 0) is None
+    assert c.lookup_exact([1, 2], 1) is None
+    assert c.stats()["misses"] == 3
