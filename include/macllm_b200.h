@@ -308,7 +308,13 @@ typedef struct mk_request {
     /* EngineRequestPolicy (src/engine.rs:222-241): 0 = the request publishes its prompt prefix after every completed
      * prefill chunk (the default policy); 1 = benchmark_measured(): it may hit the prefix cache but publishes nothing. */
     int32_t no_prefix_publication;
-    int32_t reserved_;
+    /* The request's event channel (mpsc::channel(event_capacity) with event_send_timeout, src/engine.rs:755-767,1408-1465): at most
+     * event_capacity events - one per token, one for the terminal outcome - may wait for the host to take them with
+     * mk_engine_consume_events.  While the channel is full the request pauses (it keeps its slot, runs in no forward and shifts
+     * no peer's row); one that stays full for event_send_timeout_ms is given up like a cancelled one.  0 = no bound: the host
+     * polls mk_engine_result and never calls mk_engine_consume_events. */
+    int32_t event_capacity;
+    double event_send_timeout_ms;
 } mk_request;
 
 /* One packed forward of the schedule: which request ran which token range (the shape the reference's
@@ -379,6 +385,11 @@ int32_t mk_engine_submit(mk_engine* e, const mk_request* reqs, int32_t n, int32_
 /* ServingScheduler::drive_once (src/engine.rs:1938-1964): admit, run one tick, finalize.
  * *ran_lanes receives the number of lanes in the packed forward (0 when idle). */
 int32_t mk_engine_step(mk_engine* e, int32_t* ran_lanes);
+/* The same with the caller's clock in milliseconds (drive_once(now), src/engine.rs:1938): what event-channel timeouts are
+ * measured against.  mk_engine_step uses a monotonic clock of its own. */
+int32_t mk_engine_step_at(mk_engine* e, double now_ms, int32_t* ran_lanes);
+/* The host took n events of a request out of its channel. */
+int32_t mk_engine_consume_events(mk_engine* e, int32_t request_id, int32_t n);
 /* Run ticks until every submitted request has finished. */
 int32_t mk_engine_run(mk_engine* e);
 int32_t mk_engine_pending(mk_engine* e, int32_t* out);

@@ -83,7 +83,8 @@ class Request(C.Structure):
     _fields_ = [("prompt", C.POINTER(C.c_uint32)), ("n_prompt", C.c_int32), ("max_new_tokens", C.c_int32),
                 ("ignore_stop_tokens", C.c_int32), ("temperature", C.c_float), ("top_k", C.c_int32), ("top_p", C.c_float),
                 ("repetition_penalty", C.c_float), ("presence_penalty", C.c_float), ("frequency_penalty", C.c_float),
-                ("seed", C.c_uint64), ("no_prefix_publication", C.c_int32), ("reserved_", C.c_int32)]
+                ("seed", C.c_uint64), ("no_prefix_publication", C.c_int32), ("event_capacity", C.c_int32),
+                ("event_send_timeout_ms", C.c_double)]
 
 
 class TickLane(C.Structure):
@@ -188,6 +189,8 @@ SIGNATURES = {
     "mk_engine_status": (_i32, [P, C.POINTER(_i32)]),
     "mk_engine_failure_kind": (_i32, [P, _i32, C.POINTER(_i32)]),
     "mk_engine_cancel": (_i32, [P, _i32]),
+    "mk_engine_step_at": (_i32, [P, C.c_double, C.POINTER(_i32)]),
+    "mk_engine_consume_events": (_i32, [P, _i32, _i32]),
     "mk_engine_keep_trace": (_i32, [P, _i32]),
     "mk_engine_release_request": (_i32, [P, _i32]),
     "mk_engine_request_metrics": (_i32, [P, _i32, C.POINTER(RequestMetrics)]),

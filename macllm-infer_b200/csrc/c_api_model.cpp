@@ -403,6 +403,8 @@ int32_t mk_engine_submit(mk_engine* e, const mk_request* reqs, int32_t n, int32_
             r.max_new_tokens = reqs[i].max_new_tokens;
             r.ignore_stop_tokens = reqs[i].ignore_stop_tokens != 0;
             r.publish_prompt_prefix = reqs[i].no_prefix_publication == 0;
+            r.event_capacity = reqs[i].event_capacity;
+            r.event_send_timeout_ms = reqs[i].event_send_timeout_ms;
             r.temperature = reqs[i].temperature;
             r.top_k = reqs[i].top_k;
             r.top_p = reqs[i].top_p;
@@ -550,6 +552,17 @@ int32_t mk_engine_stats_query(mk_engine* e, mk_engine_stats* out) {
 
 int32_t mk_engine_status(mk_engine* e, int32_t* status) {
     return guarded([&] { *status = (int32_t)e->e->status(); });
+}
+
+int32_t mk_engine_step_at(mk_engine* e, double now_ms, int32_t* ran_lanes) {
+    return guarded([&] {
+        int lanes = e->e->step_at(now_ms);
+        if (ran_lanes != nullptr) *ran_lanes = lanes;
+    });
+}
+
+int32_t mk_engine_consume_events(mk_engine* e, int32_t request_id, int32_t n) {
+    return guarded([&] { e->e->consume_events(request_id, n); });
 }
 
 int32_t mk_engine_keep_trace(mk_engine* e, int32_t keep) {

@@ -1,5 +1,6 @@
 // See engine.h.  Line references are into the reference's src/engine.rs and src/generation.rs.
 #include "engine.h"
+#include <chrono>
 #include "host_sampler.h"
 #include <algorithm>
 #include <cmath>
@@ -317,10 +318,56 @@ uint32_t Engine::sample(Sequence& s, float* row) {  // Sampler::sample_with_gene
     return sample_top_k_top_p(row, vocab, rq.temperature, rq.top_k, rq.top_p, next_uniform(s.rng));
 }
 
-int Engine::step() {  // one turn of ServingScheduler::run, engine.rs:1577-1647
+int Engine::step() {
+    const double now_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now().time_since_epoch()).count();
+    return step_at(now_ms);
+}
+
+void Engine::consume_events(int id, int n) {
+    if (n < 0) throw std::runtime_error("cannot take a negative number of events");
+    for (auto& slot : active_)
+        if (slot->id == id) {
+            slot->in_channel = std::max(0, slot->in_channel - n);
+            return;
+        }
+    if (results_.find(id) == results_.end()) throw std::runtime_error("unknown request id " + std::to_string(id));
+    // a request that has left the scheduler has no channel any more: nothing to do
+}
+
+// ActiveSequence::flush_pending (engine.rs:1408-1465): move waiting events into the channel while it has room.  A full channel
+// blocks the slot; the wait is timed from the moment THIS event first met a full channel - polling does not restart it, a
+// successful send does - and a wait of event_send_timeout gives the request up like a cancellation.
+Engine::Flush Engine::flush_pending(Sequence& s, double now_ms) {
+    if (is_cancelled(s.id)) {
+        s.pending_events = 0;
+        return Flush::Abandoned;
+    }
+    if (s.req.event_capacity <= 0) {
+        s.pending_events = 0;
+        return Flush::Drained;
+    }
+    while (s.pending_events > 0) {
+        if (s.in_channel < s.req.event_capacity) {
+            ++s.in_channel;
+            --s.pending_events;
+            s.blocked_since = -1.0;
+            continue;
+        }
+        if (s.blocked_since < 0.0) s.blocked_since = now_ms;
+        if (now_ms - s.blocked_since >= s.req.event_send_timeout_ms) {
+            cancel(s.id);
+            s.pending_events = 0;
+            return Flush::Abandoned;
+        }
+        return Flush::Blocked;
+    }
+    return Flush::Drained;
+}
+
+int Engine::step_at(double now_ms) {  // one turn of ServingScheduler::run, engine.rs:1577-1647
     if (poisoned_) return 0;
     try {
-        return drive_once();
+        return drive_once(now_ms);
     } catch (const std::exception& e) {
         poison(std::string("inference worker failed: ") + e.what());
     } catch (...) {
@@ -329,7 +376,7 @@ int Engine::step() {  // one turn of ServingScheduler::run, engine.rs:1577-1647
     return 0;
 }
 
-int Engine::drive_once() {  // engine.rs:1938-1964
+int Engine::drive_once(double now_ms) {  // engine.rs:1938-1964
     try_admit_available();
     if (active_.empty()) {
         forget_settled_cancellations();
@@ -348,8 +395,14 @@ int Engine::drive_once() {  // engine.rs:1938-1964
         if (token_budget == 0) break;
         Sequence& s = *active_[(size_t)index];
         Visit v;
-        if (is_cancelled(s.id)) {  // flush_pending -> Abandoned (engine.rs:1409-1417,2024-2029): leaves before the peers' forward
+        const Flush initial = flush_pending(s, now_ms);
+        if (initial == Flush::Abandoned) {  // engine.rs:1409-1417,2024-2029: leaves before the peers' forward
             v.kind = Visit::Remove;
+            actions.push_back(v);
+            continue;
+        }
+        if (initial == Flush::Blocked) {    // engine.rs:2030-2032: the slot keeps its place and runs nothing this tick
+            v.kind = Visit::Keep;
             actions.push_back(v);
             continue;
         }
@@ -425,6 +478,7 @@ int Engine::drive_once() {  // engine.rs:1938-1964
                 for (int idx : candidates) actions[(size_t)idx].kind = Visit::Keep;
                 Sequence& s = *active_[(size_t)candidates[0]];
                 fail_request(s.id, e.what(), FailureKind::ResourceExhausted);
+                ++s.pending_events;   // EngineEvent::Failed (engine.rs:2218-2221)
                 s.delivering = true;
                 reclaim(s);
                 selected = 0;
@@ -591,6 +645,7 @@ int Engine::drive_once() {  // engine.rs:1938-1964
             ++s.generated;
             s.history.push_back(token);
             res.tokens.push_back(token);
+            ++s.pending_events;   // EngineEvent::Text with its token evidence (engine.rs:2459-2470)
             if (reaches_budget) {
                 s.phase = Phase::Finished;
                 res.finish_reason = "length";
@@ -616,6 +671,7 @@ int Engine::drive_once() {  // engine.rs:1938-1964
                     res.state = FinishState::Done;
                     if (res.finish_reason.empty()) res.finish_reason = "length";
                     ++stats_.completed;
+                    ++s.pending_events;   // EngineEvent::Finished (engine.rs:2663-2669)
                 }
                 reclaim(s);
                 s.delivering = true;
@@ -627,8 +683,11 @@ int Engine::drive_once() {  // engine.rs:1938-1964
         Visit& v = actions[(size_t)i];
         Sequence& s = *active_[(size_t)i];
         if (v.kind == Visit::Remove) continue;
-        // events drain immediately here, so a delivering slot leaves in the same tick
-        if (s.delivering) { reclaim(s); v.kind = Visit::Remove; }
+        // the flush after the batch (engine.rs:2559-2580): a finished slot leaves once its last event is in the channel; one
+        // whose channel timed out leaves now if its session is already back, else at its next visit
+        const Flush final_flush = flush_pending(s, now_ms);
+        if (final_flush == Flush::Drained && s.delivering) { reclaim(s); v.kind = Visit::Remove; }
+        else if (final_flush == Flush::Abandoned) v.kind = s.reclaimed ? Visit::Remove : Visit::Keep;
     }
     for (int i = 0; i < visits; ++i) {
         std::unique_ptr<Sequence> slot = std::move(active_.front());

@@ -34,6 +34,11 @@ struct EngineRequest {
     float repetition_penalty = 1.f, presence_penalty = 0.f, frequency_penalty = 0.f;
     uint64_t seed = 0;
     bool publish_prompt_prefix = true;
+    // The request's event channel (src/engine.rs:755-767, mpsc::channel(event_capacity)): at most `event_capacity` events - one
+    // per token, one for the terminal outcome - may wait for the host to take them (Engine::consume_events); a request whose
+    // channel stays full pauses, and one that stays full for `event_send_timeout_ms` is given up.  0 = no bound.
+    int event_capacity = 0;
+    double event_send_timeout_ms = 0.0;
 };
 
 // Cancelled: the caller gave the request up (EngineTicket::cancel / a closed event channel, src/engine.rs:1136-1145); the
@@ -104,6 +109,11 @@ public:
     // lanes of the packed forward (0 when none ran).  Any error that escapes the tick poisons the engine: every active,
     // pending and queued request fails with kind Fatal, the sessions are dropped, later submissions are refused.
     int step();
+    // The same with the caller's clock (drive_once(now), src/engine.rs:1938): `now_ms` is what back-pressure timeouts are
+    // measured against, for this tick's flush before the forward and the one after it alike.
+    int step_at(double now_ms);
+    // The host took `n` events of the request out of its channel (the receiver side of src/engine.rs:1420-1447).
+    void consume_events(int id, int n);
     // EngineTicket::cancel (src/engine.rs:1136-1145): a sticky flag the scheduler reads - a queued request is skipped
     // before any validation or model work, an active one leaves at its next visit (its pages are back before the peers'
     // forward), one cancelled while its forward ran drops its row after the completion barrier.  The one entry that may be
@@ -147,6 +157,9 @@ private:
         int generated = 0;
         bool delivering = false;
         uint64_t rng = 0;
+        int pending_events = 0;      // produced, not yet in the channel (ActiveSequence::pending)
+        int in_channel = 0;          // in the channel, not yet taken by the host
+        double blocked_since = -1.0; // when the channel was first found full for the event now waiting; < 0: not blocked
     };
     struct Visit {
         enum Kind { Keep, Remove, Preview, Forward, Complete } kind = Keep;
@@ -159,7 +172,9 @@ private:
     bool try_admit_available();
     bool admit_pending_atomic();
     void admit(Job job);
-    int drive_once();
+    enum class Flush { Drained, Blocked, Abandoned };
+    Flush flush_pending(Sequence& s, double now_ms);
+    int drive_once(double now_ms);
     void poison(std::string message);
     void fail_request(int id, const std::string& message, FailureKind kind = FailureKind::InvalidRequest);
     void reclaim(Sequence& s);

@@ -28,6 +28,8 @@ class Request:
     frequency_penalty: float = 0.0
     seed: int = 0
     publish_prompt_prefix: bool = True
+    event_capacity: int = 0             # events (one per token, one terminal) that may wait for `Engine.consume`; 0 = no bound
+    event_send_timeout_ms: float = 0.0  # how long a full channel is tolerated before the request is given up
 
 
 class Session:
@@ -300,14 +302,24 @@ class Engine:
             arr[i].frequency_penalty = r.frequency_penalty
             arr[i].seed = r.seed
             arr[i].no_prefix_publication = 0 if r.publish_prompt_prefix else 1
+            arr[i].event_capacity = r.event_capacity
+            arr[i].event_send_timeout_ms = r.event_send_timeout_ms
         ids = np.empty(n, np.int32)
         capi.check(capi.lib().mk_engine_submit(self._h, arr, n, 1 if atomic_batch else 0, ids.ctypes.data))
         return [int(x) for x in ids]
 
-    def step(self) -> int:
+    def step(self, now_ms: float | None = None) -> int:
+        """One scheduler tick; `now_ms` is the clock that event-channel timeouts are measured against (the engine's own if None)."""
         lanes = C.c_int32()
-        capi.check(capi.lib().mk_engine_step(self._h, C.byref(lanes)))
+        if now_ms is None:
+            capi.check(capi.lib().mk_engine_step(self._h, C.byref(lanes)))
+        else:
+            capi.check(capi.lib().mk_engine_step_at(self._h, float(now_ms), C.byref(lanes)))
         return int(lanes.value)
+
+    def consume(self, request_id: int, n: int = 1) -> None:
+        """The host took `n` events of the request out of its channel."""
+        capi.check(capi.lib().mk_engine_consume_events(self._h, request_id, n))
 
     def run(self) -> None:
         capi.check(capi.lib().mk_engine_run(self._h))

@@ -116,6 +116,8 @@ class Req:
     presence_penalty: float = 0.0
     frequency_penalty: float = 0.0
     publish_prompt_prefix: bool = True
+    event_capacity: int = 0              # mpsc::channel(event_capacity), engine.rs:755-767; 0 = no bound
+    event_send_timeout_ms: float = 0.0
 
 
 @dataclass
@@ -131,6 +133,9 @@ class _Seq:
     generated: int = 0
     delivering: bool = False
     reclaimed: dict | None = None
+    pending_events: int = 0
+    in_channel: int = 0
+    blocked_since: float | None = None
 
 
 @dataclass
@@ -275,7 +280,34 @@ class OracleEngine:
             s.reclaimed = s.session
             s.session = None
 
-    def step(self) -> int:  # drive_once, engine.rs:1938-1964
+    def consume(self, rid, n=1):  # the receiver side of the request's event channel
+        for s in self.active:
+            if s.rid == rid:
+                s.in_channel = max(0, s.in_channel - n)
+
+    def _flush(self, s: _Seq, now_ms: float) -> str:  # ActiveSequence::flush_pending, engine.rs:1408-1465
+        if s.rid in self.cancelled:
+            s.pending_events = 0
+            return "abandoned"
+        if s.req.event_capacity <= 0:
+            s.pending_events = 0
+            return "drained"
+        while s.pending_events > 0:
+            if s.in_channel < s.req.event_capacity:
+                s.in_channel += 1
+                s.pending_events -= 1
+                s.blocked_since = None
+                continue
+            if s.blocked_since is None:
+                s.blocked_since = now_ms
+            if now_ms - s.blocked_since >= s.req.event_send_timeout_ms:
+                self.cancelled.add(s.rid)
+                s.pending_events = 0
+                return "abandoned"
+            return "blocked"
+        return "drained"
+
+    def step(self, now_ms: float = 0.0) -> int:  # drive_once, engine.rs:1938-1964
         self._try_admit()
         if not self.active:
             return 0
@@ -288,8 +320,12 @@ class OracleEngine:
             if token_budget == 0:
                 break
             s = self.active[index]
-            if s.rid in self.cancelled:  # flush_pending -> Abandoned, engine.rs:1409-1417,2024-2029
+            initial = self._flush(s, now_ms)
+            if initial == "abandoned":  # engine.rs:1409-1417,2024-2029
                 actions.append(dict(kind="remove"))
+                continue
+            if initial == "blocked":    # engine.rs:2030-2032
+                actions.append(dict(kind="keep"))
                 continue
             if s.delivering:
                 actions.append(dict(kind="remove"))
@@ -330,6 +366,7 @@ class OracleEngine:
                         actions[i] = dict(kind="keep")
                     s = self.active[candidates[0]]
                     self._fail(s.rid, str(e))
+                    s.pending_events += 1
                     s.delivering = True
                     self._reclaim(s)
                     selected = 0
@@ -383,6 +420,7 @@ class OracleEngine:
                 s.generated += 1
                 s.history.append(token)
                 res.tokens.append(token)
+                s.pending_events += 1
                 if reaches:
                     s.phase, a["finished"] = "finished", True
                     continue
@@ -395,14 +433,20 @@ class OracleEngine:
                 if a["finished"]:
                     if self.results[s.rid].state == "running":
                         self.results[s.rid].state = "done"
+                        s.pending_events += 1
                     self._reclaim(s)
                     s.delivering = True
                 a["kind"] = "keep"
         for i, a in enumerate(actions):
             s = self.active[i]
-            if a["kind"] != "remove" and s.delivering:
+            if a["kind"] == "remove":
+                continue
+            final = self._flush(s, now_ms)   # engine.rs:2559-2580
+            if final == "drained" and s.delivering:
                 self._reclaim(s)
                 a["kind"] = "remove"
+            elif final == "abandoned":
+                a["kind"] = "remove" if s.reclaimed is not None else "keep"
         for a in actions:
             slot = self.active.popleft()
             if a["kind"] == "remove":

@@ -787,3 +787,135 @@ def test_a_sequence_keeps_its_own_random_stream_and_history_across_interleaved_s
     alone, shared, other = run(7, False), run(7, True), run(8, False)
     assert alone == shared and len(alone) == 12
     assert alone != other and len(set(alone)) > 1
+
+
+# ---- event-channel back-pressure (ActiveSequence::flush_pending, src/engine.rs:1408-1465; tests at src/engine.rs:5132-5283) ----
+
+def step_both(pe, oe_, now_ms):
+    lp, lo = pe.step(now_ms), oe_.step(now_ms)
+    assert lp == lo
+    return lp
+
+
+def lanes_of(pe, rid):
+    return sum(1 for t in pe.trace() for l in t if l[0] == rid)
+
+
+def test_a_backpressured_slot_is_skipped_while_its_peer_finishes(eng):
+    """engine.rs:5132-5237: quantum 1; "a" wants 3 tokens through a channel of ONE event with a 10 ms timeout, "b" 2 tokens
+    through a roomy one. After five ticks "a" has run twice and waits with one event pending while "b" has finished. Polling
+    the full channel does not restart its clock; once the host takes an event, "a" runs again and the next full channel gets
+    a fresh clock; 9 ms later it is still waiting, 11 ms later it is given up and both sessions are back."""
+    from oracle import engine as oe
+    ekw = dict(max_active_sequences=2, scheduler_token_budget=8, prefill_token_quantum=1)
+    (pm, pe), (om, oe_) = both(eng, dict(vocab=32), ekw)
+    slow, peer = pe.submit([eng.Request([1], 3, event_capacity=1, event_send_timeout_ms=10.0),
+                            eng.Request([2], 2, event_capacity=8, event_send_timeout_ms=10.0)])
+    assert [slow, peer] == oe_.submit([oe.Req([1], 3, event_capacity=1, event_send_timeout_ms=10.0),
+                                      oe.Req([2], 2, event_capacity=8, event_send_timeout_ms=10.0)])
+    for _ in range(5):
+        step_both(pe, oe_, 0.0)
+    assert lanes_of(pe, slow) == 2, "the slow slot pauses with one event pending"
+    assert pe.result(peer)["state"] == "done" and len(pe.result(peer)["tokens"]) == 2
+    assert pe.result(slow)["state"] == "running" and len(pe.result(slow)["tokens"]) == 2
+    assert pm.pool_stats() == om.pool.stats()
+    step_both(pe, oe_, 5.0)
+    assert lanes_of(pe, slow) == 2, "a blocked slot runs no forward"
+    pe.consume(slow, 1)
+    oe_.consume(slow, 1)
+    step_both(pe, oe_, 5.0)                       # the waiting event goes out, the third token is produced, the channel is full again
+    assert lanes_of(pe, slow) == 3
+    step_both(pe, oe_, 5.0 + 9.0)
+    assert pe.pending() == 1 and pe.result(slow)["state"] == "done", "9 ms into the new wait the request is still held"
+    step_both(pe, oe_, 5.0 + 11.0)
+    step_both(pe, oe_, 5.0 + 11.0)
+    assert pe.pending() == 0 and oe_.pending() == 0, "the timed-out slot has left"
+    assert pe.trace() == [[tuple(l) for l in t] for t in oe_.trace]
+    assert pm.pool_stats()["live_blocks"] == 0
+    a, b = pe.submit([eng.Request([3], 1), eng.Request([4], 1)])       # both sessions are back
+    pe.run()
+    assert pe.result(a)["state"] == pe.result(b)["state"] == "done" and len(pe.trace()[-1]) == 2
+
+
+def test_polling_a_full_channel_does_not_restart_its_timeout(eng):
+    """engine.rs:5195-5215: the wait is timed from the moment the event first met a full channel."""
+    pm, pe = product_engine(eng, dict(vocab=32), dict(max_active_sequences=1, scheduler_token_budget=8, prefill_token_quantum=4))
+    rid = pe.submit([eng.Request([1], 4, event_capacity=1, event_send_timeout_ms=10.0)])[0]
+    pe.step(0.0)
+    pe.step(1.0)                                   # second token: the channel is full from t = 1
+    for now in (3.0, 6.0, 9.0, 10.9):
+        assert pe.step(now) == 0 and pe.pending() == 1
+    pe.step(11.0)                                  # 10 ms after t = 1
+    pe.step(11.0)
+    assert pe.pending() == 0 and pe.result(rid)["state"] == "cancelled" and len(pe.result(rid)["tokens"]) == 2
+
+
+def test_a_blocked_middle_slot_is_filtered_without_shifting_packed_rows(eng):
+    """engine.rs:5238-5283: three active one-token prompts with 3 new tokens each, budget 3, quantum 1; the middle one has a
+    channel of one event. Ticks 1 and 2 pack all three; in tick 3 the middle slot is held and the forward carries the first
+    and the third at rows 0 and 1 with their own inputs and positions."""
+    from oracle import engine as oe
+    ekw = dict(max_active_sequences=3, scheduler_token_budget=3, prefill_token_quantum=1)
+    (pm, pe), (om, oe_) = both(eng, dict(vocab=32), ekw)
+    caps = (8, 1, 8)
+    ids = pe.submit([eng.Request([p], 3, event_capacity=c, event_send_timeout_ms=1000.0) for p, c in zip((1, 2, 3), caps)])
+    assert ids == oe_.submit([oe.Req([p], 3, event_capacity=c, event_send_timeout_ms=1000.0) for p, c in zip((1, 2, 3), caps)])
+    for _ in range(3):
+        step_both(pe, oe_, 0.0)
+    trace = pe.trace()
+    assert trace == [[tuple(l) for l in t] for t in oe_.trace]
+    assert [[l[0] for l in t] for t in trace] == [[0, 1, 2], [0, 1, 2], [0, 2]]
+    assert trace[2] == [(0, 2, 1), (2, 2, 1)]
+    assert lanes_of(pe, 1) == 2, "the blocked middle slot does not run in the third tick"
+    assert pe.stats()["cleanup_drains"] == 0 and pe.stats()["ticks"] == 3
+    # the third tick's tokens are those of rows 0 and 1 of that forward, not shifted by the missing lane
+    fake = lambda t, p: (31 * t + 7 * p + 3) % 32
+    for rid, first in ((0, 1), (2, 3)):
+        want, tok = [], first
+        for pos in range(3):
+            tok = fake(tok, pos)
+            want.append(tok)
+        assert list(pe.result(rid)["tokens"]) == want
+
+
+def test_an_unbounded_channel_never_blocks_and_needs_no_consumer(eng):
+    pm, pe = product_engine(eng, dict(vocab=32), dict(max_active_sequences=1, scheduler_token_budget=8, prefill_token_quantum=4))
+    rid = pe.submit([eng.Request([1], 50)])[0]
+    pe.run()
+    assert pe.result(rid)["state"] == "done" and len(pe.result(rid)["tokens"]) == 50
+    with pytest.raises(RuntimeError, match="unknown request id 5"):
+        pe.consume(5, 1)
+    pe.consume(rid, 3)                             # a request that has left the scheduler has no channel: nothing happens
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_randomised_differential_with_backpressure(eng, seed):
+    """Channels of one to three events, hosts that take events at random moments, a clock that advances: schedules, tokens,
+    states and pool statistics agree with the oracle tick by tick."""
+    from oracle import engine as oe
+    rng = random.Random(2000 + seed)
+    ekw = dict(max_active_sequences=rng.choice([2, 3, 5]), scheduler_token_budget=rng.choice([4, 16]), prefill_token_quantum=rng.choice([1, 4]),
+               queue_capacity=64)
+    (pm, pe), (om, oe_) = both(eng, dict(vocab=64, block_tokens=4, kv_capacity_tokens=4096), ekw)
+    reqs = [([rng.randrange(3, 64) for _ in range(rng.randint(1, 9))], rng.randint(1, 10), rng.choice([0, 1, 2, 3]), rng.choice([5.0, 40.0, 1e9]))
+            for _ in range(12)]
+    ids = pe.submit([eng.Request(p, n, event_capacity=c, event_send_timeout_ms=t) for p, n, c, t in reqs])
+    assert ids == oe_.submit([oe.Req(p, n, event_capacity=c, event_send_timeout_ms=t) for p, n, c, t in reqs])
+    now = 0.0
+    for _ in range(400):
+        if pe.pending() == 0:
+            break
+        now += rng.choice([0.0, 1.0, 7.0])
+        for rid in ids:
+            if rng.random() < 0.3:
+                n = rng.randint(1, 2)
+                pe.consume(rid, n)
+                oe_.consume(rid, n)
+        step_both(pe, oe_, now)
+        assert pm.pool_stats() == om.pool.stats()
+    assert pe.pending() == 0 and oe_.pending() == 0
+    assert pe.trace() == [[tuple(l) for l in t] for t in oe_.trace]
+    for rid in ids:
+        rp, ro = pe.result(rid), oe_.results[rid]
+        assert rp["state"] == ro.state and list(rp["tokens"]) == ro.tokens
+    assert pm.pool_stats()["live_blocks"] == 0
