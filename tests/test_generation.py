@@ -123,8 +123,9 @@ def test_a_zero_budget_request_finishes_without_model_work(eng):
 
 
 def test_the_token_budget_chunks_prefill_without_sampling_intermediate_logits(eng):
-    """generation.rs:2517-2585: intermediate chunks advance the cursor and sample nothing; only the chunk that ends the
-    prompt samples, and the result equals the one-shot run."""
+    """generation.rs:2517-2585 and 2586-2639 (blocking_quantum_chunks_prefill_and_matches_one_shot_generation): intermediate
+    chunks advance the cursor and sample nothing; only the chunk that ends the prompt samples, and the result equals the
+    one-shot run."""
     _, chunked, a = one(eng, [1, 2, 3, 4, 5, 6, 7], 3, engine_kw=dict(scheduler_token_budget=3, prefill_token_quantum=3))
     _, whole, b = one(eng, [1, 2, 3, 4, 5, 6, 7], 3)
     assert [t[0][1:] for t in chunked.trace()] == [(0, 3), (3, 3), (6, 1), (7, 1), (8, 1)]
