@@ -165,3 +165,16 @@ def test_two_sequences_interleave_without_crossing_sessions(eng):
     _, eb, rb = one(eng, [4, 5], 4)
     assert list(e.result(a)["tokens"]) == list(ea.result(ra)["tokens"])
     assert list(e.result(b)["tokens"]) == list(eb.result(rb)["tokens"])
+
+
+def test_resumable_steps_run_one_forward_per_quantum_and_hide_the_stop_token(eng):
+    """resumable_steps_match_blocking_generation_and_one_forward_per_quantum (generation.rs:2312-2403): prompt [0, 0], up to
+    four tokens, stop tokens honoured: three forwards - the prompt, then each visible token at positions 2 and 3 - and the
+    third samples the stop token, which is never visible: two tokens, two decode steps, reason Stop."""
+    # the fake answers (0 at position 1) -> 2, (2 at position 2) -> 7, (7 at position 3) -> 1, the stop token
+    model, e, rid = one(eng, [0, 0], 4, dict(vocab=8), stop_ids=[1], ignore_stop_tokens=False)
+    assert e.trace() == [[(rid, 0, 2)], [(rid, 2, 1)], [(rid, 3, 1)]]
+    assert list(e.result(rid)["tokens"]) == [2, 7]
+    m = e.metrics(rid)
+    assert (m["prompt_tokens"], m["generated_tokens"], m["decode_steps"], m["finish_reason"]) == (2, 2, 2, "stop")
+    assert model.pool_stats()["live_blocks"] == 0
