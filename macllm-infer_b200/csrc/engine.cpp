@@ -81,6 +81,8 @@ void Engine::release_request(int id) {
     auto it = results_.find(id);
     if (it == results_.end()) throw std::runtime_error("unknown request id " + std::to_string(id));
     if (it->second.state == FinishState::Running) throw std::runtime_error("request " + std::to_string(id) + " is still running");
+    for (const auto& slot : active_)
+        if (slot->id == id) throw std::runtime_error("request " + std::to_string(id) + " still has events to deliver");
     results_.erase(it);
     auto b = batch_of_request_.find(id);
     if (b != batch_of_request_.end()) {   // the batch's trace goes with its last member

@@ -164,13 +164,17 @@ class _Job:
         # it on to the engine, which drops the request at its next look at it
         self.cancelled = threading.Event()
         self.cancel_sent = False
+        # the request's event channel: the handler counts the events it has dealt with, the worker tells the engine
+        self.taken = 0
+        self.taken_sent = 0
 
 
 class CompletionServer:
     """`engine_factory()` is called on the worker thread and returns (engine, model); the server owns both from then on.
     `metadata`: served_model / device / dtype strings of `/healthz` and `/v1/models`."""
 
-    def __init__(self, engine_factory, bind=("127.0.0.1", 0), tokenizer=None, metadata=None, idle_wait_s=0.001):
+    def __init__(self, engine_factory, bind=("127.0.0.1", 0), tokenizer=None, metadata=None, idle_wait_s=0.001,
+                 event_capacity=0, event_send_timeout_s=30.0):
         self._factory = engine_factory
         self._tokenizer = tokenizer
         self._meta = dict(served_model="macllm-b200", device="cuda", dtype="f16")
@@ -181,6 +185,11 @@ class CompletionServer:
         self._status = "starting"
         self._max_context = 0
         self._idle_wait_s = idle_wait_s
+        # EngineConfig::event_capacity / event_send_timeout (src/engine.rs:320-323; the reference's defaults are 16 events and
+        # 30 s): how many events of a request may wait for its connection, and for how long a full channel is tolerated before
+        # the request is given up.  0 = no bound.
+        self._event_capacity = int(event_capacity)
+        self._event_send_timeout_ms = float(event_send_timeout_s) * 1e3
         self._worker_error = None
         self._worker = threading.Thread(target=self._run_worker, name="inference-worker", daemon=True)
         server = self
@@ -261,6 +270,7 @@ class CompletionServer:
                     if ev is None:
                         self.close_connection = True
                         return
+                    job.taken += 1
                     if ev[0] == "token":
                         content += ev[3]
                     elif ev[0] == "finished":
@@ -298,6 +308,7 @@ class CompletionServer:
                                 break
                             last = n_decoded
                             send(fragment_event(text, token_id, n_decoded, len(job.tokens)))
+                            job.taken += 1            # the event has left for the client: its place in the channel is free
                         elif ev[0] == "finished":
                             err = _check_terminal(job.settings, ev[1])
                             if err is None and last != ev[1]["generated_tokens"]:
@@ -370,6 +381,7 @@ class CompletionServer:
         self._status = "ready"
         self._ready.set()
         active: dict[int, _Job] = {}
+        draining: dict[int, _Job] = {}     # answered requests whose last events the engine still holds for their channel
         try:
             while not self._stop.is_set():
                 # admit what the handlers queued; block only when there is nothing to run
@@ -383,7 +395,9 @@ class CompletionServer:
                         s = job.settings
                         (rid,) = engine.submit([_engine.Request(job.tokens, s["n_predict"], ignore_stop_tokens=True, temperature=s["temperature"],
                                                                 top_k=s["top_k"], top_p=s["top_p"], seed=s["seed"],
-                                                                publish_prompt_prefix=job.publish_prefix)])
+                                                                publish_prompt_prefix=job.publish_prefix,
+                                                                event_capacity=self._event_capacity,
+                                                                event_send_timeout_ms=self._event_send_timeout_ms)])
                         job.request_id = rid
                         active[rid] = job
                         reply.put(None)
@@ -399,8 +413,14 @@ class CompletionServer:
                         item = False
                 if item is None:
                     break
-                if not active:
+                if not active and not draining:
                     continue
+                if self._event_capacity > 0:
+                    for rid, job in list(active.items()) + list(draining.items()):
+                        taken = job.taken
+                        if taken > job.taken_sent:
+                            engine.consume(rid, taken - job.taken_sent)
+                            job.taken_sent = taken
                 try:
                     engine.step()
                 except Exception:
@@ -428,17 +448,21 @@ class CompletionServer:
                                                          stop_type={"length": "limit", "stop": "stop"}.get(reason, "cancelled"),
                                                          prefill_ms=(first - job.t_submit) * 1e3, ttft_ms=(first - job.t_submit) * 1e3,
                                                          total_ms=(now - job.t_submit) * 1e3)))
-                        del active[rid]
-                        engine.release(rid)
+                        draining[rid] = active.pop(rid)
                     elif state == "failed":
                         r = engine.result(rid)
                         job.events.put(("failed", r["kind"], r["message"]))
-                        del active[rid]
-                        engine.release(rid)
+                        draining[rid] = active.pop(rid)
                     elif state == "cancelled":   # nobody is listening any more: no event
-                        del active[rid]
+                        draining[rid] = active.pop(rid)
+                for rid in list(draining):       # the result is dropped once the engine has let go of the slot
+                    try:
                         engine.release(rid)
-                if self._status not in ("poisoned",) and not active:
+                        del draining[rid]
+                    except Exception as e:
+                        if "still has events to deliver" not in str(e):
+                            del draining[rid]
+                if self._status not in ("poisoned",) and not active and not draining:
                     self._status = "ready"
         except Exception as e:  # a scheduler panic (src/engine.rs:1600-1647): fatal for everything in flight, the worker is gone
             self._status = "poisoned"

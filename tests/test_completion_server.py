@@ -387,3 +387,39 @@ def test_completion_requires_the_exact_requested_token_boundary(mk, srv_mod, str
         assert srv_mod._check_terminal(settings, dict(good, stop_type="stop")) is not None
     finally:
         s.stop()
+
+
+def test_a_connection_that_stops_taking_events_pauses_its_request_and_is_given_up(mk, srv_mod):
+    """The request's event channel at the endpoint (EngineConfig::event_capacity / event_send_timeout, src/engine.rs:320-323,
+    1408-1465): with room for two events and 0.3 s of patience, a request whose connection takes nothing stops after its
+    first events while a peer is served in full, and is given up once its channel has stayed full for the timeout."""
+    import time
+    eng = importlib.import_module("macllm_infer_b200.engine")
+    made = {}
+
+    def factory():
+        model = eng.Model.fake(vocab=64, max_context=4096, kv_capacity_tokens=16384)
+        made["model"] = model
+        made["engine"] = _SlowEngine(eng.Engine(model, max_active_sequences=4, scheduler_token_budget=64, prefill_token_quantum=32,
+                                                queue_capacity=8), 0.002)
+        return made["engine"], model
+    s = srv_mod.CompletionServer(factory, metadata=dict(served_model="test-model", device="cpu", dtype="f32"),
+                                 event_capacity=2, event_send_timeout_s=0.3).start()
+    try:
+        settings = dict(n_predict=200, temperature=0.0, top_k=1, top_p=1.0, seed=1)
+        stuck = s._submit([5, 6, 7], settings)                       # a job nobody reads from
+        st, _, b = call(s, "POST", "/completion", body(srv_mod, prompt=[9, 8], n_predict=60))
+        assert st == 200 and json.loads(b)["tokens_predicted"] == 60       # the peer ran to its end through the same ticks
+        assert 2 <= stuck.events.qsize() <= 4, "two events in the channel, at most two more waiting in the engine"
+        deadline = time.time() + 10
+        while time.time() < deadline and made["engine"].pending() > 0:
+            time.sleep(0.02)
+        e = made["engine"]
+        assert e.pending() == 0
+        r = e.final[stuck.request_id]
+        assert r["state"] == "cancelled" and len(r["tokens"]) <= 4
+        assert made["model"].pool_stats()["live_blocks"] == 0
+        st, _, b = call(s, "GET", "/healthz")
+        assert st == 200 and json.loads(b)["worker"] == "ready"
+    finally:
+        s.stop()
