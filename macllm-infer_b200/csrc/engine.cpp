@@ -136,7 +136,7 @@ void Engine::forget_settled_cancellations() {
     std::lock_guard<std::mutex> lock(cancel_mu_);
     for (auto it = cancelled_.begin(); it != cancelled_.end();) {
         auto r = results_.find(*it);
-        if (r != results_.end() && r->second.state != FinishState::Running) it = cancelled_.erase(it);
+        if (r == results_.end() || r->second.state != FinishState::Running) it = cancelled_.erase(it);   // ended, or already released
         else ++it;
     }
     if (cancelled_.empty()) any_cancelled_.store(false, std::memory_order_release);
