@@ -1,6 +1,7 @@
 // See engine.h.  Line references are into the reference's src/engine.rs and src/generation.rs.
 #include "engine.h"
 #include <chrono>
+#include <thread>
 #include "host_sampler.h"
 #include <algorithm>
 #include <cmath>
@@ -389,6 +390,7 @@ int Engine::drive_once(double now_ms) {  // engine.rs:1938-1964
         round_budget_remaining_ = cfg_.scheduler_token_budget;
     }
 
+    blocked_last_tick_ = 0;
     // ---- collect_visits (engine.rs:2005-2095)
     const int visit_limit = std::min(round_visits_remaining_, (int)active_.size());
     std::vector<Visit> actions;
@@ -404,6 +406,7 @@ int Engine::drive_once(double now_ms) {  // engine.rs:1938-1964
             continue;
         }
         if (initial == Flush::Blocked) {    // engine.rs:2030-2032: the slot keeps its place and runs nothing this tick
+            ++blocked_last_tick_;
             v.kind = Visit::Keep;
             actions.push_back(v);
             continue;
@@ -715,6 +718,12 @@ void Engine::run() {
     int idle = 0;
     while (pending() > 0 && !poisoned_) {
         int lanes = step();
+        if (lanes == 0 && blocked_last_tick_ > 0) {
+            // every runnable slot waits for its channel: the wait ends by the host taking events or by the send timeout, so
+            // this is time passing, not a scheduler that makes no progress
+            std::this_thread::sleep_for(std::chrono::microseconds(200));
+            continue;
+        }
         idle = lanes > 0 ? 0 : idle + 1;
         if (idle > 4 * (cfg_.max_active_sequences + 4)) throw std::runtime_error("scheduler made no progress");
     }

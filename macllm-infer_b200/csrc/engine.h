@@ -202,6 +202,7 @@ private:
     std::vector<uint32_t> tokens_host_;
     bool poisoned_ = false;
     bool keep_trace_ = true;
+    int blocked_last_tick_ = 0;   // slots found waiting for their event channel in the last tick
     int orphan_ = -1;                   // request whose admission threw
     bool forward_needs_drain_ = false;  // a reservation or forward was submitted and no completion barrier ran yet
     std::string poison_message_;

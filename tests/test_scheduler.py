@@ -919,3 +919,15 @@ def test_randomised_differential_with_backpressure(eng, seed):
         rp, ro = pe.result(rid), oe_.results[rid]
         assert rp["state"] == ro.state and list(rp["tokens"]) == ro.tokens
     assert pm.pool_stats()["live_blocks"] == 0
+
+
+def test_run_waits_out_a_full_channel_instead_of_reporting_no_progress(eng):
+    """A host that drives the engine with run() and never takes events: the request pauses when its channel is full and is
+    given up when the send timeout has passed on the engine's own clock; the wait is not mistaken for a stuck scheduler."""
+    pm, pe = product_engine(eng, dict(vocab=32), dict(max_active_sequences=2, scheduler_token_budget=8, prefill_token_quantum=4))
+    held, free = pe.submit([eng.Request([1], 20, event_capacity=2, event_send_timeout_ms=30.0), eng.Request([2], 20)])
+    pe.run()
+    assert pe.pending() == 0
+    assert pe.result(free)["state"] == "done" and len(pe.result(free)["tokens"]) == 20
+    assert pe.result(held)["state"] == "cancelled" and 2 <= len(pe.result(held)["tokens"]) <= 3
+    assert pe.status() == "ready" and pm.pool_stats()["live_blocks"] == 0
