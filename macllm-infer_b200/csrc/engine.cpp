@@ -380,6 +380,7 @@ int Engine::step_at(double now_ms) {  // one turn of ServingScheduler::run, engi
 }
 
 int Engine::drive_once(double now_ms) {  // engine.rs:1938-1964
+    blocked_last_tick_ = 0;
     try_admit_available();
     if (active_.empty()) {
         forget_settled_cancellations();
@@ -390,7 +391,6 @@ int Engine::drive_once(double now_ms) {  // engine.rs:1938-1964
         round_budget_remaining_ = cfg_.scheduler_token_budget;
     }
 
-    blocked_last_tick_ = 0;
     // ---- collect_visits (engine.rs:2005-2095)
     const int visit_limit = std::min(round_visits_remaining_, (int)active_.size());
     std::vector<Visit> actions;
