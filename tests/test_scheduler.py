@@ -931,3 +931,26 @@ def test_run_waits_out_a_full_channel_instead_of_reporting_no_progress(eng):
     assert pe.result(free)["state"] == "done" and len(pe.result(free)["tokens"]) == 20
     assert pe.result(held)["state"] == "cancelled" and 2 <= len(pe.result(held)["tokens"]) <= 3
     assert pe.status() == "ready" and pm.pool_stats()["live_blocks"] == 0
+
+
+def test_token_prompts_pass_through_unchanged_and_health_is_explicit(eng):
+    """raw_token_input_bypasses_chat_rendering_and_preserves_ids (engine.rs:4178-4194): the ids [4, 0, 2] reach the model as
+    they are - id 0 included - and ignore_stop_tokens stays in force. status_health_is_explicit (engine.rs:4366-4374): Ready
+    and Busy accept work, Poisoned does not."""
+    pm, pe = product_engine(eng, dict(vocab=32), dict(max_active_sequences=1, scheduler_token_budget=8, prefill_token_quantum=8))
+    pm.script(stop_ids=[(31 * 2 + 7 * 2 + 3) % 32])          # the first sampled token would stop a request that honoured stop ids
+    assert pe.status() == "ready"
+    rid = pe.submit([eng.Request([4, 0, 2], 2, ignore_stop_tokens=True)])[0]
+    assert pe.status() == "busy"
+    pe.run()
+    assert pe.trace()[0] == [(rid, 0, 3)]                     # three prompt tokens, none dropped or added
+    fake = lambda t, p: (31 * t + 7 * p + 3) % 32
+    first = fake(2, 2)
+    assert list(pe.result(rid)["tokens"]) == [first, fake(first, 3)] and pe.metrics(rid)["finish_reason"] == "length"
+    assert pe.status() == "ready"
+    pm.inject_failure("forward", 2)
+    pe.submit([eng.Request([1], 1)])
+    pe.run()
+    assert pe.status() == "poisoned"
+    with pytest.raises(RuntimeError, match="unavailable"):
+        pe.submit([eng.Request([1], 1)])
