@@ -428,6 +428,17 @@ GgufFile::GgufFile(const std::string& path) {
     }
     for (size_t i = 0; i < tensors_.size(); ++i)
         if (!by_name_.emplace(tensors_[i].name, i).second) throw std::runtime_error("GGUF tensor `" + tensors_[i].name + "` appears more than once");
+    // validate_quantization_metadata (src/gguf.rs:664,1019-1037): block formats are only defined for quantisation version 2
+    bool quantised = false;
+    for (const GgufTensor& t : tensors_) quantised = quantised || (t.type != 0 && t.type != 1 && t.type != 30);
+    if (quantised) {
+        auto it = meta_.find("general.quantization_version");
+        if (it == meta_.end()) throw std::runtime_error("quantized GGUF tensors require general.quantization_version");
+        if (it->second.type != 4 /* U32 */)
+            throw std::runtime_error("general.quantization_version must be U32, found value type " + std::to_string(it->second.type));
+        const int64_t v = std::get<int64_t>(it->second.v);
+        if (v != 2) throw std::runtime_error("unsupported GGUF quantization version " + std::to_string(v) + "; expected version 2");
+    }
     if (first.present && first.count > 1 && (int64_t)tensors_.size() != first.tensors)
         throw std::runtime_error("GGUF split checkpoint declares " + std::to_string(first.tensors) + " tensors, but " + std::to_string(tensors_.size()) +
                                  " unique tensors were loaded");

@@ -345,3 +345,24 @@ def test_a_fifo_is_refused_without_blocking(pk, tmp_path):
     os.mkfifo(path)
     with pytest.raises(pk["capi"].MkError, match="is not a regular file"):
         pk["eng"].Model.inspect_gguf(path)
+
+
+def test_quantised_rows_must_be_whole_blocks_and_need_the_quantisation_version(pk, tmp_path):
+    """src/gguf.rs:4279-4326."""
+    seed = pk["seed"]
+    version = [seed._kv("general.quantization_version", seed.T_U32, struct.pack("<I", 2))]
+    refused_bytes(pk, tmp_path, raw_gguf(seed, metas=version, tensors=[("q8", (16, 2), 8, b"\\0" * 34, None)]), "row width 16")
+    for name, tag, nbytes in (("q2k", 10, 84), ("q3k", 11, 110), ("q4k", 12, 144)):
+        refused_bytes(pk, tmp_path, raw_gguf(seed, metas=version, tensors=[(name, (128, 2), tag, b"\\0" * nbytes, None)]), "row width 128")
+    for name, tag, block in (("q5_0", 6, 22), ("q5_1", 7, 24)):
+        refused_bytes(pk, tmp_path, raw_gguf(seed, metas=version, tensors=[(name, (32, 2), tag, b"\\0" * block * 2, None)]), "paired 32-element blocks")
+    refused_bytes(pk, tmp_path, raw_gguf(seed, tensors=[("q8", (32,), 8, b"\\0" * 34, None)]), "require general.quantization_version")
+
+
+def test_rejects_noncanonical_keys_names_ranks_and_extents(pk, tmp_path):
+    """src/gguf.rs:4397-4432."""
+    seed = pk["seed"]
+    refused_bytes(pk, tmp_path, raw_gguf(seed, metas=[seed._kv("Bad-Key", seed.T_U32, struct.pack("<I", 1))]), "dot-separated lowercase identifier")
+    refused_bytes(pk, tmp_path, raw_gguf(seed, tensors=[("a" * 64, (1,), 0, f32s(1.0), None)]), "maximum is 63")
+    refused_bytes(pk, tmp_path, raw_gguf(seed, tensors=[("scalar", (), 0, f32s(1.0), None)]), "supported ranks")
+    refused_bytes(pk, tmp_path, raw_gguf(seed, tensors=[("empty", (0,), 0, b"", None)]), "zero-sized dimension")
